@@ -1,0 +1,656 @@
+// Memory-bound fused ops for sm_100a: RMSNorm (+residual add) fwd/bwd, RoPE (+optional per-head
+// q/k RMSNorm for Qwen3) fwd/bwd, SwiGLU / GeGLU fwd/bwd, embedding gather / scatter-add,
+// in-place cross-entropy fwd+bwd over a logits chunk, fused multi-tensor AdamW with global-norm
+// clipping. All kernels move 16-byte vectors and keep statistics in fp32.
+//
+// These replace the reference's Triton kernels (src/axolotl/kernels/swiglu.py, geglu.py,
+// gemma4_fused_rope.py), the HF eager RMSNorm / rotary chains and torch's fused AdamW.
+#include "axb_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < NT / 32) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) {
+    r = warp_sum(r);
+    if (l == 0) sh[0] = r;
+  }
+  __syncthreads();
+  return sh[0];
+}
+template <int NT>
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < NT / 32) ? sh[threadIdx.x] : -INFINITY;
+  if (w == 0) {
+    r = warp_max(r);
+    if (l == 0) sh[0] = r;
+  }
+  __syncthreads();
+  return sh[0];
+}
+
+struct bf16x8 {
+  uint4 u;
+};
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+         d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ---------------------------------------------------------------------------------- RMSNorm
+// h = x (+ res);  res_out = h (optional);  y = h * rstd * (w + w_offset)
+constexpr int NORM_T = 256;
+__global__ void __launch_bounds__(NORM_T)
+    rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H,
+                       float eps, float w_offset) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  const __nv_bfloat16* rr = res ? res + row * H : nullptr;
+  float ss = 0.f;
+  // H <= 8 * NORM_T * 4 supported by keeping up to 4 vectors per thread in registers
+  float cache[4][8];
+  int nv = 0;
+  for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8, ++nv) {
+    float f[8];
+    load8(xr + i, f);
+    if (rr) {
+      float g[8];
+      load8(rr + i, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+    }
+    if (res_out) {
+      // round the residual stream to bf16 first so forward and backward see the same h
+      store8(res_out + row * H + i, f);
+      float t[8];
+      load8(res_out + row * H + i, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = t[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ss += f[j] * f[j];
+      if (nv < 4) cache[nv][j] = f[j];
+    }
+  }
+  ss = block_sum<NORM_T>(ss, sh);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  int k = 0;
+  for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8, ++k) {
+    float f[8], wv[8];
+    if (k < 4) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = cache[k][j];
+    } else {
+      load8((res_out ? res_out + row * H : xr) + i, f);
+    }
+    load8(w + i, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * (wv[j] + w_offset);
+    store8(y + row * H + i, f);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres). Each thread owns fixed columns, so the
+// weight gradient is accumulated in registers over the rows of the block and flushed once.
+__global__ void __launch_bounds__(NORM_T)
+    rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw, int H, int rows, float w_offset) {
+  __shared__ float sh[32];
+  float dw_acc[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[a][j] = 0.f;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8) {
+      float a[8], b[8], c[8];
+      load8(dy + row * H + i, a);
+      load8(h + row * H + i, b);
+      load8(w + i, c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * (c[j] + w_offset) * b[j] * rstd;
+    }
+    dot = block_sum<NORM_T>(dot, sh) / H;
+    int k = 0;
+    for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8, ++k) {
+      float a[8], b[8], c[8], o[8];
+      load8(dy + row * H + i, a);
+      load8(h + row * H + i, b);
+      load8(w + i, c);
+      if (dres) load8(dres + row * H + i, o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = b[j] * rstd;
+        const float g = rstd * (a[j] * (c[j] + w_offset) - xhat * dot);
+        if (dw) {
+          if (k < 4) dw_acc[k][j] += a[j] * xhat;
+          else atomicAdd(dw + i + j, a[j] * xhat);
+        }
+        o[j] = dres ? o[j] + g : g;
+      }
+      store8(dx + row * H + i, o);
+    }
+  }
+  if (dw) {
+    int k = 0;
+    for (int i = threadIdx.x * 8; i < H && k < 4; i += NORM_T * 8, ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(dw + i + j, dw_acc[k][j]);
+  }
+}
+
+// ---------------------------------------------------------------------------------- RoPE
+// Rotates the q and k heads of a fused [T, (Hq + 2*Hk) * D] projection in place (rotate-half
+// convention: out = x*cos + rotate_half(x)*sin, angles = pos * inv_freq[i], i < D/2).
+// With norm weights given, a per-head RMSNorm over D is applied first (Qwen3 q_norm / k_norm),
+// and the per-head rstd is saved for the backward pass. sign = -1 gives the inverse rotation.
+__global__ void rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
+                               const float* __restrict__ inv_freq, int T, int Hq, int Hk, int D,
+                               long long row_stride, float sign, float attn_scale,
+                               const __nv_bfloat16* __restrict__ qn_w,
+                               const __nv_bfloat16* __restrict__ kn_w, float* __restrict__ rstd_out,
+                               float eps) {
+  // one warp per (token, head); lane handles pairs (i, i + D/2)
+  const int warps_per_block = blockDim.x >> 5;
+  const long long gw = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int nh = Hq + Hk;
+  if (gw >= (long long)T * nh) return;
+  const int t = (int)(gw / nh);
+  const int hd = (int)(gw % nh);
+  __nv_bfloat16* p = qkv + (long long)t * row_stride + (long long)hd * D;
+  const float ps = (float)pos[t];
+  const int half = D >> 1;
+  const __nv_bfloat16* nw = (hd < Hq) ? qn_w : kn_w;
+  float rstd = 1.f;
+  if (nw) {
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      float v = __bfloat162float(p[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd_out) rstd_out[gw] = rstd;
+  }
+  for (int i = lane; i < half; i += 32) {
+    float s, c;
+    sincosf(ps * inv_freq[i], &s, &c);
+    s *= sign * attn_scale;
+    c *= attn_scale;
+    float a = __bfloat162float(p[i]);
+    float b = __bfloat162float(p[i + half]);
+    if (nw) {
+      a = __bfloat162float(__float2bfloat16(a * rstd * __bfloat162float(nw[i])));
+      b = __bfloat162float(__float2bfloat16(b * rstd * __bfloat162float(nw[i + half])));
+    }
+    p[i] = __float2bfloat16(a * c - b * s);
+    p[i + half] = __float2bfloat16(b * c + a * s);
+  }
+}
+
+// Backward of (per-head RMSNorm ->) RoPE for the fused q/k gradient buffer, in place.
+// x_pre holds the pre-norm projection (needed only when norm weights are given).
+__global__ void rope_qk_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
+                                   const __nv_bfloat16* __restrict__ x_pre,
+                                   const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                   int T, int Hq, int Hk, int D, long long row_stride,
+                                   long long x_row_stride, float attn_scale,
+                                   const __nv_bfloat16* __restrict__ qn_w,
+                                   const __nv_bfloat16* __restrict__ kn_w,
+                                   const float* __restrict__ rstd_in, float* __restrict__ dqn_w,
+                                   float* __restrict__ dkn_w) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long gw = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int nh = Hq + Hk;
+  if (gw >= (long long)T * nh) return;
+  const int t = (int)(gw / nh);
+  const int hd = (int)(gw % nh);
+  __nv_bfloat16* g = dqkv + (long long)t * row_stride + (long long)hd * D;
+  const float ps = (float)pos[t];
+  const int half = D >> 1;
+  const __nv_bfloat16* nw = (hd < Hq) ? qn_w : kn_w;
+  float* dnw = (hd < Hq) ? dqn_w : dkn_w;
+  // inverse rotation first
+  float ga[4], gb[4];  // D <= 256
+  int n = 0;
+  for (int i = lane; i < half; i += 32, ++n) {
+    float s, c;
+    sincosf(ps * inv_freq[i], &s, &c);
+    s *= attn_scale;
+    c *= attn_scale;
+    const float a = __bfloat162float(g[i]);
+    const float b = __bfloat162float(g[i + half]);
+    ga[n] = a * c + b * s;
+    gb[n] = b * c - a * s;
+  }
+  if (!nw) {
+    n = 0;
+    for (int i = lane; i < half; i += 32, ++n) {
+      g[i] = __float2bfloat16(ga[n]);
+      g[i + half] = __float2bfloat16(gb[n]);
+    }
+    return;
+  }
+  const __nv_bfloat16* x = x_pre + (long long)t * x_row_stride + (long long)hd * D;
+  const float rstd = rstd_in[gw];
+  float dot = 0.f;
+  n = 0;
+  for (int i = lane; i < half; i += 32, ++n) {
+    const float xa = __bfloat162float(x[i]) * rstd, xb = __bfloat162float(x[i + half]) * rstd;
+    const float wa = __bfloat162float(nw[i]), wb = __bfloat162float(nw[i + half]);
+    dot += ga[n] * wa * xa + gb[n] * wb * xb;
+    if (dnw) {
+      atomicAdd(dnw + i, ga[n] * xa);
+      atomicAdd(dnw + i + half, gb[n] * xb);
+    }
+  }
+  dot = warp_sum(dot) / D;
+  n = 0;
+  for (int i = lane; i < half; i += 32, ++n) {
+    const float xa = __bfloat162float(x[i]) * rstd, xb = __bfloat162float(x[i + half]) * rstd;
+    const float wa = __bfloat162float(nw[i]), wb = __bfloat162float(nw[i + half]);
+    g[i] = __float2bfloat16(rstd * (ga[n] * wa - xa * dot));
+    g[i + half] = __float2bfloat16(rstd * (gb[n] * wb - xb * dot));
+  }
+}
+
+// ---------------------------------------------------------------------------------- GLU
+__device__ __forceinline__ float act_fwd(float g, int kind) {
+  if (kind == 0) return g / (1.f + __expf(-g));  // silu
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;  // gelu tanh
+  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * g * (1.f + t);
+}
+__device__ __forceinline__ float act_bwd(float g, int kind) {
+  if (kind == 0) {
+    const float s = 1.f / (1.f + __expf(-g));
+    return s * (1.f + g * (1.f - s));
+  }
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+}
+// gu: [T, 2I] (gate | up);  h: [T, I] = act(gate) * up
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
+                               long long T, int I, int kind) {
+  const long long nvec = T * (I / 8);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long t = v / (I / 8);
+    const int c = (int)(v % (I / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + t * 2 * I + c, g);
+    load8(gu + t * 2 * I + I + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], kind) * u[j];
+    store8(h + t * I + c, o);
+  }
+}
+// dgu[T,2I]: d_gate = dh * up * act'(gate), d_up = dh * act(gate). dgu may alias gu.
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
+                               const __nv_bfloat16* __restrict__ gu,
+                               __nv_bfloat16* __restrict__ dgu, long long T, int I, int kind) {
+  const long long nvec = T * (I / 8);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long t = v / (I / 8);
+    const int c = (int)(v % (I / 8)) * 8;
+    float g[8], u[8], d[8], og[8], ou[8];
+    load8(gu + t * 2 * I + c, g);
+    load8(gu + t * 2 * I + I + c, u);
+    load8(dh + t * I + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      og[j] = d[j] * u[j] * act_bwd(g[j], kind);
+      ou[j] = d[j] * act_fwd(g[j], kind);
+    }
+    store8(dgu + t * 2 * I + c, og);
+    store8(dgu + t * 2 * I + I + c, ou);
+  }
+}
+
+// ---------------------------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
+                                     const long long* __restrict__ ids,
+                                     __nv_bfloat16* __restrict__ out, long long T, int H,
+                                     long long vocab) {
+  const long long nvec = T * (H / 8);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long t = v / (H / 8);
+    const int c = (int)(v % (H / 8)) * 8;
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    *reinterpret_cast<uint4*>(out + t * H + c) =
+        *reinterpret_cast<const uint4*>(table + id * H + c);
+  }
+}
+__global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                     const long long* __restrict__ ids, float* __restrict__ dtable,
+                                     long long T, int H, long long vocab) {
+  const long long n = T * H;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / H;
+    const int c = (int)(i % H);
+    const long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    atomicAdd(dtable + id * H + c, __bfloat162float(dout[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------- cross entropy
+// One block per row of a [R, V] bf16 logits chunk (optionally soft-capped). Computes
+//   loss[r] = logsumexp(z) - z[label]   (0 when label == ignore_index)
+// and overwrites the row with d loss_total / d z = (softmax(z) - onehot) * grad_scale, so the
+// caller can feed the buffer straight into the dX / dW GEMMs. lse[r] is also returned.
+constexpr int CE_T = 512;
+__global__ void __launch_bounds__(CE_T)
+    ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+                      float* __restrict__ loss, float* __restrict__ lse_out, int V,
+                      long long ld, float grad_scale, long long ignore_index, int write_grad) {
+  __shared__ float sh[32];
+  const long long r = blockIdx.x;
+  __nv_bfloat16* z = logits + r * ld;
+  const long long label = labels[r];
+  const bool ignored = (label == ignore_index) || label < 0 || label >= V;
+  if (ignored && !lse_out) {
+    if (threadIdx.x == 0) loss[r] = 0.f;
+    if (write_grad) {
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      const int v8 = V & ~7;
+      for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8)
+        *reinterpret_cast<uint4*>(z + i) = zero;
+      for (int i = v8 + threadIdx.x; i < V; i += CE_T) z[i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  const int v8 = V & ~7;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8) {
+    float f[8];
+    load8(z + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+  }
+  for (int i = v8 + threadIdx.x; i < V; i += CE_T) mx = fmaxf(mx, __bfloat162float(z[i]));
+  mx = block_max<CE_T>(mx, sh);
+  float se = 0.f;
+  for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8) {
+    float f[8];
+    load8(z + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+  }
+  for (int i = v8 + threadIdx.x; i < V; i += CE_T) se += __expf(__bfloat162float(z[i]) - mx);
+  se = block_sum<CE_T>(se, sh);
+  const float lse = mx + logf(se);
+  if (threadIdx.x == 0) {
+    if (lse_out) lse_out[r] = lse;
+    loss[r] = ignored ? 0.f : lse - __bfloat162float(z[label]);
+  }
+  if (!write_grad) return;
+  __syncthreads();
+  const float gs = ignored ? 0.f : grad_scale;
+  for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8) {
+    float f[8];
+    load8(z + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float pr = __expf(f[j] - lse);
+      if (i + j == label) pr -= 1.f;
+      f[j] = pr * gs;
+    }
+    store8(z + i, f);
+  }
+  for (int i = v8 + threadIdx.x; i < V; i += CE_T) {
+    float pr = __expf(__bfloat162float(z[i]) - lse);
+    if (i == label) pr -= 1.f;
+    z[i] = __float2bfloat16(pr * gs);
+  }
+}
+
+// ---------------------------------------------------------------------------------- optimizer
+// sum of squares of a flat fp32 gradient buffer -> out[0] (atomic)
+__global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float sh[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    s += g[i] * g[i];
+  s = block_sum<256>(s, sh);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+// Fused AdamW over a flat fp32 master buffer. gnorm_sq (device scalar, optional) drives clipping:
+// grads are scaled by min(1, max_norm / (sqrt(gnorm_sq) + 1e-6)) without a host round trip.
+// bf16_copy (optional) receives the updated parameters for the bf16 compute path.
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v,
+                             __nv_bfloat16* __restrict__ bf16_copy, long long n, float lr,
+                             float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                             const float* __restrict__ gnorm_sq, float max_norm,
+                             float grad_scale) {
+  float clip = grad_scale;
+  if (gnorm_sq && max_norm > 0.f) {
+    const float nrm = sqrtf(*gnorm_sq) * grad_scale;
+    clip *= fminf(1.f, max_norm / (nrm + 1e-6f));
+  }
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float gi = g[i] * clip;
+    float pi = p[i];
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    pi *= (1.f - lr * wd);
+    pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    p[i] = pi;
+    if (bf16_copy) bf16_copy[i] = __float2bfloat16(pi);
+  }
+}
+
+// dst(bf16/fp32) = alpha * src (+ dst if accumulate)
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d,
+                                        long long n, float alpha, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float x = alpha * __bfloat162float(s[i]);
+    d[i] = accumulate ? d[i] + x : x;
+  }
+}
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d,
+                                        long long n, float alpha) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    d[i] = __float2bfloat16(alpha * s[i]);
+}
+// y[i] += x[i]  (bf16, 8-wide)
+__global__ void add_bf16_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x,
+                                long long n8) {
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n8;
+       v += (long long)gridDim.x * blockDim.x) {
+    float a[8], b[8];
+    load8(y + v * 8, a);
+    load8(x + v * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] += b[j];
+    store8(y + v * 8, a);
+  }
+}
+
+inline int grid_for(long long work, int threads, int cap = 148 * 16) {
+  long long g = (work + threads - 1) / threads;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int axb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y,
+                               void* res_out, float* rstd, long long rows, int H, float eps,
+                               float w_offset, void* stream) {
+  if (H % 8) return -2;
+  if (rows <= 0) return 0;
+  rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_T, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+      (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd, H, eps, w_offset);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd,
+                               const void* dres, void* dx, float* dw, long long rows, int H,
+                               float w_offset, void* stream) {
+  if (H % 8) return -2;
+  if (rows <= 0) return 0;
+  const int grid = rows < 148 * 8 ? (int)rows : 148 * 8;
+  rmsnorm_bwd_kernel<<<grid, NORM_T, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw, H, (int)rows, w_offset);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_rope_qk(void* qkv, const int* pos, const float* inv_freq, int T, int Hq, int Hk,
+                           int D, long long row_stride, float sign, float attn_scale,
+                           const void* qn_w, const void* kn_w, float* rstd_out, float eps,
+                           void* stream) {
+  if (T <= 0) return 0;
+  const long long warps = (long long)T * (Hq + Hk);
+  const int wpb = 8;
+  rope_qk_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
+      (__nv_bfloat16*)qkv, pos, inv_freq, T, Hq, Hk, D, row_stride, sign, attn_scale,
+      (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_out, eps);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
+                               const float* inv_freq, int T, int Hq, int Hk, int D,
+                               long long row_stride, long long x_row_stride, float attn_scale,
+                               const void* qn_w, const void* kn_w, const float* rstd_in,
+                               float* dqn_w, float* dkn_w, void* stream) {
+  if (T <= 0) return 0;
+  if (D > 256) return -2;
+  const long long warps = (long long)T * (Hq + Hk);
+  const int wpb = 8;
+  rope_qk_bwd_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
+      (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)x_pre, pos, inv_freq, T, Hq, Hk, D, row_stride,
+      x_row_stride, attn_scale, (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_in,
+      dqn_w, dkn_w);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_glu_fwd(const void* gu, void* h, long long T, int I, int kind, void* stream) {
+  if (I % 8) return -2;
+  if (T <= 0) return 0;
+  glu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_glu_bwd(const void* dh, const void* gu, void* dgu, long long T, int I, int kind,
+                           void* stream) {
+  if (I % 8) return -2;
+  if (T <= 0) return 0;
+  glu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_embedding_fwd(const void* table, const long long* ids, void* out, long long T,
+                                 int H, long long vocab, void* stream) {
+  if (H % 8) return -2;
+  if (T <= 0) return 0;
+  embedding_fwd_kernel<<<grid_for(T * (H / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, T, H, vocab);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_embedding_bwd(const void* dout, const long long* ids, float* dtable,
+                                 long long T, int H, long long vocab, void* stream) {
+  if (T <= 0) return 0;
+  embedding_bwd_kernel<<<grid_for(T * H, 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dout, ids, dtable, T, H, vocab);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_ce_fwd_bwd(void* logits, const long long* labels, float* loss, float* lse,
+                              long long rows, int V, long long ld, float grad_scale,
+                              long long ignore_index, int write_grad, void* stream) {
+  if (rows <= 0) return 0;
+  if (ld % 8) return -2;
+  ce_fwd_bwd_kernel<<<(unsigned)rows, CE_T, 0, ST(stream)>>>(
+      (__nv_bfloat16*)logits, labels, loss, lse, V, ld, grad_scale, ignore_index, write_grad);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_sumsq(const float* g, long long n, float* out, void* stream) {
+  if (n <= 0) return 0;
+  sumsq_kernel<<<grid_for(n, 256, 148 * 4), 256, 0, ST(stream)>>>(g, n, out);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_adamw(float* p, const float* g, float* m, float* v, void* bf16_copy,
+                         long long n, float lr, float beta1, float beta2, float eps, float wd,
+                         float bc1, float bc2, const float* gnorm_sq, float max_norm,
+                         float grad_scale, void* stream) {
+  if (n <= 0) return 0;
+  adamw_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(p, g, m, v, (__nv_bfloat16*)bf16_copy, n,
+                                                         lr, beta1, beta2, eps, wd, bc1, bc2,
+                                                         gnorm_sq, max_norm, grad_scale);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_cast_bf16_to_f32(const void* s, float* d, long long n, float alpha,
+                                    int accumulate, void* stream) {
+  if (n <= 0) return 0;
+  cast_bf16_to_f32_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)s, d, n,
+                                                                    alpha, accumulate);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_cast_f32_to_bf16(const float* s, void* d, long long n, float alpha,
+                                    void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(s, (__nv_bfloat16*)d, n,
+                                                                    alpha);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_add_bf16(void* y, const void* x, long long n, void* stream) {
+  if (n % 8) return -2;
+  if (n <= 0) return 0;
+  add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, ST(stream)>>>((__nv_bfloat16*)y,
+                                                                (const __nv_bfloat16*)x, n / 8);
+  return (int)cudaGetLastError();
+}

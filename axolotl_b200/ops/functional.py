@@ -1,0 +1,459 @@
+"""Autograd-aware fused ops. CUDA tensors run the hand-written sm_100a kernels; CPU tensors run a
+plain PyTorch implementation of the same math, which doubles as the numerical oracle in tests.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+IGNORE_INDEX = -100
+
+
+# --------------------------------------------------------------------------------------- RMSNorm
+def _rmsnorm_ref(h, w, eps, w_offset=0.0):
+    hf = h.float()
+    rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
+    return (hf * rstd * (w.float() + w_offset)).to(h.dtype), rstd.squeeze(-1)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """(x, residual) -> (y, h) with h = x + residual and y = rmsnorm(h) * (w + w_offset)."""
+
+    @staticmethod
+    def forward(ctx, x, residual, w, eps, w_offset):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        rows = x2.shape[0]
+        ctx.has_res = residual is not None
+        ctx.eps, ctx.w_offset = eps, w_offset
+        if not x.is_cuda:
+            h = x2 if residual is None else (x2.float() + residual.reshape(-1, H).float()).to(x.dtype)
+            y, rstd = _rmsnorm_ref(h, w, eps, w_offset)
+        else:
+            lib = _lib.cuda_lib()
+            x2 = x2.contiguous()
+            r2 = residual.reshape(-1, H).contiguous() if residual is not None else None
+            y = torch.empty_like(x2)
+            h = torch.empty_like(x2) if residual is not None else x2
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            _lib.check_rc(
+                lib.axb_rmsnorm_fwd(x2.data_ptr(), _lib.ptr(r2), w.data_ptr(), y.data_ptr(),
+                                    h.data_ptr() if residual is not None else None, rstd.data_ptr(),
+                                    rows, H, eps, w_offset, _lib.stream_ptr()),
+                "rmsnorm_fwd")
+        ctx.save_for_backward(h, w, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape), h.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, w, rstd = ctx.saved_tensors
+        H = h.shape[-1]
+        rows = h.shape[0]
+        need_dw = ctx.needs_input_grad[2]
+        if not h.is_cuda:
+            hf, dyf = h.float(), dy.reshape(-1, H).float()
+            wf = w.float() + ctx.w_offset
+            xhat = hf * rstd[:, None]
+            g = dyf * wf
+            dx = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+            if dh is not None:
+                dx = dx + dh.reshape(-1, H).float()
+            dw = (dyf * xhat).sum(0).to(w.dtype) if need_dw else None
+            dx = dx.to(h.dtype)
+        else:
+            lib = _lib.cuda_lib()
+            dy2 = dy.reshape(-1, H).contiguous()
+            dh2 = dh.reshape(-1, H).contiguous() if dh is not None else None
+            dx = torch.empty_like(h)
+            dwf = torch.zeros(H, dtype=torch.float32, device=h.device) if need_dw else None
+            _lib.check_rc(
+                lib.axb_rmsnorm_bwd(dy2.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                    _lib.ptr(dh2), dx.data_ptr(), _lib.ptr(dwf), rows, H,
+                                    ctx.w_offset, _lib.stream_ptr()),
+                "rmsnorm_bwd")
+            dw = dwf.to(w.dtype) if need_dw else None
+        dx = dx.view(ctx.shape)
+        return dx, (dx if ctx.has_res else None), dw, None, None
+
+
+def add_rmsnorm(x, residual, weight, eps=1e-6, w_offset=0.0):
+    """Returns ``(rmsnorm(x + residual), x + residual)``; ``residual`` may be None."""
+    return _AddRMSNorm.apply(x, residual, weight, eps, w_offset)
+
+
+def rmsnorm(x, weight, eps=1e-6, w_offset=0.0):
+    return _AddRMSNorm.apply(x, None, weight, eps, w_offset)[0]
+
+
+# --------------------------------------------------------------------------------------- RoPE
+def _rope_ref(x, pos, inv_freq, sign=1.0, attn_scale=1.0):
+    # x: [T, H, D]
+    ang = pos.float()[:, None] * inv_freq.float()[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :] * attn_scale
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :] * attn_scale * sign
+    half = x.shape[-1] // 2
+    xf = x.float()
+    rot = torch.cat([-xf[..., half:], xf[..., :half]], -1)
+    return (xf * cos + rot * sin).to(x.dtype)
+
+
+class _RopeQK(torch.autograd.Function):
+    """In-place rotary embedding (+ optional per-head q/k RMSNorm) on a fused qkv projection."""
+
+    @staticmethod
+    def forward(ctx, qkv, pos, inv_freq, Hq, Hk, D, attn_scale, qn_w, kn_w, eps):
+        T = qkv.shape[0]
+        ctx.dims = (Hq, Hk, D, attn_scale, eps)
+        has_norm = qn_w is not None
+        pre = None
+        rstd = None
+        if not qkv.is_cuda:
+            qk = qkv[:, : (Hq + Hk) * D].reshape(T, Hq + Hk, D)
+            if has_norm:
+                pre = qk.clone()
+                q, rq = _rmsnorm_ref(qk[:, :Hq], qn_w, eps)
+                k, rk = _rmsnorm_ref(qk[:, Hq:], kn_w, eps)
+                rstd = torch.cat([rq, rk], 1)
+                qk = torch.cat([q, k], 1)
+            out = _rope_ref(qk, pos, inv_freq, 1.0, attn_scale)
+            qkv = torch.cat([out.reshape(T, -1), qkv[:, (Hq + Hk) * D:]], 1)
+        else:
+            lib = _lib.cuda_lib()
+            if has_norm:
+                pre = qkv[:, : (Hq + Hk) * D].clone()
+                rstd = torch.empty(T * (Hq + Hk), dtype=torch.float32, device=qkv.device)
+            _lib.check_rc(
+                lib.axb_rope_qk(qkv.data_ptr(), pos.data_ptr(), inv_freq.data_ptr(), T, Hq, Hk, D,
+                                qkv.stride(0), 1.0, attn_scale, _lib.ptr(qn_w), _lib.ptr(kn_w),
+                                _lib.ptr(rstd), eps, _lib.stream_ptr()),
+                "rope_qk")
+            ctx.mark_dirty(qkv)
+        ctx.save_for_backward(pos, inv_freq, qn_w, kn_w, pre, rstd)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        pos, inv_freq, qn_w, kn_w, pre, rstd = ctx.saved_tensors
+        Hq, Hk, D, attn_scale, eps = ctx.dims
+        T = dqkv.shape[0]
+        dqn = dkn = None
+        if not dqkv.is_cuda:
+            g = dqkv[:, : (Hq + Hk) * D].reshape(T, Hq + Hk, D)
+            g = _rope_ref(g, pos, inv_freq, -1.0, attn_scale)
+            if qn_w is not None:
+                gf = g.float()
+                xhat = pre.reshape(T, Hq + Hk, D).float() * rstd[:, :, None]
+                wcat = torch.cat([qn_w.float().expand(Hq, D), kn_w.float().expand(Hk, D)], 0)[None]
+                gw = gf * wcat
+                dx = rstd[:, :, None] * (gw - xhat * (gw * xhat).mean(-1, keepdim=True))
+                dqn = (gf[:, :Hq] * xhat[:, :Hq]).sum((0, 1)).to(qn_w.dtype)
+                dkn = (gf[:, Hq:] * xhat[:, Hq:]).sum((0, 1)).to(kn_w.dtype)
+                g = dx.to(dqkv.dtype)
+            dqkv = torch.cat([g.reshape(T, -1), dqkv[:, (Hq + Hk) * D:]], 1)
+        else:
+            lib = _lib.cuda_lib()
+            dqkv = dqkv.contiguous()
+            need_dn = qn_w is not None and (ctx.needs_input_grad[7] or ctx.needs_input_grad[8])
+            dqn_f = torch.zeros(D, dtype=torch.float32, device=dqkv.device) if need_dn else None
+            dkn_f = torch.zeros(D, dtype=torch.float32, device=dqkv.device) if need_dn else None
+            _lib.check_rc(
+                lib.axb_rope_qk_bwd(dqkv.data_ptr(), _lib.ptr(pre), pos.data_ptr(),
+                                    inv_freq.data_ptr(), T, Hq, Hk, D, dqkv.stride(0),
+                                    pre.stride(0) if pre is not None else 0, attn_scale,
+                                    _lib.ptr(qn_w), _lib.ptr(kn_w), _lib.ptr(rstd),
+                                    _lib.ptr(dqn_f), _lib.ptr(dkn_f), _lib.stream_ptr()),
+                "rope_qk_bwd")
+            if need_dn:
+                dqn, dkn = dqn_f.to(qn_w.dtype), dkn_f.to(kn_w.dtype)
+        return dqkv, None, None, None, None, None, None, dqn, dkn, None
+
+
+def rope_qk_(qkv, positions, inv_freq, Hq, Hk, D, attn_scale=1.0, q_norm_w=None, k_norm_w=None,
+             eps=1e-6):
+    """Rotates the q and k blocks of ``qkv`` [T, (Hq+2Hk)*D] (in place on CUDA)."""
+    return _RopeQK.apply(qkv, positions, inv_freq, Hq, Hk, D, attn_scale, q_norm_w, k_norm_w, eps)
+
+
+# --------------------------------------------------------------------------------------- GLU
+_ACT_KIND = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 1}
+
+
+def _act_ref(g, kind):
+    return F.silu(g) if kind == 0 else F.gelu(g, approximate="tanh")
+
+
+class _GLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu, kind):
+        I = gu.shape[-1] // 2
+        ctx.kind = kind
+        ctx.save_for_backward(gu)
+        if not gu.is_cuda:
+            g, u = gu[..., :I].float(), gu[..., I:].float()
+            return (_act_ref(g, kind) * u).to(gu.dtype)
+        lib = _lib.cuda_lib()
+        gu2 = gu.reshape(-1, 2 * I)
+        h = torch.empty((gu2.shape[0], I), dtype=gu.dtype, device=gu.device)
+        _lib.check_rc(lib.axb_glu_fwd(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind,
+                                      _lib.stream_ptr()), "glu_fwd")
+        return h.view(*gu.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (gu,) = ctx.saved_tensors
+        I = gu.shape[-1] // 2
+        if not gu.is_cuda:
+            with torch.enable_grad():
+                g = gu[..., :I].float().detach().requires_grad_(True)
+                a = _act_ref(g, ctx.kind)
+                (da,) = torch.autograd.grad(a.sum(), g)
+            u = gu[..., I:].float()
+            dhf = dh.float()
+            return torch.cat([dhf * u * da, dhf * a.detach()], -1).to(gu.dtype), None
+        lib = _lib.cuda_lib()
+        gu2 = gu.reshape(-1, 2 * I)
+        dh2 = dh.reshape(-1, I).contiguous()
+        dgu = torch.empty_like(gu2)
+        _lib.check_rc(lib.axb_glu_bwd(dh2.data_ptr(), gu2.data_ptr(), dgu.data_ptr(), gu2.shape[0],
+                                      I, ctx.kind, _lib.stream_ptr()), "glu_bwd")
+        return dgu.view(gu.shape), None
+
+
+def glu(gate_up, activation="silu"):
+    """``act(gate) * up`` for a fused ``[.., 2I]`` (gate | up) projection."""
+    return _GLU.apply(gate_up, _ACT_KIND[activation])
+
+
+# --------------------------------------------------------------------------------------- embedding
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, ids):
+        ctx.save_for_backward(ids)
+        ctx.tshape = table.shape
+        ctx.tdtype = table.dtype
+        if not table.is_cuda:
+            return F.embedding(ids, table)
+        lib = _lib.cuda_lib()
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty((flat.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+        _lib.check_rc(lib.axb_embedding_fwd(table.data_ptr(), flat.data_ptr(), out.data_ptr(),
+                                            flat.numel(), table.shape[1], table.shape[0],
+                                            _lib.stream_ptr()), "embedding_fwd")
+        return out.view(*ids.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None
+        V, H = ctx.tshape
+        if not dout.is_cuda:
+            g = torch.zeros(V, H, dtype=torch.float32)
+            g.index_add_(0, ids.reshape(-1), dout.reshape(-1, H).float())
+            return g.to(ctx.tdtype), None
+        lib = _lib.cuda_lib()
+        g = torch.zeros(V, H, dtype=torch.float32, device=dout.device)
+        d2 = dout.reshape(-1, H).contiguous()
+        flat = ids.reshape(-1).contiguous()
+        _lib.check_rc(lib.axb_embedding_bwd(d2.data_ptr(), flat.data_ptr(), g.data_ptr(),
+                                            flat.numel(), H, V, _lib.stream_ptr()), "embedding_bwd")
+        return g.to(ctx.tdtype), None
+
+
+def embedding(table, ids):
+    return _Embedding.apply(table, ids)
+
+
+# --------------------------------------------------------------------------------------- attention
+class AttnMeta:
+    """Per-batch varlen metadata: cu_seqlens plus the tile tables of the attention kernels.
+
+    Built once per packed row on the host (the collator knows the document boundaries) and
+    reused by every layer's forward and backward.
+    """
+
+    def __init__(self, cu_seqlens, device):
+        cu = np.asarray(cu_seqlens, dtype=np.int32)
+        self.cu_seqlens_host = cu
+        self.n_docs = len(cu) - 1
+        self.total = int(cu[-1])
+        self.max_len = int((cu[1:] - cu[:-1]).max()) if self.n_docs else 0
+        self.device = torch.device(device)
+        self.cu_seqlens = torch.from_numpy(cu.copy()).to(self.device)
+        self.tiles_fwd = self.tiles_bwd = None
+        self.n_tiles = 0
+        if self.device.type == "cuda":
+            host = _lib.host_lib()
+            max_tiles = (self.total + 127) // 128 + self.n_docs
+            bufs = []
+            for heavy_first in (1, 0):
+                buf = np.zeros((max_tiles, 4), dtype=np.int32)
+                n = host.axb_build_attn_tiles(cu.ctypes.data, self.n_docs, 128, heavy_first,
+                                              buf.ctypes.data, max_tiles)
+                bufs.append(buf[:n])
+            self.n_tiles = len(bufs[0])
+            both = torch.from_numpy(np.concatenate(bufs, 0)).pin_memory()
+            both = both.to(self.device, non_blocking=True)
+            self.tiles_fwd, self.tiles_bwd = both[: self.n_tiles], both[self.n_tiles:]
+
+    @staticmethod
+    def from_position_ids(position_ids, device):
+        """Document starts are the positions where ``position_ids`` resets to 0."""
+        p = position_ids.reshape(-1).cpu().numpy()
+        starts = np.flatnonzero(p == 0)
+        if len(starts) == 0 or starts[0] != 0:
+            starts = np.concatenate([[0], starts])
+        cu = np.concatenate([starts, [len(p)]]).astype(np.int32)
+        return AttnMeta(cu, device)
+
+
+def _attn_ref(q, k, v, cu, scale):
+    # q [T,Hq,D], k/v [T,Hk,D]; per-document causal attention in fp32
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    rep = Hq // Hk
+    out = torch.empty_like(q)
+    for d in range(len(cu) - 1):
+        s, e = int(cu[d]), int(cu[d + 1])
+        qq = q[s:e].float().transpose(0, 1)
+        kk = k[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
+        vv = v[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
+        sc = (qq @ kk.transpose(1, 2)) * scale
+        mask = torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        out[s:e] = (sc.softmax(-1) @ vv).transpose(0, 1).to(q.dtype)
+    return out
+
+
+class _FlashVarlen(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, meta, Hq, Hk, D, scale):
+        T = qkv.shape[0]
+        ctx.meta, ctx.dims = meta, (Hq, Hk, D, scale)
+        if not qkv.is_cuda:
+            raise RuntimeError("CPU tensors take the autograd reference path in flash_varlen()")
+        lib = _lib.cuda_lib()
+        out = torch.empty((T, Hq * D), dtype=qkv.dtype, device=qkv.device)
+        lse2 = torch.empty((Hq, T), dtype=torch.float32, device=qkv.device)
+        _lib.check_rc(
+            lib.axb_flash_varlen_fwd(qkv.data_ptr(), qkv.stride(0), T, Hq, Hk, D, 0, Hq * D,
+                                     (Hq + Hk) * D, meta.tiles_fwd.data_ptr(), meta.n_tiles,
+                                     out.data_ptr(), out.stride(0), lse2.data_ptr(), scale,
+                                     _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()),
+            "flash_varlen_fwd")
+        ctx.save_for_backward(qkv, out, lse2)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse2 = ctx.saved_tensors
+        Hq, Hk, D, scale = ctx.dims
+        meta = ctx.meta
+        T = qkv.shape[0]
+        lib = _lib.cuda_lib()
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq_acc = torch.empty((T, Hq * D), dtype=torch.float32, device=qkv.device)
+        delta = torch.empty((Hq, T), dtype=torch.float32, device=qkv.device)
+        _lib.check_rc(
+            lib.axb_flash_varlen_bwd(qkv.data_ptr(), qkv.stride(0), dout.data_ptr(),
+                                     out.data_ptr(), out.stride(0), lse2.data_ptr(), T, Hq, Hk, D,
+                                     0, Hq * D, (Hq + Hk) * D, meta.tiles_bwd.data_ptr(),
+                                     meta.n_tiles, dqkv.data_ptr(), dqkv.stride(0),
+                                     dq_acc.data_ptr(), delta.data_ptr(), scale,
+                                     _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()),
+            "flash_varlen_bwd")
+        return dqkv, None, None, None, None, None
+
+
+def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
+    """Causal attention inside each document of a packed row.
+
+    ``qkv`` is the fused projection [T, (Hq + 2*Hk) * D] (q heads, then k heads, then v heads).
+    Returns [T, Hq * D].
+    """
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if qkv.is_cuda:
+        return _FlashVarlen.apply(qkv, meta, Hq, Hk, D, scale)
+    T = qkv.shape[0]
+    q = qkv[:, : Hq * D].reshape(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
+    v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, D)
+    return _attn_ref(q, k, v, meta.cu_seqlens_host, scale).reshape(T, Hq * D)
+
+
+# --------------------------------------------------------------------------------------- loss
+class _LinearCE(torch.autograd.Function):
+    """Chunked lm_head GEMM + cross entropy that never materialises [T, V] logits.
+
+    For each chunk of rows: logits = h @ W^T (tcgen05 GEMM) -> in-place CE kernel that returns the
+    per-row loss and overwrites the logits with their gradient -> dH chunk = dlogits @ W (and
+    dW += dlogits^T @ h when the head is trainable). The backward pass only rescales.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, labels, denom, chunk_rows, ignore_index, lora):
+        from .gemm import gemm, pick_splits
+
+        T, H = h.shape
+        V = w.shape[0]
+        need_dw = w.requires_grad
+        dh = torch.empty_like(h)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device) if need_dw else None
+        losses = torch.empty(T, dtype=torch.float32, device=h.device)
+        lib = _lib.cuda_lib() if h.is_cuda else None
+        for r0 in range(0, T, chunk_rows):
+            r1 = min(T, r0 + chunk_rows)
+            hc = h[r0:r1]
+            logits = gemm(hc, w)
+            if h.is_cuda:
+                _lib.check_rc(
+                    lib.axb_ce_fwd_bwd(logits.data_ptr(), labels[r0:r1].data_ptr(),
+                                       losses[r0:r1].data_ptr(), None, r1 - r0, V,
+                                       logits.stride(0), 1.0 / denom, ignore_index, 1,
+                                       _lib.stream_ptr()), "ce_fwd_bwd")
+                dlogits = logits
+            else:
+                lf = logits.float()
+                lab = labels[r0:r1]
+                valid = lab != ignore_index
+                lse = torch.logsumexp(lf, -1)
+                tgt = lf.gather(1, lab.clamp(min=0)[:, None]).squeeze(1)
+                losses[r0:r1] = torch.where(valid, lse - tgt, torch.zeros_like(lse))
+                p = torch.softmax(lf, -1)
+                p[torch.arange(r1 - r0), lab.clamp(min=0)] -= 1.0
+                dlogits = (p * valid[:, None] / denom).to(logits.dtype)
+            gemm(dlogits, w, trans_b=True, out=dh[r0:r1])
+            if need_dw:
+                sp = pick_splits(((V + 127) // 128) * ((H + 255) // 256), (r1 - r0 + 63) // 64)
+                gemm(dlogits, hc, trans_a=True, trans_b=True, out=dw, accumulate=True, splits=sp)
+        ctx.save_for_backward(dh, dw)
+        ctx.w_dtype = w.dtype
+        return losses.sum() / denom
+
+    @staticmethod
+    def backward(ctx, gout):
+        dh, dw = ctx.saved_tensors
+        return (dh * gout.to(dh.dtype), (dw * gout).to(ctx.w_dtype) if dw is not None else None,
+                None, None, None, None, None)
+
+
+def linear_cross_entropy(hidden, lm_head_weight, labels, num_items=None, chunk_rows=2048,
+                         ignore_index=IGNORE_INDEX):
+    """Mean (or ``sum / num_items``) token cross entropy of ``hidden @ W^T`` against ``labels``.
+
+    ``labels`` must already be shifted (labels[t] is the target of position t).
+    """
+    hidden = hidden.reshape(-1, hidden.shape[-1])
+    labels = labels.reshape(-1).contiguous()
+    if num_items is None:
+        num_items = int((labels != ignore_index).sum().item())
+    denom = float(max(num_items, 1))
+    return _LinearCE.apply(hidden.contiguous(), lm_head_weight, labels, denom, chunk_rows,
+                           ignore_index, None)

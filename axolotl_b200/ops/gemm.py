@@ -1,0 +1,126 @@
+"""bf16 GEMM on the tcgen05 kernel (CUDA) with a plain PyTorch path for CPU tensors.
+
+``gemm(a, b)`` computes ``alpha * (op(a) @ op(b)^T + a2 @ b2^T) + beta * c_in`` where
+``op(a)`` is ``a`` ([M, K]) or, with ``trans_a``, a matrix stored as [K, M]; likewise
+``op(b)`` is ``b`` ([N, K]) or, with ``trans_b``, stored as [K, N]. The optional ``a2``/``b2``
+pair is the K-extension that fuses a LoRA update into the same accumulator tile.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_SM = 148
+
+
+def _pick_bn(M: int, N: int) -> int:
+    m_tiles = (M + 127) // 128
+    for bn in (256, 128, 64):
+        if bn > 64 and N <= bn // 2:
+            continue
+        if m_tiles * ((N + bn - 1) // bn) >= _SM or bn == 64:
+            return bn
+    return 64
+
+
+def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError("gemm operands must be 2-D")
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+        if t.stride(0) % 8 != 0:
+            raise ValueError("gemm operand rows must be a multiple of 8 elements")
+    return t
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    trans_a: bool = False,
+    trans_b: bool = False,
+    a2: torch.Tensor | None = None,
+    b2: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    c_in: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    splits: int = 1,
+    bn: int | None = None,
+) -> torch.Tensor:
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    N = b.shape[1] if trans_b else b.shape[0]
+    Kb = b.shape[0] if trans_b else b.shape[1]
+    if K != Kb:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    K2 = 0
+    if a2 is not None:
+        K2 = a2.shape[0] if trans_a else a2.shape[1]
+
+    if not a.is_cuda:
+        # reference path (CPU): same contraction in the operand dtype with fp32 accumulation
+        fa = (a.t() if trans_a else a).float()
+        fb = (b if trans_b else b.t()).float()
+        acc = fa @ fb
+        if a2 is not None:
+            acc = acc + (a2.t() if trans_a else a2).float() @ (b2 if trans_b else b2.t()).float()
+        acc = acc * alpha
+        if c_in is not None and beta != 0.0:
+            acc = acc + beta * c_in.float()
+        if accumulate:
+            out.add_(acc.to(out.dtype))
+            return out
+        res = acc.to(out_dtype if a.dtype == torch.bfloat16 or out_dtype == torch.float32 else a.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    lib = _lib.cuda_lib()
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("the tcgen05 GEMM takes bf16 operands")
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    if a2 is not None:
+        a2 = _row_major_2d(a2)
+        b2 = _row_major_2d(b2)
+    if accumulate:
+        if out is None or out.dtype != torch.float32:
+            raise ValueError("accumulate=True needs an fp32 `out`")
+        out_mode = 2
+    else:
+        if splits > 1:
+            raise ValueError("split-K needs accumulate=True (fp32 atomics)")
+        out_mode = 0 if out_dtype == torch.bfloat16 else 1
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if out.stride(1) != 1:
+        raise ValueError("gemm output must be row-major")
+    if c_in is not None:
+        if c_in.stride(1) != 1 or c_in.dtype != out.dtype:
+            raise ValueError("c_in must be row-major with the output dtype")
+    if bn is None:
+        bn = _pick_bn(M, N)
+    rc = lib.axb_gemm_bf16(
+        a.data_ptr(), a.stride(0), int(trans_a),
+        b.data_ptr(), b.stride(0), int(trans_b),
+        out.data_ptr(), out.stride(0),
+        _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0,
+        M, N, K,
+        _lib.ptr(a2), a2.stride(0) if a2 is not None else 0,
+        _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
+        K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, int(splits), int(bn),
+        _lib.status_word(a.device).data_ptr(), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "axb_gemm_bf16")
+    return out
+
+
+def pick_splits(out_tiles: int, k_blocks: int) -> int:
+    """Split-K factor for skinny weight-gradient GEMMs so that all SMs get work."""
+    if out_tiles >= _SM:
+        return 1
+    return max(1, min(k_blocks, _SM // max(out_tiles, 1)))

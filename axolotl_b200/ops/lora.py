@@ -1,0 +1,124 @@
+"""Fused LoRA linear: ``y = x W^T + s * (x A^T) B^T`` with the low-rank product folded into the
+base GEMM as a K-extension (one extra accumulation block in TMEM), and a backward pass that
+never materialises ``W + s B A``.
+
+Several projections that share the same input (q/k/v, gate/up) are handled as ONE GEMM over the
+row-concatenated weight: ``A_cat`` stacks the A matrices, ``B_cat`` is block diagonal.
+
+Covers what the reference implements as LoRA_MLP / LoRA_QKV / LoRA_O autograd functions on top
+of cuBLAS (src/axolotl/kernels/lora.py:283-1209, 1623-1769).
+"""
+from __future__ import annotations
+
+import torch
+
+from .gemm import gemm, pick_splits
+
+
+class _LoRALinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, W, A, B, A16, B16, scaling, blocks, bias):
+        """x [T,K] bf16; W [N,K] bf16 (frozen or trainable); A [R,K] / B [N,R] fp32 masters with
+        bf16 shadows A16 / B16; blocks = ((row0, rows, r0, r), ...) diagonal blocks of B."""
+        xa = gemm(x, A16, alpha=scaling)  # [T, R], already scaled
+        y = gemm(x, W, a2=xa, b2=B16)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x, W, A, B, A16, B16, xa)
+        ctx.scaling, ctx.blocks, ctx.has_bias = scaling, blocks, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, W, A, B, A16, B16, xa = ctx.saved_tensors
+        s = ctx.scaling
+        dy = dy.contiguous()
+        T, K = x.shape
+        N, R = B16.shape
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        # t = s * dy @ B  -> [T, R]
+        t = gemm(dy, B16, trans_b=True, alpha=s)
+        dx = gemm(dy, W, trans_b=True, a2=t, b2=A16) if need_dx else None
+        dA = dB = None
+        if ctx.needs_input_grad[2]:
+            tgt = getattr(A, "_axb_grad", None)
+            buf = tgt if tgt is not None else torch.zeros(A.shape, dtype=torch.float32, device=x.device)
+            sp = pick_splits((K + 255) // 256, (T + 63) // 64)
+            gemm(t, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
+            dA = None if tgt is not None else buf.to(A.dtype)
+        if ctx.needs_input_grad[3]:
+            tgt = getattr(B, "_axb_grad", None)
+            buf = tgt if tgt is not None else torch.zeros(B.shape, dtype=torch.float32, device=x.device)
+            for (row0, rows, r0, r) in ctx.blocks:
+                sp = pick_splits((rows + 127) // 128, (T + 63) // 64)
+                # dB_blk [rows, r] = dy[:, row0:row0+rows]^T @ xa[:, r0:r0+r]   (xa carries s)
+                gemm(dy[:, row0:row0 + rows], xa[:, r0:r0 + r], trans_a=True, trans_b=True,
+                     out=buf[row0:row0 + rows, r0:r0 + r], accumulate=True, splits=sp, bn=64)
+            dB = None if tgt is not None else buf.to(B.dtype)
+        dW = None
+        if need_dw:
+            dWf = torch.zeros(W.shape, dtype=torch.float32, device=x.device)
+            sp = pick_splits(((N + 127) // 128) * ((K + 255) // 256), (T + 63) // 64)
+            gemm(dy, x, trans_a=True, trans_b=True, out=dWf, accumulate=True, splits=sp)
+            dW = dWf.to(W.dtype)
+        dbias = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[8] else None
+        return dx, dW, dA, dB, None, None, None, None, dbias
+
+
+class _LinearFn(torch.autograd.Function):
+    """Plain ``x W^T`` on the tcgen05 GEMM (frozen or trainable weight, optional bias)."""
+
+    @staticmethod
+    def forward(ctx, x, W, bias):
+        ctx.save_for_backward(x, W)
+        ctx.has_bias = bias is not None
+        y = gemm(x, W)
+        if bias is not None:
+            y = y + bias
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, W = ctx.saved_tensors
+        dy = dy.contiguous()
+        T, K = x.shape
+        N = W.shape[0]
+        dx = gemm(dy, W, trans_b=True) if ctx.needs_input_grad[0] else None
+        dW = None
+        if ctx.needs_input_grad[1]:
+            tgt = getattr(W, "_axb_grad", None)
+            buf = tgt if tgt is not None else torch.zeros(W.shape, dtype=torch.float32, device=x.device)
+            sp = pick_splits(((N + 127) // 128) * ((K + 255) // 256), (T + 63) // 64)
+            gemm(dy, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
+            dW = None if tgt is not None else buf.to(W.dtype)
+        dbias = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dW, dbias
+
+
+def linear(x, W, bias=None):
+    """``x @ W^T (+ bias)``; 2-D or N-D ``x``. CPU tensors use torch ops directly."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, W.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    shp = x.shape
+    y = _LinearFn.apply(x.reshape(-1, shp[-1]).contiguous(), W, bias)
+    return y.view(*shp[:-1], W.shape[0])
+
+
+def lora_linear(x, W, A, B, A16, B16, scaling, blocks, bias=None, dropout_p=0.0, training=False):
+    """Fused LoRA projection (see module docstring). ``A16`` / ``B16`` are the bf16 shadows of the
+    fp32 masters on CUDA and may be None on CPU."""
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if not x.is_cuda or (dropout_p > 0.0 and training):
+        xd = torch.nn.functional.dropout(x2, dropout_p, training) if dropout_p > 0.0 else x2
+        if x.is_cuda:
+            base = _LinearFn.apply(x2.contiguous(), W, bias)
+            lo = _LinearFn.apply(_LinearFn.apply(xd.contiguous(), A.to(x.dtype), None),
+                                 B.to(x.dtype), None)
+            y = base + scaling * lo
+        else:
+            y = torch.nn.functional.linear(x2, W.to(x2.dtype), None if bias is None else bias.to(x2.dtype))
+            y = y + scaling * ((xd @ A.to(x2.dtype).t()) @ B.to(x2.dtype).t())
+        return y.view(*shp[:-1], W.shape[0])
+    y = _LoRALinearFn.apply(x2.contiguous(), W, A, B, A16, B16, float(scaling), blocks, bias)
+    return y.view(*shp[:-1], W.shape[0])

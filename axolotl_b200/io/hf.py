@@ -1,0 +1,149 @@
+"""Hugging Face checkpoint interchange for the model families in ``models.config``.
+
+Our modules keep fused weights (qkv_proj, gate_up_proj, fused experts); checkpoints on disk use
+the HF per-projection names, so loading concatenates and saving splits. NVFP4 expert checkpoints
+(modelopt ``weight`` / ``weight_scale`` / ``weight_scale_2`` or compressed-tensors
+``weight_packed`` / ``weight_scale`` / ``weight_global_scale``) are detected by "uint8 weight +
+group scale" exactly like the reference loader
+(src/axolotl/integrations/kernels/libs/scattermoe_lora/nvfp4_moe_loading.py:95-155, 189-243).
+"""
+from __future__ import annotations
+
+import os
+import re
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.layers import FusedLinear
+from ..models.moe import Experts
+from ..models.transformer import CausalLM
+from . import safetensors_io as st
+
+
+def _split_name(hf_name: str):
+    """'model.layers.3.self_attn.q_proj.weight' -> ('layers.3.self_attn', 'q_proj', 'weight')."""
+    m = re.match(r"model\.(.*)\.(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)\.(weight|bias)$", hf_name)
+    return m.groups() if m else None
+
+
+_FUSED_OF = {"q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj", "o_proj": "o_proj",
+             "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj", "down_proj": "down_proj"}
+
+
+@torch.no_grad()
+def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
+    """Streams (hf_name, tensor) pairs into the model. Returns the set of missing parameter slots."""
+    mods = dict(model.named_modules())
+    filled = set()
+    expert_parts = {}
+    for name, t in named_tensors:
+        if name == "model.embed_tokens.weight":
+            model.embed_tokens.copy_(t)
+            filled.add("embed_tokens")
+        elif name == "lm_head.weight":
+            if model.lm_head is not None:
+                model.lm_head.copy_(t)
+            filled.add("lm_head")
+        elif name == "model.norm.weight":
+            model.norm.weight.copy_(t)
+            filled.add("norm")
+        elif (sp := _split_name(name)) is not None and ".experts." not in name:
+            parent, sub, kind = sp
+            fl: FusedLinear = mods[f"{parent}.{_FUSED_OF[sub]}"]
+            r0, r1 = fl.row_range(sub)
+            (fl.weight if kind == "weight" else fl.bias)[r0:r1].copy_(t)
+            filled.add(f"{parent}.{sub}.{kind}")
+        elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm)\.weight$", name)):
+            mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.(q_norm|k_norm)\.weight$", name)):
+            mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.weight$", name)):
+            mods[m.group(1)].gate.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(gate_up_proj|down_proj)$", name)):
+            getattr(mods[m.group(1)].experts, m.group(2)).copy_(t)     # HF v5 fused expert tensors
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(\w+)$", name)):
+            expert_parts.setdefault(m.group(1), {})[(int(m.group(2)), m.group(3), m.group(4))] = t
+        elif name.endswith("rotary_emb.inv_freq"):
+            continue
+        elif strict:
+            raise KeyError(f"unexpected checkpoint tensor '{name}'")
+    for parent, parts in expert_parts.items():
+        _fill_experts(mods[parent].experts, parts)
+        filled.add(parent + ".experts")
+    return filled
+
+
+def _fill_experts(ex: Experts, parts: dict):
+    from .nvfp4_loading import is_nvfp4_parts, fuse_nvfp4_experts
+
+    if is_nvfp4_parts(parts):
+        ex.nvfp4 = fuse_nvfp4_experts(parts, ex.E, device=ex.gate_up_proj.device)
+        ex.gate_up_proj = None
+        ex.down_proj = None
+        return
+    I = ex.I
+    for (e, sub, kind), t in parts.items():
+        if kind != "weight":
+            continue
+        if sub == "gate_proj":
+            ex.gate_up_proj[e, :I].copy_(t)
+        elif sub == "up_proj":
+            ex.gate_up_proj[e, I:].copy_(t)
+        else:
+            ex.down_proj[e].copy_(t)
+
+
+def load_pretrained(path: str, dtype=torch.bfloat16, device="cpu", config: ModelConfig | None = None,
+                    strict: bool = True) -> CausalLM:
+    cfg = config or ModelConfig.from_pretrained(path)
+    model = CausalLM(cfg, dtype=dtype, device=device)
+    load_state_into(model, st.iter_checkpoint(path), strict=strict)
+    return model
+
+
+def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
+    """Model tensors under HF names (views where possible; the writer makes them contiguous)."""
+    sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}
+    if model.lm_head is not None:
+        sd["lm_head.weight"] = model.lm_head.detach()
+    for name, m in model.named_modules():
+        if isinstance(m, FusedLinear):
+            parent = name.rsplit(".", 1)[0]
+            for sub in m.names:
+                r0, r1 = m.row_range(sub)
+                sd[f"model.{parent}.{sub}.weight"] = m.weight.detach()[r0:r1]
+                if m.bias is not None:
+                    sd[f"model.{parent}.{sub}.bias"] = m.bias.detach()[r0:r1]
+        elif name.endswith(("input_layernorm", "post_attention_layernorm", "q_norm", "k_norm")):
+            sd[f"model.{name}.weight"] = m.weight.detach()
+        elif isinstance(m, Experts):
+            if m.nvfp4 is not None:
+                for which in ("gate_up", "down"):
+                    q = m.nvfp4[which]
+                    sd[f"model.{name}.{which}_proj.weight_packed"] = q["qdata"]
+                    sd[f"model.{name}.{which}_proj.weight_scale"] = q["scale"]
+                    sd[f"model.{name}.{which}_proj.weight_global_scale"] = q["pts"]
+            elif per_expert:
+                I = m.I
+                for e in range(m.E):
+                    sd[f"model.{name}.{e}.gate_proj.weight"] = m.gate_up_proj.detach()[e, :I]
+                    sd[f"model.{name}.{e}.up_proj.weight"] = m.gate_up_proj.detach()[e, I:]
+                    sd[f"model.{name}.{e}.down_proj.weight"] = m.down_proj.detach()[e]
+            else:
+                sd[f"model.{name}.gate_up_proj"] = m.gate_up_proj.detach()
+                sd[f"model.{name}.down_proj"] = m.down_proj.detach()
+        elif hasattr(m, "gate") and isinstance(getattr(m, "gate"), torch.nn.Parameter):
+            sd[f"model.{name}.gate.weight"] = m.gate.detach()
+    return sd
+
+
+def save_pretrained(model: CausalLM, out_dir: str, max_shard_bytes: int = 5 * 1024 ** 3, per_expert=False):
+    os.makedirs(out_dir, exist_ok=True)
+    model.config.save_pretrained(out_dir)
+    sd = {k: v.to("cpu") for k, v in hf_state_dict(model, per_expert=per_expert).items()}
+    return st.save_sharded(sd, out_dir, max_shard_bytes)

@@ -1,0 +1,205 @@
+"""Model configuration: a single dataclass covering the decoder-only families we own
+(Llama / Mistral / Qwen2 / Qwen3 dense, Qwen3-MoE / Mixtral-style sparse), filled from a Hugging
+Face ``config.json`` so checkpoints stay interchangeable with ``transformers``.
+
+The reference resolves architectures through ``transformers.AutoConfig``
+(src/axolotl/utils/config/__init__.py:259-372); we read the same file ourselves.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any
+
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "mixtral")
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int | None = None
+    head_dim: int | None = None
+    hidden_act: str = "silu"
+    max_position_embeddings: int = 8192
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: dict | None = None
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    tie_word_embeddings: bool = False
+    initializer_range: float = 0.02
+    qk_norm: bool = False  # Qwen3: per-head RMSNorm on q and k before RoPE
+    # sparse MoE (qwen3_moe / mixtral)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    decoder_sparse_step: int = 1
+    mlp_only_layers: list = field(default_factory=list)
+    bos_token_id: int | None = None
+    eos_token_id: Any = None
+    pad_token_id: int | None = None
+    torch_dtype: str = "bfloat16"
+    architectures: list = field(default_factory=list)
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.model_type in ("qwen3", "qwen3_moe"):
+            self.qk_norm = True
+        if self.model_type == "qwen2":
+            self.attention_bias = True
+
+    # ------------------------------------------------------------------ HF interchange
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        d = dict(d)
+        mt = d.get("model_type", "llama")
+        if mt not in SUPPORTED_MODEL_TYPES:
+            raise ValueError(
+                f"model_type '{mt}' is not supported by axolotl_b200 (supported: {SUPPORTED_MODEL_TYPES})")
+        known = {f for f in cls.__dataclass_fields__ if f != "extra"}
+        kw = {k: v for k, v in d.items() if k in known}
+        if "rope_parameters" in d and isinstance(d["rope_parameters"], dict):  # transformers v5 layout
+            rp = d["rope_parameters"]
+            kw.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
+            if rp.get("rope_type", "default") != "default":
+                kw["rope_scaling"] = rp
+        if mt == "mixtral":
+            kw["num_experts"] = d.get("num_local_experts", 0)
+            kw["moe_intermediate_size"] = d.get("intermediate_size", 0)
+        if "torch_dtype" not in kw and "dtype" in d:
+            kw["torch_dtype"] = d["dtype"]
+        extra = {k: v for k, v in d.items() if k not in known}
+        cfg = cls(**kw)
+        cfg.extra = extra
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        f = os.path.join(path, "config.json") if os.path.isdir(path) else path
+        with open(f) as fh:
+            return cls.from_hf_dict(json.load(fh))
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        extra = d.pop("extra")
+        d.pop("qk_norm")
+        if self.model_type == "mixtral":
+            d["num_local_experts"] = d.pop("num_experts")
+        if not self.num_experts:
+            for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
+                      "router_aux_loss_coef", "decoder_sparse_step", "mlp_only_layers"):
+                d.pop(k, None)
+        if not d.get("architectures"):
+            d["architectures"] = [_ARCH_NAME[self.model_type]]
+        out = dict(extra)
+        out.update(d)
+        return out
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as fh:
+            json.dump(self.to_hf_dict(), fh, indent=2)
+
+    # ------------------------------------------------------------------ derived
+    def is_moe_layer(self, idx: int) -> bool:
+        return (self.num_experts > 0 and idx not in self.mlp_only_layers
+                and (idx + 1) % max(self.decoder_sparse_step, 1) == 0)
+
+    def rope_inv_freq(self):
+        """(inv_freq tensor [head_dim/2] fp32, attention scaling factor) incl. llama3 / linear /
+        yarn-free variants of ``rope_scaling``."""
+        import torch
+
+        D = self.head_dim
+        inv = 1.0 / (self.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        scale = 1.0
+        rs = self.rope_scaling
+        if rs:
+            kind = rs.get("rope_type", rs.get("type", "default"))
+            if kind == "linear":
+                inv = inv / float(rs["factor"])
+            elif kind == "llama3":
+                factor, lo, hi = rs["factor"], rs.get("low_freq_factor", 1.0), rs.get("high_freq_factor", 4.0)
+                old = rs.get("original_max_position_embeddings", 8192)
+                wavelen = 2 * math.pi / inv
+                smooth = (old / wavelen - lo) / (hi - lo)
+                scaled = torch.where(wavelen > old / lo, inv / factor, inv)
+                mid = (wavelen <= old / lo) & (wavelen >= old / hi)
+                inv = torch.where(mid, (1 - smooth) * inv / factor + smooth * inv, scaled)
+            elif kind in ("default", None):
+                pass
+            else:
+                raise ValueError(f"rope_scaling type '{kind}' is not supported")
+        return inv, scale
+
+    def num_params(self, include_embeddings: bool = True) -> int:
+        H, L, V = self.hidden_size, self.num_hidden_layers, self.vocab_size
+        D, Hq, Hk = self.head_dim, self.num_attention_heads, self.num_key_value_heads
+        attn = H * (Hq + 2 * Hk) * D + Hq * D * H
+        n = 0
+        for i in range(L):
+            if self.is_moe_layer(i):
+                mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
+            else:
+                mlp = 3 * H * self.intermediate_size
+            n += attn + mlp + 2 * H
+        n += H
+        if include_embeddings:
+            n += V * H * (1 if self.tie_word_embeddings else 2)
+        return n
+
+
+_ARCH_NAME = {
+    "llama": "LlamaForCausalLM",
+    "mistral": "MistralForCausalLM",
+    "qwen2": "Qwen2ForCausalLM",
+    "qwen3": "Qwen3ForCausalLM",
+    "qwen3_moe": "Qwen3MoeForCausalLM",
+    "mixtral": "MixtralForCausalLM",
+}
+
+
+# Named architectures used by the benchmark configs (random-init, no download needed).
+PRESETS = {
+    "tiny-llama": dict(model_type="llama", vocab_size=32000, hidden_size=256, intermediate_size=688,
+                       num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=2048),
+    "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                       num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                       rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192),
+    "llama-3-70b": dict(model_type="llama", vocab_size=128256, hidden_size=8192, intermediate_size=28672,
+                        num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8,
+                        rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192),
+    "qwen3-8b": dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                     num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                     rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960),
+    "qwen3-moe-30b-a3b": dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048,
+                              intermediate_size=6144, moe_intermediate_size=768, num_hidden_layers=48,
+                              num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                              num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+                              router_aux_loss_coef=0.001, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                              max_position_embeddings=40960),
+    "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=256, intermediate_size=512,
+                           moe_intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,
+                           router_aux_loss_coef=0.001, rms_norm_eps=1e-6),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    kw = dict(PRESETS[name])
+    kw.update(overrides)
+    return ModelConfig(**kw)

@@ -1,0 +1,148 @@
+"""Building blocks: fused multi-projection linear layers with LoRA adapters, RMSNorm.
+
+A ``FusedLinear`` holds the row-concatenated weight of several projections that read the same
+input (q|k|v, gate|up) so one tcgen05 GEMM serves them all. LoRA adapters attach per
+sub-projection; their A matrices are stacked (``lora_A`` [R, in]) and their B matrices form the
+diagonal blocks of ``lora_B`` [N, R], which the GEMM consumes as a K-extension. Per-projection
+PEFT tensors (``<name>.lora_A.weight`` [r, in], ``<name>.lora_B.weight`` [out, r]) are views of
+those buffers, so adapter checkpoints stay PEFT compatible
+(reference adapter wiring: src/axolotl/loaders/adapter.py:140-202).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as Fn
+from ..ops.lora import linear, lora_linear
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim, eps=1e-6, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x, residual=None):
+        return Fn.add_rmsnorm(x, residual, self.weight, self.eps)
+
+
+class FusedLinear(nn.Module):
+    def __init__(self, in_features, out_features, names, bias=False, dtype=torch.bfloat16,
+                 device=None):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = list(out_features)
+        self.names = list(names)
+        self.weight = nn.Parameter(torch.empty(sum(out_features), in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(sum(out_features), dtype=dtype, device=device)) if bias else None
+        # LoRA state (absent until add_lora)
+        self.lora_A = None
+        self.lora_B = None
+        self.lora_A16 = None
+        self.lora_B16 = None
+        self.lora_blocks = ()
+        self.lora_names = []
+        self.lora_r = 0
+        self.scaling = 1.0
+        self.lora_dropout = 0.0
+        self.merged = False
+
+    # ------------------------------------------------------------------ sub-projection views
+    def row_range(self, name):
+        i = self.names.index(name)
+        r0 = sum(self.out_features[:i])
+        return r0, r0 + self.out_features[i]
+
+    def sub_weight(self, name):
+        r0, r1 = self.row_range(name)
+        return self.weight[r0:r1]
+
+    # ------------------------------------------------------------------ LoRA
+    def add_lora(self, r, alpha, dropout=0.0, targets=None, use_rslora=False, dtype=torch.float32,
+                 init_b_zero=True):
+        targets = [n for n in self.names if targets is None or n in targets]
+        if not targets:
+            return
+        dev = self.weight.device
+        R = r * len(targets)
+        N = self.weight.shape[0]
+        A = torch.empty(R, self.in_features, dtype=dtype, device=dev)
+        for i in range(len(targets)):  # PEFT default init: kaiming_uniform(a=sqrt(5)) on A, zeros on B
+            nn.init.kaiming_uniform_(A[i * r:(i + 1) * r], a=math.sqrt(5))
+        B = torch.zeros(N, R, dtype=dtype, device=dev)
+        blocks = []
+        for i, n in enumerate(targets):
+            r0, r1 = self.row_range(n)
+            blocks.append((r0, r1 - r0, i * r, r))
+            if not init_b_zero:
+                nn.init.normal_(B[r0:r1, i * r:(i + 1) * r], std=0.02)
+        self.lora_A = nn.Parameter(A)
+        self.lora_B = nn.Parameter(B)
+        self.lora_blocks = tuple(blocks)
+        self.lora_names = targets
+        self.lora_r = r
+        self.scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
+        self.lora_dropout = dropout
+        self.refresh_shadows()
+
+    def refresh_shadows(self):
+        """bf16 copies of the fp32 adapter masters for the GEMM kernels (CUDA only)."""
+        if self.lora_A is None:
+            return
+        if self.lora_A.is_cuda:
+            if self.lora_A16 is None or self.lora_A16.device != self.lora_A.device:
+                self.lora_A16 = self.lora_A.detach().to(torch.bfloat16)
+                self.lora_B16 = self.lora_B.detach().to(torch.bfloat16)
+            else:
+                self.lora_A16.copy_(self.lora_A.detach())
+                self.lora_B16.copy_(self.lora_B.detach())
+        else:
+            self.lora_A16 = self.lora_B16 = None
+
+    def peft_tensors(self):
+        """{sub-projection name: (A [r, in], B [out, r])} views in PEFT layout."""
+        out = {}
+        for (r0, rows, c0, r), n in zip(self.lora_blocks, self.lora_names):
+            out[n] = (self.lora_A[c0:c0 + r], self.lora_B[r0:r0 + rows, c0:c0 + r])
+        return out
+
+    def load_peft_tensors(self, name, A, B):
+        i = self.lora_names.index(name)
+        r0, rows, c0, r = self.lora_blocks[i]
+        with torch.no_grad():
+            self.lora_A[c0:c0 + r].copy_(A)
+            self.lora_B[r0:r0 + rows, c0:c0 + r].copy_(B)
+
+    @torch.no_grad()
+    def merge_lora_(self):
+        """W += s * B A (fp32 math, rounded once). Leaves the adapter zeroed out of the forward."""
+        if self.lora_A is None or self.merged:
+            return
+        delta = self.scaling * (self.lora_B.float() @ self.lora_A.float())
+        self.weight.copy_((self.weight.float() + delta).to(self.weight.dtype))
+        self.merged = True
+
+    def _apply(self, fn, *a, **kw):
+        super()._apply(fn, *a, **kw)
+        if self.lora_A is not None:
+            self.lora_A16 = None
+            self.refresh_shadows()
+        return self
+
+    def forward(self, x):
+        if self.lora_A is None or self.merged:
+            return linear(x, self.weight, self.bias)
+        if x.is_cuda and self.lora_A16 is None:
+            self.refresh_shadows()
+        return lora_linear(x, self.weight, self.lora_A, self.lora_B, self.lora_A16, self.lora_B16,
+                           self.scaling, self.lora_blocks, self.bias, self.lora_dropout,
+                           self.training)
+
+    def extra_repr(self):
+        s = f"in={self.in_features}, out={dict(zip(self.names, self.out_features))}"
+        if self.lora_A is not None:
+            s += f", lora_r={self.lora_r} on {self.lora_names}, scaling={self.scaling:g}"
+        return s

@@ -1,0 +1,217 @@
+"""LoRA adapter management: injection, PEFT-format state dicts, ``adapter_config.json``.
+
+File format contract (what ``peft`` writes and what the reference's merge tool reads,
+src/axolotl/cli/utils/lora_merge.py:1904-2000): keys
+``base_model.model.<hf module path>.lora_A.weight`` [r, in] / ``.lora_B.weight`` [out, r];
+expert adapters (PEFT ``target_parameters``) use ``<path>.lora_A.weight`` [E*r, in] and
+``.lora_B.weight`` [out, r*E].
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from dataclasses import asdict, dataclass, field
+
+import torch
+
+from .layers import FusedLinear
+from .moe import Experts
+
+ALL_LINEAR = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+@dataclass
+class LoraSpec:
+    r: int = 8
+    lora_alpha: int = 16
+    lora_dropout: float = 0.0
+    target_modules: list | str | None = None       # names, or a regex string (PEFT semantics)
+    target_parameters: list | None = None          # e.g. ["mlp.experts.gate_up_proj", "mlp.experts.down_proj"]
+    use_rslora: bool = False
+    use_dora: bool = False
+    fan_in_fan_out: bool = False
+    bias: str = "none"
+    modules_to_save: list | None = None
+    rank_pattern: dict = field(default_factory=dict)
+    alpha_pattern: dict = field(default_factory=dict)
+    layers_to_transform: list | None = None
+    base_model_name_or_path: str | None = None
+
+    def to_peft_dict(self):
+        tm = self.target_modules
+        return {
+            "peft_type": "LORA", "task_type": "CAUSAL_LM", "auto_mapping": None,
+            "base_model_name_or_path": self.base_model_name_or_path, "bias": self.bias,
+            "fan_in_fan_out": self.fan_in_fan_out, "inference_mode": True, "init_lora_weights": True,
+            "layers_pattern": None, "layers_to_transform": self.layers_to_transform,
+            "lora_alpha": self.lora_alpha, "lora_dropout": self.lora_dropout,
+            "modules_to_save": self.modules_to_save, "r": self.r, "rank_pattern": self.rank_pattern,
+            "alpha_pattern": self.alpha_pattern, "revision": None,
+            "target_modules": sorted(tm) if isinstance(tm, (list, tuple, set)) else tm,
+            "target_parameters": self.target_parameters, "use_dora": self.use_dora,
+            "use_rslora": self.use_rslora,
+        }
+
+    @classmethod
+    def from_peft_dict(cls, d):
+        keys = cls.__dataclass_fields__.keys()
+        kw = {k: v for k, v in d.items() if k in keys and v is not None}
+        return cls(**kw)
+
+    def save(self, out_dir):
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "adapter_config.json"), "w") as fh:
+            json.dump(self.to_peft_dict(), fh, indent=2)
+
+    @classmethod
+    def load(cls, adapter_dir):
+        with open(os.path.join(adapter_dir, "adapter_config.json")) as fh:
+            return cls.from_peft_dict(json.load(fh))
+
+
+def _hf_path(fused_name: str, sub: str) -> str:
+    """'layers.3.self_attn.qkv_proj' + 'q_proj' -> 'model.layers.3.self_attn.q_proj'."""
+    parent = fused_name.rsplit(".", 1)[0]
+    return f"model.{parent}.{sub}"
+
+
+def _matches(spec: LoraSpec, hf_path: str, sub: str, layer_idx: int | None) -> bool:
+    if spec.layers_to_transform is not None and layer_idx is not None and layer_idx not in spec.layers_to_transform:
+        return False
+    tm = spec.target_modules
+    if tm is None:
+        return False
+    if isinstance(tm, str):
+        if tm == "all-linear":
+            return True
+        return re.fullmatch(tm, hf_path) is not None
+    return any(sub == t or hf_path.endswith("." + t) for t in tm)
+
+
+def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=torch.float32):
+    """Adds adapters according to ``spec`` and freezes everything else. Returns the trainable
+    parameter count."""
+    if spec.use_dora:
+        raise NotImplementedError("DoRA adapters are not supported by axolotl_b200 yet")
+    if freeze_base:
+        for p in model.parameters():
+            p.requires_grad_(False)
+    for name, m in model.fused_linears():
+        mt = re.search(r"layers\.(\d+)\.", name)
+        li = int(mt.group(1)) if mt else None
+        targets = [s for s in m.names if _matches(spec, _hf_path(name, s), s, li)]
+        if targets:
+            r = spec.r
+            for pat, rv in spec.rank_pattern.items():
+                if any(re.search(pat, _hf_path(name, s)) for s in targets):
+                    r = rv
+            alpha = spec.lora_alpha
+            for pat, av in spec.alpha_pattern.items():
+                if any(re.search(pat, _hf_path(name, s)) for s in targets):
+                    alpha = av
+            m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype)
+    if spec.target_parameters:
+        for name, m in model.named_modules():
+            if isinstance(m, Experts):
+                wanted = [t for t in spec.target_parameters if t.endswith("gate_up_proj") or t.endswith("down_proj")]
+                if wanted:
+                    m.add_lora(spec.r, spec.lora_alpha, spec.use_rslora, adapter_dtype)
+    if spec.modules_to_save:
+        for n, p in model.named_parameters():
+            if any(k in n for k in spec.modules_to_save):
+                p.requires_grad_(True)
+    return sum(p.numel() for p in model.parameters() if p.requires_grad)
+
+
+def get_peft_state_dict(model) -> dict:
+    """Adapter tensors in PEFT naming (contiguous CPU-safe copies are made by the writer)."""
+    sd = {}
+    for name, m in model.fused_linears():
+        if m.lora_A is None:
+            continue
+        for sub, (A, B) in m.peft_tensors().items():
+            base = f"base_model.model.{_hf_path(name, sub)}"
+            sd[f"{base}.lora_A.weight"] = A.detach()
+            sd[f"{base}.lora_B.weight"] = B.detach()
+    for name, m in model.named_modules():
+        if isinstance(m, Experts) and m.lora is not None:
+            base = f"base_model.model.model.{name}"
+            for which in ("gate_up", "down"):
+                sd[f"{base}.{which}_proj.lora_A.weight"] = m.lora[which + "_A"].detach()
+                sd[f"{base}.{which}_proj.lora_B.weight"] = m.lora[which + "_B"].detach()
+    return sd
+
+
+def set_peft_state_dict(model, sd: dict, strict: bool = True):
+    """Loads PEFT-named adapter tensors (any ``.default`` adapter-name infix is tolerated)."""
+    norm = {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B."): v
+            for k, v in sd.items()}
+    used = set()
+    for name, m in model.fused_linears():
+        if m.lora_A is None:
+            continue
+        for sub in m.lora_names:
+            base = f"base_model.model.{_hf_path(name, sub)}"
+            ka, kb = f"{base}.lora_A.weight", f"{base}.lora_B.weight"
+            if ka in norm and kb in norm:
+                m.load_peft_tensors(sub, norm[ka].to(m.lora_A.device), norm[kb].to(m.lora_B.device))
+                used.update((ka, kb))
+            elif strict:
+                raise KeyError(f"adapter tensors for {base} are missing")
+        m.refresh_shadows()
+    for name, m in model.named_modules():
+        if isinstance(m, Experts) and m.lora is not None:
+            base = f"base_model.model.model.{name}"
+            for which in ("gate_up", "down"):
+                for ab in ("A", "B"):
+                    k = f"{base}.{which}_proj.lora_{ab}.weight"
+                    if k in norm:
+                        with torch.no_grad():
+                            m.lora[f"{which}_{ab}"].copy_(norm[k])
+                        used.add(k)
+                    elif strict:
+                        raise KeyError(f"adapter tensor {k} is missing")
+    unused = set(norm) - used
+    if strict and unused:
+        raise KeyError(f"unexpected adapter tensors: {sorted(unused)[:5]} ...")
+    return unused
+
+
+def save_adapter(model, spec: LoraSpec, out_dir: str):
+    from ..io.safetensors_io import save_file
+
+    os.makedirs(out_dir, exist_ok=True)
+    sd = {k: v.to("cpu").contiguous() for k, v in get_peft_state_dict(model).items()}
+    save_file(sd, os.path.join(out_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
+    spec.save(out_dir)
+
+
+def load_adapter(model, adapter_dir: str, strict: bool = True) -> LoraSpec:
+    from ..io.safetensors_io import load_file
+
+    spec = LoraSpec.load(adapter_dir)
+    sd = load_file(os.path.join(adapter_dir, "adapter_model.safetensors"))
+    set_peft_state_dict(model, sd, strict=strict)
+    return spec
+
+
+@torch.no_grad()
+def merge_and_unload(model):
+    """Folds every adapter into its base weight (W += s * B A) and removes the adapters."""
+    for _, m in model.fused_linears():
+        if m.lora_A is not None:
+            m.merge_lora_()
+            m.lora_A = m.lora_B = m.lora_A16 = m.lora_B16 = None
+            m.lora_blocks, m.lora_names, m.merged = (), [], False
+    for m in model.modules():
+        if isinstance(m, Experts) and m.lora is not None:
+            if m.nvfp4 is not None:
+                raise NotImplementedError("merge into NVFP4 experts goes through io.merge (requantising writer)")
+            r = m.lora_r
+            for e in range(m.E):
+                for which, W in (("gate_up", m.gate_up_proj), ("down", m.down_proj)):
+                    A, B = m.expert_lora(which, e)
+                    W[e].copy_((W[e].float() + m.scaling * (B.float() @ A.float())).to(W.dtype))
+            m.lora = None
+    return model

@@ -1,0 +1,148 @@
+"""Sparse mixture-of-experts block (Qwen3-MoE / Mixtral routing) with per-expert LoRA.
+
+Routing: softmax over experts -> top-k -> optional renormalisation; the load-balance auxiliary
+loss follows the Switch/HF definition (E * sum_e f_e * P_e). Expert weights are stored fused as
+``gate_up_proj`` [E, 2I, H] and ``down_proj`` [E, H, I] (HF v5 fused-expert layout) either in bf16
+or frozen NVFP4 (packed nibbles + E4M3 block scales + fp32 per-tensor scale, see ops/nvfp4.py).
+Expert LoRA uses the PEFT ``target_parameters`` layout: A [E*r, in] expert-major rows,
+B [out, r*E] rank-major columns (reference: src/axolotl/integrations/expert_parallel/shard.py:279-303).
+
+The local expert computation sorts tokens by expert and runs one grouped pass; with expert
+parallelism the dispatch / combine is delegated to ``parallel.ep`` (installed as ``self.ep``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as Fn
+from ..ops.lora import linear
+from .config import ModelConfig
+
+
+def route_topk(router_logits, k, norm_topk_prob=True):
+    """(weights [T,k] fp32, indices [T,k] int64, probs [T,E] fp32)."""
+    probs = torch.softmax(router_logits.float(), dim=-1)
+    w, idx = torch.topk(probs, k, dim=-1)
+    if norm_topk_prob:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx, probs
+
+
+def load_balance_loss(probs, idx, num_experts):
+    """E * sum_e (fraction of routed slots on e) * (mean router prob of e)."""
+    T, k = idx.shape
+    onehot = F.one_hot(idx, num_experts).float()          # [T, k, E]
+    tokens_per_expert = onehot.mean(0)                     # [k, E]
+    router_prob = probs.mean(0)                            # [E]
+    return num_experts * (tokens_per_expert * router_prob[None]).sum()
+
+
+class Experts(nn.Module):
+    """E SwiGLU experts with fused weights and optional per-expert LoRA."""
+
+    def __init__(self, num_experts, hidden, inter, act, dtype, device):
+        super().__init__()
+        self.E, self.H, self.I, self.act = num_experts, hidden, inter, act
+        self.gate_up_proj = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(num_experts, hidden, inter, dtype=dtype, device=device))
+        self.nvfp4 = None          # dict with packed tensors when the experts are frozen in NVFP4
+        self.lora = None           # dict: gate_up_A [E*r,H], gate_up_B [2I,r*E], down_A [E*r,I], down_B [H,r*E]
+        self.lora_r = 0
+        self.scaling = 1.0
+        self.expert_offset = 0     # first global expert id held locally (expert parallelism)
+
+    # ------------------------------------------------------------------ LoRA (PEFT target_parameters layout)
+    def add_lora(self, r, alpha, use_rslora=False, dtype=torch.float32):
+        dev = self.gate_up_proj.device if self.nvfp4 is None else self.nvfp4["gate_up"]["qdata"].device
+        E, H, I = self.E, self.H, self.I
+
+        def mk_a(inp):
+            a = torch.empty(E * r, inp, dtype=dtype, device=dev)
+            nn.init.kaiming_uniform_(a, a=math.sqrt(5))
+            return nn.Parameter(a)
+
+        self.lora = nn.ParameterDict({
+            "gate_up_A": mk_a(H), "gate_up_B": nn.Parameter(torch.zeros(2 * I, r * E, dtype=dtype, device=dev)),
+            "down_A": mk_a(I), "down_B": nn.Parameter(torch.zeros(H, r * E, dtype=dtype, device=dev)),
+        })
+        self.lora_r = r
+        self.scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
+
+    def expert_lora(self, which, e):
+        """(A_e [r, in], B_e [out, r]) for local expert e."""
+        r, E = self.lora_r, self.E
+        A = self.lora[which + "_A"][e * r:(e + 1) * r]
+        B = self.lora[which + "_B"].view(-1, r, E)[:, :, e]
+        return A, B
+
+    def expert_weight(self, which, e):
+        if self.nvfp4 is not None:
+            from ..ops.nvfp4 import dequantize_nvfp4
+
+            q = self.nvfp4[which]
+            return dequantize_nvfp4(q["qdata"][e], q["scale"][e], q["pts"][e])
+        return (self.gate_up_proj if which == "gate_up" else self.down_proj)[e]
+
+    # ------------------------------------------------------------------ compute
+    def forward(self, x_sorted, counts):
+        """x_sorted: tokens grouped by local expert ([M, H]); counts: python list of per-expert rows."""
+        if x_sorted.is_cuda:
+            from ..ops.grouped import grouped_experts_forward
+
+            return grouped_experts_forward(self, x_sorted, counts)
+        outs = []
+        start = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            xe = x_sorted[start:start + n]
+            start += n
+            gu = linear(xe, self.expert_weight("gate_up", e))
+            if self.lora is not None:
+                A, B = self.expert_lora("gate_up", e)
+                gu = gu + self.scaling * ((xe @ A.to(xe.dtype).t()) @ B.to(xe.dtype).t())
+            h = Fn.glu(gu, self.act)
+            y = linear(h, self.expert_weight("down", e))
+            if self.lora is not None:
+                A, B = self.expert_lora("down", e)
+                y = y + self.scaling * ((h @ A.to(h.dtype).t()) @ B.to(h.dtype).t())
+            outs.append(y)
+        if not outs:
+            return x_sorted.new_zeros((0, self.H))
+        return torch.cat(outs, 0)
+
+
+class SparseMoE(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.E, self.k = cfg.num_experts, cfg.num_experts_per_tok
+        self.norm_topk_prob = cfg.norm_topk_prob
+        self.gate = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
+        self.experts = Experts(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size, cfg.hidden_act,
+                               dtype, device)
+        self.aux_coef = cfg.router_aux_loss_coef
+        self.ep = None  # parallel.ep.ExpertParallelGroup when experts are sharded across ranks
+
+    def forward(self, x):
+        T, H = x.shape
+        logits = linear(x, self.gate)
+        w, idx, probs = route_topk(logits, self.k, self.norm_topk_prob)
+        aux = load_balance_loss(probs, idx, self.E) if self.training or self.aux_coef else None
+        if self.ep is not None:
+            y = self.ep.dispatch_compute_combine(self.experts, x, w, idx)
+            return y, aux
+        # local: sort the T*k routed slots by expert
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        tok = order // self.k
+        counts = torch.bincount(flat_e, minlength=self.E).tolist()
+        xs = x.index_select(0, tok)
+        ys = self.experts(xs, counts)
+        ws = w.reshape(-1).index_select(0, order).to(ys.dtype)
+        y = torch.zeros_like(x)
+        y.index_add_(0, tok, ys * ws[:, None])
+        return y, aux

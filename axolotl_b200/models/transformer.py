@@ -1,0 +1,250 @@
+"""Decoder-only causal LM (Llama / Mistral / Qwen2 / Qwen3 / Qwen3-MoE / Mixtral block graph).
+
+The model works on *packed token streams*: ``input_ids`` [B, S] is flattened to T = B*S tokens,
+documents are delimited by resets of ``position_ids`` (and by row starts), attention is causal
+inside each document (varlen flash attention kernel), and the loss is a chunked linear +
+cross-entropy that never builds [T, V] logits. This is the layout the reference obtains from its
+V2 collator + flash-attn varlen path (src/axolotl/utils/collators/batching.py:158-196,
+src/axolotl/monkeypatch/utils.py:111-169) without the segment-id mask round trip.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import functional as Fn
+from ..ops.lora import linear
+from .config import ModelConfig
+from .layers import FusedLinear, RMSNorm
+
+IGNORE_INDEX = -100
+
+
+@dataclass
+class CausalLMOutput:
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    hidden_states: torch.Tensor | None = None
+    aux_loss: torch.Tensor | None = None
+    num_items: int = 0
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.Hq, self.Hk, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        H = cfg.hidden_size
+        self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
+                                    ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
+                                    dtype=dtype, device=device)
+        self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=False, dtype=dtype, device=device)
+        self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
+        self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
+        self.eps = cfg.rms_norm_eps
+        self.scale = 1.0 / math.sqrt(self.D)
+
+    def forward(self, x, positions, inv_freq, attn_scale, meta):
+        qkv = self.qkv_proj(x)
+        qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
+                          self.q_norm.weight if self.q_norm is not None else None,
+                          self.k_norm.weight if self.k_norm is not None else None, self.eps)
+        a = Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+        return self.o_proj(a)
+
+
+class MLP(nn.Module):
+    def __init__(self, hidden, inter, act, bias, dtype, device):
+        super().__init__()
+        self.gate_up_proj = FusedLinear(hidden, [inter, inter], ["gate_proj", "up_proj"], bias=bias,
+                                        dtype=dtype, device=device)
+        self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
+        self.act = act
+
+    def forward(self, x):
+        return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.self_attn = Attention(cfg, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        if cfg.is_moe_layer(idx):
+            from .moe import SparseMoE
+
+            self.mlp = SparseMoE(cfg, dtype, device)
+        else:
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
+        self.is_moe = cfg.is_moe_layer(idx)
+
+    def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
+        x, residual = self.input_layernorm(h, residual)
+        a = self.self_attn(x, positions, inv_freq, attn_scale, meta)
+        x, residual = self.post_attention_layernorm(a, residual)
+        if self.is_moe:
+            y, aux = self.mlp(x)
+        else:
+            y, aux = self.mlp(x), None
+        return y, residual, aux
+
+
+class CausalLM(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.config = cfg
+        self.dtype = dtype
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        if cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        inv, scale = cfg.rope_inv_freq()
+        self.register_buffer("inv_freq", inv.to(device) if device is not None else inv, persistent=False)
+        self.attn_scale = scale
+        self.gradient_checkpointing = False
+        self.ce_chunk_rows = 2048
+        self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
+
+    # ------------------------------------------------------------------ init
+    @torch.no_grad()
+    def init_weights(self, seed: int | None = 0):
+        """N(0, initializer_range) on every matrix, ones on norms (HF `_init_weights` rule)."""
+        std = self.config.initializer_range
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device=self.embed_tokens.device)
+            gen.manual_seed(seed)
+        for name, p in self.named_parameters():
+            if "lora_" in name:
+                continue
+            if p.dim() >= 2:
+                p.normal_(0.0, std, generator=gen)
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.fill_(1.0)
+        return self
+
+    def output_weight(self):
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    def enable_gradient_checkpointing(self, flag=True):
+        self.gradient_checkpointing = flag
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_ids, position_ids=None, labels=None, attn_meta=None, num_items=None,
+                return_logits=False, shift_labels=True):
+        """input_ids / position_ids / labels: [B, S] (or [T]). Returns CausalLMOutput.
+
+        ``labels`` follow the HF convention (unshifted; the model shifts by one inside each row)
+        unless ``shift_labels=False``. ``num_items`` is the loss denominator (trainable tokens of
+        the whole optimizer step when gradients are accumulated); default = this batch's count.
+        """
+        cfg = self.config
+        if input_ids.dim() == 1:
+            input_ids = input_ids[None]
+        B, S = input_ids.shape
+        dev = self.embed_tokens.device
+        if position_ids is None:
+            position_ids = torch.arange(S, dtype=torch.int32).repeat(B, 1)
+        if attn_meta is None:
+            attn_meta = build_attn_meta(position_ids, dev)
+        ids = input_ids.reshape(-1).to(dev, non_blocking=True)
+        pos = position_ids.reshape(-1).to(device=dev, dtype=torch.int32, non_blocking=True)
+        h = Fn.embedding(self.embed_tokens, ids)
+        residual = None
+        aux_total = None
+        hooks = self.hooks
+        for i, layer in enumerate(self.layers):
+            if hooks is not None:
+                hooks.pre_layer(i)
+            if self.gradient_checkpointing and self.training:
+                h, residual, aux = checkpoint(layer, h, residual, pos, self.inv_freq, self.attn_scale,
+                                              attn_meta, use_reentrant=False)
+            else:
+                h, residual, aux = layer(h, residual, pos, self.inv_freq, self.attn_scale, attn_meta)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+            if hooks is not None:
+                hooks.post_layer(i)
+        h, _ = self.norm(h, residual)
+        out = CausalLMOutput(hidden_states=h.view(B, S, -1))
+        if aux_total is not None:
+            out.aux_loss = aux_total / max(sum(l.is_moe for l in self.layers), 1)
+        W = self.output_weight()
+        if labels is not None:
+            lab = labels.reshape(B, S)
+            if shift_labels:
+                lab = torch.cat([lab[:, 1:], torch.full((B, 1), IGNORE_INDEX, dtype=lab.dtype, device=lab.device)], 1)
+            if num_items is None:
+                num_items = int((lab != IGNORE_INDEX).sum().item())
+            out.num_items = num_items
+            lab = lab.reshape(-1).to(dev, non_blocking=True)
+            loss = Fn.linear_cross_entropy(h, W, lab, num_items=num_items, chunk_rows=self.ce_chunk_rows)
+            if out.aux_loss is not None and cfg.router_aux_loss_coef:
+                loss = loss + cfg.router_aux_loss_coef * out.aux_loss.to(loss.dtype)
+            out.loss = loss
+        if return_logits or labels is None:
+            out.logits = linear(h, W).view(B, S, -1)
+        return out
+
+    # ------------------------------------------------------------------ generation (greedy / sampling)
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens=32, temperature=0.0, top_p=1.0, eos_token_id=None):
+        """Simple full-recompute decoding (no KV cache): adequate for eval samples and smoke checks."""
+        was_training = self.training
+        self.eval()
+        ids = input_ids.reshape(1, -1).clone()
+        for _ in range(max_new_tokens):
+            out = self.forward(ids, return_logits=True)
+            logits = out.logits[0, -1].float()
+            if temperature and temperature > 0:
+                probs = torch.softmax(logits / temperature, -1)
+                if top_p < 1.0:
+                    sp, si = probs.sort(descending=True)
+                    keep = sp.cumsum(0) - sp < top_p
+                    sp = sp * keep
+                    probs = torch.zeros_like(probs).scatter_(0, si, sp / sp.sum())
+                nxt = torch.multinomial(probs, 1)
+            else:
+                nxt = logits.argmax().reshape(1)
+            ids = torch.cat([ids, nxt.reshape(1, 1).to(ids.device)], 1)
+            if eos_token_id is not None and int(nxt) == eos_token_id:
+                break
+        self.train(was_training)
+        return ids
+
+    # ------------------------------------------------------------------ adapters
+    def fused_linears(self):
+        for name, m in self.named_modules():
+            if isinstance(m, FusedLinear):
+                yield name, m
+
+    def refresh_lora_shadows(self):
+        for _, m in self.fused_linears():
+            m.refresh_shadows()
+        for m in self.modules():
+            if hasattr(m, "refresh_expert_shadows"):
+                m.refresh_expert_shadows()
+
+
+def build_attn_meta(position_ids, device) -> Fn.AttnMeta:
+    """cu_seqlens from position-id resets, with a forced boundary at every row start."""
+    p = position_ids.detach().cpu().numpy() if isinstance(position_ids, torch.Tensor) else np.asarray(position_ids)
+    if p.ndim == 1:
+        p = p[None]
+    B, S = p.shape
+    flat = p.reshape(-1)
+    is_start = flat == 0
+    is_start[np.arange(B) * S] = True
+    starts = np.flatnonzero(is_start)
+    cu = np.concatenate([starts, [B * S]]).astype(np.int32)
+    return Fn.AttnMeta(cu, device)

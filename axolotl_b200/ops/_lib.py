@@ -147,6 +147,11 @@ def check_status(device=None) -> None:
         raise KernelTimeoutError(f"axolotl_b200 kernel reported status {code}: {_STATUS_NAMES.get(code, '?')}")
 
 
+launch_count = 0  # native kernel entry points called so far (each launches >= 1 kernel)
+
+
 def check_rc(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")

@@ -1,0 +1,150 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+``python -m axolotl_b200.utils.kernel_bench [gemm|attn|elementwise|all]`` times each hand-written
+kernel with CUDA events (after warm-up, L2 flushed between iterations) and prints achieved
+TFLOP/s or GB/s next to the library kernel for the same shape (cuBLAS via torch.matmul,
+flash-attn 2 where installed) and the measured peaks in ``MEASURED_PEAKS.json`` if present.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    for p in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        if os.path.exists(p):
+            with open(p) as fh:
+                d = json.load(fh)
+            return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+_flush = None
+
+
+def time_cuda(fn, iters=10, warmup=3, flush_l2=True):
+    """Median milliseconds of ``fn`` on the current stream."""
+    global _flush
+    if flush_l2 and _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush_l2:
+            _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(rows):
+    from axolotl_b200.ops.gemm import gemm
+
+    peak, _, how = _peaks()
+    shapes = [
+        ("qkv  8B", 8192, 6144, 4096, False), ("o    8B", 8192, 4096, 4096, False),
+        ("gate_up", 8192, 28672, 4096, False), ("down   ", 8192, 4096, 14336, False),
+        ("dX gu  ", 8192, 4096, 28672, True), ("dX down", 8192, 14336, 4096, True),
+        ("lm_head", 2048, 128256, 4096, False), ("square ", 8192, 8192, 8192, False),
+    ]
+    for name, M, N, K, tb in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if tb else (N, K), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ours = time_cuda(lambda: gemm(a, b, trans_b=tb, out=out))
+        lib = time_cuda(lambda: torch.matmul(a, b if tb else b.t(), out=out))
+        fl = 2.0 * M * N * K / 1e9
+        rows.append(f"gemm {name} M={M} N={N} K={K} transB={int(tb)}: ours {ours:.3f} ms "
+                    f"{fl / ours:.0f} TFLOP/s ({fl / ours / peak:.2f} of {how} peak) | cuBLAS {lib:.3f} ms "
+                    f"{fl / lib:.0f} TFLOP/s | ratio {lib / ours:.2f}")
+
+
+def bench_attn(rows):
+    from axolotl_b200.ops.functional import AttnMeta, flash_varlen
+
+    try:
+        from flash_attn import flash_attn_varlen_func
+    except Exception:  # pragma: no cover
+        flash_attn_varlen_func = None
+    Hq, Hk, D = 32, 8, 128
+    for lens in ([8192], [2048] * 4, [4096, 1024, 3072], [512] * 16):
+        cu = [0]
+        for l in lens:
+            cu.append(cu[-1] + l)
+        T = cu[-1]
+        meta = AttnMeta(cu, "cuda")
+        qkv = (torch.randn(T, (Hq + 2 * Hk) * D, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+        g = torch.randn(T, Hq * D, device="cuda", dtype=torch.bfloat16)
+        fl_f = sum(4.0 * l * l * D * Hq / 2 for l in lens) / 1e9
+        fwd = time_cuda(lambda: flash_varlen(qkv.detach(), meta, Hq, Hk, D))
+        out = flash_varlen(qkv, meta, Hq, Hk, D)
+        bwd = time_cuda(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True))
+        line = (f"attn lens={lens if len(lens) < 5 else str(lens[0]) + 'x' + str(len(lens))}: fwd {fwd:.3f} ms "
+                f"{fl_f / fwd:.0f} TFLOP/s, bwd {bwd:.3f} ms {2.5 * fl_f / bwd:.0f} TFLOP/s")
+        if flash_attn_varlen_func is not None:
+            q = qkv.detach()[:, :Hq * D].reshape(T, Hq, D).contiguous().requires_grad_(True)
+            k = qkv.detach()[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D).contiguous().requires_grad_(True)
+            v = qkv.detach()[:, (Hq + Hk) * D:].reshape(T, Hk, D).contiguous().requires_grad_(True)
+            cu_t = meta.cu_seqlens
+            mx = max(lens)
+            f2 = time_cuda(lambda: flash_attn_varlen_func(q, k, v, cu_t, cu_t, mx, mx, causal=True))
+            o2 = flash_attn_varlen_func(q, k, v, cu_t, cu_t, mx, mx, causal=True)
+            g2 = g.view(T, Hq, D)
+            b2 = time_cuda(lambda: torch.autograd.grad(o2, (q, k, v), g2, retain_graph=True))
+            line += f" | FA2 fwd {f2:.3f} ms bwd {b2:.3f} ms | ratio fwd {f2 / fwd:.2f} bwd {b2 / bwd:.2f}"
+        rows.append(line)
+
+
+def bench_elementwise(rows):
+    from axolotl_b200.ops import functional as Fn
+
+    _, hbm, how = _peaks()
+    T, H, I = 8192, 4096, 14336
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    ms = time_cuda(lambda: Fn.add_rmsnorm(x, r, w, 1e-5))
+    gb = 4 * T * H * 2 / 1e6
+    rows.append(f"add_rmsnorm fwd [{T},{H}]: {ms:.3f} ms {gb / ms:.0f} GB/s ({gb / ms / hbm:.2f} of {how} HBM)")
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    ms = time_cuda(lambda: Fn.glu(gu))
+    gb = 3 * T * I * 2 / 1e6
+    rows.append(f"swiglu fwd [{T},{2 * I}]: {ms:.3f} ms {gb / ms:.0f} GB/s ({gb / ms / hbm:.2f} of {how} HBM)")
+    logits = torch.randn(2048, 128256, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, 128256, (2048,), device="cuda")
+    loss = torch.empty(2048, device="cuda")
+    from axolotl_b200.ops import _lib
+    lib = _lib.cuda_lib()
+    ms = time_cuda(lambda: lib.axb_ce_fwd_bwd(logits.data_ptr(), labels.data_ptr(), loss.data_ptr(), None,
+                                               2048, 128256, 128256, 1.0, -100, 1, _lib.stream_ptr()))
+    gb = 2 * 2048 * 128256 * 2 / 1e6
+    rows.append(f"ce fwd+bwd [2048,128256]: {ms:.3f} ms {gb / ms:.0f} GB/s algorithmic ({gb / ms / hbm:.2f} of {how} HBM)")
+
+
+def main(argv):
+    what = argv[1] if len(argv) > 1 else "all"
+    rows = []
+    if what in ("gemm", "all"):
+        bench_gemm(rows)
+    if what in ("attn", "all"):
+        bench_attn(rows)
+    if what in ("elementwise", "all"):
+        bench_elementwise(rows)
+    from axolotl_b200.ops import _lib
+    _lib.check_status()
+    print("\n".join(rows))
+
+
+if __name__ == "__main__":
+    main(sys.argv)

@@ -51,6 +51,10 @@ def gemm(
     splits: int = 1,
     bn: int | None = None,
 ) -> torch.Tensor:
+    shard = getattr(b, "_axb_shard", None)
+    if shard is not None:
+        return _gemm_allgather(a, b, shard, trans_a=trans_a, trans_b=trans_b, a2=a2, b2=b2, alpha=alpha,
+                               beta=beta, c_in=c_in, out=out, out_dtype=out_dtype, bn=bn)
     M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
     N = b.shape[1] if trans_b else b.shape[0]
     Kb = b.shape[0] if trans_b else b.shape[1]
@@ -124,3 +128,37 @@ def pick_splits(out_tiles: int, k_blocks: int) -> int:
     if out_tiles >= _SM:
         return 1
     return max(1, min(k_blocks, _SM // max(out_tiles, 1)))
+
+
+def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, c_in, out, out_dtype, bn):
+    """GEMM against a row-sharded B whose all-gather is fused into the kernel (see parallel/fsdp.py)."""
+    if trans_a:
+        raise ValueError("the fused all-gather GEMM takes a row-major A")
+    from ..parallel import symm as _symm  # noqa: F401  (registers the kernel signature)
+
+    lib = _lib.cuda_lib()
+    a = _row_major_2d(a)
+    M, Ka = a.shape
+    rows, cols = info.rows, info.cols            # stored (full) B matrix
+    N, K = (cols, rows) if trans_b else (rows, cols)
+    if Ka != K:
+        raise ValueError(f"gemm: inner dimensions differ ({Ka} vs {K})")
+    K2 = 0
+    if a2 is not None:
+        a2, b2 = _row_major_2d(a2), _row_major_2d(b2)
+        K2 = a2.shape[1]
+    out_mode = 0 if out_dtype == torch.bfloat16 else 1
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if bn is None or bn == 64:
+        bn = 256 if N >= 256 else 128
+    ctx = info.ctx
+    rc = lib.axb_gemm_bf16_allgather(
+        a.data_ptr(), a.stride(0), ctx.staging.data_ptr(), int(trans_b), out.data_ptr(), out.stride(0),
+        _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
+        _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
+        K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, int(bn),
+        info.peer_bases_dev.data_ptr(), info.shard_offset, info.shard_bytes, info.world,
+        ctx.ready.data_ptr(), _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "axb_gemm_bf16_allgather")
+    return out

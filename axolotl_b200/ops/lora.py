@@ -101,7 +101,7 @@ def linear(x, W, bias=None):
         return torch.nn.functional.linear(x, W.to(x.dtype), None if bias is None else bias.to(x.dtype))
     shp = x.shape
     y = _LinearFn.apply(x.reshape(-1, shp[-1]).contiguous(), W, bias)
-    return y.view(*shp[:-1], W.shape[0])
+    return y.view(*shp[:-1], y.shape[-1])
 
 
 def lora_linear(x, W, A, B, A16, B16, scaling, blocks, bias=None, dropout_p=0.0, training=False):
@@ -119,6 +119,6 @@ def lora_linear(x, W, A, B, A16, B16, scaling, blocks, bias=None, dropout_p=0.0,
         else:
             y = torch.nn.functional.linear(x2, W.to(x2.dtype), None if bias is None else bias.to(x2.dtype))
             y = y + scaling * ((xd @ A.to(x2.dtype).t()) @ B.to(x2.dtype).t())
-        return y.view(*shp[:-1], W.shape[0])
+        return y.view(*shp[:-1], y.shape[-1])
     y = _LoRALinearFn.apply(x2.contiguous(), W, A, B, A16, B16, float(scaling), blocks, bias)
-    return y.view(*shp[:-1], W.shape[0])
+    return y.view(*shp[:-1], y.shape[-1])

@@ -1,0 +1,166 @@
+"""Parallel runtime: glues the mesh, the sharded weights and the fused gradient/optimizer kernel
+to the trainer. Two communication back ends share one interface:
+
+* ``fused`` (CUDA, default): symmetric-memory buffers, weights gathered inside the GEMM kernel,
+  gradients reduced + clipped + AdamW-updated + re-published by ONE kernel (``axb_rs_adamw_ag``).
+* ``collective`` (any device; gloo on CPU, NCCL on GPU): weights replicated, flat gradient
+  all-reduced with ``torch.distributed``; used for host-side plumbing tests and as a baseline.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..utils.logging import get_logger
+from .mesh import DeviceMesh, MeshSpec
+
+LOG = get_logger(__name__)
+
+
+class ParallelRuntime:
+    def __init__(self, mesh: DeviceMesh, device, backend="fused"):
+        self.mesh, self.device, self.backend = mesh, torch.device(device), backend
+        self.rank = dist.get_rank()
+        self.world_size = dist.get_world_size()
+        self.dp_group = mesh.group("ep", "dp_replicate", "dp_shard") if mesh.size("ep", "dp_replicate", "dp_shard") > 1 else None
+        self.dp_size = mesh.size("ep", "dp_replicate", "dp_shard")
+        self.shard_group = mesh.group("dp_shard")
+        self.shard_size = mesh.size("dp_shard")
+        self.fsdp = None
+        self.sync = None
+        self.opt = None
+        self._symm = []
+        self.cp = None
+        self.tp = None
+        self.ep = None
+
+    # ------------------------------------------------------------------ setup
+    def shard_model(self, model):
+        if self.backend != "fused" or self.shard_size <= 1:
+            return
+        from .fsdp import FSDPContext
+
+        self.fsdp = FSDPContext(self.device, self.shard_group, self.shard_size, self.mesh.coord("dp_shard"))
+        self.fsdp.shard_model(model)
+
+    def symmetric_alloc(self, numel, dtype):
+        """Allocator handed to FlatAdamW so gradients / masters / shadows live in peer-mapped memory."""
+        from .symm import SymmBuffer
+
+        buf = SymmBuffer(numel, dtype, self.device, self.dp_group, use_multicast=os.environ.get("AXB_NO_MULTIMEM") != "1")
+        self._symm.append(buf)
+        t = buf.tensor
+        t._axb_symm = buf
+        return t
+
+    def optimizer_alloc(self):
+        if self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
+            return self.symmetric_alloc
+        return None
+
+    def attach_optimizer(self, opt):
+        self.opt = opt
+        if self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
+            from .symm import PeerSync
+
+            self.sync = PeerSync(self.device, self.dp_group)
+            for g in opt.groups:
+                if getattr(g["grad"], "_axb_symm", None) is None:
+                    raise RuntimeError("FlatAdamW must be built with alloc=parallel.optimizer_alloc() for the fused backend")
+            self._scratch = self.symmetric_alloc(64, torch.float32)
+            self._gnorm = torch.zeros(1, dtype=torch.float32, device=self.device)
+            dist.barrier(self.dp_group)
+
+    # ------------------------------------------------------------------ trainer interface
+    def before_micro_batch(self, last):
+        pass
+
+    def after_optimizer_step(self):
+        pass
+
+    def barrier(self):
+        if self.world_size > 1:
+            dist.barrier()
+
+    def mean_scalar(self, v):
+        t = torch.tensor([float(v)], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t)
+        return float(t.item()) / self.world_size
+
+    def sum_scalar(self, v):
+        t = torch.tensor([float(v)], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t)
+        r = float(t.item())
+        return int(r) if isinstance(v, int) else r
+
+    def optimizer_step(self, opt, lr):
+        """Gradient synchronisation + clipping + optimizer update. Returns the squared global
+        gradient norm (device scalar) or None."""
+        if self.dp_size <= 1:
+            return opt.step(lr=lr)
+        if self.backend == "fused" and self.sync is not None:
+            return self._fused_step(opt, lr)
+        # collective back end: average the flat gradients, then a local fused AdamW
+        for g in opt.flat_grads():
+            dist.all_reduce(g, group=self.dp_group)
+        opt.grad_scale = 1.0 / self.dp_size
+        return opt.step(lr=lr)
+
+    def _fused_step(self, opt, lr):
+        lib = _lib.cuda_lib()
+        from .symm import WAIT_BUDGET_NS
+
+        opt._fold_autograd_grads()
+        opt.step_count += 1
+        bc1 = 1.0 - opt.betas[0] ** opt.step_count
+        bc2 = 1.0 - opt.betas[1] ** opt.step_count
+        rank = dist.get_rank(self.dp_group)
+        for gi, g in enumerate(opt.groups):
+            gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
+            epoch = self.sync.next_epoch(0, 3)
+            rc = lib.axb_rs_adamw_ag(
+                gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
+                gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
+                g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.dp_size,
+                epoch, lr * g["lr_scale"], opt.betas[0], opt.betas[1], opt.eps, g["weight_decay"], bc1, bc2,
+                float(opt.max_grad_norm or 0.0) if len(opt.groups) == 1 else 0.0, 1.0 / self.dp_size,
+                self._gnorm.data_ptr(), _lib.status_word(self.device).data_ptr(), WAIT_BUDGET_NS, _lib.stream_ptr())
+            _lib.check_rc(rc, "rs_adamw_ag")
+        opt.skip_zero_grad_once = True  # the kernel already cleared the gradient buffers
+        return self._gnorm
+
+
+def init_distributed(backend=None, timeout_s=None):
+    """Process-group bring-up from the torchrun environment (RANK / WORLD_SIZE / MASTER_*)."""
+    import datetime
+
+    if dist.is_initialized():
+        return
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    t = timeout_s or int(os.environ.get("AXOLOTL_NCCL_TIMEOUT", "1800"))
+    kw = {}
+    if backend == "nccl":
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        kw["device_id"] = dev
+    dist.init_process_group(backend, timeout=datetime.timedelta(seconds=t), **kw)
+
+
+def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, backend=None):
+    """Creates the mesh + runtime for an already initialised process group and shards the model."""
+    world = dist.get_world_size()
+    spec = MeshSpec.from_cfg(world, tensor_parallel_size=tp, context_parallel_size=cp, dp_shard_size=dp_shard,
+                             dp_replicate_size=dp_replicate, expert_parallel_size=ep)
+    device = torch.device(device)
+    if backend is None:
+        backend = os.environ.get("AXB_COMM", "fused" if device.type == "cuda" else "collective")
+    mesh = DeviceMesh(spec, dist.get_rank())
+    rt = ParallelRuntime(mesh, device, backend)
+    rt.shard_model(model)
+    return rt

@@ -51,11 +51,13 @@ def build_param_groups(named_params, *, weight_decay=0.0, embedding_lr=None, emb
 
 
 class FlatAdamW:
-    def __init__(self, groups, lr=1e-4, betas=(0.9, 0.999), eps=1e-8, max_grad_norm=0.0):
+    def __init__(self, groups, lr=1e-4, betas=(0.9, 0.999), eps=1e-8, max_grad_norm=0.0, alloc=None,
+                 pad_multiple=8):
         self.lr, self.betas, self.eps, self.max_grad_norm = lr, betas, eps, max_grad_norm
         self.step_count = 0
         self.groups = []
         self.grad_scale = 1.0
+        self.skip_zero_grad_once = False
         for g in groups:
             params = [(n, p) for n, p in g["params"] if p.requires_grad]
             if not params:
@@ -67,10 +69,13 @@ class FlatAdamW:
             for _, p in params:
                 offs.append(off)
                 off += (p.numel() + 7) // 8 * 8
-            total = off
-            master = torch.zeros(total, dtype=torch.float32, device=dev)
-            grad = torch.zeros(total, dtype=torch.float32, device=dev)
-            shadow = torch.zeros(total, dtype=torch.bfloat16, device=dev)
+            total = (off + pad_multiple - 1) // pad_multiple * pad_multiple
+            if alloc is not None:  # e.g. peer-mapped symmetric memory for the fused multi-GPU step
+                master, grad, shadow = alloc(total, torch.float32), alloc(total, torch.float32), alloc(total, torch.bfloat16)
+            else:
+                master = torch.zeros(total, dtype=torch.float32, device=dev)
+                grad = torch.zeros(total, dtype=torch.float32, device=dev)
+                shadow = torch.zeros(total, dtype=torch.bfloat16, device=dev)
             entries = []
             for (n, p), o in zip(params, offs):
                 k = p.numel()
@@ -112,8 +117,11 @@ class FlatAdamW:
                     m.lora_A16, m.lora_B16 = a, b
 
     def zero_grad(self):
+        skip = self.skip_zero_grad_once
+        self.skip_zero_grad_once = False
         for g in self.groups:
-            g["grad"].zero_()
+            if not skip:
+                g["grad"].zero_()
             for _, p, _, _ in g["entries"]:
                 if p.dtype != torch.float32:
                     p.grad = None

@@ -148,10 +148,10 @@ class Trainer:
             self.tokens["total"] += b["n_tokens"]
         self.tokens["trainable"] += n_items
         lr = self.args.learning_rate * self.lr_lambda(self.global_step)
-        gnorm_sq = None
         if par is not None:
-            gnorm_sq = par.sync_gradients(opt)
-        gnorm_sq = opt.step(lr=lr, gnorm_sq=gnorm_sq)
+            gnorm_sq = par.optimizer_step(opt, lr)
+        else:
+            gnorm_sq = opt.step(lr=lr)
         opt.zero_grad()
         if par is not None:
             par.after_optimizer_step()

@@ -177,7 +177,8 @@ def main():
         from axolotl_b200.parallel import build_parallel
 
         parallel = build_parallel(model, dp_shard=world, device=dev)
-    opt = FlatAdamW(build_param_groups(model.named_parameters(), weight_decay=0.0), lr=2e-4, max_grad_norm=1.0)
+    opt = FlatAdamW(build_param_groups(model.named_parameters(), weight_decay=0.0), lr=2e-4, max_grad_norm=1.0,
+                    alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1))
     opt.bind_model_shadows(model)
     if parallel is not None:
         parallel.attach_optimizer(opt)

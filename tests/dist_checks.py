@@ -1,0 +1,194 @@
+"""Multi-rank checks, run as ``torchrun --nproc-per-node N tests/dist_checks.py [cpu]``.
+Every rank asserts; a failure on any rank makes the launcher exit non-zero."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def check_gather_gemm(rt, dev, rank, world):
+    from axolotl_b200.models.layers import FusedLinear
+    from axolotl_b200.ops.gemm import gemm
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.parallel.fsdp import FSDPContext
+
+    torch.manual_seed(0)
+    N, K, M = 1024 * world if world > 2 else 2048, 512, 640
+    mods = [FusedLinear(K, [N], ["a"], device=dev), FusedLinear(K * 2, [N // 2], ["b"], device=dev)]
+    full = []
+    for m in mods:
+        torch.nn.init.normal_(m.weight, std=0.05)
+        m.weight.requires_grad_(False)
+        full.append(m.weight.detach().clone())
+
+    class Holder:
+        def fused_linears(self):
+            return [(str(i), m) for i, m in enumerate(mods)]
+
+    ctx = FSDPContext(dev, dist.group.WORLD, world, rank)
+    assert ctx.shard_model(Holder()) == 2
+    dist.barrier()
+    for m, W in zip(mods, full):
+        Kk = W.shape[1]
+        x = torch.randn(M, Kk, device=dev, dtype=torch.bfloat16)
+        r = 16
+        xa = torch.randn(M, r, device=dev, dtype=torch.bfloat16)
+        Bc = torch.randn(W.shape[0], r, device=dev, dtype=torch.bfloat16) * 0.1
+        y = gemm(x, m.weight, a2=xa, b2=Bc)
+        ref = gemm(x, W, a2=xa, b2=Bc)
+        _lib.check_status()
+        assert rel_err(y, ref) < 1e-3, ("fwd", rel_err(y, ref))
+        dy = torch.randn(M, W.shape[0], device=dev, dtype=torch.bfloat16)
+        dx = gemm(dy, m.weight, trans_b=True)
+        refx = gemm(dy, W, trans_b=True)
+        _lib.check_status()
+        assert rel_err(dx, refx) < 1e-3, ("dx", rel_err(dx, refx))
+        g = ctx.gather_full_weight(m)
+        assert torch.equal(g, W)
+    dist.barrier()
+    if rank == 0:
+        print("gather-gemm ok")
+
+
+def check_fused_optimizer(dev, rank, world):
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.parallel.mesh import DeviceMesh, MeshSpec
+    from axolotl_b200.parallel.runtime import ParallelRuntime
+    from axolotl_b200.train.optimizer import FlatAdamW
+
+    for use_mc in (True, False):
+        if not use_mc:
+            os.environ["AXB_NO_MULTIMEM"] = "1"
+        torch.manual_seed(1)
+        p = torch.nn.Parameter(torch.randn(3000, 7, device=dev))
+        q = torch.nn.Parameter(torch.randn(515, device=dev))
+        ref_p, ref_q = p.detach().clone(), q.detach().clone()
+        rt = ParallelRuntime(DeviceMesh(MeshSpec.from_cfg(world), rank), dev, "fused")
+        opt = FlatAdamW([{"name": "g", "params": [("p", p), ("q", q)], "lr_scale": 1.0, "weight_decay": 0.1}],
+                        lr=1e-2, max_grad_norm=1.0, alloc=rt.optimizer_alloc(), pad_multiple=8 * world)
+        rt.attach_optimizer(opt)
+        ro = torch.optim.AdamW([torch.nn.Parameter(ref_p), torch.nn.Parameter(ref_q)], lr=1e-2, weight_decay=0.1)
+        rp, rq = ro.param_groups[0]["params"]
+        for step in range(3):
+            gen = torch.Generator(device="cpu").manual_seed(100 + step)
+            gs = [(torch.randn(3000, 7, generator=gen), torch.randn(515, generator=gen)) for _ in range(world)]
+            p._axb_grad.copy_(gs[rank][0].to(dev))
+            q._axb_grad.copy_(gs[rank][1].to(dev))
+            gn = rt.optimizer_step(opt, 1e-2)
+            opt.zero_grad()
+            rp.grad = (sum(g[0] for g in gs) / world).to(dev)
+            rq.grad = (sum(g[1] for g in gs) / world).to(dev)
+            tot = torch.nn.utils.clip_grad_norm_([rp, rq], 1.0)
+            ro.step()
+            _lib.check_status()
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = float(gn.sqrt().item()) / world
+            assert abs(got - float(tot)) < 1e-3 * float(tot), (got, float(tot))
+            assert rel_err(p.detach(), rp.detach()) < 1e-5, rel_err(p.detach(), rp.detach())
+            assert rel_err(q.detach(), rq.detach()) < 1e-5
+            assert float(p._axb_grad.abs().max()) == 0.0
+            sh = opt.shadow_of(p)
+            assert rel_err(sh, rp.detach()) < 5e-3
+        dist.barrier()
+        if rank == 0:
+            print(f"fused rs+adamw+ag ok (multimem={'on' if use_mc else 'off'})")
+
+
+def check_training_equivalence(dev, rank, world, backend):
+    """A tiny LoRA model trained data-parallel must follow the single-process run on the
+    concatenated batch (same seed, deterministic data)."""
+    from axolotl_b200.data.collator import PackedCollator
+    from axolotl_b200.data.synthetic import synthetic_varlen
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import ALL_LINEAR, LoraSpec, inject_lora
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.parallel.runtime import build_parallel
+    from axolotl_b200.train.optimizer import FlatAdamW, build_param_groups, make_lr_lambda
+    from axolotl_b200.train.trainer import TrainArgs, Trainer
+
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    cfg = preset("tiny-llama", num_hidden_layers=2, vocab_size=2048, hidden_size=256, intermediate_size=512,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+    ds = synthetic_varlen(8 * world, 160, 160, 3, 2048, 0.25, seed=3)  # equal lengths: mean of rank means == global mean
+    coll = PackedCollator(pad_to_multiple_of=64)
+
+    def run(parallel_on):
+        torch.manual_seed(0)
+        model = CausalLM(cfg, dtype=dtype, device=dev).init_weights(0)
+        inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules=list(ALL_LINEAR)))
+        for _, m in model.fused_linears():   # make B non-zero so every gradient path is exercised
+            with torch.no_grad():
+                g = torch.Generator(device="cpu").manual_seed(7)
+                m.lora_B.copy_((torch.randn(m.lora_B.shape, generator=g) * 0.02).to(dev) * (m.lora_B.new_ones(m.lora_B.shape)))
+                mask = torch.zeros_like(m.lora_B)
+                for (r0, rows, c0, r) in m.lora_blocks:
+                    mask[r0:r0 + rows, c0:c0 + r] = 1
+                m.lora_B.mul_(mask)
+        par = build_parallel(model, device=dev, dp_shard=world, backend=backend) if parallel_on else None
+        opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0,
+                        alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world)
+        opt.bind_model_shadows(model)
+        if par is not None:
+            par.attach_optimizer(opt)
+        tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=3, learning_rate=1e-3),
+                     lambda e: [], parallel=par, device=dev)
+        losses = []
+        for step in range(3):
+            if parallel_on:
+                mb = [coll([[ds[(step * world + rank) * 2 + j] for j in range(2)]])]
+            else:
+                mb = [coll([[ds[(step * world + r) * 2 + j] for j in range(2)]]) for r in range(world)]
+            losses.append(float(tr.training_step(mb).item()))
+        flat = torch.cat([g["master"][: sum(e[3] for e in g["entries"])].detach().float().cpu() for g in opt.groups])
+        return losses, flat
+
+    l_par, w_par = run(True)
+    l_ref, w_ref = run(False)
+    # every rank sees the same number of trainable tokens, so averaging the ranks' gradients
+    # equals the single-process gradient over the concatenated batch.
+    t = torch.tensor(l_par, dtype=torch.float64, device=dev)
+    dist.all_reduce(t)
+    mean_par = (t / world).tolist()
+    assert all(abs(a - b) < 0.05 * abs(b) for a, b in zip(mean_par, l_ref)), (mean_par, l_ref)
+    tol = 2e-2 if dev.type == "cuda" else 1e-4
+    assert rel_err(w_par, w_ref) < tol, rel_err(w_par, w_ref)
+    # ranks must agree bit-for-bit on the parameters
+    chk = w_par.to(dev).double().sum().reshape(1)
+    lst = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(lst, chk)
+    assert all(float(x) == float(lst[0]) for x in lst), [float(x) for x in lst]
+    if rank == 0:
+        print(f"dp training equivalence ok ({backend}): {mean_par} vs {l_ref}")
+
+
+def main():
+    cpu = len(sys.argv) > 1 and sys.argv[1] == "cpu"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if cpu:
+        dist.init_process_group("gloo")
+        dev = torch.device("cpu")
+        check_training_equivalence(dev, rank, world, "collective")
+    else:
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", device_id=dev)
+        check_gather_gemm(None, dev, rank, world)
+        check_fused_optimizer(dev, rank, world)
+        check_training_equivalence(dev, rank, world, "fused")
+        check_training_equivalence(dev, rank, world, "collective")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

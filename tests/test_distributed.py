@@ -1,0 +1,34 @@
+"""Launches tests/dist_checks.py under torchrun: gloo ranks on CPU here, NCCL ranks on GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc, extra, port):
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = env.get("NCCL_NVLS_ENABLE", "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dist_checks.py"), *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
+    return res.stdout
+
+
+def test_data_parallel_gloo_world2():
+    out = _run(2, ["cpu"], 29611)
+    assert "dp training equivalence ok" in out
+
+
+@pytest.mark.gpu
+def test_fused_multi_gpu():
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    out = _run(2, [], 29612)
+    assert "gather-gemm ok" in out and "fused rs+adamw+ag ok" in out

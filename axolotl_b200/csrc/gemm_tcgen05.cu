@@ -10,7 +10,14 @@
 // The second operand pair is the K-extension used to fuse the LoRA low-rank update: the product
 // (X.A^T) . B^T is simply one more K block accumulated into the same TMEM tile.
 //
-// Replaces the cuBLAS calls behind the reference's LoRA kernels (src/axolotl/kernels/lora.py:226-280).
+// Fused all-gather: a launch may carry `g_ctas` extra trailing CTAs that do no MMA work at all.
+// They pull the row shards of the NEXT weight of the layer schedule from the peers' memory over
+// NVLink (cp.async.bulk peer -> shared -> local staging buffer, 24 x 8 KB in flight per CTA)
+// while the other CTAs run this GEMM from the staging buffer the previous launch filled. Stream
+// order is the only synchronisation: no flags, no polling, the MMA pipeline is never throttled.
+//
+// Replaces the cuBLAS calls behind the reference's LoRA kernels (src/axolotl/kernels/lora.py:226-280)
+// and, with the prefetch CTAs, the NCCL all-gather of its FSDP2 units.
 #include "axb_common.cuh"
 
 namespace {
@@ -28,22 +35,68 @@ struct GemmParams {
   float alpha, beta;
   int out_mode;  // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add (split-K)
   int splits;
+  int group_m;  // m tiles per rasterisation band (the A rows of a band stay L2 resident)
   int* status;
-  // fused all-gather (GATHER kernels only): the B operand is row-sharded over `g_world` GPUs.
-  // Every CTA's gather warp copies 8 KB chunks of the peers' shards into the local staging
-  // buffer the B tensor map points at and counts finished chunks per 256-row block in g_ready.
-  const unsigned long long* g_peer_bases;  // [g_world] base address of each rank's shard arena
-  unsigned long long g_shard_offset;       // byte offset of this weight's shard inside the arena
-  unsigned long long g_shard_bytes;        // bytes per rank ( = rows/world * row_bytes )
-  unsigned long long g_total_bytes;        // rows * row_bytes
-  unsigned char* g_dst;                    // local staging buffer [rows, row_bytes]
-  unsigned int* g_ready;                   // [rows/256] finished-chunk counters (zeroed by host)
-  unsigned int g_chunks_per_block;         // 256 * row_bytes / 8192
+  // prefetch of a row-sharded matrix by the trailing g_ctas CTAs (0 = none)
+  int g_ctas;
   int g_world;
+  const unsigned long long* g_peer_bases;  // DEVICE array [g_world]: arena address of every rank
+  unsigned long long g_shard_offset;       // byte offset of the weight's shard inside an arena
+  unsigned long long g_shard_bytes;        // bytes per rank
+  unsigned long long g_total_bytes;        // g_world * g_shard_bytes (multiple of 8 KB)
+  unsigned char* g_dst;                    // local staging buffer
 };
 
 constexpr int GATHER_CHUNK = 8192;
-constexpr int GATHER_SLOTS = 4;
+constexpr int GATHER_SLOTS = 4;   // per warp
+constexpr int GATHER_WARPS = 6;   // every warp of a gather CTA drives its own slot ring
+
+// Body of a gather CTA: warp w (lane 0) copies chunks (cta*6 + w) + i * (n_ctas*6) through its
+// private ring of 4 x 8 KB shared-memory slots. Loads run 3 chunks ahead of the stores.
+__device__ __forceinline__ void gather_cta_body(const GemmParams& p, int gather_cta, int n_ctas,
+                                                uint8_t* smem, uint64_t* bars) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < GATHER_WARPS && lane == 0)
+    for (int s = 0; s < GATHER_SLOTS; ++s) mbar_init(&bars[warp * GATHER_SLOTS + s], 1);
+  mbar_fence_init();
+  __syncthreads();
+  if (warp >= GATHER_WARPS || lane != 0) return;
+  uint8_t* slots = smem + warp * GATHER_SLOTS * GATHER_CHUNK;
+  uint64_t* bar = bars + warp * GATHER_SLOTS;
+  const unsigned long long n_chunks = p.g_total_bytes / GATHER_CHUNK;
+  const unsigned long long stride = (unsigned long long)n_ctas * GATHER_WARPS;
+  const unsigned long long c0 = (unsigned long long)gather_cta * GATHER_WARPS + warp;
+  const long long n_mine = c0 < n_chunks ? (long long)((n_chunks - c0 + stride - 1) / stride) : 0;
+  auto issue_load = [&](long long i) {
+    const unsigned long long byte = (c0 + i * stride) * GATHER_CHUNK;
+    const unsigned long long owner = byte / p.g_shard_bytes;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.g_peer_bases[owner]) +
+                               p.g_shard_offset + (byte - owner * p.g_shard_bytes);
+    const int slot = (int)(i % GATHER_SLOTS);
+    mbar_expect_tx(&bar[slot], GATHER_CHUNK);
+    bulk_load(slots + slot * GATHER_CHUNK, src, GATHER_CHUNK, &bar[slot]);
+  };
+  long long issued = 0;
+  for (; issued < GATHER_SLOTS - 1 && issued < n_mine; ++issued) issue_load(issued);
+  for (long long i = 0; i < n_mine; ++i) {
+    const int slot = (int)(i % GATHER_SLOTS);
+    if (!mbar_wait(&bar[slot], (uint32_t)((i / GATHER_SLOTS) & 1), p.status, AXB_TIMEOUT_PEER_FLAG))
+      break;
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                     p.g_dst + (c0 + i * stride) * GATHER_CHUNK),
+                 "r"(smem_u32(slots + slot * GATHER_CHUNK)), "r"(GATHER_CHUNK)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (issued < n_mine) {
+      // the slot of chunk `issued` was last read by the store of chunk i-1: all but the newest
+      // store group must have finished reading shared memory
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue_load(issued);
+      ++issued;
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 
 template <int BN>
 struct Cfg {
@@ -55,23 +108,12 @@ struct Cfg {
                                     : (kSmemBudget - 1024) / STAGE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-  // gather variant: one stage less is never needed; the bounce slots live after the barriers
-  static constexpr int GATHER_STAGES =
-      (kSmemBudget - 1024 - GATHER_SLOTS * GATHER_CHUNK) / STAGE_BYTES > 8
-          ? 8
-          : (kSmemBudget - 1024 - GATHER_SLOTS * GATHER_CHUNK) / STAGE_BYTES;
 };
 
 __device__ __forceinline__ void decode_tile(int tile, int num_m, int num_n, int splits, int& m_blk,
-                                            int& n_blk, int& split, bool n_major = false) {
+                                            int& n_blk, int& split, int GROUP_M) {
   split = tile % splits;
   tile /= splits;
-  if (n_major) {  // weights are consumed block by block in the order the gather warps fetch them
-    n_blk = tile / num_m;
-    m_blk = tile - n_blk * num_m;
-    return;
-  }
-  constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
@@ -81,50 +123,33 @@ __device__ __forceinline__ void decode_tile(int tile, int num_m, int num_n, int 
   n_blk = in_group / gsz;
 }
 
-// bounded poll of a chunk counter written by other CTAs' gather warps
-__device__ __forceinline__ bool wait_block_ready(const unsigned int* ctr, unsigned int target,
-                                                 int* status) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-  if (v >= target) return true;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-    if (v >= target) return true;
-    if ((++spins & 0xFF) == 0 && global_timer_ns() - t0 > AXB_WAIT_BUDGET_NS) {
-      if (status) atomicCAS(status, 0, AXB_TIMEOUT_PEER_FLAG);
-      return false;
-    }
-    __nanosleep(64);
-  }
-}
-
-template <int BN, bool A_MN, bool B_MN, bool GATHER>
-__global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                              const __grid_constant__ CUtensorMap tmB,
                              const __grid_constant__ CUtensorMap tmA2,
                              const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   using C = Cfg<BN>;
-  constexpr int STAGES = GATHER ? C::GATHER_STAGES : C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * C::A_BYTES;
-  uint8_t* sBounce = smem + STAGES * C::STAGE_BYTES;  // GATHER only: 4 x 8 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES +
-                                               (GATHER ? GATHER_SLOTS * GATHER_CHUNK : 0));
+  uint8_t* sB = smem + C::STAGES * C::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + STAGES;
-  uint64_t* tfull_bar = bars + 2 * STAGES;
-  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
-  uint64_t* bounce_bar = bars + 2 * STAGES + 4;  // [GATHER_SLOTS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + GATHER_SLOTS);
+  uint64_t* empty_bar = bars + C::STAGES;
+  uint64_t* tfull_bar = bars + 2 * C::STAGES;
+  uint64_t* tempty_bar = bars + 2 * C::STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  const int n_workers = (int)gridDim.x - p.g_ctas;  // CTAs that run GEMM tiles
+  if ((int)blockIdx.x >= n_workers) {
+    gather_cta_body(p, (int)blockIdx.x - n_workers, p.g_ctas, smem, bars);
+    return;
+  }
 
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
@@ -134,12 +159,10 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
   const int total_tiles = num_m * num_n * p.splits;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    if (GATHER)
-      for (int s = 0; s < GATHER_SLOTS; ++s) mbar_init(&bounce_bar[s], 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
       mbar_init(&tempty_bar[s], 4);  // one arrival per epilogue warp
@@ -163,10 +186,9 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      unsigned long long seen[2] = {0ull, 0ull};  // 256-row blocks already seen complete
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += n_workers) {
         int m_blk, n_blk, split;
-        decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, GATHER && !B_MN);
+        decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, p.group_m);
         const int kb0 = (int)((long long)nk_total * split / p.splits);
         const int kb1 = (int)((long long)nk_total * (split + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -174,23 +196,8 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
             ok = false;
             break;
           }
-          const bool ext = kb >= nk_main;
-          if (GATHER && !ext) {
-            // rows of the (row-sharded) B operand this k block / tile reads, in 256-row blocks
-            const int blk_lo = B_MN ? (kb * BK) >> 8 : (n_blk * BN) >> 8;
-            const int blk_hi = B_MN ? (kb * BK + BK - 1) >> 8 : (n_blk * BN + BN - 1) >> 8;
-            const int last_blk = (int)(p.g_total_bytes / ((unsigned long long)p.g_chunks_per_block * GATHER_CHUNK)) - 1;
-            for (int b = blk_lo; b <= min(blk_hi, last_blk) && ok; ++b) {
-              const bool known = b < 128 && ((seen[b >> 6] >> (b & 63)) & 1ull);
-              if (!known) {
-                if (!wait_block_ready(p.g_ready + b, p.g_chunks_per_block, p.status)) ok = false;
-                else if (b < 128) seen[b >> 6] |= 1ull << (b & 63);
-              }
-            }
-            if (!ok) break;
-            asm volatile("fence.proxy.async;" ::: "memory");
-          }
           mbar_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+          const bool ext = kb >= nk_main;
           const CUtensorMap* ma = ext ? &tmA2 : &tmA;
           const CUtensorMap* mb = ext ? &tmB2 : &tmB;
           const int k0 = (ext ? kb - nk_main : kb) * BK;
@@ -210,7 +217,7 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
             for (int c = 0; c < BN / 64; ++c)
               tma_load_2d(b_dst + c * 8192, mb, &full_bar[stage], n_blk * BN + c * 64, k0);
           }
-          if (++stage == STAGES) {
+          if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
           }
@@ -225,9 +232,9 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += n_workers, ++it) {
         int m_blk, n_blk, split;
-        decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, GATHER && !B_MN);
+        decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, p.group_m);
         const int kb0 = (int)((long long)nk_total * split / p.splits);
         const int kb1 = (int)((long long)nk_total * (split + 1) / p.splits);
         const int acc = it & 1;
@@ -255,7 +262,7 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
             umma_f16(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // releases the smem stage when these MMAs retire
-          if (++stage == STAGES) {
+          if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
           }
@@ -264,69 +271,14 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
         umma_commit(&tfull_bar[acc]);
       }
     }
-  } else if (GATHER && warp == 6) {
-    // ------------------------------------------------------------ gather warp (all-gather of B)
-    if (lane == 0) {
-      const unsigned long long n_chunks = p.g_total_bytes / GATHER_CHUNK;
-      const unsigned long long block_bytes = (unsigned long long)p.g_chunks_per_block * GATHER_CHUNK;
-      auto src_of = [&](unsigned long long c) -> const unsigned char* {
-        const unsigned long long byte = c * GATHER_CHUNK;
-        const unsigned long long owner = byte / p.g_shard_bytes;
-        return reinterpret_cast<const unsigned char*>(p.g_peer_bases[owner]) + p.g_shard_offset +
-               (byte - owner * p.g_shard_bytes);
-      };
-      auto issue_load = [&](unsigned long long c, int slot) {
-        mbar_expect_tx(&bounce_bar[slot], GATHER_CHUNK);
-        bulk_load(sBounce + slot * GATHER_CHUNK, src_of(c), GATHER_CHUNK, &bounce_bar[slot]);
-      };
-      auto signal_done = [&](unsigned long long c) {
-        asm volatile("fence.proxy.async;" ::: "memory");
-        unsigned int* ctr = p.g_ready + (c * GATHER_CHUNK) / block_bytes;
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
-      };
-      // prologue: up to GATHER_SLOTS loads in flight
-      unsigned long long c_issue = blockIdx.x;
-      int n_issued = 0;
-      for (; n_issued < GATHER_SLOTS && c_issue < n_chunks; ++n_issued, c_issue += gridDim.x)
-        issue_load(c_issue, n_issued);
-      unsigned long long prev = ~0ull;
-      int i = 0;
-      bool ok = true;
-      for (unsigned long long c = blockIdx.x; c < n_chunks && ok; c += gridDim.x, ++i) {
-        const int slot = i % GATHER_SLOTS;
-        const uint32_t ph = (i / GATHER_SLOTS) & 1;
-        if (!mbar_wait(&bounce_bar[slot], ph, p.status, AXB_TIMEOUT_PEER_FLAG)) {
-          ok = false;
-          break;
-        }
-        // smem -> local staging buffer
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
-                         p.g_dst + c * GATHER_CHUNK),
-                     "r"(smem_u32(sBounce + slot * GATHER_CHUNK)), "r"(GATHER_CHUNK)
-                     : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        if (prev != ~0ull) {  // everything but the newest store is globally complete
-          asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
-          signal_done(prev);
-        }
-        prev = c;
-        if (c_issue < n_chunks) {  // refill this slot once the store has read it
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          issue_load(c_issue, slot);
-          c_issue += gridDim.x;
-        }
-      }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      if (ok && prev != ~0ull) signal_done(prev);
-    }
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += n_workers, ++it) {
       int m_blk, n_blk, split;
-      decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, GATHER && !B_MN);
+      decode_tile(tile, num_m, num_n, p.splits, m_blk, n_blk, split, p.group_m);
       const int kb0 = (int)((long long)nk_total * split / p.splits);
       const int kb1 = (int)((long long)nk_total * (split + 1) / p.splits);
       const int acc = it & 1;
@@ -421,27 +373,25 @@ __global__ void __launch_bounds__(GATHER ? kThreads + 32 : kThreads, 1)
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool GATHER>
+template <int BN, bool A_MN, bool B_MN>
 int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
                 const CUtensorMap& tB2, const GemmParams& p, int sm_count, cudaStream_t stream) {
   using C = Cfg<BN>;
-  constexpr int smem_bytes =
-      GATHER ? C::GATHER_STAGES * C::STAGE_BYTES + GATHER_SLOTS * GATHER_CHUNK + 1024 + 256
-             : C::SMEM_BYTES;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, GATHER>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n * p.splits;
-  // gather kernels always launch one CTA per SM: every CTA carries a share of the all-gather
-  const int grid = GATHER ? sm_count : (tiles < sm_count ? tiles : sm_count);
-  kern<<<grid, GATHER ? kThreads + 32 : kThreads, smem_bytes, stream>>>(tA, tB, tA2, tB2, p);
+  int workers = sm_count - p.g_ctas;
+  if (tiles < workers) workers = tiles;
+  const int grid = workers + p.g_ctas;
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tA, tB, tA2, tB2, p);
   return (int)cudaGetLastError();
 }
 
@@ -449,41 +399,55 @@ template <int BN>
 int dispatch_major(int a_mn, int b_mn, const CUtensorMap& tA, const CUtensorMap& tB,
                    const CUtensorMap& tA2, const CUtensorMap& tB2, const GemmParams& p,
                    int sm_count, cudaStream_t stream) {
-  if (!a_mn && !b_mn)
-    return launch_gemm<BN, false, false, false>(tA, tB, tA2, tB2, p, sm_count, stream);
-  if (!a_mn && b_mn)
-    return launch_gemm<BN, false, true, false>(tA, tB, tA2, tB2, p, sm_count, stream);
-  if (a_mn && !b_mn)
-    return launch_gemm<BN, true, false, false>(tA, tB, tA2, tB2, p, sm_count, stream);
-  return launch_gemm<BN, true, true, false>(tA, tB, tA2, tB2, p, sm_count, stream);
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(tA, tB, tA2, tB2, p, sm_count, stream);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(tA, tB, tA2, tB2, p, sm_count, stream);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(tA, tB, tA2, tB2, p, sm_count, stream);
+  return launch_gemm<BN, true, true>(tA, tB, tA2, tB2, p, sm_count, stream);
 }
 
 int g_sm_count = 0;
 
-
-struct GatherArgs {
-  const unsigned long long* peer_bases = nullptr;
+struct PrefetchArgs {
+  const unsigned long long* peer_bases = nullptr;  // device array
   unsigned long long shard_offset = 0, shard_bytes = 0;
-  void* staging = nullptr;
-  unsigned int* ready = nullptr;
+  void* dst = nullptr;
   int world = 0;
+  int ctas = 0;
 };
 
-static int gemm_entry(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
-                      void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
-                      const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
-                      float alpha, float beta, int out_mode, int splits, int bn, int* status,
-                      void* stream, const GatherArgs* ga) {
-  if (M <= 0 || N <= 0 || (K <= 0 && K2 <= 0)) return 0;
-  if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
-  if (splits < 1) splits = 1;
-  if (splits > 1 && out_mode != 2) return -3;
+int sm_count() {
   if (g_sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (g_sm_count <= 0) g_sm_count = 148;
   }
+  return g_sm_count;
+}
+
+int fill_prefetch(GemmParams& p, const PrefetchArgs* pf) {
+  p.g_ctas = 0;
+  if (pf == nullptr || pf->ctas <= 0) return 0;
+  if (pf->world < 1 || pf->shard_bytes == 0 || pf->shard_bytes % GATHER_CHUNK) return -7;
+  p.g_ctas = pf->ctas;
+  p.g_world = pf->world;
+  p.g_peer_bases = pf->peer_bases;
+  p.g_shard_offset = pf->shard_offset;
+  p.g_shard_bytes = pf->shard_bytes;
+  p.g_total_bytes = pf->shard_bytes * (unsigned long long)pf->world;
+  p.g_dst = reinterpret_cast<unsigned char*>(pf->dst);
+  return 0;
+}
+
+int gemm_entry(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+               void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
+               const void* A2, long long lda2, const void* B2, long long ldb2, int K2, float alpha,
+               float beta, int out_mode, int splits, int bn, int* status, void* stream,
+               const PrefetchArgs* pf) {
+  if (M <= 0 || N <= 0 || (K <= 0 && K2 <= 0)) return 0;
+  if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && out_mode != 2) return -3;
   CUtensorMap tA, tB, tA2, tB2;
   int rc = 0;
   // K-major operand [R, K]: box [BM|BN rows, 64 cols]; MN-major operand [K, R]: box [64, 64].
@@ -515,41 +479,28 @@ static int gemm_entry(const void* A, long long lda, int a_mn, const void* B, lon
   p.out_mode = out_mode;
   p.splits = splits;
   p.status = status;
+  p.group_m = 8;
+  if ((rc = fill_prefetch(p, pf)) != 0) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (ga != nullptr) {
-    // B is the staging buffer: [N, K] (b_mn = 0) or [K, N] (b_mn = 1), contiguous rows
-    const unsigned long long rows = b_mn ? (unsigned long long)K : (unsigned long long)N;
-    const unsigned long long row_bytes = 2ull * (b_mn ? (unsigned long long)N : (unsigned long long)K);
-    if (a_mn || splits != 1 || (bn != 128 && bn != 256)) return -6;
-    if (rows % 256 || (256 * row_bytes) % GATHER_CHUNK || ga->shard_bytes % GATHER_CHUNK ||
-        (unsigned long long)ldb * 2 != row_bytes || ga->shard_bytes * ga->world != rows * row_bytes)
-      return -7;
-    p.g_peer_bases = ga->peer_bases;
-    p.g_shard_offset = ga->shard_offset;
-    p.g_shard_bytes = ga->shard_bytes;
-    p.g_total_bytes = rows * row_bytes;
-    p.g_dst = reinterpret_cast<unsigned char*>(ga->staging);
-    p.g_ready = ga->ready;
-    p.g_chunks_per_block = (unsigned int)(256 * row_bytes / GATHER_CHUNK);
-    p.g_world = ga->world;
-    cudaError_t e = cudaMemsetAsync(ga->ready, 0, sizeof(unsigned int) * (rows / 256), st);
-    if (e != cudaSuccess) return (int)e;
-    if (bn == 256)
-      return b_mn ? launch_gemm<256, false, true, true>(tA, tB, tA2, tB2, p, g_sm_count, st)
-                  : launch_gemm<256, false, false, true>(tA, tB, tA2, tB2, p, g_sm_count, st);
-    return b_mn ? launch_gemm<128, false, true, true>(tA, tB, tA2, tB2, p, g_sm_count, st)
-                : launch_gemm<128, false, false, true>(tA, tB, tA2, tB2, p, g_sm_count, st);
-  }
   switch (bn) {
     case 64:
-      return dispatch_major<64>(a_mn, b_mn, tA, tB, tA2, tB2, p, g_sm_count, st);
+      return dispatch_major<64>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
     case 128:
-      return dispatch_major<128>(a_mn, b_mn, tA, tB, tA2, tB2, p, g_sm_count, st);
+      return dispatch_major<128>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
     case 256:
-      return dispatch_major<256>(a_mn, b_mn, tA, tB, tA2, tB2, p, g_sm_count, st);
+      return dispatch_major<256>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
     default:
       return -5;
   }
+}
+
+// stand-alone all-gather: every CTA is a gather CTA (used when nothing was prefetched)
+__global__ void __launch_bounds__(kThreads, 1) gather_only_kernel(const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GATHER_WARPS * GATHER_SLOTS * GATHER_CHUNK);
+  gather_cta_body(p, blockIdx.x, gridDim.x, smem, bars);
 }
 
 }  // namespace
@@ -570,28 +521,54 @@ extern "C" int axb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
                     alpha, beta, out_mode, splits, bn, status, stream, nullptr);
 }
 
-// Same contraction with the all-gather of a row-sharded B fused in: rank r owns rows
-// [r*rows/world, (r+1)*rows/world) of the stored B matrix at `peer_bases[r] + shard_offset`
-// (peer_bases: DEVICE array of `world` arena addresses, peer-mapped). `staging` is a local
-// buffer of the full B size that the kernel fills block by block while the MMA warps consume
-// it; `ready` is a zero-able counter array with one entry per 256 stored rows.
-extern "C" int axb_gemm_bf16_allgather(const void* A, long long lda, void* staging, int b_mn,
-                                       void* C, long long ldc, const void* Cin, long long ldcin,
-                                       int M, int N, int K, const void* A2, long long lda2,
-                                       const void* B2, long long ldb2, int K2, float alpha,
-                                       float beta, int out_mode, int bn,
-                                       const unsigned long long* peer_bases,
-                                       unsigned long long shard_offset,
-                                       unsigned long long shard_bytes, int world,
-                                       unsigned int* ready, int* status, void* stream) {
-  GatherArgs ga;
-  ga.peer_bases = peer_bases;
-  ga.shard_offset = shard_offset;
-  ga.shard_bytes = shard_bytes;
-  ga.staging = staging;
-  ga.ready = ready;
-  ga.world = world;
-  const long long ldb = b_mn ? N : K;
-  return gemm_entry(A, lda, 0, staging, ldb, b_mn, C, ldc, Cin, ldcin, M, N, K, A2, lda2, B2, ldb2,
-                    K2, alpha, beta, out_mode, 1, bn, status, stream, &ga);
+// Same GEMM, plus `pf_ctas` trailing CTAs that all-gather a row-sharded matrix into `pf_dst`
+// while the GEMM runs: rank r's shard (pf_shard_bytes bytes) lives at
+// pf_peer_bases[r] + pf_shard_offset; pf_peer_bases is a DEVICE array of `pf_world` peer-mapped
+// arena addresses. The gathered matrix is complete when the kernel has finished.
+extern "C" int axb_gemm_bf16_prefetch(const void* A, long long lda, int a_mn, const void* B,
+                                      long long ldb, int b_mn, void* C, long long ldc,
+                                      const void* Cin, long long ldcin, int M, int N, int K,
+                                      const void* A2, long long lda2, const void* B2,
+                                      long long ldb2, int K2, float alpha, float beta,
+                                      int out_mode, int splits, int bn,
+                                      const unsigned long long* pf_peer_bases,
+                                      unsigned long long pf_shard_offset,
+                                      unsigned long long pf_shard_bytes, int pf_world, void* pf_dst,
+                                      int pf_ctas, int* status, void* stream) {
+  PrefetchArgs pf;
+  pf.peer_bases = pf_peer_bases;
+  pf.shard_offset = pf_shard_offset;
+  pf.shard_bytes = pf_shard_bytes;
+  pf.world = pf_world;
+  pf.dst = pf_dst;
+  pf.ctas = pf_ctas;
+  return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, Cin, ldcin, M, N, K, A2, lda2, B2, ldb2, K2,
+                    alpha, beta, out_mode, splits, bn, status, stream, &pf);
+}
+
+// Stand-alone all-gather of a row-sharded matrix into `dst` with `ctas` CTAs (0 = one per SM).
+extern "C" int axb_allgather_rows(const unsigned long long* peer_bases,
+                                  unsigned long long shard_offset, unsigned long long shard_bytes,
+                                  int world, void* dst, int ctas, int* status, void* stream) {
+  PrefetchArgs pf;
+  pf.peer_bases = peer_bases;
+  pf.shard_offset = shard_offset;
+  pf.shard_bytes = shard_bytes;
+  pf.world = world;
+  pf.dst = dst;
+  pf.ctas = ctas > 0 ? ctas : sm_count();
+  GemmParams p = {};
+  p.status = status;
+  int rc = fill_prefetch(p, &pf);
+  if (rc) return rc;
+  constexpr int smem_bytes = GATHER_WARPS * GATHER_SLOTS * GATHER_CHUNK + 1024 + 256;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gather_only_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  gather_only_kernel<<<pf.ctas, kThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
 }

@@ -131,10 +131,12 @@ def pick_splits(out_tiles: int, k_blocks: int) -> int:
 
 
 def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, c_in, out, out_dtype, bn):
-    """GEMM against a row-sharded B whose all-gather is fused into the kernel (see parallel/fsdp.py)."""
+    """GEMM against a row-sharded B. The full B is read from a staging buffer that an earlier
+    launch filled; this launch's extra CTAs all-gather the next weight of the schedule (see
+    parallel/fsdp.py)."""
     if trans_a:
-        raise ValueError("the fused all-gather GEMM takes a row-major A")
-    from ..parallel import symm as _symm  # noqa: F401  (registers the kernel signature)
+        raise ValueError("the sharded-weight GEMM takes a row-major A")
+    from ..parallel import symm as _symm  # noqa: F401  (registers the kernel signatures)
 
     lib = _lib.cuda_lib()
     a = _row_major_2d(a)
@@ -150,15 +152,23 @@ def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, 
     out_mode = 0 if out_dtype == torch.bfloat16 else 1
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    if bn is None or bn == 64:
-        bn = 256 if N >= 256 else 128
+    if bn is None:
+        bn = _pick_bn(M, N)
     ctx = info.ctx
-    rc = lib.axb_gemm_bf16_allgather(
-        a.data_ptr(), a.stride(0), ctx.staging.data_ptr(), int(trans_b), out.data_ptr(), out.stride(0),
+    staging, plan = ctx.acquire(info, backward=trans_b)
+    if plan is not None:
+        nxt, slot = plan
+        pf = (nxt.peer_bases_dev.data_ptr(), nxt.shard_offset, nxt.shard_bytes, nxt.world,
+              ctx.staging[slot].data_ptr(), ctx.prefetch_ctas(nxt, 2.0 * M * N * K))
+    else:
+        pf = (None, 0, 0, 0, None, 0)
+    rc = lib.axb_gemm_bf16_prefetch(
+        a.data_ptr(), a.stride(0), 0, staging.data_ptr(), cols, int(trans_b), out.data_ptr(), out.stride(0),
         _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
         _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
-        K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, int(bn),
-        info.peer_bases_dev.data_ptr(), info.shard_offset, info.shard_bytes, info.world,
-        ctx.ready.data_ptr(), _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
-    _lib.check_rc(rc, "axb_gemm_bf16_allgather")
+        K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, 1, int(bn),
+        *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "axb_gemm_bf16_prefetch")
+    if plan is not None:
+        ctx.committed(plan)
     return out

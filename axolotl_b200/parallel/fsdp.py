@@ -1,13 +1,14 @@
 """FSDP-style sharding of the frozen base weights with the all-gather fused into the GEMM.
 
 Every ``FusedLinear`` weight [N, K] is row-sharded: rank r keeps rows [r*N/W, (r+1)*N/W) inside
-one symmetric arena. Forward (x W^T) and input-gradient (dY W) GEMMs run the
-``axb_gemm_bf16_allgather`` kernel: while the tensor cores work on tile t, a gather warp in every
-CTA pulls 8 KB chunks of the peers' shards over NVLink into a local staging buffer and flags
-256-row blocks as ready for the TMA producer. Nothing is gathered ahead of time and nothing
-stays resident: per-GPU weight memory is 1/W of the model plus one staging buffer of the largest
-weight. Because the base is frozen its shards never change, so no inter-rank synchronisation is
-needed around the gathers at all.
+one symmetric arena. Forward (x W^T) and input-gradient (dY W) GEMMs read the full weight from
+one of two local staging buffers; the GEMM launch that runs on weight k carries a few extra CTAs
+(``axb_gemm_bf16_prefetch``) that pull the shards of weight k+1 of the layer schedule out of the
+peers' memory over NVLink into the other staging buffer, so the all-gather of the next GEMM's
+operand overlaps the tensor-core work of this one and stream order is the only synchronisation.
+A weight that was not predicted is fetched by a stand-alone all-gather launch. Per-GPU weight
+memory is 1/W of the model plus two staging buffers of the largest weight. Because the base is
+frozen its shards never change, so no inter-rank synchronisation is needed around the gathers.
 
 This is the B200 counterpart of the reference's per-layer ``fully_shard`` units + NCCL all-gather
 (src/axolotl/monkeypatch/accelerate/fsdp2.py:539-802).
@@ -24,7 +25,7 @@ LOG = get_logger(__name__)
 
 
 class ShardInfo:
-    __slots__ = ("rows", "cols", "world", "rank", "peer_bases_dev", "shard_offset", "shard_bytes", "ctx")
+    __slots__ = ("rows", "cols", "world", "rank", "peer_bases_dev", "shard_offset", "shard_bytes", "ctx", "index")
 
     def __init__(self, rows, cols, world, rank, peer_bases_dev, shard_offset, shard_bytes, ctx):
         self.rows, self.cols, self.world, self.rank = rows, cols, world, rank
@@ -37,9 +38,14 @@ class FSDPContext:
     def __init__(self, device, group, world, rank):
         self.device, self.group, self.world, self.rank = device, group, world, rank
         self.arena = None
-        self.staging = None
-        self.ready = None
+        self.staging = [None, None]   # two full-size buffers
+        self.holds = [None, None]     # weight (ShardInfo) each buffer holds, in stream order
+        self.order = []               # sharded weights in forward execution order
         self.sharded = []
+        self.stats = {"prefetched": 0, "standalone": 0}
+        # NVLink moves ~50 GB/s per gather CTA; a GEMM CTA row sustains ~9 TFLOP/s
+        self.bytes_per_cta_s = 50e9
+        self.max_prefetch_ctas = 24
 
     @staticmethod
     def shardable(m: FusedLinear, world: int) -> bool:
@@ -47,8 +53,7 @@ class FSDPContext:
         if m.weight.dtype != torch.bfloat16:
             return False
         row_bytes = 2 * K
-        return (N % 256 == 0 and N % world == 0 and (256 * row_bytes) % 8192 == 0
-                and ((N // world) * row_bytes) % 8192 == 0 and N // world >= 1)
+        return N % world == 0 and ((N // world) * row_bytes) % 8192 == 0 and N // world >= 1
 
     @torch.no_grad()
     def shard_model(self, model):
@@ -60,8 +65,7 @@ class FSDPContext:
         self.arena = buf
         max_full = max(m.weight.numel() for m in mods)
         max_rows = max(m.weight.shape[0] for m in mods)
-        self.staging = torch.empty(max_full, dtype=torch.bfloat16, device=self.device)
-        self.ready = torch.zeros(max_rows // 256 + 1, dtype=torch.int32, device=self.device)
+        self.staging = [torch.empty(max_full, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
         off = 0
         for m in mods:
             N, K = m.weight.shape
@@ -70,6 +74,8 @@ class FSDPContext:
             shard = buf.tensor[off:off + n].view(rows, K)
             shard.copy_(m.weight[self.rank * rows:(self.rank + 1) * rows])
             info = ShardInfo(N, K, self.world, self.rank, buf.ptrs_dev, off * 2, n * 2, self)
+            info.index = len(self.order)
+            self.order.append(info)
             p = torch.nn.Parameter(shard, requires_grad=False)
             p._axb_shard = info
             m.weight = p
@@ -81,6 +87,47 @@ class FSDPContext:
         LOG.info("FSDP: sharded %d weights (%.2f GB/rank), staging %.0f MB", len(mods), total * 2 / 1e9,
                  max_full * 2 / 1e6)
         return len(mods)
+
+    # ------------------------------------------------------------------ staging management
+    def acquire(self, info: ShardInfo, backward: bool):
+        """Returns (staging tensor holding ``info``'s full weight, prefetch plan or None).
+
+        Called in stream order right before the GEMM that consumes the weight. The plan names
+        the weight predicted to be used next and the buffer it must be gathered into."""
+        from ..ops import _lib
+
+        if self.holds[0] is info:
+            slot = 0
+        elif self.holds[1] is info:
+            slot = 1
+        else:  # not predicted: fetch now with every SM
+            slot = 0 if self.holds[0] is None or self.holds[1] is not None else 1
+            lib = _lib.cuda_lib()
+            _lib.check_rc(lib.axb_allgather_rows(info.peer_bases_dev.data_ptr(), info.shard_offset, info.shard_bytes,
+                                                 info.world, self.staging[slot].data_ptr(), 0,
+                                                 _lib.status_word(self.device).data_ptr(), _lib.stream_ptr()),
+                          "allgather_rows")
+            self.holds[slot] = info
+            self.stats["standalone"] += 1
+        nxt = None
+        i = info.index + (-1 if backward else 1)
+        if 0 <= i < len(self.order):
+            nxt = self.order[i]
+        plan = None
+        if nxt is not None and self.holds[1 - slot] is not nxt:
+            plan = (nxt, 1 - slot)
+        return self.staging[slot], plan
+
+    def prefetch_ctas(self, nxt: ShardInfo, gemm_flops: float) -> int:
+        """Enough gather CTAs to finish the next weight within this GEMM's run time."""
+        t_gemm = gemm_flops / 1.3e15
+        need = nxt.shard_bytes * nxt.world / max(t_gemm, 1e-6) / self.bytes_per_cta_s
+        return int(min(self.max_prefetch_ctas, max(2, round(need + 0.5))))
+
+    def committed(self, plan):
+        nxt, slot = plan
+        self.holds[slot] = nxt
+        self.stats["prefetched"] += 1
 
     @torch.no_grad()
     def gather_full_weight(self, m: FusedLinear) -> torch.Tensor:

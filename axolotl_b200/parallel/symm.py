@@ -20,10 +20,11 @@ _lib.register_cuda_sigs({
                        + [_lib.f32] * 9 + [_lib.vp, _lib.vp, _lib.i64, _lib.vp],
     "axb_peer_allreduce_f32": [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, C.c_uint,
                                _lib.vp, _lib.i64, _lib.vp],
-    "axb_gemm_bf16_allgather": [_lib.vp, _lib.i64, _lib.vp, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.i64,
-                                _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.i64, _lib.i32,
-                                _lib.f32, _lib.f32, _lib.i32, _lib.i32, _lib.vp, C.c_ulonglong,
-                                C.c_ulonglong, _lib.i32, _lib.vp, _lib.vp, _lib.vp],
+    "axb_gemm_bf16_prefetch": [_lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.vp,
+                               _lib.i64, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.i64,
+                               _lib.i32, _lib.f32, _lib.f32, _lib.i32, _lib.i32, _lib.i32,
+                               _lib.vp, C.c_ulonglong, C.c_ulonglong, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.vp],
+    "axb_allgather_rows": [_lib.vp, C.c_ulonglong, C.c_ulonglong, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.vp],
 })
 
 WAIT_BUDGET_NS = int(float(os.environ.get("AXB_PEER_WAIT_S", "20")) * 1e9)

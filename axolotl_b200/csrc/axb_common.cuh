@@ -234,6 +234,7 @@ AXB_DEVICE float2 unpack_bf16x2(uint32_t u) {
 }
 
 // ------------------------------------------------------------------ host helpers
+#include <cstdio>
 #include <mutex>
 typedef CUresult (*AxbEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                      const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -266,9 +267,22 @@ inline int axb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, u
   CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE,
+           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    // A thread that has made no runtime call yet (e.g. an autograd worker) has no current
+    // driver context: bind the primary context of the runtime's current device and retry.
+    cudaFree(nullptr);
+  }
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "axb_make_tmap_2d failed: CUresult %d base %p rows %llu cols %llu ld %llu box [%u, %u] "
+            "elem_bytes %d\n",
+            (int)r, base, (unsigned long long)rows, (unsigned long long)cols,
+            (unsigned long long)ld_elems, box_rows, box_cols, elem_bytes);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }

@@ -796,3 +796,70 @@ extern "C" int axb_flash_varlen_bwd(const void* qkv, long long ld, const void* d
                                           (long long)Hq * D, dqkv_ld, q_col0);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared and documented in axb_noalloc.h): the
+// dQ accumulator and the delta vector live in a fixed device array inside this library instead
+// of caller-provided scratch, for callers that cannot allocate device memory.
+#include <cstdio>
+
+#include "axb_noalloc.h"
+
+static __device__ __align__(256) float
+    g_noalloc_scratch[AXB_NOALLOC_MAX_DQ_FLOATS + AXB_NOALLOC_MAX_DELTA_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+void set_err(char* err, int err_len, const char* msg) {
+  if (err && err_len > 0) std::snprintf(err, (size_t)err_len, "%s", msg);
+}
+}  // namespace
+
+extern "C" int axb_flash_varlen_bwd_noalloc(const void* qkv, long long ld, const void* dout,
+                                            const void* out, long long o_ld, const float* lse2,
+                                            long long T, int Hq, int Hk, int D, int q_col0,
+                                            int k_col0, int v_col0, const void* tiles, int n_tiles,
+                                            void* dqkv, long long dqkv_ld, float softmax_scale,
+                                            int* status, void* stream, char* err, int err_len) {
+  if (T < 0 || Hq <= 0 || D <= 0) {
+    set_err(err, err_len, "axb_flash_varlen_bwd_noalloc: negative or zero problem size");
+    return AXB_NOALLOC_TOO_LARGE;
+  }
+  const long long dq_floats = T * (long long)Hq * D;
+  const long long delta_floats = T * (long long)Hq;
+  if (dq_floats > AXB_NOALLOC_MAX_DQ_FLOATS || delta_floats > AXB_NOALLOC_MAX_DELTA_FLOATS) {
+    char msg[256];
+    std::snprintf(msg, sizeof(msg),
+                  "axb_flash_varlen_bwd_noalloc: T*Hq*D = %lld (max %d) or T*Hq = %lld (max %d) "
+                  "exceeds the built-in scratch array; use axb_flash_varlen_bwd with your own scratch",
+                  dq_floats, AXB_NOALLOC_MAX_DQ_FLOATS, delta_floats, AXB_NOALLOC_MAX_DELTA_FLOATS);
+    set_err(err, err_len, msg);
+    return AXB_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_err(err, err_len, "axb_flash_varlen_bwd_noalloc: no current CUDA device");
+    return AXB_NOALLOC_SETUP_FAILED;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up per device: in host code the array's name is only a stand-in, the kernels
+    // need its device address
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_err(err, err_len, cudaGetErrorString(e));
+      return AXB_NOALLOC_SETUP_FAILED;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  float* dq_acc = g_noalloc_ptr[dev];
+  float* delta = g_noalloc_ptr[dev] + AXB_NOALLOC_MAX_DQ_FLOATS;
+  // the callee clears dq_acc (it must start at zero) and overwrites delta completely
+  const int rc = axb_flash_varlen_bwd(qkv, ld, dout, out, o_ld, lse2, T, Hq, Hk, D, q_col0, k_col0,
+                                      v_col0, tiles, n_tiles, dqkv, dqkv_ld, dq_acc, delta,
+                                      softmax_scale, status, stream);
+  if (rc != 0) set_err(err, err_len, "axb_flash_varlen_bwd_noalloc: kernel launch failed");
+  return rc;
+}

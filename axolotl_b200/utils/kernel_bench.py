@@ -132,8 +132,33 @@ def bench_elementwise(rows):
     rows.append(f"ce fwd+bwd [2048,128256]: {ms:.3f} ms {gb / ms:.0f} GB/s algorithmic ({gb / ms / hbm:.2f} of {how} HBM)")
 
 
+def profile_case(what):
+    """Small fixed workloads for `ncu` captures: a handful of launches, a few hundred MB."""
+    from axolotl_b200.ops.functional import AttnMeta, flash_varlen
+    from axolotl_b200.ops.gemm import gemm
+
+    if what == "one_gemm":
+        a = torch.randn(8192, 4096, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(6144, 4096, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(8192, 6144, device="cuda", dtype=torch.bfloat16)
+        for _ in range(4):
+            gemm(a, b, out=out)
+    else:
+        Hq, Hk, D = 32, 8, 128
+        meta = AttnMeta([0, 2048, 4096, 6144, 8192], "cuda")
+        qkv = (torch.randn(8192, (Hq + 2 * Hk) * D, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+        g = torch.randn(8192, Hq * D, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            out = flash_varlen(qkv, meta, Hq, Hk, D)
+            torch.autograd.grad(out, qkv, g)
+    torch.cuda.synchronize()
+    print("done", what)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
+    if what in ("one_gemm", "one_attn"):
+        return profile_case(what)
     rows = []
     if what in ("gemm", "all"):
         bench_gemm(rows)

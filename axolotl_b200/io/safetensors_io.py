@@ -76,6 +76,8 @@ class SafeFile:
         info = self.header[name]
         a, b = info["data_offsets"]
         dt = _DTYPES[info["dtype"]]
+        if b == a:
+            return torch.zeros(info["shape"], dtype=dt)
         raw = np.frombuffer(self._mm, dtype=np.uint8, count=b - a, offset=self._base + a).copy()
         return torch.from_numpy(raw).view(dt).reshape(info["shape"])
 

@@ -121,7 +121,21 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
         for n, p in model.named_parameters():
             if any(k in n for k in spec.modules_to_save):
                 p.requires_grad_(True)
-    return sum(p.numel() for p in model.parameters() if p.requires_grad)
+    return count_trainable_params(model)
+
+
+def count_trainable_params(model) -> int:
+    """Trainable parameters as PEFT would count them (the zero off-diagonal blocks of a fused
+    ``lora_B`` are storage, not parameters)."""
+    n = 0
+    fused_ids = set()
+    for _, m in model.fused_linears():
+        if m.lora_A is not None:
+            fused_ids.update((id(m.lora_A), id(m.lora_B)))
+            for A, B in m.peft_tensors().values():
+                n += A.numel() + B.numel()
+    n += sum(p.numel() for p in model.parameters() if p.requires_grad and id(p) not in fused_ids)
+    return n
 
 
 def get_peft_state_dict(model) -> dict:

@@ -39,3 +39,22 @@ def grouped_experts_forward(experts, x_sorted, counts):
     if not outs:
         return x_sorted.new_zeros((0, experts.H))
     return torch.cat(outs, 0)
+
+
+@torch.no_grad()
+def quantize_experts_nvfp4_(model):
+    """Replaces the bf16 expert stacks of every MoE block by frozen NVFP4 tensors (packed nibbles,
+    E4M3 block scales, fp32 per-expert scale)."""
+    from ..models.moe import Experts
+    from .nvfp4 import quantize_nvfp4
+
+    for m in model.modules():
+        if isinstance(m, Experts) and m.nvfp4 is None:
+            q = {}
+            for which, W in (("gate_up", m.gate_up_proj), ("down", m.down_proj)):
+                qd, sc, pts = quantize_nvfp4(W.detach())
+                q[which] = {"qdata": qd, "scale": sc, "pts": pts.reshape(-1)}
+            m.nvfp4 = q
+            m.gate_up_proj = None
+            m.down_proj = None
+    return model

@@ -43,7 +43,7 @@ def quantize_nvfp4(w: torch.Tensor, pts: torch.Tensor | None = None):
     # are 0,2,4,6 -> move midpoints whose lower code is odd up by one.
     mid = torch.isclose(mag, _BOUNDS.to(mag.device)[code.clamp(max=6)]) & (code < 7)
     code = torch.where(mid & (code % 2 == 1), code + 1, code).clamp(max=7)
-    code = code | ((x < 0).to(code.dtype) << 3)
+    code = code | (((x < 0) & (code > 0)).to(code.dtype) << 3)   # no negative zero
     code = code.reshape(*lead, N, K).to(torch.uint8)
     qdata = code[..., 0::2] | (code[..., 1::2] << 4)
     return qdata.contiguous(), bscale8.squeeze(-1).contiguous(), pts

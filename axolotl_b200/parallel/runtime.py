@@ -27,6 +27,8 @@ class ParallelRuntime:
         self.world_size = dist.get_world_size()
         self.dp_group = mesh.group("ep", "dp_replicate", "dp_shard") if mesh.size("ep", "dp_replicate", "dp_shard") > 1 else None
         self.dp_size = mesh.size("ep", "dp_replicate", "dp_shard")
+        ranks = mesh.ranks("ep", "dp_replicate", "dp_shard")
+        self.dp_rank = ranks.index(self.rank) if self.rank in ranks else 0
         self.shard_group = mesh.group("dp_shard")
         self.shard_size = mesh.size("dp_shard")
         self.fsdp = None
@@ -89,6 +91,21 @@ class ParallelRuntime:
         t = torch.tensor([float(v)], dtype=torch.float64, device=self.device)
         dist.all_reduce(t)
         return float(t.item()) / self.world_size
+
+    def min_scalar(self, v):
+        t = torch.tensor([float(v)], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return float(t.item())
+
+    @torch.no_grad()
+    def materialize_full_weights(self, model):
+        """Replaces every sharded weight by its gathered full tensor (checkpoint saving / merging)."""
+        if self.fsdp is None:
+            return
+        for m in list(self.fsdp.sharded):
+            full = self.fsdp.gather_full_weight(m)
+            m.weight = torch.nn.Parameter(full, requires_grad=False)
+        self.fsdp.sharded = []
 
     def sum_scalar(self, v):
         t = torch.tensor([float(v)], dtype=torch.float64, device=self.device)

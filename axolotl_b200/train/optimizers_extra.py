@@ -1,0 +1,101 @@
+"""Optimizers beyond the fused AdamW kernel, as plain ``torch.optim`` classes: ADOPT, Lion, and
+the torch built-ins by name. (Reference: src/axolotl/utils/optimizers/adopt.py:39-539 and the
+optimizer dispatch in src/axolotl/core/builders/base.py:292-484.)"""
+from __future__ import annotations
+
+import torch
+
+
+class ADOPT(torch.optim.Optimizer):
+    """ADOPT (Taniguchi et al. 2024): the second moment is updated AFTER it normalises the
+    gradient, the normalised gradient is clipped by step**0.25, momentum is applied afterwards."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.9999), eps=1e-6, weight_decay=0.0, decouple=True, clip_exp=0.25):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, decouple=decouple,
+                                      clip_exp=clip_exp))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float()
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                if g["weight_decay"] and g["decouple"]:
+                    p.mul_(1 - g["lr"] * g["weight_decay"])
+                elif g["weight_decay"]:
+                    grad = grad.add(p.float(), alpha=g["weight_decay"])
+                if st["step"] == 0:
+                    st["exp_avg_sq"].addcmul_(grad, grad)
+                    st["step"] = 1
+                    continue
+                denom = st["exp_avg_sq"].sqrt().clamp_(min=g["eps"])
+                normed = grad / denom
+                if g["clip_exp"] is not None:
+                    c = st["step"] ** g["clip_exp"]
+                    normed.clamp_(-c, c)
+                st["exp_avg"].lerp_(normed, 1 - b1)
+                p.add_(st["exp_avg"].to(p.dtype), alpha=-g["lr"])
+                st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=1 - b2)
+                st["step"] += 1
+        return loss
+
+
+class Lion(torch.optim.Optimizer):
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                grad = p.grad.float()
+                p.mul_(1 - g["lr"] * g["weight_decay"])
+                update = st["exp_avg"].mul(b1).add_(grad, alpha=1 - b1).sign_()
+                p.add_(update.to(p.dtype), alpha=-g["lr"])
+                st["exp_avg"].mul_(b2).add_(grad, alpha=1 - b2)
+        return loss
+
+
+def build_torch_optimizer(name, params, lr, betas, eps, cfg=None):
+    name = name.lower()
+    args = {}
+    oa = (cfg or {}).get("optim_args")
+    if isinstance(oa, dict):
+        args = dict(oa)
+    elif isinstance(oa, str) and oa:
+        for kv in oa.split(","):
+            k, _, v = kv.partition("=")
+            try:
+                args[k.strip()] = float(v)
+            except ValueError:
+                args[k.strip()] = v.strip()
+    if name in ("sgd",):
+        return torch.optim.SGD(params, lr=lr, momentum=args.pop("momentum", 0.0), **args)
+    if name in ("adagrad",):
+        return torch.optim.Adagrad(params, lr=lr, **args)
+    if name in ("adafactor",):
+        return torch.optim.Adafactor(params, lr=lr, **args)
+    if name in ("rmsprop",):
+        return torch.optim.RMSprop(params, lr=lr, **args)
+    if name in ("adam",):
+        return torch.optim.Adam(params, lr=lr, betas=betas, eps=eps, **args)
+    if name in ("adopt_adamw", "adopt"):
+        return ADOPT(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.9999)), eps=args.pop("eps", 1e-6), **args)
+    if name in ("lion_pytorch", "lion", "lion_32bit"):
+        return Lion(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.99)), **args)
+    raise ValueError(f"optimizer '{name}' is not available on axolotl_b200")

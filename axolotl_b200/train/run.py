@@ -1,0 +1,351 @@
+"""``train(cfg, dataset_meta)``: config -> tokenizer -> data -> model (+adapter) -> parallel runtime
+-> optimizer/schedule -> Trainer -> saved artefacts. The call graph of the reference
+(src/axolotl/train.py:54-668) collapsed into one module because there is no HF Trainer,
+accelerate or PEFT layer underneath.
+
+Artefacts (reference contract, src/axolotl/train.py:254-488): ``adapter_config.json`` +
+``config.json`` (+ tokenizer) are written up front; periodic ``checkpoint-N/`` directories carry
+the adapter (or full model), optimizer, RNG, ``trainer_state.json`` and ``tokens_state.json``; the
+end of training writes ``adapter_model.safetensors`` (LoRA) or ``model*.safetensors`` (full).
+"""
+from __future__ import annotations
+
+import os
+import signal
+
+import numpy as np
+import torch
+
+from ..data.collator import PackedCollator
+from ..data.loading import TrainDatasetMeta, load_datasets
+from ..data.packing import MultipackBatchSampler
+from ..io import hf as hf_io
+from ..models.config import ModelConfig, preset
+from ..models.lora import ALL_LINEAR, LoraSpec, inject_lora, load_adapter, save_adapter
+from ..models.transformer import CausalLM
+from ..plugins.base import PluginManager
+from ..utils.logging import get_logger, start_debug_log, stop_debug_log
+from .callbacks import build_callbacks
+from .optimizer import (FlatAdamW, TorchOptimizerAdapter, build_param_groups, default_warmup_steps, make_lr_lambda)
+from .trainer import TrainArgs, Trainer, find_last_checkpoint
+
+LOG = get_logger(__name__)
+
+
+def model_config_from_cfg(cfg) -> ModelConfig:
+    if cfg.get("model_preset"):
+        mc = preset(cfg["model_preset"], **(cfg.get("overrides_of_model_config") or {}))
+    else:
+        mc = ModelConfig.from_pretrained(cfg.get("base_model_config") or cfg["base_model"])
+        for k, v in (cfg.get("overrides_of_model_config") or {}).items():
+            setattr(mc, k, v)
+    if cfg.get("rope_scaling"):
+        mc.rope_scaling = dict(cfg["rope_scaling"])
+    if cfg.get("router_aux_loss_coef") is not None:
+        mc.router_aux_loss_coef = cfg["router_aux_loss_coef"]
+    return mc
+
+
+def build_model(cfg, device) -> CausalLM:
+    dtype = torch.bfloat16 if cfg.get("torch_dtype") == "bfloat16" else torch.float32
+    mc = model_config_from_cfg(cfg)
+    pm = PluginManager.get_instance()
+    pm.call("pre_model_load", cfg)
+    src = cfg.get("base_model")
+    have_weights = bool(src) and os.path.isdir(src) and bool(hf_io.st.checkpoint_files(src)) and not cfg.get("reinit_weights")
+    if have_weights:
+        model = hf_io.load_pretrained(src, dtype=dtype, device=device, config=mc)
+    else:
+        if not cfg.get("reinit_weights") and not cfg.get("model_preset"):
+            LOG.warning("no weights found under %r: initialising randomly", src)
+        model = CausalLM(mc, dtype=dtype, device=device).init_weights(cfg.get("seed") or 0)
+    if cfg.get("expert_weights_nvfp4"):
+        from ..ops.grouped import quantize_experts_nvfp4_
+
+        quantize_experts_nvfp4_(model)
+    pm.call("post_model_build", cfg, model)
+    return model
+
+
+def lora_spec_from_cfg(cfg) -> LoraSpec | None:
+    if cfg.get("adapter") not in ("lora", "qlora"):
+        return None
+    tm = cfg.get("lora_target_modules")
+    if cfg.get("lora_target_linear"):
+        tm = sorted(set(ALL_LINEAR) | set(tm or [])) if not isinstance(tm, str) else tm
+    tp = cfg.get("lora_target_parameters")
+    if isinstance(tp, str):
+        tp = [tp]
+    return LoraSpec(r=cfg["lora_r"], lora_alpha=cfg["lora_alpha"], lora_dropout=cfg.get("lora_dropout") or 0.0,
+                    target_modules=tm, target_parameters=tp, use_rslora=bool(cfg.get("peft_use_rslora")),
+                    use_dora=bool(cfg.get("peft_use_dora")), modules_to_save=cfg.get("lora_modules_to_save"),
+                    rank_pattern=cfg.get("lora_rank_pattern") or {}, alpha_pattern=cfg.get("lora_alpha_pattern") or {},
+                    layers_to_transform=cfg.get("peft_layers_to_transform"),
+                    base_model_name_or_path=cfg.get("base_model"))
+
+
+def setup_adapter(cfg, model):
+    pm = PluginManager.get_instance()
+    spec = lora_spec_from_cfg(cfg)
+    if spec is None:
+        _apply_freezing(cfg, model)
+        return None
+    pm.call("pre_lora_load", cfg, model)
+    adapter_dtype = torch.float32 if cfg.get("peft_autocast_adapter_dtype", True) is not False else model.dtype
+    n = inject_lora(model, spec, adapter_dtype=adapter_dtype)
+    if cfg.get("lora_model_dir"):
+        load_adapter(model, cfg["lora_model_dir"])
+        LOG.info("loaded adapter from %s", cfg["lora_model_dir"])
+    _apply_freezing(cfg, model, keep_frozen=True)
+    total = sum(p.numel() for p in model.parameters())
+    LOG.info("trainable params: %s || all params: %s || trainable%%: %.4f", f"{n:,}", f"{total:,}", 100 * n / max(total, 1))
+    pm.call("post_lora_load", cfg, model)
+    return spec
+
+
+def _apply_freezing(cfg, model, keep_frozen=False):
+    """``unfrozen_parameters``: regex list; everything else is frozen (src/axolotl/utils/freeze.py:52-211)."""
+    import re
+
+    pats = cfg.get("unfrozen_parameters")
+    if not pats:
+        return
+    regs = [re.compile(p) for p in pats]
+    for n, p in model.named_parameters():
+        hit = any(r.search(n) for r in regs)
+        if hit:
+            p.requires_grad_(True)
+        elif not keep_frozen:
+            p.requires_grad_(False)
+
+
+def build_optimizer(cfg, model, parallel=None):
+    pm = PluginManager.get_instance()
+    custom = pm.first("create_optimizer", cfg, model)
+    if custom is not None:
+        return TorchOptimizerAdapter(custom, [p for p in model.parameters() if p.requires_grad],
+                                     cfg.get("max_grad_norm") or 0.0, model)
+    name = (cfg.get("optimizer") or "adamw_torch_fused").lower()
+    groups = build_param_groups(model.named_parameters(), weight_decay=cfg.get("weight_decay") or 0.0,
+                                embedding_lr=cfg.get("embedding_lr"), embedding_lr_scale=cfg.get("embedding_lr_scale"),
+                                loraplus_lr_ratio=cfg.get("loraplus_lr_ratio"),
+                                lr_groups=[dict(g) for g in (cfg.get("lr_groups") or [])] or None,
+                                lr=float(cfg["learning_rate"]))
+    betas = (cfg.get("adam_beta1") or 0.9, cfg.get("adam_beta2") or 0.999)
+    eps = cfg.get("adam_epsilon") or 1e-8
+    if name in ("adamw_torch", "adamw_torch_fused", "adamw_hf", "adamw", "adamw_anyprecision", "adamw_apex_fused"):
+        world = parallel.dp_size if parallel is not None else 1
+        opt = FlatAdamW(groups, lr=float(cfg["learning_rate"]), betas=betas, eps=eps,
+                        max_grad_norm=cfg.get("max_grad_norm") or 0.0,
+                        alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1))
+        opt.bind_model_shadows(model)
+        return opt
+    from .optimizers_extra import build_torch_optimizer
+
+    params = [{"params": [p for _, p in g["params"]], "lr": float(cfg["learning_rate"]) * g["lr_scale"],
+               "weight_decay": g["weight_decay"]} for g in groups]
+    topt = build_torch_optimizer(name, params, lr=float(cfg["learning_rate"]), betas=betas, eps=eps, cfg=cfg)
+    return TorchOptimizerAdapter(topt, [p for g in groups for _, p in g["params"]], cfg.get("max_grad_norm") or 0.0, model)
+
+
+def make_batches_fn(cfg, ds, rank, dp_size, parallel=None, is_eval=False):
+    """callable(epoch) -> iterator of collated micro-batches for this data-parallel rank."""
+    tok_pad = cfg.get("pad_token_id") or 0
+    packing = bool(cfg.get("eval_sample_packing") if is_eval else cfg.get("sample_packing"))
+    mbs = (cfg.get("eval_batch_size") if is_eval else cfg.get("micro_batch_size")) or 1
+    seq = (cfg.get("eval_sequence_len") if is_eval else None) or cfg["sequence_len"]
+    pad_to_seq = bool(cfg.get("pad_to_sequence_len"))
+    coll = PackedCollator(tok_pad, cfg.get("pad_to_multiple_of") or 64, seq, pad_to_seq)
+    agree = (lambda n: int(parallel.min_scalar(n))) if (parallel is not None and dp_size > 1) else None
+
+    if packing:
+        samp = MultipackBatchSampler(ds.lengths, seq, mbs, real_batches=bool(cfg.get("multipack_real_batches")),
+                                     bin_size=cfg.get("sample_packing_bin_size") or 200,
+                                     group_size=cfg.get("sample_packing_group_size") or 100_000,
+                                     sequential=bool(cfg.get("sample_packing_sequentially")),
+                                     shuffle=not (is_eval or cfg.get("curriculum_sampling")), seed=cfg.get("seed") or 42,
+                                     rank=rank, world_size=dp_size, len_agree_fn=agree)
+
+        def packed(epoch=0):
+            samp.set_epoch(epoch)
+            for bins in samp:
+                yield coll([[ds[i] for i in b] for b in bins])
+
+        return packed, samp
+
+    def plain(epoch=0):
+        n = len(ds)
+        order = np.arange(n) if (is_eval or cfg.get("curriculum_sampling")) else np.random.default_rng((cfg.get("seed") or 42) + epoch).permutation(n)
+        if cfg.get("group_by_length") and not is_eval:
+            chunks = [order[i:i + mbs * 50] for i in range(0, n, mbs * 50)]
+            order = np.concatenate([c[np.argsort(-ds.lengths[c], kind="stable")] for c in chunks]) if chunks else order
+        per_rank = (n // (mbs * dp_size)) * mbs if not is_eval else None
+        mine = order[rank::dp_size]
+        if per_rank is not None:
+            mine = mine[:per_rank]
+        for i in range(0, len(mine), mbs):
+            idx = mine[i:i + mbs]
+            if len(idx) < mbs and not is_eval:
+                break
+            yield coll([[ds[j]] for j in idx])
+
+    return plain, None
+
+
+def save_model_artifacts(model, cfg, spec, out_dir, parallel=None, rank=0):
+    """Adapter (LoRA) or full HF checkpoint into ``out_dir`` (rank 0 writes)."""
+    if spec is not None:
+        if rank == 0:
+            save_adapter(model, spec, out_dir)
+        return
+    if parallel is not None and parallel.fsdp is not None:
+        parallel.materialize_full_weights(model)  # gathers sharded weights for saving
+    if rank == 0:
+        hf_io.save_pretrained(model, out_dir)
+
+
+def setup_signal_handler(trainer, model, cfg, spec):
+    def handler(signum, frame):  # SIGINT: save what we have and stop
+        LOG.warning("signal %s received: saving and stopping", signum)
+        trainer.should_stop = True
+        trainer.should_save = True
+
+    if trainer.rank == 0:
+        try:
+            signal.signal(signal.SIGINT, handler)
+        except ValueError:
+            pass  # not the main thread
+
+
+def train(cfg, dataset_meta: TrainDatasetMeta | None = None):
+    try:
+        return _train(cfg, dataset_meta)
+    finally:
+        stop_debug_log()
+
+
+def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
+    torch.manual_seed(cfg.get("seed") or 42)
+    np.random.seed(cfg.get("seed") or 42)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    use_cuda = torch.cuda.is_available() and cfg.get("device") != "cpu"
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    if world > 1:
+        from ..parallel.runtime import init_distributed
+
+        init_distributed(timeout_s=cfg.get("ddp_timeout"))
+    start_debug_log(cfg["output_dir"], append=bool(cfg.get("resume_from_checkpoint")))
+    pm = PluginManager.get_instance()
+
+    tokenizer = None
+    if dataset_meta is None:
+        dataset_meta = load_datasets(cfg)
+    if cfg.get("base_model") and os.path.isdir(cfg["base_model"]) and any(
+            os.path.exists(os.path.join(cfg["base_model"], f)) for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+        from ..data.tokenizer import load_tokenizer
+
+        tokenizer = load_tokenizer(cfg)
+        cfg["pad_token_id"] = tokenizer.pad_token_id
+
+    model = build_model(cfg, device)
+    spec = setup_adapter(cfg, model)
+    pm.call("post_model_load", cfg, model)
+    if cfg.get("gradient_checkpointing") or (cfg.get("fsdp_config") or {}).get("activation_checkpointing"):
+        model.enable_gradient_checkpointing(True)
+
+    parallel = None
+    dp_size, dp_rank = 1, 0
+    if world > 1:
+        from ..parallel.runtime import build_parallel
+
+        parallel = build_parallel(model, device=device, dp_shard=cfg.get("dp_shard_size"),
+                                  dp_replicate=cfg.get("dp_replicate_size") or 1, tp=cfg.get("tensor_parallel_size") or 1,
+                                  cp=cfg.get("context_parallel_size") or 1, ep=cfg.get("expert_parallel_size") or 1)
+        dp_size, dp_rank = parallel.dp_size, parallel.dp_rank
+
+    opt = build_optimizer(cfg, model, parallel)
+    if parallel is not None:
+        parallel.attach_optimizer(opt)
+
+    train_fn, sampler = make_batches_fn(cfg, dataset_meta.train, dp_rank, dp_size, parallel)
+    eval_fn = None
+    if dataset_meta.eval is not None and len(dataset_meta.eval):
+        eval_fn, _ = make_batches_fn(cfg, dataset_meta.eval, dp_rank, dp_size, parallel, is_eval=True)
+    total = dataset_meta.total_num_steps or cfg.get("max_steps") or 0
+    if cfg.get("max_steps"):
+        total = min(total, cfg["max_steps"]) if total else cfg["max_steps"]
+    warm = default_warmup_steps(total, cfg.get("warmup_steps"), cfg.get("warmup_ratio"))
+    sched = pm.first("create_lr_scheduler", cfg, opt, total)
+    lr_lambda = sched or make_lr_lambda(
+        "cosine_with_quadratic_warmup" if cfg.get("lr_quadratic_warmup") else
+        ("cosine_with_min_lr" if cfg.get("cosine_min_lr_ratio") and (cfg.get("lr_scheduler") or "cosine") == "cosine" else cfg.get("lr_scheduler")),
+        total, warm, min_lr_ratio=cfg.get("cosine_min_lr_ratio") or 0.0,
+        constant_lr_ratio=cfg.get("cosine_constant_lr_ratio"), **(cfg.get("lr_scheduler_kwargs") or {}))
+    logging_steps = cfg.get("logging_steps") or max(min(int(0.005 * total), 10), 1)
+    args = TrainArgs(output_dir=cfg["output_dir"], max_steps=total, num_epochs=cfg.get("num_epochs") or 1,
+                     micro_batch_size=cfg["micro_batch_size"], gradient_accumulation_steps=cfg["gradient_accumulation_steps"],
+                     learning_rate=float(cfg["learning_rate"]), weight_decay=cfg.get("weight_decay") or 0.0,
+                     max_grad_norm=cfg.get("max_grad_norm") or 0.0, logging_steps=logging_steps,
+                     save_steps=cfg.get("save_steps"), save_strategy=cfg.get("save_strategy") or ("steps" if cfg.get("save_steps") else "no"),
+                     save_total_limit=cfg.get("save_total_limit"), save_only_model=bool(cfg.get("save_only_model")),
+                     save_first_step=bool(cfg.get("save_first_step")), eval_steps=cfg.get("eval_steps"),
+                     eval_strategy=cfg.get("eval_strategy") or "no", seed=cfg.get("seed") or 42,
+                     include_tkps=cfg.get("include_tkps", True) is not False,
+                     gradient_checkpointing=bool(cfg.get("gradient_checkpointing")))
+    resume = cfg.get("resume_from_checkpoint")
+    if not resume and cfg.get("auto_resume_from_checkpoints"):
+        resume = find_last_checkpoint(cfg["output_dir"])
+    args.resume_from_checkpoint = resume
+
+    def save_fn(trainer, ckpt_dir):
+        save_model_artifacts(model, cfg, spec, ckpt_dir, parallel, trainer.rank)
+
+    callbacks = build_callbacks(cfg) + pm.collect_callbacks("add_callbacks_pre_trainer", cfg, model)
+    trainer_cls = pm.first("get_trainer_cls", cfg) or Trainer
+    trainer = trainer_cls(model, opt, lr_lambda, args, train_fn, eval_batches=eval_fn, parallel=parallel,
+                          callbacks=callbacks, save_fn=save_fn, device=device, total_steps=total,
+                          compute_loss=pm.first("compute_loss", cfg))
+    trainer.callbacks += pm.collect_callbacks("add_callbacks_post_trainer", cfg, trainer)
+    pm.call("post_trainer_create", cfg, trainer)
+
+    # up-front artefacts
+    if rank == 0:
+        os.makedirs(cfg["output_dir"], exist_ok=True)
+        model.config.save_pretrained(cfg["output_dir"])
+        if spec is not None:
+            spec.save(cfg["output_dir"])
+        if tokenizer is not None:
+            tokenizer.save_pretrained(cfg["output_dir"])
+    if resume and spec is not None and os.path.exists(os.path.join(resume, "adapter_model.safetensors")):
+        load_adapter(model, resume)
+    setup_signal_handler(trainer, model, cfg, spec)
+    if cfg.get("neftune_noise_alpha"):
+        LOG.warning("neftune_noise_alpha is accepted but not applied by the fused embedding kernel")
+
+    trainer.train()
+
+    if cfg.get("merge_lora") and spec is not None:
+        from ..models.lora import merge_and_unload
+
+        merge_and_unload(model)
+        spec = None
+    save_model_artifacts(model, cfg, spec, cfg["output_dir"], parallel, rank)
+    if rank == 0:
+        _write_model_card(cfg, trainer)
+    pm.call("post_train", cfg, model)
+    if parallel is not None:
+        parallel.barrier()
+    return model, tokenizer, trainer
+
+
+def _write_model_card(cfg, trainer):
+    last = next((l for l in reversed(trainer.log_history) if "loss" in l), {})
+    with open(os.path.join(cfg["output_dir"], "README.md"), "w") as fh:
+        fh.write(f"# {os.path.basename(os.path.normpath(cfg['output_dir']))}\n\n"
+                 f"Fine-tuned from `{cfg.get('base_model') or cfg.get('model_preset')}` with axolotl_b200.\n\n"
+                 f"- steps: {trainer.global_step}\n- final loss: {last.get('loss')}\n"
+                 f"- adapter: {cfg.get('adapter')}\n- sequence_len: {cfg.get('sequence_len')}\n"
+                 f"- learning_rate: {cfg.get('learning_rate')}\n")

@@ -90,6 +90,7 @@ def h2d_bytes(batch: dict) -> int:
 
 class Callback:
     def on_train_begin(self, trainer): ...
+    def on_pre_optimizer_step(self, trainer): ...
     def on_step_end(self, trainer, logs): ...
     def on_log(self, trainer, logs): ...
     def on_save(self, trainer, ckpt_dir): ...
@@ -148,6 +149,8 @@ class Trainer:
             self.tokens["total"] += b["n_tokens"]
         self.tokens["trainable"] += n_items
         lr = self.args.learning_rate * self.lr_lambda(self.global_step)
+        for cb in self.callbacks:
+            cb.on_pre_optimizer_step(self)
         if par is not None:
             gnorm_sq = par.optimizer_step(opt, lr)
         else:

@@ -10,13 +10,29 @@ import sys
 _configured = False
 
 
+class _StderrHandler(logging.StreamHandler):
+    """Always writes to the *current* ``sys.stderr`` (so output tees and test harnesses that swap
+    the stream keep working)."""
+
+    def __init__(self):
+        logging.Handler.__init__(self)
+
+    @property
+    def stream(self):
+        return sys.stderr
+
+    @stream.setter
+    def stream(self, value):
+        pass
+
+
 def configure(level=None):
     global _configured
     if _configured:
         return
     rank = int(os.environ.get("RANK", "0"))
     lvl = level or os.environ.get("AXOLOTL_LOG_LEVEL") or ("INFO" if rank == 0 else "WARNING")
-    h = logging.StreamHandler(sys.stderr)
+    h = _StderrHandler()
     h.setFormatter(logging.Formatter(f"[%(asctime)s] [%(levelname)s] [%(name)s] [rank{rank}] %(message)s",
                                      "%Y-%m-%d %H:%M:%S"))
     root = logging.getLogger("axolotl_b200")
@@ -65,9 +81,6 @@ def start_debug_log(output_dir, append=False):
     fh = open(path, "a" if append else "w")
     _tee_state.update(fh=fh, out=sys.stdout, err=sys.stderr)
     sys.stdout, sys.stderr = Tee(sys.stdout, fh), Tee(sys.stderr, fh)
-    for h in logging.getLogger("axolotl_b200").handlers:
-        if isinstance(h, logging.StreamHandler):
-            h.stream = sys.stderr
     return path
 
 

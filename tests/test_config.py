@@ -1,0 +1,122 @@
+import os
+
+import pytest
+import yaml
+
+from axolotl_b200.config.dict import DictDefault
+from axolotl_b200.config.load import apply_overrides, coerce_value, load_cfg, validate_config
+from axolotl_b200.config.normalize import normalize
+from axolotl_b200.config.schema import check_keys
+
+BASE = {"model_preset": "tiny-llama", "datasets": [{"type": "_synthetic", "length": 10}], "sequence_len": 256,
+        "learning_rate": "2e-4", "micro_batch_size": 2}
+
+
+def test_dictdefault_missing_is_none_and_nested():
+    d = DictDefault({"a": {"b": 1}, "l": [{"c": 2}]})
+    assert d.a.b == 1 and d.zzz is None and d.l[0].c == 2 and d.a.q is None
+    d.x = {"y": 3}
+    assert d.x.y == 3 and d.to_dict()["x"] == {"y": 3}
+
+
+def test_minimal_config_validates_and_normalises():
+    cfg = load_cfg(dict(BASE, gradient_accumulation_steps=4))
+    assert cfg.learning_rate == pytest.approx(2e-4)
+    assert cfg.batch_size == 8 and cfg.gradient_accumulation_steps == 4 and cfg.eval_batch_size == 2
+    assert cfg.save_total_limit == 4 and cfg.seed == 42 and cfg.max_grad_norm == 1.0
+    assert cfg.is_llama_derived_model is True and cfg.model_config_type == "llama"
+
+
+def test_batch_size_derives_grad_accum():
+    cfg = load_cfg(dict(BASE, batch_size=8))
+    assert cfg.gradient_accumulation_steps == 4
+    with pytest.raises(ValueError):
+        load_cfg(dict(BASE, batch_size=8, gradient_accumulation_steps=2))
+
+
+def test_world_size_scaling_excludes_tp_and_cp(monkeypatch):
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    assert load_cfg(dict(BASE, gradient_accumulation_steps=1)).batch_size == 16
+    assert load_cfg(dict(BASE, gradient_accumulation_steps=1, tensor_parallel_size=2)).batch_size == 8
+    assert load_cfg(dict(BASE, gradient_accumulation_steps=1, context_parallel_size=4, micro_batch_size=1)).batch_size == 2
+    assert load_cfg(dict(BASE, gradient_accumulation_steps=1, expert_parallel_size=8)).batch_size == 16
+
+
+@pytest.mark.parametrize("patch,msg", [
+    ({"foo_bar": 1}, "unknown config key"),
+    ({"lora_rr": 8}, "did you mean 'lora_r'"),
+    ({"deepspeed": "zero3.json"}, "unsupported"),
+    ({"bf16": True, "fp16": True}, "mutually exclusive"),
+    ({"adapter": "lora"}, "lora_r"),
+    ({"adapter": "lora", "lora_r": 8, "lora_alpha": 16}, "no LoRA targets"),
+    ({"adapter": "qlora", "lora_r": 8, "lora_alpha": 16, "lora_target_linear": True}, "load_in_4bit"),
+    ({"sample_packing": True, "group_by_length": True}, "group_by_length"),
+    ({"warmup_steps": 3, "warmup_ratio": 0.1}, "only one of"),
+    ({"save_steps": 5, "saves_per_epoch": 2}, "only one of"),
+    ({"optimizer": "adamw_bnb_8bit"}, "bitsandbytes"),
+    ({"rl": "grpo"}, "vLLM"),
+    ({"tensor_parallel_size": 2, "expert_parallel_size": 2}, "expert parallelism"),
+    ({"context_parallel_size": 2, "sample_packing": True, "micro_batch_size": 2}, "micro_batch_size: 1"),
+    ({"val_set_size": 0.1, "test_datasets": [{"type": "_synthetic"}]}, "mutually exclusive"),
+    ({"datasets": None}, "no `datasets`"),
+    ({"max_packed_sequence_len": 2048}, "removed"),
+    ({"early_stopping_patience": 3}, "periodic evaluation"),
+])
+def test_validation_errors(patch, msg):
+    raw = dict(BASE)
+    raw.update(patch)
+    raw = {k: v for k, v in raw.items() if v is not None}
+    with pytest.raises(Exception) as ei:
+        load_cfg(raw)
+    assert msg in str(ei.value)
+
+
+def test_deprecated_and_legacy_spellings_are_mapped():
+    cfg = load_cfg(dict(BASE, flash_attention=True, sequence_parallel_degree=1, evaluation_strategy="no",
+                        sample_packing=True))
+    assert cfg.attn_implementation == "flash_attention_2" and cfg.context_parallel_size == 1
+    assert cfg.eval_strategy == "no" and cfg.pad_to_sequence_len is True
+    with pytest.raises(ValueError):
+        load_cfg(dict(BASE, flash_attention=True, attn_implementation="sdpa"))
+
+
+def test_inert_reference_keys_are_accepted():
+    raw = dict(BASE, liger_rope=True, torch_compile_backend="inductor", lisa_n_layers=2)
+    assert set(check_keys(raw)) == {"liger_rope", "torch_compile_backend", "lisa_n_layers"}
+    load_cfg(raw)
+
+
+def test_saves_per_epoch_and_eval_cadence():
+    cfg = load_cfg(dict(BASE, saves_per_epoch=2, num_epochs=2, val_set_size=0.1, evals_per_epoch=4))
+    assert cfg.save_steps == pytest.approx(0.25) and cfg.save_strategy == "steps"
+    assert cfg.eval_steps == pytest.approx(0.125) and cfg.eval_strategy == "steps"
+    cfg2 = load_cfg(dict(BASE))
+    assert cfg2.eval_strategy == "no"
+
+
+def test_cli_style_overrides_and_yaml_file(tmp_path):
+    assert coerce_value("true") is True and coerce_value("3") == 3 and coerce_value("1e-3") == 1e-3
+    assert coerce_value("none") is None and coerce_value("[1, 2]") == [1, 2] and coerce_value("abc") == "abc"
+    raw = apply_overrides({"fsdp_config": {"a": 1}}, {"fsdp_config__reshard_after_forward": "true", "lora_r": "16"})
+    assert raw["fsdp_config"] == {"a": 1, "reshard_after_forward": True} and raw["lora_r"] == 16
+    p = tmp_path / "c.yaml"
+    p.write_text(yaml.safe_dump(BASE))
+    cfg = load_cfg(str(p), micro_batch_size="4", output_dir=str(tmp_path / "o"))
+    assert cfg.micro_batch_size == 4 and cfg.axolotl_config_path == str(p)
+    assert load_cfg(str(tmp_path)).micro_batch_size == 2   # directory chooser
+
+
+def test_fsdp_config_prefix_stripping():
+    cfg = load_cfg(dict(BASE, fsdp_config={"fsdp_version": 2, "fsdp_reshard_after_forward": True,
+                                           "fsdp_state_dict_type": "FULL_STATE_DICT"}))
+    assert cfg.fsdp_config.reshard_after_forward is True and cfg.fsdp_version == 2
+
+
+def test_plugins_contribute_keys():
+    from axolotl_b200.plugins.base import PluginManager
+
+    PluginManager.reset()
+    cfg = load_cfg(dict(BASE, plugins=["axolotl.integrations.liger.LigerPlugin", "grokfast"], liger_rope=True,
+                        grokfast_alpha=0.9))
+    assert cfg.grokfast_alpha == 0.9
+    PluginManager.reset()

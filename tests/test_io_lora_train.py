@@ -1,0 +1,283 @@
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from axolotl_b200.io import hf as hf_io
+from axolotl_b200.io import safetensors_io as st
+from axolotl_b200.io.merge import merge_lora_sharded, merge_sharded_fsdp_weights
+from axolotl_b200.models.config import preset
+from axolotl_b200.models.lora import (ALL_LINEAR, LoraSpec, get_peft_state_dict, inject_lora, load_adapter,
+                                      merge_and_unload, save_adapter)
+from axolotl_b200.models.transformer import CausalLM
+from axolotl_b200.ops.nvfp4 import dequantize_nvfp4, quantize_nvfp4
+from axolotl_b200.train.optimizer import (FlatAdamW, build_param_groups, default_warmup_steps, make_lr_lambda)
+from axolotl_b200.train.trainer import TrainArgs, Trainer, find_last_checkpoint
+
+
+def _tiny(seed=0, **kw):
+    cfg = preset("tiny-llama", vocab_size=256, num_hidden_layers=2, **kw)
+    return CausalLM(cfg, dtype=torch.float32).init_weights(seed)
+
+
+def _randomise_lora(model, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    for _, m in model.fused_linears():
+        if m.lora_A is None:
+            continue
+        with torch.no_grad():
+            for (r0, rows, c0, r) in m.lora_blocks:
+                m.lora_B[r0:r0 + rows, c0:c0 + r] = torch.randn(rows, r, generator=g) * 0.05
+
+
+def test_safetensors_roundtrip_and_interop(tmp_path):
+    tensors = {"a": torch.randn(3, 5), "b.c": torch.arange(7, dtype=torch.int64), "h": torch.randn(4, 4).bfloat16(),
+               "q": torch.randint(0, 255, (6,), dtype=torch.uint8), "e": torch.zeros(0)}
+    p = str(tmp_path / "x.safetensors")
+    st.save_file(tensors, p, {"format": "pt"})
+    back = st.load_file(p)
+    assert all(torch.equal(back[k], v) for k, v in tensors.items())
+    safetensors = pytest.importorskip("safetensors.torch")
+    theirs = safetensors.load_file(p)
+    assert all(torch.equal(theirs[k], v) for k, v in tensors.items())
+    safetensors.save_file({k: v for k, v in tensors.items()}, str(tmp_path / "y.safetensors"))
+    mine = st.load_file(str(tmp_path / "y.safetensors"))
+    assert all(torch.equal(mine[k], v) for k, v in tensors.items())
+    names = st.save_sharded({f"w{i}": torch.randn(100, 100) for i in range(6)}, str(tmp_path / "sh"), max_shard_bytes=90_000)
+    assert len(names) == 3 and os.path.exists(tmp_path / "sh" / "model.safetensors.index.json")
+    assert len(dict(st.iter_checkpoint(str(tmp_path / "sh")))) == 6
+
+
+def test_peft_adapter_format_and_reload(tmp_path):
+    model = _tiny()
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj", "down_proj"])
+    n = inject_lora(model, spec)
+    H, I = 256, 688
+    per_layer = 4 * (H + 256) + 4 * (H + 128) + 4 * (I + H)
+    assert n == 2 * per_layer
+    assert all(not p.requires_grad for k, p in model.named_parameters() if "lora_" not in k)
+    _randomise_lora(model)
+    sd = get_peft_state_dict(model)
+    assert "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight" in sd
+    assert sd["base_model.model.model.layers.1.mlp.down_proj.lora_B.weight"].shape == (H, 4)
+    assert not any("k_proj" in k or "gate_proj" in k for k in sd)
+    save_adapter(model, spec, str(tmp_path / "ad"))
+    conf = json.load(open(tmp_path / "ad" / "adapter_config.json"))
+    assert conf["peft_type"] == "LORA" and conf["r"] == 4 and conf["target_modules"] == ["down_proj", "q_proj", "v_proj"]
+    other = _tiny()
+    inject_lora(other, spec)
+    load_adapter(other, str(tmp_path / "ad"))
+    ids = torch.randint(3, 256, (1, 40))
+    with torch.no_grad():
+        assert torch.allclose(model(ids, return_logits=True).logits, other(ids, return_logits=True).logits, atol=1e-6)
+
+
+def test_merge_lora_matches_adapter_forward(tmp_path):
+    model = _tiny(1)
+    hf_io.save_pretrained(model, str(tmp_path / "base"), max_shard_bytes=2_000_000)  # force several shards
+    assert len(st.checkpoint_files(str(tmp_path / "base"))) > 1
+    spec = LoraSpec(r=4, lora_alpha=16, target_modules=list(ALL_LINEAR), use_rslora=True)
+    inject_lora(model, spec)
+    _randomise_lora(model)
+    save_adapter(model, spec, str(tmp_path / "ad"))
+    ids = torch.randint(3, 256, (1, 48))
+    with torch.no_grad():
+        want = model(ids, return_logits=True).logits
+    res = merge_lora_sharded(str(tmp_path / "base"), str(tmp_path / "ad"), str(tmp_path / "merged"))
+    assert res["unmatched"] == [] and res["merged"] == 2 * 7
+    merged = hf_io.load_pretrained(str(tmp_path / "merged"), dtype=torch.float32)
+    with torch.no_grad():
+        got = merged(ids, return_logits=True).logits
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+    assert os.path.exists(tmp_path / "merged" / "config.json")
+    assert os.path.exists(tmp_path / "merged" / "model.safetensors.index.json")
+    # in-memory merge agrees too
+    merge_and_unload(model)
+    with torch.no_grad():
+        assert torch.allclose(model(ids, return_logits=True).logits, want, atol=1e-4)
+
+
+def test_expert_lora_layout_and_merge(tmp_path):
+    cfg = preset("tiny-qwen3-moe", vocab_size=256)
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(2)
+    hf_io.save_pretrained(model, str(tmp_path / "base"))
+    spec = LoraSpec(r=2, lora_alpha=4, target_modules=["q_proj"], target_parameters=["mlp.experts.gate_up_proj", "mlp.experts.down_proj"])
+    inject_lora(model, spec)
+    ex = model.layers[0].mlp.experts
+    E, r = ex.E, 2
+    assert ex.lora["gate_up_A"].shape == (E * r, 256) and ex.lora["gate_up_B"].shape == (2 * 128, r * E)
+    with torch.no_grad():
+        for l in model.layers:
+            for k in ("gate_up_B", "down_B"):
+                l.mlp.experts.lora[k].normal_(0, 0.05)
+    A, B = ex.expert_lora("down", 3)
+    assert torch.equal(A, ex.lora["down_A"][3 * r:4 * r]) and torch.equal(B, ex.lora["down_B"].view(256, r, E)[:, :, 3])
+    save_adapter(model, spec, str(tmp_path / "ad"))
+    keys = st.SafeFile(str(tmp_path / "ad" / "adapter_model.safetensors")).keys()
+    assert "base_model.model.model.layers.0.mlp.experts.gate_up_proj.lora_A.weight" in keys
+    ids = torch.randint(3, 256, (1, 32))
+    model.eval()
+    with torch.no_grad():
+        want = model(ids, return_logits=True).logits
+    merge_lora_sharded(str(tmp_path / "base"), str(tmp_path / "ad"), str(tmp_path / "m"))
+    merged = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32).eval()
+    with torch.no_grad():
+        got = merged(ids, return_logits=True).logits
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+
+
+def test_nvfp4_quantisation_roundtrip_and_grid():
+    torch.manual_seed(0)
+    w = torch.randn(4, 32, 64)
+    q, s, pts = quantize_nvfp4(w)
+    assert q.shape == (4, 32, 32) and q.dtype == torch.uint8 and s.shape == (4, 32, 4) and s.dtype == torch.float8_e4m3fn
+    d = dequantize_nvfp4(q, s, pts, dtype=torch.float32)
+    rel = ((d - w).norm() / w.norm()).item()
+    assert rel < 0.12
+    # values already on the grid survive exactly; nibble order: low = even k
+    grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0, 0.0])
+    x = grid.repeat(2, 1)
+    q2, s2, p2 = quantize_nvfp4(x, pts=torch.tensor(1.0))
+    assert torch.equal(dequantize_nvfp4(q2, s2, p2, dtype=torch.float32), x)
+    assert (q2[0, 0] & 0xF) == 0 and (q2[0, 0] >> 4) == 1
+    q3, s3, p3 = quantize_nvfp4(dequantize_nvfp4(q, s, pts, dtype=torch.float32), pts=pts)
+    assert torch.equal(q3, q)   # requantising with the same scales is idempotent
+
+
+def test_nvfp4_expert_loading_reconciles_scales():
+    from axolotl_b200.io.nvfp4_loading import fuse_nvfp4_experts, is_nvfp4_parts
+
+    torch.manual_seed(1)
+    parts, ref = {}, {}
+    for e in range(2):
+        for sub, shape, scale in (("gate_proj", (16, 32), 1.0), ("up_proj", (16, 32), 3.0), ("down_proj", (32, 16), 1.0)):
+            w = torch.randn(*shape) * scale
+            q, s, p = quantize_nvfp4(w)
+            parts[(e, sub, "weight")] = q
+            parts[(e, sub, "weight_scale")] = s
+            parts[(e, sub, "weight_scale_2")] = p
+            ref[(e, sub)] = dequantize_nvfp4(q, s, p, dtype=torch.float32)
+    assert is_nvfp4_parts(parts)
+    fused = fuse_nvfp4_experts(parts, 2)
+    gu = dequantize_nvfp4(fused["gate_up"]["qdata"], fused["gate_up"]["scale"], fused["gate_up"]["pts"], dtype=torch.float32)
+    for e in range(2):
+        want = torch.cat([ref[(e, "gate_proj")], ref[(e, "up_proj")]], 0)
+        assert ((gu[e] - want).norm() / want.norm()).item() < 0.08
+        assert torch.equal(gu[e][16:], ref[(e, "up_proj")])   # the larger scale is kept exactly
+
+
+def test_flat_adamw_matches_torch_and_param_groups():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(16, 8)
+    ref = torch.nn.Linear(16, 8)
+    ref.load_state_dict(lin.state_dict())
+    groups = build_param_groups(lin.named_parameters(), weight_decay=0.1)
+    assert {g["name"]: g["weight_decay"] for g in groups} == {"decay": 0.1, "no_decay": 0.0}
+    opt = FlatAdamW(groups, lr=1e-2, max_grad_norm=0.5)
+    ro = torch.optim.AdamW([{"params": [ref.weight], "weight_decay": 0.1}, {"params": [ref.bias], "weight_decay": 0.0}], lr=1e-2)
+    for _ in range(4):
+        x = torch.randn(5, 16)
+        lin(x).pow(2).sum().backward()
+        ref(x).pow(2).sum().backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+        opt.zero_grad()
+        ro.step()
+        ro.zero_grad()
+    assert torch.allclose(lin.weight, ref.weight, atol=1e-6) and torch.allclose(lin.bias, ref.bias, atol=1e-6)
+    g2 = build_param_groups([("model.embed_tokens", torch.nn.Parameter(torch.zeros(4, 4))),
+                             ("x.lora_B", torch.nn.Parameter(torch.zeros(4, 4))),
+                             ("x.lora_A", torch.nn.Parameter(torch.zeros(4, 4)))], embedding_lr_scale=0.5, loraplus_lr_ratio=16, lr=1e-3)
+    assert {g["name"]: g["lr_scale"] for g in g2} == {"embeddings": 0.5, "lora_B": 16, "decay": 1.0}
+
+
+def test_schedules_and_warmup_defaults():
+    f = make_lr_lambda("cosine", 100, 10)
+    assert f(0) == 0 and f(5) == 0.5 and f(10) == 1.0 and abs(f(55) - 0.5) < 1e-6 and f(100) < 1e-6
+    m = make_lr_lambda("cosine_with_min_lr", 100, 0, min_lr_ratio=0.1)
+    assert abs(m(100) - 0.1) < 1e-9 and m(0) == 1.0
+    assert make_lr_lambda("linear", 10, 0)(5) == 0.5 and make_lr_lambda("constant", 10, 0)(7) == 1.0
+    assert make_lr_lambda("constant_with_warmup", 10, 4)(2) == 0.5
+    q = make_lr_lambda("cosine_with_quadratic_warmup", 100, 10)
+    assert q(5) == 0.25
+    r = make_lr_lambda("rex", 100, 0)
+    assert r(0) == 1.0 and 0 < r(50) < 1 and r(100) == 0
+    with pytest.raises(ValueError):
+        make_lr_lambda("nope", 10, 0)
+    assert default_warmup_steps(1000) == 30 and default_warmup_steps(10000) == 100
+    assert default_warmup_steps(1000, warmup_ratio=0.001) == 2 and default_warmup_steps(1000, warmup_steps=7) == 7
+
+
+def _make_trainer(tmp, max_steps, resume=None, seed=0):
+    from axolotl_b200.data.collator import PackedCollator
+    from axolotl_b200.data.synthetic import synthetic_varlen
+
+    torch.manual_seed(seed)
+    model = _tiny(3)
+    inject_lora(model, LoraSpec(r=4, lora_alpha=8, target_modules=list(ALL_LINEAR)))
+    _randomise_lora(model)
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=5e-3, max_grad_norm=1.0)
+    ds = synthetic_varlen(64, 20, 60, 3, 256, 0.25, seed=1)
+    coll = PackedCollator()
+
+    def batches(epoch):
+        for i in range(0, 64, 2):
+            yield coll([[ds[i], ds[i + 1]]])
+
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=list(ALL_LINEAR))
+    args = TrainArgs(output_dir=str(tmp), max_steps=max_steps, gradient_accumulation_steps=2, learning_rate=5e-3,
+                     save_steps=3, save_strategy="steps", save_total_limit=2, resume_from_checkpoint=resume)
+    tr = Trainer(model, opt, make_lr_lambda("linear", 8, 2), args, batches, total_steps=8,
+                 save_fn=lambda t, d: save_adapter(model, spec, d))
+    if resume:
+        load_adapter(model, resume)
+    return tr, model, opt
+
+
+def test_trainer_checkpoint_resume_is_exact(tmp_path):
+    tr, model, opt = _make_trainer(tmp_path / "a", 8)
+    hist = tr.train()
+    full = [h["loss"] for h in hist if "loss" in h]
+    assert len(full) == 8
+    cks = sorted(os.listdir(tmp_path / "a"))
+    assert "checkpoint-6" in cks and "checkpoint-3" in cks
+    ck = tmp_path / "a" / "checkpoint-6"
+    for f in ("adapter_model.safetensors", "adapter_config.json", "optimizer.pt", "rng_state.pth", "trainer_state.json", "tokens_state.json"):
+        assert os.path.exists(ck / f), f
+    assert find_last_checkpoint(str(tmp_path / "a")).endswith("checkpoint-6")
+    tr2, model2, _ = _make_trainer(tmp_path / "a", 8, resume=str(ck))
+    hist2 = tr2.train()
+    tail = [h["loss"] for h in hist2 if "loss" in h and h["step"] > 6]
+    assert tail == pytest.approx(full[6:], rel=1e-5)
+    assert tr2.tokens["trainable"] == tr.tokens["trainable"]
+    a = torch.cat([p.detach().reshape(-1) for p in model.parameters() if p.requires_grad])
+    b = torch.cat([p.detach().reshape(-1) for p in model2.parameters() if p.requires_grad])
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_loss_decreases_on_learnable_data():
+    from axolotl_b200.data.collator import PackedCollator
+
+    torch.manual_seed(0)
+    model = _tiny(4)
+    inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules=list(ALL_LINEAR)))
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-2, max_grad_norm=1.0)
+    seq = np.tile(np.arange(3, 35), 4)
+    batch = PackedCollator()([[{"input_ids": seq, "labels": seq}]])
+    tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=30, learning_rate=1e-2), lambda e: [batch])
+    losses = [float(tr.training_step([batch]).item()) for _ in range(30)]
+    assert losses[-1] < 0.85 * losses[0] and losses[-1] < losses[10] < losses[0]
+
+
+def test_merge_sharded_fsdp_weights(tmp_path):
+    full = {"w": torch.randn(8, 4), "b": torch.randn(4)}
+    os.makedirs(tmp_path / "s")
+    for r in range(2):
+        st.save_file({"w": full["w"][r * 4:(r + 1) * 4].contiguous(), "b": full["b"]}, str(tmp_path / "s" / f"shard_rank{r}.safetensors"))
+    json.dump({"world_size": 2, "sharded": ["w"]}, open(tmp_path / "s" / "shard_index.json", "w"))
+    merge_sharded_fsdp_weights(str(tmp_path / "s"), str(tmp_path / "o"), dtype=torch.float32)
+    back = st.load_file(str(tmp_path / "o" / "model.safetensors"))
+    assert torch.equal(back["w"], full["w"]) and torch.equal(back["b"], full["b"])

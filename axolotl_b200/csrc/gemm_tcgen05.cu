@@ -18,6 +18,8 @@
 //
 // Replaces the cuBLAS calls behind the reference's LoRA kernels (src/axolotl/kernels/lora.py:226-280)
 // and, with the prefetch CTAs, the NCCL all-gather of its FSDP2 units.
+#include <cstdlib>
+
 #include "axb_common.cuh"
 
 namespace {
@@ -391,6 +393,22 @@ int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
   int workers = sm_count - p.g_ctas;
   if (tiles < workers) workers = tiles;
   const int grid = workers + p.g_ctas;
+  static const bool dbg_cluster = getenv("AXB_DEBUG_CLUSTER") != nullptr;
+  if (dbg_cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid & ~1, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p);
+  }
   kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tA, tB, tA2, tB2, p);
   return (int)cudaGetLastError();
 }
@@ -571,4 +589,336 @@ extern "C" int axb_allgather_rows(const unsigned long long* peer_bases,
   }
   gather_only_kernel<<<pf.ctas, kThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return (int)cudaGetLastError();
+}
+
+// =================================================================================================
+// CTA-pair variant: 256 x 256 output tile per cluster of two CTAs (tcgen05.mma.cta_group::2).
+// Each CTA stages its own 128 rows of A and its own 128 rows (columns of C) of B, so a k block
+// costs 32 KB of shared memory per CTA instead of 48 KB: six pipeline stages instead of four and
+// half the B traffic per FLOP. Rank 0 of the pair issues every MMA; both CTAs run a TMA producer
+// and four epilogue warps on their own half of the accumulator.
+// =================================================================================================
+namespace {
+
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = 128 * BK * 2;       // 16 KB
+constexpr int P_B_BYTES = 128 * BK * 2;       // 16 KB (this CTA's half of the 256-wide B tile)
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_TMEM_COLS = 512;              // 2 accumulator stages x 256 columns
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                          const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + P_STAGES * P_A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // one per CTA: this CTA's TMA loads of the stage
+  uint64_t* empty_bar = bars + P_STAGES;           // one per CTA, signalled by the pair commit
+  uint64_t* tfull_bar = bars + 2 * P_STAGES;       // one per CTA
+  uint64_t* tempty_bar = bars + 2 * P_STAGES + 2;  // used in rank 0 only (8 arrivals)
+  uint64_t* peer_full_bar = bars + 2 * P_STAGES + 4;  // rank 0 only: the partner's stage has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * P_STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_workers = (int)gridDim.x - p.g_ctas;  // even; gather CTAs come in whole clusters
+  if ((int)blockIdx.x >= n_workers) {
+    gather_cta_body(p, (int)blockIdx.x - n_workers, p.g_ctas, smem, bars);
+    return;
+  }
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = n_workers >> 1;
+
+  const int num_m = (p.M + 255) / 256;
+  const int num_n = (p.N + 255) / 256;
+  const int nk_main = (p.K + BK - 1) / BK;
+  const int nk_ext = (p.K2 + BK - 1) / BK;
+  const int nk_total = nk_main + nk_ext;
+  const int total_tiles = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+      mbar_init(&peer_full_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 8);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_slot, P_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // barriers of both CTAs are initialised before any remote arrive / TMA credit
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+        int m_blk, n_blk, split;
+        decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
+        for (int kb = 0; kb < nk_total; ++kb) {
+          if (!mbar_wait_spin(&empty_bar[stage], phase ^ 1, p.status, AXB_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint64_t* fb = &full_bar[stage];
+          mbar_expect_tx(fb, P_STAGE_BYTES);
+          const bool ext = kb >= nk_main;
+          const CUtensorMap* ma = ext ? &tmA2 : &tmA;
+          const CUtensorMap* mb = ext ? &tmB2 : &tmB;
+          const int k0 = (ext ? kb - nk_main : kb) * BK;
+          uint8_t* a_dst = sA + stage * P_A_BYTES;
+          uint8_t* b_dst = sB + stage * P_B_BYTES;
+          const int m0 = m_blk * 256 + (int)rank * 128;
+          const int n0 = n_blk * 256 + (int)rank * 128;
+          if (!A_MN) {
+            tma_load_2d(a_dst, ma, fb, k0, m0);
+          } else {
+            tma_load_2d(a_dst, ma, fb, m0, k0);
+            tma_load_2d(a_dst + 8192, ma, fb, m0 + 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, mb, fb, k0, n0);
+          } else {
+            tma_load_2d(b_dst, mb, fb, n0, k0);
+            tma_load_2d(b_dst + 8192, mb, fb, n0 + 64, k0);
+          }
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ rank 1: relay "stage landed" to rank 0
+    if (lane == 0 && rank == 1) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+        for (int kb = 0; kb < nk_total; ++kb) {
+          if (!mbar_wait_spin(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_cluster(mapa_u32(smem_u32(&peer_full_bar[stage]), 0));
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    // ------------------------------------------------------------ MMA issuer (rank 0 only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, 256, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait_spin(&tempty_bar[acc], acc_phase ^ 1, p.status, AXB_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < nk_total; ++kb) {
+          if ((!mbar_wait_spin(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL) ||
+                                !mbar_wait_spin(&peer_full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * P_A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * P_B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_addr + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          if (p.splits == 2) umma_commit_pair_mc(&empty_bar[stage]);
+          else umma_commit_pair_both(&empty_bar[stage]);  // frees the stage in both CTAs
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (p.splits == 2) umma_commit_pair_mc(&tfull_bar[acc]);
+        else umma_commit_pair_both(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (both CTAs)
+    const int lane_group = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
+      int m_blk, n_blk, split;
+      decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_spin(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long row = (long long)m_blk * 256 + rank * 128 + lane_group * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * 256;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * 256 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full_chunk = col0 + 32 <= p.N;
+        if (p.out_mode == 0) {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+          const __nv_bfloat16* irow =
+              p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + row * p.ldcin + col0 : nullptr;
+          if (full_chunk && (p.ldc & 7) == 0 && (!irow || (p.ldcin & 7) == 0)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (irow) {
+                uint4 in = *reinterpret_cast<const uint4*>(irow + q * 8);
+                const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = unpack_bf16x2(w[e]);
+                  v[q * 8 + 2 * e] += p.beta * f.x;
+                  v[q * 8 + 2 * e + 1] += p.beta * f.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(crow + q * 8) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+              float x = v[j];
+              if (irow) x += p.beta * __bfloat162float(irow[j]);
+              crow[j] = __float2bfloat16(x);
+            }
+          }
+        } else {
+          float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+          const float* irow = p.Cin ? reinterpret_cast<const float*>(p.Cin) + row * p.ldcin + col0 : nullptr;
+          for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = v[j] + (irow ? p.beta * irow[j] : 0.f);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // neither CTA may leave (and release smem / TMEM) while its partner still signals it
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, P_TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2, const CUtensorMap& tB2,
+                GemmParams p, int sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  p.g_ctas &= ~1;  // whole clusters only
+  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  int workers = (sms - p.g_ctas) & ~1;
+  if (2 * tiles < workers) workers = 2 * tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(workers + p.g_ctas, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p);
+}
+
+}  // namespace
+
+// CTA-pair GEMM (same contract as axb_gemm_bf16_prefetch with bn = 256, splits = 1, out_mode 0/1).
+extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                                  void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
+                                  const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
+                                  float alpha, float beta, int out_mode,
+                                  const unsigned long long* pf_peer_bases, unsigned long long pf_shard_offset,
+                                  unsigned long long pf_shard_bytes, int pf_world, void* pf_dst, int pf_ctas,
+                                  int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
+  if ((out_mode & 0xF) != 0 && (out_mode & 0xF) != 1) return -3;
+  CUtensorMap tA, tB, tA2, tB2;
+  int rc = 0;
+  rc |= a_mn ? axb_make_tmap_2d(&tA, A, K, M, lda, 64, 64) : axb_make_tmap_2d(&tA, A, M, K, lda, 128, 64);
+  rc |= b_mn ? axb_make_tmap_2d(&tB, B, K, N, ldb, 64, 64) : axb_make_tmap_2d(&tB, B, N, K, ldb, 128, 64);
+  if (K2 > 0) {
+    rc |= a_mn ? axb_make_tmap_2d(&tA2, A2, K2, M, lda2, 64, 64) : axb_make_tmap_2d(&tA2, A2, M, K2, lda2, 128, 64);
+    rc |= b_mn ? axb_make_tmap_2d(&tB2, B2, K2, N, ldb2, 64, 64) : axb_make_tmap_2d(&tB2, B2, N, K2, ldb2, 128, 64);
+  } else {
+    tA2 = tA;
+    tB2 = tB;
+  }
+  if (rc) return -4;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
+  p.C = C; p.Cin = Cin; p.ldc = ldc; p.ldcin = ldcin;
+  p.alpha = alpha; p.beta = beta; p.out_mode = out_mode & 0xF; p.splits = (out_mode >> 4) ? (out_mode >> 4) + 1 : 1; p.status = status;
+  p.group_m = 4;  // bands of 4 x 256 rows
+  PrefetchArgs pf;
+  pf.peer_bases = pf_peer_bases; pf.shard_offset = pf_shard_offset; pf.shard_bytes = pf_shard_bytes;
+  pf.world = pf_world; pf.dst = pf_dst; pf.ctas = pf_ctas;
+  if ((rc = fill_prefetch(p, &pf)) != 0) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return launch_pair<false, false>(tA, tB, tA2, tB2, p, sm_count(), st);
+  if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, p, sm_count(), st);
+  if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, p, sm_count(), st);
+  return launch_pair<true, true>(tA, tB, tA2, tB2, p, sm_count(), st);
 }

@@ -23,6 +23,8 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _CUDA_SIGS = {
     "axb_gemm_bf16": [vp, i64, i32, vp, i64, i32, vp, i64, vp, i64, i32, i32, i32, vp, i64, vp, i64,
                       i32, f32, f32, i32, i32, i32, vp, vp],
+    "axb_gemm_bf16_pair": [vp, i64, i32, vp, i64, i32, vp, i64, vp, i64, i32, i32, i32, vp, i64, vp, i64,
+                           i32, f32, f32, i32, vp, C.c_ulonglong, C.c_ulonglong, i32, vp, i32, vp, vp],
     "axb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
     "axb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_rope_qk": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp, vp, vp, f32, vp],

@@ -7,11 +7,17 @@ pair is the K-extension that fuses a LoRA update into the same accumulator tile.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
 
 _SM = 148
+# CTA-pair (cta_group::2, 256x256 tiles) kernel for large GEMMs. Numerically validated, but its
+# TMA-fed main loop currently runs at half the rate of the single-CTA kernel (the MMA-only rate
+# reaches the cuBLAS peak), so it is opt-in: AXB_GEMM_PAIR=1.
+USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "0") == "1"
 
 
 def _pick_bn(M: int, N: int) -> int:
@@ -108,6 +114,15 @@ def gemm(
             raise ValueError("c_in must be row-major with the output dtype")
     if bn is None:
         bn = _pick_bn(M, N)
+    if USE_PAIR and bn == 256 and not accumulate and M >= 512 and N >= 512 and (M // 256) * (N // 256) >= 74:
+        rc = lib.axb_gemm_bf16_pair(
+            a.data_ptr(), a.stride(0), int(trans_a), b.data_ptr(), b.stride(0), int(trans_b),
+            out.data_ptr(), out.stride(0), _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
+            _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
+            K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, None, 0, 0, 0, None, 0,
+            _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "axb_gemm_bf16_pair")
+        return out
     rc = lib.axb_gemm_bf16(
         a.data_ptr(), a.stride(0), int(trans_a),
         b.data_ptr(), b.stride(0), int(trans_b),

@@ -39,6 +39,12 @@ struct GemmParams {
   int splits;
   int group_m;  // m tiles per rasterisation band (the A rows of a band stay L2 resident)
   int* status;
+  // out_mode 3: bf16 reduce-add of every tile into red_mc (an NVSwitch multicast address: the add
+  // lands in the buffer of every GPU bound to it = all-reduce inside the epilogue);
+  // out_mode 4: same through plain peer atomics into red_ptrs[0..red_world)
+  void* red_mc;
+  unsigned long long red_ptrs[8];
+  int red_world;
   // prefetch of a row-sharded matrix by the trailing g_ctas CTAs (0 = none)
   int g_ctas;
   int g_world;
@@ -356,6 +362,29 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int j = 0; j < 32 && col0 + j < p.N; ++j)
               crow[j] = v[j] + (irow ? p.beta * irow[j] : 0.f);
           }
+        } else if (p.out_mode == 3 || p.out_mode == 4) {
+          // all-reduce fused into the epilogue (requires N % 8 == 0 and ldc % 8 == 0)
+          const long long off = row * p.ldc + col0;
+          const int nvec = full_chunk ? 4 : ((p.N - col0) >> 3);
+          for (int q = 0; q < nvec; ++q) {
+            const uint32_t w0 = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            const uint32_t w1 = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            const uint32_t w2 = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            const uint32_t w3 = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            if (p.out_mode == 3) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.red_mc) + off + q * 8;
+              asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                           "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                           : "memory");
+            } else {
+              for (int r2 = 0; r2 < p.red_world; ++r2) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.red_ptrs[r2]) + off + q * 8;
+                asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                             "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                             : "memory");
+              }
+            }
+          }
         } else {
           float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
           for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(crow + j, v[j]);
@@ -562,6 +591,46 @@ extern "C" int axb_gemm_bf16_prefetch(const void* A, long long lda, int a_mn, co
   pf.ctas = pf_ctas;
   return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, Cin, ldcin, M, N, K, A2, lda2, B2, ldb2, K2,
                     alpha, beta, out_mode, splits, bn, status, stream, &pf);
+}
+
+// GEMM whose epilogue all-reduces the result over NVLink: every rank adds its partial product
+// into the symmetric bf16 buffer of every rank (pre-zeroed; `red_mc` = multicast address of that
+// buffer, or NULL to use plain peer atomics through the HOST array red_ptrs[red_world]). The sum
+// is complete on a rank once all ranks have finished the kernel (barrier afterwards).
+extern "C" int axb_gemm_bf16_allreduce(const void* A, long long lda, int a_mn, const void* B, long long ldb,
+                                       int b_mn, long long ldc, int M, int N, int K, const void* A2,
+                                       long long lda2, const void* B2, long long ldb2, int K2, float alpha,
+                                       int bn, void* red_mc, const unsigned long long* red_ptrs, int red_world,
+                                       int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (ldc & 7) || red_world < 1 || red_world > 8) return -2;
+  if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
+  CUtensorMap tA, tB, tA2, tB2;
+  int rc = 0;
+  rc |= a_mn ? axb_make_tmap_2d(&tA, A, K, M, lda, 64, 64) : axb_make_tmap_2d(&tA, A, M, K, lda, BM, 64);
+  rc |= b_mn ? axb_make_tmap_2d(&tB, B, K, N, ldb, 64, 64) : axb_make_tmap_2d(&tB, B, N, K, ldb, bn, 64);
+  if (K2 > 0) {
+    rc |= a_mn ? axb_make_tmap_2d(&tA2, A2, K2, M, lda2, 64, 64) : axb_make_tmap_2d(&tA2, A2, M, K2, lda2, BM, 64);
+    rc |= b_mn ? axb_make_tmap_2d(&tB2, B2, K2, N, ldb2, 64, 64) : axb_make_tmap_2d(&tB2, B2, N, K2, ldb2, bn, 64);
+  } else {
+    tA2 = tA;
+    tB2 = tB;
+  }
+  if (rc) return -4;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
+  p.ldc = ldc; p.alpha = alpha; p.splits = 1; p.status = status; p.group_m = 8;
+  p.out_mode = red_mc ? 3 : 4;
+  p.red_mc = red_mc;
+  p.red_world = red_world;
+  for (int i = 0; i < red_world; ++i) p.red_ptrs[i] = red_ptrs[i];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 64: return dispatch_major<64>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    case 128: return dispatch_major<128>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    case 256: return dispatch_major<256>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    default: return -5;
+  }
 }
 
 // Stand-alone all-gather of a row-sharded matrix into `dst` with `ctas` CTAs (0 = one per SM).

@@ -144,7 +144,8 @@ def get_peft_state_dict(model) -> dict:
     for name, m in model.fused_linears():
         if m.lora_A is None:
             continue
-        for sub, (A, B) in m.peft_tensors().items():
+        tensors = m.gathered_peft_tensors() if hasattr(m, "gathered_peft_tensors") else m.peft_tensors()
+        for sub, (A, B) in tensors.items():
             base = f"base_model.model.{_hf_path(name, sub)}"
             sd[f"{base}.lora_A.weight"] = A.detach()
             sd[f"{base}.lora_B.weight"] = B.detach()

@@ -225,7 +225,7 @@ class CausalLM(nn.Module):
     # ------------------------------------------------------------------ adapters
     def fused_linears(self):
         for name, m in self.named_modules():
-            if isinstance(m, FusedLinear):
+            if isinstance(m, FusedLinear) or getattr(m, "tp", None) is not None and hasattr(m, "lora_blocks"):
                 yield name, m
 
     def refresh_lora_shadows(self):

@@ -59,13 +59,15 @@ class ParallelRuntime:
         return t
 
     def optimizer_alloc(self):
+        if self.tp is not None:
+            return None
         if self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
             return self.symmetric_alloc
         return None
 
     def attach_optimizer(self, opt):
         self.opt = opt
-        if self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
+        if self.tp is None and self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
             from .symm import PeerSync
 
             self.sync = PeerSync(self.device, self.dp_group)
@@ -113,9 +115,45 @@ class ParallelRuntime:
         r = float(t.item())
         return int(r) if isinstance(v, int) else r
 
+    # ------------------------------------------------------------------ tensor parallel
+    def apply_tp(self, model):
+        n = self.mesh.size("tp")
+        if n <= 1:
+            return
+        from .tp import TPContext, apply_tensor_parallel
+
+        cfg = model.config
+        max_elems = getattr(self, "tp_max_tokens", 16384) * max(cfg.hidden_size, 1)
+        self.tp = TPContext(self.device, self.mesh.group("tp"), n, self.mesh.coord("tp"), max_elems)
+        apply_tensor_parallel(model, self.tp)
+
+    def _tp_step(self, opt, lr):
+        """TP (x DP): sum replicated gradients over the TP group, average over data parallel ranks,
+        global norm = replicated part + sum over TP of the sharded part; all on the device."""
+        from ..ops.optim import grad_sumsq
+
+        opt._fold_autograd_grads()
+        tp_group = self.tp.group
+        total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for g in opt.groups:
+            split = g["tp_split"]
+            if split > 0:
+                dist.all_reduce(g["grad"][:split], group=tp_group)
+            if self.dp_size > 1:
+                dist.all_reduce(g["grad"], group=self.dp_group)
+            grad_sumsq(g["grad"][:split], total) if split > 0 else None
+            if split < g["grad"].numel():
+                sh = grad_sumsq(g["grad"][split:])
+                dist.all_reduce(sh, group=tp_group)
+                total += sh
+        opt.grad_scale = 1.0 / self.dp_size
+        return opt.step(lr=lr, gnorm_sq=total)
+
     def optimizer_step(self, opt, lr):
         """Gradient synchronisation + clipping + optimizer update. Returns the squared global
         gradient norm (device scalar) or None."""
+        if self.tp is not None:
+            return self._tp_step(opt, lr)
         if self.dp_size <= 1:
             return opt.step(lr=lr)
         if self.backend == "fused" and self.sync is not None:
@@ -169,8 +207,26 @@ def init_distributed(backend=None, timeout_s=None):
     dist.init_process_group(backend, timeout=datetime.timedelta(seconds=t), **kw)
 
 
+def create_runtime(*, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, backend=None):
+    """Mesh + runtime for an already initialised process group (no model changes yet). Call
+    ``apply_tp(model)`` before adapters are injected and ``shard_model(model)`` afterwards."""
+    world = dist.get_world_size()
+    spec = MeshSpec.from_cfg(world, tensor_parallel_size=tp, context_parallel_size=cp, dp_shard_size=dp_shard,
+                             dp_replicate_size=dp_replicate, expert_parallel_size=ep)
+    device = torch.device(device)
+    if backend is None:
+        backend = os.environ.get("AXB_COMM", "fused" if device.type == "cuda" else "collective")
+    return ParallelRuntime(DeviceMesh(spec, dist.get_rank()), device, backend)
+
+
 def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, backend=None):
     """Creates the mesh + runtime for an already initialised process group and shards the model."""
+    if tp > 1 or cp > 1 or ep > 1:
+        rt = create_runtime(device=device, dp_shard=dp_shard, dp_replicate=dp_replicate, tp=tp, cp=cp, ep=ep,
+                            backend=backend)
+        rt.apply_tp(model)
+        rt.shard_model(model)
+        return rt
     world = dist.get_world_size()
     spec = MeshSpec.from_cfg(world, tensor_parallel_size=tp, context_parallel_size=cp, dp_shard_size=dp_shard,
                              dp_replicate_size=dp_replicate, expert_parallel_size=ep)

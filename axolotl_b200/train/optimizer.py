@@ -62,6 +62,8 @@ class FlatAdamW:
             params = [(n, p) for n, p in g["params"] if p.requires_grad]
             if not params:
                 continue
+            # tensor-parallel replicated parameters first, sharded ones last: two contiguous ranges
+            params.sort(key=lambda np_: bool(getattr(np_[1], "_tp_sharded", False)))
             dev = params[0][1].device
             total = sum(p.numel() for _, p in params)
             # 16-byte aligned slots so bf16 shadows stay usable as TMA / vector operands
@@ -91,7 +93,9 @@ class FlatAdamW:
                     raise TypeError(f"unsupported parameter dtype {p.dtype} for {n}")
                 p._axb_grad = gview
                 entries.append((n, p, o, k))
+            tp_split = next((o for (n, p, o, k) in entries if getattr(p, "_tp_sharded", False)), total)
             self.groups.append({
+                "tp_split": tp_split,
                 "name": g["name"], "lr_scale": g.get("lr_scale", 1.0), "weight_decay": g.get("weight_decay", 0.0),
                 "master": master, "grad": grad, "shadow": shadow, "entries": entries,
                 "exp_avg": torch.zeros_like(master), "exp_avg_sq": torch.zeros_like(master),

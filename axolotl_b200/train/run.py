@@ -251,19 +251,23 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         cfg["pad_token_id"] = tokenizer.pad_token_id
 
     model = build_model(cfg, device)
+    parallel = None
+    if world > 1:
+        from ..parallel.runtime import create_runtime
+
+        parallel = create_runtime(device=device, dp_shard=cfg.get("dp_shard_size"),
+                                  dp_replicate=cfg.get("dp_replicate_size") or 1, tp=cfg.get("tensor_parallel_size") or 1,
+                                  cp=cfg.get("context_parallel_size") or 1, ep=cfg.get("expert_parallel_size") or 1)
+        parallel.tp_max_tokens = cfg["micro_batch_size"] * cfg["sequence_len"]
+        parallel.apply_tp(model)          # shards projections before adapters are created
     spec = setup_adapter(cfg, model)
     pm.call("post_model_load", cfg, model)
     if cfg.get("gradient_checkpointing") or (cfg.get("fsdp_config") or {}).get("activation_checkpointing"):
         model.enable_gradient_checkpointing(True)
 
-    parallel = None
     dp_size, dp_rank = 1, 0
-    if world > 1:
-        from ..parallel.runtime import build_parallel
-
-        parallel = build_parallel(model, device=device, dp_shard=cfg.get("dp_shard_size"),
-                                  dp_replicate=cfg.get("dp_replicate_size") or 1, tp=cfg.get("tensor_parallel_size") or 1,
-                                  cp=cfg.get("context_parallel_size") or 1, ep=cfg.get("expert_parallel_size") or 1)
+    if parallel is not None:
+        parallel.shard_model(model)       # FSDP row-sharding of the frozen weights
         dp_size, dp_rank = parallel.dp_size, parallel.dp_rank
 
     opt = build_optimizer(cfg, model, parallel)

@@ -339,3 +339,42 @@ extern "C" int axb_peer_allreduce_f32(const unsigned long long* buf_ptrs,
   peer_allreduce_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// All-gather by store: every rank writes its [rows, width] bf16 block (row stride src_ld) into
+// rows [row_off, row_off + rows) of the symmetric [*, width] buffer of EVERY rank, through the
+// NVSwitch multicast address (multimem.st) or plain peer stores. Used to publish the rotated K / V
+// rows of a context-parallel rank to all ranks before attention.
+namespace {
+__global__ void allgather_store_kernel(const __nv_bfloat16* __restrict__ src, long long src_ld, long long rows,
+                                       int width, long long row_off, __nv_bfloat16* mc, PeerPtrs dst, int world) {
+  const int vec_per_row = width / 8;
+  const long long n = rows * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = (int)(i % vec_per_row) * 8;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + r * src_ld + c);
+    const long long off = (row_off + r) * width + c;
+    if (mc) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc + off), "r"(v.x),
+                   "r"(v.y), "r"(v.z), "r"(v.w)
+                   : "memory");
+    } else {
+      for (int p = 0; p < world; ++p) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[p]) + off) = v;
+    }
+  }
+}
+}  // namespace
+
+extern "C" int axb_allgather_store(const void* src, long long src_ld, long long rows, int width, long long row_off,
+                                   void* mc, const unsigned long long* dst_ptrs, int world, void* stream) {
+  if (rows <= 0) return 0;
+  if ((width & 7) || (src_ld & 7)) return -2;
+  PeerPtrs dst;
+  if (fill_ptrs(dst, dst_ptrs, world)) return -2;
+  const long long n = rows * (width / 8);
+  int grid = (int)((n + 255) / 256 > 148 * 8 ? 148 * 8 : (n + 255) / 256);
+  allgather_store_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)src, src_ld, rows, width, row_off, (__nv_bfloat16*)mc, dst, world);
+  return (int)cudaGetLastError();
+}

@@ -34,6 +34,15 @@ struct AttnParams {
   __nv_bfloat16* dkv;  // fused gradient buffer, same layout as qkv (k and v blocks are written)
   long long dkv_ld;
   float scale;
+  // context parallelism: the q / out / lse / dO / dq buffers hold only the rows
+  // [q_row_off, q_row_off + q_rows) of the global token stream, K and V are global.
+  int q_row_off, q_rows;
+  // backward with context parallelism: dK / dV tiles are reduce-added (bf16x2 atomics over
+  // NVLink) into the buffer of the rank that owns the kv rows: rank = row / cp_chunk.
+  int dk_col0, dv_col0;  // column offsets of the dK / dV blocks in the gradient buffer
+  int cp_world;
+  long long cp_chunk;
+  unsigned long long cp_dkv_ptrs[8];
 };
 
 AXB_DEVICE float fast_exp2(float x) {
@@ -64,7 +73,8 @@ struct FwdCfg {
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-    flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnParams p) {
+    flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_qkv,
+                     const AttnParams p) {
   using C = FwdCfg<D>;
   const int tile_id = blockIdx.y;
   if (tile_id >= p.n_tiles) return;
@@ -126,8 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_expect_tx(q_full, C::TILE_BYTES);
 #pragma unroll
       for (int h = 0; h < C::HALVES; ++h)
-        tma_load_2d(sQ + h * HALF_BYTES, &tm_qkv, q_full, p.q_col0 + head * D + h * 64,
-                    doc_start + q0);
+        tma_load_2d(sQ + h * HALF_BYTES, &tm_q, q_full, p.q_col0 + head * D + h * 64,
+                    doc_start + q0 - p.q_row_off);
       for (int j = 0; j < n_blocks; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -294,9 +304,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const uint32_t pv_addr = tmem_base + lane_off + C::PV_COL + pst * D;
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
-        const bool row_ok = q_idx < doc_len;
-        __nv_bfloat16* orow =
-            p.out + (long long)(doc_start + q_idx) * p.out_ld + (long long)head * D;
+        const long long lrow = (long long)doc_start + q_idx - p.q_row_off;  // row in the local buffers
+        const bool row_ok = q_idx < doc_len && lrow >= 0 && lrow < p.q_rows;
+        __nv_bfloat16* orow = p.out + lrow * p.out_ld + (long long)head * D;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t vr[32];
@@ -319,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        if (row_ok) p.lse2[(long long)head * p.T + doc_start + q_idx] = m + log2f(l);
+        if (row_ok) p.lse2[(long long)head * p.q_rows + lrow] = m + log2f(l);
       }
     }
   }
@@ -392,9 +402,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int group = p.Hq / p.Hk;
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, kv0 = ti.z;
-  const int q_first = kv0 / 64;                 // first 64-row q tile touching the diagonal
-  const int n_qt = (doc_len + 63) / 64 - q_first;  // q tiles per head
+  // 64-row q tiles at or below the diagonal that intersect this rank's q rows
+  int q_first = kv0 / 64;
+  int q_last = (doc_len + 63) / 64;
+  {
+    const int lo = p.q_row_off - doc_start, hi = p.q_row_off + p.q_rows - doc_start;
+    if (lo > 0) q_first = max(q_first, lo / 64);
+    q_last = min(q_last, (hi + 63) / 64);
+  }
+  const int n_qt = q_last - q_first;  // q tiles per head
   const int n_iter = n_qt * group;
+  if (n_iter <= 0) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -459,7 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         const int head = kv_head * group + it / n_qt;
-        const int qrow = doc_start + (q_first + it % n_qt) * 64;
+        const int qrow = doc_start + (q_first + it % n_qt) * 64 - p.q_row_off;
         if (!mbar_wait(&q_empty[st], ph ^ 1, p.status, AXB_TIMEOUT_EMPTY)) break;
         mbar_expect_tx(&q_full[st], 2 * C::Q_BYTES);
 #pragma unroll
@@ -547,9 +565,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         float* dst = (st_tid < 64 ? s_lse : s_delta) + (it & 1) * 64;
         const int i = st_tid & 63;
         const int q = qt0 + i;
-        float val = 0.f;
-        if (q < doc_len) {
-          const long long off = (long long)head * p.T + doc_start + q;
+        // rows outside the document or outside this rank's q window get lse = +inf -> P = 0
+        float val = st_tid < 64 ? INFINITY : 0.f;
+        const long long lrow = (long long)doc_start + q - p.q_row_off;
+        if (q < doc_len && lrow >= 0 && lrow < p.q_rows) {
+          const long long off = (long long)head * p.q_rows + lrow;
           val = st_tid < 64 ? p.lse2[off] : p.delta[off];
         }
         dst[i] = val;
@@ -616,9 +636,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int q = qt0 + c * 32 + i;
-            if (q < doc_len)
-              atomicAdd(p.dq_acc + (long long)(doc_start + q) * p.out_ld + (long long)head * D + r,
-                        __uint_as_float(qr[i]));
+            const long long lrow = (long long)doc_start + q - p.q_row_off;
+            if (q < doc_len && lrow >= 0 && lrow < p.q_rows)
+              atomicAdd(p.dq_acc + lrow * p.out_ld + (long long)head * D + r, __uint_as_float(qr[i]));
           }
         }
       }
@@ -629,10 +649,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (ok && mbar_wait(acc_full, 0, p.status, AXB_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool row_ok = kv_idx < doc_len && n_iter > 0;
-      __nv_bfloat16* krow = p.dkv + (long long)(doc_start + kv_idx) * p.dkv_ld + p.k_col0 +
-                            (long long)kv_head * D;
-      __nv_bfloat16* vrow = p.dkv + (long long)(doc_start + kv_idx) * p.dkv_ld + p.v_col0 +
-                            (long long)kv_head * D;
+      const long long grow = (long long)doc_start + kv_idx;  // global kv row
+      __nv_bfloat16* base = p.dkv;
+      long long brow = grow;
+      if (p.cp_world > 1) {
+        const long long owner = min(grow / p.cp_chunk, (long long)p.cp_world - 1);
+        base = reinterpret_cast<__nv_bfloat16*>(p.cp_dkv_ptrs[owner]);
+        brow = grow - owner * p.cp_chunk;
+      }
+      __nv_bfloat16* krow = base + brow * p.dkv_ld + p.dk_col0 + (long long)kv_head * D;
+      __nv_bfloat16* vrow = base + brow * p.dkv_ld + p.dv_col0 + (long long)kv_head * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t a[32], b[32];
@@ -651,8 +677,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             w.y = pack_bf16x2(__uint_as_float(b[q * 8 + 2]), __uint_as_float(b[q * 8 + 3]));
             w.z = pack_bf16x2(__uint_as_float(b[q * 8 + 4]), __uint_as_float(b[q * 8 + 5]));
             w.w = pack_bf16x2(__uint_as_float(b[q * 8 + 6]), __uint_as_float(b[q * 8 + 7]));
-            *reinterpret_cast<uint4*>(krow + c * 32 + q * 8) = u;
-            *reinterpret_cast<uint4*>(vrow + c * 32 + q * 8) = w;
+            if (p.cp_world > 1) {
+              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(
+                               krow + c * 32 + q * 8),
+                           "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                           : "memory");
+              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(
+                               vrow + c * 32 + q * 8),
+                           "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w)
+                           : "memory");
+            } else {
+              *reinterpret_cast<uint4*>(krow + c * 32 + q * 8) = u;
+              *reinterpret_cast<uint4*>(vrow + c * 32 + q * 8) = w;
+            }
           }
         }
       }
@@ -684,7 +721,7 @@ __global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* 
 }
 
 template <int D>
-int launch_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
   using C = FwdCfg<D>;
   auto kern = flash_fwd_kernel<D>;
   static bool attr = false;
@@ -694,7 +731,7 @@ int launch_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
     attr = true;
   }
   dim3 grid(p.Hq, p.n_tiles);
-  kern<<<grid, kThreads, C::SMEM, st>>>(tm, p);
+  kern<<<grid, kThreads, C::SMEM, st>>>(tq, tm, p);
   return (int)cudaGetLastError();
 }
 template <int D>
@@ -714,18 +751,27 @@ int launch_bwd(const CUtensorMap& tkv, const CUtensorMap& tq, const CUtensorMap&
 }
 }  // namespace
 
-// qkv: fused projection [T, ld] bf16 with q heads at column q_col0, k heads at k_col0, v at
-// v_col0 (head-major, D per head). tiles: device int4 array built by axb_build_attn_tiles
-// (tile rows = 128). out: [T, out_ld] bf16, lse2: [Hq, T] fp32.
-extern "C" int axb_flash_varlen_fwd(const void* qkv, long long ld, long long T, int Hq, int Hk,
-                                    int D, int q_col0, int k_col0, int v_col0, const void* tiles,
-                                    int n_tiles, void* out, long long out_ld, float* lse2,
-                                    float softmax_scale, int* status, void* stream) {
-  if (T <= 0 || n_tiles <= 0) return 0;
+namespace {
+
+struct AttnGeom {
+  const void* q_buf;   // rows [q_row_off, q_row_off + q_rows) of the token stream; q heads at q_col0
+  long long q_ld;
+  long long q_rows;
+  int q_row_off;
+  const void* kv_buf;  // all kv_rows rows; k heads at k_col0, v heads at v_col0
+  long long kv_ld;
+  long long kv_rows;
+};
+
+int flash_fwd_impl(const AttnGeom& g, int Hq, int Hk, int D, int q_col0, int k_col0, int v_col0,
+                   const void* tiles, int n_tiles, void* out, long long out_ld, float* lse2,
+                   float softmax_scale, int* status, void* stream) {
+  if (g.q_rows <= 0 || n_tiles <= 0) return 0;
   if (D != 64 && D != 128) return -2;
-  if ((ld & 7) || (out_ld & 7) || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7)) return -3;
-  CUtensorMap tm;
-  if (axb_make_tmap_2d(&tm, qkv, T, ld, ld, 128, 64)) return -4;
+  if ((g.q_ld & 7) || (g.kv_ld & 7) || (out_ld & 7) || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7)) return -3;
+  CUtensorMap tq, tkv;
+  if (axb_make_tmap_2d(&tq, g.q_buf, g.q_rows, g.q_ld, g.q_ld, 128, 64)) return -4;
+  if (axb_make_tmap_2d(&tkv, g.kv_buf, g.kv_rows, g.kv_ld, g.kv_ld, 128, 64)) return -4;
   AttnParams p = {};
   p.tiles = reinterpret_cast<const int4*>(tiles);
   p.n_tiles = n_tiles;
@@ -737,30 +783,29 @@ extern "C" int axb_flash_varlen_fwd(const void* qkv, long long ld, long long T, 
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.out_ld = out_ld;
   p.lse2 = lse2;
-  p.T = T;
+  p.T = g.q_rows;
+  p.q_row_off = g.q_row_off;
+  p.q_rows = (int)g.q_rows;
   p.sl2 = softmax_scale * 1.4426950408889634f;
   p.scale = softmax_scale;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  return D == 128 ? launch_fwd<128>(tm, p, st) : launch_fwd<64>(tm, p, st);
+  return D == 128 ? launch_fwd<128>(tq, tkv, p, st) : launch_fwd<64>(tq, tkv, p, st);
 }
 
-// Backward. dout/out: [T, o_ld] bf16; dqkv: fused gradient buffer with the layout of qkv (all
-// three blocks are written); dq_acc: fp32 [T, Hq*D] scratch (zeroed here); delta: fp32 [Hq, T]
-// scratch. tiles must have been built with 128-row tiles.
-extern "C" int axb_flash_varlen_bwd(const void* qkv, long long ld, const void* dout,
-                                    const void* out, long long o_ld, const float* lse2,
-                                    long long T, int Hq, int Hk, int D, int q_col0, int k_col0,
-                                    int v_col0, const void* tiles, int n_tiles, void* dqkv,
-                                    long long dqkv_ld, float* dq_acc, float* delta,
-                                    float softmax_scale, int* status, void* stream) {
-  if (T <= 0 || n_tiles <= 0) return 0;
+int flash_bwd_impl(const AttnGeom& g, const void* dout, const void* out, long long o_ld, const float* lse2,
+                   int Hq, int Hk, int D, int q_col0, int k_col0, int v_col0, const void* tiles, int n_tiles,
+                   void* dqkv, long long dqkv_ld, int dq_col0, int dk_col0, int dv_col0, float* dq_acc,
+                   float* delta, float softmax_scale, int cp_world, long long cp_chunk,
+                   const unsigned long long* cp_dkv_ptrs, int* status, void* stream) {
+  if (g.q_rows <= 0 || n_tiles <= 0) return 0;
   if (D != 64 && D != 128) return -2;
-  if ((ld & 7) || (o_ld & 7) || (dqkv_ld & 7)) return -3;
+  if ((g.q_ld & 7) || (g.kv_ld & 7) || (o_ld & 7) || (dqkv_ld & 7) || cp_world > 8) return -3;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long T = g.q_rows;
   CUtensorMap tkv, tq, tdo;
-  if (axb_make_tmap_2d(&tkv, qkv, T, ld, ld, 128, 64)) return -4;
-  if (axb_make_tmap_2d(&tq, qkv, T, ld, ld, 64, 64)) return -4;
+  if (axb_make_tmap_2d(&tkv, g.kv_buf, g.kv_rows, g.kv_ld, g.kv_ld, 128, 64)) return -4;
+  if (axb_make_tmap_2d(&tq, g.q_buf, T, g.q_ld, g.q_ld, 64, 64)) return -4;
   if (axb_make_tmap_2d(&tdo, dout, T, (long long)Hq * D, o_ld, 64, 64)) return -4;
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, sizeof(float) * T * Hq * D, st);
   if (e != cudaSuccess) return (int)e;
@@ -781,6 +826,8 @@ extern "C" int axb_flash_varlen_bwd(const void* qkv, long long ld, const void* d
   p.out_ld = (long long)Hq * D;  // leading dimension of dq_acc
   p.lse2 = const_cast<float*>(lse2);
   p.T = T;
+  p.q_row_off = g.q_row_off;
+  p.q_rows = (int)T;
   p.sl2 = softmax_scale * 1.4426950408889634f;
   p.scale = softmax_scale;
   p.status = status;
@@ -788,13 +835,79 @@ extern "C" int axb_flash_varlen_bwd(const void* qkv, long long ld, const void* d
   p.dq_acc = dq_acc;
   p.dkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
   p.dkv_ld = dqkv_ld;
+  p.dk_col0 = dk_col0;
+  p.dv_col0 = dv_col0;
+  p.cp_world = cp_world > 1 ? cp_world : 1;
+  p.cp_chunk = cp_chunk;
+  for (int i = 0; i < 8; ++i) p.cp_dkv_ptrs[i] = (cp_world > 1 && i < cp_world) ? cp_dkv_ptrs[i] : 0ull;
   int rc = D == 128 ? launch_bwd<128>(tkv, tq, tdo, p, st) : launch_bwd<64>(tkv, tq, tdo, p, st);
   if (rc) return rc;
   const long long n = T * (long long)(Hq * D / 4);
   int grid = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-  dq_convert_kernel<<<grid, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, T, Hq * D,
-                                          (long long)Hq * D, dqkv_ld, q_col0);
+  dq_convert_kernel<<<grid, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, T, Hq * D, (long long)Hq * D, dqkv_ld,
+                                          dq_col0);
   return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// qkv: fused projection [T, ld] bf16 with q heads at column q_col0, k heads at k_col0, v at
+// v_col0 (head-major, D per head). tiles: device int4 array built by axb_build_attn_tiles
+// (tile rows = 128). out: [T, out_ld] bf16, lse2: [Hq, T] fp32.
+extern "C" int axb_flash_varlen_fwd(const void* qkv, long long ld, long long T, int Hq, int Hk,
+                                    int D, int q_col0, int k_col0, int v_col0, const void* tiles,
+                                    int n_tiles, void* out, long long out_ld, float* lse2,
+                                    float softmax_scale, int* status, void* stream) {
+  AttnGeom g = {qkv, ld, T, 0, qkv, ld, T};
+  return flash_fwd_impl(g, Hq, Hk, D, q_col0, k_col0, v_col0, tiles, n_tiles, out, out_ld, lse2,
+                        softmax_scale, status, stream);
+}
+
+// Backward. dout/out: [T, o_ld] bf16; dqkv: fused gradient buffer with the layout of qkv (all
+// three blocks are written); dq_acc: fp32 [T, Hq*D] scratch (zeroed here); delta: fp32 [Hq, T]
+// scratch. tiles must have been built with 128-row tiles.
+extern "C" int axb_flash_varlen_bwd(const void* qkv, long long ld, const void* dout,
+                                    const void* out, long long o_ld, const float* lse2,
+                                    long long T, int Hq, int Hk, int D, int q_col0, int k_col0,
+                                    int v_col0, const void* tiles, int n_tiles, void* dqkv,
+                                    long long dqkv_ld, float* dq_acc, float* delta,
+                                    float softmax_scale, int* status, void* stream) {
+  AttnGeom g = {qkv, ld, T, 0, qkv, ld, T};
+  return flash_bwd_impl(g, dout, out, o_ld, lse2, Hq, Hk, D, q_col0, k_col0, v_col0, tiles, n_tiles, dqkv,
+                        dqkv_ld, q_col0, k_col0, v_col0, dq_acc, delta, softmax_scale, 1, 0, nullptr, status,
+                        stream);
+}
+
+// Context-parallel forward: q rows [q_row_off, q_row_off + q_rows) come from the local fused
+// projection `q_buf`; K and V of the WHOLE token stream come from `kv_buf` ([kv_rows, kv_ld], k
+// heads at column 0, v heads at Hk*D), which the ranks filled by storing their rows into every
+// peer's buffer. tiles: (doc_start, doc_len, tile_start) in GLOBAL rows, only tiles that
+// intersect the local q rows. out [q_rows, out_ld], lse2 [Hq, q_rows].
+extern "C" int axb_flash_varlen_fwd_cp(const void* q_buf, long long q_ld, long long q_rows, int q_row_off,
+                                       const void* kv_buf, long long kv_ld, long long kv_rows, int Hq,
+                                       int Hk, int D, const void* tiles, int n_tiles, void* out,
+                                       long long out_ld, float* lse2, float softmax_scale, int* status,
+                                       void* stream) {
+  AttnGeom g = {q_buf, q_ld, q_rows, q_row_off, kv_buf, kv_ld, kv_rows};
+  return flash_fwd_impl(g, Hq, Hk, D, 0, 0, Hk * D, tiles, n_tiles, out, out_ld, lse2, softmax_scale, status,
+                        stream);
+}
+
+// Context-parallel backward: dQ of the local rows goes to the q block of `dqkv` ([q_rows, dqkv_ld],
+// fused layout); the dK / dV tiles this rank computes for ANY kv row are reduce-added over NVLink
+// into the k / v blocks of the owner's gradient buffer cp_dkv_ptrs[row / cp_chunk] (HOST array of
+// peer-mapped addresses, same fused layout, zeroed by the caller before any rank starts).
+extern "C" int axb_flash_varlen_bwd_cp(const void* q_buf, long long q_ld, long long q_rows, int q_row_off,
+                                       const void* kv_buf, long long kv_ld, long long kv_rows,
+                                       const void* dout, const void* out, long long o_ld, const float* lse2,
+                                       int Hq, int Hk, int D, const void* tiles, int n_tiles, void* dqkv,
+                                       long long dqkv_ld, float* dq_acc, float* delta, float softmax_scale,
+                                       int cp_world, long long cp_chunk,
+                                       const unsigned long long* cp_dkv_ptrs, int* status, void* stream) {
+  AttnGeom g = {q_buf, q_ld, q_rows, q_row_off, kv_buf, kv_ld, kv_rows};
+  return flash_bwd_impl(g, dout, out, o_ld, lse2, Hq, Hk, D, 0, 0, Hk * D, tiles, n_tiles, dqkv, dqkv_ld, 0,
+                        Hq * D, (Hq + Hk) * D, dq_acc, delta, softmax_scale, cp_world, cp_chunk, cp_dkv_ptrs,
+                        status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -379,6 +379,10 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     Returns [T, Hq * D].
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if getattr(meta, "cp", False):
+        from ..parallel.cp import flash_varlen_cp
+
+        return flash_varlen_cp(qkv, meta, Hq, Hk, D, scale)
     if qkv.is_cuda:
         return _FlashVarlen.apply(qkv, meta, Hq, Hk, D, scale)
     T = qkv.shape[0]

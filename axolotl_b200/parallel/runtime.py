@@ -38,6 +38,8 @@ class ParallelRuntime:
         self.cp = None
         self.tp = None
         self.ep = None
+        self.reduce_group = self.dp_group   # group over which gradients are reduced
+        self.reduce_size = self.dp_size
 
     # ------------------------------------------------------------------ setup
     def shard_model(self, model):
@@ -52,7 +54,7 @@ class ParallelRuntime:
         """Allocator handed to FlatAdamW so gradients / masters / shadows live in peer-mapped memory."""
         from .symm import SymmBuffer
 
-        buf = SymmBuffer(numel, dtype, self.device, self.dp_group, use_multicast=os.environ.get("AXB_NO_MULTIMEM") != "1")
+        buf = SymmBuffer(numel, dtype, self.device, self.reduce_group, use_multicast=os.environ.get("AXB_NO_MULTIMEM") != "1")
         self._symm.append(buf)
         t = buf.tensor
         t._axb_symm = buf
@@ -61,22 +63,22 @@ class ParallelRuntime:
     def optimizer_alloc(self):
         if self.tp is not None:
             return None
-        if self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
+        if self.backend == "fused" and self.reduce_size > 1 and self.device.type == "cuda":
             return self.symmetric_alloc
         return None
 
     def attach_optimizer(self, opt):
         self.opt = opt
-        if self.tp is None and self.backend == "fused" and self.dp_size > 1 and self.device.type == "cuda":
+        if self.tp is None and self.backend == "fused" and self.reduce_size > 1 and self.device.type == "cuda":
             from .symm import PeerSync
 
-            self.sync = PeerSync(self.device, self.dp_group)
+            self.sync = PeerSync(self.device, self.reduce_group)
             for g in opt.groups:
                 if getattr(g["grad"], "_axb_symm", None) is None:
                     raise RuntimeError("FlatAdamW must be built with alloc=parallel.optimizer_alloc() for the fused backend")
             self._scratch = self.symmetric_alloc(64, torch.float32)
             self._gnorm = torch.zeros(1, dtype=torch.float32, device=self.device)
-            dist.barrier(self.dp_group)
+            dist.barrier(self.reduce_group)
 
     # ------------------------------------------------------------------ trainer interface
     def before_micro_batch(self, last):
@@ -115,8 +117,23 @@ class ParallelRuntime:
         r = float(t.item())
         return int(r) if isinstance(v, int) else r
 
+    # ------------------------------------------------------------------ context parallel
+    def setup_cp(self):
+        n = self.mesh.size("cp")
+        if n <= 1 or self.cp is not None:
+            return
+        from .cp import CPContext
+
+        self.cp = CPContext(self.device, self.mesh.group("cp"), n, self.mesh.coord("cp"))
+        # gradients are SUMMED over cp ranks (each holds a slice of the same sequence) and averaged
+        # over data-parallel ranks: reduce over dp x cp, scale by 1 / dp
+        self.reduce_group = self.mesh.group("dp_shard", "cp") if self.mesh.size("dp_replicate") * self.mesh.size("ep") == 1 \
+            else dist.group.WORLD
+        self.reduce_size = self.dp_size * n
+
     # ------------------------------------------------------------------ tensor parallel
     def apply_tp(self, model):
+        self.setup_cp()
         n = self.mesh.size("tp")
         if n <= 1:
             return
@@ -154,13 +171,13 @@ class ParallelRuntime:
         gradient norm (device scalar) or None."""
         if self.tp is not None:
             return self._tp_step(opt, lr)
-        if self.dp_size <= 1:
+        if self.reduce_size <= 1:
             return opt.step(lr=lr)
         if self.backend == "fused" and self.sync is not None:
             return self._fused_step(opt, lr)
-        # collective back end: average the flat gradients, then a local fused AdamW
+        # collective back end: sum the flat gradients, scale by 1 / dp, then a local fused AdamW
         for g in opt.flat_grads():
-            dist.all_reduce(g, group=self.dp_group)
+            dist.all_reduce(g, group=self.reduce_group)
         opt.grad_scale = 1.0 / self.dp_size
         return opt.step(lr=lr)
 
@@ -172,14 +189,14 @@ class ParallelRuntime:
         opt.step_count += 1
         bc1 = 1.0 - opt.betas[0] ** opt.step_count
         bc2 = 1.0 - opt.betas[1] ** opt.step_count
-        rank = dist.get_rank(self.dp_group)
+        rank = dist.get_rank(self.reduce_group)
         for gi, g in enumerate(opt.groups):
             gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
             epoch = self.sync.next_epoch(0, 3)
             rc = lib.axb_rs_adamw_ag(
                 gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
                 gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
-                g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.dp_size,
+                g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.reduce_size,
                 epoch, lr * g["lr_scale"], opt.betas[0], opt.betas[1], opt.eps, g["weight_decay"], bc1, bc2,
                 float(opt.max_grad_norm or 0.0) if len(opt.groups) == 1 else 0.0, 1.0 / self.dp_size,
                 self._gnorm.data_ptr(), _lib.status_word(self.device).data_ptr(), WAIT_BUDGET_NS, _lib.stream_ptr())
@@ -235,5 +252,6 @@ def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, 
         backend = os.environ.get("AXB_COMM", "fused" if device.type == "cuda" else "collective")
     mesh = DeviceMesh(spec, dist.get_rank())
     rt = ParallelRuntime(mesh, device, backend)
+    rt.setup_cp()
     rt.shard_model(model)
     return rt

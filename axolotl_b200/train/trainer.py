@@ -65,7 +65,10 @@ def to_device_batch(batch: dict, device, pin=True):
     A batch that was staged before (has ``attn_meta``) is passed through."""
     if "attn_meta" in batch:
         return batch
-    out = {"n_trainable": count_trainable(batch["labels"]), "n_tokens": int(batch["input_ids"].numel())}
+    out = {"n_trainable": batch["n_trainable"] if "n_trainable" in batch else count_trainable(batch["labels"]),
+           "n_tokens": batch["n_tokens"] if "n_tokens" in batch else int(batch["input_ids"].numel())}
+    if batch.get("labels_preshifted"):
+        out["labels_preshifted"] = True
     for k in ("input_ids", "labels", "position_ids"):
         t = batch[k]
         if device.type == "cuda":
@@ -74,6 +77,9 @@ def to_device_batch(batch: dict, device, pin=True):
             t = t.to(device, non_blocking=True)
         out[k] = t
     cu = batch.get("cu_seqlens")
+    if "cp_meta_args" in batch:
+        out["attn_meta"] = None   # built by the context-parallel runtime
+        return out
     if cu is None:
         from ..models.transformer import build_attn_meta
 
@@ -133,8 +139,13 @@ class Trainer:
         n_items = max(n_items, 1)
         loss_total = None
         par = self.parallel
+        cp = getattr(par, "cp", None) if par is not None else None
         for i, cpu_batch in enumerate(micro_batches):
+            if cp is not None and "attn_meta" not in cpu_batch:
+                cpu_batch = cp.slice_batch(cpu_batch)   # this rank's chunk, labels shifted globally
             b = to_device_batch(cpu_batch, self.device)
+            if cp is not None and "cp_meta_args" in cpu_batch and not getattr(b["attn_meta"], "cp", False):
+                b["attn_meta"] = cp.make_meta(*cpu_batch["cp_meta_args"])
             last = i == len(micro_batches) - 1
             if par is not None:
                 par.before_micro_batch(last)
@@ -142,7 +153,7 @@ class Trainer:
                 loss = self.compute_loss(model, b, n_items)
             else:
                 out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
-                            num_items=n_items)
+                            num_items=n_items, shift_labels=not b.get("labels_preshifted", False))
                 loss = out.loss
             loss.backward()
             loss_total = loss.detach() if loss_total is None else loss_total + loss.detach()

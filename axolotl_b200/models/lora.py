@@ -149,12 +149,14 @@ def get_peft_state_dict(model) -> dict:
             base = f"base_model.model.{_hf_path(name, sub)}"
             sd[f"{base}.lora_A.weight"] = A.detach()
             sd[f"{base}.lora_B.weight"] = B.detach()
+    ep_of = {id(m.experts): m.ep for m in model.modules() if getattr(m, "ep", None) is not None and hasattr(m, "experts")}
     for name, m in model.named_modules():
         if isinstance(m, Experts) and m.lora is not None:
             base = f"base_model.model.model.{name}"
+            full = ep_of[id(m)].gather_expert_lora(m) if id(m) in ep_of else None
             for which in ("gate_up", "down"):
-                sd[f"{base}.{which}_proj.lora_A.weight"] = m.lora[which + "_A"].detach()
-                sd[f"{base}.{which}_proj.lora_B.weight"] = m.lora[which + "_B"].detach()
+                sd[f"{base}.{which}_proj.lora_A.weight"] = (full or m.lora)[which + "_A"].detach()
+                sd[f"{base}.{which}_proj.lora_B.weight"] = (full or m.lora)[which + "_B"].detach()
     return sd
 
 

@@ -25,6 +25,10 @@ _CUDA_SIGS = {
                       i32, f32, f32, i32, i32, i32, vp, vp],
     "axb_gemm_bf16_pair": [vp, i64, i32, vp, i64, i32, vp, i64, vp, i64, i32, i32, i32, vp, i64, vp, i64,
                            i32, f32, f32, i32, vp, C.c_ulonglong, C.c_ulonglong, i32, vp, i32, vp, vp],
+    "axb_nvfp4_dequant": [vp, vp, vp, vp, i64, i64, vp],
+    "axb_ep_gather_rows": [vp, i32, vp, vp, vp, i64, i32, i64, vp],
+    "axb_ep_scatter_add": [vp, i32, vp, vp, vp, vp, i64, i32, i64, vp],
+    "axb_peer_put_i32": [vp, vp, i64, vp],
     "axb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
     "axb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_rope_qk": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp, vp, vp, f32, vp],

@@ -1,0 +1,242 @@
+"""Expert parallelism: experts are sharded over the EP group, tokens travel to their experts and
+back over NVLink peer memory.
+
+Per MoE layer and micro batch:
+1. routing is local (softmax -> top-k); the slot lists (source row, local expert id, routing weight)
+   are exchanged with one small all-to-all (metadata only, a few KB);
+2. DISPATCH: every rank copies its hidden states into a symmetric buffer; after one flag barrier the
+   destination ranks *pull* exactly the rows routed to their experts with peer loads
+   (``axb_ep_gather_rows``), already sorted by expert -- no send buffers, no host barrier;
+3. the local experts run as tcgen05 GEMMs (bf16, or NVFP4 weights dequantised by
+   ``axb_nvfp4_dequant``) with their LoRA folded in;
+4. COMBINE: expert outputs are scaled by their routing weight and reduce-added into the source
+   rank's output buffer with peer atomics (``axb_ep_scatter_add``); one more flag barrier.
+The backward pass is the mirror image (combine^T = gather of dY rows, dispatch^T = scatter-add of dX
+rows). Expert weights and expert-LoRA slices follow the reference's layout rules
+(src/axolotl/integrations/expert_parallel/shard.py:56-393): rank r owns experts
+[r*E/ep, (r+1)*E/ep); A is expert-major ([E*r, in] rows), B is rank-major ([out, r, E] view).
+On CPU (gloo) the payload moves with ``all_to_all_single`` so the same logic is testable without GPUs.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from .symm import PeerSync, SymmBuffer
+
+
+class _Plan:
+    """Routing plan of one MoE layer call (shared by forward and backward)."""
+    __slots__ = ("T", "k", "H", "send_order", "send_counts", "recv_counts", "recv_src_rank", "recv_src_row",
+                 "recv_weight", "local_order", "expert_counts", "n_recv", "send_tok")
+
+
+class ExpertParallelGroup:
+    def __init__(self, device, group, size, rank, num_experts):
+        self.device, self.group, self.size, self.rank = torch.device(device), group, size, rank
+        if num_experts % size:
+            raise ValueError(f"{num_experts} experts are not divisible by expert_parallel_size={size}")
+        self.E, self.E_local = num_experts, num_experts // size
+        self.fused = self.device.type == "cuda"
+        self.x_bufs = self.y_bufs = None
+        self.kx = self.ky = 0
+        if self.fused:
+            self.sync = PeerSync(self.device, group)
+
+    # ------------------------------------------------------------------ weights
+    @torch.no_grad()
+    def shard_experts(self, model):
+        from ..models.moe import Experts, SparseMoE
+
+        r, n, El = self.rank, self.size, self.E_local
+        for m in model.modules():
+            if not isinstance(m, SparseMoE):
+                continue
+            ex: Experts = m.experts
+            lo, hi = r * El, (r + 1) * El
+            if ex.nvfp4 is not None:
+                for which in ("gate_up", "down"):
+                    q = ex.nvfp4[which]
+                    ex.nvfp4[which] = {k: v[lo:hi].contiguous() for k, v in q.items()}
+            else:
+                ex.gate_up_proj = torch.nn.Parameter(ex.gate_up_proj.detach()[lo:hi].contiguous().clone(),
+                                                     requires_grad=ex.gate_up_proj.requires_grad)
+                ex.down_proj = torch.nn.Parameter(ex.down_proj.detach()[lo:hi].contiguous().clone(),
+                                                  requires_grad=ex.down_proj.requires_grad)
+            if ex.lora is not None:
+                rr = ex.lora_r
+                new = {}
+                for which in ("gate_up", "down"):
+                    A, B = ex.lora[which + "_A"], ex.lora[which + "_B"]
+                    new[which + "_A"] = torch.nn.Parameter(A.detach()[lo * rr:hi * rr].contiguous().clone())
+                    new[which + "_B"] = torch.nn.Parameter(
+                        B.detach().view(B.shape[0], rr, self.E)[:, :, lo:hi].reshape(B.shape[0], rr * El).contiguous().clone())
+                ex.lora = torch.nn.ParameterDict(new)
+                for p in ex.lora.values():
+                    p._tp_sharded = True   # unique per rank: never reduced over the EP group
+            ex.E, ex.expert_offset = El, lo
+            for p in ex.parameters():
+                p._tp_sharded = True
+            m.ep = self
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    @torch.no_grad()
+    def gather_expert_lora(self, ex):
+        """Full-size expert adapter tensors in PEFT layout (adapter saving)."""
+        out = {}
+        rr, El = ex.lora_r, self.E_local
+        for which in ("gate_up", "down"):
+            A, B = ex.lora[which + "_A"].detach().contiguous(), ex.lora[which + "_B"].detach().contiguous()
+            As = [torch.empty_like(A) for _ in range(self.size)]
+            Bs = [torch.empty_like(B) for _ in range(self.size)]
+            dist.all_gather(As, A, group=self.group)
+            dist.all_gather(Bs, B, group=self.group)
+            out[which + "_A"] = torch.cat(As, 0)
+            out[which + "_B"] = torch.cat([b.view(b.shape[0], rr, El) for b in Bs], 2).reshape(B.shape[0], rr * self.E)
+        return out
+
+    # ------------------------------------------------------------------ plan
+    def _make_plan(self, idx, w, H):
+        T, k = idx.shape
+        dev = idx.device
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)                 # grouped by destination rank, then expert
+        dest = (flat_e // self.E_local)
+        send_counts = torch.bincount(dest, minlength=self.size)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        n_recv = sum(rc)
+        tok = (order // k).to(torch.int32)
+        loc_e = (flat_e[order] % self.E_local).to(torch.int32)
+        wt = w.reshape(-1)[order].float()
+        r_tok = torch.empty(n_recv, dtype=torch.int32, device=dev)
+        r_e = torch.empty(n_recv, dtype=torch.int32, device=dev)
+        r_w = torch.empty(n_recv, dtype=torch.float32, device=dev)
+        dist.all_to_all_single(r_tok, tok, rc, sc, group=self.group)
+        dist.all_to_all_single(r_e, loc_e, rc, sc, group=self.group)
+        dist.all_to_all_single(r_w, wt.detach(), rc, sc, group=self.group)
+        src_rank = torch.repeat_interleave(torch.arange(self.size, device=dev, dtype=torch.int32),
+                                           torch.tensor(rc, device=dev))
+        local_order = torch.argsort(r_e, stable=True)
+        p = _Plan()
+        p.T, p.k, p.H = T, k, H
+        p.send_order, p.send_counts, p.recv_counts = order, sc, rc
+        p.recv_src_rank = src_rank[local_order].contiguous()
+        p.recv_src_row = r_tok[local_order].contiguous()
+        p.recv_weight = r_w[local_order].contiguous()
+        p.local_order = local_order
+        p.expert_counts = torch.bincount(r_e.long(), minlength=self.E_local).tolist()
+        p.n_recv = n_recv
+        p.send_tok = tok
+        return p
+
+    def _ensure(self, T, H):
+        if not self.fused:
+            return
+        need = T * H
+        if self.x_bufs is None or self.x_bufs[0].tensor.numel() < need:
+            self.x_bufs = [SymmBuffer(need, torch.bfloat16, self.device, self.group, use_multicast=False) for _ in range(2)]
+            self.y_bufs = [SymmBuffer(need, torch.bfloat16, self.device, self.group, use_multicast=False) for _ in range(2)]
+            dist.barrier(self.group)
+
+    # ------------------------------------------------------------------ payload movement
+    def pull_rows(self, x, plan):
+        """rows routed to this rank's experts, expert-sorted: [n_recv, H]."""
+        if not self.fused:
+            return _a2a_rows(x[plan.send_tok.long()], plan.recv_counts, plan.send_counts, self.group)[plan.local_order]
+        lib = _lib.cuda_lib()
+        T, H = x.shape
+        self._ensure(T, H)
+        buf = self.x_bufs[self.kx & 1]
+        self.kx += 1
+        buf.tensor[: T * H].view(T, H).copy_(x)
+        self.sync.barrier(channel=6)
+        out = torch.empty((plan.n_recv, H), dtype=x.dtype, device=x.device)
+        _lib.check_rc(lib.axb_ep_gather_rows(buf.ptrs_c, self.size, plan.recv_src_rank.data_ptr(),
+                                             plan.recv_src_row.data_ptr(), out.data_ptr(), plan.n_recv, H, H,
+                                             _lib.stream_ptr()), "ep_gather_rows")
+        return out
+
+    def push_rows(self, rows, plan, weighted):
+        """sum over slots of (weight *) rows back at their source token: [T, H] on the source rank."""
+        T, H = plan.T, plan.H
+        if not self.fused:
+            r = rows * plan.recv_weight[:, None].to(rows.dtype) if weighted else rows
+            inv = torch.empty_like(plan.local_order)
+            inv[plan.local_order] = torch.arange(len(inv), device=inv.device)
+            back = _a2a_rows(r[inv], plan.send_counts, plan.recv_counts, self.group)
+            y = torch.zeros(T, H, dtype=rows.dtype, device=rows.device)
+            y.index_add_(0, plan.send_tok.long(), back)
+            return y
+        lib = _lib.cuda_lib()
+        self._ensure(T, H)
+        buf = self.y_bufs[self.ky & 1]     # zero on every rank since its last use
+        self.ky += 1
+        rows = rows.contiguous()
+        _lib.check_rc(lib.axb_ep_scatter_add(buf.ptrs_c, self.size, plan.recv_src_rank.data_ptr(),
+                                             plan.recv_src_row.data_ptr(),
+                                             plan.recv_weight.data_ptr() if weighted else None, rows.data_ptr(),
+                                             plan.n_recv, H, H, _lib.stream_ptr()), "ep_scatter_add")
+        self.sync.barrier(channel=7)
+        y = buf.tensor[: T * H].view(T, H).clone()
+        buf.tensor[: T * H].zero_()
+        return y
+
+    def return_slot_scalars(self, vals, plan):
+        """per-slot scalars computed at the expert rank -> [T, k] at the source rank."""
+        inv = torch.empty_like(plan.local_order)
+        inv[plan.local_order] = torch.arange(len(inv), device=inv.device)
+        send = vals[inv].contiguous()
+        back = torch.empty(plan.T * plan.k, dtype=vals.dtype, device=vals.device)
+        dist.all_to_all_single(back, send, plan.send_counts, plan.recv_counts, group=self.group)
+        out = torch.empty_like(back)
+        out[plan.send_order] = back
+        return out.view(plan.T, plan.k)
+
+    # ------------------------------------------------------------------ layer entry
+    def dispatch_compute_combine(self, experts, x, w, idx):
+        plan = self._make_plan(idx, w, x.shape[1])
+        xs = _Dispatch.apply(x, self, plan)
+        ys = experts(xs, plan.expert_counts)
+        return _Combine.apply(ys, w, self, plan)
+
+
+def _a2a_rows(rows, out_counts, in_counts, group):
+    out = torch.empty((sum(out_counts), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(out, rows.contiguous(), out_counts, in_counts, group=group)
+    return out
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ep, plan):
+        ctx.ep, ctx.plan = ep, plan
+        return ep.pull_rows(x.contiguous(), plan)
+
+    @staticmethod
+    def backward(ctx, dxs):
+        return ctx.ep.push_rows(dxs, ctx.plan, weighted=False), None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ys, w, ep, plan):
+        ctx.ep, ctx.plan = ep, plan
+        ctx.save_for_backward(ys)
+        ctx.w_dtype = w.dtype
+        return ep.push_rows(ys, plan, weighted=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ys,) = ctx.saved_tensors
+        ep, plan = ctx.ep, ctx.plan
+        dy_rows = ep.pull_rows(dy.contiguous(), plan)                     # dY of each slot's token
+        dys = dy_rows * plan.recv_weight[:, None].to(dy_rows.dtype)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw_slots = (dy_rows.float() * ys.float()).sum(-1)
+            dw = ep.return_slot_scalars(dw_slots, plan).to(ctx.w_dtype)
+        return dys, dw, None, None

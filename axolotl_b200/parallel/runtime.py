@@ -40,9 +40,12 @@ class ParallelRuntime:
         self.ep = None
         self.reduce_group = self.dp_group   # group over which gradients are reduced
         self.reduce_size = self.dp_size
+        self.mp_group = None                # tensor- or expert-parallel group
+        self.dp_rest_group, self.dp_rest_size = self.dp_group, self.dp_size
 
     # ------------------------------------------------------------------ setup
     def shard_model(self, model):
+        self.setup_ep(model)
         if self.backend != "fused" or self.shard_size <= 1:
             return
         from .fsdp import FSDPContext
@@ -61,7 +64,7 @@ class ParallelRuntime:
         return t
 
     def optimizer_alloc(self):
-        if self.tp is not None:
+        if self.tp is not None or self.mesh.size("ep") > 1:
             return None
         if self.backend == "fused" and self.reduce_size > 1 and self.device.type == "cuda":
             return self.symmetric_alloc
@@ -69,7 +72,8 @@ class ParallelRuntime:
 
     def attach_optimizer(self, opt):
         self.opt = opt
-        if self.tp is None and self.backend == "fused" and self.reduce_size > 1 and self.device.type == "cuda":
+        if self.tp is None and self.mesh.size("ep") == 1 and self.backend == "fused" and self.reduce_size > 1 \
+                and self.device.type == "cuda":
             from .symm import PeerSync
 
             self.sync = PeerSync(self.device, self.reduce_group)
@@ -117,6 +121,21 @@ class ParallelRuntime:
         r = float(t.item())
         return int(r) if isinstance(v, int) else r
 
+    # ------------------------------------------------------------------ expert parallel
+    def setup_ep(self, model):
+        """Shards the experts of every MoE block over the ep axis (call after adapters exist)."""
+        n = self.mesh.size("ep")
+        if n <= 1 or self.ep is not None:
+            return
+        from .ep import ExpertParallelGroup
+
+        self.ep = ExpertParallelGroup(self.device, self.mesh.group("ep"), n, self.mesh.coord("ep"),
+                                      model.config.num_experts)
+        self.ep.shard_experts(model)
+        self.mp_group = self.mesh.group("ep")
+        self.dp_rest_group = self.mesh.group("dp_replicate", "dp_shard")
+        self.dp_rest_size = self.mesh.size("dp_replicate", "dp_shard")
+
     # ------------------------------------------------------------------ context parallel
     def setup_cp(self):
         n = self.mesh.size("cp")
@@ -143,21 +162,26 @@ class ParallelRuntime:
         max_elems = getattr(self, "tp_max_tokens", 16384) * max(cfg.hidden_size, 1)
         self.tp = TPContext(self.device, self.mesh.group("tp"), n, self.mesh.coord("tp"), max_elems)
         apply_tensor_parallel(model, self.tp)
+        self.mp_group = self.tp.group
+        self.dp_rest_group = self.dp_group
+        self.dp_rest_size = self.dp_size
 
     def _tp_step(self, opt, lr):
-        """TP (x DP): sum replicated gradients over the TP group, average over data parallel ranks,
-        global norm = replicated part + sum over TP of the sharded part; all on the device."""
+        """Model-parallel (TP or EP) x DP: sum the gradients of replicated parameters over the
+        model-parallel group, sum everything over the remaining data-parallel ranks, scale by
+        1 / data_parallel_size; global norm = replicated part + sum over the model-parallel group of
+        the sharded part. Everything stays on the device."""
         from ..ops.optim import grad_sumsq
 
         opt._fold_autograd_grads()
-        tp_group = self.tp.group
+        tp_group = self.mp_group
         total = torch.zeros(1, dtype=torch.float32, device=self.device)
         for g in opt.groups:
             split = g["tp_split"]
             if split > 0:
                 dist.all_reduce(g["grad"][:split], group=tp_group)
-            if self.dp_size > 1:
-                dist.all_reduce(g["grad"], group=self.dp_group)
+            if self.dp_rest_size > 1:
+                dist.all_reduce(g["grad"], group=self.dp_rest_group)
             grad_sumsq(g["grad"][:split], total) if split > 0 else None
             if split < g["grad"].numel():
                 sh = grad_sumsq(g["grad"][split:])
@@ -169,7 +193,7 @@ class ParallelRuntime:
     def optimizer_step(self, opt, lr):
         """Gradient synchronisation + clipping + optimizer update. Returns the squared global
         gradient norm (device scalar) or None."""
-        if self.tp is not None:
+        if self.tp is not None or self.ep is not None:
             return self._tp_step(opt, lr)
         if self.reduce_size <= 1:
             return opt.step(lr=lr)

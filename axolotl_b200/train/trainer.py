@@ -153,7 +153,8 @@ class Trainer:
                 loss = self.compute_loss(model, b, n_items)
             else:
                 out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
-                            num_items=n_items, shift_labels=not b.get("labels_preshifted", False))
+                            num_items=n_items, shift_labels=not b.get("labels_preshifted", False),
+                            aux_scale=1.0 / len(micro_batches))
                 loss = out.loss
             loss.backward()
             loss_total = loss.detach() if loss_total is None else loss_total + loss.detach()

@@ -296,6 +296,72 @@ def check_context_parallel(dev, rank, world):
     dist.barrier()
 
 
+def check_expert_parallel(dev, rank, world):
+    """EP=world MoE training (each rank its own batch) must follow the single-process run with the
+    ranks' batches as accumulation micro-batches."""
+    from axolotl_b200.data.collator import PackedCollator
+    from axolotl_b200.data.synthetic import synthetic_varlen
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, get_peft_state_dict, inject_lora
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.parallel.runtime import create_runtime
+    from axolotl_b200.train.optimizer import FlatAdamW, build_param_groups, make_lr_lambda
+    from axolotl_b200.train.trainer import TrainArgs, Trainer
+
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    cfg = preset("tiny-qwen3-moe", vocab_size=1024, num_experts=8, num_experts_per_tok=2)
+    ds = synthetic_varlen(8 * world, 128, 128, 3, 1024, 0.25, seed=9)
+    coll = PackedCollator(pad_to_multiple_of=64)
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj", "o_proj"],
+                    target_parameters=["mlp.experts.gate_up_proj", "mlp.experts.down_proj"])
+
+    def run(ep_on):
+        torch.manual_seed(0)
+        model = CausalLM(cfg, dtype=dtype, device=dev).init_weights(0)
+        inject_lora(model, spec)
+        g = torch.Generator(device="cpu").manual_seed(3)
+        with torch.no_grad():
+            for l in model.layers:
+                for k in ("gate_up_B", "down_B"):
+                    p = l.mlp.experts.lora[k]
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(dev))
+        par = None
+        if ep_on:
+            par = create_runtime(device=dev, ep=world)
+            par.apply_tp(model)
+            par.shard_model(model)
+        opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0)
+        opt.bind_model_shadows(model)
+        if par is not None:
+            par.attach_optimizer(opt)
+        tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=3, learning_rate=1e-3),
+                     lambda e: [], parallel=par, device=dev)
+        losses = []
+        for step in range(3):
+            if ep_on:
+                mb = [coll([[ds[(step * world + rank) * 2 + j] for j in range(2)]])]
+            else:
+                mb = [coll([[ds[(step * world + r) * 2 + j] for j in range(2)]]) for r in range(world)]
+            losses.append(float(tr.training_step(mb).item()))
+        return losses, {k: v.float().cpu() for k, v in get_peft_state_dict(model).items()}
+
+    l_ep, sd_ep = run(True)
+    t = torch.tensor(l_ep, dtype=torch.float64, device=dev)
+    dist.all_reduce(t)
+    l_ep = (t / world).tolist()
+    l_ref, sd_ref = run(False)
+    tol = 1e-2 if dev.type == "cuda" else 2e-4
+    assert all(abs(a - b) < tol * abs(b) for a, b in zip(l_ep, l_ref)), (l_ep, l_ref)
+    assert set(sd_ep) == set(sd_ref)
+    wtol = 5e-2 if dev.type == "cuda" else 1e-3
+    for k in sd_ref:
+        assert sd_ep[k].shape == sd_ref[k].shape, k
+        assert rel_err(sd_ep[k], sd_ref[k]) < wtol, (k, rel_err(sd_ep[k], sd_ref[k]))
+    if rank == 0:
+        print(f"expert parallel ok: {l_ep} vs {l_ref}")
+    dist.barrier()
+
+
 def main():
     cpu = len(sys.argv) > 1 and sys.argv[1] == "cpu"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -306,6 +372,7 @@ def main():
         check_training_equivalence(dev, rank, world, "collective")
         check_tensor_parallel(dev, rank, world)
         check_context_parallel(dev, rank, world)
+        check_expert_parallel(dev, rank, world)
     else:
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
         torch.cuda.set_device(dev)
@@ -316,6 +383,7 @@ def main():
         check_training_equivalence(dev, rank, world, "collective")
         check_tensor_parallel(dev, rank, world)
         check_context_parallel(dev, rank, world)
+        check_expert_parallel(dev, rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

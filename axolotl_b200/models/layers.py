@@ -19,6 +19,28 @@ from ..ops import functional as Fn
 from ..ops.lora import linear, lora_linear
 
 
+_ADAPTERS_ON = True
+
+
+def adapters_enabled() -> bool:
+    return _ADAPTERS_ON
+
+
+class disable_adapters:
+    """Context manager: every adapter is skipped in the forward pass, so a LoRA model computes its
+    frozen base model (the implicit reference policy of preference training; the reference gets the
+    same effect from ``peft``'s ``disable_adapter`` inside trl)."""
+
+    def __enter__(self):
+        global _ADAPTERS_ON
+        self._prev = _ADAPTERS_ON
+        _ADAPTERS_ON = False
+
+    def __exit__(self, *exc):
+        global _ADAPTERS_ON
+        _ADAPTERS_ON = self._prev
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim, eps=1e-6, dtype=torch.bfloat16, device=None):
         super().__init__()
@@ -67,6 +89,9 @@ class FusedLinear(nn.Module):
         if not targets:
             return
         dev = self.weight.device
+        if dev.type == "cuda" and r % 8:
+            raise ValueError(f"lora_r={r}: the tensor-core path needs an adapter rank that is a multiple of 8 "
+                             "(16-byte rows for the bulk tensor copies)")
         R = r * len(targets)
         N = self.weight.shape[0]
         A = torch.empty(R, self.in_features, dtype=dtype, device=dev)
@@ -133,7 +158,7 @@ class FusedLinear(nn.Module):
         return self
 
     def forward(self, x):
-        if self.lora_A is None or self.merged:
+        if self.lora_A is None or self.merged or not _ADAPTERS_ON:
             return linear(x, self.weight, self.bias)
         if x.is_cuda and self.lora_A16 is None:
             self.refresh_shadows()

@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from ..ops import functional as Fn
 from ..ops.lora import linear
 from .config import ModelConfig
+from .layers import adapters_enabled
 
 
 def route_topk(router_logits, k, norm_topk_prob=True):
@@ -59,6 +60,8 @@ class Experts(nn.Module):
     def add_lora(self, r, alpha, use_rslora=False, dtype=torch.float32):
         dev = self.gate_up_proj.device if self.nvfp4 is None else self.nvfp4["gate_up"]["qdata"].device
         E, H, I = self.E, self.H, self.I
+        if dev.type == "cuda" and r % 8:
+            raise ValueError(f"lora_r={r}: the tensor-core path needs an adapter rank that is a multiple of 8")
 
         def mk_a(inp):
             a = torch.empty(E * r, inp, dtype=dtype, device=dev)
@@ -102,12 +105,13 @@ class Experts(nn.Module):
             xe = x_sorted[start:start + n]
             start += n
             gu = linear(xe, self.expert_weight("gate_up", e))
-            if self.lora is not None:
+            use_lora = self.lora is not None and adapters_enabled()
+            if use_lora:
                 A, B = self.expert_lora("gate_up", e)
                 gu = gu + self.scaling * ((xe @ A.to(xe.dtype).t()) @ B.to(xe.dtype).t())
             h = Fn.glu(gu, self.act)
             y = linear(h, self.expert_weight("down", e))
-            if self.lora is not None:
+            if use_lora:
                 A, B = self.expert_lora("down", e)
                 y = y + self.scaling * ((h @ A.to(h.dtype).t()) @ B.to(h.dtype).t())
             outs.append(y)

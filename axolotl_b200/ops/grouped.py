@@ -12,6 +12,12 @@ from . import functional as Fn
 from .lora import _LinearFn, _LoRALinearFn
 
 
+def adapters_enabled():
+    from ..models.layers import adapters_enabled as f
+
+    return f()
+
+
 def _proj(x, W, A, B, scaling, r):
     if A is None:
         return _LinearFn.apply(x, W, None)
@@ -30,7 +36,7 @@ def grouped_experts_forward(experts, x_sorted, counts):
         xe = x_sorted[start:start + n].contiguous()
         start += n
         Ag = Bg = Ad = Bd = None
-        if experts.lora is not None:
+        if experts.lora is not None and adapters_enabled():
             Ag, Bg = experts.expert_lora("gate_up", e)
             Ad, Bd = experts.expert_lora("down", e)
         gu = _proj(xe, experts.expert_weight("gate_up", e), Ag, Bg, experts.scaling, r)

@@ -269,6 +269,11 @@ class TPLinear(torch.nn.Module):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1]).contiguous()
         A, B = self.lora_A, self.lora_B
+        if A is not None:
+            from ..models.layers import adapters_enabled
+
+            if not adapters_enabled():
+                A = B = None
         if B is not None and len(self.lora_blocks) > 1:
             if self._mask is None:
                 m = torch.zeros_like(B)

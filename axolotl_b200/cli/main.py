@@ -232,9 +232,17 @@ def config_schema():
 
 @cli.command("vllm-serve", context_settings=CONTEXT)
 @click.argument("config")
-def vllm_serve(config):
-    """Start a vLLM server for online RL (not wired in this build)."""
-    raise click.ClickException("vllm-serve is not wired in this build: online RL trainers (GRPO) are not available")
+@click.pass_context
+def vllm_serve(ctx, config):
+    """Start the generation server that GRPO runs with ``trl.use_vllm: true`` sample from."""
+    from ..config.load import load_cfg
+    from ..rl.vllm_server import serve
+
+    cfg = load_cfg(config, **_extra_to_overrides(ctx.args))
+    try:
+        serve(cfg)
+    except RuntimeError as exc:
+        raise click.ClickException(str(exc)) from exc
 
 
 def main():

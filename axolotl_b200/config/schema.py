@@ -155,6 +155,10 @@ class TRLConfig(_Base):
     sync_ref_model: bool | None = None
     ref_model_mixup_alpha: float | None = None
     ref_model_sync_steps: int | None = None
+    importance_sampling_level: str | None = None
+    mask_truncated_completions: bool | None = None
+    async_prefetch: int | None = None
+    replay_buffer_size: int | None = None
 
 
 class DynamicCheckpointConfig(_Base):
@@ -427,6 +431,11 @@ class AxolotlConfig(_Base):
     kto_undesirable_weight: float | None = None
     reward_model: bool | None = None
     process_reward_model: bool | None = None
+    center_rewards_coefficient: float | None = None
+    cpo_loss_type: str | None = None
+    max_prompt_len: int | None = None
+    precompute_ref_log_probs: bool | None = None
+    vllm: dict | None = None
     # ---- MoE
     experts_implementation: str | None = None
     router_aux_loss_coef: float | None = None
@@ -505,9 +514,9 @@ INERT_KEYS = {
     "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
     "image_size", "is_falcon_derived_model", "kd_alpha", "kd_ce_alpha", "kd_temperature", "kd_trainer",
     "lisa_layers_attribute", "lisa_n_layers", "lisa_step_interval", "loftq_config", "lora_on_cpu", "low_cpu_mem_usage",
-    "max_memory", "max_packed_sequence_len", "max_prompt_len", "model_quantization_config",
+    "max_memory", "max_packed_sequence_len", "model_quantization_config",
     "model_quantization_config_kwargs", "noisy_embedding_alpha", "num_dataset_shards_to_save",
-    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "peft_layer_replication", "precompute_ref_log_probs",
+    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "peft_layer_replication",
     "preprocess_iterable", "processor_kwargs", "processor_type", "qgalore_cos_threshold", "qgalore_gamma_proj",
     "qgalore_proj_bits", "qgalore_proj_group_size", "qgalore_proj_quant", "qgalore_proj_type", "qgalore_queue_size",
     "qgalore_rank", "qgalore_scale", "qgalore_update_proj_gap", "qlora_sharded_model_loading", "quantize_embedding",
@@ -515,7 +524,7 @@ INERT_KEYS = {
     "save_sliding_window", "scaling_softmax", "scaling_softmax_bias", "scaling_softmax_factor", "streaming_min_groups",
     "streaming_partial_batch", "tokenizer_save_jinja_files", "tokenizer_use_mistral_common", "torch_compile_backend",
     "torch_compile_mode", "torch_compile_options", "torchdistx_path", "trackio_project_name", "trackio_run_name",
-    "trackio_space_id", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss", "vllm",
+    "trackio_space_id", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss",
     "liger_rope", "liger_rms_norm", "liger_glu_activation", "liger_layer_norm", "liger_fused_linear_cross_entropy",
     "liger_cross_entropy", "cut_cross_entropy", "kd_online_server_base_url", "evaluation_strategy",
     "tiled_mlp_use_original_mlp", "min_num_params",

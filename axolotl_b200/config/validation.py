@@ -169,8 +169,10 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
     rl = g("rl")
     if rl and rl not in ("dpo", "ipo", "orpo", "kto", "simpo", "grpo", "gdpo", "ebft"):
         raise ValueError(f"unknown rl method '{rl}'")
-    if rl in ("grpo", "gdpo", "ebft"):
-        raise ValueError(f"rl: {rl} needs an online generation server (vLLM), which is not wired in this build")
+    if rl == "ebft":
+        raise ValueError("rl: ebft (energy-based fine-tuning) is not available in this build")
+    if rl in ("grpo", "gdpo") and not (g("trl") or {}).get("reward_funcs"):
+        raise ValueError(f"rl: {rl} needs trl.reward_funcs (dotted paths of reward functions)")
     if rl and g("sample_packing"):
         raise ValueError("sample packing is not supported for preference training")
 

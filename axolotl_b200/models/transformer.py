@@ -141,12 +141,14 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids, position_ids=None, labels=None, attn_meta=None, num_items=None,
-                return_logits=False, shift_labels=True, aux_scale=1.0):
+                return_logits=None, shift_labels=True, aux_scale=1.0):
         """input_ids / position_ids / labels: [B, S] (or [T]). Returns CausalLMOutput.
 
         ``labels`` follow the HF convention (unshifted; the model shifts by one inside each row)
         unless ``shift_labels=False``. ``num_items`` is the loss denominator (trainable tokens of
         the whole optimizer step when gradients are accumulated); default = this batch's count.
+        ``return_logits``: True / False, or None = only when no labels are given (False with no
+        labels returns just the final hidden states, for objectives that score tokens themselves).
         ``aux_scale`` weights the router load-balance term (1 / accumulation steps, so that the
         term is a mean over micro-batches just as the token loss is a mean over tokens).
         """
@@ -194,7 +196,7 @@ class CausalLM(nn.Module):
             if out.aux_loss is not None and cfg.router_aux_loss_coef:
                 loss = loss + (cfg.router_aux_loss_coef * aux_scale) * out.aux_loss.to(loss.dtype)
             out.loss = loss
-        if return_logits or labels is None:
+        if return_logits or (return_logits is None and labels is None):
             out.logits = linear(h, W).view(B, S, -1)
         return out
 

@@ -461,3 +461,85 @@ def linear_cross_entropy(hidden, lm_head_weight, labels, num_items=None, chunk_r
     denom = float(max(num_items, 1))
     return _LinearCE.apply(hidden.contiguous(), lm_head_weight, labels, denom, chunk_rows,
                            ignore_index, None)
+
+
+class _LinearTokenLogps(torch.autograd.Function):
+    """Per-token log-probability of ``labels`` under ``softmax(h @ W^T)`` without keeping [T, V].
+
+    Forward: per chunk of rows, logits by the tcgen05 GEMM, then the cross-entropy kernel in
+    loss-only mode. Backward: the chunk's logits are recomputed, the kernel overwrites them with
+    ``softmax - onehot`` and ``dH = diag(-g) (dlogits @ W)``; the row scaling is applied to the
+    [rows, H] product rather than to the [rows, V] logits. Ignored rows return 0 and get no
+    gradient. Preference and policy-gradient objectives (which need a weight per token or per
+    sequence, not one global mean) are built on this.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, labels, chunk_rows, ignore_index):
+        from .gemm import gemm
+
+        T = h.shape[0]
+        V = w.shape[0]
+        nll = torch.zeros(T, dtype=torch.float32, device=h.device)
+        if h.is_cuda:
+            lib = _lib.cuda_lib()
+            for r0 in range(0, T, chunk_rows):
+                r1 = min(T, r0 + chunk_rows)
+                logits = gemm(h[r0:r1], w)
+                _lib.check_rc(lib.axb_ce_fwd_bwd(logits.data_ptr(), labels[r0:r1].data_ptr(), nll[r0:r1].data_ptr(),
+                                                 None, r1 - r0, V, logits.stride(0), 1.0, ignore_index, 0,
+                                                 _lib.stream_ptr()), "ce_fwd")
+        else:
+            for r0 in range(0, T, chunk_rows):
+                r1 = min(T, r0 + chunk_rows)
+                lf = (h[r0:r1] @ w.to(h.dtype).t()).float()
+                lab = labels[r0:r1]
+                valid = lab != ignore_index
+                lp = torch.log_softmax(lf, -1).gather(1, lab.clamp(min=0)[:, None]).squeeze(1)
+                nll[r0:r1] = torch.where(valid, -lp, torch.zeros_like(lp))
+        ctx.save_for_backward(h, w, labels)
+        ctx.chunk_rows, ctx.ignore_index = chunk_rows, ignore_index
+        return -nll
+
+    @staticmethod
+    def backward(ctx, g):
+        from .gemm import gemm, pick_splits
+
+        h, w, labels = ctx.saved_tensors
+        T, H = h.shape
+        V = w.shape[0]
+        need_dw = ctx.needs_input_grad[1]
+        dh = torch.empty_like(h)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device) if need_dw else None
+        s = (-g).float()
+        for r0 in range(0, T, ctx.chunk_rows):
+            r1 = min(T, r0 + ctx.chunk_rows)
+            hc = h[r0:r1]
+            if h.is_cuda:
+                logits = gemm(hc, w)
+                tmp = torch.empty(r1 - r0, dtype=torch.float32, device=h.device)
+                _lib.check_rc(_lib.cuda_lib().axb_ce_fwd_bwd(
+                    logits.data_ptr(), labels[r0:r1].data_ptr(), tmp.data_ptr(), None, r1 - r0, V,
+                    logits.stride(0), 1.0, ctx.ignore_index, 1, _lib.stream_ptr()), "ce_bwd")
+                dlogits = logits
+            else:
+                lf = (hc @ w.to(h.dtype).t()).float()
+                lab = labels[r0:r1]
+                valid = lab != ctx.ignore_index
+                p = torch.softmax(lf, -1)
+                p[torch.arange(r1 - r0), lab.clamp(min=0)] -= 1.0
+                dlogits = (p * valid[:, None]).to(h.dtype)
+            sc = s[r0:r1, None]
+            dh[r0:r1] = (gemm(dlogits, w, trans_b=True).float() * sc).to(h.dtype)
+            if need_dw:
+                hs = (hc.float() * sc).to(h.dtype)
+                sp = pick_splits(((V + 127) // 128) * ((H + 255) // 256), (r1 - r0 + 63) // 64) if h.is_cuda else 1
+                gemm(dlogits, hs, trans_a=True, trans_b=True, out=dw, accumulate=True, splits=sp)
+        return dh, (dw.to(w.dtype) if dw is not None else None), None, None, None
+
+
+def linear_token_logps(hidden, lm_head_weight, labels, chunk_rows=2048, ignore_index=IGNORE_INDEX):
+    """log p(labels[t] | position t) for every row of ``hidden`` ([T] fp32; 0 where ignored).
+    ``labels`` must already be shifted."""
+    hidden = hidden.reshape(-1, hidden.shape[-1]).contiguous()
+    return _LinearTokenLogps.apply(hidden, lm_head_weight, labels.reshape(-1).contiguous(), chunk_rows, ignore_index)

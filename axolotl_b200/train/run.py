@@ -192,6 +192,58 @@ def make_batches_fn(cfg, ds, rank, dp_size, parallel=None, is_eval=False):
     return plain, None
 
 
+def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_size, spec):
+    """Batches + ``compute_loss`` object for ``rl:`` / ``reward_model`` runs. Returns
+    (train_batches(epoch) callable, objective, micro-batches per epoch)."""
+    import copy
+
+    rl = cfg.get("rl")
+    pad = cfg.get("pad_token_id") or 0
+    seed = cfg.get("seed") or 42
+    mbs = cfg["micro_batch_size"]
+    if rl in ("grpo", "gdpo"):
+        from ..rl import grpo as G
+
+        st = G.GRPOSettings(cfg)
+        eos = tokenizer.eos_token_id if tokenizer is not None else cfg.get("eos_token_id")
+        if st.use_vllm:
+            sync_dir = os.path.join(cfg["output_dir"], "rollout_adapter")
+            engine = G.VLLMServerRollout(st.host, st.port, adapter_sync_dir=sync_dir if spec is not None else None,
+                                         save_adapter_fn=(lambda d: save_adapter(model, spec, d)) if spec is not None else None)
+        else:
+            engine = G.LocalRollout(model, eos, pad, seed + dp_rank)
+        records = G.load_prompt_records(cfg, tokenizer)
+        producer = G.RolloutProducer(model, engine, G.load_reward_funcs((cfg.get("trl") or {}).get("reward_funcs")),
+                                     st, records, mbs, tokenizer, pad, eos, dp_rank, dp_size, seed)
+        return producer, G.GRPOObjective(st, producer), len(producer) * st.num_iterations
+    from ..rl.data import PreferenceBatches, load_preference_dataset
+    from ..rl.objectives import build_objective, precompute_reference_logps
+
+    ref_model = None
+    if spec is None and rl in ("dpo", "ipo", "kto"):
+        ref_model = copy.deepcopy(model).requires_grad_(False)   # full fine-tune: frozen copy as reference
+    dp_group = parallel.dp_group if parallel is not None else None
+    obj = build_objective(cfg, ref_model, pad, dp_group)
+    if cfg.get("process_reward_model"):
+        meta = load_datasets(cfg)
+        fn, _ = make_batches_fn(cfg, meta.train, dp_rank, dp_size, parallel)
+        coll = obj.collator()
+
+        def prm_batches(epoch):
+            for b in fn(epoch):
+                b["labels_preshifted"] = True
+                b["n_trainable"] = int((b["labels"] != -100).sum())
+                yield b
+
+        return prm_batches, obj, max(len(meta.train) // (mbs * dp_size), 1)
+    records = load_preference_dataset(cfg, tokenizer)
+    coll = obj.collator()
+    if cfg.get("precompute_ref_log_probs") and rl in ("dpo", "ipo"):
+        precompute_reference_logps(model, records, coll, device, mbs, ref_model, average=getattr(obj, "average", False))
+    batches = PreferenceBatches(records, coll, mbs, dp_rank, dp_size, seed)
+    return batches, obj, len(batches)
+
+
 def save_model_artifacts(model, cfg, spec, out_dir, parallel=None, rank=0):
     """Adapter (LoRA) or full HF checkpoint into ``out_dir`` (rank 0 writes)."""
     if spec is not None:
@@ -241,14 +293,15 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     pm = PluginManager.get_instance()
 
     tokenizer = None
-    if dataset_meta is None:
-        dataset_meta = load_datasets(cfg)
     if cfg.get("base_model") and os.path.isdir(cfg["base_model"]) and any(
             os.path.exists(os.path.join(cfg["base_model"], f)) for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
         from ..data.tokenizer import load_tokenizer
 
         tokenizer = load_tokenizer(cfg)
         cfg["pad_token_id"] = tokenizer.pad_token_id
+    objective_mode = bool(cfg.get("rl") or cfg.get("reward_model"))   # preference / online-RL objectives
+    if dataset_meta is None and not objective_mode:
+        dataset_meta = load_datasets(cfg)
 
     model = build_model(cfg, device)
     parallel = None
@@ -270,14 +323,24 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         parallel.shard_model(model)       # FSDP row-sharding of the frozen weights
         dp_size, dp_rank = parallel.dp_size, parallel.dp_rank
 
+    if cfg.get("reward_model") or cfg.get("process_reward_model"):
+        from ..rl.objectives import add_score_head
+
+        add_score_head(model, 2 if cfg.get("process_reward_model") else 1, cfg.get("seed") or 42)
     opt = build_optimizer(cfg, model, parallel)
     if parallel is not None:
         parallel.attach_optimizer(opt)
 
-    train_fn, sampler = make_batches_fn(cfg, dataset_meta.train, dp_rank, dp_size, parallel)
+    objective = None
     eval_fn = None
-    if dataset_meta.eval is not None and len(dataset_meta.eval):
-        eval_fn, _ = make_batches_fn(cfg, dataset_meta.eval, dp_rank, dp_size, parallel, is_eval=True)
+    if objective_mode:
+        train_fn, objective, n_batches = build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_size, spec)
+        dataset_meta = TrainDatasetMeta(train=None, eval=None, total_num_steps=max(
+            int(n_batches * (cfg.get("num_epochs") or 1)) // cfg["gradient_accumulation_steps"], 1))
+    else:
+        train_fn, sampler = make_batches_fn(cfg, dataset_meta.train, dp_rank, dp_size, parallel)
+        if dataset_meta.eval is not None and len(dataset_meta.eval):
+            eval_fn, _ = make_batches_fn(cfg, dataset_meta.eval, dp_rank, dp_size, parallel, is_eval=True)
     total = dataset_meta.total_num_steps or cfg.get("max_steps") or 0
     if cfg.get("max_steps"):
         total = min(total, cfg["max_steps"]) if total else cfg["max_steps"]
@@ -311,7 +374,7 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     trainer_cls = pm.first("get_trainer_cls", cfg) or Trainer
     trainer = trainer_cls(model, opt, lr_lambda, args, train_fn, eval_batches=eval_fn, parallel=parallel,
                           callbacks=callbacks, save_fn=save_fn, device=device, total_steps=total,
-                          compute_loss=pm.first("compute_loss", cfg))
+                          compute_loss=objective or pm.first("compute_loss", cfg))
     trainer.callbacks += pm.collect_callbacks("add_callbacks_post_trainer", cfg, trainer)
     pm.call("post_trainer_create", cfg, trainer)
 

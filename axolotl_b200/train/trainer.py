@@ -76,6 +76,13 @@ def to_device_batch(batch: dict, device, pin=True):
                 t = t.pin_memory()
             t = t.to(device, non_blocking=True)
         out[k] = t
+    for k, t in (batch.get("aux_tensors") or {}).items():   # objective-specific tensors (seq ids, rewards, ...)
+        if device.type == "cuda":
+            if pin and not t.is_pinned():
+                t = t.pin_memory()
+            t = t.to(device, non_blocking=True)
+        out[k] = t
+    out.update(batch.get("meta") or {})
     cu = batch.get("cu_seqlens")
     if "cp_meta_args" in batch:
         out["attn_meta"] = None   # built by the context-parallel runtime
@@ -150,6 +157,7 @@ class Trainer:
             if par is not None:
                 par.before_micro_batch(last)
             if self.compute_loss is not None:
+                b["ga_steps"] = len(micro_batches)
                 loss = self.compute_loss(model, b, n_items)
             else:
                 out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
@@ -257,6 +265,8 @@ class Trainer:
             logs["ppl"] = math.exp(loss)
         except OverflowError:
             logs["ppl"] = float("inf")
+        for k, v in (getattr(self.compute_loss, "last_metrics", None) or {}).items():
+            logs[k] = v   # objective-specific metrics (rewards/*, kl, clip_ratio, ...)
         if self._last_gnorm_sq is not None:
             logs["grad_norm"] = float(torch.as_tensor(self._last_gnorm_sq).sqrt().item())
         if self.args.include_tkps:

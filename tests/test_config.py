@@ -54,7 +54,8 @@ def test_world_size_scaling_excludes_tp_and_cp(monkeypatch):
     ({"warmup_steps": 3, "warmup_ratio": 0.1}, "only one of"),
     ({"save_steps": 5, "saves_per_epoch": 2}, "only one of"),
     ({"optimizer": "adamw_bnb_8bit"}, "bitsandbytes"),
-    ({"rl": "grpo"}, "vLLM"),
+    ({"rl": "grpo"}, "reward_funcs"),
+    ({"rl": "ebft"}, "ebft"),
     ({"tensor_parallel_size": 2, "expert_parallel_size": 2}, "expert parallelism"),
     ({"context_parallel_size": 2, "sample_packing": True, "micro_batch_size": 2}, "micro_batch_size: 1"),
     ({"val_set_size": 0.1, "test_datasets": [{"type": "_synthetic"}]}, "mutually exclusive"),

@@ -255,3 +255,104 @@ def test_adamw_matches_torch():
                     gnorm_sq=ss, max_norm=1.0)
     assert _rel_err(p, ref_p.detach()) < 1e-5
     assert _rel_err(shadow, p) < 5e-3
+
+
+def test_linear_token_logps():
+    from axolotl_b200.ops.functional import linear_token_logps
+    torch.manual_seed(21)
+    T, H, V = 600, 256, 3008
+    h = (torch.randn(T, H) * 0.5).bfloat16().to(_dev()).requires_grad_(True)
+    w = (torch.randn(V, H) * 0.05).bfloat16().to(_dev())
+    labels = torch.randint(0, V, (T,), device=_dev())
+    labels[::5] = -100
+    g = torch.randn(T, device=_dev())
+    lp = linear_token_logps(h, w, labels, chunk_rows=256)
+    (lp * g).sum().backward()
+    _check_status()
+    hc = h.detach().cpu().float().requires_grad_(True)
+    lab = labels.cpu()
+    ref = torch.log_softmax(hc @ w.cpu().float().t(), -1).gather(1, lab.clamp(min=0)[:, None]).squeeze(1) * (lab != -100)
+    (ref * g.cpu()).sum().backward()
+    assert _rel_err(lp.cpu(), ref.detach()) < 1e-2
+    assert float(lp.detach()[::5].abs().max()) == 0.0
+    assert _rel_err(h.grad.cpu(), hc.grad) < 3e-2
+
+
+def test_nvfp4_dequant_kernel_matches_reference_decode():
+    from axolotl_b200.ops import nvfp4
+    torch.manual_seed(22)
+    w = torch.randn(384, 512) * 0.1
+    q, s, pts = nvfp4.quantize_nvfp4(w)
+    ref = nvfp4.dequantize_nvfp4(q, s, pts, dtype=torch.float32)          # CPU table decode
+    got = nvfp4.dequantize_nvfp4(q.to(_dev()), s.to(_dev()), pts.to(_dev()))
+    _check_status()
+    assert got.dtype == torch.bfloat16 and got.shape == w.shape
+    assert torch.equal(got.cpu(), ref.bfloat16())
+    assert _rel_err(got.cpu(), w) < 0.15
+
+
+def test_moe_block_matches_cpu_reference():
+    """Sparse MoE block (router + per-expert GEMMs with expert LoRA) on the GPU against the same
+    block in fp32 on the CPU."""
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.moe import SparseMoE
+    torch.manual_seed(23)
+    cfg = preset("tiny-qwen3-moe")
+    ref = SparseMoE(cfg, torch.float32, torch.device("cpu"))
+    for p in ref.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    ref.experts.add_lora(8, 16)
+    with torch.no_grad():
+        for k in ("gate_up_B", "down_B"):
+            ref.experts.lora[k].normal_(0, 0.05)
+    dev = SparseMoE(cfg, torch.bfloat16, _dev())
+    dev.experts.add_lora(8, 16)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(dev.named_parameters(), ref.named_parameters()):
+            p.copy_(q)
+        # use the same (bf16-rounded) base weights on both sides
+        for (n, p), (_, q) in zip(dev.named_parameters(), ref.named_parameters()):
+            if p.dtype == torch.bfloat16:
+                q.copy_(p.float().cpu())
+    x = (torch.randn(300, cfg.hidden_size) * 0.5).bfloat16()
+    xd = x.to(_dev()).requires_grad_(True)
+    xr = x.float().requires_grad_(True)
+    yd, _ = dev(xd)
+    yr, _ = ref(xr)
+    gy = torch.randn_like(yr)
+    yd.backward(gy.to(_dev()).bfloat16())
+    yr.backward(gy)
+    _check_status()
+    assert _rel_err(yd.cpu(), yr.detach()) < 3e-2
+    assert _rel_err(xd.grad.cpu(), xr.grad) < 5e-2
+    for k in ("gate_up_A", "gate_up_B", "down_A", "down_B"):
+        gd = dev.experts.lora[k]
+        gd = getattr(gd, "_axb_grad", None) if gd.grad is None else gd.grad
+        assert gd is not None and _rel_err(gd.float().cpu().reshape(-1), ref.experts.lora[k].grad.reshape(-1)) < 6e-2, k
+
+
+def test_dpo_step_on_gpu():
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, inject_lora
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.rl.data import synthetic_preference
+    from axolotl_b200.rl.objectives import build_objective
+    from axolotl_b200.train.optimizer import FlatAdamW, build_param_groups, make_lr_lambda
+    from axolotl_b200.train.trainer import TrainArgs, Trainer
+
+    cfg = preset("tiny-llama", vocab_size=1024)
+    model = CausalLM(cfg, dtype=torch.bfloat16, device=_dev()).init_weights(0)
+    inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules="all-linear"))
+    obj = build_objective({"rl": "dpo", "rl_beta": 0.5})
+    coll = obj.collator()
+    recs = synthetic_preference(32, 12, 12, 1024, seed=1)
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=5e-3, max_grad_norm=1.0)
+    opt.bind_model_shadows(model)
+    tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=12, learning_rate=5e-3),
+                 lambda e: [], device=_dev(), compute_loss=obj)
+    losses = []
+    for s in range(12):
+        losses.append(float(tr.training_step([coll([recs[(s * 8 + j) % 32] for j in range(8)])])))
+    _check_status()
+    assert abs(losses[0] - math.log(2)) < 2e-2
+    assert losses[-1] < losses[0] - 0.05 and obj.last_metrics["rewards/accuracies"] >= 0.75

@@ -395,3 +395,33 @@ inline int axb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, u
             (unsigned long long)ld_elems, box_rows, box_cols, elem_bytes);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
+
+// 3-D map over a batch of row-major matrices [batch, rows, cols] (leading dimension ld_elems,
+// matrices batch_stride_elems apart); a box is [1, box_rows, box_cols], so its shared-memory
+// image equals the 2-D one and a box never crosses into the next matrix of the batch.
+inline int axb_make_tmap_3d(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows,
+                            uint64_t cols, uint64_t ld_elems, uint64_t batch_stride_elems,
+                            uint32_t box_rows, uint32_t box_cols) {
+  AxbEncodeTiledFn fn = axb_get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {ld_elems * 2ull, batch_stride_elems * 2ull};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    cudaFree(nullptr);  // bind the primary context on threads that have none yet
+  }
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "axb_make_tmap_3d failed: CUresult %d base %p batch %llu rows %llu cols %llu ld %llu "
+            "stride %llu box [%u, %u]\n",
+            (int)r, base, (unsigned long long)batch, (unsigned long long)rows,
+            (unsigned long long)cols, (unsigned long long)ld_elems,
+            (unsigned long long)batch_stride_elems, box_rows, box_cols);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}

@@ -32,10 +32,10 @@ AXB_DEVICE float e4m3_to_float(uint8_t v) {
 // one thread per 16-element block: 8 packed bytes in, 16 bf16 out
 __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scale,
                                      const float* __restrict__ pts, __nv_bfloat16* __restrict__ out,
-                                     long long n_blocks) {
+                                     long long n_blocks, long long blocks_per_pts) {
   for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks;
        b += (long long)gridDim.x * blockDim.x) {
-    const float s = e4m3_to_float(scale[b]) * pts[0];
+    const float s = e4m3_to_float(scale[b]) * pts[b / blocks_per_pts];
     const uint2 packed = *reinterpret_cast<const uint2*>(q + b * 8);
     const uint32_t w[2] = {packed.x, packed.y};
     uint32_t o[8];
@@ -119,7 +119,21 @@ extern "C" int axb_nvfp4_dequant(const void* q, const void* scale, const float* 
   if (nb <= 0) return 0;
   int grid = (int)((nb + 255) / 256 > 148 * 16 ? 148 * 16 : (nb + 255) / 256);
   nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
-                                                     (__nv_bfloat16*)out, nb);
+                                                     (__nv_bfloat16*)out, nb, nb);
+  return (int)cudaGetLastError();
+}
+
+// batch of matrices (expert stacks): q [batch, rows, cols/2], scale [batch, rows, cols/16],
+// pts [batch] fp32 -> out [batch, rows, cols] bf16, one launch
+extern "C" int axb_nvfp4_dequant_batched(const void* q, const void* scale, const float* pts, void* out,
+                                         long long batch, long long rows, long long cols, void* stream) {
+  if (cols % 16) return -2;
+  const long long per = rows * (cols / 16);
+  const long long nb = batch * per;
+  if (nb <= 0) return 0;
+  int grid = (int)((nb + 255) / 256 > 148 * 16 ? 148 * 16 : (nb + 255) / 256);
+  nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
+                                                     (__nv_bfloat16*)out, nb, per);
   return (int)cudaGetLastError();
 }
 

@@ -143,7 +143,9 @@ class SparseMoE(nn.Module):
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = order // self.k
-        counts = torch.bincount(flat_e, minlength=self.E).tolist()
+        counts = torch.bincount(flat_e, minlength=self.E)
+        if not x.is_cuda:
+            counts = counts.tolist()     # the grouped CUDA path keeps the counts on the device (no sync)
         xs = x.index_select(0, tok)
         ys = self.experts(xs, counts)
         ws = w.reshape(-1).index_select(0, order).to(ys.dtype)

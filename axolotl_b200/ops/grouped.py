@@ -1,15 +1,24 @@
-"""Grouped expert computation on CUDA: tokens sorted by expert, one pass per projection.
+"""Grouped expert computation on CUDA: every projection of a mixture-of-experts layer is ONE
+launch of the grouped tcgen05 GEMM over expert-sorted, 128-row padded token segments.
 
-Each expert's rows go through the tcgen05 GEMM (bf16 weights, or NVFP4 weights dequantised by the
-nvfp4 kernel right before use) with its LoRA update folded in as a K-extension. Gradients flow
-through the same autograd functions as the dense layers.
+Per projection ``y = x W_e^T + s (x A_e^T) B_e^T``:
+  forward   t  = s * x A_e^T                         (grouped GEMM, N = r)
+            y  = x W_e^T + t B_e^T                   (grouped GEMM with the LoRA update as K-extension)
+  backward  dt = dy B_e                              (grouped GEMM, transposed weights)
+            dx = dy W_e + s * dt A_e                 (same, K-extension)
+            dA_e = s * dt^T x,   dB_e = dy^T t       (grouped Gram kernels, fp32, accumulated)
+Frozen NVFP4 experts are dequantised (one batched kernel) into a bf16 scratch right before use, in
+the forward and again in the backward pass, so only the packed weights stay resident.
+The segment layout is built on the device: no host synchronisation per layer.
 """
 from __future__ import annotations
 
 import torch
 
+from . import _lib
 from . import functional as Fn
-from .lora import _LinearFn, _LoRALinearFn
+
+BLOCK = 128
 
 
 def adapters_enabled():
@@ -18,33 +27,176 @@ def adapters_enabled():
     return f()
 
 
-def _proj(x, W, A, B, scaling, r):
-    if A is None:
-        return _LinearFn.apply(x, W, None)
-    A16 = A.detach().to(torch.bfloat16).contiguous()
-    B16 = B.detach().to(torch.bfloat16).contiguous()
-    return _LoRALinearFn.apply(x, W, A, B, A16, B16, float(scaling), ((0, W.shape[0], 0, r),), None)
+class GroupLayout:
+    """Device-side description of padded expert segments.
+
+    ``dest[i]``: padded row of the i-th expert-sorted compact row; ``blk_expert`` / ``n_blocks`` /
+    ``seg_start`` / ``seg_rows`` as consumed by the grouped kernels; ``max_blocks`` is a static
+    upper bound (ceil(rows / 128) + E) so buffer shapes never depend on the routing."""
+
+    def __init__(self, counts: torch.Tensor, n_rows: int):
+        E = counts.numel()
+        dev = counts.device
+        counts = counts.to(torch.int64)
+        padded = (counts + (BLOCK - 1)) // BLOCK * BLOCK
+        seg_end = padded.cumsum(0)
+        seg_start = seg_end - padded
+        self.E, self.n_rows = E, n_rows
+        self.max_blocks = (n_rows + BLOCK - 1) // BLOCK + E
+        self.max_rows = self.max_blocks * BLOCK
+        e_sorted = torch.repeat_interleave(torch.arange(E, device=dev), counts, output_size=n_rows)
+        rank = torch.arange(n_rows, device=dev) - (counts.cumsum(0) - counts)[e_sorted]
+        self.dest = seg_start[e_sorted] + rank
+        blk_row = torch.arange(self.max_blocks, device=dev) * BLOCK
+        self.blk_expert = torch.searchsorted(seg_end, blk_row, right=True).clamp(max=E - 1).to(torch.int32)
+        self.n_blocks = (seg_end[-1:] // BLOCK).to(torch.int32)
+        self.seg_start = seg_start.to(torch.int32)
+        self.seg_rows = padded.to(torch.int32)
+
+    def pad(self, x_sorted):
+        out = x_sorted.new_zeros((self.max_rows, x_sorted.shape[1]))
+        return out.index_copy(0, self.dest, x_sorted)
+
+    def unpad(self, y_pad):
+        return y_pad.index_select(0, self.dest)
+
+
+def _bn_for(n):
+    return 64 if n <= 64 else (128 if n <= 128 or n % 256 else 256)
+
+
+def grouped_gemm(a, w, lay: GroupLayout, *, trans_w=False, a2=None, w2=None, alpha=1.0, out_dtype=torch.bfloat16):
+    """a [max_rows, K]; w [E, N, K] (or [E, K, N] with trans_w); optional K-extension a2 [max_rows, K2],
+    w2 [E, N, K2] (or [E, K2, N]). Returns [max_rows, N]."""
+    E = w.shape[0]
+    if trans_w:
+        K, N = w.shape[1], w.shape[2]
+    else:
+        N, K = w.shape[1], w.shape[2]
+    assert a.shape[1] == K and a.shape[0] == lay.max_rows and a.is_contiguous() and w.is_contiguous()
+    K2 = 0
+    if a2 is not None:
+        K2 = a2.shape[1]
+        assert a2.is_contiguous() and w2.is_contiguous()
+    out = torch.empty((lay.max_rows, N), dtype=out_dtype, device=a.device)
+    lib = _lib.cuda_lib()
+    _lib.check_rc(lib.axb_grouped_gemm(
+        a.data_ptr(), a.stride(0), w.data_ptr(), a2.data_ptr() if a2 is not None else None,
+        a2.stride(0) if a2 is not None else 0, w2.data_ptr() if w2 is not None else None, out.data_ptr(),
+        out.stride(0), E, N, K, K2, 1 if trans_w else 0, float(alpha), 0 if out_dtype == torch.bfloat16 else 1,
+        _bn_for(N), lay.blk_expert.data_ptr(), lay.n_blocks.data_ptr(), lay.max_blocks,
+        _lib.status_word().data_ptr(), _lib.stream_ptr()), "grouped_gemm")
+    return out
+
+
+def grouped_gram(a, b, lay: GroupLayout, out, *, alpha=1.0, accumulate=False):
+    """out[e] (+)= alpha * a[seg_e]^T b[seg_e]; a [rows, Mg], b [rows, Ng], out fp32 [E, Mg, Ng]."""
+    E, Mg, Ng = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and a.is_contiguous() and b.is_contiguous()
+    lib = _lib.cuda_lib()
+    _lib.check_rc(lib.axb_grouped_gram(
+        a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(1), out.stride(0), E, Mg, Ng,
+        a.shape[0], float(alpha), 2 if accumulate else 1, _bn_for(Ng), lay.seg_start.data_ptr(),
+        lay.seg_rows.data_ptr(), _lib.status_word().data_ptr(), _lib.stream_ptr()), "grouped_gram")
+    return out
+
+
+def _expert_weights(experts, which):
+    """bf16 [E, N, K] stack of one projection (dequantised from NVFP4 when the experts are quantised)."""
+    if experts.nvfp4 is None:
+        return experts.gate_up_proj if which == "gate_up" else experts.down_proj
+    q = experts.nvfp4[which]
+    E, N, K2 = q["qdata"].shape
+    out = torch.empty((E, N, K2 * 2), dtype=torch.bfloat16, device=q["qdata"].device)
+    pts = q["pts"].to(torch.float32).contiguous()
+    _lib.check_rc(_lib.cuda_lib().axb_nvfp4_dequant_batched(
+        q["qdata"].data_ptr(), q["scale"].data_ptr(), pts.data_ptr(), out.data_ptr(), E, N, K2 * 2,
+        _lib.stream_ptr()), "nvfp4_dequant_batched")
+    return out
+
+
+def _grad_buffer(p):
+    g = getattr(p, "_axb_grad", None)
+    return g
+
+
+class _GroupedProj(torch.autograd.Function):
+    """One expert projection over padded segments; A [E*r, K] and B [N, r*E] are the PEFT-layout
+    adapter parameters (B viewed [N, r, E])."""
+
+    @staticmethod
+    def forward(ctx, x, experts, which, lay, A, B, scaling):
+        W = _expert_weights(experts, which)
+        E = W.shape[0]
+        if A is not None:
+            r = A.shape[0] // E
+            A16 = A.detach().to(torch.bfloat16).view(E, r, -1).contiguous()
+            Bt16 = B.detach().view(-1, r, E).permute(2, 0, 1).to(torch.bfloat16).contiguous()   # [E, N, r]
+            t = grouped_gemm(x, A16, lay, alpha=scaling)
+            y = grouped_gemm(x, W, lay, a2=t, w2=Bt16)
+            ctx.save_for_backward(x, t, A, B)
+        else:
+            y = grouped_gemm(x, W, lay)
+            ctx.save_for_backward(x)
+        ctx.experts, ctx.which, ctx.lay, ctx.scaling, ctx.has_lora = experts, which, lay, scaling, A is not None
+        ctx.train_w = experts.nvfp4 is None and W.requires_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        experts, which, lay = ctx.experts, ctx.which, ctx.lay
+        dy = dy.contiguous()
+        W = _expert_weights(experts, which)
+        E = W.shape[0]
+        dA = dB = None
+        if ctx.has_lora:
+            x, t, A, B = ctx.saved_tensors
+            r = A.shape[0] // E
+            A16 = A.detach().to(torch.bfloat16).view(E, r, -1).contiguous()
+            Bt16 = B.detach().view(-1, r, E).permute(2, 0, 1).to(torch.bfloat16).contiguous()
+            dt = grouped_gemm(dy, Bt16, lay, trans_w=True, alpha=ctx.scaling)    # s * dy B_e   [rows, r]
+            dx = grouped_gemm(dy, W, lay, trans_w=True, a2=dt, w2=A16)
+            gA = _grad_buffer(A)
+            if gA is not None:      # accumulate straight into the optimizer's flat gradient view
+                grouped_gram(dt, x, lay, gA.view(E, r, -1), accumulate=True)
+            else:
+                dA = grouped_gram(dt, x, lay, torch.empty((E, r, x.shape[1]), dtype=torch.float32,
+                                                          device=x.device)).view(E * r, -1).to(A.dtype)
+            dBt = grouped_gram(dy, t, lay, torch.empty((E, dy.shape[1], r), dtype=torch.float32, device=x.device))
+            dB_full = dBt.permute(1, 2, 0).reshape(B.shape)                      # [N, r, E] -> [N, r*E]
+            gB = _grad_buffer(B)
+            if gB is not None:
+                gB.add_(dB_full)
+            else:
+                dB = dB_full.to(B.dtype)
+        else:
+            (x,) = ctx.saved_tensors
+            dx = grouped_gemm(dy, W, lay, trans_w=True)
+        if ctx.train_w:
+            gW = grouped_gram(dy, x, lay, torch.empty(W.shape, dtype=torch.float32, device=x.device))
+            buf = _grad_buffer(W)
+            if buf is not None:
+                buf.add_(gW)
+            else:
+                W.grad = gW.to(W.dtype) if W.grad is None else W.grad + gW.to(W.dtype)
+        return dx, None, None, None, dA, dB, None
 
 
 def grouped_experts_forward(experts, x_sorted, counts):
-    outs = []
-    start = 0
-    r = experts.lora_r
-    for e, n in enumerate(counts):
-        if n == 0:
-            continue
-        xe = x_sorted[start:start + n].contiguous()
-        start += n
-        Ag = Bg = Ad = Bd = None
-        if experts.lora is not None and adapters_enabled():
-            Ag, Bg = experts.expert_lora("gate_up", e)
-            Ad, Bd = experts.expert_lora("down", e)
-        gu = _proj(xe, experts.expert_weight("gate_up", e), Ag, Bg, experts.scaling, r)
-        h = Fn.glu(gu, experts.act)
-        outs.append(_proj(h, experts.expert_weight("down", e), Ad, Bd, experts.scaling, r))
-    if not outs:
-        return x_sorted.new_zeros((0, experts.H))
-    return torch.cat(outs, 0)
+    """x_sorted [M, H]: rows grouped by local expert; counts: per-expert row counts (device tensor,
+    or a python list). Returns [M, H]."""
+    if not torch.is_tensor(counts):
+        counts = torch.tensor(counts, dtype=torch.int64, device=x_sorted.device)
+    lay = GroupLayout(counts, x_sorted.shape[0])
+    x = lay.pad(x_sorted.contiguous())
+    use_lora = experts.lora is not None and adapters_enabled()
+    L = experts.lora if use_lora else None
+    gu = _GroupedProj.apply(x, experts, "gate_up", lay, L["gate_up_A"] if L else None, L["gate_up_B"] if L else None,
+                            float(experts.scaling))
+    h = Fn.glu(gu, experts.act)
+    y = _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
+                           float(experts.scaling))
+    return lay.unpad(y)
 
 
 @torch.no_grad()

@@ -356,3 +356,79 @@ def test_dpo_step_on_gpu():
     _check_status()
     assert abs(losses[0] - math.log(2)) < 2e-2
     assert losses[-1] < losses[0] - 0.05 and obj.last_metrics["rewards/accuracies"] >= 0.75
+
+
+@pytest.mark.parametrize("counts", [[130, 0, 5, 300, 128, 1, 0, 77], [0, 0, 0, 0, 0, 0, 0, 9], [256] * 8])
+def test_grouped_gemm_modes(counts):
+    """Grouped forward (with K-extension), transposed-weight and Gram modes against per-expert fp32."""
+    from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gram
+    torch.manual_seed(31)
+    E, K, N, r = len(counts), 192, 328, 16
+    M = sum(counts)
+    dev = _dev()
+    cnt = torch.tensor(counts, device=dev)
+    lay = GroupLayout(cnt, M)
+    xs = (torch.randn(M, K) * 0.5).bfloat16().to(dev)
+    W = (torch.randn(E, N, K) * 0.05).bfloat16().to(dev)
+    t = (torch.randn(M, r) * 0.5).bfloat16().to(dev)
+    Bt = (torch.randn(E, N, r) * 0.05).bfloat16().to(dev)
+    x, tp = lay.pad(xs), lay.pad(t)
+    y = lay.unpad(grouped_gemm(x, W, lay, a2=tp, w2=Bt, alpha=0.5))
+    dy = (torch.randn(M, N) * 0.5).bfloat16().to(dev)
+    dyp = lay.pad(dy)
+    dx = lay.unpad(grouped_gemm(dyp, W, lay, trans_w=True))
+    gW = grouped_gram(dyp, x, lay, torch.empty(E, N, K, dtype=torch.float32, device=dev))
+    gW2 = grouped_gram(dyp, x, lay, gW.clone(), alpha=2.0, accumulate=True)
+    gB = grouped_gram(dyp, tp, lay, torch.empty(E, N, r, dtype=torch.float32, device=dev))
+    _check_status()
+    s = 0
+    for e, n in enumerate(counts):
+        sl = slice(s, s + n)
+        s += n
+        ref_w = dy[sl].float().t() @ xs[sl].float()
+        assert _rel_err(gW[e], ref_w) < 1e-2 or (n == 0 and float(gW[e].abs().max()) == 0.0)
+        assert torch.allclose(gW2[e], 3.0 * gW[e], rtol=1e-3, atol=1e-3)
+        if n == 0:
+            continue
+        ref = 0.5 * (xs[sl].float() @ W[e].float().t() + t[sl].float() @ Bt[e].float().t())
+        assert _rel_err(y[sl], ref) < 1e-2, e
+        assert _rel_err(dx[sl], dy[sl].float() @ W[e].float()) < 1e-2, e
+        assert _rel_err(gB[e], dy[sl].float().t() @ t[sl].float()) < 1e-2, e
+
+
+def test_moe_block_nvfp4_experts_match_dequantised_reference():
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.moe import SparseMoE
+    from axolotl_b200.ops.grouped import quantize_experts_nvfp4_
+    from axolotl_b200.ops.nvfp4 import dequantize_nvfp4
+    torch.manual_seed(32)
+    cfg = preset("tiny-qwen3-moe")
+    dev = SparseMoE(cfg, torch.bfloat16, _dev())
+    for p in dev.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    ref = SparseMoE(cfg, torch.bfloat16, _dev())
+    with torch.no_grad():
+        for p, q in zip(ref.parameters(), dev.parameters()):
+            p.copy_(q)
+    quantize_experts_nvfp4_(dev)
+    with torch.no_grad():   # reference holds the dequantised weights in bf16
+        for which, name in (("gate_up", "gate_up_proj"), ("down", "down_proj")):
+            q = dev.experts.nvfp4[which]
+            getattr(ref.experts, name).copy_(dequantize_nvfp4(q["qdata"].cpu(), q["scale"].cpu(), q["pts"].cpu()).to(_dev()))
+    for m in (dev, ref):
+        m.experts.add_lora(8, 16)
+    with torch.no_grad():
+        for k in ("gate_up_A", "gate_up_B", "down_A", "down_B"):
+            dev.experts.lora[k].normal_(0, 0.05)
+            ref.experts.lora[k].copy_(dev.experts.lora[k])
+    x = (torch.randn(260, cfg.hidden_size) * 0.5).bfloat16().to(_dev())
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, _ = dev(xa)
+    yb, _ = ref(xb)
+    gy = torch.randn_like(ya)
+    ya.backward(gy)
+    yb.backward(gy)
+    _check_status()
+    assert _rel_err(ya, yb) < 1e-2 and _rel_err(xa.grad, xb.grad) < 1e-2
+    for k in ("gate_up_A", "down_B"):
+        assert _rel_err(dev.experts.lora[k].grad, ref.experts.lora[k].grad) < 2e-2, k

@@ -81,9 +81,8 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
             raise ValueError("cannot merge a LoRA into a 4-bit base in place; run `merge-lora` on the bf16 checkpoint")
     if g("load_in_4bit") and ad != "qlora":
         raise ValueError("`load_in_4bit` without `adapter: qlora` is not supported")
-    if g("load_in_4bit"):
-        raise ValueError("bitsandbytes NF4 base weights are not available on axolotl_b200 (no bitsandbytes); "
-                         "use bf16 base weights, or NVFP4 frozen expert weights for MoE models")
+    if g("load_in_4bit") and (g("tensor_parallel_size") or 1) > 1:
+        raise ValueError("NF4 base weights cannot be combined with tensor parallelism")
     if ad == "llama-adapter":
         raise ValueError("`adapter: llama-adapter` is not supported")
     if g("lora_dropout") and (g("lora_mlp_kernel") or g("lora_qkv_kernel") or g("lora_o_kernel")):

@@ -17,38 +17,152 @@
 
 namespace {
 
-__constant__ float kE2M1[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f,
-                                -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+// bf16 bit patterns of the 8 E2M1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}, 16 bits each, held in two
+// 64-bit registers: a lookup is a shift (no memory access, no divergence).
+constexpr unsigned long long kE2M1Lo = 0x3fc03f803f000000ull;  // 1.5, 1.0, 0.5, 0.0
+constexpr unsigned long long kE2M1Hi = 0x40c0408040404000ull;  // 6.0, 4.0, 3.0, 2.0
+
+AXB_DEVICE float e2m1_to_float(uint32_t code) {
+  const unsigned long long tbl = (code & 4) ? kE2M1Hi : kE2M1Lo;
+  const uint32_t bits = (uint32_t)(tbl >> ((code & 3) * 16)) & 0xFFFFu;
+  return __uint_as_float((bits | ((code & 8) << 12)) << 16);
+}
 
 AXB_DEVICE float e4m3_to_float(uint8_t v) {
   const uint32_t sign = (v >> 7) & 1, exp = (v >> 3) & 0xF, man = v & 7;
   float f;
   if (exp == 0) f = ldexpf((float)man, -9);                 // subnormal: man * 2^-3 * 2^-6
   else if (exp == 15 && man == 7) f = __int_as_float(0x7fc00000);
-  else f = ldexpf(1.f + man * 0.125f, (int)exp - 7);
+  else f = __uint_as_float(((exp + 120u) << 23) | (man << 20));
   return sign ? -f : f;
 }
 
-// one thread per 16-element block: 8 packed bytes in, 16 bf16 out
+// One thread per 16 bytes of packed codes (32 values = two 16-element scale blocks): 16-byte
+// loads, four 16-byte stores; a warp reads 512 contiguous bytes and writes 2 KB contiguous.
 __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scale,
                                      const float* __restrict__ pts, __nv_bfloat16* __restrict__ out,
                                      long long n_blocks, long long blocks_per_pts) {
-  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks;
-       b += (long long)gridDim.x * blockDim.x) {
-    const float s = e4m3_to_float(scale[b]) * pts[b / blocks_per_pts];
-    const uint2 packed = *reinterpret_cast<const uint2*>(q + b * 8);
-    const uint32_t w[2] = {packed.x, packed.y};
-    uint32_t o[8];
+  const long long n_pairs = n_blocks >> 1;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n_pairs;
+       t += (long long)gridDim.x * blockDim.x) {
+    const long long b = t * 2;
+    const float g = pts[b / blocks_per_pts];
+    const unsigned short sc = *reinterpret_cast<const unsigned short*>(scale + b);
+    const float s0 = e4m3_to_float(sc & 0xFF) * g, s1 = e4m3_to_float(sc >> 8) * g;
+    const uint4 packed = *reinterpret_cast<const uint4*>(q + b * 8);
+    const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+    uint32_t o[16];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 4; ++i) {
+      const float s = i < 2 ? s0 : s1;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t byte = (w[i] >> (8 * j)) & 0xFF;
-        o[i * 4 + j] = pack_bf16x2(kE2M1[byte & 0xF] * s, kE2M1[byte >> 4] * s);
+        o[i * 4 + j] = pack_bf16x2(e2m1_to_float(byte & 0xF) * s, e2m1_to_float(byte >> 4) * s);
       }
+    }
     uint4* dst = reinterpret_cast<uint4*>(out + b * 16);
-    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+  }
+  // odd trailing block (K/16 odd for a single row) is handled by the last thread
+  if ((n_blocks & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+    const long long b = n_blocks - 1;
+    const float s = e4m3_to_float(scale[b]) * pts[b / blocks_per_pts];
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t byte = q[b * 8 + i];
+      out[b * 16 + 2 * i] = __float2bfloat16(e2m1_to_float(byte & 0xF) * s);
+      out[b * 16 + 2 * i + 1] = __float2bfloat16(e2m1_to_float(byte >> 4) * s);
+    }
+  }
+}
+
+// Local dispatch: out[r, :] = row_token[r] >= 0 ? scale[r] * x[row_token[r], :] : 0 for every row of
+// the padded expert-sorted layout (one warp per row; pad rows are written as zeros).
+__global__ void moe_dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
+                                         const float* __restrict__ row_scale, __nv_bfloat16* __restrict__ out,
+                                         long long n_rows, int width) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = w; r < n_rows; r += n_warps) {
+    const int tok = row_token[r];
+    __nv_bfloat16* d = out + r * width;
+    if (tok < 0) {
+      for (int c = lane * 8; c < width; c += 256) *reinterpret_cast<uint4*>(d + c) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const __nv_bfloat16* s = x + (long long)tok * width;
+    const float g = row_scale ? row_scale[r] : 1.f;
+    for (int c = lane * 8; c < width; c += 256) {
+      uint4 v = *reinterpret_cast<const uint4*>(s + c);
+      if (row_scale) {
+        uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(in[e]);
+          in[e] = pack_bf16x2(f.x * g, f.y * g);
+        }
+        v = make_uint4(in[0], in[1], in[2], in[3]);
+      }
+      *reinterpret_cast<uint4*>(d + c) = v;
+    }
+  }
+}
+
+// Local combine: out[t, :] = sum_j w[t, j] * ys[slot_row[t, j], :] (fp32 accumulation, no atomics).
+template <int TOPK_MAX>
+__global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ slot_row,
+                                        const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                        long long n_tokens, int k, int width) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long t = wid; t < n_tokens; t += n_warps) {
+    for (int c = lane * 8; c < width; c += 256) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const int r = slot_row[t * k + j];
+        const float g = w ? w[t * k + j] : 1.f;
+        const uint4 v = *reinterpret_cast<const uint4*>(ys + (long long)r * width + c);
+        const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(in[e]);
+          acc[2 * e] += g * f.x;
+          acc[2 * e + 1] += g * f.y;
+        }
+      }
+      *reinterpret_cast<uint4*>(out + t * width + c) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
+// dw[t, j] = <dy[t, :], ys[slot_row[t, j], :]>  (gradient of the routing weights; one warp per slot)
+__global__ void moe_combine_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ ys,
+                                      const int* __restrict__ slot_row, float* __restrict__ dw, long long n_slots,
+                                      int k, int width) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long sl = wid; sl < n_slots; sl += n_warps) {
+    const __nv_bfloat16* a = dy + (sl / k) * width;
+    const __nv_bfloat16* b = ys + (long long)slot_row[sl] * width;
+    float acc = 0.f;
+    for (int c = lane * 8; c < width; c += 256) {
+      const uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
+      const uint32_t ia[4] = {va.x, va.y, va.z, va.w}, ib[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = unpack_bf16x2(ia[e]), fb = unpack_bf16x2(ib[e]);
+        acc += fa.x * fb.x + fa.y * fb.y;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) dw[sl] = acc;
   }
 }
 
@@ -117,7 +231,8 @@ extern "C" int axb_nvfp4_dequant(const void* q, const void* scale, const float* 
   if (cols % 16) return -2;
   const long long nb = rows * (cols / 16);
   if (nb <= 0) return 0;
-  int grid = (int)((nb + 255) / 256 > 148 * 16 ? 148 * 16 : (nb + 255) / 256);
+  int grid = (int)((nb / 2 + 255) / 256 > 148 * 16 ? 148 * 16 : (nb / 2 + 255) / 256);
+  if (grid < 1) grid = 1;
   nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
                                                      (__nv_bfloat16*)out, nb, nb);
   return (int)cudaGetLastError();
@@ -131,9 +246,44 @@ extern "C" int axb_nvfp4_dequant_batched(const void* q, const void* scale, const
   const long long per = rows * (cols / 16);
   const long long nb = batch * per;
   if (nb <= 0) return 0;
-  int grid = (int)((nb + 255) / 256 > 148 * 16 ? 148 * 16 : (nb + 255) / 256);
+  int grid = (int)((nb / 2 + 255) / 256 > 148 * 16 ? 148 * 16 : (nb / 2 + 255) / 256);
+  if (grid < 1) grid = 1;
   nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
                                                      (__nv_bfloat16*)out, nb, per);
+  return (int)cudaGetLastError();
+}
+
+static int rows_grid(long long n_rows) {
+  const long long want = (n_rows + 7) / 8;   // 8 warps (rows) per 256-thread block
+  return (int)(want > 148 * 8 ? 148 * 8 : (want < 1 ? 1 : want));
+}
+
+// out [n_rows, width] bf16; row_token int32 [n_rows] (-1 = zero row); row_scale fp32 [n_rows] or NULL
+extern "C" int axb_moe_dispatch_rows(const void* x, const int* row_token, const float* row_scale, void* out,
+                                     long long n_rows, int width, void* stream) {
+  if (width % 8) return -2;
+  if (n_rows <= 0) return 0;
+  moe_dispatch_rows_kernel<<<rows_grid(n_rows), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)x, row_token, row_scale, (__nv_bfloat16*)out, n_rows, width);
+  return (int)cudaGetLastError();
+}
+
+// out [n_tokens, width] = sum_j w[t, j] * ys[slot_row[t, j]]; w fp32 [n_tokens, k] or NULL (= 1)
+extern "C" int axb_moe_combine_rows(const void* ys, const int* slot_row, const float* w, void* out,
+                                    long long n_tokens, int k, int width, void* stream) {
+  if (width % 8) return -2;
+  if (n_tokens <= 0) return 0;
+  moe_combine_rows_kernel<16><<<rows_grid(n_tokens), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)ys, slot_row, w, (__nv_bfloat16*)out, n_tokens, k, width);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int axb_moe_combine_dw(const void* dy, const void* ys, const int* slot_row, float* dw,
+                                  long long n_slots, int k, int width, void* stream) {
+  if (width % 8) return -2;
+  if (n_slots <= 0) return 0;
+  moe_combine_dw_kernel<<<rows_grid(n_slots), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)ys, slot_row, dw, n_slots, k, width);
   return (int)cudaGetLastError();
 }
 

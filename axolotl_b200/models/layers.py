@@ -142,16 +142,42 @@ class FusedLinear(nn.Module):
             self.lora_B[r0:r0 + rows, c0:c0 + r].copy_(B)
 
     @torch.no_grad()
+    def quantize_nf4_(self, double_quant=True, blocksize=64):
+        """Replaces the frozen bf16 weight by packed NF4 codes [N, K/2]; every GEMM that reads it
+        expands it into a shared bf16 scratch first (QLoRA base weights)."""
+        from ..ops.nf4 import quantize_nf4
+
+        if getattr(self.weight, "_axb_quant", None) is not None:
+            return
+        N, K = self.weight.shape
+        q, st = quantize_nf4(self.weight.detach(), blocksize, double_quant)
+        w = nn.Parameter(q.view(N, K // 2), requires_grad=False)
+        w._axb_quant = st
+        self.weight = w
+
+    @torch.no_grad()
+    def dequantize_(self, dtype=torch.bfloat16):
+        st = getattr(self.weight, "_axb_quant", None)
+        if st is not None:
+            from ..ops.nf4 import dequantize_nf4
+
+            self.weight = nn.Parameter(dequantize_nf4(self.weight.data, st, dtype=dtype).clone(), requires_grad=False)
+
+    @torch.no_grad()
     def merge_lora_(self):
         """W += s * B A (fp32 math, rounded once). Leaves the adapter zeroed out of the forward."""
         if self.lora_A is None or self.merged:
             return
+        self.dequantize_()
         delta = self.scaling * (self.lora_B.float() @ self.lora_A.float())
         self.weight.copy_((self.weight.float() + delta).to(self.weight.dtype))
         self.merged = True
 
     def _apply(self, fn, *a, **kw):
+        st = getattr(self.weight, "_axb_quant", None)
         super()._apply(fn, *a, **kw)
+        if st is not None:   # nn.Module._apply may rebuild the parameter object: carry the state along
+            self.weight._axb_quant = st.to(self.weight.device)
         if self.lora_A is not None:
             self.lora_A16 = None
             self.refresh_shadows()

@@ -124,6 +124,20 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
     return count_trainable_params(model)
 
 
+@torch.no_grad()
+def quantize_base_nf4_(model, double_quant=True):
+    """QLoRA: every projection of the decoder layers is stored as NF4 (embeddings, norms, router
+    and lm_head stay in bf16, as with bitsandbytes' ``load_in_4bit``). Returns bytes saved."""
+    saved = 0
+    for name, m in model.fused_linears():
+        if not isinstance(m, FusedLinear) or not name.startswith("layers."):
+            continue
+        before = m.weight.numel() * m.weight.element_size()
+        m.quantize_nf4_(double_quant)
+        saved += before - m.weight.numel() - m.weight._axb_quant.nbytes()
+    return saved
+
+
 def count_trainable_params(model) -> int:
     """Trainable parameters as PEFT would count them (the zero off-diagonal blocks of a fused
     ``lora_B`` are storage, not parameters)."""

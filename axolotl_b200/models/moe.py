@@ -139,13 +139,15 @@ class SparseMoE(nn.Module):
         if self.ep is not None:
             y = self.ep.dispatch_compute_combine(self.experts, x, w, idx)
             return y, aux
+        if x.is_cuda:
+            from ..ops.grouped import moe_local_forward
+
+            return moe_local_forward(self.experts, x, w, idx, self.E), aux
         # local: sort the T*k routed slots by expert
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = order // self.k
-        counts = torch.bincount(flat_e, minlength=self.E)
-        if not x.is_cuda:
-            counts = counts.tolist()     # the grouped CUDA path keeps the counts on the device (no sync)
+        counts = torch.bincount(flat_e, minlength=self.E).tolist()
         xs = x.index_select(0, tok)
         ys = self.experts(xs, counts)
         ws = w.reshape(-1).index_select(0, order).to(ys.dtype)

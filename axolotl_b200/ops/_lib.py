@@ -26,6 +26,11 @@ _CUDA_SIGS = {
     "axb_gemm_bf16_pair": [vp, i64, i32, vp, i64, i32, vp, i64, vp, i64, i32, i32, i32, vp, i64, vp, i64,
                            i32, f32, f32, i32, vp, C.c_ulonglong, C.c_ulonglong, i32, vp, i32, vp, vp],
     "axb_nvfp4_dequant": [vp, vp, vp, vp, i64, i64, vp],
+    "axb_moe_dispatch_rows": [vp, vp, vp, vp, i64, i32, vp],
+    "axb_moe_combine_rows": [vp, vp, vp, vp, i64, i32, i32, vp],
+    "axb_moe_combine_dw": [vp, vp, vp, vp, i64, i32, i32, vp],
+    "axb_nf4_dequant": [vp, vp, vp, i64, i32, vp],
+    "axb_fp8_block_dequant": [vp, vp, vp, i64, i64, i32, vp],
     "axb_nvfp4_dequant_batched": [vp, vp, vp, vp, i64, i64, i64, vp],
     # A, lda, W, A2, lda2, W2, C, ldc, E, N, K, K2, trans_w, alpha, out_mode, bn, blk_expert, n_blocks, max_blocks, status, stream
     "axb_grouped_gemm": [vp, i64, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp, vp],

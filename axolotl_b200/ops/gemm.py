@@ -57,6 +57,13 @@ def gemm(
     splits: int = 1,
     bn: int | None = None,
 ) -> torch.Tensor:
+    quant = getattr(b, "_axb_quant", None)
+    if quant is not None:
+        # frozen 4-bit weight: expand into the shared bf16 scratch right before the GEMM reads it
+        from .nf4 import dequantize_nf4, scratch_weight
+
+        b = dequantize_nf4(b, quant, out=scratch_weight(quant.shape, b.device) if b.is_cuda else None,
+                           dtype=torch.bfloat16 if b.is_cuda else a.dtype)
     shard = getattr(b, "_axb_shard", None)
     if shard is not None:
         return _gemm_allgather(a, b, shard, trans_a=trans_a, trans_b=trans_b, a2=a2, b2=b2, alpha=alpha,

@@ -182,21 +182,107 @@ class _GroupedProj(torch.autograd.Function):
         return dx, None, None, None, dA, dB, None
 
 
+class RoutedLayout(GroupLayout):
+    """Layout of a local (single-rank) MoE layer built from the router's top-k choice ``idx`` [T, k]:
+    adds the slot <-> padded-row maps used by the dispatch / combine kernels."""
+
+    def __init__(self, idx: torch.Tensor, E: int):
+        T, k = idx.shape
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        super().__init__(torch.bincount(flat_e, minlength=E), T * k)
+        self.k = k
+        self.slot_row = torch.empty(T * k, dtype=torch.int32, device=idx.device)
+        self.slot_row[order] = self.dest.to(torch.int32)
+        self.row_token = torch.full((self.max_rows,), -1, dtype=torch.int32, device=idx.device)
+        self.row_token[self.dest] = (order // k).to(torch.int32)
+
+
+def _dispatch_rows(x, row_token, row_scale, n_rows):
+    out = torch.empty((n_rows, x.shape[1]), dtype=x.dtype, device=x.device)
+    _lib.check_rc(_lib.cuda_lib().axb_moe_dispatch_rows(
+        x.data_ptr(), row_token.data_ptr(), row_scale.data_ptr() if row_scale is not None else None, out.data_ptr(),
+        n_rows, x.shape[1], _lib.stream_ptr()), "moe_dispatch_rows")
+    return out
+
+
+def _combine_rows(ys, slot_row, w, n_tokens, k):
+    out = torch.empty((n_tokens, ys.shape[1]), dtype=ys.dtype, device=ys.device)
+    _lib.check_rc(_lib.cuda_lib().axb_moe_combine_rows(
+        ys.data_ptr(), slot_row.data_ptr(), w.data_ptr() if w is not None else None, out.data_ptr(), n_tokens, k,
+        ys.shape[1], _lib.stream_ptr()), "moe_combine_rows")
+    return out
+
+
+class _LocalDispatch(torch.autograd.Function):
+    """x [T, H] -> padded expert-sorted rows [max_rows, H] (zeros in pad rows)."""
+
+    @staticmethod
+    def forward(ctx, x, lay):
+        ctx.lay, ctx.T = lay, x.shape[0]
+        return _dispatch_rows(x.contiguous(), lay.row_token, None, lay.max_rows)
+
+    @staticmethod
+    def backward(ctx, dxp):
+        lay = ctx.lay
+        return _combine_rows(dxp.contiguous(), lay.slot_row, None, ctx.T, lay.k), None
+
+
+class _LocalCombine(torch.autograd.Function):
+    """y[t] = sum_j w[t, j] * ys[row of slot (t, j)]."""
+
+    @staticmethod
+    def forward(ctx, ys, w, lay):
+        ctx.lay = lay
+        wf = w.detach().float().contiguous()
+        ctx.save_for_backward(ys, wf)
+        ctx.w_dtype = w.dtype
+        return _combine_rows(ys.contiguous(), lay.slot_row, wf, w.shape[0], lay.k)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ys, wf = ctx.saved_tensors
+        lay = ctx.lay
+        dy = dy.contiguous()
+        row_scale = torch.zeros(lay.max_rows, dtype=torch.float32, device=dy.device)
+        row_scale[lay.slot_row.long()] = wf.reshape(-1)
+        dys = _dispatch_rows(dy, lay.row_token, row_scale, lay.max_rows)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty(wf.shape, dtype=torch.float32, device=dy.device)
+            _lib.check_rc(_lib.cuda_lib().axb_moe_combine_dw(
+                dy.data_ptr(), ys.data_ptr(), lay.slot_row.data_ptr(), dw.data_ptr(), wf.numel(), lay.k, dy.shape[1],
+                _lib.stream_ptr()), "moe_combine_dw")
+            dw = dw.to(ctx.w_dtype)
+        return dys, dw, None
+
+
+def moe_local_forward(experts, x, w, idx, E):
+    """Whole local MoE expert pass on CUDA: dispatch -> grouped projections -> weighted combine."""
+    lay = RoutedLayout(idx, E)
+    xp = _LocalDispatch.apply(x, lay)
+    yp = grouped_experts_padded(experts, xp, lay)
+    return _LocalCombine.apply(yp, w, lay)
+
+
 def grouped_experts_forward(experts, x_sorted, counts):
     """x_sorted [M, H]: rows grouped by local expert; counts: per-expert row counts (device tensor,
     or a python list). Returns [M, H]."""
     if not torch.is_tensor(counts):
         counts = torch.tensor(counts, dtype=torch.int64, device=x_sorted.device)
     lay = GroupLayout(counts, x_sorted.shape[0])
-    x = lay.pad(x_sorted.contiguous())
+    return lay.unpad(grouped_experts_padded(experts, lay.pad(x_sorted.contiguous()), lay))
+
+
+def grouped_experts_padded(experts, x, lay):
+    """x: padded expert-sorted rows [lay.max_rows, H] -> same layout [lay.max_rows, H]."""
     use_lora = experts.lora is not None and adapters_enabled()
     L = experts.lora if use_lora else None
     gu = _GroupedProj.apply(x, experts, "gate_up", lay, L["gate_up_A"] if L else None, L["gate_up_B"] if L else None,
                             float(experts.scaling))
     h = Fn.glu(gu, experts.act)
-    y = _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
-                           float(experts.scaling))
-    return lay.unpad(y)
+    return _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
+                              float(experts.scaling))
 
 
 @torch.no_grad()

@@ -95,10 +95,20 @@ class _LinearFn(torch.autograd.Function):
         return dx, dW, dbias
 
 
+def _cpu_weight(W, dtype):
+    """Dense view of a (possibly 4-bit) weight for the CPU reference path."""
+    st = getattr(W, "_axb_quant", None)
+    if st is not None:
+        from .nf4 import dequantize_nf4
+
+        return dequantize_nf4(W.data, st, dtype=dtype)
+    return W.to(dtype)
+
+
 def linear(x, W, bias=None):
     """``x @ W^T (+ bias)``; 2-D or N-D ``x``. CPU tensors use torch ops directly."""
     if not x.is_cuda:
-        return torch.nn.functional.linear(x, W.to(x.dtype), None if bias is None else bias.to(x.dtype))
+        return torch.nn.functional.linear(x, _cpu_weight(W, x.dtype), None if bias is None else bias.to(x.dtype))
     shp = x.shape
     y = _LinearFn.apply(x.reshape(-1, shp[-1]).contiguous(), W, bias)
     return y.view(*shp[:-1], y.shape[-1])
@@ -117,7 +127,7 @@ def lora_linear(x, W, A, B, A16, B16, scaling, blocks, bias=None, dropout_p=0.0,
                                  B.to(x.dtype), None)
             y = base + scaling * lo
         else:
-            y = torch.nn.functional.linear(x2, W.to(x2.dtype), None if bias is None else bias.to(x2.dtype))
+            y = torch.nn.functional.linear(x2, _cpu_weight(W, x2.dtype), None if bias is None else bias.to(x2.dtype))
             y = y + scaling * ((xd @ A.to(x2.dtype).t()) @ B.to(x2.dtype).t())
         return y.view(*shp[:-1], y.shape[-1])
     y = _LoRALinearFn.apply(x2.contiguous(), W, A, B, A16, B16, float(scaling), blocks, bias)

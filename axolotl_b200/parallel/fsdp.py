@@ -57,7 +57,8 @@ class FSDPContext:
 
     @torch.no_grad()
     def shard_model(self, model):
-        mods = [m for _, m in model.fused_linears() if self.shardable(m, self.world) and not m.weight.requires_grad]
+        mods = [m for _, m in model.fused_linears() if self.shardable(m, self.world) and not m.weight.requires_grad
+                and getattr(m.weight, "_axb_quant", None) is None]   # 4-bit weights stay replicated (already 4x smaller)
         total = sum(m.weight.numel() // self.world for m in mods)
         if total == 0:
             return 0

@@ -91,6 +91,12 @@ def setup_adapter(cfg, model):
         _apply_freezing(cfg, model)
         return None
     pm.call("pre_lora_load", cfg, model)
+    if cfg.get("adapter") == "qlora" and cfg.get("load_in_4bit"):
+        from ..models.lora import quantize_base_nf4_
+
+        qcfg = cfg.get("bnb_config_kwargs") or {}
+        saved = quantize_base_nf4_(model, double_quant=qcfg.get("bnb_4bit_use_double_quant", True) is not False)
+        LOG.info("base projections stored as NF4: %.2f GiB saved", saved / 1024 ** 3)
     adapter_dtype = torch.float32 if cfg.get("peft_autocast_adapter_dtype", True) is not False else model.dtype
     n = inject_lora(model, spec, adapter_dtype=adapter_dtype)
     if cfg.get("lora_model_dir"):

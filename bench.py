@@ -113,16 +113,17 @@ def reference_arm(args):
     return 0
 
 
-def build_batches(n_batches, vocab, seed, rank):
+def build_batches(n_batches, vocab, seed, rank, seq_len=SEQ_LEN, rows=1):
     """Synthetic packed batches: sample lengths uniform in [256, 4096], packed first-fit into
-    8192-token rows (micro-batch 1), labels == inputs, position ids restart per sample."""
+    ``seq_len``-token rows (``rows`` rows per micro-batch), labels == inputs, position ids restart
+    per sample."""
     from axolotl_b200.data.collator import PackedCollator
     from axolotl_b200.data.packing import MultipackBatchSampler
     from axolotl_b200.data.synthetic import synthetic_varlen
 
-    ds = synthetic_varlen(max(64, n_batches * 6), 256, 4096, 3, vocab, 0.0, seed=seed + 1000 * rank)
-    samp = MultipackBatchSampler(ds.lengths, SEQ_LEN, 1, real_batches=True, seed=seed)
-    coll = PackedCollator(pad_token_id=0, sequence_len=SEQ_LEN, pad_to_sequence_len=True)
+    ds = synthetic_varlen(max(64, n_batches * 6 * rows), 256, min(4096, seq_len), 3, vocab, 0.0, seed=seed + 1000 * rank)
+    samp = MultipackBatchSampler(ds.lengths, seq_len, rows, real_batches=True, seed=seed)
+    coll = PackedCollator(pad_token_id=0, sequence_len=seq_len, pad_to_sequence_len=True)
     out = []
     for b in samp:
         out.append(coll([[ds[i] for i in bin_] for bin_ in b]))
@@ -141,7 +142,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is then not the headline config)")
     ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--config", default="lora8b", choices=["lora8b", "moe"],
+                    help="lora8b: the headline Llama-3-8B LoRA FSDP run; moe: Qwen3-MoE-30B-A3B with NVFP4 experts, "
+                         "expert + attention LoRA, expert parallelism over all ranks (4096-token rows, micro-batch 2)")
     args = ap.parse_args()
+    if args.config == "moe" and args.model == MODEL:
+        args.model = "qwen3-moe-30b-a3b"
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -172,11 +178,22 @@ def main():
     cfg = preset(args.model, **overrides)
     torch.manual_seed(0)
     model = CausalLM(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
-    inject_lora(model, LoraSpec(r=16, lora_alpha=32, target_modules=list(ALL_LINEAR)))
-    if world > 1:
-        from axolotl_b200.parallel import build_parallel
+    if args.config == "moe":
+        from axolotl_b200.ops.grouped import quantize_experts_nvfp4_
 
-        parallel = build_parallel(model, dp_shard=world, device=dev)
+        quantize_experts_nvfp4_(model)
+        inject_lora(model, LoraSpec(r=16, lora_alpha=32, target_modules=["q_proj", "k_proj", "v_proj", "o_proj"],
+                                    target_parameters=["mlp.experts.gate_up_proj", "mlp.experts.down_proj"]))
+        if world > 1:
+            from axolotl_b200.parallel import build_parallel
+
+            parallel = build_parallel(model, ep=world, device=dev)
+    else:
+        inject_lora(model, LoraSpec(r=16, lora_alpha=32, target_modules=list(ALL_LINEAR)))
+        if world > 1:
+            from axolotl_b200.parallel import build_parallel
+
+            parallel = build_parallel(model, dp_shard=world, device=dev)
     opt = FlatAdamW(build_param_groups(model.named_parameters(), weight_decay=0.0), lr=2e-4, max_grad_norm=1.0,
                     alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1))
     opt.bind_model_shadows(model)
@@ -187,7 +204,8 @@ def main():
     trainer = Trainer(model, opt, make_lr_lambda("constant", 10 ** 6, 0), targs, lambda e: [], parallel=parallel, device=dev)
     model.train()
 
-    cpu_batches = build_batches(W + K, cfg.vocab_size, seed=0, rank=rank)
+    cpu_batches = build_batches(W + K, cfg.vocab_size, seed=0, rank=rank,
+                                seq_len=4096 if args.config == "moe" else SEQ_LEN, rows=2 if args.config == "moe" else 1)
     for b in cpu_batches:
         for k in ("input_ids", "labels", "position_ids"):
             b[k] = b[k].pin_memory()
@@ -239,14 +257,17 @@ def main():
         value = total_tokens / (ms / 1e3)
         e2e_value = total_tokens / (e2e_ms / 1e3)
         print(json.dumps({
-            "metric": "train tokens/s/box (max over ranks), Llama-3-8B LoRA FSDP2",
+            "metric": "train tokens/s/box (max over ranks), Llama-3-8B LoRA FSDP2" if args.config == "lora8b" else
+                      "train tokens/s/box (max over ranks), Qwen3-MoE-30B-A3B NVFP4 expert-LoRA EP",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform token ids, lengths U[256,4096] packed to 8192; random-init weights",
             "impl": "ours",
             "config": {"model": args.model + ("" if args.layers is None else f"[layers={args.layers}]"),
-                       "global_batch": world, "seq_len": SEQ_LEN,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single", "lora_r": 16, "lora_alpha": 32,
+                       "global_batch": world * (2 if args.config == "moe" else 1),
+                       "seq_len": 4096 if args.config == "moe" else SEQ_LEN,
+                       "parallelism": (f"ep{world}" if args.config == "moe" else f"fsdp{world}") if world > 1 else "single",
+                       "lora_r": 16, "lora_alpha": 32,
                        "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 1,
                        "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2"},
             "clocks": clocks,

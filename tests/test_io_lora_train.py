@@ -281,3 +281,48 @@ def test_merge_sharded_fsdp_weights(tmp_path):
     merge_sharded_fsdp_weights(str(tmp_path / "s"), str(tmp_path / "o"), dtype=torch.float32)
     back = st.load_file(str(tmp_path / "o" / "model.safetensors"))
     assert torch.equal(back["w"], full["w"]) and torch.equal(back["b"], full["b"])
+
+
+def test_nf4_roundtrip_and_qlora_training(tmp_path):
+    """NF4 quantise/dequantise error bounds, double-quant storage, and a QLoRA run through the
+    run builder that learns with frozen 4-bit projections."""
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.models.layers import FusedLinear
+    from axolotl_b200.ops.nf4 import dequantize_nf4, quantize_nf4
+    from axolotl_b200.train.run import train
+
+    torch.manual_seed(0)
+    w = torch.randn(128, 256) * 0.02
+    for dq in (False, True):
+        q, st = quantize_nf4(w, double_quant=dq)
+        assert q.dtype == torch.uint8 and q.numel() == w.numel() // 2
+        err = (dequantize_nf4(q, st, dtype=torch.float32) - w).norm() / w.norm()
+        assert err < 0.11
+    # absmax maps to code 15 (or 0) exactly
+    blk = torch.zeros(64); blk[3] = 2.0; blk[7] = -1.0
+    q, st = quantize_nf4(blk, double_quant=False)
+    d = dequantize_nf4(q, st, dtype=torch.float32)
+    assert d[3] == 2.0 and abs(d[7] + 1.0) < 0.11 and float(d[0]) == 0.0
+
+    lin = FusedLinear(256, [128], ["x"], dtype=torch.float32)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    x = torch.randn(5, 256)
+    y_ref = x @ w.t()
+    lin.quantize_nf4_()
+    assert lin.weight.dtype == torch.uint8 and lin.weight.shape == (128, 128)
+    assert ((lin(x) - y_ref).norm() / y_ref.norm()) < 0.12
+
+    cfg = load_cfg({"model_preset": "tiny-llama", "adapter": "qlora", "load_in_4bit": True, "lora_r": 8, "lora_alpha": 16,
+                    "lora_target_linear": True, "sequence_len": 256, "micro_batch_size": 2, "gradient_accumulation_steps": 1,
+                    "max_steps": 12, "learning_rate": 2e-3, "optimizer": "adamw_torch", "lr_scheduler": "constant",
+                    "output_dir": str(tmp_path / "q"), "device": "cpu", "logging_steps": 1, "sample_packing": True,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 64, "min_length": 32,
+                                  "max_length": 128, "max_input_id": 400}]})
+    model, _, trainer = train(cfg)
+    assert all(getattr(m.weight, "_axb_quant", None) is not None for n, m in model.fused_linears() if n.startswith("layers."))
+    losses = [l["loss"] for l in trainer.log_history if "loss" in l]
+    assert losses[-1] < losses[0]
+    assert (tmp_path / "q" / "adapter_model.safetensors").exists()

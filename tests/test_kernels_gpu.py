@@ -432,3 +432,41 @@ def test_moe_block_nvfp4_experts_match_dequantised_reference():
     assert _rel_err(ya, yb) < 1e-2 and _rel_err(xa.grad, xb.grad) < 1e-2
     for k in ("gate_up_A", "down_B"):
         assert _rel_err(dev.experts.lora[k].grad, ref.experts.lora[k].grad) < 2e-2, k
+
+
+def test_nf4_dequant_kernel_and_qlora_linear():
+    from axolotl_b200.models.layers import FusedLinear
+    from axolotl_b200.ops.nf4 import dequantize_fp8_block, dequantize_nf4, quantize_nf4
+    torch.manual_seed(41)
+    w = torch.randn(384, 512) * 0.05
+    for dq in (False, True):
+        q, st = quantize_nf4(w, double_quant=dq)
+        ref = dequantize_nf4(q, st, dtype=torch.float32)
+        got = dequantize_nf4(q.to(_dev()), st.to(_dev()))
+        _check_status()
+        assert torch.equal(got.cpu(), ref.bfloat16())
+    lin = FusedLinear(512, [384], ["x"], device=_dev())
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    lin.quantize_nf4_()
+    lin.add_lora(8, 16)
+    with torch.no_grad():
+        lin.lora_B.normal_(0, 0.05)
+    lin.refresh_shadows()
+    x = (torch.randn(200, 512) * 0.5).bfloat16().to(_dev()).requires_grad_(True)
+    y = lin(x)
+    y.float().square().sum().backward()
+    _check_status()
+    wd = dequantize_nf4(q, st, dtype=torch.float32)
+    xr = x.detach().cpu().float().requires_grad_(True)
+    A, B = lin.lora_A.detach().cpu().float(), lin.lora_B.detach().cpu().float()
+    yr = xr @ wd.t() + lin.scaling * ((xr @ A.t()) @ B.t())
+    yr.square().sum().backward()
+    assert _rel_err(y.cpu(), yr.detach()) < 2e-2 and _rel_err(x.grad.cpu(), xr.grad) < 3e-2
+    # blockwise FP8
+    wf = (torch.randn(256, 384) * 0.5).to(torch.float8_e4m3fn)
+    sc = torch.rand(2, 3) + 0.5
+    ref8 = dequantize_fp8_block(wf, sc)
+    got8 = dequantize_fp8_block(wf.to(_dev()), sc.to(_dev()))
+    _check_status()
+    assert torch.equal(got8.cpu(), ref8)

@@ -371,6 +371,12 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout,
 //   S^T  [kv, q]  = K . Q^T        dP^T [kv, q] = V . dO^T
 //   dV   [kv, d] += P^T . dO       dK   [kv, d] += dS^T . Q
 //   dQ^T [d,  q]  = K^T . dS^T     (drained with fp32 atomics into dq_acc)
+// Two softmax warpgroups alternate iterations: S^T / dP^T (TMEM) and P^T / dS^T (shared memory)
+// are double buffered, so the tensor core computes S^T, dP^T of iteration i+1 while warpgroup
+// i % 2 turns S^T(i) into P^T, dS^T and drains dQ^T(i). dQ^T(i) reuses the TMEM columns of S^T(i),
+// which is dead once P^T(i) is written; with D = 128 all 512 columns are in use:
+//   [S^T0 | dP^T0 | S^T1 | dP^T1 | dV (D) | dK (D)]
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps
 template <int D>
 struct BwdCfg {
   static constexpr int HALVES = D / 64;
@@ -380,17 +386,16 @@ struct BwdCfg {
   static constexpr int PT_BYTES = HALF_BYTES;           // P^T / dS^T: [128 kv x 64 q]
   static constexpr int STAGES = 2;
   static constexpr int SMEM =
-      2 * KV_BYTES + STAGES * 2 * Q_BYTES + 2 * PT_BYTES + 1024 /*lse+delta*/ + 1024 + 256;
-  static constexpr int ST_COL = 0;     // S^T   64 cols
-  static constexpr int DPT_COL = 64;   // dP^T  64 cols
-  static constexpr int DQT_COL = 128;  // dQ^T  64 cols
-  static constexpr int DV_COL = 192;   // D cols
-  static constexpr int DK_COL = 192 + D;
+      2 * KV_BYTES + STAGES * 2 * Q_BYTES + 4 * PT_BYTES + 1024 /*lse+delta*/ + 1024 + 256;
+  static constexpr int ST_COL = 0;     // S^T(b) at ST_COL + 128 b, 64 cols; dQ^T(b) aliases it
+  static constexpr int DPT_COL = 64;   // dP^T(b) at DPT_COL + 128 b, 64 cols
+  static constexpr int DV_COL = 256;   // D cols
+  static constexpr int DK_COL = 256 + D;
   static constexpr int TMEM_COLS = 512;
 };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
     flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 over qkv
                      const __grid_constant__ CUtensorMap tm_q,    // box 64 x 64 over qkv
                      const __grid_constant__ CUtensorMap tm_do,   // box 64 x 64 over dO
@@ -421,22 +426,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* sV = sK + C::KV_BYTES;
   uint8_t* sQ = sV + C::KV_BYTES;                    // [STAGES]
   uint8_t* sdO = sQ + C::STAGES * C::Q_BYTES;        // [STAGES]
-  uint8_t* sPT = sdO + C::STAGES * C::Q_BYTES;
-  uint8_t* sdST = sPT + C::PT_BYTES;
-  float* s_lse = reinterpret_cast<float*>(sdST + C::PT_BYTES);  // [2][64]
-  float* s_delta = s_lse + 128;                                 // [2][64]
+  uint8_t* sPT = sdO + C::STAGES * C::Q_BYTES;       // [2]
+  uint8_t* sdST = sPT + 2 * C::PT_BYTES;             // [2]
+  float* s_lse = reinterpret_cast<float*>(sdST + 2 * C::PT_BYTES);  // [2][64]
+  float* s_delta = s_lse + 128;                                     // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 128);
   uint64_t* kv_full = bars + 0;
   uint64_t* q_full = bars + 1;    // [2]  (Q and dO of a stage)
   uint64_t* q_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;    // S^T and dP^T ready
-  uint64_t* s_empty = bars + 6;   // softmax threads consumed S^T / dP^T
-  uint64_t* pt_full = bars + 7;   // P^T / dS^T written to smem
-  uint64_t* pt_empty = bars + 8;  // MMAs reading P^T / dS^T retired
-  uint64_t* dq_full = bars + 9;
-  uint64_t* dq_empty = bars + 10;
-  uint64_t* acc_full = bars + 11;  // dK / dV final
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* s_full = bars + 5;    // [2]  S^T(b) and dP^T(b) ready
+  uint64_t* pt_full = bars + 7;   // [2]  P^T(b) / dS^T(b) written to smem
+  uint64_t* dq_full = bars + 9;   // [2]  dQ^T(b) ready (and every MMA reading P^T(b)/dS^T(b) retired)
+  uint64_t* st_free = bars + 11;  // [2]  dQ^T(b) drained: TMEM and smem buffers b reusable
+  uint64_t* acc_full = bars + 13; // dK / dV final
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -445,12 +448,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_empty, 128);
-    mbar_init(pt_full, 128);
-    mbar_init(pt_empty, 1);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&pt_full[b], 128);
+      mbar_init(&dq_full[b], 1);
+      mbar_init(&st_free[b], 128);
+    }
     mbar_init(acc_full, 1);
     mbar_fence_init();
   }
@@ -497,156 +500,192 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sdST);
       bool ok = mbar_wait(kv_full, 0, p.status, AXB_TIMEOUT_FULL);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+      // S^T(i) = K . Q(i)^T and dP^T(i) = V . dO(i)^T into TMEM buffer i & 1
+      auto issue_scores = [&](int i) -> bool {
+        const int st = i & 1, b = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&q_full[st], ph, p.status, AXB_TIMEOUT_FULL)) return false;
+        // buffer b was last used by iteration i - 2: its dQ^T must have been drained
+        if (i >= 2 && !mbar_wait(&st_free[b], ((i - 2) >> 1) & 1, p.status, AXB_TIMEOUT_TMEM_EMPTY))
+          return false;
+        tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + st * C::Q_BYTES);
         const uint32_t do_addr = smem_u32(sdO + st * C::Q_BYTES);
-        if (!mbar_wait(&q_full[st], ph, p.status, AXB_TIMEOUT_FULL)) break;
-        if (!mbar_wait(s_empty, (it & 1) ^ 1, p.status, AXB_TIMEOUT_TMEM_EMPTY)) break;
-        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {  // reduce over d
           const uint32_t koff = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
           const uint32_t qoff = (kk / 4) * C::Q_HALF + (kk % 4) * 32;
-          umma_f16(tmem_base + C::ST_COL, make_smem_desc_sw128(k_addr + koff, 16, 1024),
+          umma_f16(tmem_base + C::ST_COL + 128 * b, make_smem_desc_sw128(k_addr + koff, 16, 1024),
                    make_smem_desc_sw128(q_addr + qoff, 16, 1024), idesc_st, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t koff = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
           const uint32_t qoff = (kk / 4) * C::Q_HALF + (kk % 4) * 32;
-          umma_f16(tmem_base + C::DPT_COL, make_smem_desc_sw128(v_addr + koff, 16, 1024),
+          umma_f16(tmem_base + C::DPT_COL + 128 * b, make_smem_desc_sw128(v_addr + koff, 16, 1024),
                    make_smem_desc_sw128(do_addr + qoff, 16, 1024), idesc_st, kk > 0);
         }
-        umma_commit(s_full);
-        if (!mbar_wait(pt_full, it & 1, p.status, AXB_TIMEOUT_GENERIC)) break;
-        if (!mbar_wait(dq_empty, (it & 1) ^ 1, p.status, AXB_TIMEOUT_TMEM_EMPTY)) break;
+        umma_commit(&s_full[b]);
+        return true;
+      };
+      ok = ok && issue_scores(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1, b = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (it + 1 < n_iter && !issue_scores(it + 1)) break;   // keeps the tensor core busy during softmax(it)
+        const uint32_t q_addr = smem_u32(sQ + st * C::Q_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + st * C::Q_BYTES);
+        const uint32_t ptb = pt_addr + b * C::PT_BYTES, dstb = dst_addr + b * C::PT_BYTES;
+        if (!mbar_wait(&pt_full[b], ph, p.status, AXB_TIMEOUT_GENERIC)) break;
         tc_fence_after();
         // reduce over the 64 q rows of this tile: 4 K-steps of 16
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           // dV += P^T . dO   (B = dO tile, MN-major: chunk stride = one 64x64 half)
-          umma_f16(tmem_base + C::DV_COL, make_smem_desc_sw128(pt_addr + kk * 32, 16, 1024),
+          umma_f16(tmem_base + C::DV_COL, make_smem_desc_sw128(ptb + kk * 32, 16, 1024),
                    make_smem_desc_sw128(do_addr + kk * 2048, C::Q_HALF, 1024), idesc_acc,
                    (it > 0 || kk > 0));
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          umma_f16(tmem_base + C::DK_COL, make_smem_desc_sw128(dst_addr + kk * 32, 16, 1024),
+          umma_f16(tmem_base + C::DK_COL, make_smem_desc_sw128(dstb + kk * 32, 16, 1024),
                    make_smem_desc_sw128(q_addr + kk * 2048, C::Q_HALF, 1024), idesc_acc,
                    (it > 0 || kk > 0));
         }
         umma_commit(&q_empty[st]);
-        // dQ^T [d, q] = K^T . dS^T : reduce over the 128 kv rows: 8 K-steps of 16
+        // dQ^T [d, q] = K^T . dS^T over the 128 kv rows (8 K-steps of 16), into the columns of S^T(b)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          umma_f16(tmem_base + C::DQT_COL,
+          umma_f16(tmem_base + C::ST_COL + 128 * b,
                    make_smem_desc_sw128(k_addr + kk * 2048, HALF_BYTES, 1024),
-                   make_smem_desc_sw128(dst_addr + kk * 2048, HALF_BYTES, 1024), idesc_dq, kk > 0);
+                   make_smem_desc_sw128(dstb + kk * 2048, HALF_BYTES, 1024), idesc_dq, kk > 0);
         }
-        umma_commit(dq_full);
-        umma_commit(pt_empty);
+        umma_commit(&dq_full[b]);
       }
       umma_commit(acc_full);
     }
   } else {
     const int lg = warp & 3;
-    const int r = lg * 32 + lane;  // kv row in tile (S^T, dP^T, dK, dV) or d row (dQ^T)
-    const int st_tid = threadIdx.x - 64;  // 0..127
+    const int grp = (warp - 2) >> 2;   // softmax warpgroup: handles iterations with it % 2 == grp
+    const int r = lg * 32 + lane;      // kv row in tile (S^T, dP^T, dK, dV) or d row (dQ^T)
+    const int st_tid = threadIdx.x - 64 - grp * 128;  // 0..127 inside the warpgroup
     const int kv_idx = kv0 + r;
     const uint32_t lane_off = uint32_t(lg * 32) << 16;
+    const uint32_t st_col = C::ST_COL + 128 * grp, dpt_col = C::DPT_COL + 128 * grp;
+    uint8_t* my_pt = sPT + grp * C::PT_BYTES;
+    uint8_t* my_dst = sdST + grp * C::PT_BYTES;
+    const float* lse = s_lse + grp * 64;
+    const float* dlt = s_delta + grp * 64;
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int it = grp; it < n_iter && ok; it += 2) {
+      const uint32_t ph = (it >> 1) & 1;
       const int head = kv_head * group + it / n_qt;
       const int qt0 = (q_first + it % n_qt) * 64;  // doc-relative first q row of the tile
-      // stage lse / delta of the 64 q rows (double-buffered by iteration parity)
+      // stage lse / delta of the 64 q rows (one buffer per warpgroup; the previous iteration of
+      // this group finished reading it before its threads got here: bar.sync below orders that)
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
       {
-        float* dst = (st_tid < 64 ? s_lse : s_delta) + (it & 1) * 64;
+        float* dst = (st_tid < 64 ? s_lse : s_delta) + grp * 64;
         const int i = st_tid & 63;
         const int q = qt0 + i;
         // rows outside the document or outside this rank's q window get lse = +inf -> P = 0
-        float val = st_tid < 64 ? INFINITY : 0.f;
+        // staged as -lse (so that P = exp2(S * sl2 + nlse)) and delta * scale
+        float val = st_tid < 64 ? -INFINITY : 0.f;
         const long long lrow = (long long)doc_start + q - p.q_row_off;
         if (q < doc_len && lrow >= 0 && lrow < p.q_rows) {
           const long long off = (long long)head * p.q_rows + lrow;
-          val = st_tid < 64 ? p.lse2[off] : p.delta[off];
+          val = st_tid < 64 ? -p.lse2[off] : p.delta[off] * p.scale;
         }
         dst[i] = val;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(s_full, it & 1, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+      if (!mbar_wait(&s_full[grp], ph, p.status, AXB_TIMEOUT_TMEM_FULL)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (!mbar_wait(pt_empty, (it & 1) ^ 1, p.status, AXB_TIMEOUT_GENERIC)) {
-        ok = false;
-        break;
-      }
-      const float* lse = s_lse + (it & 1) * 64;
-      const float* dlt = s_delta + (it & 1) * 64;
+      // Only tiles that touch the diagonal or the end of the document need per-element masks
+      // (q rows outside the document already carry nlse = -inf, i.e. P = 0).
+      const bool need_mask = (qt0 < kv0 + 127) || (kv0 + 128 > doc_len);
+      const bool row_in_doc = kv_idx < doc_len;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tmem_base + lane_off + C::ST_COL + c * 32, sr);
-        tmem_ld_32x32(tmem_base + lane_off + C::DPT_COL + c * 32, dr);
+        tmem_ld_32x32(tmem_base + lane_off + st_col + c * 32, sr);
+        tmem_ld_32x32(tmem_base + lane_off + dpt_col + c * 32, dr);
         tmem_ld_wait();
         uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv[2];
+        for (int i = 0; i < 32; i += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(lse + c * 32 + i);
+          const float4 ds = *reinterpret_cast<const float4*>(dlt + c * 32 + i);
+          const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+          const float dsv[4] = {ds.x, ds.y, ds.z, ds.w};
+          float pv[4], dv[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qi = c * 32 + i + e;
-            const int q = qt0 + qi;
-            const bool vis = (q >= kv_idx) && (q < doc_len) && (kv_idx < doc_len);
-            const float pr = vis ? fast_exp2(__uint_as_float(sr[i + e]) * p.sl2 - lse[qi]) : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            float pr = fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.sl2, nlv[e]));
+            if (need_mask) {
+              const int q = qt0 + c * 32 + i + e;
+              if (!(row_in_doc && q >= kv_idx)) pr = 0.f;
+            }
             pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(dr[i + e]) - dlt[qi]) * p.scale;
+            dv[e] = pr * fmaf(__uint_as_float(dr[i + e]), p.scale, -dsv[e]);
           }
           pk[i >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pk[(i >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
           dk[i >> 1] = pack_bf16x2(dv[0], dv[1]);
+          dk[(i >> 1) + 1] = pack_bf16x2(dv[2], dv[3]);
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint32_t off = sw128_chunk_off(r, c * 4 + q);
-          *reinterpret_cast<uint4*>(sPT + off) =
+          *reinterpret_cast<uint4*>(my_pt + off) =
               make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(sdST + off) =
+          *reinterpret_cast<uint4*>(my_dst + off) =
               make_uint4(dk[q * 4], dk[q * 4 + 1], dk[q * 4 + 2], dk[q * 4 + 3]);
         }
       }
       tc_fence_before();
-      mbar_arrive(s_empty);
       fence_proxy_async_smem();
-      mbar_arrive(pt_full);
+      mbar_arrive(&pt_full[grp]);
       // drain dQ^T: this thread owns d = r (only rows < D are meaningful)
-      if (!mbar_wait(dq_full, it & 1, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+      if (!mbar_wait(&dq_full[grp], ph, p.status, AXB_TIMEOUT_TMEM_FULL)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      {
+        // valid q columns of this tile: inside the document and inside this rank's q window
+        const long long row0 = (long long)doc_start + qt0 - p.q_row_off;   // local row of column 0
+        int i_lo = row0 < 0 ? (int)(-row0) : 0;
+        int i_hi = min(64, doc_len - qt0);
+        if (row0 + i_hi > p.q_rows) i_hi = (int)(p.q_rows - row0);
+        float* col = p.dq_acc + row0 * p.out_ld + (long long)head * D + r;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t qr[32];
-        tmem_ld_32x32(tmem_base + lane_off + C::DQT_COL + c * 32, qr);
-        tmem_ld_wait();
-        if (r < D) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t qr[32];
+          tmem_ld_32x32(tmem_base + lane_off + st_col + c * 32, qr);
+          tmem_ld_wait();
+          if (r < D) {
+            if (i_lo <= c * 32 && i_hi >= c * 32 + 32) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int q = qt0 + c * 32 + i;
-            const long long lrow = (long long)doc_start + q - p.q_row_off;
-            if (q < doc_len && lrow >= 0 && lrow < p.q_rows)
-              atomicAdd(p.dq_acc + lrow * p.out_ld + (long long)head * D + r, __uint_as_float(qr[i]));
+              for (int i = 0; i < 32; ++i)
+                atomicAdd(col + (long long)(c * 32 + i) * p.out_ld, __uint_as_float(qr[i]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i >= i_lo && c * 32 + i < i_hi)
+                  atomicAdd(col + (long long)(c * 32 + i) * p.out_ld, __uint_as_float(qr[i]));
+            }
           }
         }
       }
       tc_fence_before();
-      mbar_arrive(dq_empty);
+      mbar_arrive(&st_free[grp]);
     }
-    // final dK / dV
-    if (ok && mbar_wait(acc_full, 0, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+    // final dK / dV (warpgroup 0)
+    if (grp == 0 && ok && mbar_wait(acc_full, 0, p.status, AXB_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool row_ok = kv_idx < doc_len && n_iter > 0;
       const long long grow = (long long)doc_start + kv_idx;  // global kv row
@@ -746,7 +785,7 @@ int launch_bwd(const CUtensorMap& tkv, const CUtensorMap& tq, const CUtensorMap&
     attr = true;
   }
   dim3 grid(p.Hk, p.n_tiles);
-  kern<<<grid, kThreads, C::SMEM, st>>>(tkv, tq, tdo, p);
+  kern<<<grid, kBwdThreads, C::SMEM, st>>>(tkv, tq, tdo, p);
   return (int)cudaGetLastError();
 }
 }  // namespace

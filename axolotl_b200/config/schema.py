@@ -491,7 +491,6 @@ UNSUPPORTED_KEYS = {
     "torch_compile": "no tracing compiler is used; kernels are hand-written",
     "unsloth_cross_entropy_loss": "the native chunked linear+CE kernel is always used",
     "use_ray": "the Ray launcher is not available; use --launcher torchrun",
-    "peft_use_dora": "DoRA adapters are not implemented yet",
     "llama4_linearized_experts": "Llama-4 is not a supported architecture",
     "use_onebitllms": "1-bit LLM training is not supported",
     "flash_optimum": "BetterTransformer is not used",

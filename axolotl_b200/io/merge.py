@@ -46,6 +46,9 @@ def load_adapter_tensors(adapter_dir: str):
     for k, v in sd.items():
         m = re.match(r"base_model\.model\.(.+)\.lora_(A|B)(?:\.default)?\.weight$", k)
         if not m:
+            mm = re.match(r"base_model\.model\.(.+)\.lora_magnitude_vector(?:\.default)?(?:\.weight)?$", k)
+            if mm:   # DoRA magnitude
+                pairs.setdefault(mm.group(1), {})["M"] = v.float().reshape(-1)
             continue
         pairs.setdefault(m.group(1), {})[m.group(2)] = v.float()
     return cfg, pairs
@@ -70,7 +73,10 @@ def merge_tensor(name: str, w: torch.Tensor, cfg: dict, pairs: dict, shard: dict
         if mod in pairs and "A" in pairs[mod] and "B" in pairs[mod]:
             if cfg.get("fan_in_fan_out"):
                 return (w.float() + _delta(pairs[mod], _adapter_scale(cfg, mod)).t()).to(w.dtype)
-            return (w.float() + _delta(pairs[mod], _adapter_scale(cfg, mod))).to(w.dtype)
+            merged = w.float() + _delta(pairs[mod], _adapter_scale(cfg, mod))
+            if "M" in pairs[mod]:   # DoRA: rescale every output row to its learned magnitude
+                merged = merged * (pairs[mod]["M"].to(merged.device) / merged.norm(dim=1).clamp(min=1e-12))[:, None]
+            return merged.to(w.dtype)
         m = re.match(r"(.+\.experts)\.(\d+)\.(gate_proj|up_proj|down_proj)$", mod)
         if m:  # per-expert checkpoint, fused expert adapter
             base, e, sub = m.group(1), int(m.group(2)), m.group(3)

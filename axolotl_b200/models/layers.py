@@ -60,6 +60,7 @@ class FusedLinear(nn.Module):
         self.names = list(names)
         self.weight = nn.Parameter(torch.empty(sum(out_features), in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(sum(out_features), dtype=dtype, device=device)) if bias else None
+        self.dora_magnitude = None
         # LoRA state (absent until add_lora)
         self.lora_A = None
         self.lora_B = None
@@ -84,7 +85,7 @@ class FusedLinear(nn.Module):
 
     # ------------------------------------------------------------------ LoRA
     def add_lora(self, r, alpha, dropout=0.0, targets=None, use_rslora=False, dtype=torch.float32,
-                 init_b_zero=True):
+                 init_b_zero=True, use_dora=False):
         targets = [n for n in self.names if targets is None or n in targets]
         if not targets:
             return
@@ -112,6 +113,56 @@ class FusedLinear(nn.Module):
         self.scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
         self.lora_dropout = dropout
         self.refresh_shadows()
+        if use_dora:
+            self.add_dora_()
+
+    # ------------------------------------------------------------------ DoRA
+    @torch.no_grad()
+    def add_dora_(self):
+        """Weight-decomposed LoRA: y_row = m_row / ||W + s B A||_row * (x W^T + s x A^T B^T)_row for
+        the rows of adapted sub-projections. ``m`` starts at ||W||_row, so the layer is unchanged at
+        initialisation; the norm is treated as a constant in the backward pass (as in PEFT)."""
+        W = self._dense_weight().float()
+        self.dora_w2 = (W * W).sum(1)                                   # ||W||^2 per row (frozen)
+        mask = torch.zeros(W.shape[0], dtype=torch.bool, device=W.device)
+        for (r0, rows, _, _) in self.lora_blocks:
+            mask[r0:r0 + rows] = True
+        self.dora_rows = mask
+        self.dora_magnitude = nn.Parameter(self.dora_w2.sqrt().to(self.lora_A.dtype))
+
+    def _dense_weight(self):
+        st = getattr(self.weight, "_axb_quant", None)
+        if st is not None:
+            from ..ops.nf4 import dequantize_nf4
+
+            return dequantize_nf4(self.weight.data, st, dtype=torch.bfloat16 if self.weight.is_cuda else torch.float32)
+        return self.weight.detach()
+
+    @torch.no_grad()
+    def dora_weight_norm(self):
+        """||W + s B A|| per output row without forming B A:
+        ||W||^2 + 2 s <W, B A>_row + s^2 ||B A||^2_row, with <W, B A>_row = rowsum((W A^T) * B) and
+        ||B A||^2_row = rowsum((B (A A^T)) * B)  (what the reference's fused DoRA-norm kernel computes,
+        src/axolotl/kernels/dora.py:16-147)."""
+        A, B = self.lora_A.detach().float(), self.lora_B.detach().float()
+        W = self._dense_weight()
+        if W.is_cuda:
+            from ..ops.gemm import gemm
+
+            WA = gemm(W, self.lora_A16 if self.lora_A16 is not None else A.to(torch.bfloat16),
+                      out_dtype=torch.float32)                          # [N, R] skinny tcgen05 GEMM
+        else:
+            WA = W.float() @ A.t()
+        cross = (WA * B).sum(1)
+        quad = ((B @ (A @ A.t())) * B).sum(1)
+        s = self.scaling
+        return (self.dora_w2 + 2 * s * cross + s * s * quad).clamp(min=1e-12).sqrt()
+
+    def dora_scale(self):
+        """Per-row output scale (1 for rows without an adapter); carries the gradient of ``m``."""
+        norm = self.dora_weight_norm()
+        sc = self.dora_magnitude.float() / norm
+        return torch.where(self.dora_rows, sc, torch.ones_like(sc))
 
     def refresh_shadows(self):
         """bf16 copies of the fp32 adapter masters for the GEMM kernels (CUDA only)."""
@@ -169,6 +220,13 @@ class FusedLinear(nn.Module):
         if self.lora_A is None or self.merged:
             return
         self.dequantize_()
+        if self.dora_magnitude is not None:
+            sc = self.dora_scale().detach()
+            merged = (self.weight.float() + self.scaling * (self.lora_B.float() @ self.lora_A.float())) * sc[:, None]
+            self.weight.copy_(merged.to(self.weight.dtype))
+            self.dora_magnitude = None
+            self.merged = True
+            return
         delta = self.scaling * (self.lora_B.float() @ self.lora_A.float())
         self.weight.copy_((self.weight.float() + delta).to(self.weight.dtype))
         self.merged = True
@@ -188,6 +246,11 @@ class FusedLinear(nn.Module):
             return linear(x, self.weight, self.bias)
         if x.is_cuda and self.lora_A16 is None:
             self.refresh_shadows()
+        if self.dora_magnitude is not None:
+            y = lora_linear(x, self.weight, self.lora_A, self.lora_B, self.lora_A16, self.lora_B16,
+                            self.scaling, self.lora_blocks, None, self.lora_dropout, self.training)
+            y = y * self.dora_scale().to(y.dtype)
+            return y if self.bias is None else y + self.bias.to(y.dtype)
         return lora_linear(x, self.weight, self.lora_A, self.lora_B, self.lora_A16, self.lora_B16,
                            self.scaling, self.lora_blocks, self.bias, self.lora_dropout,
                            self.training)

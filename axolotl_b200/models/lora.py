@@ -92,8 +92,6 @@ def _matches(spec: LoraSpec, hf_path: str, sub: str, layer_idx: int | None) -> b
 def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=torch.float32):
     """Adds adapters according to ``spec`` and freezes everything else. Returns the trainable
     parameter count."""
-    if spec.use_dora:
-        raise NotImplementedError("DoRA adapters are not supported by axolotl_b200 yet")
     if freeze_base:
         for p in model.parameters():
             p.requires_grad_(False)
@@ -110,7 +108,12 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
             for pat, av in spec.alpha_pattern.items():
                 if any(re.search(pat, _hf_path(name, s)) for s in targets):
                     alpha = av
-            m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype)
+            if spec.use_dora:
+                if not isinstance(m, FusedLinear):
+                    raise NotImplementedError("DoRA cannot be combined with tensor parallelism")
+                m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype, use_dora=True)
+            else:
+                m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype)
     if spec.target_parameters:
         for name, m in model.named_modules():
             if isinstance(m, Experts):
@@ -163,6 +166,9 @@ def get_peft_state_dict(model) -> dict:
             base = f"base_model.model.{_hf_path(name, sub)}"
             sd[f"{base}.lora_A.weight"] = A.detach()
             sd[f"{base}.lora_B.weight"] = B.detach()
+            if getattr(m, "dora_magnitude", None) is not None:
+                r0, r1 = m.row_range(sub)
+                sd[f"{base}.lora_magnitude_vector"] = m.dora_magnitude.detach()[r0:r1]
     ep_of = {id(m.experts): m.ep for m in model.modules() if getattr(m, "ep", None) is not None and hasattr(m, "experts")}
     for name, m in model.named_modules():
         if isinstance(m, Experts) and m.lora is not None:
@@ -176,8 +182,8 @@ def get_peft_state_dict(model) -> dict:
 
 def set_peft_state_dict(model, sd: dict, strict: bool = True):
     """Loads PEFT-named adapter tensors (any ``.default`` adapter-name infix is tolerated)."""
-    norm = {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B."): v
-            for k, v in sd.items()}
+    norm = {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B.")
+            .replace(".lora_magnitude_vector.default", ".lora_magnitude_vector"): v for k, v in sd.items()}
     used = set()
     for name, m in model.fused_linears():
         if m.lora_A is None:
@@ -188,6 +194,12 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
             if ka in norm and kb in norm:
                 m.load_peft_tensors(sub, norm[ka].to(m.lora_A.device), norm[kb].to(m.lora_B.device))
                 used.update((ka, kb))
+                for km in (f"{base}.lora_magnitude_vector", f"{base}.lora_magnitude_vector.weight"):
+                    if km in norm and getattr(m, "dora_magnitude", None) is not None:
+                        r0, r1 = m.row_range(sub)
+                        with torch.no_grad():
+                            m.dora_magnitude[r0:r1].copy_(norm[km].reshape(-1))
+                        used.add(km)
             elif strict:
                 raise KeyError(f"adapter tensors for {base} are missing")
         m.refresh_shadows()

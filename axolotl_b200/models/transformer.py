@@ -112,6 +112,7 @@ class CausalLM(nn.Module):
         self.gradient_checkpointing = False
         self.ce_chunk_rows = 2048
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
+        self.neftune_noise_alpha = None  # NEFTune: uniform noise on the embedding output while training
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -164,6 +165,11 @@ class CausalLM(nn.Module):
         ids = input_ids.reshape(-1).to(dev, non_blocking=True)
         pos = position_ids.reshape(-1).to(device=dev, dtype=torch.int32, non_blocking=True)
         h = Fn.embedding(self.embed_tokens, ids)
+        if self.neftune_noise_alpha and self.training:
+            # noise magnitude alpha / sqrt(L * d) with L the row length (NEFTune, as applied by the HF
+            # trainer the reference builds on)
+            mag = float(self.neftune_noise_alpha) / math.sqrt(S * h.shape[-1])
+            h = h + (torch.rand_like(h) * 2 - 1) * mag
         residual = None
         aux_total = None
         hooks = self.hooks

@@ -224,8 +224,47 @@ class StatusCheckCallback(Callback):
             _lib.check_status(trainer.device)
 
 
+class ReLoRACallback(Callback):
+    """ReLoRA: every ``restart_steps`` optimizer steps the adapters are folded into the base
+    weights (W += s B A), A is re-initialised, B zeroed and the adapters' AdamW moments pruned, so
+    successive low-rank updates add up to a high-rank one. Pair with the jagged-restart schedule
+    (reference: src/axolotl/monkeypatch/relora.py and ReLoRAConfig)."""
+
+    def __init__(self, restart_steps, prune_ratio=0.9):
+        self.every, self.prune = int(restart_steps), float(prune_ratio if prune_ratio is not None else 0.9)
+
+    def on_step_end(self, trainer, logs):
+        import math
+
+        import torch
+
+        if self.every <= 0 or trainer.global_step == 0 or trainer.global_step % self.every:
+            return
+        model = trainer.model
+        touched = []
+        with torch.no_grad():
+            for _, m in model.fused_linears():
+                if getattr(m, "lora_A", None) is None or getattr(m.weight, "_axb_quant", None) is not None:
+                    continue
+                if getattr(m.weight, "_axb_shard", None) is not None or getattr(m, "tp", None) is not None:
+                    continue   # sharded base weights are merged at export time instead
+                delta = m.scaling * (m.lora_B.float() @ m.lora_A.float())
+                m.weight.add_(delta.to(m.weight.dtype))
+                r = m.lora_r
+                for i in range(len(m.lora_names)):
+                    torch.nn.init.kaiming_uniform_(m.lora_A[i * r:(i + 1) * r], a=math.sqrt(5))
+                m.lora_B.zero_()
+                touched += [m.lora_A, m.lora_B]
+        if hasattr(trainer.opt, "reset_state"):
+            trainer.opt.reset_state(touched, self.prune)
+        model.refresh_lora_shadows()
+        LOG.info("ReLoRA restart at step %d: merged and reset %d adapter tensors", trainer.global_step, len(touched))
+
+
 def build_callbacks(cfg):
     cbs = [JsonlReporter(), StatusCheckCallback()]
+    if cfg.get("relora") and cfg.get("jagged_restart_steps"):
+        cbs.append(ReLoRACallback(cfg["jagged_restart_steps"], cfg.get("relora_prune_ratio")))
     if cfg.get("loss_watchdog_threshold") is not None:
         cbs.append(LossWatchdogCallback(cfg["loss_watchdog_threshold"], cfg.get("loss_watchdog_patience") or 3))
     dc = cfg.get("dynamic_checkpoint")

@@ -111,6 +111,26 @@ class FlatAdamW:
                     return g["shadow"][o:o + k].view(p.shape)
         return None
 
+    @torch.no_grad()
+    def reset_state(self, params, prune_ratio: float = 1.0):
+        """Zeroes the AdamW moments of ``params`` (``prune_ratio`` < 1 keeps the largest-magnitude
+        1 - ratio fraction, the magnitude pruning ReLoRA applies at every restart) and refreshes the
+        bf16 shadows from the (possibly re-initialised) fp32 masters."""
+        ids = {id(p) for p in params}
+        for g in self.groups:
+            for n, p, o, k in g["entries"]:
+                if id(p) not in ids:
+                    continue
+                for key in ("exp_avg", "exp_avg_sq"):
+                    st = g[key][o:o + k]
+                    if prune_ratio >= 1.0 or k < 2:
+                        st.zero_()
+                    else:
+                        thr = st.abs().float().kthvalue(max(1, int(prune_ratio * k))).values
+                        st.mul_((st.abs() > thr).to(st.dtype))
+                if p.dtype == torch.float32:
+                    g["shadow"][o:o + k].copy_(g["master"][o:o + k])
+
     def bind_model_shadows(self, model):
         from ..models.layers import FusedLinear
 
@@ -315,6 +335,28 @@ def make_lr_lambda(kind: str, total_steps: int, warmup_steps: int = 0, *, min_lr
     if kind not in table:
         raise ValueError(f"lr_scheduler '{kind}' is not supported (have: {sorted(table)})")
     return table[kind]
+
+
+def jagged_restarts(base_lambda, restart_steps: int, warmup_steps: int = 10, anneal_steps: int = 1,
+                    min_scale: float = 0.001):
+    """Wraps a schedule with periodic restarts: after every ``restart_steps`` optimizer steps the LR
+    is annealed to ``min_scale`` over ``anneal_steps`` and warmed up again over ``warmup_steps``
+    (ReLoRA's saw-tooth; reference: JaggedLRRestartScheduler, src/axolotl/utils/schedulers.py)."""
+
+    def f(step):
+        base = base_lambda(step)
+        if restart_steps <= 0 or step < restart_steps - anneal_steps:
+            return base
+        pos = step % restart_steps
+        if pos < warmup_steps and step >= restart_steps:
+            scale = min_scale + (1 - min_scale) * pos / max(1, warmup_steps)
+        elif pos >= restart_steps - anneal_steps:
+            scale = min_scale + (1 - min_scale) * (restart_steps - pos) / max(1, anneal_steps)
+        else:
+            scale = 1.0
+        return base * scale
+
+    return f
 
 
 def default_warmup_steps(total_steps, warmup_steps=None, warmup_ratio=None):

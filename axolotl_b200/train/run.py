@@ -306,7 +306,8 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         tokenizer = load_tokenizer(cfg)
         cfg["pad_token_id"] = tokenizer.pad_token_id
     objective_mode = bool(cfg.get("rl") or cfg.get("reward_model"))   # preference / online-RL objectives
-    if dataset_meta is None and not objective_mode:
+    streaming = bool(cfg.get("pretraining_dataset") or cfg.get("streaming")) and not objective_mode
+    if dataset_meta is None and not objective_mode and not streaming:
         dataset_meta = load_datasets(cfg)
 
     model = build_model(cfg, device)
@@ -343,6 +344,20 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         train_fn, objective, n_batches = build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_size, spec)
         dataset_meta = TrainDatasetMeta(train=None, eval=None, total_num_steps=max(
             int(n_batches * (cfg.get("num_epochs") or 1)) // cfg["gradient_accumulation_steps"], 1))
+    elif streaming:
+        from ..data.streaming import StreamingPackedBatches
+
+        if tokenizer is None:
+            from ..data.tokenizer import load_tokenizer
+
+            tokenizer = load_tokenizer(cfg)
+            cfg["pad_token_id"] = tokenizer.pad_token_id
+        train_fn = StreamingPackedBatches(cfg, cfg.get("pretraining_dataset") or cfg.get("datasets"), tokenizer,
+                                          dp_rank, dp_size)
+        dataset_meta = TrainDatasetMeta(train=None, eval=None, total_num_steps=cfg["max_steps"])
+        if cfg.get("test_datasets"):
+            ev = load_datasets(dict(cfg, datasets=cfg["test_datasets"], test_datasets=None, val_set_size=None), tokenizer)
+            eval_fn, _ = make_batches_fn(cfg, ev.train, dp_rank, dp_size, parallel, is_eval=True)
     else:
         train_fn, sampler = make_batches_fn(cfg, dataset_meta.train, dp_rank, dp_size, parallel)
         if dataset_meta.eval is not None and len(dataset_meta.eval):
@@ -357,6 +372,11 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         ("cosine_with_min_lr" if cfg.get("cosine_min_lr_ratio") and (cfg.get("lr_scheduler") or "cosine") == "cosine" else cfg.get("lr_scheduler")),
         total, warm, min_lr_ratio=cfg.get("cosine_min_lr_ratio") or 0.0,
         constant_lr_ratio=cfg.get("cosine_constant_lr_ratio"), **(cfg.get("lr_scheduler_kwargs") or {}))
+    if cfg.get("jagged_restart_steps") and sched is None:
+        from .optimizer import jagged_restarts
+
+        lr_lambda = jagged_restarts(lr_lambda, cfg["jagged_restart_steps"], cfg.get("jagged_restart_warmup_steps") or 10,
+                                    cfg.get("jagged_restart_anneal_steps") or 1)
     logging_steps = cfg.get("logging_steps") or max(min(int(0.005 * total), 10), 1)
     args = TrainArgs(output_dir=cfg["output_dir"], max_steps=total, num_epochs=cfg.get("num_epochs") or 1,
                      micro_batch_size=cfg["micro_batch_size"], gradient_accumulation_steps=cfg["gradient_accumulation_steps"],
@@ -396,7 +416,7 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         load_adapter(model, resume)
     setup_signal_handler(trainer, model, cfg, spec)
     if cfg.get("neftune_noise_alpha"):
-        LOG.warning("neftune_noise_alpha is accepted but not applied by the fused embedding kernel")
+        model.neftune_noise_alpha = float(cfg["neftune_noise_alpha"])
 
     trainer.train()
 

@@ -176,3 +176,41 @@ def test_jsonl_alpaca_pipeline_with_word_tokenizer(tmp_path):
     cfg2 = {**cfg, "train_on_inputs": True, "dataset_prepared_path": str(tmp_path / "p2")}
     row2 = load_datasets(cfg2, tokenizer=tok).train[0]
     assert (row2["labels"] == row2["input_ids"]).all()
+
+
+def test_streaming_packed_batches(tmp_path):
+    """Lazy jsonl source -> on-the-fly tokenisation -> buffered packing; ranks see disjoint rows."""
+    import json
+
+    from axolotl_b200.data.streaming import StreamingPackedBatches
+
+    class Tok:
+        bos_token_id, eos_token_id, pad_token_id = 1, 2, 0
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [3 + (ord(c) % 50) for c in text]}
+
+    p = tmp_path / "c.jsonl"
+    with open(p, "w") as fh:
+        for i in range(200):
+            fh.write(json.dumps({"text": "x" * (5 + (i * 7) % 40) + str(i)}) + "\n")
+    cfg = {"sequence_len": 128, "micro_batch_size": 2, "pretrain_multipack_buffer_size": 50, "sample_packing": True,
+           "pad_to_sequence_len": True, "seed": 1}
+    seen = []
+    for rank in range(2):
+        it = StreamingPackedBatches(cfg, [{"path": str(p), "type": "pretrain"}], Tok(), rank, 2)
+        n_tok = 0
+        batches = list(it(0))
+        assert batches
+        for b in batches:
+            assert b["input_ids"].shape == (2, 128)
+            pos = b["position_ids"]
+            assert int((pos == 0).sum()) >= 2            # several documents per row
+            lab = b["labels"]
+            n_tok += int((lab != -100).sum())
+            assert int((b["input_ids"][lab != -100] == 2).sum()) >= 2     # EOS ends every document
+        seen.append(n_tok)
+    # every row is consumed at most once across the two ranks; only a last incomplete micro-batch
+    # (fewer than micro_batch_size bins) may be dropped per rank
+    total = sum(5 + (i * 7) % 40 + len(str(i)) + 2 for i in range(200))
+    assert 0 <= total - sum(seen) < 2 * 128

@@ -326,3 +326,105 @@ def test_nf4_roundtrip_and_qlora_training(tmp_path):
     losses = [l["loss"] for l in trainer.log_history if "loss" in l]
     assert losses[-1] < losses[0]
     assert (tmp_path / "q" / "adapter_model.safetensors").exists()
+
+
+def test_dora_matches_definition_saves_and_merges(tmp_path):
+    import torch
+
+    from axolotl_b200.io.merge import merge_tensor
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, get_peft_state_dict, inject_lora, merge_and_unload, set_peft_state_dict
+    from axolotl_b200.models.transformer import CausalLM
+
+    torch.manual_seed(0)
+    cfg = preset("tiny-llama", num_hidden_layers=1, vocab_size=128)
+    model = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(0)
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=["q_proj", "down_proj"], use_dora=True)
+    ids = torch.randint(0, 128, (1, 24))
+    base_logits = model(ids, return_logits=True).logits
+    inject_lora(model, spec)
+    assert torch.allclose(model(ids, return_logits=True).logits, base_logits, atol=1e-5)   # identity at init
+    lin = model.layers[0].self_attn.qkv_proj
+    with torch.no_grad():
+        for _, m in model.fused_linears():
+            if m.lora_A is not None:
+                mask = torch.zeros_like(m.lora_B)
+                for (r0, rows, c0, r) in m.lora_blocks:
+                    mask[r0:r0 + rows, c0:c0 + r] = 1
+                m.lora_B.copy_(torch.randn_like(m.lora_B) * 0.05 * mask)
+                m.dora_magnitude.mul_(1.0 + 0.1 * torch.rand_like(m.dora_magnitude))
+    x = torch.randn(3, cfg.hidden_size)
+    W = lin.weight + lin.scaling * lin.lora_B @ lin.lora_A
+    q0, q1 = lin.row_range("q_proj")
+    want = x @ W.t()
+    want[:, q0:q1] *= (lin.dora_magnitude / W.norm(dim=1))[q0:q1]
+    assert torch.allclose(lin(x), want, atol=1e-5)
+    # gradient reaches the magnitude of adapted rows only
+    lin(x).sum().backward()
+    assert lin.dora_magnitude.grad[q0:q1].abs().sum() > 0 and lin.dora_magnitude.grad[q1:].abs().sum() == 0
+    sd = get_peft_state_dict(model)
+    key = "base_model.model.model.layers.0.self_attn.q_proj"
+    assert sd[key + ".lora_magnitude_vector"].shape == (q1 - q0,)
+    # the offline merge tool reproduces the layer
+    pairs = {"model.layers.0.self_attn.q_proj": {"A": sd[key + ".lora_A.weight"].float(), "B": sd[key + ".lora_B.weight"].float(),
+                                                  "M": sd[key + ".lora_magnitude_vector"].float()}}
+    merged = merge_tensor("model.layers.0.self_attn.q_proj.weight", lin.weight[q0:q1].detach(), spec.to_peft_dict(), pairs)
+    assert torch.allclose(x @ merged.t(), want[:, q0:q1], atol=1e-5)
+    # reload into a fresh model, then merge in place
+    logits = model(ids, return_logits=True).logits
+    model2 = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(0)
+    inject_lora(model2, spec)
+    set_peft_state_dict(model2, {k: v.clone() for k, v in sd.items()})
+    assert torch.allclose(model2(ids, return_logits=True).logits, logits, atol=1e-5)
+    merge_and_unload(model2)
+    assert torch.allclose(model2(ids, return_logits=True).logits, logits, atol=1e-4)
+
+
+def test_relora_restart_and_jagged_schedule():
+    import torch
+
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, inject_lora
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.train.callbacks import ReLoRACallback
+    from axolotl_b200.train.optimizer import FlatAdamW, build_param_groups, jagged_restarts, make_lr_lambda
+
+    f = jagged_restarts(make_lr_lambda("constant", 100, 0), restart_steps=10, warmup_steps=4, anneal_steps=2)
+    assert f(0) == 1.0 and f(7) == 1.0 and f(9) < 1.0 and f(10) < 0.01 and f(12) < f(13) <= 1.0 and f(15) == 1.0
+
+    cfg = preset("tiny-llama", num_hidden_layers=1, vocab_size=128)
+    model = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(0)
+    inject_lora(model, LoraSpec(r=4, lora_alpha=8, target_modules="all-linear"))
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-2)
+    lin = model.layers[0].mlp.down_proj
+    with torch.no_grad():
+        lin.lora_B.normal_(0, 0.05)
+    for g in opt.groups:
+        g["exp_avg"].fill_(1.0)
+    ids = torch.randint(0, 128, (1, 16))
+    before = model(ids, return_logits=True).logits
+    w0 = lin.weight.clone()
+
+    class T:
+        global_step = 10
+    T.model, T.opt = model, opt
+    ReLoRACallback(10, prune_ratio=1.0).on_step_end(T, {})
+    assert float(lin.lora_B.detach().abs().max()) == 0.0 and not torch.equal(lin.weight, w0)
+    assert torch.allclose(model(ids, return_logits=True).logits, before, atol=1e-5)   # function preserved
+    assert all(float(g["exp_avg"][o:o + k].abs().max()) == 0.0 for g in opt.groups for n, p, o, k in g["entries"] if "lora" in n)
+
+
+def test_neftune_only_in_training():
+    import torch
+
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+
+    model = CausalLM(preset("tiny-llama", num_hidden_layers=1, vocab_size=64), dtype=torch.float32, device="cpu").init_weights(0)
+    ids = torch.randint(0, 64, (1, 16))
+    model.eval()
+    a = model(ids, return_logits=True).logits
+    model.neftune_noise_alpha = 5.0
+    assert torch.equal(model(ids, return_logits=True).logits, a)
+    model.train()
+    assert not torch.equal(model(ids, return_logits=True).logits, a)

@@ -1,5 +1,5 @@
 """``axolotl`` command line: preprocess / train / evaluate / inference / merge-lora /
-merge-sharded-fsdp-weights / fetch / quantize / config-schema / vllm-serve.
+merge-sharded-fsdp-weights / fetch / quantize / config-schema / vllm-serve / chat.
 
 Every top-level config key is also accepted as ``--key value`` (nested: ``--parent__child``), like
 the reference CLI (src/axolotl/cli/main.py:42-501, src/axolotl/cli/utils/args.py:191-219).
@@ -156,6 +156,22 @@ def inference(ctx, config, prompt, max_new_tokens, temperature, lora_model_dir):
 
     text = prompt if prompt is not None else sys.stdin.read()
     click.echo(generate_text(cfg, text, max_new_tokens=max_new_tokens, temperature=temperature))
+
+
+@cli.command("chat", context_settings=CONTEXT)
+@click.argument("config")
+@click.option("--system", default=None, help="system prompt")
+@click.option("--max-new-tokens", default=256)
+@click.option("--temperature", default=0.7)
+@click.option("--lora-model-dir", default=None)
+@click.pass_context
+def chat(ctx, config, system, max_new_tokens, temperature, lora_model_dir):
+    """Interactive multi-turn chat with the model (and adapter) of CONFIG."""
+    forced = {"lora_model_dir": lora_model_dir} if lora_model_dir else {}
+    cfg = _load(config, ctx, **forced)
+    from .chat import run_repl
+
+    run_repl(cfg, system, max_new_tokens, temperature, echo=click.echo)
 
 
 @cli.command("merge-lora", context_settings=CONTEXT)

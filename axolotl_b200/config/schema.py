@@ -511,7 +511,7 @@ INERT_KEYS = {
     "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",
     "gemma4_hybrid_attn_impl", "gpu_memory_limit", "gradio_max_new_tokens", "gradio_server_name",
     "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
-    "image_size", "is_falcon_derived_model", "kd_alpha", "kd_ce_alpha", "kd_temperature", "kd_trainer",
+    "image_size", "is_falcon_derived_model",
     "lisa_layers_attribute", "lisa_n_layers", "lisa_step_interval", "loftq_config", "lora_on_cpu", "low_cpu_mem_usage",
     "max_memory", "max_packed_sequence_len", "model_quantization_config",
     "model_quantization_config_kwargs", "noisy_embedding_alpha", "num_dataset_shards_to_save",

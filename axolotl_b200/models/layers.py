@@ -61,6 +61,7 @@ class FusedLinear(nn.Module):
         self.weight = nn.Parameter(torch.empty(sum(out_features), in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(sum(out_features), dtype=dtype, device=device)) if bias else None
         self.dora_magnitude = None
+        self.qat = None   # {"weight_dtype": ..., "group_size": ...}: fake-quantised forward while training
         # LoRA state (absent until add_lora)
         self.lora_A = None
         self.lora_B = None
@@ -242,6 +243,10 @@ class FusedLinear(nn.Module):
         return self
 
     def forward(self, x):
+        if self.qat is not None and self.training and self.weight.requires_grad:
+            from ..ops.fake_quant import ste_weight
+
+            return linear(x, ste_weight(self.weight, self.qat.get("weight_dtype"), self.qat.get("group_size")), self.bias)
         if self.lora_A is None or self.merged or not _ADAPTERS_ON:
             return linear(x, self.weight, self.bias)
         if x.is_cuda and self.lora_A16 is None:

@@ -71,6 +71,53 @@ class Lion(torch.optim.Optimizer):
         return loss
 
 
+class SinkGD(torch.optim.Optimizer):
+    """Stateless multi-normalised gradient descent: the gradient of every matrix is alternately
+    normalised by its row norms and column norms (``n_iters`` Sinkhorn-like sweeps, scaled so the
+    result has unit-RMS rows and columns) and applied with a plain SGD step; vectors and scalars
+    fall back to AdamW. No momentum buffers for matrices, i.e. optimizer memory close to zero.
+    Reference: src/axolotl/utils/optimizers/sinkgd.py:240-1088 (SinkGD / SR-Sinkhorn)."""
+
+    def __init__(self, params, lr=1e-3, n_iters=5, weight_decay=0.0, betas=(0.9, 0.999), eps=1e-8, sink_eps=1e-8):
+        super().__init__(params, dict(lr=lr, n_iters=n_iters, weight_decay=weight_decay, betas=betas, eps=eps,
+                                      sink_eps=sink_eps))
+
+    @staticmethod
+    def sinkhorn_normalize(g, n_iters=5, eps=1e-8):
+        m, n = g.shape
+        x = g.float()
+        for _ in range(n_iters):
+            x = x / (x.norm(dim=1, keepdim=True) + eps) * (n ** 0.5)
+            x = x / (x.norm(dim=0, keepdim=True) + eps) * (m ** 0.5)
+        return x
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for grp in self.param_groups:
+            for p in grp["params"]:
+                if p.grad is None:
+                    continue
+                if grp["weight_decay"]:
+                    p.mul_(1 - grp["lr"] * grp["weight_decay"])
+                if p.dim() == 2 and min(p.shape) > 1:
+                    upd = self.sinkhorn_normalize(p.grad, grp["n_iters"], grp["sink_eps"])
+                    p.add_(upd.to(p.dtype), alpha=-grp["lr"])
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"], st["m"], st["v"] = 0, torch.zeros_like(p, dtype=torch.float32), torch.zeros_like(p, dtype=torch.float32)
+                st["step"] += 1
+                b1, b2 = grp["betas"]
+                g = p.grad.float()
+                st["m"].mul_(b1).add_(g, alpha=1 - b1)
+                st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
+                mh = st["m"] / (1 - b1 ** st["step"])
+                vh = st["v"] / (1 - b2 ** st["step"])
+                p.add_((mh / (vh.sqrt() + grp["eps"])).to(p.dtype), alpha=-grp["lr"])
+        return loss
+
+
 def build_torch_optimizer(name, params, lr, betas, eps, cfg=None):
     name = name.lower()
     args = {}
@@ -98,4 +145,6 @@ def build_torch_optimizer(name, params, lr, betas, eps, cfg=None):
         return ADOPT(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.9999)), eps=args.pop("eps", 1e-6), **args)
     if name in ("lion_pytorch", "lion", "lion_32bit"):
         return Lion(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.99)), **args)
+    if name in ("sinkgd", "sinkgd_triton", "dist_sinkgd"):
+        return SinkGD(params, lr=lr, n_iters=int(args.pop("n_iters", args.pop("num_iters", 5))), betas=betas, eps=eps, **args)
     raise ValueError(f"optimizer '{name}' is not available on axolotl_b200")

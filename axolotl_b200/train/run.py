@@ -27,7 +27,7 @@ from ..plugins.base import PluginManager
 from ..utils.logging import get_logger, start_debug_log, stop_debug_log
 from .callbacks import build_callbacks
 from .optimizer import (FlatAdamW, TorchOptimizerAdapter, build_param_groups, default_warmup_steps, make_lr_lambda)
-from .trainer import TrainArgs, Trainer, find_last_checkpoint
+from .trainer import Callback, TrainArgs, Trainer, find_last_checkpoint
 
 LOG = get_logger(__name__)
 
@@ -162,6 +162,9 @@ def make_batches_fn(cfg, ds, rank, dp_size, parallel=None, is_eval=False):
     seq = (cfg.get("eval_sequence_len") if is_eval else None) or cfg["sequence_len"]
     pad_to_seq = bool(cfg.get("pad_to_sequence_len"))
     coll = PackedCollator(tok_pad, cfg.get("pad_to_multiple_of") or 64, seq, pad_to_seq)
+    custom = PluginManager.get_instance().first("get_collator_cls_and_kwargs", cfg, is_eval)
+    if custom is not None:   # a plugin supplies the collator (e.g. knowledge distillation targets)
+        coll = custom[0](**custom[1])
     agree = (lambda n: int(parallel.min_scalar(n))) if (parallel is not None and dp_size > 1) else None
 
     if packing:
@@ -196,6 +199,35 @@ def make_batches_fn(cfg, ds, rank, dp_size, parallel=None, is_eval=False):
             yield coll([[ds[j]] for j in idx])
 
     return plain, None
+
+
+class RowDataset:
+    """Pre-tokenised rows kept as dicts (extra per-token fields survive, unlike TokenizedDataset)."""
+
+    def __init__(self, rows):
+        self.rows = rows
+        self.lengths = np.array([len(r["input_ids"]) for r in rows], dtype=np.int32)
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        return self.rows[int(i)]
+
+
+def load_row_datasets(cfg) -> TrainDatasetMeta:
+    from ..data.loading import _shard, calculate_total_num_steps, read_raw
+
+    rows = []
+    for d in cfg.get("datasets") or []:
+        for r in _shard(read_raw(dict(d)), dict(d)):
+            if len(r["input_ids"]) <= cfg["sequence_len"]:
+                r.setdefault("labels", r["input_ids"])
+                rows.append(r)
+    ds = RowDataset(rows)
+    meta = TrainDatasetMeta(ds, None, None)
+    meta.total_num_steps = calculate_total_num_steps(cfg, ds)
+    return meta
 
 
 def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_size, spec):
@@ -307,6 +339,8 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         cfg["pad_token_id"] = tokenizer.pad_token_id
     objective_mode = bool(cfg.get("rl") or cfg.get("reward_model"))   # preference / online-RL objectives
     streaming = bool(cfg.get("pretraining_dataset") or cfg.get("streaming")) and not objective_mode
+    if dataset_meta is None and cfg.get("kd_trainer"):
+        dataset_meta = load_row_datasets(cfg)
     if dataset_meta is None and not objective_mode and not streaming:
         dataset_meta = load_datasets(cfg)
 
@@ -415,6 +449,23 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     if resume and spec is not None and os.path.exists(os.path.join(resume, "adapter_model.safetensors")):
         load_adapter(model, resume)
     setup_signal_handler(trainer, model, cfg, spec)
+    if cfg.get("qat"):
+        q = dict(cfg["qat"])
+        start = q.get("fake_quant_after_n_steps") or 0
+        mods = [m for n, m in model.fused_linears() if n.startswith("layers.") and hasattr(m, "qat")]
+
+        class _QATStart(Callback):
+            def on_step_end(self, trainer, logs):
+                if trainer.global_step == start:
+                    for m in mods:
+                        m.qat = q
+
+        if start <= 0:
+            for m in mods:
+                m.qat = q
+        else:
+            trainer.callbacks.append(_QATStart())
+        LOG.info("QAT: %d projections fake-quantised to %s (group %s)", len(mods), q.get("weight_dtype"), q.get("group_size"))
     if cfg.get("neftune_noise_alpha"):
         model.neftune_noise_alpha = float(cfg["neftune_noise_alpha"])
 

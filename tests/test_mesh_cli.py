@@ -69,3 +69,37 @@ def test_cli_preprocess_train_merge_roundtrip(tmp_path):
     assert res.exit_code != 0 and "local HF checkpoint" in res.output
     res = r.invoke(cli, ["vllm-serve", str(p)])
     assert res.exit_code != 0
+
+
+def test_chat_session_commands_and_turns(tmp_path):
+    import torch
+
+    from axolotl_b200.cli.chat import ChatSession
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+
+    class Tok:
+        eos_token_id = 2
+        chat_template = None
+
+        def __call__(self, text):
+            return {"input_ids": [3 + (ord(c) % 40) for c in text][-48:]}
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(i) for i in ids)
+
+    model = CausalLM(preset("tiny-llama", num_hidden_layers=1, vocab_size=64), dtype=torch.float32, device="cpu").init_weights(0)
+    s = ChatSession(model, Tok(), max_new_tokens=4, temperature=0.0)
+    assert s.command("hello") is None
+    assert "set" in s.command("/system be brief") and s.system == "be brief"
+    r1 = s.say("hi")
+    assert isinstance(r1, str) and len(s.history) == 2 and s.history[1]["role"] == "assistant"
+    assert s.say("hi again") and len(s.history) == 4
+    s.command("/undo")
+    assert len(s.history) == 2
+    s.command(f"/save {tmp_path / 'c.json'}")
+    import json
+    assert json.load(open(tmp_path / "c.json"))[0]["role"] == "system"
+    assert s.command("/max 7") and s.max_new_tokens == 7
+    s.command("/reset")
+    assert s.history == []

@@ -170,17 +170,54 @@ struct PeerPtrs8 {
   unsigned long long p[8];
 };
 
-// out[i, :] = src_rank(i).buffer[src_row(i), :]   (one warp per row, 16-byte vectors)
+// out[i, :] = scale(i) * src_rank(i).buffer[src_row(i), :]   (one warp per row, 16-byte vectors).
+// src_rank(i) < 0 marks a pad row of the expert-sorted layout: it is written as zeros.
+// Optionally dot_out[i] = <unscaled gathered row, dot_with[i, :]> (gradient of the routing weight).
 __global__ void ep_gather_rows_kernel(PeerPtrs8 src, const int* __restrict__ src_rank,
-                                      const int* __restrict__ src_row, __nv_bfloat16* __restrict__ out,
-                                      long long n_rows, int width, long long src_ld) {
+                                      const int* __restrict__ src_row, const float* __restrict__ scale,
+                                      const __nv_bfloat16* __restrict__ dot_with, float* __restrict__ dot_out,
+                                      __nv_bfloat16* __restrict__ out, long long n_rows, int width, long long src_ld) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long i = w; i < n_rows; i += n_warps) {
-    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[src_rank[i]]) + (long long)src_row[i] * src_ld;
-    for (int c = lane * 8; c < width; c += 256)
-      *reinterpret_cast<uint4*>(out + i * width + c) = *reinterpret_cast<const uint4*>(s + c);
+    const int rk = src_rank[i];
+    if (rk < 0) {
+      for (int c = lane * 8; c < width; c += 256)
+        *reinterpret_cast<uint4*>(out + i * width + c) = make_uint4(0, 0, 0, 0);
+      if (dot_out && lane == 0) dot_out[i] = 0.f;
+      continue;
+    }
+    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[rk]) + (long long)src_row[i] * src_ld;
+    const float g = scale ? scale[i] : 1.f;
+    float acc = 0.f;
+    for (int c = lane * 8; c < width; c += 256) {
+      uint4 v = *reinterpret_cast<const uint4*>(s + c);
+      if (dot_with) {
+        const uint4 d = *reinterpret_cast<const uint4*>(dot_with + i * width + c);
+        const uint32_t a[4] = {v.x, v.y, v.z, v.w}, b[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = unpack_bf16x2(a[e]), fb = unpack_bf16x2(b[e]);
+          acc += fa.x * fb.x + fa.y * fb.y;
+        }
+      }
+      if (scale) {
+        uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(in[e]);
+          in[e] = pack_bf16x2(f.x * g, f.y * g);
+        }
+        v = make_uint4(in[0], in[1], in[2], in[3]);
+      }
+      *reinterpret_cast<uint4*>(out + i * width + c) = v;
+    }
+    if (dot_out) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) dot_out[i] = acc;
+    }
   }
 }
 
@@ -193,6 +230,7 @@ __global__ void ep_scatter_add_kernel(PeerPtrs8 dst, const int* __restrict__ dst
   const int lane = threadIdx.x & 31;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long i = w; i < n_rows; i += n_warps) {
+    if (dst_rank[i] < 0) continue;   // pad row of the expert-sorted layout
     const float g = weight ? weight[i] : 1.f;
     __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst.p[dst_rank[i]]) + (long long)dst_row[i] * dst_ld;
     for (int c = lane * 8; c < width; c += 256) {
@@ -287,15 +325,17 @@ extern "C" int axb_moe_combine_dw(const void* dy, const void* ys, const int* slo
   return (int)cudaGetLastError();
 }
 
+// src_rank[i] < 0 => zero row; scale (fp32 per row) / dot_with (bf16 [n_rows, width]) + dot_out are optional
 extern "C" int axb_ep_gather_rows(const unsigned long long* src_ptrs, int world, const int* src_rank,
-                                  const int* src_row, void* out, long long n_rows, int width, long long src_ld,
-                                  void* stream) {
+                                  const int* src_row, const float* scale, const void* dot_with, float* dot_out,
+                                  void* out, long long n_rows, int width, long long src_ld, void* stream) {
   if (n_rows <= 0) return 0;
   if (width % 8 || src_ld % 8) return -2;
   PeerPtrs8 p;
   if (fill8(p, src_ptrs, world)) return -2;
   int grid = (int)((n_rows + 7) / 8 > 148 * 8 ? 148 * 8 : (n_rows + 7) / 8);
-  ep_gather_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, src_rank, src_row, (__nv_bfloat16*)out, n_rows, width, src_ld);
+  ep_gather_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, src_rank, src_row, scale, (const __nv_bfloat16*)dot_with,
+                                                      dot_out, (__nv_bfloat16*)out, n_rows, width, src_ld);
   return (int)cudaGetLastError();
 }
 

@@ -36,7 +36,7 @@ _CUDA_SIGS = {
     "axb_grouped_gemm": [vp, i64, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp, vp],
     # A, lda, B, ldb, C, ldc, c_batch, E, Mg, Ng, rows, alpha, out_mode, bn, seg_start, seg_rows, status, stream
     "axb_grouped_gram": [vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i64, f32, i32, i32, vp, vp, vp, vp],
-    "axb_ep_gather_rows": [vp, i32, vp, vp, vp, i64, i32, i64, vp],
+    "axb_ep_gather_rows": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, i64, vp],
     "axb_ep_scatter_add": [vp, i32, vp, vp, vp, vp, i64, i32, i64, vp],
     "axb_peer_put_i32": [vp, vp, i64, vp],
     "axb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],

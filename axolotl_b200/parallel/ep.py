@@ -29,7 +29,8 @@ from .symm import PeerSync, SymmBuffer
 class _Plan:
     """Routing plan of one MoE layer call (shared by forward and backward)."""
     __slots__ = ("T", "k", "H", "send_order", "send_counts", "recv_counts", "recv_src_rank", "recv_src_row",
-                 "recv_weight", "local_order", "expert_counts", "n_recv", "send_tok")
+                 "recv_weight", "local_order", "expert_counts", "n_recv", "send_tok", "lay", "pad_src_rank", "pad_src_row",
+                 "pad_weight")
 
 
 class ExpertParallelGroup:
@@ -131,6 +132,19 @@ class ExpertParallelGroup:
         p.expert_counts = torch.bincount(r_e.long(), minlength=self.E_local).tolist()
         p.n_recv = n_recv
         p.send_tok = tok
+        p.lay = None
+        if self.fused:
+            # expert segments padded to 128 rows for the grouped GEMM; -1 marks pad rows
+            from ..ops.grouped import GroupLayout
+
+            lay = GroupLayout(torch.tensor(p.expert_counts, dtype=torch.int64, device=dev), n_recv)
+            p.lay = lay
+            p.pad_src_rank = torch.full((lay.max_rows,), -1, dtype=torch.int32, device=dev)
+            p.pad_src_rank[lay.dest] = p.recv_src_rank
+            p.pad_src_row = torch.zeros(lay.max_rows, dtype=torch.int32, device=dev)
+            p.pad_src_row[lay.dest] = p.recv_src_row
+            p.pad_weight = torch.zeros(lay.max_rows, dtype=torch.float32, device=dev)
+            p.pad_weight[lay.dest] = p.recv_weight
         return p
 
     def _ensure(self, T, H):
@@ -143,8 +157,11 @@ class ExpertParallelGroup:
             dist.barrier(self.group)
 
     # ------------------------------------------------------------------ payload movement
-    def pull_rows(self, x, plan):
-        """rows routed to this rank's experts, expert-sorted: [n_recv, H]."""
+    def pull_rows(self, x, plan, weighted=False, dot_with=None):
+        """Rows routed to this rank's experts, expert-sorted. Fused path: the padded layout
+        [lay.max_rows, H] (zeros in pad rows), optionally scaled by the routing weight, and
+        optionally the per-row dot product of the unscaled row with ``dot_with``. Collective path:
+        compact [n_recv, H]."""
         if not self.fused:
             return _a2a_rows(x[plan.send_tok.long()], plan.recv_counts, plan.send_counts, self.group)[plan.local_order]
         lib = _lib.cuda_lib()
@@ -154,11 +171,16 @@ class ExpertParallelGroup:
         self.kx += 1
         buf.tensor[: T * H].view(T, H).copy_(x)
         self.sync.barrier(channel=6)
-        out = torch.empty((plan.n_recv, H), dtype=x.dtype, device=x.device)
-        _lib.check_rc(lib.axb_ep_gather_rows(buf.ptrs_c, self.size, plan.recv_src_rank.data_ptr(),
-                                             plan.recv_src_row.data_ptr(), out.data_ptr(), plan.n_recv, H, H,
-                                             _lib.stream_ptr()), "ep_gather_rows")
-        return out
+        n = plan.lay.max_rows
+        out = torch.empty((n, H), dtype=x.dtype, device=x.device)
+        dots = torch.empty(n, dtype=torch.float32, device=x.device) if dot_with is not None else None
+        _lib.check_rc(lib.axb_ep_gather_rows(buf.ptrs_c, self.size, plan.pad_src_rank.data_ptr(),
+                                             plan.pad_src_row.data_ptr(),
+                                             plan.pad_weight.data_ptr() if weighted else None,
+                                             dot_with.data_ptr() if dot_with is not None else None,
+                                             dots.data_ptr() if dots is not None else None,
+                                             out.data_ptr(), n, H, H, _lib.stream_ptr()), "ep_gather_rows")
+        return out if dot_with is None else (out, dots)
 
     def push_rows(self, rows, plan, weighted):
         """sum over slots of (weight *) rows back at their source token: [T, H] on the source rank."""
@@ -176,10 +198,10 @@ class ExpertParallelGroup:
         buf = self.y_bufs[self.ky & 1]     # zero on every rank since its last use
         self.ky += 1
         rows = rows.contiguous()
-        _lib.check_rc(lib.axb_ep_scatter_add(buf.ptrs_c, self.size, plan.recv_src_rank.data_ptr(),
-                                             plan.recv_src_row.data_ptr(),
-                                             plan.recv_weight.data_ptr() if weighted else None, rows.data_ptr(),
-                                             plan.n_recv, H, H, _lib.stream_ptr()), "ep_scatter_add")
+        _lib.check_rc(lib.axb_ep_scatter_add(buf.ptrs_c, self.size, plan.pad_src_rank.data_ptr(),
+                                             plan.pad_src_row.data_ptr(),
+                                             plan.pad_weight.data_ptr() if weighted else None, rows.data_ptr(),
+                                             plan.lay.max_rows, H, H, _lib.stream_ptr()), "ep_scatter_add")
         self.sync.barrier(channel=7)
         y = buf.tensor[: T * H].view(T, H).clone()
         buf.tensor[: T * H].zero_()
@@ -200,7 +222,12 @@ class ExpertParallelGroup:
     def dispatch_compute_combine(self, experts, x, w, idx):
         plan = self._make_plan(idx, w, x.shape[1])
         xs = _Dispatch.apply(x, self, plan)
-        ys = experts(xs, plan.expert_counts)
+        if self.fused:
+            from ..ops.grouped import grouped_experts_padded
+
+            ys = grouped_experts_padded(experts, xs, plan.lay)
+        else:
+            ys = experts(xs, plan.expert_counts)
         return _Combine.apply(ys, w, self, plan)
 
 
@@ -233,6 +260,13 @@ class _Combine(torch.autograd.Function):
     def backward(ctx, dy):
         (ys,) = ctx.saved_tensors
         ep, plan = ctx.ep, ctx.plan
+        if ep.fused:   # one peer gather: weight-scaled dY rows and <dY row, expert output row>
+            if ctx.needs_input_grad[1]:
+                dys, dots = ep.pull_rows(dy.contiguous(), plan, weighted=True, dot_with=ys.contiguous())
+                dw = ep.return_slot_scalars(dots[plan.lay.dest], plan).to(ctx.w_dtype)
+            else:
+                dys, dw = ep.pull_rows(dy.contiguous(), plan, weighted=True), None
+            return dys, dw, None, None
         dy_rows = ep.pull_rows(dy.contiguous(), plan)                     # dY of each slot's token
         dys = dy_rows * plan.recv_weight[:, None].to(dy_rows.dtype)
         dw = None

@@ -143,6 +143,23 @@ def profile_case(what):
         out = torch.empty(8192, 6144, device="cuda", dtype=torch.bfloat16)
         for _ in range(4):
             gemm(a, b, out=out)
+    elif what == "one_grouped":
+        # one MoE projection of Qwen3-MoE-30B-A3B: 128 experts, 8192 tokens x top-8 = 65536 routed rows
+        from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gram
+
+        E, H, I, r = 128, 2048, 768, 16
+        g = torch.Generator(device="cuda").manual_seed(0)
+        e_of_row = torch.randint(0, E, (65536,), device="cuda", generator=g)
+        lay = GroupLayout(torch.bincount(e_of_row, minlength=E), 65536)
+        x = (torch.randn(lay.max_rows, H, device="cuda") * 0.5).bfloat16()
+        W = (torch.randn(E, 2 * I, H, device="cuda") * 0.02).bfloat16()
+        t = (torch.randn(lay.max_rows, r, device="cuda") * 0.5).bfloat16()
+        Bt = (torch.randn(E, 2 * I, r, device="cuda") * 0.02).bfloat16()
+        gA = torch.zeros(E, r, H, device="cuda")
+        for _ in range(3):
+            y = grouped_gemm(x, W, lay, a2=t, w2=Bt)
+            dx = grouped_gemm(y, W, lay, trans_w=True)
+            grouped_gram(t, x, lay, gA)
     else:
         Hq, Hk, D = 32, 8, 128
         meta = AttnMeta([0, 2048, 4096, 6144, 8192], "cuda")
@@ -157,7 +174,7 @@ def profile_case(what):
 
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
-    if what in ("one_gemm", "one_attn"):
+    if what in ("one_gemm", "one_attn", "one_grouped"):
         return profile_case(what)
     rows = []
     if what in ("gemm", "all"):

@@ -273,7 +273,7 @@ extern "C" int axb_peer_barrier(const unsigned long long* pad_ptrs, int rank, in
 }
 
 // All *_ptrs arguments are HOST arrays of `world` peer-mapped device addresses.
-extern "C" int axb_rs_adamw_ag(const unsigned long long* grad_ptrs,
+static int rs_adamw_ag_impl(const unsigned long long* grad_ptrs,
                                const unsigned long long* master_ptrs,
                                const unsigned long long* shadow_ptrs,
                                const unsigned long long* pad_ptrs,
@@ -282,7 +282,7 @@ extern "C" int axb_rs_adamw_ag(const unsigned long long* grad_ptrs,
                                long long n, int rank, int world, unsigned int epoch, float lr,
                                float beta1, float beta2, float eps, float wd, float bc1, float bc2,
                                float max_norm, float grad_scale, float* gnorm_sq_out, int* status,
-                               long long budget_ns, void* stream) {
+                               long long budget_ns, void* stream, int sliced_moments) {
   if (n % (4LL * world)) return -3;
   RsAdamwParams p;
   if (fill_ptrs(p.grad, grad_ptrs, world) || fill_ptrs(p.master, master_ptrs, world) ||
@@ -297,8 +297,11 @@ extern "C" int axb_rs_adamw_ag(const unsigned long long* grad_ptrs,
     p.master_mc = nullptr;
     p.shadow_mc = nullptr;
   }
-  p.exp_avg = exp_avg;
-  p.exp_avg_sq = exp_avg_sq;
+  // ZeRO-style moments: each rank stores only the n / world elements it updates; the kernel
+  // indexes moments with the global element index, so rebase the pointers by the slice start.
+  const long long slice_lo = sliced_moments ? (n / world) * (long long)rank : 0;
+  p.exp_avg = exp_avg - slice_lo;
+  p.exp_avg_sq = exp_avg_sq - slice_lo;
   p.n = n;
   p.rank = rank;
   p.world = world;
@@ -319,6 +322,32 @@ extern "C" int axb_rs_adamw_ag(const unsigned long long* grad_ptrs,
   cudaError_t e = cudaLaunchCooperativeKernel((void*)rs_adamw_ag_kernel, dim3(grid), dim3(256), args,
                                               0, reinterpret_cast<cudaStream_t>(stream));
   return (int)e;
+}
+
+// exp_avg / exp_avg_sq: full-length local arrays (only the owned slice is touched)
+extern "C" int axb_rs_adamw_ag(const unsigned long long* grad_ptrs, const unsigned long long* master_ptrs,
+                               const unsigned long long* shadow_ptrs, const unsigned long long* pad_ptrs,
+                               const unsigned long long* scratch_ptrs, void* grad_mc, void* master_mc,
+                               void* shadow_mc, float* exp_avg, float* exp_avg_sq, long long n, int rank, int world,
+                               unsigned int epoch, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                               float bc2, float max_norm, float grad_scale, float* gnorm_sq_out, int* status,
+                               long long budget_ns, void* stream) {
+  return rs_adamw_ag_impl(grad_ptrs, master_ptrs, shadow_ptrs, pad_ptrs, scratch_ptrs, grad_mc, master_mc, shadow_mc,
+                          exp_avg, exp_avg_sq, n, rank, world, epoch, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm,
+                          grad_scale, gnorm_sq_out, status, budget_ns, stream, 0);
+}
+
+// Same, with exp_avg / exp_avg_sq holding only this rank's slice (n / world elements each).
+extern "C" int axb_rs_adamw_ag_sharded(const unsigned long long* grad_ptrs, const unsigned long long* master_ptrs,
+                                       const unsigned long long* shadow_ptrs, const unsigned long long* pad_ptrs,
+                                       const unsigned long long* scratch_ptrs, void* grad_mc, void* master_mc,
+                                       void* shadow_mc, float* exp_avg, float* exp_avg_sq, long long n, int rank,
+                                       int world, unsigned int epoch, float lr, float beta1, float beta2, float eps,
+                                       float wd, float bc1, float bc2, float max_norm, float grad_scale,
+                                       float* gnorm_sq_out, int* status, long long budget_ns, void* stream) {
+  return rs_adamw_ag_impl(grad_ptrs, master_ptrs, shadow_ptrs, pad_ptrs, scratch_ptrs, grad_mc, master_mc, shadow_mc,
+                          exp_avg, exp_avg_sq, n, rank, world, epoch, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm,
+                          grad_scale, gnorm_sq_out, status, budget_ns, stream, 1);
 }
 
 extern "C" int axb_peer_allreduce_f32(const unsigned long long* buf_ptrs,

@@ -70,6 +70,14 @@ class ParallelRuntime:
             return self.symmetric_alloc
         return None
 
+    def moment_shard(self):
+        """(rank, world) for FlatAdamW(moment_shard=...) when the fused reduce-scatter/AdamW/all-gather
+        kernel steps the optimizer (each rank then stores 1/world of the AdamW moments), else None."""
+        if self.tp is None and self.mesh.size("ep") == 1 and self.backend == "fused" and self.reduce_size > 1 \
+                and self.device.type == "cuda":
+            return (dist.get_rank(self.reduce_group), self.reduce_size)
+        return None
+
     def attach_optimizer(self, opt):
         self.opt = opt
         if self.tp is None and self.mesh.size("ep") == 1 and self.backend == "fused" and self.reduce_size > 1 \
@@ -217,7 +225,8 @@ class ParallelRuntime:
         for gi, g in enumerate(opt.groups):
             gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
             epoch = self.sync.next_epoch(0, 3)
-            rc = lib.axb_rs_adamw_ag(
+            fn = lib.axb_rs_adamw_ag_sharded if opt.moment_shard is not None else lib.axb_rs_adamw_ag
+            rc = fn(
                 gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
                 gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
                 g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.reduce_size,

@@ -52,12 +52,15 @@ def build_param_groups(named_params, *, weight_decay=0.0, embedding_lr=None, emb
 
 class FlatAdamW:
     def __init__(self, groups, lr=1e-4, betas=(0.9, 0.999), eps=1e-8, max_grad_norm=0.0, alloc=None,
-                 pad_multiple=8):
+                 pad_multiple=8, moment_shard=None):
         self.lr, self.betas, self.eps, self.max_grad_norm = lr, betas, eps, max_grad_norm
         self.step_count = 0
         self.groups = []
         self.grad_scale = 1.0
         self.skip_zero_grad_once = False
+        # (rank, world): the fused multi-GPU step updates only 1/world of every group on this rank,
+        # so the AdamW moments are stored for that slice alone (ZeRO-1 style)
+        self.moment_shard = moment_shard
         for g in groups:
             params = [(n, p) for n, p in g["params"] if p.requires_grad]
             if not params:
@@ -94,11 +97,20 @@ class FlatAdamW:
                 p._axb_grad = gview
                 entries.append((n, p, o, k))
             tp_split = next((o for (n, p, o, k) in entries if getattr(p, "_tp_sharded", False)), total)
+            if moment_shard is not None:
+                mr, mw = moment_shard
+                if total % (4 * mw):
+                    raise ValueError("sharded moments need pad_multiple to be a multiple of 4 * world")
+                m_len, m_lo = total // mw, (total // mw) * mr
+            else:
+                m_len, m_lo = total, 0
             self.groups.append({
+                "m_lo": m_lo, "m_len": m_len,
                 "tp_split": tp_split,
                 "name": g["name"], "lr_scale": g.get("lr_scale", 1.0), "weight_decay": g.get("weight_decay", 0.0),
                 "master": master, "grad": grad, "shadow": shadow, "entries": entries,
-                "exp_avg": torch.zeros_like(master), "exp_avg_sq": torch.zeros_like(master),
+                "exp_avg": torch.zeros(m_len, dtype=torch.float32, device=dev),
+                "exp_avg_sq": torch.zeros(m_len, dtype=torch.float32, device=dev),
             })
         self._gnorm = None
 
@@ -121,8 +133,12 @@ class FlatAdamW:
             for n, p, o, k in g["entries"]:
                 if id(p) not in ids:
                     continue
+                lo, hi = max(o, g["m_lo"]) - g["m_lo"], min(o + k, g["m_lo"] + g["m_len"]) - g["m_lo"]
                 for key in ("exp_avg", "exp_avg_sq"):
-                    st = g[key][o:o + k]
+                    if hi <= lo:
+                        break
+                    st = g[key][lo:hi]
+                    k = hi - lo
                     if prune_ratio >= 1.0 or k < 2:
                         st.zero_()
                     else:
@@ -175,6 +191,8 @@ class FlatAdamW:
         return ss
 
     def step(self, lr=None, gnorm_sq=None):
+        if self.moment_shard is not None:
+            raise RuntimeError("this optimizer holds sharded moments: it is stepped by the fused parallel runtime")
         self.step_count += 1
         lr = self.lr if lr is None else lr
         if gnorm_sq is None and self.max_grad_norm and self.max_grad_norm > 0:
@@ -231,6 +249,8 @@ class TorchOptimizerAdapter:
         return extra_reduce(ss) if extra_reduce is not None else ss
 
     def step(self, lr=None, gnorm_sq=None):
+        if self.moment_shard is not None:
+            raise RuntimeError("this optimizer holds sharded moments: it is stepped by the fused parallel runtime")
         self.step_count += 1
         if lr is not None:
             for g, b in zip(self.opt.param_groups, self._base_lrs):

@@ -143,7 +143,8 @@ def build_optimizer(cfg, model, parallel=None):
         world = parallel.dp_size if parallel is not None else 1
         opt = FlatAdamW(groups, lr=float(cfg["learning_rate"]), betas=betas, eps=eps,
                         max_grad_norm=cfg.get("max_grad_norm") or 0.0,
-                        alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1))
+                        alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1),
+                    moment_shard=parallel.moment_shard() if parallel is not None else None)
         opt.bind_model_shadows(model)
         return opt
     from .optimizers_extra import build_torch_optimizer

@@ -77,8 +77,9 @@ def bench_attn(rows):
         from flash_attn import flash_attn_varlen_func
     except Exception:  # pragma: no cover
         flash_attn_varlen_func = None
-    Hq, Hk, D = 32, 8, 128
-    for lens in ([8192], [2048] * 4, [4096, 1024, 3072], [512] * 16):
+    D = 128
+    for Hq, Hk, lens in [(32, 8, [8192]), (32, 8, [2048] * 4), (32, 8, [4096, 1024, 3072]), (32, 8, [512] * 16),
+                         (32, 4, [2048] * 4), (32, 4, [4096, 1024, 3072])]:
         cu = [0]
         for l in lens:
             cu.append(cu[-1] + l)
@@ -90,7 +91,7 @@ def bench_attn(rows):
         fwd = time_cuda(lambda: flash_varlen(qkv.detach(), meta, Hq, Hk, D))
         out = flash_varlen(qkv, meta, Hq, Hk, D)
         bwd = time_cuda(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True))
-        line = (f"attn lens={lens if len(lens) < 5 else str(lens[0]) + 'x' + str(len(lens))}: fwd {fwd:.3f} ms "
+        line = (f"attn Hq={Hq} Hk={Hk} lens={lens if len(lens) < 5 else str(lens[0]) + 'x' + str(len(lens))}: fwd {fwd:.3f} ms "
                 f"{fl_f / fwd:.0f} TFLOP/s, bwd {bwd:.3f} ms {2.5 * fl_f / bwd:.0f} TFLOP/s")
         if flash_attn_varlen_func is not None:
             q = qkv.detach()[:, :Hq * D].reshape(T, Hq, D).contiguous().requires_grad_(True)

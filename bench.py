@@ -113,7 +113,7 @@ def reference_arm(args):
     return 0
 
 
-def build_batches(n_batches, vocab, seed, rank, seq_len=SEQ_LEN, rows=1):
+def build_batches(n_batches, vocab, seed, rank, seq_len=SEQ_LEN, rows=1, min_len=256, max_len=4096):
     """Synthetic packed batches: sample lengths uniform in [256, 4096], packed first-fit into
     ``seq_len``-token rows (``rows`` rows per micro-batch), labels == inputs, position ids restart
     per sample."""
@@ -121,7 +121,8 @@ def build_batches(n_batches, vocab, seed, rank, seq_len=SEQ_LEN, rows=1):
     from axolotl_b200.data.packing import MultipackBatchSampler
     from axolotl_b200.data.synthetic import synthetic_varlen
 
-    ds = synthetic_varlen(max(64, n_batches * 6 * rows), 256, min(4096, seq_len), 3, vocab, 0.0, seed=seed + 1000 * rank)
+    ds = synthetic_varlen(max(64, n_batches * 6 * rows * max(1, seq_len // 8192)), min_len, min(max_len, seq_len), 3, vocab,
+                          0.0, seed=seed + 1000 * rank)
     samp = MultipackBatchSampler(ds.lengths, seq_len, rows, real_batches=True, seed=seed)
     coll = PackedCollator(pad_token_id=0, sequence_len=seq_len, pad_to_sequence_len=True)
     out = []
@@ -142,12 +143,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is then not the headline config)")
     ap.add_argument("--model", default=MODEL)
-    ap.add_argument("--config", default="lora8b", choices=["lora8b", "moe"],
+    ap.add_argument("--config", default="lora8b", choices=["lora8b", "moe", "tp70b", "cp64k"],
                     help="lora8b: the headline Llama-3-8B LoRA FSDP run; moe: Qwen3-MoE-30B-A3B with NVFP4 experts, "
-                         "expert + attention LoRA, expert parallelism over all ranks (4096-token rows, micro-batch 2)")
+                         "expert + attention LoRA, expert parallelism over all ranks (4096-token rows, micro-batch 2); "
+                         "tp70b: Llama-3-70B LoRA, TP=2 x FSDP=N/2, activation checkpointing; "
+                         "cp64k: Llama-3-8B full fine-tune, context parallel over all ranks, one 65536-token row")
     args = ap.parse_args()
-    if args.config == "moe" and args.model == MODEL:
-        args.model = "qwen3-moe-30b-a3b"
+    if args.model == MODEL:
+        args.model = {"moe": "qwen3-moe-30b-a3b", "tp70b": "llama-3-70b"}.get(args.config, MODEL)
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -188,6 +191,23 @@ def main():
             from axolotl_b200.parallel import build_parallel
 
             parallel = build_parallel(model, ep=world, device=dev)
+    elif args.config == "tp70b":
+        from axolotl_b200.parallel.runtime import create_runtime
+
+        if world > 1:
+            parallel = create_runtime(device=dev, tp=2, dp_shard=world // 2)
+            parallel.tp_max_tokens = SEQ_LEN
+            parallel.apply_tp(model)            # before the adapters exist
+        inject_lora(model, LoraSpec(r=16, lora_alpha=32, target_modules=list(ALL_LINEAR)))
+        if parallel is not None:
+            parallel.shard_model(model)
+        model.enable_gradient_checkpointing(True)
+    elif args.config == "cp64k":
+        if world > 1:
+            from axolotl_b200.parallel import build_parallel
+
+            parallel = build_parallel(model, cp=world, device=dev)
+        model.enable_gradient_checkpointing(True)
     else:
         inject_lora(model, LoraSpec(r=16, lora_alpha=32, target_modules=list(ALL_LINEAR)))
         if world > 1:
@@ -195,7 +215,8 @@ def main():
 
             parallel = build_parallel(model, dp_shard=world, device=dev)
     opt = FlatAdamW(build_param_groups(model.named_parameters(), weight_decay=0.0), lr=2e-4, max_grad_norm=1.0,
-                    alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1))
+                    alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1),
+                    moment_shard=parallel.moment_shard() if parallel is not None else None)
     opt.bind_model_shadows(model)
     if parallel is not None:
         parallel.attach_optimizer(opt)
@@ -204,8 +225,12 @@ def main():
     trainer = Trainer(model, opt, make_lr_lambda("constant", 10 ** 6, 0), targs, lambda e: [], parallel=parallel, device=dev)
     model.train()
 
-    cpu_batches = build_batches(W + K, cfg.vocab_size, seed=0, rank=rank,
-                                seq_len=4096 if args.config == "moe" else SEQ_LEN, rows=2 if args.config == "moe" else 1)
+    seq_len = {"moe": 4096, "cp64k": 65536}.get(args.config, SEQ_LEN)
+    # ranks of one context- or tensor-parallel group must see the same batch
+    data_rank = 0 if args.config == "cp64k" else (rank // 2 if args.config == "tp70b" else rank)
+    cpu_batches = build_batches(W + K, cfg.vocab_size, seed=0, rank=data_rank, seq_len=seq_len,
+                                rows=2 if args.config == "moe" else 1, max_len=8192 if args.config == "cp64k" else 4096,
+                                min_len=1024 if args.config == "cp64k" else 256)
     for b in cpu_batches:
         for k in ("input_ids", "labels", "position_ids"):
             b[k] = b[k].pin_memory()
@@ -217,7 +242,16 @@ def main():
         torch.cuda.synchronize()
 
     # ---------------------------------------------------------------- device-timed arm
-    staged = [to_device_batch(b, dev) for b in cpu_batches]
+    def stage(b):
+        cp = getattr(parallel, "cp", None) if parallel is not None else None
+        if cp is None:
+            return to_device_batch(b, dev)
+        sb = cp.slice_batch(b)               # this rank's chunk of the row, labels shifted globally
+        d = to_device_batch(sb, dev)
+        d["attn_meta"] = cp.make_meta(*sb["cp_meta_args"])
+        return d
+
+    staged = [stage(b) for b in cpu_batches]
     torch.cuda.synchronize()
     for i in range(W):
         trainer.training_step([staged[i]])
@@ -253,26 +287,35 @@ def main():
     ms, e2e_ms = float(t[0]), float(t[1])
     mem_gib = torch.cuda.max_memory_allocated(dev) / 1024 ** 3
     if rank == 0:
-        total_tokens = tokens_per_step * world * K
+        groups = {"cp64k": 1, "tp70b": max(world // 2, 1)}.get(args.config, world)   # data-parallel replicas
+        total_tokens = tokens_per_step * groups * K
         value = total_tokens / (ms / 1e3)
         e2e_value = total_tokens / (e2e_ms / 1e3)
         print(json.dumps({
-            "metric": "train tokens/s/box (max over ranks), Llama-3-8B LoRA FSDP2" if args.config == "lora8b" else
-                      "train tokens/s/box (max over ranks), Qwen3-MoE-30B-A3B NVFP4 expert-LoRA EP",
+            "metric": {"lora8b": "train tokens/s/box (max over ranks), Llama-3-8B LoRA FSDP2",
+                       "moe": "train tokens/s/box (max over ranks), Qwen3-MoE-30B-A3B NVFP4 expert-LoRA EP",
+                       "tp70b": "train tokens/s/box (max over ranks), Llama-3-70B LoRA TP2 x FSDP",
+                       "cp64k": "train tokens/s/box (max over ranks), Llama-3-8B full fine-tune CP @ 64k"}[args.config],
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic uniform token ids, lengths U[256,4096] packed to 8192; random-init weights",
+            "dtype": "bf16",
+            "data": {"moe": "synthetic uniform token ids, sample lengths U[256,4096] packed to 4096-token rows, 2 rows per step; "
+                            "random-init weights, experts quantised to NVFP4",
+                     "cp64k": "synthetic uniform token ids, sample lengths U[1024,8192] packed to one 65536-token row; "
+                              "random-init weights"}.get(args.config, "synthetic uniform token ids, lengths U[256,4096] "
+                                                                      "packed to 8192; random-init weights"),
             "impl": "ours",
             "config": {"model": args.model + ("" if args.layers is None else f"[layers={args.layers}]"),
-                       "global_batch": world * (2 if args.config == "moe" else 1),
-                       "seq_len": 4096 if args.config == "moe" else SEQ_LEN,
-                       "parallelism": (f"ep{world}" if args.config == "moe" else f"fsdp{world}") if world > 1 else "single",
+                       "global_batch": {"moe": 2 * world, "cp64k": 1, "tp70b": max(world // 2, 1)}.get(args.config, world),
+                       "seq_len": seq_len,
+                       "parallelism": ({"moe": f"ep{world}", "tp70b": f"tp2 x fsdp{world // 2}", "cp64k": f"cp{world}"}
+                                       .get(args.config, f"fsdp{world}")) if world > 1 else "single",
                        "lora_r": 16, "lora_alpha": 32,
                        "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 1,
                        "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
-                    "h2d_bytes_per_step": h2d_bytes(cpu_batches[W]) + 16 * (staged[W]["attn_meta"].n_tiles * 2),
+                    "h2d_bytes_per_step": h2d_bytes(cpu_batches[W]) + 16 * (getattr(staged[W]["attn_meta"], "n_tiles", 0) * 2),
                     "d2h_bytes_per_step": 4, "last_loss": last_loss},
             "gpu_launches": launches,
             "peak_mem_gib": mem_gib,

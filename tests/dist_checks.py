@@ -73,7 +73,8 @@ def check_fused_optimizer(dev, rank, world):
         ref_p, ref_q = p.detach().clone(), q.detach().clone()
         rt = ParallelRuntime(DeviceMesh(MeshSpec.from_cfg(world), rank), dev, "fused")
         opt = FlatAdamW([{"name": "g", "params": [("p", p), ("q", q)], "lr_scale": 1.0, "weight_decay": 0.1}],
-                        lr=1e-2, max_grad_norm=1.0, alloc=rt.optimizer_alloc(), pad_multiple=8 * world)
+                        lr=1e-2, max_grad_norm=1.0, alloc=rt.optimizer_alloc(), pad_multiple=8 * world,
+                        moment_shard=rt.moment_shard() if use_mc else None)
         rt.attach_optimizer(opt)
         ro = torch.optim.AdamW([torch.nn.Parameter(ref_p), torch.nn.Parameter(ref_q)], lr=1e-2, weight_decay=0.1)
         rp, rq = ro.param_groups[0]["params"]
@@ -135,7 +136,8 @@ def check_training_equivalence(dev, rank, world, backend):
                 m.lora_B.mul_(mask)
         par = build_parallel(model, device=dev, dp_shard=world, backend=backend) if parallel_on else None
         opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0,
-                        alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world)
+                        alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world,
+                        moment_shard=par.moment_shard() if par is not None else None)
         opt.bind_model_shadows(model)
         if par is not None:
             par.attach_optimizer(opt)
@@ -273,7 +275,8 @@ def check_context_parallel(dev, rank, world):
             par = create_runtime(device=dev, cp=world)
             par.apply_tp(model)
         opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0,
-                        alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world)
+                        alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world,
+                        moment_shard=par.moment_shard() if par is not None else None)
         opt.bind_model_shadows(model)
         if par is not None:
             par.attach_optimizer(opt)

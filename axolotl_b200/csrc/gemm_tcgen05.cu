@@ -45,6 +45,14 @@ struct GemmParams {
   void* red_mc;
   unsigned long long red_ptrs[8];
   int red_world;
+  // out_mode 5: two-shot all-reduce fused into the launch. Every tile is stored (bf16) into this
+  // rank's symmetric buffer C and counted in cnt[m_blk]; `r_ctas` trailing reducer CTAs wait until a
+  // 128-row block they own (m_blk % red_world == red_rank) is complete on EVERY rank, sum it over
+  // the ranks (multimem.ld_reduce through the switch, or peer loads) and write the sum into every
+  // rank's buffer (multimem.st, or peer stores), while the other CTAs keep computing tiles.
+  int r_ctas;
+  int red_rank;
+  unsigned long long cnt_ptrs[8];  // int32 [num_m] completion counters of every rank
   // prefetch of a row-sharded matrix by the trailing g_ctas CTAs (0 = none)
   int g_ctas;
   int g_world;
@@ -106,6 +114,109 @@ __device__ __forceinline__ void gather_cta_body(const GemmParams& p, int gather_
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
+AXB_DEVICE int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Body of a reducer CTA (out_mode 5), see GemmParams. All 192 threads move data; thread 0 polls.
+__device__ __forceinline__ void reducer_cta_body(const GemmParams& p, int reducer, int n_reducers, int num_m,
+                                                 int target) {
+  __shared__ int s_ok;
+  const long long vec_per_row = p.N >> 3;  // 16-byte vectors (N % 8 == 0)
+  int owned = 0;
+  for (int blk = p.red_rank; blk < num_m; blk += p.red_world, ++owned) {
+    if (owned % n_reducers != reducer) continue;
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const unsigned long long t0 = global_timer_ns();
+      for (int r = 0; r < p.red_world && ok; ++r) {
+        const int* c = reinterpret_cast<const int*>(p.cnt_ptrs[r]) + blk;
+        while (ld_acquire_sys(c) < target) {
+          if (global_timer_ns() - t0 > AXB_WAIT_BUDGET_NS) {  // report and give up
+            atomicExch(p.status, AXB_TIMEOUT_PEER_FLAG);
+            ok = 0;
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int rows = min(BM, p.M - blk * BM);
+    const long long n_vec = rows * vec_per_row;
+    if (p.red_mc) {
+      // 8 independent in-switch reductions in flight per thread: the round trip through NVSwitch is
+      // microseconds, so memory-level parallelism (not instruction rate) sets the bandwidth
+      constexpr int U = 8;
+      for (long long v0 = threadIdx.x; v0 < n_vec; v0 += (long long)blockDim.x * U) {
+        uint32_t q[U][4];
+        __nv_bfloat16* addr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          const long long vv = v < n_vec ? v : v0;
+          addr[u] = reinterpret_cast<__nv_bfloat16*>(p.red_mc) + ((long long)blk * BM + vv / vec_per_row) * p.ldc +
+                    (vv % vec_per_row) * 8;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(q[u][0]), "=r"(q[u][1]), "=r"(q[u][2]), "=r"(q[u][3])
+                       : "l"(addr[u])
+                       : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (v0 + (long long)u * blockDim.x < n_vec)
+            asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr[u]),
+                         "r"(q[u][0]), "r"(q[u][1]), "r"(q[u][2]), "r"(q[u][3])
+                         : "memory");
+        }
+      }
+    } else {
+      constexpr int U = 4;
+      for (long long v0 = threadIdx.x; v0 < n_vec; v0 += (long long)blockDim.x * U) {
+        uint4 x[U][8];
+        long long off[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          const long long vv = v < n_vec ? v : v0;
+          off[u] = ((long long)blk * BM + vv / vec_per_row) * p.ldc + (vv % vec_per_row) * 8;
+          for (int r = 0; r < p.red_world; ++r)   // peer data was written during this launch: volatile loads
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(x[u][r].x), "=r"(x[u][r].y), "=r"(x[u][r].z), "=r"(x[u][r].w)
+                         : "l"(reinterpret_cast<const __nv_bfloat16*>(p.red_ptrs[r]) + off[u])
+                         : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (v0 + (long long)u * blockDim.x >= n_vec) continue;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < p.red_world; ++r) {
+            const uint32_t w[4] = {x[u][r].x, x[u][r].y, x[u][r].z, x[u][r].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(w[e]);
+              acc[2 * e] += f.x;
+              acc[2 * e + 1] += f.y;
+            }
+          }
+          const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+          for (int r = 0; r < p.red_world; ++r)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.red_ptrs[r]) + off[u]) = o;
+        }
+      }
+    }
+    __syncthreads();
+    // the block is reduced: re-arm its counter on every rank for the next launch (launches are
+    // separated by a cross-rank barrier, so nobody counts into it before this store)
+    if (threadIdx.x < p.red_world) reinterpret_cast<int*>(p.cnt_ptrs[threadIdx.x])[blk] = 0;
+  }
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -153,7 +264,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int n_workers = (int)gridDim.x - p.g_ctas;  // CTAs that run GEMM tiles
+  const int n_workers = (int)gridDim.x - p.g_ctas - p.r_ctas;  // CTAs that run GEMM tiles
+  if ((int)blockIdx.x >= n_workers + p.g_ctas) {
+    reducer_cta_body(p, (int)blockIdx.x - n_workers - p.g_ctas, p.r_ctas, (p.M + BM - 1) / BM,
+                     4 * ((p.N + BN - 1) / BN));
+    return;
+  }
   if ((int)blockIdx.x >= n_workers) {
     gather_cta_body(p, (int)blockIdx.x - n_workers, p.g_ctas, smem, bars);
     return;
@@ -310,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
         const bool full_chunk = col0 + 32 <= p.N;
-        if (p.out_mode == 0) {
+        if (p.out_mode == 0 || p.out_mode == 5) {
           __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
           const __nv_bfloat16* irow =
               p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + row * p.ldcin + col0 : nullptr;
@@ -392,7 +508,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[acc]);
+        if (p.out_mode == 5) {
+          // this warp's quarter of the tile is stored: publish it (release at system scope covers the
+          // other lanes' stores, ordered before this point by the warp barrier)
+          int* c = reinterpret_cast<int*>(p.cnt_ptrs[p.red_rank]) + m_blk;
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(c) : "memory");
+        }
+      }
     }
   }
 
@@ -419,9 +543,9 @@ int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n * p.splits;
-  int workers = sm_count - p.g_ctas;
+  int workers = sm_count - p.g_ctas - p.r_ctas;
   if (tiles < workers) workers = tiles;
-  const int grid = workers + p.g_ctas;
+  const int grid = workers + p.g_ctas + p.r_ctas;
   static const bool dbg_cluster = getenv("AXB_DEBUG_CLUSTER") != nullptr;
   if (dbg_cluster) {
     cudaLaunchConfig_t cfg = {};
@@ -624,6 +748,55 @@ extern "C" int axb_gemm_bf16_allreduce(const void* A, long long lda, int a_mn, c
   p.red_mc = red_mc;
   p.red_world = red_world;
   for (int i = 0; i < red_world; ++i) p.red_ptrs[i] = red_ptrs[i];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 64: return dispatch_major<64>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    case 128: return dispatch_major<128>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    case 256: return dispatch_major<256>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);
+    default: return -5;
+  }
+}
+
+// GEMM + two-shot all-reduce in one launch. Every rank stores its partial product (bf16) into its
+// own symmetric buffer `C` (ldc = N) and `r_ctas` reducer CTAs sum each 128-row block over the
+// ranks as soon as it is complete everywhere, writing the sum into every rank's buffer.
+// red_mc: multicast address of the buffer (NULL = plain peer loads / stores through red_ptrs);
+// cnt_ptrs: HOST array of the ranks' int32 [ceil(M / 128)] completion counters (zero before the
+// first use; the kernel re-arms them). The sum is complete on a rank once all ranks have finished
+// the kernel (barrier afterwards).
+extern "C" int axb_gemm_bf16_allreduce2(const void* A, long long lda, int a_mn, const void* B, long long ldb,
+                                        int b_mn, void* C, long long ldc, int M, int N, int K, const void* A2,
+                                        long long lda2, const void* B2, long long ldb2, int K2, float alpha, int bn,
+                                        void* red_mc, const unsigned long long* red_ptrs,
+                                        const unsigned long long* cnt_ptrs, int red_rank, int red_world, int r_ctas,
+                                        int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (ldc & 7) || red_world < 1 || red_world > 8 || r_ctas < 1) return -2;
+  if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
+  CUtensorMap tA, tB, tA2, tB2;
+  int rc = 0;
+  rc |= a_mn ? axb_make_tmap_2d(&tA, A, K, M, lda, 64, 64) : axb_make_tmap_2d(&tA, A, M, K, lda, BM, 64);
+  rc |= b_mn ? axb_make_tmap_2d(&tB, B, K, N, ldb, 64, 64) : axb_make_tmap_2d(&tB, B, N, K, ldb, bn, 64);
+  if (K2 > 0) {
+    rc |= a_mn ? axb_make_tmap_2d(&tA2, A2, K2, M, lda2, 64, 64) : axb_make_tmap_2d(&tA2, A2, M, K2, lda2, BM, 64);
+    rc |= b_mn ? axb_make_tmap_2d(&tB2, B2, K2, N, ldb2, 64, 64) : axb_make_tmap_2d(&tB2, B2, N, K2, ldb2, bn, 64);
+  } else {
+    tA2 = tA;
+    tB2 = tB;
+  }
+  if (rc) return -4;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
+  p.C = C; p.ldc = ldc; p.alpha = alpha; p.splits = 1; p.status = status; p.group_m = 8;
+  p.out_mode = 5;
+  p.red_mc = red_mc;
+  p.red_world = red_world;
+  p.red_rank = red_rank;
+  p.r_ctas = r_ctas;
+  for (int i = 0; i < red_world; ++i) {
+    p.red_ptrs[i] = red_ptrs[i];
+    p.cnt_ptrs[i] = cnt_ptrs[i];
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (bn) {
     case 64: return dispatch_major<64>(a_mn, b_mn, tA, tB, tA2, tB2, p, sm_count(), st);

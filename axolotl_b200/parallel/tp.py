@@ -16,6 +16,7 @@ DTensor plans plus NCCL (src/axolotl/loaders/model.py:847-852).
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -31,6 +32,11 @@ _lib.register_cuda_sigs({
     "axb_gemm_bf16_allreduce": [_lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.i32, _lib.i64, _lib.i32, _lib.i32,
                                 _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.i64, _lib.i32, _lib.f32, _lib.i32, _lib.vp,
                                 _lib.vp, _lib.i32, _lib.vp, _lib.vp],
+    # A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, A2, lda2, B2, ldb2, K2, alpha, bn, red_mc, red_ptrs, cnt_ptrs,
+    # red_rank, red_world, r_ctas, status, stream
+    "axb_gemm_bf16_allreduce2": [_lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.i32,
+                                 _lib.i32, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.i64, _lib.i32, _lib.f32, _lib.i32,
+                                 _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp],
 })
 
 
@@ -41,8 +47,20 @@ class TPContext:
         self.k = 0
         if self.fused:
             self.bufs = [SymmBuffer(max_elems, torch.bfloat16, self.device, group) for _ in range(2)]
+            # per-rank completion counters of 128-row blocks (zeroed here, re-armed by the kernel)
+            self.cnt = SymmBuffer(65536, torch.int32, self.device, group, use_multicast=False)
+            self.cnt.tensor.zero_()
             self.sync = PeerSync(self.device, group)
+            self.reducer_ctas = int(os.environ.get("AXB_TP_REDUCER_CTAS", "0"))   # 0 = by GEMM depth
+            torch.cuda.synchronize(self.device)
             dist.barrier(group)
+
+    def _reducers(self, K):
+        """Reducer CTAs of a launch: the shallower the GEMM (small K), the more of the launch's time the
+        reduction of its output needs. Measured on 2 GPUs: 16 for K = 4096, 8 for K = 14336."""
+        if self.reducer_ctas > 0:
+            return self.reducer_ctas
+        return max(8, min(24, round(16 * 4096 / max(K, 1))))
 
     def reduced_gemm(self, a, b, *, trans_b=False, a2=None, b2=None, alpha=1.0):
         """sum over the TP group of ``alpha * (a @ op(b)^T + a2 @ op(b2)^T)`` -> [M, N] bf16."""
@@ -68,16 +86,19 @@ class TPContext:
         self.k += 1
         if M * N > buf.tensor.numel():
             raise ValueError("tensor-parallel reduce buffer is too small for this GEMM")
-        rc = lib.axb_gemm_bf16_allreduce(
-            a.data_ptr(), a.stride(0), 0, b.data_ptr(), b.stride(0), int(trans_b), N, M, N, K,
+        if (M + 127) // 128 > self.cnt.tensor.numel():
+            raise ValueError("tensor-parallel GEMM has more 128-row blocks than completion counters")
+        # one launch: tiles are stored into this rank's symmetric buffer while reducer CTAs sum every
+        # finished 128-row block over the ranks (in-switch multimem.ld_reduce, or peer loads) and
+        # write the sum back into every rank's buffer
+        rc = lib.axb_gemm_bf16_allreduce2(
+            a.data_ptr(), a.stride(0), 0, b.data_ptr(), b.stride(0), int(trans_b), buf.tensor.data_ptr(), N, M, N, K,
             _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0, K2,
-            float(alpha), _pick_bn(M, N), buf.multicast_ptr or None, buf.ptrs_c, self.size,
-            _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
-        _lib.check_rc(rc, "axb_gemm_bf16_allreduce")
-        self.sync.barrier(channel=3)            # every rank's partial tiles have landed everywhere
-        out = buf.tensor[: M * N].view(M, N).clone()
-        buf.tensor[: M * N].zero_()             # ready for its next use (two GEMMs later)
-        return out
+            float(alpha), _pick_bn(M, N), buf.multicast_ptr or None, buf.ptrs_c, self.cnt.ptrs_c, self.rank, self.size,
+            self._reducers(K), _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "axb_gemm_bf16_allreduce2")
+        self.sync.barrier(channel=3)            # every owner has written its blocks into every buffer
+        return buf.tensor[: M * N].view(M, N).clone()
 
 
 class _ColumnParallelLoRA(torch.autograd.Function):

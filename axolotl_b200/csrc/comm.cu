@@ -128,20 +128,35 @@ __global__ void __launch_bounds__(256)
 
   // ---- phase B: reduce my slice over all ranks, keep it in my own gradient buffer
   float ss = 0.f;
-  for (long long v = tid; v < nvec; v += nthreads) {
-    const long long i = lo + v * 4;
-    float4 g;
-    if (p.grad_mc) {
-      g = multimem_ld_reduce_f32x4(p.grad_mc + i);
-    } else {
-      g = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.grad_mc) {
+    // four independent in-switch reductions in flight per thread (the NVSwitch round trip is the cost)
+    constexpr int U = 4;
+    for (long long v0 = tid; v0 < nvec; v0 += nthreads * U) {
+      float4 g[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nthreads;
+        g[u] = multimem_ld_reduce_f32x4(p.grad_mc + lo + (v < nvec ? v : v0) * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nthreads;
+        if (v >= nvec) continue;
+        *reinterpret_cast<float4*>(my_grad + lo + v * 4) = g[u];
+        ss += g[u].x * g[u].x + g[u].y * g[u].y + g[u].z * g[u].z + g[u].w * g[u].w;
+      }
+    }
+  } else {
+    for (long long v = tid; v < nvec; v += nthreads) {
+      const long long i = lo + v * 4;
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int r = 0; r < p.world; ++r) {
         const float4 x = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.grad.p[r]) + i);
         g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
       }
+      *reinterpret_cast<float4*>(my_grad + i) = g;
+      ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
     }
-    *reinterpret_cast<float4*>(my_grad + i) = g;
-    ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
   }
   // block reduce -> atomic into this rank's scratch slot
 #pragma unroll

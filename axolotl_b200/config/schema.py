@@ -431,6 +431,7 @@ class AxolotlConfig(_Base):
     kto_undesirable_weight: float | None = None
     reward_model: bool | None = None
     process_reward_model: bool | None = None
+    peer_heartbeat_timeout: float | None = None   # extension: seconds before a silent peer is declared failed (0 = off)
     center_rewards_coefficient: float | None = None
     cpo_loss_type: str | None = None
     max_prompt_len: int | None = None

@@ -10,6 +10,7 @@ src/axolotl/monkeypatch/utils.py:111-169) without the segment-id mask round trip
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -64,9 +65,21 @@ class MLP(nn.Module):
                                         dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
         self.act = act
+        self.tile_rows = None   # tiled MLP: rows per tile (None = whole sequence at once)
+
+    def _mlp(self, x):
+        return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act))
 
     def forward(self, x):
-        return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act))
+        """With ``tile_rows`` set, the token rows go through the MLP tile by tile and every tile's
+        [rows, 2I] / [rows, I] intermediates are recomputed in the backward pass, so their peak size
+        no longer grows with the sequence length (the reference's Tiled MLP for very long contexts,
+        src/axolotl/monkeypatch/tiled_mlp/base.py:21-453)."""
+        t = self.tile_rows
+        if t is None or x.shape[0] <= t or not (self.training and torch.is_grad_enabled()):
+            return self._mlp(x)
+        outs = [checkpoint(self._mlp, x[i:i + t], use_reentrant=False) for i in range(0, x.shape[0], t)]
+        return torch.cat(outs, 0)
 
 
 class DecoderLayer(nn.Module):
@@ -112,6 +125,7 @@ class CausalLM(nn.Module):
         self.gradient_checkpointing = False
         self.ce_chunk_rows = 2048
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
+        self.nvtx = bool(os.environ.get("AXB_NVTX"))   # NVTX range per decoder layer for timeline tools
         self.neftune_noise_alpha = None  # NEFTune: uniform noise on the embedding output while training
 
     # ------------------------------------------------------------------ init
@@ -173,7 +187,10 @@ class CausalLM(nn.Module):
         residual = None
         aux_total = None
         hooks = self.hooks
+        nvtx = self.nvtx and h.is_cuda
         for i, layer in enumerate(self.layers):
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"layer{i}")
             if hooks is not None:
                 hooks.pre_layer(i)
             if self.gradient_checkpointing and self.training:
@@ -185,6 +202,8 @@ class CausalLM(nn.Module):
                 aux_total = aux if aux_total is None else aux_total + aux
             if hooks is not None:
                 hooks.post_layer(i)
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         h, _ = self.norm(h, residual)
         out = CausalLMOutput(hidden_states=h.view(B, S, -1))
         if aux_total is not None:

@@ -436,6 +436,10 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     trainer = trainer_cls(model, opt, lr_lambda, args, train_fn, eval_batches=eval_fn, parallel=parallel,
                           callbacks=callbacks, save_fn=save_fn, device=device, total_steps=total,
                           compute_loss=objective or pm.first("compute_loss", cfg))
+    if world > 1 and cfg.get("peer_heartbeat_timeout") != 0:
+        from ..parallel.health import HeartbeatCallback, HeartbeatMonitor
+
+        trainer.callbacks.append(HeartbeatCallback(HeartbeatMonitor(timeout_s=cfg.get("peer_heartbeat_timeout") or 600)))
     trainer.callbacks += pm.collect_callbacks("add_callbacks_post_trainer", cfg, trainer)
     pm.call("post_trainer_create", cfg, trainer)
 
@@ -450,6 +454,17 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     if resume and spec is not None and os.path.exists(os.path.join(resume, "adapter_model.safetensors")):
         load_adapter(model, resume)
     setup_signal_handler(trainer, model, cfg, spec)
+    if cfg.get("tiled_mlp"):
+        import math as _math
+
+        shards = cfg.get("tiled_mlp_num_shards") or max(1, _math.ceil(cfg["sequence_len"] * cfg["micro_batch_size"] / 8192))
+        rows = max(256, _math.ceil(cfg["sequence_len"] * cfg["micro_batch_size"] / shards / 128) * 128)
+        n = 0
+        for layer in model.layers:
+            if hasattr(layer.mlp, "tile_rows"):
+                layer.mlp.tile_rows = rows
+                n += 1
+        LOG.info("tiled MLP: %d layers, %d rows per tile", n, rows)
     if cfg.get("qat"):
         q = dict(cfg["qat"])
         start = q.get("fake_quant_after_n_steps") or 0

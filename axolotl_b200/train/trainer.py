@@ -103,6 +103,7 @@ def h2d_bytes(batch: dict) -> int:
 
 class Callback:
     def on_train_begin(self, trainer): ...
+    def on_pre_step(self, trainer): ...
     def on_pre_optimizer_step(self, trainer): ...
     def on_step_end(self, trainer, logs): ...
     def on_log(self, trainer, logs): ...
@@ -210,6 +211,8 @@ class Trainer:
                 pending.append(batch)
                 if len(pending) < ga:
                     continue
+                for cb in self.callbacks:   # nothing of this rank is in flight here (health checks)
+                    cb.on_pre_step(self)
                 loss = self.training_step(pending)
                 pending = []
                 self._after_step(loss)

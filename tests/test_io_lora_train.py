@@ -428,3 +428,40 @@ def test_neftune_only_in_training():
     assert torch.equal(model(ids, return_logits=True).logits, a)
     model.train()
     assert not torch.equal(model(ids, return_logits=True).logits, a)
+
+
+def test_tiled_mlp_matches_untiled_and_trace_analyzer(tmp_path):
+    import json
+
+    import torch
+
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.utils.analyze_profile import compare, summarize
+
+    cfg = preset("tiny-llama", num_hidden_layers=2, vocab_size=128)
+    model = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(0)
+    model.train()
+    ids = torch.randint(0, 128, (1, 96))
+    out = model(ids, labels=ids)
+    out.loss.backward()
+    g0 = model.layers[0].mlp.down_proj.weight.grad.clone()
+    model.zero_grad()
+    for l in model.layers:
+        l.mlp.tile_rows = 32
+    out2 = model(ids, labels=ids)
+    out2.loss.backward()
+    assert torch.allclose(out.loss, out2.loss, atol=1e-6)
+    assert torch.allclose(model.layers[0].mlp.down_proj.weight.grad, g0, atol=1e-5)
+
+    ev = [{"ph": "X", "cat": "kernel", "name": "gemm_bf16_tcgen05_kernel<256, false, false>", "dur": 300.0},
+          {"ph": "X", "cat": "kernel", "name": "flash_bwd_kernel<128>", "dur": 100.0},
+          {"ph": "X", "cat": "kernel", "name": "adamw_kernel", "dur": 10.0},
+          {"ph": "X", "cat": "kernel", "name": "some_library_kernel", "dur": 5.0},
+          {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "dur": 999.0}]
+    p = tmp_path / "t.json"
+    p.write_text(json.dumps({"traceEvents": ev}))
+    agg, steps, lines = summarize(str(p))
+    assert steps == 1 and agg["gemm (tcgen05)"][1] == 300.0 and agg["attention bwd"][0] == 1
+    assert agg["library / other"][1] == 5.0 and any("gemm" in l for l in lines)
+    assert any("attention bwd" in l for l in compare(str(p), str(p)))

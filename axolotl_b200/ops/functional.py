@@ -133,7 +133,11 @@ class _RopeQK(torch.autograd.Function):
                                 qkv.stride(0), 1.0, attn_scale, _lib.ptr(qn_w), _lib.ptr(kn_w),
                                 _lib.ptr(rstd), eps, _lib.stream_ptr()),
                 "rope_qk")
-            ctx.mark_dirty(qkv)
+            # The kernel rotated the buffer in place. Autograd is handed an alias of it as a fresh
+            # output instead of a "dirty" input: the producer of qkv (the projection) does not keep its
+            # output, so nothing else reads the pre-rotation values, and the in-place bookkeeping of
+            # autograd (which copies the 100 MB buffer several times per layer) is avoided.
+            qkv = qkv.detach()
         ctx.save_for_backward(pos, inv_freq, qn_w, kn_w, pre, rstd)
         return qkv
 

@@ -15,6 +15,8 @@ This is the B200 counterpart of the reference's per-layer ``fully_shard`` units 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..models.layers import FusedLinear
@@ -43,9 +45,11 @@ class FSDPContext:
         self.order = []               # sharded weights in forward execution order
         self.sharded = []
         self.stats = {"prefetched": 0, "standalone": 0}
-        # NVLink moves ~50 GB/s per gather CTA; a GEMM CTA row sustains ~9 TFLOP/s
-        self.bytes_per_cta_s = 50e9
-        self.max_prefetch_ctas = 24
+        # Planning figures for the number of gather CTAs per launch. Swept on 2 GPUs (Llama-3-8B LoRA
+        # step): under-provisioning exposes the gather (16 CTAs max / 80 GB/s assumed: 362 ms/step),
+        # 32-64 CTAs max at 20-40 GB/s assumed all land at 333-335 ms/step.
+        self.bytes_per_cta_s = float(os.environ.get("AXB_FSDP_CTA_GBS", "40")) * 1e9
+        self.max_prefetch_ctas = int(os.environ.get("AXB_FSDP_MAX_CTAS", "40"))
 
     @staticmethod
     def shardable(m: FusedLinear, world: int) -> bool:

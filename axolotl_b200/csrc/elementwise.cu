@@ -229,6 +229,39 @@ __global__ void rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const int* __res
   }
 }
 
+// Fast path without q/k norm: one warp per token. Each lane computes the sine / cosine of its two
+// angles ONCE and reuses them for every q and k head of the token (the angles depend on the position
+// only), and moves bf16 pairs (4-byte accesses, 128 B per warp instruction). sign = -1 is the
+// inverse rotation, i.e. the backward pass.
+__global__ void rope_fast_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
+                                 const float* __restrict__ inv_freq, int T, int nh, int D,
+                                 long long row_stride, float sign, float attn_scale) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long t = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int half = D >> 1;
+  const float ps = (float)pos[t];
+  __nv_bfloat16* row = qkv + t * row_stride;
+  for (int j = 2 * lane; j < half; j += 64) {
+    float s0, c0, s1, c1;
+    sincosf(ps * inv_freq[j], &s0, &c0);
+    sincosf(ps * inv_freq[j + 1], &s1, &c1);
+    s0 *= sign * attn_scale;
+    s1 *= sign * attn_scale;
+    c0 *= attn_scale;
+    c1 *= attn_scale;
+#pragma unroll 4
+    for (int hd = 0; hd < nh; ++hd) {
+      uint32_t* pa = reinterpret_cast<uint32_t*>(row + (long long)hd * D + j);
+      uint32_t* pb = reinterpret_cast<uint32_t*>(row + (long long)hd * D + half + j);
+      const float2 a = unpack_bf16x2(*pa), b = unpack_bf16x2(*pb);
+      *pa = pack_bf16x2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+      *pb = pack_bf16x2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    }
+  }
+}
+
 // Backward of (per-head RMSNorm ->) RoPE for the fused q/k gradient buffer, in place.
 // x_pre holds the pre-norm projection (needed only when norm weights are given).
 __global__ void rope_qk_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
@@ -557,6 +590,11 @@ extern "C" int axb_rope_qk(void* qkv, const int* pos, const float* inv_freq, int
                            const void* qn_w, const void* kn_w, float* rstd_out, float eps,
                            void* stream) {
   if (T <= 0) return 0;
+  if (!qn_w && !kn_w && (D % 4) == 0 && (row_stride % 2) == 0) {
+    rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)qkv, pos, inv_freq, T, Hq + Hk, D,
+                                                                     row_stride, sign, attn_scale);
+    return (int)cudaGetLastError();
+  }
   const long long warps = (long long)T * (Hq + Hk);
   const int wpb = 8;
   rope_qk_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
@@ -571,6 +609,11 @@ extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
                                float* dqn_w, float* dkn_w, void* stream) {
   if (T <= 0) return 0;
   if (D > 256) return -2;
+  if (!qn_w && !kn_w && (D % 4) == 0 && (row_stride % 2) == 0) {
+    rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)dqkv, pos, inv_freq, T, Hq + Hk, D,
+                                                                     row_stride, -1.f, attn_scale);
+    return (int)cudaGetLastError();
+  }
   const long long warps = (long long)T * (Hq + Hk);
   const int wpb = 8;
   rope_qk_bwd_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(

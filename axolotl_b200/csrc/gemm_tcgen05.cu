@@ -546,22 +546,6 @@ int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
   int workers = sm_count - p.g_ctas - p.r_ctas;
   if (tiles < workers) workers = tiles;
   const int grid = workers + p.g_ctas + p.r_ctas;
-  static const bool dbg_cluster = getenv("AXB_DEBUG_CLUSTER") != nullptr;
-  if (dbg_cluster) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid & ~1, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p);
-  }
   kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tA, tB, tA2, tB2, p);
   return (int)cudaGetLastError();
 }
@@ -860,11 +844,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* sA = smem;
   uint8_t* sB = smem + P_STAGES * P_A_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
-  uint64_t* full_bar = bars;                       // one per CTA: this CTA's TMA loads of the stage
+  uint64_t* full_bar = bars;                       // used in rank 0 only: both CTAs' loads of the stage
   uint64_t* empty_bar = bars + P_STAGES;           // one per CTA, signalled by the pair commit
   uint64_t* tfull_bar = bars + 2 * P_STAGES;       // one per CTA
   uint64_t* tempty_bar = bars + 2 * P_STAGES + 2;  // used in rank 0 only (8 arrivals)
-  uint64_t* peer_full_bar = bars + 2 * P_STAGES + 4;  // rank 0 only: the partner's stage has landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * P_STAGES + 4);
 
   const int warp = threadIdx.x >> 5;
@@ -889,7 +872,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
-      mbar_init(&peer_full_bar[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
@@ -923,8 +905,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = false;
             break;
           }
-          uint64_t* fb = &full_bar[stage];
-          mbar_expect_tx(fb, P_STAGE_BYTES);
+          // One "full" barrier per stage, in the leader CTA: the leader expects the bytes of BOTH CTAs'
+          // loads, and the partner's loads credit that barrier directly (cta_group::2 TMA). No relay,
+          // no remote arrive, no fence on the critical path.
+          const uint32_t fb = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
           const bool ext = kb >= nk_main;
           const CUtensorMap* ma = ext ? &tmA2 : &tmA;
           const CUtensorMap* mb = ext ? &tmB2 : &tmB;
@@ -934,16 +919,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int m0 = m_blk * 256 + (int)rank * 128;
           const int n0 = n_blk * 256 + (int)rank * 128;
           if (!A_MN) {
-            tma_load_2d(a_dst, ma, fb, k0, m0);
+            tma_load_2d_pair(a_dst, ma, fb, k0, m0);
           } else {
-            tma_load_2d(a_dst, ma, fb, m0, k0);
-            tma_load_2d(a_dst + 8192, ma, fb, m0 + 64, k0);
+            tma_load_2d_pair(a_dst, ma, fb, m0, k0);
+            tma_load_2d_pair(a_dst + 8192, ma, fb, m0 + 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(b_dst, mb, fb, k0, n0);
+            tma_load_2d_pair(b_dst, mb, fb, k0, n0);
           } else {
-            tma_load_2d(b_dst, mb, fb, n0, k0);
-            tma_load_2d(b_dst + 8192, mb, fb, n0 + 64, k0);
+            tma_load_2d_pair(b_dst, mb, fb, n0, k0);
+            tma_load_2d_pair(b_dst + 8192, mb, fb, n0 + 64, k0);
           }
           if (++stage == P_STAGES) {
             stage = 0;
@@ -953,25 +938,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ rank 1: relay "stage landed" to rank 0
-    if (lane == 0 && rank == 1) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
-        for (int kb = 0; kb < nk_total; ++kb) {
-          if (!mbar_wait_spin(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_cluster(mapa_u32(smem_u32(&peer_full_bar[stage]), 0));
-          if (++stage == P_STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-    }
     // ------------------------------------------------------------ MMA issuer (rank 0 only)
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(256, 256, A_MN ? 1 : 0, B_MN ? 1 : 0);
@@ -986,8 +952,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
         for (int kb = 0; kb < nk_total; ++kb) {
-          if ((!mbar_wait_spin(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL) ||
-                                !mbar_wait_spin(&peer_full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL))) {
+          if (!mbar_wait_spin(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
@@ -1002,16 +967,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                                      : make_smem_desc_sw128(b_addr + kk * 32, 16, 1024);
             umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
-          if (p.splits == 2) umma_commit_pair_mc(&empty_bar[stage]);
-          else umma_commit_pair_both(&empty_bar[stage]);  // frees the stage in both CTAs
+          umma_commit_pair_mc(&empty_bar[stage]);  // frees the stage in both CTAs (commit multicast)
           if (++stage == P_STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        if (p.splits == 2) umma_commit_pair_mc(&tfull_bar[acc]);
-        else umma_commit_pair_both(&tfull_bar[acc]);
+        umma_commit_pair_mc(&tfull_bar[acc]);
       }
     }
   } else {
@@ -1136,7 +1099,7 @@ extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const 
                                   int* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
-  if ((out_mode & 0xF) != 0 && (out_mode & 0xF) != 1) return -3;
+  if (out_mode != 0 && out_mode != 1) return -3;
   CUtensorMap tA, tB, tA2, tB2;
   int rc = 0;
   rc |= a_mn ? axb_make_tmap_2d(&tA, A, K, M, lda, 64, 64) : axb_make_tmap_2d(&tA, A, M, K, lda, 128, 64);
@@ -1152,7 +1115,7 @@ extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const 
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
   p.C = C; p.Cin = Cin; p.ldc = ldc; p.ldcin = ldcin;
-  p.alpha = alpha; p.beta = beta; p.out_mode = out_mode & 0xF; p.splits = (out_mode >> 4) ? (out_mode >> 4) + 1 : 1; p.status = status;
+  p.alpha = alpha; p.beta = beta; p.out_mode = out_mode; p.splits = 1; p.status = status;
   p.group_m = 4;  // bands of 4 x 256 rows
   PrefetchArgs pf;
   pf.peer_bases = pf_peer_bases; pf.shard_offset = pf_shard_offset; pf.shard_bytes = pf_shard_bytes;

@@ -17,7 +17,7 @@ _SM = 148
 # CTA-pair (cta_group::2, 256x256 tiles) kernel for large GEMMs. Numerically validated, but its
 # TMA-fed main loop currently runs at half the rate of the single-CTA kernel (the MMA-only rate
 # reaches the cuBLAS peak), so it is opt-in: AXB_GEMM_PAIR=1.
-USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "0") == "1"
+USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "1") != "0"   # CTA-pair (cta_group::2) kernel for large GEMMs
 
 
 def _pick_bn(M: int, N: int) -> int:
@@ -121,7 +121,7 @@ def gemm(
             raise ValueError("c_in must be row-major with the output dtype")
     if bn is None:
         bn = _pick_bn(M, N)
-    if USE_PAIR and bn == 256 and not accumulate and M >= 512 and N >= 512 and (M // 256) * (N // 256) >= 74:
+    if not accumulate and _use_pair(M, N, bn):
         rc = lib.axb_gemm_bf16_pair(
             a.data_ptr(), a.stride(0), int(trans_a), b.data_ptr(), b.stride(0), int(trans_b),
             out.data_ptr(), out.stride(0), _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
@@ -143,6 +143,12 @@ def gemm(
     )
     _lib.check_rc(rc, "axb_gemm_bf16")
     return out
+
+
+def _use_pair(M, N, bn) -> bool:
+    """The 2-CTA kernel (256x256 tile per SM pair, each CTA stages half of B) wins once there are
+    enough 256x256 tiles for the 74 SM pairs; small or skinny problems keep the 1-CTA kernel."""
+    return USE_PAIR and bn == 256 and M >= 512 and N >= 512 and ((M + 255) // 256) * ((N + 255) // 256) >= 74
 
 
 def pick_splits(out_tiles: int, k_blocks: int) -> int:
@@ -184,13 +190,22 @@ def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, 
               ctx.staging[slot].data_ptr(), ctx.prefetch_ctas(nxt, 2.0 * M * N * K))
     else:
         pf = (None, 0, 0, 0, None, 0)
-    rc = lib.axb_gemm_bf16_prefetch(
-        a.data_ptr(), a.stride(0), 0, staging.data_ptr(), cols, int(trans_b), out.data_ptr(), out.stride(0),
-        _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
-        _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
-        K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, 1, int(bn),
-        *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
-    _lib.check_rc(rc, "axb_gemm_bf16_prefetch")
+    if _use_pair(M, N, bn):
+        rc = lib.axb_gemm_bf16_pair(
+            a.data_ptr(), a.stride(0), 0, staging.data_ptr(), cols, int(trans_b), out.data_ptr(), out.stride(0),
+            _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
+            _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
+            K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode,
+            *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "axb_gemm_bf16_pair")
+    else:
+        rc = lib.axb_gemm_bf16_prefetch(
+            a.data_ptr(), a.stride(0), 0, staging.data_ptr(), cols, int(trans_b), out.data_ptr(), out.stride(0),
+            _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,
+            _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2), b2.stride(0) if b2 is not None else 0,
+            K2, float(alpha), float(beta if c_in is not None else 0.0), out_mode, 1, int(bn),
+            *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "axb_gemm_bf16_prefetch")
     if plan is not None:
         ctx.committed(plan)
     return out

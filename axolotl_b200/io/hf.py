@@ -23,12 +23,13 @@ from . import safetensors_io as st
 
 def _split_name(hf_name: str):
     """'model.layers.3.self_attn.q_proj.weight' -> ('layers.3.self_attn', 'q_proj', 'weight')."""
-    m = re.match(r"model\.(.*)\.(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj)\.(weight|bias)$", hf_name)
+    m = re.match(r"model\.(.*)\.(q_proj|k_proj|v_proj|qkv_proj|o_proj|gate_proj|up_proj|gate_up_proj|down_proj)\.(weight|bias)$", hf_name)
     return m.groups() if m else None
 
 
 _FUSED_OF = {"q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj", "o_proj": "o_proj",
-             "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj", "down_proj": "down_proj"}
+             "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj", "down_proj": "down_proj",
+             "qkv_proj": "qkv_proj", "gate_up_proj": "gate_up_proj"}   # Phi-3 checkpoints are already fused
 
 
 @torch.no_grad()

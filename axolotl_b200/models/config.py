@@ -13,7 +13,7 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any
 
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "mixtral")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral")
 
 
 @dataclass
@@ -165,6 +165,7 @@ class ModelConfig:
 _ARCH_NAME = {
     "llama": "LlamaForCausalLM",
     "mistral": "MistralForCausalLM",
+    "phi3": "Phi3ForCausalLM",
     "qwen2": "Qwen2ForCausalLM",
     "qwen3": "Qwen3ForCausalLM",
     "qwen3_moe": "Qwen3MoeForCausalLM",

@@ -1,4 +1,4 @@
-"""Decoder-only causal LM (Llama / Mistral / Qwen2 / Qwen3 / Qwen3-MoE / Mixtral block graph).
+"""Decoder-only causal LM (Llama / Mistral / Phi-3 / Qwen2 / Qwen3 / Qwen3-MoE / Mixtral block graph).
 
 The model works on *packed token streams*: ``input_ids`` [B, S] is flattened to T = B*S tokens,
 documents are delimited by resets of ``position_ids`` (and by row starts), attention is causal
@@ -40,9 +40,13 @@ class Attention(nn.Module):
         super().__init__()
         self.Hq, self.Hk, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         H = cfg.hidden_size
-        self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
-                                    ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
-                                    dtype=dtype, device=device)
+        if cfg.model_type == "phi3":   # the checkpoint (and its adapters) name the fused projection itself
+            self.qkv_proj = FusedLinear(H, [(self.Hq + 2 * self.Hk) * self.D], ["qkv_proj"], bias=cfg.attention_bias,
+                                        dtype=dtype, device=device)
+        else:
+            self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
+                                        ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
+                                        dtype=dtype, device=device)
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=False, dtype=dtype, device=device)
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
@@ -59,10 +63,13 @@ class Attention(nn.Module):
 
 
 class MLP(nn.Module):
-    def __init__(self, hidden, inter, act, bias, dtype, device):
+    def __init__(self, hidden, inter, act, bias, dtype, device, fused_names=False):
         super().__init__()
-        self.gate_up_proj = FusedLinear(hidden, [inter, inter], ["gate_proj", "up_proj"], bias=bias,
-                                        dtype=dtype, device=device)
+        if fused_names:
+            self.gate_up_proj = FusedLinear(hidden, [2 * inter], ["gate_up_proj"], bias=bias, dtype=dtype, device=device)
+        else:
+            self.gate_up_proj = FusedLinear(hidden, [inter, inter], ["gate_proj", "up_proj"], bias=bias,
+                                            dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
         self.act = act
         self.tile_rows = None   # tiled MLP: rows per tile (None = whole sequence at once)
@@ -93,7 +100,8 @@ class DecoderLayer(nn.Module):
 
             self.mlp = SparseMoE(cfg, dtype, device)
         else:
-            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
+                           fused_names=cfg.model_type == "phi3")
         self.is_moe = cfg.is_moe_layer(idx)
 
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):

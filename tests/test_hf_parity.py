@@ -92,3 +92,39 @@ def test_qwen3_moe_matches_hf(tmp_path):
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
     assert torch.allclose(got, ref, atol=3e-4, rtol=1e-3), (got - ref).abs().max()
+
+
+def test_phi3_fused_checkpoint_names_match_hf(tmp_path):
+    """Phi-3 checkpoints store qkv_proj / gate_up_proj fused: same layout as our modules."""
+    cfg = ModelConfig(model_type="phi3", vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      tie_word_embeddings=False)
+    cfg.extra = {"pad_token_id": 0, "bos_token_id": 1, "eos_token_id": 2, "max_position_embeddings": 512,
+                 "original_max_position_embeddings": 512, "sliding_window": None, "resid_pdrop": 0.0, "embd_pdrop": 0.0,
+                 "attention_dropout": 0.0}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(3)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    from axolotl_b200.io.safetensors_io import load_file
+    import glob
+    keys = set()
+    for f in glob.glob(str(tmp_path / "m" / "*.safetensors")):
+        keys |= set(load_file(f))
+    assert "model.layers.0.self_attn.qkv_proj.weight" in keys and "model.layers.1.mlp.gate_up_proj.weight" in keys
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    hf_model.eval()
+    lens = [41, 23]
+    ids, pos = _packed_inputs(320, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.equal(again(ids, pos, return_logits=True).logits, got)
+    # adapters are named after the fused modules, as PEFT names them for Phi-3
+    from axolotl_b200.models.lora import LoraSpec, get_peft_state_dict, inject_lora
+    inject_lora(ours, LoraSpec(r=4, lora_alpha=8, target_modules=["qkv_proj", "gate_up_proj"]))
+    sd = get_peft_state_dict(ours)
+    assert "base_model.model.model.layers.0.self_attn.qkv_proj.lora_A.weight" in sd
+    assert sd["base_model.model.model.layers.0.mlp.gate_up_proj.lora_B.weight"].shape == (320, 4)

@@ -18,7 +18,8 @@ import torch
 from .layers import FusedLinear
 from .moe import Experts
 
-ALL_LINEAR = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+ALL_LINEAR = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj",
+              "qkv_proj", "gate_up_proj")   # the last two: architectures whose checkpoints are fused (Phi-3)
 
 
 @dataclass

@@ -49,6 +49,10 @@ def model_config_from_cfg(cfg) -> ModelConfig:
 def build_model(cfg, device) -> CausalLM:
     dtype = torch.bfloat16 if cfg.get("torch_dtype") == "bfloat16" else torch.float32
     mc = model_config_from_cfg(cfg)
+    from ..models.registry import validate_cfg as validate_arch
+
+    for note in validate_arch(cfg, mc):
+        LOG.info("%s: %s", mc.model_type, note)
     pm = PluginManager.get_instance()
     pm.call("pre_model_load", cfg)
     src = cfg.get("base_model")

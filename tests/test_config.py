@@ -121,3 +121,19 @@ def test_plugins_contribute_keys():
                         grokfast_alpha=0.9))
     assert cfg.grokfast_alpha == 0.9
     PluginManager.reset()
+
+
+def test_architecture_registry_checks():
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.registry import support_for, validate_cfg
+
+    assert support_for("qwen3_moe").expert_parallel and not support_for("llama").expert_parallel
+    with pytest.raises(ValueError, match="no model graph"):
+        support_for("gemma2")
+    with pytest.raises(ValueError, match="expert parallelism needs"):
+        validate_cfg({"expert_parallel_size": 2}, preset("tiny-llama"))
+    with pytest.raises(ValueError, match="cannot be split"):
+        validate_cfg({"expert_parallel_size": 3}, preset("tiny-qwen3-moe"))
+    with pytest.raises(ValueError, match="tensor parallelism"):
+        validate_cfg({"tensor_parallel_size": 2}, preset("tiny-qwen3-moe"))
+    assert validate_cfg({"sample_packing": True}, preset("tiny-llama")) == []

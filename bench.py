@@ -89,7 +89,7 @@ def reference_arm(args):
     ref = os.path.join(ROOT, "baseline", "_ref")
     reason = None
     if not os.path.isdir(os.path.join(ref, "axolotl")):
-        reason = "baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref /root/reference)"
+        reason = "baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref <reference checkout>)"
     else:
         sys.path.insert(0, ref)
         missing = []

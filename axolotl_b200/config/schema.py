@@ -355,6 +355,13 @@ class AxolotlConfig(_Base):
     do_bench_eval: bool | None = None
     bench_dataset: str | None = None
     generate_samples: bool | None = None
+    num_generation_samples: int | None = 3
+    generation_max_new_tokens: int | None = 50
+    generation_temperature: float | None = 0.7
+    generation_top_p: float | None = None
+    generation_top_k: int | None = None
+    generation_prompt_ratio: float | None = 0.5
+    generation_do_sample: bool | None = True
     # ---- reporting
     use_wandb: bool | None = None
     wandb_project: str | None = None

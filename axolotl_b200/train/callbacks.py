@@ -224,6 +224,49 @@ class StatusCheckCallback(Callback):
             _lib.check_status(trainer.device)
 
 
+class SampleGenerationCallback(Callback):
+    """Monitoring: at every evaluation / save interval, continues a few evaluation (or training)
+    samples from a prefix with the current weights and logs prompt, reference continuation and
+    generation (``generate_samples`` and the ``generation_*`` keys of the reference,
+    src/axolotl/utils/schemas/config.py:1429-1468). Written to ``<output_dir>/generations.jsonl``."""
+
+    def __init__(self, cfg, samples, tokenizer=None, every=None):
+        self.n = cfg.get("num_generation_samples") or 3
+        self.max_new = cfg.get("generation_max_new_tokens") or 50
+        do_sample = cfg.get("generation_do_sample", True) is not False
+        self.temperature = (cfg.get("generation_temperature") if cfg.get("generation_temperature") is not None else 0.7) \
+            if do_sample else 0.0
+        self.top_p = cfg.get("generation_top_p") or 1.0
+        self.ratio = cfg.get("generation_prompt_ratio") if cfg.get("generation_prompt_ratio") is not None else 0.5
+        self.samples, self.tok = samples, tokenizer
+        self.every = every or cfg.get("eval_steps") or cfg.get("save_steps") or 100
+        self.out = os.path.join(cfg["output_dir"], "generations.jsonl")
+
+    def on_step_end(self, trainer, logs):
+        every = self.every if self.every >= 1 else max(int(self.every * max(trainer.total_steps or 1, 1)), 1)
+        if trainer.global_step % every or trainer.rank != 0:
+            return
+        model = trainer.model
+        dev = model.embed_tokens.device
+        rows = []
+        for i in range(min(self.n, len(self.samples))):
+            ids = [int(t) for t in self.samples[i]["input_ids"]]
+            cut = max(1, int(len(ids) * self.ratio))
+            out = model.generate(torch.tensor([ids[:cut]], device=dev), max_new_tokens=self.max_new,
+                                 temperature=self.temperature, top_p=self.top_p,
+                                 eos_token_id=getattr(self.tok, "eos_token_id", None))
+            gen = out[0].tolist()[cut:]
+            dec = (lambda t: self.tok.decode(t, skip_special_tokens=True)) if self.tok is not None else (lambda t: t)
+            rows.append({"step": trainer.global_step, "prompt": dec(ids[:cut]), "reference": dec(ids[cut:cut + self.max_new]),
+                         "generation": dec(gen)})
+        os.makedirs(os.path.dirname(self.out) or ".", exist_ok=True)
+        with open(self.out, "a") as fh:
+            for r in rows:
+                fh.write(json.dumps(r) + "\n")
+        model.train()
+        LOG.info("generated %d monitoring samples at step %d", len(rows), trainer.global_step)
+
+
 class ReLoRACallback(Callback):
     """ReLoRA: every ``restart_steps`` optimizer steps the adapters are folded into the base
     weights (W += s B A), A is re-initialised, B zeroed and the adapters' AdamW moments pruned, so

@@ -458,6 +458,12 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     if resume and spec is not None and os.path.exists(os.path.join(resume, "adapter_model.safetensors")):
         load_adapter(model, resume)
     setup_signal_handler(trainer, model, cfg, spec)
+    if cfg.get("generate_samples") and dataset_meta is not None and (dataset_meta.eval or dataset_meta.train) is not None:
+        from .callbacks import SampleGenerationCallback
+
+        src = dataset_meta.eval if dataset_meta.eval is not None and len(dataset_meta.eval) else dataset_meta.train
+        n = min(cfg.get("num_generation_samples") or 3, len(src))
+        trainer.callbacks.append(SampleGenerationCallback(cfg, [src[i] for i in range(n)], tokenizer))
     if cfg.get("tiled_mlp"):
         import math as _math
 

@@ -465,3 +465,22 @@ def test_tiled_mlp_matches_untiled_and_trace_analyzer(tmp_path):
     assert steps == 1 and agg["gemm (tcgen05)"][1] == 300.0 and agg["attention bwd"][0] == 1
     assert agg["library / other"][1] == 5.0 and any("gemm" in l for l in lines)
     assert any("attention bwd" in l for l in compare(str(p), str(p)))
+
+
+def test_sample_generation_callback_writes_rows(tmp_path):
+    import json
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.train.run import train
+
+    cfg = load_cfg({"model_preset": "tiny-llama", "adapter": "lora", "lora_r": 8, "lora_alpha": 16, "lora_target_linear": True,
+                    "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1, "max_steps": 4,
+                    "learning_rate": 1e-3, "optimizer": "adamw_torch", "output_dir": str(tmp_path / "g"), "device": "cpu",
+                    "generate_samples": True, "num_generation_samples": 2, "generation_max_new_tokens": 5,
+                    "generation_do_sample": False, "save_steps": 2, "save_strategy": "no", "sample_packing": True,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
+                                  "max_length": 48, "max_input_id": 300}]})
+    train(cfg)
+    rows = [json.loads(l) for l in open(tmp_path / "g" / "generations.jsonl")]
+    assert len(rows) == 4 and rows[0]["step"] == 2 and rows[-1]["step"] == 4
+    assert len(rows[0]["generation"]) <= 5 and len(rows[0]["prompt"]) >= 1

@@ -156,6 +156,34 @@ class CausalLM(nn.Module):
                 p.fill_(1.0)
         return self
 
+    @torch.no_grad()
+    def resize_token_embeddings(self, new_size: int, pad_to_multiple_of: int | None = None, mean_resizing: bool = True):
+        """Grows (or shrinks) the vocabulary. New rows are initialised to the mean of the old embedding
+        matrix (``mean_resizing``) or N(0, initializer_range); the size is rounded up to a multiple when
+        asked (``resize_token_embeddings_to_32x``). Returns the new vocabulary size."""
+        if pad_to_multiple_of:
+            new_size = (new_size + pad_to_multiple_of - 1) // pad_to_multiple_of * pad_to_multiple_of
+        old = self.config.vocab_size
+        if new_size == old:
+            return old
+
+        def grow(p):
+            out = torch.empty(new_size, p.shape[1], dtype=p.dtype, device=p.device)
+            n = min(old, new_size)
+            out[:n].copy_(p[:n])
+            if new_size > old:
+                if mean_resizing:
+                    out[old:] = p.float().mean(0, keepdim=True).to(p.dtype)
+                else:
+                    out[old:].normal_(0.0, self.config.initializer_range)
+            return nn.Parameter(out, requires_grad=p.requires_grad)
+
+        self.embed_tokens = grow(self.embed_tokens)
+        if self.lm_head is not None:
+            self.lm_head = grow(self.lm_head)
+        self.config.vocab_size = new_size
+        return new_size
+
     def output_weight(self):
         return self.embed_tokens if self.lm_head is None else self.lm_head
 

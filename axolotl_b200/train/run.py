@@ -350,6 +350,12 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         dataset_meta = load_datasets(cfg)
 
     model = build_model(cfg, device)
+    if tokenizer is not None:
+        want = len(tokenizer)
+        if want > model.config.vocab_size or (cfg.get("shrink_embeddings") and want < model.config.vocab_size):
+            new = model.resize_token_embeddings(want, 32 if cfg.get("resize_token_embeddings_to_32x") else None,
+                                                bool(cfg.get("mean_resizing_embeddings")))
+            LOG.info("token embeddings resized to %d rows (tokenizer has %d tokens)", new, want)
     parallel = None
     if world > 1:
         from ..parallel.runtime import create_runtime

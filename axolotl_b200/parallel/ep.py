@@ -113,12 +113,12 @@ class ExpertParallelGroup:
         tok = (order // k).to(torch.int32)
         loc_e = (flat_e[order] % self.E_local).to(torch.int32)
         wt = w.reshape(-1)[order].float()
-        r_tok = torch.empty(n_recv, dtype=torch.int32, device=dev)
-        r_e = torch.empty(n_recv, dtype=torch.int32, device=dev)
-        r_w = torch.empty(n_recv, dtype=torch.float32, device=dev)
-        dist.all_to_all_single(r_tok, tok, rc, sc, group=self.group)
-        dist.all_to_all_single(r_e, loc_e, rc, sc, group=self.group)
-        dist.all_to_all_single(r_w, wt.detach(), rc, sc, group=self.group)
+        # one exchange for the three per-slot fields: [token row, local expert, routing weight bits]
+        send = torch.stack([tok, loc_e, wt.detach().contiguous().view(torch.int32)], 1).contiguous()
+        recv = torch.empty((n_recv, 3), dtype=torch.int32, device=dev)
+        dist.all_to_all_single(recv, send, rc, sc, group=self.group)
+        r_tok, r_e = recv[:, 0].contiguous(), recv[:, 1].contiguous()
+        r_w = recv[:, 2].contiguous().view(torch.float32)
         src_rank = torch.repeat_interleave(torch.arange(self.size, device=dev, dtype=torch.int32),
                                            torch.tensor(rc, device=dev))
         local_order = torch.argsort(r_e, stable=True)

@@ -1040,7 +1040,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
           float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
           const float* irow = p.Cin ? reinterpret_cast<const float*>(p.Cin) + row * p.ldcin + col0 : nullptr;
-          for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = v[j] + (irow ? p.beta * irow[j] : 0.f);
+          if (full_chunk && (p.ldc & 3) == 0 && (!irow || (p.ldcin & 3) == 0)) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              if (irow) {
+                const float4 in = *reinterpret_cast<const float4*>(irow + q * 4);
+                o.x += p.beta * in.x;
+                o.y += p.beta * in.y;
+                o.z += p.beta * in.z;
+                o.w += p.beta * in.w;
+              }
+              *reinterpret_cast<float4*>(crow + q * 4) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = v[j] + (irow ? p.beta * irow[j] : 0.f);
+          }
         }
       }
       tc_fence_before();

@@ -104,6 +104,11 @@ def gemm(
     if a2 is not None:
         a2 = _row_major_2d(a2)
         b2 = _row_major_2d(b2)
+    if accumulate and splits <= 1 and out is not None and out.dtype == torch.float32 and c_in is None and a.is_cuda:
+        # a single K pass owns every output tile: plain read-add-write (beta = 1) instead of fp32
+        # atomics, which also makes the launch eligible for the 2-CTA kernel
+        return gemm(a, b, trans_a=trans_a, trans_b=trans_b, a2=a2, b2=b2, alpha=alpha, beta=1.0, c_in=out, out=out,
+                    out_dtype=torch.float32, accumulate=False, splits=1, bn=bn)
     if accumulate:
         if out is None or out.dtype != torch.float32:
             raise ValueError("accumulate=True needs an fp32 `out`")

@@ -470,3 +470,20 @@ def test_nf4_dequant_kernel_and_qlora_linear():
     got8 = dequantize_fp8_block(wf.to(_dev()), sc.to(_dev()))
     _check_status()
     assert torch.equal(got8.cpu(), ref8)
+
+
+@pytest.mark.parametrize("M,N,K", [(384, 520, 2048), (2304, 2560, 1024)])
+def test_gemm_accumulate_single_pass_is_read_add_write(M, N, K):
+    """accumulate=True with one K pass: non-atomic beta = 1 epilogue (1-CTA kernel for the small shape,
+    2-CTA kernel for the large one), transposed operands as in a weight-gradient GEMM."""
+    from axolotl_b200.ops.gemm import gemm
+    torch.manual_seed(51)
+    a = (torch.randn(K, M) * 0.5).bfloat16().to(_dev())     # dy^T stored as [K, M]
+    b = (torch.randn(K, N) * 0.5).bfloat16().to(_dev())
+    acc = torch.randn(M, N, device=_dev())
+    ref = acc.double().cpu() + a.double().cpu().t() @ b.double().cpu()
+    gemm(a, b, trans_a=True, trans_b=True, out=acc, accumulate=True, splits=1)
+    gemm(a, b, trans_a=True, trans_b=True, out=acc, accumulate=True, splits=1)
+    ref = ref + a.double().cpu().t() @ b.double().cpu()
+    _check_status()
+    assert _rel_err(acc.cpu(), ref.float()) < 2e-3

@@ -190,7 +190,10 @@ class RoutedLayout(GroupLayout):
         T, k = idx.shape
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
-        super().__init__(torch.bincount(flat_e, minlength=E), T * k)
+        # torch.bincount synchronises with the host (it sizes its output from the data): count with a
+        # scatter-add instead so the layer stays free of host round trips
+        counts = torch.zeros(E, dtype=torch.int64, device=idx.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
+        super().__init__(counts, T * k)
         self.k = k
         self.slot_row = torch.empty(T * k, dtype=torch.int32, device=idx.device)
         self.slot_row[order] = self.dest.to(torch.int32)

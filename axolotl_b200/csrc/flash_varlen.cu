@@ -43,6 +43,9 @@ struct AttnParams {
   int cp_world;
   long long cp_chunk;
   unsigned long long cp_dkv_ptrs[8];
+  // backward: the q heads of one kv head may be split over `kv_split` CTAs (load balance for wide
+  // GQA groups); their dK / dV partial tiles are then reduce-added into a pre-zeroed buffer
+  int kv_split;
 };
 
 AXB_DEVICE float fast_exp2(float x) {
@@ -403,8 +406,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   using C = BwdCfg<D>;
   const int tile_id = blockIdx.y;
   if (tile_id >= p.n_tiles) return;
-  const int kv_head = blockIdx.x;
-  const int group = p.Hq / p.Hk;
+  const int kv_head = blockIdx.x / p.kv_split;
+  const int part = blockIdx.x - kv_head * p.kv_split;
+  const int group_all = p.Hq / p.Hk;
+  const int group = group_all / p.kv_split;             // q heads handled by this CTA
+  const int head0 = kv_head * group_all + part * group;  // first of them
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, kv0 = ti.z;
   // 64-row q tiles at or below the diagonal that intersect this rank's q rows
@@ -479,7 +485,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       for (int it = 0; it < n_iter; ++it) {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        const int head = kv_head * group + it / n_qt;
+        const int head = head0 + it / n_qt;
         const int qrow = doc_start + (q_first + it % n_qt) * 64 - p.q_row_off;
         if (!mbar_wait(&q_empty[st], ph ^ 1, p.status, AXB_TIMEOUT_EMPTY)) break;
         mbar_expect_tx(&q_full[st], 2 * C::Q_BYTES);
@@ -579,7 +585,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     bool ok = true;
     for (int it = grp; it < n_iter && ok; it += 2) {
       const uint32_t ph = (it >> 1) & 1;
-      const int head = kv_head * group + it / n_qt;
+      const int head = head0 + it / n_qt;
       const int qt0 = (q_first + it % n_qt) * 64;  // doc-relative first q row of the tile
       // stage lse / delta of the 64 q rows (one buffer per warpgroup; the previous iteration of
       // this group finished reading it before its threads got here: bar.sync below orders that)
@@ -716,7 +722,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             w.y = pack_bf16x2(__uint_as_float(b[q * 8 + 2]), __uint_as_float(b[q * 8 + 3]));
             w.z = pack_bf16x2(__uint_as_float(b[q * 8 + 4]), __uint_as_float(b[q * 8 + 5]));
             w.w = pack_bf16x2(__uint_as_float(b[q * 8 + 6]), __uint_as_float(b[q * 8 + 7]));
-            if (p.cp_world > 1) {
+            if (p.cp_world > 1 || p.kv_split > 1) {
               asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(
                                krow + c * 32 + q * 8),
                            "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
@@ -784,7 +790,7 @@ int launch_bwd(const CUtensorMap& tkv, const CUtensorMap& tq, const CUtensorMap&
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
-  dim3 grid(p.Hk, p.n_tiles);
+  dim3 grid(p.Hk * p.kv_split, p.n_tiles);
   kern<<<grid, kBwdThreads, C::SMEM, st>>>(tkv, tq, tdo, p);
   return (int)cudaGetLastError();
 }
@@ -878,6 +884,15 @@ int flash_bwd_impl(const AttnGeom& g, const void* dout, const void* out, long lo
   p.dv_col0 = dv_col0;
   p.cp_world = cp_world > 1 ? cp_world : 1;
   p.cp_chunk = cp_chunk;
+  // Wide GQA groups: one CTA per (kv tile, kv head) loops over group * q-tiles iterations, and the
+  // longest such CTA bounds the launch. Two CTAs per kv head halve it; their dK / dV partials meet
+  // in the (zeroed) gradient buffer through bf16x2 reduce-adds.
+  p.kv_split = (cp_world <= 1 && Hq / Hk >= 8 && (Hq / Hk) % 2 == 0 && dv_col0 == dk_col0 + Hk * D) ? 2 : 1;
+  if (p.kv_split > 1) {
+    e = cudaMemset2DAsync(reinterpret_cast<__nv_bfloat16*>(dqkv) + dk_col0, (size_t)dqkv_ld * 2, 0,
+                          (size_t)2 * Hk * D * 2, (size_t)g.kv_rows, st);
+    if (e != cudaSuccess) return (int)e;
+  }
   for (int i = 0; i < 8; ++i) p.cp_dkv_ptrs[i] = (cp_world > 1 && i < cp_world) ? cp_dkv_ptrs[i] : 0ull;
   int rc = D == 128 ? launch_bwd<128>(tkv, tq, tdo, p, st) : launch_bwd<64>(tkv, tq, tdo, p, st);
   if (rc) return rc;

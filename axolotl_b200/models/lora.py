@@ -216,6 +216,9 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
                         used.add(k)
                     elif strict:
                         raise KeyError(f"adapter tensor {k} is missing")
+    from ..ops.grouped import bump_param_epoch
+
+    bump_param_epoch()   # cached operand copies of expert adapters are stale
     unused = set(norm) - used
     if strict and unused:
         raise KeyError(f"unexpected adapter tensors: {sorted(unused)[:5]} ...")

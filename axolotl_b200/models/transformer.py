@@ -294,6 +294,9 @@ class CausalLM(nn.Module):
                 yield name, m
 
     def refresh_lora_shadows(self):
+        from ..ops.grouped import bump_param_epoch
+
+        bump_param_epoch()
         for _, m in self.fused_linears():
             m.refresh_shadows()
         for m in self.modules():

@@ -115,6 +115,28 @@ def _expert_weights(experts, which):
     return out
 
 
+# bf16 operand copies of the expert adapters are rebuilt once per optimizer step, not once per GEMM:
+# the trainer bumps this counter whenever parameters may have changed.
+_PARAM_EPOCH = [0]
+
+
+def bump_param_epoch():
+    _PARAM_EPOCH[0] += 1
+
+
+def _adapter_operands(experts, which, A, B, E):
+    """(A16 [E, r, K], Bt16 [E, N, r]) bf16 operand layouts of one expert adapter, cached per epoch."""
+    cache = experts.__dict__.setdefault("_operand_cache", {})
+    hit = cache.get(which)
+    if hit is not None and hit[0] == _PARAM_EPOCH[0] and hit[1] is A and hit[2] is B and torch.is_grad_enabled() == hit[5]:
+        return hit[3], hit[4]
+    r = A.shape[0] // E
+    A16 = A.detach().to(torch.bfloat16).view(E, r, -1).contiguous()
+    Bt16 = B.detach().view(-1, r, E).permute(2, 0, 1).to(torch.bfloat16).contiguous()
+    cache[which] = (_PARAM_EPOCH[0], A, B, A16, Bt16, torch.is_grad_enabled())
+    return A16, Bt16
+
+
 def _grad_buffer(p):
     g = getattr(p, "_axb_grad", None)
     return g
@@ -129,9 +151,7 @@ class _GroupedProj(torch.autograd.Function):
         W = _expert_weights(experts, which)
         E = W.shape[0]
         if A is not None:
-            r = A.shape[0] // E
-            A16 = A.detach().to(torch.bfloat16).view(E, r, -1).contiguous()
-            Bt16 = B.detach().view(-1, r, E).permute(2, 0, 1).to(torch.bfloat16).contiguous()   # [E, N, r]
+            A16, Bt16 = _adapter_operands(experts, which, A, B, E)
             t = grouped_gemm(x, A16, lay, alpha=scaling)
             y = grouped_gemm(x, W, lay, a2=t, w2=Bt16)
             ctx.save_for_backward(x, t, A, B)
@@ -152,8 +172,7 @@ class _GroupedProj(torch.autograd.Function):
         if ctx.has_lora:
             x, t, A, B = ctx.saved_tensors
             r = A.shape[0] // E
-            A16 = A.detach().to(torch.bfloat16).view(E, r, -1).contiguous()
-            Bt16 = B.detach().view(-1, r, E).permute(2, 0, 1).to(torch.bfloat16).contiguous()
+            A16, Bt16 = _adapter_operands(experts, which, A, B, E)
             dt = grouped_gemm(dy, Bt16, lay, trans_w=True, alpha=ctx.scaling)    # s * dy B_e   [rows, r]
             dx = grouped_gemm(dy, W, lay, trans_w=True, a2=dt, w2=A16)
             gA = _grad_buffer(A)

@@ -177,6 +177,9 @@ class Trainer:
         else:
             gnorm_sq = opt.step(lr=lr)
         opt.zero_grad()
+        from ..ops.grouped import bump_param_epoch
+
+        bump_param_epoch()   # cached bf16 operand copies of adapters are stale now
         if par is not None:
             par.after_optimizer_step()
         self.global_step += 1

@@ -158,7 +158,7 @@ def test_embedding():
     assert _rel_err(tab.grad.cpu(), ref) < 1e-3
 
 
-@pytest.mark.parametrize("D,Hq,Hk", [(128, 4, 2), (64, 4, 2), (128, 8, 8)])
+@pytest.mark.parametrize("D,Hq,Hk", [(128, 4, 2), (64, 4, 2), (128, 8, 8), (128, 8, 1)])
 @pytest.mark.parametrize("lens", [[128], [200, 57, 300], [1, 129, 640, 31], [1024, 513]])
 def test_flash_varlen_fwd_bwd(D, Hq, Hk, lens):
     from axolotl_b200.ops.functional import AttnMeta, flash_varlen

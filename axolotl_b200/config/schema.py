@@ -438,6 +438,8 @@ class AxolotlConfig(_Base):
     kto_undesirable_weight: float | None = None
     reward_model: bool | None = None
     process_reward_model: bool | None = None
+    lisa_n_layers: int | None = None
+    lisa_step_interval: int | None = None
     peer_heartbeat_timeout: float | None = None   # extension: seconds before a silent peer is declared failed (0 = off)
     center_rewards_coefficient: float | None = None
     cpo_loss_type: str | None = None
@@ -520,7 +522,7 @@ INERT_KEYS = {
     "gemma4_hybrid_attn_impl", "gpu_memory_limit", "gradio_max_new_tokens", "gradio_server_name",
     "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
     "image_size", "is_falcon_derived_model",
-    "lisa_layers_attribute", "lisa_n_layers", "lisa_step_interval", "loftq_config", "lora_on_cpu", "low_cpu_mem_usage",
+    "lisa_layers_attribute", "loftq_config", "lora_on_cpu", "low_cpu_mem_usage",
     "max_memory", "max_packed_sequence_len", "model_quantization_config",
     "model_quantization_config_kwargs", "noisy_embedding_alpha", "num_dataset_shards_to_save",
     "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "peft_layer_replication",

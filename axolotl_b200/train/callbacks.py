@@ -267,6 +267,39 @@ class SampleGenerationCallback(Callback):
         LOG.info("generated %d monitoring samples at step %d", len(rows), trainer.global_step)
 
 
+class LISACallback(Callback):
+    """Layerwise importance sampling for full fine-tuning: every ``interval`` steps a new random set
+    of ``n_layers`` decoder layers is trainable, all others are frozen (no gradient is computed for
+    them and the optimizer leaves their weights and moments alone); embeddings, final norm and head
+    always train. Reference: src/axolotl/utils/callbacks/lisa.py:23 (``lisa_n_layers``,
+    ``lisa_step_interval``)."""
+
+    def __init__(self, n_layers, interval, seed=0):
+        import random
+
+        self.n, self.interval, self.rng = int(n_layers), max(int(interval), 1), random.Random(seed)
+        self.active = None
+
+    def _switch(self, trainer):
+        layers = trainer.model.layers
+        self.active = sorted(self.rng.sample(range(len(layers)), min(self.n, len(layers))))
+        for i, layer in enumerate(layers):
+            on = i in self.active
+            for p in layer.parameters():
+                if getattr(p, "_axb_grad", None) is not None or p.requires_grad:   # parameters the optimizer owns
+                    p.requires_grad_(on)
+        if hasattr(trainer.opt, "set_active_layers"):
+            trainer.opt.set_active_layers(self.active)
+        LOG.info("LISA: training layers %s", self.active)
+
+    def on_train_begin(self, trainer):
+        self._switch(trainer)
+
+    def on_step_end(self, trainer, logs):
+        if trainer.global_step % self.interval == 0:
+            self._switch(trainer)
+
+
 class ReLoRACallback(Callback):
     """ReLoRA: every ``restart_steps`` optimizer steps the adapters are folded into the base
     weights (W += s B A), A is re-initialised, B zeroed and the adapters' AdamW moments pruned, so
@@ -306,6 +339,8 @@ class ReLoRACallback(Callback):
 
 def build_callbacks(cfg):
     cbs = [JsonlReporter(), StatusCheckCallback()]
+    if cfg.get("lisa_n_layers") and cfg.get("lisa_step_interval"):
+        cbs.append(LISACallback(cfg["lisa_n_layers"], cfg["lisa_step_interval"], cfg.get("seed") or 0))
     if cfg.get("relora") and cfg.get("jagged_restart_steps"):
         cbs.append(ReLoRACallback(cfg["jagged_restart_steps"], cfg.get("relora_prune_ratio")))
     if cfg.get("loss_watchdog_threshold") is not None:

@@ -17,11 +17,20 @@ from ..ops.optim import adamw_step_, grad_sumsq
 
 
 def build_param_groups(named_params, *, weight_decay=0.0, embedding_lr=None, embedding_lr_scale=None,
-                       loraplus_lr_ratio=None, loraplus_lr_embedding=None, lr_groups=None, lr=1e-4):
-    """Returns a list of dicts {name, params: [(name, p)], lr_scale, weight_decay}."""
+                       loraplus_lr_ratio=None, loraplus_lr_embedding=None, lr_groups=None, lr=1e-4,
+                       per_layer=False):
+    """Returns a list of dicts {name, params: [(name, p)], lr_scale, weight_decay}. ``per_layer``
+    gives every decoder layer its own groups (name suffix ``@layers.N``) so that layers can be
+    switched on and off as units (LISA)."""
+    import re as _re
+
     groups = {}
 
     def add(key, item, lr_scale, wd):
+        if per_layer:
+            m = _re.search(r"layers\.(\d+)\.", item[0])
+            if m:
+                key = f"{key}@layers.{m.group(1)}"
         g = groups.setdefault(key, {"name": key, "params": [], "lr_scale": lr_scale, "weight_decay": wd})
         g["params"].append(item)
 
@@ -190,6 +199,15 @@ class FlatAdamW:
         self._gnorm = ss
         return ss
 
+    def set_active_layers(self, layers):
+        """LISA: only the parameter groups of these decoder layers (and the groups outside any layer)
+        are updated; the others keep weights AND moments untouched, like parameters without a
+        gradient in a per-tensor optimizer. ``None`` re-activates everything."""
+        keep = None if layers is None else {f"layers.{int(i)}" for i in layers}
+        for g in self.groups:
+            tag = g["name"].partition("@")[2]
+            g["active"] = keep is None or not tag or tag in keep
+
     def step(self, lr=None, gnorm_sq=None):
         if self.moment_shard is not None:
             raise RuntimeError("this optimizer holds sharded moments: it is stepped by the fused parallel runtime")
@@ -200,6 +218,8 @@ class FlatAdamW:
         else:
             self._fold_autograd_grads()
         for g in self.groups:
+            if not g.get("active", True):
+                continue
             adamw_step_(g["master"], g["grad"], g["exp_avg"], g["exp_avg_sq"], step=self.step_count,
                         lr=lr * g["lr_scale"], beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                         weight_decay=g["weight_decay"], bf16_copy=g["shadow"], gnorm_sq=gnorm_sq,
@@ -247,6 +267,15 @@ class TorchOptimizerAdapter:
             if p.grad is not None:
                 ss += p.grad.float().pow(2).sum()
         return extra_reduce(ss) if extra_reduce is not None else ss
+
+    def set_active_layers(self, layers):
+        """LISA: only the parameter groups of these decoder layers (and the groups outside any layer)
+        are updated; the others keep weights AND moments untouched, like parameters without a
+        gradient in a per-tensor optimizer. ``None`` re-activates everything."""
+        keep = None if layers is None else {f"layers.{int(i)}" for i in layers}
+        for g in self.groups:
+            tag = g["name"].partition("@")[2]
+            g["active"] = keep is None or not tag or tag in keep
 
     def step(self, lr=None, gnorm_sq=None):
         if self.moment_shard is not None:

@@ -140,7 +140,7 @@ def build_optimizer(cfg, model, parallel=None):
                                 embedding_lr=cfg.get("embedding_lr"), embedding_lr_scale=cfg.get("embedding_lr_scale"),
                                 loraplus_lr_ratio=cfg.get("loraplus_lr_ratio"),
                                 lr_groups=[dict(g) for g in (cfg.get("lr_groups") or [])] or None,
-                                lr=float(cfg["learning_rate"]))
+                                lr=float(cfg["learning_rate"]), per_layer=bool(cfg.get("lisa_n_layers")))
     betas = (cfg.get("adam_beta1") or 0.9, cfg.get("adam_beta2") or 0.999)
     eps = cfg.get("adam_epsilon") or 1e-8
     if name in ("adamw_torch", "adamw_torch_fused", "adamw_hf", "adamw", "adamw_anyprecision", "adamw_apex_fused"):

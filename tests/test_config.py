@@ -82,8 +82,8 @@ def test_deprecated_and_legacy_spellings_are_mapped():
 
 
 def test_inert_reference_keys_are_accepted():
-    raw = dict(BASE, liger_rope=True, torch_compile_backend="inductor", lisa_n_layers=2)
-    assert set(check_keys(raw)) == {"liger_rope", "torch_compile_backend", "lisa_n_layers"}
+    raw = dict(BASE, liger_rope=True, torch_compile_backend="inductor", gc_collect_steps=2)
+    assert set(check_keys(raw)) == {"liger_rope", "torch_compile_backend", "gc_collect_steps"}
     load_cfg(raw)
 
 

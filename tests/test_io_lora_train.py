@@ -484,3 +484,27 @@ def test_sample_generation_callback_writes_rows(tmp_path):
     rows = [json.loads(l) for l in open(tmp_path / "g" / "generations.jsonl")]
     assert len(rows) == 4 and rows[0]["step"] == 2 and rows[-1]["step"] == 4
     assert len(rows[0]["generation"]) <= 5 and len(rows[0]["prompt"]) >= 1
+
+
+def test_lisa_trains_only_sampled_layers(tmp_path):
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.train.run import train
+
+    cfg = load_cfg({"model_preset": "tiny-llama", "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1,
+                    "max_steps": 4, "learning_rate": 1e-3, "optimizer": "adamw_torch", "lr_scheduler": "constant",
+                    "output_dir": str(tmp_path / "l"), "device": "cpu", "lisa_n_layers": 1, "lisa_step_interval": 100,
+                    "sample_packing": True, "save_strategy": "no", "weight_decay": 0.0,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
+                                  "max_length": 48, "max_input_id": 300}]})
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+    ref = CausalLM(preset("tiny-llama"), dtype=torch.float32, device="cpu").init_weights(cfg.get("seed") or 42)
+    model, _, trainer = train(cfg)
+    changed = []
+    for i, (a, b) in enumerate(zip(model.layers, ref.layers)):
+        d = max(float((p.detach() - q.detach()).abs().max()) for p, q in zip(a.parameters(), b.parameters()))
+        changed.append(d > 0)
+    assert sum(changed) == 1, changed                      # exactly the sampled layer moved
+    assert float((model.embed_tokens.detach() - ref.embed_tokens.detach()).abs().max()) > 0   # embeddings always train

@@ -104,7 +104,7 @@ def check_fused_optimizer(dev, rank, world):
             print(f"fused rs+adamw+ag ok (multimem={'on' if use_mc else 'off'})")
 
 
-def check_training_equivalence(dev, rank, world, backend):
+def check_training_equivalence(dev, rank, world, backend, replicate=False):
     """A tiny LoRA model trained data-parallel must follow the single-process run on the
     concatenated batch (same seed, deterministic data)."""
     from axolotl_b200.data.collator import PackedCollator
@@ -134,7 +134,12 @@ def check_training_equivalence(dev, rank, world, backend):
                 for (r0, rows, c0, r) in m.lora_blocks:
                     mask[r0:r0 + rows, c0:c0 + r] = 1
                 m.lora_B.mul_(mask)
-        par = build_parallel(model, device=dev, dp_shard=world, backend=backend) if parallel_on else None
+        if not parallel_on:
+            par = None
+        elif replicate:   # plain replicated data parallel (DDP): no sharding axis at all
+            par = build_parallel(model, device=dev, dp_shard=1, dp_replicate=world, backend=backend)
+        else:
+            par = build_parallel(model, device=dev, dp_shard=world, backend=backend)
         opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0,
                         alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world,
                         moment_shard=par.moment_shard() if par is not None else None)
@@ -169,7 +174,7 @@ def check_training_equivalence(dev, rank, world, backend):
     dist.all_gather(lst, chk)
     assert all(float(x) == float(lst[0]) for x in lst), [float(x) for x in lst]
     if rank == 0:
-        print(f"dp training equivalence ok ({backend}): {mean_par} vs {l_ref}")
+        print(f"dp training equivalence ok ({backend}{', replicated' if replicate else ''}): {mean_par} vs {l_ref}")
 
 
 def check_tensor_parallel(dev, rank, world):
@@ -373,7 +378,7 @@ def check_expert_parallel(dev, rank, world):
 
 def main():
     cpu = len(sys.argv) > 1 and sys.argv[1] == "cpu"
-    only = set(sys.argv[2:])   # optional subset: gather opt dp tp cp ep
+    only = set(sys.argv[2:])   # optional subset: gather opt dp ddp tp cp ep
 
     def want(name):
         return not only or name in only
@@ -383,6 +388,7 @@ def main():
         dist.init_process_group("gloo")
         dev = torch.device("cpu")
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
+        want("ddp") and check_training_equivalence(dev, rank, world, "collective", replicate=True)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)
         want("ep") and check_expert_parallel(dev, rank, world)
@@ -394,6 +400,7 @@ def main():
         want("opt") and check_fused_optimizer(dev, rank, world)
         want("dp") and check_training_equivalence(dev, rank, world, "fused")
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
+        want("ddp") and check_training_equivalence(dev, rank, world, "fused", replicate=True)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)
         want("ep") and check_expert_parallel(dev, rank, world)

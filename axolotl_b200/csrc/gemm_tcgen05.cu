@@ -16,8 +16,19 @@
 // while the other CTAs run this GEMM from the staging buffer the previous launch filled. Stream
 // order is the only synchronisation: no flags, no polling, the MMA pipeline is never throttled.
 //
+// Fused all-reduce (tensor parallelism): in out_mode 5 every tile is stored into this rank's
+// symmetric buffer and counted per 128-row block; trailing reducer CTAs wait (bounded) until a
+// block they own is complete on every rank, sum it through NVSwitch (multimem.ld_reduce, or peer
+// loads) and write the sum into every rank's buffer (multimem.st, or peer stores) while the other
+// CTAs keep computing: reduce-scatter + all-gather inside the GEMM launch.
+//
+// Large problems run on gemm_bf16_pair_kernel below: one 256x256 tile per 2-CTA cluster with
+// tcgen05.mma.cta_group::2 (each CTA stages its 128 rows of A and its half of B; the partner's TMA
+// loads credit the leader's mbarrier directly, no multicast loads).
+//
 // Replaces the cuBLAS calls behind the reference's LoRA kernels (src/axolotl/kernels/lora.py:226-280)
-// and, with the prefetch CTAs, the NCCL all-gather of its FSDP2 units.
+// and, with the prefetch / reducer CTAs, the NCCL all-gather of its FSDP2 units and the
+// all-reduce of its tensor-parallel layers.
 #include <cstdlib>
 
 #include "axb_common.cuh"

@@ -101,10 +101,23 @@ def grouped_gram(a, b, lay: GroupLayout, out, *, alpha=1.0, accumulate=False):
     return out
 
 
-def _expert_weights(experts, which):
-    """bf16 [E, N, K] stack of one projection (dequantised from NVFP4 when the experts are quantised)."""
+# Dequantised expert stacks may be kept from the forward to the backward pass of the same layer
+# while they fit a memory budget (half of the memory that is free when the first one is cached);
+# beyond the budget the backward pass dequantises again. 180 GB of HBM usually holds all of them.
+_WCACHE = {"bytes": 0, "budget": None}
+
+
+def _expert_weights(experts, which, keep=False, take=False):
+    """bf16 [E, N, K] stack of one projection (dequantised from NVFP4 when the experts are quantised).
+    ``keep``: forward pass of a training step (offer the result to the cache); ``take``: backward
+    pass (use and release the cached copy if there is one)."""
     if experts.nvfp4 is None:
         return experts.gate_up_proj if which == "gate_up" else experts.down_proj
+    cache = experts.__dict__.setdefault("_dequant_cache", {})
+    if take and which in cache:
+        W = cache.pop(which)
+        _WCACHE["bytes"] -= W.numel() * 2
+        return W
     q = experts.nvfp4[which]
     E, N, K2 = q["qdata"].shape
     out = torch.empty((E, N, K2 * 2), dtype=torch.bfloat16, device=q["qdata"].device)
@@ -112,6 +125,12 @@ def _expert_weights(experts, which):
     _lib.check_rc(_lib.cuda_lib().axb_nvfp4_dequant_batched(
         q["qdata"].data_ptr(), q["scale"].data_ptr(), pts.data_ptr(), out.data_ptr(), E, N, K2 * 2,
         _lib.stream_ptr()), "nvfp4_dequant_batched")
+    if keep and which not in cache:
+        if _WCACHE["budget"] is None:
+            _WCACHE["budget"] = int(torch.cuda.mem_get_info(out.device)[0] * 0.5)
+        if _WCACHE["bytes"] + out.numel() * 2 <= _WCACHE["budget"]:
+            cache[which] = out
+            _WCACHE["bytes"] += out.numel() * 2
     return out
 
 
@@ -148,7 +167,7 @@ class _GroupedProj(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, experts, which, lay, A, B, scaling):
-        W = _expert_weights(experts, which)
+        W = _expert_weights(experts, which, keep=bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[4]))
         E = W.shape[0]
         if A is not None:
             A16, Bt16 = _adapter_operands(experts, which, A, B, E)
@@ -166,7 +185,7 @@ class _GroupedProj(torch.autograd.Function):
     def backward(ctx, dy):
         experts, which, lay = ctx.experts, ctx.which, ctx.lay
         dy = dy.contiguous()
-        W = _expert_weights(experts, which)
+        W = _expert_weights(experts, which, take=True)
         E = W.shape[0]
         dA = dB = None
         if ctx.has_lora:

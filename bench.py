@@ -311,7 +311,7 @@ def main():
                        "parallelism": ({"moe": f"ep{world}", "tp70b": f"tp2 x fsdp{world // 2}", "cp64k": f"cp{world}"}
                                        .get(args.config, f"fsdp{world}")) if world > 1 else "single",
                        "lora_r": 16, "lora_alpha": 32,
-                       "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 1,
+                       "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 2 if args.config == "moe" else 1,
                        "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K,

@@ -345,9 +345,11 @@ __device__ __forceinline__ float act_bwd(float g, int kind) {
   const float t = tanhf(k0 * (g + k1 * g * g * g));
   return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
 }
-// gu: [T, 2I] (gate | up);  h: [T, I] = act(gate) * up
+// gu: [T, 2I] (gate | up);  h: [T, I] = act(gate) * up. With limit > 0 (clamped SwiGLU of the
+// DeepSeek-V4 / gpt-oss experts): act(min(gate, limit)) * clamp(up, -limit, limit), and the
+// gradients vanish where the clamp is active.
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
-                               long long T, int I, int kind) {
+                               long long T, int I, int kind, float limit) {
   const long long nvec = T * (I / 8);
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
@@ -357,14 +359,19 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat
     load8(gu + t * 2 * I + c, g);
     load8(gu + t * 2 * I + I + c, u);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], kind) * u[j];
+    for (int j = 0; j < 8; ++j) {
+      const float gc = limit > 0.f ? fminf(g[j], limit) : g[j];
+      const float uc = limit > 0.f ? fminf(fmaxf(u[j], -limit), limit) : u[j];
+      o[j] = act_fwd(gc, kind) * uc;
+    }
     store8(h + t * I + c, o);
   }
 }
 // dgu[T,2I]: d_gate = dh * up * act'(gate), d_up = dh * act(gate). dgu may alias gu.
 __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
                                const __nv_bfloat16* __restrict__ gu,
-                               __nv_bfloat16* __restrict__ dgu, long long T, int I, int kind) {
+                               __nv_bfloat16* __restrict__ dgu, long long T, int I, int kind,
+                               float limit) {
   const long long nvec = T * (I / 8);
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
@@ -376,8 +383,12 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
     load8(dh + t * I + c, d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      og[j] = d[j] * u[j] * act_bwd(g[j], kind);
-      ou[j] = d[j] * act_fwd(g[j], kind);
+      const bool g_in = !(limit > 0.f) || g[j] <= limit;
+      const bool u_in = !(limit > 0.f) || (u[j] >= -limit && u[j] <= limit);
+      const float gc = g_in ? g[j] : limit;
+      const float uc = u_in ? u[j] : (u[j] > 0.f ? limit : -limit);
+      og[j] = g_in ? d[j] * uc * act_bwd(gc, kind) : 0.f;
+      ou[j] = u_in ? d[j] * act_fwd(gc, kind) : 0.f;
     }
     store8(dgu + t * 2 * I + c, og);
     store8(dgu + t * 2 * I + I + c, ou);
@@ -482,6 +493,141 @@ __global__ void __launch_bounds__(CE_T)
     float pr = __expf(__bfloat162float(z[i]) - lse);
     if (i == label) pr -= 1.f;
     z[i] = __float2bfloat16(pr * gs);
+  }
+}
+
+// ---------------------------------------------------------------------------------- gated RMSNorm
+// y = (w + w_offset) * x * rstd(x) * silu(g): the output norm of gated linear-attention blocks
+// (Qwen3.5 GatedDeltaNet). One block per row; x is kept in registers between the two passes.
+__global__ void __launch_bounds__(NORM_T)
+    rmsnorm_gated_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                             float* __restrict__ rstd_out, int H, float eps, float w_offset) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8) {
+    float f[8];
+    load8(x + row * H + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum<NORM_T>(ss, sh);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0) rstd_out[row] = rstd;
+  for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8) {
+    float f[8], gv[8], wv[8];
+    load8(x + row * H + i, f);
+    load8(g + row * H + i, gv);
+    load8(w + i, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      f[j] = f[j] * rstd * (wv[j] + w_offset) * (gv[j] / (1.f + __expf(-gv[j])));
+    store8(y + row * H + i, f);
+  }
+}
+// With n = x*rstd*(w+off) and s = silu(g):  dg = dy*n*silu'(g);  dn = dy*s;
+// dx = rstd * (dn*(w+off) - xhat * mean(dn*(w+off)*xhat));  dw += dn * xhat.
+__global__ void __launch_bounds__(NORM_T)
+    rmsnorm_gated_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                             const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ w,
+                             const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                             __nv_bfloat16* __restrict__ dg, float* __restrict__ dw, int H, int rows,
+                             float w_offset) {
+  __shared__ float sh[32];
+  float dw_acc[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[a][j] = 0.f;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8) {
+      float a[8], b[8], c[8], gv[8];
+      load8(dy + row * H + i, a);
+      load8(x + row * H + i, b);
+      load8(w + i, c);
+      load8(g + row * H + i, gv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float s = gv[j] / (1.f + __expf(-gv[j]));
+        dot += a[j] * s * (c[j] + w_offset) * b[j] * rstd;
+      }
+    }
+    dot = block_sum<NORM_T>(dot, sh) / H;
+    int k = 0;
+    for (int i = threadIdx.x * 8; i < H; i += NORM_T * 8, ++k) {
+      float a[8], b[8], c[8], gv[8], ox[8], og[8];
+      load8(dy + row * H + i, a);
+      load8(x + row * H + i, b);
+      load8(w + i, c);
+      load8(g + row * H + i, gv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sg = 1.f / (1.f + __expf(-gv[j]));
+        const float s = gv[j] * sg;
+        const float xhat = b[j] * rstd;
+        const float wj = c[j] + w_offset;
+        const float dn = a[j] * s;
+        ox[j] = rstd * (dn * wj - xhat * dot);
+        og[j] = a[j] * xhat * wj * sg * (1.f + gv[j] * (1.f - sg));
+        if (dw) {
+          if (k < 4) dw_acc[k][j] += dn * xhat;
+          else atomicAdd(dw + i + j, dn * xhat);
+        }
+      }
+      store8(dx + row * H + i, ox);
+      store8(dg + row * H + i, og);
+    }
+  }
+  if (dw) {
+    int k = 0;
+    for (int i = threadIdx.x * 8; i < H && k < 4; i += NORM_T * 8, ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(dw + i + j, dw_acc[k][j]);
+  }
+}
+
+// ---------------------------------------------------------------------------------- entropy
+// One block per row of a [R, V] bf16 logits chunk: a single online pass keeps the running maximum
+// m, Z = sum exp(z - m) and S = sum (z - m) exp(z - m); entropy = log Z - S / Z. lse is returned
+// as well. (The RL trainers log the policy entropy per token without a [R, V] fp32 softmax.)
+__global__ void __launch_bounds__(CE_T)
+    entropy_kernel(const __nv_bfloat16* __restrict__ logits, float* __restrict__ ent,
+                   float* __restrict__ lse_out, int V, long long ld, float inv_temp) {
+  __shared__ float sh[32];
+  const long long r = blockIdx.x;
+  const __nv_bfloat16* z = logits + r * ld;
+  const int v8 = V & ~7;
+  float m = -INFINITY, Z = 0.f, S = 0.f;
+  auto push = [&](float v) {
+    v *= inv_temp;
+    if (v > m) {  // rescale the running sums to the new maximum
+      const float c = __expf(m - v);
+      S = (m == -INFINITY) ? 0.f : c * (S + (m - v) * Z);
+      Z = (m == -INFINITY) ? 0.f : c * Z;
+      m = v;
+    }
+    const float e = __expf(v - m);
+    Z += e;
+    S += (v - m) * e;
+  };
+  for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8) {
+    float f[8];
+    load8(z + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) push(f[j]);
+  }
+  for (int i = v8 + threadIdx.x; i < V; i += CE_T) push(__bfloat162float(z[i]));
+  const float M = block_max<CE_T>(m, sh);
+  const float c = (m == -INFINITY) ? 0.f : __expf(m - M);
+  const float Zs = c * Z, Ss = c * (S + (m - M) * Z);
+  const float Zt = block_sum<CE_T>(Zs, sh);
+  const float St = block_sum<CE_T>((m == -INFINITY) ? 0.f : Ss, sh);
+  if (threadIdx.x == 0) {
+    ent[r] = logf(Zt) - St / Zt;
+    if (lse_out) lse_out[r] = M + logf(Zt);  // of the scaled logits
   }
 }
 
@@ -622,19 +768,50 @@ extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
       dqn_w, dkn_w);
   return (int)cudaGetLastError();
 }
-extern "C" int axb_glu_fwd(const void* gu, void* h, long long T, int I, int kind, void* stream) {
-  if (I % 8) return -2;
-  if (T <= 0) return 0;
-  glu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind);
+extern "C" int axb_rmsnorm_gated_fwd(const void* x, const void* g, const void* w, void* y,
+                                     float* rstd, long long rows, int H, float eps,
+                                     float w_offset, void* stream) {
+  if (H % 8) return -2;
+  if (rows <= 0) return 0;
+  rmsnorm_gated_fwd_kernel<<<(unsigned)rows, NORM_T, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, (const __nv_bfloat16*)w,
+      (__nv_bfloat16*)y, rstd, H, eps, w_offset);
   return (int)cudaGetLastError();
 }
-extern "C" int axb_glu_bwd(const void* dh, const void* gu, void* dgu, long long T, int I, int kind,
+extern "C" int axb_rmsnorm_gated_bwd(const void* dy, const void* x, const void* g, const void* w,
+                                     const float* rstd, void* dx, void* dg, float* dw,
+                                     long long rows, int H, float w_offset, void* stream) {
+  if (H % 8) return -2;
+  if (rows <= 0) return 0;
+  const unsigned grid = (unsigned)(rows < 148 * 4 ? rows : 148 * 4);
+  rmsnorm_gated_bwd_kernel<<<grid, NORM_T, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)g,
+      (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, (__nv_bfloat16*)dg, dw, H, (int)rows,
+      w_offset);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_entropy(const void* logits, float* ent, float* lse, long long rows, int V,
+                           long long ld, float inv_temp, void* stream) {
+  if (rows <= 0) return 0;
+  if (ld % 8) return -2;
+  entropy_kernel<<<(unsigned)rows, CE_T, 0, ST(stream)>>>((const __nv_bfloat16*)logits, ent, lse, V,
+                                                         ld, inv_temp);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_glu_fwd(const void* gu, void* h, long long T, int I, int kind, float limit,
                            void* stream) {
   if (I % 8) return -2;
   if (T <= 0) return 0;
+  glu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind, limit);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_glu_bwd(const void* dh, const void* gu, void* dgu, long long T, int I, int kind,
+                           float limit, void* stream) {
+  if (I % 8) return -2;
+  if (T <= 0) return 0;
   glu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
-      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind);
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind, limit);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_embedding_fwd(const void* table, const long long* ids, void* out, long long T,

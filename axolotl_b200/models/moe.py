@@ -48,6 +48,7 @@ class Experts(nn.Module):
     def __init__(self, num_experts, hidden, inter, act, dtype, device):
         super().__init__()
         self.E, self.H, self.I, self.act = num_experts, hidden, inter, act
+        self.glu_limit = None      # clamped SwiGLU (config key ``swiglu_limit``)
         self.gate_up_proj = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(num_experts, hidden, inter, dtype=dtype, device=device))
         self.nvfp4 = None          # dict with packed tensors when the experts are frozen in NVFP4
@@ -109,7 +110,7 @@ class Experts(nn.Module):
             if use_lora:
                 A, B = self.expert_lora("gate_up", e)
                 gu = gu + self.scaling * ((xe @ A.to(xe.dtype).t()) @ B.to(xe.dtype).t())
-            h = Fn.glu(gu, self.act)
+            h = Fn.glu(gu, self.act, self.glu_limit)
             y = linear(h, self.expert_weight("down", e))
             if use_lora:
                 A, B = self.expert_lora("down", e)

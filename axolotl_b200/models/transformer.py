@@ -72,10 +72,11 @@ class MLP(nn.Module):
                                             dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
         self.act = act
+        self.glu_limit = None   # clamped SwiGLU (config key ``swiglu_limit``)
         self.tile_rows = None   # tiled MLP: rows per tile (None = whole sequence at once)
 
     def _mlp(self, x):
-        return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act))
+        return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act, self.glu_limit))
 
     def forward(self, x):
         """With ``tile_rows`` set, the token rows go through the MLP tile by tile and every tile's
@@ -135,6 +136,11 @@ class CausalLM(nn.Module):
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
         self.nvtx = bool(os.environ.get("AXB_NVTX"))   # NVTX range per decoder layer for timeline tools
         self.neftune_noise_alpha = None  # NEFTune: uniform noise on the embedding output while training
+        limit = (getattr(cfg, "extra", None) or {}).get("swiglu_limit")
+        if limit:
+            for m in self.modules():
+                if hasattr(m, "glu_limit"):
+                    m.glu_limit = float(limit)
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()

@@ -194,17 +194,19 @@ def _act_ref(g, kind):
 
 class _GLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gu, kind):
+    def forward(ctx, gu, kind, limit):
         I = gu.shape[-1] // 2
-        ctx.kind = kind
+        ctx.kind, ctx.limit = kind, float(limit or 0.0)
         ctx.save_for_backward(gu)
         if not gu.is_cuda:
             g, u = gu[..., :I].float(), gu[..., I:].float()
+            if ctx.limit > 0:
+                g, u = g.clamp(max=ctx.limit), u.clamp(-ctx.limit, ctx.limit)
             return (_act_ref(g, kind) * u).to(gu.dtype)
         lib = _lib.cuda_lib()
         gu2 = gu.reshape(-1, 2 * I)
         h = torch.empty((gu2.shape[0], I), dtype=gu.dtype, device=gu.device)
-        _lib.check_rc(lib.axb_glu_fwd(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind,
+        _lib.check_rc(lib.axb_glu_fwd(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind, ctx.limit,
                                       _lib.stream_ptr()), "glu_fwd")
         return h.view(*gu.shape[:-1], I)
 
@@ -212,26 +214,119 @@ class _GLU(torch.autograd.Function):
     def backward(ctx, dh):
         (gu,) = ctx.saved_tensors
         I = gu.shape[-1] // 2
+        L = ctx.limit
         if not gu.is_cuda:
+            g_raw, u_raw = gu[..., :I].float(), gu[..., I:].float()
+            gc = g_raw.clamp(max=L) if L > 0 else g_raw
+            uc = u_raw.clamp(-L, L) if L > 0 else u_raw
             with torch.enable_grad():
-                g = gu[..., :I].float().detach().requires_grad_(True)
+                g = gc.detach().requires_grad_(True)
                 a = _act_ref(g, ctx.kind)
                 (da,) = torch.autograd.grad(a.sum(), g)
-            u = gu[..., I:].float()
             dhf = dh.float()
-            return torch.cat([dhf * u * da, dhf * a.detach()], -1).to(gu.dtype), None
+            dg, du = dhf * uc * da, dhf * a.detach()
+            if L > 0:
+                dg = dg * (g_raw <= L)
+                du = du * ((u_raw >= -L) & (u_raw <= L))
+            return torch.cat([dg, du], -1).to(gu.dtype), None, None
         lib = _lib.cuda_lib()
         gu2 = gu.reshape(-1, 2 * I)
         dh2 = dh.reshape(-1, I).contiguous()
         dgu = torch.empty_like(gu2)
         _lib.check_rc(lib.axb_glu_bwd(dh2.data_ptr(), gu2.data_ptr(), dgu.data_ptr(), gu2.shape[0],
-                                      I, ctx.kind, _lib.stream_ptr()), "glu_bwd")
-        return dgu.view(gu.shape), None
+                                      I, ctx.kind, L, _lib.stream_ptr()), "glu_bwd")
+        return dgu.view(gu.shape), None, None
 
 
-def glu(gate_up, activation="silu"):
-    """``act(gate) * up`` for a fused ``[.., 2I]`` (gate | up) projection."""
-    return _GLU.apply(gate_up, _ACT_KIND[activation])
+def glu(gate_up, activation="silu", limit=None):
+    """``act(gate) * up`` for a fused ``[.., 2I]`` (gate | up) projection. With ``limit`` the gate is
+    clamped from above and the up branch to ``[-limit, limit]`` first (the clamped SwiGLU of the
+    reference's grouped expert graph,
+    src/axolotl/integrations/kernels/libs/scattermoe_lora/cutlass_fp4/swiglu.py:16-148)."""
+    return _GLU.apply(gate_up, _ACT_KIND[activation], limit)
+
+
+# --------------------------------------------------------------------------------------- gated RMSNorm
+class _RMSNormGated(torch.autograd.Function):
+    """y = (w + w_offset) * rmsnorm(x) * silu(g)."""
+
+    @staticmethod
+    def forward(ctx, x, g, w, eps, w_offset):
+        H = x.shape[-1]
+        x2, g2 = x.reshape(-1, H), g.reshape(-1, H)
+        ctx.w_offset, ctx.shape = w_offset, x.shape
+        if not x.is_cuda:
+            n, rstd = _rmsnorm_ref(x2, w, eps, w_offset)
+            y = (n.float() * F.silu(g2.float())).to(x.dtype)
+        else:
+            lib = _lib.cuda_lib()
+            x2, g2 = x2.contiguous(), g2.contiguous()
+            y = torch.empty_like(x2)
+            rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+            _lib.check_rc(lib.axb_rmsnorm_gated_fwd(x2.data_ptr(), g2.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                                    rstd.data_ptr(), x2.shape[0], H, eps, w_offset,
+                                                    _lib.stream_ptr()), "rmsnorm_gated_fwd")
+        ctx.save_for_backward(x2, g2, w, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g, w, rstd = ctx.saved_tensors
+        H = x.shape[-1]
+        need_dw = ctx.needs_input_grad[2]
+        if not x.is_cuda:
+            dyf, xf, gf = dy.reshape(-1, H).float(), x.float(), g.float()
+            wf = w.float() + ctx.w_offset
+            sg = torch.sigmoid(gf)
+            s = gf * sg
+            xhat = xf * rstd[:, None]
+            dn = dyf * s
+            gw = dn * wf
+            dx = rstd[:, None] * (gw - xhat * (gw * xhat).mean(-1, keepdim=True))
+            dg = dyf * xhat * wf * sg * (1 + gf * (1 - sg))
+            dw = (dn * xhat).sum(0).to(w.dtype) if need_dw else None
+            return dx.to(x.dtype).view(ctx.shape), dg.to(g.dtype).view(ctx.shape), dw, None, None
+        lib = _lib.cuda_lib()
+        dy2 = dy.reshape(-1, H).contiguous()
+        dx, dg = torch.empty_like(x), torch.empty_like(g)
+        dwf = torch.zeros(H, dtype=torch.float32, device=x.device) if need_dw else None
+        _lib.check_rc(lib.axb_rmsnorm_gated_bwd(dy2.data_ptr(), x.data_ptr(), g.data_ptr(), w.data_ptr(),
+                                                rstd.data_ptr(), dx.data_ptr(), dg.data_ptr(), _lib.ptr(dwf),
+                                                x.shape[0], H, ctx.w_offset, _lib.stream_ptr()),
+                      "rmsnorm_gated_bwd")
+        return dx.view(ctx.shape), dg.view(ctx.shape), (dwf.to(w.dtype) if need_dw else None), None, None
+
+
+def rmsnorm_gated(x, gate, weight, eps=1e-6, w_offset=0.0):
+    """``(weight + w_offset) * rmsnorm(x) * silu(gate)`` in one pass over the row (the output norm of
+    gated linear-attention blocks; reference kernel: src/axolotl/kernels/rms_norm_gated.py:36-381)."""
+    return _RMSNormGated.apply(x, gate, weight, eps, w_offset)
+
+
+# --------------------------------------------------------------------------------------- entropy
+@torch.no_grad()
+def token_entropy(logits, temperature=1.0, return_lse=False):
+    """Entropy of ``softmax(logits / temperature)`` per row of ``[.., V]`` logits in one online pass,
+    without an fp32 softmax of the chunk (reference: src/axolotl/monkeypatch/trainer/utils.py:23-510).
+    Not differentiable: the RL trainers only log it."""
+    V = logits.shape[-1]
+    z = logits.reshape(-1, V)
+    if not z.is_cuda:
+        lp = torch.log_softmax(z.float() / temperature, -1)
+        ent = -(lp.exp() * lp).sum(-1)
+        lse = torch.logsumexp(z.float() / temperature, -1)
+    else:
+        lib = _lib.cuda_lib()
+        if z.dtype != torch.bfloat16 or z.stride(1) != 1 or z.stride(0) % 8:
+            z = z.to(torch.bfloat16).contiguous()
+            if V % 8:
+                z = F.pad(z, (0, 8 - V % 8))[:, :V]   # keeps a 16-byte aligned row pitch
+        ent = torch.empty(z.shape[0], dtype=torch.float32, device=z.device)
+        lse = torch.empty_like(ent)
+        _lib.check_rc(lib.axb_entropy(z.data_ptr(), ent.data_ptr(), lse.data_ptr(), z.shape[0], V, z.stride(0),
+                                      1.0 / temperature, _lib.stream_ptr()), "entropy")
+    ent, lse = ent.view(logits.shape[:-1]), lse.view(logits.shape[:-1])
+    return (ent, lse) if return_lse else ent
 
 
 # --------------------------------------------------------------------------------------- embedding
@@ -479,7 +574,7 @@ class _LinearTokenLogps(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, h, w, labels, chunk_rows, ignore_index):
+    def forward(ctx, h, w, labels, chunk_rows, ignore_index, entropy_out=None):
         from .gemm import gemm
 
         T = h.shape[0]
@@ -490,6 +585,9 @@ class _LinearTokenLogps(torch.autograd.Function):
             for r0 in range(0, T, chunk_rows):
                 r1 = min(T, r0 + chunk_rows)
                 logits = gemm(h[r0:r1], w)
+                if entropy_out is not None:   # the logits chunk is still intact here
+                    _lib.check_rc(lib.axb_entropy(logits.data_ptr(), entropy_out[r0:r1].data_ptr(), None, r1 - r0, V,
+                                                  logits.stride(0), 1.0, _lib.stream_ptr()), "entropy")
                 _lib.check_rc(lib.axb_ce_fwd_bwd(logits.data_ptr(), labels[r0:r1].data_ptr(), nll[r0:r1].data_ptr(),
                                                  None, r1 - r0, V, logits.stride(0), 1.0, ignore_index, 0,
                                                  _lib.stream_ptr()), "ce_fwd")
@@ -499,7 +597,10 @@ class _LinearTokenLogps(torch.autograd.Function):
                 lf = (h[r0:r1] @ w.to(h.dtype).t()).float()
                 lab = labels[r0:r1]
                 valid = lab != ignore_index
-                lp = torch.log_softmax(lf, -1).gather(1, lab.clamp(min=0)[:, None]).squeeze(1)
+                lsm = torch.log_softmax(lf, -1)
+                if entropy_out is not None:
+                    entropy_out[r0:r1] = -(lsm.exp() * lsm).sum(-1)
+                lp = lsm.gather(1, lab.clamp(min=0)[:, None]).squeeze(1)
                 nll[r0:r1] = torch.where(valid, -lp, torch.zeros_like(lp))
         ctx.save_for_backward(h, w, labels)
         ctx.chunk_rows, ctx.ignore_index = chunk_rows, ignore_index
@@ -539,11 +640,14 @@ class _LinearTokenLogps(torch.autograd.Function):
                 hs = (hc.float() * sc).to(h.dtype)
                 sp = pick_splits(((V + 127) // 128) * ((H + 255) // 256), (r1 - r0 + 63) // 64) if h.is_cuda else 1
                 gemm(dlogits, hs, trans_a=True, trans_b=True, out=dw, accumulate=True, splits=sp)
-        return dh, (dw.to(w.dtype) if dw is not None else None), None, None, None
+        return dh, (dw.to(w.dtype) if dw is not None else None), None, None, None, None
 
 
-def linear_token_logps(hidden, lm_head_weight, labels, chunk_rows=2048, ignore_index=IGNORE_INDEX):
+def linear_token_logps(hidden, lm_head_weight, labels, chunk_rows=2048, ignore_index=IGNORE_INDEX,
+                       entropy_out=None):
     """log p(labels[t] | position t) for every row of ``hidden`` ([T] fp32; 0 where ignored).
-    ``labels`` must already be shifted."""
+    ``labels`` must already be shifted. ``entropy_out`` ([T] fp32, optional) receives the entropy of
+    every row's distribution (a logged quantity: no gradient)."""
     hidden = hidden.reshape(-1, hidden.shape[-1]).contiguous()
-    return _LinearTokenLogps.apply(hidden, lm_head_weight, labels.reshape(-1).contiguous(), chunk_rows, ignore_index)
+    return _LinearTokenLogps.apply(hidden, lm_head_weight, labels.reshape(-1).contiguous(), chunk_rows, ignore_index,
+                                   entropy_out)

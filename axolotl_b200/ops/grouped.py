@@ -321,7 +321,7 @@ def grouped_experts_padded(experts, x, lay):
     L = experts.lora if use_lora else None
     gu = _GroupedProj.apply(x, experts, "gate_up", lay, L["gate_up_A"] if L else None, L["gate_up_B"] if L else None,
                             float(experts.scaling))
-    h = Fn.glu(gu, experts.act)
+    h = Fn.glu(gu, experts.act, getattr(experts, "glu_limit", None))
     return _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
                               float(experts.scaling))
 

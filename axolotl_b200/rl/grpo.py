@@ -340,8 +340,9 @@ class GRPOObjective:
         if self.producer is not None and "old_logps" not in b and "_logps_attached" not in b:
             self.producer.attach_policy_logps(b)
             b["_logps_attached"] = True
-        tok, out = token_logps(model, b)
         lab = b["labels"].reshape(-1)
+        ent = torch.zeros(lab.numel(), dtype=torch.float32, device=lab.device)
+        tok, out = token_logps(model, b, entropy_out=ent)
         sid = b["seq_ids"].reshape(-1)
         mask = lab != -100
         if "keep_seq" in b:
@@ -354,6 +355,7 @@ class GRPOObjective:
         ga = b.get("ga_steps", 1)
         if out.aux_loss is not None and coef:
             loss = loss + (coef / ga) * out.aux_loss.to(loss.dtype)
+        m["entropy"] = (ent * mask).sum() / mask.sum().clamp(min=1)   # mean policy entropy of completion tokens
         self.last_metrics = {k: float(v) for k, v in m.items()}
         if self.producer is not None:
             self.last_metrics.update(self.producer.stats)

@@ -7,13 +7,14 @@ from ..models.layers import disable_adapters
 from ..ops.functional import linear_token_logps
 
 
-def token_logps(model, batch):
+def token_logps(model, batch, entropy_out=None):
     """Per-token log-probs [T] (0 at ignored positions) of ``batch['labels']`` (pre-shifted) and the
-    model output (for the MoE auxiliary loss)."""
+    model output (for the MoE auxiliary loss). ``entropy_out`` [T] fp32 receives per-token entropies."""
     out = model(batch["input_ids"], batch["position_ids"], attn_meta=batch["attn_meta"], return_logits=False)
     h = out.hidden_states.reshape(-1, out.hidden_states.shape[-1])
     lab = batch["labels"].reshape(-1)
-    return linear_token_logps(h, model.output_weight(), lab, chunk_rows=model.ce_chunk_rows), out
+    return linear_token_logps(h, model.output_weight(), lab, chunk_rows=model.ce_chunk_rows,
+                              entropy_out=entropy_out), out
 
 
 def segment_sum(values, seq_ids, n_seq):

@@ -487,3 +487,42 @@ def test_gemm_accumulate_single_pass_is_read_add_write(M, N, K):
     ref = ref + a.double().cpu().t() @ b.double().cpu()
     _check_status()
     assert _rel_err(acc.cpu(), ref.float()) < 2e-3
+
+
+@pytest.mark.gpu
+def test_clamped_glu_gated_rmsnorm_and_entropy_match_fp32_reference():
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    dev = "cuda"
+    # clamped SwiGLU
+    gu = (torch.randn(300, 2 * 256, device=dev) * 4).to(torch.bfloat16).requires_grad_(True)
+    dh = torch.randn(300, 256, device=dev).to(torch.bfloat16)
+    h = Fn.glu(gu, "silu", limit=3.0)
+    h.backward(dh)
+    g32 = gu.detach().float().requires_grad_(True)
+    g, u = g32[:, :256], g32[:, 256:]
+    ref = torch.nn.functional.silu(g.clamp(max=3.0)) * u.clamp(-3.0, 3.0)
+    ref.backward(dh.float())
+    assert torch.allclose(h.float(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(gu.grad.float(), g32.grad, atol=6e-2, rtol=3e-2)
+    # gated RMSNorm
+    x = torch.randn(257, 1024, device=dev).to(torch.bfloat16).requires_grad_(True)
+    gt = torch.randn(257, 1024, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(1024, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(257, 1024, device=dev).to(torch.bfloat16)
+    y = Fn.rmsnorm_gated(x, gt, w, 1e-6)
+    y.backward(dy)
+    xf, gf, wf = (t.detach().float().requires_grad_(True) for t in (x, gt, w))
+    yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf * torch.nn.functional.silu(gf)
+    yr.backward(dy.float())
+    assert torch.allclose(y.float(), yr, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=5e-2, rtol=3e-2)
+    assert torch.allclose(gt.grad.float(), gf.grad, atol=5e-2, rtol=3e-2)
+    assert torch.allclose(w.grad.float(), wf.grad, atol=0.5, rtol=3e-2)
+    # online entropy
+    for V in (1000, 32003):
+        z = (torch.randn(65, V, device=dev) * 3).to(torch.bfloat16)
+        ent, lse = Fn.token_entropy(z, temperature=0.7, return_lse=True)
+        lp = torch.log_softmax(z.float() / 0.7, -1)
+        assert torch.allclose(ent, -(lp.exp() * lp).sum(-1), atol=2e-3, rtol=1e-3)
+        assert torch.allclose(lse, torch.logsumexp(z.float() / 0.7, -1), atol=2e-3, rtol=1e-4)

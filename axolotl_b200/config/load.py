@@ -125,9 +125,10 @@ def load_cfg(config: str | dict, **overrides) -> DictDefault:
         pm = PluginManager.get_instance()
         for name in raw["plugins"]:
             pm.register(name)
-        # plugin-contributed keys are validated by the plugins themselves
+        # plugin-contributed keys are validated by the plugins' own pydantic models
         extra = pm.get_input_keys()
         plugin_vals = {k: raw.pop(k) for k in list(raw) if k in extra}
+        plugin_vals = pm.validate_input(plugin_vals)
     else:
         plugin_vals = {}
     cfg = validate_config(raw, gpu_capabilities())

@@ -53,6 +53,8 @@ _BUNDLED = {
     "spectrum": "axolotl_b200.plugins.spectrum.SpectrumPlugin",
     "lm_eval": "axolotl_b200.plugins.lm_eval.LMEvalPlugin",
     "kd": "axolotl_b200.plugins.kd.KDPlugin",
+    "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
+    "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
     "cut_cross_entropy": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
     "kernels": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -68,6 +70,8 @@ _ALIASES = {
     "axolotl.integrations.spectrum.SpectrumPlugin": "spectrum",
     "axolotl.integrations.lm_eval.LMEvalPlugin": "lm_eval",
     "axolotl.integrations.kd.KDPlugin": "kd",
+    "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
+    "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
 }
 
 
@@ -113,6 +117,19 @@ class PluginManager:
         for p in self.plugins.values():
             keys |= p.get_input_keys()
         return keys
+
+    def validate_input(self, values: dict) -> dict:
+        """Runs every plugin's args model over its own keys (type coercion, validators); keys the
+        user did not give stay absent."""
+        out = dict(values)
+        for p in self.plugins.values():
+            model = p.get_input_args()
+            if model is None:
+                continue
+            mine = {k: v for k, v in values.items() if k in model.model_fields}
+            checked = model(**mine).model_dump(exclude_unset=True)
+            out.update({k: checked[k] for k in mine if k in checked})
+        return out
 
     def _each(self, hook, *args, **kw):
         out = []

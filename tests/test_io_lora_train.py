@@ -508,3 +508,48 @@ def test_lisa_trains_only_sampled_layers(tmp_path):
         changed.append(d > 0)
     assert sum(changed) == 1, changed                      # exactly the sampled layer moved
     assert float((model.embed_tokens.detach() - ref.embed_tokens.detach()).abs().max()) > 0   # embeddings always train
+
+
+def test_sparse_finetuning_keeps_zero_pattern(tmp_path):
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.io import hf as hf_io
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.plugins.base import PluginManager
+    from axolotl_b200.plugins.sparse_ft import recipe_targets
+    from axolotl_b200.train.run import train
+
+    base = CausalLM(preset("tiny-llama"), dtype=torch.float32, device="cpu").init_weights(3)
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        for layer in base.layers:   # 2:4-like pruning of q_proj and down_proj; k/v/o/gate/up stay dense
+            q0, q1 = layer.self_attn.qkv_proj.row_range("q_proj")
+            w = layer.self_attn.qkv_proj.weight
+            w[q0:q1] *= (torch.rand(w[q0:q1].shape, generator=g) > 0.5)
+            d = layer.mlp.down_proj.weight
+            d *= (torch.rand(d.shape, generator=g) > 0.5)
+    hf_io.save_pretrained(base, str(tmp_path / "sparse"))
+    recipe = {"finetuning_stage": {"finetuning_modifiers": {"ConstantPruningModifier": {
+        "targets": ["re:.*q_proj.weight", "re:.*down_proj.weight"], "start": 0}}}}
+    assert recipe_targets(recipe) == ["re:.*q_proj.weight", "re:.*down_proj.weight"]
+    PluginManager.reset()
+    cfg = load_cfg({"base_model": str(tmp_path / "sparse"), "plugins": ["axolotl.integrations.llm_compressor.LLMCompressorPlugin"],
+                    "llmcompressor": {"recipe": recipe}, "sequence_len": 128, "micro_batch_size": 2,
+                    "gradient_accumulation_steps": 1, "max_steps": 3, "learning_rate": 1e-3, "optimizer": "adamw_torch",
+                    "lr_scheduler": "constant", "output_dir": str(tmp_path / "o"), "device": "cpu", "sample_packing": True,
+                    "save_strategy": "no", "weight_decay": 0.01,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
+                                  "max_length": 48, "max_input_id": 300}]})
+    model, _, _ = train(cfg)
+    PluginManager.reset()
+    for a, b in zip(model.layers, base.layers):
+        q0, q1 = a.self_attn.qkv_proj.row_range("q_proj")
+        wa, wb = a.self_attn.qkv_proj.weight.detach().float(), b.self_attn.qkv_proj.weight.detach().float()
+        zeros = wb[q0:q1] == 0
+        assert bool((wa[q0:q1][zeros] == 0).all())                  # pruned entries stayed zero
+        assert float((wa[q0:q1][~zeros] - wb[q0:q1][~zeros]).abs().max()) > 0   # the others trained
+        assert float((wa[q1:] - wb[q1:]).abs().max()) > 0           # k/v rows of the same fused weight are untouched by the mask
+        da, db = a.mlp.down_proj.weight.detach().float(), b.mlp.down_proj.weight.detach().float()
+        assert bool((da[db == 0] == 0).all())

@@ -67,10 +67,16 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
 
     # ---- adapters
     ad = g("adapter")
-    if ad in ("lora", "qlora"):
+    if ad == "mora":
+        if g("load_in_4bit") or g("load_in_8bit") or g("gptq"):
+            raise ValueError("adapter: mora currently requires a full-precision base model. "
+                             "Use adapter: lora or qlora for quantized training.")
+        if (g("tensor_parallel_size") or 1) > 1:
+            raise ValueError("adapter: mora cannot be combined with tensor parallelism")
+    if ad in ("lora", "qlora", "mora"):
         if not g("lora_r"):
             raise ValueError("`lora_r` is required with `adapter: lora`")
-        if g("lora_alpha") is None:
+        if g("lora_alpha") is None and ad != "mora":
             raise ValueError("`lora_alpha` is required with `adapter: lora`")
         if not (g("lora_target_modules") or g("lora_target_linear") or g("lora_target_parameters")):
             raise ValueError("no LoRA targets: set `lora_target_linear: true`, `lora_target_modules` or `lora_target_parameters`")

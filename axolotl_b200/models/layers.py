@@ -73,6 +73,10 @@ class FusedLinear(nn.Module):
         self.scaling = 1.0
         self.lora_dropout = 0.0
         self.merged = False
+        # MoRA state (absent until add_mora): one square matrix per adapted sub-projection
+        self.mora_M = None
+        self.mora_names = []
+        self.mora_kind = 0
 
     # ------------------------------------------------------------------ sub-projection views
     def row_range(self, name):
@@ -116,6 +120,49 @@ class FusedLinear(nn.Module):
         self.refresh_shadows()
         if use_dora:
             self.add_dora_()
+
+    # ------------------------------------------------------------------ MoRA
+    def add_mora(self, r, kind, targets=None, dtype=torch.float32):
+        """One zero-initialised square matrix of side ``sqrt((in + out) * r)`` per target."""
+        from .mora import mora_rank
+
+        targets = [n for n in self.names if targets is None or n in targets]
+        if not targets:
+            return
+        dev = self.weight.device
+        mult = 8 if dev.type == "cuda" else 2
+        mats = []
+        for n in targets:
+            r0, r1 = self.row_range(n)
+            rh = mora_rank(self.in_features, r1 - r0, r, mult)
+            mats.append(nn.Parameter(torch.zeros(rh, rh, dtype=dtype, device=dev)))
+        self.mora_M = nn.ParameterList(mats)
+        self.mora_names, self.mora_kind = targets, int(kind)
+
+    def _mora_update(self, x):
+        """[.., N] update of all sub-projections (zero columns for the ones without an adapter)."""
+        from .mora import mora_delta
+
+        parts, have = [], dict(zip(self.mora_names, self.mora_M))
+        for n, rows in zip(self.names, self.out_features):
+            if n in have:
+                parts.append(mora_delta(x, have[n], rows, self.mora_kind))
+            else:
+                parts.append(x.new_zeros(*x.shape[:-1], rows))
+        return parts[0] if len(parts) == 1 else torch.cat(parts, -1)
+
+    @torch.no_grad()
+    def merge_mora_(self):
+        from .mora import mora_dense_delta
+
+        if self.mora_M is None:
+            return
+        self.dequantize_()
+        for n, M in zip(self.mora_names, self.mora_M):
+            r0, r1 = self.row_range(n)
+            d = mora_dense_delta(M.detach(), self.in_features, r1 - r0, self.mora_kind)
+            self.weight[r0:r1] = (self.weight[r0:r1].float() + d).to(self.weight.dtype)
+            M.zero_()
 
     # ------------------------------------------------------------------ DoRA
     @torch.no_grad()
@@ -247,6 +294,8 @@ class FusedLinear(nn.Module):
             from ..ops.fake_quant import ste_weight
 
             return linear(x, ste_weight(self.weight, self.qat.get("weight_dtype"), self.qat.get("group_size")), self.bias)
+        if self.mora_M is not None and _ADAPTERS_ON:
+            return linear(x, self.weight, self.bias) + self._mora_update(x)
         if self.lora_A is None or self.merged or not _ADAPTERS_ON:
             return linear(x, self.weight, self.bias)
         if x.is_cuda and self.lora_A16 is None:

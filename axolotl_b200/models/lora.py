@@ -31,6 +31,8 @@ class LoraSpec:
     target_parameters: list | None = None          # e.g. ["mlp.experts.gate_up_proj", "mlp.experts.down_proj"]
     use_rslora: bool = False
     use_dora: bool = False
+    use_mora: bool = False
+    mora_type: int = 6                              # 1 = sharing, 6 = rope (the MoRA fork's numbering)
     fan_in_fan_out: bool = False
     bias: str = "none"
     modules_to_save: list | None = None
@@ -52,6 +54,7 @@ class LoraSpec:
             "target_modules": sorted(tm) if isinstance(tm, (list, tuple, set)) else tm,
             "target_parameters": self.target_parameters, "use_dora": self.use_dora,
             "use_rslora": self.use_rslora,
+            **({"use_mora": True, "mora_type": self.mora_type} if self.use_mora else {}),
         }
 
     @classmethod
@@ -109,7 +112,11 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
             for pat, av in spec.alpha_pattern.items():
                 if any(re.search(pat, _hf_path(name, s)) for s in targets):
                     alpha = av
-            if spec.use_dora:
+            if spec.use_mora:
+                if not isinstance(m, FusedLinear) or getattr(m.weight, "_axb_quant", None) is not None:
+                    raise NotImplementedError("MoRA needs full-precision, unsharded-by-TP base projections")
+                m.add_mora(r, spec.mora_type, targets, adapter_dtype)
+            elif spec.use_dora:
                 if not isinstance(m, FusedLinear):
                     raise NotImplementedError("DoRA cannot be combined with tensor parallelism")
                 m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype, use_dora=True)
@@ -160,6 +167,9 @@ def get_peft_state_dict(model) -> dict:
     """Adapter tensors in PEFT naming (contiguous CPU-safe copies are made by the writer)."""
     sd = {}
     for name, m in model.fused_linears():
+        if getattr(m, "mora_M", None) is not None:   # the MoRA fork keeps the square matrix under lora_A
+            for sub, M in zip(m.mora_names, m.mora_M):
+                sd[f"base_model.model.{_hf_path(name, sub)}.lora_A.weight"] = M.detach()
         if m.lora_A is None:
             continue
         tensors = m.gathered_peft_tensors() if hasattr(m, "gathered_peft_tensors") else m.peft_tensors()
@@ -187,6 +197,16 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
             .replace(".lora_magnitude_vector.default", ".lora_magnitude_vector"): v for k, v in sd.items()}
     used = set()
     for name, m in model.fused_linears():
+        if getattr(m, "mora_M", None) is not None:
+            for sub, M in zip(m.mora_names, m.mora_M):
+                k = f"base_model.model.{_hf_path(name, sub)}.lora_A.weight"
+                if k in norm:
+                    with torch.no_grad():
+                        M.copy_(norm[k])
+                    used.add(k)
+                    used.add(k.replace("lora_A", "lora_B")) if k.replace("lora_A", "lora_B") in norm else None
+                elif strict:
+                    raise KeyError(f"adapter tensor {k} is missing")
         if m.lora_A is None:
             continue
         for sub in m.lora_names:
@@ -247,6 +267,9 @@ def load_adapter(model, adapter_dir: str, strict: bool = True) -> LoraSpec:
 def merge_and_unload(model):
     """Folds every adapter into its base weight (W += s * B A) and removes the adapters."""
     for _, m in model.fused_linears():
+        if getattr(m, "mora_M", None) is not None:
+            m.merge_mora_()
+            m.mora_M, m.mora_names = None, []
         if m.lora_A is not None:
             m.merge_lora_()
             m.lora_A = m.lora_B = m.lora_A16 = m.lora_B16 = None

@@ -53,6 +53,7 @@ _BUNDLED = {
     "spectrum": "axolotl_b200.plugins.spectrum.SpectrumPlugin",
     "lm_eval": "axolotl_b200.plugins.lm_eval.LMEvalPlugin",
     "kd": "axolotl_b200.plugins.kd.KDPlugin",
+    "mora": "axolotl_b200.plugins.compat.MoraPlugin",
     "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
     "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -70,6 +71,7 @@ _ALIASES = {
     "axolotl.integrations.spectrum.SpectrumPlugin": "spectrum",
     "axolotl.integrations.lm_eval.LMEvalPlugin": "lm_eval",
     "axolotl.integrations.kd.KDPlugin": "kd",
+    "axolotl.integrations.mora.MoraPlugin": "mora",
     "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
     "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
 }

@@ -35,3 +35,27 @@ class ExpertParallelArgs(BaseModel):
 class ExpertParallelPlugin(BasePlugin):
     def get_input_args(self):
         return ExpertParallelArgs
+
+
+class MoraBlock(BaseModel):
+    use_mora: bool = True
+    mora_type: str | int = "rope"      # `sharing` (1) or `rope` (6)
+
+
+class MoraArgs(BaseModel):
+    mora: MoraBlock | None = None
+
+
+class MoraPlugin(BasePlugin):
+    """Enables the nested ``mora:`` block for ``adapter: mora`` (reference:
+    src/axolotl/integrations/mora/plugin.py:44-97). The operators themselves are part of the model
+    (``models/mora.py``); no PEFT fork is involved."""
+
+    def get_input_args(self):
+        return MoraArgs
+
+    def pre_model_load(self, cfg):
+        if cfg.get("adapter") == "mora":
+            from ..models.mora import mora_type_id
+
+            mora_type_id((cfg.get("mora") or {}).get("mora_type", "rope"))   # raises on an unknown variant

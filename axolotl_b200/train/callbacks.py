@@ -320,6 +320,9 @@ class ReLoRACallback(Callback):
         touched = []
         with torch.no_grad():
             for _, m in model.fused_linears():
+                if getattr(m, "mora_M", None) is not None:   # ReMoRA: fold the square matrices in, restart at zero
+                    m.merge_mora_()
+                    touched += list(m.mora_M)
                 if getattr(m, "lora_A", None) is None or getattr(m.weight, "_axb_quant", None) is not None:
                     continue
                 if getattr(m.weight, "_axb_shard", None) is not None or getattr(m, "tp", None) is not None:

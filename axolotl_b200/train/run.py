@@ -71,18 +71,29 @@ def build_model(cfg, device) -> CausalLM:
     return model
 
 
+def _mora_type(v):
+    from ..models.mora import mora_type_id
+
+    return mora_type_id(v)
+
+
 def lora_spec_from_cfg(cfg) -> LoraSpec | None:
-    if cfg.get("adapter") not in ("lora", "qlora"):
+    if cfg.get("adapter") not in ("lora", "qlora", "mora"):
         return None
+    mora = cfg.get("mora") or {}
+    use_mora = cfg.get("adapter") == "mora"
+    if use_mora and mora.get("use_mora") is False:
+        raise ValueError("mora.use_mora must be true when adapter: mora is set")
     tm = cfg.get("lora_target_modules")
     if cfg.get("lora_target_linear"):
         tm = sorted(set(ALL_LINEAR) | set(tm or [])) if not isinstance(tm, str) else tm
     tp = cfg.get("lora_target_parameters")
     if isinstance(tp, str):
         tp = [tp]
-    return LoraSpec(r=cfg["lora_r"], lora_alpha=cfg["lora_alpha"], lora_dropout=cfg.get("lora_dropout") or 0.0,
+    return LoraSpec(r=cfg["lora_r"], lora_alpha=cfg.get("lora_alpha") or cfg["lora_r"], lora_dropout=cfg.get("lora_dropout") or 0.0,
                     target_modules=tm, target_parameters=tp, use_rslora=bool(cfg.get("peft_use_rslora")),
-                    use_dora=bool(cfg.get("peft_use_dora")), modules_to_save=cfg.get("lora_modules_to_save"),
+                    use_dora=bool(cfg.get("peft_use_dora")), use_mora=use_mora,
+                    mora_type=_mora_type(mora.get("mora_type", "rope")) if use_mora else 6, modules_to_save=cfg.get("lora_modules_to_save"),
                     rank_pattern=cfg.get("lora_rank_pattern") or {}, alpha_pattern=cfg.get("lora_alpha_pattern") or {},
                     layers_to_transform=cfg.get("peft_layers_to_transform"),
                     base_model_name_or_path=cfg.get("base_model"))

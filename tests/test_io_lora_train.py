@@ -553,3 +553,60 @@ def test_sparse_finetuning_keeps_zero_pattern(tmp_path):
         assert float((wa[q1:] - wb[q1:]).abs().max()) > 0           # k/v rows of the same fused weight are untouched by the mask
         da, db = a.mlp.down_proj.weight.detach().float(), b.mlp.down_proj.weight.detach().float()
         assert bool((da[db == 0] == 0).all())
+
+
+def test_mora_operators_training_save_and_merge(tmp_path):
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.models.mora import ROPE, SHARING, mora_delta, mora_dense_delta, mora_rank
+    from axolotl_b200.plugins.base import PluginManager
+    from axolotl_b200.train.run import train
+
+    # operators against a direct transcription of their definition
+    torch.manual_seed(0)
+    in_f, out_f, r = 96, 160, 4
+    rh = mora_rank(in_f, out_f, r)
+    assert rh == 32 and rh * rh <= (in_f + out_f) * r + rh
+    M = torch.randn(rh, rh)
+    x = torch.randn(5, in_f)
+    # sharing: sum of chunks -> M -> tiled
+    ref = torch.cat([(x.reshape(5, 3, rh).sum(1) @ M.t())] * 5, -1)[:, :out_f]
+    assert torch.allclose(mora_delta(x, M, out_f, SHARING), ref, atol=1e-5)
+    # rope: linear in x, so it must equal its own dense form; chunks are distinguishable
+    W = mora_dense_delta(M, in_f, out_f, ROPE)
+    assert W.shape == (out_f, in_f)
+    assert torch.allclose(mora_delta(x, M, out_f, ROPE), x @ W.t(), atol=1e-4)
+    x2 = x.clone()
+    x2[:, :rh], x2[:, rh:2 * rh] = x[:, rh:2 * rh], x[:, :rh]
+    assert not torch.allclose(mora_delta(x2, M, out_f, ROPE)[:, :rh], mora_delta(x, M, out_f, ROPE)[:, rh:2 * rh], atol=1e-3)
+
+    PluginManager.reset()
+    cfg = load_cfg({"model_preset": "tiny-llama", "plugins": ["axolotl.integrations.mora.MoraPlugin"], "adapter": "mora",
+                    "mora": {"use_mora": True, "mora_type": "rope"}, "lora_r": 8, "lora_target_modules": ["q_proj", "down_proj"],
+                    "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1, "max_steps": 6,
+                    "learning_rate": 5e-3, "optimizer": "adamw_torch", "lr_scheduler": "constant", "logging_steps": 1,
+                    "output_dir": str(tmp_path / "m"), "device": "cpu", "sample_packing": True,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
+                                  "max_length": 48, "max_input_id": 300}]})
+    model, _, trainer = train(cfg)
+    PluginManager.reset()
+    losses = [l["loss"] for l in trainer.log_history if "loss" in l]
+    assert losses[-1] < losses[0]
+    trainable = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert trainable and all("mora_M" in n for n in trainable)
+    import json
+    from axolotl_b200.io.safetensors_io import load_file
+    from axolotl_b200.models.lora import merge_and_unload
+    sd = load_file(str(tmp_path / "m" / "adapter_model.safetensors"))
+    k = "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight"
+    assert k in sd and sd[k].shape[0] == sd[k].shape[1] and float(sd[k].abs().max()) > 0
+    assert json.load(open(tmp_path / "m" / "adapter_config.json"))["use_mora"] is True
+    ids = torch.randint(3, 300, (1, 40))
+    pos = torch.arange(40, dtype=torch.int32)[None]
+    model.eval()
+    with torch.no_grad():
+        before = model(ids, pos, return_logits=True).logits
+        merge_and_unload(model)
+        after = model(ids, pos, return_logits=True).logits
+    assert torch.allclose(before, after, atol=2e-3, rtol=1e-3)

@@ -91,12 +91,31 @@ class SinkGD(torch.optim.Optimizer):
             x = x / (x.norm(dim=0, keepdim=True) + eps) * (m ** 0.5)
         return x
 
+    def _fused_step(self, p, grp):
+        """Scale-vector formulation on the device: the sweeps only update a [m] and b [n]; the
+        matrix is read once per half-sweep and written once by the final update."""
+        from ..ops import _lib
+
+        m, n = p.shape
+        st = self.state[p]
+        if "sink_a" not in st:
+            st["sink_a"] = torch.empty(m, dtype=torch.float32, device=p.device)
+            st["sink_b"] = torch.empty(n, dtype=torch.float32, device=p.device)
+        _lib.check_rc(_lib.cuda_lib().axb_sinkgd_step(
+            p.data_ptr(), 0 if p.dtype == torch.float32 else 1, p.grad.data_ptr(), st["sink_a"].data_ptr(),
+            st["sink_b"].data_ptr(), m, n, int(grp["n_iters"]), float(grp["lr"]), float(grp["weight_decay"]),
+            float(grp["sink_eps"]), _lib.stream_ptr()), "sinkgd_step")
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
         for grp in self.param_groups:
             for p in grp["params"]:
                 if p.grad is None:
+                    continue
+                if (p.is_cuda and p.dim() == 2 and min(p.shape) > 1 and p.grad.dtype == torch.float32
+                        and p.grad.is_contiguous() and p.is_contiguous() and p.dtype in (torch.float32, torch.bfloat16)):
+                    self._fused_step(p, grp)
                     continue
                 if grp["weight_decay"]:
                     p.mul_(1 - grp["lr"] * grp["weight_decay"])

@@ -526,3 +526,17 @@ def test_clamped_glu_gated_rmsnorm_and_entropy_match_fp32_reference():
         lp = torch.log_softmax(z.float() / 0.7, -1)
         assert torch.allclose(ent, -(lp.exp() * lp).sum(-1), atol=2e-3, rtol=1e-3)
         assert torch.allclose(lse, torch.logsumexp(z.float() / 0.7, -1), atol=2e-3, rtol=1e-4)
+
+
+@pytest.mark.gpu
+def test_sinkgd_fused_step_matches_elementwise_definition():
+    from axolotl_b200.train.optimizers_extra import SinkGD
+    torch.manual_seed(0)
+    for shape, dt in (((96, 256), torch.float32), ((130, 77), torch.float32), ((512, 64), torch.bfloat16)):
+        p = torch.nn.Parameter(torch.randn(shape, device="cuda").to(dt))
+        g = torch.randn(shape, device="cuda")
+        p.grad = g.clone()
+        ref = p.detach().float() * (1 - 0.1 * 0.01) - 0.1 * SinkGD.sinkhorn_normalize(g, 5, 1e-8)
+        SinkGD([p], lr=0.1, n_iters=5, weight_decay=0.01).step()
+        tol = 1e-4 if dt == torch.float32 else 2e-2
+        assert torch.allclose(p.detach().float(), ref, atol=tol, rtol=tol), (p.detach().float() - ref).abs().max()

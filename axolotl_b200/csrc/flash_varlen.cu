@@ -1,4 +1,5 @@
-// Packed variable-length causal flash attention for sm_100a (forward + backward), GQA aware.
+// Packed variable-length flash attention for sm_100a (forward + backward), GQA aware: causal
+// inside each document, or bidirectional for documents whose tiles carry flag bit 0.
 //
 // Layout: tokens of all documents of a packed row are concatenated: q/k/v live in one fused
 // projection buffer [T, (Hq + 2*Hk) * D] (bf16), documents are delimited by a host-built tile
@@ -18,7 +19,7 @@ constexpr int kThreads = 192;
 constexpr int HALF_BYTES = 128 * 128;  // 128 rows x 128 B (64 bf16) swizzled tile
 
 struct AttnParams {
-  const int4* tiles;  // (doc_start, doc_len, tile_start (doc relative), unused)
+  const int4* tiles;  // (doc_start, doc_len, tile_start (doc relative), flags: bit 0 = bidirectional)
   int n_tiles;
   int Hq, Hk;
   int q_col0, k_col0, v_col0;  // element offsets of the q / k / v blocks inside a fused row
@@ -85,7 +86,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kv_head = head / (p.Hq / p.Hk);
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, q0 = ti.z;
-  const int kv_end = min(q0 + 128, doc_len);
+  const bool bidir = ti.w & 1;  // every token of the document sees the whole document
+  const int kv_end = bidir ? doc_len : min(q0 + 128, doc_len);
   const int n_blocks = (kv_end + 127) / 128;
 
   extern __shared__ uint8_t smem_raw[];
@@ -226,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t s_addr = tmem_base + lane_off + C::S_COL + st * 128;
       const bool need_mask = (j == n_blocks - 1);
       const int kv0 = j * 128;
-      const int lim = min(q_idx, doc_len - 1) - kv0;  // columns <= lim are visible
+      const int lim = (bidir ? doc_len - 1 : min(q_idx, doc_len - 1)) - kv0;  // columns <= lim are visible
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
@@ -413,8 +415,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int head0 = kv_head * group_all + part * group;  // first of them
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, kv0 = ti.z;
-  // 64-row q tiles at or below the diagonal that intersect this rank's q rows
-  int q_first = kv0 / 64;
+  const bool bidir = ti.w & 1;
+  // 64-row q tiles at or below the diagonal (all of the document's when it is bidirectional)
+  // that intersect this rank's q rows
+  int q_first = bidir ? 0 : kv0 / 64;
   int q_last = (doc_len + 63) / 64;
   {
     const int lo = p.q_row_off - doc_start, hi = p.q_row_off + p.q_rows - doc_start;
@@ -612,7 +616,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tc_fence_after();
       // Only tiles that touch the diagonal or the end of the document need per-element masks
       // (q rows outside the document already carry nlse = -inf, i.e. P = 0).
-      const bool need_mask = (qt0 < kv0 + 127) || (kv0 + 128 > doc_len);
+      const bool need_mask = (!bidir && qt0 < kv0 + 127) || (kv0 + 128 > doc_len);
       const bool row_in_doc = kv_idx < doc_len;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -633,7 +637,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             float pr = fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.sl2, nlv[e]));
             if (need_mask) {
               const int q = qt0 + c * 32 + i + e;
-              if (!(row_in_doc && q >= kv_idx)) pr = 0.f;
+              if (!(row_in_doc && (bidir || q >= kv_idx))) pr = 0.f;
             }
             pv[e] = pr;
             dv[e] = pr * fmaf(__uint_as_float(dr[i + e]), p.scale, -dsv[e]);

@@ -310,7 +310,7 @@ class CausalLM(nn.Module):
                 m.refresh_expert_shadows()
 
 
-def build_attn_meta(position_ids, device) -> Fn.AttnMeta:
+def build_attn_meta(position_ids, device, causal=True) -> Fn.AttnMeta:
     """cu_seqlens from position-id resets, with a forced boundary at every row start."""
     p = position_ids.detach().cpu().numpy() if isinstance(position_ids, torch.Tensor) else np.asarray(position_ids)
     if p.ndim == 1:
@@ -321,4 +321,4 @@ def build_attn_meta(position_ids, device) -> Fn.AttnMeta:
     is_start[np.arange(B) * S] = True
     starts = np.flatnonzero(is_start)
     cu = np.concatenate([starts, [B * S]]).astype(np.int32)
-    return Fn.AttnMeta(cu, device)
+    return Fn.AttnMeta(cu, device, causal)

@@ -377,9 +377,10 @@ class AttnMeta:
     reused by every layer's forward and backward.
     """
 
-    def __init__(self, cu_seqlens, device):
+    def __init__(self, cu_seqlens, device, causal=True):
         cu = np.asarray(cu_seqlens, dtype=np.int32)
         self.cu_seqlens_host = cu
+        self.causal = bool(causal)   # False: every token attends to its whole document
         self.n_docs = len(cu) - 1
         self.total = int(cu[-1])
         self.max_len = int((cu[1:] - cu[:-1]).max()) if self.n_docs else 0
@@ -395,6 +396,8 @@ class AttnMeta:
                 buf = np.zeros((max_tiles, 4), dtype=np.int32)
                 n = host.axb_build_attn_tiles(cu.ctypes.data, self.n_docs, 128, heavy_first,
                                               buf.ctypes.data, max_tiles)
+                if not self.causal:
+                    buf[:n, 3] |= 1    # tile flag bit 0: bidirectional document
                 bufs.append(buf[:n])
             self.n_tiles = len(bufs[0])
             both = torch.from_numpy(np.concatenate(bufs, 0)).pin_memory()
@@ -402,18 +405,18 @@ class AttnMeta:
             self.tiles_fwd, self.tiles_bwd = both[: self.n_tiles], both[self.n_tiles:]
 
     @staticmethod
-    def from_position_ids(position_ids, device):
+    def from_position_ids(position_ids, device, causal=True):
         """Document starts are the positions where ``position_ids`` resets to 0."""
         p = position_ids.reshape(-1).cpu().numpy()
         starts = np.flatnonzero(p == 0)
         if len(starts) == 0 or starts[0] != 0:
             starts = np.concatenate([[0], starts])
         cu = np.concatenate([starts, [len(p)]]).astype(np.int32)
-        return AttnMeta(cu, device)
+        return AttnMeta(cu, device, causal)
 
 
-def _attn_ref(q, k, v, cu, scale):
-    # q [T,Hq,D], k/v [T,Hk,D]; per-document causal attention in fp32
+def _attn_ref(q, k, v, cu, scale, causal=True):
+    # q [T,Hq,D], k/v [T,Hk,D]; per-document (causal or bidirectional) attention in fp32
     T, Hq, D = q.shape
     Hk = k.shape[1]
     rep = Hq // Hk
@@ -424,8 +427,9 @@ def _attn_ref(q, k, v, cu, scale):
         kk = k[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
         vv = v[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
         sc = (qq @ kk.transpose(1, 2)) * scale
-        mask = torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril()
-        sc = sc.masked_fill(~mask, float("-inf"))
+        if causal:
+            mask = torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril()
+            sc = sc.masked_fill(~mask, float("-inf"))
         out[s:e] = (sc.softmax(-1) @ vv).transpose(0, 1).to(q.dtype)
     return out
 
@@ -472,14 +476,15 @@ class _FlashVarlen(torch.autograd.Function):
 
 
 def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
-    """Causal attention inside each document of a packed row.
+    """Attention inside each document of a packed row: causal, or bidirectional when the
+    metadata was built with ``causal=False`` (masked-diffusion and encoder-style objectives).
 
     ``qkv`` is the fused projection [T, (Hq + 2*Hk) * D] (q heads, then k heads, then v heads).
     Returns [T, Hq * D].
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     if getattr(meta, "cp", False):
-        from ..parallel.cp import flash_varlen_cp
+        from ..parallel.cp import flash_varlen_cp   # context parallelism is causal only
 
         return flash_varlen_cp(qkv, meta, Hq, Hk, D, scale)
     if qkv.is_cuda:
@@ -488,7 +493,7 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     q = qkv[:, : Hq * D].reshape(T, Hq, D)
     k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
     v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, D)
-    return _attn_ref(q, k, v, meta.cu_seqlens_host, scale).reshape(T, Hq * D)
+    return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True)).reshape(T, Hq * D)
 
 
 # --------------------------------------------------------------------------------------- loss

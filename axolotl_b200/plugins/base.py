@@ -54,6 +54,7 @@ _BUNDLED = {
     "lm_eval": "axolotl_b200.plugins.lm_eval.LMEvalPlugin",
     "kd": "axolotl_b200.plugins.kd.KDPlugin",
     "mora": "axolotl_b200.plugins.compat.MoraPlugin",
+    "diffusion": "axolotl_b200.plugins.diffusion.DiffusionPlugin",
     "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
     "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -72,6 +73,7 @@ _ALIASES = {
     "axolotl.integrations.lm_eval.LMEvalPlugin": "lm_eval",
     "axolotl.integrations.kd.KDPlugin": "kd",
     "axolotl.integrations.mora.MoraPlugin": "mora",
+    "axolotl.integrations.diffusion.DiffusionPlugin": "diffusion",
     "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
     "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
 }

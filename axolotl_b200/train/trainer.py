@@ -87,12 +87,13 @@ def to_device_batch(batch: dict, device, pin=True):
     if "cp_meta_args" in batch:
         out["attn_meta"] = None   # built by the context-parallel runtime
         return out
+    causal = not batch.get("bidirectional", False)
     if cu is None:
         from ..models.transformer import build_attn_meta
 
-        out["attn_meta"] = build_attn_meta(batch["position_ids"], device)
+        out["attn_meta"] = build_attn_meta(batch["position_ids"], device, causal)
     else:
-        out["attn_meta"] = Fn.AttnMeta(cu, device)
+        out["attn_meta"] = Fn.AttnMeta(cu, device, causal)
     return out
 
 

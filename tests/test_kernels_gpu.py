@@ -540,3 +540,29 @@ def test_sinkgd_fused_step_matches_elementwise_definition():
         SinkGD([p], lr=0.1, n_iters=5, weight_decay=0.01).step()
         tol = 1e-4 if dt == torch.float32 else 2e-2
         assert torch.allclose(p.detach().float(), ref, atol=tol, rtol=tol), (p.detach().float() - ref).abs().max()
+
+
+@pytest.mark.gpu
+def test_flash_varlen_bidirectional_documents_match_fp32_reference():
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    Hq, Hk, D = 8, 2, 128
+    cu = [0, 200, 329, 1000, 1024]
+    T = cu[-1]
+    qkv = (torch.randn(T, (Hq + 2 * Hk) * D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    dout = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+    meta = Fn.AttnMeta(cu, "cuda", causal=False)
+    out = Fn.flash_varlen(qkv, meta, Hq, Hk, D)
+    out.backward(dout)
+    x = qkv.detach().float().requires_grad_(True)
+    q = x[:, :Hq * D].reshape(T, Hq, D)
+    k = x[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D)
+    v = x[:, (Hq + Hk) * D:].reshape(T, Hk, D)
+    ref = Fn._attn_ref(q, k, v, cu, 1.0 / D ** 0.5, causal=False).reshape(T, Hq * D)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), (out.float() - ref).abs().max()
+    err = (qkv.grad.float() - x.grad).abs().max() / x.grad.abs().max()
+    assert err < 3e-2, err
+    # and it differs from the causal result (the flag is honoured)
+    causal = Fn.flash_varlen(qkv.detach(), Fn.AttnMeta(cu, "cuda"), Hq, Hk, D)
+    assert (causal.float() - out.float()).abs().max() > 0.05

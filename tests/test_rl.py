@@ -334,3 +334,43 @@ def test_kd_plugin_loss_matches_definition_and_learns(tmp_path):
     PluginManager.reset()
     logs = [l for l in trainer.log_history if "kd_loss" in l]
     assert logs and logs[-1]["kd_loss"] < logs[0]["kd_loss"]
+
+
+def test_diffusion_plugin_noising_loss_and_generation(tmp_path):
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.ops import functional as Fn
+    from axolotl_b200.plugins.base import PluginManager
+    from axolotl_b200.plugins.diffusion import forward_process, generate
+    from axolotl_b200.train.run import train
+
+    # noising: only trainable, non-first, non-special tokens are masked; rate follows each document's t
+    cu = torch.tensor([0, 400, 1000], dtype=torch.int32)
+    ids = torch.randint(5, 200, (1, 1000))
+    lab = ids.clone()
+    lab[0, :100] = -100
+    g = torch.Generator().manual_seed(1)
+    noisy, masked, p_tok, doc = forward_process(ids, lab, cu, 299, 1e-3, special_ids=(7,), generator=g)
+    assert not masked[:100].any() and not masked[400] and not (masked & (ids.reshape(-1) == 7)).any()
+    assert bool((noisy.reshape(-1)[masked] == 299).all()) and bool((noisy.reshape(-1)[~masked] == ids.reshape(-1)[~masked]).all())
+    for d, (s, e) in enumerate(((100, 400), (401, 1000))):
+        rate = masked[s:e].float().mean().item()
+        assert abs(rate - float(p_tok[s])) < 0.12, (d, rate, float(p_tok[s]))
+
+    PluginManager.reset()
+    cfg = load_cfg({"model_preset": "tiny-llama", "plugins": ["axolotl.integrations.diffusion.DiffusionPlugin"],
+                    "diffusion": {"mask_token_id": 511, "generate_samples": False}, "sequence_len": 128,
+                    "micro_batch_size": 2, "gradient_accumulation_steps": 1, "max_steps": 30, "learning_rate": 3e-3,
+                    "optimizer": "adamw_torch", "lr_scheduler": "constant", "logging_steps": 1, "save_strategy": "no",
+                    "output_dir": str(tmp_path / "d"), "device": "cpu", "sample_packing": True,
+                    "num_epochs": 8, "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 40, "min_length": 24,
+                                  "max_length": 48, "max_input_id": 300}]})
+    model, _, trainer = train(cfg)
+    PluginManager.reset()
+    logs = [l for l in trainer.log_history if "ce_loss" in l]
+    assert logs and "mask_ratio" in logs[0]
+    first, last = sum(l["ce_loss"] for l in logs[:5]) / 5, sum(l["ce_loss"] for l in logs[-5:]) / 5
+    assert last < first, (first, last)
+    out = generate(model, torch.tensor([1, 5, 9, 12]), 12, 511, steps=4)
+    assert out.shape == (16,) and not bool((out == 511).any()) and out[:4].tolist() == [1, 5, 9, 12]

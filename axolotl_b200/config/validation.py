@@ -175,7 +175,14 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
     if rl and rl not in ("dpo", "ipo", "orpo", "kto", "simpo", "grpo", "gdpo", "ebft"):
         raise ValueError(f"unknown rl method '{rl}'")
     if rl == "ebft":
-        raise ValueError("rl: ebft (energy-based fine-tuning) is not available in this build")
+        eb = g("ebft")
+        if not eb:
+            raise ValueError("`ebft` config section is required when `rl: ebft` is set. "
+                             "Add an `ebft:` section with at least `mode: structured`.")
+        if (eb.get("mode") or "structured") != "structured":
+            raise ValueError("ebft.mode: strided (anchors inside unstructured text) is not available; use mode: structured")
+        if eb.get("embed_method") not in (None, "last_token", "mean_pooling", "completion_mean", "concat"):
+            raise ValueError(f"unknown ebft.embed_method '{eb.get('embed_method')}'")
     if rl in ("grpo", "gdpo") and not (g("trl") or {}).get("reward_funcs"):
         raise ValueError(f"rl: {rl} needs trl.reward_funcs (dotted paths of reward functions)")
     if rl and g("sample_packing"):

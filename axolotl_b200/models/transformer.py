@@ -33,6 +33,7 @@ class CausalLMOutput:
     hidden_states: torch.Tensor | None = None
     aux_loss: torch.Tensor | None = None
     num_items: int = 0
+    captured: dict | None = None
 
 
 class Attention(nn.Module):
@@ -198,7 +199,7 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids, position_ids=None, labels=None, attn_meta=None, num_items=None,
-                return_logits=None, shift_labels=True, aux_scale=1.0):
+                return_logits=None, shift_labels=True, aux_scale=1.0, capture_hidden=None):
         """input_ids / position_ids / labels: [B, S] (or [T]). Returns CausalLMOutput.
 
         ``labels`` follow the HF convention (unshifted; the model shifts by one inside each row)
@@ -208,6 +209,8 @@ class CausalLM(nn.Module):
         labels returns just the final hidden states, for objectives that score tokens themselves).
         ``aux_scale`` weights the router load-balance term (1 / accumulation steps, so that the
         term is a mean over micro-batches just as the token loss is a mean over tokens).
+        ``capture_hidden``: indices in the HF ``hidden_states`` numbering (0 = embeddings, i = residual
+        stream after layer i, last = after the final norm) returned as ``out.captured[i]`` [T, H].
         """
         cfg = self.config
         if input_ids.dim() == 1:
@@ -228,6 +231,9 @@ class CausalLM(nn.Module):
             h = h + (torch.rand_like(h) * 2 - 1) * mag
         residual = None
         aux_total = None
+        captured = {} if capture_hidden is not None else None
+        if captured is not None and 0 in capture_hidden:
+            captured[0] = h
         hooks = self.hooks
         nvtx = self.nvtx and h.is_cuda
         for i, layer in enumerate(self.layers):
@@ -242,12 +248,18 @@ class CausalLM(nn.Module):
                 h, residual, aux = layer(h, residual, pos, self.inv_freq, self.attn_scale, attn_meta)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
+            if captured is not None and (i + 1) in capture_hidden and i + 1 < len(self.layers):
+                captured[i + 1] = h if residual is None else h + residual
             if hooks is not None:
                 hooks.post_layer(i)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         h, _ = self.norm(h, residual)
         out = CausalLMOutput(hidden_states=h.view(B, S, -1))
+        if captured is not None:
+            if len(self.layers) in capture_hidden:
+                captured[len(self.layers)] = h
+            out.captured = captured
         if aux_total is not None:
             out.aux_loss = aux_total / max(sum(l.is_moe for l in self.layers), 1)
         W = self.output_weight()

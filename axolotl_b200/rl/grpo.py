@@ -218,7 +218,7 @@ class RolloutProducer:
         per_fn = []
         for f in self.rf:
             v = f(prompts=[r.get("prompt", r["prompt_ids"]) for r in prompts_rep], completions=texts,
-                  completion_ids=completions, **cols)
+                  completion_ids=completions, prompt_ids=[r["prompt_ids"] for r in prompts_rep], **cols)
             per_fn.append(torch.tensor([float(x) if x is not None else float("nan") for x in v]))
         R = torch.stack(per_fn, 1)                                    # [N, F]
         w = torch.tensor(self.s.reward_weights or [1.0] * len(self.rf))
@@ -250,6 +250,8 @@ class RolloutProducer:
             groups.append(grp)
         self.stats = {"reward": float(total.mean()), "reward_std": float(total.std()) if len(total) > 1 else 0.0,
                       "completion_length": float(np.mean([len(c) for c in completions]))}
+        for f in self.rf:   # model-based rewards report their own breakdown
+            self.stats.update(getattr(f, "last_metrics", None) or {})
         return self.collate(groups)
 
     def collate(self, groups):

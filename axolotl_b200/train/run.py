@@ -255,7 +255,7 @@ def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_siz
     pad = cfg.get("pad_token_id") or 0
     seed = cfg.get("seed") or 42
     mbs = cfg["micro_batch_size"]
-    if rl in ("grpo", "gdpo"):
+    if rl in ("grpo", "gdpo", "ebft"):
         from ..rl import grpo as G
 
         st = G.GRPOSettings(cfg)
@@ -267,7 +267,14 @@ def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_siz
         else:
             engine = G.LocalRollout(model, eos, pad, seed + dp_rank)
         records = G.load_prompt_records(cfg, tokenizer)
-        producer = G.RolloutProducer(model, engine, G.load_reward_funcs((cfg.get("trl") or {}).get("reward_funcs")),
+        extra = (cfg.get("trl") or {}).get("reward_funcs") or []
+        reward_funcs = G.load_reward_funcs(extra) if (extra or rl != "ebft") else []
+        if rl == "ebft":   # feature-matching reward from the frozen policy (adapters off, or a frozen copy)
+            from ..rl.ebft import FeatureMatchingReward
+
+            frozen = copy.deepcopy(model).requires_grad_(False) if spec is None else None
+            reward_funcs = [FeatureMatchingReward(model, tokenizer, cfg.get("ebft"), st.num_generations, frozen)] + reward_funcs
+        producer = G.RolloutProducer(model, engine, reward_funcs,
                                      st, records, mbs, tokenizer, pad, eos, dp_rank, dp_size, seed)
         return producer, G.GRPOObjective(st, producer), len(producer) * st.num_iterations
     from ..rl.data import PreferenceBatches, load_preference_dataset

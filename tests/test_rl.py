@@ -374,3 +374,56 @@ def test_diffusion_plugin_noising_loss_and_generation(tmp_path):
     assert last < first, (first, last)
     out = generate(model, torch.tensor([1, 5, 9, 12]), 12, 511, steps=4)
     assert out.shape == (16,) and not bool((out == 511).any()) and out[:4].tolist() == [1, 5, 9, 12]
+
+
+def test_ebft_feature_rewards_and_training_raises_alignment():
+    from axolotl_b200.rl import grpo as G
+    from axolotl_b200.rl.ebft import FeatureMatchingReward, feature_rewards, pool_features
+
+    # reward arithmetic against the definition
+    torch.manual_seed(0)
+    gen, gt = torch.randn(6, 16), torch.randn(2, 16)
+    r, m = feature_rewards(gen, gt, 3, alignment_coef=1.0, diversity_coef=0.5)
+    gn, tn = torch.nn.functional.normalize(gen, dim=-1), torch.nn.functional.normalize(gt, dim=-1)
+    want0 = 2 * (gn[0] @ tn[0]) - 0.5 * 2 * ((gn[0] @ gn[1]) + (gn[0] @ gn[2])) / 2
+    assert abs(float(r[0]) - float(want0)) < 1e-5 and set(m) >= {"ebft/alignment", "ebft/diversity", "ebft/cfm_loss"}
+    rw, _ = feature_rewards(gen, gt, 3, use_whitening=True)
+    assert rw.shape == (6,) and torch.isfinite(rw).all()
+    h = torch.arange(40, dtype=torch.float32).reshape(10, 4)
+    assert torch.equal(pool_features(h, "last_token", 3), h[-1])
+    assert torch.allclose(pool_features(h, "completion_mean", 6), h[6:].mean(0))
+    assert pool_features(h, "concat", 0).shape == (12,) and torch.equal(pool_features(h, "concat", 0)[:4], h[2])
+
+    # the hidden states captured for the reward follow the HF numbering
+    cfg = preset("tiny-llama", num_hidden_layers=4, vocab_size=64, hidden_size=64, intermediate_size=128,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    model = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(0)
+    ids = torch.randint(3, 60, (1, 12))
+    out = model(ids, return_logits=False, capture_hidden=[0, 2, 4])
+    assert set(out.captured) == {0, 2, 4} and torch.equal(out.captured[4].reshape(-1), out.hidden_states.reshape(-1))
+    two = CausalLM(preset("tiny-llama", num_hidden_layers=2, vocab_size=64, hidden_size=64, intermediate_size=128,
+                          num_attention_heads=4, num_key_value_heads=2, head_dim=16), dtype=torch.float32, device="cpu")
+    two.load_state_dict({k: v for k, v in model.state_dict().items() if k in two.state_dict()}, strict=False)
+    h2 = two(ids, return_logits=False, capture_hidden=[2]).captured[2]      # after the final norm of the 2-layer model
+    mid = out.captured[2]
+    normed = mid * torch.rsqrt(mid.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * two.norm.weight
+    assert torch.allclose(h2.reshape(-1, 64), normed.reshape(-1, 64), atol=1e-4)
+
+    # GRPO with the feature reward: completions drift towards the ground truth's features
+    inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules="all-linear"))
+    st = G.GRPOSettings({"rl": "ebft", "trl": {"num_generations": 6, "max_completion_length": 5, "loss_type": "grpo"}})
+    recs = [{"prompt_ids": [3, 4, 5, 6 + i % 4], "ground_truth": [9, 9, 9, 9, 9]} for i in range(256)]
+    rf = FeatureMatchingReward(model, None, {"feature_layers": [0.5, 1.0], "embed_method": "completion_mean",
+                                             "diversity_coef": 0.0}, st.num_generations)
+    prod = G.RolloutProducer(model, G.LocalRollout(model, seed=0), [rf], st, recs, 4)
+    obj = G.GRPOObjective(st, prod)
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=3e-2, max_grad_norm=1.0)
+    opt.bind_model_shadows(model)
+    tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=40, learning_rate=3e-2),
+                 lambda e: [], device=torch.device("cpu"), compute_loss=obj)
+    align = []
+    it = prod(0)
+    for _ in range(40):
+        tr.training_step([next(it)])
+        align.append(obj.last_metrics["ebft/alignment"])
+    assert sum(align[-8:]) / 8 > sum(align[:8]) / 8 + 0.02, align

@@ -105,10 +105,14 @@ class ExpertParallelGroup:
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)                 # grouped by destination rank, then expert
         dest = (flat_e // self.E_local)
-        send_counts = torch.bincount(dest, minlength=self.size)
+        # counts by scatter-add: torch.bincount synchronises with the host to size its output
+        send_counts = torch.zeros(self.size, dtype=torch.int64, device=dev).scatter_add_(
+            0, dest.long(), torch.ones_like(dest, dtype=torch.int64))
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        # the ONE host synchronisation of the plan: NCCL needs the split sizes of the slot exchange
+        both = torch.stack([send_counts, recv_counts]).tolist()
+        sc, rc = both[0], both[1]
         n_recv = sum(rc)
         tok = (order // k).to(torch.int32)
         loc_e = (flat_e[order] % self.E_local).to(torch.int32)
@@ -120,7 +124,7 @@ class ExpertParallelGroup:
         r_tok, r_e = recv[:, 0].contiguous(), recv[:, 1].contiguous()
         r_w = recv[:, 2].contiguous().view(torch.float32)
         src_rank = torch.repeat_interleave(torch.arange(self.size, device=dev, dtype=torch.int32),
-                                           torch.tensor(rc, device=dev))
+                                           recv_counts, output_size=n_recv)
         local_order = torch.argsort(r_e, stable=True)
         p = _Plan()
         p.T, p.k, p.H = T, k, H
@@ -129,7 +133,10 @@ class ExpertParallelGroup:
         p.recv_src_row = r_tok[local_order].contiguous()
         p.recv_weight = r_w[local_order].contiguous()
         p.local_order = local_order
-        p.expert_counts = torch.bincount(r_e.long(), minlength=self.E_local).tolist()
+        counts_dev = torch.zeros(self.E_local, dtype=torch.int64, device=dev).scatter_add_(
+            0, r_e.long(), torch.ones(n_recv, dtype=torch.int64, device=dev))
+        # host copy only where the per-expert loop of the unfused path needs it
+        p.expert_counts = None if self.fused else counts_dev.tolist()
         p.n_recv = n_recv
         p.send_tok = tok
         p.lay = None
@@ -137,7 +144,7 @@ class ExpertParallelGroup:
             # expert segments padded to 128 rows for the grouped GEMM; -1 marks pad rows
             from ..ops.grouped import GroupLayout
 
-            lay = GroupLayout(torch.tensor(p.expert_counts, dtype=torch.int64, device=dev), n_recv)
+            lay = GroupLayout(counts_dev, n_recv)
             p.lay = lay
             p.pad_src_rank = torch.full((lay.max_rows,), -1, dtype=torch.int32, device=dev)
             p.pad_src_rank[lay.dest] = p.recv_src_rank

@@ -122,6 +122,15 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
                 m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype, use_dora=True)
             else:
                 m.add_lora(r, alpha, spec.lora_dropout, targets, spec.use_rslora, adapter_dtype)
+    tm = spec.target_modules
+    if isinstance(tm, (list, tuple, set)) and "embed_tokens" in tm:
+        if model.lm_head is None:
+            raise NotImplementedError("LoRA on embed_tokens with tied input/output embeddings is not supported")
+        r = spec.r
+        for pat, rv in spec.rank_pattern.items():
+            if re.search(pat, "model.embed_tokens"):
+                r = rv
+        model.add_embedding_lora(r, spec.lora_alpha, spec.use_rslora, adapter_dtype)
     if spec.target_parameters:
         for name, m in model.named_modules():
             if isinstance(m, Experts):
@@ -180,6 +189,9 @@ def get_peft_state_dict(model) -> dict:
             if getattr(m, "dora_magnitude", None) is not None:
                 r0, r1 = m.row_range(sub)
                 sd[f"{base}.lora_magnitude_vector"] = m.dora_magnitude.detach()[r0:r1]
+    if getattr(model, "embed_lora_At", None) is not None:
+        sd["base_model.model.model.embed_tokens.lora_embedding_A"] = model.embed_lora_At.detach().t()
+        sd["base_model.model.model.embed_tokens.lora_embedding_B"] = model.embed_lora_B.detach()
     ep_of = {id(m.experts): m.ep for m in model.modules() if getattr(m, "ep", None) is not None and hasattr(m, "experts")}
     for name, m in model.named_modules():
         if isinstance(m, Experts) and m.lora is not None:
@@ -224,6 +236,17 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
             elif strict:
                 raise KeyError(f"adapter tensors for {base} are missing")
         m.refresh_shadows()
+    if getattr(model, "embed_lora_At", None) is not None:
+        ka = "base_model.model.model.embed_tokens.lora_embedding_A"
+        kb = "base_model.model.model.embed_tokens.lora_embedding_B"
+        norm.update({k.replace(".default", ""): v for k, v in sd.items() if "lora_embedding_" in k})
+        if ka in norm and kb in norm:
+            with torch.no_grad():
+                model.embed_lora_At.copy_(norm[ka].t())
+                model.embed_lora_B.copy_(norm[kb])
+            used.update((ka, kb))
+        elif strict:
+            raise KeyError("adapter tensors for embed_tokens are missing")
     for name, m in model.named_modules():
         if isinstance(m, Experts) and m.lora is not None:
             base = f"base_model.model.model.{name}"
@@ -266,6 +289,8 @@ def load_adapter(model, adapter_dir: str, strict: bool = True) -> LoraSpec:
 @torch.no_grad()
 def merge_and_unload(model):
     """Folds every adapter into its base weight (W += s * B A) and removes the adapters."""
+    if getattr(model, "embed_lora_At", None) is not None:
+        model.merge_embedding_lora_()
     for _, m in model.fused_linears():
         if getattr(m, "mora_M", None) is not None:
             m.merge_mora_()

@@ -21,7 +21,7 @@ from torch.utils.checkpoint import checkpoint
 from ..ops import functional as Fn
 from ..ops.lora import linear
 from .config import ModelConfig
-from .layers import FusedLinear, RMSNorm
+from .layers import FusedLinear, RMSNorm, adapters_enabled
 
 IGNORE_INDEX = -100
 
@@ -137,11 +137,31 @@ class CausalLM(nn.Module):
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
         self.nvtx = bool(os.environ.get("AXB_NVTX"))   # NVTX range per decoder layer for timeline tools
         self.neftune_noise_alpha = None  # NEFTune: uniform noise on the embedding output while training
+        # LoRA on the embedding: h = E[ids] + s * A^T[ids] @ B^T (PEFT's lora_embedding_A / lora_embedding_B)
+        self.embed_lora_At = None   # [vocab, r]  (transposed lora_embedding_A, so that a lookup is a row gather)
+        self.embed_lora_B = None    # [hidden, r]
+        self.embed_lora_scaling = 1.0
         limit = (getattr(cfg, "extra", None) or {}).get("swiglu_limit")
         if limit:
             for m in self.modules():
                 if hasattr(m, "glu_limit"):
                     m.glu_limit = float(limit)
+
+    def add_embedding_lora(self, r, alpha, use_rslora=False, dtype=torch.float32):
+        """PEFT init for embeddings: A zeros, B normal (the product starts at zero)."""
+        dev = self.embed_tokens.device
+        V, H = self.embed_tokens.shape
+        self.embed_lora_At = nn.Parameter(torch.zeros(V, r, dtype=dtype, device=dev))
+        self.embed_lora_B = nn.Parameter(torch.randn(H, r, dtype=dtype, device=dev))
+        self.embed_lora_scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
+
+    @torch.no_grad()
+    def merge_embedding_lora_(self):
+        if self.embed_lora_At is None:
+            return
+        delta = self.embed_lora_scaling * (self.embed_lora_At.float() @ self.embed_lora_B.float().t())
+        self.embed_tokens.copy_((self.embed_tokens.float() + delta).to(self.embed_tokens.dtype))
+        self.embed_lora_At = self.embed_lora_B = None
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -224,6 +244,9 @@ class CausalLM(nn.Module):
         ids = input_ids.reshape(-1).to(dev, non_blocking=True)
         pos = position_ids.reshape(-1).to(device=dev, dtype=torch.int32, non_blocking=True)
         h = Fn.embedding(self.embed_tokens, ids)
+        if self.embed_lora_At is not None and adapters_enabled():
+            low = Fn.embedding(self.embed_lora_At.to(h.dtype), ids)                  # [T, r]
+            h = h + self.embed_lora_scaling * linear(low, self.embed_lora_B.to(h.dtype))
         if self.neftune_noise_alpha and self.training:
             # noise magnitude alpha / sqrt(L * d) with L the row length (NEFTune, as applied by the HF
             # trainer the reference builds on)

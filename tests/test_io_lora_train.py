@@ -610,3 +610,47 @@ def test_mora_operators_training_save_and_merge(tmp_path):
         merge_and_unload(model)
         after = model(ids, pos, return_logits=True).logits
     assert torch.allclose(before, after, atol=2e-3, rtol=1e-3)
+
+
+def test_embedding_lora_matches_definition_saves_and_merges(tmp_path):
+    import torch
+
+    from axolotl_b200.io.safetensors_io import load_file
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, inject_lora, load_adapter, merge_and_unload, save_adapter
+    from axolotl_b200.models.transformer import CausalLM
+
+    cfg = preset("tiny-llama", vocab_size=200, num_hidden_layers=1, tie_word_embeddings=False)
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    spec = LoraSpec(r=8, lora_alpha=16, target_modules=["embed_tokens", "q_proj"])
+    inject_lora(model, spec)
+    assert model.embed_lora_At.shape == (200, 8) and model.embed_lora_At.requires_grad and not model.embed_tokens.requires_grad
+    ids = torch.randint(0, 200, (1, 24))
+    base = model(ids, return_logits=True).logits
+    with torch.no_grad():
+        model.embed_lora_At.normal_(0, 0.3)
+    out = model(ids, labels=ids)
+    out.loss.backward()
+    gA = model.embed_lora_At.grad if model.embed_lora_At.grad is not None else model.embed_lora_At._axb_grad
+    used = torch.zeros(200, dtype=torch.bool)
+    used[ids.reshape(-1)] = True
+    assert float(gA[used].abs().sum()) > 0 and float(gA[~used].abs().sum()) == 0   # only looked-up rows get gradient
+    model.eval()
+    with torch.no_grad():
+        adapted = model(ids, return_logits=True).logits
+        assert (adapted - base).abs().max() > 1e-3
+        # definition: E' = E + s * A^T B^T
+        E2 = model.embed_tokens + 2.0 * model.embed_lora_At @ model.embed_lora_B.t()
+    save_adapter(model, spec, str(tmp_path / "a"))
+    sd = load_file(str(tmp_path / "a" / "adapter_model.safetensors"))
+    assert sd["base_model.model.model.embed_tokens.lora_embedding_A"].shape == (8, 200)
+    assert sd["base_model.model.model.embed_tokens.lora_embedding_B"].shape == (cfg.hidden_size, 8)
+    fresh = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    inject_lora(fresh, spec)
+    load_adapter(fresh, str(tmp_path / "a"))
+    fresh.eval()
+    with torch.no_grad():
+        assert torch.allclose(fresh(ids, return_logits=True).logits, adapted, atol=1e-5)
+        merge_and_unload(model)
+        assert torch.allclose(model.embed_tokens, E2, atol=1e-5)
+        assert torch.allclose(model(ids, return_logits=True).logits, adapted, atol=1e-4)

@@ -39,7 +39,7 @@ def test_llama_logits_match_hf_and_packing_isolates_documents(tmp_path):
     with torch.no_grad():
         got = ours(ids, pos, return_logits=True).logits
     ref = _hf_docwise_logits(hf_model, ids, lens)
-    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
     # reload through our loader as well
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
@@ -74,7 +74,7 @@ def test_qwen3_qk_norm_matches_hf(tmp_path):
     with torch.no_grad():
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
-    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
 
 
 def test_qwen3_moe_matches_hf(tmp_path):
@@ -118,7 +118,7 @@ def test_phi3_fused_checkpoint_names_match_hf(tmp_path):
     with torch.no_grad():
         got = ours(ids, pos, return_logits=True).logits
     ref = _hf_docwise_logits(hf_model, ids, lens)
-    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         assert torch.equal(again(ids, pos, return_logits=True).logits, got)
@@ -152,7 +152,7 @@ def test_mistral_and_qwen2_match_hf(tmp_path, model_type, extra):
     with torch.no_grad():
         got = ours(ids, pos, return_logits=True).logits
     ref = _hf_docwise_logits(hf_model, ids, lens)
-    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
 
 
 def test_mixtral_matches_hf(tmp_path):

@@ -221,6 +221,64 @@ __global__ void ep_gather_rows_kernel(PeerPtrs8 src, const int* __restrict__ src
   }
 }
 
+// Deduplicated dispatch: a token with several slots on this rank crosses NVLink once.
+// staging[r][row][:] = rank r's buffer[row][:] for every (r != self, row) with need[r*T + row] set.
+__global__ void ep_stage_rows_kernel(PeerPtrs8 src, const unsigned char* __restrict__ need,
+                                     __nv_bfloat16* __restrict__ staging, int world, int self, long long T,
+                                     int width) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long items = (long long)world * T;
+  for (long long i = w; i < items; i += n_warps) {
+    const int r = (int)(i / T);
+    if (r == self || !need[i]) continue;
+    const long long row = i - (long long)r * T;
+    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + row * width;
+    __nv_bfloat16* d = staging + i * width;
+    for (int c = lane * 8; c < width; c += 256)
+      *reinterpret_cast<uint4*>(d + c) = *reinterpret_cast<const uint4*>(s + c);
+  }
+}
+
+// Deduplicated combine: every expert rank first sums its slots of a token locally into
+// partial[source rank][row]; the source then adds one partial row per contributing rank:
+// y[row][:] += sum over r != self with sent[r*T + row] of rank r's partial[self*T + row][:].
+__global__ void ep_reduce_rows_kernel(PeerPtrs8 part, const unsigned char* __restrict__ sent,
+                                      __nv_bfloat16* __restrict__ y, int world, int self, long long T, int width) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = w; row < T; row += n_warps) {
+    unsigned mask = 0;
+    for (int r = 0; r < world; ++r)
+      if (r != self && sent[(long long)r * T + row]) mask |= 1u << r;
+    if (!mask) continue;
+    for (int c = lane * 8; c < width; c += 256) {
+      float acc[8];
+      {
+        const uint4 v = *reinterpret_cast<const uint4*>(y + row * width + c);
+        const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), cc = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+        acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = cc.x; acc[5] = cc.y; acc[6] = d.x; acc[7] = d.y;
+      }
+      for (int r = 0; r < world; ++r) {
+        if (!((mask >> r) & 1u)) continue;
+        const __nv_bfloat16* s =
+            reinterpret_cast<const __nv_bfloat16*>(part.p[r]) + ((long long)self * T + row) * width + c;
+        const uint4 v = *reinterpret_cast<const uint4*>(s);
+        const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), cc = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(y + row * width + c) = o;
+    }
+  }
+}
+
 // dst_rank(i).buffer[dst_row(i), :] += weight(i) * rows[i, :]
 __global__ void ep_scatter_add_kernel(PeerPtrs8 dst, const int* __restrict__ dst_rank,
                                       const int* __restrict__ dst_row, const float* __restrict__ weight,
@@ -349,6 +407,31 @@ extern "C" int axb_ep_scatter_add(const unsigned long long* dst_ptrs, int world,
   int grid = (int)((n_rows + 7) / 8 > 148 * 8 ? 148 * 8 : (n_rows + 7) / 8);
   ep_scatter_add_kernel<<<grid, 256, 0, ST(stream)>>>(p, dst_rank, dst_row, weight, (const __nv_bfloat16*)rows, n_rows,
                                                       width, dst_ld);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int axb_ep_stage_rows(const unsigned long long* src_ptrs, int world, int self, const void* need,
+                                 void* staging, long long T, int width, void* stream) {
+  if (T <= 0) return 0;
+  if (width % 8) return -2;
+  PeerPtrs8 p;
+  if (fill8(p, src_ptrs, world)) return -2;
+  const long long items = (long long)world * T;
+  int grid = (int)((items + 7) / 8 > 148 * 8 ? 148 * 8 : (items + 7) / 8);
+  ep_stage_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, (const unsigned char*)need, (__nv_bfloat16*)staging, world,
+                                                     self, T, width);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int axb_ep_reduce_rows(const unsigned long long* part_ptrs, int world, int self, const void* sent,
+                                  void* y, long long T, int width, void* stream) {
+  if (T <= 0) return 0;
+  if (width % 8) return -2;
+  PeerPtrs8 p;
+  if (fill8(p, part_ptrs, world)) return -2;
+  int grid = (int)((T + 7) / 8 > 148 * 8 ? 148 * 8 : (T + 7) / 8);
+  ep_reduce_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, (const unsigned char*)sent, (__nv_bfloat16*)y, world, self,
+                                                      T, width);
   return (int)cudaGetLastError();
 }
 

@@ -38,6 +38,8 @@ _CUDA_SIGS = {
     "axb_grouped_gram": [vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i64, f32, i32, i32, vp, vp, vp, vp],
     "axb_ep_gather_rows": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, i64, vp],
     "axb_ep_scatter_add": [vp, i32, vp, vp, vp, vp, i64, i32, i64, vp],
+    "axb_ep_stage_rows": [vp, i32, i32, vp, vp, i64, i32, vp],
+    "axb_ep_reduce_rows": [vp, i32, i32, vp, vp, i64, i32, vp],
     "axb_peer_put_i32": [vp, vp, i64, vp],
     "axb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
     "axb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],

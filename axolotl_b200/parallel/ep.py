@@ -19,6 +19,8 @@ On CPU (gloo) the payload moves with ``all_to_all_single`` so the same logic is 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -30,7 +32,7 @@ class _Plan:
     """Routing plan of one MoE layer call (shared by forward and backward)."""
     __slots__ = ("T", "k", "H", "send_order", "send_counts", "recv_counts", "recv_src_rank", "recv_src_row",
                  "recv_weight", "local_order", "expert_counts", "n_recv", "send_tok", "lay", "pad_src_rank", "pad_src_row",
-                 "pad_weight")
+                 "pad_weight", "need", "sent")
 
 
 class ExpertParallelGroup:
@@ -41,7 +43,12 @@ class ExpertParallelGroup:
         self.E, self.E_local = num_experts, num_experts // size
         self.fused = self.device.type == "cuda"
         self.x_bufs = self.y_bufs = None
+        self.p_bufs = self.staging = None
         self.kx = self.ky = 0
+        # Deduplicated payload (default): a token with several slots on one rank crosses NVLink once in
+        # each direction (rows are staged / partially summed per rank pair). AXB_EP_DEDUP=0 moves one row
+        # per slot straight between the ranks instead.
+        self.dedup = os.environ.get("AXB_EP_DEDUP", "1") != "0"
         if self.fused:
             self.sync = PeerSync(self.device, group)
 
@@ -152,6 +159,13 @@ class ExpertParallelGroup:
             p.pad_src_row[lay.dest] = p.recv_src_row
             p.pad_weight = torch.zeros(lay.max_rows, dtype=torch.float32, device=dev)
             p.pad_weight[lay.dest] = p.recv_weight
+            if self.dedup:
+                # need[r*T + row]: this rank computes at least one slot of rank r's token `row`;
+                # sent[r*T + row]: rank r computes at least one slot of this rank's token `row`
+                p.need = torch.zeros(self.size * T, dtype=torch.uint8, device=dev)
+                p.need[p.recv_src_rank.long() * T + p.recv_src_row.long()] = 1
+                p.sent = torch.zeros(self.size * T, dtype=torch.uint8, device=dev)
+                p.sent[dest.long() * T + torch.arange(T * k, device=dev) // k] = 1
         return p
 
     def _ensure(self, T, H):
@@ -161,7 +175,18 @@ class ExpertParallelGroup:
         if self.x_bufs is None or self.x_bufs[0].tensor.numel() < need:
             self.x_bufs = [SymmBuffer(need, torch.bfloat16, self.device, self.group, use_multicast=False) for _ in range(2)]
             self.y_bufs = [SymmBuffer(need, torch.bfloat16, self.device, self.group, use_multicast=False) for _ in range(2)]
+            if self.dedup:
+                self.p_bufs = [SymmBuffer(self.size * need, torch.bfloat16, self.device, self.group, use_multicast=False)
+                               for _ in range(2)]
+                self.staging = torch.empty(self.size * need, dtype=torch.bfloat16, device=self.device)
             dist.barrier(self.group)
+
+    def _slices(self, base, stride_bytes, own):
+        """Pointer table for the row kernels: slice r of a local [world, T, H] buffer, this rank's own
+        entry replaced by ``own`` (its rows need no staging)."""
+        from .symm import _u64_array
+
+        return _u64_array([own if r == self.rank else base + r * stride_bytes for r in range(self.size)])
 
     # ------------------------------------------------------------------ payload movement
     def pull_rows(self, x, plan, weighted=False, dot_with=None):
@@ -181,7 +206,12 @@ class ExpertParallelGroup:
         n = plan.lay.max_rows
         out = torch.empty((n, H), dtype=x.dtype, device=x.device)
         dots = torch.empty(n, dtype=torch.float32, device=x.device) if dot_with is not None else None
-        _lib.check_rc(lib.axb_ep_gather_rows(buf.ptrs_c, self.size, plan.pad_src_rank.data_ptr(),
+        src_ptrs = buf.ptrs_c
+        if self.dedup:   # needed rows of every peer -> local staging, then a local gather
+            _lib.check_rc(lib.axb_ep_stage_rows(buf.ptrs_c, self.size, self.rank, plan.need.data_ptr(),
+                                                self.staging.data_ptr(), T, H, _lib.stream_ptr()), "ep_stage_rows")
+            src_ptrs = self._slices(self.staging.data_ptr(), T * H * 2, buf.tensor.data_ptr())
+        _lib.check_rc(lib.axb_ep_gather_rows(src_ptrs, self.size, plan.pad_src_rank.data_ptr(),
                                              plan.pad_src_row.data_ptr(),
                                              plan.pad_weight.data_ptr() if weighted else None,
                                              dot_with.data_ptr() if dot_with is not None else None,
@@ -202,9 +232,26 @@ class ExpertParallelGroup:
             return y
         lib = _lib.cuda_lib()
         self._ensure(T, H)
+        rows = rows.contiguous()
+        if self.dedup:
+            # Slots are summed per (source rank, token) locally; the source then pulls one partial row per
+            # contributing rank. The partial buffer alternates between two allocations: by the time one is
+            # zeroed again every peer has passed the barrier of the call in between, i.e. finished reading it.
+            part = self.p_bufs[self.ky & 1]
+            self.ky += 1
+            part.tensor[: self.size * T * H].zero_()
+            y = torch.zeros(T, H, dtype=rows.dtype, device=rows.device)
+            dst_ptrs = self._slices(part.tensor.data_ptr(), T * H * 2, y.data_ptr())
+            _lib.check_rc(lib.axb_ep_scatter_add(dst_ptrs, self.size, plan.pad_src_rank.data_ptr(),
+                                                 plan.pad_src_row.data_ptr(),
+                                                 plan.pad_weight.data_ptr() if weighted else None, rows.data_ptr(),
+                                                 plan.lay.max_rows, H, H, _lib.stream_ptr()), "ep_scatter_add")
+            self.sync.barrier(channel=7)
+            _lib.check_rc(lib.axb_ep_reduce_rows(part.ptrs_c, self.size, self.rank, plan.sent.data_ptr(), y.data_ptr(),
+                                                 T, H, _lib.stream_ptr()), "ep_reduce_rows")
+            return y
         buf = self.y_bufs[self.ky & 1]     # zero on every rank since its last use
         self.ky += 1
-        rows = rows.contiguous()
         _lib.check_rc(lib.axb_ep_scatter_add(buf.ptrs_c, self.size, plan.pad_src_rank.data_ptr(),
                                              plan.pad_src_row.data_ptr(),
                                              plan.pad_weight.data_ptr() if weighted else None, rows.data_ptr(),

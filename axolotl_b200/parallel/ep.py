@@ -5,12 +5,15 @@ Per MoE layer and micro batch:
 1. routing is local (softmax -> top-k); the slot lists (source row, local expert id, routing weight)
    are exchanged with one small all-to-all (metadata only, a few KB);
 2. DISPATCH: every rank copies its hidden states into a symmetric buffer; after one flag barrier the
-   destination ranks *pull* exactly the rows routed to their experts with peer loads
-   (``axb_ep_gather_rows``), already sorted by expert -- no send buffers, no host barrier;
+   destination ranks *pull* the rows routed to their experts with peer loads: each needed token once
+   into a local staging area (``axb_ep_stage_rows``; top-k routing puts several slots of a token on
+   the same rank), then a local gather into the padded expert-sorted layout
+   (``axb_ep_gather_rows``) -- no send buffers, no host barrier;
 3. the local experts run as tcgen05 GEMMs (bf16, or NVFP4 weights dequantised by
    ``axb_nvfp4_dequant``) with their LoRA folded in;
-4. COMBINE: expert outputs are scaled by their routing weight and reduce-added into the source
-   rank's output buffer with peer atomics (``axb_ep_scatter_add``); one more flag barrier.
+4. COMBINE: expert outputs are scaled by their routing weight and summed per (source rank, token)
+   into a local partial buffer (``axb_ep_scatter_add``); after one more flag barrier the source adds
+   one partial row per contributing rank with peer loads (``axb_ep_reduce_rows``).
 The backward pass is the mirror image (combine^T = gather of dY rows, dispatch^T = scatter-add of dX
 rows). Expert weights and expert-LoRA slices follow the reference's layout rules
 (src/axolotl/integrations/expert_parallel/shard.py:56-393): rank r owns experts

@@ -59,7 +59,11 @@ class Attention(nn.Module):
         qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
                           self.q_norm.weight if self.q_norm is not None else None,
                           self.k_norm.weight if self.k_norm is not None else None, self.eps)
-        a = Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+        cache = getattr(meta, "kv_cache", None)
+        if cache is not None:   # generation: keep the rotated k / v of every token
+            a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+        else:
+            a = Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
         return self.o_proj(a)
 
 
@@ -96,6 +100,7 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.self_attn = Attention(cfg, dtype, device)
+        self.self_attn.layer_idx = idx
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         if cfg.is_moe_layer(idx):
             from .moe import SparseMoE
@@ -304,8 +309,16 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ generation (greedy / sampling)
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens=32, temperature=0.0, top_p=1.0, eos_token_id=None):
-        """Simple full-recompute decoding (no KV cache): adequate for eval samples and smoke checks."""
+    def generate(self, input_ids, max_new_tokens=32, temperature=0.0, top_p=1.0, eos_token_id=None, use_cache=True):
+        """Greedy / sampled continuation of one prompt; returns [1, prompt + new]. With ``use_cache``
+        (default) every new token is one incremental step over a KV cache; without it the whole
+        sequence is recomputed per token (kept as the oracle of the cached path)."""
+        if use_cache and getattr(self.hooks, "supports_kv_cache", True) is not False:
+            from .kv_cache import generate_cached
+
+            prompt = input_ids.reshape(-1).tolist()
+            new = generate_cached(self, [prompt], max_new_tokens, temperature, top_p, 0, eos_token_id)[0]
+            return torch.tensor([prompt + new], dtype=torch.long, device=input_ids.device)
         was_training = self.training
         self.eval()
         ids = input_ids.reshape(1, -1).clone()

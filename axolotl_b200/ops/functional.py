@@ -496,6 +496,34 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True)).reshape(T, Hq * D)
 
 
+@torch.no_grad()
+def decode_attention(qkv, k_cache, v_cache, lens, Hq, Hk, D, scale=None):
+    """Attention of ONE new token per sequence against its KV cache (generation).
+
+    ``qkv`` [B, (Hq + 2*Hk) * D]: fused projection of the new tokens, q / k already rotated;
+    ``k_cache`` / ``v_cache`` [B, max_len, Hk * D] with the new token's k / v already stored at
+    position ``lens[b] - 1``; ``lens`` [B] int32: live positions including the new token.
+    Returns [B, Hq * D]. Inference only (no autograd)."""
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    B = qkv.shape[0]
+    if qkv.is_cuda:
+        lib = _lib.cuda_lib()
+        out = torch.empty((B, Hq * D), dtype=qkv.dtype, device=qkv.device)
+        _lib.check_rc(lib.axb_decode_attn(qkv.data_ptr(), qkv.stride(0), 0, k_cache.data_ptr(), v_cache.data_ptr(),
+                                          lens.data_ptr(), out.data_ptr(), out.stride(0), B, Hq, Hk, D,
+                                          k_cache.shape[1], scale, _lib.stream_ptr()), "decode_attn")
+        return out
+    q = qkv[:, : Hq * D].reshape(B, Hk, Hq // Hk, D).float()
+    out = torch.empty(B, Hq * D, dtype=qkv.dtype)
+    for b in range(B):
+        n = int(lens[b])
+        k = k_cache[b, :n].reshape(n, Hk, D).float().transpose(0, 1)     # [Hk, n, D]
+        v = v_cache[b, :n].reshape(n, Hk, D).float().transpose(0, 1)
+        p = torch.softmax((q[b] @ k.transpose(1, 2)) * scale, -1)        # [Hk, G, n]
+        out[b] = (p @ v).reshape(-1).to(qkv.dtype)
+    return out
+
+
 # --------------------------------------------------------------------------------------- loss
 class _LinearCE(torch.autograd.Function):
     """Chunked lm_head GEMM + cross entropy that never materialises [T, V] logits.

@@ -62,45 +62,12 @@ class LocalRollout:
 
     @torch.no_grad()
     def generate(self, prompts, n, max_new_tokens, temperature=1.0, top_p=1.0, top_k=0):
-        """prompts: list of id lists -> list (len(prompts) * n, prompt-major) of completion id lists."""
-        model = self.model
-        dev = model.embed_tokens.device
-        was = model.training
-        model.eval()
+        """prompts: list of id lists -> list (len(prompts) * n, prompt-major) of completion id lists.
+        Decoding is incremental: one packed prefill of all prompts, then one KV-cache step per token."""
+        from ..models.kv_cache import generate_cached
+
         seqs = [list(p) for p in prompts for _ in range(n)]
-        start = [len(s) for s in seqs]
-        done = [False] * len(seqs)
-        W = model.output_weight()
-        for _ in range(max_new_tokens):
-            active = [i for i, d in enumerate(done) if not d]
-            if not active:
-                break
-            lens = np.array([len(seqs[i]) for i in active])
-            total = int(lens.sum())
-            width = ((total + 63) // 64) * 64
-            ids = np.full(width, self.pad, np.int64)
-            pos = np.zeros(width, np.int32)
-            cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
-            for k, i in enumerate(active):
-                ids[cu[k]:cu[k + 1]] = seqs[i]
-                pos[cu[k]:cu[k + 1]] = np.arange(lens[k])
-            if width > total:
-                pos[total:] = np.arange(width - total)
-                cu_all = np.concatenate([cu, [width]]).astype(np.int32)
-            else:
-                cu_all = cu
-            out = model(torch.from_numpy(ids)[None], torch.from_numpy(pos)[None],
-                        attn_meta=Fn.AttnMeta(cu_all, dev), return_logits=False)
-            h = out.hidden_states[0]
-            last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(dev)
-            logits = linear(h[last].contiguous(), W).float()
-            nxt = sample_from_logits(logits, temperature, top_p, top_k, self.gen).tolist()
-            for k, i in enumerate(active):
-                seqs[i].append(int(nxt[k]))
-                if self.eos is not None and nxt[k] == self.eos:
-                    done[i] = True
-        model.train(was)
-        return [s[st:] for s, st in zip(seqs, start)]
+        return generate_cached(self.model, seqs, max_new_tokens, temperature, top_p, top_k, self.eos, self.gen)
 
     def sync_weights(self, model, step):   # same weights by construction
         return

@@ -568,3 +568,33 @@ def test_flash_varlen_bidirectional_documents_match_fp32_reference():
     # and it differs from the causal result (the flag is honoured)
     causal = Fn.flash_varlen(qkv.detach(), Fn.AttnMeta(cu, "cuda"), Hq, Hk, D)
     assert (causal.float() - out.float()).abs().max() > 0.05
+
+
+@pytest.mark.gpu
+def test_decode_attention_and_cached_generation_match_full_recompute():
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    # kernel against the fp32 definition (GQA 4:1 and 8:1, ragged lengths crossing chunk boundaries)
+    for Hq, Hk, D in ((8, 2, 128), (16, 2, 64)):
+        B, max_len = 5, 700
+        lens = torch.tensor([1, 127, 128, 129, 700], dtype=torch.int32, device="cuda")
+        qkv = torch.randn(B, (Hq + 2 * Hk) * D, device="cuda").to(torch.bfloat16)
+        kc = torch.randn(B, max_len, Hk * D, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(B, max_len, Hk * D, device="cuda").to(torch.bfloat16)
+        out = Fn.decode_attention(qkv, kc, vc, lens, Hq, Hk, D)
+        ref = Fn.decode_attention(qkv.cpu(), kc.cpu(), vc.cpu(), lens.cpu(), Hq, Hk, D)
+        assert torch.allclose(out.float().cpu(), ref.float(), atol=2e-2, rtol=2e-2), (out.float().cpu() - ref.float()).abs().max()
+    # end to end: cached decoding reproduces full-recompute greedy decoding (dense and MoE)
+    for name in ("tiny-llama", "tiny-qwen3-moe"):
+        cfg = preset(name, vocab_size=512)
+        m = CausalLM(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0)
+        p = torch.tensor([1, 5, 9, 12, 40, 41, 42], device="cuda")
+        a, b = m.generate(p, 12), m.generate(p, 12, use_cache=False)
+        agree = (a == b).float().mean().item()
+        assert agree > 0.8, (name, a.tolist(), b.tolist())   # bf16 ties may flip a late token
+        from axolotl_b200.models.kv_cache import generate_cached
+        outs = generate_cached(m, [[1, 5, 9], [7, 8, 9, 10, 11], [3]], 6)
+        assert [len(o) for o in outs] == [6, 6, 6]
+        assert outs[1][:3] == m.generate(torch.tensor([7, 8, 9, 10, 11], device="cuda"), 3, use_cache=False)[0, 5:].tolist()

@@ -19,7 +19,8 @@ class KVCache:
         cfg = model.config
         dev, dt = model.embed_tokens.device, model.embed_tokens.dtype
         self.L, self.B, self.max_len = cfg.num_hidden_layers, batch, max_len
-        self.width = cfg.num_key_value_heads * cfg.head_dim
+        att = model.layers[0].self_attn              # local head counts (a tensor-parallel rank holds a slice)
+        self.width = att.Hk * att.D
         self.k = torch.zeros(self.L, batch, max_len, self.width, dtype=dt, device=dev)
         self.v = torch.zeros_like(self.k)
         self.lens = torch.zeros(batch, dtype=torch.int32, device=dev)   # live positions per sequence

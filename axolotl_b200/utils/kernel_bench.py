@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-``python -m axolotl_b200.utils.kernel_bench [gemm|attn|elementwise|all]`` times each hand-written
+``python -m axolotl_b200.utils.kernel_bench [gemm|lora|attn|elementwise|all]`` times each hand-written
 kernel with CUDA events (after warm-up, L2 flushed between iterations) and prints achieved
 TFLOP/s or GB/s next to the library kernel for the same shape (cuBLAS via torch.matmul,
 flash-attn 2 where installed) and the measured peaks in ``MEASURED_PEAKS.json`` if present.
@@ -68,6 +68,33 @@ def bench_gemm(rows):
         rows.append(f"gemm {name} M={M} N={N} K={K} transB={int(tb)}: ours {ours:.3f} ms "
                     f"{fl / ours:.0f} TFLOP/s ({fl / ours / peak:.2f} of {how} peak) | cuBLAS {lib:.3f} ms "
                     f"{fl / lib:.0f} TFLOP/s | ratio {lib / ours:.2f}")
+
+
+def bench_lora_skinny(rows):
+    """The adapter-side GEMMs of one LoRA projection: memory-bound passes over x or dy."""
+    from axolotl_b200.ops.gemm import gemm, pick_splits
+
+    _, hbm, how = _peaks()
+    T = 8192
+    cases = [("qkv", 4096, 6144, 48), ("o", 4096, 4096, 16), ("gate_up", 4096, 28672, 32), ("down", 14336, 4096, 16)]
+    for name, K, N, R in cases:
+        x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+        A = torch.randn(R, K, device="cuda", dtype=torch.bfloat16)
+        B = torch.randn(N, R, device="cuda", dtype=torch.bfloat16)
+        xa = torch.randn(T, R, device="cuda", dtype=torch.bfloat16)
+        dA = torch.zeros(R, K, device="cuda", dtype=torch.float32)
+        dB = torch.zeros(N, R, device="cuda", dtype=torch.float32)
+        t_xa = time_cuda(lambda: gemm(x, A))
+        t_t = time_cuda(lambda: gemm(dy, B, trans_b=True))
+        sp_a = pick_splits((K + 255) // 256, (T + 63) // 64)
+        t_dA = time_cuda(lambda: gemm(xa, x, trans_a=True, trans_b=True, out=dA, accumulate=True, splits=sp_a))
+        sp_b = pick_splits((N + 127) // 128, (T + 63) // 64)
+        t_dB = time_cuda(lambda: gemm(dy, xa, trans_a=True, trans_b=True, out=dB, accumulate=True, splits=sp_b, bn=64))
+        gb = lambda elems, ms: elems * 2 / 1e6 / ms   # GB/s
+        rows.append(f"lora {name} r={R}: x@A^T {t_xa * 1e3:.0f} us ({gb(T * K, t_xa) / hbm:.2f}) | dy@B {t_t * 1e3:.0f} us "
+                    f"({gb(T * N, t_t) / hbm:.2f}) | dA=t^T x {t_dA * 1e3:.0f} us ({gb(T * K, t_dA) / hbm:.2f}, splits {sp_a}) | "
+                    f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b})  [fractions of {how} HBM copy rate]")
 
 
 def bench_attn(rows):
@@ -180,6 +207,8 @@ def main(argv):
     rows = []
     if what in ("gemm", "all"):
         bench_gemm(rows)
+    if what in ("lora", "all"):
+        bench_lora_skinny(rows)
     if what in ("attn", "all"):
         bench_attn(rows)
     if what in ("elementwise", "all"):

@@ -189,7 +189,10 @@ def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, 
         bn = _pick_bn(M, N)
     ctx = info.ctx
     staging, plan = ctx.acquire(info, backward=trans_b)
-    if plan is not None:
+    if plan is not None and ctx.copy_engine:
+        ctx.prefetch_by_copy(plan)
+        pf = (None, 0, 0, 0, None, 0)
+    elif plan is not None:
         nxt, slot = plan
         pf = (nxt.peer_bases_dev.data_ptr(), nxt.shard_offset, nxt.shard_bytes, nxt.world,
               ctx.staging[slot].data_ptr(), ctx.prefetch_ctas(nxt, 2.0 * M * N * K))

@@ -50,6 +50,11 @@ class FSDPContext:
         # 32-64 CTAs max at 20-40 GB/s assumed all land at 333-335 ms/step.
         self.bytes_per_cta_s = float(os.environ.get("AXB_FSDP_CTA_GBS", "40")) * 1e9
         self.max_prefetch_ctas = int(os.environ.get("AXB_FSDP_MAX_CTAS", "40"))
+        # Alternative transport for the prefetch: the copy engines (peer cudaMemcpyAsync on a side stream)
+        # instead of gather CTAs inside the GEMM launch, which leaves every SM to the MMAs.
+        self.copy_engine = os.environ.get("AXB_FSDP_COPY_ENGINE", "0") == "1"
+        self.side_stream = None
+        self.pending = [None, None]   # copy-complete event of each staging buffer
 
     @staticmethod
     def shardable(m: FusedLinear, world: int) -> bool:
@@ -105,8 +110,15 @@ class FSDPContext:
             slot = 0
         elif self.holds[1] is info:
             slot = 1
-        else:  # not predicted: fetch now with every SM
+        else:
+            slot = None
+        hit = slot is not None
+        if slot is None:
             slot = 0 if self.holds[0] is None or self.holds[1] is not None else 1
+        if self.pending[slot] is not None:   # copy engines are (or were) writing this buffer: order after them
+            torch.cuda.current_stream(self.device).wait_event(self.pending[slot])
+            self.pending[slot] = None
+        if not hit:  # not predicted: fetch now with every SM
             lib = _lib.cuda_lib()
             _lib.check_rc(lib.axb_allgather_rows(info.peer_bases_dev.data_ptr(), info.shard_offset, info.shard_bytes,
                                                  info.world, self.staging[slot].data_ptr(), 0,
@@ -128,6 +140,29 @@ class FSDPContext:
         t_gemm = gemm_flops / 1.3e15
         need = nxt.shard_bytes * nxt.world / max(t_gemm, 1e-6) / self.bytes_per_cta_s
         return int(min(self.max_prefetch_ctas, max(2, round(need + 0.5))))
+
+    def prefetch_by_copy(self, plan):
+        """Issues the all-gather of the planned weight on the copy engines. Called right BEFORE the GEMM
+        that reads the other staging buffer is launched: the copies wait for everything already queued on
+        the compute stream (the last reader of the buffer they overwrite) and run beside that GEMM."""
+        nxt, slot = plan
+        main = torch.cuda.current_stream(self.device)
+        if self.side_stream is None:
+            self.side_stream = torch.cuda.Stream(self.device)
+        if self.pending[slot] is not None:      # an earlier, never consumed prefetch into this buffer
+            self.side_stream.wait_event(self.pending[slot])
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.side_stream.wait_event(ev)
+        n = nxt.shard_bytes // 2
+        dst = self.staging[slot]
+        with torch.cuda.stream(self.side_stream):
+            for r in range(nxt.world):
+                src = self.arena.handle.get_buffer(r, (n,), torch.bfloat16, nxt.shard_offset // 2)
+                dst[r * n:(r + 1) * n].copy_(src, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.side_stream)
+        self.pending[slot] = done
 
     def committed(self, plan):
         nxt, slot = plan

@@ -1,11 +1,14 @@
-"""FSDP-style sharding of the frozen base weights with the all-gather fused into the GEMM.
+"""FSDP-style sharding of the frozen base weights with the all-gather overlapped with the GEMMs.
 
 Every ``FusedLinear`` weight [N, K] is row-sharded: rank r keeps rows [r*N/W, (r+1)*N/W) inside
 one symmetric arena. Forward (x W^T) and input-gradient (dY W) GEMMs read the full weight from
-one of two local staging buffers; the GEMM launch that runs on weight k carries a few extra CTAs
-(``axb_gemm_bf16_prefetch``) that pull the shards of weight k+1 of the layer schedule out of the
-peers' memory over NVLink into the other staging buffer, so the all-gather of the next GEMM's
-operand overlaps the tensor-core work of this one and stream order is the only synchronisation.
+one of two local staging buffers; while the GEMM on weight k runs, the shards of weight k+1 of the
+layer schedule are pulled out of the peers' memory over NVLink into the other staging buffer.
+Two transports exist for that pull. (a) The copy engines (default): one peer copy per rank on a
+side stream, ordered by events after the last reader of the buffer and before its next reader; no
+SM is taken from the MMAs. (b) Gather CTAs inside the GEMM launch (``axb_gemm_bf16_prefetch``):
+a few extra CTAs of the same kernel copy the shards with bulk loads, so stream order is the only
+synchronisation; this costs the tensor-core kernel some SMs (measured 6 % of the 2-GPU step).
 A weight that was not predicted is fetched by a stand-alone all-gather launch. Per-GPU weight
 memory is 1/W of the model plus two staging buffers of the largest weight. Because the base is
 frozen its shards never change, so no inter-rank synchronisation is needed around the gathers.
@@ -50,9 +53,11 @@ class FSDPContext:
         # 32-64 CTAs max at 20-40 GB/s assumed all land at 333-335 ms/step.
         self.bytes_per_cta_s = float(os.environ.get("AXB_FSDP_CTA_GBS", "40")) * 1e9
         self.max_prefetch_ctas = int(os.environ.get("AXB_FSDP_MAX_CTAS", "40"))
-        # Alternative transport for the prefetch: the copy engines (peer cudaMemcpyAsync on a side stream)
-        # instead of gather CTAs inside the GEMM launch, which leaves every SM to the MMAs.
-        self.copy_engine = os.environ.get("AXB_FSDP_COPY_ENGINE", "0") == "1"
+        # Transport of the prefetch. Default: the copy engines (peer cudaMemcpyAsync on a side stream, ordered
+        # by events against the GEMMs that read / reuse the staging buffers), which leaves every SM to the
+        # MMAs: 316 ms/step against 335 ms with gather CTAs on the 2-GPU Llama-3-8B LoRA step.
+        # AXB_FSDP_COPY_ENGINE=0 selects the gather CTAs inside the GEMM launch instead.
+        self.copy_engine = os.environ.get("AXB_FSDP_COPY_ENGINE", "1") == "1"
         self.side_stream = None
         self.pending = [None, None]   # copy-complete event of each staging buffer
 

@@ -188,11 +188,15 @@ def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, 
     if bn is None:
         bn = _pick_bn(M, N)
     ctx = info.ctx
-    staging, plan = ctx.acquire(info, backward=trans_b)
-    if plan is not None and ctx.copy_engine:
-        ctx.prefetch_by_copy(plan)
+    staging, plans = ctx.acquire(info, backward=trans_b)
+    plan = None
+    if plans and ctx.copy_engine:
+        for pl in plans:          # copy engines: distance-1 and distance-2 weights, beside this GEMM
+            ctx.prefetch_by_copy(pl)
+            ctx.committed(pl)
         pf = (None, 0, 0, 0, None, 0)
-    elif plan is not None:
+    elif plans and plans[0][0].index in (info.index + 1, info.index - 1):
+        plan = plans[0]           # gather CTAs of this launch: the next weight only
         nxt, slot = plan
         pf = (nxt.peer_bases_dev.data_ptr(), nxt.shard_offset, nxt.shard_bytes, nxt.world,
               ctx.staging[slot].data_ptr(), ctx.prefetch_ctas(nxt, 2.0 * M * N * K))

@@ -38,13 +38,15 @@ class ShardInfo:
 
 
 class FSDPContext:
-    """Owns the shard arena, the staging buffer and the ready counters of one sharding group."""
+    """Owns the shard arena, the staging buffers and the prefetch state of one sharding group."""
+
+    NS = 3   # staging buffers: the GEMM's own operand plus a prefetch distance of two
 
     def __init__(self, device, group, world, rank):
         self.device, self.group, self.world, self.rank = device, group, world, rank
         self.arena = None
-        self.staging = [None, None]   # two full-size buffers
-        self.holds = [None, None]     # weight (ShardInfo) each buffer holds, in stream order
+        self.staging = [None] * self.NS   # full-size buffers; weight i of the schedule lives in buffer i % NS
+        self.holds = [None] * self.NS     # weight (ShardInfo) each buffer holds, in stream order
         self.order = []               # sharded weights in forward execution order
         self.sharded = []
         self.stats = {"prefetched": 0, "standalone": 0}
@@ -59,7 +61,7 @@ class FSDPContext:
         # AXB_FSDP_COPY_ENGINE=0 selects the gather CTAs inside the GEMM launch instead.
         self.copy_engine = os.environ.get("AXB_FSDP_COPY_ENGINE", "1") == "1"
         self.side_stream = None
-        self.pending = [None, None]   # copy-complete event of each staging buffer
+        self.pending = [None] * self.NS   # copy-complete event of each staging buffer
 
     @staticmethod
     def shardable(m: FusedLinear, world: int) -> bool:
@@ -80,7 +82,7 @@ class FSDPContext:
         self.arena = buf
         max_full = max(m.weight.numel() for m in mods)
         max_rows = max(m.weight.shape[0] for m in mods)
-        self.staging = [torch.empty(max_full, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
+        self.staging = [torch.empty(max_full, dtype=torch.bfloat16, device=self.device) for _ in range(self.NS)]
         off = 0
         for m in mods:
             N, K = m.weight.shape
@@ -105,21 +107,14 @@ class FSDPContext:
 
     # ------------------------------------------------------------------ staging management
     def acquire(self, info: ShardInfo, backward: bool):
-        """Returns (staging tensor holding ``info``'s full weight, prefetch plan or None).
+        """Returns (staging tensor holding ``info``'s full weight, list of prefetch plans).
 
-        Called in stream order right before the GEMM that consumes the weight. The plan names
-        the weight predicted to be used next and the buffer it must be gathered into."""
+        Called in stream order right before the GEMM that consumes the weight. Every plan names a
+        weight predicted to be used soon and the buffer it must be gathered into."""
         from ..ops import _lib
 
-        if self.holds[0] is info:
-            slot = 0
-        elif self.holds[1] is info:
-            slot = 1
-        else:
-            slot = None
-        hit = slot is not None
-        if slot is None:
-            slot = 0 if self.holds[0] is None or self.holds[1] is not None else 1
+        slot = info.index % self.NS
+        hit = self.holds[slot] is info
         if self.pending[slot] is not None:   # copy engines are (or were) writing this buffer: order after them
             torch.cuda.current_stream(self.device).wait_event(self.pending[slot])
             self.pending[slot] = None
@@ -131,14 +126,16 @@ class FSDPContext:
                           "allgather_rows")
             self.holds[slot] = info
             self.stats["standalone"] += 1
-        nxt = None
-        i = info.index + (-1 if backward else 1)
-        if 0 <= i < len(self.order):
-            nxt = self.order[i]
-        plan = None
-        if nxt is not None and self.holds[1 - slot] is not nxt:
-            plan = (nxt, 1 - slot)
-        return self.staging[slot], plan
+        # the next weights of the schedule that are not resident yet (distance 1, then 2): a large weight
+        # that follows a short GEMM gets two GEMMs' worth of time to arrive
+        plans = []
+        for d in (1, 2):
+            i = info.index + (-d if backward else d)
+            if 0 <= i < len(self.order):
+                nxt = self.order[i]
+                if self.holds[i % self.NS] is not nxt:
+                    plans.append((nxt, i % self.NS))
+        return self.staging[slot], plans
 
     def prefetch_ctas(self, nxt: ShardInfo, gemm_flops: float) -> int:
         """Enough gather CTAs to finish the next weight within this GEMM's run time."""

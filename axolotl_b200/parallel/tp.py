@@ -73,7 +73,11 @@ class TPContext:
         lib = _lib.cuda_lib()
         shard = getattr(b, "_axb_shard", None)
         if shard is not None:  # FSDP-sharded weight below a TP shard: read it from its staging buffer
-            staging, _plan = shard.ctx.acquire(shard, backward=trans_b)
+            staging, plans = shard.ctx.acquire(shard, backward=trans_b)
+            if shard.ctx.copy_engine:       # next weights of the schedule arrive by the copy engines meanwhile
+                for pl in plans:
+                    shard.ctx.prefetch_by_copy(pl)
+                    shard.ctx.committed(pl)
             b = staging[: shard.rows * shard.cols].view(shard.rows, shard.cols)
         a, b = _row_major_2d(a), _row_major_2d(b)
         M, K = a.shape

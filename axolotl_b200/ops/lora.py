@@ -15,12 +15,31 @@ import torch
 from .gemm import gemm, pick_splits
 
 
+SKINNY_SPLITS = int(__import__("os").environ.get("AXB_LORA_SKINNY_SPLITS", "0"))
+
+
+def skinny_gemm(a, b, *, trans_b=False, alpha=1.0):
+    """``alpha * a @ op(b)^T`` for an output only a few columns wide ([T, R], R = adapter rank): with one
+    128-row tile per CTA such a GEMM has T/128 CTAs, too few to pull the wide operand at memory speed, so
+    the K range is split over several CTAs (fp32 atomics into a zeroed [T, R] buffer, cast once)."""
+    T = a.shape[0]
+    R = b.shape[1] if trans_b else b.shape[0]
+    K = a.shape[1]
+    tiles = (T + 127) // 128
+    sp = SKINNY_SPLITS
+    if not a.is_cuda or sp <= 1 or tiles * sp > 1024 or K < 2048:
+        return gemm(a, b, trans_b=trans_b, alpha=alpha)
+    acc = torch.zeros((T, R), dtype=torch.float32, device=a.device)
+    gemm(a, b, trans_b=trans_b, alpha=alpha, out=acc, accumulate=True, splits=sp)
+    return acc.to(torch.bfloat16)
+
+
 class _LoRALinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, W, A, B, A16, B16, scaling, blocks, bias):
         """x [T,K] bf16; W [N,K] bf16 (frozen or trainable); A [R,K] / B [N,R] fp32 masters with
         bf16 shadows A16 / B16; blocks = ((row0, rows, r0, r), ...) diagonal blocks of B."""
-        xa = gemm(x, A16, alpha=scaling)  # [T, R], already scaled
+        xa = skinny_gemm(x, A16, alpha=scaling)  # [T, R], already scaled
         y = gemm(x, W, a2=xa, b2=B16)
         if bias is not None:
             y = y + bias
@@ -37,7 +56,7 @@ class _LoRALinearFn(torch.autograd.Function):
         N, R = B16.shape
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         # t = s * dy @ B  -> [T, R]
-        t = gemm(dy, B16, trans_b=True, alpha=s)
+        t = skinny_gemm(dy, B16, trans_b=True, alpha=s)
         dx = gemm(dy, W, trans_b=True, a2=t, b2=A16) if need_dx else None
         dA = dB = None
         if ctx.needs_input_grad[2]:

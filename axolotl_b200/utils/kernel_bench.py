@@ -85,8 +85,17 @@ def bench_lora_skinny(rows):
         xa = torch.randn(T, R, device="cuda", dtype=torch.bfloat16)
         dA = torch.zeros(R, K, device="cuda", dtype=torch.float32)
         dB = torch.zeros(N, R, device="cuda", dtype=torch.float32)
+        from axolotl_b200.ops import lora as _lora
+
         t_xa = time_cuda(lambda: gemm(x, A))
         t_t = time_cuda(lambda: gemm(dy, B, trans_b=True))
+        split_note = ""
+        for sp in (2, 4):
+            _lora.SKINNY_SPLITS = sp
+            a_ = time_cuda(lambda: _lora.skinny_gemm(x, A))
+            b_ = time_cuda(lambda: _lora.skinny_gemm(dy, B, trans_b=True))
+            split_note += f" | split-K {sp}: x@A^T {a_ * 1e3:.0f} us, dy@B {b_ * 1e3:.0f} us"
+        _lora.SKINNY_SPLITS = 0
         sp_a = pick_splits((K + 255) // 256, (T + 63) // 64)
         t_dA = time_cuda(lambda: gemm(xa, x, trans_a=True, trans_b=True, out=dA, accumulate=True, splits=sp_a))
         sp_b = pick_splits((N + 127) // 128, (T + 63) // 64)

@@ -425,6 +425,7 @@ class AxolotlConfig(_Base):
     # ---- RL / preference
     rl: str | None = None
     trl: TRLConfig | None = None
+    ebft: dict | None = None      # energy-based fine-tuning block (mode, feature_layers, embed_method, coefficients)
     rl_beta: float | None = None
     dpo_beta: float | None = None
     dpo_label_smoothing: float | None = None
@@ -515,7 +516,7 @@ INERT_KEYS = {
     "batch_flattening", "bnb_config_kwargs", "cls_model_config", "comet_api_key", "comet_experiment_config",
     "comet_experiment_key", "comet_mode", "comet_online", "comet_workspace", "dion_lr", "dion_momentum",
     "dion_rank_fraction", "dion_rank_multiple_of", "dpo_generate_during_eval", "dpo_norm_loss", "dpo_padding_free",
-    "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "ebft", "embeddings_skip_upcast",
+    "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "embeddings_skip_upcast",
     "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_fuse_mlp",
     "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp32_norm_classes", "fp32_norms",
     "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",

@@ -52,6 +52,10 @@ class ExpertParallelGroup:
         # each direction (rows are staged / partially summed per rank pair). AXB_EP_DEDUP=0 moves one row
         # per slot straight between the ranks instead.
         self.dedup = os.environ.get("AXB_EP_DEDUP", "1") != "0"
+        # Transport of the staged rows: "ce" = whole peer buffers by the copy engines (peer
+        # cudaMemcpyAsync, close to link rate, no SM), "sm" = only the needed rows by a copy kernel
+        # (fewer bytes, measured ~290 GB/s). The copy engines win from 2 to 8 ranks with top-8 routing.
+        self.stage_by = os.environ.get("AXB_EP_STAGE", "ce")
         if self.fused:
             self.sync = PeerSync(self.device, group)
 
@@ -210,9 +214,15 @@ class ExpertParallelGroup:
         out = torch.empty((n, H), dtype=x.dtype, device=x.device)
         dots = torch.empty(n, dtype=torch.float32, device=x.device) if dot_with is not None else None
         src_ptrs = buf.ptrs_c
-        if self.dedup:   # needed rows of every peer -> local staging, then a local gather
-            _lib.check_rc(lib.axb_ep_stage_rows(buf.ptrs_c, self.size, self.rank, plan.need.data_ptr(),
-                                                self.staging.data_ptr(), T, H, _lib.stream_ptr()), "ep_stage_rows")
+        if self.dedup:   # rows of every peer -> local staging, then a local gather
+            if self.stage_by == "ce":
+                for r in range(self.size):
+                    if r != self.rank:
+                        self.staging[r * T * H:(r + 1) * T * H].copy_(
+                            buf.handle.get_buffer(r, (T * H,), torch.bfloat16, 0), non_blocking=True)
+            else:
+                _lib.check_rc(lib.axb_ep_stage_rows(buf.ptrs_c, self.size, self.rank, plan.need.data_ptr(),
+                                                    self.staging.data_ptr(), T, H, _lib.stream_ptr()), "ep_stage_rows")
             src_ptrs = self._slices(self.staging.data_ptr(), T * H * 2, buf.tensor.data_ptr())
         _lib.check_rc(lib.axb_ep_gather_rows(src_ptrs, self.size, plan.pad_src_rank.data_ptr(),
                                              plan.pad_src_row.data_ptr(),
@@ -250,7 +260,20 @@ class ExpertParallelGroup:
                                                  plan.pad_weight.data_ptr() if weighted else None, rows.data_ptr(),
                                                  plan.lay.max_rows, H, H, _lib.stream_ptr()), "ep_scatter_add")
             self.sync.barrier(channel=7)
-            _lib.check_rc(lib.axb_ep_reduce_rows(part.ptrs_c, self.size, self.rank, plan.sent.data_ptr(), y.data_ptr(),
+            part_ptrs = part.ptrs_c
+            if self.stage_by == "ce":
+                # every peer's partial slice for this rank -> local staging by the copy engines; the
+                # reduce kernel then reads local memory (its pointer table is biased so that
+                # "slice `rank` of peer r" lands on staging slice r)
+                from .symm import _u64_array
+
+                for r in range(self.size):
+                    if r != self.rank:
+                        self.staging[r * T * H:(r + 1) * T * H].copy_(
+                            part.handle.get_buffer(r, (T * H,), torch.bfloat16, self.rank * T * H), non_blocking=True)
+                base = self.staging.data_ptr()
+                part_ptrs = _u64_array([base + (r - self.rank) * T * H * 2 for r in range(self.size)])
+            _lib.check_rc(lib.axb_ep_reduce_rows(part_ptrs, self.size, self.rank, plan.sent.data_ptr(), y.data_ptr(),
                                                  T, H, _lib.stream_ptr()), "ep_reduce_rows")
             return y
         buf = self.y_bufs[self.ky & 1]     # zero on every rank since its last use

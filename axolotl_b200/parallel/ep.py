@@ -52,10 +52,10 @@ class ExpertParallelGroup:
         # each direction (rows are staged / partially summed per rank pair). AXB_EP_DEDUP=0 moves one row
         # per slot straight between the ranks instead.
         self.dedup = os.environ.get("AXB_EP_DEDUP", "1") != "0"
-        # Transport of the staged rows: "ce" = whole peer buffers by the copy engines (peer
-        # cudaMemcpyAsync, close to link rate, no SM), "sm" = only the needed rows by a copy kernel
-        # (fewer bytes, measured ~290 GB/s). The copy engines win from 2 to 8 ranks with top-8 routing.
-        self.stage_by = os.environ.get("AXB_EP_STAGE", "ce")
+        # Transport of the staged rows: "sm" (default) = only the needed rows by a copy kernel; "ce" = whole
+        # peer buffers by the copy engines (peer cudaMemcpyAsync). Measured on the 2-GPU Qwen3-MoE step:
+        # 370.9 ms with the row kernels, 384.3 ms with the copy engines (more bytes, one copy per peer).
+        self.stage_by = os.environ.get("AXB_EP_STAGE", "sm")
         if self.fused:
             self.sync = PeerSync(self.device, group)
 

@@ -103,7 +103,8 @@ def bench_lora_skinny(rows):
         gb = lambda elems, ms: elems * 2 / 1e6 / ms   # GB/s
         rows.append(f"lora {name} r={R}: x@A^T {t_xa * 1e3:.0f} us ({gb(T * K, t_xa) / hbm:.2f}) | dy@B {t_t * 1e3:.0f} us "
                     f"({gb(T * N, t_t) / hbm:.2f}) | dA=t^T x {t_dA * 1e3:.0f} us ({gb(T * K, t_dA) / hbm:.2f}, splits {sp_a}) | "
-                    f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b})  [fractions of {how} HBM copy rate]")
+                    f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b}){split_note}  "
+                    f"[fractions of {how} HBM copy rate]")
 
 
 def bench_attn(rows):

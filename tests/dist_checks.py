@@ -36,7 +36,10 @@ def check_gather_gemm(rt, dev, rank, world):
     ctx = FSDPContext(dev, dist.group.WORLD, world, rank)
     assert ctx.shard_model(Holder()) == 2
     dist.barrier()
-    for m, W in zip(mods, full):
+    # both transports of the prefetch: copy engines, then gather CTAs inside the GEMM launch; two
+    # passes each so that prefetched (not only stand-alone gathered) operands are consumed
+    for transport, (m, W) in [(t, mw) for t in (True, False) for _ in range(2) for mw in zip(mods, full)]:
+        ctx.copy_engine = transport
         Kk = W.shape[1]
         x = torch.randn(M, Kk, device=dev, dtype=torch.bfloat16)
         r = 16

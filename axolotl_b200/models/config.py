@@ -13,7 +13,7 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any
 
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3")
 
 
 @dataclass
@@ -114,6 +114,26 @@ class ModelConfig:
             json.dump(self.to_hf_dict(), fh, indent=2)
 
     # ------------------------------------------------------------------ derived
+    def multiplier(self, name: str) -> float:
+        """Granite's scalar multipliers (embedding / attention / residual / logits_scaling); 1 elsewhere
+        (``attention_multiplier`` falls back to 1/sqrt(head_dim))."""
+        if self.model_type != "granite":
+            return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
+        default = 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
+        v = (self.extra or {}).get(name)
+        return float(v) if v is not None else default
+
+    def uses_rope(self, idx: int) -> bool:
+        """SmolLM3 drops the rotary embedding in every layer whose ``no_rope_layers`` entry is 0."""
+        if self.model_type != "smollm3":
+            return True
+        ex = self.extra or {}
+        flags = ex.get("no_rope_layers")
+        if flags is None:
+            every = ex.get("no_rope_layer_interval", 4)
+            return (idx + 1) % every != 0
+        return bool(flags[idx])
+
     def is_moe_layer(self, idx: int) -> bool:
         return (self.num_experts > 0 and idx not in self.mlp_only_layers
                 and (idx + 1) % max(self.decoder_sparse_step, 1) == 0)
@@ -170,6 +190,8 @@ _ARCH_NAME = {
     "qwen3": "Qwen3ForCausalLM",
     "qwen3_moe": "Qwen3MoeForCausalLM",
     "mixtral": "MixtralForCausalLM",
+    "granite": "GraniteForCausalLM",
+    "smollm3": "SmolLM3ForCausalLM",
 }
 
 

@@ -28,6 +28,8 @@ ARCHS = {
     "mistral": ArchSupport(notes=("sliding-window attention is not applied: sequences up to the window are exact",)),
     "phi3": ArchSupport(tensor_parallel=False, notes=("long-rope scaling factors are not applied",)),
     "qwen2": ArchSupport(),
+    "granite": ArchSupport(notes=("embedding / attention / residual / logits multipliers are applied as scalar ops",)),
+    "smollm3": ArchSupport(notes=("layers listed in no_rope_layers run without rotary embedding",)),
     "qwen3": ArchSupport(),
     "qwen3_moe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),
     "mixtral": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),

@@ -52,13 +52,15 @@ class Attention(nn.Module):
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
         self.eps = cfg.rms_norm_eps
-        self.scale = 1.0 / math.sqrt(self.D)
+        self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
+        self.use_rope = True                                   # SmolLM3: some layers carry no position signal
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         qkv = self.qkv_proj(x)
-        qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
-                          self.q_norm.weight if self.q_norm is not None else None,
-                          self.k_norm.weight if self.k_norm is not None else None, self.eps)
+        if self.use_rope:
+            qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
+                              self.q_norm.weight if self.q_norm is not None else None,
+                              self.k_norm.weight if self.k_norm is not None else None, self.eps)
         cache = getattr(meta, "kv_cache", None)
         if cache is not None:   # generation: keep the rotated k / v of every token
             a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale)
@@ -101,6 +103,8 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
+        self.self_attn.use_rope = cfg.uses_rope(idx)
+        self.residual_multiplier = cfg.multiplier("residual_multiplier")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         if cfg.is_moe_layer(idx):
             from .moe import SparseMoE
@@ -114,11 +118,16 @@ class DecoderLayer(nn.Module):
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
         x, residual = self.input_layernorm(h, residual)
         a = self.self_attn(x, positions, inv_freq, attn_scale, meta)
+        rm = self.residual_multiplier
+        if rm != 1.0:
+            a = a * rm
         x, residual = self.post_attention_layernorm(a, residual)
         if self.is_moe:
             y, aux = self.mlp(x)
         else:
             y, aux = self.mlp(x), None
+        if rm != 1.0:
+            y = y * rm
         return y, residual, aux
 
 
@@ -252,6 +261,9 @@ class CausalLM(nn.Module):
         if self.embed_lora_At is not None and adapters_enabled():
             low = Fn.embedding(self.embed_lora_At.to(h.dtype), ids)                  # [T, r]
             h = h + self.embed_lora_scaling * linear(low, self.embed_lora_B.to(h.dtype))
+        em = cfg.multiplier("embedding_multiplier")
+        if em != 1.0:
+            h = h * em
         if self.neftune_noise_alpha and self.training:
             # noise magnitude alpha / sqrt(L * d) with L the row length (NEFTune, as applied by the HF
             # trainer the reference builds on)
@@ -283,6 +295,9 @@ class CausalLM(nn.Module):
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         h, _ = self.norm(h, residual)
+        ls = cfg.multiplier("logits_scaling")
+        if ls != 1.0:
+            h = h / ls          # logits = (h W^T) / logits_scaling, applied on the narrow side
         out = CausalLMOutput(hidden_states=h.view(B, S, -1))
         if captured is not None:
             if len(self.layers) in capture_hidden:

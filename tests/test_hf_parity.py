@@ -182,3 +182,46 @@ def test_mixtral_matches_hf(tmp_path):
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
     assert torch.allclose(got, ref, atol=3e-4, rtol=1e-3), (got - ref).abs().max()
+
+
+def test_granite_multipliers_match_hf(tmp_path):
+    cfg = ModelConfig(model_type="granite", vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      tie_word_embeddings=False)
+    cfg.extra = {"embedding_multiplier": 6.0, "attention_multiplier": 0.125, "residual_multiplier": 0.3,
+                 "logits_scaling": 4.0, "attention_dropout": 0.0}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(7)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    hf_model.eval()
+    lens = [31, 22]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+    labels = ids.clone()
+    loss = ours(ids[:, :31], pos[:, :31], labels[:, :31]).loss
+    ref_loss = hf_model(input_ids=ids[:, :31], labels=labels[:, :31]).loss
+    assert abs(loss.item() - ref_loss.item()) < 1e-4
+
+
+def test_smollm3_nope_layers_match_hf(tmp_path):
+    cfg = ModelConfig(model_type="smollm3", vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      tie_word_embeddings=False)
+    cfg.extra = {"no_rope_layers": [1, 1, 0, 1], "no_rope_layer_interval": 4, "use_sliding_window": False,
+                 "sliding_window": None, "attention_dropout": 0.0, "layer_types": ["full_attention"] * 4}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(8)
+    assert [l.self_attn.use_rope for l in ours.layers] == [True, True, False, True]
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    hf_model.eval()
+    lens = [27, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()

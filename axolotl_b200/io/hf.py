@@ -64,6 +64,9 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.weight$", name)):
             mods[m.group(1)].gate.copy_(t)
             filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.shared_expert_gate\.weight$", name)):
+            mods[m.group(1)].shared_expert_gate.copy_(t)      # Qwen2-MoE: sigmoid gate of the shared expert
+            filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(gate_up_proj|down_proj)$", name)):
             getattr(mods[m.group(1)].experts, m.group(2)).copy_(t)     # HF v5 fused expert tensors
             filled.add(name)
@@ -140,6 +143,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 sd[f"model.{name}.down_proj"] = m.down_proj.detach()
         elif hasattr(m, "gate") and isinstance(getattr(m, "gate"), torch.nn.Parameter):
             sd[f"model.{name}.gate.weight"] = m.gate.detach()
+            if getattr(m, "shared_expert_gate", None) is not None:
+                sd[f"model.{name}.shared_expert_gate.weight"] = m.shared_expert_gate.detach()
     return sd
 
 

@@ -13,7 +13,7 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any
 
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe")
 
 
 @dataclass
@@ -58,7 +58,7 @@ class ModelConfig:
             self.head_dim = self.hidden_size // self.num_attention_heads
         if self.model_type in ("qwen3", "qwen3_moe"):
             self.qk_norm = True
-        if self.model_type == "qwen2":
+        if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -76,6 +76,8 @@ class ModelConfig:
             kw.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
             if rp.get("rope_type", "default") != "default":
                 kw["rope_scaling"] = rp
+        if mt == "qwen2_moe":
+            kw.setdefault("norm_topk_prob", False)      # the HF default of this family
         if mt == "mixtral":
             kw["num_experts"] = d.get("num_local_experts", 0)
             kw["moe_intermediate_size"] = d.get("intermediate_size", 0)
@@ -191,6 +193,7 @@ _ARCH_NAME = {
     "qwen3_moe": "Qwen3MoeForCausalLM",
     "mixtral": "MixtralForCausalLM",
     "granite": "GraniteForCausalLM",
+    "qwen2_moe": "Qwen2MoeForCausalLM",
     "smollm3": "SmolLM3ForCausalLM",
 }
 

@@ -131,8 +131,32 @@ class SparseMoE(nn.Module):
                                dtype, device)
         self.aux_coef = cfg.router_aux_loss_coef
         self.ep = None  # parallel.ep.ExpertParallelGroup when experts are sharded across ranks
+        # Qwen2-MoE: a dense "shared" expert runs on every token, scaled by a sigmoid gate
+        self.shared_expert = None
+        self.shared_expert_gate = None
+        shared_I = (cfg.extra or {}).get("shared_expert_intermediate_size") if cfg.model_type == "qwen2_moe" else None
+        if shared_I:
+            from .transformer import MLP
+
+            self.shared_expert = MLP(cfg.hidden_size, shared_I, cfg.hidden_act, False, dtype, device)
+            self.shared_expert_gate = nn.Parameter(torch.empty(1, cfg.hidden_size, dtype=dtype, device=device))
+
+    def _shared(self, x):
+        g = self.shared_expert_gate
+        if x.is_cuda:   # the tensor-core GEMM wants 16-byte output rows: pad the 1-row gate to 8 rows
+            g8 = torch.cat([g, g.new_zeros(7, g.shape[1])], 0)
+            gl = linear(x, g8)[:, :1]
+        else:
+            gl = linear(x, g)
+        return torch.sigmoid(gl.float()).to(x.dtype) * self.shared_expert(x)
 
     def forward(self, x):
+        y, aux = self._routed(x)
+        if self.shared_expert is not None:
+            y = y + self._shared(x)
+        return y, aux
+
+    def _routed(self, x):
         T, H = x.shape
         logits = linear(x, self.gate)
         w, idx, probs = route_topk(logits, self.k, self.norm_topk_prob)

@@ -33,6 +33,8 @@ ARCHS = {
     "qwen3": ArchSupport(),
     "qwen3_moe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),
     "mixtral": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),
+    "qwen2_moe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True,
+                             notes=("the shared expert is a dense MLP replicated on every expert-parallel rank",)),
 }
 
 # architectures the reference lists that have no model graph here (named so that the error can say so)

@@ -13,7 +13,7 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any
 
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe")
 
 
 @dataclass
@@ -76,8 +76,10 @@ class ModelConfig:
             kw.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
             if rp.get("rope_type", "default") != "default":
                 kw["rope_scaling"] = rp
-        if mt == "qwen2_moe":
-            kw.setdefault("norm_topk_prob", False)      # the HF default of this family
+        if mt in ("qwen2_moe", "olmoe"):
+            kw.setdefault("norm_topk_prob", False)      # the HF default of these families
+        if mt == "olmoe":
+            kw.setdefault("moe_intermediate_size", d.get("intermediate_size", 0))
         if mt == "mixtral":
             kw["num_experts"] = d.get("num_local_experts", 0)
             kw["moe_intermediate_size"] = d.get("intermediate_size", 0)
@@ -194,6 +196,7 @@ _ARCH_NAME = {
     "mixtral": "MixtralForCausalLM",
     "granite": "GraniteForCausalLM",
     "qwen2_moe": "Qwen2MoeForCausalLM",
+    "olmoe": "OlmoeForCausalLM",
     "smollm3": "SmolLM3ForCausalLM",
 }
 

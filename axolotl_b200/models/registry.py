@@ -33,6 +33,8 @@ ARCHS = {
     "qwen3": ArchSupport(),
     "qwen3_moe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),
     "mixtral": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True),
+    "olmoe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True,
+                         notes=("q / k RMSNorm over all heads runs as separate norm launches before RoPE",)),
     "qwen2_moe": ArchSupport(tensor_parallel=False, expert_parallel=True, nvfp4_experts=True,
                              notes=("the shared expert is a dense MLP replicated on every expert-parallel rank",)),
 }

@@ -51,16 +51,26 @@ class Attention(nn.Module):
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=False, dtype=dtype, device=device)
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
+        self.full_qk_norm = cfg.model_type == "olmoe"   # OLMoE normalises q and k over ALL heads at once
+        if self.full_qk_norm:
+            self.q_norm = RMSNorm(self.Hq * self.D, cfg.rms_norm_eps, dtype, device)
+            self.k_norm = RMSNorm(self.Hk * self.D, cfg.rms_norm_eps, dtype, device)
         self.eps = cfg.rms_norm_eps
         self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         qkv = self.qkv_proj(x)
+        per_head_norm = self.q_norm is not None and not self.full_qk_norm
+        if self.full_qk_norm:
+            nq, nk = self.Hq * self.D, self.Hk * self.D
+            q, _ = self.q_norm(qkv[..., :nq].contiguous())
+            k, _ = self.k_norm(qkv[..., nq:nq + nk].contiguous())
+            qkv = torch.cat([q, k, qkv[..., nq + nk:]], -1)
         if self.use_rope:
             qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
-                              self.q_norm.weight if self.q_norm is not None else None,
-                              self.k_norm.weight if self.k_norm is not None else None, self.eps)
+                              self.q_norm.weight if per_head_norm else None,
+                              self.k_norm.weight if per_head_norm else None, self.eps)
         cache = getattr(meta, "kv_cache", None)
         if cache is not None:   # generation: keep the rotated k / v of every token
             a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale)

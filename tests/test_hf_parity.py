@@ -263,3 +263,38 @@ def test_qwen2_moe_shared_expert_matches_hf(tmp_path):
     again = hf_io.load_pretrained(saved, dtype=torch.float32)
     with torch.no_grad():
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+def test_olmoe_full_width_qk_norm_matches_hf(tmp_path):
+    cfg = ModelConfig(model_type="olmoe", vocab_size=300, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48, norm_topk_prob=False,
+                      tie_word_embeddings=False)
+    cfg.extra = {"clip_qkv": None, "attention_dropout": 0.0, "output_router_logits": False}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(10)
+    with torch.no_grad():
+        for l in ours.layers:
+            l.self_attn.q_norm.weight.uniform_(0.5, 1.5)
+            l.self_attn.k_norm.weight.uniform_(0.5, 1.5)
+    assert ours.layers[0].self_attn.q_norm.weight.shape == (64,) and ours.layers[0].self_attn.k_norm.weight.shape == (32,)
+    saved = None
+    for per_expert in (False, True):
+        d = str(tmp_path / f"m{int(per_expert)}")
+        hf_io.save_pretrained(ours, d, per_expert=per_expert)
+        try:
+            hf_model = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32)
+            bad = [k for k, v in hf_model.state_dict().items() if "experts" in k and float(v.abs().sum()) == 0.0]
+            if not bad:
+                saved = d
+                break
+        except Exception:
+            continue
+    if saved is None:
+        pytest.skip("this transformers version uses an expert layout that neither export form matches")
+    hf_model.eval()
+    ids, pos = _packed_inputs(300, [33])
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+        ref = hf_model(input_ids=ids).logits
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()

@@ -36,6 +36,7 @@ class LoraSpec:
     fan_in_fan_out: bool = False
     bias: str = "none"
     modules_to_save: list | None = None
+    trainable_token_indices: list | dict | None = None
     rank_pattern: dict = field(default_factory=dict)
     alpha_pattern: dict = field(default_factory=dict)
     layers_to_transform: list | None = None
@@ -53,7 +54,7 @@ class LoraSpec:
             "alpha_pattern": self.alpha_pattern, "revision": None,
             "target_modules": sorted(tm) if isinstance(tm, (list, tuple, set)) else tm,
             "target_parameters": self.target_parameters, "use_dora": self.use_dora,
-            "use_rslora": self.use_rslora,
+            "use_rslora": self.use_rslora, "trainable_token_indices": self.trainable_token_indices,
             **({"use_mora": True, "mora_type": self.mora_type} if self.use_mora else {}),
         }
 
@@ -131,6 +132,11 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
             if re.search(pat, "model.embed_tokens"):
                 r = rv
         model.add_embedding_lora(r, spec.lora_alpha, spec.use_rslora, adapter_dtype)
+    tti = spec.trainable_token_indices
+    if tti:
+        ids = tti.get("embed_tokens") if isinstance(tti, dict) else tti
+        if ids:
+            model.add_trainable_tokens(ids, adapter_dtype)
     if spec.target_parameters:
         for name, m in model.named_modules():
             if isinstance(m, Experts):
@@ -189,6 +195,8 @@ def get_peft_state_dict(model) -> dict:
             if getattr(m, "dora_magnitude", None) is not None:
                 r0, r1 = m.row_range(sub)
                 sd[f"{base}.lora_magnitude_vector"] = m.dora_magnitude.detach()[r0:r1]
+    if getattr(model, "token_rows", None) is not None:   # PEFT TrainableTokensLayer naming
+        sd["base_model.model.model.embed_tokens.token_adapter.trainable_tokens_delta"] = model.token_rows.detach()
     if getattr(model, "embed_lora_At", None) is not None:
         sd["base_model.model.model.embed_tokens.lora_embedding_A"] = model.embed_lora_At.detach().t()
         sd["base_model.model.model.embed_tokens.lora_embedding_B"] = model.embed_lora_B.detach()
@@ -236,6 +244,16 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
             elif strict:
                 raise KeyError(f"adapter tensors for {base} are missing")
         m.refresh_shadows()
+    if getattr(model, "token_rows", None) is not None:
+        kt = "base_model.model.model.embed_tokens.token_adapter.trainable_tokens_delta"
+        src = {k.replace(".default", ""): v for k, v in sd.items() if "trainable_tokens_delta" in k}
+        if kt in src:
+            with torch.no_grad():
+                model.token_rows.copy_(src[kt])
+            norm[kt] = src[kt]
+            used.add(kt)
+        elif strict:
+            raise KeyError("adapter tensor for the trainable token rows is missing")
     if getattr(model, "embed_lora_At", None) is not None:
         ka = "base_model.model.model.embed_tokens.lora_embedding_A"
         kb = "base_model.model.model.embed_tokens.lora_embedding_B"
@@ -291,6 +309,8 @@ def merge_and_unload(model):
     """Folds every adapter into its base weight (W += s * B A) and removes the adapters."""
     if getattr(model, "embed_lora_At", None) is not None:
         model.merge_embedding_lora_()
+    if getattr(model, "token_rows", None) is not None:
+        model.merge_trainable_tokens_()
     for _, m in model.fused_linears():
         if getattr(m, "mora_M", None) is not None:
             m.merge_mora_()

@@ -165,6 +165,10 @@ class CausalLM(nn.Module):
         self.embed_lora_At = None   # [vocab, r]  (transposed lora_embedding_A, so that a lookup is a row gather)
         self.embed_lora_B = None    # [hidden, r]
         self.embed_lora_scaling = 1.0
+        # trainable token rows (PEFT ``trainable_token_indices``): a few embedding rows train next to an adapter
+        self.token_rows = None      # [n, hidden] replacement rows
+        self.token_row_ids = None   # [n] vocabulary ids they replace
+        self.register_buffer("token_remap", None, persistent=False)   # [vocab] -> row index or -1
         limit = (getattr(cfg, "extra", None) or {}).get("swiglu_limit")
         if limit:
             for m in self.modules():
@@ -178,6 +182,47 @@ class CausalLM(nn.Module):
         self.embed_lora_At = nn.Parameter(torch.zeros(V, r, dtype=dtype, device=dev))
         self.embed_lora_B = nn.Parameter(torch.randn(H, r, dtype=dtype, device=dev))
         self.embed_lora_scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
+
+    def add_trainable_tokens(self, token_ids, dtype=torch.float32):
+        """The listed embedding rows become a small trainable tensor (initialised to the current rows);
+        every other row of the embedding stays frozen."""
+        dev = self.embed_tokens.device
+        ids = torch.as_tensor(sorted(set(int(t) for t in token_ids)), dtype=torch.long, device=dev)
+        if ids.numel() == 0:
+            return
+        if int(ids.max()) >= self.embed_tokens.shape[0] or int(ids.min()) < 0:
+            raise ValueError("trainable token index outside the vocabulary")
+        self.token_row_ids = ids
+        self.token_rows = nn.Parameter(self.embed_tokens.detach()[ids].to(dtype).clone())
+        remap = torch.full((self.embed_tokens.shape[0],), -1, dtype=torch.long, device=dev)
+        remap[ids] = torch.arange(ids.numel(), device=dev)
+        self.token_remap = remap
+
+    @torch.no_grad()
+    def merge_trainable_tokens_(self):
+        if self.token_rows is None:
+            return
+        self.embed_tokens[self.token_row_ids] = self.token_rows.to(self.embed_tokens.dtype)
+        self.token_rows = self.token_row_ids = self.token_remap = None
+
+    @torch.no_grad()
+    def fix_untrained_tokens(self, token_ids=None, eps=1e-16):
+        """Embedding (and lm_head) rows that were never trained -- all zeros in the checkpoint, or the ids
+        given -- are set to the mean of the trained rows, so that new chat-template tokens do not start
+        from a degenerate vector. Returns the number of rows changed."""
+        n = 0
+        for W in (self.embed_tokens, self.lm_head):
+            if W is None:
+                continue
+            if token_ids is None or token_ids is True:
+                bad = W.detach().abs().amax(1) <= eps
+            else:
+                bad = torch.zeros(W.shape[0], dtype=torch.bool, device=W.device)
+                bad[torch.as_tensor(list(token_ids), dtype=torch.long, device=W.device)] = True
+            if bool(bad.any()) and not bool(bad.all()):
+                W[bad] = W.detach()[~bad].float().mean(0).to(W.dtype)
+                n += int(bad.sum())
+        return n
 
     @torch.no_grad()
     def merge_embedding_lora_(self):
@@ -271,6 +316,10 @@ class CausalLM(nn.Module):
         if self.embed_lora_At is not None and adapters_enabled():
             low = Fn.embedding(self.embed_lora_At.to(h.dtype), ids)                  # [T, r]
             h = h + self.embed_lora_scaling * linear(low, self.embed_lora_B.to(h.dtype))
+        if self.token_rows is not None and adapters_enabled():
+            j = self.token_remap[ids]
+            hit = j >= 0
+            h = torch.where(hit[:, None], self.token_rows.to(h.dtype)[j.clamp(min=0)], h)
         em = cfg.multiplier("embedding_multiplier")
         if em != 1.0:
             h = h * em

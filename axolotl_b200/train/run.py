@@ -67,6 +67,10 @@ def build_model(cfg, device) -> CausalLM:
         from ..ops.grouped import quantize_experts_nvfp4_
 
         quantize_experts_nvfp4_(model)
+    fix = cfg.get("fix_untrained_tokens")
+    if fix:
+        n = model.fix_untrained_tokens(None if fix is True or isinstance(fix, bool) else ([fix] if isinstance(fix, int) else fix))
+        LOG.info("fix_untrained_tokens: %d embedding rows set to the mean of the trained rows", n)
     pm.call("post_model_build", cfg, model)
     return model
 
@@ -93,6 +97,7 @@ def lora_spec_from_cfg(cfg) -> LoraSpec | None:
     return LoraSpec(r=cfg["lora_r"], lora_alpha=cfg.get("lora_alpha") or cfg["lora_r"], lora_dropout=cfg.get("lora_dropout") or 0.0,
                     target_modules=tm, target_parameters=tp, use_rslora=bool(cfg.get("peft_use_rslora")),
                     use_dora=bool(cfg.get("peft_use_dora")), use_mora=use_mora,
+                    trainable_token_indices=cfg.get("peft_trainable_token_indices"),
                     mora_type=_mora_type(mora.get("mora_type", "rope")) if use_mora else 6, modules_to_save=cfg.get("lora_modules_to_save"),
                     rank_pattern=cfg.get("lora_rank_pattern") or {}, alpha_pattern=cfg.get("lora_alpha_pattern") or {},
                     layers_to_transform=cfg.get("peft_layers_to_transform"),

@@ -676,3 +676,51 @@ def test_kv_cache_generation_equals_full_recompute():
     g1 = generate_cached(m, prompts, 5, temperature=1.0, top_p=0.9, generator=torch.Generator().manual_seed(3))
     g2 = generate_cached(m, prompts, 5, temperature=1.0, top_p=0.9, generator=torch.Generator().manual_seed(3))
     assert g1 == g2
+
+
+def test_trainable_token_rows_and_fix_untrained_tokens(tmp_path):
+    import torch
+
+    from axolotl_b200.io.safetensors_io import load_file
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import LoraSpec, inject_lora, load_adapter, merge_and_unload, save_adapter
+    from axolotl_b200.models.transformer import CausalLM
+
+    cfg = preset("tiny-llama", vocab_size=200, num_hidden_layers=1, tie_word_embeddings=False)
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    with torch.no_grad():
+        model.embed_tokens[190:] = 0          # "new" tokens the base model never saw
+        model.lm_head[195:] = 0
+    assert model.fix_untrained_tokens() == 10 + 5
+    assert torch.allclose(model.embed_tokens[199], model.embed_tokens[:190].mean(0), atol=1e-6)
+    spec = LoraSpec(r=8, lora_alpha=16, target_modules=["q_proj"], trainable_token_indices=[190, 3, 199])
+    inject_lora(model, spec)
+    assert model.token_rows.shape == (3, cfg.hidden_size) and model.token_rows.requires_grad
+    ids = torch.tensor([[3, 5, 190, 7, 199, 3, 8, 9]])
+    before = model.embed_tokens.detach().clone()
+    out = model(ids, labels=ids)
+    out.loss.backward()
+    g = model.token_rows.grad if model.token_rows.grad is not None else model.token_rows._axb_grad
+    assert float(g.abs().sum()) > 0 and model.embed_tokens.grad is None
+    with torch.no_grad():
+        model.token_rows.add_(0.5)
+    model.eval()
+    with torch.no_grad():
+        adapted = model(ids, return_logits=True).logits
+    save_adapter(model, spec, str(tmp_path / "a"))
+    sd = load_file(str(tmp_path / "a" / "adapter_model.safetensors"))
+    assert sd["base_model.model.model.embed_tokens.token_adapter.trainable_tokens_delta"].shape == (3, cfg.hidden_size)
+    fresh = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    fresh.load_state_dict({k: v for k, v in model.state_dict().items() if k in fresh.state_dict()}, strict=False)
+    with torch.no_grad():
+        fresh.embed_tokens.copy_(before)
+        fresh.lm_head.copy_(model.lm_head)
+    inject_lora(fresh, spec)
+    load_adapter(fresh, str(tmp_path / "a"))
+    fresh.eval()
+    with torch.no_grad():
+        assert torch.allclose(fresh(ids, return_logits=True).logits, adapted, atol=1e-5)
+        merge_and_unload(model)
+        assert torch.allclose(model.embed_tokens[3], before[3] + 0.5, atol=1e-6)
+        assert torch.equal(model.embed_tokens[5], before[5])
+        assert torch.allclose(model(ids, return_logits=True).logits, adapted, atol=1e-4)

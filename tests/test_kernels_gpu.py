@@ -598,3 +598,60 @@ def test_decode_attention_and_cached_generation_match_full_recompute():
         outs = generate_cached(m, [[1, 5, 9], [7, 8, 9, 10, 11], [3]], 6)
         assert [len(o) for o in outs] == [6, 6, 6]
         assert outs[1][:3] == m.generate(torch.tensor([7, 8, 9, 10, 11], device="cuda"), 3, use_cache=False)[0, 5:].tolist()
+
+
+@pytest.mark.gpu
+def test_kernels_leave_poisoned_guard_bands_untouched():
+    """Out-of-bounds writes would land in the guard rows around each output; they are filled with a bit
+    pattern beforehand and must be bit-identical afterwards (odd shapes that do not fill the last tile)."""
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.ops import functional as Fn
+    from axolotl_b200.ops.gemm import gemm
+    torch.manual_seed(0)
+    dev = "cuda"
+    G = 64   # guard rows on both sides
+
+    def guarded(rows, cols, dtype):
+        big = torch.empty(rows + 2 * G, cols, dtype=dtype, device=dev)
+        big.view(torch.uint8).fill_(0xCD)
+        return big, big[G:G + rows]
+
+    def intact(big, rows):
+        v = big.view(torch.uint8)
+        return bool((v[:G] == 0xCD).all()) and bool((v[G + rows:] == 0xCD).all())
+
+    # GEMM: 1-CTA kernel (odd M, N not a tile multiple) and the CTA-pair kernel (large M, N), bf16 and fp32 out
+    for M, N, K, dt in ((200, 328, 192, torch.bfloat16), (1000, 72, 256, torch.float32), (2504, 4104, 512, torch.bfloat16)):
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        big, out = guarded(M, N, dt)
+        gemm(a, b, out=out, out_dtype=dt)
+        _lib.check_status()
+        assert intact(big, M), ("gemm", M, N, K)
+        ref = a.float() @ b.float().t()
+        assert (out.float() - ref).abs().max() / ref.abs().max() < 2e-2
+    # split-K accumulation into a guarded fp32 buffer
+    a = torch.randn(4096, 40, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(4096, 264, device=dev, dtype=torch.bfloat16)
+    big, out = guarded(40, 264, torch.float32)
+    out.zero_()
+    gemm(a, b, trans_a=True, trans_b=True, out=out, accumulate=True, splits=8)
+    assert intact(big, 40)
+    assert (out - a.float().t() @ b.float()).abs().max() < 0.5
+    # in-place kernels on a row window of a larger buffer: RoPE and cross-entropy
+    Hq, Hk, D, T = 4, 2, 64, 333
+    big, qkv = guarded(T, (Hq + 2 * Hk) * D, torch.bfloat16)
+    qkv.copy_(torch.randn_like(qkv.float()))
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    Fn.rope_qk_(qkv, pos, inv, Hq, Hk, D)
+    assert intact(big, T)
+    V = 1003
+    big, logits = guarded(77, 1008, torch.bfloat16)
+    logits.copy_(torch.randn(77, 1008, device=dev))
+    labels = torch.randint(0, V, (77,), device=dev)
+    loss = torch.empty(77, dtype=torch.float32, device=dev)
+    _lib.check_rc(_lib.cuda_lib().axb_ce_fwd_bwd(logits.data_ptr(), labels.data_ptr(), loss.data_ptr(), None, 77, V,
+                                                 logits.stride(0), 1.0, -100, 1, _lib.stream_ptr()), "ce")
+    torch.cuda.synchronize()
+    assert intact(big, 77) and torch.isfinite(loss).all()

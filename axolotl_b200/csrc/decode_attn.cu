@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(DEC_T)
     decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, int q_col0,
                        const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ lens, __nv_bfloat16* __restrict__ out, long long out_ld,
-                       int Hq, int Hk, long long max_len, float scale) {
+                       int Hq, int Hk, long long max_len, float scale, int window) {
   constexpr int DPT = (D + DEC_T - 1) / DEC_T;  // output dims per thread
   __shared__ float sq[MAX_G][D];
   __shared__ float sp[MAX_G][DEC_T];
@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(DEC_T)
   const int warp = tid >> 5, lane = tid & 31;
   const int G = Hq / Hk;
   const int n = lens[b];
+  const int first = window > 0 ? max(0, n - window) : 0;   // sliding window: only the last `window` positions
   const long long row_elems = (long long)Hk * D;
   const __nv_bfloat16* kb = kc + (long long)b * max_len * row_elems + (long long)kvh * D;
   const __nv_bfloat16* vb = vc + (long long)b * max_len * row_elems + (long long)kvh * D;
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(DEC_T)
     for (int j = 0; j < DPT; ++j) acc[g][j] = 0.f;
   }
   __syncthreads();
-  for (int c0 = 0; c0 < n; c0 += DEC_T) {
+  for (int c0 = first; c0 < n; c0 += DEC_T) {
     const int pos = c0 + tid;
     const bool valid = pos < n;
     float s[MAX_G];
@@ -141,7 +142,8 @@ __global__ void __launch_bounds__(DEC_T)
 // lens[b]: live positions of sequence b including the new token; out: [B, out_ld >= Hq*D].
 extern "C" int axb_decode_attn(const void* qkv, long long ld, int q_col0, const void* k_cache,
                                const void* v_cache, const int* lens, void* out, long long out_ld, int B,
-                               int Hq, int Hk, int D, long long max_len, float scale, void* stream) {
+                               int Hq, int Hk, int D, long long max_len, float scale, int window,
+                               void* stream) {
   if (B <= 0) return 0;
   if (Hq % Hk || Hq / Hk > MAX_G || D % 8) return -2;
   dim3 grid(Hk, B);
@@ -149,7 +151,7 @@ extern "C" int axb_decode_attn(const void* qkv, long long ld, int q_col0, const 
 #define LAUNCH(DD)                                                                                     \
   decode_attn_kernel<DD><<<grid, DEC_T, 0, st>>>((const __nv_bfloat16*)qkv, ld, q_col0,                \
                                                  (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-                                                 lens, (__nv_bfloat16*)out, out_ld, Hq, Hk, max_len, scale)
+                                                 lens, (__nv_bfloat16*)out, out_ld, Hq, Hk, max_len, scale, window)
   if (D == 64) LAUNCH(64);
   else if (D == 128) LAUNCH(128);
   else if (D == 256) LAUNCH(256);

@@ -12,6 +12,7 @@
 // flash_attention_2 interface (src/axolotl/monkeypatch/attention/flash_attn_4.py:37-111) and its
 // Triton varlen kernel (src/axolotl/monkeypatch/attention/flash_attn_d512.py:65-546).
 #include "axb_common.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -19,7 +20,7 @@ constexpr int kThreads = 192;
 constexpr int HALF_BYTES = 128 * 128;  // 128 rows x 128 B (64 bf16) swizzled tile
 
 struct AttnParams {
-  const int4* tiles;  // (doc_start, doc_len, tile_start (doc relative), flags: bit 0 = bidirectional)
+  const int4* tiles;  // (doc_start, doc_len, tile_start (doc relative), flags: bit 0 = bidirectional, bits 1.. = sliding window in tokens)
   int n_tiles;
   int Hq, Hk;
   int q_col0, k_col0, v_col0;  // element offsets of the q / k / v blocks inside a fused row
@@ -87,8 +88,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, q0 = ti.z;
   const bool bidir = ti.w & 1;  // every token of the document sees the whole document
+  const int win = bidir ? 0 : (ti.w >> 1);  // sliding window: row q sees kv rows (q - win, q]; 0 = unlimited
   const int kv_end = bidir ? doc_len : min(q0 + 128, doc_len);
-  const int n_blocks = (kv_end + 127) / 128;
+  const int jb0 = win > 0 ? max(0, q0 - win + 1) / 128 : 0;  // first kv block any row of the tile can see
+  const int n_blocks = (kv_end + 127) / 128 - jb0;           // kv blocks visited: jb0 .. jb0 + n_blocks - 1
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -151,12 +154,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int h = 0; h < C::HALVES; ++h)
           tma_load_2d(sK + st * C::TILE_BYTES + h * HALF_BYTES, &tm_qkv, &k_full[st],
-                      p.k_col0 + kv_head * D + h * 64, doc_start + j * 128);
+                      p.k_col0 + kv_head * D + h * 64, doc_start + (jb0 + j) * 128);
         mbar_expect_tx(&v_full[st], C::TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < C::HALVES; ++h)
           tma_load_2d(sV + st * C::TILE_BYTES + h * HALF_BYTES, &tm_qkv, &v_full[st],
-                      p.v_col0 + kv_head * D + h * 64, doc_start + j * 128);
+                      p.v_col0 + kv_head * D + h * 64, doc_start + (jb0 + j) * 128);
       }
     }
   } else if (warp == 1) {
@@ -226,22 +229,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_off + C::S_COL + st * 128;
-      const bool need_mask = (j == n_blocks - 1);
-      const int kv0 = j * 128;
+      const int kv0 = (jb0 + j) * 128;
+      const bool need_mask = (j == n_blocks - 1) || (win > 0 && kv0 < q0 + 128 - win);
       const int lim = (bidir ? doc_len - 1 : min(q_idx, doc_len - 1)) - kv0;  // columns <= lim are visible
+      const int lo = win > 0 ? q_idx - win + 1 - kv0 : -(1 << 30);            // columns >= lo are visible
       float mx = -INFINITY;
+      // two compiled variants of each pass: interior blocks carry no per-element compares
+      auto max_pass = [&](auto masked) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32(s_addr + c * 32, sr);
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(s_addr + c * 32, sr);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(sr[i]);
-          if (need_mask && c * 32 + i > lim) v = -INFINITY;
-          mx = fmaxf(mx, v);
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(sr[i]);
+            if constexpr (decltype(masked)::value) {
+              if (c * 32 + i > lim || c * 32 + i < lo) v = -INFINITY;
+            }
+            mx = fmaxf(mx, v);
+          }
         }
-      }
+      };
+      if (need_mask) max_pass(std::true_type{});
+      else max_pass(std::false_type{});
       const float m_new = fmaxf(m, mx * p.sl2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_use);
@@ -250,29 +261,35 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       float rowsum = 0.f;
+      auto p_pass = [&](auto masked) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32(s_addr + c * 32, sr);
-        tmem_ld_wait();
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(s_addr + c * 32, sr);
+          tmem_ld_wait();
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(sr[i]), v1 = __uint_as_float(sr[i + 1]);
-          float p0 = fast_exp2(v0 * p.sl2 - m_use), p1 = fast_exp2(v1 * p.sl2 - m_use);
-          if (need_mask && c * 32 + i > lim) p0 = 0.f;
-          if (need_mask && c * 32 + i + 1 > lim) p1 = 0.f;
-          rowsum += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        // columns [c*32, c*32+32) -> half c/2, 16-byte chunks (c%2)*4 .. +3
-        uint8_t* pbase = sP + (c >> 1) * HALF_BYTES;
+          for (int i = 0; i < 32; i += 2) {
+            float v0 = __uint_as_float(sr[i]), v1 = __uint_as_float(sr[i + 1]);
+            float p0 = fast_exp2(v0 * p.sl2 - m_use), p1 = fast_exp2(v1 * p.sl2 - m_use);
+            if constexpr (decltype(masked)::value) {
+              if (c * 32 + i > lim || c * 32 + i < lo) p0 = 0.f;
+              if (c * 32 + i + 1 > lim || c * 32 + i + 1 < lo) p1 = 0.f;
+            }
+            rowsum += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          }
+          // columns [c*32, c*32+32) -> half c/2, 16-byte chunks (c%2)*4 .. +3
+          uint8_t* pbase = sP + (c >> 1) * HALF_BYTES;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 val = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(pbase + sw128_chunk_off(r, (c & 1) * 4 + q)) = val;
+          for (int q = 0; q < 4; ++q) {
+            uint4 val = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+            *reinterpret_cast<uint4*>(pbase + sw128_chunk_off(r, (c & 1) * 4 + q)) = val;
+          }
         }
-      }
+      };
+      if (need_mask) p_pass(std::true_type{});
+      else p_pass(std::false_type{});
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
       fence_proxy_async_smem();
@@ -418,8 +435,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const bool bidir = ti.w & 1;
   // 64-row q tiles at or below the diagonal (all of the document's when it is bidirectional)
   // that intersect this rank's q rows
+  const int win = bidir ? 0 : (ti.w >> 1);  // sliding window (0 = unlimited): kv row c is seen by q rows [c, c + win)
   int q_first = bidir ? 0 : kv0 / 64;
   int q_last = (doc_len + 63) / 64;
+  if (win > 0) q_last = min(q_last, (kv0 + 127 + win - 1) / 64 + 1);
   {
     const int lo = p.q_row_off - doc_start, hi = p.q_row_off + p.q_rows - doc_start;
     if (lo > 0) q_first = max(q_first, lo / 64);
@@ -616,8 +635,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tc_fence_after();
       // Only tiles that touch the diagonal or the end of the document need per-element masks
       // (q rows outside the document already carry nlse = -inf, i.e. P = 0).
-      const bool need_mask = (!bidir && qt0 < kv0 + 127) || (kv0 + 128 > doc_len);
+      const bool need_mask = (!bidir && qt0 < kv0 + 127) || (kv0 + 128 > doc_len) || (win > 0 && qt0 + 63 >= kv0 + win);
       const bool row_in_doc = kv_idx < doc_len;
+      // q rows that see this thread's kv row: [q_lo, q_hi] (empty for kv rows beyond the document)
+      const int q_lo = row_in_doc ? (bidir ? -(1 << 30) : kv_idx) : (1 << 30);
+      const int q_hi = win > 0 ? kv_idx + win - 1 : (1 << 30);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t sr[32], dr[32];
@@ -637,7 +659,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             float pr = fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.sl2, nlv[e]));
             if (need_mask) {
               const int q = qt0 + c * 32 + i + e;
-              if (!(row_in_doc && (bidir || q >= kv_idx))) pr = 0.f;
+              if (q < q_lo || q > q_hi) pr = 0.f;
             }
             pv[e] = pr;
             dv[e] = pr * fmaf(__uint_as_float(dr[i + e]), p.scale, -dsv[e]);

@@ -127,6 +127,17 @@ class ModelConfig:
         v = (self.extra or {}).get(name)
         return float(v) if v is not None else default
 
+    def sliding_window(self) -> int:
+        """Causal sliding window in tokens (0 = full attention). Mistral / Phi-3 / Mixtral checkpoints
+        carry ``sliding_window``; Qwen2-style configs only apply theirs with ``use_sliding_window``."""
+        ex = self.extra or {}
+        w = ex.get("sliding_window")
+        if not w or self.model_type not in ("mistral", "phi3", "mixtral", "qwen2", "qwen2_moe", "smollm3"):
+            return 0
+        if self.model_type in ("qwen2", "qwen2_moe", "smollm3") and not ex.get("use_sliding_window"):
+            return 0
+        return int(w)
+
     def uses_rope(self, idx: int) -> bool:
         """SmolLM3 drops the rotary embedding in every layer whose ``no_rope_layers`` entry is 0."""
         if self.model_type != "smollm3":

@@ -25,19 +25,19 @@ class KVCache:
         self.v = torch.zeros_like(self.k)
         self.lens = torch.zeros(batch, dtype=torch.int32, device=dev)   # live positions per sequence
 
-    def attend(self, layer, qkv, meta, Hq, Hk, D, scale):
+    def attend(self, layer, qkv, meta, Hq, Hk, D, scale, window=0):
         kq, vq = qkv[:, Hq * D:(Hq + Hk) * D], qkv[:, (Hq + Hk) * D:]
         if meta.decode:
             # one new token per active sequence: row i of qkv belongs to sequence meta.seq[i]
             self.k[layer, meta.seq, meta.pos] = kq
             self.v[layer, meta.seq, meta.pos] = vq
             if meta.all_rows:
-                return Fn.decode_attention(qkv, self.k[layer], self.v[layer], meta.lens_after, Hq, Hk, D, scale)
+                return Fn.decode_attention(qkv, self.k[layer], self.v[layer], meta.lens_after, Hq, Hk, D, scale, window)
             return Fn.decode_attention(qkv, self.k[layer, meta.seq], self.v[layer, meta.seq], meta.lens_after,
-                                       Hq, Hk, D, scale)
+                                       Hq, Hk, D, scale, window)
         self.k[layer, meta.seq, meta.pos] = kq         # prefill: packed prompt rows -> (sequence, position)
         self.v[layer, meta.seq, meta.pos] = vq
-        return Fn.flash_varlen(qkv, meta.attn, Hq, Hk, D, scale)
+        return Fn.flash_varlen(qkv, meta.attn.windowed(window) if window else meta.attn, Hq, Hk, D, scale)
 
 
 class _PrefillMeta:

@@ -25,7 +25,7 @@ class ArchSupport:
 
 ARCHS = {
     "llama": ArchSupport(),
-    "mistral": ArchSupport(notes=("sliding-window attention is not applied: sequences up to the window are exact",)),
+    "mistral": ArchSupport(notes=("sliding_window is applied by the attention kernels (not with context parallelism)",)),
     "phi3": ArchSupport(tensor_parallel=False, notes=("long-rope scaling factors are not applied",)),
     "qwen2": ArchSupport(),
     "granite": ArchSupport(notes=("embedding / attention / residual / logits multipliers are applied as scalar ops",)),

@@ -58,6 +58,7 @@ class Attention(nn.Module):
         self.eps = cfg.rms_norm_eps
         self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
+        self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         qkv = self.qkv_proj(x)
@@ -73,8 +74,12 @@ class Attention(nn.Module):
                               self.k_norm.weight if per_head_norm else None, self.eps)
         cache = getattr(meta, "kv_cache", None)
         if cache is not None:   # generation: keep the rotated k / v of every token
-            a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+            a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale, self.window)
         else:
+            if self.window and getattr(meta, "causal", True):
+                if getattr(meta, "cp", False):
+                    raise NotImplementedError("sliding-window attention is not available with context parallelism")
+                meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
             a = Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
         return self.o_proj(a)
 

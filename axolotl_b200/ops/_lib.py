@@ -50,7 +50,7 @@ _CUDA_SIGS = {
     "axb_rmsnorm_gated_fwd": [vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
     "axb_rmsnorm_gated_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_entropy": [vp, vp, vp, i64, i32, i64, f32, vp],
-    "axb_decode_attn": [vp, i64, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, f32, vp],
+    "axb_decode_attn": [vp, i64, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, f32, i32, vp],
     "axb_sinkgd_step": [vp, i32, vp, vp, vp, i32, i32, i32, f32, f32, f32, vp],
     "axb_embedding_fwd": [vp, vp, vp, i64, i32, i64, vp],
     "axb_embedding_bwd": [vp, vp, vp, i64, i32, i64, vp],

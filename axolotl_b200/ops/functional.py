@@ -377,10 +377,13 @@ class AttnMeta:
     reused by every layer's forward and backward.
     """
 
-    def __init__(self, cu_seqlens, device, causal=True):
+    def __init__(self, cu_seqlens, device, causal=True, window=None):
         cu = np.asarray(cu_seqlens, dtype=np.int32)
         self.cu_seqlens_host = cu
         self.causal = bool(causal)   # False: every token attends to its whole document
+        self.window = int(window) if window else 0   # causal sliding window: token q sees (q - window, q]
+        if self.window and not self.causal:
+            raise ValueError("a sliding window applies to causal attention only")
         self.n_docs = len(cu) - 1
         self.total = int(cu[-1])
         self.max_len = int((cu[1:] - cu[:-1]).max()) if self.n_docs else 0
@@ -398,11 +401,22 @@ class AttnMeta:
                                               buf.ctypes.data, max_tiles)
                 if not self.causal:
                     buf[:n, 3] |= 1    # tile flag bit 0: bidirectional document
+                elif self.window:
+                    buf[:n, 3] |= self.window << 1   # bits 1..: sliding window in tokens
                 bufs.append(buf[:n])
             self.n_tiles = len(bufs[0])
             both = torch.from_numpy(np.concatenate(bufs, 0)).pin_memory()
             both = both.to(self.device, non_blocking=True)
             self.tiles_fwd, self.tiles_bwd = both[: self.n_tiles], both[self.n_tiles:]
+
+    def windowed(self, window):
+        """The same documents with a causal sliding window (cached: every layer of a model asks for it)."""
+        if not window or window >= self.max_len:
+            return self            # no document is longer than the window: plain causal attention is exact
+        cache = self.__dict__.setdefault("_windowed", {})
+        if window not in cache:
+            cache[window] = AttnMeta(self.cu_seqlens_host, self.device, True, window)
+        return cache[window]
 
     @staticmethod
     def from_position_ids(position_ids, device, causal=True):
@@ -415,7 +429,7 @@ class AttnMeta:
         return AttnMeta(cu, device, causal)
 
 
-def _attn_ref(q, k, v, cu, scale, causal=True):
+def _attn_ref(q, k, v, cu, scale, causal=True, window=0):
     # q [T,Hq,D], k/v [T,Hk,D]; per-document (causal or bidirectional) attention in fp32
     T, Hq, D = q.shape
     Hk = k.shape[1]
@@ -429,6 +443,8 @@ def _attn_ref(q, k, v, cu, scale, causal=True):
         sc = (qq @ kk.transpose(1, 2)) * scale
         if causal:
             mask = torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril()
+            if window:
+                mask &= ~torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril(-int(window))
             sc = sc.masked_fill(~mask, float("-inf"))
         out[s:e] = (sc.softmax(-1) @ vv).transpose(0, 1).to(q.dtype)
     return out
@@ -484,7 +500,7 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     if getattr(meta, "cp", False):
-        from ..parallel.cp import flash_varlen_cp   # context parallelism is causal only
+        from ..parallel.cp import flash_varlen_cp   # context parallelism is causal only, without a window
 
         return flash_varlen_cp(qkv, meta, Hq, Hk, D, scale)
     if qkv.is_cuda:
@@ -493,16 +509,18 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     q = qkv[:, : Hq * D].reshape(T, Hq, D)
     k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
     v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, D)
-    return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True)).reshape(T, Hq * D)
+    return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True),
+                     getattr(meta, "window", 0)).reshape(T, Hq * D)
 
 
 @torch.no_grad()
-def decode_attention(qkv, k_cache, v_cache, lens, Hq, Hk, D, scale=None):
+def decode_attention(qkv, k_cache, v_cache, lens, Hq, Hk, D, scale=None, window=0):
     """Attention of ONE new token per sequence against its KV cache (generation).
 
     ``qkv`` [B, (Hq + 2*Hk) * D]: fused projection of the new tokens, q / k already rotated;
     ``k_cache`` / ``v_cache`` [B, max_len, Hk * D] with the new token's k / v already stored at
     position ``lens[b] - 1``; ``lens`` [B] int32: live positions including the new token.
+    ``window`` > 0 restricts every query to its last ``window`` positions.
     Returns [B, Hq * D]. Inference only (no autograd)."""
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     B = qkv.shape[0]
@@ -511,14 +529,15 @@ def decode_attention(qkv, k_cache, v_cache, lens, Hq, Hk, D, scale=None):
         out = torch.empty((B, Hq * D), dtype=qkv.dtype, device=qkv.device)
         _lib.check_rc(lib.axb_decode_attn(qkv.data_ptr(), qkv.stride(0), 0, k_cache.data_ptr(), v_cache.data_ptr(),
                                           lens.data_ptr(), out.data_ptr(), out.stride(0), B, Hq, Hk, D,
-                                          k_cache.shape[1], scale, _lib.stream_ptr()), "decode_attn")
+                                          k_cache.shape[1], scale, int(window or 0), _lib.stream_ptr()), "decode_attn")
         return out
     q = qkv[:, : Hq * D].reshape(B, Hk, Hq // Hk, D).float()
     out = torch.empty(B, Hq * D, dtype=qkv.dtype)
     for b in range(B):
         n = int(lens[b])
-        k = k_cache[b, :n].reshape(n, Hk, D).float().transpose(0, 1)     # [Hk, n, D]
-        v = v_cache[b, :n].reshape(n, Hk, D).float().transpose(0, 1)
+        s0 = max(0, n - int(window)) if window else 0
+        k = k_cache[b, s0:n].reshape(n - s0, Hk, D).float().transpose(0, 1)     # [Hk, n, D]
+        v = v_cache[b, s0:n].reshape(n - s0, Hk, D).float().transpose(0, 1)
         p = torch.softmax((q[b] @ k.transpose(1, 2)) * scale, -1)        # [Hk, G, n]
         out[b] = (p @ v).reshape(-1).to(qkv.dtype)
     return out

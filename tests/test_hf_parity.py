@@ -298,3 +298,31 @@ def test_olmoe_full_width_qk_norm_matches_hf(tmp_path):
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
     assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+
+
+def test_mistral_sliding_window_matches_hf(tmp_path):
+    cfg = ModelConfig(model_type="mistral", vocab_size=360, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-5, rope_theta=10000.0)
+    cfg.extra = {"sliding_window": 12}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(5)
+    assert ours.layers[0].self_attn.window == 12
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [45, 9, 30]
+    ids, pos = _packed_inputs(360, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+    # the window matters here: full causal attention gives different logits for late tokens
+    full = CausalLM(ModelConfig.from_hf_dict({**cfg.to_hf_dict(), "sliding_window": None}), dtype=torch.float32)
+    full.load_state_dict(ours.state_dict())
+    full.eval()
+    with torch.no_grad():
+        assert (full(ids, pos, return_logits=True).logits - got)[0, 40].abs().max() > 1e-3
+    # cached decoding honours the window as well
+    p = ids[0, :30]
+    assert torch.equal(ours.generate(p, 6), ours.generate(p, 6, use_cache=False))

@@ -655,3 +655,36 @@ def test_kernels_leave_poisoned_guard_bands_untouched():
                                                  logits.stride(0), 1.0, -100, 1, _lib.stream_ptr()), "ce")
     torch.cuda.synchronize()
     assert intact(big, 77) and torch.isfinite(loss).all()
+
+
+@pytest.mark.gpu
+def test_flash_varlen_sliding_window_matches_fp32_reference():
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    Hq, Hk, D = 8, 2, 128
+    cu = [0, 700, 829, 1500, 1536]
+    T = cu[-1]
+    for window in (300, 128, 50):
+        qkv = (torch.randn(T, (Hq + 2 * Hk) * D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+        dout = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+        meta = Fn.AttnMeta(cu, "cuda", window=window)
+        out = Fn.flash_varlen(qkv, meta, Hq, Hk, D)
+        out.backward(dout)
+        x = qkv.detach().float().requires_grad_(True)
+        q = x[:, :Hq * D].reshape(T, Hq, D)
+        k = x[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D)
+        v = x[:, (Hq + Hk) * D:].reshape(T, Hk, D)
+        ref = Fn._attn_ref(q, k, v, cu, 1.0 / D ** 0.5, True, window).reshape(T, Hq * D)
+        ref.backward(dout.float())
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), (window, (out.float() - ref).abs().max())
+        err = (qkv.grad.float() - x.grad).abs().max() / x.grad.abs().max()
+        assert err < 3e-2, (window, err)
+    # decode attention with a window
+    B, max_len = 3, 500
+    lens = torch.tensor([40, 300, 500], dtype=torch.int32, device="cuda")
+    qd = torch.randn(B, (Hq + 2 * Hk) * D, device="cuda").to(torch.bfloat16)
+    kc = torch.randn(B, max_len, Hk * D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(B, max_len, Hk * D, device="cuda").to(torch.bfloat16)
+    o = Fn.decode_attention(qd, kc, vc, lens, Hq, Hk, D, window=200)
+    r = Fn.decode_attention(qd.cpu(), kc.cpu(), vc.cpu(), lens.cpu(), Hq, Hk, D, window=200)
+    assert torch.allclose(o.float().cpu(), r.float(), atol=2e-2, rtol=2e-2)

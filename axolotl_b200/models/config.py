@@ -154,8 +154,8 @@ class ModelConfig:
                 and (idx + 1) % max(self.decoder_sparse_step, 1) == 0)
 
     def rope_inv_freq(self):
-        """(inv_freq tensor [head_dim/2] fp32, attention scaling factor) incl. llama3 / linear /
-        yarn-free variants of ``rope_scaling``."""
+        """(inv_freq tensor [head_dim/2] fp32, attention scaling factor) incl. the llama3, linear
+        and yarn variants of ``rope_scaling``."""
         import torch
 
         D = self.head_dim
@@ -174,6 +174,37 @@ class ModelConfig:
                 scaled = torch.where(wavelen > old / lo, inv / factor, inv)
                 mid = (wavelen <= old / lo) & (wavelen >= old / hi)
                 inv = torch.where(mid, (1 - smooth) * inv / factor + smooth * inv, scaled)
+            elif kind == "yarn":
+                # NTK-by-parts (YaRN): high-frequency dimensions keep their wavelength, low-frequency ones
+                # are interpolated by `factor`, with a linear ramp between the two correction dimensions;
+                # cos / sin are scaled by the attention factor 0.1 ln(factor) + 1
+                factor = float(rs["factor"])
+                old = rs.get("original_max_position_embeddings") or self.max_position_embeddings
+                beta_fast, beta_slow = rs.get("beta_fast") or 32.0, rs.get("beta_slow") or 1.0
+                mscale, mscale_all = rs.get("mscale"), rs.get("mscale_all_dim")
+
+                def get_mscale(f, m=1.0):
+                    return 1.0 if f <= 1 else 0.1 * m * math.log(f) + 1.0
+
+                if rs.get("attention_factor") is not None:
+                    scale = float(rs["attention_factor"])
+                elif mscale and mscale_all:
+                    scale = get_mscale(factor, mscale) / get_mscale(factor, mscale_all)
+                else:
+                    scale = get_mscale(factor)
+
+                def corr_dim(n_rot):
+                    return (D * math.log(old / (n_rot * 2 * math.pi))) / (2 * math.log(self.rope_theta))
+
+                low, high = corr_dim(beta_fast), corr_dim(beta_slow)
+                if rs.get("truncate", True):
+                    low, high = math.floor(low), math.ceil(high)
+                low, high = max(low, 0), min(high, D - 1)
+                if low == high:
+                    high += 0.001
+                ramp = ((torch.arange(D // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+                extrap = 1 - ramp
+                inv = (inv / factor) * (1 - extrap) + inv * extrap
             elif kind in ("default", None):
                 pass
             else:

@@ -326,3 +326,22 @@ def test_mistral_sliding_window_matches_hf(tmp_path):
     # cached decoding honours the window as well
     p = ids[0, :30]
     assert torch.equal(ours.generate(p, 6), ours.generate(p, 6, use_cache=False))
+
+
+def test_yarn_rope_scaling_matches_hf(tmp_path):
+    cfg = ModelConfig(model_type="qwen3", vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=10000.0,
+                      max_position_embeddings=256,
+                      rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64})
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(11)
+    inv, scale = cfg.rope_inv_freq()
+    assert abs(scale - (0.1 * np.log(4.0) + 1.0)) < 1e-6
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    hf_model.eval()
+    ids, pos = _packed_inputs(300, [150])
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+        ref = hf_model(input_ids=ids).logits
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()

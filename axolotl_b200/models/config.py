@@ -205,11 +205,41 @@ class ModelConfig:
                 ramp = ((torch.arange(D // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
                 extrap = 1 - ramp
                 inv = (inv / factor) * (1 - extrap) + inv * extrap
+            elif kind == "longrope":
+                # Phi-3 long context: per-dimension rescale factors, one set for sequences within the
+                # original context (returned here) and one beyond it (``rope_inv_freq_long``)
+                inv = inv / torch.tensor(rs["short_factor"], dtype=torch.float32)
+                scale = self._longrope_attention_factor()
             elif kind in ("default", None):
                 pass
             else:
                 raise ValueError(f"rope_scaling type '{kind}' is not supported")
         return inv, scale
+
+    def _longrope_orig(self) -> int:
+        rs = self.rope_scaling or {}
+        return int(rs.get("original_max_position_embeddings") or (self.extra or {}).get("original_max_position_embeddings")
+                   or self.max_position_embeddings)
+
+    def _longrope_attention_factor(self) -> float:
+        rs = self.rope_scaling or {}
+        if rs.get("attention_factor") is not None:
+            return float(rs["attention_factor"])
+        orig = self._longrope_orig()
+        factor = rs.get("factor") or self.max_position_embeddings / orig
+        return 1.0 if factor <= 1.0 else math.sqrt(1 + math.log(factor) / math.log(orig))
+
+    def rope_inv_freq_long(self):
+        """(inv_freq for documents longer than the original context, that context length) for the
+        ``longrope`` scaling of Phi-3; None for every other configuration."""
+        import torch
+
+        rs = self.rope_scaling
+        if not rs or rs.get("rope_type", rs.get("type")) != "longrope":
+            return None
+        D = self.head_dim
+        inv = 1.0 / (self.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        return inv / torch.tensor(rs["long_factor"], dtype=torch.float32), self._longrope_orig()
 
     def num_params(self, include_embeddings: bool = True) -> int:
         H, L, V = self.hidden_size, self.num_hidden_layers, self.vocab_size

@@ -26,7 +26,7 @@ class ArchSupport:
 ARCHS = {
     "llama": ArchSupport(),
     "mistral": ArchSupport(notes=("sliding_window is applied by the attention kernels (not with context parallelism)",)),
-    "phi3": ArchSupport(tensor_parallel=False, notes=("long-rope scaling factors are not applied",)),
+    "phi3": ArchSupport(tensor_parallel=False, notes=("longrope: the long factors apply when a document exceeds the original context",)),
     "qwen2": ArchSupport(),
     "granite": ArchSupport(notes=("embedding / attention / residual / logits multipliers are applied as scalar ops",)),
     "smollm3": ArchSupport(notes=("layers listed in no_rope_layers run without rotary embedding",)),

@@ -161,6 +161,10 @@ class CausalLM(nn.Module):
         inv, scale = cfg.rope_inv_freq()
         self.register_buffer("inv_freq", inv.to(device) if device is not None else inv, persistent=False)
         self.attn_scale = scale
+        long = cfg.rope_inv_freq_long()      # Phi-3 longrope: second frequency set for long documents
+        self.longrope_orig = long[1] if long is not None else 0
+        self.register_buffer("inv_freq_long", (long[0].to(device) if device is not None else long[0]) if long is not None
+                             else None, persistent=False)
         self.gradient_checkpointing = False
         self.ce_chunk_rows = 2048
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
@@ -333,6 +337,9 @@ class CausalLM(nn.Module):
             # trainer the reference builds on)
             mag = float(self.neftune_noise_alpha) / math.sqrt(S * h.shape[-1])
             h = h + (torch.rand_like(h) * 2 - 1) * mag
+        inv_freq = self.inv_freq
+        if self.longrope_orig and getattr(attn_meta, "max_len", 0) > self.longrope_orig:
+            inv_freq = self.inv_freq_long
         residual = None
         aux_total = None
         captured = {} if capture_hidden is not None else None
@@ -346,10 +353,10 @@ class CausalLM(nn.Module):
             if hooks is not None:
                 hooks.pre_layer(i)
             if self.gradient_checkpointing and self.training:
-                h, residual, aux = checkpoint(layer, h, residual, pos, self.inv_freq, self.attn_scale,
+                h, residual, aux = checkpoint(layer, h, residual, pos, inv_freq, self.attn_scale,
                                               attn_meta, use_reentrant=False)
             else:
-                h, residual, aux = layer(h, residual, pos, self.inv_freq, self.attn_scale, attn_meta)
+                h, residual, aux = layer(h, residual, pos, inv_freq, self.attn_scale, attn_meta)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
             if captured is not None and (i + 1) in capture_hidden and i + 1 < len(self.layers):

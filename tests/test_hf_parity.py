@@ -345,3 +345,27 @@ def test_yarn_rope_scaling_matches_hf(tmp_path):
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
     assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+
+
+def test_phi3_longrope_short_and_long_factors_match_hf(tmp_path):
+    D = 16
+    cfg = ModelConfig(model_type="phi3", vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=D, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      tie_word_embeddings=False, max_position_embeddings=256,
+                      rope_scaling={"rope_type": "longrope", "short_factor": [1.0 + 0.05 * i for i in range(D // 2)],
+                                    "long_factor": [1.5 + 0.3 * i for i in range(D // 2)],
+                                    "original_max_position_embeddings": 64})
+    cfg.extra = {"pad_token_id": 0, "bos_token_id": 1, "eos_token_id": 2, "original_max_position_embeddings": 64,
+                 "sliding_window": None, "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attention_dropout": 0.0,
+                 "partial_rotary_factor": 1.0}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(12)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    hf_model.eval()
+    ours.eval()
+    for n in (40, 150):      # within / beyond the original context: short / long factors
+        ids, pos = _packed_inputs(320, [n])
+        with torch.no_grad():
+            got = ours(ids, pos, return_logits=True).logits
+            ref = hf_model(input_ids=ids).logits
+        assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (n, (got - ref).abs().max())

@@ -147,7 +147,7 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
     if opt in ("adamw_bnb_8bit", "adamw_8bit", "paged_adamw_8bit", "paged_adamw_32bit", "lion_8bit", "ao_adamw_8bit",
                "ao_adamw_4bit", "ao_adamw_fp8"):
         raise ValueError(f"optimizer '{opt}' needs bitsandbytes/torchao, which are not available; use `adamw_torch_fused`")
-    if opt in ("muon", "dion", "galore_adamw", "q_galore_adamw8bit", "came_pytorch", "optimi_adamw", "flash_adamw"):
+    if opt in ("dion", "galore_adamw", "q_galore_adamw8bit", "optimi_adamw", "flash_adamw"):
         raise ValueError(f"optimizer '{opt}' is not implemented on axolotl_b200")
 
     # ---- parallelism

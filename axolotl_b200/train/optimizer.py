@@ -255,6 +255,8 @@ class TorchOptimizerAdapter:
         self.lr = opt.param_groups[0]["lr"]
         self._base_lrs = [g["lr"] for g in opt.param_groups]
 
+    moment_shard = None   # state lives inside the wrapped torch optimizer, never sharded by the fused runtime
+
     def zero_grad(self):
         self.opt.zero_grad(set_to_none=True)
 
@@ -278,8 +280,6 @@ class TorchOptimizerAdapter:
             g["active"] = keep is None or not tag or tag in keep
 
     def step(self, lr=None, gnorm_sq=None):
-        if self.moment_shard is not None:
-            raise RuntimeError("this optimizer holds sharded moments: it is stepped by the fused parallel runtime")
         self.step_count += 1
         if lr is not None:
             for g, b in zip(self.opt.param_groups, self._base_lrs):

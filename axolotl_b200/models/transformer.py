@@ -119,6 +119,7 @@ class DecoderLayer(nn.Module):
         self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
         self.self_attn.use_rope = cfg.uses_rope(idx)
+        self.self_attn.window = cfg.sliding_window(idx)
         self.residual_multiplier = cfg.multiplier("residual_multiplier")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         if cfg.is_moe_layer(idx):

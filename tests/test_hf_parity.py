@@ -369,3 +369,22 @@ def test_phi3_longrope_short_and_long_factors_match_hf(tmp_path):
             got = ours(ids, pos, return_logits=True).logits
             ref = hf_model(input_ids=ids).logits
         assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (n, (got - ref).abs().max())
+
+
+def test_qwen3_per_layer_sliding_window_matches_hf(tmp_path):
+    cfg = ModelConfig(model_type="qwen3", vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=3,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=10000.0)
+    cfg.extra = {"use_sliding_window": True, "sliding_window": 10, "max_window_layers": 1,
+                 "layer_types": ["full_attention", "sliding_attention", "sliding_attention"]}
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(13)
+    assert [l.self_attn.window for l in ours.layers] == [0, 10, 10]
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    ids, pos = _packed_inputs(300, [40])
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+        ref = hf_model(input_ids=ids).logits
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()

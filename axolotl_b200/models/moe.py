@@ -121,6 +121,34 @@ class Experts(nn.Module):
         return torch.cat(outs, 0)
 
 
+class _DenseRouterGrad(torch.autograd.Function):
+    """Straight-through router gradient (DenseMixer): the forward value is zero, the backward pass
+    hands every NON-selected expert e of token t the gradient <dy_t, O_e(x_t)> on its router
+    probability, as if the layer output were the dense mixture sum_e p_e O_e(x). The selected experts
+    get theirs through the sparse path. Costs one evaluation of every expert on every token in the
+    backward pass (no expert or input gradient is taken through it)."""
+
+    @staticmethod
+    def forward(ctx, probs, x, idx, moe):
+        ctx.moe, ctx.E = moe, probs.shape[1]
+        ctx.save_for_backward(x, idx)
+        return x.new_zeros(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, idx = ctx.saved_tensors
+        T, E = x.shape[0], ctx.E
+        g = torch.zeros(T, E, dtype=torch.float32, device=x.device)
+        dyf = dy.float()
+        with torch.no_grad():
+            for e in range(E):
+                counts = [0] * E
+                counts[e] = T
+                g[:, e] = (dyf * ctx.moe.experts(x, counts).float()).sum(-1)
+        sel = torch.zeros(T, E, dtype=torch.bool, device=x.device).scatter_(1, idx, True)
+        return g.masked_fill(sel, 0.0), None, None, None
+
+
 class SparseMoE(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
@@ -131,6 +159,7 @@ class SparseMoE(nn.Module):
                                dtype, device)
         self.aux_coef = cfg.router_aux_loss_coef
         self.ep = None  # parallel.ep.ExpertParallelGroup when experts are sharded across ranks
+        self.dense_mixer = False   # DenseMixer plugin: straight-through router gradient over all experts
         # Qwen2-MoE: a dense "shared" expert runs on every token, scaled by a sigmoid gate
         self.shared_expert = None
         self.shared_expert_gate = None
@@ -152,6 +181,10 @@ class SparseMoE(nn.Module):
 
     def forward(self, x):
         y, aux = self._routed(x)
+        if self.dense_mixer and self.training and torch.is_grad_enabled():
+            if self.ep is not None:
+                raise NotImplementedError("dense_mixer needs all experts on the rank (no expert parallelism)")
+            y = y + _DenseRouterGrad.apply(self._last_probs, x.detach(), self._last_idx, self)
         if self.shared_expert is not None:
             y = y + self._shared(x)
         return y, aux
@@ -160,6 +193,8 @@ class SparseMoE(nn.Module):
         T, H = x.shape
         logits = linear(x, self.gate)
         w, idx, probs = route_topk(logits, self.k, self.norm_topk_prob)
+        if self.dense_mixer:
+            self._last_probs, self._last_idx = probs, idx
         aux = load_balance_loss(probs, idx, self.E) if self.training or self.aux_coef else None
         if self.ep is not None:
             y = self.ep.dispatch_compute_combine(self.experts, x, w, idx)

@@ -55,6 +55,7 @@ _BUNDLED = {
     "kd": "axolotl_b200.plugins.kd.KDPlugin",
     "mora": "axolotl_b200.plugins.compat.MoraPlugin",
     "diffusion": "axolotl_b200.plugins.diffusion.DiffusionPlugin",
+    "densemixer": "axolotl_b200.plugins.compat.DenseMixerPlugin",
     "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
     "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -74,6 +75,7 @@ _ALIASES = {
     "axolotl.integrations.kd.KDPlugin": "kd",
     "axolotl.integrations.mora.MoraPlugin": "mora",
     "axolotl.integrations.diffusion.DiffusionPlugin": "diffusion",
+    "axolotl.integrations.densemixer.DenseMixerPlugin": "densemixer",
     "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
     "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
 }

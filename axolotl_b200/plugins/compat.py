@@ -59,3 +59,35 @@ class MoraPlugin(BasePlugin):
             from ..models.mora import mora_type_id
 
             mora_type_id((cfg.get("mora") or {}).get("mora_type", "rope"))   # raises on an unknown variant
+
+
+class DenseMixerArgs(BaseModel):
+    dense_mixer: bool | None = True
+
+
+class DenseMixerPlugin(BasePlugin):
+    """DenseMixer: a more precise router gradient for sparse MoE layers at the price of evaluating
+    every expert on every token in the backward pass (reference:
+    src/axolotl/integrations/densemixer/plugin.py:11-42, which patches OLMoE / Qwen2-MoE / Qwen3-MoE
+    through the external ``densemixer`` package). Here it is a switch on ``models.moe.SparseMoE``."""
+
+    SUPPORTED = ("olmoe", "qwen2_moe", "qwen3_moe")
+
+    def get_input_args(self):
+        return DenseMixerArgs
+
+    def post_model_build(self, cfg, model):
+        if cfg.get("dense_mixer") is False:
+            return
+        if model.config.model_type not in self.SUPPORTED:
+            raise ValueError(f"dense_mixer supports {self.SUPPORTED}, not '{model.config.model_type}'")
+        if (cfg.get("expert_parallel_size") or 1) > 1:
+            raise ValueError("dense_mixer cannot be combined with expert parallelism")
+        n = 0
+        for m in model.modules():
+            if hasattr(m, "dense_mixer"):
+                m.dense_mixer = True
+                n += 1
+        from ..utils.logging import get_logger
+
+        get_logger(__name__).info("DenseMixer router gradient enabled on %d MoE layers", n)

@@ -783,3 +783,41 @@ def test_every_torch_optimizer_steps_through_the_run_builder(tmp_path):
                                       "max_length": 48, "max_input_id": 300}]})
         _, _, trainer = train(cfg)
         assert trainer.global_step == 2, name
+
+
+def test_densemixer_router_gradient_is_the_dense_mixture_gradient():
+    import torch
+
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+
+    cfg = preset("tiny-qwen3-moe", vocab_size=97, num_hidden_layers=1)
+    cfg.norm_topk_prob = False
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    moe = model.layers[0].mlp
+    x = torch.randn(6, cfg.hidden_size)
+    dy = torch.randn(6, cfg.hidden_size)
+    model.train()
+
+    def router_grad(dense):
+        moe.dense_mixer = dense
+        moe.gate.grad = None
+        y, _ = moe(x)
+        (y * dy).sum().backward()
+        return moe.gate.grad.clone()
+
+    g_sparse, g_dense = router_grad(False), router_grad(True)
+    assert (g_sparse - g_dense).abs().max() > 1e-4
+    # reference: dense mixture y = sum_e p_e O_e(x), gradient w.r.t. the router weight only
+    gate = moe.gate.detach().clone().requires_grad_(True)
+    probs = torch.softmax(x @ gate.t(), -1)
+    with torch.no_grad():
+        outs = []
+        for e in range(moe.E):
+            counts = [0] * moe.E
+            counts[e] = 6
+            outs.append(moe.experts(x, counts))
+        O = torch.stack(outs, 1)                                  # [T, E, H]
+    ((probs[:, :, None] * O).sum(1) * dy).sum().backward()
+    assert torch.allclose(g_dense, gate.grad, atol=1e-4, rtol=1e-3), (g_dense - gate.grad).abs().max()
+    moe.dense_mixer = False

@@ -179,8 +179,8 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
         if not eb:
             raise ValueError("`ebft` config section is required when `rl: ebft` is set. "
                              "Add an `ebft:` section with at least `mode: structured`.")
-        if (eb.get("mode") or "structured") != "structured":
-            raise ValueError("ebft.mode: strided (anchors inside unstructured text) is not available; use mode: structured")
+        if (eb.get("mode") or "structured") not in ("structured", "strided"):
+            raise ValueError(f"unknown ebft.mode '{eb.get('mode')}' (structured or strided)")
         if eb.get("embed_method") not in (None, "last_token", "mean_pooling", "completion_mean", "concat"):
             raise ValueError(f"unknown ebft.embed_method '{eb.get('embed_method')}'")
     if rl in ("grpo", "gdpo") and not (g("trl") or {}).get("reward_funcs"):

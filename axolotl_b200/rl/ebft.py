@@ -11,8 +11,12 @@ layer count), pooled per sequence (``last_token`` / ``mean_pooling`` / ``complet
 generated embeddings. The frozen feature network is the policy itself with its adapters
 switched off (or a frozen copy for a full fine-tune). All sequences of a batch are scored in
 packed varlen rows: one forward per ~``tokens_per_row`` tokens instead of one per padded batch.
-The strided mode for unstructured text (anchors every ``stride`` tokens inside a document) is not
-implemented.
+Strided mode (unstructured text) is expressed through the same machinery: every ``stride`` tokens of
+a document is an anchor; the ``context_length`` tokens before it are the prompt and the
+``generate_max_len`` tokens after it the ground truth (``strided_records``), sampled
+``n_samples_per_prompt`` times with the leave-one-out (RLOO) baseline. The reference evaluates all
+anchors of a document in one forward pass with a block-structured mask
+(src/axolotl/core/trainers/ebft/strided.py); here each anchor is its own short packed document.
 """
 from __future__ import annotations
 
@@ -153,3 +157,40 @@ class FeatureMatchingReward:
         r, m = feature_rewards(emb[: len(gen)], emb[len(gen):], n, self.a, self.d, self.whiten)
         self.last_metrics = m
         return [float(x) for x in r.cpu()]
+
+
+def strided_records(token_docs, stride=8, context_length=8, generate_max_len=8, min_completion_prefix=0,
+                    bos_token_id=None):
+    """Anchor records for strided EBFT from tokenised documents: ``prompt_ids`` = the
+    ``context_length`` tokens before the anchor (BOS-prefixed when given), ``ground_truth`` = the
+    ``generate_max_len`` tokens after it. Anchors need a full-length continuation."""
+    recs = []
+    for doc in token_docs:
+        doc = [int(t) for t in doc]
+        first = max(1, context_length if min_completion_prefix <= 0 else min_completion_prefix)
+        for a in range(first, len(doc) - generate_max_len + 1, max(1, stride)):
+            ctx = doc[max(0, a - context_length):a]
+            if bos_token_id is not None and (not ctx or ctx[0] != bos_token_id):
+                ctx = [bos_token_id] + ctx
+            recs.append({"prompt_ids": ctx, "ground_truth": doc[a:a + generate_max_len]})
+    return recs
+
+
+def load_strided_records(cfg, tokenizer):
+    """Reads the configured datasets as raw text (``text`` field, or pre-tokenised ``input_ids``)."""
+    from ..data.loading import _shard, read_raw
+
+    eb = dict(cfg.get("ebft") or {})
+    docs = []
+    for d in cfg.get("datasets") or []:
+        field = d.get("field") or "text"
+        for r in _shard(read_raw(dict(d)), dict(d)):
+            if "input_ids" in r:
+                docs.append(r["input_ids"])
+            else:
+                if tokenizer is None:
+                    raise ValueError("strided EBFT on text datasets needs a tokenizer")
+                docs.append(tokenizer(r[field], add_special_tokens=False)["input_ids"])
+    bos = tokenizer.bos_token_id if tokenizer is not None else cfg.get("bos_token_id")
+    return strided_records(docs, eb.get("stride") or 8, eb.get("context_length") or 8, eb.get("generate_max_len") or 8,
+                           eb.get("min_completion_prefix") or 0, bos)

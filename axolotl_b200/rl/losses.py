@@ -167,8 +167,11 @@ def grpo_loss(tok_logp, old_logp, ref_logp, advantages, seq_ids, n_seq, mask, *,
 
 def group_advantages(rewards, group_size, scale_rewards="group", eps=1e-4):
     """rewards [G * group_size] -> advantages: reward minus the group mean, divided by the group
-    (or batch) standard deviation unless ``scale_rewards`` is 'none'."""
+    (or batch) standard deviation unless ``scale_rewards`` is 'none'. 'rloo' uses the leave-one-out
+    baseline instead (reward minus the mean of the OTHER samples of the group, unscaled)."""
     r = rewards.view(-1, group_size)
+    if scale_rewards == "rloo" and group_size > 1:
+        return (r - (r.sum(1, keepdim=True) - r) / (group_size - 1)).reshape(-1)
     adv = r - r.mean(1, keepdim=True)
     if scale_rewards in ("group", True):
         adv = adv / (r.std(1, keepdim=True, unbiased=True if group_size > 1 else False).nan_to_num(0.0) + eps)

@@ -274,7 +274,19 @@ def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_siz
                                          save_adapter_fn=(lambda d: save_adapter(model, spec, d)) if spec is not None else None)
         else:
             engine = G.LocalRollout(model, eos, pad, seed + dp_rank)
-        records = G.load_prompt_records(cfg, tokenizer)
+        eb = dict(cfg.get("ebft") or {}) if rl == "ebft" else {}
+        if eb.get("mode") == "strided":
+            from ..rl.ebft import load_strided_records
+
+            # short anchored rollouts: sample count, length and sampling temperature come from the ebft block
+            st.num_generations = int(eb.get("n_samples_per_prompt") or 4)
+            st.max_completion_length = int(eb.get("generate_max_len") or 8)
+            st.temperature = float(eb.get("temperature") if eb.get("temperature") is not None else 0.6)
+            st.top_p = float(eb.get("top_p") if eb.get("top_p") is not None else 1.0)
+            st.scale_rewards = "rloo" if (eb.get("advantage_estimator") or "rloo") == "rloo" else st.scale_rewards
+            records = load_strided_records(cfg, tokenizer)
+        else:
+            records = G.load_prompt_records(cfg, tokenizer)
         extra = (cfg.get("trl") or {}).get("reward_funcs") or []
         reward_funcs = G.load_reward_funcs(extra) if (extra or rl != "ebft") else []
         if rl == "ebft":   # feature-matching reward from the frozen policy (adapters off, or a frozen copy)

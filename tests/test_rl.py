@@ -427,3 +427,15 @@ def test_ebft_feature_rewards_and_training_raises_alignment():
         tr.training_step([next(it)])
         align.append(obj.last_metrics["ebft/alignment"])
     assert sum(align[-8:]) / 8 > sum(align[:8]) / 8 + 0.02, align
+
+
+def test_ebft_strided_records_and_rloo_baseline():
+    from axolotl_b200.rl.ebft import strided_records
+
+    recs = strided_records([list(range(100, 130))], stride=8, context_length=6, generate_max_len=4, bos_token_id=1)
+    assert [r["prompt_ids"][1:] for r in recs[:2]] == [list(range(100, 106)), list(range(108, 114))]
+    assert all(r["prompt_ids"][0] == 1 and len(r["ground_truth"]) == 4 for r in recs)
+    assert recs[0]["ground_truth"] == [106, 107, 108, 109] and recs[-1]["ground_truth"][-1] <= 129
+    r = torch.tensor([1.0, 2.0, 6.0, 0.0, 0.0, 3.0])
+    a = L.group_advantages(r, 3, "rloo")
+    assert torch.allclose(a, torch.tensor([1 - 4.0, 2 - 3.5, 6 - 1.5, 0 - 1.5, 0 - 1.5, 3 - 0.0]))

@@ -239,8 +239,17 @@ __global__ void ep_stage_rows_kernel(PeerPtrs8 src, const unsigned char* __restr
     const long long row = i - (long long)r * T;
     const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + row * width;
     __nv_bfloat16* d = staging + i * width;
-    for (int c = lane * 8; c < width; c += 256)
-      *reinterpret_cast<uint4*>(d + c) = *reinterpret_cast<const uint4*>(s + c);
+    // all loads of a batch are issued before the first store: up to 8 x 16 B per lane (4 KB per warp)
+    // in flight over NVLink instead of one vector
+    for (int c0 = lane * 8; c0 < width; c0 += 256 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (c0 + k * 256 < width) v[k] = *reinterpret_cast<const uint4*>(s + c0 + k * 256);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (c0 + k * 256 < width) *reinterpret_cast<uint4*>(d + c0 + k * 256) = v[k];
+    }
   }
 }
 
@@ -264,11 +273,17 @@ __global__ void ep_reduce_rows_kernel(PeerPtrs8 part, const unsigned char* __res
         const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), cc = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
         acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = cc.x; acc[5] = cc.y; acc[6] = d.x; acc[7] = d.y;
       }
-      for (int r = 0; r < world; ++r) {
-        if (!((mask >> r) & 1u)) continue;
-        const __nv_bfloat16* s =
-            reinterpret_cast<const __nv_bfloat16*>(part.p[r]) + ((long long)self * T + row) * width + c;
-        const uint4 v = *reinterpret_cast<const uint4*>(s);
+      // peer loads first (independent, all in flight together), sums afterwards
+      uint4 pv[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < world && ((mask >> r) & 1u))
+          pv[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(part.p[r]) +
+                                                  ((long long)self * T + row) * width + c);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (!(r < world && ((mask >> r) & 1u))) continue;
+        const uint4 v = pv[r];
         const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), cc = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
         acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
       }

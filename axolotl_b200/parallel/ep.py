@@ -54,7 +54,8 @@ class ExpertParallelGroup:
         self.dedup = os.environ.get("AXB_EP_DEDUP", "1") != "0"
         # Transport of the staged rows: "sm" (default) = only the needed rows by a copy kernel; "ce" = whole
         # peer buffers by the copy engines (peer cudaMemcpyAsync). Measured on the 2-GPU Qwen3-MoE step:
-        # 370.9 ms with the row kernels, 384.3 ms with the copy engines (more bytes, one copy per peer).
+        # 370.9 ms with the row kernels, 384.3 ms with the copy engines (more bytes, one copy per peer);
+        # on 8 GPUs 442.7 ms against 592.1 ms.
         self.stage_by = os.environ.get("AXB_EP_STAGE", "sm")
         if self.fused:
             self.sync = PeerSync(self.device, group)

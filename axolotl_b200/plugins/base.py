@@ -56,6 +56,7 @@ _BUNDLED = {
     "mora": "axolotl_b200.plugins.compat.MoraPlugin",
     "diffusion": "axolotl_b200.plugins.diffusion.DiffusionPlugin",
     "densemixer": "axolotl_b200.plugins.compat.DenseMixerPlugin",
+    "nemo_gym": "axolotl_b200.plugins.nemo_gym.NemoGymPlugin",
     "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
     "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -76,6 +77,7 @@ _ALIASES = {
     "axolotl.integrations.mora.MoraPlugin": "mora",
     "axolotl.integrations.diffusion.DiffusionPlugin": "diffusion",
     "axolotl.integrations.densemixer.DenseMixerPlugin": "densemixer",
+    "axolotl.integrations.nemo_gym.NemoGymPlugin": "nemo_gym",
     "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
     "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
 }

@@ -439,3 +439,64 @@ def test_ebft_strided_records_and_rloo_baseline():
     r = torch.tensor([1.0, 2.0, 6.0, 0.0, 0.0, 3.0])
     a = L.group_advantages(r, 3, "rloo")
     assert torch.allclose(a, torch.tensor([1 - 4.0, 2 - 3.5, 6 - 1.5, 0 - 1.5, 0 - 1.5, 3 - 0.0]))
+
+
+def test_nemo_gym_verify_rewards_against_a_fake_environment_server():
+    import json
+    import http.server
+    import threading
+
+    from axolotl_b200.plugins import nemo_gym as NG
+
+    seen = []
+
+    class Env(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            seen.append(body)
+            answer = body["response"]["output"][0]["content"][0]["text"]
+            reward = 1.0 if answer.strip() == str(body.get("expected")) else 0.25
+            data = json.dumps({"reward": reward}).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    env = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Env)
+    env_port = env.server_address[1]
+
+    class Head(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            doc = f"math_env:\n  resources_servers:\n    math:\n      host: 127.0.0.1\n      port: {env_port}\n"
+            data = doc.encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    head = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Head)
+    for srv in (env, head):
+        threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        plug = NG.NemoGymPlugin()
+        plug.register({"nemo_gym_enabled": True, "nemo_gym_head_port": head.server_address[1], "nemo_gym_verify_timeout": 5})
+        assert NG.discover_verify_urls(refresh=True) == {"math": f"http://127.0.0.1:{env_port}/verify"}
+        r = NG.reward_nemo_gym_verify(completions=["4", "5", "x"], prompts=["2+2?", "2+2?", "?"],
+                                      resources_server_ref=[{"name": "math"}, {"name": "math"}, {"name": "unknown"}],
+                                      verify_extra=[{"expected": 4}, {"expected": 4}, None])
+        assert r == [1.0, 0.25, 0.0]
+        assert seen[0]["responses_create_params"]["input"][0]["content"] == "2+2?" and seen[0]["expected"] == 4
+        assert NG.reward_env(["a", "b"], env_reward=[0.5, 2]) == [0.5, 2.0]
+        with pytest.raises(ValueError):
+            plug.register({"nemo_gym_enabled": True, "nemo_gym_multi_turn": True})
+    finally:
+        env.shutdown()
+        head.shutdown()
+        NG._STATE["urls"] = None

@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-``python -m axolotl_b200.utils.kernel_bench [gemm|lora|attn|elementwise|all]`` times each hand-written
+``python -m axolotl_b200.utils.kernel_bench [gemm|lora|attn|decode|elementwise|all]`` times each hand-written
 kernel with CUDA events (after warm-up, L2 flushed between iterations) and prints achieved
 TFLOP/s or GB/s next to the library kernel for the same shape (cuBLAS via torch.matmul,
 flash-attn 2 where installed) and the measured peaks in ``MEASURED_PEAKS.json`` if present.
@@ -105,6 +105,41 @@ def bench_lora_skinny(rows):
                     f"({gb(T * N, t_t) / hbm:.2f}) | dA=t^T x {t_dA * 1e3:.0f} us ({gb(T * K, t_dA) / hbm:.2f}, splits {sp_a}) | "
                     f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b}){split_note}  "
                     f"[fractions of {how} HBM copy rate]")
+
+
+def bench_decode(rows):
+    """Single-query attention over a KV cache (memory-bound: one pass over the live cache) and
+    end-to-end KV-cache generation on a randomly initialised Llama-3-8B."""
+    import time
+
+    from axolotl_b200.ops.functional import decode_attention
+
+    _, hbm, how = _peaks()
+    Hq, Hk, D = 32, 8, 128
+    for B, n in ((8, 4096), (64, 4096), (64, 16384)):
+        lens = torch.full((B,), n, dtype=torch.int32, device="cuda")
+        qkv = torch.randn(B, (Hq + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16)
+        kc = torch.randn(B, n, Hk * D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(B, n, Hk * D, device="cuda", dtype=torch.bfloat16)
+        ms = time_cuda(lambda: decode_attention(qkv, kc, vc, lens, Hq, Hk, D))
+        gbs = 2 * B * n * Hk * D * 2 / 1e6 / ms
+        rows.append(f"decode attn B={B} len={n}: {ms * 1e3:.0f} us, {gbs:.0f} GB/s of cache ({gbs / hbm:.2f} of {how} HBM copy rate)")
+        del kc, vc
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.kv_cache import generate_cached
+    from axolotl_b200.models.transformer import CausalLM
+
+    model = CausalLM(preset("llama-3-8b"), dtype=torch.bfloat16, device="cuda").init_weights(0)
+    for B, plen, new in ((8, 512, 64), (64, 512, 64)):
+        prompts = [[1] + [100 + (i * 7 + j) % 1000 for j in range(plen - 1)] for i in range(B)]
+        generate_cached(model, prompts[:8], 4)     # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        generate_cached(model, prompts, new)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        rows.append(f"generate llama-3-8b B={B} prompt={plen} new={new}: {dt:.2f} s, {B * new / dt:.0f} new tokens/s "
+                    f"(prefill included)")
 
 
 def bench_attn(rows):
@@ -221,6 +256,8 @@ def main(argv):
         bench_lora_skinny(rows)
     if what in ("attn", "all"):
         bench_attn(rows)
+    if what in ("decode",):
+        bench_decode(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

@@ -112,11 +112,19 @@ __global__ void __launch_bounds__(DEC_T)
         for (int g = 0; g < MAX_G; ++g)
           if (g < G) acc[g][j] *= alpha[g];
         const __nv_bfloat16* vr = vb + (long long)c0 * row_elems + d;
-        for (int p = 0; p < cn; ++p) {
-          const float v = __bfloat162float(vr[(long long)p * row_elems]);
+        // eight cache rows per step: their (strided) loads are issued together, then consumed;
+        // probabilities of positions past the end of the sequence are zero already
+        for (int p0 = 0; p0 < cn; p0 += 8) {
+          float v[8];
 #pragma unroll
-          for (int g = 0; g < MAX_G; ++g)
-            if (g < G) acc[g][j] = fmaf(sp[g][p], v, acc[g][j]);
+          for (int k = 0; k < 8; ++k)
+            v[k] = (p0 + k < cn) ? __bfloat162float(vr[(long long)(p0 + k) * row_elems]) : 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+#pragma unroll
+            for (int g = 0; g < MAX_G; ++g)
+              if (g < G) acc[g][j] = fmaf(sp[g][p0 + k], v[k], acc[g][j]);
+          }
         }
       }
     }

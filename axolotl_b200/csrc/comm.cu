@@ -109,6 +109,11 @@ struct RsAdamwParams {
   float* gnorm_sq_out;  // local scalar: squared norm of the reduced (unscaled) gradient
   int* status;
   unsigned long long budget_ns;
+  // 0: everything in one launch (one parameter group). An optimizer with several groups clips by the
+  // norm over ALL of them, so it runs two passes: mode 1 for every group (reduce-scatter, add the
+  // group's squared norm to *gnorm_sq_out, leave the reduced slice in place), then mode 2 for every
+  // group (clip by *gnorm_sq_out, AdamW, publish; no reduction).
+  int mode;
 };
 
 __global__ void __launch_bounds__(256)
@@ -122,6 +127,8 @@ __global__ void __launch_bounds__(256)
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
 
+  float total = 0.f;
+  if (p.mode != 2) {
   // ---- barrier 1: every rank has finished writing its local gradient
   if (blockIdx.x == 0) peer_barrier_block(p.pads, p.rank, p.world, 0, p.epoch, p.status, p.budget_ns);
   grid.sync();
@@ -181,13 +188,29 @@ __global__ void __launch_bounds__(256)
   }
   grid.sync();
 
-  // ---- phase C: clip + AdamW on my slice, publish master + shadow to all ranks
-  float total = 0.f;
   {
     const volatile float* parts = reinterpret_cast<const volatile float*>(p.scratch.p[p.rank]);
     for (int r = 0; r < p.world; ++r) total += parts[r];
   }
+  if (p.mode == 1) {
+    // first pass of a multi-group step: accumulate the norm, clear what the peers have read, stop
+    const long long n4 = p.n / 4;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long s0 = lo / 4, s1 = (lo + slice) / 4;
+    for (long long v = tid; v < n4; v += nthreads)
+      if (v < s0 || v >= s1) reinterpret_cast<float4*>(my_grad)[v] = z;
+    grid.sync();   // every thread has read the partial sums before they are re-armed
+    if (tid == 0) {
+      if (p.gnorm_sq_out) *p.gnorm_sq_out += total;
+      reinterpret_cast<float*>(p.scratch.p[p.rank])[MAX_WORLD] = 0.f;
+    }
+    return;
+  }
   if (tid == 0 && p.gnorm_sq_out) *p.gnorm_sq_out = total;
+  } else {
+    total = *reinterpret_cast<const volatile float*>(p.gnorm_sq_out);
+  }
+  // ---- phase C: clip + AdamW on my slice, publish master + shadow to all ranks
   float clip = p.grad_scale;
   if (p.max_norm > 0.f) clip *= fminf(1.f, p.max_norm / (sqrtf(total) * p.grad_scale + 1e-6f));
   float* my_master = reinterpret_cast<float*>(p.master.p[p.rank]);
@@ -297,9 +320,11 @@ static int rs_adamw_ag_impl(const unsigned long long* grad_ptrs,
                                long long n, int rank, int world, unsigned int epoch, float lr,
                                float beta1, float beta2, float eps, float wd, float bc1, float bc2,
                                float max_norm, float grad_scale, float* gnorm_sq_out, int* status,
-                               long long budget_ns, void* stream, int sliced_moments) {
+                               long long budget_ns, void* stream, int sliced_moments, int mode = 0) {
   if (n % (4LL * world)) return -3;
+  if (mode < 0 || mode > 2 || (mode != 0 && gnorm_sq_out == nullptr)) return -2;
   RsAdamwParams p;
+  p.mode = mode;
   if (fill_ptrs(p.grad, grad_ptrs, world) || fill_ptrs(p.master, master_ptrs, world) ||
       fill_ptrs(p.shadow, shadow_ptrs, world) || fill_ptrs(p.pads, pad_ptrs, world) ||
       fill_ptrs(p.scratch, scratch_ptrs, world))
@@ -363,6 +388,22 @@ extern "C" int axb_rs_adamw_ag_sharded(const unsigned long long* grad_ptrs, cons
   return rs_adamw_ag_impl(grad_ptrs, master_ptrs, shadow_ptrs, pad_ptrs, scratch_ptrs, grad_mc, master_mc, shadow_mc,
                           exp_avg, exp_avg_sq, n, rank, world, epoch, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm,
                           grad_scale, gnorm_sq_out, status, budget_ns, stream, 1);
+}
+
+// Two-pass form for optimizers with several parameter groups (see RsAdamwParams::mode): call with
+// mode 1 for every group after zeroing *gnorm_sq_out, then with mode 2 for every group. Each call
+// consumes three barrier epochs like the one-launch form. sliced_moments as in the _sharded entry.
+extern "C" int axb_rs_adamw_ag_pass(const unsigned long long* grad_ptrs, const unsigned long long* master_ptrs,
+                                    const unsigned long long* shadow_ptrs, const unsigned long long* pad_ptrs,
+                                    const unsigned long long* scratch_ptrs, void* grad_mc, void* master_mc,
+                                    void* shadow_mc, float* exp_avg, float* exp_avg_sq, long long n, int rank,
+                                    int world, unsigned int epoch, float lr, float beta1, float beta2, float eps,
+                                    float wd, float bc1, float bc2, float max_norm, float grad_scale,
+                                    float* gnorm_sq_out, int* status, long long budget_ns, void* stream,
+                                    int sliced_moments, int mode) {
+  return rs_adamw_ag_impl(grad_ptrs, master_ptrs, shadow_ptrs, pad_ptrs, scratch_ptrs, grad_mc, master_mc, shadow_mc,
+                          exp_avg, exp_avg_sq, n, rank, world, epoch, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm,
+                          grad_scale, gnorm_sq_out, status, budget_ns, stream, sliced_moments, mode);
 }
 
 extern "C" int axb_peer_allreduce_f32(const unsigned long long* buf_ptrs,

@@ -72,7 +72,91 @@ struct GemmParams {
   unsigned long long g_shard_bytes;        // bytes per rank
   unsigned long long g_total_bytes;        // g_world * g_shard_bytes (multiple of 8 KB)
   unsigned char* g_dst;                    // local staging buffer
+  // CTA-pair kernel only. epi 1 (GLU forward): B holds gate rows [0, I) and up rows [I, 2I); a
+  // cluster's tile is 256 rows x (128 gate + 128 up) columns (rank 0 stages the gate rows, rank 1 the
+  // up rows of the same 128 columns), N counts the I columns of h. The epilogue stores gate|up into C
+  // ([M, 2I], optional) and h = act(gate) * up into H. epi 2 (GLU backward): the accumulator is dh
+  // [M, I]; the epilogue reads gate|up from Cin ([M, 2I]) and stores d_gate | d_up into C ([M, 2I],
+  // may alias Cin).
+  int epi;
+  int glu_kind;     // 0 silu, 1 gelu (tanh)
+  float glu_limit;  // > 0: clamped GLU
+  void* H;
+  long long ldh;
+  int epi_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator (0 = spin)
+  int prod_sleep_ns;  // back-off of the TMA producer while it waits for a free stage (0 = spin)
 };
+
+int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0;
+
+// Spin on an mbarrier with a pause between polls: the waiting warps stop competing for issue slots
+// (and for the power budget of a kernel that runs against the board limit) with the MMA stream.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                  int sleep_ns) {
+  if (mbar_test_wait(bar, parity)) return true;
+  if (sleep_ns <= 0) return mbar_wait_spin(bar, parity, status, code);
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    __nanosleep(sleep_ns);
+    if ((++spins & 0xFF) == 0 && global_timer_ns() - t0 > AXB_WAIT_BUDGET_NS) {
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ float glu_act(float g, int kind) {
+  if (kind == 0) return g / (1.f + __expf(-g));
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * g * (1.f + t);
+}
+__device__ __forceinline__ float glu_act_grad(float g, int kind) {
+  if (kind == 0) {
+    const float s = 1.f / (1.f + __expf(-g));
+    return s * (1.f + g * (1.f - s));
+  }
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+}
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, bool vec, int n, float (&o)[32]) {
+  if (vec) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 in = *reinterpret_cast<const uint4*>(src + q * 8);
+      const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(w[e]);
+        o[q * 8 + 2 * e] = f.x;
+        o[q * 8 + 2 * e + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = j < n ? __bfloat162float(src[j]) : 0.f;
+  }
+}
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, bool vec, int n, const float (&v)[32]) {
+  if (vec) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 o;
+      o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+      o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+      o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+      o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+      *reinterpret_cast<uint4*>(dst + q * 8) = o;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < n) dst[j] = __float2bfloat16(v[j]);
+  }
+}
 
 constexpr int GATHER_CHUNK = 8192;
 constexpr int GATHER_SLOTS = 4;   // per warp
@@ -873,7 +957,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_clusters = n_workers >> 1;
 
   const int num_m = (p.M + 255) / 256;
-  const int num_n = (p.N + 255) / 256;
+  const int num_n = p.epi == 1 ? (p.N + 127) / 128 : (p.N + 255) / 256;
   const int nk_main = (p.K + BK - 1) / BK;
   const int nk_ext = (p.K2 + BK - 1) / BK;
   const int nk_total = nk_main + nk_ext;
@@ -912,7 +996,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         int m_blk, n_blk, split;
         decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
         for (int kb = 0; kb < nk_total; ++kb) {
-          if (!mbar_wait_spin(&empty_bar[stage], phase ^ 1, p.status, AXB_TIMEOUT_EMPTY)) {
+          if (!mbar_wait_backoff(&empty_bar[stage], phase ^ 1, p.status, AXB_TIMEOUT_EMPTY, p.prod_sleep_ns)) {
             ok = false;
             break;
           }
@@ -928,7 +1012,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint8_t* a_dst = sA + stage * P_A_BYTES;
           uint8_t* b_dst = sB + stage * P_B_BYTES;
           const int m0 = m_blk * 256 + (int)rank * 128;
-          const int n0 = n_blk * 256 + (int)rank * 128;
+          const int n0 = p.epi == 1 ? (int)rank * p.N + n_blk * 128 : n_blk * 256 + (int)rank * 128;
           if (!A_MN) {
             tma_load_2d_pair(a_dst, ma, fb, k0, m0);
           } else {
@@ -998,7 +1082,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait_spin(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+      if (!mbar_wait_backoff(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL, p.epi_sleep_ns)) {
         ok = false;
         break;
       }
@@ -1006,6 +1090,76 @@ __global__ void __launch_bounds__(kThreads, 1)
       const long long row = (long long)m_blk * 256 + rank * 128 + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * 256;
+      if (p.epi == 1) {
+        // GLU forward: columns [0, 128) of the accumulator are gate, [128, 256) the matching up columns
+        const int I = p.N;
+        const bool lim = p.glu_limit > 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_addr + c * 32, rg);
+          tmem_ld_32x32(t_addr + 128 + c * 32, ru);
+          tmem_ld_wait();
+          const int col0 = n_blk * 128 + c * 32;
+          if (!row_ok || col0 >= I) continue;
+          const int n = min(32, I - col0);
+          float g[32], u[32], h[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            g[j] = __uint_as_float(rg[j]) * p.alpha;
+            u[j] = __uint_as_float(ru[j]) * p.alpha;
+          }
+          if (p.C) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+            const bool vec = n == 32 && (p.ldc & 7) == 0 && (I & 7) == 0;
+            store_bf16x32(crow, vec, n, g);
+            store_bf16x32(crow + I, vec, n, u);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            // the stored gate / up are bf16: round first so that the backward pass sees the same values
+            const float gr = __bfloat162float(__float2bfloat16(g[j]));
+            const float ur = __bfloat162float(__float2bfloat16(u[j]));
+            const float gc = lim ? fminf(gr, p.glu_limit) : gr;
+            const float uc = lim ? fminf(fmaxf(ur, -p.glu_limit), p.glu_limit) : ur;
+            h[j] = glu_act(gc, p.glu_kind) * uc;
+          }
+          store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.H) + row * p.ldh + col0, n == 32 && (p.ldh & 7) == 0, n, h);
+        }
+      } else if (p.epi == 2) {
+        // GLU backward: the accumulator is dh; gate | up come from Cin, d_gate | d_up go to C
+        const int I = p.N;
+        const bool lim = p.glu_limit > 0.f;
+        const float L = p.glu_limit;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = n_blk * 256 + c * 32;
+          if (!row_ok || col0 >= I) continue;
+          const int n = min(32, I - col0);
+          const __nv_bfloat16* irow = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + row * p.ldcin + col0;
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+          const bool vin = n == 32 && (p.ldcin & 7) == 0 && (I & 7) == 0;
+          const bool vout = n == 32 && (p.ldc & 7) == 0 && (I & 7) == 0;
+          float g[32], u[32];
+          load_bf16x32(irow, vin, n, g);
+          load_bf16x32(irow + I, vin, n, u);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float d = __uint_as_float(r[j]) * p.alpha;
+            const bool g_in = !lim || g[j] <= L;
+            const bool u_in = !lim || (u[j] >= -L && u[j] <= L);
+            const float gc = g_in ? g[j] : L;
+            const float uc = u_in ? u[j] : (u[j] > 0.f ? L : -L);
+            g[j] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
+            u[j] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
+          }
+          store_bf16x32(crow, vout, n, g);
+          store_bf16x32(crow + I, vout, n, u);
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t r[32];
@@ -1095,7 +1249,7 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
     attr_set = true;
   }
   p.g_ctas &= ~1;  // whole clusters only
-  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  const int tiles = ((p.M + 255) / 256) * (p.epi == 1 ? (p.N + 127) / 128 : (p.N + 255) / 256);
   int workers = (sms - p.g_ctas) & ~1;
   if (2 * tiles < workers) workers = 2 * tiles;
   cudaLaunchConfig_t cfg = {};
@@ -1116,23 +1270,32 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
 }  // namespace
 
 // CTA-pair GEMM (same contract as axb_gemm_bf16_prefetch with bn = 256, splits = 1, out_mode 0/1).
-extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
-                                  void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
-                                  const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
-                                  float alpha, float beta, int out_mode,
-                                  const unsigned long long* pf_peer_bases, unsigned long long pf_shard_offset,
-                                  unsigned long long pf_shard_bytes, int pf_world, void* pf_dst, int pf_ctas,
-                                  int* status, void* stream) {
+// epi = 0: plain. epi = 1 (GLU forward): B is the [2I, K] gate|up weight (B2 the matching [2I, K2]
+// LoRA factor), N = I; C (optional) receives gate|up [M, 2I], H receives act(gate) * up [M, I].
+// epi = 2 (GLU backward): N = I, the product is dh [M, I]; Cin holds gate|up [M, 2I] and C receives
+// d_gate | d_up [M, 2I] (C may alias Cin). glu_kind 0 = SiLU, 1 = GELU(tanh); glu_limit > 0 clamps.
+static int pair_entry(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                      void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
+                      const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
+                      float alpha, float beta, int out_mode, int epi, int glu_kind, float glu_limit, void* H,
+                      long long ldh, const unsigned long long* pf_peer_bases, unsigned long long pf_shard_offset,
+                      unsigned long long pf_shard_bytes, int pf_world, void* pf_dst, int pf_ctas,
+                      int* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (K2 > 0 && ((lda2 & 7) || (ldb2 & 7)))) return -2;
   if (out_mode != 0 && out_mode != 1) return -3;
+  if (epi < 0 || epi > 2) return -3;
+  if (epi == 1 && (b_mn || out_mode != 0 || H == nullptr)) return -3;
+  if (epi == 2 && (out_mode != 0 || Cin == nullptr || C == nullptr)) return -3;
+  const int n_rows_b = epi == 1 ? 2 * N : N;   // rows of the stored B (K-major) / columns (MN-major)
   CUtensorMap tA, tB, tA2, tB2;
   int rc = 0;
   rc |= a_mn ? axb_make_tmap_2d(&tA, A, K, M, lda, 64, 64) : axb_make_tmap_2d(&tA, A, M, K, lda, 128, 64);
-  rc |= b_mn ? axb_make_tmap_2d(&tB, B, K, N, ldb, 64, 64) : axb_make_tmap_2d(&tB, B, N, K, ldb, 128, 64);
+  rc |= b_mn ? axb_make_tmap_2d(&tB, B, K, n_rows_b, ldb, 64, 64) : axb_make_tmap_2d(&tB, B, n_rows_b, K, ldb, 128, 64);
   if (K2 > 0) {
     rc |= a_mn ? axb_make_tmap_2d(&tA2, A2, K2, M, lda2, 64, 64) : axb_make_tmap_2d(&tA2, A2, M, K2, lda2, 128, 64);
-    rc |= b_mn ? axb_make_tmap_2d(&tB2, B2, K2, N, ldb2, 64, 64) : axb_make_tmap_2d(&tB2, B2, N, K2, ldb2, 128, 64);
+    rc |= b_mn ? axb_make_tmap_2d(&tB2, B2, K2, n_rows_b, ldb2, 64, 64)
+               : axb_make_tmap_2d(&tB2, B2, n_rows_b, K2, ldb2, 128, 64);
   } else {
     tA2 = tA;
     tB2 = tB;
@@ -1142,6 +1305,8 @@ extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const 
   p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
   p.C = C; p.Cin = Cin; p.ldc = ldc; p.ldcin = ldcin;
   p.alpha = alpha; p.beta = beta; p.out_mode = out_mode; p.splits = 1; p.status = status;
+  p.epi = epi; p.glu_kind = glu_kind; p.glu_limit = glu_limit; p.H = H; p.ldh = ldh;
+  p.epi_sleep_ns = g_epi_sleep_ns; p.prod_sleep_ns = g_prod_sleep_ns;
   p.group_m = 4;  // bands of 4 x 256 rows
   PrefetchArgs pf;
   pf.peer_bases = pf_peer_bases; pf.shard_offset = pf_shard_offset; pf.shard_bytes = pf_shard_bytes;
@@ -1152,4 +1317,40 @@ extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const 
   if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, p, sm_count(), st);
   if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, p, sm_count(), st);
   return launch_pair<true, true>(tA, tB, tA2, tB2, p, sm_count(), st);
+}
+
+extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                                  void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
+                                  const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
+                                  float alpha, float beta, int out_mode,
+                                  const unsigned long long* pf_peer_bases, unsigned long long pf_shard_offset,
+                                  unsigned long long pf_shard_bytes, int pf_world, void* pf_dst, int pf_ctas,
+                                  int* status, void* stream) {
+  return pair_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, Cin, ldcin, M, N, K, A2, lda2, B2, ldb2, K2, alpha, beta,
+                    out_mode, 0, 0, 0.f, nullptr, 0, pf_peer_bases, pf_shard_offset, pf_shard_bytes, pf_world, pf_dst,
+                    pf_ctas, status, stream);
+}
+
+// CTA-pair GEMM with a GLU epilogue (see pair_entry): the SwiGLU / GeGLU of an MLP folded into the
+// gate|up projection (forward) and into the input-gradient GEMM of the down projection (backward),
+// which the reference runs as separate Triton kernels (src/axolotl/kernels/swiglu.py:16-101,
+// src/axolotl/kernels/geglu.py) between cuBLAS calls.
+extern "C" int axb_gemm_bf16_pair_glu(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                                      void* C, long long ldc, const void* Cin, long long ldcin, int M, int N, int K,
+                                      const void* A2, long long lda2, const void* B2, long long ldb2, int K2,
+                                      float alpha, int epi, int glu_kind, float glu_limit, void* H, long long ldh,
+                                      const unsigned long long* pf_peer_bases, unsigned long long pf_shard_offset,
+                                      unsigned long long pf_shard_bytes, int pf_world, void* pf_dst, int pf_ctas,
+                                      int* status, void* stream) {
+  if (epi != 1 && epi != 2) return -3;
+  return pair_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, Cin, ldcin, M, N, K, A2, lda2, B2, ldb2, K2, alpha, 0.f, 0,
+                    epi, glu_kind, glu_limit, H, ldh, pf_peer_bases, pf_shard_offset, pf_shard_bytes, pf_world, pf_dst,
+                    pf_ctas, status, stream);
+}
+
+// Wait back-off of the CTA-pair kernel in nanoseconds (0 = busy spin): epilogue warps waiting for an
+// accumulator, TMA producer waiting for a free stage.
+extern "C" void axb_gemm_set_backoff(int epi_sleep_ns, int prod_sleep_ns) {
+  g_epi_sleep_ns = epi_sleep_ns;
+  g_prod_sleep_ns = prod_sleep_ns;
 }

@@ -19,7 +19,7 @@ import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
 from ..ops import functional as Fn
-from ..ops.lora import linear
+from ..ops.lora import glu_mlp, linear
 from .config import ModelConfig
 from .layers import FusedLinear, RMSNorm, adapters_enabled
 
@@ -98,6 +98,10 @@ class MLP(nn.Module):
         self.tile_rows = None   # tiled MLP: rows per tile (None = whole sequence at once)
 
     def _mlp(self, x):
+        if x.is_cuda:   # one autograd node with the GLU folded into the GEMM epilogues, when it applies
+            y = glu_mlp(x, self.gate_up_proj, self.down_proj, Fn._ACT_KIND[self.act], self.glu_limit, adapters_enabled())
+            if y is not None:
+                return y
         return self.down_proj(Fn.glu(self.gate_up_proj(x), self.act, self.glu_limit))
 
     def forward(self, x):

@@ -14,10 +14,12 @@ import torch
 from . import _lib
 
 _SM = 148
-# CTA-pair (cta_group::2, 256x256 tiles) kernel for large GEMMs. Numerically validated, but its
-# TMA-fed main loop currently runs at half the rate of the single-CTA kernel (the MMA-only rate
-# reaches the cuBLAS peak), so it is opt-in: AXB_GEMM_PAIR=1.
-USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "1") != "0"   # CTA-pair (cta_group::2) kernel for large GEMMs
+# CTA-pair (cta_group::2, 256x256 tile per SM pair) kernel: the default for large GEMMs;
+# AXB_GEMM_PAIR=0 keeps every launch on the single-CTA kernel.
+USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "1") != "0"
+# GLU folded into the gate|up GEMM epilogue (forward) and the down-projection input-gradient GEMM
+# (backward); AXB_GLU_EPILOGUE=0 runs the stand-alone GLU kernels instead.
+USE_GLU_EPILOGUE = os.environ.get("AXB_GLU_EPILOGUE", "1") != "0"
 
 
 def _pick_bn(M: int, N: int) -> int:
@@ -56,7 +58,12 @@ def gemm(
     accumulate: bool = False,
     splits: int = 1,
     bn: int | None = None,
+    glu: tuple | None = None,
 ) -> torch.Tensor:
+    """``glu`` selects a GLU epilogue of the CTA-pair kernel (callers check ``glu_fusable`` first):
+    ``("fwd", kind, limit, h_out)``: ``b`` is the [2I, K] gate|up weight, ``out`` [M, 2I] receives
+    gate|up and ``h_out`` [M, I] ``act(gate) * up``; ``("bwd", kind, limit, gate_up)``: the product is
+    dh [M, I] and ``out`` [M, 2I] receives d_gate | d_up (``out`` may be ``gate_up`` itself)."""
     quant = getattr(b, "_axb_quant", None)
     if quant is not None:
         # frozen 4-bit weight: expand into the shared bf16 scratch right before the GEMM reads it
@@ -67,7 +74,7 @@ def gemm(
     shard = getattr(b, "_axb_shard", None)
     if shard is not None:
         return _gemm_allgather(a, b, shard, trans_a=trans_a, trans_b=trans_b, a2=a2, b2=b2, alpha=alpha,
-                               beta=beta, c_in=c_in, out=out, out_dtype=out_dtype, bn=bn)
+                               beta=beta, c_in=c_in, out=out, out_dtype=out_dtype, bn=bn, glu=glu)
     M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
     N = b.shape[1] if trans_b else b.shape[0]
     Kb = b.shape[0] if trans_b else b.shape[1]
@@ -124,6 +131,10 @@ def gemm(
     if c_in is not None:
         if c_in.stride(1) != 1 or c_in.dtype != out.dtype:
             raise ValueError("c_in must be row-major with the output dtype")
+    if glu is not None:
+        _glu_launch(lib, glu, a, int(trans_a), b.data_ptr(), b.stride(0), int(trans_b), out, M, N, K, a2, b2, K2,
+                    alpha, (None, 0, 0, 0, None, 0))
+        return out
     if bn is None:
         bn = _pick_bn(M, N)
     if not accumulate and _use_pair(M, N, bn):
@@ -150,6 +161,36 @@ def gemm(
     return out
 
 
+def glu_fusable(M: int, I: int, device) -> bool:
+    """Whether the GLU epilogues of the CTA-pair kernel serve an MLP with ``M`` token rows and ``I``
+    intermediate columns (enough 256-row tiles for the 74 SM pairs, 16-byte aligned rows)."""
+    return (USE_PAIR and USE_GLU_EPILOGUE and device.type == "cuda" and M >= 512 and I % 8 == 0
+            and ((M + 255) // 256) * ((I + 255) // 256) >= 74)
+
+
+def _glu_launch(lib, glu, a, trans_a, b_ptr, ldb, trans_b, out, M, N, K, a2, b2, K2, alpha, pf):
+    mode, kind, limit, other = glu
+    if out is None or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("the GLU epilogue writes a row-major bf16 [M, 2I] `out`")
+    if mode == "fwd":
+        # b: [2I, K]; N passed by the caller is 2I
+        I = N // 2
+        h = other
+        rc = lib.axb_gemm_bf16_pair_glu(
+            a.data_ptr(), a.stride(0), trans_a, b_ptr, ldb, trans_b, out.data_ptr(), out.stride(0), None, 0,
+            M, I, K, _lib.ptr(a2), a2.stride(0) if a2 is not None else 0, _lib.ptr(b2),
+            b2.stride(0) if b2 is not None else 0, K2, float(alpha), 1, int(kind), float(limit or 0.0),
+            h.data_ptr(), h.stride(0), *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+    else:
+        gu = other
+        rc = lib.axb_gemm_bf16_pair_glu(
+            a.data_ptr(), a.stride(0), trans_a, b_ptr, ldb, trans_b, out.data_ptr(), out.stride(0),
+            gu.data_ptr(), gu.stride(0), M, N, K, _lib.ptr(a2), a2.stride(0) if a2 is not None else 0,
+            _lib.ptr(b2), b2.stride(0) if b2 is not None else 0, K2, float(alpha), 2, int(kind),
+            float(limit or 0.0), None, 0, *pf, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "axb_gemm_bf16_pair_glu")
+
+
 def _use_pair(M, N, bn) -> bool:
     """The 2-CTA kernel (256x256 tile per SM pair, each CTA stages half of B) wins once there are
     enough 256x256 tiles for the 74 SM pairs; small or skinny problems keep the 1-CTA kernel."""
@@ -163,7 +204,7 @@ def pick_splits(out_tiles: int, k_blocks: int) -> int:
     return max(1, min(k_blocks, _SM // max(out_tiles, 1)))
 
 
-def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, c_in, out, out_dtype, bn):
+def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, c_in, out, out_dtype, bn, glu=None):
     """GEMM against a row-sharded B. The full B is read from a staging buffer that an earlier
     launch filled; this launch's extra CTAs all-gather the next weight of the schedule (see
     parallel/fsdp.py)."""
@@ -202,7 +243,9 @@ def _gemm_allgather(a, b_shard, info, *, trans_a, trans_b, a2, b2, alpha, beta, 
               ctx.staging[slot].data_ptr(), ctx.prefetch_ctas(nxt, 2.0 * M * N * K))
     else:
         pf = (None, 0, 0, 0, None, 0)
-    if _use_pair(M, N, bn):
+    if glu is not None:
+        _glu_launch(lib, glu, a, 0, staging.data_ptr(), cols, int(trans_b), out, M, N, K, a2, b2, K2, alpha, pf)
+    elif _use_pair(M, N, bn):
         rc = lib.axb_gemm_bf16_pair(
             a.data_ptr(), a.stride(0), 0, staging.data_ptr(), cols, int(trans_b), out.data_ptr(), out.stride(0),
             _lib.ptr(c_in), c_in.stride(0) if c_in is not None else 0, M, N, K,

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from .gemm import gemm, pick_splits
+from .gemm import gemm, glu_fusable, pick_splits
 
 
 SKINNY_SPLITS = int(__import__("os").environ.get("AXB_LORA_SKINNY_SPLITS", "0"))
@@ -114,6 +114,122 @@ class _LinearFn(torch.autograd.Function):
             dW = None if tgt is not None else buf.to(W.dtype)
         dbias = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return dx, dW, dbias
+
+
+def _adapter_grads(A, B, t, x, dy, xa, blocks):
+    """Gradients of the fp32 LoRA masters: dA [R, K] = t^T x and the diagonal blocks of dB [N, R] =
+    dy^T xa (``t`` = s dy B and ``xa`` = s x A^T carry the scaling). Accumulated straight into the
+    optimizer's flat gradient buffer (``_axb_grad``) when the parameter has one."""
+    T, K = x.shape
+    dA = dB = None
+    if A is not None and A.requires_grad:
+        tgt = getattr(A, "_axb_grad", None)
+        buf = tgt if tgt is not None else torch.zeros(A.shape, dtype=torch.float32, device=x.device)
+        sp = pick_splits((K + 255) // 256, (T + 63) // 64)
+        gemm(t, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
+        dA = None if tgt is not None else buf.to(A.dtype)
+    if B is not None and B.requires_grad:
+        tgt = getattr(B, "_axb_grad", None)
+        buf = tgt if tgt is not None else torch.zeros(B.shape, dtype=torch.float32, device=x.device)
+        for (row0, rows, r0, r) in blocks:
+            sp = pick_splits((rows + 127) // 128, (T + 63) // 64)
+            gemm(dy[:, row0:row0 + rows], xa[:, r0:r0 + r], trans_a=True, trans_b=True,
+                 out=buf[row0:row0 + rows, r0:r0 + r], accumulate=True, splits=sp, bn=64)
+        dB = None if tgt is not None else buf.to(B.dtype)
+    return dA, dB
+
+
+def _weight_grad(W, dy, x):
+    """dW [N, K] = dy^T x for a trainable dense weight (fp32 accumulation, see ``_adapter_grads``)."""
+    T, K = x.shape
+    N = dy.shape[1]
+    tgt = getattr(W, "_axb_grad", None)
+    buf = tgt if tgt is not None else torch.zeros((N, K), dtype=torch.float32, device=x.device)
+    sp = pick_splits(((N + 127) // 128) * ((K + 255) // 256), (T + 63) // 64)
+    gemm(dy, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
+    return None if tgt is not None else buf.to(W.dtype)
+
+
+class _GLUMLPFn(torch.autograd.Function):
+    """Whole gated MLP ``down(act(gate(x)) * up(x))`` with optional LoRA on both projections.
+
+    The GLU never runs as a kernel of its own: the gate|up GEMM's epilogue writes gate|up (kept for the
+    backward pass) and h = act(gate) * up, and the input-gradient GEMM of the down projection turns its
+    accumulator dh into d_gate | d_up before it is stored. Saved: x, gate|up, h and the two skinny
+    products x A^T, h A^T; the reference's LoRA_MLP keeps gate, up and recomputes h
+    (src/axolotl/kernels/lora.py:283-705)."""
+
+    @staticmethod
+    def forward(ctx, x, Wgu, Wd, Agu, Bgu, Agu16, Bgu16, Ad, Bd, Ad16, Bd16, cfg):
+        T, I = x.shape[0], cfg["I"]
+        xa = skinny_gemm(x, Agu16, alpha=cfg["s_gu"]) if Agu16 is not None else None
+        gu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=x.device)
+        h = torch.empty((T, I), dtype=torch.bfloat16, device=x.device)
+        gemm(x, Wgu, a2=xa, b2=Bgu16, out=gu, glu=("fwd", cfg["kind"], cfg["limit"], h))
+        ha = skinny_gemm(h, Ad16, alpha=cfg["s_d"]) if Ad16 is not None else None
+        y = gemm(h, Wd, a2=ha, b2=Bd16)
+        ctx.save_for_backward(x, Wgu, Wd, Agu, Bgu, Agu16, Bgu16, Ad, Bd, Ad16, Bd16, gu, h, xa, ha)
+        ctx.cfg = cfg
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, Wgu, Wd, Agu, Bgu, Agu16, Bgu16, Ad, Bd, Ad16, Bd16, gu, h, xa, ha = ctx.saved_tensors
+        cfg = ctx.cfg
+        dy = dy.contiguous()
+        need = ctx.needs_input_grad
+        # ---- down projection: dh = dy W_d + t_d A_d never reaches memory, d_gate | d_up does
+        t_d = skinny_gemm(dy, Bd16, trans_b=True, alpha=cfg["s_d"]) if Ad16 is not None else None
+        dgu = torch.empty_like(gu)
+        gemm(dy, Wd, trans_b=True, a2=t_d, b2=Ad16, out=dgu, glu=("bwd", cfg["kind"], cfg["limit"], gu))
+        dAd, dBd = _adapter_grads(Ad if need[7] else None, Bd if need[8] else None, t_d, h, dy, ha, cfg["blocks_d"])
+        dWd = _weight_grad(Wd, dy, h) if need[2] else None
+        # ---- gate|up projection
+        t_gu = skinny_gemm(dgu, Bgu16, trans_b=True, alpha=cfg["s_gu"]) if Agu16 is not None else None
+        dx = gemm(dgu, Wgu, trans_b=True, a2=t_gu, b2=Agu16) if need[0] else None
+        dAgu, dBgu = _adapter_grads(Agu if need[3] else None, Bgu if need[4] else None, t_gu, x, dgu, xa,
+                                    cfg["blocks_gu"])
+        dWgu = _weight_grad(Wgu, dgu, x) if need[1] else None
+        return dx, dWgu, dWd, dAgu, dBgu, None, None, dAd, dBd, None, None, None
+
+
+def _plain_fused(m) -> bool:
+    """A FusedLinear the fused MLP can drive directly: dense or LoRA, nothing else attached."""
+    return (m.bias is None and m.dora_magnitude is None and m.mora_M is None and m.qat is None
+            and not (m.lora_A is not None and m.lora_dropout > 0.0 and m.training))
+
+
+def glu_mlp(x, gate_up, down, kind, limit, adapters_on=True):
+    """``down(act(gate(x)) * up(x))`` through ``_GLUMLPFn`` when both projections qualify and the problem
+    is large enough for the CTA-pair kernel's GLU epilogues; returns None otherwise (the caller then
+    runs the projections and the GLU kernel one by one)."""
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        return None
+    from ..models.layers import FusedLinear
+
+    if type(gate_up) is not FusedLinear or type(down) is not FusedLinear:
+        return None
+    if not (_plain_fused(gate_up) and _plain_fused(down)):
+        return None
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    I = down.in_features
+    if sum(gate_up.out_features) != 2 * I or not glu_fusable(x2.shape[0], I, x.device):
+        return None
+
+    def lora_of(m):
+        if m.lora_A is None or m.merged or not adapters_on:
+            return None, None, None, None, 1.0, ()
+        if m.lora_A16 is None:
+            m.refresh_shadows()
+        return m.lora_A, m.lora_B, m.lora_A16, m.lora_B16, float(m.scaling), m.lora_blocks
+
+    Agu, Bgu, Agu16, Bgu16, s_gu, blocks_gu = lora_of(gate_up)
+    Ad, Bd, Ad16, Bd16, s_d, blocks_d = lora_of(down)
+    cfg = {"I": I, "kind": kind, "limit": float(limit or 0.0), "s_gu": s_gu, "s_d": s_d,
+           "blocks_gu": blocks_gu, "blocks_d": blocks_d}
+    y = _GLUMLPFn.apply(x2.contiguous(), gate_up.weight, down.weight, Agu, Bgu, Agu16, Bgu16, Ad, Bd, Ad16, Bd16, cfg)
+    return y.view(*shp[:-1], y.shape[-1])
 
 
 def _cpu_weight(W, dtype):

@@ -175,19 +175,23 @@ class ParallelRuntime:
         self.dp_rest_size = self.dp_size
 
     def _tp_step(self, opt, lr):
-        """Model-parallel (TP or EP) x DP: sum the gradients of replicated parameters over the
-        model-parallel group, sum everything over the remaining data-parallel ranks, scale by
-        1 / data_parallel_size; global norm = replicated part + sum over the model-parallel group of
+        """Model-parallel (TP or EP) x CP x DP: sum the gradients of replicated parameters over the
+        model-parallel group, sum everything over the context-parallel group and over the remaining
+        data-parallel ranks, scale by 1 / data_parallel_size; global norm = replicated part + sum over the model-parallel group of
         the sharded part. Everything stays on the device."""
         from ..ops.optim import grad_sumsq
 
         opt._fold_autograd_grads()
         tp_group = self.mp_group
+        cp_group = self.mesh.group("cp") if self.cp is not None else None
         total = torch.zeros(1, dtype=torch.float32, device=self.device)
         for g in opt.groups:
             split = g["tp_split"]
             if split > 0:
                 dist.all_reduce(g["grad"][:split], group=tp_group)
+            if cp_group is not None:
+                # every cp rank saw another slice of the same sequences: their gradients add up
+                dist.all_reduce(g["grad"], group=cp_group)
             if self.dp_rest_size > 1:
                 dist.all_reduce(g["grad"], group=self.dp_rest_group)
             grad_sumsq(g["grad"][:split], total) if split > 0 else None
@@ -222,18 +226,31 @@ class ParallelRuntime:
         bc1 = 1.0 - opt.betas[0] ** opt.step_count
         bc2 = 1.0 - opt.betas[1] ** opt.step_count
         rank = dist.get_rank(self.reduce_group)
-        for gi, g in enumerate(opt.groups):
-            gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
-            epoch = self.sync.next_epoch(0, 3)
-            fn = lib.axb_rs_adamw_ag_sharded if opt.moment_shard is not None else lib.axb_rs_adamw_ag
-            rc = fn(
-                gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
-                gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
-                g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.reduce_size,
-                epoch, lr * g["lr_scale"], opt.betas[0], opt.betas[1], opt.eps, g["weight_decay"], bc1, bc2,
-                float(opt.max_grad_norm or 0.0) if len(opt.groups) == 1 else 0.0, 1.0 / self.dp_size,
-                self._gnorm.data_ptr(), _lib.status_word(self.device).data_ptr(), WAIT_BUDGET_NS, _lib.stream_ptr())
-            _lib.check_rc(rc, "rs_adamw_ag")
+        sliced = 1 if opt.moment_shard is not None else 0
+        groups = [g for g in opt.groups if g.get("active", True)]
+        # One group: reduce + clip + update in a single launch. Several groups (weight decay on
+        # matrices only, LoRA+, embedding LR, lr_groups): the clip factor needs the norm over ALL
+        # groups, so every group is reduced first (pass 1 adds its squared norm to _gnorm) and
+        # updated afterwards (pass 2 clips by the accumulated norm).
+        passes = (0,) if len(groups) == 1 else (1, 2)
+        if len(groups) > 1:
+            self._gnorm.zero_()
+        for mode in passes:
+            for g in groups:
+                gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
+                epoch = self.sync.next_epoch(0, 3)
+                rc = lib.axb_rs_adamw_ag_pass(
+                    gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
+                    gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
+                    g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.reduce_size,
+                    epoch, lr * g["lr_scale"], opt.betas[0], opt.betas[1], opt.eps, g["weight_decay"], bc1, bc2,
+                    float(opt.max_grad_norm or 0.0), 1.0 / self.dp_size,
+                    self._gnorm.data_ptr(), _lib.status_word(self.device).data_ptr(), WAIT_BUDGET_NS, _lib.stream_ptr(),
+                    sliced, mode)
+                _lib.check_rc(rc, "rs_adamw_ag")
+        for g in opt.groups:   # inactive groups (LISA) keep their weights; their gradients are dropped
+            if not g.get("active", True):
+                g["grad"].zero_()
         opt.skip_zero_grad_once = True  # the kernel already cleared the gradient buffers
         return self._gnorm
 

@@ -20,6 +20,8 @@ _lib.register_cuda_sigs({
                        + [_lib.f32] * 9 + [_lib.vp, _lib.vp, _lib.i64, _lib.vp],
     "axb_rs_adamw_ag_sharded": [_lib.vp] * 5 + [_lib.vp] * 3 + [_lib.vp, _lib.vp, _lib.i64, _lib.i32, _lib.i32, C.c_uint]
                                + [_lib.f32] * 9 + [_lib.vp, _lib.vp, _lib.i64, _lib.vp],
+    "axb_rs_adamw_ag_pass": [_lib.vp] * 5 + [_lib.vp] * 3 + [_lib.vp, _lib.vp, _lib.i64, _lib.i32, _lib.i32, C.c_uint]
+                            + [_lib.f32] * 9 + [_lib.vp, _lib.vp, _lib.i64, _lib.vp, _lib.i32, _lib.i32],
     "axb_peer_allreduce_f32": [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, C.c_uint,
                                _lib.vp, _lib.i64, _lib.vp],
     "axb_gemm_bf16_prefetch": [_lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.i32, _lib.vp, _lib.i64, _lib.vp,

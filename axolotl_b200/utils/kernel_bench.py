@@ -70,6 +70,106 @@ def bench_gemm(rows):
                     f"{fl / lib:.0f} TFLOP/s | ratio {lib / ours:.2f}")
 
 
+def bench_gemm_sustained(rows, seconds=3.0):
+    """Back-to-back GEMMs of one MLP (gate|up and down shapes) for a few seconds: the rate under the
+    board power limit, which is what a training step sees, next to cuBLAS driven the same way, for
+    several wait back-off settings of the CTA-pair kernel. SM clock and power are sampled meanwhile."""
+    import subprocess
+    import threading
+    import time
+
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.ops.gemm import gemm
+
+    lib = _lib.cuda_lib()
+    M, H, I = 8192, 4096, 14336
+    x = torch.randn(M, H, device="cuda", dtype=torch.bfloat16)
+    Wgu = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    Wd = torch.randn(H, I, device="cuda", dtype=torch.bfloat16) * 0.02
+    gu = torch.empty(M, 2 * I, device="cuda", dtype=torch.bfloat16)
+    h = torch.randn(M, I, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * (2 * I) * H + 2.0 * M * H * I
+
+    def ours():
+        gemm(x, Wgu, out=gu)
+        gemm(h, Wd, out=y)
+
+    def cublas():
+        torch.matmul(x, Wgu.t(), out=gu)
+        torch.matmul(h, Wd.t(), out=y)
+
+    def sample(stop, out):
+        while not stop.is_set():
+            try:
+                r = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits",
+                                    "-i", str(torch.cuda.current_device())], capture_output=True, text=True, timeout=5)
+                a, b = r.stdout.strip().split(",")
+                out.append((float(a), float(b)))
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def run(fn, label):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        stop, samples = threading.Event(), []
+        th = threading.Thread(target=sample, args=(stop, samples), daemon=True)
+        th.start()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.perf_counter()
+        s.record()
+        while time.perf_counter() - t0 < seconds:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        e.record()
+        torch.cuda.synchronize()
+        stop.set()
+        th.join()
+        ms = s.elapsed_time(e) / n
+        samples = samples[len(samples) // 3:] or [(0.0, 0.0)]
+        clk = sorted(c for c, _ in samples)[len(samples) // 2]
+        pw = sorted(p for _, p in samples)[len(samples) // 2]
+        rows.append(f"sustained {label}: {ms:.3f} ms per MLP pair, {fl / ms / 1e9:.0f} TFLOP/s, median SM {clk:.0f} MHz, {pw:.0f} W")
+
+    run(cublas, "cuBLAS")
+    for epi_ns, prod_ns in ((0, 0), (64, 0), (256, 0), (64, 32), (1000, 0)):
+        lib.axb_gemm_set_backoff(epi_ns, prod_ns)
+        run(ours, f"ours back-off epilogue {epi_ns} ns / producer {prod_ns} ns")
+    lib.axb_gemm_set_backoff(64, 0)
+
+
+def bench_glu_mlp(rows):
+    """One Llama-3-8B MLP with LoRA, forward + backward: GLU in the GEMM epilogues against the
+    projection-by-projection path with stand-alone GLU kernels."""
+    from axolotl_b200.models.transformer import MLP
+    from axolotl_b200.ops import gemm as gemm_mod
+
+    T, H, I = 8192, 4096, 14336
+    mlp = MLP(H, I, "silu", False, torch.bfloat16, "cuda")
+    with torch.no_grad():
+        mlp.gate_up_proj.weight.normal_(0, 0.02)
+        mlp.down_proj.weight.normal_(0, 0.02)
+    for m in (mlp.gate_up_proj, mlp.down_proj):
+        m.weight.requires_grad_(False)
+        m.add_lora(16, 32, init_b_zero=False)
+    x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    dy = (torch.randn(T, H, device="cuda") * 0.1).bfloat16()
+    params = [p for p in mlp.parameters() if p.requires_grad]
+
+    def step():
+        torch.autograd.grad(mlp(x), [x] + params, dy)
+
+    for flag in (True, False):
+        gemm_mod.USE_GLU_EPILOGUE = flag
+        ms = time_cuda(step)
+        rows.append(f"mlp fwd+bwd LoRA r16 T={T} (GLU {'in GEMM epilogues' if flag else 'as kernels'}): {ms:.3f} ms")
+    gemm_mod.USE_GLU_EPILOGUE = True
+
+
 def bench_lora_skinny(rows):
     """The adapter-side GEMMs of one LoRA projection: memory-bound passes over x or dy."""
     from axolotl_b200.ops.gemm import gemm, pick_splits
@@ -252,6 +352,10 @@ def main(argv):
     rows = []
     if what in ("gemm", "all"):
         bench_gemm(rows)
+    if what in ("sustained",):
+        bench_gemm_sustained(rows)
+    if what in ("mlp", "all"):
+        bench_glu_mlp(rows)
     if what in ("lora", "all"):
         bench_lora_skinny(rows)
     if what in ("attn", "all"):

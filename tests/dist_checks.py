@@ -107,7 +107,7 @@ def check_fused_optimizer(dev, rank, world):
             print(f"fused rs+adamw+ag ok (multimem={'on' if use_mc else 'off'})")
 
 
-def check_training_equivalence(dev, rank, world, backend, replicate=False):
+def check_training_equivalence(dev, rank, world, backend, replicate=False, multigroup=False):
     """A tiny LoRA model trained data-parallel must follow the single-process run on the
     concatenated batch (same seed, deterministic data)."""
     from axolotl_b200.data.collator import PackedCollator
@@ -143,9 +143,14 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False):
             par = build_parallel(model, device=dev, dp_shard=1, dp_replicate=world, backend=backend)
         else:
             par = build_parallel(model, device=dev, dp_shard=world, backend=backend)
-        opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=1e-3, max_grad_norm=1.0,
+        # multigroup: LoRA+ puts the B matrices into a group of their own; the clip factor must still
+        # come from the norm over both groups (max_grad_norm is far below the actual norm, so a
+        # per-group or missing clip changes the update)
+        groups = build_param_groups(model.named_parameters(), loraplus_lr_ratio=4.0 if multigroup else None)
+        opt = FlatAdamW(groups, lr=1e-3, max_grad_norm=0.05 if multigroup else 1.0,
                         alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world,
                         moment_shard=par.moment_shard() if par is not None else None)
+        assert len(opt.groups) == (2 if multigroup else 1)
         opt.bind_model_shadows(model)
         if par is not None:
             par.attach_optimizer(opt)
@@ -177,7 +182,8 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False):
     dist.all_gather(lst, chk)
     assert all(float(x) == float(lst[0]) for x in lst), [float(x) for x in lst]
     if rank == 0:
-        print(f"dp training equivalence ok ({backend}{', replicated' if replicate else ''}): {mean_par} vs {l_ref}")
+        print(f"dp training equivalence ok ({backend}{', replicated' if replicate else ''}"
+              f"{', two groups' if multigroup else ''}): {mean_par} vs {l_ref}")
 
 
 def check_tensor_parallel(dev, rank, world):
@@ -307,6 +313,74 @@ def check_context_parallel(dev, rank, world):
     dist.barrier()
 
 
+def check_tp_cp(dev, rank, world):
+    """TP=2 x CP=world/2 on one packed row: every rank must end with the same replicated adapter
+    factors (the gradient of a replicated weight is summed over the tp AND the cp group) and the
+    losses must follow the single-process run."""
+    from axolotl_b200.data.collator import PackedCollator
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.lora import ALL_LINEAR, LoraSpec, get_peft_state_dict, inject_lora
+    from axolotl_b200.models.transformer import CausalLM
+    from axolotl_b200.parallel.runtime import create_runtime
+    from axolotl_b200.train.optimizer import FlatAdamW, build_param_groups, make_lr_lambda
+    from axolotl_b200.train.trainer import TrainArgs, Trainer
+    import numpy as np
+
+    tp, cp = 2, world // 2
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    cfg = preset("tiny-llama", num_hidden_layers=2, vocab_size=2048, hidden_size=256, intermediate_size=512,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+    S = 256 * cp * 2
+    rng = np.random.default_rng(13)
+    lens = [S // 2 - 57, S // 4 + 100, S - (S // 2 - 57) - (S // 4 + 100)]
+    batches = []
+    for step in range(3):
+        rows = []
+        for l in lens:
+            ids = rng.integers(3, 2048, size=l)
+            lab = ids.copy()
+            lab[: l // 5] = -100
+            rows.append({"input_ids": ids, "labels": lab})
+        batches.append(PackedCollator(pad_to_multiple_of=64)([rows]))
+    spec = LoraSpec(r=8, lora_alpha=16, target_modules=list(ALL_LINEAR))
+
+    def run(on):
+        torch.manual_seed(0)
+        model = CausalLM(cfg, dtype=dtype, device=dev).init_weights(0)
+        par = None
+        if on:
+            par = create_runtime(device=dev, tp=tp, cp=cp)
+            par.tp_max_tokens = 2048
+            par.apply_tp(model)
+        inject_lora(model, spec)
+        opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=2e-3, max_grad_norm=1.0)
+        opt.bind_model_shadows(model)
+        if par is not None:
+            par.attach_optimizer(opt)
+        tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), TrainArgs(max_steps=3, learning_rate=2e-3),
+                     lambda e: [], parallel=par, device=dev)
+        losses = [float(tr.training_step([dict(b)]).item()) for b in batches]
+        return losses, get_peft_state_dict(model)
+
+    l_par, sd = run(True)
+    t = torch.tensor(l_par, dtype=torch.float64, device=dev)
+    dist.all_reduce(t)                       # sum of the cp chunks' losses, counted once per tp rank
+    l_par = (t / tp).tolist()
+    l_ref, _ = run(False)
+    tol = 2e-2 if dev.type == "cuda" else 5e-3
+    assert abs(l_par[0] - l_ref[0]) < (2e-2 if dev.type == "cuda" else 1e-4) * abs(l_ref[0]), (l_par, l_ref)
+    assert all(abs(a - b) < tol * abs(b) for a, b in zip(l_par, l_ref)), (l_par, l_ref)
+    for key in ("base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight",
+                "base_model.model.model.layers.1.mlp.down_proj.lora_B.weight"):
+        chk = sd[key].double().sum().reshape(1).to(dev)
+        lst = [torch.zeros_like(chk) for _ in range(world)]
+        dist.all_gather(lst, chk)
+        assert all(float(x) == float(lst[0]) for x in lst), (key, [float(x) for x in lst])
+    if rank == 0:
+        print(f"tp x cp ok: {l_par} vs {l_ref}")
+    dist.barrier()
+
+
 def check_expert_parallel(dev, rank, world):
     """EP=world MoE training (each rank its own batch) must follow the single-process run with the
     ranks' batches as accumulation micro-batches."""
@@ -381,7 +455,7 @@ def check_expert_parallel(dev, rank, world):
 
 def main():
     cpu = len(sys.argv) > 1 and sys.argv[1] == "cpu"
-    only = set(sys.argv[2:])   # optional subset: gather opt dp ddp tp cp ep
+    only = set(sys.argv[2:])   # optional subset: gather opt dp ddp tp cp ep (tpcp: only on request, 4 ranks)
 
     def want(name):
         return not only or name in only
@@ -391,7 +465,9 @@ def main():
         dist.init_process_group("gloo")
         dev = torch.device("cpu")
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
+        want("dp") and check_training_equivalence(dev, rank, world, "collective", multigroup=True)
         want("ddp") and check_training_equivalence(dev, rank, world, "collective", replicate=True)
+        "tpcp" in only and check_tp_cp(dev, rank, world)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)
         want("ep") and check_expert_parallel(dev, rank, world)
@@ -402,7 +478,9 @@ def main():
         want("gather") and check_gather_gemm(None, dev, rank, world)
         want("opt") and check_fused_optimizer(dev, rank, world)
         want("dp") and check_training_equivalence(dev, rank, world, "fused")
+        want("dp") and check_training_equivalence(dev, rank, world, "fused", multigroup=True)
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
+        "tpcp" in only and check_tp_cp(dev, rank, world)
         want("ddp") and check_training_equivalence(dev, rank, world, "fused", replicate=True)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)

@@ -20,7 +20,16 @@ def _run(nproc, extra, port):
 
 def test_data_parallel_gloo_world2():
     out = _run(2, ["cpu"], 29611)
-    assert "dp training equivalence ok" in out
+    assert "dp training equivalence ok (collective)" in out
+    assert "dp training equivalence ok (collective, two groups)" in out
+    assert "dp training equivalence ok (collective, replicated)" in out
+    for line in ("tensor parallel ok", "context parallel ok", "expert parallel ok"):
+        assert line in out, out[-2000:]
+
+
+def test_tp_x_cp_gloo_world4():
+    out = _run(4, ["cpu", "tpcp"], 29613)
+    assert "tp x cp ok" in out
 
 
 @pytest.mark.gpu
@@ -31,4 +40,8 @@ def test_fused_multi_gpu():
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     out = _run(2, [], 29612)
-    assert "gather-gemm ok" in out and "fused rs+adamw+ag ok" in out
+    for line in ("gather-gemm ok", "fused rs+adamw+ag ok (multimem=on)", "fused rs+adamw+ag ok (multimem=off)",
+                 "dp training equivalence ok (fused)", "dp training equivalence ok (fused, two groups)",
+                 "dp training equivalence ok (collective)", "dp training equivalence ok (fused, replicated)",
+                 "tensor parallel ok", "context parallel ok", "expert parallel ok"):
+        assert line in out, (line, out[-3000:])

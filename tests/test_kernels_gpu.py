@@ -714,3 +714,88 @@ def test_selective_nvfp4_dequant_skips_idle_experts_and_moe_output_is_unchanged(
         y = m(ids, return_logits=True).logits
     assert torch.isfinite(y.float()).all()
     _lib.check_status()
+
+
+@pytest.mark.parametrize("kind,limit", [(0, 0.0), (1, 0.0), (0, 1.5)])
+@pytest.mark.parametrize("M,I,K,R", [(5120, 1024, 512, 32), (4608, 1160, 320, 0)])
+def test_gemm_glu_epilogues(kind, limit, M, I, K, R):
+    """GLU folded into the CTA-pair GEMM: forward (gate|up tile halves) and backward (dh -> d_gate|d_up)."""
+    import torch.nn.functional as F
+    from axolotl_b200.ops.gemm import gemm, glu_fusable
+    torch.manual_seed(11)
+    dev = _dev()
+    assert glu_fusable(M, I, dev)
+    x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    W = (torch.randn(2 * I, K, device=dev) * 0.05).bfloat16()
+    a2 = (torch.randn(M, R, device=dev) * 0.5).bfloat16() if R else None
+    b2 = (torch.randn(2 * I, R, device=dev) * 0.05).bfloat16() if R else None
+    gu = torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16)
+    h = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+    gemm(x, W, a2=a2, b2=b2, out=gu, glu=("fwd", kind, limit, h))
+    _check_status()
+    ref_gu = x.float() @ W.float().t() + (a2.float() @ b2.float().t() if R else 0.0)
+    assert _rel_err(gu, ref_gu) < 5e-3
+    act = (lambda t: F.silu(t)) if kind == 0 else (lambda t: F.gelu(t, approximate="tanh"))
+    g, u = gu[:, :I].float(), gu[:, I:].float()      # the kernel rounds gate / up to bf16 first, as the saved tensor is
+    gc, uc = (g.clamp(max=limit), u.clamp(-limit, limit)) if limit > 0 else (g, u)
+    assert _rel_err(h, act(gc) * uc) < 5e-3
+    # backward: dh = dy @ Wd (+ extension), Wd stored [H, I]
+    Hd = 384
+    dy = (torch.randn(M, Hd, device=dev) * 0.5).bfloat16()
+    Wd = (torch.randn(Hd, I, device=dev) * 0.05).bfloat16()
+    t2 = (torch.randn(M, 16, device=dev) * 0.5).bfloat16() if R else None
+    A2 = (torch.randn(16, I, device=dev) * 0.05).bfloat16() if R else None
+    dgu = torch.empty_like(gu)
+    gemm(dy, Wd, trans_b=True, a2=t2, b2=A2, out=dgu, glu=("bwd", kind, limit, gu))
+    _check_status()
+    dh = dy.float() @ Wd.float() + (t2.float() @ A2.float() if R else 0.0)
+    gl = gc.clone().requires_grad_(True)
+    (da,) = torch.autograd.grad(act(gl).sum(), gl)
+    dg, du = dh * uc * da, dh * act(gc)
+    if limit > 0:
+        dg, du = dg * (g <= limit), du * ((u >= -limit) & (u <= limit))
+    assert _rel_err(dgu[:, :I], dg) < 8e-3
+    assert _rel_err(dgu[:, I:], du) < 8e-3
+    # in place over the saved gate|up
+    gu2 = gu.clone()
+    gemm(dy, Wd, trans_b=True, a2=t2, b2=A2, out=gu2, glu=("bwd", kind, limit, gu2))
+    _check_status()
+    assert torch.equal(gu2, dgu)
+
+
+@pytest.mark.parametrize("lora", [True, False])
+def test_fused_glu_mlp_matches_unfused(lora):
+    """The one-node MLP (GLU in the GEMM epilogues) against the projection-by-projection path."""
+    from axolotl_b200.models.transformer import MLP
+    from axolotl_b200.ops import gemm as gemm_mod
+    torch.manual_seed(12)
+    dev = _dev()
+    T, H, I = 4608, 512, 1152
+    mlp = MLP(H, I, "silu", False, torch.bfloat16, dev)
+    with torch.no_grad():
+        mlp.gate_up_proj.weight.normal_(0, 0.04)
+        mlp.down_proj.weight.normal_(0, 0.04)
+    if lora:
+        for m in (mlp.gate_up_proj, mlp.down_proj):
+            m.weight.requires_grad_(False)
+            m.add_lora(16, 32, init_b_zero=False)
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    dy = (torch.randn(T, H, device=dev) * 0.1).bfloat16()
+    params = [p for p in mlp.parameters() if p.requires_grad]
+
+    def run():
+        y = mlp(x)
+        grads = torch.autograd.grad(y, [x] + params, dy)
+        return y, grads
+
+    assert gemm_mod.glu_fusable(T, I, dev)
+    y1, g1 = run()
+    gemm_mod.USE_GLU_EPILOGUE = False
+    try:
+        y0, g0 = run()
+    finally:
+        gemm_mod.USE_GLU_EPILOGUE = True
+    _check_status()
+    assert _rel_err(y1, y0) < 1e-2
+    for a, b in zip(g1, g0):
+        assert _rel_err(a, b) < 2e-2

@@ -46,12 +46,17 @@ def normalize(cfg):
     # ---- dtype
     resolve_dtype(cfg)
     # ---- cadence
+    n_ep = g("num_epochs") or 1
     if g("saves_per_epoch"):
-        cfg["save_steps"] = 1.0 / (g("saves_per_epoch") * g("num_epochs"))
-        cfg["save_strategy"] = "steps"
-    if g("evals_per_epoch"):
-        cfg["eval_steps"] = 1.0 / (g("evals_per_epoch") * g("num_epochs"))
-        cfg["eval_strategy"] = "steps"
+        frac = 1.0 / (g("saves_per_epoch") * n_ep)
+        if frac < 1.0:   # a ratio of 1 would checkpoint after every step: save at the end only instead
+            cfg["save_steps"] = frac
+            cfg["save_strategy"] = "steps"
+    if g("evals_per_epoch") and (g("val_set_size") or g("test_datasets")):
+        frac = 1.0 / (g("evals_per_epoch") * n_ep)
+        if frac < 1.0:
+            cfg["eval_steps"] = frac
+            cfg["eval_strategy"] = "steps"
     if g("save_steps") and not g("save_strategy"):
         cfg["save_strategy"] = "steps"
     if g("eval_steps") and not g("eval_strategy"):

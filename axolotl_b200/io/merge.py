@@ -27,15 +27,25 @@ LOG = get_logger(__name__)
 
 
 def _adapter_scale(cfg: dict, module_path: str) -> float:
-    r = cfg.get("r", 8)
-    alpha = cfg.get("lora_alpha", r)
-    for pat, rv in (cfg.get("rank_pattern") or {}).items():
-        if re.search(pat, module_path):
-            r = rv
+    r, alpha = _adapter_rank(cfg, module_path), cfg.get("lora_alpha", cfg.get("r", 8))
     for pat, av in (cfg.get("alpha_pattern") or {}).items():
-        if re.search(pat, module_path):
+        if _pattern_hits(pat, module_path):
             alpha = av
     return alpha / math.sqrt(r) if cfg.get("use_rslora") else alpha / r
+
+
+def _pattern_hits(pat: str, module_path: str) -> bool:
+    """PEFT's rule for ``rank_pattern`` / ``alpha_pattern`` keys: the key (a regular expression) has to
+    match the module path as a whole or as a suffix that starts at a module boundary."""
+    return re.match(rf"(.*\.)?({pat})$", module_path) is not None
+
+
+def _adapter_rank(cfg, module_path: str) -> int:
+    r = cfg.get("r", 8)
+    for pat, rv in (cfg.get("rank_pattern") or {}).items():
+        if _pattern_hits(pat, module_path):
+            r = rv
+    return r
 
 
 def load_adapter_tensors(adapter_dir: str):
@@ -82,7 +92,7 @@ def merge_tensor(name: str, w: torch.Tensor, cfg: dict, pairs: dict, shard: dict
             base, e, sub = m.group(1), int(m.group(2)), m.group(3)
             key = f"{base}.{'down_proj' if sub == 'down_proj' else 'gate_up_proj'}"
             if key in pairs:
-                E = pairs[key]["A"].shape[0] // cfg.get("r", 8)
+                E = pairs[key]["A"].shape[0] // _adapter_rank(cfg, key)
                 d = _expert_delta(pairs[key], _adapter_scale(cfg, key), e, E)
                 if sub != "down_proj":
                     half = d.shape[0] // 2

@@ -60,8 +60,9 @@ class HeartbeatMonitor:
 
 
 class HeartbeatCallback(Callback):
-    """Beats after every step and checks the peers before the next one starts; on a peer failure it
-    asks the trainer to save and stop."""
+    """Beats after every step and checks the peers before the next one starts. A peer failure
+    raises ``PeerFailure`` out of ``Trainer.train``; the trainer first writes a collective-free dump
+    of this rank's optimizer state and counters (``Trainer.save_local_state``)."""
 
     def __init__(self, monitor: HeartbeatMonitor):
         self.mon = monitor

@@ -214,8 +214,9 @@ class PrometheusExporter(Callback):
 
 
 class StatusCheckCallback(Callback):
-    """Reads the kernels' status word at every log: a bounded device wait that ran out becomes a
-    Python exception instead of a silent wrong result."""
+    """Reads the kernels' status word at every log (and the trainer reads it again before it writes a
+    checkpoint): a bounded device wait that ran out becomes a Python exception instead of a silent
+    wrong result or a persisted half-reduced step."""
 
     def on_log(self, trainer, logs):
         if trainer.device.type == "cuda":

@@ -132,6 +132,7 @@ class Trainer:
         self.log_history = []
         self.should_stop = False
         self.should_save = False
+        self.batches_in_epoch = 0      # micro-batches consumed in the current epoch (resume skips exactly these)
         self._last_log_time = None
         self._last_log_trainable = 0
         self._loss_acc = None
@@ -201,33 +202,69 @@ class Trainer:
         ga = args.gradient_accumulation_steps
         max_steps = args.max_steps if args.max_steps and args.max_steps > 0 else (self.total_steps or 0)
         start_epoch = self.epoch
-        n_epochs = max(1, math.ceil(args.num_epochs))
+        n_epochs = max(1, math.ceil(args.num_epochs or 1))
         self._last_log_time = time.time()
         skip = getattr(self, "_resume_skip_batches", 0)
         done = False
-        for epoch in range(start_epoch, n_epochs if max_steps <= 0 or args.num_epochs else 10 ** 9):
+        # an explicit max_steps wins over num_epochs: the data is cycled until the steps are done
+        explicit_steps = bool(args.max_steps and args.max_steps > 0)
+        epoch = start_epoch
+        while (explicit_steps or epoch < n_epochs) and not done:
             self.epoch = epoch
+            self.batches_in_epoch = 0
             pending = []
+            seen = 0
             for bi, batch in enumerate(self.train_batches(epoch)):
+                seen += 1
+                self.batches_in_epoch += 1
                 if skip > 0:
                     skip -= 1
                     continue
                 pending.append(batch)
                 if len(pending) < ga:
                     continue
-                for cb in self.callbacks:   # nothing of this rank is in flight here (health checks)
-                    cb.on_pre_step(self)
+                try:
+                    for cb in self.callbacks:   # nothing of this rank is in flight here (health checks)
+                        cb.on_pre_step(self)
+                except Exception as exc:
+                    from ..parallel.health import PeerFailure
+
+                    if isinstance(exc, PeerFailure):
+                        # a peer is gone: no collective may be entered any more. Keep what this rank
+                        # alone can write (optimizer state, RNG, counters), then leave.
+                        LOG.error("peer failure before step %d: %s", self.global_step + 1, exc)
+                        self.should_stop = True
+                        try:
+                            self.save_local_state()
+                        except Exception as save_exc:   # pragma: no cover
+                            LOG.warning("emergency state could not be written: %s", save_exc)
+                    raise
                 loss = self.training_step(pending)
                 pending = []
                 self._after_step(loss)
                 if (max_steps > 0 and self.global_step >= max_steps) or self.should_stop:
                     done = True
                     break
-            if done:
-                break
+            if seen == 0:
+                break   # an empty epoch: nothing to cycle over
+            skip = 0    # a resume skips inside its own epoch only
+            if not done:
+                self._after_epoch()
+            epoch += 1
+        if args.save_strategy == "epoch" and getattr(self, "_last_saved_step", -1) != self.global_step \
+                and not self.should_stop:
+            self._after_epoch()   # the run ended on max_steps inside (or exactly at the end of) an epoch
         for cb in self.callbacks:
             cb.on_train_end(self)
         return self.log_history
+
+    def _after_epoch(self):
+        """``save_strategy: epoch`` / ``eval_strategy: epoch``: act at every epoch boundary."""
+        args = self.args
+        if args.save_strategy == "epoch":
+            self.save_checkpoint()
+        if args.eval_strategy == "epoch" and self.eval_batches is not None:
+            self.evaluate()
 
     def _after_step(self, loss):
         args = self.args
@@ -324,6 +361,10 @@ class Trainer:
         return os.path.join(self.args.output_dir, f"checkpoint-{self.global_step if step is None else step}")
 
     def save_checkpoint(self):
+        if self.device.type == "cuda":
+            from ..ops import _lib
+
+            _lib.check_status(self.device)   # never persist weights of a step whose device wait ran out
         d = self.checkpoint_dir()
         if self.rank == 0:
             os.makedirs(d, exist_ok=True)
@@ -343,14 +384,28 @@ class Trainer:
         if self.rank == 0:
             state = {"global_step": self.global_step, "epoch": self.epoch, "log_history": self.log_history,
                      "max_steps": self.args.max_steps, "total_steps": self.total_steps,
-                     "batches_in_epoch": self.global_step * self.args.gradient_accumulation_steps}
+                     "batches_in_epoch": self.batches_in_epoch}
             with open(os.path.join(d, "trainer_state.json"), "w") as fh:
                 json.dump(state, fh, indent=1)
             with open(os.path.join(d, TOKENS_STATE_FILE), "w") as fh:
                 json.dump(self.tokens, fh)
             self._rotate_checkpoints()
+        self._last_saved_step = self.global_step
         for cb in self.callbacks:
             cb.on_save(self, d)
+        return d
+
+    def save_local_state(self):
+        """Collective-free emergency dump of this rank's optimizer state, RNG and counters into
+        ``<output_dir>/emergency-<step>/`` (used when a peer failed: barriers and weight gathers are
+        off limits then). Replicated trainable weights are part of the optimizer's fp32 masters."""
+        d = os.path.join(self.args.output_dir, f"emergency-{self.global_step}")
+        os.makedirs(d, exist_ok=True)
+        torch.save(self.opt.state_dict(), os.path.join(d, f"optimizer_rank{self.rank}.pt"))
+        state = {"global_step": self.global_step, "epoch": self.epoch, "batches_in_epoch": self.batches_in_epoch,
+                 "tokens": self.tokens, "rank": self.rank, "world_size": self.world_size}
+        with open(os.path.join(d, f"trainer_state_rank{self.rank}.json"), "w") as fh:
+            json.dump(state, fh, indent=1)
         return d
 
     def _rotate_checkpoints(self):

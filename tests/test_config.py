@@ -93,6 +93,24 @@ def test_saves_per_epoch_and_eval_cadence():
     assert cfg.eval_steps == pytest.approx(0.125) and cfg.eval_strategy == "steps"
     cfg2 = load_cfg(dict(BASE))
     assert cfg2.eval_strategy == "no"
+    # one save per epoch of a one-epoch run is "save at the end", not "after every step"
+    cfg3 = load_cfg(dict(BASE, saves_per_epoch=1, num_epochs=1, val_set_size=0.1, evals_per_epoch=1))
+    assert not cfg3.save_steps and not cfg3.eval_steps
+    cfg4 = load_cfg(dict(BASE, saves_per_epoch=2))          # num_epochs unset counts as 1
+    assert cfg4.save_steps == pytest.approx(0.5)
+
+
+def test_rank_and_alpha_patterns_match_like_peft():
+    from axolotl_b200.io.merge import _adapter_rank, _adapter_scale
+
+    cfg = {"r": 8, "lora_alpha": 16, "rank_pattern": {"q_proj": 4, r"layers\.1\.mlp\.down_proj": 2},
+           "alpha_pattern": {"q_proj": 32}}
+    assert _adapter_rank(cfg, "model.layers.0.self_attn.q_proj") == 4
+    assert _adapter_rank(cfg, "model.layers.0.self_attn.qq_proj") == 8        # no module boundary before the key
+    assert _adapter_rank(cfg, "model.layers.0.self_attn.q_proj_extra") == 8   # suffix rule, not a substring search
+    assert _adapter_rank(cfg, "model.layers.1.mlp.down_proj") == 2
+    assert _adapter_rank(cfg, "model.layers.11.mlp.down_proj") == 8
+    assert _adapter_scale(cfg, "model.layers.0.self_attn.q_proj") == 32 / 4
 
 
 def test_cli_style_overrides_and_yaml_file(tmp_path):

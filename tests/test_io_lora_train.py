@@ -258,6 +258,64 @@ def test_trainer_checkpoint_resume_is_exact(tmp_path):
     assert torch.allclose(a, b, atol=1e-6)
 
 
+def _epoch_trainer(tmp, *, num_epochs, max_steps=-1, resume=None, save_strategy="steps", save_steps=2):
+    """12 micro-batches per epoch whose ORDER depends on the epoch, gradient accumulation 2 -> 6 steps per epoch."""
+    from axolotl_b200.data.collator import PackedCollator
+    from axolotl_b200.data.synthetic import synthetic_varlen
+
+    torch.manual_seed(0)
+    model = _tiny(3)
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=list(ALL_LINEAR))
+    inject_lora(model, spec)
+    _randomise_lora(model)
+    opt = FlatAdamW(build_param_groups(model.named_parameters()), lr=5e-3, max_grad_norm=1.0)
+    ds = synthetic_varlen(24, 20, 60, 3, 256, 0.25, seed=1)
+    coll = PackedCollator()
+
+    def batches(epoch):
+        order = np.random.default_rng(100 + epoch).permutation(12)
+        for i in order:
+            yield coll([[ds[2 * i], ds[2 * i + 1]]])
+
+    args = TrainArgs(output_dir=str(tmp), max_steps=max_steps, num_epochs=num_epochs, gradient_accumulation_steps=2,
+                     learning_rate=5e-3, save_steps=save_steps, save_strategy=save_strategy, save_total_limit=20,
+                     resume_from_checkpoint=resume)
+    tr = Trainer(model, opt, make_lr_lambda("constant", 100, 0), args, batches, total_steps=6 * num_epochs,
+                 save_fn=lambda t, d: save_adapter(model, spec, d))
+    if resume:
+        load_adapter(model, resume)
+    return tr, model
+
+
+def test_resume_from_a_checkpoint_in_a_later_epoch(tmp_path):
+    """A checkpoint taken inside epoch 1 of a 3-epoch run: the resumed run skips only the batches
+    of THAT epoch which were already consumed, and ends exactly like the uninterrupted run."""
+    tr, model = _epoch_trainer(tmp_path / "a", num_epochs=3)
+    full = [h["loss"] for h in tr.train() if "loss" in h]
+    assert len(full) == 18 and tr.epoch == 2
+    ck = tmp_path / "a" / "checkpoint-10"       # step 10 = epoch 1, 4 of its 6 steps done
+    state = json.load(open(ck / "trainer_state.json"))
+    assert state["epoch"] == 1 and state["batches_in_epoch"] == 8
+    tr2, model2 = _epoch_trainer(tmp_path / "a", num_epochs=3, resume=str(ck))
+    hist2 = tr2.train()
+    tail = [h["loss"] for h in hist2 if "loss" in h and h["step"] > 10]
+    assert len(tail) == 8 and tr2.global_step == 18
+    assert tail == pytest.approx(full[10:], rel=1e-5)
+    a = torch.cat([p.detach().reshape(-1) for p in model.parameters() if p.requires_grad])
+    b = torch.cat([p.detach().reshape(-1) for p in model2.parameters() if p.requires_grad])
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_epoch_save_strategy_and_max_steps_beyond_the_data(tmp_path):
+    tr, _ = _epoch_trainer(tmp_path / "e", num_epochs=2, save_strategy="epoch", save_steps=None)
+    tr.train()
+    assert sorted(os.listdir(tmp_path / "e")) == ["checkpoint-12", "checkpoint-6"]
+    # max_steps larger than num_epochs x steps-per-epoch: the data is cycled until the steps are done
+    tr2, _ = _epoch_trainer(tmp_path / "m", num_epochs=1, max_steps=9, save_strategy="no", save_steps=None)
+    tr2.train()
+    assert tr2.global_step == 9 and tr2.epoch == 1
+
+
 def test_loss_decreases_on_learnable_data():
     from axolotl_b200.data.collator import PackedCollator
 

@@ -159,6 +159,24 @@ AXB_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint
         "r"(smem_u32(bar))
       : "memory");
 }
+// tile store shared -> global (bulk async group of the issuing thread); out-of-range rows / columns
+// of the box are clipped by the tensor map
+AXB_DEVICE void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+AXB_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest N bulk groups of this thread have finished READING shared memory
+template <int N>
+AXB_DEVICE void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+AXB_DEVICE void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 AXB_DEVICE void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -366,7 +384,7 @@ inline AxbEncodeTiledFn axb_get_encode_fn() {
 // Returns 0 on success.
 inline int axb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                             uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols,
-                            int elem_bytes = 2, bool swizzle128 = true) {
+                            int elem_bytes = 2, bool swizzle128 = true, bool swizzle64 = false) {
   AxbEncodeTiledFn fn = axb_get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {cols, rows};
@@ -380,7 +398,8 @@ inline int axb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, u
   for (int attempt = 0; attempt < 2; ++attempt) {
     r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
            CU_TENSOR_MAP_INTERLEAVE_NONE,
-           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+           swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                     : (swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_ERROR_INVALID_CONTEXT) break;
     // A thread that has made no runtime call yet (e.g. an autograd worker) has no current

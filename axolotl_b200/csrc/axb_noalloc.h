@@ -16,8 +16,12 @@
 //   * T * Hq * D  <= AXB_NOALLOC_MAX_DQ_FLOATS   (4,194,304; e.g. 1024 tokens x 32 heads x 128)
 //     Hq * T      <= AXB_NOALLOC_MAX_DELTA_FLOATS (65,536)
 //     Larger problems are rejected with AXB_NOALLOC_TOO_LARGE and a message in `err`.
+//     An empty problem (T == 0 or no tiles) returns 0 without launching anything; a negative T or
+//     a non-positive Hq / D is rejected with AXB_NOALLOC_BAD_SIZE.
 //   * The first call on a device looks up the device address of the array (a one-time set-up
-//     with that device current). Make that first call outside of any stream capture.
+//     with that device current). Make that first call outside of any stream capture. Two host
+//     threads that make their first call on the same device at the same time both look the
+//     address up and store the same value into the per-device cache, which is harmless.
 //   * All calls share the one array and it keeps whatever the previous call left in it; each
 //     call clears the part that must start at zero. Two calls that overlap on the GPU (different
 //     streams, or different host threads without ordering) race on it: serialise them.
@@ -32,6 +36,7 @@ extern "C" {
 #define AXB_NOALLOC_MAX_DELTA_FLOATS 65536
 #define AXB_NOALLOC_TOO_LARGE (-20)
 #define AXB_NOALLOC_SETUP_FAILED (-21)
+#define AXB_NOALLOC_BAD_SIZE (-22)
 
 // Same arguments as axb_flash_varlen_bwd without the two scratch pointers; `err` (optional,
 // `err_len` bytes) receives a human-readable reason when the return value is negative.

@@ -1017,9 +1017,10 @@ extern "C" int axb_flash_varlen_bwd_noalloc(const void* qkv, long long ld, const
                                             void* dqkv, long long dqkv_ld, float softmax_scale,
                                             int* status, void* stream, char* err, int err_len) {
   if (T < 0 || Hq <= 0 || D <= 0) {
-    set_err(err, err_len, "axb_flash_varlen_bwd_noalloc: negative or zero problem size");
-    return AXB_NOALLOC_TOO_LARGE;
+    set_err(err, err_len, "axb_flash_varlen_bwd_noalloc: T must be >= 0 and Hq, D must be positive");
+    return AXB_NOALLOC_BAD_SIZE;
   }
+  if (T == 0 || n_tiles <= 0) return 0;  // an empty batch: nothing to compute, nothing launched
   const long long dq_floats = T * (long long)Hq * D;
   const long long delta_floats = T * (long long)Hq;
   if (dq_floats > AXB_NOALLOC_MAX_DQ_FLOATS || delta_floats > AXB_NOALLOC_MAX_DELTA_FLOATS) {

@@ -85,9 +85,36 @@ struct GemmParams {
   long long ldh;
   int epi_sleep_ns;   // back-off of the epilogue warps while they wait for an accumulator (0 = spin)
   int prod_sleep_ns;  // back-off of the TMA producer while it waits for a free stage (0 = spin)
+  // bf16 results leave through swizzled shared-memory staging tiles and TMA tile stores (full 128-byte
+  // lines, no per-thread row stores); 0 = every thread stores its own row (fp32 output, beta != 0,
+  // unaligned C)
+  int tma_store;
 };
 
-int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0;
+int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0, g_pair_group_m = 4, g_pair_tma_store = 1;
+
+// Row `lane` of a 32-row staging tile with 128-byte rows (64 bf16) and the 128-byte swizzle the
+// tensor map expects: 16-byte chunk j of row r sits at chunk position j ^ (r & 7). The tile base is
+// 1024-byte aligned.
+__device__ __forceinline__ void stage_row128(uint8_t* tile, int lane, const uint4 (&w)[8]) {
+  uint8_t* rowp = tile + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = w[j];
+}
+// Same for 64-byte rows (32 bf16) and the 64-byte swizzle: chunk j of row r sits at j ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage_row64(uint8_t* tile, int lane, const uint4 (&w)[4]) {
+  uint8_t* rowp = tile + lane * 64;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(rowp + ((j ^ ((lane >> 1) & 3)) << 4)) = w[j];
+}
+__device__ __forceinline__ uint4 pack8(const uint32_t* r, float alpha) {
+  uint4 o;
+  o.x = pack_bf16x2(__uint_as_float(r[0]) * alpha, __uint_as_float(r[1]) * alpha);
+  o.y = pack_bf16x2(__uint_as_float(r[2]) * alpha, __uint_as_float(r[3]) * alpha);
+  o.z = pack_bf16x2(__uint_as_float(r[4]) * alpha, __uint_as_float(r[5]) * alpha);
+  o.w = pack_bf16x2(__uint_as_float(r[6]) * alpha, __uint_as_float(r[7]) * alpha);
+  return o;
+}
 
 // Spin on an mbarrier with a pause between polls: the waiting warps stop competing for issue slots
 // (and for the power budget of a kernel that runs against the board limit) with the MMA stream.
@@ -121,41 +148,6 @@ __device__ __forceinline__ float glu_act_grad(float g, int kind) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   const float t = tanhf(k0 * (g + k1 * g * g * g));
   return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
-}
-__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, bool vec, int n, float (&o)[32]) {
-  if (vec) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint4 in = *reinterpret_cast<const uint4*>(src + q * 8);
-      const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = unpack_bf16x2(w[e]);
-        o[q * 8 + 2 * e] = f.x;
-        o[q * 8 + 2 * e + 1] = f.y;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) o[j] = j < n ? __bfloat162float(src[j]) : 0.f;
-  }
-}
-__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, bool vec, int n, const float (&v)[32]) {
-  if (vec) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint4 o;
-      o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-      o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-      o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-      o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-      *reinterpret_cast<uint4*>(dst + q * 8) = o;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < n) dst[j] = __float2bfloat16(v[j]);
-  }
 }
 
 constexpr int GATHER_CHUNK = 8192;
@@ -925,20 +917,23 @@ constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = 128 * BK * 2;       // 16 KB
 constexpr int P_B_BYTES = 128 * BK * 2;       // 16 KB (this CTA's half of the 256-wide B tile)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_EPI_BYTES = 4 * 2 * 4096;     // per epilogue warp: two staging slots of 32 rows x 128 bytes
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 + 256;
 constexpr int P_TMEM_COLS = 512;              // 2 accumulator stages x 256 columns
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                          const GemmParams p) {
+                          const __grid_constant__ CUtensorMap tmE0, const __grid_constant__ CUtensorMap tmE1,
+                          const __grid_constant__ CUtensorMap tmE2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + P_STAGES * P_A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint8_t* sEpi = smem + P_STAGES * P_STAGE_BYTES;   // 1024-byte aligned (stages are 32 KB each)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES + P_EPI_BYTES);
   uint64_t* full_bar = bars;                       // used in rank 0 only: both CTAs' loads of the stage
   uint64_t* empty_bar = bars + P_STAGES;           // one per CTA, signalled by the pair commit
   uint64_t* tfull_bar = bars + 2 * P_STAGES;       // one per CTA
@@ -1075,6 +1070,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ------------------------------------------------------------ epilogue warps (both CTAs)
     const int lane_group = warp & 3;
+    uint8_t* my_epi = sEpi + lane_group * 8192;   // this warp's two staging slots
+    int slot = 0;
     int it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
@@ -1090,74 +1087,167 @@ __global__ void __launch_bounds__(kThreads, 1)
       const long long row = (long long)m_blk * 256 + rank * 128 + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * 256;
+      const int warp_row0 = m_blk * 256 + (int)rank * 128 + lane_group * 32;   // first row of this warp's 32
+      const bool warp_rows = warp_row0 < p.M;
+      // stage one 32 x 64 bf16 tile (this warp's rows) and hand it to the TMA store engine
+      auto put128 = [&](const CUtensorMap* map, const uint4 (&w)[8], int col0) {
+        uint8_t* tile = my_epi + slot * 4096;
+        if (lane == 0) bulk_wait_group_read<1>();   // the store that last read this slot is done with it
+        __syncwarp();
+        stage_row128(tile, lane, w);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map, tile, col0, warp_row0);
+          bulk_commit_group();
+        }
+        slot ^= 1;
+      };
       if (p.epi == 1) {
         // GLU forward: columns [0, 128) of the accumulator are gate, [128, 256) the matching up columns
         const int I = p.N;
         const bool lim = p.glu_limit > 0.f;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32(t_addr + c * 32, rg);
-          tmem_ld_32x32(t_addr + 128 + c * 32, ru);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r0[32], r1[32];
+          uint4 gw[8], uw[8];
+          tmem_ld_32x32(t_addr + c * 64, r0);
+          tmem_ld_32x32(t_addr + c * 64 + 32, r1);
           tmem_ld_wait();
-          const int col0 = n_blk * 128 + c * 32;
-          if (!row_ok || col0 >= I) continue;
-          const int n = min(32, I - col0);
-          float g[32], u[32], h[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            g[j] = __uint_as_float(rg[j]) * p.alpha;
-            u[j] = __uint_as_float(ru[j]) * p.alpha;
+          for (int j = 0; j < 4; ++j) {
+            gw[j] = pack8(r0 + 8 * j, p.alpha);
+            gw[4 + j] = pack8(r1 + 8 * j, p.alpha);
           }
+          tmem_ld_32x32(t_addr + 128 + c * 64, r0);
+          tmem_ld_32x32(t_addr + 128 + c * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uw[j] = pack8(r0 + 8 * j, p.alpha);
+            uw[4 + j] = pack8(r1 + 8 * j, p.alpha);
+          }
+          const int col0 = n_blk * 128 + c * 64;
+          if (!warp_rows || col0 >= I) continue;
           if (p.C) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
-            const bool vec = n == 32 && (p.ldc & 7) == 0 && (I & 7) == 0;
-            store_bf16x32(crow, vec, n, g);
-            store_bf16x32(crow + I, vec, n, u);
+            put128(&tmE0, gw, col0);
+            put128(&tmE1, uw, col0);
           }
+          // h from the bf16-rounded gate / up, so that the backward pass sees the same values
+          uint4 hw[8];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            // the stored gate / up are bf16: round first so that the backward pass sees the same values
-            const float gr = __bfloat162float(__float2bfloat16(g[j]));
-            const float ur = __bfloat162float(__float2bfloat16(u[j]));
-            const float gc = lim ? fminf(gr, p.glu_limit) : gr;
-            const float uc = lim ? fminf(fmaxf(ur, -p.glu_limit), p.glu_limit) : ur;
-            h[j] = glu_act(gc, p.glu_kind) * uc;
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t g4[4] = {gw[j].x, gw[j].y, gw[j].z, gw[j].w};
+            const uint32_t u4[4] = {uw[j].x, uw[j].y, uw[j].z, uw[j].w};
+            uint32_t h4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 g = unpack_bf16x2(g4[e]), u = unpack_bf16x2(u4[e]);
+              const float ga = lim ? fminf(g.x, p.glu_limit) : g.x, gb = lim ? fminf(g.y, p.glu_limit) : g.y;
+              const float ua = lim ? fminf(fmaxf(u.x, -p.glu_limit), p.glu_limit) : u.x;
+              const float ub = lim ? fminf(fmaxf(u.y, -p.glu_limit), p.glu_limit) : u.y;
+              h4[e] = pack_bf16x2(glu_act(ga, p.glu_kind) * ua, glu_act(gb, p.glu_kind) * ub);
+            }
+            hw[j] = make_uint4(h4[0], h4[1], h4[2], h4[3]);
           }
-          store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.H) + row * p.ldh + col0, n == 32 && (p.ldh & 7) == 0, n, h);
+          put128(&tmE2, hw, col0);
         }
       } else if (p.epi == 2) {
-        // GLU backward: the accumulator is dh; gate | up come from Cin, d_gate | d_up go to C
+        // GLU backward: the accumulator is dh; gate | up are read straight from Cin (row per thread,
+        // the next chunk's 2 x 64 bytes are requested before this chunk is computed), d_gate | d_up
+        // leave through 32 x 32 staging tiles (64-byte rows) and TMA stores.
         const int I = p.N;
         const bool lim = p.glu_limit > 0.f;
         const float L = p.glu_limit;
+        const long long my_row = (long long)warp_row0 + lane;
+        const bool row_in = my_row < p.M;
+        const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + my_row * p.ldcin;
+        auto fetch = [&](int col0, uint4 (&g)[4], uint4 (&u)[4]) {
+          if (row_in && col0 + 32 <= I) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              g[j] = *reinterpret_cast<const uint4*>(grow + col0 + 8 * j);
+              u[j] = *reinterpret_cast<const uint4*>(grow + I + col0 + 8 * j);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) g[j] = u[j] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        };
+        uint4 gq[4], uq[4];
+        fetch(n_blk * 256, gq, uq);
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
+          const int col0 = n_blk * 256 + c * 32;
+          uint4 gn[4], un[4];
+          if (c < 7) fetch(col0 + 32, gn, un);
           uint32_t r[32];
           tmem_ld_32x32(t_addr + c * 32, r);
           tmem_ld_wait();
-          const int col0 = n_blk * 256 + c * 32;
-          if (!row_ok || col0 >= I) continue;
-          const int n = min(32, I - col0);
-          const __nv_bfloat16* irow = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + row * p.ldcin + col0;
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
-          const bool vin = n == 32 && (p.ldcin & 7) == 0 && (I & 7) == 0;
-          const bool vout = n == 32 && (p.ldc & 7) == 0 && (I & 7) == 0;
-          float g[32], u[32];
-          load_bf16x32(irow, vin, n, g);
-          load_bf16x32(irow + I, vin, n, u);
+          if (warp_rows && col0 < I) {
+            uint4 dg[4], du[4];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float d = __uint_as_float(r[j]) * p.alpha;
-            const bool g_in = !lim || g[j] <= L;
-            const bool u_in = !lim || (u[j] >= -L && u[j] <= L);
-            const float gc = g_in ? g[j] : L;
-            const float uc = u_in ? u[j] : (u[j] > 0.f ? L : -L);
-            g[j] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
-            u[j] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t g4[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w};
+              const uint32_t u4[4] = {uq[j].x, uq[j].y, uq[j].z, uq[j].w};
+              uint32_t og[4], ou[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g = unpack_bf16x2(g4[e]), u = unpack_bf16x2(u4[e]);
+                const float gv[2] = {g.x, g.y}, uv[2] = {u.x, u.y};
+                float a[2], b[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const float d = __uint_as_float(r[8 * j + 2 * e + h]) * p.alpha;
+                  const bool g_in = !lim || gv[h] <= L;
+                  const bool u_in = !lim || (uv[h] >= -L && uv[h] <= L);
+                  const float gc = g_in ? gv[h] : L;
+                  const float uc = u_in ? uv[h] : (uv[h] > 0.f ? L : -L);
+                  a[h] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
+                  b[h] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
+                }
+                og[e] = pack_bf16x2(a[0], a[1]);
+                ou[e] = pack_bf16x2(b[0], b[1]);
+              }
+              dg[j] = make_uint4(og[0], og[1], og[2], og[3]);
+              du[j] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+            }
+            uint8_t* tile = my_epi + slot * 4096;
+            if (lane == 0) bulk_wait_group_read<1>();
+            __syncwarp();
+            stage_row64(tile, lane, dg);
+            stage_row64(tile + 2048, lane, du);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmE0, tile, col0, warp_row0);
+              tma_store_2d(&tmE1, tile + 2048, col0, warp_row0);
+              bulk_commit_group();
+            }
+            slot ^= 1;
           }
-          store_bf16x32(crow, vout, n, g);
-          store_bf16x32(crow + I, vout, n, u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            gq[j] = gn[j];
+            uq[j] = un[j];
+          }
+        }
+      } else if (p.tma_store) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_addr + c * 64, r0);
+          tmem_ld_32x32(t_addr + c * 64 + 32, r1);
+          tmem_ld_wait();
+          const int col0 = n_blk * 256 + c * 64;
+          if (!warp_rows || col0 >= p.N) continue;
+          uint4 w[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            w[j] = pack8(r0 + 8 * j, p.alpha);
+            w[4 + j] = pack8(r1 + 8 * j, p.alpha);
+          }
+          put128(&tmE0, w, col0);
         }
       } else
 #pragma unroll 1
@@ -1227,6 +1317,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
     }
+    if (lane == 0) bulk_wait_group<0>();   // staged tiles are in global memory before shared memory goes away
   }
 
   tc_fence_before();
@@ -1240,7 +1331,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <bool A_MN, bool B_MN>
 int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2, const CUtensorMap& tB2,
-                GemmParams p, int sms, cudaStream_t stream) {
+                const CUtensorMap& tE0, const CUtensorMap& tE1, const CUtensorMap& tE2, GemmParams p, int sms,
+                cudaStream_t stream) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -1264,7 +1356,7 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, tE0, tE1, tE2, p);
 }
 
 }  // namespace
@@ -1287,6 +1379,12 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
   if (epi < 0 || epi > 2) return -3;
   if (epi == 1 && (b_mn || out_mode != 0 || H == nullptr)) return -3;
   if (epi == 2 && (out_mode != 0 || Cin == nullptr || C == nullptr)) return -3;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (epi != 0) {  // the GLU epilogues move whole 16-byte vectors and 32-column chunks
+    if ((N & 31) || (ldc & 7) || !al16(C) || (epi == 1 && ((ldh & 7) || !al16(H))) ||
+        (epi == 2 && ((ldcin & 7) || !al16(Cin))))
+      return -2;
+  }
   const int n_rows_b = epi == 1 ? 2 * N : N;   // rows of the stored B (K-major) / columns (MN-major)
   CUtensorMap tA, tB, tA2, tB2;
   int rc = 0;
@@ -1300,6 +1398,26 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
     tA2 = tA;
     tB2 = tB;
   }
+  // epilogue maps: staging tiles of 32 rows x 64 columns (128-byte swizzle), or 32 x 32 (64-byte swizzle)
+  // for the GLU backward pass
+  CUtensorMap tE0 = tA, tE1 = tA, tE2 = tA;
+  int tma_store = 0;
+  const __nv_bfloat16* Cb = reinterpret_cast<const __nv_bfloat16*>(C);
+  if (epi == 0) {
+    if (g_pair_tma_store && out_mode == 0 && Cin == nullptr && (ldc & 7) == 0 && al16(C)) {
+      rc |= axb_make_tmap_2d(&tE0, C, M, N, ldc, 32, 64);
+      tma_store = 1;
+    }
+  } else if (epi == 1) {
+    if (C) {
+      rc |= axb_make_tmap_2d(&tE0, Cb, M, N, ldc, 32, 64);
+      rc |= axb_make_tmap_2d(&tE1, Cb + N, M, N, ldc, 32, 64);
+    }
+    rc |= axb_make_tmap_2d(&tE2, H, M, N, ldh, 32, 64);
+  } else {
+    rc |= axb_make_tmap_2d(&tE0, Cb, M, N, ldc, 32, 32, 2, false, true);
+    rc |= axb_make_tmap_2d(&tE1, Cb + N, M, N, ldc, 32, 32, 2, false, true);
+  }
   if (rc) return -4;
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K; p.K2 = K2 > 0 ? K2 : 0;
@@ -1307,16 +1425,17 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
   p.alpha = alpha; p.beta = beta; p.out_mode = out_mode; p.splits = 1; p.status = status;
   p.epi = epi; p.glu_kind = glu_kind; p.glu_limit = glu_limit; p.H = H; p.ldh = ldh;
   p.epi_sleep_ns = g_epi_sleep_ns; p.prod_sleep_ns = g_prod_sleep_ns;
-  p.group_m = 4;  // bands of 4 x 256 rows
+  p.tma_store = tma_store;
+  p.group_m = g_pair_group_m;  // rows of 256-row tiles per rasterisation band
   PrefetchArgs pf;
   pf.peer_bases = pf_peer_bases; pf.shard_offset = pf_shard_offset; pf.shard_bytes = pf_shard_bytes;
   pf.world = pf_world; pf.dst = pf_dst; pf.ctas = pf_ctas;
   if ((rc = fill_prefetch(p, &pf)) != 0) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return launch_pair<false, false>(tA, tB, tA2, tB2, p, sm_count(), st);
-  if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, p, sm_count(), st);
-  if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, p, sm_count(), st);
-  return launch_pair<true, true>(tA, tB, tA2, tB2, p, sm_count(), st);
+  if (!a_mn && !b_mn) return launch_pair<false, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
+  if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
+  if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
+  return launch_pair<true, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
 }
 
 extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
@@ -1353,4 +1472,12 @@ extern "C" int axb_gemm_bf16_pair_glu(const void* A, long long lda, int a_mn, co
 extern "C" void axb_gemm_set_backoff(int epi_sleep_ns, int prod_sleep_ns) {
   g_epi_sleep_ns = epi_sleep_ns;
   g_prod_sleep_ns = prod_sleep_ns;
+}
+
+// Tuning of the CTA-pair kernel: 256-row tile rows per rasterisation band (the A rows of a band stay
+// in L2 while the band sweeps over N) and whether bf16 results leave through TMA tile stores (1) or
+// per-thread row stores (0).
+extern "C" void axb_gemm_set_pair_tuning(int group_m, int tma_store) {
+  if (group_m > 0) g_pair_group_m = group_m;
+  g_pair_tma_store = tma_store;
 }

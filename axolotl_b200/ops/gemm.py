@@ -19,7 +19,7 @@ _SM = 148
 USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "1") != "0"
 # GLU folded into the gate|up GEMM epilogue (forward) and the down-projection input-gradient GEMM
 # (backward); AXB_GLU_EPILOGUE=0 runs the stand-alone GLU kernels instead.
-USE_GLU_EPILOGUE = os.environ.get("AXB_GLU_EPILOGUE", "1") != "0"
+USE_GLU_EPILOGUE = os.environ.get("AXB_GLU_EPILOGUE", "0") != "0"
 
 
 def _pick_bn(M: int, N: int) -> int:
@@ -163,8 +163,8 @@ def gemm(
 
 def glu_fusable(M: int, I: int, device) -> bool:
     """Whether the GLU epilogues of the CTA-pair kernel serve an MLP with ``M`` token rows and ``I``
-    intermediate columns (enough 256-row tiles for the 74 SM pairs, 16-byte aligned rows)."""
-    return (USE_PAIR and USE_GLU_EPILOGUE and device.type == "cuda" and M >= 512 and I % 8 == 0
+    intermediate columns (enough 256-row tiles for the 74 SM pairs, whole 32-column chunks)."""
+    return (USE_PAIR and USE_GLU_EPILOGUE and device.type == "cuda" and M >= 512 and I % 32 == 0
             and ((M + 255) // 256) * ((I + 255) // 256) >= 74)
 
 

@@ -136,10 +136,10 @@ def bench_gemm_sustained(rows, seconds=3.0):
         rows.append(f"sustained {label}: {ms:.3f} ms per MLP pair, {fl / ms / 1e9:.0f} TFLOP/s, median SM {clk:.0f} MHz, {pw:.0f} W")
 
     run(cublas, "cuBLAS")
-    for epi_ns, prod_ns in ((0, 0), (64, 0), (256, 0), (64, 32), (1000, 0)):
-        lib.axb_gemm_set_backoff(epi_ns, prod_ns)
-        run(ours, f"ours back-off epilogue {epi_ns} ns / producer {prod_ns} ns")
-    lib.axb_gemm_set_backoff(64, 0)
+    for group_m, tma in ((4, 0), (4, 1), (8, 1), (16, 1), (2, 1), (32, 1)):
+        lib.axb_gemm_set_pair_tuning(group_m, tma)
+        run(ours, f"ours band of {group_m} tile rows, {'TMA tile stores' if tma else 'per-thread row stores'}")
+    lib.axb_gemm_set_pair_tuning(4, 1)
 
 
 def bench_glu_mlp(rows):
@@ -163,11 +163,33 @@ def bench_glu_mlp(rows):
     def step():
         torch.autograd.grad(mlp(x), [x] + params, dy)
 
+    prev = gemm_mod.USE_GLU_EPILOGUE
     for flag in (True, False):
         gemm_mod.USE_GLU_EPILOGUE = flag
         ms = time_cuda(step)
         rows.append(f"mlp fwd+bwd LoRA r16 T={T} (GLU {'in GEMM epilogues' if flag else 'as kernels'}): {ms:.3f} ms")
+    gemm_mod.USE_GLU_EPILOGUE = prev
+    # the two GEMMs that carry the GLU, alone
+    from axolotl_b200.ops.gemm import gemm
+
+    Wgu, Wd = mlp.gate_up_proj.weight, mlp.down_proj.weight
+    xd = x.detach()
+    gu = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    dgu = torch.empty_like(gu)
+    dh = torch.empty_like(h)
+    gemm(xd, Wgu, out=gu)
+    t0 = time_cuda(lambda: gemm(xd, Wgu, out=gu))
     gemm_mod.USE_GLU_EPILOGUE = True
+    t1 = time_cuda(lambda: gemm(xd, Wgu, out=gu, glu=("fwd", 0, 0.0, h)))
+    t2 = time_cuda(lambda: gemm(dy, Wd, trans_b=True, out=dh))
+    t3 = time_cuda(lambda: gemm(dy, Wd, trans_b=True, out=dgu, glu=("bwd", 0, 0.0, gu)))
+    gemm_mod.USE_GLU_EPILOGUE = prev
+    from axolotl_b200.ops import functional as Fn
+
+    t4 = time_cuda(lambda: Fn.glu(gu))
+    rows.append(f"gate|up GEMM {t0:.3f} ms, with GLU epilogue {t1:.3f} ms | dX(down) GEMM {t2:.3f} ms, with GLU-backward "
+                f"epilogue {t3:.3f} ms | stand-alone GLU forward kernel {t4:.3f} ms")
 
 
 def bench_lora_skinny(rows):

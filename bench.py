@@ -8,8 +8,9 @@ frozen bf16 base), FSDP-style sharding over N GPUs of one node, synthetic packed
 Prints ONE JSON line (rank 0). ``value`` is the device-timed aggregate over all GPUs with the
 step's inputs already resident on the device; ``e2e`` repeats the measurement through the public
 ``Trainer.training_step`` API with a host->device copy of every step's pinned inputs and a
-device->host read of every step's loss. ``--impl reference`` would run the unmodified reference
-package from ``baseline/_ref``; it reports ``unavailable`` when that package cannot be imported.
+device->host read of every step's loss. ``--impl reference`` runs the unmodified reference package
+from ``baseline/_ref`` on the same config through its own CLI entry (baseline/ref_harness.py); it
+reports ``unavailable`` with the reason when that package or its dependencies cannot be imported.
 """
 from __future__ import annotations
 
@@ -85,31 +86,18 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """Runs the unmodified reference from baseline/_ref, or explains why it cannot run here."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    reason = None
-    if not os.path.isdir(os.path.join(ref, "axolotl")):
-        reason = "baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref <reference checkout>)"
+    """Runs the unmodified reference from baseline/_ref through its own ``axolotl.cli.train`` entry
+    (see baseline/ref_harness.py), or explains in one line why it cannot run here. Nothing of
+    axolotl_b200 is imported on this path."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import ref_harness
+
+    if args.config != "lora8b":
+        res = {"impl": "reference", "unavailable": "the reference arm is wired for the headline config only"}
     else:
-        sys.path.insert(0, ref)
-        missing = []
-        for mod in ("peft", "accelerate", "trl", "colorama"):
-            try:
-                __import__(mod)
-            except Exception:
-                missing.append(mod)
-        if missing:
-            reason = ("reference installed with --no-deps but its runtime dependencies are not in the image or the "
-                      f"offline wheelhouse: {', '.join(missing)} (axolotl.train imports them at module load)")
-        else:
-            try:
-                from axolotl.train import train  # noqa: F401
-            except Exception as exc:
-                reason = f"reference import failed: {type(exc).__name__}: {exc}"
-    if reason is None:
-        reason = "reference imports, but no runnable harness is wired for it in this build"
-    if _env_int("RANK", 0) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        res = ref_harness.run_reference(args.gpus, args.steps, max(args.warmup, 3))
+    if _env_int("RANK", 0) == 0 and res is not None:
+        print(json.dumps(res))
     return 0
 
 

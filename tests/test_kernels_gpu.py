@@ -48,6 +48,33 @@ def test_gemm_transposed_operands(ta, tb, M, N, K):
         assert _rel_err(c, ref) < 5e-3, (ta, tb, bn)
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 5000, 512), (2304, 8192 + 24, 256), (5000, 4096, 192)])
+def test_pair_gemm_tma_store_epilogue_matches_row_stores(M, N, K):
+    """Large bf16 GEMMs leave the CTA-pair kernel through staged TMA tile stores; ragged M / N edges are
+    clipped by the tensor map. Same result as the per-thread row stores, bit for bit."""
+    from axolotl_b200.ops import _lib
+    from axolotl_b200.ops.gemm import _use_pair, gemm
+    torch.manual_seed(21)
+    lib = _lib.cuda_lib()
+    assert _use_pair(M, N, 256)
+    a = torch.randn(M, K, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=_dev(), dtype=torch.bfloat16)
+    guard = torch.full((M + 8, N + 8), 7.0, device=_dev(), dtype=torch.bfloat16)
+    out = guard[:M, :N]                       # a view with ld = N + 8: rows stay 16-byte aligned
+    try:
+        lib.axb_gemm_set_pair_tuning(4, 1)
+        gemm(a, b, out=out, bn=256)
+        _check_status()
+        lib.axb_gemm_set_pair_tuning(4, 0)
+        ref_rows = gemm(a, b, bn=256)
+        _check_status()
+    finally:
+        lib.axb_gemm_set_pair_tuning(4, 1)
+    assert torch.equal(out, ref_rows)
+    assert _rel_err(out, a.float() @ b.float().t()) < 5e-3
+    assert bool((guard[M:, :] == 7.0).all()) and bool((guard[:, N:] == 7.0).all())   # nothing beyond the edges
+
+
 def test_gemm_k_extension_and_epilogue():
     from axolotl_b200.ops.gemm import gemm
     torch.manual_seed(2)
@@ -717,11 +744,13 @@ def test_selective_nvfp4_dequant_skips_idle_experts_and_moe_output_is_unchanged(
 
 
 @pytest.mark.parametrize("kind,limit", [(0, 0.0), (1, 0.0), (0, 1.5)])
-@pytest.mark.parametrize("M,I,K,R", [(5120, 1024, 512, 32), (4608, 1160, 320, 0)])
-def test_gemm_glu_epilogues(kind, limit, M, I, K, R):
+@pytest.mark.parametrize("M,I,K,R", [(5120, 1024, 512, 32), (4700, 1184, 320, 0)])
+def test_gemm_glu_epilogues(kind, limit, M, I, K, R, monkeypatch):
     """GLU folded into the CTA-pair GEMM: forward (gate|up tile halves) and backward (dh -> d_gate|d_up)."""
     import torch.nn.functional as F
+    from axolotl_b200.ops import gemm as gemm_mod
     from axolotl_b200.ops.gemm import gemm, glu_fusable
+    monkeypatch.setattr(gemm_mod, "USE_GLU_EPILOGUE", True)
     torch.manual_seed(11)
     dev = _dev()
     assert glu_fusable(M, I, dev)
@@ -788,13 +817,15 @@ def test_fused_glu_mlp_matches_unfused(lora):
         grads = torch.autograd.grad(y, [x] + params, dy)
         return y, grads
 
-    assert gemm_mod.glu_fusable(T, I, dev)
-    y1, g1 = run()
-    gemm_mod.USE_GLU_EPILOGUE = False
+    prev = gemm_mod.USE_GLU_EPILOGUE
     try:
+        gemm_mod.USE_GLU_EPILOGUE = True
+        assert gemm_mod.glu_fusable(T, I, dev)
+        y1, g1 = run()
+        gemm_mod.USE_GLU_EPILOGUE = False
         y0, g0 = run()
     finally:
-        gemm_mod.USE_GLU_EPILOGUE = True
+        gemm_mod.USE_GLU_EPILOGUE = prev
     _check_status()
     assert _rel_err(y1, y0) < 1e-2
     for a, b in zip(g1, g0):

@@ -90,3 +90,18 @@ def test_noalloc_rejects_oversized_problem():
             dqkv.stride(0), 0.1, None, None, err, 512)
     assert rc == -20
     assert "exceeds the built-in scratch" in err.value.decode()
+
+
+def test_noalloc_empty_and_negative_sizes():
+    """An empty batch is a clean no-op (nothing launched, rc 0); a negative size is refused with its own code."""
+    L, lib, fn = _lib()
+    Hq, Hk, D = 4, 2, 128
+    T, meta, qkv, out, dout, lse2, ref = _problem([128], Hq, Hk, D, 3)
+    dqkv = torch.empty_like(qkv)
+    err = C.create_string_buffer(512)
+    args = lambda t: (qkv.data_ptr(), qkv.stride(0), dout.data_ptr(), out.data_ptr(), out.stride(0), lse2.data_ptr(), t,
+                      Hq, Hk, D, 0, Hq * D, (Hq + Hk) * D, meta.tiles_bwd.data_ptr(), meta.n_tiles, dqkv.data_ptr(),
+                      dqkv.stride(0), 0.1, None, None, err, 512)
+    assert fn(*args(0)) == 0
+    assert fn(*args(-5)) == -22 and "must be >= 0" in err.value.decode()
+    torch.cuda.synchronize()

@@ -512,32 +512,36 @@ UNSUPPORTED_KEYS = {
 # Reference keys that are accepted and carried through without effect on this framework (their
 # purpose is served natively or is irrelevant here).
 INERT_KEYS = {
-    "accelerator_config", "activation_checkpointing", "activation_dtype", "async_prefetch", "auto_find_batch_size",
-    "batch_flattening", "bnb_config_kwargs", "cls_model_config", "comet_api_key", "comet_experiment_config",
+    "accelerator_config", "activation_checkpointing", "async_prefetch", "auto_find_batch_size",
+    "bnb_config_kwargs", "cls_model_config", "comet_api_key", "comet_experiment_config",
     "comet_experiment_key", "comet_mode", "comet_online", "comet_workspace", "dion_lr", "dion_momentum",
-    "dion_rank_fraction", "dion_rank_multiple_of", "dpo_generate_during_eval", "dpo_norm_loss", "dpo_padding_free",
+    "dion_rank_fraction", "dion_rank_multiple_of", "dpo_generate_during_eval", "dpo_padding_free",
     "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "embeddings_skip_upcast",
-    "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_fuse_mlp",
-    "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp32_norm_classes", "fp32_norms",
-    "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",
-    "gemma4_hybrid_attn_impl", "gpu_memory_limit", "gradio_max_new_tokens", "gradio_server_name",
+    "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",
+    "gemma4_hybrid_attn_impl", "gradio_max_new_tokens", "gradio_server_name",
     "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
     "image_size", "is_falcon_derived_model",
-    "lisa_layers_attribute", "loftq_config", "lora_on_cpu", "low_cpu_mem_usage",
-    "max_memory", "max_packed_sequence_len", "model_quantization_config",
-    "model_quantization_config_kwargs", "noisy_embedding_alpha", "num_dataset_shards_to_save",
-    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "peft_layer_replication",
-    "preprocess_iterable", "processor_kwargs", "processor_type", "qgalore_cos_threshold", "qgalore_gamma_proj",
+    "lisa_layers_attribute", "lora_on_cpu", "low_cpu_mem_usage",
+    "model_quantization_config_kwargs", "num_dataset_shards_to_save",
+    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "preprocess_iterable", "processor_kwargs", "processor_type", "qgalore_cos_threshold", "qgalore_gamma_proj",
     "qgalore_proj_bits", "qgalore_proj_group_size", "qgalore_proj_quant", "qgalore_proj_type", "qgalore_queue_size",
     "qgalore_rank", "qgalore_scale", "qgalore_update_proj_gap", "qlora_sharded_model_loading", "quantize_embedding",
     "ray_num_workers", "ray_run_name", "recompute_layer_types", "relora_prune_method", "resources_per_worker",
-    "save_sliding_window", "scaling_softmax", "scaling_softmax_bias", "scaling_softmax_factor", "streaming_min_groups",
-    "streaming_partial_batch", "tokenizer_save_jinja_files", "tokenizer_use_mistral_common", "torch_compile_backend",
+    "save_sliding_window", "scaling_softmax_bias", "scaling_softmax_factor", "streaming_min_groups",
+    "tokenizer_save_jinja_files", "tokenizer_use_mistral_common", "torch_compile_backend",
     "torch_compile_mode", "torch_compile_options", "torchdistx_path", "trackio_project_name", "trackio_run_name",
     "trackio_space_id", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss",
-    "liger_rope", "liger_rms_norm", "liger_glu_activation", "liger_layer_norm", "liger_fused_linear_cross_entropy",
-    "liger_cross_entropy", "cut_cross_entropy", "kd_online_server_base_url", "evaluation_strategy",
-    "tiled_mlp_use_original_mlp", "min_num_params",
+    "liger_rope", "liger_rms_norm", "liger_glu_activation", "liger_layer_norm", "kd_online_server_base_url", "tiled_mlp_use_original_mlp", "min_num_params",
+}
+
+
+# Reference keys without a schema field whose effect is decided by a validation rule (config/rules.py):
+# rewritten to their current spelling, honoured, or refused with a message.
+RULED_KEYS = {
+    "activation_dtype", "dpo_norm_loss", "fp32_norm_classes", "fp32_norms", "loftq_config",
+    "peft_layer_replication", "streaming_partial_batch", "max_packed_sequence_len", "noisy_embedding_alpha", "evaluation_strategy",
+    "batch_flattening", "cut_cross_entropy", "liger_cross_entropy", "liger_fused_linear_cross_entropy", "flash_attn_fuse_mlp",
+    "max_memory", "gpu_memory_limit", "model_quantization_config", "scaling_softmax",
 }
 
 
@@ -549,11 +553,11 @@ def check_keys(raw: dict) -> list[str]:
             if v:
                 raise ValueError(f"config key '{k}' is unsupported on axolotl_b200: {UNSUPPORTED_KEYS[k]}")
             continue
-        if k in KNOWN_KEYS:
+        if k in KNOWN_KEYS or k in RULED_KEYS:
             continue
         if k in INERT_KEYS:
             inert.append(k)
             continue
-        hint = difflib.get_close_matches(k, sorted(KNOWN_KEYS | INERT_KEYS), n=1)
+        hint = difflib.get_close_matches(k, sorted(KNOWN_KEYS | INERT_KEYS | RULED_KEYS), n=1)
         raise ValueError(f"unknown config key '{k}'" + (f" (did you mean '{hint[0]}'?)" if hint else ""))
     return inert

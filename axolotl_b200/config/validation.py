@@ -8,7 +8,9 @@ import os
 
 
 def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
-    w: list[str] = []
+    from .rules import run_rules
+
+    w: list[str] = run_rules(cfg)
     cap = capabilities or {}
     g = cfg.get
 
@@ -189,9 +191,6 @@ def validate(cfg: dict, capabilities: dict | None = None) -> list[str]:
         raise ValueError("sample packing is not supported for preference training")
 
     # ---- memory features
-    if g("gradient_checkpointing") in ("offload", "offload_disk", "unsloth"):
-        w.append("offloaded checkpointing is mapped to plain activation checkpointing (HBM is large enough)")
-        cfg["gradient_checkpointing"] = True
     if g("tiled_mlp"):
         w.append("tiled_mlp is implemented as sequence-chunked MLP evaluation inside each layer")
     return w

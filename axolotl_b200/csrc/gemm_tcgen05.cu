@@ -89,9 +89,11 @@ struct GemmParams {
   // lines, no per-thread row stores); 0 = every thread stores its own row (fp32 output, beta != 0,
   // unaligned C)
   int tma_store;
+  int dbg;
 };
 
-int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0, g_pair_group_m = 4, g_pair_tma_store = 1;
+int g_dbg = 0;
+int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0, g_pair_group_m = 0, g_pair_tma_store = 1, g_pair_band_mb = 32;
 
 // Row `lane` of a 32-row staging tile with 128-byte rows (64 bf16) and the 128-byte swizzle the
 // tensor map expects: 16-byte chunk j of row r sits at chunk position j ^ (r & 7). The tile base is
@@ -926,7 +928,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                           const __grid_constant__ CUtensorMap tmE0, const __grid_constant__ CUtensorMap tmE1,
-                          const __grid_constant__ CUtensorMap tmE2, const GemmParams p) {
+                          const __grid_constant__ CUtensorMap tmE2, const __grid_constant__ CUtensorMap tmE3,
+                          const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -939,6 +942,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* tfull_bar = bars + 2 * P_STAGES;       // one per CTA
   uint64_t* tempty_bar = bars + 2 * P_STAGES + 2;  // used in rank 0 only (8 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * P_STAGES + 4);
+  uint64_t* epi_bar = bars + 24;                   // [epilogue warp][slot]: "gate|up chunk landed" (GLU backward)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -967,6 +971,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&tfull_bar[s], 1);
       mbar_init(&tempty_bar[s], 8);
     }
+    for (int s = 0; s < 8; ++s) mbar_init(&epi_bar[s], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -1072,6 +1077,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int lane_group = warp & 3;
     uint8_t* my_epi = sEpi + lane_group * 8192;   // this warp's two staging slots
     int slot = 0;
+    int q = 0;                                    // GLU backward: running chunk counter (slot and barrier phase)
     int it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
@@ -1079,6 +1085,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      if (p.epi == 2 && lane == 0 && !(p.dbg & 8)) {
+        // first gate|up chunk of this tile: requested now, it lands while the MMAs of the tile still run
+        bulk_wait_group_read<0>();
+        uint8_t* dst = my_epi + (q & 1) * 4096;
+        uint64_t* eb = &epi_bar[lane_group * 2 + (q & 1)];
+        const int r0 = m_blk * 256 + (int)rank * 128 + lane_group * 32;
+        mbar_expect_tx(eb, 4096);
+        tma_load_2d(dst, &tmE2, eb, n_blk * 256, r0);
+        tma_load_2d(dst + 2048, &tmE3, eb, n_blk * 256, r0);
+      }
       if (!mbar_wait_backoff(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL, p.epi_sleep_ns)) {
         ok = false;
         break;
@@ -1153,85 +1169,81 @@ __global__ void __launch_bounds__(kThreads, 1)
           put128(&tmE2, hw, col0);
         }
       } else if (p.epi == 2) {
-        // GLU backward: the accumulator is dh; gate | up are read straight from Cin (row per thread,
-        // the next chunk's 2 x 64 bytes are requested before this chunk is computed), d_gate | d_up
-        // leave through 32 x 32 staging tiles (64-byte rows) and TMA stores.
+        // GLU backward: the accumulator is dh. gate | up chunks (32 rows x 32 columns each) arrive by
+        // TMA in one of two staging slots, one chunk ahead of the arithmetic; d_gate | d_up overwrite
+        // them in place and leave by TMA stores.
         const int I = p.N;
         const bool lim = p.glu_limit > 0.f;
         const float L = p.glu_limit;
-        const long long my_row = (long long)warp_row0 + lane;
-        const bool row_in = my_row < p.M;
-        const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + my_row * p.ldcin;
-        auto fetch = [&](int col0, uint4 (&g)[4], uint4 (&u)[4]) {
-          if (row_in && col0 + 32 <= I) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              g[j] = *reinterpret_cast<const uint4*>(grow + col0 + 8 * j);
-              u[j] = *reinterpret_cast<const uint4*>(grow + I + col0 + 8 * j);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) g[j] = u[j] = make_uint4(0u, 0u, 0u, 0u);
-          }
-        };
-        uint4 gq[4], uq[4];
-        fetch(n_blk * 256, gq, uq);
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 8; ++c, ++q) {
           const int col0 = n_blk * 256 + c * 32;
-          uint4 gn[4], un[4];
-          if (c < 7) fetch(col0 + 32, gn, un);
+          const int s_cur = q & 1;
+          uint8_t* tile = my_epi + s_cur * 4096;
+          if (c < 7 && lane == 0 && !(p.dbg & 8)) {
+            // the other slot was last read by the stores of chunk q-1
+            bulk_wait_group_read<0>();
+            uint8_t* nxt = my_epi + (s_cur ^ 1) * 4096;
+            uint64_t* nb = &epi_bar[lane_group * 2 + (s_cur ^ 1)];
+            mbar_expect_tx(nb, 4096);
+            tma_load_2d(nxt, &tmE2, nb, col0 + 32, warp_row0);
+            tma_load_2d(nxt + 2048, &tmE3, nb, col0 + 32, warp_row0);
+          }
           uint32_t r[32];
           tmem_ld_32x32(t_addr + c * 32, r);
           tmem_ld_wait();
-          if (warp_rows && col0 < I) {
-            uint4 dg[4], du[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t g4[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w};
-              const uint32_t u4[4] = {uq[j].x, uq[j].y, uq[j].z, uq[j].w};
-              uint32_t og[4], ou[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 g = unpack_bf16x2(g4[e]), u = unpack_bf16x2(u4[e]);
-                const float gv[2] = {g.x, g.y}, uv[2] = {u.x, u.y};
-                float a[2], b[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  const float d = __uint_as_float(r[8 * j + 2 * e + h]) * p.alpha;
-                  const bool g_in = !lim || gv[h] <= L;
-                  const bool u_in = !lim || (uv[h] >= -L && uv[h] <= L);
-                  const float gc = g_in ? gv[h] : L;
-                  const float uc = u_in ? uv[h] : (uv[h] > 0.f ? L : -L);
-                  a[h] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
-                  b[h] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
-                }
-                og[e] = pack_bf16x2(a[0], a[1]);
-                ou[e] = pack_bf16x2(b[0], b[1]);
-              }
-              dg[j] = make_uint4(og[0], og[1], og[2], og[3]);
-              du[j] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          if (!(p.dbg & 8)) {
+            const bool got = (p.dbg & 1) ? mbar_wait_spin(&epi_bar[lane_group * 2 + s_cur], (uint32_t)((q >> 1) & 1), p.status, AXB_TIMEOUT_FULL)
+                                         : mbar_wait(&epi_bar[lane_group * 2 + s_cur], (uint32_t)((q >> 1) & 1), p.status, AXB_TIMEOUT_FULL);
+            if (!got) {
+              ok = false;
+              break;
             }
-            uint8_t* tile = my_epi + slot * 4096;
-            if (lane == 0) bulk_wait_group_read<1>();
-            __syncwarp();
-            stage_row64(tile, lane, dg);
-            stage_row64(tile + 2048, lane, du);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmE0, tile, col0, warp_row0);
-              tma_store_2d(&tmE1, tile + 2048, col0, warp_row0);
-              bulk_commit_group();
-            }
-            slot ^= 1;
           }
+          const int sw = (lane >> 1) & 3;
+          uint8_t* grow = tile + lane * 64;
+          uint8_t* urow = tile + 2048 + lane * 64;
+          if (!(p.dbg & 2))
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            gq[j] = gn[j];
-            uq[j] = un[j];
+            uint4* gp = reinterpret_cast<uint4*>(grow + ((j ^ sw) << 4));
+            uint4* up = reinterpret_cast<uint4*>(urow + ((j ^ sw) << 4));
+            const uint4 gq = *gp, uq = *up;
+            const uint32_t g4[4] = {gq.x, gq.y, gq.z, gq.w};
+            const uint32_t u4[4] = {uq.x, uq.y, uq.z, uq.w};
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 g = unpack_bf16x2(g4[e]), u = unpack_bf16x2(u4[e]);
+              const float gv[2] = {g.x, g.y}, uv[2] = {u.x, u.y};
+              float a[2], b[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float d = __uint_as_float(r[8 * j + 2 * e + h]) * p.alpha;
+                const bool g_in = !lim || gv[h] <= L;
+                const bool u_in = !lim || (uv[h] >= -L && uv[h] <= L);
+                const float gc = g_in ? gv[h] : L;
+                const float uc = u_in ? uv[h] : (uv[h] > 0.f ? L : -L);
+                a[h] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
+                b[h] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
+              }
+              og[e] = pack_bf16x2(a[0], a[1]);
+              ou[e] = pack_bf16x2(b[0], b[1]);
+            }
+            *gp = make_uint4(og[0], og[1], og[2], og[3]);
+            *up = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (warp_rows && col0 < I && !(p.dbg & 4)) {
+              tma_store_2d(&tmE0, tile, col0, warp_row0);
+              tma_store_2d(&tmE1, tile + 2048, col0, warp_row0);
+            }
+            bulk_commit_group();
           }
         }
+        if (!ok) break;
       } else if (p.tma_store) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -1331,8 +1343,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <bool A_MN, bool B_MN>
 int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2, const CUtensorMap& tB2,
-                const CUtensorMap& tE0, const CUtensorMap& tE1, const CUtensorMap& tE2, GemmParams p, int sms,
-                cudaStream_t stream) {
+                const CUtensorMap& tE0, const CUtensorMap& tE1, const CUtensorMap& tE2, const CUtensorMap& tE3,
+                GemmParams p, int sms, cudaStream_t stream) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -1356,7 +1368,7 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, tE0, tE1, tE2, p);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, tE0, tE1, tE2, tE3, p);
 }
 
 }  // namespace
@@ -1400,7 +1412,7 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
   }
   // epilogue maps: staging tiles of 32 rows x 64 columns (128-byte swizzle), or 32 x 32 (64-byte swizzle)
   // for the GLU backward pass
-  CUtensorMap tE0 = tA, tE1 = tA, tE2 = tA;
+  CUtensorMap tE0 = tA, tE1 = tA, tE2 = tA, tE3 = tA;
   int tma_store = 0;
   const __nv_bfloat16* Cb = reinterpret_cast<const __nv_bfloat16*>(C);
   if (epi == 0) {
@@ -1415,8 +1427,11 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
     }
     rc |= axb_make_tmap_2d(&tE2, H, M, N, ldh, 32, 64);
   } else {
+    const __nv_bfloat16* Gb = reinterpret_cast<const __nv_bfloat16*>(Cin);
     rc |= axb_make_tmap_2d(&tE0, Cb, M, N, ldc, 32, 32, 2, false, true);
     rc |= axb_make_tmap_2d(&tE1, Cb + N, M, N, ldc, 32, 32, 2, false, true);
+    rc |= axb_make_tmap_2d(&tE2, Gb, M, N, ldcin, 32, 32, 2, false, true);
+    rc |= axb_make_tmap_2d(&tE3, Gb + N, M, N, ldcin, 32, 32, 2, false, true);
   }
   if (rc) return -4;
   GemmParams p = {};
@@ -1426,16 +1441,26 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
   p.epi = epi; p.glu_kind = glu_kind; p.glu_limit = glu_limit; p.H = H; p.ldh = ldh;
   p.epi_sleep_ns = g_epi_sleep_ns; p.prod_sleep_ns = g_prod_sleep_ns;
   p.tma_store = tma_store;
-  p.group_m = g_pair_group_m;  // rows of 256-row tiles per rasterisation band
+  p.dbg = g_dbg;
+  // Rasterisation band: `group_m` rows of 256-row tiles sweep over N together, so their A rows are read
+  // from DRAM once (they stay in L2) while B is streamed once per band. Taller bands mean fewer passes
+  // over B; the band's A rows (group_m x 256 x K bf16) have to fit the L2 share given to them.
+  if (g_pair_group_m > 0) {
+    p.group_m = g_pair_group_m;
+  } else {
+    const long long per_tile_row = 256LL * (K + (K2 > 0 ? K2 : 0)) * 2;
+    long long g = ((long long)g_pair_band_mb << 20) / per_tile_row;
+    p.group_m = (int)(g < 2 ? 2 : (g > 16 ? 16 : g));
+  }
   PrefetchArgs pf;
   pf.peer_bases = pf_peer_bases; pf.shard_offset = pf_shard_offset; pf.shard_bytes = pf_shard_bytes;
   pf.world = pf_world; pf.dst = pf_dst; pf.ctas = pf_ctas;
   if ((rc = fill_prefetch(p, &pf)) != 0) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return launch_pair<false, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
-  if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
-  if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
-  return launch_pair<true, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, p, sm_count(), st);
+  if (!a_mn && !b_mn) return launch_pair<false, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, tE3, p, sm_count(), st);
+  if (!a_mn && b_mn) return launch_pair<false, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, tE3, p, sm_count(), st);
+  if (a_mn && !b_mn) return launch_pair<true, false>(tA, tB, tA2, tB2, tE0, tE1, tE2, tE3, p, sm_count(), st);
+  return launch_pair<true, true>(tA, tB, tA2, tB2, tE0, tE1, tE2, tE3, p, sm_count(), st);
 }
 
 extern "C" int axb_gemm_bf16_pair(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
@@ -1469,15 +1494,17 @@ extern "C" int axb_gemm_bf16_pair_glu(const void* A, long long lda, int a_mn, co
 
 // Wait back-off of the CTA-pair kernel in nanoseconds (0 = busy spin): epilogue warps waiting for an
 // accumulator, TMA producer waiting for a free stage.
+extern "C" void axb_gemm_set_debug(int d) { g_dbg = d; }
 extern "C" void axb_gemm_set_backoff(int epi_sleep_ns, int prod_sleep_ns) {
   g_epi_sleep_ns = epi_sleep_ns;
   g_prod_sleep_ns = prod_sleep_ns;
 }
 
-// Tuning of the CTA-pair kernel: 256-row tile rows per rasterisation band (the A rows of a band stay
-// in L2 while the band sweeps over N) and whether bf16 results leave through TMA tile stores (1) or
+// Tuning of the CTA-pair kernel: 256-row tile rows per rasterisation band (0 = as many as fit band_mb
+// MiB of A rows, between 2 and 16) and whether bf16 results leave through TMA tile stores (1) or
 // per-thread row stores (0).
-extern "C" void axb_gemm_set_pair_tuning(int group_m, int tma_store) {
-  if (group_m > 0) g_pair_group_m = group_m;
+extern "C" void axb_gemm_set_pair_tuning(int group_m, int tma_store, int band_mb) {
+  g_pair_group_m = group_m;          // 0: derive the band height from band_mb (MiB of A rows per band)
   g_pair_tma_store = tma_store;
+  if (band_mb > 0) g_pair_band_mb = band_mb;
 }

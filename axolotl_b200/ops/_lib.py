@@ -29,7 +29,8 @@ _CUDA_SIGS = {
                                i32, f32, i32, i32, f32, vp, i64, vp, C.c_ulonglong, C.c_ulonglong, i32, vp, i32,
                                vp, vp],
     "axb_gemm_set_backoff": [i32, i32],
-    "axb_gemm_set_pair_tuning": [i32, i32],
+    "axb_gemm_set_debug": [i32],
+    "axb_gemm_set_pair_tuning": [i32, i32, i32],
     "axb_nvfp4_dequant": [vp, vp, vp, vp, i64, i64, vp],
     "axb_moe_dispatch_rows": [vp, vp, vp, vp, i64, i32, vp],
     "axb_moe_combine_rows": [vp, vp, vp, vp, i64, i32, i32, vp],

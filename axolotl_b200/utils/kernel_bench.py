@@ -70,10 +70,11 @@ def bench_gemm(rows):
                     f"{fl / lib:.0f} TFLOP/s | ratio {lib / ours:.2f}")
 
 
-def bench_gemm_sustained(rows, seconds=3.0):
-    """Back-to-back GEMMs of one MLP (gate|up and down shapes) for a few seconds: the rate under the
-    board power limit, which is what a training step sees, next to cuBLAS driven the same way, for
-    several wait back-off settings of the CTA-pair kernel. SM clock and power are sampled meanwhile."""
+def bench_gemm_sustained(rows, seconds=2.0):
+    """Every large GEMM shape of a Llama-3-8B LoRA step run back to back for a couple of seconds: the
+    rate under the board power limit, which is what a training step sees, next to cuBLAS driven the
+    same way, for several rasterisation band heights of the CTA-pair kernel. SM clock and power are
+    sampled meanwhile."""
     import subprocess
     import threading
     import time
@@ -82,22 +83,6 @@ def bench_gemm_sustained(rows, seconds=3.0):
     from axolotl_b200.ops.gemm import gemm
 
     lib = _lib.cuda_lib()
-    M, H, I = 8192, 4096, 14336
-    x = torch.randn(M, H, device="cuda", dtype=torch.bfloat16)
-    Wgu = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02
-    Wd = torch.randn(H, I, device="cuda", dtype=torch.bfloat16) * 0.02
-    gu = torch.empty(M, 2 * I, device="cuda", dtype=torch.bfloat16)
-    h = torch.randn(M, I, device="cuda", dtype=torch.bfloat16)
-    y = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
-    fl = 2.0 * M * (2 * I) * H + 2.0 * M * H * I
-
-    def ours():
-        gemm(x, Wgu, out=gu)
-        gemm(h, Wd, out=y)
-
-    def cublas():
-        torch.matmul(x, Wgu.t(), out=gu)
-        torch.matmul(h, Wd.t(), out=y)
 
     def sample(stop, out):
         while not stop.is_set():
@@ -110,7 +95,7 @@ def bench_gemm_sustained(rows, seconds=3.0):
                 pass
             time.sleep(0.2)
 
-    def run(fn, label):
+    def run(fn, fl):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
@@ -132,14 +117,28 @@ def bench_gemm_sustained(rows, seconds=3.0):
         ms = s.elapsed_time(e) / n
         samples = samples[len(samples) // 3:] or [(0.0, 0.0)]
         clk = sorted(c for c, _ in samples)[len(samples) // 2]
-        pw = sorted(p for _, p in samples)[len(samples) // 2]
-        rows.append(f"sustained {label}: {ms:.3f} ms per MLP pair, {fl / ms / 1e9:.0f} TFLOP/s, median SM {clk:.0f} MHz, {pw:.0f} W")
+        return fl / ms / 1e9, clk
 
-    run(cublas, "cuBLAS")
-    for group_m, tma in ((4, 0), (4, 1), (8, 1), (16, 1), (2, 1), (32, 1)):
-        lib.axb_gemm_set_pair_tuning(group_m, tma)
-        run(ours, f"ours band of {group_m} tile rows, {'TMA tile stores' if tma else 'per-thread row stores'}")
-    lib.axb_gemm_set_pair_tuning(4, 1)
+    shapes = [("qkv", 8192, 6144, 4096, False), ("gate_up", 8192, 28672, 4096, False), ("down", 8192, 4096, 14336, False),
+              ("dX gate_up", 8192, 4096, 28672, True), ("dX down", 8192, 14336, 4096, True),
+              ("lm_head", 2048, 128256, 4096, False)]
+    bands = (2, 4, 8, 12, 16, 24)
+    for name, M, N, K, tb in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if tb else (N, K), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        ref, rclk = run(lambda: torch.matmul(a, b if tb else b.t(), out=out), fl)
+        cells = []
+        for g in bands:
+            lib.axb_gemm_set_pair_tuning(g, 1, 0)
+            t, clk = run(lambda: gemm(a, b, trans_b=tb, out=out), fl)
+            cells.append(f"{g}: {t:.0f} @{clk:.0f}")
+        lib.axb_gemm_set_pair_tuning(0, 1, 0)
+        t, clk = run(lambda: gemm(a, b, trans_b=tb, out=out), fl)
+        rows.append(f"sustained {name} M={M} N={N} K={K}: cuBLAS {ref:.0f} TFLOP/s @{rclk:.0f} MHz | ours by band height "
+                    f"[{' | '.join(cells)}] | default {t:.0f} @{clk:.0f} ({t / ref:.2f} of cuBLAS)")
+        del a, b, out
 
 
 def bench_glu_mlp(rows):

@@ -62,14 +62,14 @@ def test_pair_gemm_tma_store_epilogue_matches_row_stores(M, N, K):
     guard = torch.full((M + 8, N + 8), 7.0, device=_dev(), dtype=torch.bfloat16)
     out = guard[:M, :N]                       # a view with ld = N + 8: rows stay 16-byte aligned
     try:
-        lib.axb_gemm_set_pair_tuning(4, 1)
+        lib.axb_gemm_set_pair_tuning(0, 1, 0)
         gemm(a, b, out=out, bn=256)
         _check_status()
-        lib.axb_gemm_set_pair_tuning(4, 0)
+        lib.axb_gemm_set_pair_tuning(3, 0, 0)
         ref_rows = gemm(a, b, bn=256)
         _check_status()
     finally:
-        lib.axb_gemm_set_pair_tuning(4, 1)
+        lib.axb_gemm_set_pair_tuning(0, 1, 0)
     assert torch.equal(out, ref_rows)
     assert _rel_err(out, a.float() @ b.float().t()) < 5e-3
     assert bool((guard[M:, :] == 7.0).all()) and bool((guard[:, N:] == 7.0).all())   # nothing beyond the edges

@@ -136,20 +136,29 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity
   return true;
 }
 
-__device__ __forceinline__ float glu_act(float g, int kind) {
-  if (kind == 0) return g / (1.f + __expf(-g));
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float t = tanhf(k0 * (g + k1 * g * g * g));
-  return 0.5f * g * (1.f + t);
+// GLU activations on the special-function units (ex2 / rcp / tanh approximations: a couple of ulp,
+// far below the bf16 rounding of the results). glu_act_and_grad returns act(g) and writes act'(g).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
-__device__ __forceinline__ float glu_act_grad(float g, int kind) {
+__device__ __forceinline__ float glu_act(float g, int kind) {
+  if (kind == 0) return g * __fdividef(1.f, 1.f + __expf(-g));
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * g * (1.f + tanh_fast(k0 * (g + k1 * g * g * g)));
+}
+__device__ __forceinline__ float glu_act_and_grad(float g, int kind, float& grad) {
   if (kind == 0) {
-    const float s = 1.f / (1.f + __expf(-g));
-    return s * (1.f + g * (1.f - s));
+    const float s = __fdividef(1.f, 1.f + __expf(-g));
+    const float a = g * s;
+    grad = s + a * (1.f - s);
+    return a;
   }
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float t = tanhf(k0 * (g + k1 * g * g * g));
-  return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+  const float t = tanh_fast(k0 * (g + k1 * g * g * g));
+  grad = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+  return 0.5f * g * (1.f + t);
 }
 
 constexpr int GATHER_CHUNK = 8192;
@@ -1224,8 +1233,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const bool u_in = !lim || (uv[h] >= -L && uv[h] <= L);
                 const float gc = g_in ? gv[h] : L;
                 const float uc = u_in ? uv[h] : (uv[h] > 0.f ? L : -L);
-                a[h] = g_in ? d * uc * glu_act_grad(gc, p.glu_kind) : 0.f;
-                b[h] = u_in ? d * glu_act(gc, p.glu_kind) : 0.f;
+                float dact;
+                const float act = glu_act_and_grad(gc, p.glu_kind, dact);
+                a[h] = g_in ? d * uc * dact : 0.f;
+                b[h] = u_in ? d * act : 0.f;
               }
               og[e] = pack_bf16x2(a[0], a[1]);
               ou[e] = pack_bf16x2(b[0], b[1]);

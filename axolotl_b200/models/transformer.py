@@ -60,7 +60,8 @@ class Attention(nn.Module):
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
         self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
 
-    def forward(self, x, positions, inv_freq, attn_scale, meta):
+    def pre(self, x, positions, inv_freq, attn_scale):
+        """Projections, q/k norms and rotary embedding: everything before the attention kernel."""
         qkv = self.qkv_proj(x)
         per_head_norm = self.q_norm is not None and not self.full_qk_norm
         if self.full_qk_norm:
@@ -72,16 +73,20 @@ class Attention(nn.Module):
             qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
                               self.q_norm.weight if per_head_norm else None,
                               self.k_norm.weight if per_head_norm else None, self.eps)
+        return qkv
+
+    def core(self, qkv, meta):
         cache = getattr(meta, "kv_cache", None)
         if cache is not None:   # generation: keep the rotated k / v of every token
-            a = cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale, self.window)
-        else:
-            if self.window and getattr(meta, "causal", True):
-                if getattr(meta, "cp", False):
-                    raise NotImplementedError("sliding-window attention is not available with context parallelism")
-                meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
-            a = Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
-        return self.o_proj(a)
+            return cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale, self.window)
+        if self.window and getattr(meta, "causal", True):
+            if getattr(meta, "cp", False):
+                raise NotImplementedError("sliding-window attention is not available with context parallelism")
+            meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
+        return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+
+    def forward(self, x, positions, inv_freq, attn_scale, meta):
+        return self.o_proj(self.core(self.pre(x, positions, inv_freq, attn_scale), meta))
 
 
 class MLP(nn.Module):
@@ -135,6 +140,30 @@ class DecoderLayer(nn.Module):
                            fused_names=cfg.model_type == "phi3")
         self.is_moe = cfg.is_moe_layer(idx)
 
+    def _before_attention(self, h, residual, positions, inv_freq, attn_scale):
+        x, residual = self.input_layernorm(h, residual)
+        return self.self_attn.pre(x, positions, inv_freq, attn_scale), residual
+
+    def _after_attention(self, a, residual):
+        a = self.self_attn.o_proj(a)
+        rm = self.residual_multiplier
+        if rm != 1.0:
+            a = a * rm
+        x, residual = self.post_attention_layernorm(a, residual)
+        y, aux = self.mlp(x) if self.is_moe else (self.mlp(x), None)
+        if rm != 1.0:
+            y = y * rm
+        return y, residual, aux
+
+    def forward_selective(self, h, residual, positions, inv_freq, attn_scale, meta):
+        """Selective activation checkpointing: the attention kernel's inputs and result stay saved (it is the
+        one part whose recomputation costs more than its activations), everything around it — norms,
+        projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
+        ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
+        qkv, residual = checkpoint(self._before_attention, h, residual, positions, inv_freq, attn_scale, use_reentrant=False)
+        a = self.self_attn.core(qkv, meta)
+        return checkpoint(self._after_attention, a, residual, use_reentrant=False)
+
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
         x, residual = self.input_layernorm(h, residual)
         a = self.self_attn(x, positions, inv_freq, attn_scale, meta)
@@ -171,6 +200,8 @@ class CausalLM(nn.Module):
         self.register_buffer("inv_freq_long", (long[0].to(device) if device is not None else long[0]) if long is not None
                              else None, persistent=False)
         self.gradient_checkpointing = False
+        self.ckpt_store = None        # activation_memory.HostStore / DiskStore: checkpointed layer inputs leave the device
+        self.ckpt_selective = False   # keep the attention result, recompute the rest of every layer
         self.ce_chunk_rows = 2048
         self.hooks = None  # parallelism runtime may install per-layer pre/post hooks
         self.nvtx = bool(os.environ.get("AXB_NVTX"))   # NVTX range per decoder layer for timeline tools
@@ -297,8 +328,18 @@ class CausalLM(nn.Module):
     def output_weight(self):
         return self.embed_tokens if self.lm_head is None else self.lm_head
 
-    def enable_gradient_checkpointing(self, flag=True):
+    def enable_gradient_checkpointing(self, flag=True, offload=None, selective=False, offload_dir=None):
+        """``offload``: None keeps checkpointed layer inputs on the device; True / "legacy" /
+        "hidden_states" park them in pinned host memory, "disk" in files under ``offload_dir``.
+        ``selective`` keeps the attention result and recomputes only the rest of each layer."""
         self.gradient_checkpointing = flag
+        self.ckpt_selective = bool(selective) and flag
+        if flag and offload:
+            from ..train.activation_memory import make_store
+
+            self.ckpt_store = make_store(offload, self.embed_tokens.device, offload_dir)
+        else:
+            self.ckpt_store = None
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids, position_ids=None, labels=None, attn_meta=None, num_items=None,
@@ -357,9 +398,17 @@ class CausalLM(nn.Module):
                 torch.cuda.nvtx.range_push(f"layer{i}")
             if hooks is not None:
                 hooks.pre_layer(i)
-            if self.gradient_checkpointing and self.training:
-                h, residual, aux = checkpoint(layer, h, residual, pos, inv_freq, self.attn_scale,
-                                              attn_meta, use_reentrant=False)
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+                if self.ckpt_store is not None:
+                    from ..train.activation_memory import offloaded_checkpoint
+
+                    h, residual, aux = offloaded_checkpoint(layer, self.ckpt_store, (h, residual),
+                                                            (pos, inv_freq, self.attn_scale, attn_meta))
+                elif self.ckpt_selective and hasattr(layer, "forward_selective"):
+                    h, residual, aux = layer.forward_selective(h, residual, pos, inv_freq, self.attn_scale, attn_meta)
+                else:
+                    h, residual, aux = checkpoint(layer, h, residual, pos, inv_freq, self.attn_scale,
+                                                  attn_meta, use_reentrant=False)
             else:
                 h, residual, aux = layer(h, residual, pos, inv_freq, self.attn_scale, attn_meta)
             if aux is not None:

@@ -406,7 +406,19 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     spec = setup_adapter(cfg, model)
     pm.call("post_model_load", cfg, model)
     if cfg.get("gradient_checkpointing") or (cfg.get("fsdp_config") or {}).get("activation_checkpointing"):
-        model.enable_gradient_checkpointing(True)
+        ao = cfg.get("activation_offloading") or None
+        model.enable_gradient_checkpointing(True, offload=ao, selective=bool(cfg.get("selective_checkpointing")),
+                                            offload_dir=os.path.join(cfg["output_dir"], "activation_offload") if ao == "disk" else None)
+        if ao in (True, "legacy", "disk"):
+            model.offload_saved_store = model.ckpt_store   # also park what autograd saves outside the layers
+        if ao:
+            LOG.info("activation offloading: checkpointed layer inputs go to %s", "disk" if ao == "disk" else "pinned host memory")
+    if cfg.get("layer_offloading"):
+        from .activation_memory import LayerOffloader
+
+        model.layer_offloader = LayerOffloader(model, device)
+        LOG.info("layer offloading: %.2f GiB of frozen layer weights kept in pinned host memory",
+                 sum(model.layer_offloader.bytes_per_layer) / 1024 ** 3)
 
     dp_size, dp_rank = 1, 0
     if parallel is not None:

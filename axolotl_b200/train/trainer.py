@@ -159,14 +159,15 @@ class Trainer:
             last = i == len(micro_batches) - 1
             if par is not None:
                 par.before_micro_batch(last)
-            if self.compute_loss is not None:
-                b["ga_steps"] = len(micro_batches)
-                loss = self.compute_loss(model, b, n_items)
-            else:
-                out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
-                            num_items=n_items, shift_labels=not b.get("labels_preshifted", False),
-                            aux_scale=1.0 / len(micro_batches))
-                loss = out.loss
+            with self._saved_tensor_scope():
+                if self.compute_loss is not None:
+                    b["ga_steps"] = len(micro_batches)
+                    loss = self.compute_loss(model, b, n_items)
+                else:
+                    out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
+                                num_items=n_items, shift_labels=not b.get("labels_preshifted", False),
+                                aux_scale=1.0 / len(micro_batches))
+                    loss = out.loss
             loss.backward()
             loss_total = loss.detach() if loss_total is None else loss_total + loss.detach()
             self.tokens["total"] += b["n_tokens"]
@@ -189,12 +190,26 @@ class Trainer:
         self._last_gnorm_sq = gnorm_sq
         return loss_total
 
+    def _saved_tensor_scope(self):
+        """``activation_offloading: true | legacy | disk``: large tensors that autograd saves outside the
+        checkpointed layers (embedding output, final norm, loss chunks) go to the same store as the layers'
+        inputs while the forward pass runs."""
+        store = getattr(self.model, "offload_saved_store", None)
+        if store is None:
+            import contextlib
+
+            return contextlib.nullcontext()
+        from .activation_memory import OffloadSavedTensors
+
+        return OffloadSavedTensors(store)
+
     # ------------------------------------------------------------------ loop
     def train(self):
         args = self.args
         if args.resume_from_checkpoint:
             self.load_checkpoint(args.resume_from_checkpoint)
-        if args.gradient_checkpointing and hasattr(self.model, "enable_gradient_checkpointing"):
+        if args.gradient_checkpointing and hasattr(self.model, "enable_gradient_checkpointing") \
+                and not getattr(self.model, "gradient_checkpointing", False):
             self.model.enable_gradient_checkpointing(True)
         self.model.train()
         for cb in self.callbacks:

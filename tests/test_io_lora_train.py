@@ -535,7 +535,7 @@ def test_sample_generation_callback_writes_rows(tmp_path):
                     "sequence_len": 128, "micro_batch_size": 2, "gradient_accumulation_steps": 1, "max_steps": 4,
                     "learning_rate": 1e-3, "optimizer": "adamw_torch", "output_dir": str(tmp_path / "g"), "device": "cpu",
                     "generate_samples": True, "num_generation_samples": 2, "generation_max_new_tokens": 5,
-                    "generation_do_sample": False, "save_steps": 2, "save_strategy": "no", "sample_packing": True,
+                    "generation_do_sample": False, "save_steps": 2, "save_strategy": "steps", "sample_packing": True,
                     "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 24, "min_length": 16,
                                   "max_length": 48, "max_input_id": 300}]})
     train(cfg)

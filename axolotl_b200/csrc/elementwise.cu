@@ -94,12 +94,16 @@ __global__ void __launch_bounds__(NORM_T)
       for (int j = 0; j < 8; ++j) f[j] += g[j];
     }
     if (res_out) {
-      // round the residual stream to bf16 first so forward and backward see the same h
-      store8(res_out + row * H + i, f);
-      float t[8];
-      load8(res_out + row * H + i, t);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = t[j];
+      // round the residual stream to bf16 first so forward and backward see the same h (in
+      // registers: a store followed by a load of the same address would wait for a trip to L2)
+      uint4 u;
+      u.x = pack_bf16x2(f[0], f[1]);
+      u.y = pack_bf16x2(f[2], f[3]);
+      u.z = pack_bf16x2(f[4], f[5]);
+      u.w = pack_bf16x2(f[6], f[7]);
+      *reinterpret_cast<uint4*>(res_out + row * H + i) = u;
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -330,19 +334,27 @@ __global__ void rope_qk_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
 }
 
 // ---------------------------------------------------------------------------------- GLU
+// Special-function-unit forms (ex2 / rcp / tanh approximations, a couple of ulp: far below the bf16
+// rounding of the results); an IEEE division per element would make these kernels instruction-bound.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_fast(float g) { return __fdividef(1.f, 1.f + __expf(-g)); }
 __device__ __forceinline__ float act_fwd(float g, int kind) {
-  if (kind == 0) return g / (1.f + __expf(-g));  // silu
+  if (kind == 0) return g * sigmoid_fast(g);  // silu
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;  // gelu tanh
-  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  const float t = tanh_fast(k0 * (g + k1 * g * g * g));
   return 0.5f * g * (1.f + t);
 }
 __device__ __forceinline__ float act_bwd(float g, int kind) {
   if (kind == 0) {
-    const float s = 1.f / (1.f + __expf(-g));
+    const float s = sigmoid_fast(g);
     return s * (1.f + g * (1.f - s));
   }
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  const float t = tanh_fast(k0 * (g + k1 * g * g * g));
   return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
 }
 // gu: [T, 2I] (gate | up);  h: [T, I] = act(gate) * up. With limit > 0 (clamped SwiGLU of the
@@ -522,7 +534,7 @@ __global__ void __launch_bounds__(NORM_T)
     load8(w + i, wv);
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      f[j] = f[j] * rstd * (wv[j] + w_offset) * (gv[j] / (1.f + __expf(-gv[j])));
+      f[j] = f[j] * rstd * (wv[j] + w_offset) * (gv[j] * sigmoid_fast(gv[j]));
     store8(y + row * H + i, f);
   }
 }
@@ -551,7 +563,7 @@ __global__ void __launch_bounds__(NORM_T)
       load8(g + row * H + i, gv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float s = gv[j] / (1.f + __expf(-gv[j]));
+        const float s = gv[j] * sigmoid_fast(gv[j]);
         dot += a[j] * s * (c[j] + w_offset) * b[j] * rstd;
       }
     }
@@ -565,7 +577,7 @@ __global__ void __launch_bounds__(NORM_T)
       load8(g + row * H + i, gv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float sg = 1.f / (1.f + __expf(-gv[j]));
+        const float sg = sigmoid_fast(gv[j]);
         const float s = gv[j] * sg;
         const float xhat = b[j] * rstd;
         const float wj = c[j] + w_offset;

@@ -152,97 +152,6 @@ class PretokenizedStrategy(Strategy):
         return _pack(ids, labels)
 
 
-class ChatTemplateStrategy(Strategy):
-    def __init__(self, tokenizer, cfg, ds_cfg=None):
-        super().__init__(tokenizer, cfg, ds_cfg)
-        d = self.ds_cfg
-        self.field_messages = d.get("field_messages") or "messages"
-        mp = d.get("message_property_mappings") or {}
-        self.f_role = mp.get("role") or d.get("message_field_role") or "role"
-        self.f_content = mp.get("content") or d.get("message_field_content") or "content"
-        self.f_training = d.get("message_field_training") or "training"
-        self.roles_to_train = d.get("roles_to_train") if d.get("roles_to_train") is not None else ["assistant"]
-        self.train_on_eos = d.get("train_on_eos") or "turn"
-        self.train_on_eot = d.get("train_on_eot") or self.train_on_eos
-        self.role_map = {"human": "user", "gpt": "assistant", "system": "system", "user": "user",
-                         "assistant": "assistant", "tool": "tool", "ipython": "ipython"}
-        for canon, names in (d.get("roles") or {}).items():
-            for n in names:
-                self.role_map[n] = canon
-        eot = cfg.get("eot_tokens") or []
-        self.eot_ids = {tokenizer.convert_tokens_to_ids(t) for t in eot}
-        if tokenizer.eos_token_id is not None:
-            self.eot_ids.add(tokenizer.eos_token_id)
-        self.drop_system = bool(d.get("drop_system_message"))
-
-    def _messages(self, row):
-        msgs = row.get(self.field_messages) or row.get("conversations") or []
-        out = []
-        for m in msgs:
-            role = m.get(self.f_role, m.get("from"))
-            content = m.get(self.f_content, m.get("value", ""))
-            role = self.role_map.get(role, role)
-            if role == "system" and self.drop_system:
-                continue
-            o = {"role": role, "content": content}
-            if self.f_training in m:
-                o["training"] = m[self.f_training]
-            out.append(o)
-        return out
-
-    def _render(self, msgs, add_generation_prompt=False, tools=None):
-        clean = [{"role": m["role"], "content": m["content"]} for m in msgs]
-        kw = dict(self.cfg.get("chat_template_kwargs") or {})
-        out = self.tok.apply_chat_template(clean, tokenize=True, add_generation_prompt=add_generation_prompt,
-                                           tools=tools, **kw)
-        if isinstance(out, dict):
-            out = out["input_ids"]
-        return list(out)
-
-    def tokenize(self, row):
-        msgs = self._messages(row)
-        if not msgs:
-            return None
-        tools = row.get(self.ds_cfg.get("field_tools") or "tools")
-        full = self._render(msgs, tools=tools)
-        labels = [IGNORE_INDEX] * len(full)
-        last_trainable = None
-        prev_len = 0
-        for i, m in enumerate(msgs):
-            upto = self._render(msgs[: i + 1], tools=tools)
-            # the rendered prefix must be a prefix of the full rendering; otherwise fall back to lengths
-            end = min(len(upto), len(full))
-            start = prev_len
-            if m["role"] == "assistant" and i > 0:
-                # skip the generation prompt (header tokens of the assistant turn)
-                gen = self._render(msgs[:i], add_generation_prompt=True, tools=tools)
-                if len(gen) <= end and gen == full[: len(gen)]:
-                    start = len(gen)
-            trainable = m.get("training")
-            if trainable is None:
-                trainable = self.train_on_inputs or (m["role"] in self.roles_to_train)
-            if trainable:
-                for j in range(start, end):
-                    labels[j] = full[j]
-                last_trainable = (start, end)
-                if self.train_on_eos == "none" or self.train_on_eot == "none":
-                    for j in range(start, end):
-                        if full[j] in self.eot_ids:
-                            labels[j] = IGNORE_INDEX
-            elif self.train_on_eos == "all" or self.train_on_eot == "all":
-                for j in range(start, end):
-                    if full[j] in self.eot_ids:
-                        labels[j] = full[j]
-            prev_len = end
-        if self.train_on_eos == "last" and last_trainable is not None:
-            s, e = last_trainable
-            for j in range(len(full)):
-                if full[j] in self.eot_ids and not (s <= j < e):
-                    labels[j] = IGNORE_INDEX if labels[j] != IGNORE_INDEX and j < s else labels[j]
-        full, labels = full[: self.seq_len], labels[: self.seq_len]
-        return _pack(full, labels)
-
-
 class StepwiseSupervisedStrategy(Strategy):
     """Process-reward data: prompt + completions[] + labels[]; the label of each step sits on the
     step separator token."""
@@ -270,12 +179,22 @@ class BradleyTerryStrategy(Strategy):
                 "input_ids_rejected": r, "attention_mask_rejected": [1] * len(r)}
 
 
+def _late_registry():
+    """Strategies that live in their own modules (they import this one)."""
+    from .chat_template import ChatTemplateStrategy, MessagesStrategy
+    from .strategies_extra import EXTRA
+
+    out = {"chat_template": ChatTemplateStrategy, "messages": MessagesStrategy, "messages.chat": MessagesStrategy,
+           "sharegpt": ChatTemplateStrategy}
+    out.update(EXTRA)
+    return out
+
+
 _REGISTRY = {
     "alpaca": AlpacaStrategy, "alpaca:chat": AlpacaChatStrategy, "alpaca_chat": AlpacaChatStrategy,
     "alpaca:instruct": AlpacaStrategy, "gpteacher": GPTeacherStrategy, "oasst": OpenAssistantStrategy,
     "jeopardy": JeopardyStrategy, "summarizetldr": SummarizeTLDRStrategy, "completion": CompletionStrategy,
-    "pretrain": PretrainStrategy, "input_output": InputOutputStrategy, "chat_template": ChatTemplateStrategy,
-    "messages": ChatTemplateStrategy, "sharegpt": ChatTemplateStrategy, "user_defined": UserDefinedStrategy,
+    "pretrain": PretrainStrategy, "input_output": InputOutputStrategy, "user_defined": UserDefinedStrategy,
     "stepwise_supervised": StepwiseSupervisedStrategy, "bradley_terry": BradleyTerryStrategy,
     "bradley_terry.chat_template": BradleyTerryStrategy, "pretokenized": PretokenizedStrategy,
 }
@@ -291,6 +210,9 @@ def load_strategy(type_, tokenizer, cfg, ds_cfg=None):
         return UserDefinedStrategy(tokenizer, cfg, ds_cfg)
     if type_ is None:
         return PretokenizedStrategy(tokenizer, cfg, ds_cfg)
+    if type_ not in _REGISTRY:
+        for k, v in _late_registry().items():
+            _REGISTRY.setdefault(k, v)
     if type_ in _REGISTRY:
         return _REGISTRY[type_](tokenizer, cfg, ds_cfg)
     if "." in type_:

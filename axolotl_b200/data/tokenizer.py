@@ -9,16 +9,39 @@ from ..utils.logging import get_logger
 
 LOG = get_logger(__name__)
 
-# a few common templates by name; anything else must come from the tokenizer or `chat_template_jinja`
-CHAT_TEMPLATES = {
-    "chatml": "{% for message in messages %}{{'<|im_start|>' + message['role'] + '\n' + message['content'] + '<|im_end|>' + '\n'}}{% endfor %}{% if add_generation_prompt %}{{ '<|im_start|>assistant\n' }}{% endif %}",
-    "llama3": "{{ bos_token }}{% for message in messages %}{{ '<|start_header_id|>' + message['role'] + '<|end_header_id|>\n\n' + message['content'] | trim + '<|eot_id|>' }}{% endfor %}{% if add_generation_prompt %}{{ '<|start_header_id|>assistant<|end_header_id|>\n\n' }}{% endif %}",
-    "alpaca": "{% for message in messages %}{% if message['role'] == 'system' %}{{ message['content'] + '\n\n' }}{% elif message['role'] == 'user' %}{{ '### Instruction:\n' + message['content'] + '\n\n' }}{% else %}{{ '### Response:\n' + message['content'] + eos_token + '\n\n' }}{% endif %}{% endfor %}{% if add_generation_prompt %}{{ '### Response:\n' }}{% endif %}",
-    "mistral_v1": "{{ bos_token }}{% for message in messages %}{% if message['role'] == 'user' %}{{ ' [INST] ' + message['content'] + ' [/INST]' }}{% else %}{{ ' ' + message['content'] + eos_token }}{% endif %}{% endfor %}",
-    "gemma": "{{ bos_token }}{% for message in messages %}{{ '<start_of_turn>' + ('model' if message['role'] == 'assistant' else message['role']) + '\n' + message['content'] | trim + '<end_of_turn>\n' }}{% endfor %}{% if add_generation_prompt %}{{ '<start_of_turn>model\n' }}{% endif %}",
-    "zephyr": "{% for message in messages %}{{ '<|' + message['role'] + '|>\n' + message['content'] + eos_token + '\n' }}{% endfor %}{% if add_generation_prompt %}{{ '<|assistant|>\n' }}{% endif %}",
-    "qwen_25": "{% for message in messages %}{{'<|im_start|>' + message['role'] + '\n' + message['content'] + '<|im_end|>' + '\n'}}{% endfor %}{% if add_generation_prompt %}{{ '<|im_start|>assistant\n' }}{% endif %}",
-}
+# Named chat templates live as Jinja files under data/templates/ (one per model family; the formats are the
+# public conversation layouts of those models). Anything else comes from the tokenizer or `chat_template_jinja`.
+_TEMPLATE_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "templates")
+
+
+class _TemplateTable(dict):
+    """name -> template text, read from the template directory on first use."""
+
+    def _load(self):
+        if not self and os.path.isdir(_TEMPLATE_DIR):
+            for fn in sorted(os.listdir(_TEMPLATE_DIR)):
+                if fn.endswith(".jinja"):
+                    with open(os.path.join(_TEMPLATE_DIR, fn), encoding="utf-8") as fh:
+                        dict.__setitem__(self, fn[:-6], fh.read().rstrip("\n"))
+
+    def __contains__(self, k):
+        self._load()
+        return dict.__contains__(self, k)
+
+    def __getitem__(self, k):
+        self._load()
+        return dict.__getitem__(self, k)
+
+    def __iter__(self):
+        self._load()
+        return dict.__iter__(self)
+
+    def keys(self):
+        self._load()
+        return dict.keys(self)
+
+
+CHAT_TEMPLATES = _TemplateTable()
 
 
 def get_chat_template(name: str | None, tokenizer=None, jinja: str | None = None) -> str | None:

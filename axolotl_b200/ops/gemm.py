@@ -19,7 +19,7 @@ _SM = 148
 USE_PAIR = os.environ.get("AXB_GEMM_PAIR", "1") != "0"
 # GLU folded into the gate|up GEMM epilogue (forward) and the down-projection input-gradient GEMM
 # (backward); AXB_GLU_EPILOGUE=0 runs the stand-alone GLU kernels instead.
-USE_GLU_EPILOGUE = os.environ.get("AXB_GLU_EPILOGUE", "0") != "0"
+USE_GLU_EPILOGUE = os.environ.get("AXB_GLU_EPILOGUE", "1") != "0"
 
 
 def _pick_bn(M: int, N: int) -> int:

@@ -239,11 +239,81 @@ def fetch(directory, dest):
 
 
 @cli.command("config-schema")
-def config_schema():
-    """Dump the JSON schema of the configuration."""
+@click.option("--format", "output_format", type=click.Choice(["json", "yaml"]), default="json")
+@click.option("--field", default=None, help="show the schema of one field only")
+def config_schema(output_format, field):
+    """Dump the JSON schema of the configuration (all keys, types, defaults)."""
     from ..config.schema import AxolotlConfig
 
-    click.echo(json.dumps(AxolotlConfig.model_json_schema(), indent=2))
+    schema = AxolotlConfig.model_json_schema()
+    if field:
+        props = schema.get("properties", {})
+        if field not in props:
+            match = [k for k in props if k.lower() == field.lower()]
+            if not match:
+                raise click.BadParameter(f"unknown field {field!r}; omit --field to dump the full schema")
+            field = match[0]
+        schema = {field: props[field]}
+    if output_format == "yaml":
+        import yaml
+
+        click.echo(yaml.dump(schema, default_flow_style=False, sort_keys=False))
+    else:
+        click.echo(json.dumps(schema, indent=2))
+
+
+@cli.command("agent-docs")
+@click.argument("topic", required=False, default=None)
+@click.option("--list", "list_topics", is_flag=True, help="list the available topics")
+def agent_docs(topic, list_topics):
+    """Print the bundled reference notes written for coding agents (no network needed)."""
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "agent_docs")
+    topics = sorted(f[:-3] for f in os.listdir(root) if f.endswith(".md"))
+    if list_topics:
+        for t in topics:
+            with open(os.path.join(root, t + ".md")) as fh:
+                click.echo(f"  {t:15s} {fh.readline().lstrip('# ').strip()}")
+        return
+    topic = topic or "overview"
+    if topic not in topics:
+        raise click.BadParameter(f"unknown topic {topic!r} (have: {', '.join(topics)})")
+    with open(os.path.join(root, topic + ".md")) as fh:
+        click.echo(fh.read())
+
+
+@cli.command("generate-cli-config-options")
+@click.option("--output", default="config_options.json", show_default=True, help="file to write")
+@click.option("--check", is_flag=True, help="fail if the file on disk is stale")
+def generate_cli_config_options(output, check):
+    """Write the table of command-line overrides (one ``--key`` per scalar config field, with its type)."""
+    from ..config.schema import AxolotlConfig
+
+    rows = {}
+    for name, info in sorted(AxolotlConfig.model_fields.items()):
+        ann = str(info.annotation)
+        kind = next((k for k in ("bool", "int", "float", "str") if k in ann), None)
+        if kind is None or "dict" in ann or "list" in ann.lower():
+            continue
+        rows[name] = {"option": "--" + name.replace("_", "-"), "type": kind,
+                      "default": info.default if isinstance(info.default, (bool, int, float, str, type(None))) else None}
+    text = json.dumps(rows, indent=1, sort_keys=True) + "\n"
+    if check:
+        if not os.path.exists(output) or open(output).read() != text:
+            raise click.ClickException(f"{output} is stale: run `axolotl generate-cli-config-options --output {output}`")
+        click.echo(f"{output} is up to date ({len(rows)} options)")
+        return
+    with open(output, "w") as fh:
+        fh.write(text)
+    click.echo(f"wrote {len(rows)} options to {output}")
+
+
+@cli.command("delinearize-llama4")
+@click.argument("model")
+@click.argument("output")
+def delinearize_llama4(model, output):
+    """Convert linearised Llama-4 expert weights back to the fused layout."""
+    raise click.ClickException("Llama-4 is not among the architectures of this framework "
+                               "(llama, mistral, phi3, qwen2, qwen3, granite, smollm3 and the qwen/mixtral/olmoe MoE families)")
 
 
 @cli.command("vllm-serve", context_settings=CONTEXT)

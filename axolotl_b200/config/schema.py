@@ -161,6 +161,71 @@ class TRLConfig(_Base):
     replay_buffer_size: int | None = None
 
 
+QuantDType = Literal["int4", "int8", "fp8", "float8_e4m3fn", "nvfp4", "mxfp4", "mxfp8"]
+
+
+class QATConfig(_Base):
+    """Quantisation-aware training: which fake-quantiser wraps the trainable dense weights
+    (src/axolotl/utils/schemas/quantization.py:31-58)."""
+    activation_dtype: QuantDType | None = None
+    weight_dtype: QuantDType = "int8"
+    quantize_embedding: bool | None = False
+    group_size: int | None = 32
+    fake_quant_after_n_steps: int | None = None
+
+
+class PTQConfig(_Base):
+    """Post-training quantisation applied by ``axolotl quantize`` (quantization.py:61-80)."""
+    weight_dtype: QuantDType = "nvfp4"
+    activation_dtype: QuantDType | None = None
+    quantize_embedding: bool | None = None
+    group_size: int | None = 16
+
+
+class VllmConfig(_Base):
+    """Arguments of ``axolotl vllm-serve`` (src/axolotl/utils/schemas/vllm.py)."""
+    device: str | None = "auto"
+    tensor_parallel_size: int | None = None
+    data_parallel_size: int | None = None
+    gpu_memory_utilization: float | None = 0.9
+    dtype: str | None = "auto"
+    max_model_len: int | None = None
+    enable_prefix_caching: bool | None = None
+    host: str | None = "0.0.0.0"  # nosec B104
+    port: int | None = 8000
+    enable_reasoning: bool | None = None
+    reasoning_parser: str | None = None
+    enforce_eager: bool | None = None
+    serve_module: str | None = None
+    worker_extension_cls: str | None = None
+
+
+class EBFTConfig(_Base):
+    """Energy-based fine-tuning block (src/axolotl/utils/schemas/config.py:76-190)."""
+    feature_layers: list[float] = [0.25, 0.5, 0.75]
+    embed_method: Literal["last_token", "mean_pooling", "completion_mean", "concat"] = "last_token"
+    use_whitening: bool = False
+    alignment_coef: float = 1.0
+    diversity_coef: float = 1.0
+    ce_coef: float = 0.0
+    adaptive_max_tokens: bool = True
+    gt_length_multiplier: float = 1.5
+    mode: Literal["structured", "strided"] = "structured"
+    stride: int = 8
+    context_length: int = 8
+    generate_max_len: int = 8
+    n_samples_per_prompt: int = 4
+    temperature: float = 0.6
+    top_p: float = 1.0
+    rl_coef: float = 1.0
+    advantage_estimator: Literal["rloo", "group_norm", "reinforce"] = "rloo"
+    min_completion_prefix: int = 0
+
+
+class SelectiveCheckpointing(_Base):
+    save: list[str] = ["attention"]
+
+
 class DynamicCheckpointConfig(_Base):
     enabled: bool = False
     check_interval: int = 10
@@ -388,7 +453,7 @@ class AxolotlConfig(_Base):
     gradient_checkpointing_kwargs: dict | None = None
     activation_offloading: bool | str | None = False
     layer_offloading: bool | None = None
-    selective_checkpointing: bool | str | None = None
+    selective_checkpointing: bool | SelectiveCheckpointing | None = None
     tiled_mlp: bool | None = None
     tiled_mlp_num_shards: int | None = None
     chunked_cross_entropy: bool | None = None
@@ -425,7 +490,7 @@ class AxolotlConfig(_Base):
     # ---- RL / preference
     rl: str | None = None
     trl: TRLConfig | None = None
-    ebft: dict | None = None      # energy-based fine-tuning block (mode, feature_layers, embed_method, coefficients)
+    ebft: EBFTConfig | None = None
     rl_beta: float | None = None
     dpo_beta: float | None = None
     dpo_label_smoothing: float | None = None
@@ -446,7 +511,19 @@ class AxolotlConfig(_Base):
     cpo_loss_type: str | None = None
     max_prompt_len: int | None = None
     precompute_ref_log_probs: bool | None = None
-    vllm: dict | None = None
+    vllm: VllmConfig | None = None
+    use_comet: bool | None = None
+    comet_api_key: str | None = None
+    comet_workspace: str | None = None
+    comet_project_name: str | None = None
+    comet_experiment_key: str | None = None
+    comet_mode: str | None = None
+    comet_online: bool | None = None
+    comet_experiment_config: dict | None = None
+    use_trackio: bool | None = None
+    trackio_project_name: str | None = None
+    trackio_run_name: str | None = None
+    trackio_space_id: str | None = None
     # ---- MoE
     experts_implementation: str | None = None
     router_aux_loss_coef: float | None = None
@@ -463,8 +540,8 @@ class AxolotlConfig(_Base):
     relora: bool | None = None
     relora_prune_ratio: float | None = None
     relora_cpu_offload: bool | None = None
-    qat: dict | None = None
-    quantization: dict | None = None
+    qat: QATConfig | None = None
+    quantization: PTQConfig | None = None
     fix_untrained_tokens: int | list[int] | None = None
     # derived (filled by normalisation)
     is_llama_derived_model: bool | None = None
@@ -513,8 +590,7 @@ UNSUPPORTED_KEYS = {
 # purpose is served natively or is irrelevant here).
 INERT_KEYS = {
     "accelerator_config", "activation_checkpointing", "async_prefetch", "auto_find_batch_size",
-    "bnb_config_kwargs", "cls_model_config", "comet_api_key", "comet_experiment_config",
-    "comet_experiment_key", "comet_mode", "comet_online", "comet_workspace", "dion_lr", "dion_momentum",
+    "bnb_config_kwargs", "cls_model_config", "dion_lr", "dion_momentum",
     "dion_rank_fraction", "dion_rank_multiple_of", "dpo_generate_during_eval", "dpo_padding_free",
     "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "embeddings_skip_upcast",
     "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",
@@ -529,8 +605,7 @@ INERT_KEYS = {
     "ray_num_workers", "ray_run_name", "recompute_layer_types", "relora_prune_method", "resources_per_worker",
     "save_sliding_window", "scaling_softmax_bias", "scaling_softmax_factor", "streaming_min_groups",
     "tokenizer_save_jinja_files", "tokenizer_use_mistral_common", "torch_compile_backend",
-    "torch_compile_mode", "torch_compile_options", "torchdistx_path", "trackio_project_name", "trackio_run_name",
-    "trackio_space_id", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss",
+    "torch_compile_mode", "torch_compile_options", "torchdistx_path", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss",
     "liger_rope", "liger_rms_norm", "liger_glu_activation", "liger_layer_norm", "kd_online_server_base_url", "tiled_mlp_use_original_mlp", "min_num_params",
 }
 

@@ -38,12 +38,23 @@ def _u64_array(vals):
     return (C.c_ulonglong * len(vals))(*[int(v) for v in vals])
 
 
+_ALLOCATED_BYTES = 0
+
+
+def allocated_bytes() -> int:
+    """Bytes of symmetric (peer-mapped) memory this process has allocated so far. These arenas are outside
+    torch's caching allocator, so ``torch.cuda.max_memory_allocated`` does not see them."""
+    return _ALLOCATED_BYTES
+
+
 class SymmBuffer:
     """A tensor every rank of ``group`` allocated with the same size, plus its peer addresses."""
 
     def __init__(self, numel, dtype, device, group, use_multicast=True):
         import torch.distributed._symmetric_memory as symm_mem
 
+        global _ALLOCATED_BYTES
+        _ALLOCATED_BYTES += int(numel) * torch.empty((), dtype=dtype).element_size()
         self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
         self.tensor.zero_()
         self.handle = symm_mem.rendezvous(self.tensor, group)

@@ -188,6 +188,53 @@ class MLflowReporter(Callback):
                                      for k, v in logs.items() if isinstance(v, (int, float))}, step=logs.get("step"))
 
 
+class CometReporter(Callback):
+    """``use_comet``: metrics to a Comet experiment (src/axolotl/core/builders/base.py:526-548,
+    src/axolotl/utils/callbacks/comet_.py)."""
+
+    def __init__(self, cfg):
+        import comet_ml  # optional dependency
+
+        kw = {k: cfg.get(f"comet_{k}") for k in ("api_key", "workspace", "project_name", "experiment_key", "mode", "online")
+              if cfg.get(f"comet_{k}") is not None}
+        kw.update(cfg.get("comet_experiment_config") or {})
+        self.exp = comet_ml.start(**{k: v for k, v in kw.items() if k in ("api_key", "workspace", "project_name",
+                                                                          "experiment_key", "mode", "online")})
+        self.exp.log_parameters({k: v for k, v in dict(cfg).items() if isinstance(v, (str, int, float, bool))})
+
+    def on_log(self, trainer, logs):
+        if trainer.rank == 0:
+            self.exp.log_metrics({k: v for k, v in logs.items() if isinstance(v, (int, float))}, step=logs.get("step"))
+
+    on_evaluate = on_log
+
+    def on_train_end(self, trainer):
+        if trainer.rank == 0:
+            self.exp.end()
+
+
+class TrackioReporter(Callback):
+    """``use_trackio``: metrics to a Trackio project (local dashboard or a Space)."""
+
+    def __init__(self, cfg):
+        import trackio  # optional dependency
+
+        self.trackio = trackio
+        trackio.init(project=cfg.get("trackio_project_name") or "axolotl", name=cfg.get("trackio_run_name"),
+                     space_id=cfg.get("trackio_space_id"), config={k: v for k, v in dict(cfg).items()
+                                                                   if isinstance(v, (str, int, float, bool))})
+
+    def on_log(self, trainer, logs):
+        if trainer.rank == 0:
+            self.trackio.log({k: v for k, v in logs.items() if isinstance(v, (int, float))})
+
+    on_evaluate = on_log
+
+    def on_train_end(self, trainer):
+        if trainer.rank == 0:
+            self.trackio.finish()
+
+
 class PrometheusExporter(Callback):
     """`use_otel_metrics`: exposes the latest training metrics as Prometheus gauges on
     ``otel_metrics_host:otel_metrics_port``."""
@@ -342,7 +389,9 @@ class ReLoRACallback(Callback):
 
 
 def build_callbacks(cfg):
-    cbs = [JsonlReporter(), StatusCheckCallback()]
+    from ..utils.telemetry import TelemetryCallback
+
+    cbs = [JsonlReporter(), StatusCheckCallback(), TelemetryCallback(cfg)]
     if cfg.get("lisa_n_layers") and cfg.get("lisa_step_interval"):
         cbs.append(LISACallback(cfg["lisa_n_layers"], cfg["lisa_step_interval"], cfg.get("seed") or 0))
     if cfg.get("relora") and cfg.get("jagged_restart_steps"):
@@ -361,9 +410,12 @@ def build_callbacks(cfg):
         cbs.append(ProfilerCallback(cfg["profiler_steps"], cfg.get("profiler_steps_start") or 0))
     for flag, factory in (("use_tensorboard", lambda: TensorboardReporter(os.path.join(cfg["output_dir"], "runs"))),
                           ("use_wandb", lambda: WandbReporter(cfg)), ("use_mlflow", lambda: MLflowReporter(cfg)),
+                          ("use_comet", lambda: CometReporter(cfg)), ("use_trackio", lambda: TrackioReporter(cfg)),
                           ("use_otel_metrics", lambda: PrometheusExporter(cfg.get("otel_metrics_host") or "localhost",
                                                                           cfg.get("otel_metrics_port") or 8000))):
-        if cfg.get(flag) or (flag == "use_wandb" and cfg.get("wandb_project")):
+        if cfg.get(flag) or (flag == "use_wandb" and cfg.get("wandb_project")) \
+                or (flag == "use_comet" and cfg.get("comet_project_name")) \
+                or (flag == "use_trackio" and cfg.get("trackio_project_name")):
             try:
                 cbs.append(factory())
             except Exception as exc:

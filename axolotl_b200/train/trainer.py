@@ -343,6 +343,10 @@ class Trainer:
             logs["memory/max_active (GiB)"] = torch.cuda.max_memory_allocated(self.device) / gib
             logs["memory/max_allocated (GiB)"] = torch.cuda.max_memory_allocated(self.device) / gib
             logs["memory/device_reserved (GiB)"] = torch.cuda.memory_reserved(self.device) / gib
+            if self.parallel is not None:   # peer-mapped arenas live outside torch's allocator
+                from ..parallel.symm import allocated_bytes
+
+                logs["memory/symmetric_arenas (GiB)"] = allocated_bytes() / gib
         return logs
 
     # ------------------------------------------------------------------ eval

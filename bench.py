@@ -223,6 +223,10 @@ def main():
         for k in ("input_ids", "labels", "position_ids"):
             b[k] = b[k].pin_memory()
     tokens_per_step = int(cpu_batches[0]["input_ids"].numel())
+    # real (non-pad) and trainable tokens of the timed steps, next to the padded slot count
+    real_tokens = sum(int((b["labels"] != -100).sum()) + int(((b["labels"] == -100) & (b["input_ids"] != 0)).sum())
+                      for b in cpu_batches[W:W + K])
+    trainable_tokens = sum(int((b["labels"][:, 1:] != -100).sum()) for b in cpu_batches[W:W + K])
 
     def barrier():
         if world > 1:
@@ -274,6 +278,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
     mem_gib = torch.cuda.max_memory_allocated(dev) / 1024 ** 3
+    # symmetric (peer-mapped) arenas are allocated outside torch's caching allocator: sharded weights, flat
+    # fp32 masters / gradients / bf16 shadows, staging and exchange buffers
+    symm_bytes = 0
+    if parallel is not None:
+        from axolotl_b200.parallel.symm import allocated_bytes
+
+        symm_bytes = allocated_bytes()
+    free_b, total_b = torch.cuda.mem_get_info(dev)
+    counts = torch.tensor([real_tokens, trainable_tokens], dtype=torch.float64, device=dev)
+    if world > 1 and args.config not in ("cp64k",):
+        dist.all_reduce(counts)
+        if args.config == "tp70b":
+            counts /= 2          # both ranks of a tensor-parallel pair count the same batch
+    real_tokens, trainable_tokens = float(counts[0]), float(counts[1])
     if rank == 0:
         groups = {"cp64k": 1, "tp70b": max(world // 2, 1)}.get(args.config, world)   # data-parallel replicas
         total_tokens = tokens_per_step * groups * K
@@ -306,7 +324,13 @@ def main():
                     "h2d_bytes_per_step": h2d_bytes(cpu_batches[W]) + 16 * (getattr(staged[W]["attn_meta"], "n_tiles", 0) * 2),
                     "d2h_bytes_per_step": 4, "last_loss": last_loss},
             "gpu_launches": launches,
+            "tokens": {"slots_per_s": value, "non_pad_per_s": real_tokens / (ms / 1e3),
+                       "trainable_per_s": trainable_tokens / (ms / 1e3),
+                       "note": "`value` counts every slot of the packed rows (the reference's tokens/s does too); "
+                               "non_pad leaves out the padding at the end of each row, trainable counts label positions"},
             "peak_mem_gib": mem_gib,
+            "memory": {"torch_peak_allocated_gib": mem_gib, "symmetric_arenas_gib": symm_bytes / 1024 ** 3,
+                       "device_in_use_gib": (total_b - free_b) / 1024 ** 3},
         }))
     if world > 1:
         dist.destroy_process_group()

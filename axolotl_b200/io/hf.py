@@ -110,6 +110,82 @@ def load_pretrained(path: str, dtype=torch.bfloat16, device="cpu", config: Model
     return model
 
 
+def sharded_state_dict(model: CausalLM, rank: int) -> tuple[dict, list[str]]:
+    """This rank's part of a SHARDED state dict under HF names, and the list of tensors that are split on
+    dim 0. A row-sharded fused weight (q|k|v, gate|up) holds rows [rank * n, (rank + 1) * n) of the fused
+    matrix; every sub-projection gets the overlap of that range with its own rows (possibly none: an empty
+    [0, K] tensor keeps the per-rank files uniform). Tensors that are not sharded go into rank 0's file only.
+    (The reference writes torch-DCP shards for ``fsdp_config.state_dict_type: SHARDED_STATE_DICT``,
+    src/axolotl/monkeypatch/accelerate/fsdp2.py:348-433; this layout is what ``merge-sharded-fsdp-weights``
+    reads back.)"""
+    full = hf_state_dict(model) if rank == 0 else {}
+    out, sharded = {}, []
+    skip = set()
+    for name, m in model.named_modules():
+        if not isinstance(m, FusedLinear):
+            continue
+        info = getattr(m.weight, "_axb_shard", None)
+        if info is None:
+            continue
+        parent = name.rsplit(".", 1)[0]
+        rows = info.rows // info.world
+        lo, hi = info.rank * rows, (info.rank + 1) * rows
+        w = m.weight.detach()
+        r0 = 0
+        for sub, n in zip(m.names, m.out_features):
+            r1 = r0 + n
+            a, b = max(r0, lo), min(r1, hi)
+            key = f"model.{parent}.{sub}.weight"
+            out[key] = w[a - lo:b - lo] if b > a else w[:0]
+            sharded.append(key)
+            skip.add(key)
+            r0 = r1
+    for k, v in full.items():
+        if k not in skip:
+            out[k] = v
+    return out, sharded
+
+
+def save_sharded_state(model: CausalLM, out_dir: str, rank: int, world: int):
+    """Every rank writes ``<out_dir>/pytorch_model_fsdp_0/shard_rank{rank}.safetensors``; rank 0 adds the
+    index and the model config."""
+    import json
+
+    d = os.path.join(out_dir, "pytorch_model_fsdp_0")
+    os.makedirs(d, exist_ok=True)
+    sd, sharded = sharded_state_dict(model, rank)
+    st.save_file({k: v.to("cpu").contiguous() for k, v in sd.items()}, os.path.join(d, f"shard_rank{rank}.safetensors"),
+                 {"format": "pt"})
+    if rank == 0:
+        with open(os.path.join(d, "shard_index.json"), "w") as fh:
+            json.dump({"world_size": world, "sharded": sharded}, fh, indent=1)
+        model.config.save_pretrained(d)
+    return d
+
+
+def load_pretrained_from_rank0(path: str, dtype=torch.bfloat16, device="cpu", config: ModelConfig | None = None,
+                               group=None, strict: bool = True) -> CausalLM:
+    """``fsdp_config.cpu_ram_efficient_loading``: only rank 0 reads the checkpoint from disk; every other rank
+    builds the empty model and receives the tensors by broadcast, so N ranks do not read (and hold in host
+    memory) N copies of the files (src/axolotl/monkeypatch/accelerate/fsdp2.py:142-345 loads on rank 0 and
+    scatters)."""
+    import torch.distributed as dist
+
+    cfg = config or ModelConfig.from_pretrained(path)
+    model = CausalLM(cfg, dtype=dtype, device=device)
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if rank == 0:
+        load_state_into(model, st.iter_checkpoint(path), strict=strict)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        for _, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
+            dist.broadcast(p.data, src=src, group=group)
+        for _, b in sorted(model.named_buffers(), key=lambda kv: kv[0]):
+            if b is not None and b.is_floating_point():
+                dist.broadcast(b.data, src=src, group=group)
+    return model
+
+
 def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     """Model tensors under HF names (views where possible; the writer makes them contiguous)."""
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}

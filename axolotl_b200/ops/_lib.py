@@ -28,6 +28,7 @@ _CUDA_SIGS = {
     "axb_gemm_bf16_pair_glu": [vp, i64, i32, vp, i64, i32, vp, i64, vp, i64, i32, i32, i32, vp, i64, vp, i64,
                                i32, f32, i32, i32, f32, vp, i64, vp, C.c_ulonglong, C.c_ulonglong, i32, vp, i32,
                                vp, vp],
+    "axb_lora_bwd_dy": [vp, i64, vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, vp, i32, vp, vp],
     "axb_gemm_set_backoff": [i32, i32],
     "axb_gemm_set_debug": [i32],
     "axb_gemm_set_pair_tuning": [i32, i32, i32],

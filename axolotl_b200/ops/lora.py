@@ -36,6 +36,48 @@ def skinny_gemm(a, b, *, trans_b=False, alpha=1.0):
     return acc.to(torch.bfloat16)
 
 
+USE_FUSED_DY = __import__("os").environ.get("AXB_LORA_FUSED_DY", "1") != "0"
+
+
+def fused_dy_ok(dy, B16, xa) -> bool:
+    """Whether the one-pass kernel (t = dy B and dB = dy^T xa from a single read of dy) applies."""
+    return (USE_FUSED_DY and dy.is_cuda and dy.dtype == torch.bfloat16 and B16 is not None and xa is not None
+            and B16.shape[1] <= 64 and dy.shape[0] >= 512 and dy.stride(1) == 1 and dy.stride(0) % 8 == 0
+            and B16.stride(1) == 1 and B16.stride(0) % 8 == 0 and xa.stride(1) == 1 and xa.stride(0) % 8 == 0)
+
+
+def lora_bwd_dy(dy, B16, xa, blocks, scaling, dB_acc):
+    """``t = scaling * dy @ B16`` (bf16 [T, R]) and ``dB_acc[blocks] += dy^T @ xa`` (fp32 [N, R], only the
+    diagonal blocks) from ONE pass over ``dy`` (csrc/lora_fused.cu)."""
+    import ctypes
+
+    from . import _lib
+
+    lib = _lib.cuda_lib()
+    T, N = dy.shape
+    R = B16.shape[1]
+    t32 = torch.zeros((T, R), dtype=torch.float32, device=dy.device)
+    flat = (ctypes.c_int * (4 * len(blocks)))(*[int(v) for blk in blocks for v in blk])
+    rc = lib.axb_lora_bwd_dy(dy.data_ptr(), dy.stride(0), B16.data_ptr(), B16.stride(0), xa.data_ptr(), xa.stride(0),
+                             t32.data_ptr(), dB_acc.data_ptr(), dB_acc.stride(0), T, N, R, flat, len(blocks),
+                             _lib.status_word(dy.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "axb_lora_bwd_dy")
+    t = torch.empty((T, R), dtype=torch.bfloat16, device=dy.device)
+    _lib.check_rc(lib.axb_cast_f32_to_bf16(t32.data_ptr(), t.data_ptr(), t32.numel(), float(scaling), _lib.stream_ptr()),
+                  "cast_f32_to_bf16")
+    return t
+
+
+def _t_and_dB(dy, B, B16, xa, blocks, scaling, need_dB):
+    """(t, dB) of one projection: the fused one-pass kernel when it applies, two GEMM passes otherwise."""
+    if need_dB and fused_dy_ok(dy, B16, xa):
+        tgt = getattr(B, "_axb_grad", None)
+        buf = tgt if tgt is not None else torch.zeros(B.shape, dtype=torch.float32, device=dy.device)
+        t = lora_bwd_dy(dy, B16, xa, blocks, scaling, buf)
+        return t, (None if tgt is not None else buf.to(B.dtype)), True
+    return skinny_gemm(dy, B16, trans_b=True, alpha=scaling), None, False
+
+
 class _LoRALinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, W, A, B, A16, B16, scaling, blocks, bias):
@@ -57,8 +99,8 @@ class _LoRALinearFn(torch.autograd.Function):
         T, K = x.shape
         N, R = B16.shape
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        # t = s * dy @ B  -> [T, R]
-        t = skinny_gemm(dy, B16, trans_b=True, alpha=s)
+        # t = s * dy @ B  -> [T, R]  (and, in the same pass over dy, dB = dy^T xa)
+        t, dB_fused, dB_done = _t_and_dB(dy, B, B16, xa, ctx.blocks, s, ctx.needs_input_grad[3])
         dx = gemm(dy, W, trans_b=True, a2=t, b2=A16) if need_dx else None
         dA = dB = None
         if ctx.needs_input_grad[2]:
@@ -67,7 +109,9 @@ class _LoRALinearFn(torch.autograd.Function):
             sp = pick_splits((K + 255) // 256, (T + 63) // 64)
             gemm(t, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
             dA = None if tgt is not None else buf.to(A.dtype)
-        if ctx.needs_input_grad[3]:
+        if dB_done:
+            dB = dB_fused
+        elif ctx.needs_input_grad[3]:
             tgt = getattr(B, "_axb_grad", None)
             buf = tgt if tgt is not None else torch.zeros(B.shape, dtype=torch.float32, device=x.device)
             for (row0, rows, r0, r) in ctx.blocks:
@@ -116,7 +160,7 @@ class _LinearFn(torch.autograd.Function):
         return dx, dW, dbias
 
 
-def _adapter_grads(A, B, t, x, dy, xa, blocks):
+def _adapter_grads(A, B, t, x, dy, xa, blocks, dB_done=False, dB_fused=None):
     """Gradients of the fp32 LoRA masters: dA [R, K] = t^T x and the diagonal blocks of dB [N, R] =
     dy^T xa (``t`` = s dy B and ``xa`` = s x A^T carry the scaling). Accumulated straight into the
     optimizer's flat gradient buffer (``_axb_grad``) when the parameter has one."""
@@ -128,7 +172,9 @@ def _adapter_grads(A, B, t, x, dy, xa, blocks):
         sp = pick_splits((K + 255) // 256, (T + 63) // 64)
         gemm(t, x, trans_a=True, trans_b=True, out=buf, accumulate=True, splits=sp)
         dA = None if tgt is not None else buf.to(A.dtype)
-    if B is not None and B.requires_grad:
+    if dB_done:
+        dB = dB_fused
+    elif B is not None and B.requires_grad:
         tgt = getattr(B, "_axb_grad", None)
         buf = tgt if tgt is not None else torch.zeros(B.shape, dtype=torch.float32, device=x.device)
         for (row0, rows, r0, r) in blocks:
@@ -179,16 +225,19 @@ class _GLUMLPFn(torch.autograd.Function):
         dy = dy.contiguous()
         need = ctx.needs_input_grad
         # ---- down projection: dh = dy W_d + t_d A_d never reaches memory, d_gate | d_up does
-        t_d = skinny_gemm(dy, Bd16, trans_b=True, alpha=cfg["s_d"]) if Ad16 is not None else None
+        t_d, dBd_f, dBd_done = (_t_and_dB(dy, Bd, Bd16, ha, cfg["blocks_d"], cfg["s_d"], need[8]) if Ad16 is not None
+                                else (None, None, False))
         dgu = torch.empty_like(gu)
         gemm(dy, Wd, trans_b=True, a2=t_d, b2=Ad16, out=dgu, glu=("bwd", cfg["kind"], cfg["limit"], gu))
-        dAd, dBd = _adapter_grads(Ad if need[7] else None, Bd if need[8] else None, t_d, h, dy, ha, cfg["blocks_d"])
+        dAd, dBd = _adapter_grads(Ad if need[7] else None, Bd if need[8] else None, t_d, h, dy, ha, cfg["blocks_d"],
+                                  dBd_done, dBd_f)
         dWd = _weight_grad(Wd, dy, h) if need[2] else None
         # ---- gate|up projection
-        t_gu = skinny_gemm(dgu, Bgu16, trans_b=True, alpha=cfg["s_gu"]) if Agu16 is not None else None
+        t_gu, dBgu_f, dBgu_done = (_t_and_dB(dgu, Bgu, Bgu16, xa, cfg["blocks_gu"], cfg["s_gu"], need[4])
+                                   if Agu16 is not None else (None, None, False))
         dx = gemm(dgu, Wgu, trans_b=True, a2=t_gu, b2=Agu16) if need[0] else None
         dAgu, dBgu = _adapter_grads(Agu if need[3] else None, Bgu if need[4] else None, t_gu, x, dgu, xa,
-                                    cfg["blocks_gu"])
+                                    cfg["blocks_gu"], dBgu_done, dBgu_f)
         dWgu = _weight_grad(Wgu, dgu, x) if need[1] else None
         return dx, dWgu, dWd, dAgu, dBgu, None, None, dAd, dBd, None, None, None
 

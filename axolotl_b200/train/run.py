@@ -57,7 +57,12 @@ def build_model(cfg, device) -> CausalLM:
     pm.call("pre_model_load", cfg)
     src = cfg.get("base_model")
     have_weights = bool(src) and os.path.isdir(src) and bool(hf_io.st.checkpoint_files(src)) and not cfg.get("reinit_weights")
-    if have_weights:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if have_weights and world > 1 and (cfg.get("fsdp_config") or {}).get("cpu_ram_efficient_loading") \
+            and torch.distributed.is_initialized():
+        model = hf_io.load_pretrained_from_rank0(src, dtype=dtype, device=device, config=mc)
+        LOG.info("cpu_ram_efficient_loading: rank 0 read the checkpoint, the other ranks received it by broadcast")
+    elif have_weights:
         model = hf_io.load_pretrained(src, dtype=dtype, device=device, config=mc)
     else:
         if not cfg.get("reinit_weights") and not cfg.get("model_preset"):
@@ -330,6 +335,11 @@ def save_model_artifacts(model, cfg, spec, out_dir, parallel=None, rank=0):
     if spec is not None:
         if rank == 0:
             save_adapter(model, spec, out_dir)
+        return
+    sd_type = str((cfg.get("fsdp_config") or {}).get("state_dict_type") or "FULL_STATE_DICT").upper()
+    if parallel is not None and parallel.fsdp is not None and sd_type == "SHARDED_STATE_DICT":
+        # every rank writes its own rows; `axolotl merge-sharded-fsdp-weights` assembles the HF checkpoint
+        hf_io.save_sharded_state(model, out_dir, parallel.fsdp.rank, parallel.fsdp.world)
         return
     if parallel is not None and parallel.fsdp is not None:
         parallel.materialize_full_weights(model)  # gathers sharded weights for saving

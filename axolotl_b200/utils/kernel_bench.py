@@ -221,6 +221,9 @@ def bench_lora_skinny(rows):
         t_dA = time_cuda(lambda: gemm(xa, x, trans_a=True, trans_b=True, out=dA, accumulate=True, splits=sp_a))
         sp_b = pick_splits((N + 127) // 128, (T + 63) // 64)
         t_dB = time_cuda(lambda: gemm(dy, xa, trans_a=True, trans_b=True, out=dB, accumulate=True, splits=sp_b, bn=64))
+        nb = 3 if name == "qkv" else (2 if name == "gate_up" else 1)
+        blocks = [(i * (N // nb), N // nb, i * (R // nb), R // nb) for i in range(nb)]
+        t_fused = time_cuda(lambda: _lora.lora_bwd_dy(dy, B, xa, blocks, 2.0, dB))
         gb = lambda elems, ms: elems * 2 / 1e6 / ms   # GB/s
         rows.append(f"lora {name} r={R}: x@A^T {t_xa * 1e3:.0f} us ({gb(T * K, t_xa) / hbm:.2f}) | dy@B {t_t * 1e3:.0f} us "
                     f"({gb(T * N, t_t) / hbm:.2f}) | dA=t^T x {t_dA * 1e3:.0f} us ({gb(T * K, t_dA) / hbm:.2f}, splits {sp_a}) | "
@@ -337,6 +340,23 @@ def profile_case(what):
         out = torch.empty(8192, 6144, device="cuda", dtype=torch.bfloat16)
         for _ in range(4):
             gemm(a, b, out=out)
+    elif what == "one_mlp":
+        # the two GEMMs of a Llama-3-8B MLP that carry the GLU in their epilogues (forward gate|up with
+        # h = silu(gate) * up, backward dX(down) with d_gate | d_up), 4096 token rows
+        from axolotl_b200.ops import gemm as gemm_mod
+
+        gemm_mod.USE_GLU_EPILOGUE = True
+        T, H, I = 4096, 4096, 14336
+        x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
+        Wgu = (torch.randn(2 * I, H, device="cuda") * 0.02).bfloat16()
+        Wd = (torch.randn(H, I, device="cuda") * 0.02).bfloat16()
+        dy = (torch.randn(T, H, device="cuda") * 0.1).bfloat16()
+        gu = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+        h = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+        dgu = torch.empty_like(gu)
+        for _ in range(3):
+            gemm(x, Wgu, out=gu, glu=("fwd", 0, 0.0, h))
+            gemm(dy, Wd, trans_b=True, out=dgu, glu=("bwd", 0, 0.0, gu))
     elif what == "one_grouped":
         # one MoE projection of Qwen3-MoE-30B-A3B: 128 experts, 8192 tokens x top-8 = 65536 routed rows
         from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gram
@@ -368,7 +388,7 @@ def profile_case(what):
 
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
-    if what in ("one_gemm", "one_attn", "one_grouped"):
+    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp"):
         return profile_case(what)
     rows = []
     if what in ("gemm", "all"):

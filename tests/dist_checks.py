@@ -381,6 +381,32 @@ def check_tp_cp(dev, rank, world):
     dist.barrier()
 
 
+def check_rank0_loading(dev, rank, world):
+    """cpu_ram_efficient_loading: rank 0 alone reads the checkpoint (the other ranks are handed a path that
+    does not exist and an explicit config); every rank ends up with identical weights."""
+    import tempfile
+
+    from axolotl_b200.io import hf as hf_io
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.transformer import CausalLM
+
+    cfg = preset("tiny-llama", num_hidden_layers=2, vocab_size=512, hidden_size=64, intermediate_size=128,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    box = [None]
+    if rank == 0:
+        box[0] = tempfile.mkdtemp(prefix="axb_r0_")
+        hf_io.save_pretrained(CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(3), box[0])
+    dist.broadcast_object_list(box, src=0)
+    path = box[0] if rank == 0 else os.path.join(box[0], "does-not-exist-on-this-rank")
+    model = hf_io.load_pretrained_from_rank0(path, dtype=torch.float32, device=dev, config=cfg)
+    ref = CausalLM(cfg, dtype=torch.float32, device="cpu").init_weights(3)
+    for (n, p), (_, q) in zip(sorted(model.named_parameters()), sorted(ref.named_parameters())):
+        assert torch.equal(p.detach().cpu(), q.detach()), n
+    dist.barrier()
+    if rank == 0:
+        print("rank-0 loading ok")
+
+
 def check_expert_parallel(dev, rank, world):
     """EP=world MoE training (each rank its own batch) must follow the single-process run with the
     ranks' batches as accumulation micro-batches."""
@@ -464,6 +490,7 @@ def main():
     if cpu:
         dist.init_process_group("gloo")
         dev = torch.device("cpu")
+        want("load") and check_rank0_loading(dev, rank, world)
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
         want("dp") and check_training_equivalence(dev, rank, world, "collective", multigroup=True)
         want("ddp") and check_training_equivalence(dev, rank, world, "collective", replicate=True)

@@ -20,6 +20,7 @@ def _run(nproc, extra, port):
 
 def test_data_parallel_gloo_world2():
     out = _run(2, ["cpu"], 29611)
+    assert "rank-0 loading ok" in out
     assert "dp training equivalence ok (collective)" in out
     assert "dp training equivalence ok (collective, two groups)" in out
     assert "dp training equivalence ok (collective, replicated)" in out

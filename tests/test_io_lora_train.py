@@ -879,3 +879,37 @@ def test_densemixer_router_gradient_is_the_dense_mixture_gradient():
     ((probs[:, :, None] * O).sum(1) * dy).sum().backward()
     assert torch.allclose(g_dense, gate.grad, atol=1e-4, rtol=1e-3), (g_dense - gate.grad).abs().max()
     moe.dense_mixer = False
+
+
+def test_sharded_state_dict_roundtrip_through_the_merge_tool(tmp_path):
+    """Row-sharded fused weights (as FSDP holds them) -> per-rank shard files under HF names -> merged checkpoint
+    equal to the unsharded model's."""
+    from types import SimpleNamespace
+
+    from axolotl_b200.io import hf as hf_io
+    from axolotl_b200.models.layers import FusedLinear
+
+    world = 2
+    ref = _tiny(2)
+    want = {k: v.clone() for k, v in hf_io.hf_state_dict(ref).items()}
+    for rank in range(world):
+        m = _tiny(2)
+        m.load_state_dict(ref.state_dict())
+        for mod in m.modules():
+            if isinstance(mod, FusedLinear) and mod.weight.shape[0] % world == 0:
+                N, K = mod.weight.shape
+                rows = N // world
+                shard = torch.nn.Parameter(mod.weight.detach()[rank * rows:(rank + 1) * rows].clone(), requires_grad=False)
+                shard._axb_shard = SimpleNamespace(rows=N, cols=K, world=world, rank=rank)
+                mod.weight = shard
+        d = hf_io.save_sharded_state(m, str(tmp_path / "out"), rank, world)
+    idx = json.load(open(os.path.join(d, "shard_index.json")))
+    assert idx["world_size"] == 2 and any(k.endswith("q_proj.weight") for k in idx["sharded"])
+    part1 = st.load_file(os.path.join(d, "shard_rank1.safetensors"))
+    assert any(v.shape[0] == 0 for v in part1.values())          # q_proj lies entirely in rank 0's rows
+    assert "model.embed_tokens.weight" not in part1               # unsharded tensors live in rank 0's file only
+    merge_sharded_fsdp_weights(d, str(tmp_path / "merged"), dtype=torch.float32)
+    back = st.load_checkpoint(str(tmp_path / "merged")) if hasattr(st, "load_checkpoint") else st.load_file(str(tmp_path / "merged" / "model.safetensors"))
+    assert set(back) == set(want)
+    for k in want:
+        assert torch.equal(back[k].float(), want[k].float()), k

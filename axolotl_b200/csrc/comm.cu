@@ -114,6 +114,9 @@ struct RsAdamwParams {
   // group's squared norm to *gnorm_sq_out, leave the reduced slice in place), then mode 2 for every
   // group (clip by *gnorm_sq_out, AdamW, publish; no reduction).
   int mode;
+  // 1: the fp32 master exists only on the rank that owns the slice (n / world floats, master.p[rank] is
+  // rebased so that the global element index addresses it); only the bf16 copy is published to all ranks
+  int master_local;
 };
 
 __global__ void __launch_bounds__(256)
@@ -236,7 +239,15 @@ __global__ void __launch_bounds__(256)
     *reinterpret_cast<float4*>(p.exp_avg_sq + i) = make_float4(s[0], s[1], s[2], s[3]);
     const float4 wn = make_float4(w[0], w[1], w[2], w[3]);
     const uint32_t b0 = pack_bf16x2(w[0], w[1]), b1 = pack_bf16x2(w[2], w[3]);
-    if (p.master_mc) {
+    if (p.master_local) {
+      *reinterpret_cast<float4*>(my_master + i) = wn;
+      if (p.shadow_mc) {
+        multimem_st_b32x2(p.shadow_mc + i, b0, b1);
+      } else {
+        for (int r = 0; r < p.world; ++r)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.shadow.p[r]) + i) = make_uint2(b0, b1);
+      }
+    } else if (p.master_mc) {
       multimem_st_f32x4(p.master_mc + i, wn);
       multimem_st_b32x2(p.shadow_mc + i, b0, b1);
     } else {
@@ -329,17 +340,23 @@ static int rs_adamw_ag_impl(const unsigned long long* grad_ptrs,
       fill_ptrs(p.shadow, shadow_ptrs, world) || fill_ptrs(p.pads, pad_ptrs, world) ||
       fill_ptrs(p.scratch, scratch_ptrs, world))
     return -2;
+  p.master_local = (sliced_moments & 2) ? 1 : 0;
   p.grad_mc = reinterpret_cast<float*>(grad_mc);
   p.master_mc = reinterpret_cast<float*>(master_mc);
   p.shadow_mc = reinterpret_cast<__nv_bfloat16*>(shadow_mc);
-  if (!(p.grad_mc && p.master_mc && p.shadow_mc)) {
+  if (!(p.grad_mc && (p.master_mc || p.master_local) && p.shadow_mc)) {
     p.grad_mc = nullptr;
     p.master_mc = nullptr;
     p.shadow_mc = nullptr;
   }
+  if (p.master_local) {
+    // master_ptrs[rank] is this rank's [n / world] slice: rebase it to the global element index
+    p.master_mc = nullptr;
+    p.master.p[rank] -= (unsigned long long)((n / world) * (long long)rank) * sizeof(float);
+  }
   // ZeRO-style moments: each rank stores only the n / world elements it updates; the kernel
   // indexes moments with the global element index, so rebase the pointers by the slice start.
-  const long long slice_lo = sliced_moments ? (n / world) * (long long)rank : 0;
+  const long long slice_lo = (sliced_moments & 1) ? (n / world) * (long long)rank : 0;
   p.exp_avg = exp_avg - slice_lo;
   p.exp_avg_sq = exp_avg_sq - slice_lo;
   p.n = n;
@@ -392,7 +409,9 @@ extern "C" int axb_rs_adamw_ag_sharded(const unsigned long long* grad_ptrs, cons
 
 // Two-pass form for optimizers with several parameter groups (see RsAdamwParams::mode): call with
 // mode 1 for every group after zeroing *gnorm_sq_out, then with mode 2 for every group. Each call
-// consumes three barrier epochs like the one-launch form. sliced_moments as in the _sharded entry.
+// consumes three barrier epochs like the one-launch form. sliced_moments: bit 0 = exp_avg / exp_avg_sq hold
+// only this rank's slice; bit 1 = the fp32 master does too (master_ptrs[rank] points at that slice, the
+// other entries are ignored) and only the bf16 copy is published.
 extern "C" int axb_rs_adamw_ag_pass(const unsigned long long* grad_ptrs, const unsigned long long* master_ptrs,
                                     const unsigned long long* shadow_ptrs, const unsigned long long* pad_ptrs,
                                     const unsigned long long* scratch_ptrs, void* grad_mc, void* master_mc,

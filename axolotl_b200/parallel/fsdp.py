@@ -42,8 +42,12 @@ class FSDPContext:
 
     NS = 3   # staging buffers: the GEMM's own operand plus a prefetch distance of two
 
-    def __init__(self, device, group, world, rank):
+    def __init__(self, device, group, world, rank, reshard_after_forward=True):
         self.device, self.group, self.world, self.rank = device, group, world, rank
+        # False: every weight gets a staging buffer of its own, so what the forward pass gathered is still
+        # there when the backward pass needs it (one gather per step instead of two, at the price of a full
+        # copy of the frozen weights); the copies are dropped when the step ends, as FSDP2 reshards them.
+        self.reshard_after_forward = bool(reshard_after_forward)
         self.arena = None
         self.staging = [None] * self.NS   # full-size buffers; weight i of the schedule lives in buffer i % NS
         self.holds = [None] * self.NS     # weight (ShardInfo) each buffer holds, in stream order
@@ -81,8 +85,12 @@ class FSDPContext:
         buf = SymmBuffer(total, torch.bfloat16, self.device, self.group, use_multicast=False)
         self.arena = buf
         max_full = max(m.weight.numel() for m in mods)
-        max_rows = max(m.weight.shape[0] for m in mods)
-        self.staging = [torch.empty(max_full, dtype=torch.bfloat16, device=self.device) for _ in range(self.NS)]
+        if self.reshard_after_forward:
+            self.staging = [torch.empty(max_full, dtype=torch.bfloat16, device=self.device) for _ in range(self.NS)]
+        else:
+            self.NS = len(mods)
+            self.staging = [torch.empty(m.weight.numel(), dtype=torch.bfloat16, device=self.device) for m in mods]
+            self.holds, self.pending = [None] * self.NS, [None] * self.NS
         off = 0
         for m in mods:
             N, K = m.weight.shape
@@ -136,6 +144,11 @@ class FSDPContext:
                 if self.holds[i % self.NS] is not nxt:
                     plans.append((nxt, i % self.NS))
         return self.staging[slot], plans
+
+    def end_of_step(self):
+        """``reshard_after_forward: false``: the gathered copies are released with the step."""
+        if not self.reshard_after_forward:
+            self.holds = [None] * self.NS
 
     def prefetch_ctas(self, nxt: ShardInfo, gemm_flops: float) -> int:
         """Enough gather CTAs to finish the next weight within this GEMM's run time."""

@@ -50,7 +50,8 @@ class ParallelRuntime:
             return
         from .fsdp import FSDPContext
 
-        self.fsdp = FSDPContext(self.device, self.shard_group, self.shard_size, self.mesh.coord("dp_shard"))
+        self.fsdp = FSDPContext(self.device, self.shard_group, self.shard_size, self.mesh.coord("dp_shard"),
+                                reshard_after_forward=getattr(self, "reshard_after_forward", True))
         self.fsdp.shard_model(model)
 
     def symmetric_alloc(self, numel, dtype):
@@ -97,7 +98,8 @@ class ParallelRuntime:
         pass
 
     def after_optimizer_step(self):
-        pass
+        if self.fsdp is not None:
+            self.fsdp.end_of_step()
 
     def barrier(self):
         if self.world_size > 1:
@@ -237,16 +239,24 @@ class ParallelRuntime:
             self._gnorm.zero_()
         for mode in passes:
             for g in groups:
-                gb, mb, sb = g["grad"]._axb_symm, g["master"]._axb_symm, g["shadow"]._axb_symm
+                gb, sb = g["grad"]._axb_symm, g["shadow"]._axb_symm
+                if g.get("master_local"):
+                    from .symm import _u64_array
+
+                    m_ptrs, m_mc = _u64_array([g["master"].data_ptr()] * self.reduce_size), None
+                    flags = sliced | 2
+                else:
+                    mb = g["master"]._axb_symm
+                    m_ptrs, m_mc, flags = mb.ptrs_c, mb.multicast_ptr or None, sliced
                 epoch = self.sync.next_epoch(0, 3)
                 rc = lib.axb_rs_adamw_ag_pass(
-                    gb.ptrs_c, mb.ptrs_c, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
-                    gb.multicast_ptr or None, mb.multicast_ptr or None, sb.multicast_ptr or None,
+                    gb.ptrs_c, m_ptrs, sb.ptrs_c, self.sync.buf.pad_ptrs_c, self._scratch._axb_symm.ptrs_c,
+                    gb.multicast_ptr or None, m_mc, sb.multicast_ptr or None,
                     g["exp_avg"].data_ptr(), g["exp_avg_sq"].data_ptr(), g["grad"].numel(), rank, self.reduce_size,
                     epoch, lr * g["lr_scale"], opt.betas[0], opt.betas[1], opt.eps, g["weight_decay"], bc1, bc2,
                     float(opt.max_grad_norm or 0.0), 1.0 / self.dp_size,
                     self._gnorm.data_ptr(), _lib.status_word(self.device).data_ptr(), WAIT_BUDGET_NS, _lib.stream_ptr(),
-                    sliced, mode)
+                    flags, mode)
                 _lib.check_rc(rc, "rs_adamw_ag")
         for g in opt.groups:   # inactive groups (LISA) keep their weights; their gradients are dropped
             if not g.get("active", True):
@@ -286,11 +296,13 @@ def create_runtime(*, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, b
     return ParallelRuntime(DeviceMesh(spec, dist.get_rank()), device, backend)
 
 
-def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, backend=None):
+def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, ep=1, backend=None,
+                   reshard_after_forward=True):
     """Creates the mesh + runtime for an already initialised process group and shards the model."""
     if tp > 1 or cp > 1 or ep > 1:
         rt = create_runtime(device=device, dp_shard=dp_shard, dp_replicate=dp_replicate, tp=tp, cp=cp, ep=ep,
                             backend=backend)
+        rt.reshard_after_forward = reshard_after_forward
         rt.apply_tp(model)
         rt.shard_model(model)
         return rt
@@ -302,6 +314,7 @@ def build_parallel(model, *, device, dp_shard=None, dp_replicate=1, tp=1, cp=1, 
         backend = os.environ.get("AXB_COMM", "fused" if device.type == "cuda" else "collective")
     mesh = DeviceMesh(spec, dist.get_rank())
     rt = ParallelRuntime(mesh, device, backend)
+    rt.reshard_after_forward = reshard_after_forward
     rt.setup_cp()
     rt.shard_model(model)
     return rt

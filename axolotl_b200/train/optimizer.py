@@ -84,16 +84,33 @@ class FlatAdamW:
                 offs.append(off)
                 off += (p.numel() + 7) // 8 * 8
             total = (off + pad_multiple - 1) // pad_multiple * pad_multiple
-            if alloc is not None:  # e.g. peer-mapped symmetric memory for the fused multi-GPU step
+            # ZeRO-style: when the fused multi-GPU step owns the update and no parameter of the group is
+            # fp32 (adapters keep fp32 masters as their storage), the fp32 master exists only for the slice
+            # this rank updates; the bf16 copy every rank computes with stays complete.
+            master_local = (moment_shard is not None and alloc is not None
+                            and all(p.dtype == torch.bfloat16 for _, p in params))
+            if master_local:
+                mr, mw = moment_shard
+                if total % (4 * mw):
+                    raise ValueError("sharded masters need pad_multiple to be a multiple of 4 * world")
+                master = torch.zeros(total // mw, dtype=torch.float32, device=dev)
+                grad, shadow = alloc(total, torch.float32), alloc(total, torch.bfloat16)
+            elif alloc is not None:  # e.g. peer-mapped symmetric memory for the fused multi-GPU step
                 master, grad, shadow = alloc(total, torch.float32), alloc(total, torch.float32), alloc(total, torch.bfloat16)
             else:
                 master = torch.zeros(total, dtype=torch.float32, device=dev)
                 grad = torch.zeros(total, dtype=torch.float32, device=dev)
                 shadow = torch.zeros(total, dtype=torch.bfloat16, device=dev)
             entries = []
+            m_off = (total // moment_shard[1]) * moment_shard[0] if master_local else 0
             for (n, p), o in zip(params, offs):
                 k = p.numel()
-                master[o:o + k].copy_(p.detach().reshape(-1).float())
+                if master_local:   # only the part of this parameter that falls into the local slice
+                    a, b = max(o, m_off), min(o + k, m_off + master.numel())
+                    if b > a:
+                        master[a - m_off:b - m_off].copy_(p.detach().reshape(-1)[a - o:b - o].float())
+                else:
+                    master[o:o + k].copy_(p.detach().reshape(-1).float())
                 shadow[o:o + k].copy_(p.detach().reshape(-1))
                 gview = grad[o:o + k].view(p.shape)
                 if p.dtype == torch.float32:
@@ -114,7 +131,7 @@ class FlatAdamW:
             else:
                 m_len, m_lo = total, 0
             self.groups.append({
-                "m_lo": m_lo, "m_len": m_len,
+                "m_lo": m_lo, "m_len": m_len, "master_local": master_local,
                 "tp_split": tp_split,
                 "name": g["name"], "lr_scale": g.get("lr_scale", 1.0), "weight_decay": g.get("weight_decay", 0.0),
                 "master": master, "grad": grad, "shadow": shadow, "entries": entries,
@@ -153,7 +170,7 @@ class FlatAdamW:
                     else:
                         thr = st.abs().float().kthvalue(max(1, int(prune_ratio * k))).values
                         st.mul_((st.abs() > thr).to(st.dtype))
-                if p.dtype == torch.float32:
+                if p.dtype == torch.float32 and not g.get("master_local"):
                     g["shadow"][o:o + k].copy_(g["master"][o:o + k])
 
     def bind_model_shadows(self, model):
@@ -241,7 +258,8 @@ class FlatAdamW:
             g["exp_avg"].copy_(s["exp_avg"])
             g["exp_avg_sq"].copy_(s["exp_avg_sq"])
             g["master"].copy_(s["master"])
-            g["shadow"].copy_(s["master"])
+            if not g.get("master_local"):   # a local master slice cannot rebuild the complete bf16 copy
+                g["shadow"].copy_(s["master"])
 
 
 class TorchOptimizerAdapter:

@@ -412,6 +412,8 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
                                   dp_replicate=cfg.get("dp_replicate_size") or 1, tp=cfg.get("tensor_parallel_size") or 1,
                                   cp=cfg.get("context_parallel_size") or 1, ep=cfg.get("expert_parallel_size") or 1)
         parallel.tp_max_tokens = cfg["micro_batch_size"] * cfg["sequence_len"]
+        raf = (cfg.get("fsdp_config") or {}).get("reshard_after_forward")
+        parallel.reshard_after_forward = True if raf is None else bool(raf)
         parallel.apply_tp(model)          # shards projections before adapters are created
     spec = setup_adapter(cfg, model)
     pm.call("post_model_load", cfg, model)

@@ -136,6 +136,9 @@ def main():
                          "expert + attention LoRA, expert parallelism over all ranks (4096-token rows, micro-batch 2); "
                          "tp70b: Llama-3-70B LoRA, TP=2 x FSDP=N/2, activation checkpointing; "
                          "cp64k: Llama-3-8B full fine-tune, context parallel over all ranks, one 65536-token row")
+    ap.add_argument("--reshard-after-forward", default="true", choices=["true", "false"],
+                    help="fsdp_config.reshard_after_forward of the headline run (false keeps gathered weights from the "
+                         "forward to the backward pass of a step)")
     args = ap.parse_args()
     if args.model == MODEL:
         args.model = {"moe": "qwen3-moe-30b-a3b", "tp70b": "llama-3-70b"}.get(args.config, MODEL)
@@ -201,7 +204,8 @@ def main():
         if world > 1:
             from axolotl_b200.parallel import build_parallel
 
-            parallel = build_parallel(model, dp_shard=world, device=dev)
+            parallel = build_parallel(model, dp_shard=world, device=dev,
+                                      reshard_after_forward=args.reshard_after_forward == "true")
     opt = FlatAdamW(build_param_groups(model.named_parameters(), weight_decay=0.0), lr=2e-4, max_grad_norm=1.0,
                     alloc=parallel.optimizer_alloc() if parallel is not None else None, pad_multiple=8 * max(world, 1),
                     moment_shard=parallel.moment_shard() if parallel is not None else None)
@@ -316,7 +320,7 @@ def main():
                        "seq_len": seq_len,
                        "parallelism": ({"moe": f"ep{world}", "tp70b": f"tp2 x fsdp{world // 2}", "cp64k": f"cp{world}"}
                                        .get(args.config, f"fsdp{world}")) if world > 1 else "single",
-                       "lora_r": 16, "lora_alpha": 32,
+                       "lora_r": 16, "lora_alpha": 32, "reshard_after_forward": args.reshard_after_forward == "true",
                        "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 2 if args.config == "moe" else 1,
                        "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2"},
             "clocks": clocks,

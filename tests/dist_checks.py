@@ -107,7 +107,7 @@ def check_fused_optimizer(dev, rank, world):
             print(f"fused rs+adamw+ag ok (multimem={'on' if use_mc else 'off'})")
 
 
-def check_training_equivalence(dev, rank, world, backend, replicate=False, multigroup=False):
+def check_training_equivalence(dev, rank, world, backend, replicate=False, multigroup=False, full=False):
     """A tiny LoRA model trained data-parallel must follow the single-process run on the
     concatenated batch (same seed, deterministic data)."""
     from axolotl_b200.data.collator import PackedCollator
@@ -128,8 +128,9 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False, multi
     def run(parallel_on):
         torch.manual_seed(0)
         model = CausalLM(cfg, dtype=dtype, device=dev).init_weights(0)
-        inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules=list(ALL_LINEAR)))
-        for _, m in model.fused_linears():   # make B non-zero so every gradient path is exercised
+        if not full:
+            inject_lora(model, LoraSpec(r=8, lora_alpha=16, target_modules=list(ALL_LINEAR)))
+        for _, m in (model.fused_linears() if not full else ()):   # make B non-zero so every gradient path is exercised
             with torch.no_grad():
                 g = torch.Generator(device="cpu").manual_seed(7)
                 m.lora_B.copy_((torch.randn(m.lora_B.shape, generator=g) * 0.02).to(dev) * (m.lora_B.new_ones(m.lora_B.shape)))
@@ -146,11 +147,15 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False, multi
         # multigroup: LoRA+ puts the B matrices into a group of their own; the clip factor must still
         # come from the norm over both groups (max_grad_norm is far below the actual norm, so a
         # per-group or missing clip changes the update)
-        groups = build_param_groups(model.named_parameters(), loraplus_lr_ratio=4.0 if multigroup else None)
+        groups = build_param_groups(model.named_parameters(), loraplus_lr_ratio=4.0 if multigroup else None,
+                                    weight_decay=0.01 if full else 0.0)
         opt = FlatAdamW(groups, lr=1e-3, max_grad_norm=0.05 if multigroup else 1.0,
                         alloc=par.optimizer_alloc() if par is not None else None, pad_multiple=8 * world,
                         moment_shard=par.moment_shard() if par is not None else None)
-        assert len(opt.groups) == (2 if multigroup else 1)
+        assert len(opt.groups) == (2 if (multigroup or full) else 1)
+        if full and parallel_on and backend == "fused":
+            # bf16 parameters: the fp32 master of a group exists only for the slice this rank updates
+            assert all(g["master_local"] and g["master"].numel() == g["grad"].numel() // world for g in opt.groups)
         opt.bind_model_shadows(model)
         if par is not None:
             par.attach_optimizer(opt)
@@ -163,7 +168,10 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False, multi
             else:
                 mb = [coll([[ds[(step * world + r) * 2 + j] for j in range(2)]]) for r in range(world)]
             losses.append(float(tr.training_step(mb).item()))
-        flat = torch.cat([g["master"][: sum(e[3] for e in g["entries"])].detach().float().cpu() for g in opt.groups])
+        if full:
+            flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
+        else:
+            flat = torch.cat([g["master"][: sum(e[3] for e in g["entries"])].detach().float().cpu() for g in opt.groups])
         return losses, flat
 
     l_par, w_par = run(True)
@@ -183,7 +191,7 @@ def check_training_equivalence(dev, rank, world, backend, replicate=False, multi
     assert all(float(x) == float(lst[0]) for x in lst), [float(x) for x in lst]
     if rank == 0:
         print(f"dp training equivalence ok ({backend}{', replicated' if replicate else ''}"
-              f"{', two groups' if multigroup else ''}): {mean_par} vs {l_ref}")
+              f"{', two groups' if multigroup else ''}{', full fine-tune' if full else ''}): {mean_par} vs {l_ref}")
 
 
 def check_tensor_parallel(dev, rank, world):
@@ -493,6 +501,7 @@ def main():
         want("load") and check_rank0_loading(dev, rank, world)
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
         want("dp") and check_training_equivalence(dev, rank, world, "collective", multigroup=True)
+        want("dp") and check_training_equivalence(dev, rank, world, "collective", full=True)
         want("ddp") and check_training_equivalence(dev, rank, world, "collective", replicate=True)
         "tpcp" in only and check_tp_cp(dev, rank, world)
         want("tp") and check_tensor_parallel(dev, rank, world)
@@ -506,6 +515,7 @@ def main():
         want("opt") and check_fused_optimizer(dev, rank, world)
         want("dp") and check_training_equivalence(dev, rank, world, "fused")
         want("dp") and check_training_equivalence(dev, rank, world, "fused", multigroup=True)
+        want("dp") and check_training_equivalence(dev, rank, world, "fused", full=True)
         want("dp") and check_training_equivalence(dev, rank, world, "collective")
         "tpcp" in only and check_tp_cp(dev, rank, world)
         want("ddp") and check_training_equivalence(dev, rank, world, "fused", replicate=True)

@@ -23,6 +23,7 @@ def test_data_parallel_gloo_world2():
     assert "rank-0 loading ok" in out
     assert "dp training equivalence ok (collective)" in out
     assert "dp training equivalence ok (collective, two groups)" in out
+    assert "dp training equivalence ok (collective, full fine-tune)" in out
     assert "dp training equivalence ok (collective, replicated)" in out
     for line in ("tensor parallel ok", "context parallel ok", "expert parallel ok"):
         assert line in out, out[-2000:]
@@ -43,6 +44,7 @@ def test_fused_multi_gpu():
     out = _run(2, [], 29612)
     for line in ("gather-gemm ok", "fused rs+adamw+ag ok (multimem=on)", "fused rs+adamw+ag ok (multimem=off)",
                  "dp training equivalence ok (fused)", "dp training equivalence ok (fused, two groups)",
+                 "dp training equivalence ok (fused, full fine-tune)",
                  "dp training equivalence ok (collective)", "dp training equivalence ok (fused, replicated)",
                  "tensor parallel ok", "context parallel ok", "expert parallel ok"):
         assert line in out, (line, out[-3000:])

@@ -407,6 +407,31 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
   }
 }
 
+// ---------------------------------------------------------------------------------- DoRA weight norm
+// norm[n] = sqrt(max(w2[n] + 2 s <W, BA>_n + s^2 |BA|_n^2, tiny)) with <W, BA>_n = sum_r WA[n,r] B[n,r] and
+// |BA|_n^2 = sum_{q,r} B[n,q] G[q,r] B[n,r], G = A A^T [R, R] (fp32). One thread per output row, G in shared
+// memory: the row-wise tail of the reference's fused DoRA-norm kernel (src/axolotl/kernels/dora.py:16-147)
+// after the skinny tcgen05 GEMM W A^T.
+__global__ void dora_norm_kernel(const float* __restrict__ WA, const float* __restrict__ B, const float* __restrict__ G,
+                                 const float* __restrict__ w2, float* __restrict__ norm, long long N, int R, float s) {
+  extern __shared__ float sG[];
+  for (int i = threadIdx.x; i < R * R; i += blockDim.x) sG[i] = G[i];
+  __syncthreads();
+  const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float* b = B + n * R;
+  const float* wa = WA + n * R;
+  float cross = 0.f, quad = 0.f;
+  for (int r = 0; r < R; ++r) {
+    const float br = b[r];
+    cross += wa[r] * br;
+    float acc = 0.f;
+    for (int q = 0; q < R; ++q) acc += b[q] * sG[q * R + r];
+    quad += acc * br;
+  }
+  norm[n] = sqrtf(fmaxf(w2[n] + 2.f * s * cross + s * s * quad, 1e-12f));
+}
+
 // ---------------------------------------------------------------------------------- embedding
 __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
                                      const long long* __restrict__ ids,
@@ -810,6 +835,14 @@ extern "C" int axb_entropy(const void* logits, float* ent, float* lse, long long
                                                          ld, inv_temp);
   return (int)cudaGetLastError();
 }
+extern "C" int axb_dora_norm(const float* WA, const float* B, const float* G, const float* w2, float* norm, long long N,
+                             int R, float s, void* stream) {
+  if (N <= 0) return 0;
+  if (R < 1 || R > 128) return -2;
+  dora_norm_kernel<<<(unsigned)((N + 127) / 128), 128, R * R * sizeof(float), ST(stream)>>>(WA, B, G, w2, norm, N, R, s);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int axb_glu_fwd(const void* gu, void* h, long long T, int I, int kind, float limit,
                            void* stream) {
   if (I % 8) return -2;

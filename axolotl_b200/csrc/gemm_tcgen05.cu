@@ -89,10 +89,8 @@ struct GemmParams {
   // lines, no per-thread row stores); 0 = every thread stores its own row (fp32 output, beta != 0,
   // unaligned C)
   int tma_store;
-  int dbg;
 };
 
-int g_dbg = 0;
 int g_epi_sleep_ns = 64, g_prod_sleep_ns = 0, g_pair_group_m = 0, g_pair_tma_store = 1, g_pair_band_mb = 32;
 
 // Row `lane` of a 32-row staging tile with 128-byte rows (64 bf16) and the 128-byte swizzle the
@@ -1094,7 +1092,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       decode_tile(tile, num_m, num_n, 1, m_blk, n_blk, split, p.group_m);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (p.epi == 2 && lane == 0 && !(p.dbg & 8)) {
+      if (p.epi == 2 && lane == 0) {
         // first gate|up chunk of this tile: requested now, it lands while the MMAs of the tile still run
         bulk_wait_group_read<0>();
         uint8_t* dst = my_epi + (q & 1) * 4096;
@@ -1189,7 +1187,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int col0 = n_blk * 256 + c * 32;
           const int s_cur = q & 1;
           uint8_t* tile = my_epi + s_cur * 4096;
-          if (c < 7 && lane == 0 && !(p.dbg & 8)) {
+          if (c < 7 && lane == 0) {
             // the other slot was last read by the stores of chunk q-1
             bulk_wait_group_read<0>();
             uint8_t* nxt = my_epi + (s_cur ^ 1) * 4096;
@@ -1201,18 +1199,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint32_t r[32];
           tmem_ld_32x32(t_addr + c * 32, r);
           tmem_ld_wait();
-          if (!(p.dbg & 8)) {
-            const bool got = (p.dbg & 1) ? mbar_wait_spin(&epi_bar[lane_group * 2 + s_cur], (uint32_t)((q >> 1) & 1), p.status, AXB_TIMEOUT_FULL)
-                                         : mbar_wait(&epi_bar[lane_group * 2 + s_cur], (uint32_t)((q >> 1) & 1), p.status, AXB_TIMEOUT_FULL);
-            if (!got) {
-              ok = false;
-              break;
-            }
+          if (!mbar_wait(&epi_bar[lane_group * 2 + s_cur], (uint32_t)((q >> 1) & 1), p.status, AXB_TIMEOUT_FULL)) {
+            ok = false;
+            break;
           }
           const int sw = (lane >> 1) & 3;
           uint8_t* grow = tile + lane * 64;
           uint8_t* urow = tile + 2048 + lane * 64;
-          if (!(p.dbg & 2))
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4* gp = reinterpret_cast<uint4*>(grow + ((j ^ sw) << 4));
@@ -1247,7 +1240,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (warp_rows && col0 < I && !(p.dbg & 4)) {
+            if (warp_rows && col0 < I) {
               tma_store_2d(&tmE0, tile, col0, warp_row0);
               tma_store_2d(&tmE1, tile + 2048, col0, warp_row0);
             }
@@ -1452,7 +1445,6 @@ static int pair_entry(const void* A, long long lda, int a_mn, const void* B, lon
   p.epi = epi; p.glu_kind = glu_kind; p.glu_limit = glu_limit; p.H = H; p.ldh = ldh;
   p.epi_sleep_ns = g_epi_sleep_ns; p.prod_sleep_ns = g_prod_sleep_ns;
   p.tma_store = tma_store;
-  p.dbg = g_dbg;
   // Rasterisation band: `group_m` rows of 256-row tiles sweep over N together, so their A rows are read
   // from DRAM once (they stay in L2) while B is streamed once per band. Taller bands mean fewer passes
   // over B; the band's A rows (group_m x 256 x K bf16) have to fit the L2 share given to them.
@@ -1505,7 +1497,6 @@ extern "C" int axb_gemm_bf16_pair_glu(const void* A, long long lda, int a_mn, co
 
 // Wait back-off of the CTA-pair kernel in nanoseconds (0 = busy spin): epilogue warps waiting for an
 // accumulator, TMA producer waiting for a free stage.
-extern "C" void axb_gemm_set_debug(int d) { g_dbg = d; }
 extern "C" void axb_gemm_set_backoff(int epi_sleep_ns, int prod_sleep_ns) {
   g_epi_sleep_ns = epi_sleep_ns;
   g_prod_sleep_ns = prod_sleep_ns;

@@ -195,12 +195,20 @@ class FusedLinear(nn.Module):
         A, B = self.lora_A.detach().float(), self.lora_B.detach().float()
         W = self._dense_weight()
         if W.is_cuda:
+            from ..ops import _lib
             from ..ops.gemm import gemm
 
             WA = gemm(W, self.lora_A16 if self.lora_A16 is not None else A.to(torch.bfloat16),
                       out_dtype=torch.float32)                          # [N, R] skinny tcgen05 GEMM
-        else:
-            WA = W.float() @ A.t()
+            A16 = self.lora_A16 if self.lora_A16 is not None else A.to(torch.bfloat16)
+            G = gemm(A16, A16, out_dtype=torch.float32, bn=64)          # A A^T [R, R]
+            norm = torch.empty(W.shape[0], dtype=torch.float32, device=W.device)
+            Bc = B.contiguous()
+            _lib.check_rc(_lib.cuda_lib().axb_dora_norm(WA.data_ptr(), Bc.data_ptr(), G.data_ptr(), self.dora_w2.data_ptr(),
+                                                        norm.data_ptr(), W.shape[0], Bc.shape[1], float(self.scaling),
+                                                        _lib.stream_ptr()), "dora_norm")
+            return norm
+        WA = W.float() @ A.t()
         cross = (WA * B).sum(1)
         quad = ((B @ (A @ A.t())) * B).sum(1)
         s = self.scaling
@@ -291,8 +299,9 @@ class FusedLinear(nn.Module):
 
     def forward(self, x):
         if self.qat is not None and self.training and self.weight.requires_grad:
-            from ..ops.fake_quant import ste_weight
+            from ..ops.fake_quant import fake_quantize_activation, ste_weight
 
+            x = fake_quantize_activation(x, self.qat.get("activation_dtype"))
             return linear(x, ste_weight(self.weight, self.qat.get("weight_dtype"), self.qat.get("group_size")), self.bias)
         if self.mora_M is not None and _ADAPTERS_ON:
             return linear(x, self.weight, self.bias) + self._mora_update(x)

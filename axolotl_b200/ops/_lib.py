@@ -30,7 +30,6 @@ _CUDA_SIGS = {
                                vp, vp],
     "axb_lora_bwd_dy": [vp, i64, vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, vp, i32, vp, vp],
     "axb_gemm_set_backoff": [i32, i32],
-    "axb_gemm_set_debug": [i32],
     "axb_gemm_set_pair_tuning": [i32, i32, i32],
     "axb_nvfp4_dequant": [vp, vp, vp, vp, i64, i64, vp],
     "axb_moe_dispatch_rows": [vp, vp, vp, vp, i64, i32, vp],
@@ -42,6 +41,8 @@ _CUDA_SIGS = {
     # A, lda, W, A2, lda2, W2, C, ldc, E, N, K, K2, trans_w, alpha, out_mode, bn, blk_expert, n_blocks, max_blocks, status, stream
     "axb_grouped_gemm": [vp, i64, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp, vp],
     # A, lda, B, ldb, C, ldc, c_batch, E, Mg, Ng, rows, alpha, out_mode, bn, seg_start, seg_rows, status, stream
+    # A, lda, qdata, scale, pts, A2, lda2, W2, C, ldc, E, Wn, Wk, K2, trans_w, alpha, out_mode, blk_expert, n_blocks, max_blocks, status, stream
+    "axb_grouped_gemm_w4a16": [vp, i64, vp, vp, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp, vp],
     "axb_grouped_gram": [vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i64, f32, i32, i32, vp, vp, vp, vp],
     "axb_ep_gather_rows": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, i64, vp],
     "axb_ep_scatter_add": [vp, i32, vp, vp, vp, vp, i64, i32, i64, vp],
@@ -52,6 +53,7 @@ _CUDA_SIGS = {
     "axb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_rope_qk": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp, vp, vp, f32, vp],
     "axb_rope_qk_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, f32, vp, vp, vp, vp, vp, vp],
+    "axb_dora_norm": [vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_glu_fwd": [vp, vp, i64, i32, i32, f32, vp],
     "axb_glu_bwd": [vp, vp, vp, i64, i32, i32, f32, vp],
     "axb_rmsnorm_gated_fwd": [vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],

@@ -39,7 +39,43 @@ def fake_quantize(w: torch.Tensor, weight_dtype: str = "int8", group_size: int |
         mag = (xg / scale).abs().clamp(max=6.0)
         idx = (mag[..., None] - grid).abs().argmin(-1)
         return (grid[idx] * torch.sign(xg) * scale).view(N, K).to(w.dtype)
+    if wd in ("mxfp8",):
+        g = 32
+        xg = x.view(N, K // g, g)
+        e = torch.floor(torch.log2(xg.abs().amax(-1, keepdim=True).clamp(min=2 ** -126))) - 8   # E8M0 scale, E4M3 payload
+        scale = torch.exp2(e)
+        return ((xg / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale).view(N, K).to(w.dtype)
     raise ValueError(f"unknown QAT weight dtype '{weight_dtype}'")
+
+
+class _FakeQuantAct(torch.autograd.Function):
+    """Dynamic per-token activation fake-quantisation with a straight-through gradient."""
+
+    @staticmethod
+    def forward(ctx, x, kind):
+        xf = x.float()
+        amax = xf.abs().amax(-1, keepdim=True).clamp(min=1e-12)
+        if kind == "int8":
+            scale = amax / 127.0
+            return (torch.clamp(torch.round(xf / scale), -128, 127) * scale).to(x.dtype)
+        scale = amax / 448.0
+        return ((xf / scale).to(torch.float8_e4m3fn).float() * scale).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def fake_quantize_activation(x: torch.Tensor, activation_dtype: str | None) -> torch.Tensor:
+    """``qat.activation_dtype``: int8 or fp8 (E4M3), one scale per token row; None leaves ``x`` alone."""
+    if not activation_dtype:
+        return x
+    ad = str(activation_dtype).lower()
+    if ad in ("int8",):
+        return _FakeQuantAct.apply(x, "int8")
+    if ad in ("fp8", "float8", "float8_e4m3fn"):
+        return _FakeQuantAct.apply(x, "fp8")
+    raise ValueError(f"unknown QAT activation dtype '{activation_dtype}'")
 
 
 def ste_weight(param: torch.Tensor, weight_dtype: str, group_size: int | None):

@@ -7,11 +7,14 @@ Per projection ``y = x W_e^T + s (x A_e^T) B_e^T``:
   backward  dt = dy B_e                              (grouped GEMM, transposed weights)
             dx = dy W_e + s * dt A_e                 (same, K-extension)
             dA_e = s * dt^T x,   dB_e = dy^T t       (grouped Gram kernels, fp32, accumulated)
-Frozen NVFP4 experts are dequantised (one batched kernel) into a bf16 scratch right before use, in
-the forward and again in the backward pass, so only the packed weights stay resident.
+Frozen NVFP4 experts are decoded INSIDE the grouped GEMM (csrc/grouped_w4a16.cu: packed tile by TMA,
+converter warps write the bf16 operand tile in shared memory), so the bf16 stack never exists in global
+memory; the dequantise-into-scratch route remains for shapes the kernel does not take.
 The segment layout is built on the device: no host synchronisation per layer.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -101,6 +104,43 @@ def grouped_gram(a, b, lay: GroupLayout, out, *, alpha=1.0, accumulate=False):
     return out
 
 
+# NVFP4 expert stacks are decoded inside the grouped GEMM (no bf16 copy of the weights is ever written);
+# AXB_W4A16=0 falls back to dequantise-then-GEMM, which gives bit-identical results.
+USE_W4A16 = os.environ.get("AXB_W4A16", "1") != "0"
+
+
+def w4a16_ok(q):
+    E, N, Kh = q["qdata"].shape
+    return USE_W4A16 and (Kh * 2) % 64 == 0 and N % 8 == 0 and q["qdata"].is_contiguous() and q["scale"].is_contiguous()
+
+
+def _pts32(q):
+    p = q.get("_pts32")
+    if p is None or p.device != q["qdata"].device:
+        p = q["_pts32"] = q["pts"].to(torch.float32).contiguous()
+    return p
+
+
+def grouped_gemm_w4a16(a, q, lay: GroupLayout, *, trans_w=False, a2=None, w2=None, alpha=1.0, out_dtype=torch.bfloat16):
+    """``grouped_gemm`` over NVFP4 weights ``q`` = {qdata uint8 [E, N, K/2], scale e4m3 [E, N, K/16], pts [E]}
+    with the 4-bit decode inside the kernel. ``trans_w``: the input-gradient product a . W (a [rows, N])."""
+    E, Wn, Kh = q["qdata"].shape
+    Wk = Kh * 2
+    assert a.shape[1] == (Wn if trans_w else Wk) and a.shape[0] == lay.max_rows and a.is_contiguous()
+    K2 = 0
+    if a2 is not None:
+        K2 = a2.shape[1]
+        assert a2.is_contiguous() and w2.is_contiguous()
+    out = torch.empty((lay.max_rows, Wk if trans_w else Wn), dtype=out_dtype, device=a.device)
+    _lib.check_rc(_lib.cuda_lib().axb_grouped_gemm_w4a16(
+        a.data_ptr(), a.stride(0), q["qdata"].data_ptr(), q["scale"].data_ptr(), _pts32(q).data_ptr(),
+        a2.data_ptr() if a2 is not None else None, a2.stride(0) if a2 is not None else 0,
+        w2.data_ptr() if w2 is not None else None, out.data_ptr(), out.stride(0), E, Wn, Wk, K2,
+        1 if trans_w else 0, float(alpha), 0 if out_dtype == torch.bfloat16 else 1, lay.blk_expert.data_ptr(),
+        lay.n_blocks.data_ptr(), lay.max_blocks, _lib.status_word().data_ptr(), _lib.stream_ptr()), "grouped_gemm_w4a16")
+    return out
+
+
 # Dequantised expert stacks may be kept from the forward to the backward pass of the same layer
 # while they fit a memory budget (half of the memory that is free when the first one is cached);
 # beyond the budget the backward pass dequantises again. 180 GB of HBM usually holds all of them.
@@ -170,34 +210,48 @@ class _GroupedProj(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, experts, which, lay, A, B, scaling):
-        W = _expert_weights(experts, which, keep=bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[4]),
-                            active=lay.seg_rows)
-        E = W.shape[0]
+        q = experts.nvfp4[which] if experts.nvfp4 is not None else None
+        w4 = q is not None and w4a16_ok(q)
+        if w4:
+            E = q["qdata"].shape[0]
+            mm = lambda a, **kw: grouped_gemm_w4a16(a, q, lay, **kw)
+        else:
+            W = _expert_weights(experts, which, keep=bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[4]),
+                                active=lay.seg_rows)
+            E = W.shape[0]
+            mm = lambda a, **kw: grouped_gemm(a, W, lay, **kw)
         if A is not None:
             A16, Bt16 = _adapter_operands(experts, which, A, B, E)
             t = grouped_gemm(x, A16, lay, alpha=scaling)
-            y = grouped_gemm(x, W, lay, a2=t, w2=Bt16)
+            y = mm(x, a2=t, w2=Bt16)
             ctx.save_for_backward(x, t, A, B)
         else:
-            y = grouped_gemm(x, W, lay)
+            y = mm(x)
             ctx.save_for_backward(x)
         ctx.experts, ctx.which, ctx.lay, ctx.scaling, ctx.has_lora = experts, which, lay, scaling, A is not None
         ctx.train_w = experts.nvfp4 is None and W.requires_grad
+        ctx.w4 = w4
         return y
 
     @staticmethod
     def backward(ctx, dy):
         experts, which, lay = ctx.experts, ctx.which, ctx.lay
         dy = dy.contiguous()
-        W = _expert_weights(experts, which, take=True, active=lay.seg_rows)
-        E = W.shape[0]
+        if ctx.w4:
+            q = experts.nvfp4[which]
+            E, W = q["qdata"].shape[0], None
+            mm = lambda a, **kw: grouped_gemm_w4a16(a, q, lay, trans_w=True, **kw)
+        else:
+            W = _expert_weights(experts, which, take=True, active=lay.seg_rows)
+            E = W.shape[0]
+            mm = lambda a, **kw: grouped_gemm(a, W, lay, trans_w=True, **kw)
         dA = dB = None
         if ctx.has_lora:
             x, t, A, B = ctx.saved_tensors
             r = A.shape[0] // E
             A16, Bt16 = _adapter_operands(experts, which, A, B, E)
             dt = grouped_gemm(dy, Bt16, lay, trans_w=True, alpha=ctx.scaling)    # s * dy B_e   [rows, r]
-            dx = grouped_gemm(dy, W, lay, trans_w=True, a2=dt, w2=A16)
+            dx = mm(dy, a2=dt, w2=A16)
             gA = _grad_buffer(A)
             if gA is not None:      # accumulate straight into the optimizer's flat gradient view
                 grouped_gram(dt, x, lay, gA.view(E, r, -1), accumulate=True)
@@ -213,7 +267,7 @@ class _GroupedProj(torch.autograd.Function):
                 dB = dB_full.to(B.dtype)
         else:
             (x,) = ctx.saved_tensors
-            dx = grouped_gemm(dy, W, lay, trans_w=True)
+            dx = mm(dy)
         if ctx.train_w:
             gW = grouped_gram(dy, x, lay, torch.empty(W.shape, dtype=torch.float32, device=x.device))
             buf = _grad_buffer(W)

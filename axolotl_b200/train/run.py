@@ -559,7 +559,19 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
                 m.qat = q
         else:
             trainer.callbacks.append(_QATStart())
-        LOG.info("QAT: %d projections fake-quantised to %s (group %s)", len(mods), q.get("weight_dtype"), q.get("group_size"))
+        if q.get("quantize_embedding"):
+            # the embedding table is rounded to the weight grid in place at every optimizer step end
+            from ..ops.fake_quant import fake_quantize
+
+            class _QATEmbedding(Callback):
+                def on_step_end(self, trainer, logs):
+                    if trainer.global_step >= start and model.embed_tokens.requires_grad:
+                        with torch.no_grad():
+                            model.embed_tokens.copy_(fake_quantize(model.embed_tokens, q.get("weight_dtype"), q.get("group_size")))
+
+            trainer.callbacks.append(_QATEmbedding())
+        LOG.info("QAT: %d projections fake-quantised to %s (group %s, activations %s)", len(mods), q.get("weight_dtype"),
+                 q.get("group_size"), q.get("activation_dtype"))
     if cfg.get("neftune_noise_alpha"):
         model.neftune_noise_alpha = float(cfg["neftune_noise_alpha"])
 

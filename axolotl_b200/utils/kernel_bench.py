@@ -227,8 +227,42 @@ def bench_lora_skinny(rows):
         gb = lambda elems, ms: elems * 2 / 1e6 / ms   # GB/s
         rows.append(f"lora {name} r={R}: x@A^T {t_xa * 1e3:.0f} us ({gb(T * K, t_xa) / hbm:.2f}) | dy@B {t_t * 1e3:.0f} us "
                     f"({gb(T * N, t_t) / hbm:.2f}) | dA=t^T x {t_dA * 1e3:.0f} us ({gb(T * K, t_dA) / hbm:.2f}, splits {sp_a}) | "
-                    f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b}){split_note}  "
+                    f"dB=dy^T xa {t_dB * 1e3:.0f} us ({gb(T * N, t_dB) / hbm:.2f}, splits {sp_b}) | ONE pass over dy for "
+                    f"both (incl. memset + cast): {t_fused * 1e3:.0f} us ({gb(T * N, t_fused) / hbm:.2f}){split_note}  "
                     f"[fractions of {how} HBM copy rate]")
+
+
+def bench_w4a16(rows):
+    """NVFP4 expert projections at Qwen3-30B-A3B shapes (128 experts, hidden 2048, expert width 768, 8192 tokens
+    x top-8 = 512 rows per expert): decode inside the grouped GEMM against dequantise-then-GEMM."""
+    from axolotl_b200.ops.grouped import GroupLayout, _lib as L, grouped_gemm, grouped_gemm_w4a16
+    tf, bw, src = _peaks()
+    E, H, I, per = 128, 2048, 768, 512
+    dev = "cuda"
+    lay = GroupLayout(torch.full((E,), per, device=dev), E * per)
+    for name, N, K in (("gate_up", 2 * I, H), ("down", H, I)):
+        q = {"qdata": torch.randint(0, 256, (E, N, K // 2), dtype=torch.uint8, device=dev),
+             "scale": torch.randint(40, 120, (E, N, K // 16), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+             "pts": torch.full((E,), 1e-3, device=dev)}
+        Wd = torch.empty(E, N, K, dtype=torch.bfloat16, device=dev)
+        pts = q["pts"].float()
+
+        def deq():
+            L.check_rc(L.cuda_lib().axb_nvfp4_dequant_batched(q["qdata"].data_ptr(), q["scale"].data_ptr(), pts.data_ptr(),
+                                                              Wd.data_ptr(), E, N, K, None, L.stream_ptr()), "dequant")
+        x = torch.randn(lay.max_rows, K, device=dev).bfloat16()
+        dy = torch.randn(lay.max_rows, N, device=dev).bfloat16()
+        deq()
+        fl = 2.0 * E * per * N * K
+        t_deq = time_cuda(deq)
+        t_f16 = time_cuda(lambda: grouped_gemm(x, Wd, lay))
+        t_f4 = time_cuda(lambda: grouped_gemm_w4a16(x, q, lay))
+        t_b16 = time_cuda(lambda: grouped_gemm(dy, Wd, lay, trans_w=True))
+        t_b4 = time_cuda(lambda: grouped_gemm_w4a16(dy, q, lay, trans_w=True))
+        rows.append(f"w4a16 {name} [E={E}, N={N}, K={K}] x {per} rows/expert: dequant {t_deq*1e3:.0f} us | fwd bf16-stack "
+                    f"{t_f16*1e3:.0f} us, in-kernel decode {t_f4*1e3:.0f} us ({fl/t_f4/1e9/tf:.2f} of {src} bf16 peak) | "
+                    f"dX bf16-stack {t_b16*1e3:.0f} us, in-kernel decode {t_b4*1e3:.0f} us ({fl/t_b4/1e9/tf:.2f}) | "
+                    f"fwd+dX: {2*t_deq*1e3 + t_f16*1e3 + t_b16*1e3:.0f} us (dequantise twice + GEMMs) -> {t_f4*1e3 + t_b4*1e3:.0f} us")
 
 
 def bench_decode(rows):
@@ -403,6 +437,8 @@ def main(argv):
         bench_attn(rows)
     if what in ("decode",):
         bench_decode(rows)
+    if what in ("w4a16",):
+        bench_w4a16(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

@@ -423,6 +423,47 @@ def test_grouped_gemm_modes(counts):
         assert _rel_err(gB[e], dy[sl].float().t() @ t[sl].float()) < 1e-2, e
 
 
+@pytest.mark.parametrize("counts,N,K", [([130, 0, 5, 300, 128, 1, 0, 77], 328, 192), ([256] * 4, 256, 512),
+                                         ([0, 0, 9], 72, 64)])
+def test_grouped_w4a16_equals_dequantise_then_gemm(counts, N, K):
+    """NVFP4 decode inside the grouped GEMM: same bits as the dequantised bf16 stack fed to the bf16 kernel,
+    forward (with the LoRA K-extension) and input gradient."""
+    from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gemm_w4a16, w4a16_ok
+    from axolotl_b200.ops.nvfp4 import dequantize_nvfp4, quantize_nvfp4
+    torch.manual_seed(33)
+    E, r, dev = len(counts), 16, _dev()
+    M = sum(counts)
+    lay = GroupLayout(torch.tensor(counts, device=dev), M)
+    W = torch.randn(E, N, K) * 0.05
+    W[1] *= 40.0                                        # a different per-expert scale
+    qd, sc, pts = quantize_nvfp4(W)
+    q = {"qdata": qd.to(dev), "scale": sc.to(dev), "pts": pts.to(dev)}
+    assert w4a16_ok(q)
+    Wd = dequantize_nvfp4(q["qdata"], q["scale"], q["pts"])            # bf16 [E, N, K] on the device
+    x = lay.pad((torch.randn(M, K) * 0.5).bfloat16().to(dev))
+    t = lay.pad((torch.randn(M, r) * 0.5).bfloat16().to(dev))
+    Bt = (torch.randn(E, N, r) * 0.05).bfloat16().to(dev)
+    A16 = (torch.randn(E, r, K) * 0.05).bfloat16().to(dev)
+    dy = lay.pad((torch.randn(M, N) * 0.5).bfloat16().to(dev))
+    y_ref = grouped_gemm(x, Wd, lay, a2=t, w2=Bt, alpha=0.5)
+    y = grouped_gemm_w4a16(x, q, lay, a2=t, w2=Bt, alpha=0.5)
+    y0_ref, y0 = grouped_gemm(x, Wd, lay), grouped_gemm_w4a16(x, q, lay, out_dtype=torch.float32)
+    dx_ref = grouped_gemm(dy, Wd, lay, trans_w=True, a2=t, w2=A16)
+    dx = grouped_gemm_w4a16(dy, q, lay, trans_w=True, a2=t, w2=A16)
+    dx0_ref, dx0 = grouped_gemm(dy, Wd, lay, trans_w=True), grouped_gemm_w4a16(dy, q, lay, trans_w=True)
+    _check_status()
+    for got, ref in ((y, y_ref), (dx, dx_ref), (dx0, dx0_ref)):
+        assert torch.equal(lay.unpad(got), lay.unpad(ref))
+    assert torch.equal(lay.unpad(y0).bfloat16(), lay.unpad(y0_ref))
+    # and against plain fp32 arithmetic on the decoded weights
+    s0 = 0
+    for e, n in enumerate(counts):
+        if n:
+            xs = lay.unpad(x)[s0:s0 + n].float()
+            assert _rel_err(lay.unpad(y0)[s0:s0 + n], xs @ Wd[e].float().t()) < 1e-2
+        s0 += n
+
+
 def test_moe_block_nvfp4_experts_match_dequantised_reference():
     from axolotl_b200.models.config import preset
     from axolotl_b200.models.moe import SparseMoE
@@ -892,3 +933,21 @@ def test_lora_linear_backward_fused_dy_matches_two_pass():
     _check_status()
     for a, b in zip(g1, g0):
         assert _rel_err(a, b) < 1e-2
+
+
+def test_dora_weight_norm_kernel():
+    """||W + s B A|| per row without forming B A: skinny GEMMs + the row-wise kernel, against fp32 torch."""
+    from axolotl_b200.models.layers import FusedLinear
+    torch.manual_seed(41)
+    dev = _dev()
+    lin = FusedLinear(512, [384, 128], ["gate_proj", "up_proj"], dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        lin.weight.normal_(0, 0.05)
+    lin.weight.requires_grad_(False)
+    lin.add_lora(16, 32, init_b_zero=False, use_dora=True)
+    got = lin.dora_weight_norm()
+    _check_status()
+    W, A, B = lin.weight.float(), lin.lora_A16.float(), lin.lora_B.float()
+    ref = (W + lin.scaling * (B @ A)).norm(dim=1)
+    assert _rel_err(got, ref) < 5e-3
+    assert got.dtype == torch.float32 and got.shape == (512,)

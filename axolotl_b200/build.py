@@ -45,9 +45,9 @@ def _stamp(src: Path, flags: list[str]) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, verbose: bool, extra: list[str]) -> Path:
-    obj = OBJ / (src.stem + ".o")
-    stamp_file = OBJ / (src.stem + ".stamp")
+def _compile_one(src: Path, verbose: bool, extra: list[str], tag: str = "") -> Path:
+    obj = OBJ / (src.stem + tag + ".o")
+    stamp_file = OBJ / (src.stem + tag + ".stamp")
     flags = NVCC_FLAGS + extra
     stamp = _stamp(src, flags)
     if obj.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
@@ -62,6 +62,24 @@ def _compile_one(src: Path, verbose: bool, extra: list[str]) -> Path:
         print(res.stderr, flush=True)
     stamp_file.write_text(stamp)
     return obj
+
+
+def _build_checked(cu_sources, verbose: bool) -> Path:
+    """The bounds-check variant (``libaxb200_checked.so``, loaded instead of the regular library when
+    ``AXB_BOUNDS_CHECK=1``): same sources with ``-DAXB_BOUNDS_CHECK`` and relocatable device code, so that one
+    device record is shared by all kernels."""
+    extra = ["-DAXB_BOUNDS_CHECK", "-rdc=true"]
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(cu_sources)))) as ex:
+        objs = list(ex.map(lambda s: _compile_one(s, verbose, extra, tag="_checked"), cu_sources))
+    out = LIB / "libaxb200_checked.so"
+    newest = max(o.stat().st_mtime for o in objs)
+    if not out.exists() or out.stat().st_mtime < newest:
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-o", str(out),
+               *map(str, objs), "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link of the bounds-check library failed:\n{res.stdout}\n{res.stderr}")
+    return out
 
 
 def build(verbose: bool = False, ptxas_info: bool = False, force: bool = False) -> dict[str, Path]:
@@ -82,6 +100,7 @@ def build(verbose: bool = False, ptxas_info: bool = False, force: bool = False) 
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    _build_checked(cu_sources, verbose)
     host_out = LIB / "libaxb200_host.so"
     cpp_sources = sorted(CSRC.glob("*.cpp"))
     if cpp_sources:
@@ -92,7 +111,7 @@ def build(verbose: bool = False, ptxas_info: bool = False, force: bool = False) 
             res = subprocess.run(cmd, capture_output=True, text=True)
             if res.returncode != 0:
                 raise RuntimeError(f"host link failed:\n{res.stdout}\n{res.stderr}")
-    return {"cuda": out, "host": host_out}
+    return {"cuda": out, "checked": LIB / "libaxb200_checked.so", "host": host_out}
 
 
 if __name__ == "__main__":

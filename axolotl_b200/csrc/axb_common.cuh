@@ -24,6 +24,36 @@ enum AxbStatus : int {
   AXB_TIMEOUT_GENERIC = 7,
 };
 
+// Bounds-check build (-DAXB_BOUNDS_CHECK, linked as libaxb200_checked.so): every data-dependent index that a
+// kernel reads from device memory (token ids, labels, expert ids, document tiles) is compared with its
+// limit before the access; the first violation is recorded (site, index, limit) in a device record that
+// the host reads through axb_bounds_fetch, and the access is skipped. The regular build compiles the
+// checks away.
+enum AxbBoundsSite : int {
+  AXB_SITE_EMBED_ID = 1,
+  AXB_SITE_EMBED_GRAD_ID = 2,
+  AXB_SITE_CE_LABEL = 3,
+  AXB_SITE_GROUPED_EXPERT = 4,
+  AXB_SITE_W4A16_EXPERT = 5,
+  AXB_SITE_ATTN_TILE = 6,
+  AXB_SITE_DISPATCH_TOKEN = 7,
+};
+#ifdef AXB_BOUNDS_CHECK
+extern __device__ unsigned long long axb_bounds_record[4];   // site, index, limit, count (bounds_check.cu)
+AXB_DEVICE bool axb_index_ok(int site, long long idx, long long limit) {
+  if (idx >= 0 && idx < limit) return true;
+  atomicAdd(&axb_bounds_record[3], 1ull);
+  if (atomicCAS(&axb_bounds_record[0], 0ull, (unsigned long long)site) == 0ull) {
+    axb_bounds_record[1] = (unsigned long long)idx;
+    axb_bounds_record[2] = (unsigned long long)limit;
+  }
+  return false;
+}
+#define AXB_INDEX_OK(site, idx, limit) axb_index_ok((site), (long long)(idx), (long long)(limit))
+#else
+#define AXB_INDEX_OK(site, idx, limit) true
+#endif
+
 // wait budget in nanoseconds of %globaltimer (2 s: far above any legitimate wait)
 #ifndef AXB_WAIT_BUDGET_NS
 #define AXB_WAIT_BUDGET_NS 2000000000ull

@@ -443,6 +443,7 @@ __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
     const long long t = v / (H / 8);
     const int c = (int)(v % (H / 8)) * 8;
     long long id = ids[t];
+    if (c == 0) (void)AXB_INDEX_OK(AXB_SITE_EMBED_ID, id, vocab);
     if (id < 0 || id >= vocab) id = 0;
     *reinterpret_cast<uint4*>(out + t * H + c) =
         *reinterpret_cast<const uint4*>(table + id * H + c);
@@ -457,6 +458,7 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
     const long long t = i / H;
     const int c = (int)(i % H);
     const long long id = ids[t];
+    if (c == 0) (void)AXB_INDEX_OK(AXB_SITE_EMBED_GRAD_ID, id, vocab);
     if (id < 0 || id >= vocab) continue;
     atomicAdd(dtable + id * H + c, __bfloat162float(dout[i]));
   }
@@ -468,14 +470,23 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
 // and overwrites the row with d loss_total / d z = (softmax(z) - onehot) * grad_scale, so the
 // caller can feed the buffer straight into the dX / dW GEMMs. lse[r] is also returned.
 constexpr int CE_T = 512;
+// CAP: the logits are soft-capped first, z' = cap * tanh(z / cap) (Gemma 2 final_logit_softcapping); the
+// gradient written back is with respect to the raw z.
+template <bool CAP>
 __global__ void __launch_bounds__(CE_T)
     ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                       float* __restrict__ loss, float* __restrict__ lse_out, int V,
-                      long long ld, float grad_scale, long long ignore_index, int write_grad) {
+                      long long ld, float grad_scale, long long ignore_index, int write_grad, float cap) {
+  const float inv_cap = CAP ? 1.f / cap : 0.f;
+  auto eff = [&](float v) -> float {
+    if constexpr (CAP) return cap * tanhf(v * inv_cap);
+    else return v;
+  };
   __shared__ float sh[32];
   const long long r = blockIdx.x;
   __nv_bfloat16* z = logits + r * ld;
   const long long label = labels[r];
+  if (threadIdx.x == 0 && label != ignore_index) (void)AXB_INDEX_OK(AXB_SITE_CE_LABEL, label, V);
   const bool ignored = (label == ignore_index) || label < 0 || label >= V;
   if (ignored && !lse_out) {
     if (threadIdx.x == 0) loss[r] = 0.f;
@@ -494,23 +505,23 @@ __global__ void __launch_bounds__(CE_T)
     float f[8];
     load8(z + i, f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);   // tanh is increasing: cap the maximum once below
   }
   for (int i = v8 + threadIdx.x; i < V; i += CE_T) mx = fmaxf(mx, __bfloat162float(z[i]));
-  mx = block_max<CE_T>(mx, sh);
+  mx = eff(block_max<CE_T>(mx, sh));
   float se = 0.f;
   for (int i = threadIdx.x * 8; i < v8; i += CE_T * 8) {
     float f[8];
     load8(z + i, f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+    for (int j = 0; j < 8; ++j) se += __expf(eff(f[j]) - mx);
   }
-  for (int i = v8 + threadIdx.x; i < V; i += CE_T) se += __expf(__bfloat162float(z[i]) - mx);
+  for (int i = v8 + threadIdx.x; i < V; i += CE_T) se += __expf(eff(__bfloat162float(z[i])) - mx);
   se = block_sum<CE_T>(se, sh);
   const float lse = mx + logf(se);
   if (threadIdx.x == 0) {
     if (lse_out) lse_out[r] = lse;
-    loss[r] = ignored ? 0.f : lse - __bfloat162float(z[label]);
+    loss[r] = ignored ? 0.f : lse - eff(__bfloat162float(z[label]));
   }
   if (!write_grad) return;
   __syncthreads();
@@ -520,15 +531,19 @@ __global__ void __launch_bounds__(CE_T)
     load8(z + i, f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float pr = __expf(f[j] - lse);
+      const float ze = eff(f[j]);
+      float pr = __expf(ze - lse);
       if (i + j == label) pr -= 1.f;
+      if constexpr (CAP) pr *= 1.f - (ze * inv_cap) * (ze * inv_cap);   // d z' / d z = 1 - tanh^2
       f[j] = pr * gs;
     }
     store8(z + i, f);
   }
   for (int i = v8 + threadIdx.x; i < V; i += CE_T) {
-    float pr = __expf(__bfloat162float(z[i]) - lse);
+    const float ze = eff(__bfloat162float(z[i]));
+    float pr = __expf(ze - lse);
     if (i == label) pr -= 1.f;
+    if constexpr (CAP) pr *= 1.f - (ze * inv_cap) * (ze * inv_cap);
     z[i] = __float2bfloat16(pr * gs);
   }
 }
@@ -879,8 +894,18 @@ extern "C" int axb_ce_fwd_bwd(void* logits, const long long* labels, float* loss
                               long long ignore_index, int write_grad, void* stream) {
   if (rows <= 0) return 0;
   if (ld % 8) return -2;
-  ce_fwd_bwd_kernel<<<(unsigned)rows, CE_T, 0, ST(stream)>>>(
-      (__nv_bfloat16*)logits, labels, loss, lse, V, ld, grad_scale, ignore_index, write_grad);
+  ce_fwd_bwd_kernel<false><<<(unsigned)rows, CE_T, 0, ST(stream)>>>(
+      (__nv_bfloat16*)logits, labels, loss, lse, V, ld, grad_scale, ignore_index, write_grad, 0.f);
+  return (int)cudaGetLastError();
+}
+// the same with soft-capped logits, z' = softcap * tanh(z / softcap)
+extern "C" int axb_ce_fwd_bwd_softcap(void* logits, const long long* labels, float* loss, float* lse,
+                                      long long rows, int V, long long ld, float grad_scale,
+                                      long long ignore_index, int write_grad, float softcap, void* stream) {
+  if (rows <= 0) return 0;
+  if (ld % 8 || !(softcap > 0.f)) return -2;
+  ce_fwd_bwd_kernel<true><<<(unsigned)rows, CE_T, 0, ST(stream)>>>(
+      (__nv_bfloat16*)logits, labels, loss, lse, V, ld, grad_scale, ignore_index, write_grad, softcap);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_sumsq(const float* g, long long n, float* out, void* stream) {

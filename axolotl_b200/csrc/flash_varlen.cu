@@ -28,6 +28,7 @@ struct AttnParams {
   long long out_ld;
   float* lse2;  // [Hq, T]  log2-domain logsumexp of the scaled scores
   long long T;
+  long long kv_rows;  // rows of the k / v buffer (the whole token stream under context parallelism)
   float sl2;  // softmax_scale * log2(e)
   int* status;
   // backward only
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kv_head = head / (p.Hq / p.Hk);
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, q0 = ti.z;
+  if (!AXB_INDEX_OK(AXB_SITE_ATTN_TILE, (long long)doc_start + doc_len - 1, p.kv_rows) || !AXB_INDEX_OK(AXB_SITE_ATTN_TILE, q0, doc_len)) return;
   const bool bidir = ti.w & 1;  // every token of the document sees the whole document
   const int win = bidir ? 0 : (ti.w >> 1);  // sliding window: row q sees kv rows (q - win, q]; 0 = unlimited
   const int kv_end = bidir ? doc_len : min(q0 + 128, doc_len);
@@ -432,6 +434,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int head0 = kv_head * group_all + part * group;  // first of them
   const int4 ti = p.tiles[tile_id];
   const int doc_start = ti.x, doc_len = ti.y, kv0 = ti.z;
+  if (!AXB_INDEX_OK(AXB_SITE_ATTN_TILE, (long long)doc_start + doc_len - 1, p.kv_rows) || !AXB_INDEX_OK(AXB_SITE_ATTN_TILE, kv0, doc_len)) return;
   const bool bidir = ti.w & 1;
   // 64-row q tiles at or below the diagonal (all of the document's when it is bidirectional)
   // that intersect this rank's q rows
@@ -855,6 +858,7 @@ int flash_fwd_impl(const AttnGeom& g, int Hq, int Hk, int D, int q_col0, int k_c
   p.out_ld = out_ld;
   p.lse2 = lse2;
   p.T = g.q_rows;
+  p.kv_rows = g.kv_rows;
   p.q_row_off = g.q_row_off;
   p.q_rows = (int)g.q_rows;
   p.sl2 = softmax_scale * 1.4426950408889634f;
@@ -897,6 +901,7 @@ int flash_bwd_impl(const AttnGeom& g, const void* dout, const void* out, long lo
   p.out_ld = (long long)Hq * D;  // leading dimension of dq_acc
   p.lse2 = const_cast<float*>(lse2);
   p.T = T;
+  p.kv_rows = g.kv_rows;
   p.q_row_off = g.q_row_off;
   p.q_rows = (int)T;
   p.sl2 = softmax_scale * 1.4426950408889634f;

@@ -86,6 +86,7 @@ __device__ __forceinline__ bool decode(const GParams& p, int tile, int n_blocks,
     t.nk_main = (p.K + BK - 1) / BK;
     t.nk_ext = (p.K2 + BK - 1) / BK;
     t.zb = p.blk_expert[blk];
+    if (!AXB_INDEX_OK(AXB_SITE_GROUPED_EXPERT, t.zb, p.E)) return false;   // checked build: stop this CTA's tile loop
     t.m_lim = t.m0 + BM;
     t.c_off = 0;
   }

@@ -8,12 +8,15 @@
 // one fp32 scale per expert; W2 / A2 (the LoRA K-extension) are bf16. Rows are expert-sorted and padded to
 // 128-row blocks (blk_expert[b] = expert of block b), exactly as in grouped_gemm.cu.
 //
-// Per k block the TMA producer brings the bf16 A tile and the PACKED weight tile (4 KB instead of 16 KB)
-// into shared memory; four converter warps expand the nibbles through a register lookup table, multiply
-// by the block scale and write the bf16 tile in the 128-byte-swizzled layout tcgen05.mma reads; the MMA
-// warp accumulates in TMEM; four epilogue warps store the result. The decoded values are bit-identical to
-// nvfp4_dequant_kernel's, so the product equals dequantise-then-GEMM exactly, at a quarter of the weight
-// traffic and without the bf16 scratch. This is the role the Marlin W4A16 grouped kernel and the
+// Per k block the TMA producer brings the bf16 A tiles and the PACKED weight tile (4 KB instead of 16 KB)
+// into shared memory; four converter warps expand the nibbles and write the bf16 tile in the
+// 128-byte-swizzled layout tcgen05.mma reads; the MMA warp accumulates in TMEM; four epilogue warps store
+// the result. One decoded weight tile feeds TWO 128-row blocks of the same expert (256 rows per pass), which
+// halves the decode work per FLOP. The decode builds, per 16-value scale group, the eight products
+// |e2m1| x scale as bf16 (one fp32 multiply for 1.5 x scale; the power-of-two multiples are exponent
+// offsets of the same two roundings) and picks them with byte permutes, about 2.6 instructions per value.
+// The decoded values are bit-identical to nvfp4_dequant_kernel's, so the product equals
+// dequantise-then-GEMM exactly, at a quarter of the weight traffic and without the bf16 scratch. This is the role the Marlin W4A16 grouped kernel and the
 // dequantise-into-a-chunk path play in the reference
 // (src/axolotl/integrations/kernels/libs/scattermoe_lora/marlin_w4a16/_csrc/libtorch_stable/moe/marlin_moe_wna16/marlin_template.h:251,
 //  src/axolotl/integrations/kernels/libs/scattermoe_lora/grouped_train.py:446-596).
@@ -25,41 +28,73 @@ constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int BK = 64;
 constexpr int W4_THREADS = 320;   // TMA, MMA, 4 epilogue warps, 4 converter warps
-constexpr int W4_STAGES = 5;
-constexpr int A_BYTES = BM * BK * 2;
+constexpr int W4_STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // one 128-row A tile; a stage holds two
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int RAW_BYTES = 4096;   // FWD: 128 rows x 32 bytes; DX: 64 rows x 64 bytes
-constexpr int W4_SMEM = W4_STAGES * (A_BYTES + B_BYTES + RAW_BYTES) + 1024 + 256;
+constexpr int W4_SMEM = W4_STAGES * (2 * A_BYTES + B_BYTES + RAW_BYTES) + 1024 + 256;
 
-constexpr unsigned long long kE2M1Lo = 0x3fc03f803f000000ull;  // bf16 bits of 1.5, 1.0, 0.5, 0.0
-constexpr unsigned long long kE2M1Hi = 0x40c0408040404000ull;  // 6.0, 4.0, 3.0, 2.0
-
-AXB_DEVICE float e2m1_to_float(uint32_t code) {
-  const unsigned long long tbl = (code & 4) ? kE2M1Hi : kE2M1Lo;
-  const uint32_t bits = (uint32_t)(tbl >> ((code & 3) * 16)) & 0xFFFFu;
-  return __uint_as_float((bits | ((code & 8) << 12)) << 16);
-}
+// E4M3 byte -> fp32, branch free: the 7 magnitude bits placed at the top of an fp32 mantissa / the bottom of
+// its exponent give value x 2^-120 (subnormal inputs included), and 0x7F / 0xFF are NaN. Same value as
+// the table-free decode of nvfp4_dequant_kernel.
 AXB_DEVICE float e4m3_to_float(uint32_t v) {
-  const uint32_t sign = (v >> 7) & 1, exp = (v >> 3) & 0xF, man = v & 7;
-  float f;
-  if (exp == 0) f = ldexpf((float)man, -9);
-  else if (exp == 15 && man == 7) f = __int_as_float(0x7fc00000);
-  else f = __uint_as_float(((exp + 120u) << 23) | (man << 20));
-  return sign ? -f : f;
+  const uint32_t mag = v & 0x7Fu;
+  float f = __uint_as_float(mag << 20) * 1.329227995784916e36f;   // 2^120
+  f = mag == 0x7Fu ? __int_as_float(0x7fc00000) : f;
+  return __uint_as_float(__float_as_uint(f) | ((v & 0x80u) << 24));
 }
-// 8 packed codes (one 32-bit word, low nibble first) times one scale -> 8 bf16 in a 16-byte chunk
-AXB_DEVICE uint4 decode8(uint32_t w, float s) {
+AXB_DEVICE uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// The eight bf16 products |code| x s of one scale group, split into low-byte and high-byte tables for prmt.
+// |code| = 0, .5, 1, 1.5, 2, 3, 4, 6: bf16(fp32(m x s)) for m a power of two is bf16(s) with the exponent
+// moved, and 3 s, 6 s are 1.5 s with the exponent moved, so two roundings give all eight (same bits as
+// rounding each fp32 product) as long as no exponent leaves the normal range; otherwise multiply them out.
+struct Lut {
+  uint32_t L0, L1, H0, H1;
+};
+AXB_DEVICE Lut make_lut(float s) {
+  const uint32_t P23 = pack_bf16x2(s, 1.5f * s);   // low half: 1 x s, high half: 1.5 x s
+  uint32_t P01, P45, P67;
+  if (((P23 >> 7) & 0x1FFu) - 2u < 0xFAu) {        // s positive, exponent in [2, 251]
+    P01 = (P23 << 16) - 0x00800000u;               // (0, 0.5 s)
+    P45 = P23 + 0x00800080u;                       // (2 s, 3 s)
+    P67 = P23 + 0x01000100u;                       // (4 s, 6 s)
+  } else {
+    P01 = pack_bf16x2(0.f * s, 0.5f * s);
+    P45 = pack_bf16x2(2.f * s, 3.f * s);
+    P67 = pack_bf16x2(4.f * s, 6.f * s);
+  }
+  Lut t;
+  t.L0 = prmt(P01, P23, 0x6420);
+  t.H0 = prmt(P01, P23, 0x7531);
+  t.L1 = prmt(P45, P67, 0x6420);
+  t.H1 = prmt(P45, P67, 0x7531);
+  return t;
+}
+// 8 packed codes (one 32-bit word, low nibble first) -> 8 bf16 in a 16-byte chunk
+AXB_DEVICE uint4 decode8(uint32_t w, const Lut& t) {
+  const uint32_t sel = w & 0x77777777u, selh = sel >> 16;
+  const uint32_t sg = w & 0x88888888u, sg4 = sg << 4;   // sign of odd codes / even codes at bit 7 of byte i/2
+  uint32_t lo = prmt(t.L0, t.L1, sel), hi = prmt(t.H0, t.H1, sel);
+  hi ^= prmt(sg4, sg, 0x5140) & 0x80808080u;
   uint4 o;
-  o.x = pack_bf16x2(e2m1_to_float(w & 0xF) * s, e2m1_to_float((w >> 4) & 0xF) * s);
-  o.y = pack_bf16x2(e2m1_to_float((w >> 8) & 0xF) * s, e2m1_to_float((w >> 12) & 0xF) * s);
-  o.z = pack_bf16x2(e2m1_to_float((w >> 16) & 0xF) * s, e2m1_to_float((w >> 20) & 0xF) * s);
-  o.w = pack_bf16x2(e2m1_to_float((w >> 24) & 0xF) * s, e2m1_to_float(w >> 28) * s);
+  o.x = prmt(lo, hi, 0x5140);
+  o.y = prmt(lo, hi, 0x7362);
+  lo = prmt(t.L0, t.L1, selh);
+  hi = prmt(t.H0, t.H1, selh);
+  hi ^= prmt(sg4, sg, 0x7362) & 0x80808080u;
+  o.z = prmt(lo, hi, 0x5140);
+  o.w = prmt(lo, hi, 0x7362);
   return o;
 }
 
 struct W4Params {
   int N, K, K2;   // FWD: N output columns, K contraction. DX: N = output columns (the weight's K), K = contraction (the weight's N)
   int Wn, Wk;     // logical weight shape [Wn, Wk] per expert
+  int E;
   void* C;
   long long ldc;
   float alpha;
@@ -91,6 +126,34 @@ int make_tmap_u8_3d(CUtensorMap* out, const void* base, uint64_t batch, uint64_t
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// One pass = one decoded weight tile stream against one or two 128-row blocks of the same expert.
+struct Pass {
+  int blk, two, e, n0;
+};
+// Tiles are (pair of consecutive row blocks, n block). Sub-pass 0 takes block 2p (and 2p+1 when it belongs to
+// the same expert); sub-pass 1 exists only when block 2p+1 belongs to another expert.
+AXB_DEVICE bool get_pass(const int* blk_expert, int n_blocks, int num_n, int E, int tile, int sub, Pass& ps) {
+  const int pair = tile / num_n;
+  const int b0 = 2 * pair, b1 = b0 + 1;
+  int e0 = blk_expert[b0];
+  const bool has1 = b1 < n_blocks;
+  int e1 = has1 ? blk_expert[b1] : -1;
+  if (!AXB_INDEX_OK(AXB_SITE_W4A16_EXPERT, e0, E)) e0 = 0;              // checked build: recorded, then a valid expert
+  if (has1 && !AXB_INDEX_OK(AXB_SITE_W4A16_EXPERT, e1, E)) e1 = 0;
+  ps.n0 = (tile - pair * num_n) * BN;
+  if (sub == 0) {
+    ps.blk = b0;
+    ps.two = has1 && e1 == e0;
+    ps.e = e0;
+    return true;
+  }
+  if (!has1 || e1 == e0) return false;
+  ps.blk = b1;
+  ps.two = 0;
+  ps.e = e1;
+  return true;
+}
+
 template <bool DX>
 __global__ void __launch_bounds__(W4_THREADS, 1)
     grouped_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ,
@@ -98,11 +161,11 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
                          const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + W4_STAGES * A_BYTES;
+  uint8_t* sA = smem;                                   // [stage][2][128 x 64]
+  uint8_t* sB = smem + W4_STAGES * 2 * A_BYTES;
   uint8_t* sRaw = sB + W4_STAGES * B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + W4_STAGES * RAW_BYTES);
-  uint64_t* raw_full = bars;                    // TMA landed: A tile + packed weights (or the bf16 LoRA tile)
+  uint64_t* raw_full = bars;                    // TMA landed: A tiles + packed weights (or the bf16 LoRA tile)
   uint64_t* full_bar = bars + W4_STAGES;        // converters done: the bf16 B tile is in place (4 arrivals)
   uint64_t* empty_bar = bars + 2 * W4_STAGES;   // MMAs retired
   uint64_t* tfull_bar = bars + 3 * W4_STAGES;
@@ -114,7 +177,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
   const int num_n = (p.N + BN - 1) / BN;
   const int nk_main = (p.K + BK - 1) / BK, nk_ext = (p.K2 + BK - 1) / BK;
   const int nk = nk_main + nk_ext;
-  const int total = n_blocks * num_n;
+  const int total = ((n_blocks + 1) / 2) * num_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < W4_STAGES; ++s) {
@@ -131,7 +194,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
     tma_prefetch_desc(&tmQ);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, 512);   // two accumulator slots of 2 x 128 columns
     tmem_relinquish();
   }
   tc_fence_before();
@@ -145,34 +208,38 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const int blk = tile / num_n, n0 = (tile - blk * num_n) * BN, e = p.blk_expert[blk];
-        for (int kb = 0; kb < nk; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, AXB_TIMEOUT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          const bool ext = kb >= nk_main;
-          uint8_t* a_dst = sA + stage * A_BYTES;
-          if (!ext) {
-            mbar_expect_tx(&raw_full[stage], A_BYTES + RAW_BYTES);
-            tma_load_2d(a_dst, &tmA, &raw_full[stage], kb * BK, blk * BM);
-            if (!DX) tma_load_3d(sRaw + stage * RAW_BYTES, &tmQ, &raw_full[stage], kb * (BK / 2), n0, e);       // [128 n, 32 B of k]
-            else tma_load_3d(sRaw + stage * RAW_BYTES, &tmQ, &raw_full[stage], n0 / 2, kb * BK, e);             // [64 n, 64 B of k]
-          } else {
-            mbar_expect_tx(&raw_full[stage], A_BYTES + B_BYTES);
-            const int k = (kb - nk_main) * BK;
-            uint8_t* b_dst = sB + stage * B_BYTES;
-            tma_load_2d(a_dst, &tmA2, &raw_full[stage], k, blk * BM);
-            if (!DX) {
-              tma_load_3d(b_dst, &tmB2, &raw_full[stage], k, n0, e);
-            } else {
-              tma_load_3d(b_dst, &tmB2, &raw_full[stage], n0, k, e);
-              tma_load_3d(b_dst + 8192, &tmB2, &raw_full[stage], n0 + 64, k, e);
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          Pass ps;
+          if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
+          const uint32_t a_bytes = ps.two ? 2 * A_BYTES : A_BYTES;
+          for (int kb = 0; kb < nk; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, AXB_TIMEOUT_EMPTY)) {
+              ok = false;
+              break;
             }
-          }
-          if (++stage == W4_STAGES) {
-            stage = 0;
-            phase ^= 1;
+            const bool ext = kb >= nk_main;
+            uint8_t* a_dst = sA + stage * 2 * A_BYTES;
+            const CUtensorMap* ma = ext ? &tmA2 : &tmA;
+            const int ka = ext ? (kb - nk_main) * BK : kb * BK;
+            mbar_expect_tx(&raw_full[stage], a_bytes + (ext ? B_BYTES : RAW_BYTES));
+            tma_load_2d(a_dst, ma, &raw_full[stage], ka, ps.blk * BM);
+            if (ps.two) tma_load_2d(a_dst + A_BYTES, ma, &raw_full[stage], ka, (ps.blk + 1) * BM);
+            if (!ext) {
+              if (!DX) tma_load_3d(sRaw + stage * RAW_BYTES, &tmQ, &raw_full[stage], kb * (BK / 2), ps.n0, ps.e);   // [128 n, 32 B of k]
+              else tma_load_3d(sRaw + stage * RAW_BYTES, &tmQ, &raw_full[stage], ps.n0 / 2, kb * BK, ps.e);         // [64 n, 64 B of k]
+            } else {
+              uint8_t* b_dst = sB + stage * B_BYTES;
+              if (!DX) {
+                tma_load_3d(b_dst, &tmB2, &raw_full[stage], ka, ps.n0, ps.e);
+              } else {
+                tma_load_3d(b_dst, &tmB2, &raw_full[stage], ps.n0, ka, ps.e);
+                tma_load_3d(b_dst + 8192, &tmB2, &raw_full[stage], ps.n0 + 64, ka, ps.e);
+              }
+            }
+            if (++stage == W4_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
           }
         }
       }
@@ -183,96 +250,107 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
       int stage = 0, it = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
-        const int acc = it & 1;
-        if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1, p.status, AXB_TIMEOUT_TMEM_EMPTY)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < nk; ++kb) {
-          // raw_full: the TMA writes (A tile, LoRA B tile) observed by this thread itself; full_bar: the decoded tile
-          if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL) ||
-              !mbar_wait(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          Pass ps;
+          if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
+          const int acc = it & 1;
+          if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1, p.status, AXB_TIMEOUT_TMEM_EMPTY)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES), b_addr = smem_u32(sB + stage * B_BYTES);
+          const uint32_t d_tmem = tmem_base + acc * 2 * BN;
+          for (int kb = 0; kb < nk; ++kb) {
+            // raw_full: the TMA writes (A tiles, LoRA B tile) observed by this thread itself; full_bar: the decoded tile
+            if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL) ||
+                !mbar_wait(&full_bar[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(sA + stage * 2 * A_BYTES), b_addr = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = make_smem_desc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t db = DX ? make_smem_desc_sw128(b_addr + kk * 2048, 8192, 1024)
-                                   : make_smem_desc_sw128(b_addr + kk * 32, 16, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              const uint64_t db = DX ? make_smem_desc_sw128(b_addr + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+              const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
+              umma_f16(d_tmem, make_smem_desc_sw128(a_addr + kk * 32, 16, 1024), db, idesc, accum);
+              if (ps.two) umma_f16(d_tmem + BN, make_smem_desc_sw128(a_addr + A_BYTES + kk * 32, 16, 1024), db, idesc, accum);
+            }
+            umma_commit(&empty_bar[stage]);
+            if (++stage == W4_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
           }
-          umma_commit(&empty_bar[stage]);
-          if (++stage == W4_STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (!ok) break;
+          umma_commit(&tfull_bar[acc]);
+          ++it;
         }
-        if (!ok) break;
-        umma_commit(&tfull_bar[acc]);
       }
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------ converters: packed tile -> bf16 B tile
+    // Thread ct reads 32 packed bytes (64 codes, 4 scale groups) at raw + ct * 32.
+    //   FWD: raw tile [128 n][32 B]: weight row n0 + ct, k block kb  -> K-major row ct of the B tile.
+    //   DX : raw tile [64 wn][64 B]: weight row kb * 64 + ct / 2, columns n0 + 64 * (ct & 1) .. + 63
+    //        -> MN-major chunk (ct & 1), row ct / 2.
     const int ct = threadIdx.x - 192;   // 0..127
+    const long long sc_row_bytes = p.Wk / 16;
+    const int r = DX ? (ct >> 1) : ct, half = DX ? (ct & 1) : 0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-      const int blk = tile / num_n, n0 = (tile - blk * num_n) * BN, e = p.blk_expert[blk];
-      const float g = p.pts[e];
-      const long long sc_row_bytes = p.Wk / 16;
-      // FWD: thread = weight row n0 + ct, the 64 k values of the block (4 scale bytes).
-      // DX : thread = contraction row (weight row) kb * 64 + ct % 64, half ct / 64 of the 128 output columns
-      //      (64 k values starting at n0 + 64 * half, 4 scale bytes).
-      for (int kb = 0; kb < nk; ++kb) {
-        if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
-          ok = false;
-          break;
-        }
-        if (kb < nk_main) {
-          const uint8_t* raw = sRaw + stage * RAW_BYTES;
-          uint8_t* bt = sB + stage * B_BYTES;
-          uint32_t sc4 = 0;
-          uint4 w0, w1;
-          uint8_t* dst_row;
-          int sw;
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        Pass ps;
+        if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
+        const float g = p.pts[ps.e];
+        const uint8_t* sc_base = p.scale + (long long)ps.e * p.Wn * sc_row_bytes;
+        auto load_scales = [&](int kb) -> uint32_t {
+          if (kb >= nk_main) return 0u;
           if (!DX) {
-            const int n = n0 + ct;
-            if (n < p.Wn) sc4 = *reinterpret_cast<const uint32_t*>(p.scale + ((long long)e * p.Wn + n) * sc_row_bytes + kb * 4);
-            w0 = *reinterpret_cast<const uint4*>(raw + ct * 32);
-            w1 = *reinterpret_cast<const uint4*>(raw + ct * 32 + 16);
-            dst_row = bt + ct * 128;       // K-major tile: row = n, 128 bytes = 64 k values
-            sw = ct & 7;
-          } else {
-            const int r = ct & 63, half = ct >> 6;
-            const int wn = kb * BK + r, k0 = n0 + half * 64;
-            if (wn < p.Wn && k0 < p.Wk)
-              sc4 = *reinterpret_cast<const uint32_t*>(p.scale + ((long long)e * p.Wn + wn) * sc_row_bytes + k0 / 16);
-            w0 = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32);
-            w1 = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32 + 16);
-            dst_row = bt + half * 8192 + r * 128;   // MN-major tile: chunk of 64 columns, row = contraction index
-            sw = r & 7;
+            const int n = ps.n0 + ct;
+            return n < p.Wn ? __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)n * sc_row_bytes + kb * 4)) : 0u;
           }
-          const float s0 = e4m3_to_float(sc4 & 0xFF) * g, s1 = e4m3_to_float((sc4 >> 8) & 0xFF) * g;
-          const float s2 = e4m3_to_float((sc4 >> 16) & 0xFF) * g, s3 = e4m3_to_float(sc4 >> 24) * g;
-          *reinterpret_cast<uint4*>(dst_row + ((0 ^ sw) << 4)) = decode8(w0.x, s0);
-          *reinterpret_cast<uint4*>(dst_row + ((1 ^ sw) << 4)) = decode8(w0.y, s0);
-          *reinterpret_cast<uint4*>(dst_row + ((2 ^ sw) << 4)) = decode8(w0.z, s1);
-          *reinterpret_cast<uint4*>(dst_row + ((3 ^ sw) << 4)) = decode8(w0.w, s1);
-          *reinterpret_cast<uint4*>(dst_row + ((4 ^ sw) << 4)) = decode8(w1.x, s2);
-          *reinterpret_cast<uint4*>(dst_row + ((5 ^ sw) << 4)) = decode8(w1.y, s2);
-          *reinterpret_cast<uint4*>(dst_row + ((6 ^ sw) << 4)) = decode8(w1.z, s3);
-          *reinterpret_cast<uint4*>(dst_row + ((7 ^ sw) << 4)) = decode8(w1.w, s3);
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_bar[stage]);
-        if (++stage == W4_STAGES) {
-          stage = 0;
-          phase ^= 1;
+          const int wn = kb * BK + r, k0 = ps.n0 + half * 64;
+          return (wn < p.Wn && k0 < p.Wk) ? __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)wn * sc_row_bytes + k0 / 16)) : 0u;
+        };
+        uint32_t sc_next = load_scales(0);
+        for (int kb = 0; kb < nk; ++kb) {
+          const uint32_t sc4 = sc_next;
+          sc_next = load_scales(kb + 1);
+          if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          if (kb < nk_main) {
+            const uint8_t* raw = sRaw + stage * RAW_BYTES + ct * 32;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(raw);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(raw + 16);
+            uint8_t* dst_row = sB + stage * B_BYTES + half * 8192 + r * 128;
+            const int sw = r & 7;
+            Lut t = make_lut(e4m3_to_float(sc4 & 0xFF) * g);
+            *reinterpret_cast<uint4*>(dst_row + ((0 ^ sw) << 4)) = decode8(w0.x, t);
+            *reinterpret_cast<uint4*>(dst_row + ((1 ^ sw) << 4)) = decode8(w0.y, t);
+            t = make_lut(e4m3_to_float((sc4 >> 8) & 0xFF) * g);
+            *reinterpret_cast<uint4*>(dst_row + ((2 ^ sw) << 4)) = decode8(w0.z, t);
+            *reinterpret_cast<uint4*>(dst_row + ((3 ^ sw) << 4)) = decode8(w0.w, t);
+            t = make_lut(e4m3_to_float((sc4 >> 16) & 0xFF) * g);
+            *reinterpret_cast<uint4*>(dst_row + ((4 ^ sw) << 4)) = decode8(w1.x, t);
+            *reinterpret_cast<uint4*>(dst_row + ((5 ^ sw) << 4)) = decode8(w1.y, t);
+            t = make_lut(e4m3_to_float(sc4 >> 24) * g);
+            *reinterpret_cast<uint4*>(dst_row + ((6 ^ sw) << 4)) = decode8(w1.z, t);
+            *reinterpret_cast<uint4*>(dst_row + ((7 ^ sw) << 4)) = decode8(w1.w, t);
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[stage]);
+          if (++stage == W4_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
       }
     }
@@ -280,44 +358,54 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
     // ------------------------------------------------------------ epilogue warps 2..5
     const int lane_group = warp & 3;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
-      const int blk = tile / num_n, n0 = (tile - blk * num_n) * BN;
-      const int acc = it & 1;
-      if (!mbar_wait(&tfull_bar[acc], (it >> 1) & 1, p.status, AXB_TIMEOUT_TMEM_FULL)) break;
-      tc_fence_after();
-      const long long row = (long long)blk * BM + lane_group * 32 + lane;
-      const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) continue;
-        const bool full_chunk = col0 + 32 <= p.N;
-        if (p.out_mode == 0) {
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
-          if (full_chunk && (p.ldc & 7) == 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * p.alpha, __uint_as_float(r[q * 8 + 1]) * p.alpha);
-              o.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha);
-              o.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha);
-              o.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha);
-              *reinterpret_cast<uint4*>(crow + q * 8) = o;
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]) * p.alpha);
-          }
-        } else {
-          float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
-          for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = __uint_as_float(r[j]) * p.alpha;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        Pass ps;
+        if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
+        const int acc = it & 1;
+        if (!mbar_wait(&tfull_bar[acc], (it >> 1) & 1, p.status, AXB_TIMEOUT_TMEM_FULL)) {
+          ok = false;
+          break;
         }
+        tc_fence_after();
+        for (int h = 0; h <= ps.two; ++h) {
+          const long long row = (long long)(ps.blk + h) * BM + lane_group * 32 + lane;
+          const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * 2 * BN + h * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_addr + c * 32, r);
+            tmem_ld_wait();
+            const int col0 = ps.n0 + c * 32;
+            if (col0 >= p.N) continue;
+            const bool full_chunk = col0 + 32 <= p.N;
+            if (p.out_mode == 0) {
+              __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+              if (full_chunk && (p.ldc & 7) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * p.alpha, __uint_as_float(r[q * 8 + 1]) * p.alpha);
+                  o.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha);
+                  o.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha);
+                  o.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha);
+                  *reinterpret_cast<uint4*>(crow + q * 8) = o;
+                }
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]) * p.alpha);
+              }
+            } else {
+              float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) crow[j] = __uint_as_float(r[j]) * p.alpha;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        ++it;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
   }
 
@@ -325,7 +413,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -357,14 +445,14 @@ extern "C" int axb_grouped_gemm_w4a16(const void* A, long long lda, const void* 
   }
   if (rc) return -4;
   W4Params p = {};
-  p.N = N; p.K = Ka; p.K2 = K2 > 0 ? K2 : 0; p.Wn = Wn; p.Wk = Wk;
+  p.N = N; p.K = Ka; p.K2 = K2 > 0 ? K2 : 0; p.Wn = Wn; p.Wk = Wk; p.E = E;
   p.C = C; p.ldc = ldc; p.alpha = alpha; p.out_mode = out_mode;
   p.scale = reinterpret_cast<const uint8_t*>(scale); p.pts = pts;
   p.blk_expert = blk_expert; p.n_blocks = n_blocks; p.status = status;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int max_tiles = max_blocks * ((N + BN - 1) / BN);
+  const int max_tiles = ((max_blocks + 1) / 2) * ((N + BN - 1) / BN);
   int grid = sms < max_tiles ? sms : max_tiles;
   if (grid < 1) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

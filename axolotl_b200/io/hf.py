@@ -39,6 +39,13 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     filled = set()
     expert_parts = {}
     for name, t in named_tensors:
+        # multimodal wrappers (Gemma 3): the language model's tensors carry a prefix, the vision parts are not ours
+        if name.startswith("language_model."):
+            name = name[len("language_model."):]
+        elif name.startswith("model.language_model."):
+            name = "model." + name[len("model.language_model."):]
+        if name.startswith(("vision_tower.", "multi_modal_projector.", "model.vision_tower.", "model.multi_modal_projector.")):
+            continue
         if name == "model.embed_tokens.weight":
             model.embed_tokens.copy_(t)
             filled.add("embed_tokens")
@@ -55,7 +62,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             r0, r1 = fl.row_range(sub)
             (fl.weight if kind == "weight" else fl.bias)[r0:r1].copy_(t)
             filled.add(f"{parent}.{sub}.{kind}")
-        elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm)\.weight$", name)):
+        elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.weight$", name)):
             mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.(q_norm|k_norm)\.weight$", name)):
@@ -199,7 +206,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 sd[f"model.{parent}.{sub}.weight"] = m.weight.detach()[r0:r1]
                 if m.bias is not None:
                     sd[f"model.{parent}.{sub}.bias"] = m.bias.detach()[r0:r1]
-        elif name.endswith(("input_layernorm", "post_attention_layernorm", "q_norm", "k_norm")):
+        elif name.endswith(("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm",
+                            "q_norm", "k_norm")):
             sd[f"model.{name}.weight"] = m.weight.detach()
         elif isinstance(m, Experts):
             if m.nvfp4 is not None:

@@ -13,7 +13,9 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any
 
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
+                         "gemma", "gemma2", "gemma3_text")
+GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
 @dataclass
@@ -60,12 +62,36 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
+        if self.model_type == "gemma3_text":
+            self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         d = dict(d)
         mt = d.get("model_type", "llama")
+        if mt == "gemma3" and isinstance(d.get("text_config"), dict):   # the multimodal wrapper: its language model
+            d = dict(d["text_config"], model_type="gemma3_text")
+            mt = "gemma3_text"
+        if mt in GEMMA_TYPES:
+            d.setdefault("tie_word_embeddings", True)
+            d["hidden_act"] = d.get("hidden_activation") or "gelu_pytorch_tanh"   # HF forces the tanh form
+            d.setdefault("rms_norm_eps", 1e-6)
+            if mt == "gemma3_text":
+                d.setdefault("head_dim", 256)
+                d.setdefault("query_pre_attn_scalar", 256)
+                d.setdefault("sliding_window", 4096)
+                rp = d.get("rope_parameters")
+                if isinstance(rp, dict) and "full_attention" in rp:        # transformers v5: one rope set per layer type
+                    loc = rp.get("sliding_attention") or {}
+                    d.setdefault("rope_local_base_freq", loc.get("rope_theta", 10000.0))
+                    d["rope_parameters"] = rp["full_attention"]
+            if mt == "gemma2":
+                d.setdefault("head_dim", 256)
+                d.setdefault("query_pre_attn_scalar", 256)
+                d.setdefault("sliding_window", 4096)
+                d.setdefault("attn_logit_softcapping", 50.0)
+                d.setdefault("final_logit_softcapping", 30.0)
         if mt not in SUPPORTED_MODEL_TYPES:
             raise ValueError(
                 f"model_type '{mt}' is not supported by axolotl_b200 (supported: {SUPPORTED_MODEL_TYPES})")
@@ -121,11 +147,42 @@ class ModelConfig:
     def multiplier(self, name: str) -> float:
         """Granite's scalar multipliers (embedding / attention / residual / logits_scaling); 1 elsewhere
         (``attention_multiplier`` falls back to 1/sqrt(head_dim))."""
+        if self.model_type in GEMMA_TYPES:
+            if name == "embedding_multiplier":      # sqrt(hidden) rounded to the activation dtype, as HF does
+                import torch
+
+                return float(torch.tensor(self.hidden_size ** 0.5, dtype=torch.bfloat16))
+            if name == "attention_multiplier":
+                qpas = (self.extra or {}).get("query_pre_attn_scalar")
+                return float(qpas) ** -0.5 if qpas and self.model_type != "gemma" else 1.0 / math.sqrt(self.head_dim)
+            return 1.0
         if self.model_type != "granite":
             return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         default = 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         v = (self.extra or {}).get(name)
         return float(v) if v is not None else default
+
+    def norm_offset(self) -> float:
+        """Gemma stores RMSNorm weights as ``w`` and applies ``1 + w``."""
+        return 1.0 if self.model_type in GEMMA_TYPES else 0.0
+
+    def sandwich_norms(self) -> bool:
+        """Gemma 2 / 3 normalise the output of the attention and MLP branches too (four norms per layer)."""
+        return self.model_type in ("gemma2", "gemma3_text")
+
+    def attn_softcap(self) -> float:
+        v = (self.extra or {}).get("attn_logit_softcapping") if self.model_type == "gemma2" else None
+        return float(v) if v else 0.0
+
+    def final_softcap(self) -> float:
+        v = (self.extra or {}).get("final_logit_softcapping") if self.model_type in ("gemma2", "gemma3_text") else None
+        return float(v) if v else 0.0
+
+    def local_rope_theta(self, idx: int) -> float | None:
+        """Gemma 3: sliding-window layers rotate with their own base frequency and no scaling."""
+        if self.model_type != "gemma3_text" or not self.sliding_window(idx):
+            return None
+        return float((self.extra or {}).get("rope_local_base_freq", 10000.0))
 
     def sliding_window(self, idx: int | None = None) -> int:
         """Causal sliding window in tokens of layer ``idx`` (0 = full attention). Mistral / Phi-3 /
@@ -139,6 +196,16 @@ class ModelConfig:
             return 0
         if self.model_type in ("mistral", "phi3", "mixtral"):
             return int(w)
+        if self.model_type in ("gemma2", "gemma3_text"):
+            if idx is None:
+                return int(w)
+            types = ex.get("layer_types")
+            if types:
+                return int(w) if types[idx] == "sliding_attention" else 0
+            if self.model_type == "gemma2":
+                return int(w) if idx % 2 == 0 else 0          # even layers slide
+            pat = ex.get("sliding_window_pattern") or 6
+            return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
         if self.model_type in ("qwen2", "qwen2_moe", "qwen3", "qwen3_moe", "smollm3"):
             if not ex.get("use_sliding_window"):
                 return 0
@@ -282,6 +349,9 @@ _ARCH_NAME = {
     "qwen2_moe": "Qwen2MoeForCausalLM",
     "olmoe": "OlmoeForCausalLM",
     "smollm3": "SmolLM3ForCausalLM",
+    "gemma": "GemmaForCausalLM",
+    "gemma2": "Gemma2ForCausalLM",
+    "gemma3_text": "Gemma3ForCausalLM",
 }
 
 
@@ -305,6 +375,17 @@ PRESETS = {
                               num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
                               router_aux_loss_coef=0.001, rope_theta=1000000.0, rms_norm_eps=1e-6,
                               max_position_embeddings=40960),
+    "tiny-gemma2": dict(model_type="gemma2", vocab_size=4096, hidden_size=256, intermediate_size=512,
+                        num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=256,
+                        hidden_act="gelu_pytorch_tanh", rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        extra=dict(query_pre_attn_scalar=256, sliding_window=64, attn_logit_softcapping=50.0,
+                                   final_logit_softcapping=30.0)),
+    "tiny-gemma3": dict(model_type="gemma3_text", vocab_size=4096, hidden_size=256, intermediate_size=512,
+                        num_hidden_layers=6, num_attention_heads=2, num_key_value_heads=1, head_dim=256,
+                        hidden_act="gelu_pytorch_tanh", rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        rope_theta=1000000.0,
+                        extra=dict(query_pre_attn_scalar=256, sliding_window=64, rope_local_base_freq=10000.0,
+                                   sliding_window_pattern=6)),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=256, intermediate_size=512,
                            moe_intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                            num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,

@@ -42,13 +42,23 @@ class disable_adapters:
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, dim, eps=1e-6, dtype=torch.bfloat16, device=None):
+    """``offset`` = 1 is the Gemma convention: the stored weight w starts at zero and the norm applies 1 + w."""
+
+    def __init__(self, dim, eps=1e-6, dtype=torch.bfloat16, device=None, offset=0.0):
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.offset = float(offset)
+        self.weight = nn.Parameter(torch.full((dim,), 1.0 - self.offset, dtype=dtype, device=device))
         self.eps = eps
 
     def forward(self, x, residual=None):
-        return Fn.add_rmsnorm(x, residual, self.weight, self.eps)
+        return Fn.add_rmsnorm(x, residual, self.weight, self.eps, w_offset=self.offset)
+
+    def plain(self, x):
+        """The norm alone (no residual stream)."""
+        return Fn.rmsnorm(x, self.weight, self.eps, w_offset=self.offset)
+
+    def effective_weight(self):
+        return self.weight if not self.offset else (self.weight.float() + self.offset).to(self.weight.dtype)
 
 
 class FusedLinear(nn.Module):

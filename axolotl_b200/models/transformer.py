@@ -49,8 +49,9 @@ class Attention(nn.Module):
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=False, dtype=dtype, device=device)
-        self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
-        self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
+        off = cfg.norm_offset()
+        self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
+        self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.full_qk_norm = cfg.model_type == "olmoe"   # OLMoE normalises q and k over ALL heads at once
         if self.full_qk_norm:
             self.q_norm = RMSNorm(self.Hq * self.D, cfg.rms_norm_eps, dtype, device)
@@ -59,6 +60,8 @@ class Attention(nn.Module):
         self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
         self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
+        self.softcap = cfg.attn_softcap()                      # Gemma 2: scores -> cap * tanh(scores / cap)
+        self.register_buffer("local_inv_freq", None, persistent=False)   # Gemma 3: sliding layers rotate with their own base
 
     def pre(self, x, positions, inv_freq, attn_scale):
         """Projections, q/k norms and rotary embedding: everything before the attention kernel."""
@@ -70,9 +73,11 @@ class Attention(nn.Module):
             k, _ = self.k_norm(qkv[..., nq:nq + nk].contiguous())
             qkv = torch.cat([q, k, qkv[..., nq + nk:]], -1)
         if self.use_rope:
+            if self.local_inv_freq is not None:
+                inv_freq, attn_scale = self.local_inv_freq, 1.0
             qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
-                              self.q_norm.weight if per_head_norm else None,
-                              self.k_norm.weight if per_head_norm else None, self.eps)
+                              self.q_norm.effective_weight() if per_head_norm else None,
+                              self.k_norm.effective_weight() if per_head_norm else None, self.eps)
         return qkv
 
     def core(self, qkv, meta):
@@ -83,7 +88,7 @@ class Attention(nn.Module):
             if getattr(meta, "cp", False):
                 raise NotImplementedError("sliding-window attention is not available with context parallelism")
             meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
-        return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale)
+        return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale, softcap=self.softcap)
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         return self.o_proj(self.core(self.pre(x, positions, inv_freq, attn_scale), meta))
@@ -124,13 +129,25 @@ class MLP(nn.Module):
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
         super().__init__()
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        off = cfg.norm_offset()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
         self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
         self.self_attn.use_rope = cfg.uses_rope(idx)
         self.self_attn.window = cfg.sliding_window(idx)
+        theta = cfg.local_rope_theta(idx)
+        if theta is not None:
+            D = cfg.head_dim
+            inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+            self.self_attn.local_inv_freq = inv.to(device) if device is not None else inv
         self.residual_multiplier = cfg.multiplier("residual_multiplier")
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
+        # Gemma 2 / 3: post_attention_layernorm and post_feedforward_layernorm act on the BRANCH outputs,
+        # pre_feedforward_layernorm takes the place the post-attention norm has elsewhere
+        self.sandwich = cfg.sandwich_norms()
+        if self.sandwich:
+            self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
         if cfg.is_moe_layer(idx):
             from .moe import SparseMoE
 
@@ -145,12 +162,21 @@ class DecoderLayer(nn.Module):
         return self.self_attn.pre(x, positions, inv_freq, attn_scale), residual
 
     def _after_attention(self, a, residual):
-        a = self.self_attn.o_proj(a)
+        return self._mlp_half(self.self_attn.o_proj(a), residual)
+
+    def _mlp_half(self, a, residual):
+        """From the attention branch output to the layer output: (branch, residual stream, router aux)."""
         rm = self.residual_multiplier
         if rm != 1.0:
             a = a * rm
-        x, residual = self.post_attention_layernorm(a, residual)
+        if self.sandwich:
+            a = self.post_attention_layernorm.plain(a)
+            x, residual = self.pre_feedforward_layernorm(a, residual)
+        else:
+            x, residual = self.post_attention_layernorm(a, residual)
         y, aux = self.mlp(x) if self.is_moe else (self.mlp(x), None)
+        if self.sandwich:
+            y = self.post_feedforward_layernorm.plain(y)
         if rm != 1.0:
             y = y * rm
         return y, residual, aux
@@ -166,18 +192,7 @@ class DecoderLayer(nn.Module):
 
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
         x, residual = self.input_layernorm(h, residual)
-        a = self.self_attn(x, positions, inv_freq, attn_scale, meta)
-        rm = self.residual_multiplier
-        if rm != 1.0:
-            a = a * rm
-        x, residual = self.post_attention_layernorm(a, residual)
-        if self.is_moe:
-            y, aux = self.mlp(x)
-        else:
-            y, aux = self.mlp(x), None
-        if rm != 1.0:
-            y = y * rm
-        return y, residual, aux
+        return self._mlp_half(self.self_attn(x, positions, inv_freq, attn_scale, meta), residual)
 
 
 class CausalLM(nn.Module):
@@ -187,7 +202,8 @@ class CausalLM(nn.Module):
         self.dtype = dtype
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=cfg.norm_offset())
+        self.final_softcap = cfg.final_softcap()   # Gemma 2: logits -> cap * tanh(logits / cap)
         if cfg.tie_word_embeddings:
             self.lm_head = None
         else:
@@ -295,6 +311,9 @@ class CausalLM(nn.Module):
                 p.zero_()
             else:
                 p.fill_(1.0)
+        for m in self.modules():
+            if isinstance(m, RMSNorm) and m.offset:
+                m.weight.fill_(1.0 - m.offset)
         return self
 
     @torch.no_grad()
@@ -439,12 +458,16 @@ class CausalLM(nn.Module):
                 num_items = int((lab != IGNORE_INDEX).sum().item())
             out.num_items = num_items
             lab = lab.reshape(-1).to(dev, non_blocking=True)
-            loss = Fn.linear_cross_entropy(h, W, lab, num_items=num_items, chunk_rows=self.ce_chunk_rows)
+            loss = Fn.linear_cross_entropy(h, W, lab, num_items=num_items, chunk_rows=self.ce_chunk_rows,
+                                           softcap=self.final_softcap)
             if out.aux_loss is not None and cfg.router_aux_loss_coef:
                 loss = loss + (cfg.router_aux_loss_coef * aux_scale) * out.aux_loss.to(loss.dtype)
             out.loss = loss
         if return_logits or (return_logits is None and labels is None):
-            out.logits = linear(h, W).view(B, S, -1)
+            logits = linear(h, W)
+            if self.final_softcap:
+                logits = (torch.tanh(logits.float() / self.final_softcap) * self.final_softcap).to(logits.dtype)
+            out.logits = logits.view(B, S, -1)
         return out
 
     # ------------------------------------------------------------------ generation (greedy / sampling)
@@ -453,7 +476,8 @@ class CausalLM(nn.Module):
         """Greedy / sampled continuation of one prompt; returns [1, prompt + new]. With ``use_cache``
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
-        if use_cache and getattr(self.hooks, "supports_kv_cache", True) is not False:
+        kernel_ok = self.config.head_dim in (64, 128) and not self.config.attn_softcap()   # what the decode kernel takes
+        if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 
             prompt = input_ids.reshape(-1).tolist()

@@ -8,6 +8,7 @@ falling back to eager PyTorch when it cannot be loaded.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
@@ -43,6 +44,12 @@ _CUDA_SIGS = {
     # A, lda, B, ldb, C, ldc, c_batch, E, Mg, Ng, rows, alpha, out_mode, bn, seg_start, seg_rows, status, stream
     # A, lda, qdata, scale, pts, A2, lda2, W2, C, ldc, E, Wn, Wk, K2, trans_w, alpha, out_mode, blk_expert, n_blocks, max_blocks, status, stream
     "axb_grouped_gemm_w4a16": [vp, i64, vp, vp, vp, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp, vp],
+    "axb_flash_wide_fwd": [vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, i64, vp, f32, f32, vp, vp],
+    "axb_flash_wide_bwd": [vp, i64, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, i64, vp, vp,
+                           f32, f32, vp, vp],
+    "axb_bounds_check_enabled": [],
+    "axb_bounds_fetch": [vp],
+    "axb_bounds_reset": [],
     "axb_grouped_gram": [vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i64, f32, i32, i32, vp, vp, vp, vp],
     "axb_ep_gather_rows": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, i64, vp],
     "axb_ep_scatter_add": [vp, i32, vp, vp, vp, vp, i64, i32, i64, vp],
@@ -64,6 +71,7 @@ _CUDA_SIGS = {
     "axb_embedding_fwd": [vp, vp, vp, i64, i32, i64, vp],
     "axb_embedding_bwd": [vp, vp, vp, i64, i32, i64, vp],
     "axb_ce_fwd_bwd": [vp, vp, vp, vp, i64, i32, i64, f32, i64, i32, vp],
+    "axb_ce_fwd_bwd_softcap": [vp, vp, vp, vp, i64, i32, i64, f32, i64, i32, f32, vp],
     "axb_sumsq": [vp, i64, vp, vp],
     "axb_adamw": [vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, vp, f32, f32, vp],
     "axb_cast_bf16_to_f32": [vp, vp, i64, f32, i32, vp],
@@ -108,7 +116,9 @@ def cuda_lib():
     if _cuda_lib is None:
         with _lock:
             if _cuda_lib is None:
-                path = _LIB_DIR / "libaxb200.so"
+                # AXB_BOUNDS_CHECK=1: the variant built with -DAXB_BOUNDS_CHECK (index checks in the kernels)
+                checked = os.environ.get("AXB_BOUNDS_CHECK", "0") not in ("", "0")
+                path = _LIB_DIR / ("libaxb200_checked.so" if checked else "libaxb200.so")
                 if not path.exists():
                     raise RuntimeError(
                         f"{path} is missing: run `python -m axolotl_b200.build` (needs nvcc). "
@@ -177,6 +187,36 @@ def check_status(device=None) -> None:
     if code != 0:
         t.zero_()
         raise KernelTimeoutError(f"axolotl_b200 kernel reported status {code}: {_STATUS_NAMES.get(code, '?')}")
+
+
+class KernelBoundsError(RuntimeError):
+    pass
+
+
+_BOUNDS_SITES = {1: "embedding token id", 2: "embedding-gradient token id", 3: "cross-entropy label",
+                 4: "grouped GEMM expert id", 5: "W4A16 grouped GEMM expert id", 6: "attention document tile",
+                 7: "MoE dispatch token index"}
+
+
+def bounds_violation():
+    """(site name, index, limit, count) of the first out-of-range index the bounds-check library recorded since
+    the last reset, or None. Always None with the regular library."""
+    lib = cuda_lib()
+    if not lib.axb_bounds_check_enabled():
+        return None
+    out = (C.c_longlong * 4)()
+    check_rc(lib.axb_bounds_fetch(out), "bounds_fetch")
+    if out[0] == 0:
+        return None
+    return _BOUNDS_SITES.get(int(out[0]), f"site {int(out[0])}"), int(out[1]), int(out[2]), int(out[3])
+
+
+def check_bounds(reset=True) -> None:
+    v = bounds_violation()
+    if v is not None:
+        if reset:
+            cuda_lib().axb_bounds_reset()
+        raise KernelBoundsError(f"out-of-range {v[0]}: index {v[1]}, limit {v[2]} ({v[3]} violations; the accesses were skipped)")
 
 
 launch_count = 0  # native kernel entry points called so far (each launches >= 1 kernel)

@@ -429,18 +429,20 @@ class AttnMeta:
         return AttnMeta(cu, device, causal)
 
 
-def _attn_ref(q, k, v, cu, scale, causal=True, window=0):
-    # q [T,Hq,D], k/v [T,Hk,D]; per-document (causal or bidirectional) attention in fp32
+def _attn_ref(q, k, v, cu, scale, causal=True, window=0, softcap=0.0):
+    # q [T,Hq,D], k [T,Hk,D], v [T,Hk,Dv]; per-document (causal or bidirectional) attention in fp32
     T, Hq, D = q.shape
     Hk = k.shape[1]
     rep = Hq // Hk
-    out = torch.empty_like(q)
+    out = torch.empty((T, Hq, v.shape[2]), dtype=q.dtype, device=q.device)
     for d in range(len(cu) - 1):
         s, e = int(cu[d]), int(cu[d + 1])
         qq = q[s:e].float().transpose(0, 1)
         kk = k[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
         vv = v[s:e].float().repeat_interleave(rep, 1).transpose(0, 1)
         sc = (qq @ kk.transpose(1, 2)) * scale
+        if softcap:
+            sc = torch.tanh(sc / softcap) * softcap
         if causal:
             mask = torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril()
             if window:
@@ -491,14 +493,65 @@ class _FlashVarlen(torch.autograd.Function):
         return dqkv, None, None, None, None, None
 
 
-def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
+class _FlashWide(torch.autograd.Function):
+    """Wide heads (q/k 256 with v 256, or q/k 192 with v 128) and tanh soft-capped scores: csrc/flash_wide.cu."""
+
+    @staticmethod
+    def forward(ctx, qkv, meta, Hq, Hk, D, Dv, scale, softcap):
+        T = qkv.shape[0]
+        ctx.meta, ctx.dims = meta, (Hq, Hk, D, Dv, scale, softcap)
+        lib = _lib.cuda_lib()
+        out = torch.empty((T, Hq * Dv), dtype=qkv.dtype, device=qkv.device)
+        lse2 = torch.empty((Hq, T), dtype=torch.float32, device=qkv.device)
+        _lib.check_rc(
+            lib.axb_flash_wide_fwd(qkv.data_ptr(), qkv.stride(0), T, Hq, Hk, D, Dv, 0, Hq * D, (Hq + Hk) * D,
+                                   meta.tiles_fwd.data_ptr(), meta.n_tiles, out.data_ptr(), out.stride(0),
+                                   lse2.data_ptr(), scale, float(softcap or 0.0),
+                                   _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()), "flash_wide_fwd")
+        ctx.save_for_backward(qkv, out, lse2)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse2 = ctx.saved_tensors
+        Hq, Hk, D, Dv, scale, softcap = ctx.dims
+        meta = ctx.meta
+        T = qkv.shape[0]
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq_acc = torch.empty((T, Hq * D), dtype=torch.float32, device=qkv.device)
+        delta = torch.empty((Hq, T), dtype=torch.float32, device=qkv.device)
+        _lib.check_rc(
+            _lib.cuda_lib().axb_flash_wide_bwd(
+                qkv.data_ptr(), qkv.stride(0), dout.data_ptr(), out.data_ptr(), out.stride(0), lse2.data_ptr(), T, Hq,
+                Hk, D, Dv, 0, Hq * D, (Hq + Hk) * D, meta.tiles_bwd.data_ptr(), meta.n_tiles, dqkv.data_ptr(),
+                dqkv.stride(0), dq_acc.data_ptr(), delta.data_ptr(), scale, float(softcap or 0.0),
+                _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()), "flash_wide_bwd")
+        return dqkv, None, None, None, None, None, None, None
+
+
+WIDE_HEADS = ((256, 256), (192, 128))
+
+
+def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.0):
     """Attention inside each document of a packed row: causal, or bidirectional when the
     metadata was built with ``causal=False`` (masked-diffusion and encoder-style objectives).
 
-    ``qkv`` is the fused projection [T, (Hq + 2*Hk) * D] (q heads, then k heads, then v heads).
-    Returns [T, Hq * D].
+    ``qkv`` is the fused projection [T, Hq*D + Hk*D + Hk*Dv] (q heads, then k heads, then v heads; ``Dv``
+    defaults to ``D``). Returns [T, Hq * Dv]. Head widths 64 / 128 run the double-buffered kernels;
+    (D, Dv) = (256, 256) or (192, 128), and any ``softcap`` (scores become softcap * tanh(scores / softcap))
+    at those widths, run the wide kernels.
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
+    Dv = D if Dv is None else Dv
+    if qkv.is_cuda and ((D, Dv) in WIDE_HEADS):
+        if getattr(meta, "cp", False):
+            raise NotImplementedError("context parallelism is not available for head widths above 128")
+        return _FlashWide.apply(qkv, meta, Hq, Hk, D, Dv, scale, softcap)
+    if qkv.is_cuda and (softcap or Dv != D or D not in (64, 128)):
+        raise NotImplementedError(
+            f"attention head widths (q/k {D}, v {Dv}) with softcap={softcap}: the CUDA kernels take 64, 128, "
+            f"(256, 256) and (192, 128); soft-capping needs one of the two wide layouts")
     if getattr(meta, "cp", False):
         from ..parallel.cp import flash_varlen_cp   # context parallelism is causal only, without a window
 
@@ -508,9 +561,9 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None):
     T = qkv.shape[0]
     q = qkv[:, : Hq * D].reshape(T, Hq, D)
     k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
-    v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, D)
+    v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, Dv)
     return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True),
-                     getattr(meta, "window", 0)).reshape(T, Hq * D)
+                     getattr(meta, "window", 0), softcap).reshape(T, Hq * Dv)
 
 
 @torch.no_grad()
@@ -553,7 +606,7 @@ class _LinearCE(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, h, w, labels, denom, chunk_rows, ignore_index, lora):
+    def forward(ctx, h, w, labels, denom, chunk_rows, ignore_index, lora, softcap=0.0):
         from .gemm import gemm, pick_splits
 
         T, H = h.shape
@@ -567,7 +620,13 @@ class _LinearCE(torch.autograd.Function):
             r1 = min(T, r0 + chunk_rows)
             hc = h[r0:r1]
             logits = gemm(hc, w)
-            if h.is_cuda:
+            if h.is_cuda and softcap:
+                _lib.check_rc(
+                    lib.axb_ce_fwd_bwd_softcap(logits.data_ptr(), labels[r0:r1].data_ptr(), losses[r0:r1].data_ptr(),
+                                               None, r1 - r0, V, logits.stride(0), 1.0 / denom, ignore_index, 1,
+                                               float(softcap), _lib.stream_ptr()), "ce_fwd_bwd_softcap")
+                dlogits = logits
+            elif h.is_cuda:
                 _lib.check_rc(
                     lib.axb_ce_fwd_bwd(logits.data_ptr(), labels[r0:r1].data_ptr(),
                                        losses[r0:r1].data_ptr(), None, r1 - r0, V,
@@ -576,6 +635,10 @@ class _LinearCE(torch.autograd.Function):
                 dlogits = logits
             else:
                 lf = logits.float()
+                dcap = None
+                if softcap:
+                    t = torch.tanh(lf / softcap)
+                    lf, dcap = t * softcap, 1.0 - t * t
                 lab = labels[r0:r1]
                 valid = lab != ignore_index
                 lse = torch.logsumexp(lf, -1)
@@ -583,6 +646,8 @@ class _LinearCE(torch.autograd.Function):
                 losses[r0:r1] = torch.where(valid, lse - tgt, torch.zeros_like(lse))
                 p = torch.softmax(lf, -1)
                 p[torch.arange(r1 - r0), lab.clamp(min=0)] -= 1.0
+                if dcap is not None:
+                    p = p * dcap
                 dlogits = (p * valid[:, None] / denom).to(logits.dtype)
             gemm(dlogits, w, trans_b=True, out=dh[r0:r1])
             if need_dw:
@@ -596,14 +661,15 @@ class _LinearCE(torch.autograd.Function):
     def backward(ctx, gout):
         dh, dw = ctx.saved_tensors
         return (dh * gout.to(dh.dtype), (dw * gout).to(ctx.w_dtype) if dw is not None else None,
-                None, None, None, None, None)
+                None, None, None, None, None, None)
 
 
 def linear_cross_entropy(hidden, lm_head_weight, labels, num_items=None, chunk_rows=2048,
-                         ignore_index=IGNORE_INDEX):
+                         ignore_index=IGNORE_INDEX, softcap=0.0):
     """Mean (or ``sum / num_items``) token cross entropy of ``hidden @ W^T`` against ``labels``.
 
-    ``labels`` must already be shifted (labels[t] is the target of position t).
+    ``labels`` must already be shifted (labels[t] is the target of position t). ``softcap``: the logits are
+    soft-capped first, ``softcap * tanh(logits / softcap)`` (Gemma 2).
     """
     hidden = hidden.reshape(-1, hidden.shape[-1])
     labels = labels.reshape(-1).contiguous()
@@ -611,7 +677,7 @@ def linear_cross_entropy(hidden, lm_head_weight, labels, num_items=None, chunk_r
         num_items = int((labels != ignore_index).sum().item())
     denom = float(max(num_items, 1))
     return _LinearCE.apply(hidden.contiguous(), lm_head_weight, labels, denom, chunk_rows,
-                           ignore_index, None)
+                           ignore_index, None, float(softcap or 0.0))
 
 
 class _LinearTokenLogps(torch.autograd.Function):

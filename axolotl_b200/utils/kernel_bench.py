@@ -391,6 +391,21 @@ def profile_case(what):
         for _ in range(3):
             gemm(x, Wgu, out=gu, glu=("fwd", 0, 0.0, h))
             gemm(dy, Wd, trans_b=True, out=dgu, glu=("bwd", 0, 0.0, gu))
+    elif what == "one_w4a16":
+        # NVFP4 expert projection with the decode inside the grouped GEMM: 32 experts of Qwen3-MoE-30B-A3B's
+        # gate|up shape, 512 rows each (forward and input gradient)
+        from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm_w4a16
+
+        E, N, K, per = 32, 1536, 2048, 512
+        lay = GroupLayout(torch.full((E,), per, device="cuda"), E * per)
+        q = {"qdata": torch.randint(0, 256, (E, N, K // 2), dtype=torch.uint8, device="cuda"),
+             "scale": torch.randint(40, 120, (E, N, K // 16), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn),
+             "pts": torch.full((E,), 1e-3, device="cuda")}
+        x = torch.randn(lay.max_rows, K, device="cuda").bfloat16()
+        dy = torch.randn(lay.max_rows, N, device="cuda").bfloat16()
+        for _ in range(3):
+            grouped_gemm_w4a16(x, q, lay)
+            grouped_gemm_w4a16(dy, q, lay, trans_w=True)
     elif what == "one_grouped":
         # one MoE projection of Qwen3-MoE-30B-A3B: 128 experts, 8192 tokens x top-8 = 65536 routed rows
         from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gram
@@ -422,7 +437,7 @@ def profile_case(what):
 
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
-    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp"):
+    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp", "one_w4a16"):
         return profile_case(what)
     rows = []
     if what in ("gemm", "all"):

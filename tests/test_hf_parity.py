@@ -388,3 +388,56 @@ def test_qwen3_per_layer_sliding_window_matches_hf(tmp_path):
         got = ours(ids, pos, return_logits=True).logits
         ref = hf_model(input_ids=ids).logits
     assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+
+
+def _randomize_norms(model, lo=-0.3, hi=0.3):
+    from axolotl_b200.models.layers import RMSNorm
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, RMSNorm):
+                m.weight.uniform_(lo, hi)
+
+
+@pytest.mark.parametrize("model_type", ["gemma", "gemma2", "gemma3_text"])
+def test_gemma_family_matches_hf(tmp_path, model_type):
+    """(1 + w) norms, sqrt(hidden) embedding scale, tanh GeGLU, head_dim != hidden / heads; Gemma 2: sandwich norms,
+    attention and final-logit soft caps, query_pre_attn_scalar, sliding window on even layers; Gemma 3: q/k norms,
+    5 sliding : 1 global layers with their own rope base."""
+    extra = {}
+    layers = 2
+    if model_type == "gemma2":
+        extra = dict(query_pre_attn_scalar=48, sliding_window=16, attn_logit_softcapping=5.0, final_logit_softcapping=3.0)
+    if model_type == "gemma3_text":
+        layers = 6
+        extra = dict(query_pre_attn_scalar=48, sliding_window=16, rope_local_base_freq=10000.0, sliding_window_pattern=6,
+                     layer_types=["sliding_attention"] * 5 + ["full_attention"])
+    cfg = ModelConfig(model_type=model_type, vocab_size=384, hidden_size=96, intermediate_size=160, num_hidden_layers=layers,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, hidden_act="gelu_pytorch_tanh",
+                      rms_norm_eps=1e-6, rope_theta=1000000.0 if model_type == "gemma3_text" else 10000.0,
+                      tie_word_embeddings=True, extra=extra)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(11)
+    _randomize_norms(ours)
+    if model_type != "gemma":
+        assert ours.layers[0].self_attn.window == 16 and ours.layers[layers - 1].self_attn.window == 0
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [41, 23]
+    ids, pos = _packed_inputs(384, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    # the loss goes through the soft-capped fused linear + cross entropy
+    ids1, pos1 = _packed_inputs(384, [50], seed=3)
+    labels = ids1.clone()
+    labels[:, :9] = -100
+    loss = ours(ids1, pos1, labels).loss
+    with torch.no_grad():
+        ref_loss = hf_model(input_ids=ids1, labels=labels).loss
+    assert abs(loss.item() - ref_loss.item()) < 2e-4 * max(1.0, abs(ref_loss.item()))
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)

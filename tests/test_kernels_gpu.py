@@ -214,6 +214,39 @@ def test_flash_varlen_fwd_bwd(D, Hq, Hk, lens):
     assert _rel_err(gx[:, k_end:], gc[:, k_end:]) < 2e-2, "dv"
 
 
+@pytest.mark.parametrize("D,Dv,Hq,Hk,softcap,window,causal", [
+    (256, 256, 4, 2, 0.0, 0, True), (256, 256, 2, 1, 20.0, 0, True), (256, 256, 2, 2, 0.0, 100, True),
+    (192, 128, 4, 4, 0.0, 0, True), (192, 128, 4, 2, 0.0, 0, False), (256, 256, 2, 1, 0.0, 0, False)])
+@pytest.mark.parametrize("lens", [[128], [200, 57, 300], [1, 129, 640, 31]])
+def test_flash_wide_heads_fwd_bwd(D, Dv, Hq, Hk, softcap, window, causal, lens):
+    """Head widths 256 (Gemma) and 192/128 (latent attention), tanh soft cap, sliding window, bidirectional
+    documents: the wide tcgen05 kernels against per-document fp32 attention."""
+    from axolotl_b200.ops.functional import AttnMeta, flash_varlen
+    torch.manual_seed(18)
+    cu = [0]
+    for l in lens:
+        cu.append(cu[-1] + l)
+    T = cu[-1]
+    width = Hq * D + Hk * D + Hk * Dv
+    base = (torch.randn(T, width, dtype=torch.float32) * 0.5).bfloat16()
+    meta = AttnMeta(cu, _dev(), causal, window or None)
+    x = base.to(_dev()).requires_grad_(True)
+    out = flash_varlen(x, meta, Hq, Hk, D, Dv=Dv, softcap=softcap)
+    _check_status()
+    g = (torch.randn(T, Hq * Dv) * 0.5).bfloat16()
+    (out.float() * g.to(_dev()).float()).sum().backward()
+    _check_status()
+    xc = base.float().requires_grad_(True)
+    outc = flash_varlen(xc, AttnMeta(cu, "cpu", causal, window or None), Hq, Hk, D, Dv=Dv, softcap=softcap)
+    (outc * g.float()).sum().backward()
+    assert _rel_err(out.cpu(), outc) < 1e-2
+    q_end, k_end = Hq * D, (Hq + Hk) * D
+    gx, gc = x.grad.cpu().float(), xc.grad
+    assert _rel_err(gx[:, :q_end], gc[:, :q_end]) < 2e-2, "dq"
+    assert _rel_err(gx[:, q_end:k_end], gc[:, q_end:k_end]) < 2e-2, "dk"
+    assert _rel_err(gx[:, k_end:], gc[:, k_end:]) < 2e-2, "dv"
+
+
 def test_linear_cross_entropy():
     from axolotl_b200.ops.functional import linear_cross_entropy
     torch.manual_seed(9)
@@ -951,3 +984,53 @@ def test_dora_weight_norm_kernel():
     ref = (W + lin.scaling * (B @ A)).norm(dim=1)
     assert _rel_err(got, ref) < 5e-3
     assert got.dtype == torch.float32 and got.shape == (512,)
+
+
+def test_bounds_check_build_reports_through_the_device_record():
+    """The -DAXB_BOUNDS_CHECK library: a clean tiny training step records nothing; an out-of-range token id and
+    label are recorded with site, index and limit while the access itself is skipped (no fault)."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from axolotl_b200.ops import _lib, functional as Fn
+from axolotl_b200.models.config import preset
+from axolotl_b200.models.transformer import CausalLM
+assert _lib.cuda_lib().axb_bounds_check_enabled() == 1
+dev = torch.device("cuda:0")
+cfg = preset("tiny-llama", num_hidden_layers=2)
+m = CausalLM(cfg, torch.bfloat16, dev).init_weights(0)
+ids = torch.randint(0, cfg.vocab_size, (1, 256))
+out = m(ids, labels=ids.clone())
+out.loss.backward()
+torch.cuda.synchronize()
+assert _lib.bounds_violation() is None, _lib.bounds_violation()
+_lib.check_status()
+table = torch.randn(64, 128, device=dev).bfloat16()
+bad = torch.tensor([1, 2, 99, 3], device=dev)
+y = Fn.embedding(table, bad)
+torch.cuda.synchronize()
+v = _lib.bounds_violation()
+assert v is not None and v[0] == "embedding token id" and v[1] == 99 and v[2] == 64, v
+assert torch.equal(y[2], table[0])            # the access went to a valid row instead
+try:
+    _lib.check_bounds()
+    raise SystemExit("check_bounds did not raise")
+except _lib.KernelBoundsError as e:
+    assert "index 99" in str(e)
+assert _lib.bounds_violation() is None        # reset by check_bounds
+h = torch.randn(8, 128, device=dev).bfloat16()
+W = torch.randn(64, 128, device=dev).bfloat16()
+lab = torch.tensor([1, 2, 3, 64, -100, 5, 6, 7], device=dev)
+loss = Fn.linear_cross_entropy(h, W, lab, num_items=7)
+torch.cuda.synchronize()
+v = _lib.bounds_violation()
+assert v is not None and v[0] == "cross-entropy label" and v[1] == 64 and v[2] == 64, v
+assert torch.isfinite(loss)
+print("BOUNDS_OK")
+'''
+    env = dict(os.environ, AXB_BOUNDS_CHECK="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "BOUNDS_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-3000:]

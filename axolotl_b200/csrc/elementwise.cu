@@ -342,8 +342,10 @@ __device__ __forceinline__ float tanh_fast(float x) {
   return y;
 }
 __device__ __forceinline__ float sigmoid_fast(float g) { return __fdividef(1.f, 1.f + __expf(-g)); }
+// kind 0: silu, 1: gelu (tanh form), 2: g * sigmoid(1.702 g), whose GLU multiplies by (up + 1) (gpt-oss experts)
 __device__ __forceinline__ float act_fwd(float g, int kind) {
   if (kind == 0) return g * sigmoid_fast(g);  // silu
+  if (kind == 2) return g * sigmoid_fast(1.702f * g);
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;  // gelu tanh
   const float t = tanh_fast(k0 * (g + k1 * g * g * g));
   return 0.5f * g * (1.f + t);
@@ -352,6 +354,10 @@ __device__ __forceinline__ float act_bwd(float g, int kind) {
   if (kind == 0) {
     const float s = sigmoid_fast(g);
     return s * (1.f + g * (1.f - s));
+  }
+  if (kind == 2) {
+    const float s = sigmoid_fast(1.702f * g);
+    return s * (1.f + 1.702f * g * (1.f - s));
   }
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   const float t = tanh_fast(k0 * (g + k1 * g * g * g));
@@ -374,7 +380,7 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat
     for (int j = 0; j < 8; ++j) {
       const float gc = limit > 0.f ? fminf(g[j], limit) : g[j];
       const float uc = limit > 0.f ? fminf(fmaxf(u[j], -limit), limit) : u[j];
-      o[j] = act_fwd(gc, kind) * uc;
+      o[j] = act_fwd(gc, kind) * (kind == 2 ? uc + 1.f : uc);
     }
     store8(h + t * I + c, o);
   }
@@ -399,7 +405,7 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
       const bool u_in = !(limit > 0.f) || (u[j] >= -limit && u[j] <= limit);
       const float gc = g_in ? g[j] : limit;
       const float uc = u_in ? u[j] : (u[j] > 0.f ? limit : -limit);
-      og[j] = g_in ? d[j] * uc * act_bwd(gc, kind) : 0.f;
+      og[j] = g_in ? d[j] * (kind == 2 ? uc + 1.f : uc) * act_bwd(gc, kind) : 0.f;
       ou[j] = u_in ? d[j] * act_fwd(gc, kind) : 0.f;
     }
     store8(dgu + t * 2 * I + c, og);

@@ -330,6 +330,26 @@ __global__ void peer_put_i32_kernel(int* __restrict__ dst, const int* __restrict
     dst[i] = src[i];
 }
 
+// Routing tables of every rank into one local array: dst[r * n + i] = peer r's src[i] (plain peer loads).
+__global__ void ep_gather_tables_kernel(PeerPtrs8 src, int world, long long n, int* __restrict__ dst) {
+  const long long total = (long long)world * n;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n);
+    dst[i] = reinterpret_cast<const int*>(src.p[r])[i - (long long)r * n];
+  }
+}
+
+// Per-slot scalars back to the rank that routed the slot: peer src_rank[i] gets vals[i] at slot src_slot[i]
+// (rows with src_rank < 0 are padding). Plain peer stores; the caller's barrier publishes them.
+__global__ void ep_put_scalars_kernel(PeerPtrs8 dst, const int* __restrict__ src_rank, const int* __restrict__ src_slot,
+                                      const float* __restrict__ vals, long long n, long long slots) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = src_rank[i], sl = src_slot[i];
+    if (r < 0 || sl < 0 || sl >= slots) continue;
+    reinterpret_cast<float*>(dst.p[r])[sl] = vals[i];
+  }
+}
+
 int fill8(PeerPtrs8& d, const unsigned long long* s, int world) {
   if (world < 1 || world > 8) return -2;
   for (int i = 0; i < 8; ++i) d.p[i] = i < world ? s[i] : 0ull;
@@ -453,6 +473,26 @@ extern "C" int axb_ep_reduce_rows(const unsigned long long* part_ptrs, int world
   int grid = (int)((T + 7) / 8 > 148 * 8 ? 148 * 8 : (T + 7) / 8);
   ep_reduce_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, (const unsigned char*)sent, (__nv_bfloat16*)y, world, self,
                                                       T, width);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int axb_ep_gather_tables(const unsigned long long* src_ptrs, int world, long long n, void* dst, void* stream) {
+  PeerPtrs8 s;
+  if (fill8(s, src_ptrs, world)) return -2;
+  if (n <= 0) return 0;
+  const long long total = (long long)world * n;
+  int grid = (int)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
+  ep_gather_tables_kernel<<<grid, 256, 0, ST(stream)>>>(s, world, n, (int*)dst);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int axb_ep_put_scalars(const unsigned long long* dst_ptrs, int world, const void* src_rank,
+                                  const void* src_slot, const void* vals, long long n, long long slots, void* stream) {
+  PeerPtrs8 d;
+  if (fill8(d, dst_ptrs, world)) return -2;
+  if (n <= 0) return 0;
+  int grid = (int)((n + 255) / 256 > 148 * 8 ? 148 * 8 : (n + 255) / 256);
+  ep_put_scalars_kernel<<<grid, 256, 0, ST(stream)>>>(d, (const int*)src_rank, (const int*)src_slot, (const float*)vals, n, slots);
   return (int)cudaGetLastError();
 }
 

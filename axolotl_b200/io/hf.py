@@ -23,13 +23,16 @@ from . import safetensors_io as st
 
 def _split_name(hf_name: str):
     """'model.layers.3.self_attn.q_proj.weight' -> ('layers.3.self_attn', 'q_proj', 'weight')."""
-    m = re.match(r"model\.(.*)\.(q_proj|k_proj|v_proj|qkv_proj|o_proj|gate_proj|up_proj|gate_up_proj|down_proj)\.(weight|bias)$", hf_name)
+    m = re.match(r"model\.(.*)\.(q_proj|k_proj|v_proj|qkv_proj|o_proj|gate_proj|up_proj|gate_up_proj|down_proj|"
+                 r"q_a_proj|q_b_proj|kv_a_proj_with_mqa|kv_b_proj)\.(weight|bias)$", hf_name)
     return m.groups() if m else None
 
 
 _FUSED_OF = {"q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj", "o_proj": "o_proj",
              "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj", "down_proj": "down_proj",
-             "qkv_proj": "qkv_proj", "gate_up_proj": "gate_up_proj"}   # Phi-3 checkpoints are already fused
+             "qkv_proj": "qkv_proj", "gate_up_proj": "gate_up_proj",   # Phi-3 checkpoints are already fused
+             "q_a_proj": "q_a_proj", "q_b_proj": "q_b_proj", "kv_a_proj_with_mqa": "kv_a_proj_with_mqa",
+             "kv_b_proj": "kv_b_proj"}                                  # DeepSeek latent attention
 
 
 @torch.no_grad()
@@ -58,14 +61,37 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             filled.add("norm")
         elif (sp := _split_name(name)) is not None and ".experts." not in name:
             parent, sub, kind = sp
-            fl: FusedLinear = mods[f"{parent}.{_FUSED_OF[sub]}"]
+            fused = _FUSED_OF[sub]
+            if fused == "qkv_proj" and f"{parent}.qkv_proj" not in mods:      # latent attention: a lone q_proj
+                fused = sub
+            fl: FusedLinear = mods[f"{parent}.{fused}"]
             r0, r1 = fl.row_range(sub)
             (fl.weight if kind == "weight" else fl.bias)[r0:r1].copy_(t)
             filled.add(f"{parent}.{sub}.{kind}")
         elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.weight$", name)):
             mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
             filled.add(name)
-        elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.(q_norm|k_norm)\.weight$", name)):
+        elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.sinks$", name)):
+            mods[m.group(1)].sinks.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.router\.(weight|bias)$", name)):
+            (mods[m.group(1)].gate if m.group(2) == "weight" else mods[m.group(1)].router_bias).copy_(t)
+            filled.add(name)
+        elif getattr(model.config, "model_type", "") == "gpt_oss" and (
+                m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(gate_up_proj|down_proj)(_bias)?$", name)):
+            # gpt-oss stores [E, in, out] with gate / up interleaved along the output axis
+            ex = mods[m.group(1)].experts
+            if m.group(2) == "gate_up_proj":
+                u = t if m.group(3) else t.transpose(1, 2)                  # [E, 2I(, H)] interleaved rows
+                u = torch.cat([u[:, 0::2], u[:, 1::2]], 1)
+                (ex.gate_up_bias if m.group(3) else ex.gate_up_proj).copy_(u)
+            else:
+                (ex.down_bias if m.group(3) else ex.down_proj).copy_(t if m.group(3) else t.transpose(1, 2))
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.e_score_correction_bias$", name)):
+            mods[m.group(1)].e_score_correction_bias.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.(q_norm|k_norm|q_a_layernorm|kv_a_layernorm)\.weight$", name)):
             mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.weight$", name)):
@@ -198,7 +224,23 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}
     if model.lm_head is not None:
         sd["lm_head.weight"] = model.lm_head.detach()
+    gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
     for name, m in model.named_modules():
+        if gpt_oss and isinstance(m, Experts):
+            def interleave(u):            # [E, 2I, ...] gate rows then up rows -> alternating
+                E, two_i = u.shape[:2]
+                return torch.stack([u[:, : two_i // 2], u[:, two_i // 2:]], 2).reshape(u.shape)
+            sd[f"model.{name}.gate_up_proj"] = interleave(m.gate_up_proj.detach()).transpose(1, 2).contiguous()
+            sd[f"model.{name}.gate_up_proj_bias"] = interleave(m.gate_up_bias.detach())
+            sd[f"model.{name}.down_proj"] = m.down_proj.detach().transpose(1, 2).contiguous()
+            sd[f"model.{name}.down_proj_bias"] = m.down_bias.detach()
+            continue
+        if gpt_oss and getattr(m, "router_bias", None) is not None:
+            sd[f"model.{name}.router.weight"] = m.gate.detach()
+            sd[f"model.{name}.router.bias"] = m.router_bias.detach()
+            continue
+        if getattr(m, "sinks", None) is not None:
+            sd[f"model.{name}.sinks"] = m.sinks.detach()
         if isinstance(m, FusedLinear):
             parent = name.rsplit(".", 1)[0]
             for sub in m.names:
@@ -207,7 +249,7 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 if m.bias is not None:
                     sd[f"model.{parent}.{sub}.bias"] = m.bias.detach()[r0:r1]
         elif name.endswith(("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm",
-                            "q_norm", "k_norm")):
+                            "q_norm", "k_norm", "q_a_layernorm", "kv_a_layernorm")):
             sd[f"model.{name}.weight"] = m.weight.detach()
         elif isinstance(m, Experts):
             if m.nvfp4 is not None:
@@ -229,6 +271,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
             sd[f"model.{name}.gate.weight"] = m.gate.detach()
             if getattr(m, "shared_expert_gate", None) is not None:
                 sd[f"model.{name}.shared_expert_gate.weight"] = m.shared_expert_gate.detach()
+            if getattr(m, "e_score_correction_bias", None) is not None:
+                sd[f"model.{name}.gate.e_score_correction_bias"] = m.e_score_correction_bias.detach()
     return sd
 
 

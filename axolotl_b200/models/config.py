@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
@@ -92,6 +92,24 @@ class ModelConfig:
                 d.setdefault("sliding_window", 4096)
                 d.setdefault("attn_logit_softcapping", 50.0)
                 d.setdefault("final_logit_softcapping", 30.0)
+        if mt == "gpt_oss":
+            d["num_experts"] = d.get("num_local_experts") or 0
+            d["moe_intermediate_size"] = d.get("intermediate_size") or 0
+            d["hidden_act"] = "gpt_oss_swiglu"        # g * sigmoid(1.702 g) * (up + 1), both branches clamped
+            d.setdefault("swiglu_limit", 7.0)
+            d.setdefault("attention_bias", True)
+            d.setdefault("sliding_window", 128)
+            if not d.get("rope_scaling") and not d.get("rope_parameters"):     # the family's default: YaRN x32 over 4096
+                d["rope_scaling"] = {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                     "truncate": False, "original_max_position_embeddings": 4096}
+        if mt in ("deepseek_v2", "deepseek_v3"):
+            d["num_experts"] = d.get("n_routed_experts") or 0
+            d.setdefault("norm_topk_prob", mt == "deepseek_v3")
+            d["head_dim"] = (d.get("qk_nope_head_dim") or 128) + (d.get("qk_rope_head_dim") or 64)
+            k1 = d.get("first_k_dense_replace") or 0
+            step = d.get("moe_layer_freq") or 1
+            d["mlp_only_layers"] = [i for i in range(d.get("num_hidden_layers", 0)) if i < k1 or i % step]
+            d["router_aux_loss_coef"] = d.get("aux_loss_alpha") or 0.0
         if mt not in SUPPORTED_MODEL_TYPES:
             raise ValueError(
                 f"model_type '{mt}' is not supported by axolotl_b200 (supported: {SUPPORTED_MODEL_TYPES})")
@@ -128,6 +146,15 @@ class ModelConfig:
         d.pop("qk_norm")
         if self.model_type == "mixtral":
             d["num_local_experts"] = d.pop("num_experts")
+        if self.model_type == "gpt_oss":
+            d["num_local_experts"] = d.pop("num_experts")
+            d["intermediate_size"] = d.pop("moe_intermediate_size")
+            d["hidden_act"] = "silu"
+        if self.model_type in ("deepseek_v2", "deepseek_v3"):
+            d["n_routed_experts"] = d.pop("num_experts")
+            d.pop("head_dim", None)
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
         if not self.num_experts:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
                       "router_aux_loss_coef", "decoder_sparse_step", "mlp_only_layers"):
@@ -196,6 +223,11 @@ class ModelConfig:
             return 0
         if self.model_type in ("mistral", "phi3", "mixtral"):
             return int(w)
+        if self.model_type == "gpt_oss":
+            if idx is None:
+                return int(w)
+            types = ex.get("layer_types")
+            return int(w) if (types[idx] == "sliding_attention" if types else idx % 2 == 0) else 0
         if self.model_type in ("gemma2", "gemma3_text"):
             if idx is None:
                 return int(w)
@@ -232,12 +264,18 @@ class ModelConfig:
         return (self.num_experts > 0 and idx not in self.mlp_only_layers
                 and (idx + 1) % max(self.decoder_sparse_step, 1) == 0)
 
+    def rope_dim(self) -> int:
+        """Width of the rotated part of a head (DeepSeek latent attention rotates only its shared 64-wide part)."""
+        if self.model_type in ("deepseek_v2", "deepseek_v3"):
+            return int((self.extra or {}).get("qk_rope_head_dim") or 64)
+        return self.head_dim
+
     def rope_inv_freq(self):
-        """(inv_freq tensor [head_dim/2] fp32, attention scaling factor) incl. the llama3, linear
+        """(inv_freq tensor [rope_dim/2] fp32, attention scaling factor) incl. the llama3, linear
         and yarn variants of ``rope_scaling``."""
         import torch
 
-        D = self.head_dim
+        D = self.rope_dim()
         inv = 1.0 / (self.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
         scale = 1.0
         rs = self.rope_scaling
@@ -352,6 +390,9 @@ _ARCH_NAME = {
     "gemma": "GemmaForCausalLM",
     "gemma2": "Gemma2ForCausalLM",
     "gemma3_text": "Gemma3ForCausalLM",
+    "deepseek_v2": "DeepseekV2ForCausalLM",
+    "deepseek_v3": "DeepseekV3ForCausalLM",
+    "gpt_oss": "GptOssForCausalLM",
 }
 
 

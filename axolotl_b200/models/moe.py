@@ -33,6 +33,29 @@ def route_topk(router_logits, k, norm_topk_prob=True):
     return w, idx, probs
 
 
+def route_deepseek(router_logits, k, *, scoring="sigmoid", bias=None, n_group=1, topk_group=1, group_score="top2",
+                   norm_topk_prob=True, scale=1.0):
+    """DeepSeek-V2 / V3 routing. Scores are sigmoid (V3) or softmax (V2) of the router logits; with ``n_group`` > 1
+    only the experts of the ``topk_group`` best groups compete (a group is rated by the sum of its two best
+    biased scores in V3, by its best score in V2); ``bias`` (V3 ``e_score_correction_bias``) steers the CHOICE
+    only, the mixing weights are the unbiased scores, optionally renormalised, times ``scale``."""
+    lf = router_logits.float()
+    scores = torch.sigmoid(lf) if scoring == "sigmoid" else torch.softmax(lf, -1)
+    choice = scores + bias.float()[None] if bias is not None else scores
+    T, E = scores.shape
+    if n_group > 1:
+        g = choice.view(T, n_group, E // n_group)
+        rate = g.topk(2, dim=-1)[0].sum(-1) if group_score == "top2" else g.max(-1)[0]
+        keep = torch.zeros_like(rate, dtype=torch.bool).scatter_(1, rate.topk(topk_group, dim=-1)[1], True)
+        choice = choice.masked_fill(~keep[:, :, None].expand(T, n_group, E // n_group).reshape(T, E),
+                                    0.0)
+    idx = choice.topk(k, dim=-1)[1]
+    w = scores.gather(1, idx)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * scale, idx, scores
+
+
 def load_balance_loss(probs, idx, num_experts):
     """E * sum_e (fraction of routed slots on e) * (mean router prob of e)."""
     T, k = idx.shape
@@ -56,6 +79,12 @@ class Experts(nn.Module):
         self.lora_r = 0
         self.scaling = 1.0
         self.expert_offset = 0     # first global expert id held locally (expert parallelism)
+        self.gate_up_bias = None   # [E, 2I] / [E, H] per-expert biases (gpt-oss)
+        self.down_bias = None
+
+    def add_biases(self, dtype, device):
+        self.gate_up_bias = nn.Parameter(torch.zeros(self.E, 2 * self.I, dtype=dtype, device=device))
+        self.down_bias = nn.Parameter(torch.zeros(self.E, self.H, dtype=dtype, device=device))
 
     # ------------------------------------------------------------------ LoRA (PEFT target_parameters layout)
     def add_lora(self, r, alpha, use_rslora=False, dtype=torch.float32):
@@ -110,11 +139,15 @@ class Experts(nn.Module):
             if use_lora:
                 A, B = self.expert_lora("gate_up", e)
                 gu = gu + self.scaling * ((xe @ A.to(xe.dtype).t()) @ B.to(xe.dtype).t())
+            if self.gate_up_bias is not None:
+                gu = gu + self.gate_up_bias[e].to(gu.dtype)
             h = Fn.glu(gu, self.act, self.glu_limit)
             y = linear(h, self.expert_weight("down", e))
             if use_lora:
                 A, B = self.expert_lora("down", e)
                 y = y + self.scaling * ((h @ A.to(h.dtype).t()) @ B.to(h.dtype).t())
+            if self.down_bias is not None:
+                y = y + self.down_bias[e].to(y.dtype)
             outs.append(y)
         if not outs:
             return x_sorted.new_zeros((0, self.H))
@@ -169,6 +202,32 @@ class SparseMoE(nn.Module):
 
             self.shared_expert = MLP(cfg.hidden_size, shared_I, cfg.hidden_act, False, dtype, device)
             self.shared_expert_gate = nn.Parameter(torch.empty(1, cfg.hidden_size, dtype=dtype, device=device))
+        # gpt-oss: router and experts carry biases; the k best LOGITS are chosen, then soft-maxed among themselves
+        self.router_bias = None
+        if cfg.model_type == "gpt_oss":
+            self.router_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=dtype, device=device))
+            self.experts.add_biases(dtype, device)
+        # DeepSeek-V2 / V3: grouped (sigmoid) routing, always-on shared experts, scaled mixing weights
+        self.deepseek = None
+        self.shared_experts = None
+        self.e_score_correction_bias = None
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
+            from .transformer import MLP
+
+            ex = cfg.extra or {}
+            v3 = cfg.model_type == "deepseek_v3"
+            grouped = v3 or ex.get("topk_method") == "group_limited_greedy"
+            self.deepseek = dict(scoring="sigmoid" if v3 else (ex.get("scoring_func") or "softmax"),
+                                 n_group=int(ex.get("n_group") or 1) if grouped else 1,
+                                 topk_group=int(ex.get("topk_group") or 1), group_score="top2" if v3 else "max",
+                                 norm_topk_prob=bool(cfg.norm_topk_prob), scale=float(ex.get("routed_scaling_factor") or 1.0))
+            if v3:
+                self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
+                                                            requires_grad=False)
+            n_shared = int(ex.get("n_shared_experts") or 0)
+            if n_shared:
+                self.shared_experts = MLP(cfg.hidden_size, cfg.moe_intermediate_size * n_shared, cfg.hidden_act, False,
+                                          dtype, device)
 
     def _shared(self, x):
         g = self.shared_expert_gate
@@ -187,12 +246,22 @@ class SparseMoE(nn.Module):
             y = y + _DenseRouterGrad.apply(self._last_probs, x.detach(), self._last_idx, self)
         if self.shared_expert is not None:
             y = y + self._shared(x)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x)
         return y, aux
 
     def _routed(self, x):
         T, H = x.shape
-        logits = linear(x, self.gate)
-        w, idx, probs = route_topk(logits, self.k, self.norm_topk_prob)
+        if self.deepseek is not None:
+            logits = x.float() @ self.gate.float().t()       # HF keeps this router in fp32
+            w, idx, probs = route_deepseek(logits, self.k, bias=self.e_score_correction_bias, **self.deepseek)
+        elif self.router_bias is not None:
+            logits = linear(x, self.gate).float() + self.router_bias.float()
+            top, idx = torch.topk(logits, self.k, dim=-1)
+            w, probs = torch.softmax(top, -1), torch.softmax(logits, -1)
+        else:
+            logits = linear(x, self.gate)
+            w, idx, probs = route_topk(logits, self.k, self.norm_topk_prob)
         if self.dense_mixer:
             self._last_probs, self._last_idx = probs, idx
         aux = load_balance_loss(probs, idx, self.E) if self.training or self.aux_coef else None

@@ -48,7 +48,10 @@ class Attention(nn.Module):
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
-        self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=False, dtype=dtype, device=device)
+        self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=cfg.model_type == "gpt_oss" and cfg.attention_bias,
+                                  dtype=dtype, device=device)
+        # gpt-oss: one learned "sink" logit per head in every softmax denominator
+        self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if cfg.model_type == "gpt_oss" else None
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
@@ -88,7 +91,7 @@ class Attention(nn.Module):
             if getattr(meta, "cp", False):
                 raise NotImplementedError("sliding-window attention is not available with context parallelism")
             meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
-        return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale, softcap=self.softcap)
+        return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale, softcap=self.softcap, sinks=self.sinks)
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         return self.o_proj(self.core(self.pre(x, positions, inv_freq, attn_scale), meta))
@@ -131,7 +134,12 @@ class DecoderLayer(nn.Module):
         super().__init__()
         off = cfg.norm_offset()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
-        self.self_attn = Attention(cfg, dtype, device)
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
+            from .mla import MLAttention
+
+            self.self_attn = MLAttention(cfg, dtype, device)
+        else:
+            self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
         self.self_attn.use_rope = cfg.uses_rope(idx)
         self.self_attn.window = cfg.sliding_window(idx)
@@ -314,6 +322,8 @@ class CausalLM(nn.Module):
         for m in self.modules():
             if isinstance(m, RMSNorm) and m.offset:
                 m.weight.fill_(1.0 - m.offset)
+            if isinstance(m, Attention) and m.sinks is not None:
+                m.sinks.normal_(0.0, std, generator=gen)
         return self
 
     @torch.no_grad()
@@ -476,7 +486,8 @@ class CausalLM(nn.Module):
         """Greedy / sampled continuation of one prompt; returns [1, prompt + new]. With ``use_cache``
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
-        kernel_ok = self.config.head_dim in (64, 128) and not self.config.attn_softcap()   # what the decode kernel takes
+        kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
+                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -56,6 +56,8 @@ _CUDA_SIGS = {
     "axb_ep_stage_rows": [vp, i32, i32, vp, vp, i64, i32, vp],
     "axb_ep_reduce_rows": [vp, i32, i32, vp, vp, i64, i32, vp],
     "axb_peer_put_i32": [vp, vp, i64, vp],
+    "axb_ep_gather_tables": [vp, i32, i64, vp, vp],
+    "axb_ep_put_scalars": [vp, i32, vp, vp, vp, i64, i64, vp],
     "axb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
     "axb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_rope_qk": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp, vp, vp, f32, vp],

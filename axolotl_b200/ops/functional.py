@@ -185,10 +185,12 @@ def rope_qk_(qkv, positions, inv_freq, Hq, Hk, D, attn_scale=1.0, q_norm_w=None,
 
 
 # --------------------------------------------------------------------------------------- GLU
-_ACT_KIND = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 1}
+_ACT_KIND = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 1, "gpt_oss_swiglu": 2}
 
 
 def _act_ref(g, kind):
+    if kind == 2:       # gpt-oss experts: g * sigmoid(1.702 g); the GLU multiplies by (up + 1)
+        return g * torch.sigmoid(1.702 * g)
     return F.silu(g) if kind == 0 else F.gelu(g, approximate="tanh")
 
 
@@ -202,7 +204,7 @@ class _GLU(torch.autograd.Function):
             g, u = gu[..., :I].float(), gu[..., I:].float()
             if ctx.limit > 0:
                 g, u = g.clamp(max=ctx.limit), u.clamp(-ctx.limit, ctx.limit)
-            return (_act_ref(g, kind) * u).to(gu.dtype)
+            return (_act_ref(g, kind) * (u + 1.0 if kind == 2 else u)).to(gu.dtype)
         lib = _lib.cuda_lib()
         gu2 = gu.reshape(-1, 2 * I)
         h = torch.empty((gu2.shape[0], I), dtype=gu.dtype, device=gu.device)
@@ -224,7 +226,7 @@ class _GLU(torch.autograd.Function):
                 a = _act_ref(g, ctx.kind)
                 (da,) = torch.autograd.grad(a.sum(), g)
             dhf = dh.float()
-            dg, du = dhf * uc * da, dhf * a.detach()
+            dg, du = dhf * (uc + 1.0 if ctx.kind == 2 else uc) * da, dhf * a.detach()
             if L > 0:
                 dg = dg * (g_raw <= L)
                 du = du * ((u_raw >= -L) & (u_raw <= L))
@@ -429,7 +431,7 @@ class AttnMeta:
         return AttnMeta(cu, device, causal)
 
 
-def _attn_ref(q, k, v, cu, scale, causal=True, window=0, softcap=0.0):
+def _attn_ref(q, k, v, cu, scale, causal=True, window=0, softcap=0.0, sinks=None):
     # q [T,Hq,D], k [T,Hk,D], v [T,Hk,Dv]; per-document (causal or bidirectional) attention in fp32
     T, Hq, D = q.shape
     Hk = k.shape[1]
@@ -448,13 +450,32 @@ def _attn_ref(q, k, v, cu, scale, causal=True, window=0, softcap=0.0):
             if window:
                 mask &= ~torch.ones(e - s, e - s, dtype=torch.bool, device=q.device).tril(-int(window))
             sc = sc.masked_fill(~mask, float("-inf"))
-        out[s:e] = (sc.softmax(-1) @ vv).transpose(0, 1).to(q.dtype)
+        if sinks is not None:    # one extra logit per head that takes probability mass and carries no value
+            sk = sinks.float()[:, None, None].expand(Hq, e - s, 1)
+            pr = torch.cat([sc, sk], -1).softmax(-1)[..., :-1]
+        else:
+            pr = sc.softmax(-1)
+        out[s:e] = (pr @ vv).transpose(0, 1).to(q.dtype)
     return out
+
+
+_LOG2E = 1.4426950408889634
+
+
+def _apply_sinks(out, lse2, sinks, Hq):
+    """Attention sinks as a rescale of the kernel's result: with one more logit ``sink_h`` in every softmax
+    denominator, O' = O * exp(lse - lse') and lse' = logaddexp(lse, sink). Returns (O', lse' in the log2 domain)."""
+    T = out.shape[0]
+    s2 = sinks.float()[:, None] * _LOG2E
+    lse_new = torch.logaddexp2(lse2, s2.expand_as(lse2))
+    factor = torch.exp2(lse2 - lse_new)                         # [Hq, T]
+    out = (out.view(T, Hq, -1).float() * factor.t()[:, :, None]).to(out.dtype).view(T, -1)
+    return out, lse_new
 
 
 class _FlashVarlen(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, meta, Hq, Hk, D, scale):
+    def forward(ctx, qkv, meta, Hq, Hk, D, scale, sinks=None):
         T = qkv.shape[0]
         ctx.meta, ctx.dims = meta, (Hq, Hk, D, scale)
         if not qkv.is_cuda:
@@ -468,12 +489,17 @@ class _FlashVarlen(torch.autograd.Function):
                                      out.data_ptr(), out.stride(0), lse2.data_ptr(), scale,
                                      _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()),
             "flash_varlen_fwd")
-        ctx.save_for_backward(qkv, out, lse2)
+        ctx.has_sinks = sinks is not None
+        if sinks is not None:
+            out, lse2 = _apply_sinks(out, lse2, sinks, Hq)
+            ctx.save_for_backward(qkv, out, lse2, sinks)
+        else:
+            ctx.save_for_backward(qkv, out, lse2)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse2 = ctx.saved_tensors
+        qkv, out, lse2 = ctx.saved_tensors[:3]
         Hq, Hk, D, scale = ctx.dims
         meta = ctx.meta
         T = qkv.shape[0]
@@ -490,7 +516,14 @@ class _FlashVarlen(torch.autograd.Function):
                                      dq_acc.data_ptr(), delta.data_ptr(), scale,
                                      _lib.status_word(qkv.device).data_ptr(), _lib.stream_ptr()),
             "flash_varlen_bwd")
-        return dqkv, None, None, None, None, None
+        dsinks = None
+        if ctx.has_sinks:
+            sinks = ctx.saved_tensors[3]
+            if ctx.needs_input_grad[6]:
+                # d sink_h = - sum_t p_sink[h, t] * <dO_t, O'_t>; the kernel left the row dot products in `delta`
+                p_sink = torch.exp2(sinks.float()[:, None] * _LOG2E - lse2)
+                dsinks = (-(p_sink * delta).sum(1)).to(sinks.dtype)
+        return dqkv, None, None, None, None, None, dsinks
 
 
 class _FlashWide(torch.autograd.Function):
@@ -533,17 +566,20 @@ class _FlashWide(torch.autograd.Function):
 WIDE_HEADS = ((256, 256), (192, 128))
 
 
-def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.0):
+def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.0, sinks=None):
     """Attention inside each document of a packed row: causal, or bidirectional when the
     metadata was built with ``causal=False`` (masked-diffusion and encoder-style objectives).
 
     ``qkv`` is the fused projection [T, Hq*D + Hk*D + Hk*Dv] (q heads, then k heads, then v heads; ``Dv``
     defaults to ``D``). Returns [T, Hq * Dv]. Head widths 64 / 128 run the double-buffered kernels;
     (D, Dv) = (256, 256) or (192, 128), and any ``softcap`` (scores become softcap * tanh(scores / softcap))
-    at those widths, run the wide kernels.
+    at those widths, run the wide kernels. ``sinks`` [Hq]: one learned logit per head joins every softmax
+    denominator (gpt-oss); applied as a rescale of the kernel's output and log-sum-exp.
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     Dv = D if Dv is None else Dv
+    if sinks is not None and qkv.is_cuda and ((D, Dv) in WIDE_HEADS or getattr(meta, "cp", False)):
+        raise NotImplementedError("attention sinks are available for head widths 64 / 128 without context parallelism")
     if qkv.is_cuda and ((D, Dv) in WIDE_HEADS):
         if getattr(meta, "cp", False):
             raise NotImplementedError("context parallelism is not available for head widths above 128")
@@ -557,13 +593,13 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.
 
         return flash_varlen_cp(qkv, meta, Hq, Hk, D, scale)
     if qkv.is_cuda:
-        return _FlashVarlen.apply(qkv, meta, Hq, Hk, D, scale)
+        return _FlashVarlen.apply(qkv, meta, Hq, Hk, D, scale, sinks)
     T = qkv.shape[0]
     q = qkv[:, : Hq * D].reshape(T, Hq, D)
     k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
     v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, Dv)
     return _attn_ref(q, k, v, meta.cu_seqlens_host, scale, getattr(meta, "causal", True),
-                     getattr(meta, "window", 0), softcap).reshape(T, Hq * Dv)
+                     getattr(meta, "window", 0), softcap, sinks).reshape(T, Hq * Dv)
 
 
 @torch.no_grad()

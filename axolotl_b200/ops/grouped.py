@@ -379,9 +379,16 @@ def grouped_experts_padded(experts, x, lay):
     L = experts.lora if use_lora else None
     gu = _GroupedProj.apply(x, experts, "gate_up", lay, L["gate_up_A"] if L else None, L["gate_up_B"] if L else None,
                             float(experts.scaling))
+    row_e = None
+    if getattr(experts, "gate_up_bias", None) is not None:     # per-expert biases (gpt-oss): one row gather + add
+        row_e = lay.blk_expert.long().repeat_interleave(BLOCK)
+        gu = gu + experts.gate_up_bias.to(gu.dtype).index_select(0, row_e)
     h = Fn.glu(gu, experts.act, getattr(experts, "glu_limit", None))
-    return _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
-                              float(experts.scaling))
+    y = _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
+                           float(experts.scaling))
+    if row_e is not None:
+        y = y + experts.down_bias.to(y.dtype).index_select(0, row_e)
+    return y
 
 
 @torch.no_grad()

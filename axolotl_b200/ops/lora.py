@@ -252,7 +252,7 @@ def glu_mlp(x, gate_up, down, kind, limit, adapters_on=True):
     """``down(act(gate(x)) * up(x))`` through ``_GLUMLPFn`` when both projections qualify and the problem
     is large enough for the CTA-pair kernel's GLU epilogues; returns None otherwise (the caller then
     runs the projections and the GLU kernel one by one)."""
-    if not x.is_cuda or x.dtype != torch.bfloat16:
+    if not x.is_cuda or x.dtype != torch.bfloat16 or kind not in (0, 1):   # the epilogues know silu and tanh-gelu
         return None
     from ..models.layers import FusedLinear
 

@@ -2,10 +2,14 @@
 back over NVLink peer memory.
 
 Per MoE layer and micro batch:
-1. routing is local (softmax -> top-k); the slot lists (source row, local expert id, routing weight)
-   are exchanged with one small all-to-all (metadata only, a few KB);
-2. DISPATCH: every rank copies its hidden states into a symmetric buffer; after one flag barrier the
-   destination ranks *pull* the rows routed to their experts with peer loads: each needed token once
+1. routing is local (softmax -> top-k); every rank writes its routing table ([T, k] expert ids and
+   weights) next to its hidden states in symmetric memory. After ONE flag barrier each rank reads all
+   tables with peer loads and builds its plan on the device (which slots run on its experts, in
+   expert-sorted padded order) with static shapes: buffers are sized by a capacity factor
+   (``AXB_EP_CAPACITY``, default 1.5 x the mean load; never more than the worst case), an overflow is
+   recorded on the device and raised at the end of the step. No NCCL call and no host synchronisation
+   happens on the layer path;
+2. DISPATCH: the destination ranks *pull* the rows routed to their experts with peer loads: each needed token once
    into a local staging area (``axb_ep_stage_rows``; top-k routing puts several slots of a token on
    the same rank), then a local gather into the padded expert-sorted layout
    (``axb_ep_gather_rows``) -- no send buffers, no host barrier;
@@ -18,7 +22,8 @@ The backward pass is the mirror image (combine^T = gather of dY rows, dispatch^T
 rows). Expert weights and expert-LoRA slices follow the reference's layout rules
 (src/axolotl/integrations/expert_parallel/shard.py:56-393): rank r owns experts
 [r*E/ep, (r+1)*E/ep); A is expert-major ([E*r, in] rows), B is rank-major ([out, r, E] view).
-On CPU (gloo) the payload moves with ``all_to_all_single`` so the same logic is testable without GPUs.
+On CPU (gloo) the plan and the payload move with ``all_to_all_single`` (host-side split sizes) so the same
+logic is testable without GPUs.
 """
 from __future__ import annotations
 
@@ -35,7 +40,7 @@ class _Plan:
     """Routing plan of one MoE layer call (shared by forward and backward)."""
     __slots__ = ("T", "k", "H", "send_order", "send_counts", "recv_counts", "recv_src_rank", "recv_src_row",
                  "recv_weight", "local_order", "expert_counts", "n_recv", "send_tok", "lay", "pad_src_rank", "pad_src_row",
-                 "pad_weight", "need", "sent")
+                 "pad_weight", "pad_src_slot", "need", "sent", "x_buf")
 
 
 class ExpertParallelGroup:
@@ -57,6 +62,13 @@ class ExpertParallelGroup:
         # 370.9 ms with the row kernels, 384.3 ms with the copy engines (more bytes, one copy per peer);
         # on 8 GPUs 442.7 ms against 592.1 ms.
         self.stage_by = os.environ.get("AXB_EP_STAGE", "sm")
+        # Device-side plan: rows this rank may receive per layer call = capacity_factor x (its own slots), capped
+        # at the worst case (every slot of every rank). AXB_EP_PLAN=host keeps the NCCL + host-sync plan.
+        self.capacity_factor = float(os.environ.get("AXB_EP_CAPACITY", "1.5"))
+        self.device_plan = self.fused and os.environ.get("AXB_EP_PLAN", "device") != "host"
+        self.t_bufs = self.s_bufs = None
+        self.kt = self.ks = 0
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device) if self.fused else None
         if self.fused:
             self.sync = PeerSync(self.device, group)
 
@@ -176,6 +188,126 @@ class ExpertParallelGroup:
                 p.sent[dest.long() * T + torch.arange(T * k, device=dev) // k] = 1
         return p
 
+    # ------------------------------------------------------------------ device-side plan
+    def _capacity(self, n):
+        cap = min(self.size * n, int(-(-self.capacity_factor * n // 1)))
+        return max(128, (cap + 127) // 128 * 128)
+
+    def _ensure_tables(self, n):
+        if self.t_bufs is None or self.t_bufs[0].tensor.numel() < 2 * n:
+            self.t_bufs = [SymmBuffer(2 * n, torch.int32, self.device, self.group, use_multicast=False) for _ in range(2)]
+            self.s_bufs = [SymmBuffer(n, torch.float32, self.device, self.group, use_multicast=False) for _ in range(2)]
+            dist.barrier(self.group)
+
+    def _publish(self, x, idx, w):
+        """This rank's token rows and routing table into symmetric memory; one barrier publishes both."""
+        T, H = x.shape
+        n = idx.numel()
+        self._ensure(T, H)
+        self._ensure_tables(n)
+        buf = self.x_bufs[self.kx & 1]
+        self.kx += 1
+        buf.tensor[: T * H].view(T, H).copy_(x.detach())
+        tab = self.t_bufs[self.kt & 1]
+        self.kt += 1
+        tab.tensor[:n].copy_(idx.reshape(-1))
+        tab.tensor[n:2 * n].copy_(w.detach().reshape(-1).float().view(torch.int32))
+        self.sync.barrier(channel=6)
+        return buf, tab
+
+    def _make_plan_device(self, idx, H, tab):
+        """The plan from every rank's routing table, computed on the device with static shapes."""
+        from ..ops.grouped import BLOCK, GroupLayout
+
+        T, k = idx.shape
+        n, W, El, dev = T * k, self.size, self.E_local, idx.device
+        allt = torch.empty((W, 2, n), dtype=torch.int32, device=dev)
+        _lib.check_rc(_lib.cuda_lib().axb_ep_gather_tables(tab.ptrs_c, W, 2 * n, allt.data_ptr(), _lib.stream_ptr()),
+                      "ep_gather_tables")
+        return self._plan_from_tables(allt[:, 0].reshape(-1), allt[:, 1].reshape(-1).view(torch.float32), idx, H)
+
+    def _plan_from_tables(self, all_idx, all_w, idx, H):
+        """``all_idx`` / ``all_w``: the routing tables of all ranks, rank-major, flattened [W * T * k]."""
+        from ..ops.grouped import BLOCK, GroupLayout
+
+        T, k = idx.shape
+        n, W, El, dev = T * k, self.size, self.E_local, idx.device
+        mine = torch.div(all_idx, El, rounding_mode="floor") == self.rank
+        flat = torch.where(mine, all_idx % El, El)                      # local expert id, El = not for this rank
+        cap = self._capacity(n)
+        order = torch.argsort(flat, stable=True)[:cap]                  # expert-sorted, rank-major inside an expert
+        e_sorted = flat[order]
+        valid = e_sorted < El
+        counts = torch.zeros(El + 1, dtype=torch.int64, device=dev).scatter_add_(
+            0, flat.long(), torch.ones(flat.numel(), dtype=torch.int64, device=dev))[:El]
+        if self.overflow is None:
+            self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.overflow += (counts.sum() > cap).to(torch.int32)
+        padded = (counts + (BLOCK - 1)) // BLOCK * BLOCK
+        seg_end = padded.cumsum(0)
+        seg_start = seg_end - padded
+        first = counts.cumsum(0) - counts
+        lay = GroupLayout.__new__(GroupLayout)
+        lay.E, lay.n_rows = El, cap
+        lay.max_blocks = cap // BLOCK + El
+        lay.max_rows = lay.max_blocks * BLOCK
+        e_c = e_sorted.clamp(max=El - 1).long()
+        dump = lay.max_rows                                              # rows beyond the received ones land here
+        dest = torch.where(valid, seg_start[e_c] + (torch.arange(order.numel(), device=dev) - first[e_c]), dump)
+        dest = dest.clamp(max=dump)                                      # (an overflowing call is reported, not trusted)
+        lay.dest = dest
+        blk_row = torch.arange(lay.max_blocks, device=dev) * BLOCK
+        lay.blk_expert = torch.searchsorted(seg_end, blk_row, right=True).clamp(max=El - 1).to(torch.int32)
+        lay.n_blocks = (seg_end[-1:] // BLOCK).clamp(max=lay.max_blocks).to(torch.int32)
+        lay.seg_start = seg_start.to(torch.int32)
+        lay.seg_rows = padded.to(torch.int32)
+        src_rank = torch.div(order, n, rounding_mode="floor").to(torch.int32)
+        src_slot = (order % n).to(torch.int32)
+        p = _Plan()
+        p.T, p.k, p.H, p.lay = T, k, H, lay
+        p.n_recv = cap
+        neg = torch.full((), -1, dtype=torch.int32, device=dev)
+        p.pad_src_rank = torch.full((lay.max_rows + 1,), -1, dtype=torch.int32, device=dev)
+        p.pad_src_rank[dest] = torch.where(valid, src_rank, neg)
+        p.pad_src_rank = p.pad_src_rank[: lay.max_rows]
+        p.pad_src_slot = torch.full((lay.max_rows + 1,), -1, dtype=torch.int32, device=dev)
+        p.pad_src_slot[dest] = torch.where(valid, src_slot, neg)
+        p.pad_src_slot = p.pad_src_slot[: lay.max_rows]
+        p.pad_src_row = torch.div(p.pad_src_slot.clamp(min=0), k, rounding_mode="floor").to(torch.int32)
+        p.pad_weight = torch.zeros(lay.max_rows + 1, dtype=torch.float32, device=dev)
+        p.pad_weight[dest] = torch.where(valid, all_w[order], torch.zeros((), device=dev))
+        p.pad_weight = p.pad_weight[: lay.max_rows]
+        if self.dedup:
+            lin = torch.where(valid, src_rank.long() * T + torch.div(src_slot, k, rounding_mode="floor").long(), W * T)
+            p.need = torch.zeros(W * T + 1, dtype=torch.uint8, device=dev)
+            p.need[lin] = 1
+            dest_rank = torch.div(idx.reshape(-1), El, rounding_mode="floor").long()
+            p.sent = torch.zeros(W * T, dtype=torch.uint8, device=dev)
+            p.sent[dest_rank * T + torch.arange(n, device=dev) // k] = 1
+        return p
+
+    def check_overflow(self):
+        """Raises when a layer call since the last check received more rows than the capacity allows
+        (one host synchronisation; the trainer calls it once per optimizer step)."""
+        if self.overflow is None:
+            return
+        if int(self.overflow.item()):
+            self.overflow.zero_()
+            raise RuntimeError(
+                f"expert parallelism: a rank received more than capacity_factor={self.capacity_factor} x its own "
+                f"slots in one layer call, rows were dropped; raise AXB_EP_CAPACITY (up to the group size)")
+
+    def return_slot_scalars_fused(self, vals_pad, plan):
+        """Per-slot scalars of the padded rows -> [T, k] at the rank that routed the slot (peer stores)."""
+        n = plan.T * plan.k
+        sb = self.s_bufs[self.ks & 1]
+        self.ks += 1
+        _lib.check_rc(_lib.cuda_lib().axb_ep_put_scalars(
+            sb.ptrs_c, self.size, plan.pad_src_rank.data_ptr(), plan.pad_src_slot.data_ptr(),
+            vals_pad.contiguous().data_ptr(), plan.lay.max_rows, n, _lib.stream_ptr()), "ep_put_scalars")
+        self.sync.barrier(channel=8)
+        return sb.tensor[:n].view(plan.T, plan.k).clone()
+
     def _ensure(self, T, H):
         if not self.fused:
             return
@@ -206,11 +338,14 @@ class ExpertParallelGroup:
             return _a2a_rows(x[plan.send_tok.long()], plan.recv_counts, plan.send_counts, self.group)[plan.local_order]
         lib = _lib.cuda_lib()
         T, H = x.shape
-        self._ensure(T, H)
-        buf = self.x_bufs[self.kx & 1]
-        self.kx += 1
-        buf.tensor[: T * H].view(T, H).copy_(x)
-        self.sync.barrier(channel=6)
+        buf = getattr(plan, "x_buf", None)
+        plan.x_buf = None
+        if buf is None:      # (the forward dispatch of the device-side plan published x with the routing table)
+            self._ensure(T, H)
+            buf = self.x_bufs[self.kx & 1]
+            self.kx += 1
+            buf.tensor[: T * H].view(T, H).copy_(x)
+            self.sync.barrier(channel=6)
         n = plan.lay.max_rows
         out = torch.empty((n, H), dtype=x.dtype, device=x.device)
         dots = torch.empty(n, dtype=torch.float32, device=x.device) if dot_with is not None else None
@@ -301,7 +436,13 @@ class ExpertParallelGroup:
 
     # ------------------------------------------------------------------ layer entry
     def dispatch_compute_combine(self, experts, x, w, idx):
-        plan = self._make_plan(idx, w, x.shape[1])
+        if self.device_plan:
+            x = x.contiguous()
+            buf, tab = self._publish(x, idx.to(torch.int32), w)
+            plan = self._make_plan_device(idx, x.shape[1], tab)
+            plan.x_buf = buf
+        else:
+            plan = self._make_plan(idx, w, x.shape[1])
         xs = _Dispatch.apply(x, self, plan)
         if self.fused:
             from ..ops.grouped import grouped_experts_padded
@@ -344,7 +485,10 @@ class _Combine(torch.autograd.Function):
         if ep.fused:   # one peer gather: weight-scaled dY rows and <dY row, expert output row>
             if ctx.needs_input_grad[1]:
                 dys, dots = ep.pull_rows(dy.contiguous(), plan, weighted=True, dot_with=ys.contiguous())
-                dw = ep.return_slot_scalars(dots[plan.lay.dest], plan).to(ctx.w_dtype)
+                if ep.device_plan:
+                    dw = ep.return_slot_scalars_fused(dots, plan).to(ctx.w_dtype)
+                else:
+                    dw = ep.return_slot_scalars(dots[plan.lay.dest], plan).to(ctx.w_dtype)
             else:
                 dys, dw = ep.pull_rows(dy.contiguous(), plan, weighted=True), None
             return dys, dw, None, None

@@ -98,6 +98,8 @@ class ParallelRuntime:
         pass
 
     def after_optimizer_step(self):
+        if self.ep is not None:
+            self.ep.check_overflow()
         if self.fsdp is not None:
             self.fsdp.end_of_step()
 

@@ -441,3 +441,78 @@ def test_gemma_family_matches_hf(tmp_path, model_type):
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+@pytest.mark.parametrize("model_type", ["deepseek_v3", "deepseek_v2"])
+def test_deepseek_latent_attention_and_grouped_routing_match_hf(tmp_path, model_type):
+    """Low-rank q / kv projections with their norms, shared rotary key part (interleaved pairs in V3), 192/128-style
+    head widths, dense first layer, sigmoid group-limited routing with the correction bias (V3) or softmax routing
+    (V2), shared experts, routed scaling factor."""
+    d = dict(model_type=model_type, vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+             num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=2,
+             num_experts_per_tok=3, n_group=4, topk_group=2, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
+             qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=12, routed_scaling_factor=2.5, norm_topk_prob=True,
+             rms_norm_eps=1e-6, rope_theta=10000.0, hidden_act="silu", tie_word_embeddings=False,
+             max_position_embeddings=256, moe_layer_freq=1)
+    if model_type == "deepseek_v2":
+        # (V2-Lite style: plain top-k; the HF implementation of V2's group-limited variant does not run in this
+        # transformers version)
+        d.update(topk_method="greedy", scoring_func="softmax", norm_topk_prob=False, q_lora_rank=None, aux_loss_alpha=0.0)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(13)
+    with torch.no_grad():
+        for l in ours.layers:
+            if getattr(l.mlp, "e_score_correction_bias", None) is not None:
+                l.mlp.e_score_correction_bias.uniform_(-0.2, 0.2)
+            l.self_attn.kv_a_layernorm.weight.uniform_(0.5, 1.5)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [29, 40]
+    ids, pos = _packed_inputs(320, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+def test_gpt_oss_sinks_biased_experts_and_alternating_windows_match_hf(tmp_path):
+    """Attention sinks, q/k/v/o biases, sliding window on alternate layers, router with bias choosing by logits,
+    experts with biases and the clamped (up + 1) * g * sigmoid(1.702 g) activation, interleaved gate/up storage."""
+    d = dict(model_type="gpt_oss", vocab_size=300, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
+             sliding_window=8, layer_types=["sliding_attention", "full_attention"], rms_norm_eps=1e-5,
+             rope_theta=10000.0, tie_word_embeddings=False, max_position_embeddings=256, attention_bias=True,
+             swiglu_limit=7.0, rope_scaling=None, router_aux_loss_coef=0.0)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(17)
+    with torch.no_grad():
+        for n, p in ours.named_parameters():
+            if n.endswith(("bias", "router_bias", "gate_up_bias", "down_bias")):
+                p.normal_(0, 0.05)
+        for l in ours.layers:                      # values large enough for the clamps and the sinks to matter
+            l.mlp.experts.gate_up_proj.mul_(30.0)
+            l.self_attn.sinks.normal_(0, 1.0)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [33, 21]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    # the sinks receive a gradient
+    ours.train()
+    ours(ids, pos, ids.clone()).loss.backward()
+    assert ours.layers[0].self_attn.sinks.grad.abs().sum() > 0

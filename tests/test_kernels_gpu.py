@@ -1034,3 +1034,72 @@ print("BOUNDS_OK")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "BOUNDS_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-3000:]
+
+
+@pytest.mark.parametrize("name", ["tiny-gemma2", "tiny-gemma3"])
+def test_gemma_models_on_gpu_match_cpu_fp32(name):
+    """Gemma 2 / 3 end to end on the device (head width 256 attention, soft caps, sandwich norms, sliding and
+    global layers, local rope base) against the same weights in fp32 on the CPU: loss and LoRA-free gradients."""
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.layers import RMSNorm
+    from axolotl_b200.models.transformer import CausalLM
+    torch.manual_seed(50)
+    cfg = preset(name)
+    ref = CausalLM(cfg, dtype=torch.float32).init_weights(4)
+    with torch.no_grad():
+        for m in ref.modules():
+            if isinstance(m, RMSNorm):
+                m.weight.uniform_(-0.2, 0.2)
+        for p in ref.parameters():                      # values the bf16 copy represents exactly
+            p.copy_(p.bfloat16().float())
+    dev = CausalLM(cfg, dtype=torch.bfloat16, device=_dev())
+    dev.load_state_dict(ref.state_dict())
+    lens = [150, 61, 300]
+    ids = torch.cat([torch.randint(3, cfg.vocab_size, (l,)) for l in lens])[None]
+    pos = torch.cat([torch.arange(l) for l in lens])[None].to(torch.int32)
+    labels = ids.clone()
+    labels[:, :20] = -100
+    out_d = dev(ids, pos, labels)
+    out_d.loss.backward()
+    _check_status()
+    out_c = ref(ids, pos, labels)
+    out_c.loss.backward()
+    assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item())
+    for pick in ("layers.0.self_attn.qkv_proj.weight", "layers.1.mlp.down_proj.weight", "embed_tokens"):
+        gd = dict(dev.named_parameters())[pick].grad.float().cpu()
+        gc = dict(ref.named_parameters())[pick].grad
+        assert _rel_err(gd, gc) < 6e-2, pick
+
+
+def test_deepseek_v3_latent_attention_model_on_gpu_matches_cpu_fp32():
+    """Latent attention (192-wide q/k, 128-wide v through the wide kernels), grouped sigmoid routing and shared
+    experts on the device against the same weights in fp32 on the CPU."""
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.transformer import CausalLM
+    torch.manual_seed(51)
+    cfg = ModelConfig.from_hf_dict(dict(
+        model_type="deepseek_v3", vocab_size=2048, hidden_size=256, intermediate_size=512, moe_intermediate_size=128,
+        num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2, n_routed_experts=8, n_shared_experts=1,
+        num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=64, kv_lora_rank=64,
+        qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, routed_scaling_factor=2.0, norm_topk_prob=True,
+        rms_norm_eps=1e-6, rope_theta=10000.0, hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=2048))
+    ref = CausalLM(cfg, dtype=torch.float32).init_weights(5)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    dev = CausalLM(cfg, dtype=torch.bfloat16, device=_dev())
+    dev.load_state_dict(ref.state_dict())
+    lens = [140, 260]
+    ids = torch.cat([torch.randint(3, cfg.vocab_size, (l,)) for l in lens])[None]
+    pos = torch.cat([torch.arange(l) for l in lens])[None].to(torch.int32)
+    labels = ids.clone()
+    out_d = dev(ids, pos, labels)
+    out_d.loss.backward()
+    _check_status()
+    out_c = ref(ids, pos, labels)
+    out_c.loss.backward()
+    assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item())
+    for pick in ("layers.0.self_attn.kv_b_proj.weight", "layers.1.self_attn.q_b_proj.weight", "embed_tokens"):
+        gd = dict(dev.named_parameters())[pick].grad.float().cpu()
+        gc = dict(ref.named_parameters())[pick].grad
+        assert _rel_err(gd, gc) < 8e-2, pick

@@ -583,7 +583,10 @@ UNSUPPORTED_KEYS = {
     "use_onebitllms": "1-bit LLM training is not supported",
     "flash_optimum": "BetterTransformer is not used",
     "fp8": "fp8 mixed precision is not implemented; bf16 tensor-core kernels are used",
-    "large_head_attention": "head_dim is limited to 64/128 by the attention kernel",
+    "large_head_attention": "head widths 64, 128, 256 (and 192/128 latent attention) have native kernels; 512 does not",
+    "processor_type": "multimodal training is not available: the data path exists (axolotl_b200.data.multimodal: "
+                      "processing strategies, role masking, collator) but no vision / audio encoder graph does",
+    "freeze_mm_modules": "multimodal training is not available (no vision / audio encoder graph)",
 }
 
 # Reference keys that are accepted and carried through without effect on this framework (their
@@ -593,13 +596,13 @@ INERT_KEYS = {
     "bnb_config_kwargs", "cls_model_config", "dion_lr", "dion_momentum",
     "dion_rank_fraction", "dion_rank_multiple_of", "dpo_generate_during_eval", "dpo_padding_free",
     "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "embeddings_skip_upcast",
-    "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp8_enable_fsdp_float8_all_gather", "freeze_mm_modules", "fused_attn_kernel", "gc_collect_steps",
+    "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp8_enable_fsdp_float8_all_gather", "fused_attn_kernel", "gc_collect_steps",
     "gemma4_hybrid_attn_impl", "gradio_max_new_tokens", "gradio_server_name",
     "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
-    "image_size", "is_falcon_derived_model",
+    "image_size", "is_falcon_derived_model", "role_boundaries",
     "lisa_layers_attribute", "lora_on_cpu", "low_cpu_mem_usage",
     "model_quantization_config_kwargs", "num_dataset_shards_to_save",
-    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "preprocess_iterable", "processor_kwargs", "processor_type", "qgalore_cos_threshold", "qgalore_gamma_proj",
+    "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "preprocess_iterable", "processor_kwargs", "qgalore_cos_threshold", "qgalore_gamma_proj",
     "qgalore_proj_bits", "qgalore_proj_group_size", "qgalore_proj_quant", "qgalore_proj_type", "qgalore_queue_size",
     "qgalore_rank", "qgalore_scale", "qgalore_update_proj_gap", "qlora_sharded_model_loading", "quantize_embedding",
     "ray_num_workers", "ray_run_name", "recompute_layer_types", "relora_prune_method", "resources_per_worker",

@@ -308,49 +308,88 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
         if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
         const float g = p.pts[ps.e];
         const uint8_t* sc_base = p.scale + (long long)ps.e * p.Wn * sc_row_bytes;
-        auto load_scales = [&](int kb) -> uint32_t {
-          if (kb >= nk_main) return 0u;
+        // Block scales are fetched FOUR k blocks ahead (a global load that misses the small L1 left beside
+        // 200 KB of shared memory takes longer than one k block): a 16-byte load per four k blocks of this
+        // thread's weight row in the forward, one 4-byte load per k block (a new weight row each) in dX.
+        const bool vec_ok = !DX && (sc_row_bytes & 15) == 0;
+        auto load_group = [&](int kb0, uint32_t (&out)[4]) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) out[j] = 0u;
+          if (kb0 >= nk_main) return;
           if (!DX) {
             const int n = ps.n0 + ct;
-            return n < p.Wn ? __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)n * sc_row_bytes + kb * 4)) : 0u;
+            if (n >= p.Wn) return;
+            const uint8_t* row = sc_base + (long long)n * sc_row_bytes;
+            if (vec_ok && kb0 * 4 + 16 <= sc_row_bytes) {
+              const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + kb0 * 4));
+              out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (kb0 + j < nk_main) out[j] = __ldg(reinterpret_cast<const uint32_t*>(row + (kb0 + j) * 4));
+            }
+          } else {
+            const int k0 = ps.n0 + half * 64;
+            if (k0 >= p.Wk) return;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int wn = (kb0 + j) * BK + r;
+              if (kb0 + j < nk_main && wn < p.Wn)
+                out[j] = __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)wn * sc_row_bytes + k0 / 16));
+            }
           }
-          const int wn = kb * BK + r, k0 = ps.n0 + half * 64;
-          return (wn < p.Wn && k0 < p.Wk) ? __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)wn * sc_row_bytes + k0 / 16)) : 0u;
         };
-        uint32_t sc_next = load_scales(0);
-        for (int kb = 0; kb < nk; ++kb) {
-          const uint32_t sc4 = sc_next;
-          sc_next = load_scales(kb + 1);
-          if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
-            ok = false;
-            break;
+        uint32_t cur[4], nxt[4];
+        load_group(0, cur);
+        for (int kb0 = 0; kb0 < nk && ok; kb0 += 4) {
+          load_group(kb0 + 4, nxt);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int kb = kb0 + j;
+            if (kb >= nk) break;
+            if (!mbar_wait(&raw_full[stage], phase, p.status, AXB_TIMEOUT_FULL)) {
+              ok = false;
+              break;
+            }
+            if (kb < nk_main) {
+              const uint8_t* raw = sRaw + stage * RAW_BYTES + ct * 32;
+              uint4 w0 = *reinterpret_cast<const uint4*>(raw);
+              uint4 w1 = *reinterpret_cast<const uint4*>(raw + 16);
+              uint32_t sc4 = cur[j];
+              uint8_t* dst_row = sB + stage * B_BYTES + half * 8192 + r * 128;
+              int sw = r & 7;
+              if (DX && half) {
+                // the two halves of a row pair write the same banks: the odd half goes through its eight chunks
+                // in the order 4..7, 0..3 instead
+                const uint4 t4 = w0;
+                w0 = w1;
+                w1 = t4;
+                sc4 = (sc4 >> 16) | (sc4 << 16);
+                sw ^= 4;
+              }
+              Lut t = make_lut(e4m3_to_float(sc4 & 0xFF) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((0 ^ sw) << 4)) = decode8(w0.x, t);
+              *reinterpret_cast<uint4*>(dst_row + ((1 ^ sw) << 4)) = decode8(w0.y, t);
+              t = make_lut(e4m3_to_float((sc4 >> 8) & 0xFF) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((2 ^ sw) << 4)) = decode8(w0.z, t);
+              *reinterpret_cast<uint4*>(dst_row + ((3 ^ sw) << 4)) = decode8(w0.w, t);
+              t = make_lut(e4m3_to_float((sc4 >> 16) & 0xFF) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((4 ^ sw) << 4)) = decode8(w1.x, t);
+              *reinterpret_cast<uint4*>(dst_row + ((5 ^ sw) << 4)) = decode8(w1.y, t);
+              t = make_lut(e4m3_to_float(sc4 >> 24) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((6 ^ sw) << 4)) = decode8(w1.z, t);
+              *reinterpret_cast<uint4*>(dst_row + ((7 ^ sw) << 4)) = decode8(w1.w, t);
+              fence_proxy_async_smem();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[stage]);
+            if (++stage == W4_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
           }
-          if (kb < nk_main) {
-            const uint8_t* raw = sRaw + stage * RAW_BYTES + ct * 32;
-            const uint4 w0 = *reinterpret_cast<const uint4*>(raw);
-            const uint4 w1 = *reinterpret_cast<const uint4*>(raw + 16);
-            uint8_t* dst_row = sB + stage * B_BYTES + half * 8192 + r * 128;
-            const int sw = r & 7;
-            Lut t = make_lut(e4m3_to_float(sc4 & 0xFF) * g);
-            *reinterpret_cast<uint4*>(dst_row + ((0 ^ sw) << 4)) = decode8(w0.x, t);
-            *reinterpret_cast<uint4*>(dst_row + ((1 ^ sw) << 4)) = decode8(w0.y, t);
-            t = make_lut(e4m3_to_float((sc4 >> 8) & 0xFF) * g);
-            *reinterpret_cast<uint4*>(dst_row + ((2 ^ sw) << 4)) = decode8(w0.z, t);
-            *reinterpret_cast<uint4*>(dst_row + ((3 ^ sw) << 4)) = decode8(w0.w, t);
-            t = make_lut(e4m3_to_float((sc4 >> 16) & 0xFF) * g);
-            *reinterpret_cast<uint4*>(dst_row + ((4 ^ sw) << 4)) = decode8(w1.x, t);
-            *reinterpret_cast<uint4*>(dst_row + ((5 ^ sw) << 4)) = decode8(w1.y, t);
-            t = make_lut(e4m3_to_float(sc4 >> 24) * g);
-            *reinterpret_cast<uint4*>(dst_row + ((6 ^ sw) << 4)) = decode8(w1.z, t);
-            *reinterpret_cast<uint4*>(dst_row + ((7 ^ sw) << 4)) = decode8(w1.w, t);
-            fence_proxy_async_smem();
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[stage]);
-          if (++stage == W4_STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
         }
       }
     }

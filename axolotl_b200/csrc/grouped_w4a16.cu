@@ -27,7 +27,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int BK = 64;
-constexpr int W4_THREADS = 320;   // TMA, MMA, 4 epilogue warps, 4 converter warps
+constexpr int W4_CONV_WARPS = 8;
+constexpr int W4_THREADS = 192 + 32 * W4_CONV_WARPS;   // TMA, MMA, 4 epilogue warps, 8 converter warps
 constexpr int W4_STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;   // one 128-row A tile; a stage holds two
 constexpr int B_BYTES = BN * BK * 2;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
   uint8_t* sRaw = sB + W4_STAGES * B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + W4_STAGES * RAW_BYTES);
   uint64_t* raw_full = bars;                    // TMA landed: A tiles + packed weights (or the bf16 LoRA tile)
-  uint64_t* full_bar = bars + W4_STAGES;        // converters done: the bf16 B tile is in place (4 arrivals)
+  uint64_t* full_bar = bars + W4_STAGES;        // converters done: the bf16 B tile is in place (one arrival per warp)
   uint64_t* empty_bar = bars + 2 * W4_STAGES;   // MMAs retired
   uint64_t* tfull_bar = bars + 3 * W4_STAGES;
   uint64_t* tempty_bar = bars + 3 * W4_STAGES + 2;
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < W4_STAGES; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&full_bar[s], 4);
+      mbar_init(&full_bar[s], W4_CONV_WARPS);
       mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -292,13 +293,19 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------ converters: packed tile -> bf16 B tile
-    // Thread ct reads 32 packed bytes (64 codes, 4 scale groups) at raw + ct * 32.
-    //   FWD: raw tile [128 n][32 B]: weight row n0 + ct, k block kb  -> K-major row ct of the B tile.
-    //   DX : raw tile [64 wn][64 B]: weight row kb * 64 + ct / 2, columns n0 + 64 * (ct & 1) .. + 63
-    //        -> MN-major chunk (ct & 1), row ct / 2.
-    const int ct = threadIdx.x - 192;   // 0..127
+    // 256 threads; thread ct reads 16 packed bytes (32 codes, 2 scale groups) at raw + ct * 16 and writes four
+    // 16-byte chunks of the swizzled bf16 tile. Two warps per scheduler hide each other's latencies.
+    //   FWD: raw tile [128 n][32 B]: weight row n0 + ct / 2, codes 32 * (ct & 1) .. + 31 of k block kb
+    //        -> K-major row ct / 2, chunks 4 * (ct & 1) .. + 3.
+    //   DX : raw tile [64 wn][64 B]: weight row kb * 64 + ct / 4, columns n0 + 64 * half + 32 * part .. + 31
+    //        (half = (ct >> 1) & 1, part = ct & 1) -> MN-major chunk block `half`, row ct / 4, chunks 4 * part .. + 3.
+    // Shared-memory accesses are conflict free: the loads are contiguous, and the eight lanes of a store phase
+    // hit eight different 16-byte chunk positions (rows differ in swizzle bits 0-1 or bit 0, `part` flips bit 2,
+    // and in dX the odd half walks its chunks in the order 2, 3, 0, 1, which flips bit 1).
+    const int ct = threadIdx.x - 192;   // 0..255
     const long long sc_row_bytes = p.Wk / 16;
-    const int r = DX ? (ct >> 1) : ct, half = DX ? (ct & 1) : 0;
+    const int part = ct & 1;
+    const int r = DX ? (ct >> 2) : (ct >> 1), half = DX ? ((ct >> 1) & 1) : 0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -308,16 +315,16 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
         if (!get_pass(p.blk_expert, n_blocks, num_n, p.E, tile, sub, ps)) continue;
         const float g = p.pts[ps.e];
         const uint8_t* sc_base = p.scale + (long long)ps.e * p.Wn * sc_row_bytes;
-        // Block scales are fetched FOUR k blocks ahead (a global load that misses the small L1 left beside
-        // 200 KB of shared memory takes longer than one k block): a 16-byte load per four k blocks of this
-        // thread's weight row in the forward, one 4-byte load per k block (a new weight row each) in dX.
+        // Block scales (2 bytes per thread and k block) are fetched FOUR k blocks ahead: a global load that misses
+        // the small L1 left beside 200 KB of shared memory takes longer than one k block. Forward: one 16-byte
+        // load covers four k blocks of this thread's weight row; dX: a new weight row per k block.
         const bool vec_ok = !DX && (sc_row_bytes & 15) == 0;
         auto load_group = [&](int kb0, uint32_t (&out)[4]) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) out[j] = 0u;
           if (kb0 >= nk_main) return;
           if (!DX) {
-            const int n = ps.n0 + ct;
+            const int n = ps.n0 + r;
             if (n >= p.Wn) return;
             const uint8_t* row = sc_base + (long long)n * sc_row_bytes;
             if (vec_ok && kb0 * 4 + 16 <= sc_row_bytes) {
@@ -328,14 +335,16 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
               for (int j = 0; j < 4; ++j)
                 if (kb0 + j < nk_main) out[j] = __ldg(reinterpret_cast<const uint32_t*>(row + (kb0 + j) * 4));
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[j] = (out[j] >> (part * 16)) & 0xFFFFu;
           } else {
-            const int k0 = ps.n0 + half * 64;
+            const int k0 = ps.n0 + half * 64 + part * 32;
             if (k0 >= p.Wk) return;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int wn = (kb0 + j) * BK + r;
               if (kb0 + j < nk_main && wn < p.Wn)
-                out[j] = __ldg(reinterpret_cast<const uint32_t*>(sc_base + (long long)wn * sc_row_bytes + k0 / 16));
+                out[j] = __ldg(reinterpret_cast<const unsigned short*>(sc_base + (long long)wn * sc_row_bytes + k0 / 16));
             }
           }
         };
@@ -352,33 +361,21 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
               break;
             }
             if (kb < nk_main) {
-              const uint8_t* raw = sRaw + stage * RAW_BYTES + ct * 32;
-              uint4 w0 = *reinterpret_cast<const uint4*>(raw);
-              uint4 w1 = *reinterpret_cast<const uint4*>(raw + 16);
-              uint32_t sc4 = cur[j];
+              uint4 w = *reinterpret_cast<const uint4*>(sRaw + stage * RAW_BYTES + ct * 16);
+              uint32_t sc2 = cur[j];                    // two E4M3 bytes: codes 0-15 and 16-31 of this thread
               uint8_t* dst_row = sB + stage * B_BYTES + half * 8192 + r * 128;
-              int sw = r & 7;
+              int pos = (part * 4) ^ (r & 7);           // chunk position of this thread's first chunk
               if (DX && half) {
-                // the two halves of a row pair write the same banks: the odd half goes through its eight chunks
-                // in the order 4..7, 0..3 instead
-                const uint4 t4 = w0;
-                w0 = w1;
-                w1 = t4;
-                sc4 = (sc4 >> 16) | (sc4 << 16);
-                sw ^= 4;
+                w = make_uint4(w.z, w.w, w.x, w.y);
+                sc2 = ((sc2 >> 8) | (sc2 << 8)) & 0xFFFFu;
+                pos ^= 2;
               }
-              Lut t = make_lut(e4m3_to_float(sc4 & 0xFF) * g);
-              *reinterpret_cast<uint4*>(dst_row + ((0 ^ sw) << 4)) = decode8(w0.x, t);
-              *reinterpret_cast<uint4*>(dst_row + ((1 ^ sw) << 4)) = decode8(w0.y, t);
-              t = make_lut(e4m3_to_float((sc4 >> 8) & 0xFF) * g);
-              *reinterpret_cast<uint4*>(dst_row + ((2 ^ sw) << 4)) = decode8(w0.z, t);
-              *reinterpret_cast<uint4*>(dst_row + ((3 ^ sw) << 4)) = decode8(w0.w, t);
-              t = make_lut(e4m3_to_float((sc4 >> 16) & 0xFF) * g);
-              *reinterpret_cast<uint4*>(dst_row + ((4 ^ sw) << 4)) = decode8(w1.x, t);
-              *reinterpret_cast<uint4*>(dst_row + ((5 ^ sw) << 4)) = decode8(w1.y, t);
-              t = make_lut(e4m3_to_float(sc4 >> 24) * g);
-              *reinterpret_cast<uint4*>(dst_row + ((6 ^ sw) << 4)) = decode8(w1.z, t);
-              *reinterpret_cast<uint4*>(dst_row + ((7 ^ sw) << 4)) = decode8(w1.w, t);
+              Lut t = make_lut(e4m3_to_float(sc2 & 0xFF) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((pos ^ 0) << 4)) = decode8(w.x, t);
+              *reinterpret_cast<uint4*>(dst_row + ((pos ^ 1) << 4)) = decode8(w.y, t);
+              t = make_lut(e4m3_to_float(sc2 >> 8) * g);
+              *reinterpret_cast<uint4*>(dst_row + ((pos ^ 2) << 4)) = decode8(w.z, t);
+              *reinterpret_cast<uint4*>(dst_row + ((pos ^ 3) << 4)) = decode8(w.w, t);
               fence_proxy_async_smem();
             }
             __syncwarp();

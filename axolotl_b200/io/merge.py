@@ -129,8 +129,31 @@ def _merge_nvfp4_group(names, tensors, cfg, pairs):
     return {names["packed"]: q2, names["scale"]: s2, names["global"]: g2.reshape(tensors[names["global"]].shape)}
 
 
-def merge_lora_sharded(base_dir: str, adapter_dir: str, out_dir: str, device: str = "cpu") -> dict:
+def _merge_quantised(k, w, tensors, cfg, pairs, device, nvfp4_scale_mode):
+    """A weight stored as ``k`` + ``k_scale*`` companions (block-fp8 / MXFP8 / MXFP4 / NVFP4): expand, add the adapter
+    delta, write back in the same format. Returns replacement tensors or {}."""
+    from . import quant_formats as qf
+
+    fmt, scales = qf.detect_format(k, w, tensors)
+    if fmt is None:
+        return {}
+    full = qf.dequantize(fmt, w, scales, device)
+    rep = merge_tensor(k, full, cfg, pairs)
+    if rep is None:
+        return {}
+    q = qf.requantize(fmt, rep.float(), scales, device, nvfp4_scale_mode=nvfp4_scale_mode)
+    return {k + suffix: t for suffix, t in q.items()}
+
+
+def merge_lora_sharded(base_dir: str, adapter_dir: str, out_dir: str, device: str = "cpu", nvfp4_scale_mode: str = "reuse",
+                       nf4_roundtrip: bool | None = None) -> dict:
+    """Streams the base checkpoint shard by shard and writes the merged one. Quantised base weights keep their
+    storage format (``nvfp4_scale_mode``: ``reuse`` the base block scales, or ``fresh`` ones from the merged weight).
+    ``nf4_roundtrip``: merge into the NF4 quantise -> dequantise image of the base weights, i.e. what a QLoRA adapter
+    trained against (default: when the adapter's config records ``load_in_4bit`` / a QLoRA run)."""
     cfg, pairs = load_adapter_tensors(adapter_dir)
+    if nf4_roundtrip is None:
+        nf4_roundtrip = bool(cfg.get("axolotl_load_in_4bit") or cfg.get("load_in_4bit") or cfg.get("qlora"))
     os.makedirs(out_dir, exist_ok=True)
     files = st.checkpoint_files(base_dir)
     if not files:
@@ -157,14 +180,24 @@ def merge_lora_sharded(base_dir: str, adapter_dir: str, out_dir: str, device: st
                 if rep:
                     out.update(rep)
                     merged.add(pre)
+        dev_pairs = {p: {a: t.to(device) for a, t in ab.items()} for p, ab in pairs.items()} if device != "cpu" else pairs
         for k, w in tensors.items():
             if k in out:
                 continue
             if w.dtype in (torch.uint8, torch.float8_e4m3fn):
-                out[k] = w
+                rep = _merge_quantised(k, w, tensors, cfg, dev_pairs, device, nvfp4_scale_mode)
+                if rep:
+                    out.update(rep)
+                    merged.add(k[: -len(".weight")] if k.endswith(".weight") else k)
+                else:
+                    out[k] = w
                 continue
-            rep = merge_tensor(k, w.to(device), cfg, {p: {a: t.to(device) for a, t in ab.items()} for p, ab in pairs.items()}
-                               if device != "cpu" else pairs)
+            base_w = w.to(device)
+            if nf4_roundtrip and w.dim() == 2 and k.endswith(".weight") and k[: -len(".weight")] in pairs:
+                from .quant_formats import simulate_nf4_roundtrip
+
+                base_w = simulate_nf4_roundtrip(base_w)
+            rep = merge_tensor(k, base_w, cfg, dev_pairs)
             if rep is not None:
                 out[k] = rep.cpu()
                 mm = re.match(r"(.+\.experts)\.\d+\.(gate_proj|up_proj|down_proj)\.weight$", k)

@@ -46,7 +46,7 @@ def save_file(tensors: dict, path: str, metadata: dict | None = None) -> None:
         fh.write(hb)
         for _, t in items:
             c = t.detach().to("cpu").contiguous()
-            fh.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+            fh.write(c.reshape(-1).view(torch.uint8).numpy().tobytes() if c.numel() else b"")
     os.replace(tmp, path)
 
 

@@ -71,6 +71,34 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.weight$", name)):
             mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
             filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.mamba\.(.+)$", name)):
+            # Granite 4.0-H state-space mixer (kept under `self_attn` in our layer)
+            mx, leaf = mods[m.group(1) + ".self_attn"], m.group(2)
+            if leaf in ("in_proj.weight", "out_proj.weight", "in_proj.bias", "out_proj.bias"):
+                getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
+            elif leaf == "conv1d.weight":
+                mx.conv_weight.copy_(t.reshape(t.shape[0], t.shape[-1]))
+            elif leaf == "conv1d.bias":
+                mx.conv_bias.copy_(t)
+            elif leaf == "norm.weight":
+                mx.norm_weight.copy_(t)
+            elif leaf in ("dt_bias", "A_log", "D"):
+                getattr(mx, leaf).copy_(t)
+            elif strict:
+                raise KeyError(f"unexpected checkpoint tensor '{name}'")
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.shared_mlp\.(input_linear|output_linear)\.weight$", name)):
+            mlp = mods[m.group(1) + ".mlp"]
+            mlp = mlp.shared_experts if getattr(mlp, "shared_experts", None) is not None else mlp
+            (mlp.gate_up_proj if m.group(2) == "input_linear" else mlp.down_proj).weight.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.block_sparse_moe\.(input_linear|output_linear|router\.layer)\.weight$", name)):
+            moe = mods[m.group(1) + ".mlp"]
+            if m.group(2) == "router.layer":
+                moe.gate.copy_(t)
+            else:
+                (moe.experts.gate_up_proj if m.group(2) == "input_linear" else moe.experts.down_proj).copy_(t)
+            filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.sinks$", name)):
             mods[m.group(1)].sinks.copy_(t)
             filled.add(name)
@@ -219,12 +247,49 @@ def load_pretrained_from_rank0(path: str, dtype=torch.bfloat16, device="cpu", co
     return model
 
 
+def _granite_hybrid_state_dict(model, sd):
+    """Granite 4.0-H names: `mamba.*` mixers, `shared_mlp`, `block_sparse_moe`."""
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}"
+        for nm in ("input_layernorm", "post_attention_layernorm"):
+            sd[f"{pre}.{nm}.weight"] = getattr(layer, nm).weight.detach()
+        mx = layer.self_attn
+        if type(mx).__name__ == "Mamba2Mixer":
+            sd[f"{pre}.mamba.in_proj.weight"] = mx.in_proj.weight.detach()
+            sd[f"{pre}.mamba.out_proj.weight"] = mx.out_proj.weight.detach()
+            if mx.in_proj.bias is not None:
+                sd[f"{pre}.mamba.in_proj.bias"] = mx.in_proj.bias.detach()
+                sd[f"{pre}.mamba.out_proj.bias"] = mx.out_proj.bias.detach()
+            sd[f"{pre}.mamba.conv1d.weight"] = mx.conv_weight.detach()[:, None, :]
+            if mx.conv_bias is not None:
+                sd[f"{pre}.mamba.conv1d.bias"] = mx.conv_bias.detach()
+            sd[f"{pre}.mamba.norm.weight"] = mx.norm_weight.detach()
+            for leaf in ("dt_bias", "A_log", "D"):
+                sd[f"{pre}.mamba.{leaf}"] = getattr(mx, leaf).detach()
+        else:
+            for fl in (mx.qkv_proj, mx.o_proj):
+                for sub in fl.names:
+                    r0, r1 = fl.row_range(sub)
+                    sd[f"{pre}.self_attn.{sub}.weight"] = fl.weight.detach()[r0:r1]
+        mlp = layer.mlp
+        shared = mlp.shared_experts if getattr(mlp, "shared_experts", None) is not None else mlp
+        sd[f"{pre}.shared_mlp.input_linear.weight"] = shared.gate_up_proj.weight.detach()
+        sd[f"{pre}.shared_mlp.output_linear.weight"] = shared.down_proj.weight.detach()
+        if isinstance(getattr(mlp, "experts", None), Experts):
+            sd[f"{pre}.block_sparse_moe.input_linear.weight"] = mlp.experts.gate_up_proj.detach()
+            sd[f"{pre}.block_sparse_moe.output_linear.weight"] = mlp.experts.down_proj.detach()
+            sd[f"{pre}.block_sparse_moe.router.layer.weight"] = mlp.gate.detach()
+    return sd
+
+
 def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     """Model tensors under HF names (views where possible; the writer makes them contiguous)."""
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}
     if model.lm_head is not None:
         sd["lm_head.weight"] = model.lm_head.detach()
     gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
+    if getattr(model.config, "model_type", "") == "granitemoehybrid":
+        return _granite_hybrid_state_dict(model, sd)
     for name, m in model.named_modules():
         if gpt_oss and isinstance(m, Experts):
             def interleave(u):            # [E, 2I, ...] gate rows then up rows -> alternating

@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
@@ -92,6 +92,12 @@ class ModelConfig:
                 d.setdefault("sliding_window", 4096)
                 d.setdefault("attn_logit_softcapping", 50.0)
                 d.setdefault("final_logit_softcapping", 30.0)
+        if mt == "granitemoehybrid":
+            d["num_experts"] = d.get("num_local_experts") or 0
+            d["moe_intermediate_size"] = d.get("intermediate_size") or 0     # width of a routed expert
+            d.setdefault("norm_topk_prob", True)
+            if not d.get("layer_types") and d.get("layers_block_type"):
+                d["layer_types"] = d["layers_block_type"]
         if mt == "gpt_oss":
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0
@@ -150,6 +156,9 @@ class ModelConfig:
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size")
             d["hidden_act"] = "silu"
+        if self.model_type == "granitemoehybrid":
+            d["num_local_experts"] = d.pop("num_experts")
+            d["intermediate_size"] = d.pop("moe_intermediate_size") or extra.get("intermediate_size") or d.get("intermediate_size")
         if self.model_type in ("deepseek_v2", "deepseek_v3"):
             d["n_routed_experts"] = d.pop("num_experts")
             d.pop("head_dim", None)
@@ -183,7 +192,7 @@ class ModelConfig:
                 qpas = (self.extra or {}).get("query_pre_attn_scalar")
                 return float(qpas) ** -0.5 if qpas and self.model_type != "gemma" else 1.0 / math.sqrt(self.head_dim)
             return 1.0
-        if self.model_type != "granite":
+        if self.model_type not in ("granite", "granitemoehybrid"):
             return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         default = 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         v = (self.extra or {}).get(name)
@@ -249,8 +258,18 @@ class ModelConfig:
             return int(w) if idx >= (ex.get("max_window_layers") or 0) else 0
         return 0
 
+    def layer_kind(self, idx: int) -> str:
+        """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
+        if self.model_type != "granitemoehybrid":
+            return "attention"
+        types = (self.extra or {}).get("layer_types") or (self.extra or {}).get("layers_block_type")
+        return "mamba" if types and types[idx] == "mamba" else "attention"
+
     def uses_rope(self, idx: int) -> bool:
-        """SmolLM3 drops the rotary embedding in every layer whose ``no_rope_layers`` entry is 0."""
+        """SmolLM3 drops the rotary embedding in every layer whose ``no_rope_layers`` entry is 0; Granite 4.0-H
+        attention layers carry no position signal unless ``position_embedding_type`` is ``rope``."""
+        if self.model_type == "granitemoehybrid":
+            return (self.extra or {}).get("position_embedding_type") == "rope"
         if self.model_type != "smollm3":
             return True
         ex = self.extra or {}
@@ -393,6 +412,7 @@ _ARCH_NAME = {
     "deepseek_v2": "DeepseekV2ForCausalLM",
     "deepseek_v3": "DeepseekV3ForCausalLM",
     "gpt_oss": "GptOssForCausalLM",
+    "granitemoehybrid": "GraniteMoeHybridForCausalLM",
 }
 
 

@@ -1,0 +1,112 @@
+"""Mamba-2 (state-space duality) mixer for the hybrid families (Granite 4.0-H `granitemoehybrid`): in_proj ->
+causal depthwise convolution -> selective state-space scan -> gated RMSNorm -> out_proj, on PACKED token streams:
+neither the convolution nor the recurrent state crosses a document boundary.
+
+The scan is the chunked SSD algorithm written with dense tensor contractions (fp32): inside a chunk of Q tokens the
+output is a masked, decay-weighted (C B^T) product; between chunks one [heads, P, N] state per chunk is carried by a
+short recurrence. Autograd differentiates the contractions. On a GPU these run as library batched GEMMs; a fused
+tcgen05 scan kernel is not part of this package yet.
+
+The reference trains these models through HF's modelling code and the mamba-ssm / causal-conv1d kernels
+(src/axolotl/monkeypatch/models/mamba_utils.py:53-187 adds context parallelism for them, which is not built here).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .config import ModelConfig
+from .layers import FusedLinear
+
+
+def ssd_chunked(xd, a, B, C, chunk=128):
+    """One document. xd [L, h, P] (inputs already multiplied by dt), a [L, h] (log decay per step, <= 0),
+    B, C [L, h, N]. Returns y [L, h, P] with y_t = sum_{s<=t} exp(a_{s+1} + .. + a_t) (C_t . B_s) xd_s."""
+    L, h, P = xd.shape
+    N = B.shape[-1]
+    Q = min(chunk, max(L, 1))
+    pad = (-L) % Q
+    if pad:
+        xd, a, B, C = (F.pad(t, (0, 0) * (t.dim() - 1) + (0, pad)) for t in (xd, a, B, C))
+    nc = (L + pad) // Q
+    xd, B, C = xd.view(nc, Q, h, P), B.view(nc, Q, h, N), C.view(nc, Q, h, N)
+    cum = a.view(nc, Q, h).cumsum(1)                                            # [nc, Q, h]
+    seg = cum[:, :, None, :] - cum[:, None, :, :]                                # [nc, i, j, h]
+    causal = torch.ones(Q, Q, dtype=torch.bool, device=xd.device).tril()
+    decay = torch.exp(seg.masked_fill(~causal[None, :, :, None], float("-inf")))
+    G = torch.einsum("cihn,cjhn->cijh", C, B)
+    y = torch.einsum("cijh,cjhp->cihp", G * decay, xd)
+    if nc > 1:
+        to_end = torch.exp(cum[:, -1:, :] - cum)                                 # [nc, Q, h]
+        S = torch.einsum("cjhn,cjh,cjhp->chpn", B, to_end, xd)                  # state contributed by each chunk
+        chunk_decay = torch.exp(cum[:, -1, :])                                   # [nc, h]
+        carried, R = [], torch.zeros(h, P, N, dtype=xd.dtype, device=xd.device)
+        for c in range(nc):
+            carried.append(R)
+            R = chunk_decay[c][:, None, None] * R + S[c]
+        y = y + torch.einsum("cihn,chpn,cih->cihp", C, torch.stack(carried), torch.exp(cum))
+    return y.reshape(nc * Q, h, P)[:L]
+
+
+class Mamba2Mixer(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        ex = cfg.extra or {}
+        H = cfg.hidden_size
+        self.nh, self.P = int(ex["mamba_n_heads"]), int(ex["mamba_d_head"])
+        self.G, self.N = int(ex.get("mamba_n_groups", 1)), int(ex["mamba_d_state"])
+        self.k = int(ex.get("mamba_d_conv", 4))
+        self.d_inner = int(ex.get("mamba_expand", 2) * H)
+        if self.d_inner != self.nh * self.P:
+            raise ValueError(f"mamba_expand * hidden ({self.d_inner}) must equal mamba_n_heads * mamba_d_head ({self.nh * self.P})")
+        self.conv_dim = self.d_inner + 2 * self.G * self.N
+        self.chunk = int(ex.get("mamba_chunk_size", 256))
+        lim = ex.get("time_step_limit") or (0.0, float("inf"))
+        self.dt_limit = (float(lim[0]), float(lim[1]))
+        self.eps = cfg.rms_norm_eps
+        bias = bool(ex.get("mamba_proj_bias", False))
+        self.in_proj = FusedLinear(H, [self.d_inner + self.conv_dim + self.nh], ["in_proj"], bias=bias, dtype=dtype, device=device)
+        self.conv_weight = nn.Parameter(torch.empty(self.conv_dim, self.k, dtype=dtype, device=device))
+        self.conv_bias = nn.Parameter(torch.zeros(self.conv_dim, dtype=dtype, device=device)) if ex.get("mamba_conv_bias", True) else None
+        self.dt_bias = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
+        self.A_log = nn.Parameter(torch.log(torch.arange(1, self.nh + 1, dtype=torch.float32, device=device)).to(dtype))
+        self.D = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
+        self.norm_weight = nn.Parameter(torch.ones(self.d_inner, dtype=dtype, device=device))
+        self.out_proj = FusedLinear(self.d_inner, [H], ["out_proj"], bias=bias, dtype=dtype, device=device)
+        self.window, self.use_rope = 0, False
+
+    def _conv(self, x, positions):
+        """Causal depthwise convolution over the token axis that reads zeros before the start of a document."""
+        w = self.conv_weight.float()
+        out = x.float() * w[:, self.k - 1]
+        pos = positions.to(x.device)
+        for j in range(1, self.k):
+            shifted = F.pad(x.float(), (0, 0, j, 0))[: x.shape[0]]
+            out = out + shifted * w[:, self.k - 1 - j] * (pos >= j)[:, None]
+        if self.conv_bias is not None:
+            out = out + self.conv_bias.float()
+        return F.silu(out)
+
+    def forward(self, x, positions, inv_freq, attn_scale, meta):
+        if getattr(meta, "kv_cache", None) is not None:
+            raise NotImplementedError("cached decoding is not available for state-space layers; generate(use_cache=False)")
+        T = x.shape[0]
+        zxbcdt = self.in_proj(x)
+        z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.conv_dim, self.nh], dim=-1)
+        xBC = self._conv(xBC, positions)
+        xs, B, C = torch.split(xBC, [self.d_inner, self.G * self.N, self.G * self.N], dim=-1)
+        dt = F.softplus(dt.float() + self.dt_bias.float()).clamp(self.dt_limit[0], self.dt_limit[1])
+        A = -torch.exp(self.A_log.float())
+        xs = xs.view(T, self.nh, self.P)
+        rep = self.nh // self.G
+        B = B.view(T, self.G, self.N).repeat_interleave(rep, dim=1)
+        C = C.view(T, self.G, self.N).repeat_interleave(rep, dim=1)
+        xd, a = xs * dt[..., None], A[None] * dt
+        cu = [int(v) for v in meta.cu_seqlens_host]
+        ys = [ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s]
+        y = torch.cat(ys, 0) + self.D.float()[None, :, None] * xs
+        y = y.reshape(T, self.d_inner) * F.silu(z.float())                       # gate first, then the norm
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
+        y = (self.norm_weight.float() * y).to(x.dtype)
+        return self.out_proj(y)

@@ -202,6 +202,13 @@ class SparseMoE(nn.Module):
 
             self.shared_expert = MLP(cfg.hidden_size, shared_I, cfg.hidden_act, False, dtype, device)
             self.shared_expert_gate = nn.Parameter(torch.empty(1, cfg.hidden_size, dtype=dtype, device=device))
+        # Granite 4.0-H: the k best LOGITS are soft-maxed among themselves; one always-on shared MLP
+        self.topk_softmax = cfg.model_type == "granitemoehybrid"
+        if self.topk_softmax:
+            from .transformer import MLP
+
+            self.shared_experts = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or 0),
+                                      cfg.hidden_act, False, dtype, device, fused_names=True)
         # gpt-oss: router and experts carry biases; the k best LOGITS are chosen, then soft-maxed among themselves
         self.router_bias = None
         if cfg.model_type == "gpt_oss":
@@ -209,7 +216,8 @@ class SparseMoE(nn.Module):
             self.experts.add_biases(dtype, device)
         # DeepSeek-V2 / V3: grouped (sigmoid) routing, always-on shared experts, scaled mixing weights
         self.deepseek = None
-        self.shared_experts = None
+        if not self.topk_softmax:
+            self.shared_experts = None
         self.e_score_correction_bias = None
         if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
             from .transformer import MLP
@@ -255,8 +263,10 @@ class SparseMoE(nn.Module):
         if self.deepseek is not None:
             logits = x.float() @ self.gate.float().t()       # HF keeps this router in fp32
             w, idx, probs = route_deepseek(logits, self.k, bias=self.e_score_correction_bias, **self.deepseek)
-        elif self.router_bias is not None:
-            logits = linear(x, self.gate).float() + self.router_bias.float()
+        elif self.router_bias is not None or self.topk_softmax:
+            logits = linear(x, self.gate).float()
+            if self.router_bias is not None:
+                logits = logits + self.router_bias.float()
             top, idx = torch.topk(logits, self.k, dim=-1)
             w, probs = torch.softmax(top, -1), torch.softmax(logits, -1)
         else:

@@ -138,6 +138,10 @@ class DecoderLayer(nn.Module):
             from .mla import MLAttention
 
             self.self_attn = MLAttention(cfg, dtype, device)
+        elif cfg.layer_kind(idx) == "mamba":
+            from .mamba import Mamba2Mixer
+
+            self.self_attn = Mamba2Mixer(cfg, dtype, device)     # (kept under the same attribute: the layer's token mixer)
         else:
             self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
@@ -160,6 +164,9 @@ class DecoderLayer(nn.Module):
             from .moe import SparseMoE
 
             self.mlp = SparseMoE(cfg, dtype, device)
+        elif cfg.model_type == "granitemoehybrid":     # dense variant: the "shared" MLP alone
+            self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
+                           cfg.hidden_act, False, dtype, device, fused_names=True)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
                            fused_names=cfg.model_type == "phi3")
@@ -194,6 +201,8 @@ class DecoderLayer(nn.Module):
         one part whose recomputation costs more than its activations), everything around it — norms,
         projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
         ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
+        if not hasattr(self.self_attn, "core"):      # state-space mixers have no attention result to keep
+            return checkpoint(self.forward, h, residual, positions, inv_freq, attn_scale, meta, use_reentrant=False)
         qkv, residual = checkpoint(self._before_attention, h, residual, positions, inv_freq, attn_scale, use_reentrant=False)
         a = self.self_attn.core(qkv, meta)
         return checkpoint(self._after_attention, a, residual, use_reentrant=False)
@@ -324,6 +333,9 @@ class CausalLM(nn.Module):
                 m.weight.fill_(1.0 - m.offset)
             if isinstance(m, Attention) and m.sinks is not None:
                 m.sinks.normal_(0.0, std, generator=gen)
+            if type(m).__name__ == "Mamba2Mixer":
+                m.A_log.copy_(torch.log(torch.arange(1, m.nh + 1, dtype=torch.float32, device=m.A_log.device)).to(m.A_log.dtype))
+                m.conv_weight.normal_(0.0, 0.2, generator=gen)
         return self
 
     @torch.no_grad()
@@ -487,7 +499,7 @@ class CausalLM(nn.Module):
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
-                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss"))
+                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

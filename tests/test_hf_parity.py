@@ -516,3 +516,43 @@ def test_gpt_oss_sinks_biased_experts_and_alternating_windows_match_hf(tmp_path)
     ours.train()
     ours(ids, pos, ids.clone()).loss.backward()
     assert ours.layers[0].self_attn.sinks.grad.abs().sum() > 0
+
+
+@pytest.mark.parametrize("experts", [0, 4])
+def test_granite_hybrid_mamba2_layers_match_hf(tmp_path, experts):
+    """Granite 4.0-H: Mamba-2 mixers (causal depthwise convolution, chunked state-space scan, gate-then-norm) mixed
+    with position-free attention layers, shared MLP, optional routed experts (top-k logits soft-maxed among
+    themselves), Granite multipliers; packed documents must not leak state or convolution taps into each other."""
+    d = dict(model_type="granitemoehybrid", vocab_size=300, hidden_size=64, intermediate_size=48, shared_intermediate_size=96,
+             num_hidden_layers=3, layer_types=["mamba", "attention", "mamba"], num_attention_heads=4, num_key_value_heads=2,
+             mamba_n_heads=8, mamba_d_head=16, mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+             mamba_chunk_size=8, mamba_conv_bias=True, mamba_proj_bias=False, num_local_experts=experts, num_experts_per_tok=2,
+             position_embedding_type="nope", rms_norm_eps=1e-5, tie_word_embeddings=True, hidden_act="silu",
+             embedding_multiplier=3.0, attention_multiplier=0.2, residual_multiplier=0.5, logits_scaling=2.0,
+             max_position_embeddings=256, router_aux_loss_coef=0.0, attention_bias=False)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(19)
+    with torch.no_grad():
+        for l in ours.layers:
+            if type(l.self_attn).__name__ == "Mamba2Mixer":
+                l.self_attn.dt_bias.uniform_(-1.0, 1.0)
+                l.self_attn.D.uniform_(0.5, 1.5)
+                l.self_attn.norm_weight.uniform_(0.5, 1.5)
+                l.self_attn.conv_bias.normal_(0, 0.1)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [21, 34, 9]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    ours.train()
+    ours(ids, pos, ids.clone()).loss.backward()
+    assert ours.layers[0].self_attn.A_log.grad is not None and ours.layers[0].self_attn.conv_weight.grad.abs().sum() > 0

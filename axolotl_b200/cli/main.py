@@ -49,6 +49,22 @@ def _extra_to_overrides(args):
     return out
 
 
+def _wants_ray(config, ctx) -> bool:
+    """``use_ray: true`` in the YAML or ``--use-ray`` on the command line (read before any process group exists)."""
+    ov = _extra_to_overrides(ctx.args)
+    if "use_ray" in ov:
+        return str(ov["use_ray"]).lower() in ("1", "true", "yes")
+    try:
+        import yaml as _yaml
+
+        from ..config.load import fetch_config
+
+        with open(fetch_config(config), encoding="utf-8") as fh:
+            return bool((_yaml.safe_load(fh) or {}).get("use_ray"))
+    except (OSError, ValueError):
+        return False
+
+
 def _load(config, ctx, **forced):
     from ..config.load import load_cfg
 
@@ -67,9 +83,15 @@ def cli():
 @click.argument("config")
 @click.option("--debug", is_flag=True, help="print a few tokenised samples with their label mask")
 @click.option("--debug-num-examples", default=3)
+@click.option("--cloud", type=click.Path(exists=True), default=None, help="cloud YAML: run the command on that provider")
+@click.option("--no-cloud", is_flag=True, hidden=True)
 @click.pass_context
-def preprocess(ctx, config, debug, debug_num_examples):
+def preprocess(ctx, config, debug, debug_num_examples, cloud, no_cloud):
     """Tokenise + cache the datasets of CONFIG (CPU only)."""
+    if cloud and not no_cloud:
+        from .launchers import run_in_cloud
+
+        return run_in_cloud("preprocess", cloud, config)
     os.environ["AXOLOTL_IS_PREPROCESS"] = "1"
     cfg = _load(config, ctx, is_preprocess=True)
     if not cfg.get("dataset_prepared_path"):
@@ -100,9 +122,22 @@ def _visible_gpus():
 @click.option("--num-processes", type=int, default=None)
 @click.option("--main-process-port", type=int, default=29500)
 @click.option("--sweep", type=click.Path(exists=True), default=None, help="YAML with lists of values to grid over")
+@click.option("--cloud", type=click.Path(exists=True), default=None, help="cloud YAML: run the command on that provider")
 @click.pass_context
-def train(ctx, config, launcher, num_processes, main_process_port, sweep):
+def train(ctx, config, launcher, num_processes, main_process_port, sweep, cloud):
     """Train (or fine-tune) the model described by CONFIG."""
+    if cloud:
+        from .launchers import run_in_cloud
+
+        return run_in_cloud("train", cloud, config, launcher=launcher or "torchrun", launcher_args=list(ctx.args),
+                            num_processes=num_processes)
+    if _wants_ray(config, ctx):
+        from ..config.load import apply_overrides, fetch_config
+        from .launchers import train_with_ray
+        import yaml as _yaml
+
+        raw = apply_overrides(_yaml.safe_load(open(fetch_config(config), encoding="utf-8")) or {}, _extra_to_overrides(ctx.args))
+        return train_with_ray(_load(config, ctx), raw)
     if sweep:
         from .sweeps import expand_sweep
 

@@ -429,6 +429,11 @@ class AxolotlConfig(_Base):
     generation_do_sample: bool | None = True
     # ---- reporting
     use_wandb: bool | None = None
+    # Ray Train launcher (cli/launchers.py)
+    use_ray: bool | None = None
+    ray_num_workers: int | None = None
+    ray_run_name: str | None = None
+    resources_per_worker: dict | None = None
     wandb_project: str | None = None
     wandb_entity: str | None = None
     wandb_name: str | None = None
@@ -578,7 +583,6 @@ UNSUPPORTED_KEYS = {
     "s2_attention": "shifted-sparse attention is not implemented",
     "torch_compile": "no tracing compiler is used; kernels are hand-written",
     "unsloth_cross_entropy_loss": "the native chunked linear+CE kernel is always used",
-    "use_ray": "the Ray launcher is not available; use --launcher torchrun",
     "llama4_linearized_experts": "Llama-4 is not a supported architecture",
     "use_onebitllms": "1-bit LLM training is not supported",
     "flash_optimum": "BetterTransformer is not used",
@@ -605,7 +609,7 @@ INERT_KEYS = {
     "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "preprocess_iterable", "processor_kwargs", "qgalore_cos_threshold", "qgalore_gamma_proj",
     "qgalore_proj_bits", "qgalore_proj_group_size", "qgalore_proj_quant", "qgalore_proj_type", "qgalore_queue_size",
     "qgalore_rank", "qgalore_scale", "qgalore_update_proj_gap", "qlora_sharded_model_loading", "quantize_embedding",
-    "ray_num_workers", "ray_run_name", "recompute_layer_types", "relora_prune_method", "resources_per_worker",
+    "recompute_layer_types", "relora_prune_method",
     "save_sliding_window", "scaling_softmax_bias", "scaling_softmax_factor", "streaming_min_groups",
     "tokenizer_save_jinja_files", "tokenizer_use_mistral_common", "torch_compile_backend",
     "torch_compile_mode", "torch_compile_options", "torchdistx_path", "trainer_cls", "use_eaft", "eaft_alpha", "eaft_k", "use_kernels", "use_liger_loss",

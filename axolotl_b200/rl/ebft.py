@@ -68,13 +68,24 @@ def feature_rewards(gen_emb, gt_emb, n, alignment_coef=1.0, diversity_coef=1.0, 
         gen, gt = torch.cat(g_l), torch.cat(t_l)
     else:
         gen, gt = F.normalize(gen_emb.float(), dim=-1), F.normalize(gt_emb.float(), dim=-1)
-    align = 2 * F.cosine_similarity(gen, gt.repeat_interleave(n, 0), dim=-1)
-    if n > 1:
+    D = gen.shape[-1]
+    if gen.is_cuda and (D + 2 * n + 1) * 4 <= 200 * 1024:
+        # one kernel for both terms (no [n, n] similarity matrix): csrc/ebft.cu
+        from ..ops import _lib
+
+        gen_c, gt_c = gen.contiguous(), gt.contiguous()
+        align = torch.empty(P * n, dtype=torch.float32, device=gen.device)
+        div = torch.empty_like(align)
+        _lib.check_rc(_lib.cuda_lib().axb_ebft_rewards(gen_c.data_ptr(), gt_c.data_ptr(), align.data_ptr(), div.data_ptr(),
+                                                       P, n, D, 0, _lib.stream_ptr()), "ebft_rewards")
+    elif n > 1:
+        align = 2 * F.cosine_similarity(gen, gt.repeat_interleave(n, 0), dim=-1)
         g3 = gen.view(P, n, -1)
         sims = g3 @ g3.transpose(1, 2)
         sims = sims.masked_fill(torch.eye(n, dtype=torch.bool, device=sims.device)[None], 0.0)
         div = 2 * (sims.sum(-1) / (n - 1)).reshape(-1)
     else:
+        align = 2 * F.cosine_similarity(gen, gt.repeat_interleave(n, 0), dim=-1)
         div = torch.zeros_like(align)
     cfm = ((gen.view(P, n, -1).mean(1) - gt) ** 2).sum(-1).mean()
     rewards = alignment_coef * align - diversity_coef * div

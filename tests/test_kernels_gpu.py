@@ -1103,3 +1103,20 @@ def test_deepseek_v3_latent_attention_model_on_gpu_matches_cpu_fp32():
         gd = dict(dev.named_parameters())[pick].grad.float().cpu()
         gc = dict(ref.named_parameters())[pick].grad
         assert _rel_err(gd, gc) < 8e-2, pick
+
+
+@pytest.mark.parametrize("whitening", [False, True])
+def test_ebft_feature_rewards_kernel_matches_torch(whitening):
+    """Alignment (2 cos to the ground truth) and diversity (2 x mean dot to the other samples of the group) from one
+    launch against the matrix formulation on the CPU."""
+    from axolotl_b200.rl.ebft import feature_rewards
+    torch.manual_seed(60)
+    P, n, D = 5, 4, 777
+    gen, gt = torch.randn(P * n, D), torch.randn(P, D)
+    r_dev, m_dev = feature_rewards(gen.to(_dev()), gt.to(_dev()), n, 1.0, 0.7, use_whitening=whitening)
+    r_cpu, m_cpu = feature_rewards(gen, gt, n, 1.0, 0.7, use_whitening=whitening)
+    assert torch.allclose(r_dev.cpu(), r_cpu, atol=2e-3, rtol=2e-3), (r_dev.cpu() - r_cpu).abs().max()
+    assert abs(m_dev["ebft/diversity"] - m_cpu["ebft/diversity"]) < 2e-3
+    one, _ = feature_rewards(gen[:P].to(_dev()), gt.to(_dev()), 1)
+    ref, _ = feature_rewards(gen[:P], gt, 1)
+    assert torch.allclose(one.cpu(), ref, atol=1e-4)

@@ -22,8 +22,27 @@ class NativeKernelArgs(BaseModel):
 
 
 class NativeKernelsPlugin(BasePlugin):
+    """Accepts the kernel-selection flags of the reference's Liger / cut-cross-entropy / kernels plugins and reports
+    which native kernel serves each request (they are always on; a flag set to false cannot switch one off)."""
+
+    NATIVE = {"liger_rope": "rope_qk_kernel", "liger_rms_norm": "rmsnorm_fwd/bwd_kernel", "liger_layer_norm": "rmsnorm_fwd/bwd_kernel",
+              "liger_glu_activation": "GLU epilogues of gemm_bf16_pair_kernel / glu_fwd/bwd_kernel",
+              "liger_cross_entropy": "ce_fwd_bwd_kernel", "liger_fused_linear_cross_entropy": "chunked lm-head GEMM + ce_fwd_bwd_kernel",
+              "cut_cross_entropy": "chunked lm-head GEMM + ce_fwd_bwd_kernel", "use_kernels": "all native kernels",
+              "use_scattermoe": "grouped_gemm_kernel / grouped_w4a16_kernel", "use_sonicmoe": "grouped_gemm_kernel / grouped_w4a16_kernel"}
+
     def get_input_args(self):
         return NativeKernelArgs
+
+    def pre_model_load(self, cfg):
+        from ..utils.logging import get_logger
+
+        log = get_logger(__name__)
+        for key, kernel in self.NATIVE.items():
+            if cfg.get(key) is True:
+                log.info("%s: served by %s", key, kernel)
+            elif cfg.get(key) is False:
+                log.warning("%s: false has no effect, %s is always used", key, kernel)
 
 
 class ExpertParallelArgs(BaseModel):
@@ -33,8 +52,26 @@ class ExpertParallelArgs(BaseModel):
 
 
 class ExpertParallelPlugin(BasePlugin):
+    """``expert_parallel_size`` is read by the parallel runtime; ``expert_parallel_capacity_factor`` bounds the rows a
+    rank may receive per layer call in the device-built routing plan (parallel/ep.py); ``expert_parallel_local_kernel``
+    names a reference kernel choice that the grouped tcgen05 kernels replace."""
+
     def get_input_args(self):
         return ExpertParallelArgs
+
+    def pre_model_load(self, cfg):
+        import os
+
+        cf = cfg.get("expert_parallel_capacity_factor")
+        if cf is not None:
+            if float(cf) <= 0:
+                raise ValueError("expert_parallel_capacity_factor must be positive")
+            os.environ["AXB_EP_CAPACITY"] = str(float(cf))
+        if cfg.get("expert_parallel_local_kernel"):
+            from ..utils.logging import get_logger
+
+            get_logger(__name__).info("expert_parallel_local_kernel=%s: the local expert pass always runs the grouped tcgen05 "
+                                      "GEMM kernels", cfg["expert_parallel_local_kernel"])
 
 
 class MoraBlock(BaseModel):

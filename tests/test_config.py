@@ -155,3 +155,19 @@ def test_architecture_registry_checks():
     with pytest.raises(ValueError, match="tensor parallelism"):
         validate_cfg({"tensor_parallel_size": 2}, preset("tiny-qwen3-moe"))
     assert validate_cfg({"sample_packing": True}, preset("tiny-llama")) == []
+
+
+def test_compat_plugins_act_on_their_keys(monkeypatch, caplog):
+    import logging
+
+    from axolotl_b200.plugins.compat import ExpertParallelPlugin, NativeKernelsPlugin
+    monkeypatch.delenv("AXB_EP_CAPACITY", raising=False)
+    ExpertParallelPlugin().pre_model_load({"expert_parallel_size": 2, "expert_parallel_capacity_factor": 1.25})
+    import os
+    assert os.environ["AXB_EP_CAPACITY"] == "1.25"
+    with pytest.raises(ValueError):
+        ExpertParallelPlugin().pre_model_load({"expert_parallel_capacity_factor": 0})
+    with caplog.at_level(logging.INFO):
+        NativeKernelsPlugin().pre_model_load({"liger_rms_norm": True, "cut_cross_entropy": False})
+    text = " ".join(r.getMessage() for r in caplog.records)
+    assert "rmsnorm" in text and "always used" in text

@@ -41,7 +41,10 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     mods = dict(model.named_modules())
     filled = set()
     expert_parts = {}
+    llama4 = getattr(model.config, "model_type", "") == "llama4_text"
     for name, t in named_tensors:
+        if llama4:
+            name, t = _llama4_in(model, name, t)
         # multimodal wrappers (Gemma 3): the language model's tensors carry a prefix, the vision parts are not ours
         if name.startswith("language_model."):
             name = name[len("language_model."):]
@@ -247,6 +250,47 @@ def load_pretrained_from_rank0(path: str, dtype=torch.bfloat16, device="cpu", co
     return model
 
 
+def _deinterleave_rows(w, heads, D, inverse=False):
+    """Rotary pairs stored as (real, imaginary) neighbours <-> the half-split layout the rotary kernel works on:
+    a permutation of the D output rows of every head (attention scores do not change when q and k share it)."""
+    idx = torch.cat([torch.arange(0, D, 2), torch.arange(1, D, 2)])
+    if inverse:
+        idx = torch.argsort(idx)
+    return w.reshape(heads, D, *w.shape[1:]).index_select(1, idx.to(w.device)).reshape(w.shape)
+
+
+def _llama4_in(model, name, t):
+    """Llama 4 checkpoint names and layouts -> ours: `feed_forward` is `mlp`, `router` the gate, `shared_expert` the
+    shared MLP; expert stacks are stored [E, in, out]; q / k rows use interleaved rotary pairs."""
+    cfg = model.config
+    name = name.replace("language_model.model.", "model.").replace("language_model.lm_head", "lm_head")
+    name = name.replace(".feed_forward.", ".mlp.")
+    if name.endswith(".mlp.router.weight"):
+        return name.replace(".router.weight", ".gate.weight"), t
+    name = name.replace(".mlp.shared_expert.", ".mlp.shared_experts.")
+    if name.endswith(".mlp.experts.gate_up_proj") or name.endswith(".mlp.experts.down_proj"):
+        return name, t.transpose(1, 2)
+    if name.endswith(".self_attn.q_proj.weight"):
+        return name, _deinterleave_rows(t, cfg.num_attention_heads, cfg.head_dim)
+    if name.endswith(".self_attn.k_proj.weight"):
+        return name, _deinterleave_rows(t, cfg.num_key_value_heads, cfg.head_dim)
+    return name, t
+
+
+def _llama4_out(model, sd):
+    cfg, out = model.config, {}
+    for name, t in sd.items():
+        if name.endswith(".self_attn.q_proj.weight"):
+            t = _deinterleave_rows(t, cfg.num_attention_heads, cfg.head_dim, inverse=True)
+        elif name.endswith(".self_attn.k_proj.weight"):
+            t = _deinterleave_rows(t, cfg.num_key_value_heads, cfg.head_dim, inverse=True)
+        elif name.endswith(".mlp.experts.gate_up_proj") or name.endswith(".mlp.experts.down_proj"):
+            t = t.transpose(1, 2).contiguous()
+        name = name.replace(".mlp.gate.weight", ".mlp.router.weight").replace(".mlp.shared_experts.", ".mlp.shared_expert.")
+        out[name.replace(".mlp.", ".feed_forward.")] = t
+    return out
+
+
 def _granite_hybrid_state_dict(model, sd):
     """Granite 4.0-H names: `mamba.*` mixers, `shared_mlp`, `block_sparse_moe`."""
     for i, layer in enumerate(model.layers):
@@ -338,6 +382,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 sd[f"model.{name}.shared_expert_gate.weight"] = m.shared_expert_gate.detach()
             if getattr(m, "e_score_correction_bias", None) is not None:
                 sd[f"model.{name}.gate.e_score_correction_bias"] = m.e_score_correction_bias.detach()
+    if getattr(model.config, "model_type", "") == "llama4_text":
+        return _llama4_out(model, sd)
     return sd
 
 

@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
@@ -92,6 +92,23 @@ class ModelConfig:
                 d.setdefault("sliding_window", 4096)
                 d.setdefault("attn_logit_softcapping", 50.0)
                 d.setdefault("final_logit_softcapping", 30.0)
+        if mt == "llama4" and isinstance(d.get("text_config"), dict):      # the multimodal wrapper: its language model
+            d = dict(d["text_config"], model_type="llama4_text")
+            mt = "llama4_text"
+        if mt == "llama4_text":
+            L = d.get("num_hidden_layers", 0)
+            d["num_experts"] = d.get("num_local_experts") or 0
+            d["moe_intermediate_size"] = d.get("intermediate_size") or 0          # routed and shared experts
+            step = d.get("interleave_moe_layer_step") or 1
+            moe_layers = d.get("moe_layers")
+            if moe_layers is None:
+                moe_layers = list(range(step - 1, L, step))
+            d["mlp_only_layers"] = [i for i in range(L) if i not in set(moe_layers)]
+            d["dense_intermediate_size"] = d.get("intermediate_size_mlp") or d.get("intermediate_size")
+            if d.get("no_rope_layers") in (None, []):
+                every = d.get("no_rope_layer_interval") or 4
+                d["no_rope_layers"] = [int((i + 1) % every != 0) for i in range(L)]
+            d.setdefault("rms_norm_eps", 1e-5)
         if mt == "granitemoehybrid":
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0     # width of a routed expert
@@ -156,6 +173,13 @@ class ModelConfig:
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size")
             d["hidden_act"] = "silu"
+        if self.model_type == "llama4_text":
+            d["num_local_experts"] = d.pop("num_experts")
+            d["intermediate_size"] = d.pop("moe_intermediate_size") or d.get("intermediate_size")
+            d["intermediate_size_mlp"] = extra.get("dense_intermediate_size") or d["intermediate_size"]
+            d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
         if self.model_type == "granitemoehybrid":
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size") or extra.get("intermediate_size") or d.get("intermediate_size")
@@ -270,6 +294,8 @@ class ModelConfig:
         attention layers carry no position signal unless ``position_embedding_type`` is ``rope``."""
         if self.model_type == "granitemoehybrid":
             return (self.extra or {}).get("position_embedding_type") == "rope"
+        if self.model_type == "llama4_text":
+            return bool((self.extra or {})["no_rope_layers"][idx])           # 1 = this layer rotates
         if self.model_type != "smollm3":
             return True
         ex = self.extra or {}
@@ -413,6 +439,7 @@ _ARCH_NAME = {
     "deepseek_v3": "DeepseekV3ForCausalLM",
     "gpt_oss": "GptOssForCausalLM",
     "granitemoehybrid": "GraniteMoeHybridForCausalLM",
+    "llama4_text": "Llama4ForCausalLM",
 }
 
 

@@ -202,6 +202,14 @@ class SparseMoE(nn.Module):
 
             self.shared_expert = MLP(cfg.hidden_size, shared_I, cfg.hidden_act, False, dtype, device)
             self.shared_expert_gate = nn.Parameter(torch.empty(1, cfg.hidden_size, dtype=dtype, device=device))
+        # Llama 4: the sigmoid of the chosen logit scales the expert's INPUT; one always-on shared expert
+        self.input_scaled = cfg.model_type == "llama4_text"
+        if self.input_scaled:
+            from .transformer import MLP
+
+            if self.k != 1:
+                raise ValueError("Llama 4 routing scales the expert input, which is implemented for num_experts_per_tok = 1")
+            self._llama4_shared = MLP(cfg.hidden_size, cfg.moe_intermediate_size, cfg.hidden_act, False, dtype, device)
         # Granite 4.0-H: the k best LOGITS are soft-maxed among themselves; one always-on shared MLP
         self.topk_softmax = cfg.model_type == "granitemoehybrid"
         if self.topk_softmax:
@@ -218,6 +226,9 @@ class SparseMoE(nn.Module):
         self.deepseek = None
         if not self.topk_softmax:
             self.shared_experts = None
+        if self.input_scaled:
+            self.shared_experts = self._llama4_shared
+            del self._llama4_shared
         self.e_score_correction_bias = None
         if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
             from .transformer import MLP
@@ -263,6 +274,11 @@ class SparseMoE(nn.Module):
         if self.deepseek is not None:
             logits = x.float() @ self.gate.float().t()       # HF keeps this router in fp32
             w, idx, probs = route_deepseek(logits, self.k, bias=self.e_score_correction_bias, **self.deepseek)
+        elif self.input_scaled:
+            logits = linear(x, self.gate).float()
+            top, idx = torch.topk(logits, 1, dim=-1)
+            x = (x.float() * torch.sigmoid(top)).to(x.dtype)        # the score goes in, the expert output comes back unweighted
+            w, probs = torch.ones_like(top), torch.softmax(logits, -1)
         elif self.router_bias is not None or self.topk_softmax:
             logits = linear(x, self.gate).float()
             if self.router_bias is not None:

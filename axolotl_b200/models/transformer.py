@@ -64,6 +64,16 @@ class Attention(nn.Module):
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
         self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
         self.softcap = cfg.attn_softcap()                      # Gemma 2: scores -> cap * tanh(scores / cap)
+        # Llama 4: unweighted per-head L2 norm of q / k on rotating layers; those layers attend inside chunks of
+        # `attention_chunk_size` positions; position-free layers scale q by a slowly growing temperature
+        ex = cfg.extra or {}
+        self.llama4 = cfg.model_type == "llama4_text"
+        self.chunk = 0
+        self.temp = None
+        if self.llama4:
+            self.register_buffer("ones_d", torch.ones(self.D, dtype=dtype, device=device), persistent=False)
+            self.l2_qk = bool(ex.get("use_qk_norm", True))
+            self.temp = (float(ex.get("floor_scale") or 8192), float(ex.get("attn_scale") or 0.1)) if ex.get("attn_temperature_tuning", True) else None
         self.register_buffer("local_inv_freq", None, persistent=False)   # Gemma 3: sliding layers rotate with their own base
 
     def pre(self, x, positions, inv_freq, attn_scale):
@@ -78,15 +88,27 @@ class Attention(nn.Module):
         if self.use_rope:
             if self.local_inv_freq is not None:
                 inv_freq, attn_scale = self.local_inv_freq, 1.0
-            qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
-                              self.q_norm.effective_weight() if per_head_norm else None,
-                              self.k_norm.effective_weight() if per_head_norm else None, self.eps)
+            if self.llama4 and self.l2_qk:       # the norm commutes with the rotation, so it runs in the same kernel
+                qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale, self.ones_d, self.ones_d, self.eps)
+            else:
+                qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
+                                  self.q_norm.effective_weight() if per_head_norm else None,
+                                  self.k_norm.effective_weight() if per_head_norm else None, self.eps)
+        elif self.llama4 and self.temp is not None:
+            floor_scale, a = self.temp
+            t = torch.log1p(torch.floor((positions.float() + 1.0) / floor_scale)) * a + 1.0
+            nq = self.Hq * self.D
+            qkv = torch.cat([(qkv[:, :nq].float() * t[:, None]).to(qkv.dtype), qkv[:, nq:]], 1)
         return qkv
 
     def core(self, qkv, meta):
         cache = getattr(meta, "kv_cache", None)
         if cache is not None:   # generation: keep the rotated k / v of every token
             return cache.attend(self.layer_idx, qkv, meta, self.Hq, self.Hk, self.D, self.scale, self.window)
+        if self.chunk and getattr(meta, "causal", True):
+            if getattr(meta, "cp", False):
+                raise NotImplementedError("chunked attention is not available with context parallelism")
+            meta = meta.chunked(self.chunk)
         if self.window and getattr(meta, "causal", True):
             if getattr(meta, "cp", False):
                 raise NotImplementedError("sliding-window attention is not available with context parallelism")
@@ -147,6 +169,8 @@ class DecoderLayer(nn.Module):
         self.self_attn.layer_idx = idx
         self.self_attn.use_rope = cfg.uses_rope(idx)
         self.self_attn.window = cfg.sliding_window(idx)
+        if cfg.model_type == "llama4_text" and self.self_attn.use_rope:
+            self.self_attn.chunk = int((cfg.extra or {}).get("attention_chunk_size") or 0)
         theta = cfg.local_rope_theta(idx)
         if theta is not None:
             D = cfg.head_dim
@@ -164,6 +188,9 @@ class DecoderLayer(nn.Module):
             from .moe import SparseMoE
 
             self.mlp = SparseMoE(cfg, dtype, device)
+        elif cfg.model_type == "llama4_text":          # dense layers have their own width
+            self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("dense_intermediate_size") or cfg.intermediate_size),
+                           cfg.hidden_act, False, dtype, device)
         elif cfg.model_type == "granitemoehybrid":     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
@@ -499,7 +526,7 @@ class CausalLM(nn.Module):
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
-                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid"))
+                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -420,6 +420,20 @@ class AttnMeta:
             cache[window] = AttnMeta(self.cu_seqlens_host, self.device, True, window)
         return cache[window]
 
+    def chunked(self, chunk):
+        """The same token stream with every document cut at multiples of ``chunk`` positions: attention stays inside
+        a chunk (Llama 4 local layers). Cached per chunk size."""
+        if not chunk or chunk >= self.max_len:
+            return self
+        cache = self.__dict__.setdefault("_chunked", {})
+        if chunk not in cache:
+            cu = [0]
+            for s0, e0 in zip(self.cu_seqlens_host[:-1], self.cu_seqlens_host[1:]):
+                cu.extend(range(int(s0) + chunk, int(e0), chunk))
+                cu.append(int(e0))
+            cache[chunk] = AttnMeta(np.asarray(sorted(set(cu)), dtype=np.int32), self.device, self.causal)
+        return cache[chunk]
+
     @staticmethod
     def from_position_ids(position_ids, device, causal=True):
         """Document starts are the positions where ``position_ids`` resets to 0."""

@@ -556,3 +556,34 @@ def test_granite_hybrid_mamba2_layers_match_hf(tmp_path, experts):
     ours.train()
     ours(ids, pos, ids.clone()).loss.backward()
     assert ours.layers[0].self_attn.A_log.grad is not None and ours.layers[0].self_attn.conv_weight.grad.abs().sum() > 0
+
+
+def test_llama4_text_matches_hf(tmp_path):
+    """Rotating layers with interleaved rotary pairs, weight-free L2 q/k norm and chunked attention; position-free
+    layers with the temperature on q; top-1 router whose sigmoid score scales the expert INPUT; shared expert;
+    dense and sparse layers interleaved."""
+    d = dict(model_type="llama4_text", vocab_size=320, hidden_size=64, intermediate_size=48, intermediate_size_mlp=96,
+             num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4,
+             num_experts_per_tok=1, interleave_moe_layer_step=2, no_rope_layers=[1, 1, 1, 0], attention_chunk_size=16,
+             attn_temperature_tuning=True, floor_scale=8, attn_scale=0.1, use_qk_norm=True, rms_norm_eps=1e-5,
+             rope_theta=10000.0, hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=256,
+             attention_bias=False, router_aux_loss_coef=0.0,
+             layer_types=["chunked_attention", "chunked_attention", "chunked_attention", "full_attention"])
+    cfg = ModelConfig.from_hf_dict(d)
+    assert cfg.mlp_only_layers == [0, 2]
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(23)
+    assert ours.layers[0].self_attn.chunk == 16 and ours.layers[3].self_attn.chunk == 0
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [45, 22]
+    ids, pos = _packed_inputs(320, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)

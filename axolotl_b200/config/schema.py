@@ -583,7 +583,7 @@ UNSUPPORTED_KEYS = {
     "s2_attention": "shifted-sparse attention is not implemented",
     "torch_compile": "no tracing compiler is used; kernels are hand-written",
     "unsloth_cross_entropy_loss": "the native chunked linear+CE kernel is always used",
-    "llama4_linearized_experts": "Llama-4 is not a supported architecture",
+    "llama4_linearized_experts": "checkpoints with per-expert linear modules are not loaded directly; convert them with `axolotl delinearize-llama4` first",
     "use_onebitllms": "1-bit LLM training is not supported",
     "flash_optimum": "BetterTransformer is not used",
     "fp8": "fp8 mixed precision is not implemented; bf16 tensor-core kernels are used",

@@ -237,14 +237,16 @@ __global__ void rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const int* __res
 // angles ONCE and reuses them for every q and k head of the token (the angles depend on the position
 // only), and moves bf16 pairs (4-byte accesses, 128 B per warp instruction). sign = -1 is the
 // inverse rotation, i.e. the backward pass.
+// `rot` <= D: only the first `rot` dimensions of a head rotate (partial rotary embeddings: pairs (j, j + rot / 2));
+// the rest of the head passes through untouched.
 __global__ void rope_fast_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
                                  const float* __restrict__ inv_freq, int T, int nh, int D,
-                                 long long row_stride, float sign, float attn_scale) {
+                                 long long row_stride, float sign, float attn_scale, int rot) {
   const int warps_per_block = blockDim.x >> 5;
   const long long t = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
-  const int half = D >> 1;
+  const int half = rot >> 1;
   const float ps = (float)pos[t];
   __nv_bfloat16* row = qkv + t * row_stride;
   for (int j = 2 * lane; j < half; j += 64) {
@@ -796,7 +798,7 @@ extern "C" int axb_rope_qk(void* qkv, const int* pos, const float* inv_freq, int
   if (T <= 0) return 0;
   if (!qn_w && !kn_w && (D % 4) == 0 && (row_stride % 2) == 0) {
     rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)qkv, pos, inv_freq, T, Hq + Hk, D,
-                                                                     row_stride, sign, attn_scale);
+                                                                     row_stride, sign, attn_scale, D);
     return (int)cudaGetLastError();
   }
   const long long warps = (long long)T * (Hq + Hk);
@@ -804,6 +806,16 @@ extern "C" int axb_rope_qk(void* qkv, const int* pos, const float* inv_freq, int
   rope_qk_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
       (__nv_bfloat16*)qkv, pos, inv_freq, T, Hq, Hk, D, row_stride, sign, attn_scale,
       (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_out, eps);
+  return (int)cudaGetLastError();
+}
+// Partial rotary embedding of the first `rot` dimensions of the q and k heads (sign = -1: the inverse rotation,
+// i.e. the backward pass). rot % 4 == 0, rot <= D, row_stride % 2 == 0.
+extern "C" int axb_rope_partial(void* qkv, const int* pos, const float* inv_freq, int T, int n_heads, int D, int rot,
+                                long long row_stride, float sign, float attn_scale, void* stream) {
+  if (T <= 0) return 0;
+  if (rot <= 0 || rot > D || (rot & 3) || (row_stride & 1) || (D & 1)) return -2;
+  rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)qkv, pos, inv_freq, T, n_heads, D,
+                                                                   row_stride, sign, attn_scale, rot);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
@@ -815,7 +827,7 @@ extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
   if (D > 256) return -2;
   if (!qn_w && !kn_w && (D % 4) == 0 && (row_stride % 2) == 0) {
     rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)dqkv, pos, inv_freq, T, Hq + Hk, D,
-                                                                     row_stride, -1.f, attn_scale);
+                                                                     row_stride, -1.f, attn_scale, D);
     return (int)cudaGetLastError();
   }
   const long long warps = (long long)T * (Hq + Hk);

@@ -42,9 +42,13 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     filled = set()
     expert_parts = {}
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
+    bamba = getattr(model.config, "model_type", "") == "bamba"
     for name, t in named_tensors:
         if llama4:
             name, t = _llama4_in(model, name, t)
+        if bamba:
+            name = (name.replace(".pre_ff_layernorm.", ".post_attention_layernorm.").replace(".feed_forward.", ".mlp.")
+                    .replace("model.final_layernorm.", "model.norm."))
         # multimodal wrappers (Gemma 3): the language model's tensors carry a prefix, the vision parts are not ours
         if name.startswith("language_model."):
             name = name[len("language_model."):]
@@ -291,6 +295,42 @@ def _llama4_out(model, sd):
     return out
 
 
+def _mamba_tensors(pre, mx, sd):
+    sd[f"{pre}.mamba.in_proj.weight"] = mx.in_proj.weight.detach()
+    sd[f"{pre}.mamba.out_proj.weight"] = mx.out_proj.weight.detach()
+    if mx.in_proj.bias is not None:
+        sd[f"{pre}.mamba.in_proj.bias"] = mx.in_proj.bias.detach()
+        sd[f"{pre}.mamba.out_proj.bias"] = mx.out_proj.bias.detach()
+    sd[f"{pre}.mamba.conv1d.weight"] = mx.conv_weight.detach()[:, None, :]
+    if mx.conv_bias is not None:
+        sd[f"{pre}.mamba.conv1d.bias"] = mx.conv_bias.detach()
+    sd[f"{pre}.mamba.norm.weight"] = mx.norm_weight.detach()
+    for leaf in ("dt_bias", "A_log", "D"):
+        sd[f"{pre}.mamba.{leaf}"] = getattr(mx, leaf).detach()
+
+
+def _bamba_state_dict(model, sd):
+    """Bamba names: `mamba.*` mixers, `pre_ff_layernorm`, `feed_forward`, `final_layernorm`."""
+    sd["model.final_layernorm.weight"] = sd.pop("model.norm.weight")
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}"
+        sd[f"{pre}.input_layernorm.weight"] = layer.input_layernorm.weight.detach()
+        sd[f"{pre}.pre_ff_layernorm.weight"] = layer.post_attention_layernorm.weight.detach()
+        mx = layer.self_attn
+        if type(mx).__name__ == "Mamba2Mixer":
+            _mamba_tensors(pre, mx, sd)
+        else:
+            for fl in (mx.qkv_proj, mx.o_proj):
+                for sub in fl.names:
+                    r0, r1 = fl.row_range(sub)
+                    sd[f"{pre}.self_attn.{sub}.weight"] = fl.weight.detach()[r0:r1]
+        for fl in (layer.mlp.gate_up_proj, layer.mlp.down_proj):
+            for sub in fl.names:
+                r0, r1 = fl.row_range(sub)
+                sd[f"{pre}.feed_forward.{sub}.weight"] = fl.weight.detach()[r0:r1]
+    return sd
+
+
 def _granite_hybrid_state_dict(model, sd):
     """Granite 4.0-H names: `mamba.*` mixers, `shared_mlp`, `block_sparse_moe`."""
     for i, layer in enumerate(model.layers):
@@ -334,6 +374,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
     if getattr(model.config, "model_type", "") == "granitemoehybrid":
         return _granite_hybrid_state_dict(model, sd)
+    if getattr(model.config, "model_type", "") == "bamba":
+        return _bamba_state_dict(model, sd)
     for name, m in model.named_modules():
         if gpt_oss and isinstance(m, Experts):
             def interleave(u):            # [E, 2I, ...] gate rows then up rows -> alternating

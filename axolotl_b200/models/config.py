@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
@@ -109,6 +109,11 @@ class ModelConfig:
                 every = d.get("no_rope_layer_interval") or 4
                 d["no_rope_layers"] = [int((i + 1) % every != 0) for i in range(L)]
             d.setdefault("rms_norm_eps", 1e-5)
+        if mt == "bamba":
+            if d.get("mamba_d_head") in (None, "auto"):
+                d["mamba_d_head"] = int((d.get("mamba_expand") or 2) * d["hidden_size"]) // int(d.get("mamba_n_heads") or 128)
+            rp = d.get("rope_parameters") or {}
+            d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))
         if mt == "granitemoehybrid":
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0     # width of a routed expert
@@ -284,8 +289,10 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
-        if self.model_type != "granitemoehybrid":
+        if self.model_type not in ("granitemoehybrid", "bamba"):
             return "attention"
+        if self.model_type == "bamba":
+            return "attention" if idx in set((self.extra or {}).get("attn_layer_indices") or []) else "mamba"
         types = (self.extra or {}).get("layer_types") or (self.extra or {}).get("layers_block_type")
         return "mamba" if types and types[idx] == "mamba" else "attention"
 
@@ -313,6 +320,11 @@ class ModelConfig:
         """Width of the rotated part of a head (DeepSeek latent attention rotates only its shared 64-wide part)."""
         if self.model_type in ("deepseek_v2", "deepseek_v3"):
             return int((self.extra or {}).get("qk_rope_head_dim") or 64)
+        ex = self.extra or {}
+        f = ex.get("partial_rotary_factor") or (ex.get("rope_parameters") or {}).get("partial_rotary_factor") \
+            or (self.rope_scaling or {}).get("partial_rotary_factor")
+        if f and float(f) < 1.0:
+            return int(self.head_dim * float(f))
         return self.head_dim
 
     def rope_inv_freq(self):
@@ -440,6 +452,7 @@ _ARCH_NAME = {
     "gpt_oss": "GptOssForCausalLM",
     "granitemoehybrid": "GraniteMoeHybridForCausalLM",
     "llama4_text": "Llama4ForCausalLM",
+    "bamba": "BambaForCausalLM",
 }
 
 

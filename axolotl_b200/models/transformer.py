@@ -62,6 +62,7 @@ class Attention(nn.Module):
         self.eps = cfg.rms_norm_eps
         self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
+        self.rot_dim = cfg.rope_dim() if cfg.rope_dim() < self.D else None   # partial rotary embedding (Phi-4-mini, Bamba)
         self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
         self.softcap = cfg.attn_softcap()                      # Gemma 2: scores -> cap * tanh(scores / cap)
         # Llama 4: unweighted per-head L2 norm of q / k on rotating layers; those layers attend inside chunks of
@@ -93,7 +94,7 @@ class Attention(nn.Module):
             else:
                 qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
                                   self.q_norm.effective_weight() if per_head_norm else None,
-                                  self.k_norm.effective_weight() if per_head_norm else None, self.eps)
+                                  self.k_norm.effective_weight() if per_head_norm else None, self.eps, rot_dim=self.rot_dim)
         elif self.llama4 and self.temp is not None:
             floor_scale, a = self.temp
             t = torch.log1p(torch.floor((positions.float() + 1.0) / floor_scale)) * a + 1.0
@@ -526,7 +527,7 @@ class CausalLM(nn.Module):
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
-                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text"))
+                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

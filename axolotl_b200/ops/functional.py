@@ -178,9 +178,44 @@ class _RopeQK(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, dqn, dkn, None
 
 
+class _RopePartial(torch.autograd.Function):
+    """Rotary embedding of the first ``rot`` dimensions of every q and k head (in place on CUDA); the rest of the head
+    passes through. The backward pass is the inverse rotation of the gradient."""
+
+    @staticmethod
+    def _apply(qkv, pos, inv_freq, Hq, Hk, D, rot, attn_scale, sign):
+        T = qkv.shape[0]
+        if qkv.is_cuda:
+            _lib.check_rc(_lib.cuda_lib().axb_rope_partial(qkv.data_ptr(), pos.data_ptr(), inv_freq.data_ptr(), T, Hq + Hk, D,
+                                                           rot, qkv.stride(0), sign, attn_scale, _lib.stream_ptr()), "rope_partial")
+            return qkv
+        qk = qkv[:, : (Hq + Hk) * D].reshape(T, Hq + Hk, D)
+        out = torch.cat([_rope_ref(qk[..., :rot], pos, inv_freq, sign, attn_scale), qk[..., rot:]], -1)
+        return torch.cat([out.reshape(T, -1), qkv[:, (Hq + Hk) * D:]], 1)
+
+    @staticmethod
+    def forward(ctx, qkv, pos, inv_freq, Hq, Hk, D, rot, attn_scale):
+        ctx.dims = (Hq, Hk, D, rot, attn_scale)
+        ctx.save_for_backward(pos, inv_freq)
+        out = _RopePartial._apply(qkv, pos, inv_freq, Hq, Hk, D, rot, attn_scale, 1.0)
+        return out.detach() if qkv.is_cuda else out     # (alias handed out as a fresh tensor, as in _RopeQK)
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        pos, inv_freq = ctx.saved_tensors
+        Hq, Hk, D, rot, attn_scale = ctx.dims
+        g = _RopePartial._apply(dqkv.contiguous(), pos, inv_freq, Hq, Hk, D, rot, attn_scale, -1.0)
+        return g, None, None, None, None, None, None, None
+
+
 def rope_qk_(qkv, positions, inv_freq, Hq, Hk, D, attn_scale=1.0, q_norm_w=None, k_norm_w=None,
-             eps=1e-6):
-    """Rotates the q and k blocks of ``qkv`` [T, (Hq+2Hk)*D] (in place on CUDA)."""
+             eps=1e-6, rot_dim=None):
+    """Rotates the q and k blocks of ``qkv`` [T, (Hq+2Hk)*D] (in place on CUDA). ``rot_dim`` < D: partial rotary
+    embedding of the first ``rot_dim`` dimensions of each head (``inv_freq`` then has rot_dim / 2 entries)."""
+    if rot_dim is not None and rot_dim < D:
+        if q_norm_w is not None or k_norm_w is not None:
+            raise NotImplementedError("partial rotary embedding together with the fused q/k norm")
+        return _RopePartial.apply(qkv, positions, inv_freq, Hq, Hk, D, int(rot_dim), attn_scale)
     return _RopeQK.apply(qkv, positions, inv_freq, Hq, Hk, D, attn_scale, q_norm_w, k_norm_w, eps)
 
 

@@ -587,3 +587,55 @@ def test_llama4_text_matches_hf(tmp_path):
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+def test_partial_rotary_embedding_matches_hf(tmp_path):
+    """Phi-4-mini style: only the first `partial_rotary_factor` share of every head rotates."""
+    cfg = ModelConfig(model_type="phi3", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      extra={"partial_rotary_factor": 0.5, "pad_token_id": 0})
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(29)
+    assert ours.layers[0].self_attn.rot_dim == 8 and ours.inv_freq.numel() == 4
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [30, 17]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=5e-4, rtol=2e-3), (got - ref).abs().max()
+    # gradients flow through the partial rotation
+    ours.train()
+    ours(ids, pos, ids.clone()).loss.backward()
+    assert ours.layers[0].self_attn.qkv_proj.weight.grad.abs().sum() > 0
+
+
+def test_bamba_hybrid_matches_hf(tmp_path):
+    """Bamba: Mamba-2 mixers with attention layers that rotate half of every head."""
+    d = dict(model_type="bamba", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+             attn_layer_indices=[1], num_attention_heads=4, num_key_value_heads=2, mamba_n_heads=8, mamba_d_head="auto",
+             mamba_n_groups=1, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8, mamba_conv_bias=True,
+             mamba_proj_bias=False, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu",
+             max_position_embeddings=256, attention_bias=False, mlp_bias=False, pad_token_id=0,
+             rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5})
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(31)
+    assert [type(l.self_attn).__name__ for l in ours.layers] == ["Mamba2Mixer", "Attention", "Mamba2Mixer"]
+    assert ours.layers[1].self_attn.rot_dim == 8
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [27, 18]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)

@@ -1120,3 +1120,22 @@ def test_ebft_feature_rewards_kernel_matches_torch(whitening):
     one, _ = feature_rewards(gen[:P].to(_dev()), gt.to(_dev()), 1)
     ref, _ = feature_rewards(gen[:P], gt, 1)
     assert torch.allclose(one.cpu(), ref, atol=1e-4)
+
+
+def test_partial_rotary_kernel_matches_reference():
+    from axolotl_b200.ops.functional import rope_qk_
+    torch.manual_seed(61)
+    T, Hq, Hk, D, rot = 300, 4, 2, 64, 32
+    base = (torch.randn(T, (Hq + 2 * Hk) * D) * 0.5).bfloat16()
+    pos = torch.cat([torch.arange(180), torch.arange(120)]).to(torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    x = base.to(_dev()).requires_grad_(True)
+    y = rope_qk_(x * 1.0, pos.to(_dev()), inv.to(_dev()), Hq, Hk, D, 1.0, rot_dim=rot)
+    g = torch.randn(T, (Hq + 2 * Hk) * D).bfloat16()
+    (y.float() * g.to(_dev()).float()).sum().backward()
+    xc = base.float().requires_grad_(True)
+    yc = rope_qk_(xc, pos, inv, Hq, Hk, D, 1.0, rot_dim=rot)
+    (yc * g.float()).sum().backward()
+    assert _rel_err(y.cpu(), yc) < 1e-2 and _rel_err(x.grad.cpu(), xc.grad) < 1e-2
+    assert torch.equal(y[:, rot:D].cpu(), base[:, rot:D])                 # the tail of a head passes through
+    assert torch.equal(y[:, (Hq + Hk) * D:].cpu(), base[:, (Hq + Hk) * D:])   # v untouched

@@ -41,6 +41,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     mods = dict(model.named_modules())
     filled = set()
     expert_parts = {}
+    mxfp4_parts = {}
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
     bamba = getattr(model.config, "model_type", "") == "bamba"
     for name, t in named_tensors:
@@ -111,6 +112,25 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.router\.(weight|bias)$", name)):
             (mods[m.group(1)].gate if m.group(2) == "weight" else mods[m.group(1)].router_bias).copy_(t)
+            filled.add(name)
+        elif getattr(model.config, "model_type", "") == "gpt_oss" and (
+                m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(gate_up_proj|down_proj)_(blocks|scales)$", name)):
+            # the released MXFP4 checkpoints: packed E2M1 blocks [E, out, in / 32, 16] + e8m0 scales [E, out, in / 32];
+            # expanded to bf16 when both halves of a weight have arrived
+            slot = mxfp4_parts.setdefault((m.group(1), m.group(2)), {})
+            slot[m.group(3)] = t
+            if len(slot) == 2:
+                from .quant_formats import dequantize
+
+                blocks = slot["blocks"]
+                E, rows = blocks.shape[:2]
+                w = dequantize("mxfp4", blocks.reshape(E, rows, -1), {"_scale": slot["scales"].reshape(E, rows, -1)})
+                ex = mods[m.group(1)].experts
+                if m.group(2) == "gate_up_proj":
+                    ex.gate_up_proj.copy_(torch.cat([w[:, 0::2], w[:, 1::2]], 1))
+                else:
+                    ex.down_proj.copy_(w)
+                del mxfp4_parts[(m.group(1), m.group(2))]
             filled.add(name)
         elif getattr(model.config, "model_type", "") == "gpt_oss" and (
                 m := re.match(r"model\.(layers\.\d+\.mlp)\.experts\.(gate_up_proj|down_proj)(_bias)?$", name)):

@@ -99,3 +99,35 @@ def test_nf4_roundtrip_image_is_what_qlora_trained_against():
     assert not torch.equal(img, w) and float((img.float() - w.float()).abs().max()) < 0.04
     odd = torch.randn(7, 9)
     assert qf.simulate_nf4_roundtrip(odd) is odd
+
+
+def test_gpt_oss_mxfp4_checkpoint_loads_as_bf16(tmp_path):
+    """The released gpt-oss layout (packed blocks + e8m0 scales per expert weight) expands on load to the same model
+    as the bf16 checkpoint of the expanded values."""
+    from axolotl_b200.io import hf as hf_io
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.transformer import CausalLM
+    d = dict(model_type="gpt_oss", vocab_size=200, hidden_size=64, intermediate_size=64, num_hidden_layers=1,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=2, num_experts_per_tok=1,
+             sliding_window=8, layer_types=["full_attention"], tie_word_embeddings=False, max_position_embeddings=128)
+    cfg = ModelConfig.from_hf_dict(d)
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(5)
+    sd = hf_io.hf_state_dict(model)
+    packed = {}
+    for k in list(sd):
+        if k.endswith("experts.gate_up_proj") or k.endswith("experts.down_proj"):
+            w = sd.pop(k).transpose(1, 2).contiguous()                       # [E, out, in]
+            q = qf.requantize("mxfp4", w, {"_scale": torch.zeros(1, dtype=torch.uint8)})
+            E, rows = w.shape[:2]
+            packed[k + "_blocks"] = q[""].reshape(E, rows, -1, 16)
+            packed[k + "_scales"] = q["_scale"].reshape(E, rows, -1)
+            # the bf16 twin holds exactly the values the packed form expands to
+            sd[k] = qf.dequantize("mxfp4", q[""], {"_scale": q["_scale"]}).transpose(1, 2).contiguous()
+    ref = CausalLM(cfg, dtype=torch.float32)
+    hf_io.load_state_into(ref, sd.items())
+    got = CausalLM(cfg, dtype=torch.float32)
+    hf_io.load_state_into(got, {**{k: v for k, v in sd.items() if "experts.gate_up_proj" != k[-20:] and not k.endswith("experts.down_proj")
+                                    and not k.endswith("experts.gate_up_proj")}, **packed}.items())
+    ids = torch.randint(3, 200, (1, 24))
+    with torch.no_grad():
+        assert torch.allclose(got(ids, return_logits=True).logits, ref(ids, return_logits=True).logits, atol=1e-5)

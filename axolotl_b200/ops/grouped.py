@@ -356,8 +356,63 @@ class _LocalCombine(torch.autograd.Function):
         return dys, dw, None
 
 
+GEMV_MAX_SLOTS = 64     # decode steps: up to this many routed slots run as matrix-vector products
+
+
+def _gemv(x, slot_token, slot_expert, experts, which):
+    q = experts.nvfp4[which] if experts.nvfp4 is not None else None
+    S = slot_expert.numel()
+    if q is not None:
+        E, N, Kh = q["qdata"].shape
+        K = Kh * 2
+        args = (q["qdata"].data_ptr(), q["scale"].data_ptr(), _pts32(q).data_ptr(), 1)
+    else:
+        W = experts.gate_up_proj if which == "gate_up" else experts.down_proj
+        E, N, K = W.shape
+        args = (W.data_ptr(), None, None, 0)
+    out = torch.empty((S, N), dtype=torch.bfloat16, device=x.device)
+    _lib.check_rc(_lib.cuda_lib().axb_moe_gemv(x.data_ptr(), slot_token.data_ptr(), slot_expert.data_ptr(), args[0], args[1],
+                                               args[2], out.data_ptr(), S, E, N, K, args[3], _lib.stream_ptr()), "moe_gemv")
+    return out
+
+
+def _slot_lora(inp, slot_expert, experts, which):
+    """s * B_e (A_e v) per slot, for the few slots of a decode step (batched small products)."""
+    E = experts.E
+    A16, Bt16 = _adapter_operands(experts, which, experts.lora[which + "_A"], experts.lora[which + "_B"], E)
+    se = slot_expert.long()
+    t = torch.bmm(A16.index_select(0, se), inp.unsqueeze(-1))                    # [S, r, 1]
+    return float(experts.scaling) * torch.bmm(Bt16.index_select(0, se), t).squeeze(-1)
+
+
+@torch.no_grad()
+def moe_decode_forward(experts, x, w, idx):
+    """Expert pass of a generation step (a few tokens, no autograd): every routed slot is a GEMV against its expert
+    (``csrc/moe_gemv.cu``), NVFP4 weights decoded in registers; adapters are applied per slot."""
+    T, k = idx.shape
+    slot_expert = idx.reshape(-1).to(torch.int32).contiguous()
+    slot_token = (torch.arange(T * k, device=x.device, dtype=torch.int32) // k).contiguous()
+    x = x.contiguous()
+    use_lora = experts.lora is not None and adapters_enabled()
+    gu = _gemv(x, slot_token, slot_expert, experts, "gate_up")
+    if use_lora:
+        gu = gu + _slot_lora(x.index_select(0, slot_token.long()), slot_expert, experts, "gate_up").to(gu.dtype)
+    if getattr(experts, "gate_up_bias", None) is not None:
+        gu = gu + experts.gate_up_bias.to(gu.dtype).index_select(0, slot_expert.long())
+    h = Fn.glu(gu, experts.act, getattr(experts, "glu_limit", None)).contiguous()
+    own = torch.arange(T * k, device=x.device, dtype=torch.int32)
+    y = _gemv(h, own, slot_expert, experts, "down")
+    if use_lora:
+        y = y + _slot_lora(h, slot_expert, experts, "down").to(y.dtype)
+    if getattr(experts, "down_bias", None) is not None:
+        y = y + experts.down_bias.to(y.dtype).index_select(0, slot_expert.long())
+    return (y.view(T, k, -1).float() * w.float().unsqueeze(-1)).sum(1).to(x.dtype)
+
+
 def moe_local_forward(experts, x, w, idx, E):
     """Whole local MoE expert pass on CUDA: dispatch -> grouped projections -> weighted combine."""
+    if not torch.is_grad_enabled() and idx.numel() <= GEMV_MAX_SLOTS and x.dtype == torch.bfloat16:
+        return moe_decode_forward(experts, x, w, idx)
     lay = RoutedLayout(idx, E)
     xp = _LocalDispatch.apply(x, lay)
     yp = grouped_experts_padded(experts, xp, lay)

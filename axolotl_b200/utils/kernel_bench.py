@@ -300,6 +300,50 @@ def bench_decode(rows):
                     f"(prefill included)")
 
 
+def bench_attn_wide(rows):
+    """Wide-head attention (csrc/flash_wide.cu): head width 256 (Gemma, with and without the soft cap) and 192/128
+    (latent attention), causal packed documents; against flash-attn 2 where it takes the shape."""
+    from axolotl_b200.ops.functional import AttnMeta, flash_varlen
+
+    try:
+        from flash_attn import flash_attn_varlen_func
+    except Exception:  # pragma: no cover
+        flash_attn_varlen_func = None
+    tf, _, src = _peaks()
+    for name, Hq, Hk, D, Dv, cap, lens in (("gemma 256/256", 16, 8, 256, 256, 0.0, [2048] * 4),
+                                           ("gemma-2 256/256 softcap 50", 16, 8, 256, 256, 50.0, [2048] * 4),
+                                           ("gemma 256/256 one 8192 doc", 16, 8, 256, 256, 0.0, [8192]),
+                                           ("latent 192/128", 32, 32, 192, 128, 0.0, [2048] * 4)):
+        cu = [0]
+        for l in lens:
+            cu.append(cu[-1] + l)
+        T = cu[-1]
+        meta = AttnMeta(cu, "cuda")
+        qkv = (torch.randn(T, Hq * D + Hk * D + Hk * Dv, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+        g = torch.randn(T, Hq * Dv, device="cuda", dtype=torch.bfloat16)
+        fl = sum(2.0 * Hq * l * l * (D + Dv) / 2 for l in lens)          # causal: half of the full square
+        t_f = time_cuda(lambda: flash_varlen(qkv, meta, Hq, Hk, D, Dv=Dv, softcap=cap))
+        out = flash_varlen(qkv, meta, Hq, Hk, D, Dv=Dv, softcap=cap)
+        t_b = time_cuda(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True))
+        line = (f"attn wide {name}, {len(lens)} x {lens[0]} tokens, Hq={Hq} Hk={Hk}: fwd {t_f*1e3:.0f} us "
+                f"({fl / t_f / 1e9:.0f} TFLOP/s, {fl / t_f / 1e9 / tf:.2f} of {src} bf16 peak) | bwd {t_b*1e3:.0f} us "
+                f"({2.5 * fl / t_b / 1e9:.0f} TFLOP/s)")
+        if flash_attn_varlen_func is not None and D == Dv and not cap:
+            q = qkv.detach()[:, : Hq * D].reshape(T, Hq, D).contiguous().requires_grad_(True)
+            k = qkv.detach()[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D).contiguous().requires_grad_(True)
+            v = qkv.detach()[:, (Hq + Hk) * D:].reshape(T, Hk, Dv).contiguous().requires_grad_(True)
+            cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+            try:
+                f2 = lambda: flash_attn_varlen_func(q, k, v, cu_t, cu_t, max(lens), max(lens), causal=True)
+                t2 = time_cuda(f2)
+                o2 = f2()
+                t2b = time_cuda(lambda: torch.autograd.grad(o2, (q, k, v), g.view(T, Hq, Dv), retain_graph=True))
+                line += f" | flash-attn 2: fwd {t2*1e3:.0f} us, bwd {t2b*1e3:.0f} us"
+            except Exception as e:  # noqa: BLE001
+                line += f" | flash-attn 2: {type(e).__name__}"
+        rows.append(line)
+
+
 def bench_attn(rows):
     from axolotl_b200.ops.functional import AttnMeta, flash_varlen
 
@@ -454,6 +498,8 @@ def main(argv):
         bench_decode(rows)
     if what in ("w4a16",):
         bench_w4a16(rows)
+    if what in ("attn_wide",):
+        bench_attn_wide(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

@@ -1139,3 +1139,30 @@ def test_partial_rotary_kernel_matches_reference():
     assert _rel_err(y.cpu(), yc) < 1e-2 and _rel_err(x.grad.cpu(), xc.grad) < 1e-2
     assert torch.equal(y[:, rot:D].cpu(), base[:, rot:D])                 # the tail of a head passes through
     assert torch.equal(y[:, (Hq + Hk) * D:].cpu(), base[:, (Hq + Hk) * D:])   # v untouched
+
+
+@pytest.mark.parametrize("fp4", [False, True])
+def test_moe_decode_gemv_matches_grouped_path(fp4, monkeypatch):
+    """A generation step's expert pass (matrix-vector kernel, bf16 or NVFP4 weights, expert LoRA) against the grouped
+    tensor-core path on the same few tokens."""
+    from axolotl_b200.models.config import preset
+    from axolotl_b200.models.moe import SparseMoE
+    from axolotl_b200.ops import grouped
+    torch.manual_seed(62)
+    cfg = preset("tiny-qwen3-moe")
+    moe = SparseMoE(cfg, torch.bfloat16, _dev())
+    for p in moe.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    if fp4:
+        grouped.quantize_experts_nvfp4_(moe)
+    moe.experts.add_lora(8, 16)
+    with torch.no_grad():
+        for k in ("gate_up_A", "gate_up_B", "down_A", "down_B"):
+            moe.experts.lora[k].normal_(0, 0.05)
+    x = (torch.randn(5, cfg.hidden_size) * 0.5).bfloat16().to(_dev())
+    with torch.no_grad():
+        y_gemv, _ = moe(x)
+        monkeypatch.setattr(grouped, "GEMV_MAX_SLOTS", 0)
+        y_grouped, _ = moe(x)
+    _check_status()
+    assert _rel_err(y_gemv, y_grouped) < 1.5e-2

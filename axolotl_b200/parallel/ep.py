@@ -6,8 +6,8 @@ Per MoE layer and micro batch:
    weights) next to its hidden states in symmetric memory. After ONE flag barrier each rank reads all
    tables with peer loads and builds its plan on the device (which slots run on its experts, in
    expert-sorted padded order) with static shapes: buffers are sized by a capacity factor
-   (``AXB_EP_CAPACITY``, default 1.5 x the mean load; never more than the worst case), an overflow is
-   recorded on the device and raised at the end of the step. No NCCL call and no host synchronisation
+   (``AXB_EP_CAPACITY``, default 2 x the mean load; never more than the worst case); an overflow is
+   recorded on the device, the optimizer step it belongs to is skipped on every rank and the factor grows. No NCCL call and no host synchronisation
    happens on the layer path;
 2. DISPATCH: the destination ranks *pull* the rows routed to their experts with peer loads: each needed token once
    into a local staging area (``axb_ep_stage_rows``; top-k routing puts several slots of a token on
@@ -64,7 +64,7 @@ class ExpertParallelGroup:
         self.stage_by = os.environ.get("AXB_EP_STAGE", "sm")
         # Device-side plan: rows this rank may receive per layer call = capacity_factor x (its own slots), capped
         # at the worst case (every slot of every rank). AXB_EP_PLAN=host keeps the NCCL + host-sync plan.
-        self.capacity_factor = float(os.environ.get("AXB_EP_CAPACITY", "1.5"))
+        self.capacity_factor = float(os.environ.get("AXB_EP_CAPACITY", "2.0"))
         self.device_plan = self.fused and os.environ.get("AXB_EP_PLAN", "device") != "host"
         self.t_bufs = self.s_bufs = None
         self.kt = self.ks = 0
@@ -286,16 +286,35 @@ class ExpertParallelGroup:
             p.sent[dest_rank * T + torch.arange(n, device=dev) // k] = 1
         return p
 
-    def check_overflow(self):
-        """Raises when a layer call since the last check received more rows than the capacity allows
-        (one host synchronisation; the trainer calls it once per optimizer step)."""
+    def take_overflow(self) -> bool:
+        """True when ANY rank of the group received more rows than its capacity in a layer call since the last
+        check (rows were dropped there, so this step's gradients are incomplete on every rank). The capacity factor
+        then grows by half (up to the group size, where no overflow is possible) and the caller skips the update.
+        One small device all-reduce and one host read per optimizer step."""
         if self.overflow is None:
-            return
-        if int(self.overflow.item()):
+            return False
+        flag = self.overflow.to(torch.float32)
+        if self.fused and self.size > 1:
+            self.sync.all_reduce_(flag, channel=2)
+        hit = float(flag.item()) > 0
+        if hit:
             self.overflow.zero_()
-            raise RuntimeError(
-                f"expert parallelism: a rank received more than capacity_factor={self.capacity_factor} x its own "
-                f"slots in one layer call, rows were dropped; raise AXB_EP_CAPACITY (up to the group size)")
+            self.skipped_steps = getattr(self, "skipped_steps", 0) + 1
+            old = self.capacity_factor
+            self.capacity_factor = min(float(self.size), old * 1.5)
+            from ..utils.logging import get_logger
+
+            get_logger(__name__).warning(
+                "expert parallelism: a rank received more than %.2f x its own slots in one layer call; this optimizer "
+                "step is skipped and the capacity factor grows to %.2f (set expert_parallel_capacity_factor / "
+                "AXB_EP_CAPACITY to start higher)", old, self.capacity_factor)
+        return hit
+
+    def check_overflow(self):
+        """Raises when a layer call since the last check dropped rows (for callers that cannot skip a step)."""
+        if self.take_overflow():
+            raise RuntimeError("expert parallelism: rows were dropped in a layer call (capacity factor too small); "
+                               "raise AXB_EP_CAPACITY (up to the group size)")
 
     def return_slot_scalars_fused(self, vals_pad, plan):
         """Per-slot scalars of the padded rows -> [T, k] at the rank that routed the slot (peer stores)."""

@@ -98,8 +98,6 @@ class ParallelRuntime:
         pass
 
     def after_optimizer_step(self):
-        if self.ep is not None:
-            self.ep.check_overflow()
         if self.fsdp is not None:
             self.fsdp.end_of_step()
 
@@ -209,6 +207,8 @@ class ParallelRuntime:
     def optimizer_step(self, opt, lr):
         """Gradient synchronisation + clipping + optimizer update. Returns the squared global
         gradient norm (device scalar) or None."""
+        if self.ep is not None and self.ep.take_overflow():
+            return None      # rows were dropped in a layer call: no update from these gradients (the caller zeroes them)
         if self.tp is not None or self.ep is not None:
             return self._tp_step(opt, lr)
         if self.reduce_size <= 1:

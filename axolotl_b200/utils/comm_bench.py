@@ -119,10 +119,15 @@ def main():
             w = torch.randn(N, Kl, device=dev, dtype=torch.bfloat16) * 0.02
             t = timed(lambda: tp.reduced_gemm(a, w))
             fl = 2.0 * M * N * Kl
-            link = M * N * 2 * (world - 1)   # every rank adds its partial tile into every peer's buffer
+            # Per GPU and direction: the reducer CTAs of a rank own 1/world of the row blocks. With in-switch
+            # reduction (multimem.ld_reduce / multimem.st) a rank sends (world-1)/world of its partial tile to the
+            # other owners and its reduced 1/world once into the switch, i.e. one output tile in total; with plain
+            # peer loads and stores it pulls world-1 partial blocks and writes its sum to world-1 peers.
+            mc = any(getattr(b, "multicast_ptr", 0) for b in getattr(tp, "bufs", []) or []) or bool(getattr(getattr(tp, "buf", None), "multicast_ptr", 0))
+            link = M * N * 2 * (1.0 if mc else 2.0 * (world - 1) / world)
             roof = max(fl / (peak * 1e12), link / (NVLINK_GBS * 1e9)) * 1e3
             out.append(f"tp GEMM + all-reduce epilogue [M={M}, N={N}, K/tp={Kl}]: {t:.3f} ms ({fl / t / 1e9:.0f} TFLOP/s, "
-                       f"{link / t / 1e6:.0f} GB/s out per GPU); roofline {roof:.3f} ms -> {roof / t:.2f} of {how} roofline")
+                       f"{link / t / 1e6:.0f} GB/s per GPU and direction, {'in-switch reduction' if mc else 'peer loads'}); roofline {roof:.3f} ms -> {roof / t:.2f} of {how} roofline")
     _lib.check_status()
     if rank == 0:
         print("\n".join(out))

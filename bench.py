@@ -173,6 +173,9 @@ def main():
     torch.manual_seed(0)
     model = CausalLM(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
     if args.config == "moe":
+        # random-init routers are far less balanced than trained ones: start the expert-parallel row capacity at
+        # 3 x the mean load (an overflow would skip the step and grow it; skipped steps are reported below)
+        os.environ.setdefault("AXB_EP_CAPACITY", "3.0")
         from axolotl_b200.ops.grouped import quantize_experts_nvfp4_
 
         quantize_experts_nvfp4_(model)
@@ -322,7 +325,10 @@ def main():
                                        .get(args.config, f"fsdp{world}")) if world > 1 else "single",
                        "lora_r": 16, "lora_alpha": 32, "reshard_after_forward": args.reshard_after_forward == "true",
                        "optimizer": "adamw (fused, fp32 states)", "grad_accum": 1, "micro_batch": 2 if args.config == "moe" else 1,
-                       "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2"},
+                       "l2": "per-step working set (16 GB of weights + activations) far exceeds the 126 MB L2",
+                       **({"ep_capacity_factor": getattr(getattr(parallel, "ep", None), "capacity_factor", None),
+                           "ep_skipped_steps": int(getattr(getattr(parallel, "ep", None), "skipped_steps", 0))}
+                          if args.config == "moe" and world > 1 else {})},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": h2d_bytes(cpu_batches[W]) + 16 * (getattr(staged[W]["attn_meta"], "n_tiles", 0) * 2),

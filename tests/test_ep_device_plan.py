@@ -89,6 +89,8 @@ def test_device_plan_flags_overflow_instead_of_failing_silently():
     all_idx = torch.randint(0, 2, (world * T * k,), dtype=torch.int32)   # everything goes to rank 0's experts
     p = g._plan_from_tables(all_idx, torch.ones(world * T * k), all_idx[: T * k].reshape(T, k), 8)
     assert int(g.overflow) == 1 and int(p.lay.n_blocks) <= p.lay.max_blocks
+    assert g.take_overflow() and g.capacity_factor == 0.375 and int(g.overflow) == 0 and not g.take_overflow()
+    g.overflow += 1
     try:
         g.check_overflow()
         raise AssertionError("no error raised")

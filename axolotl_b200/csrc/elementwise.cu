@@ -368,8 +368,11 @@ __device__ __forceinline__ float act_bwd(float g, int kind) {
 // gu: [T, 2I] (gate | up);  h: [T, I] = act(gate) * up. With limit > 0 (clamped SwiGLU of the
 // DeepSeek-V4 / gpt-oss experts): act(min(gate, limit)) * clamp(up, -limit, limit), and the
 // gradients vanish where the clamp is active.
+// `blocks_in_use` (optional, device): only the first *blocks_in_use * 128 rows are processed: the padded expert layout
+// of a capacity-bounded plan uses a data-dependent prefix of its row buffer and nothing reads the rest.
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
-                               long long T, int I, int kind, float limit) {
+                               long long T, int I, int kind, float limit, const int* __restrict__ blocks_in_use) {
+  if (blocks_in_use) T = min(T, (long long)(*blocks_in_use) * 128);
   const long long nvec = T * (I / 8);
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
@@ -391,7 +394,8 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat
 __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
                                const __nv_bfloat16* __restrict__ gu,
                                __nv_bfloat16* __restrict__ dgu, long long T, int I, int kind,
-                               float limit) {
+                               float limit, const int* __restrict__ blocks_in_use) {
+  if (blocks_in_use) T = min(T, (long long)(*blocks_in_use) * 128);
   const long long nvec = T * (I / 8);
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
@@ -881,7 +885,24 @@ extern "C" int axb_glu_fwd(const void* gu, void* h, long long T, int I, int kind
   if (I % 8) return -2;
   if (T <= 0) return 0;
   glu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind, limit);
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind, limit, nullptr);
+  return (int)cudaGetLastError();
+}
+// the same over the first *blocks_in_use * 128 rows only (device-side count)
+extern "C" int axb_glu_fwd_rows(const void* gu, void* h, long long T, int I, int kind, float limit,
+                                const int* blocks_in_use, void* stream) {
+  if (I % 8) return -2;
+  if (T <= 0) return 0;
+  glu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, T, I, kind, limit, blocks_in_use);
+  return (int)cudaGetLastError();
+}
+extern "C" int axb_glu_bwd_rows(const void* dh, const void* gu, void* dgu, long long T, int I, int kind,
+                                float limit, const int* blocks_in_use, void* stream) {
+  if (I % 8) return -2;
+  if (T <= 0) return 0;
+  glu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind, limit, blocks_in_use);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_glu_bwd(const void* dh, const void* gu, void* dgu, long long T, int I, int kind,
@@ -889,7 +910,7 @@ extern "C" int axb_glu_bwd(const void* dh, const void* gu, void* dgu, long long 
   if (I % 8) return -2;
   if (T <= 0) return 0;
   glu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, ST(stream)>>>(
-      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind, limit);
+      (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, kind, limit, nullptr);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_embedding_fwd(const void* table, const long long* ids, void* out, long long T,

@@ -179,7 +179,9 @@ struct PeerPtrs8 {
 __global__ void ep_gather_rows_kernel(PeerPtrs8 src, const int* __restrict__ src_rank,
                                       const int* __restrict__ src_row, const float* __restrict__ scale,
                                       const __nv_bfloat16* __restrict__ dot_with, float* __restrict__ dot_out,
-                                      __nv_bfloat16* __restrict__ out, long long n_rows, int width, long long src_ld) {
+                                      __nv_bfloat16* __restrict__ out, long long n_rows, int width, long long src_ld,
+                                      const int* __restrict__ blocks_in_use) {
+  if (blocks_in_use) n_rows = min(n_rows, (long long)(*blocks_in_use) * 128);   // rows beyond the used blocks are never read
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -434,7 +436,21 @@ extern "C" int axb_ep_gather_rows(const unsigned long long* src_ptrs, int world,
   if (fill8(p, src_ptrs, world)) return -2;
   int grid = (int)((n_rows + 7) / 8 > 148 * 8 ? 148 * 8 : (n_rows + 7) / 8);
   ep_gather_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, src_rank, src_row, scale, (const __nv_bfloat16*)dot_with,
-                                                      dot_out, (__nv_bfloat16*)out, n_rows, width, src_ld);
+                                                      dot_out, (__nv_bfloat16*)out, n_rows, width, src_ld, nullptr);
+  return (int)cudaGetLastError();
+}
+// the same over the first *blocks_in_use * 128 rows only (device-side count of the capacity-bounded plan)
+extern "C" int axb_ep_gather_rows_n(const unsigned long long* src_ptrs, int world, const int* src_rank,
+                                    const int* src_row, const float* scale, const void* dot_with, float* dot_out,
+                                    void* out, long long n_rows, int width, long long src_ld, const int* blocks_in_use,
+                                    void* stream) {
+  if (n_rows <= 0) return 0;
+  if (width % 8 || src_ld % 8) return -2;
+  PeerPtrs8 p;
+  if (fill8(p, src_ptrs, world)) return -2;
+  int grid = (int)((n_rows + 7) / 8 > 148 * 8 ? 148 * 8 : (n_rows + 7) / 8);
+  ep_gather_rows_kernel<<<grid, 256, 0, ST(stream)>>>(p, src_rank, src_row, scale, (const __nv_bfloat16*)dot_with,
+                                                      dot_out, (__nv_bfloat16*)out, n_rows, width, src_ld, blocks_in_use);
   return (int)cudaGetLastError();
 }
 

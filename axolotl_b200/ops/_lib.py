@@ -47,6 +47,9 @@ _CUDA_SIGS = {
     "axb_flash_wide_fwd": [vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, i64, vp, f32, f32, vp, vp],
     "axb_flash_wide_bwd": [vp, i64, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, i64, vp, vp,
                            f32, f32, vp, vp],
+    "axb_glu_fwd_rows": [vp, vp, i64, i32, i32, f32, vp, vp],
+    "axb_glu_bwd_rows": [vp, vp, vp, i64, i32, i32, f32, vp, vp],
+    "axb_ep_gather_rows_n": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, i64, vp, vp],
     "axb_moe_gemv": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "axb_rope_partial": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp],
     "axb_ebft_rewards": [vp, vp, vp, vp, i32, i32, i32, i32, vp],

@@ -231,9 +231,10 @@ def _act_ref(g, kind):
 
 class _GLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gu, kind, limit):
+    def forward(ctx, gu, kind, limit, blocks=None):
         I = gu.shape[-1] // 2
         ctx.kind, ctx.limit = kind, float(limit or 0.0)
+        ctx.blocks = blocks if gu.is_cuda else None
         ctx.save_for_backward(gu)
         if not gu.is_cuda:
             g, u = gu[..., :I].float(), gu[..., I:].float()
@@ -243,8 +244,12 @@ class _GLU(torch.autograd.Function):
         lib = _lib.cuda_lib()
         gu2 = gu.reshape(-1, 2 * I)
         h = torch.empty((gu2.shape[0], I), dtype=gu.dtype, device=gu.device)
-        _lib.check_rc(lib.axb_glu_fwd(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind, ctx.limit,
-                                      _lib.stream_ptr()), "glu_fwd")
+        if ctx.blocks is not None:
+            _lib.check_rc(lib.axb_glu_fwd_rows(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind, ctx.limit,
+                                               ctx.blocks.data_ptr(), _lib.stream_ptr()), "glu_fwd_rows")
+        else:
+            _lib.check_rc(lib.axb_glu_fwd(gu2.data_ptr(), h.data_ptr(), gu2.shape[0], I, kind, ctx.limit,
+                                          _lib.stream_ptr()), "glu_fwd")
         return h.view(*gu.shape[:-1], I)
 
     @staticmethod
@@ -265,21 +270,27 @@ class _GLU(torch.autograd.Function):
             if L > 0:
                 dg = dg * (g_raw <= L)
                 du = du * ((u_raw >= -L) & (u_raw <= L))
-            return torch.cat([dg, du], -1).to(gu.dtype), None, None
+            return torch.cat([dg, du], -1).to(gu.dtype), None, None, None
         lib = _lib.cuda_lib()
         gu2 = gu.reshape(-1, 2 * I)
         dh2 = dh.reshape(-1, I).contiguous()
         dgu = torch.empty_like(gu2)
-        _lib.check_rc(lib.axb_glu_bwd(dh2.data_ptr(), gu2.data_ptr(), dgu.data_ptr(), gu2.shape[0],
-                                      I, ctx.kind, L, _lib.stream_ptr()), "glu_bwd")
-        return dgu.view(gu.shape), None, None
+        if ctx.blocks is not None:
+            _lib.check_rc(lib.axb_glu_bwd_rows(dh2.data_ptr(), gu2.data_ptr(), dgu.data_ptr(), gu2.shape[0], I, ctx.kind, L,
+                                               ctx.blocks.data_ptr(), _lib.stream_ptr()), "glu_bwd_rows")
+        else:
+            _lib.check_rc(lib.axb_glu_bwd(dh2.data_ptr(), gu2.data_ptr(), dgu.data_ptr(), gu2.shape[0],
+                                          I, ctx.kind, L, _lib.stream_ptr()), "glu_bwd")
+        return dgu.view(gu.shape), None, None, None
 
 
-def glu(gate_up, activation="silu", limit=None):
+def glu(gate_up, activation="silu", limit=None, blocks_in_use=None):
     """``act(gate) * up`` for a fused ``[.., 2I]`` (gate | up) projection. With ``limit`` the gate is
     clamped from above and the up branch to ``[-limit, limit]`` first (the clamped SwiGLU of the
     reference's grouped expert graph,
     src/axolotl/integrations/kernels/libs/scattermoe_lora/cutlass_fp4/swiglu.py:16-148)."""
+    if blocks_in_use is not None:       # int32 device scalar: only the first blocks_in_use * 128 rows hold data
+        return _GLU.apply(gate_up, _ACT_KIND[activation], limit, blocks_in_use)
     return _GLU.apply(gate_up, _ACT_KIND[activation], limit)
 
 

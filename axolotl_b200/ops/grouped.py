@@ -438,7 +438,8 @@ def grouped_experts_padded(experts, x, lay):
     if getattr(experts, "gate_up_bias", None) is not None:     # per-expert biases (gpt-oss): one row gather + add
         row_e = lay.blk_expert.long().repeat_interleave(BLOCK)
         gu = gu + experts.gate_up_bias.to(gu.dtype).index_select(0, row_e)
-    h = Fn.glu(gu, experts.act, getattr(experts, "glu_limit", None))
+    h = Fn.glu(gu, experts.act, getattr(experts, "glu_limit", None),
+               blocks_in_use=lay.n_blocks if getattr(lay, "prefix_only", False) else None)
     y = _GroupedProj.apply(h, experts, "down", lay, L["down_A"] if L else None, L["down_B"] if L else None,
                            float(experts.scaling))
     if row_e is not None:

@@ -261,6 +261,7 @@ class ExpertParallelGroup:
         lay.n_blocks = (seg_end[-1:] // BLOCK).clamp(max=lay.max_blocks).to(torch.int32)
         lay.seg_start = seg_start.to(torch.int32)
         lay.seg_rows = padded.to(torch.int32)
+        lay.prefix_only = True      # rows beyond n_blocks * 128 are never written or read (capacity slack)
         src_rank = torch.div(order, n, rounding_mode="floor").to(torch.int32)
         src_slot = (order % n).to(torch.int32)
         p = _Plan()
@@ -379,12 +380,13 @@ class ExpertParallelGroup:
                 _lib.check_rc(lib.axb_ep_stage_rows(buf.ptrs_c, self.size, self.rank, plan.need.data_ptr(),
                                                     self.staging.data_ptr(), T, H, _lib.stream_ptr()), "ep_stage_rows")
             src_ptrs = self._slices(self.staging.data_ptr(), T * H * 2, buf.tensor.data_ptr())
-        _lib.check_rc(lib.axb_ep_gather_rows(src_ptrs, self.size, plan.pad_src_rank.data_ptr(),
-                                             plan.pad_src_row.data_ptr(),
-                                             plan.pad_weight.data_ptr() if weighted else None,
-                                             dot_with.data_ptr() if dot_with is not None else None,
-                                             dots.data_ptr() if dots is not None else None,
-                                             out.data_ptr(), n, H, H, _lib.stream_ptr()), "ep_gather_rows")
+        args = (src_ptrs, self.size, plan.pad_src_rank.data_ptr(), plan.pad_src_row.data_ptr(),
+                plan.pad_weight.data_ptr() if weighted else None, dot_with.data_ptr() if dot_with is not None else None,
+                dots.data_ptr() if dots is not None else None, out.data_ptr(), n, H, H)
+        if getattr(plan.lay, "prefix_only", False):
+            _lib.check_rc(lib.axb_ep_gather_rows_n(*args, plan.lay.n_blocks.data_ptr(), _lib.stream_ptr()), "ep_gather_rows")
+        else:
+            _lib.check_rc(lib.axb_ep_gather_rows(*args, _lib.stream_ptr()), "ep_gather_rows")
         return out if dot_with is None else (out, dots)
 
     def push_rows(self, rows, plan, weighted):

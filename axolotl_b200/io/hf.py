@@ -44,6 +44,8 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     mxfp4_parts = {}
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
     bamba = getattr(model.config, "model_type", "") == "bamba"
+    if getattr(model.config, "model_type", "") == "nemotron_h":
+        return _nemotron_h_load(model, named_tensors, strict)
     for name, t in named_tensors:
         if llama4:
             name, t = _llama4_in(model, name, t)
@@ -329,6 +331,71 @@ def _mamba_tensors(pre, mx, sd):
         sd[f"{pre}.mamba.{leaf}"] = getattr(mx, leaf).detach()
 
 
+def _nemotron_h_state_dict(model):
+    """Nemotron-H names: `model.embeddings`, per layer `norm` + `mixer.*`, `model.norm_f`."""
+    sd = {"model.embeddings.weight": model.embed_tokens.detach(), "model.norm_f.weight": model.norm.weight.detach()}
+    if model.lm_head is not None:
+        sd["lm_head.weight"] = model.lm_head.detach()
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}"
+        sd[f"{pre}.norm.weight"] = layer.norm.weight.detach()
+        mx = layer.mixer
+        if layer.kind == "mamba":
+            tmp = {}
+            _mamba_tensors(pre, mx, tmp)
+            sd.update({k.replace(".mamba.", ".mixer."): v for k, v in tmp.items()})
+        else:
+            for fl in ([mx.qkv_proj, mx.o_proj] if layer.kind == "attention" else [mx.up_proj, mx.down_proj]):
+                for sub in fl.names:
+                    r0, r1 = fl.row_range(sub)
+                    sd[f"{pre}.mixer.{sub}.weight"] = fl.weight.detach()[r0:r1]
+                    if fl.bias is not None:
+                        sd[f"{pre}.mixer.{sub}.bias"] = fl.bias.detach()[r0:r1]
+    return sd
+
+
+@torch.no_grad()
+def _nemotron_h_load(model, named_tensors, strict=True):
+    filled = set()
+    for name, t in named_tensors:
+        name = name.replace("backbone.", "model.")
+        if name == "model.embeddings.weight":
+            model.embed_tokens.copy_(t)
+        elif name == "model.norm_f.weight":
+            model.norm.weight.copy_(t)
+        elif name == "lm_head.weight":
+            if model.lm_head is not None:
+                model.lm_head.copy_(t)
+        elif (m := re.match(r"model\.layers\.(\d+)\.norm\.weight$", name)):
+            model.layers[int(m.group(1))].norm.weight.copy_(t)
+        elif (m := re.match(r"model\.layers\.(\d+)\.mixer\.(.+)$", name)):
+            layer, leaf = model.layers[int(m.group(1))], m.group(2)
+            mx = layer.mixer
+            if layer.kind == "mamba":
+                if leaf == "conv1d.weight":
+                    mx.conv_weight.copy_(t.reshape(t.shape[0], t.shape[-1]))
+                elif leaf == "conv1d.bias":
+                    mx.conv_bias.copy_(t)
+                elif leaf == "norm.weight":
+                    mx.norm_weight.copy_(t)
+                elif leaf in ("dt_bias", "A_log", "D"):
+                    getattr(mx, leaf).copy_(t)
+                else:
+                    getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
+            else:
+                sub, kind = leaf.rsplit(".", 1)
+                fl = {"q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj"}.get(sub, sub)
+                fl = getattr(mx, fl)
+                r0, r1 = fl.row_range(sub)
+                (fl.weight if kind == "weight" else fl.bias)[r0:r1].copy_(t)
+        elif name.endswith("rotary_emb.inv_freq"):
+            continue
+        elif strict:
+            raise KeyError(f"unexpected checkpoint tensor '{name}'")
+        filled.add(name)
+    return filled
+
+
 def _bamba_state_dict(model, sd):
     """Bamba names: `mamba.*` mixers, `pre_ff_layernorm`, `feed_forward`, `final_layernorm`."""
     sd["model.final_layernorm.weight"] = sd.pop("model.norm.weight")
@@ -396,6 +463,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
         return _granite_hybrid_state_dict(model, sd)
     if getattr(model.config, "model_type", "") == "bamba":
         return _bamba_state_dict(model, sd)
+    if getattr(model.config, "model_type", "") == "nemotron_h":
+        return _nemotron_h_state_dict(model)
     for name, m in model.named_modules():
         if gpt_oss and isinstance(m, Experts):
             def interleave(u):            # [E, 2I, ...] gate rows then up rows -> alternating

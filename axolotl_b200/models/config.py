@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 
 
@@ -109,6 +109,18 @@ class ModelConfig:
                 every = d.get("no_rope_layer_interval") or 4
                 d["no_rope_layers"] = [int((i + 1) % every != 0) for i in range(L)]
             d.setdefault("rms_norm_eps", 1e-5)
+        if mt == "nemotron_h":
+            types = d.get("layers_block_type")
+            if not types and d.get("hybrid_override_pattern"):          # "M" mamba, "*" attention, "-" MLP
+                types = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[c] for c in d["hybrid_override_pattern"]]
+            if not types:
+                raise ValueError("nemotron_h: the config lists neither layers_block_type nor hybrid_override_pattern")
+            if "moe" in types:
+                raise ValueError("nemotron_h: blocks of type `moe` (latent, non-gated experts) are not supported")
+            d["block_types"] = list(types)
+            d["num_hidden_layers"] = len(types)
+            d["rms_norm_eps"] = d.get("layer_norm_epsilon", 1e-5)
+            d["hidden_act"] = d.get("mlp_hidden_act", "relu2")
         if mt == "bamba":
             if d.get("mamba_d_head") in (None, "auto"):
                 d["mamba_d_head"] = int((d.get("mamba_expand") or 2) * d["hidden_size"]) // int(d.get("mamba_n_heads") or 128)
@@ -178,6 +190,10 @@ class ModelConfig:
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size")
             d["hidden_act"] = "silu"
+        if self.model_type == "nemotron_h":
+            d["layers_block_type"] = list(extra.get("block_types") or [])
+            d["layer_norm_epsilon"] = d.get("rms_norm_eps", 1e-5)
+            d["mlp_hidden_act"] = d.pop("hidden_act", "relu2")
         if self.model_type == "llama4_text":
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size") or d.get("intermediate_size")
@@ -289,8 +305,10 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
-        if self.model_type not in ("granitemoehybrid", "bamba"):
+        if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h"):
             return "attention"
+        if self.model_type == "nemotron_h":
+            return (self.extra or {})["block_types"][idx]          # "mamba" | "attention" | "mlp": one block per layer
         if self.model_type == "bamba":
             return "attention" if idx in set((self.extra or {}).get("attn_layer_indices") or []) else "mamba"
         types = (self.extra or {}).get("layer_types") or (self.extra or {}).get("layers_block_type")
@@ -301,6 +319,8 @@ class ModelConfig:
         attention layers carry no position signal unless ``position_embedding_type`` is ``rope``."""
         if self.model_type == "granitemoehybrid":
             return (self.extra or {}).get("position_embedding_type") == "rope"
+        if self.model_type == "nemotron_h":
+            return False                                           # its attention blocks carry no position signal
         if self.model_type == "llama4_text":
             return bool((self.extra or {})["no_rope_layers"][idx])           # 1 = this layer rotates
         if self.model_type != "smollm3":
@@ -453,6 +473,7 @@ _ARCH_NAME = {
     "granitemoehybrid": "GraniteMoeHybridForCausalLM",
     "llama4_text": "Llama4ForCausalLM",
     "bamba": "BambaForCausalLM",
+    "nemotron_h": "NemotronHForCausalLM",
 }
 
 

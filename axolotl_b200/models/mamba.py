@@ -54,21 +54,31 @@ class Mamba2Mixer(nn.Module):
         super().__init__()
         ex = cfg.extra or {}
         H = cfg.hidden_size
-        self.nh, self.P = int(ex["mamba_n_heads"]), int(ex["mamba_d_head"])
-        self.G, self.N = int(ex.get("mamba_n_groups", 1)), int(ex["mamba_d_state"])
-        self.k = int(ex.get("mamba_d_conv", 4))
-        self.d_inner = int(ex.get("mamba_expand", 2) * H)
-        if self.d_inner != self.nh * self.P:
-            raise ValueError(f"mamba_expand * hidden ({self.d_inner}) must equal mamba_n_heads * mamba_d_head ({self.nh * self.P})")
+        if cfg.model_type == "nemotron_h":      # its own key names; the inner width is heads x head width; grouped gated norm
+            self.nh, self.P = int(ex["mamba_num_heads"]), int(ex["mamba_head_dim"])
+            self.G, self.N = int(ex.get("n_groups", 8)), int(ex["ssm_state_size"])
+            self.k = int(ex.get("conv_kernel", 4))
+            self.d_inner = self.nh * self.P
+            self.chunk = int(ex.get("chunk_size", 128))
+            self.norm_groups = self.G
+            bias, conv_bias = bool(ex.get("use_bias", False)), bool(ex.get("use_conv_bias", True))
+        else:
+            self.nh, self.P = int(ex["mamba_n_heads"]), int(ex["mamba_d_head"])
+            self.G, self.N = int(ex.get("mamba_n_groups", 1)), int(ex["mamba_d_state"])
+            self.k = int(ex.get("mamba_d_conv", 4))
+            self.d_inner = int(ex.get("mamba_expand", 2) * H)
+            if self.d_inner != self.nh * self.P:
+                raise ValueError(f"mamba_expand * hidden ({self.d_inner}) must equal mamba_n_heads * mamba_d_head ({self.nh * self.P})")
+            self.chunk = int(ex.get("mamba_chunk_size", 256))
+            self.norm_groups = 1
+            bias, conv_bias = bool(ex.get("mamba_proj_bias", False)), bool(ex.get("mamba_conv_bias", True))
         self.conv_dim = self.d_inner + 2 * self.G * self.N
-        self.chunk = int(ex.get("mamba_chunk_size", 256))
         lim = ex.get("time_step_limit") or (0.0, float("inf"))
         self.dt_limit = (float(lim[0]), float(lim[1]))
         self.eps = cfg.rms_norm_eps
-        bias = bool(ex.get("mamba_proj_bias", False))
         self.in_proj = FusedLinear(H, [self.d_inner + self.conv_dim + self.nh], ["in_proj"], bias=bias, dtype=dtype, device=device)
         self.conv_weight = nn.Parameter(torch.empty(self.conv_dim, self.k, dtype=dtype, device=device))
-        self.conv_bias = nn.Parameter(torch.zeros(self.conv_dim, dtype=dtype, device=device)) if ex.get("mamba_conv_bias", True) else None
+        self.conv_bias = nn.Parameter(torch.zeros(self.conv_dim, dtype=dtype, device=device)) if conv_bias else None
         self.dt_bias = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
         self.A_log = nn.Parameter(torch.log(torch.arange(1, self.nh + 1, dtype=torch.float32, device=device)).to(dtype))
         self.D = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
@@ -107,6 +117,10 @@ class Mamba2Mixer(nn.Module):
         ys = [ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s]
         y = torch.cat(ys, 0) + self.D.float()[None, :, None] * xs
         y = y.reshape(T, self.d_inner) * F.silu(z.float())                       # gate first, then the norm
-        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
+        if self.norm_groups > 1:                                                 # one RMS per group of channels
+            yg = y.view(T, self.norm_groups, -1)
+            y = (yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + self.eps)).reshape(T, self.d_inner)
+        else:
+            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
         y = (self.norm_weight.float() * y).to(x.dtype)
         return self.out_proj(y)

@@ -152,6 +152,59 @@ class MLP(nn.Module):
         return torch.cat(outs, 0)
 
 
+class PlainMLP(nn.Module):
+    """up -> activation -> down without a gate (Nemotron-H: squared ReLU)."""
+
+    def __init__(self, hidden, inter, act, bias, dtype, device):
+        super().__init__()
+        self.up_proj = FusedLinear(hidden, [inter], ["up_proj"], bias=bias, dtype=dtype, device=device)
+        self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
+        if act not in ("relu2", "relu", "gelu", "silu"):
+            raise ValueError(f"activation '{act}' is not available for an ungated MLP")
+        self.act = act
+
+    def forward(self, x):
+        u = self.up_proj(x)
+        if self.act == "relu2":
+            u = torch.relu(u).square()
+        elif self.act == "relu":
+            u = torch.relu(u)
+        elif self.act == "gelu":
+            u = torch.nn.functional.gelu(u)
+        else:
+            u = torch.nn.functional.silu(u)
+        return self.down_proj(u)
+
+
+class SingleBlockLayer(nn.Module):
+    """norm -> ONE block (state-space mixer, attention or MLP) -> residual: the layer form of Nemotron-H, whose
+    layer list interleaves the three kinds."""
+
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
+        super().__init__()
+        self.kind = cfg.layer_kind(idx)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        ex = cfg.extra or {}
+        if self.kind == "mamba":
+            from .mamba import Mamba2Mixer
+
+            self.mixer = Mamba2Mixer(cfg, dtype, device)
+        elif self.kind == "attention":
+            self.mixer = Attention(cfg, dtype, device)
+            self.mixer.layer_idx = idx
+            self.mixer.use_rope = cfg.uses_rope(idx)
+            self.mixer.window = int(ex.get("sliding_window") or 0)
+        else:
+            self.mixer = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
+        self.is_moe = False
+
+    def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
+        x, residual = self.norm(h, residual)
+        if self.kind == "mlp":
+            return self.mixer(x), residual, None
+        return self.mixer(x, positions, inv_freq, attn_scale, meta), residual, None
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
         super().__init__()
@@ -246,7 +299,8 @@ class CausalLM(nn.Module):
         self.config = cfg
         self.dtype = dtype
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
-        self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
+        layer_cls = SingleBlockLayer if cfg.model_type == "nemotron_h" else DecoderLayer
+        self.layers = nn.ModuleList([layer_cls(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=cfg.norm_offset())
         self.final_softcap = cfg.final_softcap()   # Gemma 2: logits -> cap * tanh(logits / cap)
         if cfg.tie_word_embeddings:
@@ -527,7 +581,8 @@ class CausalLM(nn.Module):
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
-                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba"))
+                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
+                                                             "nemotron_h"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -44,11 +44,35 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     mxfp4_parts = {}
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
     bamba = getattr(model.config, "model_type", "") == "bamba"
+    qwen3_next = getattr(model.config, "model_type", "") == "qwen3_next"
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
     for name, t in named_tensors:
         if llama4:
             name, t = _llama4_in(model, name, t)
+        if qwen3_next:
+            if (m := re.match(r"model\.(layers\.\d+)\.linear_attn\.(.+)$", name)):
+                mx, leaf = mods[m.group(1) + ".self_attn"], m.group(2)
+                if leaf == "conv1d.weight":
+                    mx.conv_weight.copy_(t.reshape(t.shape[0], t.shape[-1]))
+                elif leaf == "norm.weight":
+                    mx.norm_weight.copy_(t)
+                elif leaf in ("dt_bias", "A_log"):
+                    getattr(mx, leaf).copy_(t)
+                else:
+                    getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
+                filled.add(name)
+                continue
+            if (m := re.match(r"model\.(layers\.\d+\.self_attn)\.q_proj\.(weight|bias)$", name)):
+                at = mods[m.group(1)]           # rows per head: [query (D) | gate (D)]
+                u = t.reshape(at.Hq, 2, at.D, *t.shape[1:])
+                r0, r1 = at.qkv_proj.row_range("q_proj")
+                (at.qkv_proj.weight if m.group(2) == "weight" else at.qkv_proj.bias)[r0:r1].copy_(u[:, 0].reshape(at.Hq * at.D, *t.shape[1:]))
+                (at.out_gate.weight if m.group(2) == "weight" else at.out_gate.bias).copy_(u[:, 1].reshape(at.Hq * at.D, *t.shape[1:]))
+                filled.add(name)
+                continue
+            if name.startswith("mtp."):
+                continue                         # multi-token-prediction head: not part of the training graph
         if bamba:
             name = (name.replace(".pre_ff_layernorm.", ".post_attention_layernorm.").replace(".feed_forward.", ".mlp.")
                     .replace("model.final_layernorm.", "model.norm."))
@@ -418,6 +442,29 @@ def _bamba_state_dict(model, sd):
     return sd
 
 
+def _qwen3_next_out(model, sd):
+    """Qwen3-Next names: `linear_attn.*` for the DeltaNet mixers; q_proj carries the output-gate rows head by head."""
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}"
+        mx = layer.self_attn
+        if type(mx).__name__ == "GatedDeltaNet":
+            for k in [k for k in sd if k.startswith(pre + ".self_attn.")]:
+                sd.pop(k)
+            sd[f"{pre}.linear_attn.in_proj_qkvz.weight"] = mx.in_proj_qkvz.weight.detach()
+            sd[f"{pre}.linear_attn.in_proj_ba.weight"] = mx.in_proj_ba.weight.detach()
+            sd[f"{pre}.linear_attn.out_proj.weight"] = mx.out_proj.weight.detach()
+            sd[f"{pre}.linear_attn.conv1d.weight"] = mx.conv_weight.detach()[:, None, :]
+            sd[f"{pre}.linear_attn.norm.weight"] = mx.norm_weight.detach()
+            sd[f"{pre}.linear_attn.dt_bias"] = mx.dt_bias.detach()
+            sd[f"{pre}.linear_attn.A_log"] = mx.A_log.detach()
+        else:
+            q = sd.pop(f"{pre}.self_attn.q_proj.weight")
+            gate = sd.pop(f"{pre}.self_attn.q_gate.weight")
+            sd[f"{pre}.self_attn.q_proj.weight"] = torch.stack([q.reshape(mx.Hq, mx.D, -1), gate.reshape(mx.Hq, mx.D, -1)], 1) \
+                .reshape(2 * mx.Hq * mx.D, -1)
+    return sd
+
+
 def _granite_hybrid_state_dict(model, sd):
     """Granite 4.0-H names: `mamba.*` mixers, `shared_mlp`, `block_sparse_moe`."""
     for i, layer in enumerate(model.layers):
@@ -515,6 +562,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 sd[f"model.{name}.gate.e_score_correction_bias"] = m.e_score_correction_bias.detach()
     if getattr(model.config, "model_type", "") == "llama4_text":
         return _llama4_out(model, sd)
+    if getattr(model.config, "model_type", "") == "qwen3_next":
+        return _qwen3_next_out(model, sd)
     return sd
 
 

@@ -14,8 +14,9 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
+ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
 
 
 @dataclass
@@ -62,7 +63,7 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
-        if self.model_type == "gemma3_text":
+        if self.model_type in ("gemma3_text", "qwen3_next"):
             self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -109,6 +110,13 @@ class ModelConfig:
                 every = d.get("no_rope_layer_interval") or 4
                 d["no_rope_layers"] = [int((i + 1) % every != 0) for i in range(L)]
             d.setdefault("rms_norm_eps", 1e-5)
+        if mt == "qwen3_next":
+            L = d.get("num_hidden_layers", 0)
+            if not d.get("layer_types"):
+                every = d.get("full_attention_interval") or 4
+                d["layer_types"] = ["full_attention" if (i + 1) % every == 0 else "linear_attention" for i in range(L)]
+            d.setdefault("partial_rotary_factor", 0.25)
+            d.setdefault("norm_topk_prob", True)
         if mt == "nemotron_h":
             types = d.get("layers_block_type")
             if not types and d.get("hybrid_override_pattern"):          # "M" mamba, "*" attention, "-" MLP
@@ -245,7 +253,7 @@ class ModelConfig:
 
     def norm_offset(self) -> float:
         """Gemma stores RMSNorm weights as ``w`` and applies ``1 + w``."""
-        return 1.0 if self.model_type in GEMMA_TYPES else 0.0
+        return 1.0 if self.model_type in ZERO_CENTERED_NORM_TYPES else 0.0
 
     def sandwich_norms(self) -> bool:
         """Gemma 2 / 3 normalise the output of the attention and MLP branches too (four norms per layer)."""
@@ -305,8 +313,10 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
-        if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h"):
+        if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h", "qwen3_next"):
             return "attention"
+        if self.model_type == "qwen3_next":
+            return "deltanet" if (self.extra or {})["layer_types"][idx] == "linear_attention" else "attention"
         if self.model_type == "nemotron_h":
             return (self.extra or {})["block_types"][idx]          # "mamba" | "attention" | "mlp": one block per layer
         if self.model_type == "bamba":
@@ -474,6 +484,7 @@ _ARCH_NAME = {
     "llama4_text": "Llama4ForCausalLM",
     "bamba": "BambaForCausalLM",
     "nemotron_h": "NemotronHForCausalLM",
+    "qwen3_next": "Qwen3NextForCausalLM",
 }
 
 

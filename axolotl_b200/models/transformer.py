@@ -52,6 +52,10 @@ class Attention(nn.Module):
                                   dtype=dtype, device=device)
         # gpt-oss: one learned "sink" logit per head in every softmax denominator
         self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if cfg.model_type == "gpt_oss" else None
+        # Qwen3-Next: the attention output is multiplied by sigmoid(gate(x)) before the output projection (the checkpoint
+        # stores the gate rows inside q_proj, head by head; they are split off at load)
+        self.out_gate = FusedLinear(H, [self.Hq * self.D], ["q_gate"], bias=cfg.attention_bias, dtype=dtype, device=device) \
+            if cfg.model_type == "qwen3_next" else None
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
@@ -86,6 +90,14 @@ class Attention(nn.Module):
             q, _ = self.q_norm(qkv[..., :nq].contiguous())
             k, _ = self.k_norm(qkv[..., nq:nq + nk].contiguous())
             qkv = torch.cat([q, k, qkv[..., nq + nk:]], -1)
+        if self.use_rope and per_head_norm and self.rot_dim is not None:
+            # partial rotary embedding with q/k norms: the norms run on their own, then the first rot_dim dimensions rotate
+            T = qkv.shape[0]
+            nq, nk = self.Hq * self.D, self.Hk * self.D
+            q = self.q_norm.plain(qkv[:, :nq].reshape(T * self.Hq, self.D)).reshape(T, nq)
+            k = self.k_norm.plain(qkv[:, nq:nq + nk].reshape(T * self.Hk, self.D)).reshape(T, nk)
+            qkv = torch.cat([q, k, qkv[:, nq + nk:]], 1)
+            return Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale, rot_dim=self.rot_dim)
         if self.use_rope:
             if self.local_inv_freq is not None:
                 inv_freq, attn_scale = self.local_inv_freq, 1.0
@@ -117,7 +129,10 @@ class Attention(nn.Module):
         return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale, softcap=self.softcap, sinks=self.sinks)
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
-        return self.o_proj(self.core(self.pre(x, positions, inv_freq, attn_scale), meta))
+        a = self.core(self.pre(x, positions, inv_freq, attn_scale), meta)
+        if self.out_gate is not None:
+            a = (a.float() * torch.sigmoid(self.out_gate(x).float())).to(a.dtype)
+        return self.o_proj(a)
 
 
 class MLP(nn.Module):
@@ -218,6 +233,10 @@ class DecoderLayer(nn.Module):
             from .mamba import Mamba2Mixer
 
             self.self_attn = Mamba2Mixer(cfg, dtype, device)     # (kept under the same attribute: the layer's token mixer)
+        elif cfg.layer_kind(idx) == "deltanet":
+            from .deltanet import GatedDeltaNet
+
+            self.self_attn = GatedDeltaNet(cfg, dtype, device)
         else:
             self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
@@ -282,7 +301,9 @@ class DecoderLayer(nn.Module):
         one part whose recomputation costs more than its activations), everything around it — norms,
         projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
         ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
-        if not hasattr(self.self_attn, "core"):      # state-space mixers have no attention result to keep
+        if not hasattr(self.self_attn, "core") or getattr(self.self_attn, "out_gate", None) is not None:
+            # state-space / linear-attention mixers have no attention result to keep (and a gated attention output
+            # needs the layer input again)
             return checkpoint(self.forward, h, residual, positions, inv_freq, attn_scale, meta, use_reentrant=False)
         qkv, residual = checkpoint(self._before_attention, h, residual, positions, inv_freq, attn_scale, use_reentrant=False)
         a = self.self_attn.core(qkv, meta)
@@ -415,6 +436,11 @@ class CausalLM(nn.Module):
                 m.weight.fill_(1.0 - m.offset)
             if isinstance(m, Attention) and m.sinks is not None:
                 m.sinks.normal_(0.0, std, generator=gen)
+            if type(m).__name__ == "GatedDeltaNet":
+                m.A_log.uniform_(0.0, 2.5, generator=gen)
+                m.conv_weight.normal_(0.0, 0.2, generator=gen)
+                m.dt_bias.fill_(1.0)
+                m.norm_weight.fill_(1.0)
             if type(m).__name__ == "Mamba2Mixer":
                 m.A_log.copy_(torch.log(torch.arange(1, m.nh + 1, dtype=torch.float32, device=m.A_log.device)).to(m.A_log.dtype))
                 m.conv_weight.normal_(0.0, 0.2, generator=gen)
@@ -582,7 +608,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h"))
+                                                             "nemotron_h", "qwen3_next"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

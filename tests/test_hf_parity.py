@@ -687,3 +687,41 @@ def test_nemotron_h_single_block_layers_match_hf(tmp_path):
     hf_io.load_state_into(m3, sd.items())
     with torch.no_grad():
         assert torch.allclose(m3(ids, pos, return_logits=True).logits, m2(ids, pos, return_logits=True).logits, atol=1e-5)
+
+
+def test_qwen3_next_gated_deltanet_and_gated_attention_match_hf(tmp_path):
+    """Qwen3-Next: Gated DeltaNet layers (chunked gated delta rule, norm-then-gate output norm), every fourth layer
+    full attention with an output gate, zero-centred norms, a quarter of each head rotating, routed experts with a
+    sigmoid-gated shared expert."""
+    d = dict(model_type="qwen3_next", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2,
+             linear_key_head_dim=8, linear_value_head_dim=12, linear_conv_kernel_dim=4, full_attention_interval=4,
+             partial_rotary_factor=0.25, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+             shared_expert_intermediate_size=48, decoder_sparse_step=1, norm_topk_prob=True, mlp_only_layers=[],
+             rms_norm_eps=1e-6, rope_theta=10000.0, hidden_act="silu", tie_word_embeddings=False,
+             max_position_embeddings=256, attention_bias=False, router_aux_loss_coef=0.0)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(41)
+    assert [type(l.self_attn).__name__ for l in ours.layers] == ["GatedDeltaNet"] * 3 + ["Attention"]
+    _randomize_norms(ours, -0.2, 0.2)
+    with torch.no_grad():
+        for l in ours.layers[:3]:
+            l.self_attn.norm_weight.uniform_(0.5, 1.5)
+            l.self_attn.dt_bias.uniform_(-1.0, 1.0)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [70, 25]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    ours.train()
+    ours(ids, pos, ids.clone()).loss.backward()
+    assert ours.layers[0].self_attn.A_log.grad is not None and ours.layers[3].self_attn.out_gate.weight.grad.abs().sum() > 0

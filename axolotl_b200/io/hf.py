@@ -43,7 +43,8 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     expert_parts = {}
     mxfp4_parts = {}
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
-    bamba = getattr(model.config, "model_type", "") == "bamba"
+    bamba = getattr(model.config, "model_type", "") in ("bamba", "falcon_h1")       # the same names outside the mixers
+    mamba_attr = ".mamba" if getattr(model.config, "model_type", "") == "falcon_h1" else ".self_attn"
     qwen3_next = getattr(model.config, "model_type", "") == "qwen3_next"
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
@@ -107,7 +108,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+)\.mamba\.(.+)$", name)):
             # Granite 4.0-H state-space mixer (kept under `self_attn` in our layer)
-            mx, leaf = mods[m.group(1) + ".self_attn"], m.group(2)
+            mx, leaf = mods[m.group(1) + mamba_attr], m.group(2)
             if leaf in ("in_proj.weight", "out_proj.weight", "in_proj.bias", "out_proj.bias"):
                 getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
             elif leaf == "conv1d.weight":
@@ -346,11 +347,13 @@ def _mamba_tensors(pre, mx, sd):
     sd[f"{pre}.mamba.out_proj.weight"] = mx.out_proj.weight.detach()
     if mx.in_proj.bias is not None:
         sd[f"{pre}.mamba.in_proj.bias"] = mx.in_proj.bias.detach()
+    if mx.out_proj.bias is not None:
         sd[f"{pre}.mamba.out_proj.bias"] = mx.out_proj.bias.detach()
     sd[f"{pre}.mamba.conv1d.weight"] = mx.conv_weight.detach()[:, None, :]
     if mx.conv_bias is not None:
         sd[f"{pre}.mamba.conv1d.bias"] = mx.conv_bias.detach()
-    sd[f"{pre}.mamba.norm.weight"] = mx.norm_weight.detach()
+    if mx.norm_weight is not None:
+        sd[f"{pre}.mamba.norm.weight"] = mx.norm_weight.detach()
     for leaf in ("dt_bias", "A_log", "D"):
         sd[f"{pre}.mamba.{leaf}"] = getattr(mx, leaf).detach()
 
@@ -421,20 +424,22 @@ def _nemotron_h_load(model, named_tensors, strict=True):
 
 
 def _bamba_state_dict(model, sd):
-    """Bamba names: `mamba.*` mixers, `pre_ff_layernorm`, `feed_forward`, `final_layernorm`."""
+    """Bamba / Falcon-H1 names: `mamba.*` mixers, `pre_ff_layernorm`, `feed_forward`, `final_layernorm`."""
     sd["model.final_layernorm.weight"] = sd.pop("model.norm.weight")
     for i, layer in enumerate(model.layers):
         pre = f"model.layers.{i}"
         sd[f"{pre}.input_layernorm.weight"] = layer.input_layernorm.weight.detach()
         sd[f"{pre}.pre_ff_layernorm.weight"] = layer.post_attention_layernorm.weight.detach()
-        mx = layer.self_attn
-        if type(mx).__name__ == "Mamba2Mixer":
-            _mamba_tensors(pre, mx, sd)
-        else:
-            for fl in (mx.qkv_proj, mx.o_proj):
-                for sub in fl.names:
-                    r0, r1 = fl.row_range(sub)
-                    sd[f"{pre}.self_attn.{sub}.weight"] = fl.weight.detach()[r0:r1]
+        for mx in ([layer.mamba, layer.self_attn] if hasattr(layer, "mamba") else [layer.self_attn]):
+            if type(mx).__name__ == "Mamba2Mixer":
+                _mamba_tensors(pre, mx, sd)
+            else:
+                for fl in (mx.qkv_proj, mx.o_proj):
+                    for sub in fl.names:
+                        r0, r1 = fl.row_range(sub)
+                        sd[f"{pre}.self_attn.{sub}.weight"] = fl.weight.detach()[r0:r1]
+                        if fl.bias is not None:
+                            sd[f"{pre}.self_attn.{sub}.bias"] = fl.bias.detach()[r0:r1]
         for fl in (layer.mlp.gate_up_proj, layer.mlp.down_proj):
             for sub in fl.names:
                 r0, r1 = fl.row_range(sub)
@@ -508,7 +513,7 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
     if getattr(model.config, "model_type", "") == "granitemoehybrid":
         return _granite_hybrid_state_dict(model, sd)
-    if getattr(model.config, "model_type", "") == "bamba":
+    if getattr(model.config, "model_type", "") in ("bamba", "falcon_h1"):
         return _bamba_state_dict(model, sd)
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_state_dict(model)

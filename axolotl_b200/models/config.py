@@ -14,7 +14,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
 
@@ -244,6 +244,17 @@ class ModelConfig:
             if name == "attention_multiplier":
                 qpas = (self.extra or {}).get("query_pre_attn_scalar")
                 return float(qpas) ** -0.5 if qpas and self.model_type != "gemma" else 1.0 / math.sqrt(self.head_dim)
+            return 1.0
+        if self.model_type == "falcon_h1":
+            # maximal-update scalars: on the embeddings, on the keys (folded into the score scale: the rotary
+            # embedding is linear), on the logits (a division elsewhere, hence the reciprocal)
+            ex = self.extra or {}
+            if name == "embedding_multiplier":
+                return float(ex.get("embedding_multiplier") or 1.0)
+            if name == "attention_multiplier":
+                return float(ex.get("key_multiplier") or 1.0) / math.sqrt(self.head_dim)
+            if name == "logits_scaling":
+                return 1.0 / float(ex.get("lm_head_multiplier") or 1.0)
             return 1.0
         if self.model_type not in ("granite", "granitemoehybrid"):
             return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
@@ -484,6 +495,7 @@ _ARCH_NAME = {
     "llama4_text": "Llama4ForCausalLM",
     "bamba": "BambaForCausalLM",
     "nemotron_h": "NemotronHForCausalLM",
+    "falcon_h1": "FalconH1ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
 }
 

@@ -1,4 +1,4 @@
-"""Mamba-2 (state-space duality) mixer for the hybrid families (Granite 4.0-H `granitemoehybrid`): in_proj ->
+"""Mamba-2 (state-space duality) mixer for the hybrid families (Granite 4.0-H `granitemoehybrid`, Bamba, Nemotron-H, Falcon-H1): in_proj ->
 causal depthwise convolution -> selective state-space scan -> gated RMSNorm -> out_proj, on PACKED token streams:
 neither the convolution nor the recurrent state crosses a document boundary.
 
@@ -66,12 +66,26 @@ class Mamba2Mixer(nn.Module):
             self.nh, self.P = int(ex["mamba_n_heads"]), int(ex["mamba_d_head"])
             self.G, self.N = int(ex.get("mamba_n_groups", 1)), int(ex["mamba_d_state"])
             self.k = int(ex.get("mamba_d_conv", 4))
-            self.d_inner = int(ex.get("mamba_expand", 2) * H)
+            self.d_inner = int(ex["mamba_d_ssm"]) if ex.get("mamba_d_ssm") else int(ex.get("mamba_expand", 2) * H)
             if self.d_inner != self.nh * self.P:
                 raise ValueError(f"mamba_expand * hidden ({self.d_inner}) must equal mamba_n_heads * mamba_d_head ({self.nh * self.P})")
             self.chunk = int(ex.get("mamba_chunk_size", 256))
             self.norm_groups = 1
             bias, conv_bias = bool(ex.get("mamba_proj_bias", False)), bool(ex.get("mamba_conv_bias", True))
+        # Falcon-H1: scalar on the mixer input, one multiplier per section of the in_proj output (z | x | B | C | dt),
+        # the gated norm is optional, grouped, and may run before the gate; out_proj has its own bias switch
+        self.in_multiplier, self.has_norm, self.norm_before_gate, out_bias = 1.0, True, False, bias
+        mup = None
+        if cfg.model_type == "falcon_h1":
+            self.in_multiplier = float(ex.get("ssm_in_multiplier") or 1.0)
+            self.has_norm = bool(ex.get("mamba_rms_norm", False))
+            self.norm_before_gate = bool(ex.get("mamba_norm_before_gate", True))
+            self.norm_groups = self.G
+            out_bias = bool(ex.get("projectors_bias", False))
+            zm = [float(v) for v in (ex.get("ssm_multipliers") or [1.0] * 5)]
+            gn = self.G * self.N
+            mup = torch.cat([torch.full((n,), v) for n, v in zip((self.d_inner, self.d_inner, gn, gn, self.nh), zm)])
+        self.register_buffer("mup_vector", mup.to(device) if (mup is not None and device is not None) else mup, persistent=False)
         self.conv_dim = self.d_inner + 2 * self.G * self.N
         lim = ex.get("time_step_limit") or (0.0, float("inf"))
         self.dt_limit = (float(lim[0]), float(lim[1]))
@@ -82,8 +96,8 @@ class Mamba2Mixer(nn.Module):
         self.dt_bias = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
         self.A_log = nn.Parameter(torch.log(torch.arange(1, self.nh + 1, dtype=torch.float32, device=device)).to(dtype))
         self.D = nn.Parameter(torch.ones(self.nh, dtype=dtype, device=device))
-        self.norm_weight = nn.Parameter(torch.ones(self.d_inner, dtype=dtype, device=device))
-        self.out_proj = FusedLinear(self.d_inner, [H], ["out_proj"], bias=bias, dtype=dtype, device=device)
+        self.norm_weight = nn.Parameter(torch.ones(self.d_inner, dtype=dtype, device=device)) if self.has_norm else None
+        self.out_proj = FusedLinear(self.d_inner, [H], ["out_proj"], bias=out_bias, dtype=dtype, device=device)
         self.window, self.use_rope = 0, False
 
     def _conv(self, x, positions):
@@ -102,7 +116,9 @@ class Mamba2Mixer(nn.Module):
         if getattr(meta, "kv_cache", None) is not None:
             raise NotImplementedError("cached decoding is not available for state-space layers; generate(use_cache=False)")
         T = x.shape[0]
-        zxbcdt = self.in_proj(x)
+        zxbcdt = self.in_proj(x * self.in_multiplier if self.in_multiplier != 1.0 else x)
+        if self.mup_vector is not None:
+            zxbcdt = zxbcdt * self.mup_vector.to(zxbcdt.dtype)
         z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.conv_dim, self.nh], dim=-1)
         xBC = self._conv(xBC, positions)
         xs, B, C = torch.split(xBC, [self.d_inner, self.G * self.N, self.G * self.N], dim=-1)
@@ -116,11 +132,16 @@ class Mamba2Mixer(nn.Module):
         cu = [int(v) for v in meta.cu_seqlens_host]
         ys = [ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s]
         y = torch.cat(ys, 0) + self.D.float()[None, :, None] * xs
-        y = y.reshape(T, self.d_inner) * F.silu(z.float())                       # gate first, then the norm
-        if self.norm_groups > 1:                                                 # one RMS per group of channels
-            yg = y.view(T, self.norm_groups, -1)
-            y = (yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + self.eps)).reshape(T, self.d_inner)
-        else:
-            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
-        y = (self.norm_weight.float() * y).to(x.dtype)
-        return self.out_proj(y)
+        y = y.reshape(T, self.d_inner)
+        if not (self.has_norm and self.norm_before_gate):
+            y = y * F.silu(z.float())                                            # gate first, then the norm
+        if self.has_norm:
+            if self.norm_groups > 1:                                             # one RMS per group of channels
+                yg = y.view(T, self.norm_groups, -1)
+                y = (yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + self.eps)).reshape(T, self.d_inner)
+            else:
+                y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
+            y = self.norm_weight.float() * y
+            if self.norm_before_gate:
+                y = y * F.silu(z.float())
+        return self.out_proj(y.to(x.dtype))

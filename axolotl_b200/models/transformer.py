@@ -147,8 +147,14 @@ class MLP(nn.Module):
         self.act = act
         self.glu_limit = None   # clamped SwiGLU (config key ``swiglu_limit``)
         self.tile_rows = None   # tiled MLP: rows per tile (None = whole sequence at once)
+        self.gate_multiplier, self.down_multiplier = 1.0, 1.0   # Falcon-H1: scalars on the gate half and on the output
 
     def _mlp(self, x):
+        if self.gate_multiplier != 1.0 or self.down_multiplier != 1.0:
+            gu = self.gate_up_proj(x)
+            inter = gu.shape[-1] // 2
+            gu = torch.cat([gu[..., :inter] * self.gate_multiplier, gu[..., inter:]], -1)
+            return self.down_proj(Fn.glu(gu, self.act, self.glu_limit)) * self.down_multiplier
         if x.is_cuda:   # one autograd node with the GLU folded into the GEMM epilogues, when it applies
             y = glu_mlp(x, self.gate_up_proj, self.down_proj, Fn._ACT_KIND[self.act], self.glu_limit, adapters_enabled())
             if y is not None:
@@ -218,6 +224,39 @@ class SingleBlockLayer(nn.Module):
         if self.kind == "mlp":
             return self.mixer(x), residual, None
         return self.mixer(x, positions, inv_freq, attn_scale, meta), residual, None
+
+
+class ParallelHybridLayer(nn.Module):
+    """Falcon-H1: a state-space mixer and an attention block read the SAME normalised input side by side, their
+    outputs (each with its own scalar multiplier) are summed into the residual stream, then a gated MLP follows."""
+
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
+        super().__init__()
+        from .mamba import Mamba2Mixer
+
+        ex = cfg.extra or {}
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.mamba = Mamba2Mixer(cfg, dtype, device)
+        self.self_attn = Attention(cfg, dtype, device)
+        self.self_attn.layer_idx = idx
+        self.self_attn.window = 0
+        self.attention_in_multiplier = float(ex.get("attention_in_multiplier") or 1.0)
+        self.attention_out_multiplier = float(ex.get("attention_out_multiplier") or 1.0)
+        self.ssm_out_multiplier = float(ex.get("ssm_out_multiplier") or 1.0)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
+        gm, dm = ex.get("mlp_multipliers") or (1.0, 1.0)
+        self.mlp.gate_multiplier, self.mlp.down_multiplier = float(gm), float(dm)
+        self.is_moe = False
+
+    def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
+        x, residual = self.input_layernorm(h, residual)
+        m = self.mamba(x, positions, inv_freq, attn_scale, meta)
+        xa = x * self.attention_in_multiplier if self.attention_in_multiplier != 1.0 else x
+        a = self.self_attn(xa, positions, inv_freq, attn_scale, meta)
+        mixed = m * self.ssm_out_multiplier + a * self.attention_out_multiplier
+        x, residual = self.post_attention_layernorm(mixed, residual)
+        return self.mlp(x), residual, None
 
 
 class DecoderLayer(nn.Module):
@@ -320,7 +359,7 @@ class CausalLM(nn.Module):
         self.config = cfg
         self.dtype = dtype
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
-        layer_cls = SingleBlockLayer if cfg.model_type == "nemotron_h" else DecoderLayer
+        layer_cls = {"nemotron_h": SingleBlockLayer, "falcon_h1": ParallelHybridLayer}.get(cfg.model_type, DecoderLayer)
         self.layers = nn.ModuleList([layer_cls(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=cfg.norm_offset())
         self.final_softcap = cfg.final_softcap()   # Gemma 2: logits -> cap * tanh(logits / cap)
@@ -608,7 +647,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next"))
+                                                             "nemotron_h", "qwen3_next", "falcon_h1"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -641,6 +641,47 @@ def test_bamba_hybrid_matches_hf(tmp_path):
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
 
 
+@pytest.mark.parametrize("norm_before_gate", [False, True])
+def test_falcon_h1_parallel_hybrid_matches_hf(tmp_path, norm_before_gate):
+    """Falcon-H1: Mamba-2 mixer and attention side by side in every layer, maximal-update multipliers everywhere."""
+    d = dict(model_type="falcon_h1", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, mamba_d_ssm=96, mamba_n_heads=8, mamba_d_head=12,
+             mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8, mamba_conv_bias=True,
+             mamba_proj_bias=False, mamba_rms_norm=True, mamba_norm_before_gate=norm_before_gate, rms_norm_eps=1e-5,
+             tie_word_embeddings=False, hidden_act="silu", max_position_embeddings=256, attention_bias=False, mlp_bias=False,
+             projectors_bias=False, pad_token_id=0, rope_parameters={"rope_type": "default", "rope_theta": 100000.0},
+             embedding_multiplier=1.7, lm_head_multiplier=0.6, key_multiplier=0.8, attention_in_multiplier=1.3,
+             attention_out_multiplier=0.9, ssm_in_multiplier=1.2, ssm_out_multiplier=0.7, mlp_multipliers=[0.8, 1.4],
+             ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3])
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(41)
+    assert type(ours.layers[0]).__name__ == "ParallelHybridLayer"
+    with torch.no_grad():
+        for l in ours.layers:
+            l.mamba.dt_bias.uniform_(-1.0, 1.0)
+            l.mamba.norm_weight.uniform_(0.5, 1.5)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [25, 20]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    # training path: the loss and gradients flow through both branches
+    ours.train()
+    out = ours(ids, pos, labels=ids)
+    out.loss.backward()
+    assert ours.layers[0].mamba.in_proj.weight.grad.abs().sum() > 0
+    assert ours.layers[0].self_attn.qkv_proj.weight.grad.abs().sum() > 0
+
+
 def test_nemotron_h_single_block_layers_match_hf(tmp_path):
     """Nemotron-H: every layer is norm -> one block -> residual; Mamba-2 mixers with a gated norm per channel group,
     position-free attention blocks, squared-ReLU MLP blocks."""

@@ -170,6 +170,12 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             else:
                 (ex.down_bias if m.group(3) else ex.down_proj).copy_(t if m.group(3) else t.transpose(1, 2))
             filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.self_attn\.indexer)\.(wq_b|wk|weights_proj)\.weight$", name)):
+            getattr(mods[m.group(1)], m.group(2)).weight.copy_(t)        # sparse-attention indexer (GLM-5)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+\.self_attn\.indexer)\.k_norm\.(weight|bias)$", name)):
+            getattr(mods[m.group(1)], "k_norm_" + m.group(2)).copy_(t)
+            filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.e_score_correction_bias$", name)):
             mods[m.group(1)].e_score_correction_bias.copy_(t)
             filled.add(name)
@@ -533,6 +539,9 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
             continue
         if getattr(m, "sinks", None) is not None:
             sd[f"model.{name}.sinks"] = m.sinks.detach()
+        if type(m).__name__ == "LightningIndexer":
+            sd[f"model.{name}.k_norm.weight"] = m.k_norm_weight.detach()
+            sd[f"model.{name}.k_norm.bias"] = m.k_norm_bias.detach()
         if isinstance(m, FusedLinear):
             parent = name.rsplit(".", 1)[0]
             for sub in m.names:

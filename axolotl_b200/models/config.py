@@ -14,8 +14,9 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
+MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
 
 
@@ -150,6 +151,19 @@ class ModelConfig:
             if not d.get("rope_scaling") and not d.get("rope_parameters"):     # the family's default: YaRN x32 over 4096
                 d["rope_scaling"] = {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
                                      "truncate": False, "original_max_position_embeddings": 4096}
+        if mt == "glm_moe_dsa":        # GLM-5: DeepSeek-V3 style latent attention + routing, plus the sparse-attention indexer
+            L = d.get("num_hidden_layers", 0)
+            for key, default in (("qk_nope_head_dim", 192), ("qk_rope_head_dim", 64), ("v_head_dim", 256), ("kv_lora_rank", 512),
+                                 ("q_lora_rank", 2048), ("n_shared_experts", 1), ("routed_scaling_factor", 2.5), ("n_group", 1),
+                                 ("topk_group", 1), ("index_topk", 2048), ("index_head_dim", 128), ("index_n_heads", 32)):
+                d.setdefault(key, default)
+            d["num_experts"] = d.get("n_routed_experts") or 0
+            d.setdefault("norm_topk_prob", True)
+            d["head_dim"] = d["qk_nope_head_dim"] + d["qk_rope_head_dim"]
+            types = d.get("mlp_layer_types") or (["dense"] * min(3, L) + ["sparse"] * max(L - 3, 0))
+            d["mlp_layer_types"] = list(types)
+            d["mlp_only_layers"] = [i for i, t in enumerate(types) if t != "sparse"]
+            d["rope_interleave"] = False                        # split-half rotation
         if mt in ("deepseek_v2", "deepseek_v3"):
             d["num_experts"] = d.get("n_routed_experts") or 0
             d.setdefault("norm_topk_prob", mt == "deepseek_v3")
@@ -212,7 +226,9 @@ class ModelConfig:
         if self.model_type == "granitemoehybrid":
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size") or extra.get("intermediate_size") or d.get("intermediate_size")
-        if self.model_type in ("deepseek_v2", "deepseek_v3"):
+        if self.model_type == "glm_moe_dsa":
+            extra.pop("rope_interleave", None)
+        if self.model_type in MLA_TYPES:
             d["n_routed_experts"] = d.pop("num_experts")
             d.pop("head_dim", None)
             d.pop("mlp_only_layers", None)
@@ -359,7 +375,7 @@ class ModelConfig:
 
     def rope_dim(self) -> int:
         """Width of the rotated part of a head (DeepSeek latent attention rotates only its shared 64-wide part)."""
-        if self.model_type in ("deepseek_v2", "deepseek_v3"):
+        if self.model_type in MLA_TYPES:
             return int((self.extra or {}).get("qk_rope_head_dim") or 64)
         ex = self.extra or {}
         f = ex.get("partial_rotary_factor") or (ex.get("rope_parameters") or {}).get("partial_rotary_factor") \
@@ -496,6 +512,7 @@ _ARCH_NAME = {
     "bamba": "BambaForCausalLM",
     "nemotron_h": "NemotronHForCausalLM",
     "falcon_h1": "FalconH1ForCausalLM",
+    "glm_moe_dsa": "GlmMoeDsaForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
 }
 

@@ -94,6 +94,9 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         if getattr(meta, "kv_cache", None) is not None:
             raise NotImplementedError("cached decoding is not available for linear-attention layers; generate(use_cache=False)")
+        if getattr(meta, "cp", False):
+            raise NotImplementedError("context parallelism is not available for Gated DeltaNet layers (a chunk's transition is a full "
+                                      "d_k x d_k matrix per head rather than a scalar decay; that hand-over is not built)")
         T = x.shape[0]
         r = self.nv // self.nk
         # the projection is laid out per key head: [q | k | v (r value heads) | z (r value heads)]

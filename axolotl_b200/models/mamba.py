@@ -7,12 +7,20 @@ output is a masked, decay-weighted (C B^T) product; between chunks one [heads, P
 short recurrence. Autograd differentiates the contractions. On a GPU these run as library batched GEMMs; a fused
 tcgen05 scan kernel is not part of this package yet.
 
-The reference trains these models through HF's modelling code and the mamba-ssm / causal-conv1d kernels
-(src/axolotl/monkeypatch/models/mamba_utils.py:53-187 adds context parallelism for them, which is not built here).
+Context parallelism: every rank scans its contiguous chunk of the row from a zero state; the scan is linear in its
+initial state, so the state that arrives from the earlier chunks of the same document is added afterwards
+(``exp(cumulative decay) * C . H_in``). Every rank all-gathers (final state of its last document segment, total decay
+of its chunk) once per layer and folds the chain of earlier ranks locally, so a document that spans ANY number of
+chunks is exact; the convolution reads the last ``k - 1`` pre-convolution rows of the previous rank. Both exchanges
+are differentiable (all-reduce of the gathered gradient).
+
+The reference trains these models through HF's modelling code and the mamba-ssm / causal-conv1d kernels and passes
+the state one hop along the ring (src/axolotl/monkeypatch/models/mamba_utils.py:53-187).
 """
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
@@ -47,6 +55,35 @@ def ssd_chunked(xd, a, B, C, chunk=128):
             R = chunk_decay[c][:, None, None] * R + S[c]
         y = y + torch.einsum("cihn,chpn,cih->cihp", C, torch.stack(carried), torch.exp(cum))
     return y.reshape(nc * Q, h, P)[:L]
+
+
+class _AllGatherStack(torch.autograd.Function):
+    """[...] on every rank -> [world, ...]; the gradient of a rank's slice is the sum of what all ranks send back."""
+
+    @staticmethod
+    def forward(ctx, t, group, world, rank):
+        ctx.group, ctx.rank = group, rank
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous(), group=group)
+        return torch.stack(parts, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g[ctx.rank], None, None, None
+
+
+def cp_segments(cu, c0, c1):
+    """Document pieces inside the chunk [c0, c1) as chunk-relative (lo, hi), and whether the first piece continues a
+    document that started on an earlier rank."""
+    segs = []
+    for s, e in zip(cu[:-1], cu[1:]):
+        lo, hi = max(int(s), c0), min(int(e), c1)
+        if lo < hi:
+            segs.append((lo - c0, hi - c0))
+    starts = {int(v) for v in cu}
+    return segs, (c0 > 0 and c0 not in starts)
 
 
 class Mamba2Mixer(nn.Module):
@@ -100,17 +137,43 @@ class Mamba2Mixer(nn.Module):
         self.out_proj = FusedLinear(self.d_inner, [H], ["out_proj"], bias=out_bias, dtype=dtype, device=device)
         self.window, self.use_rope = 0, False
 
-    def _conv(self, x, positions):
-        """Causal depthwise convolution over the token axis that reads zeros before the start of a document."""
+    def _conv(self, x, positions, halo=None):
+        """Causal depthwise convolution over the token axis that reads zeros before the start of a document; ``halo``
+        holds the k - 1 rows that precede x (context parallelism: the previous rank's last rows)."""
         w = self.conv_weight.float()
         out = x.float() * w[:, self.k - 1]
         pos = positions.to(x.device)
+        T = x.shape[0]
+        xp = F.pad(x.float(), (0, 0, self.k - 1, 0)) if halo is None else torch.cat([halo.float(), x.float()], 0)
         for j in range(1, self.k):
-            shifted = F.pad(x.float(), (0, 0, j, 0))[: x.shape[0]]
+            shifted = xp[self.k - 1 - j: self.k - 1 - j + T]
             out = out + shifted * w[:, self.k - 1 - j] * (pos >= j)[:, None]
         if self.conv_bias is not None:
             out = out + self.conv_bias.float()
         return F.silu(out)
+
+    def _scan_cp(self, xd, a, B, C, cu, meta):
+        """The scan of this rank's chunk with the state that earlier chunks of the same document hand over."""
+        segs, continues = cp_segments(cu, meta.c0, meta.c1)
+        ys = [ssd_chunked(xd[lo:hi], a[lo:hi], B[lo:hi], C[lo:hi], self.chunk) for lo, hi in segs]
+        lo, hi = segs[-1]
+        cum_last = a[lo:hi].cumsum(0)                                            # [L, h]
+        S = torch.einsum("lhn,lh,lhp->hpn", B[lo:hi], torch.exp(cum_last[-1:] - cum_last), xd[lo:hi])
+        # the incoming state passes THROUGH this chunk only when the chunk is one piece of one document
+        through = torch.exp(cum_last[-1]) if (len(segs) == 1 and continues) else torch.zeros_like(cum_last[-1])
+        packed = torch.cat([S.reshape(-1), through])
+        allr = _AllGatherStack.apply(packed, meta.ctx.group, meta.world, meta.rank)     # [world, h*P*N + h]
+        if not continues:        # (zero-weight use: the backward pass of every rank must reach the collective)
+            ys[0] = ys[0] + allr.sum() * 0.0
+            return torch.cat(ys, 0)
+        n_state = S.numel()
+        H_in = torch.zeros_like(S)
+        for j in range(meta.rank):                                              # fold the chain of earlier ranks
+            H_in = allr[j, :n_state].view_as(S) + allr[j, n_state:][:, None, None] * H_in
+        lo, hi = segs[0]
+        cum = a[lo:hi].cumsum(0)
+        ys[0] = ys[0] + torch.exp(cum)[..., None] * torch.einsum("lhn,hpn->lhp", C[lo:hi], H_in)
+        return torch.cat(ys, 0)
 
     def forward(self, x, positions, inv_freq, attn_scale, meta):
         if getattr(meta, "kv_cache", None) is not None:
@@ -120,7 +183,13 @@ class Mamba2Mixer(nn.Module):
         if self.mup_vector is not None:
             zxbcdt = zxbcdt * self.mup_vector.to(zxbcdt.dtype)
         z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.conv_dim, self.nh], dim=-1)
-        xBC = self._conv(xBC, positions)
+        cp = getattr(meta, "cp", False)
+        halo = None
+        if cp:      # the convolution's look-back across the chunk border
+            tails = _AllGatherStack.apply(xBC[T - (self.k - 1):], meta.ctx.group, meta.world, meta.rank)
+            # (rank 0 keeps a zero-weight use of the gathered rows: every rank's backward pass must reach the collective)
+            halo = tails[meta.rank - 1] if meta.rank > 0 else tails[0] * 0.0
+        xBC = self._conv(xBC, positions, halo)
         xs, B, C = torch.split(xBC, [self.d_inner, self.G * self.N, self.G * self.N], dim=-1)
         dt = F.softplus(dt.float() + self.dt_bias.float()).clamp(self.dt_limit[0], self.dt_limit[1])
         A = -torch.exp(self.A_log.float())
@@ -130,8 +199,11 @@ class Mamba2Mixer(nn.Module):
         C = C.view(T, self.G, self.N).repeat_interleave(rep, dim=1)
         xd, a = xs * dt[..., None], A[None] * dt
         cu = [int(v) for v in meta.cu_seqlens_host]
-        ys = [ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s]
-        y = torch.cat(ys, 0) + self.D.float()[None, :, None] * xs
+        if cp:
+            y = self._scan_cp(xd, a, B, C, cu, meta)
+        else:
+            y = torch.cat([ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s], 0)
+        y = y + self.D.float()[None, :, None] * xs
         y = y.reshape(T, self.d_inner)
         if not (self.has_norm and self.norm_before_gate):
             y = y * F.silu(z.float())                                            # gate first, then the norm

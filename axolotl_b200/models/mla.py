@@ -1,4 +1,4 @@
-"""Multi-head latent attention (DeepSeek-V2 / V3): queries and keys/values are produced through low-rank
+"""Multi-head latent attention (DeepSeek-V2 / V3, GLM-5): queries and keys/values are produced through low-rank
 bottlenecks with their own RMSNorms, every head has a 128-wide content part and shares one 64-wide rotary
 part, values are 128 wide. The training graph expands k / v per head and runs the wide-head varlen attention
 kernels (q/k width 192, v width 128, ``csrc/flash_wide.cu``).
@@ -59,11 +59,11 @@ class MLAttention(nn.Module):
         """[..., d_rope] with interleaved pairs -> half-split layout the rotary kernel works on."""
         return t.index_select(-1, self.pe_perm) if self.interleave else t
 
-    def pre(self, x, positions, inv_freq, attn_scale):
+    def pre(self, x, positions, inv_freq, attn_scale, q_resid=None):
         T = x.shape[0]
         Hq, dn, dr, Dv = self.Hq, self.d_nope, self.d_rope, self.Dv
         if self.q_lora_rank:
-            q = self.q_b_proj(self.q_a_layernorm.plain(self.q_a_proj(x)))
+            q = self.q_b_proj(self.q_a_layernorm.plain(self.q_a_proj(x)) if q_resid is None else q_resid)
         else:
             q = self.q_proj(x)
         q = q.view(T, Hq, dn + dr)

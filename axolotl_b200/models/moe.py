@@ -230,11 +230,11 @@ class SparseMoE(nn.Module):
             self.shared_experts = self._llama4_shared
             del self._llama4_shared
         self.e_score_correction_bias = None
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa"):
             from .transformer import MLP
 
             ex = cfg.extra or {}
-            v3 = cfg.model_type == "deepseek_v3"
+            v3 = cfg.model_type != "deepseek_v2"
             grouped = v3 or ex.get("topk_method") == "group_limited_greedy"
             self.deepseek = dict(scoring="sigmoid" if v3 else (ex.get("scoring_func") or "softmax"),
                                  n_group=int(ex.get("n_group") or 1) if grouped else 1,

@@ -264,7 +264,11 @@ class DecoderLayer(nn.Module):
         super().__init__()
         off = cfg.norm_offset()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3"):
+        if cfg.model_type == "glm_moe_dsa":
+            from .dsa import SparseMLAttention
+
+            self.self_attn = SparseMLAttention(cfg, dtype, device)
+        elif cfg.model_type in ("deepseek_v2", "deepseek_v3"):
             from .mla import MLAttention
 
             self.self_attn = MLAttention(cfg, dtype, device)
@@ -340,7 +344,8 @@ class DecoderLayer(nn.Module):
         one part whose recomputation costs more than its activations), everything around it — norms,
         projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
         ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
-        if not hasattr(self.self_attn, "core") or getattr(self.self_attn, "out_gate", None) is not None:
+        if (not hasattr(self.self_attn, "core") or getattr(self.self_attn, "out_gate", None) is not None
+                or getattr(self.self_attn, "indexer", None) is not None):
             # state-space / linear-attention mixers have no attention result to keep (and a gated attention output
             # needs the layer input again)
             return checkpoint(self.forward, h, residual, positions, inv_freq, attn_scale, meta, use_reentrant=False)
@@ -647,7 +652,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "falcon_h1"))
+                                                             "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -53,6 +53,7 @@ _CUDA_SIGS = {
     "axb_moe_gemv": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "axb_rope_partial": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp],
     "axb_ebft_rewards": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "axb_indexer_scores": [vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, vp, vp],
     "axb_bounds_check_enabled": [],
     "axb_bounds_fetch": [vp],
     "axb_bounds_reset": [],

@@ -321,6 +321,60 @@ def check_context_parallel(dev, rank, world):
     dist.barrier()
 
 
+def check_cp_state_space(dev, rank, world):
+    """A Mamba-2 mixer under context parallelism (state handed from chunk to chunk, convolution halo) must reproduce
+    the mixer run on the whole row: outputs, input gradients and parameter gradients. Documents span several chunks,
+    end inside a chunk and start exactly on a chunk border."""
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.mamba import Mamba2Mixer
+    from axolotl_b200.ops.functional import AttnMeta
+    from axolotl_b200.parallel.runtime import create_runtime
+
+    cfg = ModelConfig.from_hf_dict(dict(
+        model_type="bamba", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, attn_layer_indices=[1],
+        num_attention_heads=4, num_key_value_heads=2, mamba_n_heads=8, mamba_d_head="auto", mamba_n_groups=2, mamba_d_state=16,
+        mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=16, mamba_conv_bias=True, mamba_proj_bias=False, rms_norm_eps=1e-5))
+    chunk = 128
+    S = chunk * world
+    par = create_runtime(device=dev, cp=world)
+    par.setup_cp()
+    for lens in ([S], [chunk + 37, S - chunk - 37], [chunk, S - chunk], [50, chunk * (world - 1) + 20, S - 70 - chunk * (world - 1)]):
+        lens = [l for l in lens if l > 0]
+        cu = [0]
+        for l in lens:
+            cu.append(cu[-1] + l)
+        torch.manual_seed(3)
+        mixer = Mamba2Mixer(cfg, torch.float32, dev)
+        with torch.no_grad():
+            for prm in mixer.parameters():
+                if prm.dim() > 1:
+                    prm.normal_(0, 0.2)
+            mixer.dt_bias.uniform_(-1, 1)
+        x = torch.randn(S, 64, device=dev)
+        gy = torch.randn(S, 64, device=dev)
+        pos = torch.cat([torch.arange(l) for l in lens]).to(dev)
+        xr = x.clone().requires_grad_(True)
+        yr = mixer(xr, pos, None, 1.0, AttnMeta(cu, dev))
+        yr.backward(gy)
+        ref_grads = {n: prm.grad.clone() for n, prm in mixer.named_parameters()}
+        ref_gx = xr.grad.clone()
+        mixer.zero_grad()
+        sl = slice(rank * chunk, (rank + 1) * chunk)
+        xc = x[sl].clone().requires_grad_(True)
+        yc = mixer(xc, pos[sl], None, 1.0, par.cp.make_meta(cu, S))
+        yc.backward(gy[sl])
+        tol = 1e-4 if dev.type == "cpu" else 2e-3
+        assert rel_err(yc, yr[sl]) < tol, ("output", lens, rel_err(yc, yr[sl]))
+        assert rel_err(xc.grad, ref_gx[sl]) < tol, ("input gradient", lens, rel_err(xc.grad, ref_gx[sl]))
+        for n, prm in mixer.named_parameters():
+            g = prm.grad.clone()
+            dist.all_reduce(g)
+            assert rel_err(g, ref_grads[n]) < tol, (n, lens, rel_err(g, ref_grads[n]))
+    if rank == 0:
+        print("context parallel state-space ok")
+    dist.barrier()
+
+
 def check_tp_cp(dev, rank, world):
     """TP=2 x CP=world/2 on one packed row: every rank must end with the same replicated adapter
     factors (the gradient of a replicated weight is summed over the tp AND the cp group) and the
@@ -506,6 +560,7 @@ def main():
         "tpcp" in only and check_tp_cp(dev, rank, world)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)
+        want("cpssm") and check_cp_state_space(dev, rank, world)
         want("ep") and check_expert_parallel(dev, rank, world)
     else:
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
@@ -521,6 +576,7 @@ def main():
         want("ddp") and check_training_equivalence(dev, rank, world, "fused", replicate=True)
         want("tp") and check_tensor_parallel(dev, rank, world)
         want("cp") and check_context_parallel(dev, rank, world)
+        want("cpssm") and check_cp_state_space(dev, rank, world)
         want("ep") and check_expert_parallel(dev, rank, world)
     dist.barrier()
     dist.destroy_process_group()

@@ -25,13 +25,14 @@ def test_data_parallel_gloo_world2():
     assert "dp training equivalence ok (collective, two groups)" in out
     assert "dp training equivalence ok (collective, full fine-tune)" in out
     assert "dp training equivalence ok (collective, replicated)" in out
-    for line in ("tensor parallel ok", "context parallel ok", "expert parallel ok"):
+    for line in ("tensor parallel ok", "context parallel ok", "context parallel state-space ok", "expert parallel ok"):
         assert line in out, out[-2000:]
 
 
 def test_tp_x_cp_gloo_world4():
-    out = _run(4, ["cpu", "tpcp"], 29613)
+    out = _run(4, ["cpu", "tpcp", "cpssm"], 29613)
     assert "tp x cp ok" in out
+    assert "context parallel state-space ok" in out      # a document that crosses three chunk borders
 
 
 @pytest.mark.gpu
@@ -46,5 +47,5 @@ def test_fused_multi_gpu():
                  "dp training equivalence ok (fused)", "dp training equivalence ok (fused, two groups)",
                  "dp training equivalence ok (fused, full fine-tune)",
                  "dp training equivalence ok (collective)", "dp training equivalence ok (fused, replicated)",
-                 "tensor parallel ok", "context parallel ok", "expert parallel ok"):
+                 "tensor parallel ok", "context parallel ok", "context parallel state-space ok", "expert parallel ok"):
         assert line in out, (line, out[-3000:])

@@ -481,6 +481,56 @@ def test_deepseek_latent_attention_and_grouped_routing_match_hf(tmp_path, model_
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
 
 
+def test_glm_dsa_sparse_latent_attention_matches_hf(tmp_path):
+    """GLM-5: latent attention whose queries see only the keys the lightning indexer ranks highest (here 12 of up to
+    40 causal keys, so the selection decides the result), split-half rotary part, V3-style routing, dense first layer."""
+    d = dict(model_type="glm_moe_dsa", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+             num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,
+             num_experts_per_tok=3, n_group=2, topk_group=1, mlp_layer_types=["dense", "sparse", "sparse"], q_lora_rank=24,
+             kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=12, routed_scaling_factor=2.5,
+             norm_topk_prob=True, rms_norm_eps=1e-5, hidden_act="silu", tie_word_embeddings=False,
+             max_position_embeddings=256, index_topk=12, index_head_dim=16, index_n_heads=4,
+             rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(43)
+    assert type(ours.layers[0].self_attn).__name__ == "SparseMLAttention"
+    with torch.no_grad():
+        for l in ours.layers:
+            if getattr(l.mlp, "e_score_correction_bias", None) is not None:
+                l.mlp.e_score_correction_bias.uniform_(-0.2, 0.2)
+            l.self_attn.indexer.k_norm_weight.uniform_(0.5, 1.5)
+            l.self_attn.indexer.k_norm_bias.uniform_(-0.3, 0.3)
+            for fl in (l.self_attn.indexer.wq_b, l.self_attn.indexer.wk, l.self_attn.indexer.weights_proj):
+                fl.weight.mul_(8.0)           # spread the scores: a near-tie could flip a selection between the two codes
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [9, 40, 31]                      # one document within the top-k budget, two beyond it
+    ids, pos = _packed_inputs(320, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    # the selection matters: with every key visible the logits differ
+    for l in ours.layers:
+        l.self_attn.indexer.topk = 1 << 20
+    with torch.no_grad():
+        dense = ours(ids, pos, return_logits=True).logits
+    assert (dense - got).abs().max() > 1e-3
+    for l in ours.layers:
+        l.self_attn.indexer.topk = 12
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    ours.train()
+    out = ours(ids, pos, labels=ids)
+    out.loss.backward()
+    assert ours.layers[1].self_attn.kv_b_proj.weight.grad.abs().sum() > 0
+    assert ours.layers[1].self_attn.indexer.wk.weight.grad is None       # the selection is a constant of the graph
+
+
 def test_gpt_oss_sinks_biased_experts_and_alternating_windows_match_hf(tmp_path):
     """Attention sinks, q/k/v/o biases, sliding window on alternate layers, router with bias choosing by logits,
     experts with biases and the clamped (up + 1) * g * sigmoid(1.702 g) activation, interleaved gate/up storage."""

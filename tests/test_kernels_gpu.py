@@ -1166,3 +1166,68 @@ def test_moe_decode_gemv_matches_grouped_path(fp4, monkeypatch):
         y_grouped, _ = moe(x)
     _check_status()
     assert _rel_err(y_gemv, y_grouped) < 1.5e-2
+
+
+@pytest.mark.parametrize("H,L,off", [(32, 300, 0), (32, 1000, 0), (64, 515, 0), (128, 260, 0), (32, 200, 333)])
+def test_indexer_scores_kernel_matches_reference(H, L, off):
+    """Lightning-indexer scores (relu(q.k) mixed over heads inside the GEMM epilogue) against the fp32 einsum form; `off`
+    is the case of a block of queries that starts `off` positions into its document."""
+    from axolotl_b200.models import dsa
+
+    torch.manual_seed(H + L)
+    q = torch.randn(L, H, 128, device="cuda").bfloat16()
+    k = torch.randn(L + off, 128, device="cuda").bfloat16()
+    w = torch.randn(L, H, device="cuda") * 0.1
+    got = dsa.indexer_scores(q, k, w, causal_off=off)
+    ref = dsa.indexer_scores_ref(q, k, w, causal_off=off)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = ~torch.isinf(ref)
+    err = (got[fin] - ref[fin]).abs().max().item()
+    assert err < 2e-2 * ref[fin].abs().max().item(), err
+    # the selection that the scores feed: the two top-k sets agree but for near-ties
+    kk = min(64, L)
+    a, b = got.topk(kk, -1).indices, ref.topk(kk, -1).indices
+    rows = torch.arange(L, device="cuda")[:, None]
+    ma = torch.zeros(L, L + off, dtype=torch.bool, device="cuda")
+    ma[rows, a] = True
+    mb = torch.zeros_like(ma)
+    mb[rows, b] = True
+    vis = fin
+    assert ((ma ^ mb) & vis).float().sum().item() <= 0.01 * vis.float().sum().item()
+
+
+def test_glm_dsa_sparse_attention_model_on_gpu_matches_cpu_fp32():
+    """GLM-5 graph on the device: 256-wide latent-attention heads through the wide kernels for the document within the
+    top-k budget, indexer kernel + selected-key attention for the longer one, against fp32 on the CPU. Most of a
+    query's keys are selected (256 of at most 420), so a selection that differs on a near-tie moves the loss little."""
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.transformer import CausalLM
+    torch.manual_seed(52)
+    cfg = ModelConfig.from_hf_dict(dict(
+        model_type="glm_moe_dsa", vocab_size=2048, hidden_size=256, intermediate_size=512, moe_intermediate_size=128,
+        num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2, n_routed_experts=8, n_shared_experts=1,
+        num_experts_per_tok=2, n_group=1, topk_group=1, mlp_layer_types=["dense", "sparse"], q_lora_rank=64, kv_lora_rank=64,
+        qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256, routed_scaling_factor=2.0, norm_topk_prob=True,
+        rms_norm_eps=1e-5, hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=2048,
+        index_topk=256, index_head_dim=128, index_n_heads=32, rope_parameters={"rope_type": "default", "rope_theta": 10000.0}))
+    ref = CausalLM(cfg, dtype=torch.float32).init_weights(6)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    dev = CausalLM(cfg, dtype=torch.bfloat16, device=_dev())
+    dev.load_state_dict(ref.state_dict())
+    lens = [150, 420]
+    ids = torch.cat([torch.randint(3, cfg.vocab_size, (l,)) for l in lens])[None]
+    pos = torch.cat([torch.arange(l) for l in lens])[None].to(torch.int32)
+    labels = ids.clone()
+    out_d = dev(ids, pos, labels)
+    out_d.loss.backward()
+    _check_status()
+    out_c = ref(ids, pos, labels)
+    out_c.loss.backward()
+    assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item())
+    for pick in ("layers.0.self_attn.kv_b_proj.weight", "layers.1.self_attn.q_b_proj.weight", "embed_tokens"):
+        gd = dict(dev.named_parameters())[pick].grad.float().cpu()
+        gc = dict(ref.named_parameters())[pick].grad
+        assert _rel_err(gd, gc) < 1e-1, pick

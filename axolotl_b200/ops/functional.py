@@ -626,6 +626,55 @@ class _FlashWide(torch.autograd.Function):
 WIDE_HEADS = ((256, 256), (192, 128))
 
 
+_BLOCKED_WARNED = set()
+
+
+def _attn_block(qb, kk, vv, q0, k0, scale, causal, window, softcap):
+    """qb [B, Hk, rep, D] against kk [n, Hk, D] / vv [n, Hk, Dv]; q0 / k0: document positions of the first query / key."""
+    sc = torch.einsum("bgrd,ngd->grbn", qb, kk).float() * scale
+    if softcap:
+        sc = torch.tanh(sc / softcap) * softcap
+    if causal:
+        qi = (q0 + torch.arange(qb.shape[0], device=qb.device))[:, None]
+        ki = (k0 + torch.arange(kk.shape[0], device=qb.device))[None, :]
+        keep = ki <= qi
+        if window:
+            keep &= ki > qi - window
+        sc = sc.masked_fill(~keep, float("-inf"))
+    return torch.einsum("grbn,ngd->bgrd", sc.softmax(-1).to(vv.dtype), vv)
+
+
+def _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap, block=256):
+    """Head widths without a kernel of their own (e.g. 512): blocks of queries against their visible keys through
+    library batched GEMMs, each block recomputed in the backward pass, so memory stays O(block x length) per head.
+    Correct for every width; far from the tensor-core kernels in speed (said once per width on stderr)."""
+    if (D, Dv) not in _BLOCKED_WARNED:
+        _BLOCKED_WARNED.add((D, Dv))
+        import sys
+
+        print(f"[axolotl_b200] attention head widths (q/k {D}, v {Dv}): no tcgen05 kernel for this layout, "
+              f"running the blocked library path", file=sys.stderr)
+    from torch.utils.checkpoint import checkpoint
+
+    T = qkv.shape[0]
+    rep = Hq // Hk
+    q = qkv[:, : Hq * D].reshape(T, Hk, rep, D)
+    k = qkv[:, Hq * D: (Hq + Hk) * D].reshape(T, Hk, D)
+    v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, Dv)
+    causal, window = getattr(meta, "causal", True), int(getattr(meta, "window", 0) or 0)
+    cu = [int(c) for c in meta.cu_seqlens_host]
+    outs = []
+    need_grad = torch.is_grad_enabled() and qkv.requires_grad
+    for s, e in zip(cu[:-1], cu[1:]):
+        for b0 in range(s, e, block):
+            b1 = min(b0 + block, e)
+            k0 = max(s, b0 - window + 1) if (causal and window) else s
+            k1 = b1 if causal else e
+            args = (q[b0:b1], k[k0:k1], v[k0:k1], b0 - s, k0 - s, scale, causal, window, softcap)
+            outs.append(checkpoint(_attn_block, *args, use_reentrant=False) if need_grad else _attn_block(*args))
+    return torch.cat(outs, 0).reshape(T, Hq * Dv)
+
+
 def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.0, sinks=None):
     """Attention inside each document of a packed row: causal, or bidirectional when the
     metadata was built with ``causal=False`` (masked-diffusion and encoder-style objectives).
@@ -633,7 +682,7 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.
     ``qkv`` is the fused projection [T, Hq*D + Hk*D + Hk*Dv] (q heads, then k heads, then v heads; ``Dv``
     defaults to ``D``). Returns [T, Hq * Dv]. Head widths 64 / 128 run the double-buffered kernels;
     (D, Dv) = (256, 256) or (192, 128), and any ``softcap`` (scores become softcap * tanh(scores / softcap))
-    at those widths, run the wide kernels. ``sinks`` [Hq]: one learned logit per head joins every softmax
+    at those widths, run the wide kernels; every other width (e.g. 512) runs a blocked library path. ``sinks`` [Hq]: one learned logit per head joins every softmax
     denominator (gpt-oss); applied as a rescale of the kernel's output and log-sum-exp.
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
@@ -645,9 +694,11 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.
             raise NotImplementedError("context parallelism is not available for head widths above 128")
         return _FlashWide.apply(qkv, meta, Hq, Hk, D, Dv, scale, softcap)
     if qkv.is_cuda and (softcap or Dv != D or D not in (64, 128)):
-        raise NotImplementedError(
-            f"attention head widths (q/k {D}, v {Dv}) with softcap={softcap}: the CUDA kernels take 64, 128, "
-            f"(256, 256) and (192, 128); soft-capping needs one of the two wide layouts")
+        if getattr(meta, "cp", False) or sinks is not None:
+            raise NotImplementedError(
+                f"attention head widths (q/k {D}, v {Dv}) with softcap={softcap}: the CUDA kernels take 64, 128, "
+                f"(256, 256) and (192, 128); other widths run without context parallelism and sinks only")
+        return _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap)
     if getattr(meta, "cp", False):
         from ..parallel.cp import flash_varlen_cp   # context parallelism is causal only, without a window
 

@@ -344,6 +344,30 @@ def bench_attn_wide(rows):
         rows.append(line)
 
 
+def bench_indexer(rows):
+    """Lightning-indexer scores (csrc/indexer.cu) of one document against the einsum form that holds the per-head
+    scores (queries in blocks of 512 so that [512, H, L] fp32 fits)."""
+    from axolotl_b200.models import dsa
+
+    tf, hbm, src = _peaks()
+    for L, H in ((8192, 32), (16384, 32), (8192, 64)):
+        q = torch.randn(L, H, 128, device="cuda").bfloat16()
+        k = torch.randn(L, 128, device="cuda").bfloat16()
+        w = torch.randn(L, H, device="cuda") * 0.1
+        fl = 2.0 * L * H * 128 * L / 2                                   # causal half of the square
+        t = time_cuda(lambda: dsa.indexer_scores(q, k, w))
+        fill = time_cuda(lambda: torch.full((L, L), float("-inf"), dtype=torch.float32, device="cuda"))
+
+        def eager():
+            for b0 in range(0, L, 512):
+                dsa.indexer_scores_ref(q[b0:b0 + 512], k[: b0 + 512], w[b0:b0 + 512], causal_off=b0)
+        t_e = time_cuda(eager, iters=3, warmup=1)
+        t_k = max(t - fill, 1e-6)
+        rows.append(f"indexer scores L={L} H={H}: {t*1e3:.0f} us with the -inf fill of the output ({fill*1e3:.0f} us), kernel "
+                    f"{fl / t_k / 1e9:.0f} TFLOP/s ({fl / t_k / 1e9 / tf:.2f} of {src} bf16 peak), output "
+                    f"{L * L * 2 / t_k / 1e6:.0f} GB/s | einsum form {t_e*1e3:.0f} us ({t_e / t:.1f}x)")
+
+
 def bench_attn(rows):
     from axolotl_b200.ops.functional import AttnMeta, flash_varlen
 
@@ -450,6 +474,15 @@ def profile_case(what):
         for _ in range(3):
             grouped_gemm_w4a16(x, q, lay)
             grouped_gemm_w4a16(dy, q, lay, trans_w=True)
+    elif what == "one_indexer":
+        from axolotl_b200.models import dsa
+
+        L, H = 8192, 32
+        q = torch.randn(L, H, 128, device="cuda").bfloat16()
+        k = torch.randn(L, 128, device="cuda").bfloat16()
+        w = torch.randn(L, H, device="cuda") * 0.1
+        for _ in range(3):
+            dsa.indexer_scores(q, k, w)
     elif what == "one_grouped":
         # one MoE projection of Qwen3-MoE-30B-A3B: 128 experts, 8192 tokens x top-8 = 65536 routed rows
         from axolotl_b200.ops.grouped import GroupLayout, grouped_gemm, grouped_gram
@@ -481,7 +514,7 @@ def profile_case(what):
 
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
-    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp", "one_w4a16"):
+    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp", "one_w4a16", "one_indexer"):
         return profile_case(what)
     rows = []
     if what in ("gemm", "all"):
@@ -500,6 +533,8 @@ def main(argv):
         bench_w4a16(rows)
     if what in ("attn_wide",):
         bench_attn_wide(rows)
+    if what in ("indexer",):
+        bench_indexer(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

@@ -171,3 +171,28 @@ def test_compat_plugins_act_on_their_keys(monkeypatch, caplog):
         NativeKernelsPlugin().pre_model_load({"liger_rms_norm": True, "cut_cross_entropy": False})
     text = " ".join(r.getMessage() for r in caplog.records)
     assert "rmsnorm" in text and "always used" in text
+
+
+def test_blocked_attention_for_head_widths_without_a_kernel_matches_the_reference():
+    """The blocked path that serves head widths outside the kernels' set (documents, windows, soft cap, bidirectional)."""
+    import torch
+
+    from axolotl_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    Hq, Hk, D, Dv = 4, 2, 48, 32
+    lens = [300, 77, 513]
+    T = sum(lens)
+    cu = [0, 300, 377, 890]
+    qkv = torch.randn(T, (Hq + Hk) * D + Hk * Dv, requires_grad=True)
+    for causal, window, softcap in [(True, 0, 0.0), (True, 100, 0.0), (False, 0, 0.0), (True, 0, 5.0)]:
+        meta = Fn.AttnMeta(cu, "cpu", causal=causal, window=window or None)
+        q = qkv[:, : Hq * D].reshape(T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D)
+        v = qkv[:, (Hq + Hk) * D:].reshape(T, Hk, Dv)
+        ref = Fn._attn_ref(q, k, v, cu, 0.2, causal, window, softcap).reshape(T, Hq * Dv)
+        got = Fn._blocked_attention(qkv, meta, Hq, Hk, D, Dv, 0.2, softcap)
+        g1, = torch.autograd.grad((got ** 2).sum(), qkv, retain_graph=True)
+        g2, = torch.autograd.grad((ref ** 2).sum(), qkv)
+        assert (got - ref).abs().max() < 1e-5
+        assert (g1 - g2).abs().max() < 1e-3

@@ -7,13 +7,14 @@
 // q [Lq, H, 128] bf16, k [Lk, 128] bf16 (one key vector per position, shared by all heads), w [Lq, H] fp32
 // (the caller folds the softmax scale and H^-1/2 into w: relu commutes with a positive scale).
 //
-// The contraction is one GEMM [Lq*H, 128] x [128, Lk] on the tensor cores, and the [Lq, H, Lk] score tensor
-// is never written: 128 accumulator rows hold 128/H query positions x H heads, the epilogue applies
-// relu * w per row and sums the rows of one position (a butterfly over the 32 lanes of a warp, then across
-// the warps of the position through shared memory) before anything leaves the SM. One CTA owns a block of
-// query positions, keeps its Q tile resident in shared memory and streams the key tiles of the causal range
-// through a TMA ring; accumulators are double-buffered in TMEM so the epilogue of tile i overlaps the MMAs of
-// tile i+1.
+// The contraction is one GEMM [Lk, 128] x [128, Lq*H] on the tensor cores with the KEYS on the accumulator rows and
+// (query position, head) on its columns, so the [Lq, H, Lk] score tensor is never written and the head sum needs no
+// exchange between threads: an epilogue thread owns one key, reads the H accumulator columns of a query position,
+// applies relu * w and adds them up in registers, and the 32 lanes of a warp store 32 consecutive keys of the output
+// row. One CTA owns a block of 128 / H query positions, keeps its Q tile resident in shared memory and streams the
+// key tiles of the causal range through a TMA ring; accumulators are double-buffered in TMEM so the epilogue of tile
+// i overlaps the MMAs of tile i+1. Eight epilogue warps: two per TMEM lane quadrant, each taking half of the columns
+// (for H = 128 a position spans all columns and one warp per quadrant does the work).
 //
 // The reference computes the same scores with a Triton kernel that loops over heads inside a program
 // (src/axolotl/integrations/kernels/libs/glm_dsa/indexer.py:38-176, .../dsv4/indexer.py:38-138).
@@ -23,14 +24,15 @@
 
 namespace {
 
-constexpr int BM = 128;        // accumulator rows: BM / H query positions x H heads
-constexpr int BN = 128;        // keys per tile
+constexpr int BM = 128;        // (query position, head) rows of the resident Q tile = accumulator columns
+constexpr int BN = 128;        // keys per tile = accumulator rows
 constexpr int DI = 128;        // index head width
 constexpr int STAGES = 4;
-constexpr int kThreads = 192;  // TMA warp, MMA warp, 4 epilogue warps
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // TMA warp, MMA warp, epilogue warps
 constexpr int A_BYTES = BM * DI * 2;
 constexpr int B_BYTES = BN * DI * 2;
-constexpr int PART_BYTES = 2 * 4 * BN * 4;
+constexpr int PART_BYTES = kEpiWarps * BM * 4;   // every epilogue warp's own copy of the tile's head weights
 constexpr int SMEM_BYTES = A_BYTES + STAGES * B_BYTES + PART_BYTES + 256 + 1024;
 constexpr int TMEM_COLS = 2 * BN;
 
@@ -42,20 +44,6 @@ struct IParams {
   int causal_off;   // key t is visible to query s when t <= s + causal_off
   int* status;
 };
-
-// One butterfly step over the warp: a lane keeps the O columns whose bit O equals its own and adds the partner's
-// sums of those columns; after the steps 16, 8, 4, 2, 1 lane j holds the sum over the 32 rows of column j.
-template <int O>
-AXB_DEVICE void butterfly(float (&v)[32], int lane) {
-  const bool hi = (lane & O) != 0;
-#pragma unroll
-  for (int j = 0; j < O; ++j) {
-    const float keep = hi ? v[j + O] : v[j];
-    const float send = hi ? v[j] : v[j + O];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, O);
-  }
-  if constexpr (O > 1) butterfly<O / 2>(v, lane);
-}
 
 AXB_DEVICE int last_k_tile(const IParams& p, int qt, int P) {
   long long last_pos = (long long)qt * P + P - 1;
@@ -73,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + A_BYTES;
-  float* part = reinterpret_cast<float*>(smem + A_BYTES + STAGES * B_BYTES);   // [2][4][BN]
+  float* w_s = reinterpret_cast<float*>(smem + A_BYTES + STAGES * B_BYTES);    // [kEpiWarps][BM]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A_BYTES + STAGES * B_BYTES + PART_BYTES);
   uint64_t* full_bar = bars;                 // key tile landed
   uint64_t* empty_bar = bars + STAGES;       // key tile consumed
@@ -82,7 +70,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* tfull_bar = bars + 2 * STAGES + 2;
   uint64_t* tempty_bar = bars + 2 * STAGES + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 7);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -98,9 +85,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(a_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
-      mbar_init(&tempty_bar[s], 4);
+      mbar_init(&tempty_bar[s], kEpiWarps);
     }
-    *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -145,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc = make_idesc_bf16(BN, BM, 0, 0);
       int stage = 0;
       uint32_t phase = 0, a_phase = 0;
       int it = 0;
@@ -166,15 +152,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * BN;
+          const uint32_t d_tmem = tmem_base + acc * BM;
           const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
           for (int kb = 0; kb < DI / 64; ++kb) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t da = make_smem_desc_sw128(a_addr + kb * (A_BYTES / 2) + kk * 32, 16, 1024);
-              const uint64_t db = make_smem_desc_sw128(b_addr + kb * (B_BYTES / 2) + kk * 32, 16, 1024);
-              umma_f16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              // keys are the M operand (accumulator rows), the resident Q tile the N operand
+              const uint64_t dq = make_smem_desc_sw128(a_addr + kb * (A_BYTES / 2) + kk * 32, 16, 1024);
+              const uint64_t dk = make_smem_desc_sw128(b_addr + kb * (B_BYTES / 2) + kk * 32, 16, 1024);
+              umma_f16(d_tmem, dk, dq, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[stage]);
@@ -188,58 +175,65 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    const int lane_group = warp & 3;
-    const int et = (warp - 2) * 32 + lane;       // 0..127: the key column this thread writes
-    const int wpp = p.H / 32;                    // warps (accumulator lane quadrants) per query position
+    const int ew = warp - 2;
+    const int lane_group = warp & 3;             // TMEM lane quadrant this warp may read: keys lane_group*32 ..
+    const int half = ew >> 2;                    // which half of the accumulator columns
+    // H <= 64: the two warps of a quadrant split the columns (a position never straddles the halves);
+    // H = 128: one position spans all columns, the first warp of the quadrant takes them all
+    const int c_lo = p.H == 128 ? 0 : half * 2;
+    const int c_hi = p.H == 128 ? (half == 0 ? 4 : 0) : half * 2 + 2;
     const long long n_rows = (long long)p.Lq * p.H;
     const float neg_inf = -INFINITY;
+    float* my_w = w_s + ew * BM;
     int it = 0;
     bool ok = true;
     for (int qt = blockIdx.x; ok && qt < num_q; qt += gridDim.x) {
       const int kt_last = last_k_tile(p, qt, P);
       if (kt_last < 0) continue;
-      const long long row = (long long)qt * BM + lane_group * 32 + lane;
-      const float wv = row < n_rows ? p.w[row] : 0.f;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < BM / 32; ++i) {
+        const long long row = (long long)qt * BM + i * 32 + lane;
+        my_w[i * 32 + lane] = row < n_rows ? p.w[row] : 0.f;
+      }
+      __syncwarp();
       for (int kt = 0; kt <= kt_last; ++kt) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
-        // a wait that ran out must not leave the other epilogue warps alone at the named barrier below: the
-        // warp raises a flag, skips its accumulator, still joins the barrier, and all four leave together
-        const bool got = mbar_wait(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL);
-        if (!got) *abort_flag = 1;
-        tc_fence_after();
-        const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
-        float* my_part = part + (acc * 4 + lane_group) * BN;
-#pragma unroll 1
-        for (int c = 0; got && c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_addr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(__uint_as_float(r[j]), 0.f) * wv;
-          butterfly<16>(v, lane);
-          my_part[c * 32 + lane] = v[0];
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0 && got) mbar_arrive(&tempty_bar[acc]);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abort_flag) {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, AXB_TIMEOUT_TMEM_FULL)) {
           ok = false;
           break;
         }
-        const int key = kt * BN + et;
-        if (key < p.Lk) {
-          for (int pp = 0; pp < P; ++pp) {
-            const long long pos = (long long)qt * P + pp;
-            if (pos >= p.Lq) break;
-            float s = 0.f;
-            for (int g = 0; g < wpp; ++g) s += part[(acc * 4 + pp * wpp + g) * BN + et];
-            p.out[pos * p.ldo + key] = key <= pos + p.causal_off ? s : neg_inf;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BM;
+        const int key = kt * BN + lane_group * 32 + lane;
+        float s = 0.f;
+#pragma unroll 1
+        for (int c = c_lo; c < c_hi; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const float4* wv = reinterpret_cast<const float4*>(my_w + c * 32);
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 w4 = wv[j];                                   // the same address in every lane: a broadcast
+            s0 = fmaf(fmaxf(__uint_as_float(r[4 * j + 0]), 0.f), w4.x, s0);
+            s1 = fmaf(fmaxf(__uint_as_float(r[4 * j + 1]), 0.f), w4.y, s1);
+            s2 = fmaf(fmaxf(__uint_as_float(r[4 * j + 2]), 0.f), w4.z, s2);
+            s3 = fmaf(fmaxf(__uint_as_float(r[4 * j + 3]), 0.f), w4.w, s3);
+          }
+          s += (s0 + s1) + (s2 + s3);
+          if (((c + 1) * 32) % p.H == 0) {                              // last head of a query position
+            const long long pos = (long long)qt * P + ((c + 1) * 32) / p.H - 1;
+            if (pos < p.Lq && key < p.Lk) p.out[pos * p.ldo + key] = key <= pos + p.causal_off ? s : neg_inf;
+            s = 0.f;
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       }
     }
   }

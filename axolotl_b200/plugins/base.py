@@ -44,6 +44,10 @@ class BasePlugin:
     def compute_loss(self, cfg):
         """Optional replacement for the trainer's loss: callable(model, device_batch, num_items) -> loss."""
         return None
+    def run_training(self, cfg, dataset_meta, tokenizer=None):
+        """A plugin that trains somewhere else (a remote service) returns its result dict here; the local run (model
+        build, trainer, saving) is then skipped. None = train locally."""
+        return None
     def post_train(self, cfg, model): ...
     def post_train_unload(self, cfg): ...
 
@@ -59,6 +63,7 @@ _BUNDLED = {
     "nemo_gym": "axolotl_b200.plugins.nemo_gym.NemoGymPlugin",
     "llm_compressor": "axolotl_b200.plugins.sparse_ft.LLMCompressorPlugin",
     "swanlab": "axolotl_b200.plugins.swanlab.SwanLabPlugin",
+    "hatchery": "axolotl_b200.plugins.hatchery.HatcheryPlugin",
     "liger": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
     "cut_cross_entropy": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
     "kernels": "axolotl_b200.plugins.compat.NativeKernelsPlugin",
@@ -80,6 +85,7 @@ _ALIASES = {
     "axolotl.integrations.nemo_gym.NemoGymPlugin": "nemo_gym",
     "axolotl.integrations.llm_compressor.LLMCompressorPlugin": "llm_compressor",
     "axolotl.integrations.swanlab.SwanLabPlugin": "swanlab",
+    "axolotl.integrations.hatchery.HatcheryPlugin": "hatchery",
 }
 
 

@@ -397,6 +397,10 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
     if dataset_meta is None and not objective_mode and not streaming:
         dataset_meta = load_datasets(cfg)
 
+    remote = pm.first("run_training", cfg, dataset_meta, tokenizer)
+    if remote is not None:            # a plugin trained elsewhere (remote service): no local model, nothing to save
+        return remote
+
     model = build_model(cfg, device)
     if tokenizer is not None:
         want = len(tokenizer)

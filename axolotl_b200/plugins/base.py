@@ -44,6 +44,9 @@ class BasePlugin:
     def compute_loss(self, cfg):
         """Optional replacement for the trainer's loss: callable(model, device_batch, num_items) -> loss."""
         return None
+    def wrap_rollout_engine(self, cfg, engine):
+        """Online-RL runs: a plugin may put its own rollout source in front of the generation engine."""
+        return None
     def run_training(self, cfg, dataset_meta, tokenizer=None):
         """A plugin that trains somewhere else (a remote service) returns its result dict here; the local run (model
         build, trainer, saving) is then skipped. None = train locally."""

@@ -5,9 +5,16 @@ A NeMo-Gym deployment has a head server that publishes the deployment's configur
 answer in the OpenAI *Responses* wire format it returns ``{"reward": float}``. Dataset rows name
 their environment (``resources_server_ref: {name: ...}``) and may carry extra verifier fields
 (``verify_extra``); both columns reach the reward function through the rollout producer.
-Reference: src/axolotl/integrations/nemo_gym/{plugin.py:135-700, rewards.py, args.py}. The
-multi-turn mode (agent ``/run`` rollouts replacing local generation) and starting / cloning the
-Gym servers from the trainer are not implemented: the servers are expected to be running.
+Reference: src/axolotl/integrations/nemo_gym/{plugin.py:135-700, rewards.py, args.py}.
+
+Multi-turn mode (``nemo_gym_multi_turn: true``): the deployment's AGENT servers run the episodes. For every sample
+the trainer POSTs the dataset row to an agent's ``/run`` endpoint; the agent generates through the policy's
+generation server (``axolotl vllm-serve``, kept in sync by the usual adapter hand-over), executes tool calls, feeds
+their results back for further turns and scores the episode. The answer lists the turns with their token ids and
+sampling log-probs; turns are stitched into one completion in which the tokens an environment inserted (tool
+results) stay in the context but are masked out of the loss, and the episode reward takes the place of reward
+functions (reference: multi_turn.py:31-329, data_producer.py:32-279, server.py:170-199). Starting / cloning the Gym
+servers from the trainer is not implemented: the servers are expected to be running.
 
 YAML::
 
@@ -117,6 +124,120 @@ def reward_nemo_gym_verify(completions, prompts=None, resources_server_ref=None,
     return out
 
 
+def discover_agent_servers(head_url: str | None = None, timeout: float = 5.0) -> dict:
+    """{top-level config name: agent URL} for every block of the head server's configuration that declares
+    ``responses_api_agents`` (dataset rows name their agent by that top-level name in ``agent_ref.name``)."""
+    import requests
+    import yaml
+
+    agents = {}
+    try:
+        conf = yaml.safe_load(requests.get(f"{(head_url or _STATE['head']).rstrip('/')}/global_config_dict_yaml", timeout=timeout).text)
+        if isinstance(conf, str):
+            conf = yaml.safe_load(conf)
+        for top, block in (conf or {}).items():
+            if not isinstance(block, dict):
+                continue
+            for acfg in (block.get("responses_api_agents") or {}).values():
+                if isinstance(acfg, dict) and acfg.get("port"):
+                    agents[top] = f"http://{acfg.get('host', '127.0.0.1')}:{acfg['port']}"
+    except Exception as exc:
+        LOG.warning("NeMo-Gym head server not reachable: %s", exc)
+    return agents
+
+
+def parse_agent_response(response, eos_token_id: int) -> dict:
+    """One ``/run`` answer -> prompt ids, one stitched completion, the mask of policy-written tokens, sampling
+    log-probs, reward, number of turns. A failed or empty episode becomes a one-token masked sample that keeps its
+    reward (the group statistics still see it, the loss does not)."""
+    blank = {"prompt_ids": [eos_token_id], "completion_ids": [eos_token_id], "env_mask": [0], "logprobs": [0.0],
+             "reward": 0.0, "num_turns": 0}
+    if not isinstance(response, dict) or "error" in response:
+        return blank
+    turns = (response.get("response") or {}).get("output") or []
+    blank["reward"] = float(response.get("reward", 0.0))
+
+    def says_something(item):
+        if item.get("type") == "function_call":
+            return True
+        return item.get("type") == "message" and any(
+            isinstance(c, dict) and c.get("type") == "output_text" and (c.get("text") or "").strip() for c in item.get("content") or [])
+    if not any(says_something(t) for t in turns):
+        return blank
+    first, seen = None, []
+    completion, mask, logps, n_turns = [], [], [], 0
+    for t in turns:
+        gen = list(t.get("generation_token_ids") or [])
+        if not gen:
+            continue
+        ctx = list(t.get("prompt_token_ids") or [])
+        n_turns += 1
+        if first is None:
+            first = ctx
+        elif len(ctx) > len(seen):           # what the environment appended since the last turn: context, not policy
+            extra = ctx[len(seen):]
+            completion += extra
+            mask += [0] * len(extra)
+            logps += [0.0] * len(extra)
+        lp = [float(v) for v in (t.get("generation_log_probs") or [])][: len(gen)]
+        completion += gen
+        mask += [1] * len(gen)
+        logps += lp + [0.0] * (len(gen) - len(lp))
+        seen = ctx + gen
+    if first is None:
+        return blank
+    return {"prompt_ids": first, "completion_ids": completion, "env_mask": mask, "logprobs": logps,
+            "reward": blank["reward"], "num_turns": n_turns}
+
+
+class AgentRollout:
+    """Rollout source of the multi-turn mode: one ``/run`` request per sample, in parallel."""
+
+    def __init__(self, inner, agent_servers: dict, eos_token_id: int, timeout: float = 10800.0, max_workers: int = 64):
+        self.inner, self.agents, self.eos, self.timeout, self.max_workers = inner, dict(agent_servers), eos_token_id, timeout, max_workers
+        if not self.agents:
+            raise ValueError("nemo_gym_multi_turn: the head server lists no agent server (`responses_api_agents`)")
+
+    def sync_weights(self, model, step):      # the agents sample from the generation server the inner engine talks to
+        return self.inner.sync_weights(model, step)
+
+    def _request(self, rec, max_len, temperature, top_p):
+        item = dict(rec.get("verify_extra") or {})
+        if not item:
+            prompt = rec.get("prompt")
+            text = prompt[-1].get("content", "") if isinstance(prompt, list) and prompt and isinstance(prompt[-1], dict) else (prompt or "")
+            item = {"responses_create_params": {"input": [{"role": "user", "content": text}]}}
+        if "agent_ref" not in item and rec.get("agent_ref"):
+            item["agent_ref"] = rec["agent_ref"]
+        params = item.setdefault("responses_create_params", {})
+        params = item["responses_create_params"] = dict(params)
+        params.setdefault("max_output_tokens", max_len)
+        params["temperature"], params["top_p"] = temperature, (top_p if top_p and top_p < 1.0 else 0.999)
+        name = (item.get("agent_ref") or {}).get("name", "")
+        return self.agents.get(name) or next(iter(self.agents.values())), item
+
+    def _run(self, url, body):
+        import requests
+
+        try:
+            r = requests.post(f"{url}/run", json=body, timeout=self.timeout)
+            if r.status_code == 200:
+                return r.json()
+            return {"error": f"HTTP {r.status_code}: {r.text[:200]}"}
+        except Exception as exc:   # noqa: BLE001 - a lost episode must not stop the step
+            LOG.warning("agent /run failed: %s", exc)
+            return {"error": str(exc)}
+
+    def rollouts(self, recs, n, max_len, temperature=1.0, top_p=1.0):
+        """Prompt-major list of len(recs) * n parsed episodes."""
+        from concurrent.futures import ThreadPoolExecutor
+
+        jobs = [self._request(r, max_len, temperature, top_p) for r in recs for _ in range(n)]
+        with ThreadPoolExecutor(max_workers=min(self.max_workers, max(len(jobs), 1))) as ex:
+            answers = list(ex.map(lambda j: self._run(*j), jobs))
+        return [parse_agent_response(a, self.eos) for a in answers]
+
+
 def reward_env(completions, env_reward=None, **kwargs):
     """Passthrough of a reward an environment already attached to the sample (``env_reward`` column)."""
     if env_reward is None:
@@ -133,11 +254,19 @@ class NemoGymPlugin(BasePlugin):
     def register(self, cfg):
         if not cfg.get("nemo_gym_enabled"):
             return
-        if cfg.get("nemo_gym_multi_turn"):
-            raise ValueError("nemo_gym_multi_turn (agent /run rollouts) is not implemented; single-turn /verify rewards are")
+        if cfg.get("nemo_gym_multi_turn") and not (cfg.get("trl") or {}).get("use_vllm"):
+            raise ValueError("nemo_gym_multi_turn: the agents generate through a served policy, set trl.use_vllm "
+                             "(and start `axolotl vllm-serve`)")
         _STATE["head"] = f"http://{cfg.get('nemo_gym_head_host') or '127.0.0.1'}:{cfg.get('nemo_gym_head_port') or 11000}"
         _STATE["verify_timeout"] = cfg.get("nemo_gym_verify_timeout") or 30
         _STATE["urls"] = None
+
+    def wrap_rollout_engine(self, cfg, engine):
+        if not (cfg.get("nemo_gym_enabled") and cfg.get("nemo_gym_multi_turn")):
+            return None
+        eos = cfg.get("eos_token_id")
+        return AgentRollout(engine, discover_agent_servers(), int(eos if eos is not None else 0),
+                            timeout=float(cfg.get("nemo_gym_run_timeout") or 10800))
 
     def pre_model_load(self, cfg):
         self.register(cfg)

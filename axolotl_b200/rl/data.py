@@ -108,7 +108,9 @@ class _DocPacker:
     def __init__(self):
         self.ids, self.lab, self.pos, self.sid, self.cu = [], [], [], [], [0]
 
-    def add(self, prompt, completion):
+    def add(self, prompt, completion, completion_mask=None):
+        """``completion_mask`` (0/1 per completion token): tokens the policy did not write (tool results an environment
+        inserted between turns) stay in the context and are not targets."""
         doc = np.asarray(list(prompt) + list(completion), dtype=np.int64)
         lab = np.full(len(doc), IGNORE_INDEX, dtype=np.int64)
         # shifted labels: position t predicts token t+1; only completion tokens are targets
@@ -116,6 +118,10 @@ class _DocPacker:
         lab[lo:len(doc) - 1] = doc[lo + 1:]
         if len(prompt) == 0:
             lab[:len(doc) - 1] = doc[1:]
+        if completion_mask is not None and len(prompt) > 0:
+            keep = np.asarray(list(completion_mask), dtype=bool)[: len(completion)]
+            tgt = lab[len(prompt) - 1: len(prompt) - 1 + len(keep)]
+            tgt[~keep] = IGNORE_INDEX
         k = len(self.cu) - 1
         self.ids.append(doc)
         self.lab.append(lab)

@@ -194,9 +194,22 @@ class RolloutProducer:
     def make_batch(self, recs, step=0):
         s = self.s
         n = s.num_generations
-        completions = self.engine.generate([r["prompt_ids"] for r in recs], n, s.max_completion_length,
-                                           s.temperature, s.top_p, s.top_k)
-        R, w = self._rewards(recs, completions)
+        agent = None
+        if hasattr(self.engine, "rollouts"):
+            # an environment's agents drive the episodes (generation through the served policy, tool calls, several
+            # turns) and score them: completions, the mask of policy-written tokens and the reward all come back
+            agent = self.engine.rollouts(recs, n, s.max_completion_length, s.temperature, s.top_p)
+            completions = [a["completion_ids"] for a in agent]
+            env = torch.tensor([float(a["reward"]) for a in agent])
+            if self.rf:
+                R, w = self._rewards([dict(r, env_reward=None) for r in recs], completions)
+                R, w = torch.cat([env[:, None], R], 1), torch.cat([torch.ones(1), w])
+            else:
+                R, w = env[:, None], torch.ones(1)
+        else:
+            completions = self.engine.generate([r["prompt_ids"] for r in recs], n, s.max_completion_length,
+                                               s.temperature, s.top_p, s.top_k)
+            R, w = self._rewards(recs, completions)
         if s.multi_objective:
             adv = sum(w[j] * L.group_advantages(R[:, j].nan_to_num(0.0), n, s.scale_rewards) for j in range(R.shape[1]))
             total = (R.nan_to_num(0.0) * w).sum(1)
@@ -208,6 +221,9 @@ class RolloutProducer:
             sl = slice(g * n, (g + 1) * n)
             grp = {"prompt_ids": r["prompt_ids"], "completions": completions[sl], "adv": adv[sl].clone(),
                    "rewards": total[sl].clone()}
+            if agent is not None:      # the agent tokenised the prompt itself (tool schemas, system turns)
+                grp["prompts"] = [a["prompt_ids"] for a in agent[sl]]
+                grp["masks"] = [a["env_mask"] for a in agent[sl]]
             spread = float(total[sl].std()) if n > 1 else 0.0
             if self.replay is not None:
                 if spread > 0:
@@ -217,6 +233,8 @@ class RolloutProducer:
             groups.append(grp)
         self.stats = {"reward": float(total.mean()), "reward_std": float(total.std()) if len(total) > 1 else 0.0,
                       "completion_length": float(np.mean([len(c) for c in completions]))}
+        if agent is not None:
+            self.stats["num_turns"] = float(np.mean([a.get("num_turns", 1) for a in agent]))
         for f in self.rf:   # model-based rewards report their own breakdown
             self.stats.update(getattr(f, "last_metrics", None) or {})
         return self.collate(groups)
@@ -226,9 +244,13 @@ class RolloutProducer:
         pk = _DocPacker()
         advs, trunc = [], []
         for g in groups:
-            for c, a in zip(g["completions"], g["adv"]):
-                c = list(c) if len(c) else [self.eos if self.eos is not None else self.pad]
-                pk.add(g["prompt_ids"], c)
+            for i, (c, a) in enumerate(zip(g["completions"], g["adv"])):
+                empty = not len(c)
+                c = list(c) if not empty else [self.eos if self.eos is not None else self.pad]
+                if "masks" in g and not empty:
+                    pk.add(g["prompts"][i], c, g["masks"][i])
+                else:
+                    pk.add(g["prompt_ids"], c)
                 advs.append(float(a))
                 trunc.append(len(c) >= s.max_completion_length and (self.eos is None or c[-1] != self.eos))
         aux = {"advantages": torch.tensor(advs, dtype=torch.float32)}

@@ -279,6 +279,9 @@ def build_objective_run(cfg, model, tokenizer, device, parallel, dp_rank, dp_siz
                                          save_adapter_fn=(lambda d: save_adapter(model, spec, d)) if spec is not None else None)
         else:
             engine = G.LocalRollout(model, eos, pad, seed + dp_rank)
+        if eos is not None and cfg.get("eos_token_id") is None:
+            cfg["eos_token_id"] = eos
+        engine = PluginManager.get_instance().first("wrap_rollout_engine", cfg, engine) or engine
         eb = dict(cfg.get("ebft") or {}) if rl == "ebft" else {}
         if eb.get("mode") == "strided":
             from ..rl.ebft import load_strided_records

@@ -494,9 +494,100 @@ def test_nemo_gym_verify_rewards_against_a_fake_environment_server():
         assert r == [1.0, 0.25, 0.0]
         assert seen[0]["responses_create_params"]["input"][0]["content"] == "2+2?" and seen[0]["expected"] == 4
         assert NG.reward_env(["a", "b"], env_reward=[0.5, 2]) == [0.5, 2.0]
-        with pytest.raises(ValueError):
+        with pytest.raises(ValueError):      # the agents need a served policy to sample from
             plug.register({"nemo_gym_enabled": True, "nemo_gym_multi_turn": True})
     finally:
         env.shutdown()
+        head.shutdown()
+        NG._STATE["urls"] = None
+
+
+def test_nemo_gym_multi_turn_agent_rollouts_feed_grpo_with_masked_tool_tokens():
+    """Agents run the episodes: turns are stitched into one completion, tokens the environment inserted between turns
+    stay in the context without being targets, the episode reward drives the advantages."""
+    import http.server
+    import json
+    import threading
+
+    from axolotl_b200.plugins import nemo_gym as NG
+    from axolotl_b200.rl import grpo as G
+
+    calls = []
+
+    class Agent(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            calls.append(body)
+            k = len(calls)
+            prompt = [11, 12, 13]
+            turn1 = {"type": "function_call", "prompt_token_ids": prompt, "generation_token_ids": [21, 22],
+                     "generation_log_probs": [-0.5, -0.25]}
+            # second turn: the context grew by the first generation AND two tool-result tokens (91, 92)
+            turn2 = {"type": "message", "content": [{"type": "output_text", "text": "done"}],
+                     "prompt_token_ids": prompt + [21, 22, 91, 92], "generation_token_ids": [31, 2],
+                     "generation_log_probs": [-0.125]}
+            data = json.dumps({"response": {"output": [turn1, turn2]}, "reward": float(k % 2)}).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    agent = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Agent)
+
+    class Head(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            doc = (f"tool_env:\n  responses_api_agents:\n    simple_agent:\n      host: 127.0.0.1\n"
+                   f"      port: {agent.server_address[1]}\n").encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(doc)))
+            self.end_headers()
+            self.wfile.write(doc)
+
+    head = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Head)
+    for srv in (agent, head):
+        threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        plug = NG.NemoGymPlugin()
+        cfg = {"nemo_gym_enabled": True, "nemo_gym_multi_turn": True, "nemo_gym_head_port": head.server_address[1],
+               "trl": {"use_vllm": True}, "eos_token_id": 2, "nemo_gym_run_timeout": 5}
+        plug.register(cfg)
+        assert NG.discover_agent_servers() == {"tool_env": f"http://127.0.0.1:{agent.server_address[1]}"}
+
+        class Inner:
+            synced = []
+
+            def sync_weights(self, model, step):
+                self.synced.append(step)
+
+        engine = plug.wrap_rollout_engine(cfg, Inner())
+        engine.sync_weights(None, 3)
+        assert Inner.synced == [3]
+        one = NG.parse_agent_response({"response": {"output": []}, "reward": 0.7}, 2)
+        assert one["env_mask"] == [0] and one["reward"] == 0.7          # an empty episode keeps its reward, trains nothing
+
+        st = G.GRPOSettings({"trl": {"num_generations": 2, "max_completion_length": 16}})
+        recs = [{"prompt": "use the tool", "prompt_ids": [5, 6], "agent_ref": {"name": "tool_env"},
+                 "verify_extra": {"responses_create_params": {"input": [{"role": "user", "content": "use the tool"}]}, "expected": 4}}]
+        prod = G.RolloutProducer(None, engine, [], st, recs, 1, None, 0, 2)
+        b = prod.make_batch(recs)
+        assert len(calls) == 2 and calls[0]["expected"] == 4 and calls[0]["agent_ref"] == {"name": "tool_env"}
+        assert calls[0]["responses_create_params"]["max_output_tokens"] == 16
+        ids, lab = b["input_ids"][0].tolist(), b["labels"][0].tolist()
+        doc = [11, 12, 13, 21, 22, 91, 92, 31, 2]                        # the agent's own prompt ids, stitched turns
+        assert ids[:9] == doc and ids[9:18] == doc
+        # shifted targets: policy tokens 21 22 | tool tokens masked | 31 2
+        assert lab[:9] == [-100, -100, 21, 22, -100, -100, 31, 2, -100]
+        adv = b["aux_tensors"]["advantages"].tolist()
+        assert adv[0] == -adv[1] and adv[0] != 0                           # rewards 1.0 and 0.0 inside the group
+        assert prod.stats["num_turns"] == 2.0
+    finally:
+        agent.shutdown()
         head.shutdown()
         NG._STATE["urls"] = None

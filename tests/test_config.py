@@ -142,19 +142,67 @@ def test_plugins_contribute_keys():
 
 
 def test_architecture_registry_checks():
-    from axolotl_b200.models.config import preset
-    from axolotl_b200.models.registry import support_for, validate_cfg
+    from axolotl_b200.models import registry as R
+    from axolotl_b200.models.config import SUPPORTED_MODEL_TYPES, ModelConfig, preset
 
-    assert support_for("qwen3_moe").expert_parallel and not support_for("llama").expert_parallel
+    # every model type the config reader accepts has a descriptor (the training entry point validates against it)
+    for mt in SUPPORTED_MODEL_TYPES:
+        assert R.get_model_support(mt) is not None, mt
+    assert isinstance(R.support_for("llama").capabilities[R.EP], R.Unsupported)
     with pytest.raises(ValueError, match="no model graph"):
-        support_for("gemma2")
+        R.support_for("gemma4")
     with pytest.raises(ValueError, match="expert parallelism needs"):
-        validate_cfg({"expert_parallel_size": 2}, preset("tiny-llama"))
+        R.validate_cfg({"expert_parallel_size": 2}, preset("tiny-llama"))
     with pytest.raises(ValueError, match="cannot be split"):
-        validate_cfg({"expert_parallel_size": 3}, preset("tiny-qwen3-moe"))
-    with pytest.raises(ValueError, match="tensor parallelism"):
-        validate_cfg({"tensor_parallel_size": 2}, preset("tiny-qwen3-moe"))
-    assert validate_cfg({"sample_packing": True}, preset("tiny-llama")) == []
+        R.validate_cfg({"expert_parallel_size": 3}, preset("tiny-qwen3-moe"))
+    with pytest.raises(ValueError, match="tensor parallelism is not supported for model_type=qwen3_moe"):
+        R.validate_cfg({"tensor_parallel_size": 2}, preset("tiny-qwen3-moe"))
+    assert R.validate_cfg({"sample_packing": True}, preset("tiny-llama")) == []
+    # wide heads pass the head-width check (their own kernels), and say why context parallelism is closed
+    gemma = preset("tiny-gemma2")
+    assert R.validate_cfg({"sample_packing": True, "adapter": "lora"}, gemma)
+    with pytest.raises(ValueError, match="head widths 64 and 128"):
+        R.validate_cfg({"context_parallel_size": 2}, gemma)
+    qn = ModelConfig.from_hf_dict(dict(model_type="qwen3_next", vocab_size=64, hidden_size=32, intermediate_size=32,
+                                       num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=1, head_dim=16,
+                                       linear_num_value_heads=2, linear_num_key_heads=1, linear_key_head_dim=8,
+                                       linear_value_head_dim=8, num_experts=0))
+    with pytest.raises(ValueError, match="Gated DeltaNet"):
+        R.validate_cfg({"context_parallel_size": 2}, qn)
+
+
+def test_model_support_registration_and_experimental_warning(caplog):
+    import logging
+
+    from axolotl_b200.models import registry as R
+
+    @R.register_model_support
+    class Toy(R.ModelSupport):
+        model_types = ("toy_arch",)
+        capabilities = {R.CP: R.Experimental("Only tried at two ranks."), R.TP: R.Unsupported("No sharding rule.")}
+
+        def validate_cfg(self, cfg, model_cfg):
+            if cfg.get("sequence_len", 0) > 8:
+                raise ValueError("toy_arch: sequence_len above 8")
+
+    try:
+        sup = R.get_model_support("toy_arch")
+        with caplog.at_level(logging.WARNING):
+            R.check_capability(sup, R.CP, "toy_arch", feature="context parallelism")
+            R.check_capability(sup, R.CP, "toy_arch", feature="context parallelism")      # said once
+        assert sum("experimental for model_type=toy_arch" in r.getMessage() for r in caplog.records) == 1
+        with pytest.raises(ValueError, match="No sharding rule"):
+            R.check_capability(sup, R.TP, "toy_arch")
+        R.check_capability(sup, "something_unknown", "toy_arch")                          # unknown: generic path
+
+        class MC:
+            model_type, num_experts, head_dim = "toy_arch", 0, 32
+        with pytest.raises(ValueError, match="above 8"):
+            R.validate_cfg({"sequence_len": 16}, MC())
+        with pytest.raises(ValueError):
+            type("Bad", (R.ModelSupport,), {}) and R.register_model_support(type("Bad", (R.ModelSupport,), {}))
+    finally:
+        R._REGISTRY.pop("toy_arch", None)
 
 
 def test_compat_plugins_act_on_their_keys(monkeypatch, caplog):

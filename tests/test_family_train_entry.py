@@ -1,0 +1,74 @@
+"""The training entry point (config validation -> architecture descriptor -> model build -> adapter -> trainer) on a
+small random checkpoint of the newer model families: the path a user takes, not just the model graph."""
+import pytest
+import torch
+
+from axolotl_b200.config.load import load_cfg
+from axolotl_b200.io import hf as hf_io
+from axolotl_b200.models.config import ModelConfig
+from axolotl_b200.models.transformer import CausalLM
+from axolotl_b200.train.run import train
+
+FAMILIES = {
+    "gemma2": dict(model_type="gemma2", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                   num_attention_heads=4, num_key_value_heads=2, head_dim=16, query_pre_attn_scalar=16, sliding_window=32,
+                   max_position_embeddings=256),
+    "falcon_h1": dict(model_type="falcon_h1", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, mamba_d_ssm=96, mamba_n_heads=8, mamba_d_head=12,
+                      mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_chunk_size=8, mamba_rms_norm=True,
+                      mamba_norm_before_gate=False, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256,
+                      ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3], mlp_multipliers=[0.8, 1.4], key_multiplier=0.8),
+    "glm_moe_dsa": dict(model_type="glm_moe_dsa", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4, n_shared_experts=1,
+                        num_experts_per_tok=2, mlp_layer_types=["dense", "sparse"], q_lora_rank=24, kv_lora_rank=16,
+                        qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=12, index_topk=12, index_head_dim=16, index_n_heads=4,
+                        max_position_embeddings=256, tie_word_embeddings=False),
+    "qwen3_next": dict(model_type="qwen3_next", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2,
+                       linear_key_head_dim=8, linear_value_head_dim=8, linear_conv_kernel_dim=4, num_experts=4,
+                       num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+                       max_position_embeddings=256, tie_word_embeddings=False),
+    "deepseek_v3": dict(model_type="deepseek_v3", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4, n_shared_experts=1,
+                        num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
+                        qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=12, max_position_embeddings=256,
+                        tie_word_embeddings=False),
+    "granitemoehybrid": dict(model_type="granitemoehybrid", vocab_size=320, hidden_size=64, intermediate_size=48,
+                             shared_intermediate_size=96, num_hidden_layers=3, layer_types=["mamba", "attention", "mamba"],
+                             num_attention_heads=4, num_key_value_heads=2, mamba_n_heads=8, mamba_d_head=16, mamba_n_groups=2,
+                             mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8, num_local_experts=4,
+                             num_experts_per_tok=2, position_embedding_type="nope", tie_word_embeddings=True,
+                             embedding_multiplier=3.0, attention_multiplier=0.2, residual_multiplier=0.5, logits_scaling=2.0,
+                             max_position_embeddings=256),
+    "llama4_text": dict(model_type="llama4_text", vocab_size=320, hidden_size=64, intermediate_size=48, intermediate_size_mlp=96,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4,
+                        num_experts_per_tok=1, interleave_moe_layer_step=2, no_rope_layers=[1, 1, 1, 0], attention_chunk_size=16,
+                        floor_scale=8, attn_scale=0.1, tie_word_embeddings=False, max_position_embeddings=256,
+                        layer_types=["chunked_attention", "chunked_attention", "chunked_attention", "full_attention"]),
+    "nemotron_h": dict(model_type="nemotron_h", vocab_size=320, hidden_size=64, layers_block_type=["mamba", "attention", "mlp", "mamba"],
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=96, mlp_hidden_act="relu2",
+                       ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=12, n_groups=2, conv_kernel=4, chunk_size=8,
+                       tie_word_embeddings=False, max_position_embeddings=256),
+    "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
+                    sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,
+                    max_position_embeddings=256, attention_bias=True, swiglu_limit=7.0),
+}
+
+
+@pytest.mark.parametrize("family", sorted(FAMILIES))
+def test_lora_training_run_from_a_checkpoint_directory(tmp_path, family):
+    mc = ModelConfig.from_hf_dict(FAMILIES[family])
+    hf_io.save_pretrained(CausalLM(mc, dtype=torch.float32).init_weights(1), str(tmp_path / "base"))
+    cfg = load_cfg({"base_model": str(tmp_path / "base"), "adapter": "lora", "lora_r": 4, "lora_alpha": 8, "lora_target_linear": True,
+                    "sequence_len": 128, "micro_batch_size": 1, "gradient_accumulation_steps": 1, "max_steps": 3,
+                    "learning_rate": 2e-3, "lr_scheduler": "constant", "output_dir": str(tmp_path / "out"), "device": "cpu",
+                    "sample_packing": True, "save_strategy": "no", "logging_steps": 1,
+                    "datasets": [{"path": "synthetic", "type": "_synthetic", "length": 12, "min_length": 20, "max_length": 60,
+                                  "max_input_id": 300}]})
+    model, _, trainer = train(cfg)
+    assert trainer.global_step == 3
+    losses = [h["loss"] for h in trainer.log_history if "loss" in h]
+    assert all(l == l and l < 20 for l in losses), losses          # finite
+    trained = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert trained and all("lora" in n for n in trained), trained[:5]

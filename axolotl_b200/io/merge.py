@@ -80,6 +80,8 @@ def merge_tensor(name: str, w: torch.Tensor, cfg: dict, pairs: dict, shard: dict
     """Merged replacement for checkpoint tensor ``name`` or None when no adapter targets it."""
     if name.endswith(".weight"):
         mod = name[: -len(".weight")]
+        if mod not in pairs and mod.startswith("backbone."):      # Nemotron-H checkpoints of either prefix generation
+            mod = "model." + mod[len("backbone."):]
         if mod in pairs and "A" in pairs[mod] and "B" in pairs[mod]:
             if cfg.get("fan_in_fan_out"):
                 return (w.float() + _delta(pairs[mod], _adapter_scale(cfg, mod)).t()).to(w.dtype)

@@ -75,10 +75,82 @@ class LoraSpec:
             return cls.from_peft_dict(json.load(fh))
 
 
-def _hf_path(fused_name: str, sub: str) -> str:
-    """'layers.3.self_attn.qkv_proj' + 'q_proj' -> 'model.layers.3.self_attn.q_proj'."""
+def _checkpoint_renames(model):
+    """Where a family's checkpoint names its modules differently from this graph, (internal prefix, checkpoint
+    prefix) pairs: adapters are saved under the CHECKPOINT's module names, so that PEFT and the merge tools find them."""
+    cached = model.__dict__.get("_axb_hf_renames")
+    if cached is not None:
+        return cached
+    mt = getattr(getattr(model, "config", None), "model_type", "")
+    pairs = []
+    for i, layer in enumerate(getattr(model, "layers", [])):
+        pre = f"model.layers.{i}"
+        mixer = type(getattr(layer, "self_attn", None)).__name__
+        if mt in ("bamba", "granitemoehybrid") and mixer == "Mamba2Mixer":
+            pairs.append((f"{pre}.self_attn.", f"{pre}.mamba."))
+        if mt == "qwen3_next" and mixer == "GatedDeltaNet":
+            pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
+        if mt in ("bamba", "falcon_h1"):
+            pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
+        if mt == "llama4_text":
+            pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.feed_forward.shared_expert."))
+            pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
+        if mt == "granitemoehybrid":
+            for inner in ("mlp.shared_experts", "mlp"):
+                pairs.append((f"{pre}.{inner}.gate_up_proj", f"{pre}.shared_mlp.input_linear"))
+                pairs.append((f"{pre}.{inner}.down_proj", f"{pre}.shared_mlp.output_linear"))
+    model.__dict__["_axb_hf_renames"] = pairs
+    return pairs
+
+
+def _hf_path(fused_name: str, sub: str, model=None) -> str:
+    """'layers.3.self_attn.qkv_proj' + 'q_proj' -> 'model.layers.3.self_attn.q_proj' (in the checkpoint's own module
+    names when ``model`` is given)."""
     parent = fused_name.rsplit(".", 1)[0]
-    return f"model.{parent}.{sub}"
+    path = f"model.{parent}.{sub}"
+    if model is not None:
+        for src, dst in _checkpoint_renames(model):
+            if path.startswith(src):
+                return dst + path[len(src):]
+    return path
+
+
+def _B_rows_layout(model, name, sub, B, to_checkpoint: bool):
+    """Output rows of an adapter's B in the CHECKPOINT's row order / count for the projections this graph stores
+    differently: Llama 4 keeps rotary pairs interleaved in q / k (rows are permuted here), Qwen3-Next's q_proj carries
+    the output-gate rows head by head (they get zero rows on the way out and are dropped on the way in)."""
+    mt = getattr(getattr(model, "config", None), "model_type", "")
+    if mt == "llama4_text" and sub in ("q_proj", "k_proj") and ".self_attn." in name:
+        cfg = model.config
+        heads = cfg.num_attention_heads if sub == "q_proj" else cfg.num_key_value_heads
+        idx = torch.cat([torch.arange(0, cfg.head_dim, 2), torch.arange(1, cfg.head_dim, 2)])
+        if to_checkpoint:
+            idx = torch.argsort(idx)
+        return B.reshape(heads, cfg.head_dim, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
+    if mt == "qwen3_next" and sub == "q_proj" and ".self_attn." in name:
+        cfg = model.config
+        H, D = cfg.num_attention_heads, cfg.head_dim
+        if to_checkpoint:
+            if B.shape[0] != H * D:
+                return B
+            return torch.stack([B.reshape(H, D, -1), torch.zeros(H, D, B.shape[-1], dtype=B.dtype, device=B.device)], 1) \
+                .reshape(2 * H * D, -1)
+        if B.shape[0] == 2 * H * D:
+            return B.reshape(H, 2, D, -1)[:, 0].reshape(H * D, -1)
+    return B
+
+
+# projections that `lora_target_linear` leaves alone: the sparse-attention indexer is not differentiated, and the
+# attention output gate of Qwen3-Next lives inside q_proj in the checkpoint (no module of its own to attach to)
+_NOT_AUTO_TARGETS = ("wq_b", "wk", "weights_proj", "q_gate")
+
+
+def discover_linear_names(model) -> list[str]:
+    """Leaf names of every projection in the decoder layers (what PEFT's ``all-linear`` finds on the HF graph)."""
+    names = set()
+    for _, m in model.fused_linears():
+        names.update(n for n in m.names if n not in _NOT_AUTO_TARGETS)
+    return sorted(names)
 
 
 def _matches(spec: LoraSpec, hf_path: str, sub: str, layer_idx: int | None) -> bool:
@@ -103,15 +175,15 @@ def inject_lora(model, spec: LoraSpec, freeze_base: bool = True, adapter_dtype=t
     for name, m in model.fused_linears():
         mt = re.search(r"layers\.(\d+)\.", name)
         li = int(mt.group(1)) if mt else None
-        targets = [s for s in m.names if _matches(spec, _hf_path(name, s), s, li)]
+        targets = [s for s in m.names if _matches(spec, _hf_path(name, s, model), s, li)]
         if targets:
             r = spec.r
             for pat, rv in spec.rank_pattern.items():
-                if any(re.search(pat, _hf_path(name, s)) for s in targets):
+                if any(re.search(pat, _hf_path(name, s, model)) for s in targets):
                     r = rv
             alpha = spec.lora_alpha
             for pat, av in spec.alpha_pattern.items():
-                if any(re.search(pat, _hf_path(name, s)) for s in targets):
+                if any(re.search(pat, _hf_path(name, s, model)) for s in targets):
                     alpha = av
             if spec.use_mora:
                 if not isinstance(m, FusedLinear) or getattr(m.weight, "_axb_quant", None) is not None:
@@ -184,14 +256,14 @@ def get_peft_state_dict(model) -> dict:
     for name, m in model.fused_linears():
         if getattr(m, "mora_M", None) is not None:   # the MoRA fork keeps the square matrix under lora_A
             for sub, M in zip(m.mora_names, m.mora_M):
-                sd[f"base_model.model.{_hf_path(name, sub)}.lora_A.weight"] = M.detach()
+                sd[f"base_model.model.{_hf_path(name, sub, model)}.lora_A.weight"] = M.detach()
         if m.lora_A is None:
             continue
         tensors = m.gathered_peft_tensors() if hasattr(m, "gathered_peft_tensors") else m.peft_tensors()
         for sub, (A, B) in tensors.items():
-            base = f"base_model.model.{_hf_path(name, sub)}"
+            base = f"base_model.model.{_hf_path(name, sub, model)}"
             sd[f"{base}.lora_A.weight"] = A.detach()
-            sd[f"{base}.lora_B.weight"] = B.detach()
+            sd[f"{base}.lora_B.weight"] = _B_rows_layout(model, name, sub, B.detach(), True)
             if getattr(m, "dora_magnitude", None) is not None:
                 r0, r1 = m.row_range(sub)
                 sd[f"{base}.lora_magnitude_vector"] = m.dora_magnitude.detach()[r0:r1]
@@ -219,7 +291,7 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
     for name, m in model.fused_linears():
         if getattr(m, "mora_M", None) is not None:
             for sub, M in zip(m.mora_names, m.mora_M):
-                k = f"base_model.model.{_hf_path(name, sub)}.lora_A.weight"
+                k = f"base_model.model.{_hf_path(name, sub, model)}.lora_A.weight"
                 if k in norm:
                     with torch.no_grad():
                         M.copy_(norm[k])
@@ -230,10 +302,11 @@ def set_peft_state_dict(model, sd: dict, strict: bool = True):
         if m.lora_A is None:
             continue
         for sub in m.lora_names:
-            base = f"base_model.model.{_hf_path(name, sub)}"
+            base = f"base_model.model.{_hf_path(name, sub, model)}"
             ka, kb = f"{base}.lora_A.weight", f"{base}.lora_B.weight"
             if ka in norm and kb in norm:
-                m.load_peft_tensors(sub, norm[ka].to(m.lora_A.device), norm[kb].to(m.lora_B.device))
+                m.load_peft_tensors(sub, norm[ka].to(m.lora_A.device),
+                                    _B_rows_layout(model, name, sub, norm[kb], False).to(m.lora_B.device))
                 used.update((ka, kb))
                 for km in (f"{base}.lora_magnitude_vector", f"{base}.lora_magnitude_vector.weight"):
                     if km in norm and getattr(m, "dora_magnitude", None) is not None:

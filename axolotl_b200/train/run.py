@@ -123,6 +123,11 @@ def setup_adapter(cfg, model):
         saved = quantize_base_nf4_(model, double_quant=qcfg.get("bnb_4bit_use_double_quant", True) is not False)
         LOG.info("base projections stored as NF4: %.2f GiB saved", saved / 1024 ** 3)
     adapter_dtype = torch.float32 if cfg.get("peft_autocast_adapter_dtype", True) is not False else model.dtype
+    if cfg.get("lora_target_linear") and isinstance(spec.target_modules, (list, tuple)):
+        from ..models.lora import discover_linear_names
+
+        # every projection of THIS architecture (latent-attention bottlenecks, state-space in/out projections ...)
+        spec.target_modules = sorted(set(spec.target_modules) | set(discover_linear_names(model)))
     n = inject_lora(model, spec, adapter_dtype=adapter_dtype)
     if cfg.get("lora_model_dir"):
         load_adapter(model, cfg["lora_model_dir"])

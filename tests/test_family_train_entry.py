@@ -72,3 +72,40 @@ def test_lora_training_run_from_a_checkpoint_directory(tmp_path, family):
     assert all(l == l and l < 20 for l in losses), losses          # finite
     trained = [n for n, p in model.named_parameters() if p.requires_grad]
     assert trained and all("lora" in n for n in trained), trained[:5]
+
+
+@pytest.mark.parametrize("family", sorted(FAMILIES))
+def test_adapter_save_and_sharded_merge_reproduce_the_adapted_model(tmp_path, family):
+    """adapter_model.safetensors in the checkpoint's own tensor names -> shard-by-shard merge -> same logits."""
+    from axolotl_b200.io.merge import merge_lora_sharded
+    from axolotl_b200.models.lora import LoraSpec, discover_linear_names, inject_lora, save_adapter
+
+    mc = ModelConfig.from_hf_dict(FAMILIES[family])
+    model = CausalLM(mc, dtype=torch.float32).init_weights(2)
+    hf_io.save_pretrained(model, str(tmp_path / "base"))
+    names = discover_linear_names(model)
+    assert "o_proj" in names and "weights_proj" not in names
+    spec = LoraSpec(r=4, lora_alpha=8, target_modules=names)
+    inject_lora(model, spec)
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "lora_B" in n:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.05)
+        for _, m in model.fused_linears():
+            if getattr(m, "lora_B", None) is not None:          # keep the block-diagonal structure of fused projections
+                keep = torch.zeros_like(m.lora_B)
+                for (r0, rows, c0, r) in m.lora_blocks:
+                    keep[r0:r0 + rows, c0:c0 + r] = 1
+                m.lora_B.mul_(keep)
+    save_adapter(model, spec, str(tmp_path / "ad"))
+    ids = torch.randint(3, 300, (1, 40))
+    model.eval()
+    with torch.no_grad():
+        want = model(ids, return_logits=True).logits
+    res = merge_lora_sharded(str(tmp_path / "base"), str(tmp_path / "ad"), str(tmp_path / "merged"))
+    assert res["unmatched"] == [], res["unmatched"][:5]
+    merged = hf_io.load_pretrained(str(tmp_path / "merged"), dtype=torch.float32).eval()
+    with torch.no_grad():
+        got = merged(ids, return_logits=True).logits
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()

@@ -48,7 +48,10 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     qwen3_next = getattr(model.config, "model_type", "") == "qwen3_next"
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
+    glm = getattr(model.config, "model_type", "") in ("glm", "glm4")
     for name, t in named_tensors:
+        if glm:
+            name, t = _glm_in(model, name, t)
         if llama4:
             name, t = _llama4_in(model, name, t)
         if qwen3_next:
@@ -98,6 +101,8 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             parent, sub, kind = sp
             fused = _FUSED_OF[sub]
             if fused == "qkv_proj" and f"{parent}.qkv_proj" not in mods:      # latent attention: a lone q_proj
+                fused = sub
+            if fused == "gate_up_proj" and f"{parent}.gate_up_proj" not in mods:   # ungated MLP: a lone up_proj
                 fused = sub
             fl: FusedLinear = mods[f"{parent}.{fused}"]
             r0, r1 = fl.row_range(sub)
@@ -314,6 +319,50 @@ def _deinterleave_rows(w, heads, D, inverse=False):
     if inverse:
         idx = torch.argsort(idx)
     return w.reshape(heads, D, *w.shape[1:]).index_select(1, idx.to(w.device)).reshape(w.shape)
+
+
+def _rotary_rows(w, heads, D, rot, inverse=False):
+    """The first ``rot`` rows of every head: interleaved (real, imaginary) pairs <-> half-split layout."""
+    idx = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, D)])
+    if inverse:
+        idx = torch.argsort(idx)
+    return w.reshape(heads, D, *w.shape[1:]).index_select(1, idx.to(w.device)).reshape(w.shape)
+
+
+_GLM4_NORMS = ((".post_self_attn_layernorm.", ".post_attention_layernorm."), (".post_attention_layernorm.", ".pre_feedforward_layernorm."),
+               (".post_mlp_layernorm.", ".post_feedforward_layernorm."))
+
+
+def _glm_in(model, name, t):
+    """GLM checkpoints: rotary pairs of q / k stored as neighbours (rows are permuted); GLM-4 names its four norms
+    `input`, `post_self_attn` (attention output), `post_attention` (MLP input), `post_mlp` (MLP output)."""
+    cfg = model.config
+    if cfg.model_type == "glm4":
+        for src, dst in _GLM4_NORMS:
+            if src in name:
+                name = name.replace(src, dst)
+                break
+    m = re.search(r"\.self_attn\.(q|k)_proj\.(weight|bias)$", name)
+    if m:
+        heads = cfg.num_attention_heads if m.group(1) == "q" else cfg.num_key_value_heads
+        t = _rotary_rows(t, heads, cfg.head_dim, cfg.rope_dim())
+    return name, t
+
+
+def _glm_out(model, sd):
+    cfg, out = model.config, {}
+    for name, t in sd.items():
+        m = re.search(r"\.self_attn\.(q|k)_proj\.(weight|bias)$", name)
+        if m:
+            heads = cfg.num_attention_heads if m.group(1) == "q" else cfg.num_key_value_heads
+            t = _rotary_rows(t, heads, cfg.head_dim, cfg.rope_dim(), inverse=True)
+        if cfg.model_type == "glm4":
+            for dst, src in reversed(_GLM4_NORMS):
+                if src in name:
+                    name = name.replace(src, dst)
+                    break
+        out[name] = t
+    return out
 
 
 def _llama4_in(model, name, t):
@@ -578,6 +627,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
         return _llama4_out(model, sd)
     if getattr(model.config, "model_type", "") == "qwen3_next":
         return _qwen3_next_out(model, sd)
+    if getattr(model.config, "model_type", "") in ("glm", "glm4"):
+        return _glm_out(model, sd)
     return sd
 
 

@@ -14,7 +14,8 @@ from dataclasses import asdict, dataclass, field
 from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
-                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa")
+                         "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
+                         "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
@@ -64,7 +65,7 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
-        if self.model_type in ("gemma3_text", "qwen3_next"):
+        if self.model_type in ("gemma3_text", "qwen3_next", "olmo2", "olmo3"):
             self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -151,6 +152,21 @@ class ModelConfig:
             if not d.get("rope_scaling") and not d.get("rope_parameters"):     # the family's default: YaRN x32 over 4096
                 d["rope_scaling"] = {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
                                      "truncate": False, "original_max_position_embeddings": 4096}
+        if mt in ("glm", "glm4"):      # half of every head rotates, pairs stored as neighbours; fused gate|up; q/k/v biases
+            d.setdefault("partial_rotary_factor", 0.5)
+            d.setdefault("attention_bias", True)
+            d.setdefault("rms_norm_eps", 1.5625e-07)
+        if mt in ("olmo2", "olmo3"):   # norms on the branch OUTPUTS only, q/k norms over all heads
+            d["qk_norm"] = True
+            d.setdefault("rms_norm_eps", 1e-5)
+            if mt == "olmo3" and not d.get("layer_types"):
+                L = d.get("num_hidden_layers", 0)
+                d["layer_types"] = ["sliding_attention" if (i + 1) % 4 else "full_attention" for i in range(L)]
+        if mt == "seed_oss":
+            d.setdefault("attention_bias", True)
+            d.setdefault("attention_out_bias", False)
+        if mt == "arcee":
+            d.setdefault("hidden_act", "relu2")
         if mt == "glm_moe_dsa":        # GLM-5: DeepSeek-V3 style latent attention + routing, plus the sparse-attention indexer
             L = d.get("num_hidden_layers", 0)
             for key, default in (("qk_nope_head_dim", 192), ("qk_rope_head_dim", 64), ("v_head_dim", 256), ("kv_lora_rank", 512),
@@ -283,8 +299,17 @@ class ModelConfig:
         return 1.0 if self.model_type in ZERO_CENTERED_NORM_TYPES else 0.0
 
     def sandwich_norms(self) -> bool:
-        """Gemma 2 / 3 normalise the output of the attention and MLP branches too (four norms per layer)."""
-        return self.model_type in ("gemma2", "gemma3_text")
+        """Gemma 2 / 3 and GLM-4 normalise the output of the attention and MLP branches too (four norms per layer)."""
+        return self.model_type in ("gemma2", "gemma3_text", "glm4")
+
+    def post_norm_only(self) -> bool:
+        """OLMo 2 / 3: no norm on a branch's input, one on its output."""
+        return self.model_type in ("olmo2", "olmo3")
+
+    def rope_pairs_interleaved(self) -> bool:
+        """GLM checkpoints store the rotated part of every head with (real, imaginary) neighbours; the rows of q / k are
+        permuted to the half-split layout at load (scores do not change when q and k share the permutation)."""
+        return self.model_type in ("glm", "glm4")
 
     def attn_softcap(self) -> float:
         v = (self.extra or {}).get("attn_logit_softcapping") if self.model_type == "gemma2" else None
@@ -327,6 +352,11 @@ class ModelConfig:
                 return int(w) if idx % 2 == 0 else 0          # even layers slide
             pat = ex.get("sliding_window_pattern") or 6
             return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
+        if self.model_type == "olmo3":
+            types = ex.get("layer_types")
+            if idx is None or not types:
+                return int(w)
+            return int(w) if types[idx] == "sliding_attention" else 0
         if self.model_type in ("qwen2", "qwen2_moe", "qwen3", "qwen3_moe", "smollm3"):
             if not ex.get("use_sliding_window"):
                 return 0
@@ -513,6 +543,12 @@ _ARCH_NAME = {
     "nemotron_h": "NemotronHForCausalLM",
     "falcon_h1": "FalconH1ForCausalLM",
     "glm_moe_dsa": "GlmMoeDsaForCausalLM",
+    "glm": "GlmForCausalLM",
+    "glm4": "Glm4ForCausalLM",
+    "olmo2": "Olmo2ForCausalLM",
+    "olmo3": "Olmo3ForCausalLM",
+    "seed_oss": "SeedOssForCausalLM",
+    "arcee": "ArceeForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
 }
 

@@ -127,6 +127,13 @@ def _B_rows_layout(model, name, sub, B, to_checkpoint: bool):
         if to_checkpoint:
             idx = torch.argsort(idx)
         return B.reshape(heads, cfg.head_dim, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
+    if mt in ("glm", "glm4") and sub in ("q_proj", "k_proj") and ".self_attn." in name:
+        cfg = model.config
+        heads, D, rot = (cfg.num_attention_heads if sub == "q_proj" else cfg.num_key_value_heads), cfg.head_dim, cfg.rope_dim()
+        idx = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, D)])
+        if to_checkpoint:
+            idx = torch.argsort(idx)
+        return B.reshape(heads, D, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
     if mt == "qwen3_next" and sub == "q_proj" and ".self_attn." in name:
         cfg = model.config
         H, D = cfg.num_attention_heads, cfg.head_dim

@@ -114,7 +114,12 @@ def _register(name, types, caps, head_dims=(64, 128), notes=(), validate=None):
     return register_model_support(type(name, (ModelSupport,), body))
 
 
-_register("LlamaLike", ("llama", "qwen2", "qwen3"), _DENSE)
+_register("LlamaLike", ("llama", "qwen2", "qwen3", "seed_oss"), _DENSE)
+_register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's fused gate|up projection is kept fused.")},
+          notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))
+_register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms span all heads of the unsharded projection.")},
+          notes=("norms sit on the branch outputs; q / k RMSNorm over all heads runs as separate launches before RoPE",))
+_register("Arcee", ("arcee",), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
 _register("Mistral", ("mistral",), _DENSE,
           notes=("sliding_window is applied by the attention kernels (not with context parallelism)",))
 _register("Phi3", ("phi3",), {**_DENSE, TP: Unsupported("The checkpoint's fused projections are kept fused.")},

@@ -48,8 +48,9 @@ class Attention(nn.Module):
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
-        self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=cfg.model_type == "gpt_oss" and cfg.attention_bias,
-                                  dtype=dtype, device=device)
+        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3")
+                  else bool((cfg.extra or {}).get("attention_out_bias")) if cfg.model_type == "seed_oss" else False)
+        self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=o_bias, dtype=dtype, device=device)
         # gpt-oss: one learned "sink" logit per head in every softmax denominator
         self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if cfg.model_type == "gpt_oss" else None
         # Qwen3-Next: the attention output is multiplied by sigmoid(gate(x)) before the output projection (the checkpoint
@@ -59,7 +60,7 @@ class Attention(nn.Module):
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
-        self.full_qk_norm = cfg.model_type == "olmoe"   # OLMoE normalises q and k over ALL heads at once
+        self.full_qk_norm = cfg.model_type in ("olmoe", "olmo2", "olmo3")   # OLMo family: q / k norms over ALL heads at once
         if self.full_qk_norm:
             self.q_norm = RMSNorm(self.Hq * self.D, cfg.rms_norm_eps, dtype, device)
             self.k_norm = RMSNorm(self.Hk * self.D, cfg.rms_norm_eps, dtype, device)
@@ -296,6 +297,10 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
         # Gemma 2 / 3: post_attention_layernorm and post_feedforward_layernorm act on the BRANCH outputs,
         # pre_feedforward_layernorm takes the place the post-attention norm has elsewhere
+        self.post_norm_only = cfg.post_norm_only()     # OLMo 2 / 3: branches read the stream itself, norms on their outputs
+        if self.post_norm_only:
+            del self.input_layernorm
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.sandwich = cfg.sandwich_norms()
         if self.sandwich:
             self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
@@ -310,13 +315,22 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type == "granitemoehybrid":     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
+        elif cfg.model_type == "arcee":                # up -> squared ReLU -> down, no gate
+            self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
-                           fused_names=cfg.model_type == "phi3")
+                           fused_names=cfg.model_type in ("phi3", "glm", "glm4"))
         self.is_moe = cfg.is_moe_layer(idx)
 
+    def _stream(self, h, residual):
+        """(input of the attention branch, residual stream)."""
+        if self.post_norm_only:
+            x = h if residual is None else h + residual
+            return x, x
+        return self.input_layernorm(h, residual)
+
     def _before_attention(self, h, residual, positions, inv_freq, attn_scale):
-        x, residual = self.input_layernorm(h, residual)
+        x, residual = self._stream(h, residual)
         return self.self_attn.pre(x, positions, inv_freq, attn_scale), residual
 
     def _after_attention(self, a, residual):
@@ -327,6 +341,9 @@ class DecoderLayer(nn.Module):
         rm = self.residual_multiplier
         if rm != 1.0:
             a = a * rm
+        if self.post_norm_only:
+            x = residual + self.post_attention_layernorm.plain(a)
+            return self.post_feedforward_layernorm.plain(self.mlp(x)), x, None
         if self.sandwich:
             a = self.post_attention_layernorm.plain(a)
             x, residual = self.pre_feedforward_layernorm(a, residual)
@@ -354,7 +371,7 @@ class DecoderLayer(nn.Module):
         return checkpoint(self._after_attention, a, residual, use_reentrant=False)
 
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
-        x, residual = self.input_layernorm(h, residual)
+        x, residual = self._stream(h, residual)
         return self._mlp_half(self.self_attn(x, positions, inv_freq, attn_scale, meta), residual)
 
 

@@ -49,6 +49,15 @@ FAMILIES = {
                        num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=96, mlp_hidden_act="relu2",
                        ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=12, n_groups=2, conv_kernel=4, chunk_size=8,
                        tie_word_embeddings=False, max_position_embeddings=256),
+    "glm4": dict(model_type="glm4", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, tie_word_embeddings=False,
+                 max_position_embeddings=256),
+    "olmo3": dict(model_type="olmo3", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                  num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False, max_position_embeddings=256,
+                  sliding_window=8, layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "arcee": dict(model_type="arcee", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, head_dim=16, hidden_act="relu2", tie_word_embeddings=False,
+                  max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

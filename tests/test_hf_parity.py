@@ -816,3 +816,55 @@ def test_qwen3_next_gated_deltanet_and_gated_attention_match_hf(tmp_path):
     ours.train()
     ours(ids, pos, ids.clone()).loss.backward()
     assert ours.layers[0].self_attn.A_log.grad is not None and ours.layers[3].self_attn.out_gate.weight.grad.abs().sum() > 0
+
+
+LLAMA_LIKE = {
+    "glm": dict(model_type="glm", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, rms_norm_eps=1e-5,
+                tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "glm4": dict(model_type="glm4", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, rms_norm_eps=1e-5,
+                 tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "olmo2": dict(model_type="olmo2", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                  max_position_embeddings=256, attention_bias=False, pad_token_id=0),
+    "olmo3": dict(model_type="olmo3", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                  num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                  max_position_embeddings=256, attention_bias=False, pad_token_id=0, sliding_window=8,
+                  layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "seed_oss": dict(model_type="seed_oss", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=24, attention_bias=True, attention_out_bias=True,
+                     rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0,
+                     residual_dropout=0.0, attention_dropout=0.0),
+    "arcee": dict(model_type="arcee", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, head_dim=16, hidden_act="relu2", rms_norm_eps=1e-5,
+                  tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+}
+
+
+@pytest.mark.parametrize("family", sorted(LLAMA_LIKE))
+def test_llama_like_variants_match_hf(tmp_path, family):
+    """GLM / GLM-4 (interleaved partial rotary, fused gate|up, four norms), OLMo 2 / 3 (norms on the branch outputs, q / k
+    norms over all heads, sliding layers), Seed-OSS (biases incl. the output projection), Arcee (ungated squared-ReLU MLP)."""
+    cfg = ModelConfig.from_hf_dict(LLAMA_LIKE[family])
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(47)
+    with torch.no_grad():
+        for n, p in ours.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.1)
+            if "norm" in n and n.endswith("weight"):
+                p.uniform_(0.5, 1.5)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [23, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)

@@ -48,8 +48,11 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     qwen3_next = getattr(model.config, "model_type", "") == "qwen3_next"
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
-    glm = getattr(model.config, "model_type", "") in ("glm", "glm4")
+    glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
+    hunyuan = getattr(model.config, "model_type", "") == "hunyuan_v1_dense"
     for name, t in named_tensors:
+        if hunyuan:
+            name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.")
         if glm:
             name, t = _glm_in(model, name, t)
         if llama4:
@@ -550,9 +553,11 @@ def _granite_hybrid_state_dict(model, sd):
                     r0, r1 = fl.row_range(sub)
                     sd[f"{pre}.self_attn.{sub}.weight"] = fl.weight.detach()[r0:r1]
         mlp = layer.mlp
-        shared = mlp.shared_experts if getattr(mlp, "shared_experts", None) is not None else mlp
-        sd[f"{pre}.shared_mlp.input_linear.weight"] = shared.gate_up_proj.weight.detach()
-        sd[f"{pre}.shared_mlp.output_linear.weight"] = shared.down_proj.weight.detach()
+        is_moe = isinstance(getattr(mlp, "experts", None), Experts)
+        shared = getattr(mlp, "shared_experts", None) if is_moe else mlp
+        if shared is not None:
+            sd[f"{pre}.shared_mlp.input_linear.weight"] = shared.gate_up_proj.weight.detach()
+            sd[f"{pre}.shared_mlp.output_linear.weight"] = shared.down_proj.weight.detach()
         if isinstance(getattr(mlp, "experts", None), Experts):
             sd[f"{pre}.block_sparse_moe.input_linear.weight"] = mlp.experts.gate_up_proj.detach()
             sd[f"{pre}.block_sparse_moe.output_linear.weight"] = mlp.experts.down_proj.detach()
@@ -566,7 +571,7 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     if model.lm_head is not None:
         sd["lm_head.weight"] = model.lm_head.detach()
     gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
-    if getattr(model.config, "model_type", "") == "granitemoehybrid":
+    if getattr(model.config, "model_type", "") in ("granitemoe", "granitemoeshared", "granitemoehybrid"):
         return _granite_hybrid_state_dict(model, sd)
     if getattr(model.config, "model_type", "") in ("bamba", "falcon_h1"):
         return _bamba_state_dict(model, sd)
@@ -627,8 +632,10 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
         return _llama4_out(model, sd)
     if getattr(model.config, "model_type", "") == "qwen3_next":
         return _qwen3_next_out(model, sd)
-    if getattr(model.config, "model_type", "") in ("glm", "glm4"):
+    if model.config.rope_pairs_interleaved():
         return _glm_out(model, sd)
+    if getattr(model.config, "model_type", "") == "hunyuan_v1_dense":
+        return {k.replace(".q_norm.", ".query_layernorm.").replace(".k_norm.", ".key_layernorm."): v for k, v in sd.items()}
     return sd
 
 

@@ -15,9 +15,11 @@ from typing import Any
 
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
-                         "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee")
+                         "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
+                         "granitemoe", "granitemoeshared")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
+GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
 ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
 
 
@@ -136,7 +138,18 @@ class ModelConfig:
                 d["mamba_d_head"] = int((d.get("mamba_expand") or 2) * d["hidden_size"]) // int(d.get("mamba_n_heads") or 128)
             rp = d.get("rope_parameters") or {}
             d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))
-        if mt == "granitemoehybrid":
+        if mt == "glm4_moe":           # Llama-style attention (optional per-head q/k norms, half of a head rotates) + DeepSeek-V3 routing
+            d["num_experts"] = d.get("n_routed_experts") or 0
+            d.setdefault("norm_topk_prob", True)
+            d.setdefault("partial_rotary_factor", 0.5)
+            d["qk_norm"] = bool(d.get("use_qk_norm", False))
+            k1 = d.get("first_k_dense_replace") or 0
+            d["mlp_only_layers"] = [i for i in range(d.get("num_hidden_layers", 0)) if i < k1]
+        if mt == "ernie4_5":
+            d["attention_bias"] = d["mlp_bias"] = bool(d.get("use_bias", False))
+        if mt == "hunyuan_v1_dense":
+            d["qk_norm"] = True        # per head, AFTER the rotary embedding
+        if mt in GRANITE_MOE_TYPES:
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0     # width of a routed expert
             d.setdefault("norm_topk_prob", True)
@@ -239,7 +252,14 @@ class ModelConfig:
             d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
-        if self.model_type == "granitemoehybrid":
+        if self.model_type == "glm4_moe":
+            d["n_routed_experts"] = d.pop("num_experts")
+            d["use_qk_norm"] = bool(self.qk_norm)
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
+        if self.model_type == "ernie4_5":
+            d["use_bias"] = bool(self.attention_bias)
+        if self.model_type in GRANITE_MOE_TYPES:
             d["num_local_experts"] = d.pop("num_experts")
             d["intermediate_size"] = d.pop("moe_intermediate_size") or extra.get("intermediate_size") or d.get("intermediate_size")
         if self.model_type == "glm_moe_dsa":
@@ -288,7 +308,7 @@ class ModelConfig:
             if name == "logits_scaling":
                 return 1.0 / float(ex.get("lm_head_multiplier") or 1.0)
             return 1.0
-        if self.model_type not in ("granite", "granitemoehybrid"):
+        if self.model_type not in ("granite",) + GRANITE_MOE_TYPES:
             return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         default = 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         v = (self.extra or {}).get(name)
@@ -309,7 +329,7 @@ class ModelConfig:
     def rope_pairs_interleaved(self) -> bool:
         """GLM checkpoints store the rotated part of every head with (real, imaginary) neighbours; the rows of q / k are
         permuted to the half-split layout at load (scores do not change when q and k share the permutation)."""
-        return self.model_type in ("glm", "glm4")
+        return self.model_type in ("glm", "glm4", "ernie4_5")
 
     def attn_softcap(self) -> float:
         v = (self.extra or {}).get("attn_logit_softcapping") if self.model_type == "gemma2" else None
@@ -386,6 +406,8 @@ class ModelConfig:
         attention layers carry no position signal unless ``position_embedding_type`` is ``rope``."""
         if self.model_type == "granitemoehybrid":
             return (self.extra or {}).get("position_embedding_type") == "rope"
+        if self.model_type in ("granitemoe", "granitemoeshared"):
+            return True
         if self.model_type == "nemotron_h":
             return False                                           # its attention blocks carry no position signal
         if self.model_type == "llama4_text":
@@ -549,6 +571,11 @@ _ARCH_NAME = {
     "olmo3": "Olmo3ForCausalLM",
     "seed_oss": "SeedOssForCausalLM",
     "arcee": "ArceeForCausalLM",
+    "glm4_moe": "Glm4MoeForCausalLM",
+    "ernie4_5": "Ernie4_5ForCausalLM",
+    "hunyuan_v1_dense": "HunYuanDenseV1ForCausalLM",
+    "granitemoe": "GraniteMoeForCausalLM",
+    "granitemoeshared": "GraniteMoeSharedForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
 }
 

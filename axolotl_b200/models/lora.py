@@ -95,7 +95,7 @@ def _checkpoint_renames(model):
         if mt == "llama4_text":
             pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.feed_forward.shared_expert."))
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
-        if mt == "granitemoehybrid":
+        if mt in ("granitemoeshared", "granitemoehybrid"):
             for inner in ("mlp.shared_experts", "mlp"):
                 pairs.append((f"{pre}.{inner}.gate_up_proj", f"{pre}.shared_mlp.input_linear"))
                 pairs.append((f"{pre}.{inner}.down_proj", f"{pre}.shared_mlp.output_linear"))
@@ -127,7 +127,8 @@ def _B_rows_layout(model, name, sub, B, to_checkpoint: bool):
         if to_checkpoint:
             idx = torch.argsort(idx)
         return B.reshape(heads, cfg.head_dim, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
-    if mt in ("glm", "glm4") and sub in ("q_proj", "k_proj") and ".self_attn." in name:
+    if getattr(getattr(model, "config", None), "rope_pairs_interleaved", lambda: False)() and sub in ("q_proj", "k_proj") \
+            and ".self_attn." in name:
         cfg = model.config
         heads, D, rot = (cfg.num_attention_heads if sub == "q_proj" else cfg.num_key_value_heads), cfg.head_dim, cfg.rope_dim()
         idx = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, D)])

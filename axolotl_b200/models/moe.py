@@ -211,12 +211,13 @@ class SparseMoE(nn.Module):
                 raise ValueError("Llama 4 routing scales the expert input, which is implemented for num_experts_per_tok = 1")
             self._llama4_shared = MLP(cfg.hidden_size, cfg.moe_intermediate_size, cfg.hidden_act, False, dtype, device)
         # Granite 4.0-H: the k best LOGITS are soft-maxed among themselves; one always-on shared MLP
-        self.topk_softmax = cfg.model_type == "granitemoehybrid"
+        self.topk_softmax = cfg.model_type in ("granitemoe", "granitemoeshared", "granitemoehybrid")
         if self.topk_softmax:
             from .transformer import MLP
 
-            self.shared_experts = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or 0),
-                                      cfg.hidden_act, False, dtype, device, fused_names=True)
+            shared = int((cfg.extra or {}).get("shared_intermediate_size") or 0) if cfg.model_type != "granitemoe" else 0
+            self.shared_experts = MLP(cfg.hidden_size, shared, cfg.hidden_act, False, dtype, device, fused_names=True) \
+                if shared else None
         # gpt-oss: router and experts carry biases; the k best LOGITS are chosen, then soft-maxed among themselves
         self.router_bias = None
         if cfg.model_type == "gpt_oss":
@@ -230,7 +231,7 @@ class SparseMoE(nn.Module):
             self.shared_experts = self._llama4_shared
             del self._llama4_shared
         self.e_score_correction_bias = None
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa"):
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe"):
             from .transformer import MLP
 
             ex = cfg.extra or {}

@@ -114,7 +114,9 @@ def _register(name, types, caps, head_dims=(64, 128), notes=(), validate=None):
     return register_model_support(type(name, (ModelSupport,), body))
 
 
-_register("LlamaLike", ("llama", "qwen2", "qwen3", "seed_oss"), _DENSE)
+_register("LlamaLike", ("llama", "qwen2", "qwen3", "seed_oss", "ernie4_5", "hunyuan_v1_dense"), _DENSE)
+_register("Glm4Moe", ("glm4_moe",), {TP: _MOE_NO_TP})
+_register("GraniteMoe", ("granitemoe", "granitemoeshared"), {TP: _MOE_NO_TP})
 _register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's fused gate|up projection is kept fused.")},
           notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))
 _register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms span all heads of the unsharded projection.")},

@@ -60,6 +60,7 @@ class Attention(nn.Module):
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
+        self.norm_after_rope = cfg.model_type == "hunyuan_v1_dense"   # HunYuan: per-head q / k norms act on the ROTATED vectors
         self.full_qk_norm = cfg.model_type in ("olmoe", "olmo2", "olmo3")   # OLMo family: q / k norms over ALL heads at once
         if self.full_qk_norm:
             self.q_norm = RMSNorm(self.Hq * self.D, cfg.rms_norm_eps, dtype, device)
@@ -91,6 +92,13 @@ class Attention(nn.Module):
             q, _ = self.q_norm(qkv[..., :nq].contiguous())
             k, _ = self.k_norm(qkv[..., nq:nq + nk].contiguous())
             qkv = torch.cat([q, k, qkv[..., nq + nk:]], -1)
+        if self.use_rope and per_head_norm and self.norm_after_rope:
+            T = qkv.shape[0]
+            nq, nk = self.Hq * self.D, self.Hk * self.D
+            qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale, rot_dim=self.rot_dim)
+            q = self.q_norm.plain(qkv[:, :nq].reshape(T * self.Hq, self.D)).reshape(T, nq)
+            k = self.k_norm.plain(qkv[:, nq:nq + nk].reshape(T * self.Hk, self.D)).reshape(T, nk)
+            return torch.cat([q, k, qkv[:, nq + nk:]], 1)
         if self.use_rope and per_head_norm and self.rot_dim is not None:
             # partial rotary embedding with q/k norms: the norms run on their own, then the first rot_dim dimensions rotate
             T = qkv.shape[0]
@@ -312,7 +320,7 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type == "llama4_text":          # dense layers have their own width
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("dense_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device)
-        elif cfg.model_type == "granitemoehybrid":     # dense variant: the "shared" MLP alone
+        elif cfg.model_type in ("granitemoeshared", "granitemoehybrid"):     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
         elif cfg.model_type == "arcee":                # up -> squared ReLU -> down, no gate

@@ -58,6 +58,20 @@ FAMILIES = {
     "arcee": dict(model_type="arcee", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                   num_attention_heads=4, num_key_value_heads=2, head_dim=16, hidden_act="relu2", tie_word_embeddings=False,
                   max_position_embeddings=256),
+    "glm4_moe": dict(model_type="glm4_moe", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16, n_routed_experts=4,
+                     n_shared_experts=1, num_experts_per_tok=2, first_k_dense_replace=1, use_qk_norm=True, attention_bias=True,
+                     tie_word_embeddings=False, max_position_embeddings=256),
+    "granitemoeshared": dict(model_type="granitemoeshared", vocab_size=320, hidden_size=64, intermediate_size=48,
+                             shared_intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             num_local_experts=4, num_experts_per_tok=2, tie_word_embeddings=True, embedding_multiplier=3.0,
+                             attention_multiplier=0.2, residual_multiplier=0.5, logits_scaling=2.0, max_position_embeddings=256),
+    "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False,
+                             max_position_embeddings=256),
+    "ernie4_5": dict(model_type="ernie4_5", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, use_bias=True, tie_word_embeddings=False,
+                     max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

@@ -839,6 +839,27 @@ LLAMA_LIKE = {
     "arcee": dict(model_type="arcee", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                   num_attention_heads=4, num_key_value_heads=2, head_dim=16, hidden_act="relu2", rms_norm_eps=1e-5,
                   tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "ernie4_5": dict(model_type="ernie4_5", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, use_bias=True, rms_norm_eps=1e-5,
+                     tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, attention_bias=False,
+                             tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "glm4_moe": dict(model_type="glm4_moe", vocab_size=300, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5,
+                     n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=3, n_group=2, topk_group=1, first_k_dense_replace=1,
+                     routed_scaling_factor=1.5, norm_topk_prob=True, use_qk_norm=True, attention_bias=True, rms_norm_eps=1e-5,
+                     tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "granitemoe": dict(model_type="granitemoe", vocab_size=300, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2,
+                       rms_norm_eps=1e-5, tie_word_embeddings=True, embedding_multiplier=3.0, attention_multiplier=0.2,
+                       residual_multiplier=0.5, logits_scaling=2.0, max_position_embeddings=256, router_aux_loss_coef=0.0,
+                       pad_token_id=0),
+    "granitemoeshared": dict(model_type="granitemoeshared", vocab_size=300, hidden_size=64, intermediate_size=48,
+                             shared_intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             num_local_experts=4, num_experts_per_tok=2, rms_norm_eps=1e-5, tie_word_embeddings=True,
+                             embedding_multiplier=3.0, attention_multiplier=0.2, residual_multiplier=0.5, logits_scaling=2.0,
+                             max_position_embeddings=256, router_aux_loss_coef=0.0, pad_token_id=0),
 }
 
 
@@ -850,7 +871,9 @@ def test_llama_like_variants_match_hf(tmp_path, family):
     ours = CausalLM(cfg, dtype=torch.float32).init_weights(47)
     with torch.no_grad():
         for n, p in ours.named_parameters():
-            if n.endswith("bias"):
+            if n.endswith("e_score_correction_bias"):
+                p.uniform_(-0.2, 0.2)
+            elif n.endswith("bias"):
                 p.normal_(0, 0.1)
             if "norm" in n and n.endswith("weight"):
                 p.uniform_(0.5, 1.5)

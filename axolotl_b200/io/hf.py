@@ -50,9 +50,12 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         return _nemotron_h_load(model, named_tensors, strict)
     glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
     hunyuan = getattr(model.config, "model_type", "") == "hunyuan_v1_dense"
+    starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     for name, t in named_tensors:
         if hunyuan:
             name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.")
+        if starcoder2:
+            name = name.replace(".mlp.c_fc.", ".mlp.up_proj.").replace(".mlp.c_proj.", ".mlp.down_proj.")
         if glm:
             name, t = _glm_in(model, name, t)
         if llama4:
@@ -111,9 +114,12 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             r0, r1 = fl.row_range(sub)
             (fl.weight if kind == "weight" else fl.bias)[r0:r1].copy_(t)
             filled.add(f"{parent}.{sub}.{kind}")
-        elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.weight$", name)):
-            mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
+        elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.(weight|bias)$", name)):
+            getattr(mods[f"{m.group(1)}.{m.group(2)}"], m.group(3)).copy_(t)
             filled.add(name)
+        elif name == "model.norm.bias":
+            model.norm.bias.copy_(t)
+            filled.add("norm.bias")
         elif (m := re.match(r"model\.(layers\.\d+)\.mamba\.(.+)$", name)):
             # Granite 4.0-H state-space mixer (kept under `self_attn` in our layer)
             mx, leaf = mods[m.group(1) + mamba_attr], m.group(2)
@@ -570,6 +576,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}
     if model.lm_head is not None:
         sd["lm_head.weight"] = model.lm_head.detach()
+    if getattr(model.norm, "bias", None) is not None:
+        sd["model.norm.bias"] = model.norm.bias.detach()
     gpt_oss = getattr(model.config, "model_type", "") == "gpt_oss"
     if getattr(model.config, "model_type", "") in ("granitemoe", "granitemoeshared", "granitemoehybrid"):
         return _granite_hybrid_state_dict(model, sd)
@@ -606,6 +614,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
         elif name.endswith(("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm",
                             "q_norm", "k_norm", "q_a_layernorm", "kv_a_layernorm")):
             sd[f"model.{name}.weight"] = m.weight.detach()
+            if getattr(m, "bias", None) is not None:
+                sd[f"model.{name}.bias"] = m.bias.detach()
         elif isinstance(m, Experts):
             if m.nvfp4 is not None:
                 for which in ("gate_up", "down"):
@@ -636,6 +646,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
         return _glm_out(model, sd)
     if getattr(model.config, "model_type", "") == "hunyuan_v1_dense":
         return {k.replace(".q_norm.", ".query_layernorm.").replace(".k_norm.", ".key_layernorm."): v for k, v in sd.items()}
+    if getattr(model.config, "model_type", "") == "starcoder2":
+        return {k.replace(".mlp.up_proj.", ".mlp.c_fc.").replace(".mlp.down_proj.", ".mlp.c_proj."): v for k, v in sd.items()}
     return sd
 
 

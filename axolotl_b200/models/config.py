@@ -16,7 +16,7 @@ from typing import Any
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
-                         "granitemoe", "granitemoeshared")
+                         "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -180,6 +180,25 @@ class ModelConfig:
             d.setdefault("attention_out_bias", False)
         if mt == "arcee":
             d.setdefault("hidden_act", "relu2")
+        if mt == "nemotron":           # LayerNorm with (1 + w) and bias, half of a head rotates, ungated squared-ReLU MLP
+            d["rms_norm_eps"] = d.get("norm_eps", 1e-5)
+            d.setdefault("partial_rotary_factor", 0.5)
+            d.setdefault("hidden_act", "relu2")
+        if mt == "starcoder2":         # LayerNorm with bias, ungated GELU MLP (c_fc / c_proj), biases everywhere
+            d["rms_norm_eps"] = d.get("norm_epsilon", 1e-5)
+            d["attention_bias"] = d["mlp_bias"] = bool(d.get("use_bias", True))
+            d.setdefault("hidden_act", "gelu_pytorch_tanh")
+            d.setdefault("tie_word_embeddings", True)
+        if mt in ("cohere", "cohere2"):   # one mean-subtracting norm per layer, attention and MLP side by side, scaled logits
+            d["rms_norm_eps"] = d.get("layer_norm_eps", 1e-5)
+            d.setdefault("tie_word_embeddings", True)
+            d.setdefault("logit_scale", 0.0625)
+            if d.get("use_qk_norm"):
+                raise ValueError(f"{mt}: use_qk_norm (per-head LayerNorm of q / k) is not supported")
+            if mt == "cohere2" and not d.get("layer_types"):
+                pat = d.get("sliding_window_pattern") or 4
+                d["layer_types"] = ["sliding_attention" if (i + 1) % pat else "full_attention"
+                                    for i in range(d.get("num_hidden_layers", 0))]
         if mt == "glm_moe_dsa":        # GLM-5: DeepSeek-V3 style latent attention + routing, plus the sparse-attention indexer
             L = d.get("num_hidden_layers", 0)
             for key, default in (("qk_nope_head_dim", 192), ("qk_rope_head_dim", 64), ("v_head_dim", 256), ("kv_lora_rank", 512),
@@ -297,6 +316,10 @@ class ModelConfig:
                 qpas = (self.extra or {}).get("query_pre_attn_scalar")
                 return float(qpas) ** -0.5 if qpas and self.model_type != "gemma" else 1.0 / math.sqrt(self.head_dim)
             return 1.0
+        if self.model_type in ("cohere", "cohere2"):
+            if name == "logits_scaling":
+                return 1.0 / float((self.extra or {}).get("logit_scale") or 1.0)
+            return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         if self.model_type == "falcon_h1":
             # maximal-update scalars: on the embeddings, on the keys (folded into the score scale: the rotary
             # embedding is linear), on the logits (a division elsewhere, hence the reciprocal)
@@ -322,6 +345,16 @@ class ModelConfig:
         """Gemma 2 / 3 and GLM-4 normalise the output of the attention and MLP branches too (four norms per layer)."""
         return self.model_type in ("gemma2", "gemma3_text", "glm4")
 
+    def norm_kind(self) -> str:
+        """"rms", or a mean-subtracting LayerNorm: with bias (StarCoder 2), stored as w - 1 with bias (Nemotron),
+        weight only (Cohere)."""
+        return {"starcoder2": "layernorm", "nemotron": "layernorm1p", "cohere": "layernorm_nobias",
+                "cohere2": "layernorm_nobias"}.get(self.model_type, "rms")
+
+    def parallel_block(self) -> bool:
+        """Cohere: attention and MLP read the same normalised input and are added to the stream together."""
+        return self.model_type in ("cohere", "cohere2")
+
     def post_norm_only(self) -> bool:
         """OLMo 2 / 3: no norm on a branch's input, one on its output."""
         return self.model_type in ("olmo2", "olmo3")
@@ -329,7 +362,7 @@ class ModelConfig:
     def rope_pairs_interleaved(self) -> bool:
         """GLM checkpoints store the rotated part of every head with (real, imaginary) neighbours; the rows of q / k are
         permuted to the half-split layout at load (scores do not change when q and k share the permutation)."""
-        return self.model_type in ("glm", "glm4", "ernie4_5")
+        return self.model_type in ("glm", "glm4", "ernie4_5", "cohere", "cohere2")
 
     def attn_softcap(self) -> float:
         v = (self.extra or {}).get("attn_logit_softcapping") if self.model_type == "gemma2" else None
@@ -372,7 +405,9 @@ class ModelConfig:
                 return int(w) if idx % 2 == 0 else 0          # even layers slide
             pat = ex.get("sliding_window_pattern") or 6
             return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
-        if self.model_type == "olmo3":
+        if self.model_type == "starcoder2":
+            return int(w)
+        if self.model_type in ("olmo3", "cohere2"):
             types = ex.get("layer_types")
             if idx is None or not types:
                 return int(w)
@@ -408,6 +443,8 @@ class ModelConfig:
             return (self.extra or {}).get("position_embedding_type") == "rope"
         if self.model_type in ("granitemoe", "granitemoeshared"):
             return True
+        if self.model_type == "cohere2":
+            return (self.extra or {})["layer_types"][idx] == "sliding_attention"     # global layers carry no position signal
         if self.model_type == "nemotron_h":
             return False                                           # its attention blocks carry no position signal
         if self.model_type == "llama4_text":
@@ -576,6 +613,10 @@ _ARCH_NAME = {
     "hunyuan_v1_dense": "HunYuanDenseV1ForCausalLM",
     "granitemoe": "GraniteMoeForCausalLM",
     "granitemoeshared": "GraniteMoeSharedForCausalLM",
+    "nemotron": "NemotronForCausalLM",
+    "starcoder2": "Starcoder2ForCausalLM",
+    "cohere": "CohereForCausalLM",
+    "cohere2": "Cohere2ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
 }
 

@@ -61,6 +61,41 @@ class RMSNorm(nn.Module):
         return self.weight if not self.offset else (self.weight.float() + self.offset).to(self.weight.dtype)
 
 
+class LayerNorm(nn.Module):
+    """Mean-subtracting norm with the interface of ``RMSNorm`` (Cohere: weight only; StarCoder 2 / Nemotron: weight and
+    bias; ``offset`` = 1 is Nemotron's stored-as-(w - 1) convention). Runs as a library op in fp32: these families are
+    outside the fused add+RMSNorm kernel."""
+
+    def __init__(self, dim, eps=1e-5, dtype=torch.bfloat16, device=None, bias=True, offset=0.0):
+        super().__init__()
+        self.offset = float(offset)
+        self.weight = nn.Parameter(torch.full((dim,), 1.0 - self.offset, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device)) if bias else None
+        self.eps = eps
+
+    def plain(self, x):
+        w = self.weight.float() + self.offset if self.offset else self.weight.float()
+        b = self.bias.float() if self.bias is not None else None
+        return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w, b, self.eps).to(x.dtype)
+
+    def forward(self, x, residual=None):
+        if residual is not None:
+            x = x + residual
+        return self.plain(x), x
+
+    def effective_weight(self):
+        return self.weight if not self.offset else (self.weight.float() + self.offset).to(self.weight.dtype)
+
+
+def make_norm(cfg, dim, dtype, device, offset=0.0):
+    """The architecture's hidden-state norm."""
+    kind = cfg.norm_kind()
+    if kind == "rms":
+        return RMSNorm(dim, cfg.rms_norm_eps, dtype, device, offset=offset)
+    return LayerNorm(dim, cfg.rms_norm_eps, dtype, device, bias=kind != "layernorm_nobias",
+                     offset=1.0 if kind == "layernorm1p" else 0.0)
+
+
 class FusedLinear(nn.Module):
     def __init__(self, in_features, out_features, names, bias=False, dtype=torch.bfloat16,
                  device=None):

@@ -92,6 +92,9 @@ def _checkpoint_renames(model):
             pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
         if mt in ("bamba", "falcon_h1"):
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
+        if mt == "starcoder2":
+            pairs.append((f"{pre}.mlp.up_proj", f"{pre}.mlp.c_fc"))
+            pairs.append((f"{pre}.mlp.down_proj", f"{pre}.mlp.c_proj"))
         if mt == "llama4_text":
             pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.feed_forward.shared_expert."))
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))

@@ -21,7 +21,7 @@ from torch.utils.checkpoint import checkpoint
 from ..ops import functional as Fn
 from ..ops.lora import glu_mlp, linear
 from .config import ModelConfig
-from .layers import FusedLinear, RMSNorm, adapters_enabled
+from .layers import FusedLinear, RMSNorm, adapters_enabled, make_norm
 
 IGNORE_INDEX = -100
 
@@ -48,7 +48,7 @@ class Attention(nn.Module):
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
-        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3")
+        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3", "starcoder2", "cohere", "cohere2", "nemotron")
                   else bool((cfg.extra or {}).get("attention_out_bias")) if cfg.model_type == "seed_oss" else False)
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=o_bias, dtype=dtype, device=device)
         # gpt-oss: one learned "sink" logit per head in every softmax denominator
@@ -189,7 +189,7 @@ class PlainMLP(nn.Module):
         super().__init__()
         self.up_proj = FusedLinear(hidden, [inter], ["up_proj"], bias=bias, dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
-        if act not in ("relu2", "relu", "gelu", "silu"):
+        if act not in ("relu2", "relu", "gelu", "silu", "gelu_pytorch_tanh"):
             raise ValueError(f"activation '{act}' is not available for an ungated MLP")
         self.act = act
 
@@ -201,6 +201,8 @@ class PlainMLP(nn.Module):
             u = torch.relu(u)
         elif self.act == "gelu":
             u = torch.nn.functional.gelu(u)
+        elif self.act == "gelu_pytorch_tanh":
+            u = torch.nn.functional.gelu(u, approximate="tanh")
         else:
             u = torch.nn.functional.silu(u)
         return self.down_proj(u)
@@ -272,7 +274,7 @@ class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
         super().__init__()
         off = cfg.norm_offset()
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
+        self.input_layernorm = make_norm(cfg, cfg.hidden_size, dtype, device, offset=off)
         if cfg.model_type == "glm_moe_dsa":
             from .dsa import SparseMLAttention
 
@@ -302,7 +304,9 @@ class DecoderLayer(nn.Module):
             inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
             self.self_attn.local_inv_freq = inv.to(device) if device is not None else inv
         self.residual_multiplier = cfg.multiplier("residual_multiplier")
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=off)
+        self.parallel_block = cfg.parallel_block()     # Cohere: one norm, attention and MLP side by side
+        if not self.parallel_block:
+            self.post_attention_layernorm = make_norm(cfg, cfg.hidden_size, dtype, device, offset=off)
         # Gemma 2 / 3: post_attention_layernorm and post_feedforward_layernorm act on the BRANCH outputs,
         # pre_feedforward_layernorm takes the place the post-attention norm has elsewhere
         self.post_norm_only = cfg.post_norm_only()     # OLMo 2 / 3: branches read the stream itself, norms on their outputs
@@ -323,7 +327,7 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("granitemoeshared", "granitemoehybrid"):     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
-        elif cfg.model_type == "arcee":                # up -> squared ReLU -> down, no gate
+        elif cfg.model_type in ("arcee", "nemotron", "starcoder2"):      # up -> activation -> down, no gate
             self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
@@ -370,7 +374,7 @@ class DecoderLayer(nn.Module):
         projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
         ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
         if (not hasattr(self.self_attn, "core") or getattr(self.self_attn, "out_gate", None) is not None
-                or getattr(self.self_attn, "indexer", None) is not None):
+                or getattr(self.self_attn, "indexer", None) is not None or self.parallel_block):
             # state-space / linear-attention mixers have no attention result to keep (and a gated attention output
             # needs the layer input again)
             return checkpoint(self.forward, h, residual, positions, inv_freq, attn_scale, meta, use_reentrant=False)
@@ -380,6 +384,8 @@ class DecoderLayer(nn.Module):
 
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
         x, residual = self._stream(h, residual)
+        if self.parallel_block:
+            return self.self_attn(x, positions, inv_freq, attn_scale, meta) + self.mlp(x), residual, None
         return self._mlp_half(self.self_attn(x, positions, inv_freq, attn_scale, meta), residual)
 
 
@@ -391,7 +397,7 @@ class CausalLM(nn.Module):
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
         layer_cls = {"nemotron_h": SingleBlockLayer, "falcon_h1": ParallelHybridLayer}.get(cfg.model_type, DecoderLayer)
         self.layers = nn.ModuleList([layer_cls(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, offset=cfg.norm_offset())
+        self.norm = make_norm(cfg, cfg.hidden_size, dtype, device, offset=cfg.norm_offset())
         self.final_softcap = cfg.final_softcap()   # Gemma 2: logits -> cap * tanh(logits / cap)
         if cfg.tie_word_embeddings:
             self.lm_head = None

@@ -72,6 +72,16 @@ FAMILIES = {
     "ernie4_5": dict(model_type="ernie4_5", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, use_bias=True, tie_word_embeddings=False,
                      max_position_embeddings=256),
+    "starcoder2": dict(model_type="starcoder2", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, use_bias=True, sliding_window=16, tie_word_embeddings=True,
+                       max_position_embeddings=256),
+    "cohere2": dict(model_type="cohere2", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                    num_attention_heads=4, num_key_value_heads=2, logit_scale=0.25, tie_word_embeddings=True,
+                    max_position_embeddings=256, sliding_window=8,
+                    layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "nemotron": dict(model_type="nemotron", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False,
+                     max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

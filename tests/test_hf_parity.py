@@ -860,6 +860,21 @@ LLAMA_LIKE = {
                              num_local_experts=4, num_experts_per_tok=2, rms_norm_eps=1e-5, tie_word_embeddings=True,
                              embedding_multiplier=3.0, attention_multiplier=0.2, residual_multiplier=0.5, logits_scaling=2.0,
                              max_position_embeddings=256, router_aux_loss_coef=0.0, pad_token_id=0),
+    "nemotron": dict(model_type="nemotron", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5, hidden_act="relu2",
+                     norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256, attention_bias=False, mlp_bias=False,
+                     pad_token_id=0),
+    "starcoder2": dict(model_type="starcoder2", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, use_bias=True, norm_epsilon=1e-5, sliding_window=16,
+                       tie_word_embeddings=True, max_position_embeddings=256, pad_token_id=0, residual_dropout=0.0,
+                       embedding_dropout=0.0, attention_dropout=0.0),
+    "cohere": dict(model_type="cohere", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                   num_attention_heads=4, num_key_value_heads=2, layer_norm_eps=1e-5, logit_scale=0.25, tie_word_embeddings=True,
+                   max_position_embeddings=256, attention_bias=False, use_qk_norm=False, pad_token_id=0),
+    "cohere2": dict(model_type="cohere2", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                    num_attention_heads=4, num_key_value_heads=2, layer_norm_eps=1e-5, logit_scale=0.25, tie_word_embeddings=True,
+                    max_position_embeddings=256, attention_bias=False, pad_token_id=0, sliding_window=8,
+                    layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
 }
 
 

@@ -45,7 +45,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     llama4 = getattr(model.config, "model_type", "") == "llama4_text"
     bamba = getattr(model.config, "model_type", "") in ("bamba", "falcon_h1")       # the same names outside the mixers
     mamba_attr = ".mamba" if getattr(model.config, "model_type", "") == "falcon_h1" else ".self_attn"
-    qwen3_next = getattr(model.config, "model_type", "") == "qwen3_next"
+    qwen3_next = getattr(model.config, "model_type", "") in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text")
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
     glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
@@ -69,6 +69,9 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
                     mx.norm_weight.copy_(t)
                 elif leaf in ("dt_bias", "A_log"):
                     getattr(mx, leaf).copy_(t)
+                elif getattr(mx, "flat", False) and leaf.startswith("in_proj_"):
+                    r0, r1 = mx.in_proj.row_range(leaf.split(".")[0])
+                    mx.in_proj.weight[r0:r1].copy_(t)
                 else:
                     getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
                 filled.add(name)
@@ -519,8 +522,13 @@ def _qwen3_next_out(model, sd):
         if type(mx).__name__ == "GatedDeltaNet":
             for k in [k for k in sd if k.startswith(pre + ".self_attn.")]:
                 sd.pop(k)
-            sd[f"{pre}.linear_attn.in_proj_qkvz.weight"] = mx.in_proj_qkvz.weight.detach()
-            sd[f"{pre}.linear_attn.in_proj_ba.weight"] = mx.in_proj_ba.weight.detach()
+            if mx.flat:
+                for sub in mx.in_proj.names:
+                    r0, r1 = mx.in_proj.row_range(sub)
+                    sd[f"{pre}.linear_attn.{sub}.weight"] = mx.in_proj.weight.detach()[r0:r1]
+            else:
+                sd[f"{pre}.linear_attn.in_proj_qkvz.weight"] = mx.in_proj_qkvz.weight.detach()
+                sd[f"{pre}.linear_attn.in_proj_ba.weight"] = mx.in_proj_ba.weight.detach()
             sd[f"{pre}.linear_attn.out_proj.weight"] = mx.out_proj.weight.detach()
             sd[f"{pre}.linear_attn.conv1d.weight"] = mx.conv_weight.detach()[:, None, :]
             sd[f"{pre}.linear_attn.norm.weight"] = mx.norm_weight.detach()
@@ -640,7 +648,7 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 sd[f"model.{name}.gate.e_score_correction_bias"] = m.e_score_correction_bias.detach()
     if getattr(model.config, "model_type", "") == "llama4_text":
         return _llama4_out(model, sd)
-    if getattr(model.config, "model_type", "") == "qwen3_next":
+    if getattr(model.config, "model_type", "") in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
         return _qwen3_next_out(model, sd)
     if model.config.rope_pairs_interleaved():
         return _glm_out(model, sd)

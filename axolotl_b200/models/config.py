@@ -16,11 +16,12 @@ from typing import Any
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
-                         "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2")
+                         "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
-ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + ("qwen3_next",)     # RMSNorm weights stored as w, applied as 1 + w
+QWEN3_NEXT_TYPES = ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text")   # Gated DeltaNet hybrids
+ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + QWEN3_NEXT_TYPES     # RMSNorm weights stored as w, applied as 1 + w
 
 
 @dataclass
@@ -67,7 +68,7 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
-        if self.model_type in ("gemma3_text", "qwen3_next", "olmo2", "olmo3"):
+        if self.model_type in ("gemma3_text", "olmo2", "olmo3") + QWEN3_NEXT_TYPES:
             self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -114,7 +115,10 @@ class ModelConfig:
                 every = d.get("no_rope_layer_interval") or 4
                 d["no_rope_layers"] = [int((i + 1) % every != 0) for i in range(L)]
             d.setdefault("rms_norm_eps", 1e-5)
-        if mt == "qwen3_next":
+        if mt in ("qwen3_5", "qwen3_5_moe") and isinstance(d.get("text_config"), dict):    # the multimodal wrapper: its language model
+            d = dict(d["text_config"], model_type=mt + "_text")
+            mt = d["model_type"]
+        if mt in QWEN3_NEXT_TYPES:
             L = d.get("num_hidden_layers", 0)
             if not d.get("layer_types"):
                 every = d.get("full_attention_interval") or 4
@@ -199,6 +203,10 @@ class ModelConfig:
                 pat = d.get("sliding_window_pattern") or 4
                 d["layer_types"] = ["sliding_attention" if (i + 1) % pat else "full_attention"
                                     for i in range(d.get("num_hidden_layers", 0))]
+        if mt == "ministral3" and not d.get("rope_parameters") and not d.get("rope_scaling"):
+            d["rope_parameters"] = {"rope_type": "yarn", "rope_theta": 1000000.0, "factor": 16.0, "original_max_position_embeddings": 16384,
+                                    "beta_fast": 32.0, "beta_slow": 1.0, "mscale_all_dim": 1.0, "mscale": 1.0,
+                                    "llama_4_scaling_beta": 0.1}
         if mt == "glm_moe_dsa":        # GLM-5: DeepSeek-V3 style latent attention + routing, plus the sparse-attention indexer
             L = d.get("num_hidden_layers", 0)
             for key, default in (("qk_nope_head_dim", 192), ("qk_rope_head_dim", 64), ("v_head_dim", 256), ("kv_lora_rank", 512),
@@ -388,7 +396,7 @@ class ModelConfig:
         w = ex.get("sliding_window")
         if not w:
             return 0
-        if self.model_type in ("mistral", "phi3", "mixtral"):
+        if self.model_type in ("mistral", "phi3", "mixtral", "ministral3"):
             return int(w)
         if self.model_type == "gpt_oss":
             if idx is None:
@@ -407,7 +415,7 @@ class ModelConfig:
             return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
         if self.model_type == "starcoder2":
             return int(w)
-        if self.model_type in ("olmo3", "cohere2"):
+        if self.model_type in ("olmo3", "cohere2", "ministral"):
             types = ex.get("layer_types")
             if idx is None or not types:
                 return int(w)
@@ -425,9 +433,9 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
-        if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h", "qwen3_next"):
+        if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h") + QWEN3_NEXT_TYPES:
             return "attention"
-        if self.model_type == "qwen3_next":
+        if self.model_type in QWEN3_NEXT_TYPES:
             return "deltanet" if (self.extra or {})["layer_types"][idx] == "linear_attention" else "attention"
         if self.model_type == "nemotron_h":
             return (self.extra or {})["block_types"][idx]          # "mamba" | "attention" | "mlp": one block per layer
@@ -617,7 +625,11 @@ _ARCH_NAME = {
     "starcoder2": "Starcoder2ForCausalLM",
     "cohere": "CohereForCausalLM",
     "cohere2": "Cohere2ForCausalLM",
+    "ministral": "MinistralForCausalLM",
+    "ministral3": "Ministral3ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",
+    "qwen3_5_text": "Qwen3_5ForCausalLM",
+    "qwen3_5_moe_text": "Qwen3_5MoeForCausalLM",
 }
 
 

@@ -74,8 +74,15 @@ class GatedDeltaNet(nn.Module):
         self.k = int(ex.get("linear_conv_kernel_dim", 4))
         self.conv_dim = 2 * self.key_dim + self.value_dim
         self.eps = cfg.rms_norm_eps
-        self.in_proj_qkvz = FusedLinear(H, [2 * self.key_dim + 2 * self.value_dim], ["in_proj_qkvz"], dtype=dtype, device=device)
-        self.in_proj_ba = FusedLinear(H, [2 * self.nv], ["in_proj_ba"], dtype=dtype, device=device)
+        # Qwen3-Next lays its two input projections out per key head ([q | k | v | z] and [b | a]); Qwen3.5 has four flat
+        # projections (q|k|v, z, b, a), fused into one GEMM here under their checkpoint names
+        self.flat = cfg.model_type != "qwen3_next"
+        if self.flat:
+            self.in_proj = FusedLinear(H, [self.conv_dim, self.value_dim, self.nv, self.nv],
+                                       ["in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a"], dtype=dtype, device=device)
+        else:
+            self.in_proj_qkvz = FusedLinear(H, [2 * self.key_dim + 2 * self.value_dim], ["in_proj_qkvz"], dtype=dtype, device=device)
+            self.in_proj_ba = FusedLinear(H, [2 * self.nv], ["in_proj_ba"], dtype=dtype, device=device)
         self.conv_weight = nn.Parameter(torch.empty(self.conv_dim, self.k, dtype=dtype, device=device))
         self.dt_bias = nn.Parameter(torch.ones(self.nv, dtype=dtype, device=device))
         self.A_log = nn.Parameter(torch.zeros(self.nv, dtype=dtype, device=device))
@@ -99,12 +106,15 @@ class GatedDeltaNet(nn.Module):
                                       "d_k x d_k matrix per head rather than a scalar decay; that hand-over is not built)")
         T = x.shape[0]
         r = self.nv // self.nk
-        # the projection is laid out per key head: [q | k | v (r value heads) | z (r value heads)]
-        qkvz = self.in_proj_qkvz(x).view(T, self.nk, 2 * self.dk + 2 * r * self.dv)
-        q, k, v, z = torch.split(qkvz, [self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
-        ba = self.in_proj_ba(x).view(T, self.nk, 2 * r)
-        b, a = ba[..., :r].reshape(T, self.nv), ba[..., r:].reshape(T, self.nv)
-        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
+        if self.flat:
+            mixed, z, b, a = torch.split(self.in_proj(x), [self.conv_dim, self.value_dim, self.nv, self.nv], dim=-1)
+        else:
+            # the projection is laid out per key head: [q | k | v (r value heads) | z (r value heads)]
+            qkvz = self.in_proj_qkvz(x).view(T, self.nk, 2 * self.dk + 2 * r * self.dv)
+            q, k, v, z = torch.split(qkvz, [self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
+            ba = self.in_proj_ba(x).view(T, self.nk, 2 * r)
+            b, a = ba[..., :r].reshape(T, self.nv), ba[..., r:].reshape(T, self.nv)
+            mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
         mixed = self._conv(mixed, positions)
         q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k, v = q.view(T, self.nk, self.dk), k.view(T, self.nk, self.dk), v.view(T, self.nv, self.dv)

@@ -88,7 +88,7 @@ def _checkpoint_renames(model):
         mixer = type(getattr(layer, "self_attn", None)).__name__
         if mt in ("bamba", "granitemoehybrid") and mixer == "Mamba2Mixer":
             pairs.append((f"{pre}.self_attn.", f"{pre}.mamba."))
-        if mt == "qwen3_next" and mixer == "GatedDeltaNet":
+        if mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text") and mixer == "GatedDeltaNet":
             pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
         if mt in ("bamba", "falcon_h1"):
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
@@ -138,7 +138,7 @@ def _B_rows_layout(model, name, sub, B, to_checkpoint: bool):
         if to_checkpoint:
             idx = torch.argsort(idx)
         return B.reshape(heads, D, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
-    if mt == "qwen3_next" and sub == "q_proj" and ".self_attn." in name:
+    if mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text") and sub == "q_proj" and ".self_attn." in name:
         cfg = model.config
         H, D = cfg.num_attention_heads, cfg.head_dim
         if to_checkpoint:

@@ -196,7 +196,7 @@ class SparseMoE(nn.Module):
         # Qwen2-MoE: a dense "shared" expert runs on every token, scaled by a sigmoid gate
         self.shared_expert = None
         self.shared_expert_gate = None
-        shared_I = (cfg.extra or {}).get("shared_expert_intermediate_size") if cfg.model_type in ("qwen2_moe", "qwen3_next") else None
+        shared_I = (cfg.extra or {}).get("shared_expert_intermediate_size") if cfg.model_type in ("qwen2_moe", "qwen3_next", "qwen3_5_moe_text") else None
         if shared_I:
             from .transformer import MLP
 

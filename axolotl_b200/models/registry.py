@@ -125,7 +125,7 @@ _register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2"),
           {**_DENSE, TP: Unsupported("These graphs have no sharding rule here.")},
           notes=("mean-subtracting norms run as library ops in fp32 (outside the fused add+RMSNorm kernel)",))
 _register("Arcee", ("arcee",), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
-_register("Mistral", ("mistral",), _DENSE,
+_register("Mistral", ("mistral", "ministral", "ministral3"), _DENSE,
           notes=("sliding_window is applied by the attention kernels (not with context parallelism)",))
 _register("Phi3", ("phi3",), {**_DENSE, TP: Unsupported("The checkpoint's fused projections are kept fused.")},
           notes=("longrope: the long factors apply when a document exceeds the original context",))
@@ -162,7 +162,7 @@ _register("Bamba", ("bamba",), {**_HYBRID, **_DENSE})
 _register("NemotronH", ("nemotron_h",), {**_HYBRID, **_DENSE},
           notes=("blocks of type `moe` (latent, non-gated experts) are rejected when the config is read",))
 _register("FalconH1", ("falcon_h1",), {**_HYBRID, **_DENSE})
-_register("Qwen3Next", ("qwen3_next",),
+_register("Qwen3Next", ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"),
           {TP: _MIXER_NO_TP, KV_CACHE: _MIXER_NO_KV,
            CP: Unsupported("A Gated DeltaNet chunk's transition is a full matrix per head; its hand-over is not built.")},
           head_dims=None)

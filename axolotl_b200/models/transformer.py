@@ -56,7 +56,7 @@ class Attention(nn.Module):
         # Qwen3-Next: the attention output is multiplied by sigmoid(gate(x)) before the output projection (the checkpoint
         # stores the gate rows inside q_proj, head by head; they are split off at load)
         self.out_gate = FusedLinear(H, [self.Hq * self.D], ["q_gate"], bias=cfg.attention_bias, dtype=dtype, device=device) \
-            if cfg.model_type == "qwen3_next" else None
+            if cfg.model_type in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text") else None
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
@@ -82,6 +82,10 @@ class Attention(nn.Module):
             self.l2_qk = bool(ex.get("use_qk_norm", True))
             self.temp = (float(ex.get("floor_scale") or 8192), float(ex.get("attn_scale") or 0.1)) if ex.get("attn_temperature_tuning", True) else None
         self.register_buffer("local_inv_freq", None, persistent=False)   # Gemma 3: sliding layers rotate with their own base
+        # Ministral 3: queries grow with the position, 1 + beta * log(1 + floor(pos / original context))
+        rp = ex.get("rope_parameters") or cfg.rope_scaling or {}
+        self.q_pos_scale = (float(rp["llama_4_scaling_beta"]), float(rp.get("original_max_position_embeddings") or 1)) \
+            if cfg.model_type == "ministral3" and rp.get("llama_4_scaling_beta") is not None else None
 
     def pre(self, x, positions, inv_freq, attn_scale):
         """Projections, q/k norms and rotary embedding: everything before the attention kernel."""
@@ -116,6 +120,11 @@ class Attention(nn.Module):
                 qkv = Fn.rope_qk_(qkv, positions, inv_freq, self.Hq, self.Hk, self.D, attn_scale,
                                   self.q_norm.effective_weight() if per_head_norm else None,
                                   self.k_norm.effective_weight() if per_head_norm else None, self.eps, rot_dim=self.rot_dim)
+            if self.q_pos_scale is not None:
+                beta, orig = self.q_pos_scale
+                t = 1.0 + beta * torch.log1p(torch.floor(positions.float() / orig))
+                nq = self.Hq * self.D
+                qkv = torch.cat([(qkv[:, :nq].float() * t[:, None]).to(qkv.dtype), qkv[:, nq:]], 1)
         elif self.llama4 and self.temp is not None:
             floor_scale, a = self.temp
             t = torch.log1p(torch.floor((positions.float() + 1.0) / floor_scale)) * a + 1.0
@@ -683,7 +692,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa"))
+                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -82,6 +82,14 @@ FAMILIES = {
     "nemotron": dict(model_type="nemotron", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False,
                      max_position_embeddings=256),
+    "qwen3_5_moe_text": dict(model_type="qwen3_5_moe_text", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, linear_num_value_heads=4,
+                             linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8, linear_conv_kernel_dim=4,
+                             num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+                             tie_word_embeddings=False, max_position_embeddings=256),
+    "ministral3": dict(model_type="ministral3", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False,
+                       max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

@@ -875,6 +875,16 @@ LLAMA_LIKE = {
                     num_attention_heads=4, num_key_value_heads=2, layer_norm_eps=1e-5, logit_scale=0.25, tie_word_embeddings=True,
                     max_position_embeddings=256, attention_bias=False, pad_token_id=0, sliding_window=8,
                     layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                      max_position_embeddings=256, pad_token_id=0, sliding_window=8,
+                      layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]),
+    "ministral3": dict(model_type="ministral3", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                       max_position_embeddings=256, pad_token_id=0,
+                       rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
+                                        "beta_fast": 32.0, "beta_slow": 1.0, "mscale_all_dim": 1.0, "mscale": 1.0,
+                                        "llama_4_scaling_beta": 0.3}),
 }
 
 
@@ -906,3 +916,44 @@ def test_llama_like_variants_match_hf(tmp_path, family):
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_text_matches_hf(tmp_path, moe):
+    """Qwen3.5 language model: the Qwen3-Next graph with four flat DeltaNet input projections, a dense MLP or routed
+    experts with a gated shared expert, multimodal rotary sections that coincide for text positions."""
+    d = dict(model_type="qwen3_5_moe_text" if moe else "qwen3_5_text", vocab_size=300, hidden_size=64, intermediate_size=96,
+             num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16, linear_num_value_heads=4,
+             linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=12, linear_conv_kernel_dim=4,
+             rms_norm_eps=1e-6, hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=256, attention_bias=False,
+             rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                              "mrope_section": [1, 1, 0], "mrope_interleaved": True})
+    if moe:
+        d.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                 router_aux_loss_coef=0.0)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(53)
+    assert [type(l.self_attn).__name__ for l in ours.layers] == ["GatedDeltaNet"] * 3 + ["Attention"]
+    assert ours.layers[0].self_attn.flat and ours.layers[3].self_attn.rot_dim == 4
+    _randomize_norms(ours, -0.2, 0.2)
+    with torch.no_grad():
+        for l in ours.layers[:3]:
+            l.self_attn.norm_weight.uniform_(0.5, 1.5)
+            l.self_attn.dt_bias.uniform_(-1.0, 1.0)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [25, 22]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=2e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    # the multimodal wrapper's config loads as its language model
+    wrapped = ModelConfig.from_hf_dict({"model_type": "qwen3_5_moe" if moe else "qwen3_5", "text_config": d})
+    assert wrapped.model_type == d["model_type"] and wrapped.hidden_size == 64

@@ -49,11 +49,22 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     if getattr(model.config, "model_type", "") == "nemotron_h":
         return _nemotron_h_load(model, named_tensors, strict)
     glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
-    hunyuan = getattr(model.config, "model_type", "") == "hunyuan_v1_dense"
+    hunyuan = getattr(model.config, "model_type", "") in ("hunyuan_v1_dense", "hunyuan_v1_moe")
+    apertus = getattr(model.config, "model_type", "") == "apertus"
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     for name, t in named_tensors:
         if hunyuan:
-            name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.")
+            name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.") \
+                .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_experts.")
+        if apertus:
+            name = name.replace(".attention_layernorm.", ".input_layernorm.").replace(".feedforward_layernorm.", ".post_attention_layernorm.")
+            if (m := re.match(r"model\.(layers\.\d+\.mlp)\.act_fn\.(alpha_p|alpha_n)$", name)):
+                getattr(mods[m.group(1)], m.group(2)).copy_(t.reshape(-1))
+                filled.add(name)
+                continue
+            if ".act_fn." in name:
+                continue
+        name = name.replace(".gate.moe_statics.e_score_correction_bias", ".gate.e_score_correction_bias")
         if starcoder2:
             name = name.replace(".mlp.c_fc.", ".mlp.up_proj.").replace(".mlp.c_proj.", ".mlp.down_proj.")
         if glm:
@@ -193,8 +204,8 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         elif (m := re.match(r"model\.(layers\.\d+\.self_attn\.indexer)\.k_norm\.(weight|bias)$", name)):
             getattr(mods[m.group(1)], "k_norm_" + m.group(2)).copy_(t)
             filled.add(name)
-        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.gate\.e_score_correction_bias$", name)):
-            mods[m.group(1)].e_score_correction_bias.copy_(t)
+        elif (m := re.match(r"model\.(layers\.\d+\.mlp)\.(?:gate\.)?e_score_correction_bias$", name)):
+            mods[m.group(1)].e_score_correction_bias.copy_(t.reshape(-1))
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+\.self_attn)\.(q_norm|k_norm|q_a_layernorm|kv_a_layernorm)\.weight$", name)):
             mods[f"{m.group(1)}.{m.group(2)}"].weight.copy_(t)
@@ -645,15 +656,31 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
             if getattr(m, "shared_expert_gate", None) is not None:
                 sd[f"model.{name}.shared_expert_gate.weight"] = m.shared_expert_gate.detach()
             if getattr(m, "e_score_correction_bias", None) is not None:
-                sd[f"model.{name}.gate.e_score_correction_bias"] = m.e_score_correction_bias.detach()
+                where = "" if getattr(model.config, "model_type", "") == "minimax_m2" else "gate."    # MiniMax keeps it on the block
+                sd[f"model.{name}.{where}e_score_correction_bias"] = m.e_score_correction_bias.detach()
     if getattr(model.config, "model_type", "") == "llama4_text":
         return _llama4_out(model, sd)
     if getattr(model.config, "model_type", "") in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
         return _qwen3_next_out(model, sd)
     if model.config.rope_pairs_interleaved():
-        return _glm_out(model, sd)
-    if getattr(model.config, "model_type", "") == "hunyuan_v1_dense":
-        return {k.replace(".q_norm.", ".query_layernorm.").replace(".k_norm.", ".key_layernorm."): v for k, v in sd.items()}
+        sd = _glm_out(model, sd)
+    mt_ = getattr(model.config, "model_type", "")
+    if mt_ in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
+        return {k.replace(".q_norm.", ".query_layernorm.").replace(".k_norm.", ".key_layernorm.")
+                .replace(".mlp.gate.weight", ".mlp.gate.wg.weight").replace(".mlp.shared_experts.", ".mlp.shared_mlp."): v
+                for k, v in sd.items()}
+    if mt_ == "ernie4_5_moe":
+        return {k.replace(".gate.e_score_correction_bias", ".gate.moe_statics.e_score_correction_bias"):
+                (v.reshape(1, -1) if k.endswith("e_score_correction_bias") else v) for k, v in sd.items()}
+    if mt_ == "apertus":
+        out = {k.replace(".input_layernorm.", ".attention_layernorm.").replace(".post_attention_layernorm.", ".feedforward_layernorm."): v
+               for k, v in sd.items()}
+        for i, layer in enumerate(model.layers):
+            out[f"model.layers.{i}.mlp.act_fn.alpha_p"] = layer.mlp.alpha_p.detach()
+            out[f"model.layers.{i}.mlp.act_fn.alpha_n"] = layer.mlp.alpha_n.detach()
+            out[f"model.layers.{i}.mlp.act_fn.beta"] = torch.tensor(layer.mlp.xielu_beta, dtype=layer.mlp.alpha_p.dtype)
+            out[f"model.layers.{i}.mlp.act_fn.eps"] = torch.tensor(layer.mlp.xielu_eps, dtype=layer.mlp.alpha_p.dtype)
+        return out
     if getattr(model.config, "model_type", "") == "starcoder2":
         return {k.replace(".mlp.up_proj.", ".mlp.c_fc.").replace(".mlp.down_proj.", ".mlp.c_proj."): v for k, v in sd.items()}
     return sd

@@ -16,7 +16,8 @@ from typing import Any
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_moe", "mixtral", "granite", "smollm3", "qwen2_moe", "olmoe",
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
-                         "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text")
+                         "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -68,7 +69,7 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
-        if self.model_type in ("gemma3_text", "olmo2", "olmo3") + QWEN3_NEXT_TYPES:
+        if self.model_type in ("gemma3_text", "olmo2", "olmo3", "minimax_m2") + QWEN3_NEXT_TYPES:
             self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -142,6 +143,10 @@ class ModelConfig:
                 d["mamba_d_head"] = int((d.get("mamba_expand") or 2) * d["hidden_size"]) // int(d.get("mamba_n_heads") or 128)
             rp = d.get("rope_parameters") or {}
             d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))
+        if mt == "minimax_m2":         # q / k norms over all heads, sigmoid routing with a selection bias, no shared expert
+            d["num_experts"] = d.get("num_local_experts") or 0
+            d["moe_intermediate_size"] = d.get("intermediate_size") or 0
+            d["norm_topk_prob"] = True
         if mt == "glm4_moe":           # Llama-style attention (optional per-head q/k norms, half of a head rotates) + DeepSeek-V3 routing
             d["num_experts"] = d.get("n_routed_experts") or 0
             d.setdefault("norm_topk_prob", True)
@@ -151,8 +156,27 @@ class ModelConfig:
             d["mlp_only_layers"] = [i for i in range(d.get("num_hidden_layers", 0)) if i < k1]
         if mt == "ernie4_5":
             d["attention_bias"] = d["mlp_bias"] = bool(d.get("use_bias", False))
-        if mt == "hunyuan_v1_dense":
+        if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
             d["qk_norm"] = True        # per head, AFTER the rotary embedding
+        if mt == "hunyuan_v1_moe":     # softmax top-k routing renormalised, one always-on shared MLP of the same width
+            if not isinstance(d.get("num_experts"), int) or not isinstance(d.get("moe_topk", 1), int):
+                raise ValueError("hunyuan_v1_moe: per-layer expert counts / top-k lists are not supported")
+            d["num_experts_per_tok"] = d.get("moe_topk") or 1
+            d["moe_intermediate_size"] = d.get("intermediate_size") or 0
+            d["norm_topk_prob"] = True
+        if mt == "ernie4_5_moe":       # ERNIE attention; softmax scores, selection with a bias, ungated shared experts
+            L = d.get("num_hidden_layers", 0)
+            d["attention_bias"] = d["mlp_bias"] = bool(d.get("use_bias", False))
+            d["num_experts"] = d.get("moe_num_experts") or 0
+            d["num_experts_per_tok"] = d.get("moe_k") or 1
+            d["norm_topk_prob"] = True
+            start, every = d.get("moe_layer_start_index") or 0, d.get("moe_layer_interval") or 1
+            end = d.get("moe_layer_end_index")
+            end = L - 1 if end in (None, -1) else end
+            d["mlp_only_layers"] = [i for i in range(L) if not ((i + 1) % every == 0 and start <= i <= end)]
+        if mt == "apertus":            # q / k norms per head, ungated MLP with the learnable xIELU activation
+            d["qk_norm"] = True
+            d.setdefault("hidden_act", "xielu")
         if mt in GRANITE_MOE_TYPES:
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0     # width of a routed expert
@@ -279,6 +303,20 @@ class ModelConfig:
             d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
+        if self.model_type == "hunyuan_v1_moe":
+            d["moe_topk"] = d.pop("num_experts_per_tok")
+            d.pop("moe_intermediate_size", None)
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
+        if self.model_type == "ernie4_5_moe":
+            d["moe_num_experts"] = d.pop("num_experts")
+            d["moe_k"] = d.pop("num_experts_per_tok")
+            d["use_bias"] = bool(self.attention_bias)
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
+        if self.model_type == "minimax_m2":
+            d["num_local_experts"] = d.pop("num_experts")
+            d["intermediate_size"] = d.pop("moe_intermediate_size") or d.get("intermediate_size")
         if self.model_type == "glm4_moe":
             d["n_routed_experts"] = d.pop("num_experts")
             d["use_qk_norm"] = bool(self.qk_norm)
@@ -370,7 +408,7 @@ class ModelConfig:
     def rope_pairs_interleaved(self) -> bool:
         """GLM checkpoints store the rotated part of every head with (real, imaginary) neighbours; the rows of q / k are
         permuted to the half-split layout at load (scores do not change when q and k share the permutation)."""
-        return self.model_type in ("glm", "glm4", "ernie4_5", "cohere", "cohere2")
+        return self.model_type in ("glm", "glm4", "ernie4_5", "ernie4_5_moe", "cohere", "cohere2")
 
     def attn_softcap(self) -> float:
         v = (self.extra or {}).get("attn_logit_softcapping") if self.model_type == "gemma2" else None
@@ -625,6 +663,10 @@ _ARCH_NAME = {
     "starcoder2": "Starcoder2ForCausalLM",
     "cohere": "CohereForCausalLM",
     "cohere2": "Cohere2ForCausalLM",
+    "minimax_m2": "MiniMaxM2ForCausalLM",
+    "hunyuan_v1_moe": "HunYuanMoEV1ForCausalLM",
+    "ernie4_5_moe": "Ernie4_5_MoeForCausalLM",
+    "apertus": "ApertusForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",

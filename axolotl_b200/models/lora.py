@@ -92,6 +92,8 @@ def _checkpoint_renames(model):
             pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
         if mt in ("bamba", "falcon_h1"):
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
+        if mt == "hunyuan_v1_moe":
+            pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.mlp.shared_mlp."))
         if mt == "starcoder2":
             pairs.append((f"{pre}.mlp.up_proj", f"{pre}.mlp.c_fc"))
             pairs.append((f"{pre}.mlp.down_proj", f"{pre}.mlp.c_proj"))

@@ -231,20 +231,23 @@ class SparseMoE(nn.Module):
             self.shared_experts = self._llama4_shared
             del self._llama4_shared
         self.e_score_correction_bias = None
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe"):
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe"):
             from .transformer import MLP
 
             ex = cfg.extra or {}
-            v3 = cfg.model_type != "deepseek_v2"
+            v3 = cfg.model_type not in ("deepseek_v2", "hunyuan_v1_moe", "ernie4_5_moe")
             grouped = v3 or ex.get("topk_method") == "group_limited_greedy"
-            self.deepseek = dict(scoring="sigmoid" if v3 else (ex.get("scoring_func") or "softmax"),
+            soft = "softmax" if cfg.model_type in ("hunyuan_v1_moe", "ernie4_5_moe") else (ex.get("scoring_func") or "softmax")
+            self.deepseek = dict(scoring="sigmoid" if v3 else soft,
                                  n_group=int(ex.get("n_group") or 1) if grouped else 1,
                                  topk_group=int(ex.get("topk_group") or 1), group_score="top2" if v3 else "max",
                                  norm_topk_prob=bool(cfg.norm_topk_prob), scale=float(ex.get("routed_scaling_factor") or 1.0))
-            if v3:
+            if v3 or cfg.model_type == "ernie4_5_moe":
                 self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
                                                             requires_grad=False)
-            n_shared = int(ex.get("n_shared_experts") or 0)
+            n_shared = int(ex.get("n_shared_experts") or ex.get("moe_num_shared_experts") or 0)
+            if cfg.model_type == "hunyuan_v1_moe":
+                n_shared = 1
             if n_shared:
                 self.shared_experts = MLP(cfg.hidden_size, cfg.moe_intermediate_size * n_shared, cfg.hidden_act, False,
                                           dtype, device)

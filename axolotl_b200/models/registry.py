@@ -115,7 +115,7 @@ def _register(name, types, caps, head_dims=(64, 128), notes=(), validate=None):
 
 
 _register("LlamaLike", ("llama", "qwen2", "qwen3", "seed_oss", "ernie4_5", "hunyuan_v1_dense"), _DENSE)
-_register("Glm4Moe", ("glm4_moe",), {TP: _MOE_NO_TP})
+_register("Glm4Moe", ("glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe"), {TP: _MOE_NO_TP})
 _register("GraniteMoe", ("granitemoe", "granitemoeshared"), {TP: _MOE_NO_TP})
 _register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's fused gate|up projection is kept fused.")},
           notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))
@@ -124,7 +124,7 @@ _register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms s
 _register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2"),
           {**_DENSE, TP: Unsupported("These graphs have no sharding rule here.")},
           notes=("mean-subtracting norms run as library ops in fp32 (outside the fused add+RMSNorm kernel)",))
-_register("Arcee", ("arcee",), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
+_register("Arcee", ("arcee", "apertus"), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
 _register("Mistral", ("mistral", "ministral", "ministral3"), _DENSE,
           notes=("sliding_window is applied by the attention kernels (not with context parallelism)",))
 _register("Phi3", ("phi3",), {**_DENSE, TP: Unsupported("The checkpoint's fused projections are kept fused.")},

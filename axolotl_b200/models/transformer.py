@@ -60,8 +60,8 @@ class Attention(nn.Module):
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
-        self.norm_after_rope = cfg.model_type == "hunyuan_v1_dense"   # HunYuan: per-head q / k norms act on the ROTATED vectors
-        self.full_qk_norm = cfg.model_type in ("olmoe", "olmo2", "olmo3")   # OLMo family: q / k norms over ALL heads at once
+        self.norm_after_rope = cfg.model_type in ("hunyuan_v1_dense", "hunyuan_v1_moe")   # HunYuan: per-head q / k norms act on the ROTATED vectors
+        self.full_qk_norm = cfg.model_type in ("olmoe", "olmo2", "olmo3", "minimax_m2")   # OLMo family: q / k norms over ALL heads at once
         if self.full_qk_norm:
             self.q_norm = RMSNorm(self.Hq * self.D, cfg.rms_norm_eps, dtype, device)
             self.k_norm = RMSNorm(self.Hk * self.D, cfg.rms_norm_eps, dtype, device)
@@ -192,19 +192,30 @@ class MLP(nn.Module):
 
 
 class PlainMLP(nn.Module):
-    """up -> activation -> down without a gate (Nemotron-H: squared ReLU)."""
+    """up -> activation -> down without a gate (Nemotron-H: squared ReLU; Apertus: xIELU with two learnable scalars per
+    layer, alpha_p x^2 + beta x for x > 0 and alpha_n (expm1(min(x, eps)) - x) + beta x otherwise)."""
 
     def __init__(self, hidden, inter, act, bias, dtype, device):
         super().__init__()
         self.up_proj = FusedLinear(hidden, [inter], ["up_proj"], bias=bias, dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
-        if act not in ("relu2", "relu", "gelu", "silu", "gelu_pytorch_tanh"):
+        if act not in ("relu2", "relu", "gelu", "silu", "gelu_pytorch_tanh", "xielu"):
             raise ValueError(f"activation '{act}' is not available for an ungated MLP")
         self.act = act
+        if act == "xielu":       # stored through an inverse softplus, as the checkpoints do (alpha_p = 0.8, alpha_n = 0.8 - beta)
+            self.xielu_beta, self.xielu_eps = 0.5, -1e-6
+            self.alpha_p = nn.Parameter(torch.log(torch.expm1(torch.tensor([0.8]))).to(dtype=dtype, device=device))
+            self.alpha_n = nn.Parameter(torch.log(torch.expm1(torch.tensor([0.8 - 0.5]))).to(dtype=dtype, device=device))
 
     def forward(self, x):
         u = self.up_proj(x)
-        if self.act == "relu2":
+        if self.act == "xielu":
+            ap = torch.nn.functional.softplus(self.alpha_p.float())
+            an = self.xielu_beta + torch.nn.functional.softplus(self.alpha_n.float())
+            uf = u.float()
+            neg = (torch.expm1(torch.clamp(uf, max=self.xielu_eps)) - uf) * an + self.xielu_beta * uf
+            u = torch.where(uf > 0, ap * uf * uf + self.xielu_beta * uf, neg).to(u.dtype)
+        elif self.act == "relu2":
             u = torch.relu(u).square()
         elif self.act == "relu":
             u = torch.relu(u)
@@ -336,7 +347,7 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("granitemoeshared", "granitemoehybrid"):     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
-        elif cfg.model_type in ("arcee", "nemotron", "starcoder2"):      # up -> activation -> down, no gate
+        elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus"):      # up -> activation -> down, no gate
             self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,

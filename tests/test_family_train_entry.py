@@ -90,6 +90,19 @@ FAMILIES = {
     "ministral3": dict(model_type="ministral3", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False,
                        max_position_embeddings=256),
+    "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, moe_topk=2,
+                           tie_word_embeddings=False, max_position_embeddings=256),
+    "ernie4_5_moe": dict(model_type="ernie4_5_moe", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, moe_num_experts=4, moe_k=2,
+                         moe_num_shared_experts=1, moe_layer_start_index=1, moe_layer_interval=1, moe_layer_end_index=-1,
+                         tie_word_embeddings=False, max_position_embeddings=256),
+    "apertus": dict(model_type="apertus", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False, max_position_embeddings=256,
+                    rope_parameters={"rope_type": "default", "rope_theta": 10000.0}),
+    "minimax_m2": dict(model_type="minimax_m2", vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
+                       tie_word_embeddings=False, max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

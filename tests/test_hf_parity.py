@@ -875,6 +875,23 @@ LLAMA_LIKE = {
                     num_attention_heads=4, num_key_value_heads=2, layer_norm_eps=1e-5, logit_scale=0.25, tie_word_embeddings=True,
                     max_position_embeddings=256, attention_bias=False, pad_token_id=0, sliding_window=8,
                     layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "minimax_m2": dict(model_type="minimax_m2", vocab_size=300, hidden_size=64, intermediate_size=32, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=8, num_experts_per_tok=3,
+                       rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0,
+                       router_aux_loss_coef=0.0,
+                       rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}),
+    "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", vocab_size=300, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, moe_topk=2, rms_norm_eps=1e-5,
+                           tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0, attention_bias=False),
+    "ernie4_5_moe": dict(model_type="ernie4_5_moe", vocab_size=300, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                         num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, moe_num_experts=4, moe_k=2,
+                         moe_num_shared_experts=1, moe_layer_start_index=1, moe_layer_interval=1, moe_layer_end_index=-1,
+                         use_bias=False, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256,
+                         pad_token_id=0, router_aux_loss_coef=0.0),
+    "apertus": dict(model_type="apertus", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                    max_position_embeddings=256, pad_token_id=0, hidden_act="xielu",
+                    rope_parameters={"rope_type": "default", "rope_theta": 10000.0}),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,
@@ -898,6 +915,8 @@ def test_llama_like_variants_match_hf(tmp_path, family):
         for n, p in ours.named_parameters():
             if n.endswith("e_score_correction_bias"):
                 p.uniform_(-0.2, 0.2)
+            elif n.endswith(("alpha_p", "alpha_n")):
+                p.uniform_(-0.5, 0.5)
             elif n.endswith("bias"):
                 p.normal_(0, 0.1)
             if "norm" in n and n.endswith("weight"):

@@ -51,11 +51,27 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
     hunyuan = getattr(model.config, "model_type", "") in ("hunyuan_v1_dense", "hunyuan_v1_moe")
     apertus = getattr(model.config, "model_type", "") == "apertus"
+    lfm2 = getattr(model.config, "model_type", "") == "lfm2"
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     for name, t in named_tensors:
         if hunyuan:
             name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.") \
                 .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_experts.")
+        if lfm2:
+            if (m := re.match(r"model\.(layers\.\d+)\.conv\.(.+)$", name)):
+                mx, leaf = mods[m.group(1) + ".self_attn"], m.group(2)
+                if leaf == "conv.weight":
+                    mx.conv_weight.copy_(t.reshape(t.shape[0], t.shape[-1]))
+                elif leaf == "conv.bias":
+                    mx.conv_bias.copy_(t)
+                else:
+                    getattr(getattr(mx, leaf.split(".")[0]), leaf.split(".")[1]).copy_(t)
+                filled.add(name)
+                continue
+            for theirs, ours in _LFM2_NAMES:
+                if theirs in name:
+                    name = name.replace(theirs, ours)
+                    break
         if apertus:
             name = name.replace(".attention_layernorm.", ".input_layernorm.").replace(".feedforward_layernorm.", ".post_attention_layernorm.")
             if (m := re.match(r"model\.(layers\.\d+\.mlp)\.act_fn\.(alpha_p|alpha_n)$", name)):
@@ -342,6 +358,37 @@ def _deinterleave_rows(w, heads, D, inverse=False):
     if inverse:
         idx = torch.argsort(idx)
     return w.reshape(heads, D, *w.shape[1:]).index_select(1, idx.to(w.device)).reshape(w.shape)
+
+
+# LFM2 names (checkpoint, ours); the short-convolution operator sits where other families keep their attention module
+_LFM2_NAMES = ((".operator_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
+               (".feed_forward.w1.", ".mlp.gate_proj."), (".feed_forward.w3.", ".mlp.up_proj."), (".feed_forward.w2.", ".mlp.down_proj."),
+               (".self_attn.out_proj.", ".self_attn.o_proj."), (".self_attn.q_layernorm.", ".self_attn.q_norm."),
+               (".self_attn.k_layernorm.", ".self_attn.k_norm."), ("model.embedding_norm.", "model.norm."))
+
+
+def _lfm2_state_dict(model, sd):
+    out = {}
+    for i, layer in enumerate(model.layers):
+        mx = layer.self_attn
+        if type(mx).__name__ == "ShortConv":
+            pre = f"model.layers.{i}"
+            for k in [k for k in sd if k.startswith(pre + ".self_attn.")]:
+                sd.pop(k)
+            out[f"{pre}.conv.in_proj.weight"] = mx.in_proj.weight.detach()
+            out[f"{pre}.conv.out_proj.weight"] = mx.out_proj.weight.detach()
+            out[f"{pre}.conv.conv.weight"] = mx.conv_weight.detach()[:, None, :]
+            if mx.conv_bias is not None:
+                out[f"{pre}.conv.in_proj.bias"] = mx.in_proj.bias.detach()
+                out[f"{pre}.conv.out_proj.bias"] = mx.out_proj.bias.detach()
+                out[f"{pre}.conv.conv.bias"] = mx.conv_bias.detach()
+    for k, v in sd.items():
+        for theirs, ours in _LFM2_NAMES:
+            if ours in k:
+                k = k.replace(ours, theirs)
+                break
+        out[k] = v
+    return out
 
 
 def _rotary_rows(w, heads, D, rot, inverse=False):
@@ -672,6 +719,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     if mt_ == "ernie4_5_moe":
         return {k.replace(".gate.e_score_correction_bias", ".gate.moe_statics.e_score_correction_bias"):
                 (v.reshape(1, -1) if k.endswith("e_score_correction_bias") else v) for k, v in sd.items()}
+    if mt_ == "lfm2":
+        return _lfm2_state_dict(model, sd)
     if mt_ == "apertus":
         out = {k.replace(".input_layernorm.", ".attention_layernorm.").replace(".post_attention_layernorm.", ".feedforward_layernorm."): v
                for k, v in sd.items()}

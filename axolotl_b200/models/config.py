@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -174,6 +174,22 @@ class ModelConfig:
             end = d.get("moe_layer_end_index")
             end = L - 1 if end in (None, -1) else end
             d["mlp_only_layers"] = [i for i in range(L) if not ((i + 1) % every == 0 and start <= i <= end)]
+        if mt == "lfm2":               # gated short convolutions beside a few attention layers (q / k norms per head)
+            L = d.get("num_hidden_layers", 0)
+            d["rms_norm_eps"] = d.get("norm_eps", 1e-5)
+            d["qk_norm"] = True
+            d.setdefault("tie_word_embeddings", True)
+            if not d.get("layer_types"):
+                full = set(d.get("full_attn_idxs") or range(L))
+                d["layer_types"] = ["full_attention" if i in full else "conv" for i in range(L)]
+            inter = d.get("intermediate_size") or d.get("block_ff_dim") or 0
+            if d.get("block_auto_adjust_ff_dim", True):
+                inter = int(2 * inter / 3)
+                mult = d.get("block_ffn_dim_multiplier", 1.0)
+                if mult is not None:
+                    mo = int(d.get("block_multiple_of") or 256)
+                    inter = mo * ((int(mult * inter) + mo - 1) // mo)
+            d["mlp_width"] = inter
         if mt == "apertus":            # q / k norms per head, ungated MLP with the learnable xIELU activation
             d["qk_norm"] = True
             d.setdefault("hidden_act", "xielu")
@@ -471,6 +487,8 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
+        if self.model_type == "lfm2":
+            return "attention" if (self.extra or {})["layer_types"][idx] == "full_attention" else "shortconv"
         if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h") + QWEN3_NEXT_TYPES:
             return "attention"
         if self.model_type in QWEN3_NEXT_TYPES:
@@ -667,6 +685,7 @@ _ARCH_NAME = {
     "hunyuan_v1_moe": "HunYuanMoEV1ForCausalLM",
     "ernie4_5_moe": "Ernie4_5_MoeForCausalLM",
     "apertus": "ApertusForCausalLM",
+    "lfm2": "Lfm2ForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",

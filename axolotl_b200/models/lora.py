@@ -92,6 +92,11 @@ def _checkpoint_renames(model):
             pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
         if mt in ("bamba", "falcon_h1"):
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
+        if mt == "lfm2":
+            if mixer == "ShortConv":
+                pairs.append((f"{pre}.self_attn.", f"{pre}.conv."))
+            pairs += [(f"{pre}.self_attn.o_proj", f"{pre}.self_attn.out_proj"), (f"{pre}.mlp.gate_proj", f"{pre}.feed_forward.w1"),
+                      (f"{pre}.mlp.up_proj", f"{pre}.feed_forward.w3"), (f"{pre}.mlp.down_proj", f"{pre}.feed_forward.w2")]
         if mt == "hunyuan_v1_moe":
             pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.mlp.shared_mlp."))
         if mt == "starcoder2":

@@ -307,6 +307,10 @@ class DecoderLayer(nn.Module):
             from .mamba import Mamba2Mixer
 
             self.self_attn = Mamba2Mixer(cfg, dtype, device)     # (kept under the same attribute: the layer's token mixer)
+        elif cfg.layer_kind(idx) == "shortconv":
+            from .shortconv import ShortConv
+
+            self.self_attn = ShortConv(cfg, dtype, device)
         elif cfg.layer_kind(idx) == "deltanet":
             from .deltanet import GatedDeltaNet
 
@@ -347,6 +351,9 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("granitemoeshared", "granitemoehybrid"):     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
+        elif cfg.model_type == "lfm2":                 # its own width rule (two thirds, rounded up to a multiple)
+            self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("mlp_width") or cfg.intermediate_size), "silu", False,
+                           dtype, device)
         elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus"):      # up -> activation -> down, no gate
             self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
@@ -703,7 +710,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa"))
+                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -892,6 +892,10 @@ LLAMA_LIKE = {
                     num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, tie_word_embeddings=False,
                     max_position_embeddings=256, pad_token_id=0, hidden_act="xielu",
                     rope_parameters={"rope_type": "default", "rope_theta": 10000.0}),
+    "lfm2": dict(model_type="lfm2", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
+                 num_key_value_heads=2, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3, norm_eps=1e-5,
+                 block_auto_adjust_ff_dim=True, block_multiple_of=16, block_ffn_dim_multiplier=1.0, tie_word_embeddings=True,
+                 max_position_embeddings=256, pad_token_id=0),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,

@@ -344,14 +344,15 @@ def check_cp_state_space(dev, rank, world):
         for l in lens:
             cu.append(cu[-1] + l)
         torch.manual_seed(3)
-        mixer = Mamba2Mixer(cfg, torch.float32, dev)
+        dt = torch.float32 if dev.type == "cpu" else torch.bfloat16       # the device GEMMs take bf16 operands
+        mixer = Mamba2Mixer(cfg, dt, dev)
         with torch.no_grad():
             for prm in mixer.parameters():
                 if prm.dim() > 1:
                     prm.normal_(0, 0.2)
             mixer.dt_bias.uniform_(-1, 1)
-        x = torch.randn(S, 64, device=dev)
-        gy = torch.randn(S, 64, device=dev)
+        x = torch.randn(S, 64, device=dev).to(dt)
+        gy = torch.randn(S, 64, device=dev).to(dt)
         pos = torch.cat([torch.arange(l) for l in lens]).to(dev)
         xr = x.clone().requires_grad_(True)
         yr = mixer(xr, pos, None, 1.0, AttnMeta(cu, dev))
@@ -363,7 +364,7 @@ def check_cp_state_space(dev, rank, world):
         xc = x[sl].clone().requires_grad_(True)
         yc = mixer(xc, pos[sl], None, 1.0, par.cp.make_meta(cu, S))
         yc.backward(gy[sl])
-        tol = 1e-4 if dev.type == "cpu" else 2e-3
+        tol = 1e-4 if dev.type == "cpu" else 3e-2
         assert rel_err(yc, yr[sl]) < tol, ("output", lens, rel_err(yc, yr[sl]))
         assert rel_err(xc.grad, ref_gx[sl]) < tol, ("input gradient", lens, rel_err(xc.grad, ref_gx[sl]))
         for n, prm in mixer.named_parameters():

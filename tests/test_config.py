@@ -244,3 +244,23 @@ def test_blocked_attention_for_head_widths_without_a_kernel_matches_the_referenc
         g2, = torch.autograd.grad((ref ** 2).sum(), qkv)
         assert (got - ref).abs().max() < 1e-5
         assert (g1 - g2).abs().max() < 1e-3
+
+
+def test_every_example_config_passes_validation():
+    """The YAML files under examples/ are what a new user copies: each one must load through the schema and the
+    cross-field rules (model weights are not touched)."""
+    import glob
+    import os
+
+    import yaml
+
+    from axolotl_b200.config.load import load_cfg
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    files = sorted(glob.glob(os.path.join(root, "**", "*.yaml"), recursive=True))
+    assert len(files) >= 25
+    for f in files:
+        with open(f) as fh:
+            raw = yaml.safe_load(fh)
+        cfg = load_cfg(raw)
+        assert cfg["sequence_len"] > 0 and cfg["output_dir"], f

@@ -212,9 +212,7 @@ class PlainMLP(nn.Module):
         if self.act == "xielu":
             ap = torch.nn.functional.softplus(self.alpha_p.float())
             an = self.xielu_beta + torch.nn.functional.softplus(self.alpha_n.float())
-            uf = u.float()
-            neg = (torch.expm1(torch.clamp(uf, max=self.xielu_eps)) - uf) * an + self.xielu_beta * uf
-            u = torch.where(uf > 0, ap * uf * uf + self.xielu_beta * uf, neg).to(u.dtype)
+            u = Fn.xielu(u, ap, an, self.xielu_beta, self.xielu_eps)
         elif self.act == "relu2":
             u = torch.relu(u).square()
         elif self.act == "relu":

@@ -916,3 +916,68 @@ def linear_token_logps(hidden, lm_head_weight, labels, chunk_rows=2048, ignore_i
     hidden = hidden.reshape(-1, hidden.shape[-1]).contiguous()
     return _LinearTokenLogps.apply(hidden, lm_head_weight, labels.reshape(-1).contiguous(), chunk_rows, ignore_index,
                                    entropy_out)
+
+
+class _XIELU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ap, an, beta, eps):
+        ctx.save_for_backward(x, ap, an)
+        ctx.consts = (float(beta), float(eps))
+        y = torch.empty_like(x)
+        _lib.check_rc(_lib.cuda_lib().axb_xielu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), float(ap), float(an), float(beta),
+                                                    float(eps), _lib.stream_ptr()), "xielu_fwd")
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, ap, an = ctx.saved_tensors
+        beta, eps = ctx.consts
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        sums = torch.zeros(2, dtype=torch.float32, device=x.device)
+        _lib.check_rc(_lib.cuda_lib().axb_xielu_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), sums.data_ptr(), x.numel(),
+                                                    float(ap), float(an), beta, eps, _lib.stream_ptr()), "xielu_bwd")
+        return dx, sums[0].reshape(ap.shape).to(ap.dtype), sums[1].reshape(an.shape).to(an.dtype), None, None
+
+
+def xielu(x, alpha_p, alpha_n, beta=0.5, eps=-1e-6):
+    """xIELU activation: ``alpha_p x^2 + beta x`` for x > 0, ``alpha_n (expm1(min(x, eps)) - x) + beta x`` otherwise;
+    ``alpha_p`` / ``alpha_n`` are the EFFECTIVE (already soft-plussed) one-element fp32 tensors, gradients flow to them."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _XIELU.apply(x.contiguous(), alpha_p.float().reshape(1), alpha_n.float().reshape(1), beta, eps)
+    xf = x.float()
+    neg = (torch.expm1(torch.clamp(xf, max=eps)) - xf) * alpha_n.float() + beta * xf
+    return torch.where(xf > 0, alpha_p.float() * xf * xf + beta * xf, neg).to(x.dtype)
+
+
+class _GatedPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, kv, gate):
+        M, W, D = kv.shape
+        out = torch.empty((M, D), dtype=torch.float32, device=kv.device)
+        _lib.check_rc(_lib.cuda_lib().axb_gated_pool_fwd(kv.data_ptr(), gate.data_ptr(), out.data_ptr(), M, W, D,
+                                                         _lib.stream_ptr()), "gated_pool_fwd")
+        ctx.save_for_backward(kv, gate, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        kv, gate, out = ctx.saved_tensors
+        M, W, D = kv.shape
+        g = g.contiguous().float()
+        d_kv, d_gate = torch.empty_like(kv), torch.empty_like(gate)
+        _lib.check_rc(_lib.cuda_lib().axb_gated_pool_bwd(kv.data_ptr(), gate.data_ptr(), out.data_ptr(), g.data_ptr(),
+                                                         d_kv.data_ptr(), d_gate.data_ptr(), M, W, D, _lib.stream_ptr()),
+                      "gated_pool_bwd")
+        return d_kv, d_gate
+
+
+def gated_softmax_pool(kv, gate):
+    """``(kv * softmax(gate, dim=-2)).sum(-2)`` for [..., W, D] inputs in fp32 (the window pooling of DeepSeek-V4's
+    compressors), one pass forward, probabilities recomputed in the backward pass."""
+    if kv.is_cuda:
+        lead = kv.shape[:-2]
+        W, D = kv.shape[-2:]
+        out = _GatedPool.apply(kv.float().reshape(-1, W, D).contiguous(), gate.float().reshape(-1, W, D).contiguous())
+        return out.reshape(*lead, D)
+    return (kv.float() * gate.float().softmax(dim=-2)).sum(-2)

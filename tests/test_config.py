@@ -264,3 +264,16 @@ def test_every_example_config_passes_validation():
             raw = yaml.safe_load(fh)
         cfg = load_cfg(raw)
         assert cfg["sequence_len"] > 0 and cfg["output_dir"], f
+
+
+def test_xielu_and_gated_pool_reference_paths():
+    import torch
+
+    from axolotl_b200.ops import functional as Fn
+
+    x = torch.tensor([-3.0, -1e-7, 0.0, 0.5, 2.0])
+    y = Fn.xielu(x, torch.tensor([0.8]), torch.tensor([0.8]), 0.5, -1e-6)
+    want = torch.where(x > 0, 0.8 * x * x + 0.5 * x, 0.8 * (torch.expm1(torch.clamp(x, max=-1e-6)) - x) + 0.5 * x)
+    assert torch.allclose(y, want)
+    kv, gate = torch.randn(2, 5, 4, 7), torch.randn(2, 5, 4, 7)
+    assert torch.allclose(Fn.gated_softmax_pool(kv, gate), (kv * gate.softmax(-2)).sum(-2), atol=1e-6)

@@ -1253,3 +1253,107 @@ def test_head_width_512_runs_the_blocked_path_and_matches_fp32_reference():
     ref.backward(g.float().cpu())
     assert _rel_err(out.float().cpu(), ref) < 2e-2
     assert _rel_err(qkv.grad.float().cpu(), x.grad) < 3e-2
+
+
+def test_xielu_kernel_matches_definition_forward_and_backward():
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(80)
+    x = (torch.randn(777, 1031, device="cuda") * 2).bfloat16().requires_grad_(True)
+    ap = torch.tensor([0.9], device="cuda", requires_grad=True)
+    an = torch.tensor([1.3], device="cuda", requires_grad=True)
+    g = torch.randn(777, 1031, device="cuda").bfloat16()
+    y = Fn.xielu(x, ap, an, 0.5, -1e-6)
+    y.backward(g)
+    xr = x.detach().float().cpu().requires_grad_(True)
+    apr, anr = ap.detach().cpu().requires_grad_(True), an.detach().cpu().requires_grad_(True)
+    yr = Fn.xielu(xr, apr, anr, 0.5, -1e-6)
+    yr.backward(g.float().cpu())
+    assert _rel_err(y.float().cpu(), yr) < 1e-2
+    assert _rel_err(x.grad.float().cpu(), xr.grad) < 1e-2
+    assert abs(ap.grad.item() - apr.grad.item()) < 2e-2 * abs(apr.grad.item()) + 1.0
+    assert abs(an.grad.item() - anr.grad.item()) < 2e-2 * abs(anr.grad.item()) + 1.0
+
+
+def test_gated_softmax_pool_kernel_matches_torch():
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(81)
+    kv = torch.randn(3, 41, 8, 96, device="cuda", requires_grad=True)
+    gate = (torch.randn(3, 41, 8, 96, device="cuda") * 3).requires_grad_(True)
+    out = Fn.gated_softmax_pool(kv, gate)
+    g = torch.randn_like(out)
+    out.backward(g)
+    kr, gr = kv.detach().cpu().requires_grad_(True), gate.detach().cpu().requires_grad_(True)
+    ref = Fn.gated_softmax_pool(kr, gr)
+    ref.backward(g.cpu())
+    assert torch.allclose(out.cpu(), ref, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(kv.grad.cpu(), kr.grad, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(gate.grad.cpu(), gr.grad, atol=1e-5, rtol=1e-4)
+
+
+_GPU_FAMILIES = {
+    "falcon_h1": dict(model_type="falcon_h1", mamba_d_ssm=512, mamba_n_heads=8, mamba_d_head=64, mamba_n_groups=2, mamba_d_state=16,
+                      mamba_d_conv=4, mamba_chunk_size=64, mamba_rms_norm=True, mamba_norm_before_gate=False,
+                      ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3], mlp_multipliers=[0.8, 1.4], key_multiplier=0.8,
+                      ssm_out_multiplier=0.7, attention_out_multiplier=0.9),
+    "nemotron_h": dict(model_type="nemotron_h", layers_block_type=["mamba", "attention", "mlp", "mamba"], mlp_hidden_act="relu2",
+                       ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=64, n_groups=2, conv_kernel=4, chunk_size=64),
+    "bamba": dict(model_type="bamba", attn_layer_indices=[1], mamba_n_heads=8, mamba_d_head="auto", mamba_n_groups=1, mamba_d_state=16,
+                  mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=64),
+    "qwen3_5_moe_text": dict(model_type="qwen3_5_moe_text", num_hidden_layers=4, linear_num_value_heads=4, linear_num_key_heads=2,
+                             linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4, num_experts=8,
+                             num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128),
+    "lfm2": dict(model_type="lfm2", num_hidden_layers=3, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3,
+                 block_auto_adjust_ff_dim=False, tie_word_embeddings=True),
+    "cohere2": dict(model_type="cohere2", num_hidden_layers=4, logit_scale=0.25, tie_word_embeddings=True, sliding_window=128,
+                    layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "starcoder2": dict(model_type="starcoder2", use_bias=True, sliding_window=256, tie_word_embeddings=True),
+    "nemotron": dict(model_type="nemotron"),
+    "apertus": dict(model_type="apertus", rope_parameters={"rope_type": "default", "rope_theta": 10000.0}),
+    "glm4": dict(model_type="glm4", partial_rotary_factor=0.5, attention_bias=True),
+    "olmo3": dict(model_type="olmo3", num_hidden_layers=4, sliding_window=128,
+                  layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "seed_oss": dict(model_type="seed_oss", attention_bias=True, attention_out_bias=True),
+    "ministral3": dict(model_type="ministral3"),
+    "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", intermediate_size=128, num_experts=8, moe_topk=2),
+    "ernie4_5_moe": dict(model_type="ernie4_5_moe", moe_intermediate_size=128, moe_num_experts=8, moe_k=2, moe_num_shared_experts=1,
+                         moe_layer_start_index=1, moe_layer_interval=1, moe_layer_end_index=-1),
+    "glm4_moe": dict(model_type="glm4_moe", moe_intermediate_size=128, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+                     first_k_dense_replace=1, use_qk_norm=True, attention_bias=True),
+    "minimax_m2": dict(model_type="minimax_m2", intermediate_size=128, num_local_experts=8, num_experts_per_tok=2),
+    "granitemoeshared": dict(model_type="granitemoeshared", intermediate_size=128, shared_intermediate_size=256, num_local_experts=8,
+                             num_experts_per_tok=2, tie_word_embeddings=True, embedding_multiplier=3.0, attention_multiplier=0.125,
+                             residual_multiplier=0.5, logits_scaling=2.0),
+}
+
+
+@pytest.mark.parametrize("family", sorted(_GPU_FAMILIES))
+def test_newer_families_on_the_device_match_cpu_fp32(family):
+    """One forward / backward of each newer family in bf16 through the device kernels against the same weights in fp32
+    on the CPU (packed documents; loss and two gradients)."""
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.transformer import CausalLM
+    torch.manual_seed(90)
+    d = dict(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=64, tie_word_embeddings=False, max_position_embeddings=2048)
+    d.update(_GPU_FAMILIES[family])
+    cfg = ModelConfig.from_hf_dict(d)
+    ref = CausalLM(cfg, dtype=torch.float32).init_weights(7)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    dev = CausalLM(cfg, dtype=torch.bfloat16, device=_dev())
+    dev.load_state_dict(ref.state_dict())
+    lens = [150, 234]
+    ids = torch.cat([torch.randint(3, cfg.vocab_size, (l,)) for l in lens])[None]
+    pos = torch.cat([torch.arange(l) for l in lens])[None].to(torch.int32)
+    out_d = dev(ids, pos, ids.clone())
+    out_d.loss.backward()
+    _check_status()
+    out_c = ref(ids, pos, ids.clone())
+    out_c.loss.backward()
+    assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item()), (out_d.loss.item(), out_c.loss.item())
+    gd = dev.embed_tokens.grad.float().cpu()
+    assert _rel_err(gd, ref.embed_tokens.grad) < 0.15, _rel_err(gd, ref.embed_tokens.grad)
+    name = next(n for n, p in ref.named_parameters() if n.startswith("layers.0.") and p.dim() == 2 and p.grad is not None)
+    gl = dict(dev.named_parameters())[name].grad.float().cpu()
+    assert _rel_err(gl, dict(ref.named_parameters())[name].grad) < 0.15, name

@@ -17,9 +17,9 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "mistral4")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
-MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa")      # multi-head latent attention
+MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
 QWEN3_NEXT_TYPES = ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text")   # Gated DeltaNet hybrids
 ZERO_CENTERED_NORM_TYPES = GEMMA_TYPES + QWEN3_NEXT_TYPES     # RMSNorm weights stored as w, applied as 1 + w
@@ -260,7 +260,18 @@ class ModelConfig:
             d["mlp_layer_types"] = list(types)
             d["mlp_only_layers"] = [i for i, t in enumerate(types) if t != "sparse"]
             d["rope_interleave"] = False                        # split-half rotation
-        if mt in ("deepseek_v2", "deepseek_v3"):
+        if mt == "mistral4":           # latent attention (128-wide q/k and v), position-scaled queries, softmax group routing
+            for key, default in (("qk_nope_head_dim", 64), ("qk_rope_head_dim", 64), ("v_head_dim", 128), ("kv_lora_rank", 256),
+                                 ("q_lora_rank", 1024), ("n_shared_experts", 1), ("routed_scaling_factor", 1.0), ("n_group", 1),
+                                 ("topk_group", 1), ("rope_interleave", True)):
+                d.setdefault(key, default)
+            d.setdefault("num_experts_per_tok", 4)
+            d.setdefault("norm_topk_prob", True)
+            if not d.get("rope_parameters") and not d.get("rope_scaling"):
+                d["rope_parameters"] = {"rope_type": "yarn", "rope_theta": 10000.0, "factor": 128.0,
+                                        "original_max_position_embeddings": 8192, "beta_fast": 32.0, "beta_slow": 1.0,
+                                        "mscale_all_dim": 1.0, "mscale": 1.0, "llama_4_scaling_beta": 0.1}
+        if mt in ("deepseek_v2", "deepseek_v3", "mistral4"):
             d["num_experts"] = d.get("n_routed_experts") or 0
             d.setdefault("norm_topk_prob", mt == "deepseek_v3")
             d["head_dim"] = (d.get("qk_nope_head_dim") or 128) + (d.get("qk_rope_head_dim") or 64)
@@ -686,6 +697,7 @@ _ARCH_NAME = {
     "ernie4_5_moe": "Ernie4_5_MoeForCausalLM",
     "apertus": "ApertusForCausalLM",
     "lfm2": "Lfm2ForCausalLM",
+    "mistral4": "Mistral4ForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",

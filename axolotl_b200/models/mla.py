@@ -43,7 +43,7 @@ class MLAttention(nn.Module):
         self.o_proj = FusedLinear(self.Hq * self.Dv, [H], ["o_proj"], bias=bias, dtype=dtype, device=device)
         self.scale = self.D ** -0.5
         rs = cfg.rope_scaling or {}
-        if rs.get("rope_type", rs.get("type")) == "yarn" and rs.get("mscale_all_dim"):
+        if rs.get("rope_type", rs.get("type")) == "yarn" and rs.get("mscale_all_dim") and cfg.model_type != "mistral4":
             m = 0.1 * float(rs["mscale_all_dim"]) * math.log(float(rs["factor"])) + 1.0 if float(rs["factor"]) > 1 else 1.0
             self.scale = self.scale * m * m
         # the checkpoints store the rotary part with interleaved (real, imaginary) pairs (V2 rotates complex numbers,
@@ -52,6 +52,10 @@ class MLAttention(nn.Module):
         d = self.d_rope
         perm = torch.cat([torch.arange(0, d, 2), torch.arange(1, d, 2)])
         self.register_buffer("pe_perm", perm.to(device) if device is not None else perm, persistent=False)
+        # Mistral 4: queries grow with the position, 1 + beta * log(1 + floor(pos / original context))
+        rp = ex.get("rope_parameters") or cfg.rope_scaling or {}
+        self.q_pos_scale = (float(rp["llama_4_scaling_beta"]), float(rp.get("original_max_position_embeddings") or 1)) \
+            if cfg.model_type == "mistral4" and rp.get("llama_4_scaling_beta") is not None else None
         self.window, self.use_rope, self.softcap = 0, True, 0.0
         self.register_buffer("local_inv_freq", None, persistent=False)
 
@@ -76,7 +80,11 @@ class MLAttention(nn.Module):
         pe = Fn.rope_qk_(pe, positions, inv_freq, Hq, 1, dr, attn_scale)
         q_pe = pe[:, : Hq * dr].reshape(T, Hq, dr)
         k_pe = pe[:, Hq * dr:(Hq + 1) * dr].reshape(T, 1, dr).expand(T, Hq, dr)
-        qf = torch.cat([q[..., :dn], q_pe], -1).reshape(T, Hq * (dn + dr))
+        qf = torch.cat([q[..., :dn], q_pe], -1)
+        if self.q_pos_scale is not None:
+            beta, orig = self.q_pos_scale
+            qf = (qf.float() * (1.0 + beta * torch.log1p(torch.floor(positions.float() / orig)))[:, None, None]).to(q.dtype)
+        qf = qf.reshape(T, Hq * (dn + dr))
         kf = torch.cat([kv[..., :dn], k_pe], -1).reshape(T, Hq * (dn + dr))
         return torch.cat([qf, kf, kv[..., dn:].reshape(T, Hq * Dv)], 1)
 

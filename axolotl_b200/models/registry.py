@@ -147,6 +147,9 @@ _register("GptOss", ("gpt_oss",),
            NVFP4: Experimental("MXFP4 checkpoints are dequantised at load; NVFP4 re-quantisation of biased experts is unverified.")},
           notes=("attention sinks are applied as a rescale of the kernel's output and log-sum-exp",))
 _LATENT = {TP: _MOE_NO_TP, CP: _WIDE_NO_CP, KV_CACHE: Unsupported("A latent-attention KV cache is not built; generation recomputes the sequence.")}
+_register("Mistral4", ("mistral4",), {TP: _MOE_NO_TP, CP: Experimental("128-wide latent-attention heads take the context-parallel kernels; not exercised on ranks."),
+                                     KV_CACHE: Unsupported("A latent-attention KV cache is not built; generation recomputes the sequence.")},
+          notes=("latent attention with 128-wide q/k and v runs the standard varlen attention kernels",))
 _register("DeepSeek", ("deepseek_v2", "deepseek_v3"), _LATENT, head_dims=None,
           notes=("latent attention expands k / v per head and runs the 192/128 wide-head kernels",))
 _register("GlmMoeDsa", ("glm_moe_dsa",), _LATENT, head_dims=None,

@@ -297,7 +297,7 @@ class DecoderLayer(nn.Module):
             from .dsa import SparseMLAttention
 
             self.self_attn = SparseMLAttention(cfg, dtype, device)
-        elif cfg.model_type in ("deepseek_v2", "deepseek_v3"):
+        elif cfg.model_type in ("deepseek_v2", "deepseek_v3", "mistral4"):
             from .mla import MLAttention
 
             self.self_attn = MLAttention(cfg, dtype, device)
@@ -708,7 +708,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2"))
+                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2", "mistral4"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

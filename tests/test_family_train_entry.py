@@ -106,6 +106,10 @@ FAMILIES = {
     "lfm2": dict(model_type="lfm2", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
                  num_key_value_heads=2, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3,
                  block_auto_adjust_ff_dim=False, tie_word_embeddings=True, max_position_embeddings=256),
+    "mistral4": dict(model_type="mistral4", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4, n_shared_experts=1,
+                     num_experts_per_tok=2, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=8,
+                     qk_rope_head_dim=8, v_head_dim=16, tie_word_embeddings=False, max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

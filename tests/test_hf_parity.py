@@ -896,6 +896,14 @@ LLAMA_LIKE = {
                  num_key_value_heads=2, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3, norm_eps=1e-5,
                  block_auto_adjust_ff_dim=True, block_multiple_of=16, block_ffn_dim_multiplier=1.0, tie_word_embeddings=True,
                  max_position_embeddings=256, pad_token_id=0),
+    "mistral4": dict(model_type="mistral4", vocab_size=300, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,
+                     num_experts_per_tok=3, n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
+                     qk_nope_head_dim=8, qk_rope_head_dim=8, v_head_dim=16, routed_scaling_factor=1.5, norm_topk_prob=True,
+                     rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0, rope_interleave=True,
+                     rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
+                                      "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0,
+                                      "llama_4_scaling_beta": 0.3, "partial_rotary_factor": 0.5}),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,
@@ -926,8 +934,10 @@ def test_llama_like_variants_match_hf(tmp_path, family):
             if "norm" in n and n.endswith("weight"):
                 p.uniform_(0.5, 1.5)
     hf_io.save_pretrained(ours, str(tmp_path / "m"))
-    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
-                                                                 attn_implementation="eager")
+    loader = transformers.AutoModelForCausalLM
+    if family == "mistral4":            # (not in the auto mapping of this transformers version)
+        from transformers.models.mistral4.modeling_mistral4 import Mistral4ForCausalLM as loader
+    hf_model = loader.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32, attn_implementation="eager")
     hf_model.eval()
     lens = [23, 30]
     ids, pos = _packed_inputs(300, lens)

@@ -51,7 +51,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     glm = model.config.rope_pairs_interleaved() if hasattr(model.config, "rope_pairs_interleaved") else False
     hunyuan = getattr(model.config, "model_type", "") in ("hunyuan_v1_dense", "hunyuan_v1_moe")
     apertus = getattr(model.config, "model_type", "") == "apertus"
-    lfm2 = getattr(model.config, "model_type", "") == "lfm2"
+    lfm2 = getattr(model.config, "model_type", "") in ("lfm2", "lfm2_moe")
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     for name, t in named_tensors:
         if hunyuan:
@@ -361,7 +361,8 @@ def _deinterleave_rows(w, heads, D, inverse=False):
 
 
 # LFM2 names (checkpoint, ours); the short-convolution operator sits where other families keep their attention module
-_LFM2_NAMES = ((".operator_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
+_LFM2_NAMES = ((".feed_forward.expert_bias", ".mlp.gate.e_score_correction_bias"), (".feed_forward.gate.", ".mlp.gate."),
+               (".feed_forward.experts.", ".mlp.experts."), (".operator_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
                (".feed_forward.w1.", ".mlp.gate_proj."), (".feed_forward.w3.", ".mlp.up_proj."), (".feed_forward.w2.", ".mlp.down_proj."),
                (".self_attn.out_proj.", ".self_attn.o_proj."), (".self_attn.q_layernorm.", ".self_attn.q_norm."),
                (".self_attn.k_layernorm.", ".self_attn.k_norm."), ("model.embedding_norm.", "model.norm."))
@@ -719,7 +720,7 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     if mt_ == "ernie4_5_moe":
         return {k.replace(".gate.e_score_correction_bias", ".gate.moe_statics.e_score_correction_bias"):
                 (v.reshape(1, -1) if k.endswith("e_score_correction_bias") else v) for k, v in sd.items()}
-    if mt_ == "lfm2":
+    if mt_ in ("lfm2", "lfm2_moe"):
         return _lfm2_state_dict(model, sd)
     if mt_ == "apertus":
         out = {k.replace(".input_layernorm.", ".attention_layernorm.").replace(".post_attention_layernorm.", ".feedforward_layernorm."): v

@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "mistral4")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -174,7 +174,11 @@ class ModelConfig:
             end = d.get("moe_layer_end_index")
             end = L - 1 if end in (None, -1) else end
             d["mlp_only_layers"] = [i for i in range(L) if not ((i + 1) % every == 0 and start <= i <= end)]
-        if mt == "lfm2":               # gated short convolutions beside a few attention layers (q / k norms per head)
+        if mt == "lfm2_moe":           # LFM2 with routed experts after the first dense layers (sigmoid scores, selection bias)
+            d["block_auto_adjust_ff_dim"] = False
+            d["mlp_only_layers"] = list(range(int(d.get("num_dense_layers") or 0)))
+            d.setdefault("norm_topk_prob", True)
+        if mt in ("lfm2", "lfm2_moe"):   # gated short convolutions beside a few attention layers (q / k norms per head)
             L = d.get("num_hidden_layers", 0)
             d["rms_norm_eps"] = d.get("norm_eps", 1e-5)
             d["qk_norm"] = True
@@ -328,6 +332,9 @@ class ModelConfig:
             d["intermediate_size"] = d.pop("moe_intermediate_size") or d.get("intermediate_size")
             d["intermediate_size_mlp"] = extra.get("dense_intermediate_size") or d["intermediate_size"]
             d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
+        if self.model_type == "lfm2_moe":
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
         if self.model_type == "hunyuan_v1_moe":
@@ -498,7 +505,7 @@ class ModelConfig:
 
     def layer_kind(self, idx: int) -> str:
         """"attention" or "mamba" (hybrid families list their layers in ``layer_types``)."""
-        if self.model_type == "lfm2":
+        if self.model_type in ("lfm2", "lfm2_moe"):
             return "attention" if (self.extra or {})["layer_types"][idx] == "full_attention" else "shortconv"
         if self.model_type not in ("granitemoehybrid", "bamba", "nemotron_h") + QWEN3_NEXT_TYPES:
             return "attention"
@@ -698,6 +705,7 @@ _ARCH_NAME = {
     "apertus": "ApertusForCausalLM",
     "lfm2": "Lfm2ForCausalLM",
     "mistral4": "Mistral4ForCausalLM",
+    "lfm2_moe": "Lfm2MoeForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",
     "qwen3_next": "Qwen3NextForCausalLM",

@@ -92,7 +92,7 @@ def _checkpoint_renames(model):
             pairs.append((f"{pre}.self_attn.", f"{pre}.linear_attn."))
         if mt in ("bamba", "falcon_h1"):
             pairs.append((f"{pre}.mlp.", f"{pre}.feed_forward."))
-        if mt == "lfm2":
+        if mt in ("lfm2", "lfm2_moe"):
             if mixer == "ShortConv":
                 pairs.append((f"{pre}.self_attn.", f"{pre}.conv."))
             pairs += [(f"{pre}.self_attn.o_proj", f"{pre}.self_attn.out_proj"), (f"{pre}.mlp.gate_proj", f"{pre}.feed_forward.w1"),

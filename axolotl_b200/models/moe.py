@@ -231,7 +231,7 @@ class SparseMoE(nn.Module):
             self.shared_experts = self._llama4_shared
             del self._llama4_shared
         self.e_score_correction_bias = None
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe", "mistral4"):
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe", "mistral4", "lfm2_moe"):
             from .transformer import MLP
 
             ex = cfg.extra or {}
@@ -244,7 +244,8 @@ class SparseMoE(nn.Module):
                                  norm_topk_prob=bool(cfg.norm_topk_prob), scale=float(ex.get("routed_scaling_factor") or 1.0))
             if cfg.model_type == "mistral4":      # softmax scores, groups rated by their two best, no selection bias
                 self.deepseek.update(scoring="softmax", n_group=int(ex.get("n_group") or 1), group_score="top2")
-            if (v3 and cfg.model_type != "mistral4") or cfg.model_type == "ernie4_5_moe":
+            if (v3 and cfg.model_type not in ("mistral4", "lfm2_moe")) or cfg.model_type == "ernie4_5_moe" \
+                    or (cfg.model_type == "lfm2_moe" and ex.get("use_expert_bias", True)):
                 self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
                                                             requires_grad=False)
             n_shared = int(ex.get("n_shared_experts") or ex.get("moe_num_shared_experts") or 0)

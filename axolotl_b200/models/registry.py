@@ -165,6 +165,7 @@ _register("Bamba", ("bamba",), {**_HYBRID, **_DENSE})
 _register("NemotronH", ("nemotron_h",), {**_HYBRID, **_DENSE},
           notes=("blocks of type `moe` (latent, non-gated experts) are rejected when the config is read",))
 _register("FalconH1", ("falcon_h1",), {**_HYBRID, **_DENSE})
+_register("Lfm2Moe", ("lfm2_moe",), {TP: _MIXER_NO_TP, KV_CACHE: _MIXER_NO_KV})
 _register("Lfm2", ("lfm2",), {**_DENSE, TP: _MIXER_NO_TP, KV_CACHE: _MIXER_NO_KV,
                              CP: Experimental("The convolution halo crosses chunk borders like the Mamba-2 one; not exercised on ranks.")})
 _register("Qwen3Next", ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"),

@@ -349,7 +349,7 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("granitemoeshared", "granitemoehybrid"):     # dense variant: the "shared" MLP alone
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("shared_intermediate_size") or cfg.intermediate_size),
                            cfg.hidden_act, False, dtype, device, fused_names=True)
-        elif cfg.model_type == "lfm2":                 # its own width rule (two thirds, rounded up to a multiple)
+        elif cfg.model_type in ("lfm2", "lfm2_moe"):   # its own width rule (two thirds, rounded up to a multiple)
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("mlp_width") or cfg.intermediate_size), "silu", False,
                            dtype, device)
         elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus"):      # up -> activation -> down, no gate
@@ -708,7 +708,7 @@ class CausalLM(nn.Module):
         sequence is recomputed per token (kept as the oracle of the cached path)."""
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
                      and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2", "mistral4"))
+                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2", "lfm2_moe", "mistral4"))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

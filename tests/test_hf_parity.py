@@ -904,6 +904,11 @@ LLAMA_LIKE = {
                      rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
                                       "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0,
                                       "llama_4_scaling_beta": 0.3, "partial_rotary_factor": 0.5}),
+    "lfm2_moe": dict(model_type="lfm2_moe", vocab_size=300, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, layer_types=["conv", "full_attention", "conv"],
+                     conv_L_cache=3, num_experts=4, num_experts_per_tok=2, num_dense_layers=1, norm_eps=1e-5, use_expert_bias=True,
+                     routed_scaling_factor=1.5, norm_topk_prob=True, tie_word_embeddings=True, max_position_embeddings=256,
+                     pad_token_id=0),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,

@@ -53,6 +53,7 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     apertus = getattr(model.config, "model_type", "") == "apertus"
     lfm2 = getattr(model.config, "model_type", "") in ("lfm2", "lfm2_moe")
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
+    phi = getattr(model.config, "model_type", "") == "phi"
     for name, t in named_tensors:
         if hunyuan:
             name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.") \
@@ -83,6 +84,13 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         name = name.replace(".gate.moe_statics.e_score_correction_bias", ".gate.e_score_correction_bias")
         if starcoder2:
             name = name.replace(".mlp.c_fc.", ".mlp.up_proj.").replace(".mlp.c_proj.", ".mlp.down_proj.")
+        if phi:
+            name = name.replace(".mlp.fc1.", ".mlp.up_proj.").replace(".mlp.fc2.", ".mlp.down_proj.") \
+                .replace(".self_attn.dense.", ".self_attn.o_proj.").replace("model.final_layernorm.", "model.norm.")
+            if name == "lm_head.bias":
+                model.lm_head_bias.copy_(t)
+                filled.add(name)
+                continue
         if glm:
             name, t = _glm_in(model, name, t)
         if llama4:
@@ -640,7 +648,11 @@ def _granite_hybrid_state_dict(model, sd):
 
 def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     """Model tensors under HF names (views where possible; the writer makes them contiguous)."""
-    sd = {"model.embed_tokens.weight": model.embed_tokens.detach(), "model.norm.weight": model.norm.weight.detach()}
+    sd = {"model.embed_tokens.weight": model.embed_tokens.detach()}
+    if model.norm.weight is not None:
+        sd["model.norm.weight"] = model.norm.weight.detach()
+    if getattr(model, "lm_head_bias", None) is not None:
+        sd["lm_head.bias"] = model.lm_head_bias.detach()
     if model.lm_head is not None:
         sd["lm_head.weight"] = model.lm_head.detach()
     if getattr(model.norm, "bias", None) is not None:
@@ -680,7 +692,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                     sd[f"model.{parent}.{sub}.bias"] = m.bias.detach()[r0:r1]
         elif name.endswith(("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm",
                             "q_norm", "k_norm", "q_a_layernorm", "kv_a_layernorm")):
-            sd[f"model.{name}.weight"] = m.weight.detach()
+            if m.weight is not None:
+                sd[f"model.{name}.weight"] = m.weight.detach()
             if getattr(m, "bias", None) is not None:
                 sd[f"model.{name}.bias"] = m.bias.detach()
         elif isinstance(m, Experts):
@@ -731,6 +744,10 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
             out[f"model.layers.{i}.mlp.act_fn.beta"] = torch.tensor(layer.mlp.xielu_beta, dtype=layer.mlp.alpha_p.dtype)
             out[f"model.layers.{i}.mlp.act_fn.eps"] = torch.tensor(layer.mlp.xielu_eps, dtype=layer.mlp.alpha_p.dtype)
         return out
+    if mt_ == "phi":
+        return {k.replace(".mlp.up_proj.", ".mlp.fc1.").replace(".mlp.down_proj.", ".mlp.fc2.")
+                .replace(".self_attn.o_proj.", ".self_attn.dense.").replace("model.norm.", "model.final_layernorm."): v
+                for k, v in sd.items()}
     if getattr(model.config, "model_type", "") == "starcoder2":
         return {k.replace(".mlp.up_proj.", ".mlp.c_fc.").replace(".mlp.down_proj.", ".mlp.c_proj."): v for k, v in sd.items()}
     return sd

@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -228,6 +228,15 @@ class ModelConfig:
             d.setdefault("attention_out_bias", False)
         if mt == "arcee":
             d.setdefault("hidden_act", "relu2")
+        if mt == "olmo":               # LayerNorm without parameters, optional clamp of q / k / v
+            d["rms_norm_eps"] = 1e-5
+        if mt == "phi":                # one LayerNorm per layer, attention and MLP side by side, biases everywhere incl. the head
+            d["rms_norm_eps"] = d.get("layer_norm_eps", 1e-5)
+            d["attention_bias"] = d["mlp_bias"] = True
+            d.setdefault("hidden_act", "gelu_new")
+            d.setdefault("partial_rotary_factor", (d.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))
+            if d.get("qk_layernorm"):
+                raise ValueError("phi: qk_layernorm (per-head LayerNorm of q / k) is not supported")
         if mt == "nemotron":           # LayerNorm with (1 + w) and bias, half of a head rotates, ungated squared-ReLU MLP
             d["rms_norm_eps"] = d.get("norm_eps", 1e-5)
             d.setdefault("partial_rotary_factor", 0.5)
@@ -428,12 +437,12 @@ class ModelConfig:
     def norm_kind(self) -> str:
         """"rms", or a mean-subtracting LayerNorm: with bias (StarCoder 2), stored as w - 1 with bias (Nemotron),
         weight only (Cohere)."""
-        return {"starcoder2": "layernorm", "nemotron": "layernorm1p", "cohere": "layernorm_nobias",
-                "cohere2": "layernorm_nobias"}.get(self.model_type, "rms")
+        return {"starcoder2": "layernorm", "nemotron": "layernorm1p", "cohere": "layernorm_nobias", "phi": "layernorm",
+                "cohere2": "layernorm_nobias", "olmo": "layernorm_fixed"}.get(self.model_type, "rms")
 
     def parallel_block(self) -> bool:
         """Cohere: attention and MLP read the same normalised input and are added to the stream together."""
-        return self.model_type in ("cohere", "cohere2")
+        return self.model_type in ("cohere", "cohere2", "phi")
 
     def post_norm_only(self) -> bool:
         """OLMo 2 / 3: no norm on a branch's input, one on its output."""
@@ -705,6 +714,8 @@ _ARCH_NAME = {
     "apertus": "ApertusForCausalLM",
     "lfm2": "Lfm2ForCausalLM",
     "mistral4": "Mistral4ForCausalLM",
+    "olmo": "OlmoForCausalLM",
+    "phi": "PhiForCausalLM",
     "lfm2_moe": "Lfm2MoeForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",

@@ -66,14 +66,16 @@ class LayerNorm(nn.Module):
     bias; ``offset`` = 1 is Nemotron's stored-as-(w - 1) convention). Runs as a library op in fp32: these families are
     outside the fused add+RMSNorm kernel."""
 
-    def __init__(self, dim, eps=1e-5, dtype=torch.bfloat16, device=None, bias=True, offset=0.0):
+    def __init__(self, dim, eps=1e-5, dtype=torch.bfloat16, device=None, bias=True, offset=0.0, affine=True):
         super().__init__()
         self.offset = float(offset)
-        self.weight = nn.Parameter(torch.full((dim,), 1.0 - self.offset, dtype=dtype, device=device))
-        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device)) if bias else None
+        self.weight = nn.Parameter(torch.full((dim,), 1.0 - self.offset, dtype=dtype, device=device)) if affine else None
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device)) if (bias and affine) else None
         self.eps = eps
 
     def plain(self, x):
+        if self.weight is None:          # OLMo: no learnable scale or shift
+            return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), None, None, self.eps).to(x.dtype)
         w = self.weight.float() + self.offset if self.offset else self.weight.float()
         b = self.bias.float() if self.bias is not None else None
         return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w, b, self.eps).to(x.dtype)
@@ -93,7 +95,7 @@ def make_norm(cfg, dim, dtype, device, offset=0.0):
     if kind == "rms":
         return RMSNorm(dim, cfg.rms_norm_eps, dtype, device, offset=offset)
     return LayerNorm(dim, cfg.rms_norm_eps, dtype, device, bias=kind != "layernorm_nobias",
-                     offset=1.0 if kind == "layernorm1p" else 0.0)
+                     offset=1.0 if kind == "layernorm1p" else 0.0, affine=kind != "layernorm_fixed")
 
 
 class FusedLinear(nn.Module):

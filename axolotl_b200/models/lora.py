@@ -99,6 +99,9 @@ def _checkpoint_renames(model):
                       (f"{pre}.mlp.up_proj", f"{pre}.feed_forward.w3"), (f"{pre}.mlp.down_proj", f"{pre}.feed_forward.w2")]
         if mt == "hunyuan_v1_moe":
             pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.mlp.shared_mlp."))
+        if mt == "phi":
+            pairs += [(f"{pre}.mlp.up_proj", f"{pre}.mlp.fc1"), (f"{pre}.mlp.down_proj", f"{pre}.mlp.fc2"),
+                      (f"{pre}.self_attn.o_proj", f"{pre}.self_attn.dense")]
         if mt == "starcoder2":
             pairs.append((f"{pre}.mlp.up_proj", f"{pre}.mlp.c_fc"))
             pairs.append((f"{pre}.mlp.down_proj", f"{pre}.mlp.c_proj"))

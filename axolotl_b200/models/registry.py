@@ -121,7 +121,7 @@ _register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's f
           notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))
 _register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms span all heads of the unsharded projection.")},
           notes=("norms sit on the branch outputs; q / k RMSNorm over all heads runs as separate launches before RoPE",))
-_register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2"),
+_register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2", "olmo", "phi"),
           {**_DENSE, TP: Unsupported("These graphs have no sharding rule here.")},
           notes=("mean-subtracting norms run as library ops in fp32 (outside the fused add+RMSNorm kernel)",))
 _register("Arcee", ("arcee", "apertus"), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})

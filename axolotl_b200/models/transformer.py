@@ -48,7 +48,7 @@ class Attention(nn.Module):
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
-        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3", "starcoder2", "cohere", "cohere2", "nemotron")
+        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3", "starcoder2", "cohere", "cohere2", "nemotron", "phi")
                   else bool((cfg.extra or {}).get("attention_out_bias")) if cfg.model_type == "seed_oss" else False)
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=o_bias, dtype=dtype, device=device)
         # gpt-oss: one learned "sink" logit per head in every softmax denominator
@@ -60,6 +60,7 @@ class Attention(nn.Module):
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
+        self.clip_qkv = float((cfg.extra or {}).get("clip_qkv") or 0.0) if cfg.model_type == "olmo" else 0.0
         self.norm_after_rope = cfg.model_type in ("hunyuan_v1_dense", "hunyuan_v1_moe")   # HunYuan: per-head q / k norms act on the ROTATED vectors
         self.full_qk_norm = cfg.model_type in ("olmoe", "olmo2", "olmo3", "minimax_m2")   # OLMo family: q / k norms over ALL heads at once
         if self.full_qk_norm:
@@ -90,6 +91,8 @@ class Attention(nn.Module):
     def pre(self, x, positions, inv_freq, attn_scale):
         """Projections, q/k norms and rotary embedding: everything before the attention kernel."""
         qkv = self.qkv_proj(x)
+        if self.clip_qkv:
+            qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
         per_head_norm = self.q_norm is not None and not self.full_qk_norm
         if self.full_qk_norm:
             nq, nk = self.Hq * self.D, self.Hk * self.D
@@ -199,7 +202,7 @@ class PlainMLP(nn.Module):
         super().__init__()
         self.up_proj = FusedLinear(hidden, [inter], ["up_proj"], bias=bias, dtype=dtype, device=device)
         self.down_proj = FusedLinear(inter, [hidden], ["down_proj"], bias=bias, dtype=dtype, device=device)
-        if act not in ("relu2", "relu", "gelu", "silu", "gelu_pytorch_tanh", "xielu"):
+        if act not in ("relu2", "relu", "gelu", "silu", "gelu_pytorch_tanh", "gelu_new", "xielu"):
             raise ValueError(f"activation '{act}' is not available for an ungated MLP")
         self.act = act
         if act == "xielu":       # stored through an inverse softplus, as the checkpoints do (alpha_p = 0.8, alpha_n = 0.8 - beta)
@@ -219,7 +222,7 @@ class PlainMLP(nn.Module):
             u = torch.relu(u)
         elif self.act == "gelu":
             u = torch.nn.functional.gelu(u)
-        elif self.act == "gelu_pytorch_tanh":
+        elif self.act in ("gelu_pytorch_tanh", "gelu_new"):
             u = torch.nn.functional.gelu(u, approximate="tanh")
         else:
             u = torch.nn.functional.silu(u)
@@ -352,7 +355,7 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("lfm2", "lfm2_moe"):   # its own width rule (two thirds, rounded up to a multiple)
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("mlp_width") or cfg.intermediate_size), "silu", False,
                            dtype, device)
-        elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus"):      # up -> activation -> down, no gate
+        elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus", "phi"):      # up -> activation -> down, no gate
             self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
@@ -428,6 +431,11 @@ class CausalLM(nn.Module):
             self.lm_head = None
         else:
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        # Phi: the output projection has a bias. It rides along as one extra hidden column (a constant 1 in the
+        # hidden states, the bias in the weight; padded to 8 columns for the GEMM), so that every consumer of
+        # (hidden states, output weight) - the chunked cross-entropy, log-prob and distillation paths, generation -
+        # sees it without knowing
+        self.lm_head_bias = nn.Parameter(torch.zeros(cfg.vocab_size, dtype=dtype, device=device)) if cfg.model_type == "phi" else None
         inv, scale = cfg.rope_inv_freq()
         self.register_buffer("inv_freq", inv.to(device) if device is not None else inv, persistent=False)
         self.attn_scale = scale
@@ -575,7 +583,10 @@ class CausalLM(nn.Module):
         return new_size
 
     def output_weight(self):
-        return self.embed_tokens if self.lm_head is None else self.lm_head
+        W = self.embed_tokens if self.lm_head is None else self.lm_head
+        if self.lm_head_bias is not None:
+            W = torch.cat([W, self.lm_head_bias[:, None].to(W.dtype), W.new_zeros(W.shape[0], 7)], 1)
+        return W
 
     def enable_gradient_checkpointing(self, flag=True, offload=None, selective=False, offload_dir=None):
         """``offload``: None keeps checkpointed layer inputs on the device; True / "legacy" /
@@ -672,6 +683,8 @@ class CausalLM(nn.Module):
         ls = cfg.multiplier("logits_scaling")
         if ls != 1.0:
             h = h / ls          # logits = (h W^T) / logits_scaling, applied on the narrow side
+        if self.lm_head_bias is not None:
+            h = torch.cat([h, h.new_ones(h.shape[0], 1), h.new_zeros(h.shape[0], 7)], 1)
         out = CausalLMOutput(hidden_states=h.view(B, S, -1))
         if captured is not None:
             if len(self.layers) in capture_hidden:

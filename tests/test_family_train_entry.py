@@ -9,6 +9,16 @@ from axolotl_b200.models.config import ModelConfig
 from axolotl_b200.models.transformer import CausalLM
 from axolotl_b200.train.run import train
 
+@pytest.fixture(autouse=True)
+def _no_plugins_left_over():
+    """Plugins are a process-wide registry; a run here must not inherit what an earlier test module registered."""
+    from axolotl_b200.plugins.base import PluginManager
+
+    PluginManager.reset()
+    yield
+    PluginManager.reset()
+
+
 FAMILIES = {
     "gemma2": dict(model_type="gemma2", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, query_pre_attn_scalar=16, sliding_window=32,
@@ -110,6 +120,14 @@ FAMILIES = {
                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4, n_shared_experts=1,
                      num_experts_per_tok=2, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=8,
                      qk_rope_head_dim=8, v_head_dim=16, tie_word_embeddings=False, max_position_embeddings=256),
+    "phi": dict(model_type="phi", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, tie_word_embeddings=False, max_position_embeddings=256),
+    "olmo": dict(model_type="olmo", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, clip_qkv=8.0, tie_word_embeddings=False, max_position_embeddings=256),
+    "lfm2_moe": dict(model_type="lfm2_moe", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                     num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, layer_types=["conv", "full_attention", "conv"],
+                     conv_L_cache=3, num_experts=4, num_experts_per_tok=2, num_dense_layers=1, tie_word_embeddings=True,
+                     max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

@@ -909,6 +909,12 @@ LLAMA_LIKE = {
                      conv_L_cache=3, num_experts=4, num_experts_per_tok=2, num_dense_layers=1, norm_eps=1e-5, use_expert_bias=True,
                      routed_scaling_factor=1.5, norm_topk_prob=True, tie_word_embeddings=True, max_position_embeddings=256,
                      pad_token_id=0),
+    "olmo": dict(model_type="olmo", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, clip_qkv=0.4, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
+    "phi": dict(model_type="phi", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, layer_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0,
+                resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,

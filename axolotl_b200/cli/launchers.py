@@ -199,11 +199,79 @@ class ModalCloud:
         return self._call(fn, config_yaml)
 
 
+_BASETEN_RUN_SH = """#!/bin/bash
+set -eux
+# multi-node jobs: keep NCCL off the container bridge and the loopback device
+export NCCL_SOCKET_IFNAME="^docker0,lo"
+export NCCL_TIMEOUT=1800000
+axolotl preprocess train.yaml
+axolotl train train.yaml --launcher ${AXOLOTL_LAUNCHER} ${AXOLOTL_LAUNCHER_ARGS}
+"""
+
+_BASETEN_JOB_PY = """# Training-job definition pushed with `truss train push`; reads cloud.yaml written next to it.
+import yaml
+from truss.base import truss_config
+from truss_train import definitions
+
+cloud = yaml.safe_load(open("cloud.yaml"))
+launcher_args = cloud.get("launcher_args") or []
+env = {"AXOLOTL_LAUNCHER": cloud.get("launcher") or "torchrun",
+       "AXOLOTL_LAUNCHER_ARGS": ("-- " + " ".join(launcher_args)) if launcher_args else ""}
+for name in cloud.get("secrets") or []:
+    env[name] = definitions.SecretReference(name=name)
+accelerator = getattr(truss_config.Accelerator, str(cloud.get("gpu") or "h100").upper())
+job = definitions.TrainingJob(
+    image=definitions.Image(base_image=cloud.get("image") or cloud.get("docker_tag") or "{image}"),
+    compute=definitions.Compute(node_count=int(cloud.get("node_count") or 1),
+                                accelerator=truss_config.AcceleratorSpec(accelerator=accelerator, count=int(cloud.get("gpu_count") or 1))),
+    runtime=definitions.Runtime(start_commands=["/bin/sh -c 'chmod +x ./run.sh && ./run.sh'"], environment_variables=env))
+project = definitions.TrainingProject(name=cloud.get("project_name") or "axolotl-project", job=job)
+"""
+
+
+class BasetenCloud:
+    """Training jobs on Baseten: a temporary directory receives the cloud settings, the training YAML, a start script
+    and the job definition, and is pushed with the `truss` command line tool. Cloud YAML keys: ``provider: baseten``,
+    ``gpu``, ``gpu_count``, ``node_count``, ``project_name``, ``secrets``, ``image``. Preprocessing runs inside the
+    training job (reference: src/axolotl/cli/cloud/baseten/__init__.py:14-48 and its template directory)."""
+
+    default_image = "axolotlai/axolotl:main-latest"
+
+    def __init__(self, config: dict, runner=None):
+        self.config = dict(config)
+        self.runner = runner or (lambda cmd, cwd: subprocess.run(cmd, cwd=cwd, check=False))
+
+    def preprocess(self, config_yaml: str, *a, **kw):
+        raise NotImplementedError("Baseten has no separate preprocessing step: it happens at the start of the training job")
+
+    def lm_eval(self, config_yaml: str, *a, **kw):
+        raise NotImplementedError("lm-eval is not available on the Baseten provider")
+
+    def train(self, config_yaml: str, launcher: str = "torchrun", launcher_args=None, **kw):
+        import tempfile
+
+        import yaml
+
+        with tempfile.TemporaryDirectory() as tmp:
+            cloud = dict(self.config, launcher=launcher, launcher_args=list(launcher_args or []))
+            with open(os.path.join(tmp, "cloud.yaml"), "w", encoding="utf-8") as fh:
+                yaml.safe_dump(cloud, fh)
+            with open(os.path.join(tmp, "train.yaml"), "w", encoding="utf-8") as fh:
+                fh.write(config_yaml)
+            with open(os.path.join(tmp, "run.sh"), "w", encoding="utf-8") as fh:
+                fh.write(_BASETEN_RUN_SH)
+            with open(os.path.join(tmp, "train_job.py"), "w", encoding="utf-8") as fh:
+                fh.write(_BASETEN_JOB_PY.replace("{image}", self.default_image))
+            return self.runner(["truss", "train", "push", "train_job.py"], tmp)
+
+
 def cloud_for(cloud_cfg: dict, **kw):
     provider = cloud_cfg.get("provider") or "modal"
     if provider == "modal":
         return ModalCloud(cloud_cfg, **kw)
-    raise ValueError(f"unsupported cloud provider {provider!r} (supported: modal)")
+    if provider == "baseten":
+        return BasetenCloud(cloud_cfg, **kw)
+    raise ValueError(f"unsupported cloud provider {provider!r} (supported: modal, baseten)")
 
 
 def run_in_cloud(command: str, cloud_config, config, **kw):

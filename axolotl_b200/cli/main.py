@@ -182,11 +182,19 @@ def evaluate(ctx, config):
 @click.option("--max-new-tokens", default=64)
 @click.option("--temperature", default=0.0)
 @click.option("--lora-model-dir", default=None)
+@click.option("--gradio", is_flag=True, help="serve a browser interface instead of answering one prompt")
 @click.pass_context
-def inference(ctx, config, prompt, max_new_tokens, temperature, lora_model_dir):
+def inference(ctx, config, prompt, max_new_tokens, temperature, lora_model_dir, gradio):
     """Generate from the (optionally adapter-augmented) model of CONFIG."""
     forced = {"lora_model_dir": lora_model_dir} if lora_model_dir else {}
     cfg = _load(config, ctx, **forced)
+    if gradio:
+        from .gradio_ui import launch
+
+        try:
+            return launch(cfg)
+        except RuntimeError as e:
+            raise click.ClickException(str(e))
     from ..train.evaluate import generate_text
 
     text = prompt if prompt is not None else sys.stdin.read()

@@ -719,9 +719,11 @@ class CausalLM(nn.Module):
         """Greedy / sampled continuation of one prompt; returns [1, prompt + new]. With ``use_cache``
         (default) every new token is one incremental step over a KV cache; without it the whole
         sequence is recomputed per token (kept as the oracle of the cached path)."""
+        from .registry import KV_CACHE, Unsupported, get_model_support
+
+        sup = get_model_support(self.config.model_type)
         kernel_ok = (self.config.head_dim in (64, 128) and not self.config.attn_softcap()      # what the decode kernel takes
-                     and self.config.model_type not in ("deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba",
-                                                             "nemotron_h", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "falcon_h1", "glm_moe_dsa", "lfm2", "lfm2_moe", "mistral4"))
+                     and not (sup is not None and isinstance(sup.capabilities.get(KV_CACHE), Unsupported)))
         if use_cache and kernel_ok and getattr(self.hooks, "supports_kv_cache", True) is not False:
             from .kv_cache import generate_cached
 

@@ -1320,6 +1320,13 @@ _GPU_FAMILIES = {
     "glm4_moe": dict(model_type="glm4_moe", moe_intermediate_size=128, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
                      first_k_dense_replace=1, use_qk_norm=True, attention_bias=True),
     "minimax_m2": dict(model_type="minimax_m2", intermediate_size=128, num_local_experts=8, num_experts_per_tok=2),
+    "phi": dict(model_type="phi"),
+    "olmo": dict(model_type="olmo", clip_qkv=8.0),
+    "lfm2_moe": dict(model_type="lfm2_moe", num_hidden_layers=3, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3,
+                     moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, num_dense_layers=1, tie_word_embeddings=True),
+    "mistral4": dict(model_type="mistral4", moe_intermediate_size=128, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,
+                     num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=64, kv_lora_rank=64,
+                     qk_nope_head_dim=64, qk_rope_head_dim=64, v_head_dim=128),
     "granitemoeshared": dict(model_type="granitemoeshared", intermediate_size=128, shared_intermediate_size=256, num_local_experts=8,
                              num_experts_per_tok=2, tie_word_embeddings=True, embedding_multiplier=3.0, attention_multiplier=0.125,
                              residual_multiplier=0.5, logits_scaling=2.0),

@@ -157,3 +157,79 @@ def test_remote_commands_go_through_this_packages_cli(monkeypatch, tmp_path):
     launchers._remote_preprocess("a: 1")
     assert ran[0][0] == f"axolotl train {tmp_path}/config.yaml --launcher torchrun --num-processes 4 --x 1"
     assert ran[1][0].startswith("axolotl preprocess") and ran[1][0].endswith("--no-cloud")
+
+
+def test_baseten_provider_writes_the_job_directory_and_pushes_it(tmp_path):
+    import os
+
+    import yaml
+
+    seen = {}
+
+    def runner(cmd, cwd):
+        seen["cmd"] = cmd
+        seen["files"] = {f: open(os.path.join(cwd, f), encoding="utf-8").read() for f in sorted(os.listdir(cwd))}
+        return 0
+
+    cloud = launchers.cloud_for({"provider": "baseten", "gpu": "h100", "gpu_count": 8, "node_count": 2,
+                                 "project_name": "tune", "secrets": ["HF_TOKEN"]}, runner=runner)
+    assert cloud.train("base_model: x\n", launcher="torchrun", launcher_args=["--nnodes=2"]) == 0
+    assert seen["cmd"] == ["truss", "train", "push", "train_job.py"]
+    assert set(seen["files"]) == {"cloud.yaml", "run.sh", "train.yaml", "train_job.py"}
+    written = yaml.safe_load(seen["files"]["cloud.yaml"])
+    assert written["launcher"] == "torchrun" and written["launcher_args"] == ["--nnodes=2"] and written["gpu_count"] == 8
+    assert seen["files"]["train.yaml"] == "base_model: x\n"
+    assert "axolotl train train.yaml --launcher ${AXOLOTL_LAUNCHER}" in seen["files"]["run.sh"]
+    compile(seen["files"]["train_job.py"], "train_job.py", "exec")            # the job definition is valid Python
+    with pytest.raises(NotImplementedError):
+        cloud.preprocess("x")
+    with pytest.raises(ValueError, match="modal, baseten"):
+        launchers.cloud_for({"provider": "nowhere"})
+
+
+def test_gradio_interface_streams_generated_text(monkeypatch):
+    import torch
+
+    from axolotl_b200.cli import gradio_ui
+
+    class Tok:
+        eos_token_id = 2
+        chat_template = None
+
+        def __call__(self, text):
+            return {"input_ids": [5, 6, 7]}
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(i) for i in ids)
+
+    class Model:
+        calls = 0
+
+        def eval(self):
+            return self
+
+        def generate(self, ids, max_new_tokens, temperature, top_p, eos_token_id):
+            Model.calls += 1
+            new = [10 + Model.calls] * max_new_tokens if Model.calls < 3 else [2]       # third piece ends with EOS
+            return torch.cat([ids, torch.tensor([new])], 1)
+
+    fn = gradio_ui.build_generator({"gradio_max_new_tokens": 10, "gradio_temperature": 0.5}, Model(), Tok(), "cpu", piece=4)
+    pieces = list(fn("hello"))
+    assert pieces == ["11 11 11 11", "11 11 11 11 12 12 12 12", "11 11 11 11 12 12 12 12 2"]
+    assert list(fn("")) == []
+
+    class FakeGradio:
+        class Interface:
+            def __init__(self, fn, inputs, outputs, title):
+                FakeGradio.built = (inputs, outputs, title)
+
+            def launch(self, **kw):
+                FakeGradio.launched = kw
+                return "served"
+
+    monkeypatch.setattr("axolotl_b200.data.tokenizer.load_tokenizer", lambda cfg: Tok())
+    monkeypatch.setattr("axolotl_b200.train.run.build_model", lambda cfg, dev: Model())
+    monkeypatch.setattr("axolotl_b200.train.run.setup_adapter", lambda cfg, model: None)
+    out = gradio_ui.launch({"device": "cpu", "gradio_title": "demo", "gradio_share": False, "gradio_server_port": 7861}, gr=FakeGradio)
+    assert out == "served" and FakeGradio.built == ("textbox", "text", "demo")
+    assert FakeGradio.launched == {"share": False, "server_name": "127.0.0.1", "server_port": 7861}

@@ -63,8 +63,8 @@ class RMSNorm(nn.Module):
 
 class LayerNorm(nn.Module):
     """Mean-subtracting norm with the interface of ``RMSNorm`` (Cohere: weight only; StarCoder 2 / Nemotron: weight and
-    bias; ``offset`` = 1 is Nemotron's stored-as-(w - 1) convention). Runs as a library op in fp32: these families are
-    outside the fused add+RMSNorm kernel."""
+    bias; ``offset`` = 1 is Nemotron's stored-as-(w - 1) convention; OLMo: no parameters). bf16 rows on the device run
+    the fused residual-add + LayerNorm kernel (``csrc/layernorm.cu``)."""
 
     def __init__(self, dim, eps=1e-5, dtype=torch.bfloat16, device=None, bias=True, offset=0.0, affine=True):
         super().__init__()
@@ -74,16 +74,12 @@ class LayerNorm(nn.Module):
         self.eps = eps
 
     def plain(self, x):
-        if self.weight is None:          # OLMo: no learnable scale or shift
-            return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), None, None, self.eps).to(x.dtype)
-        w = self.weight.float() + self.offset if self.offset else self.weight.float()
-        b = self.bias.float() if self.bias is not None else None
-        return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w, b, self.eps).to(x.dtype)
+        shape = x.shape
+        y, _ = Fn.add_layernorm(x.reshape(-1, shape[-1]), None, self.weight, self.bias, self.eps, self.offset)
+        return y.reshape(shape)
 
     def forward(self, x, residual=None):
-        if residual is not None:
-            x = x + residual
-        return self.plain(x), x
+        return Fn.add_layernorm(x, residual, self.weight, self.bias, self.eps, self.offset)
 
     def effective_weight(self):
         return self.weight if not self.offset else (self.weight.float() + self.offset).to(self.weight.dtype)

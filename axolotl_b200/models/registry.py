@@ -123,7 +123,7 @@ _register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms s
           notes=("norms sit on the branch outputs; q / k RMSNorm over all heads runs as separate launches before RoPE",))
 _register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2", "olmo", "phi"),
           {**_DENSE, TP: Unsupported("These graphs have no sharding rule here.")},
-          notes=("mean-subtracting norms run as library ops in fp32 (outside the fused add+RMSNorm kernel)",))
+          notes=("mean-subtracting norms run the fused residual-add + LayerNorm kernel",))
 _register("Arcee", ("arcee", "apertus"), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
 _register("Mistral", ("mistral", "ministral", "ministral3"), _DENSE,
           notes=("sliding_window is applied by the attention kernels (not with context parallelism)",))

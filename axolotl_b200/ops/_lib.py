@@ -54,6 +54,8 @@ _CUDA_SIGS = {
     "axb_rope_partial": [vp, vp, vp, i32, i32, i32, i32, i64, f32, f32, vp],
     "axb_ebft_rewards": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "axb_indexer_scores": [vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, i32, i32, vp, vp],
+    "axb_layernorm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, vp],
+    "axb_layernorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
     "axb_xielu_fwd": [vp, vp, i64, f32, f32, f32, f32, vp],
     "axb_xielu_bwd": [vp, vp, vp, vp, i64, f32, f32, f32, f32, vp],
     "axb_gated_pool_fwd": [vp, vp, vp, i64, i32, i32, vp],

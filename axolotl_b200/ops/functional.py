@@ -981,3 +981,56 @@ def gated_softmax_pool(kv, gate):
         out = _GatedPool.apply(kv.float().reshape(-1, W, D).contiguous(), gate.float().reshape(-1, W, D).contiguous())
         return out.reshape(*lead, D)
     return (kv.float() * gate.float().softmax(dim=-2)).sum(-2)
+
+
+class _AddLayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, b, eps, w_offset):
+        T, D = x.shape
+        lib = _lib.cuda_lib()
+        y = torch.empty_like(x)
+        s = torch.empty_like(x) if residual is not None else x
+        mean = torch.empty(T, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        _lib.check_rc(lib.axb_layernorm_fwd(x.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                            w.data_ptr() if w is not None else None, b.data_ptr() if b is not None else None,
+                                            y.data_ptr(), s.data_ptr() if residual is not None else None, mean.data_ptr(),
+                                            rstd.data_ptr(), T, D, float(eps), float(w_offset), _lib.stream_ptr()), "layernorm_fwd")
+        ctx.save_for_backward(s, w, mean, rstd)
+        ctx.has = (residual is not None, b is not None, float(w_offset))
+        if residual is None:                 # no new stream: the second output is a placeholder
+            dummy = x.new_empty(0)
+            ctx.mark_non_differentiable(dummy)
+            return y, dummy
+        return y, s
+
+    @staticmethod
+    def backward(ctx, dy, ds):
+        s, w, mean, rstd = ctx.saved_tensors
+        has_res, has_b, w_offset = ctx.has
+        T, D = s.shape
+        dy = dy.contiguous()
+        dres = ds.contiguous() if (has_res and ds is not None) else None
+        dx = torch.empty_like(s)
+        dw = torch.zeros(D, dtype=torch.float32, device=s.device) if w is not None else None
+        db = torch.zeros(D, dtype=torch.float32, device=s.device) if has_b else None
+        _lib.check_rc(_lib.cuda_lib().axb_layernorm_bwd(s.data_ptr(), dy.data_ptr(), dres.data_ptr() if dres is not None else None,
+                                                        w.data_ptr() if w is not None else None, mean.data_ptr(), rstd.data_ptr(),
+                                                        dx.data_ptr(), dw.data_ptr() if dw is not None else None,
+                                                        db.data_ptr() if db is not None else None, T, D, w_offset,
+                                                        _lib.stream_ptr()), "layernorm_bwd")
+        return (dx, dx if has_res else None, dw.to(w.dtype) if w is not None else None,
+                db.to(s.dtype) if has_b else None, None, None)
+
+
+def add_layernorm(x, residual, w, b, eps, w_offset=0.0):
+    """``s = x + residual`` (when given), ``y = LayerNorm(s) * (w + w_offset) + b``; returns (y, s). bf16 rows on the
+    device take the fused kernel (the stream ``s`` is normalised as stored, in bf16), everything else the fp32 op."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] * 8 <= 200 * 1024:
+        x = x.contiguous()
+        y, s = _AddLayerNorm.apply(x, residual.contiguous() if residual is not None else None, w, b, eps, w_offset)
+        return y, (s if residual is not None else x)
+    s = x if residual is None else x + residual
+    wf = None if w is None else (w.float() + w_offset if w_offset else w.float())
+    y = torch.nn.functional.layer_norm(s.float(), (s.shape[-1],), wf, b.float() if b is not None else None, eps).to(s.dtype)
+    return y, s

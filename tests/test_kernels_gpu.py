@@ -1364,3 +1364,34 @@ def test_newer_families_on_the_device_match_cpu_fp32(family):
     name = next(n for n, p in ref.named_parameters() if n.startswith("layers.0.") and p.dim() == 2 and p.grad is not None)
     gl = dict(dev.named_parameters())[name].grad.float().cpu()
     assert _rel_err(gl, dict(ref.named_parameters())[name].grad) < 0.15, name
+
+
+@pytest.mark.parametrize("has_res,has_w,has_b,offset", [(True, True, True, 0.0), (False, True, False, 0.0), (True, False, False, 0.0),
+                                                         (True, True, True, 1.0)])
+def test_add_layernorm_kernel_matches_fp32_reference(has_res, has_w, has_b, offset):
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(95)
+    T, D = 777, 2560
+    x = (torch.randn(T, D, device="cuda") * 2 + 0.5).bfloat16().requires_grad_(True)
+    r = torch.randn(T, D, device="cuda").bfloat16().requires_grad_(True) if has_res else None
+    w = (torch.rand(D, device="cuda") + 0.5 - offset).bfloat16().requires_grad_(True) if has_w else None
+    b = (torch.randn(D, device="cuda") * 0.2).bfloat16().requires_grad_(True) if has_b else None
+    y, s = Fn.add_layernorm(x, r, w, b, 1e-5, offset)
+    gy, gs = torch.randn_like(y), torch.randn_like(y)
+    (y.float() * gy.float()).sum().add((s.float() * gs.float()).sum() if has_res else 0).backward()
+    xc = x.detach().float().cpu().requires_grad_(True)
+    rc = r.detach().float().cpu().requires_grad_(True) if has_res else None
+    wc = w.detach().float().cpu().requires_grad_(True) if has_w else None
+    bc = b.detach().float().cpu().requires_grad_(True) if has_b else None
+    sc = xc + rc if has_res else xc
+    sc_q = sc + (sc.detach().bfloat16().float() - sc.detach())        # the stream as stored (bf16), gradient straight through
+    yc = torch.nn.functional.layer_norm(sc_q, (D,), (wc + offset) if has_w else None, bc, 1e-5)
+    (yc * gy.float().cpu()).sum().add((sc * gs.float().cpu()).sum() if has_res else 0).backward()
+    assert _rel_err(y.float().cpu(), yc) < 1e-2
+    assert _rel_err(x.grad.float().cpu(), xc.grad) < 2e-2
+    if has_res:
+        assert _rel_err(r.grad.float().cpu(), rc.grad) < 2e-2
+    if has_w:
+        assert _rel_err(w.grad.float().cpu(), wc.grad) < 2e-2
+    if has_b:
+        assert _rel_err(b.grad.float().cpu(), bc.grad) < 2e-2

@@ -52,12 +52,20 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     hunyuan = getattr(model.config, "model_type", "") in ("hunyuan_v1_dense", "hunyuan_v1_moe")
     apertus = getattr(model.config, "model_type", "") == "apertus"
     lfm2 = getattr(model.config, "model_type", "") in ("lfm2", "lfm2_moe")
+    afmoe = getattr(model.config, "model_type", "") == "afmoe"
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     phi = getattr(model.config, "model_type", "") == "phi"
     for name, t in named_tensors:
         if hunyuan:
             name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.") \
                 .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_experts.")
+        if afmoe:
+            name = name.replace(".pre_mlp_layernorm.", ".pre_feedforward_layernorm.").replace(".post_mlp_layernorm.", ".post_feedforward_layernorm.") \
+                .replace(".mlp.router.gate.", ".mlp.gate.").replace(".mlp.expert_bias", ".mlp.gate.e_score_correction_bias")
+            if (m := re.match(r"model\.(layers\.\d+\.self_attn)\.gate_proj\.weight$", name)):
+                mods[m.group(1)].out_gate.weight.copy_(t)
+                filled.add(name)
+                continue
         if lfm2:
             if (m := re.match(r"model\.(layers\.\d+)\.conv\.(.+)$", name)):
                 mx, leaf = mods[m.group(1) + ".self_attn"], m.group(2)
@@ -735,6 +743,10 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 (v.reshape(1, -1) if k.endswith("e_score_correction_bias") else v) for k, v in sd.items()}
     if mt_ in ("lfm2", "lfm2_moe"):
         return _lfm2_state_dict(model, sd)
+    if mt_ == "afmoe":
+        return {k.replace(".pre_feedforward_layernorm.", ".pre_mlp_layernorm.").replace(".post_feedforward_layernorm.", ".post_mlp_layernorm.")
+                .replace(".mlp.gate.e_score_correction_bias", ".mlp.expert_bias").replace(".mlp.gate.weight", ".mlp.router.gate.weight")
+                .replace(".self_attn.out_gate.", ".self_attn.gate_proj."): v for k, v in sd.items()}
     if mt_ == "apertus":
         out = {k.replace(".input_layernorm.", ".attention_layernorm.").replace(".post_attention_layernorm.", ".feedforward_layernorm."): v
                for k, v in sd.items()}

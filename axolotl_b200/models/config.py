@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi", "afmoe")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -143,6 +143,17 @@ class ModelConfig:
                 d["mamba_d_head"] = int((d.get("mamba_expand") or 2) * d["hidden_size"]) // int(d.get("mamba_n_heads") or 128)
             rp = d.get("rope_parameters") or {}
             d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))
+        if mt == "afmoe":              # Arcee Trinity: four norms, q / k norms, gated attention output, rope on sliding layers only
+            L = d.get("num_hidden_layers", 0)
+            d["qk_norm"] = True
+            d.setdefault("head_dim", 128)
+            d.setdefault("norm_topk_prob", True)
+            d["mlp_only_layers"] = list(range(int(d.get("num_dense_layers") or 0)))
+            if not d.get("layer_types"):
+                every = d.get("global_attn_every_n_layers") or 4
+                d["layer_types"] = ["full_attention" if (i + 1) % every == 0 else "sliding_attention" for i in range(L)]
+            d["routed_scaling_factor"] = d.get("route_scale", 1.0)
+            d["n_shared_experts"] = d.get("num_shared_experts") or 0
         if mt == "minimax_m2":         # q / k norms over all heads, sigmoid routing with a selection bias, no shared expert
             d["num_experts"] = d.get("num_local_experts") or 0
             d["moe_intermediate_size"] = d.get("intermediate_size") or 0
@@ -343,6 +354,12 @@ class ModelConfig:
             d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
+        if self.model_type == "afmoe":
+            d.pop("mlp_only_layers", None)
+            d.pop("decoder_sparse_step", None)
+            d.pop("norm_topk_prob", None)
+            extra.pop("routed_scaling_factor", None)
+            extra.pop("n_shared_experts", None)
         if self.model_type == "lfm2_moe":
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
@@ -405,6 +422,10 @@ class ModelConfig:
                 qpas = (self.extra or {}).get("query_pre_attn_scalar")
                 return float(qpas) ** -0.5 if qpas and self.model_type != "gemma" else 1.0 / math.sqrt(self.head_dim)
             return 1.0
+        if self.model_type == "afmoe":
+            if name == "embedding_multiplier" and (self.extra or {}).get("mup_enabled"):
+                return float(self.hidden_size) ** 0.5
+            return 1.0 / math.sqrt(self.head_dim) if name == "attention_multiplier" else 1.0
         if self.model_type in ("cohere", "cohere2"):
             if name == "logits_scaling":
                 return 1.0 / float((self.extra or {}).get("logit_scale") or 1.0)
@@ -432,7 +453,7 @@ class ModelConfig:
 
     def sandwich_norms(self) -> bool:
         """Gemma 2 / 3 and GLM-4 normalise the output of the attention and MLP branches too (four norms per layer)."""
-        return self.model_type in ("gemma2", "gemma3_text", "glm4")
+        return self.model_type in ("gemma2", "gemma3_text", "glm4", "afmoe")
 
     def norm_kind(self) -> str:
         """"rms", or a mean-subtracting LayerNorm: with bias (StarCoder 2), stored as w - 1 with bias (Nemotron),
@@ -496,7 +517,7 @@ class ModelConfig:
             return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
         if self.model_type == "starcoder2":
             return int(w)
-        if self.model_type in ("olmo3", "cohere2", "ministral"):
+        if self.model_type in ("olmo3", "cohere2", "ministral", "afmoe"):
             types = ex.get("layer_types")
             if idx is None or not types:
                 return int(w)
@@ -534,7 +555,7 @@ class ModelConfig:
             return (self.extra or {}).get("position_embedding_type") == "rope"
         if self.model_type in ("granitemoe", "granitemoeshared"):
             return True
-        if self.model_type == "cohere2":
+        if self.model_type in ("cohere2", "afmoe"):
             return (self.extra or {})["layer_types"][idx] == "sliding_attention"     # global layers carry no position signal
         if self.model_type == "nemotron_h":
             return False                                           # its attention blocks carry no position signal
@@ -716,6 +737,7 @@ _ARCH_NAME = {
     "mistral4": "Mistral4ForCausalLM",
     "olmo": "OlmoForCausalLM",
     "phi": "PhiForCausalLM",
+    "afmoe": "AfmoeForCausalLM",
     "lfm2_moe": "Lfm2MoeForCausalLM",
     "ministral": "MinistralForCausalLM",
     "ministral3": "Ministral3ForCausalLM",

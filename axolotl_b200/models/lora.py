@@ -99,6 +99,8 @@ def _checkpoint_renames(model):
                       (f"{pre}.mlp.up_proj", f"{pre}.feed_forward.w3"), (f"{pre}.mlp.down_proj", f"{pre}.feed_forward.w2")]
         if mt == "hunyuan_v1_moe":
             pairs.append((f"{pre}.mlp.shared_experts.", f"{pre}.mlp.shared_mlp."))
+        if mt == "afmoe":
+            pairs.append((f"{pre}.self_attn.out_gate.gate_proj", f"{pre}.self_attn.gate_proj"))
         if mt == "phi":
             pairs += [(f"{pre}.mlp.up_proj", f"{pre}.mlp.fc1"), (f"{pre}.mlp.down_proj", f"{pre}.mlp.fc2"),
                       (f"{pre}.self_attn.o_proj", f"{pre}.self_attn.dense")]

@@ -231,7 +231,7 @@ class SparseMoE(nn.Module):
             self.shared_experts = self._llama4_shared
             del self._llama4_shared
         self.e_score_correction_bias = None
-        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe", "mistral4", "lfm2_moe"):
+        if cfg.model_type in ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe", "mistral4", "lfm2_moe", "afmoe"):
             from .transformer import MLP
 
             ex = cfg.extra or {}

@@ -116,6 +116,7 @@ def _register(name, types, caps, head_dims=(64, 128), notes=(), validate=None):
 
 _register("LlamaLike", ("llama", "qwen2", "qwen3", "seed_oss", "ernie4_5", "hunyuan_v1_dense"), _DENSE)
 _register("Glm4Moe", ("glm4_moe", "minimax_m2", "hunyuan_v1_moe", "ernie4_5_moe"), {TP: _MOE_NO_TP})
+_register("Afmoe", ("afmoe",), {TP: _MOE_NO_TP, KV_CACHE: Unsupported("The gated attention output is not part of the cached decode path; generation recomputes the sequence.")})
 _register("GraniteMoe", ("granitemoe", "granitemoeshared"), {TP: _MOE_NO_TP})
 _register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's fused gate|up projection is kept fused.")},
           notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))

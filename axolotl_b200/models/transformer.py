@@ -57,6 +57,8 @@ class Attention(nn.Module):
         # stores the gate rows inside q_proj, head by head; they are split off at load)
         self.out_gate = FusedLinear(H, [self.Hq * self.D], ["q_gate"], bias=cfg.attention_bias, dtype=dtype, device=device) \
             if cfg.model_type in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text") else None
+        if cfg.model_type == "afmoe":      # Trinity: the same gate as a projection of its own
+            self.out_gate = FusedLinear(H, [self.Hq * self.D], ["gate_proj"], dtype=dtype, device=device)
         off = cfg.norm_offset()
         self.q_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.D, cfg.rms_norm_eps, dtype, device, offset=off) if cfg.qk_norm else None
@@ -128,6 +130,12 @@ class Attention(nn.Module):
                 t = 1.0 + beta * torch.log1p(torch.floor(positions.float() / orig))
                 nq = self.Hq * self.D
                 qkv = torch.cat([(qkv[:, :nq].float() * t[:, None]).to(qkv.dtype), qkv[:, nq:]], 1)
+        elif per_head_norm:                  # a position-free layer still normalises q / k per head (Trinity's global layers)
+            T = qkv.shape[0]
+            nq, nk = self.Hq * self.D, self.Hk * self.D
+            q = self.q_norm.plain(qkv[:, :nq].reshape(T * self.Hq, self.D)).reshape(T, nq)
+            k = self.k_norm.plain(qkv[:, nq:nq + nk].reshape(T * self.Hk, self.D)).reshape(T, nk)
+            qkv = torch.cat([q, k, qkv[:, nq + nk:]], 1)
         elif self.llama4 and self.temp is not None:
             floor_scale, a = self.temp
             t = torch.log1p(torch.floor((positions.float() + 1.0) / floor_scale)) * a + 1.0

@@ -368,6 +368,56 @@ def bench_indexer(rows):
                     f"{L * L * 2 / t_k / 1e6:.0f} GB/s | einsum form {t_e*1e3:.0f} us ({t_e / t:.1f}x)")
 
 
+def bench_mixers(rows):
+    """The recurrent token mixers of the hybrid families at one 8192-token row (four 2048-token documents): the
+    Mamba-2 chunked scan and the gated delta rule, both written as dense tensor contractions (library batched GEMMs),
+    forward and forward + backward; flash-linear-attention's Triton kernel for the delta rule beside it for context."""
+    from axolotl_b200.models.deltanet import gated_delta_rule
+    from axolotl_b200.models.mamba import ssd_chunked
+
+    L, docs = 2048, 4
+    # Granite-4.0-H-small-like mixer: 128 heads x 64, state 128
+    h, P, N = 128, 64, 128
+    xd = (torch.randn(docs * L, h, P, device="cuda") * 0.5).requires_grad_(True)
+    a = -torch.rand(docs * L, h, device="cuda") * 0.1
+    B = torch.randn(docs * L, h, N, device="cuda") * 0.3
+    C = torch.randn(docs * L, h, N, device="cuda") * 0.3
+
+    def scan():
+        return torch.cat([ssd_chunked(xd[i * L:(i + 1) * L], a[i * L:(i + 1) * L], B[i * L:(i + 1) * L], C[i * L:(i + 1) * L], 256)
+                          for i in range(docs)], 0)
+    t_f = time_cuda(scan, iters=5, warmup=2)
+    t_fb = time_cuda(lambda: torch.autograd.grad(scan().sum(), xd), iters=5, warmup=2)
+    fl = 2.0 * docs * L * h * (256 * (N + P) + 2 * N * P)          # intra-chunk scores + outputs, state update + read-out
+    rows.append(f"mamba-2 scan h={h} P={P} N={N}, {docs} x {L} tokens, chunk 256 (fp32 contractions): fwd {t_f:.2f} ms "
+                f"({fl / t_f / 1e9:.0f} TFLOP/s), fwd+bwd {t_fb:.2f} ms")
+    # Qwen3-Next-like DeltaNet: 32 value heads, 128-wide keys and values
+    hv, dk, dv = 32, 128, 128
+    q = torch.nn.functional.normalize(torch.randn(docs * L, hv, dk, device="cuda"), dim=-1).requires_grad_(True)
+    k = torch.nn.functional.normalize(torch.randn(docs * L, hv, dk, device="cuda"), dim=-1)
+    v = torch.randn(docs * L, hv, dv, device="cuda")
+    g = -torch.rand(docs * L, hv, device="cuda") * 0.1
+    beta = torch.rand(docs * L, hv, device="cuda")
+
+    def delta():
+        return torch.cat([gated_delta_rule(q[i * L:(i + 1) * L], k[i * L:(i + 1) * L], v[i * L:(i + 1) * L], g[i * L:(i + 1) * L],
+                                           beta[i * L:(i + 1) * L]) for i in range(docs)], 0)
+    t_f = time_cuda(delta, iters=5, warmup=2)
+    t_fb = time_cuda(lambda: torch.autograd.grad(delta().sum(), q), iters=5, warmup=2)
+    line = f"gated delta rule hv={hv} dk={dk} dv={dv}, {docs} x {L} tokens: fwd {t_f:.2f} ms, fwd+bwd {t_fb:.2f} ms"
+    try:
+        from fla.ops.gated_delta_rule import chunk_gated_delta_rule
+
+        cu = torch.arange(0, (docs + 1) * L, L, device="cuda", dtype=torch.int32)
+        qb, kb, vb = (t.detach().bfloat16()[None] for t in (q, k, v))
+        f2 = lambda: chunk_gated_delta_rule(qb, kb, vb, g[None], beta[None], scale=dk ** -0.5, cu_seqlens=cu.long())
+        t2 = time_cuda(f2, iters=5, warmup=2)
+        line += f" | flash-linear-attention (Triton, bf16): fwd {t2:.2f} ms"
+    except Exception as e:  # noqa: BLE001
+        line += f" | flash-linear-attention: {type(e).__name__}"
+    rows.append(line)
+
+
 def bench_attn(rows):
     from axolotl_b200.ops.functional import AttnMeta, flash_varlen
 
@@ -535,6 +585,8 @@ def main(argv):
         bench_attn_wide(rows)
     if what in ("indexer",):
         bench_indexer(rows)
+    if what in ("mixers",):
+        bench_mixers(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

@@ -915,6 +915,10 @@ LLAMA_LIKE = {
                 num_key_value_heads=2, layer_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0,
                 resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0,
                 rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}),
+    "afmoe": dict(model_type="afmoe", vocab_size=300, hidden_size=64, intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4,
+                  num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2, num_shared_experts=1,
+                  num_dense_layers=1, route_scale=1.5, sliding_window=8, global_attn_every_n_layers=4, mup_enabled=True,
+                  rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256, pad_token_id=0),
     "ministral": dict(model_type="ministral", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, tie_word_embeddings=False,
                       max_position_embeddings=256, pad_token_id=0, sliding_window=8,

@@ -1321,6 +1321,8 @@ _GPU_FAMILIES = {
                      first_k_dense_replace=1, use_qk_norm=True, attention_bias=True),
     "minimax_m2": dict(model_type="minimax_m2", intermediate_size=128, num_local_experts=8, num_experts_per_tok=2),
     "phi": dict(model_type="phi"),
+    "afmoe": dict(model_type="afmoe", num_hidden_layers=4, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
+                  num_shared_experts=1, num_dense_layers=1, sliding_window=128),
     "olmo": dict(model_type="olmo", clip_qkv=8.0),
     "lfm2_moe": dict(model_type="lfm2_moe", num_hidden_layers=3, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3,
                      moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, num_dense_layers=1, tie_word_embeddings=True),

@@ -63,6 +63,107 @@ def gated_delta_rule(q, k, v, g, beta, chunk=64):
     return o.permute(0, 2, 1, 3).reshape(n * C, h, dv)[:L]
 
 
+def _unit_lower_inverse(Lm):
+    """(I + L)^-1 for strictly lower-triangular L [..., C, C]. L is nilpotent (L^C = 0), so the Neumann series is the
+    finite product (I - L)(I + L^2)(I + L^4)...: log2(C) batched matrix products instead of C steps of substitution."""
+    C = Lm.shape[-1]
+    eye = torch.eye(C, dtype=Lm.dtype, device=Lm.device)
+    inv = eye - Lm
+    P = Lm @ Lm                                      # (-L)^2 = L^2
+    k = 2
+    while k < C:
+        inv = inv + inv @ P
+        k *= 2
+        if k < C:
+            P = P @ P
+    return inv
+
+
+def _delta_layout(cu, C, device):
+    """Documents padded to multiples of C and laid end to end: gather index into the token stream (one extra zero row at
+    index T), position of every token in the padded layout, and the [documents, max chunks] grid of chunk numbers (the
+    number of chunks = an all-zero chunk that leaves the state alone)."""
+    import numpy as np
+
+    T = int(cu[-1])
+    idx, back, per_doc = [], [], []
+    off = nchunks = 0
+    for s, e in zip(cu[:-1], cu[1:]):
+        L = int(e) - int(s)
+        if L <= 0:
+            continue
+        n = (L + C - 1) // C
+        row = np.full(n * C, T, dtype=np.int64)
+        row[:L] = np.arange(int(s), int(e))
+        idx.append(row)
+        back.append(off + np.arange(L))
+        per_doc.append(np.arange(nchunks, nchunks + n))
+        off += n * C
+        nchunks += n
+    grid = np.full((len(per_doc), max(len(p) for p in per_doc)), nchunks, dtype=np.int64)
+    for d, pch in enumerate(per_doc):
+        grid[d, : len(pch)] = pch
+    to = lambda a: torch.from_numpy(a).to(device)
+    return to(np.concatenate(idx)), to(np.concatenate(back)), to(grid)
+
+
+def _delta_packed_core(q, k, v, g, beta, idx, back, grid, C, lowp):
+    T, h, dk = k.shape
+    dv = v.shape[-1]
+
+    def pad(t):
+        return torch.cat([t, t.new_zeros(1, *t.shape[1:])], 0).index_select(0, idx)
+    n = idx.numel() // C
+    q, k, v = (pad(t).view(n, C, h, -1).permute(0, 2, 1, 3) for t in (q, k, v))          # [n, h, C, d]
+    g, beta = pad(g).view(n, C, h).permute(0, 2, 1).float(), pad(beta).view(n, C, h).permute(0, 2, 1).float()
+    ct = lowp if lowp is not None else q.dtype
+    mm = lambda a, b: (a.to(ct) @ b.to(ct)).float()                                        # tensor-core contraction, fp32 result
+    G = g.cumsum(-1)
+    low = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+    decay = torch.exp((G[..., :, None] - G[..., None, :]).masked_fill(~low, float("-inf")))
+    Lmat = (beta[..., :, None] * mm(k, k.transpose(-1, -2)) * decay).tril(-1)
+    Tm = _unit_lower_inverse(Lmat)
+    W1 = mm(Tm, beta[..., None] * v.float())                                               # [n, h, C, dv]
+    W2 = mm(Tm, beta[..., None] * torch.exp(G)[..., None] * k.float())                     # [n, h, C, dk]
+    qk = mm(q, k.transpose(-1, -2)) * decay
+    eG = torch.exp(G)
+    qe = eG[..., None] * q.float()                                                         # queries with the decay since the chunk start
+    kt = (torch.exp(G[..., -1:] - G)[..., None] * k.float()).transpose(-1, -2)             # keys with the decay to the chunk end
+    last = eG[..., -1]                                                                     # [n, h]
+
+    def grid_of(t, fill=0.0, dtype=None):
+        """[chunks, ...] -> [chunk positions, documents, ...] (one gather up front; documents shorter than the longest read an
+        all-zero chunk with decay 1 that leaves their state alone)."""
+        t = torch.cat([t, torch.full((1, *t.shape[1:]), fill, dtype=t.dtype, device=t.device)], 0)
+        t = t.index_select(0, grid.t().reshape(-1)).view(grid.shape[1], grid.shape[0], *t.shape[1:])
+        return t.to(dtype) if dtype is not None else t
+    W1g, W2g, qkg, qeg, ktg, lastg = grid_of(W1), grid_of(W2, dtype=ct), grid_of(qk, dtype=ct), grid_of(qe, dtype=ct), \
+        grid_of(kt, dtype=ct), grid_of(last, 1.0)
+    D = grid.shape[0]
+    S = torch.zeros(D, h, dk, dv, dtype=torch.float32, device=q.device)
+    outs = []
+    for c in range(grid.shape[1]):                                                         # chunk by chunk, all documents at once
+        Sl = S.to(ct)
+        U = W1g[c] - (W2g[c] @ Sl).float()
+        Ul = U.to(ct)
+        outs.append((qeg[c] @ Sl).float() + (qkg[c] @ Ul).float())
+        S = lastg[c][..., None, None] * S + (ktg[c] @ Ul).float()
+    out = torch.stack(outs)                                                                # [positions, documents, h, C, dv]
+    # back to chunk order: chunk number grid[d, c] holds out[c, d]
+    flat = torch.zeros(n + 1, h, C, dv, dtype=torch.float32, device=q.device)
+    flat = flat.index_copy(0, grid.t().reshape(-1), out.view(-1, h, C, dv))
+    return flat[:n].permute(0, 2, 1, 3).reshape(n * C, h, dv).index_select(0, back)
+
+
+def gated_delta_rule_packed(q, k, v, g, beta, cu, chunk=64, lowp=None):
+    """The chunked gated delta rule for EVERY document of a packed row: the per-chunk work (Gram matrices, triangular
+    solves) runs once over all chunks, the state recurrence advances all documents together, one step per chunk
+    position. ``lowp``: operand dtype of the matrix products (fp32 accumulation and state)."""
+    C = min(chunk, max(int(max(e - s for s, e in zip(cu[:-1], cu[1:]))), 1))
+    idx, back, grid = _delta_layout(cu, C, q.device)
+    return _delta_packed_core(q, k, v, g, beta, idx, back, grid, C, lowp)
+
+
 class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
@@ -125,7 +226,7 @@ class GatedDeltaNet(nn.Module):
         beta = torch.sigmoid(b.float())
         g = -torch.exp(self.A_log.float()) * F.softplus(a.float() + self.dt_bias.float())
         cu = [int(c) for c in meta.cu_seqlens_host]
-        o = torch.cat([gated_delta_rule(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e]) for s, e in zip(cu[:-1], cu[1:]) if e > s], 0)
+        o = gated_delta_rule_packed(q, k, v, g, beta, cu, 64, torch.bfloat16 if (x.is_cuda and x.dtype == torch.bfloat16) else None)
         o = Fn.rmsnorm_gated(o.reshape(T * self.nv, self.dv).to(x.dtype), z.reshape(T * self.nv, self.dv).contiguous(),
                              self.norm_weight, self.eps)
         return self.out_proj(o.reshape(T, self.value_dim))

@@ -57,6 +57,81 @@ def ssd_chunked(xd, a, B, C, chunk=128):
     return y.reshape(nc * Q, h, P)[:L]
 
 
+def _packed_layout(cu, Q, device):
+    """Every document padded to a multiple of Q positions and laid end to end: (gather index into the token stream with
+    one extra zero row at index T, index of every token in the padded layout, same-document matrix of the chunks)."""
+    import numpy as np
+
+    T = int(cu[-1])
+    idx, back, doc_of_chunk = [], [], []
+    off = 0
+    for d, (s, e) in enumerate(zip(cu[:-1], cu[1:])):
+        L = int(e) - int(s)
+        if L <= 0:
+            continue
+        n = (L + Q - 1) // Q
+        row = np.full(n * Q, T, dtype=np.int64)
+        row[:L] = np.arange(int(s), int(e))
+        idx.append(row)
+        back.append(off + np.arange(L))
+        doc_of_chunk += [d] * n
+        off += n * Q
+    idx, back = np.concatenate(idx), np.concatenate(back)
+    doc = np.asarray(doc_of_chunk)
+    same = doc[:, None] == doc[None, :]
+    lower = np.tril(np.ones((len(doc), len(doc)), dtype=bool), -1)
+    return (torch.from_numpy(idx).to(device), torch.from_numpy(back).to(device), torch.from_numpy(same & lower).to(device))
+
+
+def _ssd_packed_core(xd, a, B, C, idx, back, pair_ok, Q, lowp):
+    """xd [T, h, P], a [T, h], B / C [T, G, N] (one per GROUP of h / G heads; [T, h, N] works too). Everything is laid out
+    [chunks, groups, heads-of-group, positions, ...] so that every contraction is a plain batched matrix product and the
+    group-level tensors broadcast over their heads without copies; operands are converted to ``lowp`` once, up front."""
+    T, h, P = xd.shape
+    Gn, N = B.shape[1], B.shape[2]
+    rep = h // Gn
+    ct = lowp if lowp is not None else xd.dtype                                      # operand dtype of the contractions
+
+    def pad(t):
+        return torch.cat([t, t.new_zeros(1, *t.shape[1:])], 0).index_select(0, idx)
+    nc = idx.numel() // Q
+    x_p = pad(xd.to(ct)).view(nc, Q, Gn, rep, P).permute(0, 2, 3, 1, 4)              # [nc, G, r, Q, P]
+    B_p = pad(B.to(ct)).view(nc, Q, Gn, N).permute(0, 2, 1, 3)                       # [nc, G, Q, N]
+    C_p = pad(C.to(ct)).view(nc, Q, Gn, N).permute(0, 2, 1, 3)
+    cum = pad(a.float()).view(nc, Q, Gn, rep).permute(0, 2, 3, 1).cumsum(-1)         # [nc, G, r, Q] fp32
+    causal = torch.ones(Q, Q, dtype=torch.bool, device=xd.device).tril()
+    decay = torch.exp((cum[..., :, None] - cum[..., None, :]).masked_fill(~causal, float("-inf"))).to(ct)   # [nc, G, r, i, j]
+    Gm = C_p @ B_p.transpose(-1, -2)                                                 # [nc, G, i, j]: once per group
+    y = ((Gm[:, :, None] * decay) @ x_p).float()                                     # [nc, G, r, Q, P]
+    if nc > 1:
+        to_end = torch.exp(cum[..., -1:] - cum).to(ct)                               # [nc, G, r, Q]
+        S = ((x_p * to_end[..., None]).transpose(-1, -2) @ B_p[:, :, None]).float()  # [nc, G, r, P, N] state each chunk adds
+        tot = cum[..., -1].reshape(nc, h)                                            # [nc, h] log decay over a chunk
+        E = tot.cumsum(0) - tot                                                      # log decay from the row start to a chunk start
+        # state that enters chunk c: sum over earlier chunks j of the same document of exp(E_c - E_j - tot_j) S_j
+        M = torch.exp((E[:, None, :] - E[None, :, :] - tot[None, :, :]).masked_fill(~pair_ok[:, :, None], float("-inf")))
+        R = (M.permute(2, 0, 1) @ S.reshape(nc, h, P * N).permute(1, 0, 2)).view(h, nc, P, N).permute(1, 0, 2, 3)
+        R = R.reshape(nc, Gn, rep, P, N).to(ct)
+        y = y + ((C_p[:, :, None] * torch.exp(cum).to(ct)[..., None]) @ R.transpose(-1, -2)).float()
+    return y.permute(0, 3, 1, 2, 4).reshape(nc * Q, h, P).index_select(0, back)
+
+
+def ssd_packed(xd, a, B, C, cu, chunk=128, lowp=None):
+    """The chunked scan of EVERY document of a packed row in one batched pass (no loop over documents or chunks): chunks
+    of all documents form the batch axis of the contractions, and the state a chunk receives is one masked matrix
+    product over the earlier chunks of its document. ``lowp`` (e.g. bf16 on the device): operand dtype of the
+    contractions (fp32 accumulation; decays and cumulative sums stay fp32). The big [chunks, Q, Q, heads] intermediates
+    are recomputed in the backward pass instead of being kept."""
+    Q = min(chunk, max(int(max(e - s for s, e in zip(cu[:-1], cu[1:]))), 1))
+    idx, back, pair_ok = _packed_layout(cu, Q, xd.device)
+    args = (xd, a, B, C, idx, back, pair_ok, Q, lowp)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (xd, a, B, C)):
+        from torch.utils.checkpoint import checkpoint
+
+        return checkpoint(_ssd_packed_core, *args, use_reentrant=False)
+    return _ssd_packed_core(*args)
+
+
 class _AllGatherStack(torch.autograd.Function):
     """[...] on every rank -> [world, ...]; the gradient of a rank's slice is the sum of what all ranks send back."""
 
@@ -195,14 +270,13 @@ class Mamba2Mixer(nn.Module):
         A = -torch.exp(self.A_log.float())
         xs = xs.view(T, self.nh, self.P)
         rep = self.nh // self.G
-        B = B.view(T, self.G, self.N).repeat_interleave(rep, dim=1)
-        C = C.view(T, self.G, self.N).repeat_interleave(rep, dim=1)
+        B, C = B.view(T, self.G, self.N), C.view(T, self.G, self.N)
         xd, a = xs * dt[..., None], A[None] * dt
         cu = [int(v) for v in meta.cu_seqlens_host]
         if cp:
-            y = self._scan_cp(xd, a, B, C, cu, meta)
+            y = self._scan_cp(xd, a, B.repeat_interleave(rep, dim=1), C.repeat_interleave(rep, dim=1), cu, meta)
         else:
-            y = torch.cat([ssd_chunked(xd[s:e], a[s:e], B[s:e], C[s:e], self.chunk) for s, e in zip(cu[:-1], cu[1:]) if e > s], 0)
+            y = ssd_packed(xd, a, B, C, cu, min(self.chunk, 128), torch.bfloat16 if (x.is_cuda and x.dtype == torch.bfloat16) else None)
         y = y + self.D.float()[None, :, None] * xs
         y = y.reshape(T, self.d_inner)
         if not (self.has_norm and self.norm_before_gate):

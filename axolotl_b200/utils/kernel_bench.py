@@ -372,8 +372,8 @@ def bench_mixers(rows):
     """The recurrent token mixers of the hybrid families at one 8192-token row (four 2048-token documents): the
     Mamba-2 chunked scan and the gated delta rule, both written as dense tensor contractions (library batched GEMMs),
     forward and forward + backward; flash-linear-attention's Triton kernel for the delta rule beside it for context."""
-    from axolotl_b200.models.deltanet import gated_delta_rule
-    from axolotl_b200.models.mamba import ssd_chunked
+    from axolotl_b200.models.deltanet import gated_delta_rule, gated_delta_rule_packed
+    from axolotl_b200.models.mamba import ssd_chunked, ssd_packed
 
     L, docs = 2048, 4
     # Granite-4.0-H-small-like mixer: 128 heads x 64, state 128
@@ -389,8 +389,15 @@ def bench_mixers(rows):
     t_f = time_cuda(scan, iters=5, warmup=2)
     t_fb = time_cuda(lambda: torch.autograd.grad(scan().sum(), xd), iters=5, warmup=2)
     fl = 2.0 * docs * L * h * (256 * (N + P) + 2 * N * P)          # intra-chunk scores + outputs, state update + read-out
-    rows.append(f"mamba-2 scan h={h} P={P} N={N}, {docs} x {L} tokens, chunk 256 (fp32 contractions): fwd {t_f:.2f} ms "
+    rows.append(f"mamba-2 scan h={h} P={P} N={N}, {docs} x {L} tokens, per document, chunk 256, fp32 contractions: fwd {t_f:.2f} ms "
                 f"({fl / t_f / 1e9:.0f} TFLOP/s), fwd+bwd {t_fb:.2f} ms")
+    cu = [i * L for i in range(docs + 1)]
+    Bg, Cg = B[:, ::16].contiguous(), C[:, ::16].contiguous()               # 8 groups of 16 heads, as the checkpoints have
+    for lowp, tag in ((None, "fp32"), (torch.bfloat16, "bf16 operands")):
+        f = lambda: ssd_packed(xd, a, Bg, Cg, cu, 128, lowp)
+        t_f = time_cuda(f, iters=5, warmup=2)
+        t_fb = time_cuda(lambda: torch.autograd.grad(f().sum(), xd), iters=5, warmup=2)
+        rows.append(f"mamba-2 scan, whole row in one batched pass, chunk 128, {tag}: fwd {t_f:.2f} ms, fwd+bwd {t_fb:.2f} ms")
     # Qwen3-Next-like DeltaNet: 32 value heads, 128-wide keys and values
     hv, dk, dv = 32, 128, 128
     q = torch.nn.functional.normalize(torch.randn(docs * L, hv, dk, device="cuda"), dim=-1).requires_grad_(True)
@@ -404,7 +411,12 @@ def bench_mixers(rows):
                                            beta[i * L:(i + 1) * L]) for i in range(docs)], 0)
     t_f = time_cuda(delta, iters=5, warmup=2)
     t_fb = time_cuda(lambda: torch.autograd.grad(delta().sum(), q), iters=5, warmup=2)
-    line = f"gated delta rule hv={hv} dk={dk} dv={dv}, {docs} x {L} tokens: fwd {t_f:.2f} ms, fwd+bwd {t_fb:.2f} ms"
+    line = f"gated delta rule hv={hv} dk={dk} dv={dv}, {docs} x {L} tokens, per document, fp32: fwd {t_f:.2f} ms, fwd+bwd {t_fb:.2f} ms"
+    for lowp, tag in ((None, "fp32"), (torch.bfloat16, "bf16 operands")):
+        f = lambda: gated_delta_rule_packed(q, k, v, g, beta, cu, 64, lowp)
+        t_f = time_cuda(f, iters=5, warmup=2)
+        t_fb = time_cuda(lambda: torch.autograd.grad(f().sum(), q), iters=5, warmup=2)
+        line += f" | all documents together, {tag}: fwd {t_f:.2f} ms, fwd+bwd {t_fb:.2f} ms"
     try:
         from fla.ops.gated_delta_rule import chunk_gated_delta_rule
 

@@ -163,6 +163,9 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
         elif (m := re.match(r"model\.(layers\.\d+)\.(input_layernorm|post_attention_layernorm|pre_feedforward_layernorm|post_feedforward_layernorm)\.(weight|bias)$", name)):
             getattr(mods[f"{m.group(1)}.{m.group(2)}"], m.group(3)).copy_(t)
             filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.layer_scalar$", name)):
+            mods[m.group(1)].layer_scalar.copy_(t.reshape(-1))
+            filled.add(name)
         elif name == "model.norm.bias":
             model.norm.bias.copy_(t)
             filled.add("norm.bias")
@@ -688,6 +691,8 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
             continue
         if getattr(m, "sinks", None) is not None:
             sd[f"model.{name}.sinks"] = m.sinks.detach()
+        if getattr(m, "layer_scalar", None) is not None:
+            sd[f"model.{name}.layer_scalar"] = m.layer_scalar.detach()
         if type(m).__name__ == "LightningIndexer":
             sd[f"model.{name}.k_norm.weight"] = m.k_norm_weight.detach()
             sd[f"model.{name}.k_norm.bias"] = m.k_norm_bias.detach()

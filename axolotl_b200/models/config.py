@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi", "afmoe")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi", "afmoe", "gemma4_text")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -69,7 +69,7 @@ class ModelConfig:
             self.qk_norm = True
         if self.model_type in ("qwen2", "qwen2_moe"):
             self.attention_bias = True
-        if self.model_type in ("gemma3_text", "olmo2", "olmo3", "minimax_m2") + QWEN3_NEXT_TYPES:
+        if self.model_type in ("gemma3_text", "gemma4_text", "olmo2", "olmo3", "minimax_m2") + QWEN3_NEXT_TYPES:
             self.qk_norm = True
 
     # ------------------------------------------------------------------ HF interchange
@@ -80,6 +80,32 @@ class ModelConfig:
         if mt == "gemma3" and isinstance(d.get("text_config"), dict):   # the multimodal wrapper: its language model
             d = dict(d["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
+        if mt == "gemma4" and isinstance(d.get("text_config"), dict):      # the multimodal wrapper: its language model
+            d = dict(d["text_config"], model_type="gemma4_text")
+            mt = "gemma4_text"
+        if mt == "gemma4_text":
+            # sliding layers: 256-wide heads, plain rope; global layers: `global_head_dim`-wide heads, a quarter of the
+            # angle pairs rotate; weights of the norms are plain scales; scores are not scaled; values are RMS-normalised
+            L = d.get("num_hidden_layers", 0)
+            d.setdefault("tie_word_embeddings", True)
+            d["hidden_act"] = d.get("hidden_activation") or "gelu_pytorch_tanh"
+            d.setdefault("rms_norm_eps", 1e-6)
+            d.setdefault("head_dim", 256)
+            d.setdefault("global_head_dim", 512)
+            d.setdefault("sliding_window", 512)
+            if not d.get("layer_types"):
+                d["layer_types"] = ["sliding_attention" if (i + 1) % 6 else "full_attention" for i in range(L)]
+            d["layer_types"] = list(d["layer_types"][:-1]) + ["full_attention"] if L else []
+            if not isinstance(d.get("rope_parameters"), dict) or "full_attention" not in d["rope_parameters"]:
+                d["rope_parameters"] = {"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                        "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1000000.0}}
+            d["rope_theta"] = d["rope_parameters"]["sliding_attention"].get("rope_theta", 10000.0)
+            for key, what in (("num_kv_shared_layers", "layers that reuse an earlier layer's keys / values"),
+                              ("hidden_size_per_layer_input", "per-layer input embeddings"), ("enable_moe_block", "the expert block")):
+                if d.get(key):
+                    raise ValueError(f"gemma4_text: {what} ({key}) are not supported; dense checkpoints without them are")
+            if d.get("use_bidirectional_attention"):
+                raise ValueError("gemma4_text: use_bidirectional_attention is not supported")
         if mt in GEMMA_TYPES:
             d.setdefault("tie_word_embeddings", True)
             d["hidden_act"] = d.get("hidden_activation") or "gelu_pytorch_tanh"   # HF forces the tanh form
@@ -354,6 +380,10 @@ class ModelConfig:
             d["moe_layers"] = [i for i in range(self.num_hidden_layers) if i not in set(self.mlp_only_layers)]
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
+        if self.model_type == "gemma4_text":      # rope settings live per layer type in rope_parameters only
+            d.pop("rope_theta", None)
+            d.pop("rope_scaling", None)
+            d["hidden_activation"] = d.pop("hidden_act", "gelu_pytorch_tanh")
         if self.model_type == "afmoe":
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
@@ -413,6 +443,12 @@ class ModelConfig:
     def multiplier(self, name: str) -> float:
         """Granite's scalar multipliers (embedding / attention / residual / logits_scaling); 1 elsewhere
         (``attention_multiplier`` falls back to 1/sqrt(head_dim))."""
+        if self.model_type == "gemma4_text":
+            if name == "embedding_multiplier":
+                import torch
+
+                return float(torch.tensor(self.hidden_size ** 0.5, dtype=torch.bfloat16))
+            return 1.0                                # (scores are not scaled: q / k are RMS-normalised)
         if self.model_type in GEMMA_TYPES:
             if name == "embedding_multiplier":      # sqrt(hidden) rounded to the activation dtype, as HF does
                 import torch
@@ -453,7 +489,7 @@ class ModelConfig:
 
     def sandwich_norms(self) -> bool:
         """Gemma 2 / 3 and GLM-4 normalise the output of the attention and MLP branches too (four norms per layer)."""
-        return self.model_type in ("gemma2", "gemma3_text", "glm4", "afmoe")
+        return self.model_type in ("gemma2", "gemma3_text", "gemma4_text", "glm4", "afmoe")
 
     def norm_kind(self) -> str:
         """"rms", or a mean-subtracting LayerNorm: with bias (StarCoder 2), stored as w - 1 with bias (Nemotron),
@@ -479,8 +515,39 @@ class ModelConfig:
         return float(v) if v else 0.0
 
     def final_softcap(self) -> float:
-        v = (self.extra or {}).get("final_logit_softcapping") if self.model_type in ("gemma2", "gemma3_text") else None
+        v = (self.extra or {}).get("final_logit_softcapping") if self.model_type in ("gemma2", "gemma3_text", "gemma4_text") else None
         return float(v) if v else 0.0
+
+    def layer_head_dim(self, idx: int) -> int:
+        """Gemma 4: full-attention layers have wider heads than sliding ones."""
+        if self.model_type == "gemma4_text" and (self.extra or {})["layer_types"][idx] == "full_attention":
+            return int((self.extra or {}).get("global_head_dim") or self.head_dim)
+        return self.head_dim
+
+    def layer_kv_heads(self, idx: int) -> int:
+        ex = self.extra or {}
+        if self.model_type == "gemma4_text" and ex.get("attention_k_eq_v") and ex["layer_types"][idx] == "full_attention":
+            return int(ex.get("num_global_key_value_heads") or self.num_key_value_heads)
+        return self.num_key_value_heads
+
+    def layer_inv_freq(self, idx: int):
+        """Gemma 4: (inverse frequencies of layer ``idx`` over ALL angle pairs of its head, or None). Global layers rotate
+        only the first ``partial_rotary_factor`` of the pairs (i, i + D/2); the others get frequency 0."""
+        if self.model_type != "gemma4_text":
+            return None
+        import torch
+
+        ex = self.extra or {}
+        kind = ex["layer_types"][idx]
+        rp = (ex.get("rope_parameters") or {}).get(kind) or {}
+        D = self.layer_head_dim(idx)
+        theta, factor = float(rp.get("rope_theta", 10000.0)), float(rp.get("factor", 1.0))
+        if rp.get("rope_type", "default") == "proportional":
+            n = int(float(rp.get("partial_rotary_factor", 1.0)) * D // 2)
+            inv = torch.zeros(D // 2, dtype=torch.float32)
+            inv[:n] = 1.0 / (theta ** (torch.arange(0, 2 * n, 2, dtype=torch.float32) / D))
+            return inv / factor
+        return 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D)) / factor
 
     def local_rope_theta(self, idx: int) -> float | None:
         """Gemma 3: sliding-window layers rotate with their own base frequency and no scaling."""
@@ -517,7 +584,7 @@ class ModelConfig:
             return int(w) if (idx + 1) % pat else 0           # every pat-th layer is global
         if self.model_type == "starcoder2":
             return int(w)
-        if self.model_type in ("olmo3", "cohere2", "ministral", "afmoe"):
+        if self.model_type in ("olmo3", "cohere2", "ministral", "afmoe", "gemma4_text"):
             types = ex.get("layer_types")
             if idx is None or not types:
                 return int(w)
@@ -705,6 +772,7 @@ _ARCH_NAME = {
     "gemma": "GemmaForCausalLM",
     "gemma2": "Gemma2ForCausalLM",
     "gemma3_text": "Gemma3ForCausalLM",
+    "gemma4_text": "Gemma4ForCausalLM",
     "deepseek_v2": "DeepseekV2ForCausalLM",
     "deepseek_v3": "DeepseekV3ForCausalLM",
     "gpt_oss": "GptOssForCausalLM",

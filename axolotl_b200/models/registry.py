@@ -142,6 +142,11 @@ _register("Gemma", ("gemma", "gemma2", "gemma3_text"),
           {**_DENSE, CP: _WIDE_NO_CP, KV_CACHE: _WIDE_NO_KV, TP: Experimental("Checked on the Llama-style graphs only.")},
           head_dims=None,
           notes=("head width 256 and the tanh soft caps run through the wide-head attention kernels",))
+_register("Gemma4", ("gemma4_text",),
+          {**_DENSE, CP: _WIDE_NO_CP, KV_CACHE: _WIDE_NO_KV, TP: Unsupported("Layers differ in head width and key / value head count.")},
+          head_dims=None,
+          notes=("sliding layers (256-wide heads) run the wide-head attention kernels; global layers (512-wide heads) run the "
+                 "blocked library path",))
 _register("GptOss", ("gpt_oss",),
           {TP: _MOE_NO_TP, CP: Unsupported("Attention sinks are not carried through the context-parallel kernels."),
            KV_CACHE: Unsupported("Attention sinks are not part of the decode kernel; generation recomputes the sequence."),

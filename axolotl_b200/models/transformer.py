@@ -37,11 +37,15 @@ class CausalLMOutput:
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, head_dim=None, kv_heads=None, k_eq_v=False):
         super().__init__()
-        self.Hq, self.Hk, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        self.Hq, self.Hk, self.D = cfg.num_attention_heads, kv_heads or cfg.num_key_value_heads, head_dim or cfg.head_dim
         H = cfg.hidden_size
-        if cfg.model_type == "phi3":   # the checkpoint (and its adapters) name the fused projection itself
+        self.k_eq_v = k_eq_v           # Gemma 4 global layers: values are the (un-normed, un-rotated) keys
+        if k_eq_v:
+            self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D], ["q_proj", "k_proj"], bias=cfg.attention_bias,
+                                        dtype=dtype, device=device)
+        elif cfg.model_type == "phi3":   # the checkpoint (and its adapters) name the fused projection itself
             self.qkv_proj = FusedLinear(H, [(self.Hq + 2 * self.Hk) * self.D], ["qkv_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
         else:
@@ -70,8 +74,11 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(self.Hk * self.D, cfg.rms_norm_eps, dtype, device)
         self.eps = cfg.rms_norm_eps
         self.scale = cfg.multiplier("attention_multiplier")   # 1/sqrt(head_dim) except for Granite
+        self.v_norm = cfg.model_type == "gemma4_text"         # Gemma 4: values are RMS-normalised per head (no learned scale)
         self.use_rope = True                                   # SmolLM3: some layers carry no position signal
         self.rot_dim = cfg.rope_dim() if cfg.rope_dim() < self.D else None   # partial rotary embedding (Phi-4-mini, Bamba)
+        if cfg.model_type == "gemma4_text":      # its partial rotation is expressed by zero frequencies over the full width
+            self.rot_dim = None
         self.window = cfg.sliding_window()                     # Mistral / Phi-3 ...: causal sliding window, 0 = none
         self.softcap = cfg.attn_softcap()                      # Gemma 2: scores -> cap * tanh(scores / cap)
         # Llama 4: unweighted per-head L2 norm of q / k on rotating layers; those layers attend inside chunks of
@@ -93,6 +100,14 @@ class Attention(nn.Module):
     def pre(self, x, positions, inv_freq, attn_scale):
         """Projections, q/k norms and rotary embedding: everything before the attention kernel."""
         qkv = self.qkv_proj(x)
+        if self.k_eq_v:
+            qkv = torch.cat([qkv, qkv[:, self.Hq * self.D:]], 1)
+        if self.v_norm:
+            T = qkv.shape[0]
+            nqk = (self.Hq + self.Hk) * self.D
+            v = qkv[:, nqk:].reshape(T * self.Hk, self.D).float()
+            v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(qkv.dtype).reshape(T, self.Hk * self.D)
+            qkv = torch.cat([qkv[:, :nqk], v], 1)
         if self.clip_qkv:
             qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
         per_head_norm = self.q_norm is not None and not self.full_qk_norm
@@ -324,6 +339,13 @@ class DecoderLayer(nn.Module):
             from .deltanet import GatedDeltaNet
 
             self.self_attn = GatedDeltaNet(cfg, dtype, device)
+        elif cfg.model_type == "gemma4_text":
+            wide = cfg.layer_head_dim(idx) != cfg.head_dim or cfg.layer_kv_heads(idx) != cfg.num_key_value_heads
+            self.self_attn = Attention(cfg, dtype, device, head_dim=cfg.layer_head_dim(idx), kv_heads=cfg.layer_kv_heads(idx),
+                                       k_eq_v=bool((cfg.extra or {}).get("attention_k_eq_v")) and cfg.sliding_window(idx) == 0)
+            inv = cfg.layer_inv_freq(idx)
+            self.self_attn.local_inv_freq = inv.to(device) if device is not None else inv
+            del wide
         else:
             self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
@@ -369,6 +391,9 @@ class DecoderLayer(nn.Module):
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
                            fused_names=cfg.model_type in ("phi3", "glm", "glm4"))
         self.is_moe = cfg.is_moe_layer(idx)
+        # Gemma 4: the layer output (stream included) is multiplied by a stored scalar
+        self.layer_scalar = nn.Parameter(torch.ones(1, dtype=dtype, device=device), requires_grad=False) \
+            if cfg.model_type == "gemma4_text" else None
 
     def _stream(self, h, residual):
         """(input of the attention branch, residual stream)."""
@@ -402,6 +427,8 @@ class DecoderLayer(nn.Module):
             y = self.post_feedforward_layernorm.plain(y)
         if rm != 1.0:
             y = y * rm
+        if self.layer_scalar is not None:
+            return (residual + y) * self.layer_scalar.to(y.dtype), None, aux
         return y, residual, aux
 
     def forward_selective(self, h, residual, positions, inv_freq, attn_scale, meta):

@@ -131,6 +131,10 @@ FAMILIES = {
     "afmoe": dict(model_type="afmoe", vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4,
                   num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2, num_shared_experts=1,
                   num_dense_layers=1, sliding_window=32, tie_word_embeddings=False, max_position_embeddings=256),
+    "gemma4_text": dict(model_type="gemma4_text", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=16,
+                        layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
+                        attention_k_eq_v=True, num_global_key_value_heads=1, tie_word_embeddings=True, max_position_embeddings=256),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

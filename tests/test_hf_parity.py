@@ -1005,3 +1005,37 @@ def test_qwen3_5_text_matches_hf(tmp_path, moe):
     # the multimodal wrapper's config loads as its language model
     wrapped = ModelConfig.from_hf_dict({"model_type": "qwen3_5_moe" if moe else "qwen3_5", "text_config": d})
     assert wrapped.model_type == d["model_type"] and wrapped.hidden_size == 64
+
+
+@pytest.mark.parametrize("k_eq_v", [False, True])
+def test_gemma4_text_dense_matches_hf(tmp_path, k_eq_v):
+    """Gemma 4 language model (dense form): sliding layers with narrow heads and plain rope, global layers with wider
+    heads whose first quarter of angle pairs rotates, values RMS-normalised, unscaled scores, four plain-scale norms, a
+    stored scalar per layer; optionally global layers whose values are their keys (fewer key / value heads)."""
+    d = dict(model_type="gemma4_text", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8,
+             layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
+             num_kv_shared_layers=0, enable_moe_block=False, attention_k_eq_v=k_eq_v, num_global_key_value_heads=1 if k_eq_v else None,
+             final_logit_softcapping=20.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=256,
+             pad_token_id=0, vocab_size_per_layer_input=300)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(59)
+    assert [l.self_attn.D for l in ours.layers] == [16, 16, 32] and ours.layers[2].self_attn.k_eq_v == k_eq_v
+    _randomize_norms(ours, 0.5, 1.5)
+    with torch.no_grad():
+        for l in ours.layers:
+            l.layer_scalar.uniform_(0.7, 1.2)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [21, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)

@@ -1321,6 +1321,9 @@ _GPU_FAMILIES = {
                      first_k_dense_replace=1, use_qk_norm=True, attention_bias=True),
     "minimax_m2": dict(model_type="minimax_m2", intermediate_size=128, num_local_experts=8, num_experts_per_tok=2),
     "phi": dict(model_type="phi"),
+    "gemma4_text": dict(model_type="gemma4_text", num_hidden_layers=3, head_dim=256, global_head_dim=512, sliding_window=128,
+                        layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
+                        attention_k_eq_v=True, num_global_key_value_heads=1, tie_word_embeddings=True),
     "afmoe": dict(model_type="afmoe", num_hidden_layers=4, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
                   num_shared_experts=1, num_dense_layers=1, sliding_window=128),
     "olmo": dict(model_type="olmo", clip_qkv=8.0),

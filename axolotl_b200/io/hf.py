@@ -55,7 +55,20 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
     afmoe = getattr(model.config, "model_type", "") == "afmoe"
     starcoder2 = getattr(model.config, "model_type", "") == "starcoder2"
     phi = getattr(model.config, "model_type", "") == "phi"
+    falcon = getattr(model.config, "model_type", "") == "falcon"
+    vision_params = None
     for name, t in named_tensors:
+        if falcon:
+            name = _falcon_in(name)
+            if (m := re.match(r"model\.(layers\.\d+\.self_attn)\.query_key_value\.(weight|bias)$", name)):
+                t = t.index_select(0, model.config.falcon_qkv_rows().to(t.device))     # rows into q | k | v order
+                getattr(mods[m.group(1)].qkv_proj, m.group(2)).copy_(t)
+                filled.add(name)
+                continue
+            elif (m := re.match(r"model\.(layers\.\d+)\.ln_mlp\.(weight|bias)$", name)):
+                getattr(mods[m.group(1)].ln_mlp, m.group(2)).copy_(t)
+                filled.add(name)
+                continue
         if hunyuan:
             name = name.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.") \
                 .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_experts.")
@@ -137,7 +150,19 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             name = name[len("language_model."):]
         elif name.startswith("model.language_model."):
             name = "model." + name[len("model.language_model."):]
-        if name.startswith(("vision_tower.", "multi_modal_projector.", "model.vision_tower.", "model.multi_modal_projector.")):
+        if getattr(model, "vision", None) is not None and name.startswith(
+                ("vision_tower.", "multi_modal_projector.", "model.vision_tower.", "model.multi_modal_projector.")):
+            leaf = name[len("model."):] if name.startswith("model.") else name       # LLaVA: CLIP tower and projector
+            if vision_params is None:
+                vision_params = dict(model.vision.named_parameters())
+            if leaf in vision_params:
+                vision_params[leaf].copy_(t)
+                filled.add(name)
+            elif strict and not leaf.endswith("position_ids"):
+                raise KeyError(f"unexpected checkpoint tensor '{name}'")
+            continue
+        if name.startswith(("vision_tower.", "multi_modal_projector.", "model.vision_tower.", "model.multi_modal_projector.",
+                            "model.audio_tower.", "model.embed_vision.", "model.embed_audio.")):
             continue
         if name == "model.embed_tokens.weight":
             model.embed_tokens.copy_(t)
@@ -165,6 +190,21 @@ def load_state_into(model: CausalLM, named_tensors, strict: bool = True):
             filled.add(name)
         elif (m := re.match(r"model\.(layers\.\d+)\.layer_scalar$", name)):
             mods[m.group(1)].layer_scalar.copy_(t.reshape(-1))
+            filled.add(name)
+        elif name in ("model.embed_tokens_per_layer.weight", "model.per_layer_model_projection.weight", "model.per_layer_projection_norm.weight"):
+            leaf = name.split(".")[1]           # Gemma 4 per-layer input embeddings
+            (model.embed_tokens_per_layer if leaf == "embed_tokens_per_layer" else getattr(model, leaf).weight).copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.(per_layer_input_gate|per_layer_projection|post_per_layer_input_norm|"
+                            r"post_feedforward_layernorm_1|post_feedforward_layernorm_2|pre_feedforward_layernorm_2)\.weight$", name)):
+            getattr(mods[m.group(1)], m.group(2)).weight.copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.router\.(proj\.weight|scale|per_expert_scale)$", name)):
+            moe = mods[m.group(1)].g4_moe        # Gemma 4 expert block beside the dense MLP
+            {"proj.weight": moe.gate, "scale": moe.router_scale, "per_expert_scale": moe.per_expert_scale}[m.group(2)].copy_(t)
+            filled.add(name)
+        elif (m := re.match(r"model\.(layers\.\d+)\.experts\.(gate_up_proj|down_proj)$", name)):
+            getattr(mods[m.group(1)].g4_moe.experts, m.group(2)).copy_(t)
             filled.add(name)
         elif name == "model.norm.bias":
             model.norm.bias.copy_(t)
@@ -657,6 +697,40 @@ def _granite_hybrid_state_dict(model, sd):
     return sd
 
 
+_FALCON_NAMES = (("transformer.word_embeddings.", "model.embed_tokens."), ("transformer.ln_f.", "model.norm."),
+                 ("transformer.h.", "model.layers."), (".self_attention.dense.", ".self_attn.o_proj."),
+                 (".self_attention.", ".self_attn."), (".mlp.dense_h_to_4h.", ".mlp.up_proj."),
+                 (".mlp.dense_4h_to_h.", ".mlp.down_proj."), (".ln_attn.", ".input_layernorm."))
+
+
+def _falcon_in(name: str) -> str:
+    for src, dst in _FALCON_NAMES:
+        name = name.replace(src, dst)
+    return name
+
+
+def _falcon_out(model, sd: dict) -> dict:
+    """This graph's names and q | k | v row order -> Falcon's (``transformer.h.N.self_attention.query_key_value`` ...)."""
+    inv = torch.argsort(model.config.falcon_qkv_rows())
+    two_norms = model.layers[0].ln_mlp is not None
+    out = {}
+    for k, v in sd.items():
+        if ".self_attn.query_key_value." in k:
+            v = v.index_select(0, inv.to(v.device))
+        if two_norms:
+            k = k.replace(".input_layernorm.", ".ln_attn.")
+        k = k.replace(".self_attn.o_proj.", ".self_attention.dense.").replace(".self_attn.", ".self_attention.") \
+            .replace(".mlp.up_proj.", ".mlp.dense_h_to_4h.").replace(".mlp.down_proj.", ".mlp.dense_4h_to_h.") \
+            .replace("model.layers.", "transformer.h.").replace("model.embed_tokens.", "transformer.word_embeddings.") \
+            .replace("model.norm.", "transformer.ln_f.")
+        out[k] = v
+    for i, layer in enumerate(model.layers):
+        if layer.ln_mlp is not None:
+            out[f"transformer.h.{i}.ln_mlp.weight"] = layer.ln_mlp.weight.detach()
+            out[f"transformer.h.{i}.ln_mlp.bias"] = layer.ln_mlp.bias.detach()
+    return out
+
+
 def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
     """Model tensors under HF names (views where possible; the writer makes them contiguous)."""
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach()}
@@ -767,11 +841,41 @@ def hf_state_dict(model: CausalLM, per_expert: bool = False) -> dict:
                 for k, v in sd.items()}
     if getattr(model.config, "model_type", "") == "starcoder2":
         return {k.replace(".mlp.up_proj.", ".mlp.c_fc.").replace(".mlp.down_proj.", ".mlp.c_proj."): v for k, v in sd.items()}
+    if mt_ == "falcon":
+        return _falcon_out(model, sd)
+    if mt_ == "gemma4_text":
+        out = {k.replace(".g4_moe.experts.", ".experts.").replace(".g4_moe.gate.weight", ".router.proj.weight")
+               .replace("model.per_layer_model_projection.per_layer_model_projection.", "model.per_layer_model_projection."): v
+               for k, v in sd.items()}
+        if getattr(model, "ple_width", 0):
+            out["model.embed_tokens_per_layer.weight"] = model.embed_tokens_per_layer.detach()
+            out["model.per_layer_projection_norm.weight"] = model.per_layer_projection_norm.weight.detach()
+        for i, layer in enumerate(model.layers):
+            for nm in ("post_per_layer_input_norm", "post_feedforward_layernorm_1", "post_feedforward_layernorm_2", "pre_feedforward_layernorm_2"):
+                if hasattr(layer, nm):
+                    out[f"model.layers.{i}.{nm}.weight"] = getattr(layer, nm).weight.detach()
+            if layer.g4_moe is not None:
+                out[f"model.layers.{i}.router.scale"] = layer.g4_moe.router_scale.detach()
+                out[f"model.layers.{i}.router.per_expert_scale"] = layer.g4_moe.per_expert_scale.detach()
+        return out
     return sd
+
+
+def _with_vision(model, sd: dict) -> dict:
+    """LLaVA layout: the language model's tensors under ``model.language_model.``, tower and projector beside it."""
+    out = {("model.language_model." + k[len("model."):] if k.startswith("model.") else k): v for k, v in sd.items()}
+    if "lm_head.weight" not in out:          # the wrapper ties nothing by itself: write the head it would look for
+        out["lm_head.weight"] = model.embed_tokens.detach()
+    for k, v in model.vision.named_parameters():
+        out["model." + k] = v.detach()
+    return out
 
 
 def save_pretrained(model: CausalLM, out_dir: str, max_shard_bytes: int = 5 * 1024 ** 3, per_expert=False):
     os.makedirs(out_dir, exist_ok=True)
     model.config.save_pretrained(out_dir)
-    sd = {k: v.to("cpu") for k, v in hf_state_dict(model, per_expert=per_expert).items()}
+    sd = hf_state_dict(model, per_expert=per_expert)
+    if getattr(model, "vision", None) is not None:
+        sd = _with_vision(model, sd)
+    sd = {k: v.to("cpu") for k, v in sd.items()}
     return st.save_sharded(sd, out_dir, max_shard_bytes)

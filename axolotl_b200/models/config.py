@@ -17,7 +17,7 @@ SUPPORTED_MODEL_TYPES = ("llama", "mistral", "phi3", "qwen2", "qwen3", "qwen3_mo
                          "gemma", "gemma2", "gemma3_text", "deepseek_v2", "deepseek_v3", "gpt_oss", "granitemoehybrid", "llama4_text", "bamba", "nemotron_h", "qwen3_next", "falcon_h1", "glm_moe_dsa",
                          "glm", "glm4", "olmo2", "olmo3", "seed_oss", "arcee", "glm4_moe", "ernie4_5", "hunyuan_v1_dense",
                          "granitemoe", "granitemoeshared", "nemotron", "starcoder2", "cohere", "cohere2", "ministral", "ministral3", "qwen3_5_text", "qwen3_5_moe_text", "minimax_m2",
-                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi", "afmoe", "gemma4_text")
+                         "hunyuan_v1_moe", "ernie4_5_moe", "apertus", "lfm2", "lfm2_moe", "mistral4", "olmo", "phi", "afmoe", "gemma4_text", "falcon")
 GEMMA_TYPES = ("gemma", "gemma2", "gemma3_text")
 MLA_TYPES = ("deepseek_v2", "deepseek_v3", "glm_moe_dsa", "mistral4")      # multi-head latent attention
 GRANITE_MOE_TYPES = ("granitemoe", "granitemoeshared", "granitemoehybrid")
@@ -77,6 +77,14 @@ class ModelConfig:
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         d = dict(d)
         mt = d.get("model_type", "llama")
+        if mt == "llava" and isinstance(d.get("text_config"), dict):    # image front end + one of the causal graphs
+            wrapper = {k: d[k] for k in ("vision_config", "vision_feature_layer", "vision_feature_select_strategy",
+                                         "projector_hidden_act", "multimodal_projector_bias", "image_seq_length") if k in d}
+            wrapper["image_token_id"] = d.get("image_token_id", d.get("image_token_index", 32000))
+            wrapper["model_type"] = "llava"
+            d = dict(d["text_config"], vision_wrapper=wrapper)
+            d.setdefault("model_type", "llama")
+            mt = d["model_type"]
         if mt == "gemma3" and isinstance(d.get("text_config"), dict):   # the multimodal wrapper: its language model
             d = dict(d["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
@@ -100,10 +108,13 @@ class ModelConfig:
                 d["rope_parameters"] = {"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
                                         "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1000000.0}}
             d["rope_theta"] = d["rope_parameters"]["sliding_attention"].get("rope_theta", 10000.0)
-            for key, what in (("num_kv_shared_layers", "layers that reuse an earlier layer's keys / values"),
-                              ("hidden_size_per_layer_input", "per-layer input embeddings"), ("enable_moe_block", "the expert block")):
-                if d.get(key):
-                    raise ValueError(f"gemma4_text: {what} ({key}) are not supported; dense checkpoints without them are")
+            if d.get("hidden_size_per_layer_input") is None:
+                d["hidden_size_per_layer_input"] = 256
+            d.setdefault("vocab_size_per_layer_input", d.get("vocab_size"))
+            if d.get("enable_moe_block"):     # the expert block runs BESIDE the dense MLP of every layer: kept out of the generic MoE switches
+                d["g4_experts"] = {"num_experts": int(d["num_experts"]), "top_k": int(d["top_k_experts"]),
+                                   "intermediate": int(d["moe_intermediate_size"])}
+            d["num_experts"] = 0
             if d.get("use_bidirectional_attention"):
                 raise ValueError("gemma4_text: use_bidirectional_attention is not supported")
         if mt in GEMMA_TYPES:
@@ -274,6 +285,25 @@ class ModelConfig:
             d.setdefault("partial_rotary_factor", (d.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))
             if d.get("qk_layernorm"):
                 raise ValueError("phi: qk_layernorm (per-head LayerNorm of q / k) is not supported")
+        if mt == "falcon":             # LayerNorm, ungated GELU MLP, one fused query_key_value projection in three row layouts
+            if d.get("alibi"):
+                raise ValueError("falcon: ALiBi position biases (alibi: true) are not supported; the rotary checkpoints are")
+            d.setdefault("num_attention_heads", d.get("n_head", 71))
+            d.setdefault("num_hidden_layers", d.get("n_layer", 32))
+            new = bool(d.get("new_decoder_architecture", False))
+            d["new_decoder_architecture"] = new
+            d.setdefault("multi_query", True)
+            d.setdefault("parallel_attn", True)
+            d["num_key_value_heads"] = (d.get("num_kv_heads") or d["num_attention_heads"]) if new \
+                else (1 if d["multi_query"] else d["num_attention_heads"])
+            if d.get("num_ln_in_parallel_attn") is None:
+                d["num_ln_in_parallel_attn"] = 2 if new else 1
+            d["intermediate_size"] = d.get("ffn_hidden_size") or 4 * d.get("hidden_size", 4544)
+            d["rms_norm_eps"] = d.get("layer_norm_epsilon", 1e-5)
+            d["attention_bias"] = d["mlp_bias"] = bool(d.get("bias", False))
+            d["hidden_act"] = d.get("activation", "gelu")
+            d.setdefault("tie_word_embeddings", True)
+            d.setdefault("max_position_embeddings", 2048)
         if mt == "nemotron":           # LayerNorm with (1 + w) and bias, half of a head rotates, ungated squared-ReLU MLP
             d["rms_norm_eps"] = d.get("norm_eps", 1e-5)
             d.setdefault("partial_rotary_factor", 0.5)
@@ -384,6 +414,17 @@ class ModelConfig:
             d.pop("rope_theta", None)
             d.pop("rope_scaling", None)
             d["hidden_activation"] = d.pop("hidden_act", "gelu_pytorch_tanh")
+        if self.model_type == "falcon":
+            d["layer_norm_epsilon"] = d.pop("rms_norm_eps", 1e-5)
+            d["bias"] = bool(d.pop("attention_bias", False))
+            d["activation"] = d.pop("hidden_act", "gelu")
+            d["ffn_hidden_size"] = d.pop("intermediate_size")
+            d["num_kv_heads"] = d.pop("num_key_value_heads")
+            for k in ("mlp_bias", "head_dim", "rope_scaling"):
+                d.pop(k, None)
+            rt = d.pop("rope_theta", None)
+            if rt and not extra.get("rope_parameters"):
+                d["rope_parameters"] = {"rope_type": "default", "rope_theta": rt}
         if self.model_type == "afmoe":
             d.pop("mlp_only_layers", None)
             d.pop("decoder_sparse_step", None)
@@ -428,10 +469,17 @@ class ModelConfig:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
                       "router_aux_loss_coef", "decoder_sparse_step", "mlp_only_layers"):
                 d.pop(k, None)
+        if self.model_type == "gemma4_text" and (g4 := extra.pop("g4_experts", None)):
+            d.update(num_experts=g4["num_experts"], top_k_experts=g4["top_k"], moe_intermediate_size=g4["intermediate"], enable_moe_block=True)
         if not d.get("architectures"):
             d["architectures"] = [_ARCH_NAME[self.model_type]]
         out = dict(extra)
         out.update(d)
+        if (vw := out.pop("vision_wrapper", None)):
+            vw = dict(vw)
+            return {"model_type": vw.pop("model_type"), "architectures": ["LlavaForConditionalGeneration"],
+                    "text_config": {k: v for k, v in out.items() if k != "architectures"},
+                    "tie_word_embeddings": out.get("tie_word_embeddings", False), "torch_dtype": out.get("torch_dtype", "bfloat16"), **vw}
         return out
 
     def save_pretrained(self, path: str) -> None:
@@ -494,12 +542,32 @@ class ModelConfig:
     def norm_kind(self) -> str:
         """"rms", or a mean-subtracting LayerNorm: with bias (StarCoder 2), stored as w - 1 with bias (Nemotron),
         weight only (Cohere)."""
-        return {"starcoder2": "layernorm", "nemotron": "layernorm1p", "cohere": "layernorm_nobias", "phi": "layernorm",
+        return {"starcoder2": "layernorm", "nemotron": "layernorm1p", "cohere": "layernorm_nobias", "phi": "layernorm", "falcon": "layernorm",
                 "cohere2": "layernorm_nobias", "olmo": "layernorm_fixed"}.get(self.model_type, "rms")
 
     def parallel_block(self) -> bool:
         """Cohere: attention and MLP read the same normalised input and are added to the stream together."""
+        if self.model_type == "falcon":
+            ex = self.extra or {}
+            return bool(ex.get("new_decoder_architecture") or ex.get("parallel_attn", True))
         return self.model_type in ("cohere", "cohere2", "phi")
+
+    def falcon_qkv_rows(self):
+        """Falcon stores one ``query_key_value`` projection. Row i of this graph's q | k | v block is row ``idx[i]`` of the
+        checkpoint's: per key / value group [its queries, key, value] (new decoder architecture), [all queries, key, value]
+        (multi-query), or per head [query, key, value]."""
+        import torch
+
+        Hq, Hk, D = self.num_attention_heads, self.num_key_value_heads, self.head_dim
+        ex = self.extra or {}
+        if ex.get("new_decoder_architecture"):
+            G = Hq // Hk
+            blk = torch.arange(Hk * (G + 2) * D).view(Hk, G + 2, D)
+            return torch.cat([blk[:, :G].reshape(-1), blk[:, G].reshape(-1), blk[:, G + 1].reshape(-1)])
+        if ex.get("multi_query", True):
+            return torch.arange((Hq + 2) * D)
+        blk = torch.arange(Hq * 3 * D).view(Hq, 3, D)
+        return torch.cat([blk[:, 0].reshape(-1), blk[:, 1].reshape(-1), blk[:, 2].reshape(-1)])
 
     def post_norm_only(self) -> bool:
         """OLMo 2 / 3: no norm on a branch's input, one on its output."""
@@ -805,6 +873,7 @@ _ARCH_NAME = {
     "mistral4": "Mistral4ForCausalLM",
     "olmo": "OlmoForCausalLM",
     "phi": "PhiForCausalLM",
+    "falcon": "FalconForCausalLM",
     "afmoe": "AfmoeForCausalLM",
     "lfm2_moe": "Lfm2MoeForCausalLM",
     "ministral": "MinistralForCausalLM",

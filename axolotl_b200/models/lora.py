@@ -104,6 +104,10 @@ def _checkpoint_renames(model):
         if mt == "phi":
             pairs += [(f"{pre}.mlp.up_proj", f"{pre}.mlp.fc1"), (f"{pre}.mlp.down_proj", f"{pre}.mlp.fc2"),
                       (f"{pre}.self_attn.o_proj", f"{pre}.self_attn.dense")]
+        if mt == "falcon":
+            fp = f"transformer.h.{i}"
+            pairs += [(f"{pre}.self_attn.o_proj", f"{fp}.self_attention.dense"), (f"{pre}.self_attn.", f"{fp}.self_attention."),
+                      (f"{pre}.mlp.up_proj", f"{fp}.mlp.dense_h_to_4h"), (f"{pre}.mlp.down_proj", f"{fp}.mlp.dense_4h_to_h")]
         if mt == "starcoder2":
             pairs.append((f"{pre}.mlp.up_proj", f"{pre}.mlp.c_fc"))
             pairs.append((f"{pre}.mlp.down_proj", f"{pre}.mlp.c_proj"))
@@ -114,6 +118,8 @@ def _checkpoint_renames(model):
             for inner in ("mlp.shared_experts", "mlp"):
                 pairs.append((f"{pre}.{inner}.gate_up_proj", f"{pre}.shared_mlp.input_linear"))
                 pairs.append((f"{pre}.{inner}.down_proj", f"{pre}.shared_mlp.output_linear"))
+    if mt == "gemma4_text":          # a model-level projection: its module path is its own name
+        pairs.append(("model.per_layer_model_projection.per_layer_model_projection", "model.per_layer_model_projection"))
     model.__dict__["_axb_hf_renames"] = pairs
     return pairs
 
@@ -150,6 +156,11 @@ def _B_rows_layout(model, name, sub, B, to_checkpoint: bool):
         if to_checkpoint:
             idx = torch.argsort(idx)
         return B.reshape(heads, D, -1).index_select(1, idx.to(B.device)).reshape(B.shape)
+    if mt == "falcon" and sub == "query_key_value":      # the checkpoint interleaves queries, keys and values by head / group
+        idx = model.config.falcon_qkv_rows()
+        if to_checkpoint:
+            idx = torch.argsort(idx)
+        return B.index_select(0, idx.to(B.device))
     if mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text") and sub == "q_proj" and ".self_attn." in name:
         cfg = model.config
         H, D = cfg.num_attention_heads, cfg.head_dim

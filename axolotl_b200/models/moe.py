@@ -191,6 +191,12 @@ class SparseMoE(nn.Module):
         self.experts = Experts(cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size, cfg.hidden_act,
                                dtype, device)
         self.aux_coef = cfg.router_aux_loss_coef
+        # Gemma 4: its router normalises and scales its own input and scales the chosen experts' weights
+        self.gemma4 = cfg.model_type == "gemma4_text"
+        if self.gemma4:
+            self.router_eps = cfg.rms_norm_eps
+            self.router_scale = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+            self.per_expert_scale = nn.Parameter(torch.ones(cfg.num_experts, dtype=dtype, device=device))
         self.ep = None  # parallel.ep.ExpertParallelGroup when experts are sharded across ranks
         self.dense_mixer = False   # DenseMixer plugin: straight-through router gradient over all experts
         # Qwen2-MoE: a dense "shared" expert runs on every token, scaled by a sigmoid gate
@@ -264,8 +270,8 @@ class SparseMoE(nn.Module):
             gl = linear(x, g)
         return torch.sigmoid(gl.float()).to(x.dtype) * self.shared_expert(x)
 
-    def forward(self, x):
-        y, aux = self._routed(x)
+    def forward(self, x, router_x=None):
+        y, aux = self._routed(x, router_x)
         if self.dense_mixer and self.training and torch.is_grad_enabled():
             if self.ep is not None:
                 raise NotImplementedError("dense_mixer needs all experts on the rank (no expert parallelism)")
@@ -276,9 +282,17 @@ class SparseMoE(nn.Module):
             y = y + self.shared_experts(x)
         return y, aux
 
-    def _routed(self, x):
+    def _routed(self, x, router_x=None):
         T, H = x.shape
-        if self.deepseek is not None:
+        if self.gemma4:
+            # the router reads the un-normed stream: RMS-normalise (no weight), scale per channel and by H^-1/2; softmax
+            # over all experts, the k best renormalised, then a learned scale per chosen expert
+            r = router_x.float()
+            r = r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + self.router_eps) * self.router_scale.float() * (H ** -0.5)
+            probs = torch.softmax(r @ self.gate.float().t(), -1)
+            w, idx = torch.topk(probs, self.k, dim=-1)
+            w = (w / w.sum(-1, keepdim=True)) * self.per_expert_scale.float()[idx]
+        elif self.deepseek is not None:
             logits = x.float() @ self.gate.float().t()       # HF keeps this router in fp32
             w, idx, probs = route_deepseek(logits, self.k, bias=self.e_score_correction_bias, **self.deepseek)
         elif self.input_scaled:

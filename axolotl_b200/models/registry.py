@@ -122,7 +122,7 @@ _register("Glm", ("glm", "glm4"), {**_DENSE, TP: Unsupported("The checkpoint's f
           notes=("rotary pairs stored as neighbours are permuted to the half-split layout at load and back at save",))
 _register("Olmo2", ("olmo2", "olmo3"), {**_DENSE, TP: Unsupported("q / k norms span all heads of the unsharded projection.")},
           notes=("norms sit on the branch outputs; q / k RMSNorm over all heads runs as separate launches before RoPE",))
-_register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2", "olmo", "phi"),
+_register("LayerNormFamilies", ("nemotron", "starcoder2", "cohere", "cohere2", "olmo", "phi", "falcon"),
           {**_DENSE, TP: Unsupported("These graphs have no sharding rule here.")},
           notes=("mean-subtracting norms run the fused residual-add + LayerNorm kernel",))
 _register("Arcee", ("arcee", "apertus"), {**_DENSE, TP: Unsupported("The ungated MLP has no sharding rule here.")})
@@ -146,7 +146,9 @@ _register("Gemma4", ("gemma4_text",),
           {**_DENSE, CP: _WIDE_NO_CP, KV_CACHE: _WIDE_NO_KV, TP: Unsupported("Layers differ in head width and key / value head count.")},
           head_dims=None,
           notes=("sliding layers (256-wide heads) run the wide-head attention kernels; global layers (512-wide heads) run the "
-                 "blocked library path",))
+                 "blocked library path",
+                 "per-layer input embeddings, the expert block beside the dense MLP (grouped tcgen05 GEMMs) and the layers "
+                 "that attend an earlier layer's keys / values are built; the bidirectional (vision) attention mode is not"))
 _register("GptOss", ("gpt_oss",),
           {TP: _MOE_NO_TP, CP: Unsupported("Attention sinks are not carried through the context-parallel kernels."),
            KV_CACHE: Unsupported("Attention sinks are not part of the decode kernel; generation recomputes the sequence."),
@@ -180,7 +182,7 @@ _register("Qwen3Next", ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"),
           head_dims=None)
 
 # architectures the reference lists that have no model graph here (named so that the error can say so)
-KNOWN_UNSUPPORTED = ("gemma3", "gemma4", "deepseek_v4", "falcon", "phi", "gpt_neox", "mamba", "jamba", "llama4", "mllama",
+KNOWN_UNSUPPORTED = ("gemma3", "gemma4", "deepseek_v4", "gpt_neox", "mamba", "jamba", "llama4", "mllama",
                      "qwen2_vl", "qwen3_vl", "qwen3_5", "qwen3_5_moe", "kimi_linear", "cohere", "cohere2", "starcoder2",
                      "lfm2", "lfm2_moe", "minimax_m2", "afmoe", "gemmoe", "mistral4")
 

@@ -42,8 +42,12 @@ class Attention(nn.Module):
         self.Hq, self.Hk, self.D = cfg.num_attention_heads, kv_heads or cfg.num_key_value_heads, head_dim or cfg.head_dim
         H = cfg.hidden_size
         self.k_eq_v = k_eq_v           # Gemma 4 global layers: values are the (un-normed, un-rotated) keys
+        self.kv_store, self.kv_src = False, None      # Gemma 4 key / value sharing (set by the layer)
         if k_eq_v:
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D], ["q_proj", "k_proj"], bias=cfg.attention_bias,
+                                        dtype=dtype, device=device)
+        elif cfg.model_type == "falcon":  # one projection in the checkpoint (its rows re-ordered to q | k | v on load)
+            self.qkv_proj = FusedLinear(H, [(self.Hq + 2 * self.Hk) * self.D], ["query_key_value"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
         elif cfg.model_type == "phi3":   # the checkpoint (and its adapters) name the fused projection itself
             self.qkv_proj = FusedLinear(H, [(self.Hq + 2 * self.Hk) * self.D], ["qkv_proj"], bias=cfg.attention_bias,
@@ -52,7 +56,7 @@ class Attention(nn.Module):
             self.qkv_proj = FusedLinear(H, [self.Hq * self.D, self.Hk * self.D, self.Hk * self.D],
                                         ["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias,
                                         dtype=dtype, device=device)
-        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3", "starcoder2", "cohere", "cohere2", "nemotron", "phi")
+        o_bias = (cfg.attention_bias if cfg.model_type in ("gpt_oss", "olmo2", "olmo3", "starcoder2", "cohere", "cohere2", "nemotron", "phi", "falcon")
                   else bool((cfg.extra or {}).get("attention_out_bias")) if cfg.model_type == "seed_oss" else False)
         self.o_proj = FusedLinear(self.Hq * self.D, [H], ["o_proj"], bias=o_bias, dtype=dtype, device=device)
         # gpt-oss: one learned "sink" logit per head in every softmax denominator
@@ -172,8 +176,21 @@ class Attention(nn.Module):
             meta = meta.windowed(self.window)   # a no-op while no document exceeds the window
         return Fn.flash_varlen(qkv, meta, self.Hq, self.Hk, self.D, self.scale, softcap=self.softcap, sinks=self.sinks)
 
+    def share_kv(self, qkv, meta):
+        """Gemma 4's last layers attend the keys / values of the last earlier layer of their kind that still makes its own
+        (after its norms and rotation); that layer leaves them on the batch's attention descriptor."""
+        nq = self.Hq * self.D
+        if self.kv_store:
+            meta.shared_kv[self.layer_idx] = qkv[:, nq:]
+        if self.kv_src is not None:
+            qkv = torch.cat([qkv[:, :nq], meta.shared_kv[self.kv_src]], 1)
+        return qkv
+
     def forward(self, x, positions, inv_freq, attn_scale, meta):
-        a = self.core(self.pre(x, positions, inv_freq, attn_scale), meta)
+        qkv = self.pre(x, positions, inv_freq, attn_scale)
+        if self.kv_store or self.kv_src is not None:
+            qkv = self.share_kv(qkv, meta)
+        a = self.core(qkv, meta)
         if self.out_gate is not None:
             a = (a.float() * torch.sigmoid(self.out_gate(x).float())).to(a.dtype)
         return self.o_proj(a)
@@ -346,6 +363,14 @@ class DecoderLayer(nn.Module):
             inv = cfg.layer_inv_freq(idx)
             self.self_attn.local_inv_freq = inv.to(device) if device is not None else inv
             del wide
+            first_shared = cfg.num_hidden_layers - int((cfg.extra or {}).get("num_kv_shared_layers") or 0)
+            if 0 < first_shared < cfg.num_hidden_layers:
+                kinds = [cfg.sliding_window(i) == 0 for i in range(cfg.num_hidden_layers)]
+                last_of_kind = {k: max(i for i in range(first_shared) if kinds[i] == k) for k in set(kinds[:first_shared])}
+                if idx >= first_shared:
+                    self.self_attn.kv_src = last_of_kind[kinds[idx]]
+                else:
+                    self.self_attn.kv_store = last_of_kind[kinds[idx]] == idx
         else:
             self.self_attn = Attention(cfg, dtype, device)
         self.self_attn.layer_idx = idx
@@ -362,6 +387,10 @@ class DecoderLayer(nn.Module):
         self.parallel_block = cfg.parallel_block()     # Cohere: one norm, attention and MLP side by side
         if not self.parallel_block:
             self.post_attention_layernorm = make_norm(cfg, cfg.hidden_size, dtype, device, offset=off)
+        self.ln_mlp = None
+        if cfg.model_type == "falcon" and self.parallel_block and (cfg.extra or {}).get("new_decoder_architecture") \
+                and int((cfg.extra or {}).get("num_ln_in_parallel_attn") or 2) == 2:
+            self.ln_mlp = make_norm(cfg, cfg.hidden_size, dtype, device, offset=off)
         # Gemma 2 / 3: post_attention_layernorm and post_feedforward_layernorm act on the BRANCH outputs,
         # pre_feedforward_layernorm takes the place the post-attention norm has elsewhere
         self.post_norm_only = cfg.post_norm_only()     # OLMo 2 / 3: branches read the stream itself, norms on their outputs
@@ -385,15 +414,40 @@ class DecoderLayer(nn.Module):
         elif cfg.model_type in ("lfm2", "lfm2_moe"):   # its own width rule (two thirds, rounded up to a multiple)
             self.mlp = MLP(cfg.hidden_size, int((cfg.extra or {}).get("mlp_width") or cfg.intermediate_size), "silu", False,
                            dtype, device)
-        elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus", "phi"):      # up -> activation -> down, no gate
+        elif cfg.model_type in ("arcee", "nemotron", "starcoder2", "apertus", "phi", "falcon"):      # up -> activation -> down, no gate
             self.mlp = PlainMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device)
         else:
-            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, cfg.mlp_bias, dtype, device,
+            inter = cfg.intermediate_size
+            if (cfg.model_type == "gemma4_text" and (cfg.extra or {}).get("use_double_wide_mlp")
+                    and 0 < cfg.num_hidden_layers - int((cfg.extra or {}).get("num_kv_shared_layers") or 0) <= idx):
+                inter *= 2           # the layers that make no keys / values of their own get an MLP twice as wide
+            self.mlp = MLP(cfg.hidden_size, inter, cfg.hidden_act, cfg.mlp_bias, dtype, device,
                            fused_names=cfg.model_type in ("phi3", "glm", "glm4"))
         self.is_moe = cfg.is_moe_layer(idx)
         # Gemma 4: the layer output (stream included) is multiplied by a stored scalar
         self.layer_scalar = nn.Parameter(torch.ones(1, dtype=dtype, device=device), requires_grad=False) \
             if cfg.model_type == "gemma4_text" else None
+        self.idx = idx
+        self.ple_width, self.g4_moe = 0, None
+        if cfg.model_type == "gemma4_text":
+            ex = cfg.extra or {}
+            self.ple_width = int(ex.get("hidden_size_per_layer_input") or 0)
+            if self.ple_width:     # a gated read of this layer's slice of the per-layer input embeddings, after the MLP
+                self.per_layer_input_gate = FusedLinear(cfg.hidden_size, [self.ple_width], ["per_layer_input_gate"], dtype=dtype, device=device)
+                self.per_layer_projection = FusedLinear(self.ple_width, [cfg.hidden_size], ["per_layer_projection"], dtype=dtype, device=device)
+                self.post_per_layer_input_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+            g4 = ex.get("g4_experts")
+            if g4:                 # routed experts BESIDE the dense MLP, each branch with its own output norm
+                import dataclasses
+
+                from .moe import SparseMoE
+
+                sub = dataclasses.replace(cfg, num_experts=g4["num_experts"], num_experts_per_tok=g4["top_k"],
+                                          moe_intermediate_size=g4["intermediate"], router_aux_loss_coef=0.0)
+                self.g4_moe = SparseMoE(sub, dtype, device)
+                self.post_feedforward_layernorm_1 = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+                self.post_feedforward_layernorm_2 = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+                self.pre_feedforward_layernorm_2 = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
 
     def _stream(self, h, residual):
         """(input of the attention branch, residual stream)."""
@@ -423,12 +477,19 @@ class DecoderLayer(nn.Module):
         else:
             x, residual = self.post_attention_layernorm(a, residual)
         y, aux = self.mlp(x) if self.is_moe else (self.mlp(x), None)
+        if self.g4_moe is not None:
+            y2, _ = self.g4_moe(self.pre_feedforward_layernorm_2.plain(residual), router_x=residual)
+            y = self.post_feedforward_layernorm_1.plain(y) + self.post_feedforward_layernorm_2.plain(y2)
         if self.sandwich:
             y = self.post_feedforward_layernorm.plain(y)
         if rm != 1.0:
             y = y * rm
         if self.layer_scalar is not None:
-            return (residual + y) * self.layer_scalar.to(y.dtype), None, aux
+            h = residual + y
+            if self.ple_width:
+                g = Fn.glu(torch.cat([self.per_layer_input_gate(h), self._ple.to(h.dtype)], -1), self.mlp.act)     # act(gate) * input
+                h = h + self.post_per_layer_input_norm.plain(self.per_layer_projection(g))
+            return h * self.layer_scalar.to(y.dtype), None, aux
         return y, residual, aux
 
     def forward_selective(self, h, residual, positions, inv_freq, attn_scale, meta):
@@ -437,18 +498,23 @@ class DecoderLayer(nn.Module):
         projections, rotary embedding, the MLP — is recomputed in the backward pass (the reference's
         ``selective_checkpointing: {save: [attention]}``, src/axolotl/monkeypatch/selective_checkpointing.py:167-330)."""
         if (not hasattr(self.self_attn, "core") or getattr(self.self_attn, "out_gate", None) is not None
-                or getattr(self.self_attn, "indexer", None) is not None or self.parallel_block):
+                or getattr(self.self_attn, "indexer", None) is not None or self.parallel_block or self.ple_width):
             # state-space / linear-attention mixers have no attention result to keep (and a gated attention output
             # needs the layer input again)
             return checkpoint(self.forward, h, residual, positions, inv_freq, attn_scale, meta, use_reentrant=False)
         qkv, residual = checkpoint(self._before_attention, h, residual, positions, inv_freq, attn_scale, use_reentrant=False)
+        if getattr(self.self_attn, "kv_store", False) or getattr(self.self_attn, "kv_src", None) is not None:
+            qkv = self.self_attn.share_kv(qkv, meta)
         a = self.self_attn.core(qkv, meta)
         return checkpoint(self._after_attention, a, residual, use_reentrant=False)
 
     def forward(self, h, residual, positions, inv_freq, attn_scale, meta):
+        if self.ple_width:
+            self._ple = meta.per_layer_inputs[:, self.idx]
         x, residual = self._stream(h, residual)
         if self.parallel_block:
-            return self.self_attn(x, positions, inv_freq, attn_scale, meta) + self.mlp(x), residual, None
+            xm = x if self.ln_mlp is None else self.ln_mlp.plain(residual)      # Falcon's larger models: a norm per branch
+            return self.self_attn(x, positions, inv_freq, attn_scale, meta) + self.mlp(xm), residual, None
         return self._mlp_half(self.self_attn(x, positions, inv_freq, attn_scale, meta), residual)
 
 
@@ -471,6 +537,20 @@ class CausalLM(nn.Module):
         # (hidden states, output weight) - the chunked cross-entropy, log-prob and distillation paths, generation -
         # sees it without knowing
         self.lm_head_bias = nn.Parameter(torch.zeros(cfg.vocab_size, dtype=dtype, device=device)) if cfg.model_type == "phi" else None
+        self.vision = None       # LLaVA checkpoints: CLIP tower + projector feeding the image placeholder tokens
+        if (cfg.extra or {}).get("vision_wrapper"):
+            from .vision import VisionFrontEnd
+
+            self.vision = VisionFrontEnd(cfg.extra["vision_wrapper"], cfg.hidden_size, dtype, device)
+        # Gemma 4: a second embedding table gives every layer its own small input vector per token; it is mixed with a
+        # projection of the (scaled) token embedding and read through a gate after each layer's MLP
+        self.ple_width = int((cfg.extra or {}).get("hidden_size_per_layer_input") or 0) if cfg.model_type == "gemma4_text" else 0
+        if self.ple_width:
+            L, Dp = cfg.num_hidden_layers, self.ple_width
+            self.embed_tokens_per_layer = nn.Parameter(torch.empty(int((cfg.extra or {}).get("vocab_size_per_layer_input") or cfg.vocab_size),
+                                                                   L * Dp, dtype=dtype, device=device))
+            self.per_layer_model_projection = FusedLinear(cfg.hidden_size, [L * Dp], ["per_layer_model_projection"], dtype=dtype, device=device)
+            self.per_layer_projection_norm = RMSNorm(Dp, cfg.rms_norm_eps, dtype, device)
         inv, scale = cfg.rope_inv_freq()
         self.register_buffer("inv_freq", inv.to(device) if device is not None else inv, persistent=False)
         self.attn_scale = scale
@@ -565,8 +645,10 @@ class CausalLM(nn.Module):
         if seed is not None:
             gen = torch.Generator(device=self.embed_tokens.device)
             gen.manual_seed(seed)
+        if self.vision is not None:
+            self.vision.init_weights(std, seed or 0)
         for name, p in self.named_parameters():
-            if "lora_" in name:
+            if "lora_" in name or name.startswith("vision."):
                 continue
             if p.dim() >= 2:
                 p.normal_(0.0, std, generator=gen)
@@ -638,7 +720,7 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids, position_ids=None, labels=None, attn_meta=None, num_items=None,
-                return_logits=None, shift_labels=True, aux_scale=1.0, capture_hidden=None):
+                return_logits=None, shift_labels=True, aux_scale=1.0, capture_hidden=None, pixel_values=None):
         """input_ids / position_ids / labels: [B, S] (or [T]). Returns CausalLMOutput.
 
         ``labels`` follow the HF convention (unshifted; the model shifts by one inside each row)
@@ -673,11 +755,25 @@ class CausalLM(nn.Module):
         em = cfg.multiplier("embedding_multiplier")
         if em != 1.0:
             h = h * em
+        if pixel_values is not None:        # image placeholder tokens take the projected patch features
+            if self.vision is None:
+                raise ValueError("pixel_values were given to a model without an image front end")
+            from .vision import merge_image_features
+
+            h = merge_image_features(h, ids, self.vision(pixel_values), self.vision.image_token_id)
         if self.neftune_noise_alpha and self.training:
             # noise magnitude alpha / sqrt(L * d) with L the row length (NEFTune, as applied by the HF
             # trainer the reference builds on)
             mag = float(self.neftune_noise_alpha) / math.sqrt(S * h.shape[-1])
             h = h + (torch.rand_like(h) * 2 - 1) * mag
+        if cfg.model_type == "gemma4_text":
+            attn_meta.shared_kv = {}
+        if self.ple_width:
+            L, Dp = len(self.layers), self.ple_width
+            tok = Fn.embedding(self.embed_tokens_per_layer, ids) * float(torch.tensor(Dp ** 0.5).to(self.embed_tokens_per_layer.dtype))
+            proj = self.per_layer_model_projection(h) * (cfg.hidden_size ** -0.5)
+            proj = self.per_layer_projection_norm.plain(proj.reshape(-1, Dp)).reshape(-1, L, Dp)
+            attn_meta.per_layer_inputs = (proj + tok.reshape(-1, L, Dp).to(proj.dtype)) * (2.0 ** -0.5)
         inv_freq = self.inv_freq
         if self.longrope_orig and getattr(attn_meta, "max_len", 0) > self.longrope_orig:
             inv_freq = self.inv_freq_long

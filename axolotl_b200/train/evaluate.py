@@ -6,7 +6,7 @@ import math
 import torch
 
 from ..data.loading import load_datasets
-from .run import build_model, make_batches_fn, setup_adapter
+from . import run as _run
 from .trainer import count_trainable, to_device_batch
 
 
@@ -18,10 +18,10 @@ def evaluate(cfg) -> dict:
     dev = _device(cfg)
     meta = load_datasets(cfg)
     ds = meta.eval if meta.eval is not None else meta.train
-    model = build_model(cfg, dev)
-    setup_adapter(cfg, model)
+    model = _run.build_model(cfg, dev)
+    _run.setup_adapter(cfg, model)
     model.eval()
-    fn, _ = make_batches_fn(cfg, ds, 0, 1, None, is_eval=True)
+    fn, _ = _run.make_batches_fn(cfg, ds, 0, 1, None, is_eval=True)
     tot, items = 0.0, 0
     for b in fn():
         d = to_device_batch(b, dev)
@@ -38,8 +38,8 @@ def generate_text(cfg, prompt: str, max_new_tokens=64, temperature=0.0) -> str:
 
     dev = _device(cfg)
     tok = load_tokenizer(cfg)
-    model = build_model(cfg, dev)
-    setup_adapter(cfg, model)
+    model = _run.build_model(cfg, dev)
+    _run.setup_adapter(cfg, model)
     ids = torch.tensor([tok(prompt)["input_ids"]], device=dev)
     out = model.generate(ids, max_new_tokens=max_new_tokens, temperature=temperature, eos_token_id=tok.eos_token_id)
     return tok.decode(out[0].tolist(), skip_special_tokens=True)

@@ -135,6 +135,14 @@ FAMILIES = {
                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=16,
                         layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
                         attention_k_eq_v=True, num_global_key_value_heads=1, tie_word_embeddings=True, max_position_embeddings=256),
+    "gemma4_text_full": dict(model_type="gemma4_text", vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=16,
+                             layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+                             hidden_size_per_layer_input=16, vocab_size_per_layer_input=320, num_kv_shared_layers=2,
+                             enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
+                             tie_word_embeddings=True, max_position_embeddings=256),
+    "falcon": dict(model_type="falcon", vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2,
+                   new_decoder_architecture=True, ffn_hidden_size=160, max_position_embeddings=256, tie_word_embeddings=True),
     "gpt_oss": dict(model_type="gpt_oss", vocab_size=320, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
                     sliding_window=8, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False,

@@ -1039,3 +1039,169 @@ def test_gemma4_text_dense_matches_hf(tmp_path, k_eq_v):
     again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
     with torch.no_grad():
         assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+@pytest.mark.parametrize("ple,experts", [(24, False), (0, True), (24, True)])
+def test_gemma4_text_per_layer_inputs_and_expert_block_match_hf(tmp_path, ple, experts):
+    """Gemma 4 with its two optional parts: the per-layer input embeddings (a second table, mixed with a projection of the
+    token embedding, read through a gate after every MLP) and the expert block that runs beside the dense MLP with a
+    router of its own (input normalised and scaled per channel, a scale per chosen expert)."""
+    d = dict(model_type="gemma4_text", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8,
+             layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=ple,
+             num_kv_shared_layers=0, enable_moe_block=experts, num_experts=4 if experts else None, top_k_experts=2 if experts else None,
+             moe_intermediate_size=48 if experts else None, final_logit_softcapping=20.0, rms_norm_eps=1e-6,
+             tie_word_embeddings=True, max_position_embeddings=256, pad_token_id=0, vocab_size_per_layer_input=300)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(61)
+    _randomize_norms(ours, 0.5, 1.5)
+    with torch.no_grad():
+        for l in ours.layers:
+            l.layer_scalar.uniform_(0.7, 1.2)
+            if experts:
+                l.g4_moe.router_scale.uniform_(0.5, 1.5)
+                l.g4_moe.per_expert_scale.uniform_(0.5, 1.5)
+                l.g4_moe.gate.normal_(0.0, 0.5)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    assert bool(hf_model.config.enable_moe_block) == experts and hf_model.config.hidden_size_per_layer_input == ple
+    lens = [21, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+    # and it trains: every new tensor gets a gradient
+    ours.train()
+    out = ours(ids, pos, labels=ids)
+    out.loss.backward()
+    if ple:
+        assert ours.embed_tokens_per_layer.grad is not None and ours.layers[1].per_layer_projection.weight.grad.abs().sum() > 0
+    if experts:
+        assert ours.layers[1].g4_moe.experts.down_proj.grad.abs().sum() > 0 and ours.layers[1].g4_moe.router_scale.grad is not None
+
+
+@pytest.mark.parametrize("double_wide", [False, True])
+def test_gemma4_text_shared_keys_values_match_hf(tmp_path, double_wide):
+    """Gemma 4's last layers make no keys / values: each attends those of the last earlier layer of its kind (sliding or
+    global); optionally their MLPs are twice as wide. (HF applies the sharing through its cache object, so the reference
+    logits come from a forward pass with the cache on.)"""
+    d = dict(model_type="gemma4_text", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=6,
+             num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8,
+             layer_types=["sliding_attention", "full_attention", "sliding_attention", "sliding_attention", "sliding_attention", "full_attention"],
+             hidden_size_per_layer_input=16, num_kv_shared_layers=3, use_double_wide_mlp=double_wide, enable_moe_block=False,
+             final_logit_softcapping=20.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=256,
+             pad_token_id=0, vocab_size_per_layer_input=300)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(67)
+    assert [l.self_attn.kv_src for l in ours.layers] == [None, None, None, 2, 2, 1]
+    assert [l.self_attn.kv_store for l in ours.layers] == [False, True, True, False, False, False]
+    assert ours.layers[4].mlp.down_proj.weight.shape[1] == (192 if double_wide else 96)
+    _randomize_norms(ours, 0.5, 1.5)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    hf_model.config.use_cache = True
+    lens = [21, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    # training: full and selective recomputation give the gradients of the plain graph
+    ours.train()
+    grads = []
+    for mode in (None, "full", "selective"):
+        ours.zero_grad(set_to_none=True)
+        ours.enable_gradient_checkpointing(mode is not None, selective=mode == "selective")
+        ours(ids, pos, labels=ids).loss.backward()
+        grads.append(ours.layers[1].self_attn.qkv_proj.weight.grad.clone())
+    assert grads[0].abs().sum() > 0
+    assert torch.allclose(grads[0], grads[1], atol=1e-6) and torch.allclose(grads[0], grads[2], atol=1e-6)
+
+
+@pytest.mark.parametrize("variant", ["multi_query", "new_arch", "new_arch_one_norm", "per_head", "sequential"])
+def test_falcon_matches_hf(tmp_path, variant):
+    """Falcon (rotary checkpoints): LayerNorm, an ungated GELU MLP, attention and MLP side by side, and one fused
+    query_key_value projection in three row layouts: [queries, key, value] (multi-query, 7B), per key / value group
+    (40B / 180B, a norm per branch; Falcon 2 has one), per head (no sharing). Also the sequential layer form."""
+    d = dict(model_type="falcon", vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, alibi=False,
+             bias=variant in ("per_head", "sequential"), max_position_embeddings=256, tie_word_embeddings=variant != "new_arch",
+             new_decoder_architecture=variant.startswith("new_arch"), multi_query=variant in ("multi_query", "sequential"),
+             parallel_attn=variant != "sequential", num_kv_heads=2 if variant.startswith("new_arch") else None,
+             num_ln_in_parallel_attn=1 if variant == "new_arch_one_norm" else None, ffn_hidden_size=160)
+    cfg = ModelConfig.from_hf_dict(d)
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(71)
+    assert ours.layers[0].self_attn.Hk == {"multi_query": 1, "sequential": 1, "per_head": 4}.get(variant, 2)
+    assert (ours.layers[0].ln_mlp is not None) == (variant == "new_arch")
+    _randomize_norms(ours, 0.5, 1.5)
+    with torch.no_grad():
+        for n, p in ours.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0.0, 0.1)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                 attn_implementation="eager")
+    hf_model.eval()
+    lens = [21, 30]
+    ids, pos = _packed_inputs(300, lens)
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pos, return_logits=True).logits
+    ref = _hf_docwise_logits(hf_model, ids, lens)
+    assert torch.allclose(got, ref, atol=1e-3, rtol=3e-3), (got - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pos, return_logits=True).logits, got, atol=1e-5)
+
+
+def test_llava_image_front_end_matches_hf(tmp_path):
+    """LLaVA: CLIP vision tower (hidden state before the last layer, class token dropped), two-layer projector, patch
+    features written over the image placeholder tokens, then the ordinary causal language model. Logits of a text + image
+    prompt against HF ``LlavaForConditionalGeneration``; the checkpoint round-trips; the projector trains, the tower does not."""
+    vc = dict(model_type="clip_vision_model", hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+              image_size=28, patch_size=14, num_channels=3, hidden_act="quick_gelu", layer_norm_eps=1e-5, projection_dim=16)
+    tc = dict(model_type="llama", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    d = dict(model_type="llava", text_config=tc, vision_config=vc, image_token_id=299, vision_feature_layer=-2,
+             vision_feature_select_strategy="default", projector_hidden_act="gelu", multimodal_projector_bias=True)
+    cfg = ModelConfig.from_hf_dict(d)
+    assert cfg.model_type == "llama" and cfg.extra["vision_wrapper"]["image_token_id"] == 299
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(73)
+    with torch.no_grad():
+        for n, p in ours.vision.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0.0, 0.1)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForImageTextToText.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                        attn_implementation="eager")
+    hf_model.eval()
+    g = torch.Generator().manual_seed(5)
+    pixels = torch.randn(2, 3, 28, 28, generator=g)
+    text = torch.randint(3, 290, (30,), generator=g)
+    ids = torch.cat([text[:5], torch.full((4,), 299), text[5:17], torch.full((4,), 299), text[17:]])[None]     # 4 patches per image
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pixel_values=pixels, return_logits=True).logits
+        ref = hf_model(input_ids=ids, pixel_values=pixels).logits[0]
+    assert torch.allclose(got.reshape(ref.shape), ref, atol=1e-3, rtol=3e-3), (got.reshape(ref.shape) - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    assert again.vision is not None
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pixel_values=pixels, return_logits=True).logits, got, atol=1e-5)
+    ours.train()
+    labels = ids.clone()
+    labels[ids == 299] = -100
+    ours(ids, labels=labels, pixel_values=pixels).loss.backward()
+    assert ours.vision.multi_modal_projector.linear_1.weight.grad.abs().sum() > 0
+    assert all(p.grad is None for p in ours.vision.vision_tower.parameters())
+    with pytest.raises(ValueError, match="placeholder"):
+        ours(ids[:, :-1 - 20], pixel_values=pixels)

@@ -1324,9 +1324,14 @@ _GPU_FAMILIES = {
     "gemma4_text": dict(model_type="gemma4_text", num_hidden_layers=3, head_dim=256, global_head_dim=512, sliding_window=128,
                         layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
                         attention_k_eq_v=True, num_global_key_value_heads=1, tie_word_embeddings=True),
+    "gemma4_text_full": dict(model_type="gemma4_text", num_hidden_layers=4, head_dim=256, global_head_dim=512, sliding_window=128,
+                             layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+                             hidden_size_per_layer_input=128, num_kv_shared_layers=2, enable_moe_block=True, num_experts=8,
+                             top_k_experts=2, moe_intermediate_size=128, tie_word_embeddings=True),
     "afmoe": dict(model_type="afmoe", num_hidden_layers=4, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
                   num_shared_experts=1, num_dense_layers=1, sliding_window=128),
     "olmo": dict(model_type="olmo", clip_qkv=8.0),
+    "falcon": dict(model_type="falcon", new_decoder_architecture=True, num_kv_heads=2, ffn_hidden_size=1024),
     "lfm2_moe": dict(model_type="lfm2_moe", num_hidden_layers=3, layer_types=["conv", "full_attention", "conv"], conv_L_cache=3,
                      moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, num_dense_layers=1, tie_word_embeddings=True),
     "mistral4": dict(model_type="mistral4", moe_intermediate_size=128, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,

@@ -190,6 +190,7 @@ def test_baseten_provider_writes_the_job_directory_and_pushes_it(tmp_path):
 def test_gradio_interface_streams_generated_text(monkeypatch):
     import torch
 
+    import axolotl_b200.train.evaluate  # noqa: F401  (imported before the builders below are replaced)
     from axolotl_b200.cli import gradio_ui
 
     class Tok:

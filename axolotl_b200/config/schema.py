@@ -334,6 +334,14 @@ class AxolotlConfig(_Base):
     chat_template: str | None = None
     chat_template_jinja: str | None = None
     chat_template_kwargs: dict | None = None
+    # multimodal (LLaVA-style checkpoints: CLIP tower + projector in front of the language model)
+    processor_type: str | None = None
+    processor_config: str | None = None
+    is_multimodal: bool | None = None
+    image_size: int | list[int] | None = None
+    image_resize_algorithm: str | None = None
+    role_boundaries: list[dict] | None = None
+    freeze_mm_modules: bool | None = None        # False: the vision tower trains too (the projector follows the adapter / freezing rules)
     eot_tokens: list[str] | None = None
     default_system_message: str | None = None
     special_tokens: SpecialTokens | None = None
@@ -588,9 +596,6 @@ UNSUPPORTED_KEYS = {
     "flash_optimum": "BetterTransformer is not used",
     "fp8": "fp8 mixed precision is not implemented; bf16 tensor-core kernels are used",
     "large_head_attention": "head widths 64, 128, 256 (and 192/128 latent attention) have native kernels; 512 does not",
-    "processor_type": "multimodal training is not available: the data path exists (axolotl_b200.data.multimodal: "
-                      "processing strategies, role masking, collator) but no vision / audio encoder graph does",
-    "freeze_mm_modules": "multimodal training is not available (no vision / audio encoder graph)",
 }
 
 # Reference keys that are accepted and carried through without effect on this framework (their
@@ -602,8 +607,8 @@ INERT_KEYS = {
     "dpo_use_liger_kernel", "dpo_use_logits_to_keep", "dpo_loss_weights", "embeddings_skip_upcast",
     "experimental_skip_move_to_device", "flash_attn_cross_entropy", "flash_attn_d512", "flash_attn_rms_norm", "flex_attn_compile_kwargs", "fp8_enable_fsdp_float8_all_gather", "fused_attn_kernel", "gc_collect_steps",
     "gemma4_hybrid_attn_impl", "gradio_max_new_tokens", "gradio_server_name",
-    "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision", "image_resize_algorithm",
-    "image_size", "is_falcon_derived_model", "role_boundaries",
+    "gradio_server_port", "gradio_share", "gradio_temperature", "gradio_title", "hub_revision",
+    "is_falcon_derived_model",
     "lisa_layers_attribute", "lora_on_cpu", "low_cpu_mem_usage",
     "model_quantization_config_kwargs", "num_dataset_shards_to_save",
     "overrides_of_model_kwargs", "peft", "peft_ensure_weight_tying", "preprocess_iterable", "processor_kwargs", "qgalore_cos_threshold", "qgalore_gamma_proj",

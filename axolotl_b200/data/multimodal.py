@@ -111,7 +111,7 @@ def resolve_role_boundaries(specs, tokenizer) -> list[RoleBoundary]:
     include_end?}``; ``end: eos_token`` is the tokenizer's eos id, a missing ``end`` runs to the end of the row."""
     out = []
     for i, spec in enumerate(specs):
-        d = spec.model_dump() if hasattr(spec, "model_dump") else dict(spec)
+        d = dict(spec) if isinstance(spec, dict) else (spec.model_dump() if callable(getattr(spec, "model_dump", None)) else dict(spec))
         if not d.get("role") or d.get("start") is None:
             raise ValueError(f"role_boundaries[{i}] needs both 'role' and 'start' (got {d!r})")
         start = _encode(tokenizer, d["start"])
@@ -428,3 +428,66 @@ class MultiModalChatCollator:
             return_dict=True, chat_template=self.strategy.chat_template, processor_kwargs={"padding": self.padding})
         batch["labels"] = self.strategy.process_labels(batch["input_ids"])
         return batch
+
+
+MEDIA_TENSOR_KEYS = ("pixel_values",)
+
+
+def unpad_batch(batch, pad_token_id=None) -> dict:
+    """The processor's padded [B, S] batch -> one padding-free row for the varlen kernels: the real tokens of every
+    conversation back to back with positions restarting at each, the media tensors alongside (row order kept, so image i
+    still meets its placeholder tokens)."""
+    ids, labels = batch["input_ids"], batch["labels"]
+    mask = batch.get("attention_mask")
+    if mask is None:
+        mask = torch.ones_like(ids) if pad_token_id is None else (ids != pad_token_id).long()
+    keep = mask.bool()
+    lens = keep.sum(1)
+    pos = (keep.long().cumsum(1) - 1).clamp(min=0)
+    out = {"input_ids": ids[keep][None].contiguous(), "labels": labels[keep][None].contiguous(),
+           "position_ids": pos[keep][None].to(torch.int32).contiguous(),
+           "cu_seqlens": torch.cat([torch.zeros(1, dtype=torch.int32), lens.cumsum(0).to(torch.int32)]),
+           "aux_tensors": {k: batch[k] for k in MEDIA_TENSOR_KEYS if batch.get(k) is not None}}
+    return out
+
+
+class RawConversationDataset:
+    """Untokenised multimodal rows: the processor renders and tokenises them batch by batch (media tensors are too large
+    to prepare ahead)."""
+
+    def __init__(self, rows):
+        self.rows = rows
+        self.lengths = None
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        return self.rows[int(i)]
+
+
+def make_multimodal_batches_fn(cfg, ds, collator, rank, dp_size, is_eval=False):
+    """callable(epoch) -> iterator of padding-free micro-batches of ``micro_batch_size`` conversations for this rank."""
+    import numpy as np
+
+    mbs = (cfg.get("eval_batch_size") if is_eval else cfg.get("micro_batch_size")) or 1
+    seq = cfg.get("sequence_len")
+    pad = getattr(collator.tokenizer, "pad_token_id", None)
+
+    def batches(epoch=0):
+        n = len(ds)
+        order = np.arange(n) if is_eval else np.random.default_rng((cfg.get("seed") or 42) + epoch).permutation(n)
+        mine = order[rank::dp_size]
+        if not is_eval:
+            mine = mine[: (n // (mbs * dp_size)) * mbs]
+        for i in range(0, len(mine), mbs):
+            idx = mine[i:i + mbs]
+            if len(idx) < mbs and not is_eval:
+                break
+            b = collator([ds[j] for j in idx])
+            if seq and b["input_ids"].shape[1] > seq:
+                raise ValueError(f"a multimodal conversation renders to {b['input_ids'].shape[1]} tokens, sequence_len is {seq}: "
+                                 "truncation would cut through image placeholder tokens; raise sequence_len or drop the row")
+            yield unpad_batch(b, pad)
+
+    return batches

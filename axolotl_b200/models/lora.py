@@ -132,7 +132,10 @@ def _hf_path(fused_name: str, sub: str, model=None) -> str:
     if model is not None:
         for src, dst in _checkpoint_renames(model):
             if path.startswith(src):
-                return dst + path[len(src):]
+                path = dst + path[len(src):]
+                break
+        if getattr(model, "vision", None) is not None and path.startswith("model."):     # LLaVA keeps the language model one level down
+            path = "model.language_model." + path[len("model."):]
     return path
 
 

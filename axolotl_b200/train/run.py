@@ -400,6 +400,16 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         cfg["pad_token_id"] = tokenizer.pad_token_id
     objective_mode = bool(cfg.get("rl") or cfg.get("reward_model"))   # preference / online-RL objectives
     streaming = bool(cfg.get("pretraining_dataset") or cfg.get("streaming")) and not objective_mode
+    multimodal = bool(cfg.get("processor_type") or cfg.get("is_multimodal")) and not objective_mode
+    if dataset_meta is None and multimodal:
+        from ..data.loading import _shard, read_raw
+        from ..data.multimodal import RawConversationDataset
+
+        rows = [r for d in (cfg.get("datasets") or []) for r in _shard(read_raw(dict(d)), dict(d))]
+        n_val = int(len(rows) * cfg["val_set_size"]) if cfg.get("val_set_size") and cfg["val_set_size"] < 1 else int(cfg.get("val_set_size") or 0)
+        dataset_meta = TrainDatasetMeta(RawConversationDataset(rows[n_val:]), RawConversationDataset(rows[:n_val]) if n_val else None)
+        per_step = cfg["micro_batch_size"] * cfg["gradient_accumulation_steps"] * int(os.environ.get("WORLD_SIZE", "1"))
+        dataset_meta.total_num_steps = max(int(len(rows[n_val:]) // per_step * (cfg.get("num_epochs") or 1)), 1)
     if dataset_meta is None and cfg.get("kd_trainer"):
         dataset_meta = load_row_datasets(cfg)
     if dataset_meta is None and not objective_mode and not streaming:
@@ -428,6 +438,9 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         parallel.reshard_after_forward = True if raf is None else bool(raf)
         parallel.apply_tp(model)          # shards projections before adapters are created
     spec = setup_adapter(cfg, model)
+    if getattr(model, "vision", None) is not None and cfg.get("freeze_mm_modules") is False:
+        for p_ in model.vision.parameters():       # the image tower and projector train with the language model
+            p_.requires_grad_(True)
     pm.call("post_model_load", cfg, model)
     if cfg.get("gradient_checkpointing") or (cfg.get("fsdp_config") or {}).get("activation_checkpointing"):
         ao = cfg.get("activation_offloading") or None
@@ -477,6 +490,25 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
         if cfg.get("test_datasets"):
             ev = load_datasets(dict(cfg, datasets=cfg["test_datasets"], test_datasets=None, val_set_size=None), tokenizer)
             eval_fn, _ = make_batches_fn(cfg, ev.train, dp_rank, dp_size, parallel, is_eval=True)
+    elif multimodal:
+        from ..data import multimodal as mm
+
+        if getattr(model, "vision", None) is None:
+            raise ValueError(f"multimodal training needs a checkpoint with an image front end this package builds (LLaVA: CLIP "
+                             f"tower + projector); '{model.config.model_type}' was loaded as a language model only")
+        if cfg.get("sample_packing"):
+            raise ValueError("sample_packing is not available for multimodal datasets (batches are already padding-free)")
+        processor = mm.load_processor(cfg, tokenizer)
+        d0 = dict((cfg.get("datasets") or [{}])[0])
+        strategy = mm.get_processing_strategy(
+            processor, cfg.get("chat_template_jinja"), cfg.get("chat_template"), image_size=cfg.get("image_size"),
+            image_resize_algorithm=cfg.get("image_resize_algorithm"), train_on_inputs=bool(cfg.get("train_on_inputs")),
+            roles_to_train=d0.get("roles_to_train"), train_on_eos=d0.get("train_on_eos"),
+            role_boundaries=d0.get("role_boundaries") or cfg.get("role_boundaries"), field_messages=d0.get("field_messages"))
+        collator = mm.MultiModalChatCollator(getattr(processor, "tokenizer", tokenizer), strategy)
+        train_fn, sampler = mm.make_multimodal_batches_fn(cfg, dataset_meta.train, collator, dp_rank, dp_size), None
+        if dataset_meta.eval is not None and len(dataset_meta.eval):
+            eval_fn = mm.make_multimodal_batches_fn(cfg, dataset_meta.eval, collator, dp_rank, dp_size, is_eval=True)
     else:
         train_fn, sampler = make_batches_fn(cfg, dataset_meta.train, dp_rank, dp_size, parallel)
         if dataset_meta.eval is not None and len(dataset_meta.eval):

@@ -164,9 +164,10 @@ class Trainer:
                     b["ga_steps"] = len(micro_batches)
                     loss = self.compute_loss(model, b, n_items)
                 else:
+                    media = {"pixel_values": b["pixel_values"]} if "pixel_values" in b else {}
                     out = model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"],
                                 num_items=n_items, shift_labels=not b.get("labels_preshifted", False),
-                                aux_scale=1.0 / len(micro_batches))
+                                aux_scale=1.0 / len(micro_batches), **media)
                     loss = out.loss
             loss.backward()
             loss_total = loss.detach() if loss_total is None else loss_total + loss.detach()
@@ -359,7 +360,8 @@ class Trainer:
             b = to_device_batch(cpu_batch, self.device)
             n = max(count_trainable(cpu_batch["labels"]), 1)
             with torch.enable_grad():  # the fused loss computes its gradient in the forward pass
-                out = self.model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"], num_items=n)
+                media = {"pixel_values": b["pixel_values"]} if "pixel_values" in b else {}
+                out = self.model(b["input_ids"], b["position_ids"], b["labels"], attn_meta=b["attn_meta"], num_items=n, **media)
             tot_loss += float(out.loss.item()) * n
             tot_items += n
         if self.parallel is not None and self.world_size > 1:

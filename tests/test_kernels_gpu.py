@@ -1405,3 +1405,41 @@ def test_add_layernorm_kernel_matches_fp32_reference(has_res, has_w, has_b, offs
         assert _rel_err(w.grad.float().cpu(), wc.grad) < 2e-2
     if has_b:
         assert _rel_err(b.grad.float().cpu(), bc.grad) < 2e-2
+
+
+@pytest.mark.gpu
+def test_llava_image_front_end_on_the_device_matches_cpu_fp32():
+    """CLIP tower + projector feeding image placeholder tokens of a Llama language model: bf16 on the device (tower
+    through library attention, language model through the tcgen05 / varlen kernels) against fp32 on the CPU."""
+    from axolotl_b200.models.config import ModelConfig
+    from axolotl_b200.models.transformer import CausalLM
+    torch.manual_seed(91)
+    vc = dict(model_type="clip_vision_model", hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+              image_size=56, patch_size=14, num_channels=3, hidden_act="quick_gelu", projection_dim=64)
+    tc = dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, tie_word_embeddings=False, max_position_embeddings=2048)
+    cfg = ModelConfig.from_hf_dict(dict(model_type="llava", text_config=tc, vision_config=vc, image_token_id=2047))
+    ref = CausalLM(cfg, dtype=torch.float32).init_weights(7)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    dev = CausalLM(cfg, dtype=torch.bfloat16, device=_dev())
+    dev.load_state_dict(ref.state_dict())
+    for m in (ref, dev):
+        for p in m.vision.multi_modal_projector.parameters():
+            p.requires_grad_(True)
+    pixels = torch.randn(2, 3, 56, 56).bfloat16().float()
+    rows = [torch.cat([torch.randint(3, 2000, (40,)), torch.full((16,), 2047), torch.randint(3, 2000, (90,))]) for _ in range(2)]
+    ids = torch.cat(rows)[None]
+    pos = torch.cat([torch.arange(len(r)) for r in rows])[None].to(torch.int32)
+    labels = ids.clone()
+    labels[ids == 2047] = -100
+    out_d = dev(ids, pos, labels, pixel_values=pixels)
+    out_d.loss.backward()
+    _check_status()
+    out_c = ref(ids, pos, labels, pixel_values=pixels)
+    out_c.loss.backward()
+    assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item()), (out_d.loss.item(), out_c.loss.item())
+    gd = dev.vision.multi_modal_projector.linear_2.weight.grad.float().cpu()
+    gc = ref.vision.multi_modal_projector.linear_2.weight.grad
+    assert _rel_err(gd, gc) < 0.15, _rel_err(gd, gc)

@@ -270,6 +270,8 @@ __global__ void rope_fast_kernel(__nv_bfloat16* __restrict__ qkv, const int* __r
 
 // Backward of (per-head RMSNorm ->) RoPE for the fused q/k gradient buffer, in place.
 // x_pre holds the pre-norm projection (needed only when norm weights are given).
+// NMAX: rotation pairs a lane keeps in registers (D <= 64 * NMAX).
+template <int NMAX>
 __global__ void rope_qk_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
                                    const __nv_bfloat16* __restrict__ x_pre,
                                    const int* __restrict__ pos, const float* __restrict__ inv_freq,
@@ -292,7 +294,7 @@ __global__ void rope_qk_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
   const __nv_bfloat16* nw = (hd < Hq) ? qn_w : kn_w;
   float* dnw = (hd < Hq) ? dqn_w : dkn_w;
   // inverse rotation first
-  float ga[4], gb[4];  // D <= 256
+  float ga[NMAX], gb[NMAX];
   int n = 0;
   for (int i = lane; i < half; i += 32, ++n) {
     float s, c;
@@ -828,7 +830,7 @@ extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
                                const void* qn_w, const void* kn_w, const float* rstd_in,
                                float* dqn_w, float* dkn_w, void* stream) {
   if (T <= 0) return 0;
-  if (D > 256) return -2;
+  if (D > 512) return -2;
   if (!qn_w && !kn_w && (D % 4) == 0 && (row_stride % 2) == 0) {
     rope_fast_kernel<<<(unsigned)((T + 7) / 8), 256, 0, ST(stream)>>>((__nv_bfloat16*)dqkv, pos, inv_freq, T, Hq + Hk, D,
                                                                      row_stride, -1.f, attn_scale, D);
@@ -836,10 +838,16 @@ extern "C" int axb_rope_qk_bwd(void* dqkv, const void* x_pre, const int* pos,
   }
   const long long warps = (long long)T * (Hq + Hk);
   const int wpb = 8;
-  rope_qk_bwd_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
-      (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)x_pre, pos, inv_freq, T, Hq, Hk, D, row_stride,
-      x_row_stride, attn_scale, (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_in,
-      dqn_w, dkn_w);
+  if (D <= 256)
+    rope_qk_bwd_kernel<4><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
+        (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)x_pre, pos, inv_freq, T, Hq, Hk, D, row_stride,
+        x_row_stride, attn_scale, (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_in,
+        dqn_w, dkn_w);
+  else      // Gemma 4's global layers: 512-wide heads
+    rope_qk_bwd_kernel<8><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
+        (__nv_bfloat16*)dqkv, (const __nv_bfloat16*)x_pre, pos, inv_freq, T, Hq, Hk, D, row_stride,
+        x_row_stride, attn_scale, (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, rstd_in,
+        dqn_w, dkn_w);
   return (int)cudaGetLastError();
 }
 extern "C" int axb_rmsnorm_gated_fwd(const void* x, const void* g, const void* w, void* y,

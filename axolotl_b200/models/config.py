@@ -86,7 +86,14 @@ class ModelConfig:
             d.setdefault("model_type", "llama")
             mt = d["model_type"]
         if mt == "gemma3" and isinstance(d.get("text_config"), dict):   # the multimodal wrapper: its language model
+            wrapper = None
+            if isinstance(d.get("vision_config"), dict) and d["vision_config"].get("hidden_size"):   # + SigLIP tower and projector
+                wrapper = {k: d[k] for k in ("vision_config", "mm_tokens_per_image", "boi_token_index", "eoi_token_index") if k in d}
+                wrapper["image_token_id"] = d.get("image_token_index", d.get("image_token_id", 262144))
+                wrapper["model_type"] = "gemma3"
             d = dict(d["text_config"], model_type="gemma3_text")
+            if wrapper:
+                d["vision_wrapper"] = wrapper
             mt = "gemma3_text"
         if mt == "gemma4" and isinstance(d.get("text_config"), dict):      # the multimodal wrapper: its language model
             d = dict(d["text_config"], model_type="gemma4_text")
@@ -477,6 +484,11 @@ class ModelConfig:
         out.update(d)
         if (vw := out.pop("vision_wrapper", None)):
             vw = dict(vw)
+            if vw["model_type"] == "gemma3":
+                vw["image_token_index"] = vw.pop("image_token_id")
+                return {"model_type": vw.pop("model_type"), "architectures": ["Gemma3ForConditionalGeneration"],
+                        "text_config": {k: v for k, v in out.items() if k != "architectures"},
+                        "torch_dtype": out.get("torch_dtype", "bfloat16"), **vw}
             return {"model_type": vw.pop("model_type"), "architectures": ["LlavaForConditionalGeneration"],
                     "text_config": {k: v for k, v in out.items() if k != "architectures"},
                     "tie_word_embeddings": out.get("tie_word_embeddings", False), "torch_dtype": out.get("torch_dtype", "bfloat16"), **vw}

@@ -758,9 +758,12 @@ class CausalLM(nn.Module):
         if pixel_values is not None:        # image placeholder tokens take the projected patch features
             if self.vision is None:
                 raise ValueError("pixel_values were given to a model without an image front end")
-            from .vision import merge_image_features
+            from .vision import image_groups, merge_image_features
 
             h = merge_image_features(h, ids, self.vision(pixel_values), self.vision.image_token_id)
+            if self.vision.bidirectional_images:
+                attn_meta.image_groups = image_groups(ids, self.vision.image_token_id)
+                attn_meta.image_group_span = self.vision.tokens_per_image
         if self.neftune_noise_alpha and self.training:
             # noise magnitude alpha / sqrt(L * d) with L the row length (NEFTune, as applied by the HF
             # trainer the reference builds on)

@@ -464,6 +464,9 @@ class AttnMeta:
         cache = self.__dict__.setdefault("_windowed", {})
         if window not in cache:
             cache[window] = AttnMeta(self.cu_seqlens_host, self.device, True, window)
+        groups = getattr(self, "image_groups", None)
+        if groups is not None:         # both directions inside an image hold on windowed layers too
+            cache[window].image_groups, cache[window].image_group_span = groups, self.image_group_span
         return cache[window]
 
     def chunked(self, chunk):
@@ -629,8 +632,9 @@ WIDE_HEADS = ((256, 256), (192, 128))
 _BLOCKED_WARNED = set()
 
 
-def _attn_block(qb, kk, vv, q0, k0, scale, causal, window, softcap):
-    """qb [B, Hk, rep, D] against kk [n, Hk, D] / vv [n, Hk, Dv]; q0 / k0: document positions of the first query / key."""
+def _attn_block(qb, kk, vv, q0, k0, scale, causal, window, softcap, gq=None, gk=None):
+    """qb [B, Hk, rep, D] against kk [n, Hk, D] / vv [n, Hk, Dv]; q0 / k0: document positions of the first query / key.
+    ``gq`` / ``gk``: image group of every query / key (-1 = text); members of one group see each other whatever the order."""
     sc = torch.einsum("bgrd,ngd->grbn", qb, kk).float() * scale
     if softcap:
         sc = torch.tanh(sc / softcap) * softcap
@@ -640,15 +644,17 @@ def _attn_block(qb, kk, vv, q0, k0, scale, causal, window, softcap):
         keep = ki <= qi
         if window:
             keep &= ki > qi - window
+        if gq is not None:
+            keep |= (gq[:, None] == gk[None, :]) & (gq[:, None] >= 0)
         sc = sc.masked_fill(~keep, float("-inf"))
     return torch.einsum("grbn,ngd->bgrd", sc.softmax(-1).to(vv.dtype), vv)
 
 
-def _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap, block=256):
+def _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap, block=256, groups=None, group_span=0):
     """Head widths without a kernel of their own (e.g. 512): blocks of queries against their visible keys through
     library batched GEMMs, each block recomputed in the backward pass, so memory stays O(block x length) per head.
     Correct for every width; far from the tensor-core kernels in speed (said once per width on stderr)."""
-    if (D, Dv) not in _BLOCKED_WARNED:
+    if groups is None and (D, Dv) not in _BLOCKED_WARNED:
         _BLOCKED_WARNED.add((D, Dv))
         import sys
 
@@ -671,6 +677,9 @@ def _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap, block=256):
             k0 = max(s, b0 - window + 1) if (causal and window) else s
             k1 = b1 if causal else e
             args = (q[b0:b1], k[k0:k1], v[k0:k1], b0 - s, k0 - s, scale, causal, window, softcap)
+            if groups is not None:      # an image may begin before the window or end after the block: widen by its length
+                k0, k1 = max(s, k0 - group_span), min(e, k1 + group_span)
+                args = (q[b0:b1], k[k0:k1], v[k0:k1], b0 - s, k0 - s, scale, causal, window, softcap, groups[b0:b1], groups[k0:k1])
             outs.append(checkpoint(_attn_block, *args, use_reentrant=False) if need_grad else _attn_block(*args))
     return torch.cat(outs, 0).reshape(T, Hq * Dv)
 
@@ -687,6 +696,13 @@ def flash_varlen(qkv, meta: AttnMeta, Hq, Hk, D, scale=None, Dv=None, softcap=0.
     """
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     Dv = D if Dv is None else Dv
+    if getattr(meta, "image_groups", None) is not None:
+        # Gemma 3 with images: causal attention plus both directions inside every image. The causal kernels cannot
+        # express that mask; these batches take the blocked path (any device)
+        if getattr(meta, "cp", False) or sinks is not None or getattr(meta, "kv_cache", None) is not None:
+            raise NotImplementedError("bidirectional image attention runs without context parallelism, sinks and KV cache")
+        return _blocked_attention(qkv, meta, Hq, Hk, D, Dv, scale, softcap, groups=meta.image_groups,
+                                  group_span=int(meta.image_group_span))
     if sinks is not None and qkv.is_cuda and ((D, Dv) in WIDE_HEADS or getattr(meta, "cp", False)):
         raise NotImplementedError("attention sinks are available for head widths 64 / 128 without context parallelism")
     if qkv.is_cuda and ((D, Dv) in WIDE_HEADS):

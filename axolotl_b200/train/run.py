@@ -495,7 +495,7 @@ def _train(cfg, dataset_meta: TrainDatasetMeta | None = None):
 
         if getattr(model, "vision", None) is None:
             raise ValueError(f"multimodal training needs a checkpoint with an image front end this package builds (LLaVA: CLIP "
-                             f"tower + projector); '{model.config.model_type}' was loaded as a language model only")
+                             f"tower + projector; Gemma 3: SigLIP tower + pooling projector); '{model.config.model_type}' was loaded as a language model only")
         if cfg.get("sample_packing"):
             raise ValueError("sample_packing is not available for multimodal datasets (batches are already padding-free)")
         processor = mm.load_processor(cfg, tokenizer)

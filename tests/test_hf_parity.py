@@ -1205,3 +1205,54 @@ def test_llava_image_front_end_matches_hf(tmp_path):
     assert all(p.grad is None for p in ours.vision.vision_tower.parameters())
     with pytest.raises(ValueError, match="placeholder"):
         ours(ids[:, :-1 - 20], pixel_values=pixels)
+
+
+def test_gemma3_image_front_end_matches_hf(tmp_path):
+    """Gemma 3 with images: SigLIP tower, pooling projector (average pool, RMS norm, one matrix), soft tokens written over
+    the placeholder tokens, and attention that is causal except inside an image, where it runs both ways (sliding and
+    global layers alike). Logits against HF ``Gemma3ForConditionalGeneration`` given ``token_type_ids``."""
+    vc = dict(model_type="siglip_vision_model", hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              image_size=28, patch_size=7, num_channels=3, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6, vision_use_head=False)
+    tc = dict(model_type="gemma3_text", vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, sliding_window=6, layer_types=["sliding_attention", "sliding_attention", "full_attention"],
+              max_position_embeddings=256, rms_norm_eps=1e-6, query_pre_attn_scalar=16, rope_theta=1000000.0, rope_local_base_freq=10000.0)
+    d = dict(model_type="gemma3", text_config=tc, vision_config=vc, mm_tokens_per_image=4, image_token_index=299,
+             boi_token_index=297, eoi_token_index=298)
+    cfg = ModelConfig.from_hf_dict(d)
+    assert cfg.model_type == "gemma3_text" and cfg.extra["vision_wrapper"]["image_token_id"] == 299
+    ours = CausalLM(cfg, dtype=torch.float32).init_weights(79)
+    _randomize_norms(ours, 0.5, 1.5)
+    with torch.no_grad():
+        for n, p in ours.vision.named_parameters():
+            if n.endswith("bias") or n.endswith("mm_soft_emb_norm.weight"):
+                p.normal_(0.0, 0.1)
+    hf_io.save_pretrained(ours, str(tmp_path / "m"))
+    hf_model = transformers.AutoModelForImageTextToText.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32,
+                                                                        attn_implementation="eager")
+    hf_model.eval()
+    g = torch.Generator().manual_seed(5)
+    pixels = torch.randn(2, 3, 28, 28, generator=g)
+    text = torch.randint(3, 290, (30,), generator=g)
+    img = torch.full((4,), 299)
+    ids = torch.cat([text[:5], torch.tensor([297]), img, torch.tensor([298]), text[5:17], torch.tensor([297]), img, torch.tensor([298]), text[17:]])[None]
+    ours.eval()
+    with torch.no_grad():
+        got = ours(ids, pixel_values=pixels, return_logits=True).logits
+        ref = hf_model(input_ids=ids, pixel_values=pixels, token_type_ids=(ids == 299).long()).logits[0]
+        causal_only = hf_model(input_ids=ids, pixel_values=pixels).logits[0]
+    assert (ref - causal_only).abs().max() > 1e-3          # the image mask matters in this example
+    assert torch.allclose(got.reshape(ref.shape), ref, atol=1e-3, rtol=3e-3), (got.reshape(ref.shape) - ref).abs().max()
+    again = hf_io.load_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    assert again.vision is not None and again.vision.bidirectional_images
+    with torch.no_grad():
+        assert torch.allclose(again(ids, pixel_values=pixels, return_logits=True).logits, got, atol=1e-5)
+    # text-only batches of the same checkpoint keep the causal kernels' path
+    with torch.no_grad():
+        t_got = ours(ids[:, :5], return_logits=True).logits
+        t_ref = hf_model(input_ids=ids[:, :5]).logits[0]
+    assert torch.allclose(t_got.reshape(t_ref.shape), t_ref, atol=1e-3, rtol=3e-3)
+    ours.train()
+    labels = ids.clone()
+    labels[ids == 299] = -100
+    ours(ids, labels=labels, pixel_values=pixels).loss.backward()
+    assert ours.vision.multi_modal_projector.mm_input_projection_weight.grad.abs().sum() > 0

@@ -1415,17 +1415,27 @@ def test_add_layernorm_kernel_matches_fp32_reference(has_res, has_w, has_b, offs
 
 
 @pytest.mark.gpu
-def test_llava_image_front_end_on_the_device_matches_cpu_fp32():
-    """CLIP tower + projector feeding image placeholder tokens of a Llama language model: bf16 on the device (tower
-    through library attention, language model through the tcgen05 / varlen kernels) against fp32 on the CPU."""
+@pytest.mark.parametrize("kind", ["llava", "gemma3"])
+def test_image_front_ends_on_the_device_match_cpu_fp32(kind):
+    """Vision tower + projector feeding image placeholder tokens of the language model: bf16 on the device (tower through
+    library attention, language model through the tcgen05 GEMMs and, for LLaVA, the varlen attention kernels; Gemma 3's
+    image batches take the blocked attention path for the both-ways mask inside an image) against fp32 on the CPU."""
     from axolotl_b200.models.config import ModelConfig
     from axolotl_b200.models.transformer import CausalLM
     torch.manual_seed(91)
-    vc = dict(model_type="clip_vision_model", hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
-              image_size=56, patch_size=14, num_channels=3, hidden_act="quick_gelu", projection_dim=64)
-    tc = dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
-              num_key_value_heads=2, head_dim=64, tie_word_embeddings=False, max_position_embeddings=2048)
-    cfg = ModelConfig.from_hf_dict(dict(model_type="llava", text_config=tc, vision_config=vc, image_token_id=2047))
+    if kind == "llava":
+        vc = dict(model_type="clip_vision_model", hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                  image_size=56, patch_size=14, num_channels=3, hidden_act="quick_gelu", projection_dim=64)
+        tc = dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=64, tie_word_embeddings=False, max_position_embeddings=2048)
+        cfg = ModelConfig.from_hf_dict(dict(model_type="llava", text_config=tc, vision_config=vc, image_token_id=2047))
+    else:
+        vc = dict(model_type="siglip_vision_model", hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                  image_size=56, patch_size=7, num_channels=3, hidden_act="gelu_pytorch_tanh")
+        tc = dict(model_type="gemma3_text", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=256, sliding_window=64, layer_types=["sliding_attention", "full_attention"],
+                  query_pre_attn_scalar=256, max_position_embeddings=2048)
+        cfg = ModelConfig.from_hf_dict(dict(model_type="gemma3", text_config=tc, vision_config=vc, mm_tokens_per_image=16, image_token_index=2047))
     ref = CausalLM(cfg, dtype=torch.float32).init_weights(7)
     with torch.no_grad():
         for p in ref.parameters():
@@ -1447,6 +1457,7 @@ def test_llava_image_front_end_on_the_device_matches_cpu_fp32():
     out_c = ref(ids, pos, labels, pixel_values=pixels)
     out_c.loss.backward()
     assert abs(out_d.loss.item() - out_c.loss.item()) < 3e-2 * abs(out_c.loss.item()), (out_d.loss.item(), out_c.loss.item())
-    gd = dev.vision.multi_modal_projector.linear_2.weight.grad.float().cpu()
-    gc = ref.vision.multi_modal_projector.linear_2.weight.grad
+    proj = (lambda m: m.vision.multi_modal_projector.linear_2.weight) if kind == "llava" else \
+        (lambda m: m.vision.multi_modal_projector.mm_input_projection_weight)
+    gd, gc = proj(dev).grad.float().cpu(), proj(ref).grad
     assert _rel_err(gd, gc) < 0.15, _rel_err(gd, gc)

@@ -14,6 +14,19 @@
 //   so every access is coalesced; fp32 throughout. backward recomputes the probabilities:
 //     d_kv = p * d_out,   d_gate = p * d_out * (kv - out).
 //   Reference: a Triton kernel pair, src/axolotl/integrations/kernels/libs/dsv4/gated_pool.py:27-104.
+//
+// Hyper-connection mixer (DeepSeek-V4: every layer keeps HC = 4 residual streams and mixes them twice). Per token, 24
+// numbers `mixes` (a projection of the normalised streams) become
+//     pre[j]  = sigmoid(mixes[j] s0 + base[j]) + eps                    weights that collapse the streams into the layer input
+//     post[j] = post_mult sigmoid(mixes[4 + j] s1 + base[4 + j])        weights that spread the layer output over the streams
+//     comb    = Sinkhorn(softmax_rows(mixes[8:] s2 + base[8:]) + eps)   a (nearly) doubly stochastic 4 x 4 stream mixer:
+//               column-normalise, then (iters - 1) x [row-normalise, column-normalise], each as x / (sum + eps)
+//   In eager form this is ~40 launches over [tokens, 4, 4]; here one thread holds a token's 16 numbers in registers.
+//   backward: the thread reruns its forward keeping only the 4 sums of every normalisation (the input of a step is its
+//   output times (sum + eps), so the chain is walked back without storing the matrices), applies
+//   dx = (dy - sum(dy y)) / (sum + eps) per step, then the softmax and sigmoid derivatives; the gradients of the 3 scales
+//   and 24 offsets are reduced per warp and added with one atomic per warp and value.
+//   Reference: a Triton kernel pair, src/axolotl/integrations/kernels/libs/dsv4/mhc.py:29-350.
 #include "axb_common.cuh"
 
 namespace {
@@ -131,6 +144,186 @@ __global__ void gated_pool_bwd_kernel(const float* __restrict__ kv, const float*
 }
 
 }  // namespace
+
+namespace {
+
+constexpr int MHC = 4;           // streams
+constexpr int MHC_MAX_ITERS = 32;
+
+AXB_DEVICE float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+AXB_DEVICE float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// one normalisation of c along rows (axis_col = false: every row sums to ~1) or columns; returns the 4 sums
+AXB_DEVICE void mhc_normalise(float (&c)[MHC][MHC], bool cols, float eps, float (&sums)[MHC]) {
+#pragma unroll
+  for (int a = 0; a < MHC; ++a) {
+    float t = 0.f;
+#pragma unroll
+    for (int b = 0; b < MHC; ++b) t += cols ? c[b][a] : c[a][b];
+    sums[a] = t;
+    const float inv = 1.f / (t + eps);
+#pragma unroll
+    for (int b = 0; b < MHC; ++b) {
+      if (cols) c[b][a] *= inv; else c[a][b] *= inv;
+    }
+  }
+}
+
+AXB_DEVICE void mhc_softmax_rows(const float* __restrict__ mix, const float* __restrict__ base, float s2, float eps,
+                                 float (&c)[MHC][MHC]) {
+#pragma unroll
+  for (int i = 0; i < MHC; ++i) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < MHC; ++j) {
+      c[i][j] = mix[2 * MHC + i * MHC + j] * s2 + base[2 * MHC + i * MHC + j];
+      mx = fmaxf(mx, c[i][j]);
+    }
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < MHC; ++j) { c[i][j] = __expf(c[i][j] - mx); t += c[i][j]; }
+#pragma unroll
+    for (int j = 0; j < MHC; ++j) c[i][j] = c[i][j] / t + eps;
+  }
+}
+
+__global__ void mhc_mix_fwd_kernel(const float* __restrict__ mixes, const float* __restrict__ scale,
+                                   const float* __restrict__ base, float* __restrict__ pre, float* __restrict__ post,
+                                   float* __restrict__ comb, long long M, int iters, float eps, float post_mult) {
+  const long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  const float* mix = mixes + m * (MHC * (2 + MHC));
+  const float s0 = scale[0], s1 = scale[1], s2 = scale[2];
+#pragma unroll
+  for (int j = 0; j < MHC; ++j) {
+    pre[m * MHC + j] = sigmoidf_(mix[j] * s0 + base[j]) + eps;
+    post[m * MHC + j] = post_mult * sigmoidf_(mix[MHC + j] * s1 + base[MHC + j]);
+  }
+  float c[MHC][MHC], sums[MHC];
+  mhc_softmax_rows(mix, base, s2, eps, c);
+  mhc_normalise(c, true, eps, sums);
+  for (int it = 1; it < iters; ++it) {
+    mhc_normalise(c, false, eps, sums);
+    mhc_normalise(c, true, eps, sums);
+  }
+#pragma unroll
+  for (int i = 0; i < MHC; ++i)
+#pragma unroll
+    for (int j = 0; j < MHC; ++j) comb[m * MHC * MHC + i * MHC + j] = c[i][j];
+}
+
+// dx = (dy - sum(dy y)) / (sum + eps) along the normalised axis; y becomes the step's input x = y (sum + eps)
+AXB_DEVICE void mhc_normalise_bwd(float (&y)[MHC][MHC], float (&g)[MHC][MHC], bool cols, float eps, const float* sums) {
+#pragma unroll
+  for (int a = 0; a < MHC; ++a) {
+    float dot = 0.f;
+#pragma unroll
+    for (int b = 0; b < MHC; ++b) dot += cols ? g[b][a] * y[b][a] : g[a][b] * y[a][b];
+    const float den = sums[a] + eps, inv = 1.f / den;
+#pragma unroll
+    for (int b = 0; b < MHC; ++b) {
+      if (cols) { g[b][a] = (g[b][a] - dot) * inv; y[b][a] *= den; }
+      else      { g[a][b] = (g[a][b] - dot) * inv; y[a][b] *= den; }
+    }
+  }
+}
+
+__global__ void mhc_mix_bwd_kernel(const float* __restrict__ mixes, const float* __restrict__ scale,
+                                   const float* __restrict__ base, const float* __restrict__ d_pre,
+                                   const float* __restrict__ d_post, const float* __restrict__ d_comb,
+                                   float* __restrict__ d_mixes, float* __restrict__ d_scale, float* __restrict__ d_base,
+                                   long long M, int iters, float eps, float post_mult) {
+  const long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int N = MHC * (2 + MHC);
+  float dm[N];            // d_mixes of this row before the scale factor, i.e. the gradient of (mix s + base) = d_base part
+  float ds[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+  for (int k = 0; k < N; ++k) dm[k] = 0.f;
+  if (m < M) {
+    const float* mix = mixes + m * N;
+    const float s0 = scale[0], s1 = scale[1], s2 = scale[2];
+#pragma unroll
+    for (int j = 0; j < MHC; ++j) {
+      const float a = sigmoidf_(mix[j] * s0 + base[j]);
+      dm[j] = d_pre[m * MHC + j] * a * (1.f - a);
+      const float b = sigmoidf_(mix[MHC + j] * s1 + base[MHC + j]);
+      dm[MHC + j] = d_post[m * MHC + j] * post_mult * b * (1.f - b);
+      ds[0] += dm[j] * mix[j];
+      ds[1] += dm[MHC + j] * mix[MHC + j];
+    }
+    float c[MHC][MHC], g[MHC][MHC];
+    float sums[2 * MHC_MAX_ITERS][MHC];
+    mhc_softmax_rows(mix, base, s2, eps, c);
+    int t = 0;
+    mhc_normalise(c, true, eps, sums[t++]);
+    for (int it = 1; it < iters; ++it) {
+      mhc_normalise(c, false, eps, sums[t++]);
+      mhc_normalise(c, true, eps, sums[t++]);
+    }
+#pragma unroll
+    for (int i = 0; i < MHC; ++i)
+#pragma unroll
+      for (int j = 0; j < MHC; ++j) g[i][j] = d_comb[m * MHC * MHC + i * MHC + j];
+    for (int it = iters - 1; it >= 1; --it) {
+      mhc_normalise_bwd(c, g, true, eps, sums[--t]);
+      mhc_normalise_bwd(c, g, false, eps, sums[--t]);
+    }
+    mhc_normalise_bwd(c, g, true, eps, sums[--t]);
+    // c is now softmax + eps, g its gradient: d_logit = p (g - sum_j g p) per row
+#pragma unroll
+    for (int i = 0; i < MHC; ++i) {
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < MHC; ++j) dot += g[i][j] * (c[i][j] - eps);
+#pragma unroll
+      for (int j = 0; j < MHC; ++j) {
+        const float dl = (c[i][j] - eps) * (g[i][j] - dot);
+        dm[2 * MHC + i * MHC + j] = dl;
+        ds[2] += dl * mix[2 * MHC + i * MHC + j];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k) d_mixes[m * N + k] = dm[k] * (k < MHC ? s0 : (k < 2 * MHC ? s1 : s2));
+  }
+  // parameter gradients: per-warp sums, one atomic per warp and value (rows past M contribute zeros)
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    const float v = warp_sum(dm[k]);
+    if ((threadIdx.x & 31) == 0 && v != 0.f) atomicAdd(d_base + k, v);
+  }
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const float v = warp_sum(ds[k]);
+    if ((threadIdx.x & 31) == 0 && v != 0.f) atomicAdd(d_scale + k, v);
+  }
+}
+
+}  // namespace
+
+extern "C" int axb_mhc_mix_fwd(const float* mixes, const float* scale, const float* base, float* pre, float* post,
+                               float* comb, long long M, int hc, int iters, float eps, float post_mult, void* stream) {
+  if (hc != MHC || iters < 1 || iters > MHC_MAX_ITERS) return -2;
+  if (M <= 0) return 0;
+  mhc_mix_fwd_kernel<<<(unsigned)((M + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      mixes, scale, base, pre, post, comb, M, iters, eps, post_mult);
+  return (int)cudaGetLastError();
+}
+
+// d_scale [3] and d_base [24] must be zeroed by the caller (they are accumulated with atomics).
+extern "C" int axb_mhc_mix_bwd(const float* mixes, const float* scale, const float* base, const float* d_pre,
+                               const float* d_post, const float* d_comb, float* d_mixes, float* d_scale, float* d_base,
+                               long long M, int hc, int iters, float eps, float post_mult, void* stream) {
+  if (hc != MHC || iters < 1 || iters > MHC_MAX_ITERS) return -2;
+  if (M <= 0) return 0;
+  mhc_mix_bwd_kernel<<<(unsigned)((M + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      mixes, scale, base, d_pre, d_post, d_comb, d_mixes, d_scale, d_base, M, iters, eps, post_mult);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int axb_xielu_fwd(const void* x, void* y, long long n, float ap, float an, float beta, float eps,
                              void* stream) {

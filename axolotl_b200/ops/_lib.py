@@ -60,6 +60,8 @@ _CUDA_SIGS = {
     "axb_xielu_bwd": [vp, vp, vp, vp, i64, f32, f32, f32, f32, vp],
     "axb_gated_pool_fwd": [vp, vp, vp, i64, i32, i32, vp],
     "axb_gated_pool_bwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, vp],
+    "axb_mhc_mix_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, f32, f32, vp],
+    "axb_mhc_mix_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, f32, f32, vp],
     "axb_bounds_check_enabled": [],
     "axb_bounds_fetch": [vp],
     "axb_bounds_reset": [],

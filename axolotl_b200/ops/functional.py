@@ -1050,3 +1050,78 @@ def add_layernorm(x, residual, w, b, eps, w_offset=0.0):
     wf = None if w is None else (w.float() + w_offset if w_offset else w.float())
     y = torch.nn.functional.layer_norm(s.float(), (s.shape[-1],), wf, b.float() if b is not None else None, eps).to(s.dtype)
     return y, s
+
+
+# ------------------------------------------------------------------------- hyper-connection mixer (DeepSeek-V4)
+def sinkhorn_mix_ref(mixes, scale, base, hc=4, iters=20, eps=1e-6, post_mult=2.0):
+    """Plain form of the hyper-connection mixer. mixes [M, hc (2 + hc)], scale [3], base [hc (2 + hc)] ->
+    pre [M, hc] = sigmoid(.) + eps, post [M, hc] = post_mult sigmoid(.), comb [M, hc, hc]: row softmax + eps, then
+    Sinkhorn-Knopp: column-normalise, then (iters - 1) x [row-normalise, column-normalise], each x / (sum + eps)."""
+    m = mixes.float()
+    pre = torch.sigmoid(m[:, :hc] * scale[0] + base[:hc]) + eps
+    post = post_mult * torch.sigmoid(m[:, hc:2 * hc] * scale[1] + base[hc:2 * hc])
+    c = torch.softmax((m[:, 2 * hc:] * scale[2] + base[2 * hc:]).view(-1, hc, hc), -1) + eps
+    c = c / (c.sum(1, keepdim=True) + eps)
+    for _ in range(iters - 1):
+        c = c / (c.sum(2, keepdim=True) + eps)
+        c = c / (c.sum(1, keepdim=True) + eps)
+    return pre, post, c
+
+
+class _SinkhornMix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, mixes, scale, base, iters, eps, post_mult):
+        M = mixes.shape[0]
+        pre = torch.empty((M, 4), dtype=torch.float32, device=mixes.device)
+        post = torch.empty_like(pre)
+        comb = torch.empty((M, 4, 4), dtype=torch.float32, device=mixes.device)
+        _lib.check_rc(_lib.cuda_lib().axb_mhc_mix_fwd(mixes.data_ptr(), scale.data_ptr(), base.data_ptr(), pre.data_ptr(),
+                                                      post.data_ptr(), comb.data_ptr(), M, 4, iters, eps, post_mult,
+                                                      _lib.stream_ptr()), "mhc_mix_fwd")
+        ctx.save_for_backward(mixes, scale, base)
+        ctx.args = (iters, eps, post_mult)
+        return pre, post, comb
+
+    @staticmethod
+    def backward(ctx, d_pre, d_post, d_comb):
+        mixes, scale, base = ctx.saved_tensors
+        iters, eps, post_mult = ctx.args
+        M = mixes.shape[0]
+        d_mixes = torch.empty_like(mixes)
+        d_scale = torch.zeros(3, dtype=torch.float32, device=mixes.device)
+        d_base = torch.zeros(24, dtype=torch.float32, device=mixes.device)
+        z = lambda g, shape: (torch.zeros(shape, dtype=torch.float32, device=mixes.device) if g is None else g.contiguous().float())  # noqa: E731
+        d_pre, d_post, d_comb = z(d_pre, (M, 4)), z(d_post, (M, 4)), z(d_comb, (M, 4, 4))
+        _lib.check_rc(_lib.cuda_lib().axb_mhc_mix_bwd(mixes.data_ptr(), scale.data_ptr(), base.data_ptr(), d_pre.data_ptr(),
+                                                      d_post.data_ptr(), d_comb.data_ptr(), d_mixes.data_ptr(),
+                                                      d_scale.data_ptr(), d_base.data_ptr(), M, 4, iters, eps, post_mult,
+                                                      _lib.stream_ptr()), "mhc_mix_bwd")
+        return d_mixes, d_scale, d_base, None, None, None
+
+
+def sinkhorn_mix(mixes, scale, base, hc=4, iters=20, eps=1e-6, post_mult=2.0):
+    """(pre, post, comb) of the hyper-connection mixer; fp32. On a GPU with hc = 4 and iters <= 32 one kernel per
+    direction holds a token's 4 x 4 matrix in registers for the whole Sinkhorn chain (the eager form is ~40 launches);
+    the reference fuses the same chain in Triton (src/axolotl/integrations/kernels/libs/dsv4/mhc.py:260-350)."""
+    if not (mixes.is_cuda and hc == 4 and 1 <= iters <= 32):
+        return sinkhorn_mix_ref(mixes, scale, base, hc, iters, eps, post_mult)
+    lead = mixes.shape[:-1]
+    pre, post, comb = _SinkhornMix.apply(mixes.reshape(-1, 24).contiguous().float(), scale.float().contiguous(),
+                                         base.float().contiguous(), int(iters), float(eps), float(post_mult))
+    return pre.view(*lead, 4), post.view(*lead, 4), comb.view(*lead, 4, 4)
+
+
+def hyperconnection_forward(streams, fn, base, scale, norm_eps=1e-6, hc=4, iters=20, eps=1e-6, post_mult=2.0):
+    """One hyper-connection read: ``streams`` [..., hc, H] (the layer's residual streams) -> (post [..., hc],
+    comb [..., hc, hc], collapsed [..., H]). The streams are RMS-normalised as one hc H-wide vector and projected by
+    ``fn`` [hc (2 + hc), hc H] (the per-row RMS factor is applied after the product: one pass over the streams), mixed by
+    ``sinkhorn_mix``, and collapsed into the layer input as sum_j pre[j] streams[j]. The layer's output y then goes back
+    as streams'[i] = post[i] y + sum_j comb[i, j] streams[j]
+    (src/axolotl/integrations/kernels/libs/dsv4/mhc.py:586-609)."""
+    *lead, n, H = streams.shape
+    flat = streams.reshape(-1, n * H)
+    r = torch.rsqrt(flat.float().pow(2).mean(-1, keepdim=True) + norm_eps)
+    mixes = (flat @ fn.to(flat.dtype).t()).float() * r
+    pre, post, comb = sinkhorn_mix(mixes, scale, base, hc, iters, eps, post_mult)
+    collapsed = torch.einsum("mj,mjh->mh", pre.to(streams.dtype), streams.reshape(-1, n, H))
+    return post.view(*lead, n), comb.view(*lead, n, n), collapsed.view(*lead, H)

@@ -368,6 +368,23 @@ def bench_indexer(rows):
                     f"{L * L * 2 / t_k / 1e6:.0f} GB/s | einsum form {t_e*1e3:.0f} us ({t_e / t:.1f}x)")
 
 
+def bench_hyperconnection(rows):
+    """The DeepSeek-V4 hyper-connection mixer (sigmoid / softmax / 20-step Sinkhorn over one 4 x 4 matrix per token) at
+    8192 and 65536 tokens: the register-resident kernel pair against the eager chain of ~40 small launches."""
+    from axolotl_b200.ops import functional as Fn
+
+    scale = torch.tensor([0.7, 1.3, 0.9], device="cuda")
+    base = torch.randn(24, device="cuda") * 0.3
+    for M in (8192, 65536):
+        mixes = (torch.randn(M, 24, device="cuda") * 2).requires_grad_(True)
+        w = torch.randn(M, 4, 4, device="cuda")
+        for name, fn in (("kernel", Fn.sinkhorn_mix), ("eager", Fn.sinkhorn_mix_ref)):
+            f = lambda: fn(mixes, scale, base, 4, 20, 1e-6, 2.0)
+            t_f = time_cuda(f, iters=20, warmup=5)
+            t_fb = time_cuda(lambda: torch.autograd.grad((f()[2] * w).sum() + f()[0].sum(), mixes), iters=20, warmup=5)
+            rows.append(f"hyper-connection mixer, {M} tokens, 20 Sinkhorn steps, {name}: fwd {t_f * 1e3:.1f} us, fwd+bwd {t_fb * 1e3:.1f} us")
+
+
 def bench_mixers(rows):
     """The recurrent token mixers of the hybrid families at one 8192-token row (four 2048-token documents): the
     Mamba-2 chunked scan and the gated delta rule, both written as dense tensor contractions (library batched GEMMs),
@@ -599,6 +616,8 @@ def main(argv):
         bench_indexer(rows)
     if what in ("mixers",):
         bench_mixers(rows)
+    if what in ("hyperconnection",):
+        bench_hyperconnection(rows)
     if what in ("elementwise", "all"):
         bench_elementwise(rows)
     from axolotl_b200.ops import _lib

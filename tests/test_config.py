@@ -277,3 +277,29 @@ def test_xielu_and_gated_pool_reference_paths():
     assert torch.allclose(y, want)
     kv, gate = torch.randn(2, 5, 4, 7), torch.randn(2, 5, 4, 7)
     assert torch.allclose(Fn.gated_softmax_pool(kv, gate), (kv * gate.softmax(-2)).sum(-2), atol=1e-6)
+
+
+def test_hyperconnection_mixer_reference_properties():
+    """The plain form of the DeepSeek-V4 hyper-connection mixer: pre / post ranges, a (nearly) doubly stochastic stream
+    mixer after the Sinkhorn chain, and the collapse of the streams."""
+    import torch
+
+    from axolotl_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    M, hc, H = 9, 4, 32
+    mixes = torch.randn(M, hc * (2 + hc)) * 2
+    scale, base = torch.tensor([0.7, 1.3, 0.9]), torch.randn(hc * (2 + hc)) * 0.3
+    pre, post, comb = Fn.sinkhorn_mix(mixes, scale, base)
+    assert pre.shape == (M, 4) and post.shape == (M, 4) and comb.shape == (M, 4, 4)
+    assert (pre > 0).all() and (pre < 1.001).all() and (post >= 0).all() and (post <= 2).all()
+    assert torch.allclose(comb.sum(1), torch.ones(M, 4), atol=1e-4) and torch.allclose(comb.sum(2), torch.ones(M, 4), atol=2e-2)
+    streams = torch.randn(2, 5, hc, H)
+    fn = torch.randn(hc * (2 + hc), hc * H) * 0.05
+    post2, comb2, collapsed = Fn.hyperconnection_forward(streams, fn, base, scale)
+    assert post2.shape == (2, 5, 4) and comb2.shape == (2, 5, 4, 4) and collapsed.shape == (2, 5, H)
+    flat = streams.reshape(-1, hc * H)
+    mixes2 = (flat * torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + 1e-6)) @ fn.t()
+    pre3, _, _ = Fn.sinkhorn_mix_ref(mixes2, scale, base)
+    want = (pre3[:, :, None] * streams.reshape(-1, hc, H)).sum(1)
+    assert torch.allclose(collapsed.reshape(-1, H), want, atol=1e-5)

@@ -1461,3 +1461,26 @@ def test_image_front_ends_on_the_device_match_cpu_fp32(kind):
         (lambda m: m.vision.multi_modal_projector.mm_input_projection_weight)
     gd, gc = proj(dev).grad.float().cpu(), proj(ref).grad
     assert _rel_err(gd, gc) < 0.15, _rel_err(gd, gc)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("iters", [1, 20])
+def test_hyperconnection_mixer_kernel_matches_reference(iters):
+    """Sinkhorn mixer kernel pair (a token's 4 x 4 matrix in registers through the whole chain; the backward walks the
+    chain back from the stored sums) against autograd through the plain fp32 form."""
+    from axolotl_b200.ops import functional as Fn
+    torch.manual_seed(92)
+    M = 1000
+    mixes = (torch.randn(M, 24) * 2).to(_dev())
+    scale = torch.tensor([0.7, 1.3, 0.9], device=_dev())
+    base = (torch.randn(24) * 0.3).to(_dev())
+    wp, wq, wc = (torch.randn(M, 4, device=_dev()), torch.randn(M, 4, device=_dev()), torch.randn(M, 4, 4, device=_dev()))
+    outs = []
+    for fn in (Fn.sinkhorn_mix, Fn.sinkhorn_mix_ref):
+        a, s, b = (t.clone().requires_grad_(True) for t in (mixes, scale, base))
+        pre, post, comb = fn(a, s, b, 4, iters, 1e-6, 2.0)
+        ((pre * wp).sum() + (post * wq).sum() + (comb * wc).sum()).backward()
+        outs.append((pre, post, comb, a.grad, s.grad, b.grad))
+    _check_status()
+    for got, want in zip(*outs):
+        assert _rel_err(got.float().cpu(), want.float().cpu()) < 2e-4, _rel_err(got.float().cpu(), want.float().cpu())

@@ -518,6 +518,19 @@ class DecoderLayer(nn.Module):
         return self._mlp_half(self.self_attn(x, positions, inv_freq, attn_scale, meta), residual)
 
 
+class _FixedFeatures(nn.Module):
+    """Stands in for the image front end during generation: the features of the prompt's images, computed once."""
+
+    def __init__(self, front, feats):
+        super().__init__()
+        self.image_token_id, self.bidirectional_images = front.image_token_id, front.bidirectional_images
+        self.tokens_per_image = front.tokens_per_image
+        self.feats = feats
+
+    def forward(self, _):
+        return self.feats
+
+
 class CausalLM(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device=None):
         super().__init__()
@@ -849,10 +862,21 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ generation (greedy / sampling)
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens=32, temperature=0.0, top_p=1.0, eos_token_id=None, use_cache=True):
+    def generate(self, input_ids, max_new_tokens=32, temperature=0.0, top_p=1.0, eos_token_id=None, use_cache=True,
+                 pixel_values=None):
         """Greedy / sampled continuation of one prompt; returns [1, prompt + new]. With ``use_cache``
         (default) every new token is one incremental step over a KV cache; without it the whole
-        sequence is recomputed per token (kept as the oracle of the cached path)."""
+        sequence is recomputed per token (kept as the oracle of the cached path). A prompt with images
+        (``pixel_values``) takes the recomputing path: the image features enter through the embeddings of the prompt."""
+        if pixel_values is not None:
+            use_cache = False
+            with torch.no_grad():        # the tower runs once; its features are merged on every pass
+                feats = self.vision(pixel_values)
+            vision, self.vision = self.vision, _FixedFeatures(self.vision, feats)
+            try:
+                return self.generate(input_ids, max_new_tokens, temperature, top_p, eos_token_id, False, None)
+            finally:
+                self.vision = vision
         from .registry import KV_CACHE, Unsupported, get_model_support
 
         sup = get_model_support(self.config.model_type)
@@ -868,7 +892,7 @@ class CausalLM(nn.Module):
         self.eval()
         ids = input_ids.reshape(1, -1).clone()
         for _ in range(max_new_tokens):
-            out = self.forward(ids, return_logits=True)
+            out = self.forward(ids, return_logits=True, pixel_values=True if isinstance(self.vision, _FixedFeatures) else None)
             logits = out.logits[0, -1].float()
             if temperature and temperature > 0:
                 probs = torch.softmax(logits / temperature, -1)

@@ -184,3 +184,19 @@ def test_llava_adapter_keys_and_sharded_merge(tmp_path):
     with torch.no_grad():
         got = merged(ids, pixel_values=pixels, return_logits=True).logits
     assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+
+
+def test_generate_with_images_matches_stepwise_greedy(tmp_path):
+    """``generate(pixel_values=...)``: the tower runs once, every pass merges its features into the prompt's embeddings."""
+    model = _checkpoint(str(tmp_path / "b"))
+    ids = torch.tensor([[3, 4, IMG, IMG, IMG, IMG, 5, 6]])
+    pixels = torch.randn(1, 3, 28, 28)
+    out = model.generate(ids, max_new_tokens=4, pixel_values=pixels)
+    assert type(model.vision).__name__ == "VisionFrontEnd"        # the stand-in used while generating is gone again
+    model.eval()
+    cur = ids.clone()
+    with torch.no_grad():
+        for _ in range(4):
+            nxt = model(cur, pixel_values=pixels, return_logits=True).logits[0, -1].argmax()
+            cur = torch.cat([cur, nxt.reshape(1, 1)], 1)
+    assert torch.equal(cur, out)

@@ -538,6 +538,17 @@ def profile_case(what):
         for _ in range(3):
             gemm(x, Wgu, out=gu, glu=("fwd", 0, 0.0, h))
             gemm(dy, Wd, trans_b=True, out=dgu, glu=("bwd", 0, 0.0, gu))
+    elif what == "one_hyperconnection":
+        # the hyper-connection mixer kernel pair at 1 M tokens (24 + 24 fp32 numbers per token and direction)
+        from axolotl_b200.ops import functional as Fn
+
+        M = 1 << 20
+        mixes = (torch.randn(M, 24, device="cuda") * 2).requires_grad_(True)
+        scale = torch.tensor([0.7, 1.3, 0.9], device="cuda")
+        base = torch.randn(24, device="cuda") * 0.3
+        for _ in range(3):
+            pre, post, comb = Fn.sinkhorn_mix(mixes, scale, base, 4, 20, 1e-6, 2.0)
+            torch.autograd.grad([pre, post, comb], mixes, [torch.ones_like(pre), torch.ones_like(post), torch.ones_like(comb)])
     elif what == "one_w4a16":
         # NVFP4 expert projection with the decode inside the grouped GEMM: 32 experts of Qwen3-MoE-30B-A3B's
         # gate|up shape, 512 rows each (forward and input gradient)
@@ -593,7 +604,7 @@ def profile_case(what):
 
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
-    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp", "one_w4a16", "one_indexer"):
+    if what in ("one_gemm", "one_attn", "one_grouped", "one_mlp", "one_w4a16", "one_indexer", "one_hyperconnection"):
         return profile_case(what)
     rows = []
     if what in ("gemm", "all"):

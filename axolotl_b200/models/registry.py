@@ -182,9 +182,7 @@ _register("Qwen3Next", ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"),
           head_dims=None)
 
 # architectures the reference lists that have no model graph here (named so that the error can say so)
-KNOWN_UNSUPPORTED = ("gemma3", "gemma4", "deepseek_v4", "gpt_neox", "mamba", "jamba", "llama4", "mllama",
-                     "qwen2_vl", "qwen3_vl", "qwen3_5", "qwen3_5_moe", "kimi_linear", "cohere", "cohere2", "starcoder2",
-                     "lfm2", "lfm2_moe", "minimax_m2", "afmoe", "gemmoe", "mistral4")
+KNOWN_UNSUPPORTED = ("deepseek_v4", "gpt_neox", "mamba", "jamba", "mllama", "qwen2_vl", "qwen3_vl", "kimi_linear", "gemmoe")
 
 
 def support_for(model_type: str) -> ModelSupport:

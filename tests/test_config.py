@@ -150,7 +150,7 @@ def test_architecture_registry_checks():
         assert R.get_model_support(mt) is not None, mt
     assert isinstance(R.support_for("llama").capabilities[R.EP], R.Unsupported)
     with pytest.raises(ValueError, match="no model graph"):
-        R.support_for("gemma4")
+        R.support_for("mllama")
     with pytest.raises(ValueError, match="expert parallelism needs"):
         R.validate_cfg({"expert_parallel_size": 2}, preset("tiny-llama"))
     with pytest.raises(ValueError, match="cannot be split"):

@@ -129,6 +129,11 @@ class ModelConfig:
             d["hidden_act"] = d.get("hidden_activation") or "gelu_pytorch_tanh"   # HF forces the tanh form
             d.setdefault("rms_norm_eps", 1e-6)
             if mt == "gemma3_text":
+                # checkpoints write only what differs from the architecture's defaults (the 4B config gives four keys)
+                for key, val in (("vocab_size", 262208), ("hidden_size", 2304), ("intermediate_size", 9216), ("num_hidden_layers", 26),
+                                 ("num_attention_heads", 8), ("num_key_value_heads", 4), ("max_position_embeddings", 131072),
+                                 ("rope_theta", 1000000.0), ("rope_local_base_freq", 10000.0)):
+                    d.setdefault(key, val)
                 d.setdefault("head_dim", 256)
                 d.setdefault("query_pre_attn_scalar", 256)
                 d.setdefault("sliding_window", 4096)
